@@ -1,0 +1,407 @@
+"""Checkpoint / resume: adapters, optimizer moments, sampler state, manifest.
+
+On-disk layout (reference ``crates/ferrl/src/checkpoint.rs:192-196``)::
+
+    <run>/checkpoints/step-N/adapter.safetensors     keys lora.00000 ...
+                             optimizer.safetensors   keys m.00000 / v.00000 ...
+                             manifest.json           written last
+
+Format version 4 (``:208``). The manifest (``:370-412``) records step, var
+count, optimizer step counter, sampler state bytes, LoRA recipe and an
+``ordinary_checkpoint`` identity: payload SHA-256s, tensor-schema digest and
+the binding digests (frozen policy, trainer config).  Digests are
+length-prefixed and domain-separated (``:447-456``).  Publication is staged:
+payloads are written and fsynced into a temp directory, ``manifest.json`` goes
+last, the directory is renamed into place atomically under an advisory writer
+lock (``:649-1275``); an existing ``step-N`` is never replaced.  Loading
+verifies every digest and the binding *before* mutating any live state
+(``:2236-2348``).  ``latest_checkpoint`` picks the highest complete step and
+treats a newer malformed one as an error rather than silently falling back
+(``:2436``).
+"""
+from __future__ import annotations
+
+import fcntl
+import hashlib
+import json
+import os
+import re
+import shutil
+import struct
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+
+from .optim import OptimizerState
+
+ADAPTER_FILE = "adapter.safetensors"
+OPTIMIZER_FILE = "optimizer.safetensors"
+MANIFEST_FILE = "manifest.json"
+LOCK_SUFFIX = ".lock"
+FORMAT_VERSION = 4
+MIN_READ_VERSION = 4
+_STEP_RE = re.compile(r"^step-(\d+)$")
+
+
+class CheckpointError(RuntimeError):
+    pass
+
+
+class CheckpointMismatch(CheckpointError):
+    pass
+
+
+def domain_sha256(domain: str, fields: Sequence[bytes]) -> str:
+    h = hashlib.sha256()
+    h.update(struct.pack("<Q", len(domain)))
+    h.update(domain.encode())
+    for f in fields:
+        h.update(struct.pack("<Q", len(f)))
+        h.update(f)
+    return h.hexdigest()
+
+
+def _validate_sha(label: str, s: str) -> None:
+    if not (isinstance(s, str) and len(s) == 64 and all(c in "0123456789abcdef" for c in s)):
+        raise CheckpointMismatch(f"{label} must be 64 lowercase hexadecimal characters")
+
+
+@dataclass(frozen=True)
+class CheckpointBinding:
+    frozen_policy_sha256: str
+    trainer_config_sha256: str
+    lora_recipe: Optional[str] = None
+
+    def __post_init__(self):
+        _validate_sha("frozen_policy_sha256", self.frozen_policy_sha256)
+        _validate_sha("trainer_config_sha256", self.trainer_config_sha256)
+
+
+def var_key(i: int) -> str:
+    return f"lora.{i:05d}"
+
+
+def moment_key(kind: str, i: int) -> str:
+    return f"{kind}.{i:05d}"
+
+
+def tensor_schema_sha256(tensors: Sequence[torch.Tensor], lora_recipe: Optional[str]) -> str:
+    fields = [(lora_recipe or "").encode()]
+    for t in tensors:
+        fields.append(json.dumps([list(t.shape), str(t.dtype)]).encode())
+    return domain_sha256("ferrl.checkpoint.tensor-schema.v1", fields)
+
+
+def _file_sha256(path: str) -> str:
+    h = hashlib.sha256()
+    with open(path, "rb") as f:
+        while True:
+            b = f.read(1 << 20)
+            if not b:
+                break
+            h.update(b)
+    return h.hexdigest()
+
+
+def _fsync_file(path: str) -> None:
+    fd = os.open(path, os.O_RDONLY)
+    try:
+        os.fsync(fd)
+    finally:
+        os.close(fd)
+
+
+def _fsync_dir(path: str) -> None:
+    fd = os.open(path, os.O_RDONLY | os.O_DIRECTORY)
+    try:
+        os.fsync(fd)
+    finally:
+        os.close(fd)
+
+
+def _save_tensors(path: str, named: dict) -> None:
+    from safetensors.torch import save_file
+    save_file({k: v.detach().to("cpu").contiguous() for k, v in named.items()}, path)
+    _fsync_file(path)
+
+
+def _load_tensors(path: str) -> dict:
+    from safetensors.torch import load_file
+    try:
+        return load_file(path)
+    except Exception as e:  # noqa: BLE001 - any parse failure is a corrupt payload
+        raise CheckpointMismatch(f"cannot parse {path}: {e}") from e
+
+
+@dataclass
+class CheckpointManifest:
+    format_version: int
+    step: int
+    num_vars: int
+    optimizer_step_t: Optional[int] = None
+    optimizer_num_vars: Optional[int] = None
+    sampler_state: Optional[list] = None      # bytes as a list of ints (JSON friendly)
+    lora_recipe: Optional[str] = None
+    world_size: int = 1
+    topology: str = "dp"
+    ordinary_checkpoint: Optional[dict] = None
+    rollout_ledger_continuation: Optional[dict] = None
+
+    FIELDS = ("format_version", "step", "num_vars", "optimizer_step_t", "optimizer_num_vars", "sampler_state",
+              "lora_recipe", "world_size", "topology", "ordinary_checkpoint", "rollout_ledger_continuation")
+
+    def to_json(self) -> dict:
+        return {k: getattr(self, k) for k in self.FIELDS}
+
+    @staticmethod
+    def from_json(d: dict) -> "CheckpointManifest":
+        if not isinstance(d, dict):
+            raise CheckpointMismatch("manifest is not a JSON object")
+        unknown = set(d) - set(CheckpointManifest.FIELDS)
+        if unknown:
+            raise CheckpointMismatch(f"manifest has unknown fields {sorted(unknown)}")
+        for req in ("format_version", "step", "num_vars"):
+            if req not in d:
+                raise CheckpointMismatch(f"manifest is missing {req}")
+        return CheckpointManifest(**d)
+
+    def sampler_bytes(self) -> Optional[bytes]:
+        return None if self.sampler_state is None else bytes(self.sampler_state)
+
+
+@dataclass
+class LoadedCheckpoint:
+    manifest: CheckpointManifest
+    adapters: list
+    optimizer: Optional[OptimizerState]
+    path: str
+
+
+def step_dir(checkpoints_dir: str, step: int) -> str:
+    return os.path.join(checkpoints_dir, f"step-{step}")
+
+
+class _WriterLock:
+    def __init__(self, path: str):
+        self.path = path
+        self.fd = None
+
+    def __enter__(self):
+        self.fd = os.open(self.path, os.O_WRONLY | os.O_CREAT, 0o644)
+        try:
+            fcntl.flock(self.fd, fcntl.LOCK_EX | fcntl.LOCK_NB)
+        except OSError as e:
+            os.close(self.fd)
+            raise CheckpointError(f"another writer holds {self.path}") from e
+        return self
+
+    def __exit__(self, *exc):
+        fcntl.flock(self.fd, fcntl.LOCK_UN)
+        os.close(self.fd)
+        return False
+
+
+def save_checkpoint(checkpoints_dir: str, step: int, adapters: Sequence[torch.Tensor],
+                    optimizer: Optional[OptimizerState], sampler_state: Optional[bytes],
+                    binding: CheckpointBinding, *, world_size: int = 1, topology: str = "dp",
+                    fault_hook=None) -> str:
+    """Stage, fsync, publish atomically.  ``fault_hook(stage_name)`` lets tests
+    inject host-side failures between stages."""
+    os.makedirs(checkpoints_dir, exist_ok=True)
+    final = step_dir(checkpoints_dir, step)
+    if os.path.exists(final):
+        raise CheckpointError(f"{final} already exists; a published checkpoint is never replaced")
+    with _WriterLock(final + LOCK_SUFFIX):
+        stage = final + f".staging-{os.getpid()}"
+        if os.path.exists(stage):
+            shutil.rmtree(stage)
+        os.makedirs(stage)
+        try:
+            ap = os.path.join(stage, ADAPTER_FILE)
+            _save_tensors(ap, {var_key(i): t for i, t in enumerate(adapters)})
+            if fault_hook:
+                fault_hook("adapter_written")
+            op = os.path.join(stage, OPTIMIZER_FILE)
+            named = {}
+            if optimizer is not None:
+                for i, (m, v) in enumerate(zip(optimizer.m, optimizer.v)):
+                    named[moment_key("m", i)] = m
+                    named[moment_key("v", i)] = v
+            _save_tensors(op, named)
+            if fault_hook:
+                fault_hook("optimizer_written")
+            sampler = sampler_state or b""
+            ident = {
+                "kind": "ordinary",
+                "frozen_policy_sha256": binding.frozen_policy_sha256,
+                "trainer_config_sha256": binding.trainer_config_sha256,
+                "tensor_schema_sha256": tensor_schema_sha256(adapters, binding.lora_recipe),
+                "adapter_sha256": _file_sha256(ap),
+                "optimizer_sha256": _file_sha256(op),
+                "sampler_sha256": domain_sha256("ferrl.checkpoint.sampler.v1", [sampler]),
+            }
+            ident["state_envelope_sha256"] = domain_sha256(
+                "ferrl.checkpoint.state-envelope.v1",
+                [str(step).encode(), str(optimizer.step if optimizer else 0).encode(),
+                 ident["adapter_sha256"].encode(), ident["optimizer_sha256"].encode(),
+                 ident["sampler_sha256"].encode(), str(world_size).encode(), topology.encode()])
+            man = CheckpointManifest(FORMAT_VERSION, step, len(adapters),
+                                     optimizer.step if optimizer else None,
+                                     len(optimizer.m) if optimizer else None,
+                                     list(sampler) if sampler_state is not None else None,
+                                     binding.lora_recipe, world_size, topology, ident)
+            mp = os.path.join(stage, MANIFEST_FILE)
+            with open(mp, "w", encoding="utf-8") as f:
+                json.dump(man.to_json(), f, sort_keys=True)
+                f.flush()
+                os.fsync(f.fileno())
+            if fault_hook:
+                fault_hook("manifest_written")
+            _fsync_dir(stage)
+            os.rename(stage, final)
+            _fsync_dir(checkpoints_dir)
+        except BaseException:
+            shutil.rmtree(stage, ignore_errors=True)
+            raise
+    try:
+        os.unlink(final + LOCK_SUFFIX)
+    except OSError:
+        pass
+    return final
+
+
+def read_manifest(path: str) -> CheckpointManifest:
+    mp = os.path.join(path, MANIFEST_FILE)
+    try:
+        with open(mp, encoding="utf-8") as f:
+            return CheckpointManifest.from_json(json.load(f))
+    except FileNotFoundError:
+        raise CheckpointMismatch(f"{path} has no manifest (incomplete checkpoint)") from None
+    except json.JSONDecodeError as e:
+        raise CheckpointMismatch(f"{mp} is not valid JSON: {e}") from e
+    except TypeError as e:
+        raise CheckpointMismatch(f"{mp} is malformed: {e}") from e
+
+
+def prepare_checkpoint(path: str, binding: Optional[CheckpointBinding], expected_shapes: Optional[Sequence] = None,
+                       *, world_size: Optional[int] = None, topology: Optional[str] = None) -> LoadedCheckpoint:
+    """Read and verify everything; touches no live state."""
+    man = read_manifest(path)
+    if not (MIN_READ_VERSION <= man.format_version <= FORMAT_VERSION):
+        raise CheckpointMismatch(f"unsupported checkpoint format {man.format_version}")
+    ident = man.ordinary_checkpoint
+    if ident is None:
+        raise CheckpointMismatch("manifest carries no checkpoint identity")
+    ap, op = os.path.join(path, ADAPTER_FILE), os.path.join(path, OPTIMIZER_FILE)
+    for p, key in ((ap, "adapter_sha256"), (op, "optimizer_sha256")):
+        if not os.path.exists(p):
+            raise CheckpointMismatch(f"missing payload {p}")
+        if _file_sha256(p) != ident.get(key):
+            raise CheckpointMismatch(f"{os.path.basename(p)} does not match its recorded SHA-256")
+    sampler = man.sampler_bytes() or b""
+    if domain_sha256("ferrl.checkpoint.sampler.v1", [sampler]) != ident.get("sampler_sha256"):
+        raise CheckpointMismatch("sampler state does not match its recorded digest")
+    if binding is not None:
+        if ident.get("frozen_policy_sha256") != binding.frozen_policy_sha256:
+            raise CheckpointMismatch("checkpoint was written for a different frozen policy")
+        if ident.get("trainer_config_sha256") != binding.trainer_config_sha256:
+            raise CheckpointMismatch("checkpoint was written under a different trainer config")
+        if man.lora_recipe != binding.lora_recipe:
+            raise CheckpointMismatch(f"checkpoint LoRA recipe {man.lora_recipe!r} differs from "
+                                     f"the live recipe {binding.lora_recipe!r}")
+    if world_size is not None and man.world_size != world_size:
+        raise CheckpointMismatch(f"checkpoint world size {man.world_size} differs from the live world {world_size}")
+    if topology is not None and man.topology != topology:
+        raise CheckpointMismatch(f"checkpoint topology {man.topology!r} differs from {topology!r}")
+    at = _load_tensors(ap)
+    adapters = []
+    for i in range(man.num_vars):
+        k = var_key(i)
+        if k not in at:
+            raise CheckpointMismatch(f"adapter payload is missing {k}")
+        adapters.append(at[k])
+    if len(at) != man.num_vars:
+        raise CheckpointMismatch("adapter payload has unexpected extra tensors")
+    if tensor_schema_sha256(adapters, man.lora_recipe) != ident.get("tensor_schema_sha256"):
+        raise CheckpointMismatch("tensor schema digest mismatch")
+    if expected_shapes is not None:
+        if len(expected_shapes) != len(adapters):
+            raise CheckpointMismatch(f"checkpoint has {len(adapters)} tensors, live model has {len(expected_shapes)}")
+        for i, (t, s) in enumerate(zip(adapters, expected_shapes)):
+            if tuple(t.shape) != tuple(s):
+                raise CheckpointMismatch(f"tensor {i} shape {tuple(t.shape)} differs from live {tuple(s)}")
+    opt = None
+    if man.optimizer_num_vars is not None:
+        ot = _load_tensors(op)
+        m, v = [], []
+        for i in range(man.optimizer_num_vars):
+            for kind, dst in (("m", m), ("v", v)):
+                k = moment_key(kind, i)
+                if k not in ot:
+                    raise CheckpointMismatch(f"optimizer payload is missing {k}")
+                dst.append(ot[k])
+        opt = OptimizerState(int(man.optimizer_step_t or 0), m, v)
+    return LoadedCheckpoint(man, adapters, opt, path)
+
+
+def load_checkpoint(path: str, binding: Optional[CheckpointBinding], params: Sequence[torch.nn.Parameter],
+                    **kw) -> LoadedCheckpoint:
+    """Verify, then copy adapter values into ``params`` (all-or-nothing)."""
+    lc = prepare_checkpoint(path, binding, [tuple(p.shape) for p in params], **kw)
+    with torch.no_grad():
+        for p, t in zip(params, lc.adapters):
+            p.copy_(t.to(p.dtype))
+    return lc
+
+
+def latest_checkpoint(checkpoints_dir: str) -> Optional[tuple[int, str]]:
+    """Highest complete ``step-N``; a newer malformed final directory is an error."""
+    if not os.path.isdir(checkpoints_dir):
+        return None
+    steps = []
+    for name in os.listdir(checkpoints_dir):
+        m = _STEP_RE.match(name)
+        if m and os.path.isdir(os.path.join(checkpoints_dir, name)):
+            steps.append(int(m.group(1)))
+    if not steps:
+        return None
+    best = max(steps)
+    path = step_dir(checkpoints_dir, best)
+    man = read_manifest(path)  # raises CheckpointMismatch if the newest is malformed
+    if man.step != best:
+        raise CheckpointMismatch(f"{path} manifest records step {man.step}")
+    return best, path
+
+
+def save_adapter(path: str, adapters: Sequence[torch.Tensor], lora_recipe: Optional[str] = None) -> None:
+    """Bare adapter file for evaluation (no optimizer, no manifest)."""
+    from safetensors.torch import save_file
+    tmp = path + ".tmp"
+    save_file({var_key(i): t.detach().cpu().contiguous() for i, t in enumerate(adapters)}, tmp,
+              metadata={"lora_recipe": lora_recipe or "", "format": "ferrl-b200-adapter-v1"})
+    _fsync_file(tmp)
+    os.rename(tmp, path)
+
+
+def load_adapter(path: str, params: Sequence[torch.nn.Parameter], lora_recipe: Optional[str] = None) -> None:
+    from safetensors import safe_open
+    try:
+        with safe_open(path, framework="pt") as f:
+            meta = f.metadata() or {}
+            tensors = {k: f.get_tensor(k) for k in f.keys()}
+    except Exception as e:  # noqa: BLE001
+        raise CheckpointMismatch(f"cannot read adapter {path}: {e}") from e
+    if lora_recipe is not None and meta.get("lora_recipe", "") not in ("", lora_recipe):
+        raise CheckpointMismatch(f"adapter recipe {meta.get('lora_recipe')!r} differs from live {lora_recipe!r}")
+    if len(tensors) != len(params):
+        raise CheckpointMismatch(f"adapter has {len(tensors)} tensors, live model has {len(params)}")
+    vals = []
+    for i, p in enumerate(params):
+        t = tensors.get(var_key(i))
+        if t is None or tuple(t.shape) != tuple(p.shape):
+            raise CheckpointMismatch(f"adapter tensor {i} is missing or has the wrong shape")
+        vals.append(t)
+    with torch.no_grad():
+        for p, t in zip(params, vals):
+            p.copy_(t.to(p.dtype))

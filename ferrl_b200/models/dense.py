@@ -1,0 +1,384 @@
+"""Shared dense decoder backbone (Qwen3 and Llama-3.x) with LoRA, activation
+rematerialisation, tensor parallelism and a KV-cached rollout twin.
+
+What the reference does (``crates/ferrl/src/dense.rs``): pre-norm RMSNorm +
+GQA attention + SwiGLU residual stack (``:276-566``); the variation between
+the two families is data on the spec (per-head QK-norm, fp32 softmax, head_dim
+rule, RoPE frequencies; knob table ``:9-17``); an uncached grad-bearing forward
+whose hidden state is narrowed to the completion window *before* the final
+norm and LM head (``:802-815``, ``:929-935``); a remat forward (``:941-955``);
+and a grad-free cached decoder over merged weights (``:1635-1828``).
+
+How it is laid out here for B200:
+
+* q|k|v and gate|up are single fused projections (one GEMM each, LoRA deltas
+  as extra k-tiles, see ``models.lora``); a transposed copy of every frozen
+  weight stays resident so backward GEMMs also stream K-major tiles.
+* attention goes through ``ops.attention`` (flash kernel, GQA native, causal
+  mask in-kernel) and ``ops.decode_attention`` (KV-cached, GQA groups share the
+  K/V loads) - no ``repeat_kv`` copies, no mask tensors, no cache ``cat``.
+* rollout keeps its KV cache preallocated ``[B, Smax, Hkv, D]`` per layer and
+  all per-row state (lengths, finished flags) on the device, so a decode step
+  has fixed shapes and can be replayed as a CUDA graph.
+* the group's shared prompt is prefilled once and its KV rows are broadcast to
+  the G completions instead of prefilling G identical copies.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from ..comm import Comm, SoloComm
+from ..parallel.tp import TensorParallelPlan, copy_to_tp, reduce_from_tp
+from ..remat import remat_segment
+from .lora import BaseQuantization, DenseLoraTargets, FusedLoraLinear, LoraSpec, Shard
+
+
+@dataclass
+class DenseSpec:
+    vocab_size: int
+    hidden_size: int
+    num_hidden_layers: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    head_dim: int
+    intermediate_size: int
+    rms_norm_eps: float = 1e-6
+    tie_word_embeddings: bool = False
+    qk_norm: bool = True
+    sdpa_f32: bool = False
+    activation: str = "silu"
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 4096
+    inv_freq: Optional[torch.Tensor] = None  # overrides rope_theta (llama3 smoothing)
+    family: str = "qwen3"
+
+    def validate(self) -> None:
+        if self.num_attention_heads % self.num_key_value_heads:
+            raise ValueError("query heads must be a multiple of kv heads")
+        if self.head_dim % 2:
+            raise ValueError("head_dim must be even for RoPE")
+        for n in ("vocab_size", "hidden_size", "num_hidden_layers", "intermediate_size"):
+            if getattr(self, n) <= 0:
+                raise ValueError(f"{n} must be > 0")
+
+    def rope_inv_freq(self) -> torch.Tensor:
+        return self.inv_freq if self.inv_freq is not None else ops.default_inv_freq(self.head_dim, self.rope_theta)
+
+
+class DenseLayer(nn.Module):
+    def __init__(self, spec: DenseSpec, lora: Optional[LoraSpec], dtype, device,
+                 tp: Optional[TensorParallelPlan], keep_transpose: bool, quant: BaseQuantization,
+                 trainable_base: bool = False):
+        super().__init__()
+        H, D = spec.hidden_size, spec.head_dim
+        hq, hkv, F = spec.num_attention_heads, spec.num_key_value_heads, spec.intermediate_size
+        w = tp.world if tp else 1
+        r = tp.rank if tp else 0
+        t = lora.targets if lora else DenseLoraTargets(*(False,) * 7)
+        col = Shard("column", r, w) if tp and w > 1 else None
+        row = Shard("row", r, w) if tp and w > 1 else None
+        kw = dict(dtype=dtype, device=device, keep_transpose=keep_transpose, quant=quant,
+                  trainable_base=trainable_base)
+        self.hq, self.hkv, self.D = hq // w, hkv // w, D
+        self.qkv = FusedLoraLinear(H, [hq * D // w, hkv * D // w, hkv * D // w], ("q", "k", "v"),
+                                   (t.attn_q, t.attn_k, t.attn_v), lora, shard=col,
+                                   full_out_sizes=[hq * D, hkv * D, hkv * D], **kw)
+        self.o = FusedLoraLinear(hq * D // w, [H], ("o",), (t.attn_o,), lora, shard=row,
+                                 full_in=hq * D, **kw)
+        self.gate_up = FusedLoraLinear(H, [F // w, F // w], ("gate", "up"), (t.mlp_gate, t.mlp_up), lora,
+                                       shard=col, full_out_sizes=[F, F], **kw)
+        self.down = FusedLoraLinear(F // w, [H], ("down",), (t.mlp_down,), lora, shard=row, full_in=F, **kw)
+        mk = (lambda n: nn.Parameter(torch.ones(n, dtype=dtype, device=device))) if trainable_base else None
+        for name, n in (("input_norm", H), ("post_norm", H)) + ((("q_norm", D), ("k_norm", D)) if spec.qk_norm else ()):
+            if trainable_base:
+                setattr(self, name, mk(n))
+            else:
+                self.register_buffer(name, torch.ones(n, dtype=dtype, device=device), persistent=False)
+        if not spec.qk_norm:
+            self.q_norm = None
+            self.k_norm = None
+        self.eps = spec.rms_norm_eps
+        self.scale = 1.0 / math.sqrt(D)
+        self.act = spec.activation
+        self.sdpa_f32 = spec.sdpa_f32
+
+    def projections(self):
+        return (self.qkv, self.o, self.gate_up, self.down)
+
+    def adapter_params(self):
+        out = []
+        for p in self.projections():
+            out += p.adapter_params()
+        return out
+
+    # full-sequence forward (training / scoring / prefill)
+    def forward(self, h, positions, cos, sin, comm: Comm, merged: bool = False, kv_out=None):
+        B, S, _ = h.shape
+        lin = (lambda m, x: m.forward_merged(x)) if merged else (lambda m, x: m(x))
+        x = ops.rmsnorm(h, self.input_norm, self.eps)
+        x = copy_to_tp(x, comm)
+        qkv = lin(self.qkv, x)
+        q, k, v = qkv.split([self.hq * self.D, self.hkv * self.D, self.hkv * self.D], dim=-1)
+        q = q.reshape(B, S, self.hq, self.D)
+        k = k.reshape(B, S, self.hkv, self.D)
+        v = v.reshape(B, S, self.hkv, self.D)
+        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin, positions)
+        if kv_out is not None:
+            kv_out[0][:, :S].copy_(k)
+            kv_out[1][:, :S].copy_(v)
+        a = ops.attention(q, k, v, scale=self.scale, causal=True, softmax_fp32=True)
+        o = lin(self.o, a.reshape(B, S, self.hq * self.D))
+        o = reduce_from_tp(o, comm)
+        x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
+        x = copy_to_tp(x, comm)
+        d = lin(self.down, ops.swiglu(lin(self.gate_up, x), self.act))
+        d = reduce_from_tp(d, comm)
+        return h + d
+
+    # one-token forward against the cache (rollout; merged weights)
+    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm):
+        B = h.shape[0]
+        x = ops.rmsnorm(h, self.input_norm, self.eps)
+        qkv = self.qkv.forward_merged(x)
+        q, k, v = qkv.split([self.hq * self.D, self.hkv * self.D, self.hkv * self.D], dim=-1)
+        q = q.reshape(B, 1, self.hq, self.D)
+        k = k.reshape(B, 1, self.hkv, self.D)
+        v = v.reshape(B, 1, self.hkv, self.D)
+        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin, kv_len[:, None].long())
+        ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
+        a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_len + 1, scale=self.scale)
+        o = self.o.forward_merged(a.reshape(B, self.hq * self.D))
+        o = reduce_from_tp(o, comm)
+        x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
+        d = self.down.forward_merged(ops.swiglu(self.gate_up.forward_merged(x), self.act))
+        d = reduce_from_tp(d, comm)
+        return h + d
+
+
+def ops_cache_write(k_cache, v_cache, k, v, kv_len):
+    """Write one token's K/V per row at that row's current length."""
+    idx = kv_len.long()
+    rows = torch.arange(k.shape[0], device=k.device)
+    k_cache[rows, idx] = k
+    v_cache[rows, idx] = v
+
+
+class DenseGradModel(nn.Module):
+    """Policy network: grad-bearing scoring forward plus the cached decoder."""
+
+    def __init__(self, spec: DenseSpec, lora: Optional[LoraSpec] = None, *, dtype=torch.float32,
+                 device=None, tp: Optional[TensorParallelPlan] = None, keep_transpose: Optional[bool] = None,
+                 quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False,
+                 full_ft: bool = False):
+        super().__init__()
+        spec.validate()
+        if tp is not None and (tp.num_heads != spec.num_attention_heads or tp.num_kv_heads != spec.num_key_value_heads):
+            raise ValueError("tensor-parallel plan does not match the model's head counts")
+        self.spec = spec
+        self.lora = lora
+        self.tp = tp
+        self.remat = remat
+        self.full_ft = full_ft
+        dev = torch.device(device) if device is not None else torch.device("cpu")
+        if keep_transpose is None:
+            keep_transpose = dev.type == "cuda" and not full_ft
+        self.dtype = dtype
+        emb = torch.zeros(spec.vocab_size, spec.hidden_size, dtype=dtype, device=dev)
+        if full_ft:
+            self.embed = nn.Parameter(emb)
+            self.final_norm = nn.Parameter(torch.ones(spec.hidden_size, dtype=dtype, device=dev))
+        else:
+            self.register_buffer("embed", emb, persistent=False)
+            self.register_buffer("final_norm", torch.ones(spec.hidden_size, dtype=dtype, device=dev), persistent=False)
+        if spec.tie_word_embeddings:
+            self.lm_head = None
+        elif full_ft:
+            self.lm_head = nn.Parameter(torch.zeros(spec.vocab_size, spec.hidden_size, dtype=dtype, device=dev))
+        else:
+            self.register_buffer("lm_head", torch.zeros(spec.vocab_size, spec.hidden_size, dtype=dtype, device=dev),
+                                 persistent=False)
+        self.register_buffer("head_t", None, persistent=False)
+        self.layers = nn.ModuleList([DenseLayer(spec, lora, dtype, dev, tp, keep_transpose, quant, full_ft)
+                                     for _ in range(spec.num_hidden_layers)])
+        cos, sin = ops.rope_tables(spec.rope_inv_freq(), spec.max_position_embeddings)
+        self.register_buffer("cos", cos.to(dev), persistent=False)
+        self.register_buffer("sin", sin.to(dev), persistent=False)
+        self.keep_transpose = keep_transpose
+
+    # ------------------------------------------------------------ weights
+    @torch.no_grad()
+    def init_random(self, seed: int = 0, std: float = 0.02):
+        """Random-init base weights (synthetic benchmarks) and LoRA adapters."""
+        g = torch.Generator().manual_seed(seed)
+        dev = self.embed.device
+
+        def rnd(shape):
+            # generate on the host in chunks to bound peak host memory
+            out = torch.empty(shape, dtype=self.dtype, device=dev)
+            flat = out.view(-1)
+            step = 1 << 24
+            for s in range(0, flat.numel(), step):
+                n = min(step, flat.numel() - s)
+                flat[s:s + n] = (torch.randn(n, generator=g) * std).to(self.dtype).to(dev)
+            return out
+
+        fast = dev.type == "cuda"
+        if fast:
+            gg = torch.Generator(device=dev).manual_seed(seed)
+
+            def rnd(shape):  # noqa: F811 - device-side generation for the 8B-class benchmarks
+                return (torch.randn(shape, generator=gg, device=dev, dtype=torch.float32) * std).to(self.dtype)
+        self.embed.copy_(rnd(self.embed.shape))
+        if self.lm_head is not None:
+            self.lm_head.copy_(rnd(self.lm_head.shape))
+        for l in self.layers:
+            for p in l.projections():
+                p.set_weight(rnd(p.weight.shape))
+                p.init_adapters(g)
+        self.refresh_head()
+
+    @torch.no_grad()
+    def refresh_head(self):
+        if self.keep_transpose:
+            self.head_t = self.head_weight().t().contiguous()
+
+    def head_weight(self) -> torch.Tensor:
+        return self.embed if self.lm_head is None else self.lm_head
+
+    def trainable_params(self) -> list[nn.Parameter]:
+        if self.full_ft:
+            return [p for p in self.parameters()]
+        out = []
+        for l in self.layers:
+            out += l.adapter_params()
+        return out
+
+    def set_adapter_enabled(self, on: bool):
+        for l in self.layers:
+            for p in l.projections():
+                p.enabled = on
+
+    def lora_recipe(self) -> str:
+        if self.full_ft:
+            return "full_ft"
+        return self.lora.recipe() if self.lora else "none"
+
+    @torch.no_grad()
+    def merge_adapters(self):
+        for l in self.layers:
+            for p in l.projections():
+                p.merge()
+
+    # ------------------------------------------------------------- forward
+    def forward_hidden(self, ids: torch.Tensor, comm: Optional[Comm] = None, merged: bool = False,
+                       kv_out=None, detached: bool = False) -> torch.Tensor:
+        comm = comm or SoloComm()
+        B, S = ids.shape
+        if S > self.cos.shape[0]:
+            raise ValueError(f"sequence length {S} exceeds max_position_embeddings {self.cos.shape[0]}")
+        positions = torch.arange(S, device=ids.device)
+        h = ops.embedding(ids, self.embed)
+        cot = (lambda g: g)  # boundary cotangents are already reduced by copy_to_tp's backward
+        for i, layer in enumerate(self.layers):
+            kv = None if kv_out is None else kv_out[i]
+            if self.remat and torch.is_grad_enabled() and not detached:
+                fn = (lambda x, layer=layer: layer(x, positions, self.cos, self.sin, comm, merged, None))
+                h = remat_segment(fn, h, layer.adapter_params() if not self.full_ft else list(layer.parameters()), None)
+            else:
+                h = layer(h, positions, self.cos, self.sin, comm, merged, kv)
+        del cot
+        return h
+
+    def forward(self, ids: torch.Tensor, comm: Optional[Comm] = None) -> torch.Tensor:
+        """Full-position logits ``[B, S, V]`` in float32 (oracle/test surface)."""
+        h = self.forward_hidden(ids, comm)
+        h = ops.rmsnorm(h, self.final_norm, self.spec.rms_norm_eps)
+        return torch.nn.functional.linear(h, self.head_weight()).float()
+
+    def token_logprobs(self, ids: torch.Tensor, win_start: torch.Tensor, targets: torch.Tensor,
+                       temperature: float = 1.0, comm: Optional[Comm] = None) -> torch.Tensor:
+        """Log-probs of ``targets[b, t]`` predicted at position ``win_start[b]+t``.
+        The hidden state is narrowed to the window before the final norm and the
+        head, and ``[.., V]`` logits never outlive a chunk."""
+        h = self.forward_hidden(ids, comm, detached=not torch.is_grad_enabled())
+        B, L = targets.shape
+        idx = (win_start.view(B, 1).long() + torch.arange(L, device=ids.device)[None, :]).clamp(max=ids.shape[1] - 1)
+        hw = torch.gather(h, 1, idx[:, :, None].expand(B, L, h.shape[-1]))
+        hw = ops.rmsnorm(hw, self.final_norm, self.spec.rms_norm_eps)
+        lp = ops.logprob_gather(hw.reshape(B * L, -1), self.head_weight(), targets.reshape(-1), temperature,
+                                0.0, head_wt=self.head_t)
+        return lp.view(B, L)
+
+    # ------------------------------------------------------------- rollout
+    def new_decoder(self, batch: int, max_len: int, comm: Optional[Comm] = None) -> "DenseCachedDecoder":
+        return DenseCachedDecoder(self, batch, max_len, comm or SoloComm())
+
+
+class DenseCachedDecoder:
+    """KV-cached, grad-free twin over merged weights. ``kv_len[b]`` tokens of row
+    ``b`` are cached; a decode step must be fed position ``kv_len[b]`` exactly
+    (the reference guards the same invariant, dense.rs:1708-1717)."""
+
+    def __init__(self, model: DenseGradModel, batch: int, max_len: int, comm: Comm):
+        self.m = model
+        self.comm = comm
+        spec = model.spec
+        if max_len > spec.max_position_embeddings:
+            raise ValueError("cache longer than the RoPE table")
+        dev, dt = model.embed.device, model.dtype
+        hkv = model.layers[0].hkv
+        self.k = [torch.zeros(batch, max_len, hkv, spec.head_dim, dtype=dt, device=dev) for _ in model.layers]
+        self.v = [torch.zeros(batch, max_len, hkv, spec.head_dim, dtype=dt, device=dev) for _ in model.layers]
+        self.kv_len = torch.zeros(batch, dtype=torch.int32, device=dev)
+        self.max_len = max_len
+        self.batch = batch
+
+    def cache_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.k + self.v)
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, lens: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Prefill ``ids`` ``[P, L]`` (right-padded, true lengths ``lens``) into
+        cache rows ``rows`` (default ``0..P``); returns last-token logits ``[P, V]``."""
+        m = self.m
+        P, L = ids.shape
+        rows = torch.arange(P, device=ids.device) if rows is None else rows
+        tmp = [(torch.empty(P, L, self.k[0].shape[2], self.k[0].shape[3], dtype=m.dtype, device=ids.device),
+                torch.empty(P, L, self.k[0].shape[2], self.k[0].shape[3], dtype=m.dtype, device=ids.device))
+               for _ in m.layers]
+        h = m.forward_hidden(ids, self.comm, merged=True, kv_out=tmp, detached=True)
+        for i in range(len(m.layers)):
+            self.k[i][rows, :L] = tmp[i][0]
+            self.v[i][rows, :L] = tmp[i][1]
+        self.kv_len[rows] = lens.to(torch.int32)
+        last = h[torch.arange(P, device=ids.device), (lens - 1).long()]
+        last = ops.rmsnorm(last, m.final_norm, m.spec.rms_norm_eps)
+        return ops.lora_linear(last, m.head_weight(), None, None).float()
+
+    @torch.no_grad()
+    def broadcast_groups(self, group: int):
+        """Rows ``0..P`` hold one prefilled prompt each; replicate so that row
+        ``p*group + g`` holds prompt ``p`` (the group shares its prompt's KV)."""
+        P = self.batch // group
+        src = torch.arange(P, device=self.kv_len.device).repeat_interleave(group)
+        for i in range(len(self.k)):
+            self.k[i].copy_(self.k[i][src])
+            self.v[i].copy_(self.v[i][src])
+        self.kv_len.copy_(self.kv_len[src])
+
+    @torch.no_grad()
+    def decode(self, tokens: torch.Tensor) -> torch.Tensor:
+        """Feed one token per row; returns next-token logits ``[B, V]`` float32."""
+        m = self.m
+        h = ops.embedding(tokens, m.embed)
+        for i, layer in enumerate(m.layers):
+            h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm)
+        self.kv_len += 1
+        h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
+        return ops.lora_linear(h, m.head_weight(), None, None).float()

@@ -1,0 +1,288 @@
+"""LoRA over frozen linear projections, grouped by shared input.
+
+A ``FusedLoraLinear`` owns one frozen weight whose rows are the concatenation
+of several logical projections that read the same activation (q|k|v, gate|up)
+or a single projection (o, down).  Each adapted projection ``i`` has float32
+master adapters ``A_i [r, in]`` (normal, std 0.02) and ``B_i [out_i, r]``
+(zeros) with scale ``alpha / r`` over a bf16 (or fp32) frozen base, as in the
+reference (``crates/ferrl/src/lora.rs:1044-1406``).
+
+B200 layout: the group is evaluated as ONE GEMM whose K dimension is extended
+by the stacked LoRA width, ``y = [x | x A_stackᵀ] · [W | s·B_blockdiag]ᵀ``,
+so the LoRA delta is extra k-tiles of the same tcgen05 tile loop instead of
+three more matmuls and an add.  ``x A_stackᵀ`` is one skinny GEMM for the whole
+group.  The stacks are rebuilt from the masters each call with differentiable
+torch ops, so autograd delivers per-projection gradients in master layout and
+checkpoints keep one tensor per adapter.
+
+Rollout does not run the side path at all: ``merged_weight`` folds ``W+s·B·A``
+into a second resident copy of the weights (HBM3e has room), rebuilt once per
+policy update (reference lora.rs:1335-1350 rebuilds per ``generate`` call).
+
+Tensor parallelism follows the reference's slicing-at-use rule
+(``lora.rs:1245-1304``): adapters stay replicated; a column-parallel shard uses
+the matching rows of ``B``, a row-parallel shard the matching columns of ``A``.
+"""
+from __future__ import annotations
+
+import enum
+import math
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import torch
+from torch import nn
+
+from .. import ops
+
+
+class BaseQuantization(str, enum.Enum):
+    NONE = "none"
+    Q8_0 = "q8_0"
+
+
+def validated_lora_scale(rank: int, alpha: float) -> float:
+    if rank <= 0:
+        raise ValueError("LoRA rank must be > 0")
+    if not math.isfinite(alpha) or alpha <= 0:
+        raise ValueError("LoRA alpha must be finite and > 0")
+    s = alpha / rank
+    if not math.isfinite(s) or s <= 0:
+        raise ValueError("LoRA scale alpha/rank must be finite and > 0")
+    return s
+
+
+@dataclass(frozen=True)
+class DenseLoraTargets:
+    """Which of the seven dense projections carry adapters (reference
+    lora.rs:635-735). ``canonical()`` is part of the checkpoint recipe."""
+
+    attn_q: bool = True
+    attn_k: bool = True
+    attn_v: bool = True
+    attn_o: bool = True
+    mlp_gate: bool = True
+    mlp_up: bool = True
+    mlp_down: bool = True
+
+    @staticmethod
+    def industrial() -> "DenseLoraTargets":
+        return DenseLoraTargets()
+
+    @staticmethod
+    def legacy() -> "DenseLoraTargets":
+        return DenseLoraTargets(True, False, True, False, False, False, False)
+
+    @staticmethod
+    def attention_only() -> "DenseLoraTargets":
+        return DenseLoraTargets(True, True, True, True, False, False, False)
+
+    def any(self) -> bool:
+        return any((self.attn_q, self.attn_k, self.attn_v, self.attn_o,
+                    self.mlp_gate, self.mlp_up, self.mlp_down))
+
+    def canonical(self) -> str:
+        def pick(pairs):
+            s = "".join(c for on, c in pairs if on)
+            return s or "-"
+        return "attn:{}|mlp:{}".format(
+            pick([(self.attn_q, "q"), (self.attn_k, "k"), (self.attn_v, "v"), (self.attn_o, "o")]),
+            pick([(self.mlp_gate, "g"), (self.mlp_up, "u"), (self.mlp_down, "d")]))
+
+    @staticmethod
+    def parse(s: str) -> "DenseLoraTargets":
+        if s in ("industrial", "all"):
+            return DenseLoraTargets.industrial()
+        if s in ("legacy", "qv"):
+            return DenseLoraTargets.legacy()
+        try:
+            parts = dict(p.split(":") for p in s.split("|"))
+            a, m = parts.get("attn", "-"), parts.get("mlp", "-")
+        except ValueError as e:
+            raise ValueError(f"bad LoRA target string {s!r}") from e
+        if set(a) - set("qkvo-") or set(m) - set("gud-"):
+            raise ValueError(f"bad LoRA target string {s!r}")
+        return DenseLoraTargets("q" in a, "k" in a, "v" in a, "o" in a, "g" in m, "u" in m, "d" in m)
+
+
+@dataclass
+class LoraSpec:
+    rank: int = 8
+    alpha: float = 16.0
+    targets: DenseLoraTargets = field(default_factory=DenseLoraTargets)
+
+    @property
+    def scale(self) -> float:
+        return validated_lora_scale(self.rank, self.alpha)
+
+    def recipe(self) -> str:
+        return f"lora:r{self.rank}:a{self.alpha:g}:{self.targets.canonical()}"
+
+
+@dataclass(frozen=True)
+class Shard:
+    """Tensor-parallel placement of a projection group. ``kind`` is ``column``
+    (output rows split) or ``row`` (input columns split)."""
+
+    kind: str
+    rank: int
+    world: int
+
+
+def q8_0_quantize(w: torch.Tensor):
+    """GGML-style Q8_0: blocks of 32 along the input dim, one fp16 scale each."""
+    out, inn = w.shape
+    if inn % 32:
+        raise ValueError("Q8_0 needs the input dim to be a multiple of 32")
+    blocks = w.float().reshape(out, inn // 32, 32)
+    d = blocks.abs().amax(-1, keepdim=True) / 127.0
+    q = torch.where(d > 0, blocks / d.clamp(min=1e-30), torch.zeros_like(blocks)).round().clamp(-127, 127)
+    return q.to(torch.int8).reshape(out, inn), d.squeeze(-1).half()
+
+
+def q8_0_dequantize(q: torch.Tensor, d: torch.Tensor, dtype) -> torch.Tensor:
+    out, inn = q.shape
+    return (q.reshape(out, inn // 32, 32).float() * d.float().unsqueeze(-1)).reshape(out, inn).to(dtype)
+
+
+class FusedLoraLinear(nn.Module):
+    """Frozen ``[sum(out_sizes), in]`` weight + optional adapters per logical
+    projection.  ``names`` label the projections (``("q","k","v")``)."""
+
+    def __init__(self, in_features: int, out_sizes: Sequence[int], names: Sequence[str],
+                 adapted: Sequence[bool], lora: Optional[LoraSpec], *, dtype=torch.float32,
+                 device=None, shard: Optional[Shard] = None, full_in: Optional[int] = None,
+                 full_out_sizes: Optional[Sequence[int]] = None, keep_transpose: bool = False,
+                 quant: BaseQuantization = BaseQuantization.NONE, trainable_base: bool = False):
+        super().__init__()
+        self.in_features = in_features
+        self.out_sizes = list(out_sizes)
+        self.names = list(names)
+        self.shard = shard
+        # adapters are replicated at FULL size under TP and sliced at use
+        self.full_in = full_in if full_in is not None else in_features
+        self.full_out_sizes = list(full_out_sizes) if full_out_sizes is not None else list(out_sizes)
+        self.quant = BaseQuantization(quant)
+        self.keep_transpose = keep_transpose
+        self.enabled = True
+        w = torch.empty(sum(out_sizes), in_features, dtype=dtype, device=device)
+        if trainable_base:
+            self.weight = nn.Parameter(w)
+        else:
+            self.register_buffer("weight", w, persistent=False)
+        self.register_buffer("weight_t", None, persistent=False)
+        self.register_buffer("weight_merged", None, persistent=False)
+        self._q = None
+        self.scale = lora.scale if lora is not None else 0.0
+        self.rank = lora.rank if lora is not None else 0
+        self.lora_A = nn.ParameterList()
+        self.lora_B = nn.ParameterList()
+        self.adapted_idx: list[int] = []
+        if lora is not None:
+            for i, on in enumerate(adapted):
+                if not on:
+                    continue
+                self.adapted_idx.append(i)
+                a = torch.empty(lora.rank, self.full_in, dtype=torch.float32, device=device)
+                self.lora_A.append(nn.Parameter(a))
+                self.lora_B.append(nn.Parameter(torch.zeros(self.full_out_sizes[i], lora.rank,
+                                                            dtype=torch.float32, device=device)))
+
+    # ---------------------------------------------------------------- init
+    @torch.no_grad()
+    def init_adapters(self, generator: Optional[torch.Generator] = None):
+        for a in self.lora_A:
+            a.copy_(torch.randn(a.shape, generator=generator, dtype=torch.float32) * 0.02)
+        for b in self.lora_B:
+            b.zero_()
+
+    @torch.no_grad()
+    def set_weight(self, w: torch.Tensor):
+        """Install the (local shard of the) frozen weight and derived copies."""
+        assert tuple(w.shape) == tuple(self.weight.shape), (w.shape, self.weight.shape)
+        if self.quant is BaseQuantization.Q8_0:
+            q, d = q8_0_quantize(w)
+            self._q = (q.to(self.weight.device), d.to(self.weight.device))
+            w = q8_0_dequantize(q, d, self.weight.dtype)
+        self.weight.copy_(w)
+        self.refresh_derived()
+
+    @torch.no_grad()
+    def refresh_derived(self):
+        if self.keep_transpose:
+            self.weight_t = self.weight.t().contiguous()
+        self.weight_merged = None
+
+    # ------------------------------------------------------------- adapters
+    def has_adapters(self) -> bool:
+        return len(self.adapted_idx) > 0
+
+    def _stacks(self):
+        """Differentiable ``(A_stack [n*r, in_local], B_stack [out_local, n*r])``
+        with the LoRA scale folded into ``B_stack`` and TP slicing applied."""
+        if not self.has_adapters() or not self.enabled:
+            return None, None
+        r = self.rank
+        A = torch.cat(list(self.lora_A), dim=0)  # [n*r, full_in]
+        cols = []
+        offs = 0
+        starts = []
+        for o in self.out_sizes:
+            starts.append(offs)
+            offs += o
+        B = A.new_zeros(sum(self.out_sizes), r * len(self.adapted_idx))
+        pieces = []
+        for j, i in enumerate(self.adapted_idx):
+            b = self.lora_B[j]
+            if self.shard is not None and self.shard.kind == "column":
+                per = self.full_out_sizes[i] // self.shard.world
+                b = b[self.shard.rank * per:(self.shard.rank + 1) * per]
+            pieces.append((starts[i], j, b))
+        # block placement via padding keeps autograd simple and cheap
+        rows = []
+        cur = 0
+        for start, j, b in sorted(pieces, key=lambda p: p[0]):
+            if start > cur:
+                rows.append(A.new_zeros(start - cur, r * len(self.adapted_idx)))
+            left = A.new_zeros(b.shape[0], j * r)
+            right = A.new_zeros(b.shape[0], (len(self.adapted_idx) - j - 1) * r)
+            rows.append(torch.cat([left, b * self.scale, right], dim=1))
+            cur = start + b.shape[0]
+        if cur < sum(self.out_sizes):
+            rows.append(A.new_zeros(sum(self.out_sizes) - cur, r * len(self.adapted_idx)))
+        B = torch.cat(rows, dim=0)
+        if self.shard is not None and self.shard.kind == "row":
+            per = self.full_in // self.shard.world
+            A = A[:, self.shard.rank * per:(self.shard.rank + 1) * per]
+        del cols
+        return A, B
+
+    # --------------------------------------------------------------- forward
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        a, b = self._stacks()
+        return ops.lora_linear(x, self.weight, a, b, wt=self.weight_t)
+
+    def forward_merged(self, x: torch.Tensor) -> torch.Tensor:
+        """Rollout path over the merged snapshot (no adapter side path)."""
+        w = self.weight_merged if self.weight_merged is not None else self.weight
+        return ops.lora_linear(x, w, None, None)
+
+    @torch.no_grad()
+    def merge(self):
+        """Refresh the merged snapshot ``W + s·B·A`` (call after each update)."""
+        a, b = self._stacks()
+        if a is None:
+            self.weight_merged = None
+            return
+        self.weight_merged = ops.lora_merge(self.weight, a.detach(), b.detach())
+
+    def merged_weight(self) -> torch.Tensor:
+        a, b = self._stacks()
+        return ops.lora_merge(self.weight, None if a is None else a.detach(),
+                              None if b is None else b.detach())
+
+    def adapter_params(self) -> list[nn.Parameter]:
+        out = []
+        for a, b in zip(self.lora_A, self.lora_B):
+            out += [a, b]
+        return out
