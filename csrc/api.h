@@ -1,0 +1,96 @@
+// Host-callable launchers of the sm_100a kernels. Every launcher takes raw device pointers
+// plus a stream, returns nullptr on success or a static error string, and never allocates.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+namespace ferrl {
+
+enum { kBF16 = 0, kF32 = 1 };
+enum { kActSilu = 0, kActGeluTanh = 1 };
+
+// ---- tcgen05 GEMM: out[M,N] = A[M,K] B[N,K]^T (+ A2[M,K2] B2[N,K2]^T) (+ residual) ----
+struct GemmArgs {
+  const void* A; const void* B; const void* A2; const void* B2;  // bf16, K-major
+  long long lda, ldb, lda2, ldb2;                                 // row strides in elements
+  int M, N, K, K2;
+  void* out; long long ldo; bool out_f32;
+  const void* residual; long long ldr;                            // optional bf16 [M, ldr]
+  int* status;                                                    // device status word (kStatus*)
+  int num_sms;
+  int force_bn;                                                   // 0 = heuristic
+};
+const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);
+int gemm_pick_bn(int M, int N, int num_sms);
+
+// ---- norms / rope ----
+const char* rmsnorm(int dtype, const void* x, const void* res, const void* w, const void* gate, void* y, void* h_out,
+                    long long rows, int H, float eps, bool zero_centered, cudaStream_t s);
+const char* rmsnorm_bwd(int dtype, const void* x, const void* w, const void* dy, void* dx, long long rows, int H,
+                        float eps, bool zero_centered, cudaStream_t s);
+struct QkNormRopeArgs {
+  int dtype; bool backward;
+  const void* q_in; long long ld_q;                     // [n_tok, Hq*D] rows with token stride ld_q (may be a view
+  const void* k_in; long long ld_k;                     //  into the fused qkv projection output)
+  const void* qw; const void* kw;                       // per-head norm weights or nullptr
+  const float* cos_t; const float* sin_t;               // [max_pos, half]
+  const long long* pos64; const int* pos32; int pos_div; // position of token t is pos[t / pos_div]
+  void* q_out; void* k_out;     // forward: contiguous [n_tok,Hq,D] / [n_tok,Hkv,D]; backward: d(q_in) / d(k_in)
+  long long ld_dq, ld_dk;       // backward: token strides of the two gradient destinations
+  const void* dq; const void* dk;                       // backward inputs (contiguous)
+  long long n_tok; int Hq, Hkv, D, half; float eps; bool zero_centered;
+};
+const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s);
+const char* kv_append(int dtype, const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
+                      int batch, int smax, int HD, cudaStream_t s);
+
+// ---- misc ----
+const char* glu(int dtype, bool backward, const void* gu, const void* dout, void* out, long long rows, int F, int act,
+                cudaStream_t s);
+const char* embedding(int dtype, const long long* ids, const void* table, void* out, long long n_tok, int H,
+                      long long vocab, float scale, cudaStream_t s);
+const char* lora_merge(int dtype, const void* w, const float* a, const float* b, void* out, int O, int I, int R,
+                       cudaStream_t s);
+struct AdamTensor { float* p; const float* g; float* m; float* v; long long n; };
+const char* adamw_multi(const AdamTensor* tab_dev, const int* blk_tensor_dev, const long long* blk_off_dev,
+                        int n_blocks, int chunk, double* sumsq_dev, bool compute_norm, float lr, float b1, float b2,
+                        float eps, float wd, float bc1_inv, float bc2_inv, float max_norm, float pre_scale,
+                        float* norm_out_dev, cudaStream_t s);
+const char* grpo_loss_rows(const float* logp, const float* logp_old, const float* logp_ref, const float* adv,
+                           const float* mask, const float* tis, float* row_sum, float* row_cnt, float* dlogp, int G,
+                           int L, float eps_lo, float eps_hi, float beta, int mode, cudaStream_t s);
+const char* grpo_scale_rows(float* dlogp, const float* row_scale, int G, int L, cudaStream_t s);
+
+// ---- decode attention ----
+struct DecodeAttnArgs {
+  const void* q; const void* k; const void* v;  // q [B,Hq,D]; caches [B,Smax,Hkv,D] (or paged)
+  const int* kv_len; const int* block_table; int bt_stride, page;
+  void* out; float* workspace;
+  int B, Hq, Hkv, D; long long seq_stride, tok_stride; float scale; int window, n_splits;
+};
+const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s);
+size_t decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);
+int decode_attn_pick_splits(int B, int Hkv, int max_len, int num_sms);
+
+// ---- flash attention (prefill / training) ----
+struct FlashArgs {
+  const void* q; const void* k; const void* v; void* o; float* lse;   // bf16; lse [B,Hq,Sq]
+  long long q_bs, q_ts, k_bs, k_ts, v_bs, v_ts, o_bs, o_ts;            // batch / token strides (elements)
+  int B, Sq, Sk, Hq, Hkv, D; float scale; int causal, window, q_offset;
+  // backward only
+  const void* d_o; void* dq; void* dk; void* dv; float* delta;
+  long long do_bs, do_ts, dq_bs, dq_ts, dk_bs, dk_ts, dv_bs, dv_ts;
+};
+const char* flash_fwd(const FlashArgs& a, cudaStream_t s);
+const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
+
+// ---- vocabulary rows ----
+const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,
+                         long long rows, int V, float temperature, float softcap, cudaStream_t s);
+const char* logprob_rows_bwd(int dtype, void* logits, long long ld, const long long* targets, const float* lse,
+                             const float* dlp, long long rows, int V, float temperature, float softcap, cudaStream_t s);
+const char* sample_rows(int dtype, const void* logits, long long ld, const long long* global_rows,
+                        unsigned long long seed, const int* draw_dev, int draw_host, long long* tok_out, float* lp_out,
+                        int rows, int V, float temperature, float top_p, cudaStream_t s);
+
+}  // namespace ferrl

@@ -1,0 +1,443 @@
+// torch op registration for the ferrl_b200 native library (namespace torch.ops.ferrl_b200).
+// Thin argument checking + pointer extraction; all device work is in the .cu files.
+#include <ATen/ATen.h>
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <atomic>
+#include <mutex>
+#include <unordered_map>
+#include <vector>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace ferrl {
+static std::atomic<long long> g_launches{0};
+void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+}  // namespace ferrl
+
+namespace {
+
+using at::Tensor;
+using c10::optional;
+
+#define FERRL_CHECK(err) do { const char* e__ = (err); TORCH_CHECK(e__ == nullptr, "ferrl_b200: ", e__); } while (0)
+
+cudaStream_t stream() { return c10::cuda::getCurrentCUDAStream().stream(); }
+
+int dt(const Tensor& t) {
+  if (t.scalar_type() == at::kBFloat16) return ferrl::kBF16;
+  if (t.scalar_type() == at::kFloat) return ferrl::kF32;
+  TORCH_CHECK(false, "ferrl_b200: tensors must be bfloat16 or float32, got ", t.scalar_type());
+}
+
+const void* optr(const optional<Tensor>& t) { return t.has_value() && t->defined() ? t->data_ptr() : nullptr; }
+
+int num_sms() {
+  static int n = 0;
+  if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+// one status word per device, allocated once
+int* status_word() {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> words;
+  std::lock_guard<std::mutex> g(mu);
+  int dev = c10::cuda::current_device();
+  auto it = words.find(dev);
+  if (it == words.end())
+    it = words.emplace(dev, at::zeros({4}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, dev))).first;
+  return it->second.data_ptr<int>();
+}
+
+int64_t kernel_status() {
+  int h = 0;
+  C10_CUDA_CHECK(cudaMemcpy(&h, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
+  return h;
+}
+void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(int), stream())); }
+
+// out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
+Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
+            const optional<Tensor>& residual, bool out_f32, int64_t force_bn) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
+  TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1, "gemm: operands must be K-major");
+  c10::cuda::CUDAGuard guard(A.device());
+  ferrl::GemmArgs a{};
+  a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
+  a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
+  if (A2.has_value() && A2->defined()) {
+    TORCH_CHECK(B2.has_value() && B2->defined(), "gemm: A2 without B2");
+    TORCH_CHECK(A2->scalar_type() == at::kBFloat16 && B2->scalar_type() == at::kBFloat16, "gemm: side operands bf16");
+    TORCH_CHECK(A2->dim() == 2 && B2->dim() == 2 && A2->size(0) == a.M && B2->size(0) == a.N &&
+                    A2->size(1) == B2->size(1) && A2->stride(1) == 1 && B2->stride(1) == 1,
+                "gemm: side operand shapes");
+    a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
+  }
+  Tensor out = at::empty({a.M, a.N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = out_f32;
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == a.M &&
+                    residual->size(1) == a.N && residual->stride(1) == 1,
+                "gemm: residual must be bf16 [M,N]");
+    a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
+  }
+  a.status = status_word(); a.num_sms = num_sms(); a.force_bn = static_cast<int>(force_bn);
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
+std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const optional<Tensor>& res, const optional<Tensor>& w,
+                                   const optional<Tensor>& gate, double eps, bool zc) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "rmsnorm: contiguous CUDA tensor required");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int H = x.size(-1);
+  const long long rows = x.numel() / H;
+  Tensor y = at::empty_like(x);
+  Tensor h;
+  if (res.has_value() && res->defined()) {
+    TORCH_CHECK(res->is_contiguous() && res->sizes() == x.sizes() && res->scalar_type() == x.scalar_type(), "rmsnorm: residual");
+    h = at::empty_like(x);
+  }
+  if (w.has_value() && w->defined()) TORCH_CHECK(w->scalar_type() == x.scalar_type() && w->numel() == H && w->is_contiguous(), "rmsnorm: weight");
+  if (gate.has_value() && gate->defined()) TORCH_CHECK(gate->is_contiguous() && gate->sizes() == x.sizes() && gate->scalar_type() == x.scalar_type(), "rmsnorm: gate");
+  FERRL_CHECK(ferrl::rmsnorm(dt(x), x.data_ptr(), optr(res), optr(w), optr(gate), y.data_ptr(),
+                             h.defined() ? h.data_ptr() : nullptr, rows, H, static_cast<float>(eps), zc, stream()));
+  return {y, h.defined() ? h : Tensor()};
+}
+
+Tensor rmsnorm_bwd(const Tensor& x, const optional<Tensor>& w, const Tensor& dy, double eps, bool zc) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && dy.is_contiguous() && dy.sizes() == x.sizes() &&
+                  dy.scalar_type() == x.scalar_type(), "rmsnorm_bwd: shapes");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int H = x.size(-1);
+  Tensor dx = at::empty_like(x);
+  FERRL_CHECK(ferrl::rmsnorm_bwd(dt(x), x.data_ptr(), optr(w), dy.data_ptr(), dx.data_ptr(), x.numel() / H, H,
+                                 static_cast<float>(eps), zc, stream()));
+  return dx;
+}
+
+void fill_qknr(ferrl::QkNormRopeArgs& a, const Tensor& q, const Tensor& k, const optional<Tensor>& qw,
+               const optional<Tensor>& kw, const Tensor& cos_t, const Tensor& sin_t, const Tensor& pos, int64_t pos_div,
+               double eps, bool zc) {
+  // q [T, Hq, D], k [T, Hkv, D]: heads packed (stride(1) == D, stride(2) == 1), arbitrary token stride
+  TORCH_CHECK(q.is_cuda() && q.dim() == 3 && k.dim() == 3 && q.size(0) == k.size(0) && q.size(2) == k.size(2),
+              "qk_norm_rope: q [T,Hq,D], k [T,Hkv,D]");
+  TORCH_CHECK(q.stride(2) == 1 && k.stride(2) == 1 && q.stride(1) == q.size(2) && k.stride(1) == k.size(2),
+              "qk_norm_rope: heads must be packed");
+  TORCH_CHECK(q.scalar_type() == k.scalar_type(), "qk_norm_rope: dtype mismatch");
+  TORCH_CHECK(cos_t.scalar_type() == at::kFloat && sin_t.scalar_type() == at::kFloat && cos_t.is_contiguous() &&
+                  sin_t.is_contiguous() && cos_t.dim() == 2, "qk_norm_rope: float32 tables [max_pos, half]");
+  TORCH_CHECK(pos.is_contiguous() && (pos.scalar_type() == at::kLong || pos.scalar_type() == at::kInt), "qk_norm_rope: positions int64/int32");
+  a.dtype = dt(q);
+  a.q_in = q.data_ptr(); a.ld_q = q.stride(0); a.k_in = k.data_ptr(); a.ld_k = k.stride(0);
+  a.qw = optr(qw); a.kw = optr(kw);
+  a.cos_t = cos_t.data_ptr<float>(); a.sin_t = sin_t.data_ptr<float>();
+  a.pos64 = pos.scalar_type() == at::kLong ? reinterpret_cast<long long*>(pos.data_ptr<int64_t>()) : nullptr;
+  a.pos32 = pos.scalar_type() == at::kInt ? pos.data_ptr<int>() : nullptr;
+  a.pos_div = pos_div;
+  a.n_tok = q.size(0); a.Hq = q.size(1); a.Hkv = k.size(1); a.D = q.size(2); a.half = cos_t.size(1);
+  a.eps = static_cast<float>(eps); a.zero_centered = zc;
+  TORCH_CHECK(pos.numel() * pos_div >= a.n_tok, "qk_norm_rope: too few positions");
+}
+
+std::tuple<Tensor, Tensor> qk_norm_rope_fwd(const Tensor& q, const Tensor& k, const optional<Tensor>& qw,
+                                            const optional<Tensor>& kw, const Tensor& cos_t, const Tensor& sin_t,
+                                            const Tensor& pos, int64_t pos_div, double eps, bool zc) {
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::QkNormRopeArgs a{};
+  fill_qknr(a, q, k, qw, kw, cos_t, sin_t, pos, pos_div, eps, zc);
+  Tensor qo = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor ko = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
+  a.backward = false; a.q_out = qo.data_ptr(); a.k_out = ko.data_ptr();
+  FERRL_CHECK(ferrl::qk_norm_rope(a, stream()));
+  return {qo, ko};
+}
+
+// d(q_in), d(k_in) written into dq_in / dk_in (views with packed heads, any token stride)
+void qk_norm_rope_bwd(const Tensor& q, const Tensor& k, const optional<Tensor>& qw, const optional<Tensor>& kw,
+                      const Tensor& cos_t, const Tensor& sin_t, const Tensor& pos, int64_t pos_div, double eps, bool zc,
+                      const Tensor& dq, const Tensor& dk, Tensor dq_in, Tensor dk_in) {
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::QkNormRopeArgs a{};
+  fill_qknr(a, q, k, qw, kw, cos_t, sin_t, pos, pos_div, eps, zc);
+  TORCH_CHECK(dq.is_contiguous() && dk.is_contiguous() && dq_in.sizes() == q.sizes() && dk_in.sizes() == k.sizes() &&
+                  dq_in.stride(2) == 1 && dk_in.stride(2) == 1 && dq_in.stride(1) == q.size(2) &&
+                  dk_in.stride(1) == k.size(2), "qk_norm_rope_bwd: shapes");
+  a.backward = true; a.dq = dq.data_ptr(); a.dk = dk.data_ptr();
+  a.q_out = dq_in.data_ptr(); a.k_out = dk_in.data_ptr(); a.ld_dq = dq_in.stride(0); a.ld_dk = dk_in.stride(0);
+  FERRL_CHECK(ferrl::qk_norm_rope(a, stream()));
+}
+
+void kv_append(const Tensor& k, const Tensor& v, Tensor kc, Tensor vc, const Tensor& kv_len) {
+  // k [B, Hkv*D] contiguous, v [B, Hkv*D] row-strided view, caches [B, Smax, Hkv, D]
+  c10::cuda::CUDAGuard guard(k.device());
+  TORCH_CHECK(k.is_contiguous() && v.stride(-1) == 1 && kc.is_contiguous() && vc.is_contiguous() &&
+                  kv_len.scalar_type() == at::kInt, "kv_append: layout");
+  const int B = kc.size(0), smax = kc.size(1), HD = kc.size(2) * kc.size(3);
+  FERRL_CHECK(ferrl::kv_append(dt(k), k.data_ptr(), v.data_ptr(), v.stride(0), kc.data_ptr(), vc.data_ptr(),
+                               kv_len.data_ptr<int>(), B, smax, HD, stream()));
+}
+
+Tensor glu_fwd(const Tensor& gu, int64_t act) {
+  TORCH_CHECK(gu.is_cuda() && gu.is_contiguous(), "glu: contiguous CUDA tensor");
+  c10::cuda::CUDAGuard guard(gu.device());
+  const int F = gu.size(-1) / 2;
+  auto sizes = gu.sizes().vec();
+  sizes.back() = F;
+  Tensor out = at::empty(sizes, gu.options());
+  FERRL_CHECK(ferrl::glu(dt(gu), false, gu.data_ptr(), nullptr, out.data_ptr(), gu.numel() / (2 * F), F, act, stream()));
+  return out;
+}
+
+Tensor glu_bwd(const Tensor& gu, const Tensor& dout, int64_t act) {
+  TORCH_CHECK(gu.is_contiguous() && dout.is_contiguous(), "glu_bwd: contiguous");
+  c10::cuda::CUDAGuard guard(gu.device());
+  const int F = gu.size(-1) / 2;
+  Tensor dgu = at::empty_like(gu);
+  FERRL_CHECK(ferrl::glu(dt(gu), true, gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), gu.numel() / (2 * F), F, act, stream()));
+  return dgu;
+}
+
+Tensor embedding(const Tensor& ids, const Tensor& table, double scale) {
+  TORCH_CHECK(ids.scalar_type() == at::kLong && table.is_contiguous() && table.dim() == 2, "embedding: args");
+  c10::cuda::CUDAGuard guard(table.device());
+  Tensor idc = ids.contiguous();
+  auto sizes = idc.sizes().vec();
+  sizes.push_back(table.size(1));
+  Tensor out = at::empty(sizes, table.options());
+  FERRL_CHECK(ferrl::embedding(dt(table), reinterpret_cast<long long*>(idc.data_ptr<int64_t>()), table.data_ptr(), out.data_ptr(), idc.numel(),
+                               table.size(1), table.size(0), static_cast<float>(scale), stream()));
+  return out;
+}
+
+Tensor lora_merge(const Tensor& w, const Tensor& a, const Tensor& b) {
+  TORCH_CHECK(w.is_contiguous() && a.is_contiguous() && b.is_contiguous() && a.scalar_type() == at::kFloat &&
+                  b.scalar_type() == at::kFloat && a.size(1) == w.size(1) && b.size(0) == w.size(0) &&
+                  a.size(0) == b.size(1), "lora_merge: shapes");
+  c10::cuda::CUDAGuard guard(w.device());
+  Tensor out = at::empty_like(w);
+  FERRL_CHECK(ferrl::lora_merge(dt(w), w.data_ptr(), a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr(),
+                                w.size(0), w.size(1), a.size(0), stream()));
+  return out;
+}
+
+// Multi-tensor AdamW with optional in-kernel global-norm clip. Returns the pre-clip gradient norm
+// (a 1-element device tensor; zeros when compute_norm is false).
+Tensor adamw_step(std::vector<Tensor> params, std::vector<Tensor> grads, std::vector<Tensor> m, std::vector<Tensor> v,
+                  double lr, double b1, double b2, double eps, double wd, int64_t step, double max_norm,
+                  double pre_scale, bool compute_norm) {
+  const size_t n = params.size();
+  TORCH_CHECK(grads.size() == n && m.size() == n && v.size() == n, "adamw: list sizes");
+  Tensor norm = at::zeros({1}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, c10::cuda::current_device()));
+  if (n == 0) return norm;
+  c10::cuda::CUDAGuard guard(params[0].device());
+  const int chunk = 1 << 16;
+  std::vector<ferrl::AdamTensor> tab(n);
+  std::vector<int> blk_t;
+  std::vector<long long> blk_o;
+  for (size_t i = 0; i < n; ++i) {
+    TORCH_CHECK(params[i].scalar_type() == at::kFloat && grads[i].scalar_type() == at::kFloat &&
+                    params[i].is_contiguous() && grads[i].is_contiguous() && m[i].is_contiguous() &&
+                    v[i].is_contiguous() && grads[i].numel() == params[i].numel(), "adamw: float32 contiguous tensors");
+    tab[i] = {params[i].data_ptr<float>(), grads[i].data_ptr<float>(), m[i].data_ptr<float>(), v[i].data_ptr<float>(),
+              params[i].numel()};
+    for (long long o = 0; o < params[i].numel(); o += chunk) {
+      blk_t.push_back(static_cast<int>(i));
+      blk_o.push_back(o);
+    }
+  }
+  const size_t tab_b = n * sizeof(ferrl::AdamTensor), bt_b = blk_t.size() * sizeof(int), bo_b = blk_o.size() * sizeof(long long);
+  const size_t off1 = (tab_b + 15) & ~size_t(15), off2 = (off1 + bt_b + 15) & ~size_t(15), total = off2 + bo_b + 16;
+  Tensor host = at::empty({static_cast<long long>(total)}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
+  memcpy(host.data_ptr<uint8_t>(), tab.data(), tab_b);
+  memcpy(host.data_ptr<uint8_t>() + off1, blk_t.data(), bt_b);
+  memcpy(host.data_ptr<uint8_t>() + off2, blk_o.data(), bo_b);
+  Tensor dev = host.to(params[0].device(), /*non_blocking=*/true);
+  Tensor sumsq = at::zeros({1}, norm.options().dtype(at::kDouble));
+  uint8_t* d = dev.data_ptr<uint8_t>();
+  const float bc1 = 1.f / (1.f - static_cast<float>(std::pow(b1, static_cast<double>(step))));
+  const float bc2 = 1.f / (1.f - static_cast<float>(std::pow(b2, static_cast<double>(step))));
+  FERRL_CHECK(ferrl::adamw_multi(reinterpret_cast<ferrl::AdamTensor*>(d), reinterpret_cast<int*>(d + off1),
+                                 reinterpret_cast<long long*>(d + off2), static_cast<int>(blk_t.size()), chunk,
+                                 sumsq.data_ptr<double>(), compute_norm, lr, b1, b2, eps, wd, bc1, bc2,
+                                 static_cast<float>(max_norm), static_cast<float>(pre_scale), norm.data_ptr<float>(),
+                                 stream()));
+  return norm;
+}
+
+std::tuple<Tensor, Tensor, Tensor> grpo_loss_rows(const Tensor& logp, const Tensor& logp_old,
+                                                  const optional<Tensor>& logp_ref, const Tensor& adv,
+                                                  const Tensor& mask, const optional<Tensor>& tis, double eps_lo,
+                                                  double eps_hi, double beta, bool seq_level, bool want_grad) {
+  TORCH_CHECK(logp.is_cuda() && logp.scalar_type() == at::kFloat && logp.is_contiguous() && logp_old.is_contiguous() &&
+                  mask.is_contiguous() && adv.is_contiguous() && logp.dim() == 2, "grpo_loss: float32 [G,L] tensors");
+  c10::cuda::CUDAGuard guard(logp.device());
+  const int G = logp.size(0), L = logp.size(1);
+  Tensor row_sum = at::empty({G}, logp.options()), row_cnt = at::empty({G}, logp.options());
+  Tensor dl = want_grad ? at::empty_like(logp) : Tensor();
+  int mode = (seq_level ? 1 : 0) | (logp_ref.has_value() && logp_ref->defined() ? 2 : 0) |
+             (tis.has_value() && tis->defined() ? 4 : 0);
+  FERRL_CHECK(ferrl::grpo_loss_rows(logp.data_ptr<float>(), logp_old.data_ptr<float>(),
+                                    static_cast<const float*>(optr(logp_ref)), adv.data_ptr<float>(),
+                                    mask.data_ptr<float>(), static_cast<const float*>(optr(tis)),
+                                    row_sum.data_ptr<float>(), row_cnt.data_ptr<float>(),
+                                    want_grad ? dl.data_ptr<float>() : nullptr, G, L, eps_lo, eps_hi, beta, mode, stream()));
+  return {row_sum, row_cnt, dl};
+}
+
+void grpo_scale_rows(Tensor dlogp, const Tensor& row_scale) {
+  c10::cuda::CUDAGuard guard(dlogp.device());
+  FERRL_CHECK(ferrl::grpo_scale_rows(dlogp.data_ptr<float>(), row_scale.data_ptr<float>(), dlogp.size(0), dlogp.size(1), stream()));
+}
+
+Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& kv_len, double scale,
+                   int64_t window, int64_t n_splits, const optional<Tensor>& block_table, int64_t page) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.dim() == 3, "decode_attn: q bf16 [B,Hq,D]");
+  TORCH_CHECK(kc.scalar_type() == at::kBFloat16 && kc.is_contiguous() && vc.is_contiguous() && kc.dim() == 4, "decode_attn: caches bf16 [B,S,Hkv,D]");
+  TORCH_CHECK(kv_len.scalar_type() == at::kInt && kv_len.is_contiguous(), "decode_attn: kv_len int32");
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::DecodeAttnArgs a{};
+  a.B = q.size(0); a.Hq = q.size(1); a.D = q.size(2); a.Hkv = kc.size(2);
+  a.q = q.data_ptr(); a.k = kc.data_ptr(); a.v = vc.data_ptr(); a.kv_len = kv_len.data_ptr<int>();
+  a.seq_stride = kc.stride(0); a.tok_stride = kc.stride(1);
+  if (block_table.has_value() && block_table->defined()) {
+    TORCH_CHECK(block_table->scalar_type() == at::kInt && block_table->is_contiguous(), "decode_attn: block_table int32");
+    a.block_table = block_table->data_ptr<int>(); a.bt_stride = block_table->size(1); a.page = page;
+  }
+  a.scale = scale; a.window = window;
+  a.n_splits = n_splits > 0 ? n_splits : ferrl::decode_attn_pick_splits(a.B, a.Hkv, kc.size(1), num_sms());
+  Tensor out = at::empty_like(q);
+  Tensor ws;
+  if (a.n_splits > 1) {
+    ws = at::empty({static_cast<long long>(ferrl::decode_attn_workspace_bytes(a.B, a.Hq, a.D, a.n_splits) / 4)},
+                   q.options().dtype(at::kFloat));
+    a.workspace = ws.data_ptr<float>();
+  }
+  a.out = out.data_ptr();
+  FERRL_CHECK(ferrl::decode_attn(a, stream()));
+  return out;
+}
+
+void fill_flash(ferrl::FlashArgs& a, const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
+                int64_t window, int64_t q_offset) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                  v.scalar_type() == at::kBFloat16, "flash: bf16 tensors");
+  TORCH_CHECK(q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "flash: [B,S,H,D] tensors");
+  TORCH_CHECK(q.stride(3) == 1 && k.stride(3) == 1 && v.stride(3) == 1 && q.stride(2) == q.size(3) &&
+                  k.stride(2) == k.size(3) && v.stride(2) == v.size(3), "flash: heads must be packed along the last dims");
+  a.q = q.data_ptr(); a.k = k.data_ptr(); a.v = v.data_ptr();
+  a.q_bs = q.stride(0); a.q_ts = q.stride(1); a.k_bs = k.stride(0); a.k_ts = k.stride(1);
+  a.v_bs = v.stride(0); a.v_ts = v.stride(1);
+  a.B = q.size(0); a.Sq = q.size(1); a.Sk = k.size(1); a.Hq = q.size(2); a.Hkv = k.size(2); a.D = q.size(3);
+  a.scale = scale; a.causal = causal; a.window = window; a.q_offset = q_offset;
+}
+
+std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
+                                     int64_t window, int64_t q_offset) {
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::FlashArgs a{};
+  fill_flash(a, q, k, v, scale, causal, window, q_offset);
+  Tensor o = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
+  Tensor lse = at::empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
+  a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
+  FERRL_CHECK(ferrl::flash_fwd(a, stream()));
+  return {o, lse};
+}
+
+std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
+                                             const Tensor& lse, const Tensor& d_o, double scale, bool causal,
+                                             int64_t window, int64_t q_offset) {
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::FlashArgs a{};
+  fill_flash(a, q, k, v, scale, causal, window, q_offset);
+  TORCH_CHECK(o.is_contiguous() && d_o.is_contiguous() && lse.is_contiguous(), "flash_bwd: o, do, lse contiguous");
+  Tensor dq = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
+  Tensor dk = at::empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
+  Tensor dv = at::empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
+  Tensor delta = at::empty({a.B, a.Hq, a.Sq}, lse.options());
+  a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
+  a.d_o = d_o.data_ptr(); a.do_bs = d_o.stride(0); a.do_ts = d_o.stride(1);
+  a.dq = dq.data_ptr(); a.dq_bs = dq.stride(0); a.dq_ts = dq.stride(1);
+  a.dk = dk.data_ptr(); a.dk_bs = dk.stride(0); a.dk_ts = dk.stride(1);
+  a.dv = dv.data_ptr(); a.dv_bs = dv.stride(0); a.dv_ts = dv.stride(1);
+  a.delta = delta.data_ptr<float>();
+  FERRL_CHECK(ferrl::flash_bwd(a, stream()));
+  return {dq, dk, dv};
+}
+
+std::tuple<Tensor, Tensor> logprob_rows(const Tensor& logits, const Tensor& targets, double temperature, double softcap) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && targets.scalar_type() == at::kLong &&
+                  targets.is_contiguous() && targets.numel() == logits.size(0), "logprob_rows: args");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor lp = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat)), lse = at::empty_like(lp);
+  FERRL_CHECK(ferrl::logprob_rows(dt(logits), logits.data_ptr(), logits.stride(0), reinterpret_cast<long long*>(targets.data_ptr<int64_t>()),
+                                  lp.data_ptr<float>(), lse.data_ptr<float>(), logits.size(0), logits.size(1),
+                                  temperature, softcap, stream()));
+  return {lp, lse};
+}
+
+void logprob_rows_bwd(Tensor logits, const Tensor& targets, const Tensor& lse, const Tensor& dlp, double temperature,
+                      double softcap) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(dlp.scalar_type() == at::kFloat && dlp.is_contiguous() && lse.is_contiguous(), "logprob_rows_bwd: args");
+  FERRL_CHECK(ferrl::logprob_rows_bwd(dt(logits), logits.data_ptr(), logits.stride(0), reinterpret_cast<long long*>(targets.data_ptr<int64_t>()),
+                                      lse.data_ptr<float>(), dlp.data_ptr<float>(), logits.size(0), logits.size(1),
+                                      temperature, softcap, stream()));
+}
+
+std::tuple<Tensor, Tensor> sample_rows(const Tensor& logits, const Tensor& global_rows, int64_t seed,
+                                       const optional<Tensor>& draw_dev, int64_t draw, double temperature, double top_p) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && global_rows.scalar_type() == at::kLong &&
+                  global_rows.is_contiguous() && global_rows.numel() == logits.size(0), "sample_rows: args");
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor tok = at::empty({logits.size(0)}, logits.options().dtype(at::kLong));
+  Tensor lp = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  const int* dd = nullptr;
+  if (draw_dev.has_value() && draw_dev->defined()) {
+    TORCH_CHECK(draw_dev->scalar_type() == at::kInt, "sample_rows: draw counter int32");
+    dd = draw_dev->data_ptr<int>();
+  }
+  FERRL_CHECK(ferrl::sample_rows(dt(logits), logits.data_ptr(), logits.stride(0), reinterpret_cast<long long*>(global_rows.data_ptr<int64_t>()),
+                                 static_cast<unsigned long long>(seed), dd, draw, reinterpret_cast<long long*>(tok.data_ptr<int64_t>()),
+                                 lp.data_ptr<float>(), logits.size(0), logits.size(1), temperature, top_p, stream()));
+  return {tok, lp};
+}
+
+int64_t launches() { return ferrl::launch_count(); }
+void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
+
+}  // namespace
+
+TORCH_LIBRARY(ferrl_b200, m) {
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn) -> Tensor", &gemm);
+  m.def("kernel_status() -> int", &kernel_status);
+  m.def("reset_status() -> ()", &reset_status);
+  m.def("rmsnorm(Tensor x, Tensor? res, Tensor? w, Tensor? gate, float eps, bool zc) -> (Tensor, Tensor)", &rmsnorm);
+  m.def("rmsnorm_bwd(Tensor x, Tensor? w, Tensor dy, float eps, bool zc) -> Tensor", &rmsnorm_bwd);
+  m.def("qk_norm_rope_fwd(Tensor q, Tensor k, Tensor? qw, Tensor? kw, Tensor cos, Tensor sin, Tensor pos, int pos_div, float eps, bool zc) -> (Tensor, Tensor)", &qk_norm_rope_fwd);
+  m.def("qk_norm_rope_bwd(Tensor q, Tensor k, Tensor? qw, Tensor? kw, Tensor cos, Tensor sin, Tensor pos, int pos_div, float eps, bool zc, Tensor dq, Tensor dk, Tensor(a!) dq_in, Tensor(b!) dk_in) -> ()", &qk_norm_rope_bwd);
+  m.def("kv_append(Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len) -> ()", &kv_append);
+  m.def("glu_fwd(Tensor gu, int act) -> Tensor", &glu_fwd);
+  m.def("glu_bwd(Tensor gu, Tensor dout, int act) -> Tensor", &glu_bwd);
+  m.def("embedding(Tensor ids, Tensor table, float scale) -> Tensor", &embedding);
+  m.def("lora_merge(Tensor w, Tensor a, Tensor b) -> Tensor", &lora_merge);
+  m.def("adamw_step(Tensor[] params, Tensor[] grads, Tensor[] m, Tensor[] v, float lr, float b1, float b2, float eps, float wd, int step, float max_norm, float pre_scale, bool compute_norm) -> Tensor", &adamw_step);
+  m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
+  m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
+  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page) -> Tensor", &decode_attn);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
+  m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);
+  m.def("sample_rows(Tensor logits, Tensor global_rows, int seed, Tensor? draw_dev, int draw, float temperature, float top_p) -> (Tensor, Tensor)", &sample_rows);
+  m.def("launches() -> int", &launches);
+  m.def("add_launches(int n) -> ()", &add_launches);
+}

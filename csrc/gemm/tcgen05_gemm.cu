@@ -1,0 +1,475 @@
+// bf16 GEMM core for sm_100a:  C[M,N] = A[M,K] * B[N,K]^T  (+ A2[M,K2] * B2[N,K2]^T) (+ R[M,N])
+//
+// * tcgen05.mma (cta_group::1, kind::f16, M=128, N=BN, K=16 per instruction) issued by one
+//   elected thread; fp32 accumulators live in TMEM, two of them so the epilogue of tile i
+//   overlaps the main loop of tile i+1.
+// * operands are staged in shared memory by TMA (cp.async.bulk.tensor.2d, 128B swizzle,
+//   no cluster multicast: this kernel runs inside multi-GPU jobs) through an
+//   mbarrier-driven ring of STAGES buffers.
+// * the optional second operand pair (A2, B2) is the LoRA side path: A2 = x*A_stack^T
+//   ([M, n*r]) and B2 = s*B_blockdiag ([N, n*r]) are consumed as extra k-tiles of the same
+//   accumulator, so the low-rank delta costs no extra pass over the output.
+// * persistent: one CTA per SM walks a grouped-M raster so concurrently running CTAs share
+//   A and B tiles in L2.
+// * warp roles: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner, warps 2..5 =
+//   epilogue (tcgen05.ld -> convert -> 16-byte global stores, optional residual add).
+// * every mbarrier wait is bounded: on expiry the role records a status code in global
+//   memory, raises a CTA-wide abort flag, and all roles fall through to the common exit
+//   where TMEM is released.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../api.h"
+#include "../common.cuh"
+
+namespace ferrl {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;           // 64 bf16 = 128 bytes = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr int NUM_THREADS = 192;
+constexpr uint64_t WAIT_LIMIT_NS = 2000000000ull;  // 2 s
+
+struct GemmParams {
+  int M, N, K, K2;
+  void* out;            // bf16 or fp32, row stride ldo elements
+  const __nv_bfloat16* residual;  // optional [M, ldr]
+  long long ldo, ldr;
+  int* status;          // device status word
+  int group_m;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait. Returns false when the CTA is aborting or the limit expired (and then
+// records `code`).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                          int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, kStatusOk, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+      : "memory");
+}
+
+// K-major, 128B-swizzled operand tile: rows are 128 bytes, 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);   // start address
+  d |= static_cast<uint64_t>(1) << 16;                      // leading byte offset (unused for swizzled K-major)
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;              // stride byte offset
+  d |= static_cast<uint64_t>(1) << 46;                      // descriptor version (Blackwell)
+  d |= static_cast<uint64_t>(2) << 61;                      // SWIZZLE_128B
+  return d;
+}
+
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+  return (1u << 4)                        // D format F32
+         | (1u << 7)                      // A format BF16
+         | (1u << 10)                     // B format BF16
+         | (static_cast<uint32_t>(n >> 3) << 17)
+         | (static_cast<uint32_t>(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <int BN> struct Cfg {
+  static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+  int per_group = group_m * n_tiles;
+  int g = tile / per_group;
+  int first_m = g * group_m;
+  int gsz = min(group_m, m_tiles - first_m);
+  int in = tile - g * per_group;
+  mi = first_m + in % gsz;
+  ni = in / gsz;
+}
+
+// OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
+template <int BN, bool OUT_F32, bool HAS_RES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;                    // [STAGES]
+  uint64_t* empty = bars + C::STAGES;       // [STAGES]
+  uint64_t* acc_full = bars + 2 * C::STAGES;   // [2]
+  uint64_t* acc_empty = acc_full + 2;          // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int m_tiles = (p.M + BM - 1) / BM;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int kb1 = (p.K + BK - 1) / BK;
+  const int kb2 = (p.K2 + BK - 1) / BK;
+  const int kb_total = kb1 + kb2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int mi, ni;
+        tile_coords(tile, m_tiles, n_tiles, p.group_m, mi, ni);
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          uint8_t* sb = sa + BM * BK * 2;
+          mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+          if (kb < kb1) {
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, mi * BM);
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, ni * BN);
+          } else {
+            tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, mi * BM);
+            tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, ni * BN);
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before the CTA's shared memory goes away
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) break;
+        acc_phase[acc] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + BM * BK * 2;
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advance 32 bytes (16 bf16) inside the 128-byte swizzle row: +2 in 16-byte units
+            umma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);  // frees the smem stage when these MMAs retire
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;  // TMEM lane quarter this warp may read
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      int mi, ni;
+      tile_coords(tile, m_tiles, n_tiles, p.group_m, mi, ni);
+      const int acc = it & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue)) break;
+      acc_phase[acc] ^= 1;
+      tc_fence_after();
+      const int row = mi * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c, r);
+        tmem_ld_wait();
+        const int col = ni * BN + c;
+        if (row_ok && col < p.N) {
+          const int ncols = min(32, p.N - col);
+          if (HAS_RES) {
+            const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 x = reinterpret_cast<const uint4*>(rp)[v];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = __bfloat1622float2(h[e]);
+                  r[v * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e]) + f.x);
+                  r[v * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e + 1]) + f.y);
+                }
+              }
+            } else {
+              for (int e = 0; e < ncols; ++e)
+                r[e] = __float_as_uint(__uint_as_float(r[e]) + __bfloat162float(rp[e]));
+            }
+          }
+          if (OUT_F32) {
+            float* op = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(op)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+              for (int e = 0; e < ncols; ++e) op[e] = __uint_as_float(r[e]);
+            }
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 x;
+                uint32_t* xp = reinterpret_cast<uint32_t*>(&x);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
+                                                          __uint_as_float(r[v * 8 + 2 * e + 1]));
+                  xp[e] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                reinterpret_cast<uint4*>(op)[v] = x;
+              }
+            } else {
+              for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) != cudaSuccess || !p)
+      return nullptr;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 2-D bf16 row-major [rows, cols] with row stride ld (elements); box = [box_rows, 64 cols].
+bool make_map(CUtensorMap* map, const void* ptr, long long rows, long long cols, long long ld, int box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(BK), static_cast<cuuint32_t>(box_rows)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+template <int BN, bool OUT_F32, bool HAS_RES>
+const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
+  using C = Cfg<BN>;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  if (!make_map(&tmA, a.A, a.M, a.K, a.lda, BM)) return "cuTensorMapEncodeTiled failed for A";
+  if (!make_map(&tmB, a.B, a.N, a.K, a.ldb, BN)) return "cuTensorMapEncodeTiled failed for B";
+  if (a.K2 > 0) {
+    if (!make_map(&tmA2, a.A2, a.M, a.K2, a.lda2, BM)) return "cuTensorMapEncodeTiled failed for A2";
+    if (!make_map(&tmB2, a.B2, a.N, a.K2, a.ldb2, BN)) return "cuTensorMapEncodeTiled failed for B2";
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
+  GemmParams p;
+  p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
+  p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 16;
+  auto kern = gemm_kernel<BN, OUT_F32, HAS_RES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic smem) failed";
+    attr_set = true;
+  }
+  int m_tiles = (a.M + BM - 1) / BM, n_tiles = (a.N + BN - 1) / BN;
+  int tiles = m_tiles * n_tiles;
+  int grid = tiles < a.num_sms ? tiles : a.num_sms;
+  if (grid < 1) return nullptr;
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
+}
+
+template <int BN>
+const char* launch_flags(const GemmArgs& a, cudaStream_t stream) {
+  if (a.out_f32) return a.residual ? launch_bn<BN, true, true>(a, stream) : launch_bn<BN, true, false>(a, stream);
+  return a.residual ? launch_bn<BN, false, true>(a, stream) : launch_bn<BN, false, false>(a, stream);
+}
+
+}  // namespace
+
+int gemm_pick_bn(int M, int N, int num_sms) {
+  // Large problems take the widest tile; when that leaves SMs idle shrink BN so that the
+  // tile count approaches the SM count (decode-shaped GEMMs are bandwidth bound).
+  int m_tiles = (M + BM - 1) / BM;
+  const int cands[4] = {256, 128, 64, 32};
+  for (int i = 0; i < 4; ++i) {
+    int bn = cands[i];
+    if (bn > 32 && N < bn) continue;
+    long long tiles = static_cast<long long>(m_tiles) * ((N + bn - 1) / bn);
+    if (tiles >= num_sms || bn == 32) return bn;
+  }
+  return 32;
+}
+
+const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
+  if (a.M <= 0 || a.N <= 0) return nullptr;
+  if (a.K <= 0) return "K must be > 0";
+  if ((a.K % 8) || (a.lda % 8) || (a.ldb % 8)) return "K and operand row strides must be multiples of 8 elements";
+  if (a.K2 > 0 && ((a.K2 % 8) || (a.lda2 % 8) || (a.ldb2 % 8)))
+    return "K2 and side-operand row strides must be multiples of 8 elements";
+  if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
+      (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
+    return "operand base addresses must be 16-byte aligned";
+  int bn = a.force_bn > 0 ? a.force_bn : gemm_pick_bn(a.M, a.N, a.num_sms);
+  switch (bn) {
+    case 256: return launch_flags<256>(a, stream);
+    case 128: return launch_flags<128>(a, stream);
+    case 64: return launch_flags<64>(a, stream);
+    case 32: return launch_flags<32>(a, stream);
+    default: return "unsupported BN";
+  }
+}
+
+}  // namespace ferrl

@@ -1,0 +1,237 @@
+// KV-cached decode attention for sm_100a (bf16 cache, fp32 math), GQA-native.
+//
+// One CTA handles one (sequence, kv-head, kv-split): the `rep = Hq/Hkv` query heads that share
+// the kv head are processed together, so every K and V row is read from HBM exactly once per
+// step (the reference repeats the whole cache per query head and re-allocates it per token).
+// K rows are consumed lane-per-key (each lane streams one 2*D-byte row with 16-byte loads, q is
+// broadcast from shared memory); V rows are consumed warp-per-key (coalesced) with the key's
+// probabilities broadcast by shuffle.  Online softmax per warp, warps merged through shared
+// memory, kv-splits merged by a second tiny kernel through a caller-provided workspace.
+// Supports a sliding window (keys older than `window` are skipped without being read) and a
+// page table (`block_table[b, j / page]` gives the physical page of logical key j).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../api.h"
+#include "../common.cuh"
+
+namespace ferrl {
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int MAX_REP = 8;
+constexpr int MAX_DPL = 8;  // dims per lane: D <= 256
+
+__global__ void __launch_bounds__(WARPS * 32)
+decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                   const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
+                   const int* __restrict__ block_table, int bt_stride, int page, __nv_bfloat16* __restrict__ out,
+                   float* __restrict__ ws, int Hq, int Hkv, int D, long long seq_stride, long long tok_stride,
+                   float scale, int window, int n_splits) {
+  extern __shared__ float sm[];
+  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int rep = Hq / Hkv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int dpl = (D + 31) / 32;
+  float* q_s = sm;                               // [rep][D]
+  float* m_s = q_s + rep * D;                    // [WARPS][rep]
+  float* l_s = m_s + WARPS * rep;                // [WARPS][rep]
+  float* o_s = l_s + WARPS * rep;                // [WARPS][rep][D]
+
+  for (int i = threadIdx.x; i < rep * D; i += blockDim.x) {
+    int r = i / D, d = i - r * D;
+    q_s[i] = __bfloat162float(q[(static_cast<long long>(b) * Hq + hk * rep + r) * D + d]) * scale;
+  }
+  __syncthreads();
+
+  const int len = kv_len[b];
+  int lo = (window > 0 && len > window) ? len - window : 0;
+  // split the live range [lo, len) evenly
+  const int span = len - lo;
+  const int per = (span + n_splits - 1) / n_splits;
+  const int s0 = lo + split * per;
+  const int s1 = min(len, s0 + per);
+
+  float m_run[MAX_REP], l_run[MAX_REP], o_acc[MAX_REP][MAX_DPL];
+#pragma unroll
+  for (int r = 0; r < MAX_REP; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.f;
+#pragma unroll
+    for (int i = 0; i < MAX_DPL; ++i) o_acc[r][i] = 0.f;
+  }
+
+  for (int base = s0 + warp * 32; base < s1; base += WARPS * 32) {
+    const int j = base + lane;
+    const bool live = j < s1;
+    long long row = 0;
+    if (live) {
+      if (block_table) {
+        int pg = block_table[static_cast<long long>(b) * bt_stride + j / page];
+        row = (static_cast<long long>(pg) * page + (j % page)) * tok_stride + hk * D;
+      } else {
+        row = static_cast<long long>(b) * seq_stride + static_cast<long long>(j) * tok_stride + hk * D;
+      }
+    }
+    float sc[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; ++r) sc[r] = 0.f;
+    if (live) {
+      const uint4* kp = reinterpret_cast<const uint4*>(kc + row);
+      for (int d8 = 0; d8 < D / 8; ++d8) {
+        uint4 x = kp[d8];
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+        float kf[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float2 f = __bfloat1622float2(h[e]);
+          kf[2 * e] = f.x;
+          kf[2 * e + 1] = f.y;
+        }
+#pragma unroll
+        for (int r = 0; r < MAX_REP; ++r) {
+          if (r < rep) {
+            const float* qr = q_s + r * D + d8 * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sc[r] += kf[e] * qr[e];
+          }
+        }
+      }
+    }
+    // online softmax update for this tile of up to 32 keys
+    float p[MAX_REP];
+#pragma unroll
+    for (int r = 0; r < MAX_REP; ++r) {
+      p[r] = 0.f;
+      if (r < rep) {
+        float s = live ? sc[r] : -INFINITY;
+        float tmax = warp_max(s);
+        float m_new = fmaxf(m_run[r], tmax);
+        float corr = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - m_new);
+        p[r] = live ? __expf(s - m_new) : 0.f;
+        float psum = warp_sum(p[r]);
+        l_run[r] = l_run[r] * corr + psum;
+        m_run[r] = m_new;
+#pragma unroll
+        for (int i = 0; i < MAX_DPL; ++i) o_acc[r][i] *= corr;
+      }
+    }
+    const int nk = min(32, s1 - base);
+    for (int kk = 0; kk < nk; ++kk) {
+      const long long vrow = __shfl_sync(0xffffffffu, row, kk);
+      float vv[MAX_DPL];
+#pragma unroll
+      for (int i = 0; i < MAX_DPL; ++i) {
+        int d = lane + 32 * i;
+        vv[i] = (i < dpl && d < D) ? __bfloat162float(vc[vrow + d]) : 0.f;
+      }
+#pragma unroll
+      for (int r = 0; r < MAX_REP; ++r) {
+        if (r < rep) {
+          float pj = __shfl_sync(0xffffffffu, p[r], kk);
+#pragma unroll
+          for (int i = 0; i < MAX_DPL; ++i) o_acc[r][i] += pj * vv[i];
+        }
+      }
+    }
+  }
+
+  // merge warps
+  for (int r = 0; r < rep; ++r) {
+    if (lane == 0) {
+      m_s[warp * rep + r] = m_run[r];
+      l_s[warp * rep + r] = l_run[r];
+    }
+    for (int i = 0; i < dpl; ++i) {
+      int d = lane + 32 * i;
+      if (d < D) o_s[(warp * rep + r) * D + d] = o_acc[r][i];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < rep * D; i += blockDim.x) {
+    int r = i / D, d = i - r * D;
+    float m = -INFINITY;
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, m_s[w * rep + r]);
+    float l = 0.f, o = 0.f;
+    for (int w = 0; w < WARPS; ++w) {
+      float mw = m_s[w * rep + r];
+      float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+      l += l_s[w * rep + r] * c;
+      o += o_s[(w * rep + r) * D + d] * c;
+    }
+    const long long head = static_cast<long long>(b) * Hq + hk * rep + r;
+    if (n_splits == 1) {
+      out[head * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    } else {
+      float* w_ = ws + (head * n_splits + split) * (D + 2);
+      w_[d] = o;
+      if (d == 0) {
+        w_[D] = m;
+        w_[D + 1] = l;
+      }
+    }
+  }
+}
+
+__global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
+                                      int n_splits) {
+  const long long head = blockIdx.x;
+  const float* base = ws + head * n_splits * (D + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) m = fmaxf(m, base[s * (D + 2) + D]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float l = 0.f, o = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      float ms = base[s * (D + 2) + D];
+      float c = (ms == -INFINITY) ? 0.f : __expf(ms - m);
+      l += base[s * (D + 2) + D + 1] * c;
+      o += base[s * (D + 2) + d] * c;
+    }
+    out[head * D + d] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+  }
+}
+
+}  // namespace
+
+size_t decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits) {
+  return n_splits <= 1 ? 0 : static_cast<size_t>(B) * Hq * n_splits * (D + 2) * sizeof(float);
+}
+
+int decode_attn_pick_splits(int B, int Hkv, int max_len, int num_sms) {
+  long long ctas = static_cast<long long>(B) * Hkv;
+  int s = 1;
+  while (ctas * s < 2LL * num_sms && s < 16 && max_len / (s * 2) >= 256) s *= 2;
+  return s;
+}
+
+const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
+  if (a.B == 0) return nullptr;
+  if (a.Hq % a.Hkv) return "decode_attn: Hq must be a multiple of Hkv";
+  const int rep = a.Hq / a.Hkv;
+  if (rep > MAX_REP) return "decode_attn: more than 8 query heads per kv head";
+  if (a.D % 8 || a.D > 256) return "decode_attn: head_dim must be a multiple of 8 and <= 256";
+  if (a.n_splits > 1 && !a.workspace) return "decode_attn: workspace required for split-kv";
+  size_t smem = (static_cast<size_t>(rep) * a.D + 2 * WARPS * rep + static_cast<size_t>(WARPS) * rep * a.D) * 4;
+  auto kern = decode_attn_kernel;
+  if (smem > 48 * 1024) {
+    static bool set = false;
+    if (!set) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+      set = true;
+    }
+  }
+  dim3 grid(a.B, a.Hkv, a.n_splits < 1 ? 1 : a.n_splits);
+  kern<<<grid, WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),
+                                      static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride,
+                                      a.page, static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.D,
+                                      a.seq_stride, a.tok_stride, a.scale, a.window, grid.z);
+  count_launch();
+  if (grid.z > 1) {
+    decode_combine_kernel<<<a.B * a.Hq, 128, 0, s>>>(a.workspace, static_cast<__nv_bfloat16*>(a.out), a.D, grid.z);
+    count_launch();
+  }
+  return cudaGetLastError() == cudaSuccess ? nullptr : "decode_attn launch failed";
+}
+
+}  // namespace ferrl

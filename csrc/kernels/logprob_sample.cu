@@ -1,0 +1,265 @@
+// Vocabulary-wide row kernels for sm_100a.
+//
+//   logprob_rows      per row: log_softmax(f(logit)/T)[target] with an online (single read) max/sum;
+//                     f = identity or cap*tanh(x/cap); keeps the row's log-sum-exp for backward
+//   logprob_rows_bwd  overwrites the logits row in place with d(loss)/d(logit)
+//                     = dlp * (onehot - softmax) * f'(x) / T, ready to feed the dX GEMM
+//   sample_rows       temperature + nucleus (top-p) sampling, one CTA per row, counter RNG keyed by
+//                     (seed, global row, draw); returns token and behaviour log-prob
+//
+// sample_rows does all probability mass arithmetic in 2^-40 fixed point with integer atomics, so
+// the nucleus threshold and the drawn token do not depend on the order in which threads add
+// (bit-reproducible across runs).  The nucleus threshold is found with a 4-pass radix select over
+// the float bit pattern of the unnormalised probabilities - no sort, no host copy of the row.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../api.h"
+#include "../common.cuh"
+
+namespace ferrl {
+namespace {
+
+__device__ __forceinline__ float capf(float x, float cap) { return cap > 0.f ? cap * tanhf(x / cap) : x; }
+
+template <typename T>
+__global__ void logprob_rows_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                                    float* __restrict__ lp, float* __restrict__ lse, int V, float inv_t, float cap) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* x = logits + row * ld;
+  float m = -INFINITY, s = 0.f;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float z = capf(to_f(x[i]), cap) * inv_t;
+    if (z > m) {
+      s = s * __expf(m - z) + 1.f;
+      m = z;
+    } else {
+      s += __expf(z - m);
+    }
+  }
+  float gm = block_max(m, red);
+  float part = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  float tot = block_sum(part, red);
+  if (threadIdx.x == 0) {
+    float l = gm + logf(tot);
+    long long t = targets[row];
+    float zt = (t >= 0 && t < V) ? capf(to_f(x[t]), cap) * inv_t : -INFINITY;
+    lp[row] = zt - l;
+    lse[row] = l;
+  }
+}
+
+template <typename T>
+__global__ void logprob_rows_bwd_kernel(T* __restrict__ logits, long long ld, const long long* __restrict__ targets,
+                                        const float* __restrict__ lse, const float* __restrict__ dlp, int V,
+                                        float inv_t, float cap) {
+  const long long row = blockIdx.x;
+  T* x = logits + row * ld;
+  const float l = lse[row], g = dlp[row];
+  const long long t = targets[row];
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float raw = to_f(x[i]);
+    float y = capf(raw, cap);
+    float p = __expf(y * inv_t - l);
+    float d = g * ((i == t ? 1.f : 0.f) - p) * inv_t;
+    if (cap > 0.f) {
+      float th = y / cap;
+      d *= (1.f - th * th);
+    }
+    x[i] = from_f<T>(d);
+  }
+}
+
+__device__ __forceinline__ uint64_t mix64(uint64_t z) {
+  z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+  z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+  return z ^ (z >> 31);
+}
+
+constexpr int ST = 1024;  // threads per row
+
+template <typename T>
+__global__ void __launch_bounds__(ST)
+sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ global_rows,
+                   uint64_t seed, const int* __restrict__ draw_dev, int draw_host, long long* __restrict__ tok_out,
+                   float* __restrict__ lp_out, int V, float inv_t, float top_p) {
+  __shared__ float red[32];
+  __shared__ unsigned long long hist[256];
+  __shared__ unsigned long long scan[ST];
+  __shared__ unsigned long long sh_u64[4];
+  __shared__ unsigned int sh_u32[2];
+  const long long row = blockIdx.x;
+  const T* x = logits + row * ld;
+  const int tid = threadIdx.x;
+  const float FIX = 1099511627776.f;  // 2^40
+
+  float m = -INFINITY;
+  for (int i = tid; i < V; i += ST) m = fmaxf(m, to_f(x[i]));
+  m = block_max(m, red);
+
+  auto e_of = [&](int i) -> float { return __expf((to_f(x[i]) - m) * inv_t); };
+  auto fix_of = [&](float e) -> unsigned long long { return static_cast<unsigned long long>(e * FIX); };
+
+  // total mass
+  if (tid == 0) sh_u64[0] = 0;
+  __syncthreads();
+  {
+    unsigned long long part = 0;
+    for (int i = tid; i < V; i += ST) part += fix_of(e_of(i));
+    // warp-level integer reduction, then one atomic per warp
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((tid & 31) == 0) atomicAdd(&sh_u64[0], part);
+  }
+  __syncthreads();
+  const unsigned long long Z = sh_u64[0];
+
+  unsigned int thresh_key = 0;          // keep everything
+  unsigned long long kept_mass = Z;
+  if (top_p > 0.f && top_p < 1.f) {
+    const unsigned long long target =
+        static_cast<unsigned long long>(static_cast<double>(Z) * static_cast<double>(top_p));
+    unsigned int prefix = 0;
+    unsigned long long above = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+      const int shift = 24 - 8 * pass;
+      for (int i = tid; i < 256; i += ST) hist[i] = 0;
+      __syncthreads();
+      for (int i = tid; i < V; i += ST) {
+        float e = e_of(i);
+        unsigned int key = __float_as_uint(e);
+        if (pass == 0 || (key >> (shift + 8)) == prefix) {
+          unsigned long long f = fix_of(e);
+          if (f) atomicAdd(&hist[(key >> shift) & 0xFF], f);
+        }
+      }
+      __syncthreads();
+      if (tid == 0) {
+        unsigned long long cum = above;
+        int b = 255;
+        for (; b > 0; --b) {
+          if (hist[b] > 0 && cum + hist[b] >= target) break;
+          cum += hist[b];
+        }
+        sh_u64[1] = cum;                 // mass strictly above the chosen bucket
+        sh_u64[2] = cum + hist[b];       // mass of chosen bucket and above
+        sh_u32[0] = (prefix << 8) | static_cast<unsigned int>(b);
+      }
+      __syncthreads();
+      above = sh_u64[1];
+      kept_mass = sh_u64[2];
+      prefix = sh_u32[0];
+      __syncthreads();
+    }
+    thresh_key = prefix;
+  }
+
+  // draw
+  const int draw = draw_dev ? *draw_dev : draw_host;
+  const uint64_t key = mix64(seed + static_cast<uint64_t>(global_rows[row]) * 0x9E3779B97F4A7C15ull);
+  const uint64_t bits = mix64(key + static_cast<uint64_t>(draw + 1) * 0x9E3779B97F4A7C15ull);
+  const unsigned long long u24 = bits >> 40;
+  const unsigned long long target = (kept_mass >> 24) * u24 + (((kept_mass & 0xFFFFFFull) * u24) >> 24);
+
+  // contiguous chunk per thread, block scan of chunk masses, then the owning thread walks its chunk
+  const int chunk = (V + ST - 1) / ST;
+  const int c0 = tid * chunk, c1 = min(V, c0 + chunk);
+  unsigned long long mine = 0;
+  for (int i = c0; i < c1; ++i) {
+    float e = e_of(i);
+    if (__float_as_uint(e) >= thresh_key) mine += fix_of(e);
+  }
+  scan[tid] = mine;
+  __syncthreads();
+  // Hillis-Steele inclusive scan (1024 entries, 10 steps)
+  for (int off = 1; off < ST; off <<= 1) {
+    unsigned long long v = (tid >= off) ? scan[tid - off] : 0;
+    __syncthreads();
+    scan[tid] += v;
+    __syncthreads();
+  }
+  const unsigned long long incl = scan[tid], excl = incl - mine;
+  if (tid == 0) sh_u32[1] = 0xFFFFFFFFu;
+  __syncthreads();
+  if (mine > 0 && target >= excl && target < incl) {
+    unsigned long long cum = excl;
+    int pick = c1 - 1;
+    for (int i = c0; i < c1; ++i) {
+      float e = e_of(i);
+      if (__float_as_uint(e) >= thresh_key) {
+        cum += fix_of(e);
+        if (cum > target) {
+          pick = i;
+          break;
+        }
+      }
+    }
+    sh_u32[1] = static_cast<unsigned int>(pick);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    unsigned int pick = sh_u32[1];
+    if (pick == 0xFFFFFFFFu) {
+      // degenerate row (all mass rounded to zero): fall back to the arg-max element
+      pick = 0;
+      float best = -INFINITY;
+      for (int i = 0; i < V; ++i) {
+        float v = to_f(x[i]);
+        if (v > best) { best = v; pick = i; }
+      }
+    }
+    tok_out[row] = pick;
+    float le = (to_f(x[pick]) - m) * inv_t;
+    float lmass = logf(static_cast<float>(static_cast<double>(kept_mass) / 1099511627776.0));
+    lp_out[row] = fminf(le - lmass, 0.f);
+  }
+}
+
+}  // namespace
+
+const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,
+                         long long rows, int V, float temperature, float softcap, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  float inv_t = 1.f / temperature;
+  if (dtype == kF32)
+    logprob_rows_kernel<float><<<static_cast<unsigned>(rows), 1024, 0, s>>>(static_cast<const float*>(logits), ld,
+                                                                           targets, lp, lse, V, inv_t, softcap);
+  else
+    logprob_rows_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 1024, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(logits), ld, targets, lp, lse, V, inv_t, softcap);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "logprob_rows launch failed";
+}
+
+const char* logprob_rows_bwd(int dtype, void* logits, long long ld, const long long* targets, const float* lse,
+                             const float* dlp, long long rows, int V, float temperature, float softcap,
+                             cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  float inv_t = 1.f / temperature;
+  if (dtype == kF32)
+    logprob_rows_bwd_kernel<float><<<static_cast<unsigned>(rows), 1024, 0, s>>>(static_cast<float*>(logits), ld,
+                                                                               targets, lse, dlp, V, inv_t, softcap);
+  else
+    logprob_rows_bwd_kernel<__nv_bfloat16><<<static_cast<unsigned>(rows), 1024, 0, s>>>(
+        static_cast<__nv_bfloat16*>(logits), ld, targets, lse, dlp, V, inv_t, softcap);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "logprob_rows_bwd launch failed";
+}
+
+const char* sample_rows(int dtype, const void* logits, long long ld, const long long* global_rows,
+                        unsigned long long seed, const int* draw_dev, int draw_host, long long* tok_out, float* lp_out,
+                        int rows, int V, float temperature, float top_p, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  float inv_t = 1.f / temperature;
+  if (dtype == kF32)
+    sample_rows_kernel<float><<<rows, ST, 0, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
+                                                  draw_host, tok_out, lp_out, V, inv_t, top_p);
+  else
+    sample_rows_kernel<__nv_bfloat16><<<rows, ST, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
+                                                          seed, draw_dev, draw_host, tok_out, lp_out, V, inv_t, top_p);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "sample_rows launch failed";
+}
+
+}  // namespace ferrl

@@ -1,0 +1,286 @@
+// RMSNorm family and RoPE for sm_100a: bandwidth-bound row kernels.
+//
+//   rmsnorm            y = x * rsqrt(mean(x^2)+eps) * w        (w or 1+w)
+//   add_rmsnorm        h = x + res (written back), y = rmsnorm(h)
+//   rmsnorm_gated      y = rmsnorm(x) * w * silu(gate)
+//   rmsnorm_bwd        dx for a frozen weight (LoRA training never needs dw)
+//   qk_norm_rope       per-head RMSNorm of q and k fused with rotate-half RoPE (full or
+//                      partial rotary width), reading the fused qkv GEMM output in place
+//                      and writing contiguous q / k; optional direct write of k, v into a
+//                      KV cache row at each sequence's current length (decode)
+//   qk_norm_rope_bwd   inverse rotation + norm backward
+//
+// One row per CTA (hidden-size rows) or one head-row per warp (head_dim rows); 16-byte
+// vector loads; fp32 math; each element is read once and written once.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../api.h"
+#include "../common.cuh"
+
+namespace ferrl {
+namespace {
+
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
+                               const T* __restrict__ gate, T* __restrict__ y, T* __restrict__ h_out, int H, float eps,
+                               int zero_centered) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * H;
+  const T* rr = res ? res + row * H : nullptr;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = to_f(xr[i]);
+    if (rr) {
+      v += to_f(rr[i]);
+      // round through the storage type so the norm sees exactly what the residual stream holds
+      T hv = from_f<T>(v);
+      h_out[row * H + i] = hv;
+      v = to_f(hv);
+    }
+    ss += v * v;
+  }
+  float tot = block_sum(ss, red);
+  float rstd = rsqrtf(tot / H + eps);
+  const T* src = rr ? h_out + row * H : xr;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = to_f(src[i]) * rstd;
+    if (w) {
+      float wv = to_f(w[i]);
+      v *= zero_centered ? (1.f + wv) : wv;
+    }
+    if (gate) {
+      float g = to_f(gate[row * H + i]);
+      v *= g / (1.f + __expf(-g));
+    }
+    y[row * H + i] = from_f<T>(v);
+  }
+}
+
+// dx_i = rstd * (w_i dy_i - x_i * rstd^2 * mean_j(w_j dy_j x_j))
+template <typename T>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict__ w, const T* __restrict__ dy,
+                                   T* __restrict__ dx, int H, float eps, int zero_centered) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* xr = x + row * H;
+  const T* gr = dy + row * H;
+  float ss = 0.f, dot = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = to_f(xr[i]);
+    float wv = w ? to_f(w[i]) : 1.f;
+    if (zero_centered) wv += 1.f;
+    ss += v * v;
+    dot += v * wv * to_f(gr[i]);
+  }
+  float tot = block_sum(ss, red);
+  float d = block_sum(dot, red);
+  float rstd = rsqrtf(tot / H + eps);
+  float c = d * rstd * rstd / H;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = to_f(xr[i]);
+    float wv = w ? to_f(w[i]) : 1.f;
+    if (zero_centered) wv += 1.f;
+    dx[row * H + i] = from_f<T>(rstd * (wv * to_f(gr[i]) - v * c));
+  }
+}
+
+// One warp per (token, head). D <= 512, D even. rot = 2*half <= D.
+template <typename T, bool BWD>
+__global__ void qk_norm_rope_kernel(const T* __restrict__ q_in, long long ld_q, const T* __restrict__ k_in,
+                                    long long ld_k, long long ld_dq, long long ld_dk, const T* __restrict__ qw, const T* __restrict__ kw,
+                                    const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                    const long long* __restrict__ pos, const int* __restrict__ pos32, int pos_div,
+                                    T* __restrict__ q_out, T* __restrict__ k_out, const T* __restrict__ dq,
+                                    const T* __restrict__ dk, long long n_tok, int Hq, int Hkv, int D, int half,
+                                    float eps, int zero_centered) {
+  const int warps_per_block = blockDim.x >> 5;
+  const long long wid = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + Hkv;
+  if (wid >= n_tok * heads) return;
+  const long long tok = wid / heads;
+  const int hh = static_cast<int>(wid % heads);
+  const bool is_q = hh < Hq;
+  const int h = is_q ? hh : hh - Hq;
+  const T* src = (is_q ? q_in + tok * ld_q : k_in + tok * ld_k) + h * D;
+  const T* wv = is_q ? qw : kw;
+  const long long p = pos ? pos[tok / pos_div] : static_cast<long long>(pos32[tok / pos_div]);
+  const float* cr = cos_t + p * half;
+  const float* sr = sin_t + p * half;
+  const int rot = 2 * half;
+  constexpr int MAXE = 16;  // D <= 512
+  float xv[MAXE];
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < MAXE; ++e) {
+    int i = lane + 32 * e;
+    xv[e] = (i < D) ? to_f(src[i]) : 0.f;
+    ss += xv[e] * xv[e];
+  }
+  float rstd = 1.f;
+  if (wv) {
+    ss = warp_sum(ss);
+    rstd = rsqrtf(ss / D + eps);
+  }
+  if (!BWD) {
+    T* dst = (is_q ? q_out + (tok * Hq + h) * D : k_out + (tok * Hkv + h) * D);
+    // normalise, then rotate pairs (i, i+half). The partner value comes from a shuffle-free
+    // re-read of registers: element i lives in lane i%32 slot i/32; its partner i+half has the
+    // same lane when half % 32 == 0, otherwise fall back to shared-free global re-read.
+#pragma unroll
+    for (int e = 0; e < MAXE; ++e) {
+      int i = lane + 32 * e;
+      if (i >= D) break;
+      float w0 = wv ? to_f(wv[i]) + (zero_centered ? 1.f : 0.f) : 1.f;
+      float v = xv[e] * rstd * w0;
+      if (i < rot) {
+        int j = (i < half) ? i + half : i - half;
+        float wj = wv ? to_f(wv[j]) + (zero_centered ? 1.f : 0.f) : 1.f;
+        float u = to_f(src[j]) * rstd * wj;
+        // round the normalised values through T as the unfused reference does
+        v = to_f(from_f<T>(v));
+        u = to_f(from_f<T>(u));
+        int f = (i < half) ? i : i - half;
+        float c = cr[f], s = sr[f];
+        v = (i < half) ? (v * c - u * s) : (v * c + u * s);
+      }
+      dst[i] = from_f<T>(v);
+    }
+  } else {
+    // g = d(out); first undo the rotation: dn_i = g_i c + g_{i+half} s (i<half); dn_i = g_i c - g_{i-half} s
+    const T* g = is_q ? dq + (tok * Hq + h) * D : dk + (tok * Hkv + h) * D;
+    float dn[MAXE];
+    float dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < MAXE; ++e) {
+      int i = lane + 32 * e;
+      dn[e] = 0.f;
+      if (i < D) {
+        float gi = to_f(g[i]);
+        if (i < rot) {
+          int j = (i < half) ? i + half : i - half;
+          int f = (i < half) ? i : i - half;
+          float gj = to_f(g[j]);
+          float c = cr[f], s = sr[f];
+          gi = (i < half) ? (gi * c + gj * s) : (gi * c - gj * s);
+        }
+        dn[e] = gi;
+        float w0 = wv ? to_f(wv[i]) + (zero_centered ? 1.f : 0.f) : 1.f;
+        dot += xv[e] * w0 * gi;
+      }
+    }
+    // in backward q_out / k_out are the destinations of d(q_in) / d(k_in) with their own token strides
+    T* dst = (is_q ? q_out + tok * ld_dq : k_out + tok * ld_dk) + h * D;
+    if (wv) {
+      dot = warp_sum(dot);
+      float c2 = dot * rstd * rstd / D;
+#pragma unroll
+      for (int e = 0; e < MAXE; ++e) {
+        int i = lane + 32 * e;
+        if (i >= D) break;
+        float w0 = to_f(wv[i]) + (zero_centered ? 1.f : 0.f);
+        dst[i] = from_f<T>(rstd * (w0 * dn[e] - xv[e] * c2));
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < MAXE; ++e) {
+        int i = lane + 32 * e;
+        if (i >= D) break;
+        dst[i] = from_f<T>(dn[e]);
+      }
+    }
+  }
+}
+
+// Decode: append this step's k (already normed+roped, [B,Hkv,D]) and v (view into qkv) to the cache
+// at each row's current length.
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, long long ldv, T* __restrict__ kc,
+                                 T* __restrict__ vc, const int* __restrict__ kv_len, int smax, int HD) {
+  const int b = blockIdx.x;
+  const long long slot = static_cast<long long>(b) * smax + kv_len[b];
+  if (kv_len[b] >= smax) return;  // cache full: drop rather than write out of bounds
+  for (int i = threadIdx.x; i < HD; i += blockDim.x) {
+    kc[slot * HD + i] = k[static_cast<long long>(b) * HD + i];
+    vc[slot * HD + i] = v[static_cast<long long>(b) * ldv + i];
+  }
+}
+
+}  // namespace
+
+template <typename T>
+static const char* rmsnorm_t(const void* x, const void* res, const void* w, const void* gate, void* y, void* h_out,
+                             long long rows, int H, float eps, bool zc, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  rmsnorm_kernel<T><<<static_cast<unsigned>(rows), threads, 0, s>>>(
+      static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(w), static_cast<const T*>(gate),
+      static_cast<T*>(y), static_cast<T*>(h_out), H, eps, zc ? 1 : 0);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm launch failed";
+}
+
+const char* rmsnorm(int dtype, const void* x, const void* res, const void* w, const void* gate, void* y, void* h_out,
+                    long long rows, int H, float eps, bool zero_centered, cudaStream_t s) {
+  return dtype == kF32 ? rmsnorm_t<float>(x, res, w, gate, y, h_out, rows, H, eps, zero_centered, s)
+                       : rmsnorm_t<__nv_bfloat16>(x, res, w, gate, y, h_out, rows, H, eps, zero_centered, s);
+}
+
+template <typename T>
+static const char* rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, long long rows, int H,
+                                 float eps, bool zc, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  rmsnorm_bwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, s>>>(
+      static_cast<const T*>(x), static_cast<const T*>(w), static_cast<const T*>(dy), static_cast<T*>(dx), H, eps,
+      zc ? 1 : 0);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_bwd launch failed";
+}
+
+const char* rmsnorm_bwd(int dtype, const void* x, const void* w, const void* dy, void* dx, long long rows, int H,
+                        float eps, bool zero_centered, cudaStream_t s) {
+  return dtype == kF32 ? rmsnorm_bwd_t<float>(x, w, dy, dx, rows, H, eps, zero_centered, s)
+                       : rmsnorm_bwd_t<__nv_bfloat16>(x, w, dy, dx, rows, H, eps, zero_centered, s);
+}
+
+template <typename T, bool BWD>
+static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
+  if (a.D > 512 || (a.D & 1) || 2 * a.half > a.D) return "qk_norm_rope: head_dim must be even, <= 512, rot <= D";
+  long long units = a.n_tok * (a.Hq + a.Hkv);
+  if (units == 0) return nullptr;
+  int wpb = 8;
+  long long blocks = (units + wpb - 1) / wpb;
+  qk_norm_rope_kernel<T, BWD><<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
+      static_cast<const T*>(a.q_in), a.ld_q, static_cast<const T*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,
+      static_cast<const T*>(a.qw),
+      static_cast<const T*>(a.kw), a.cos_t, a.sin_t, a.pos64, a.pos32, a.pos_div, static_cast<T*>(a.q_out),
+      static_cast<T*>(a.k_out), static_cast<const T*>(a.dq), static_cast<const T*>(a.dk), a.n_tok, a.Hq, a.Hkv, a.D,
+      a.half, a.eps, a.zero_centered ? 1 : 0);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "qk_norm_rope launch failed";
+}
+
+const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s) {
+  if (a.dtype == kF32) return a.backward ? qknr_t<float, true>(a, s) : qknr_t<float, false>(a, s);
+  return a.backward ? qknr_t<__nv_bfloat16, true>(a, s) : qknr_t<__nv_bfloat16, false>(a, s);
+}
+
+const char* kv_append(int dtype, const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
+                      int batch, int smax, int HD, cudaStream_t s) {
+  if (batch == 0) return nullptr;
+  if (dtype == kF32)
+    kv_append_kernel<float><<<batch, 256, 0, s>>>(static_cast<const float*>(k), static_cast<const float*>(v), ldv,
+                                                  static_cast<float*>(kc), static_cast<float*>(vc), kv_len, smax, HD);
+  else
+    kv_append_kernel<__nv_bfloat16><<<batch, 256, 0, s>>>(
+        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ldv,
+        static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, smax, HD);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "kv_append launch failed";
+}
+
+}  // namespace ferrl

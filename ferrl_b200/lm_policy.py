@@ -38,6 +38,11 @@ class LmPolicy(Policy):
         self._adapter_on = True
         self._merged_fresh = False
         self.last_cache_bytes = 0
+        self.use_cuda_graph = True
+        self._decoders: dict = {}      # (batch, max_len) -> cached decoder (KV buffers are reused across rollouts)
+        self._graphs: dict = {}        # (batch, max_len, sampling) -> GraphedDecodeStep
+        self.h2d_bytes = 0             # bytes copied host->device / device->host since the last reset
+        self.d2h_bytes = 0
 
     # ------------------------------------------------------------ plumbing
     def device(self):
@@ -50,6 +55,7 @@ class LmPolicy(Policy):
         self._adapter_on = bool(on)
         self.model.set_adapter_enabled(on)
         self._merged_fresh = False
+        self._graphs.clear()  # merged-weight addresses may change with the adapter state
 
     def adapter_enabled(self) -> bool:
         return self._adapter_on
@@ -102,20 +108,39 @@ class LmPolicy(Policy):
             ids_host, lens_host = ids_host.pin_memory(), lens_host.pin_memory()
         ids = ids_host.to(dev, non_blocking=True)
         lens = lens_host.to(dev, non_blocking=True)
+        self.h2d_bytes += ids_host.numel() * 8 + lens_host.numel() * 8 + B * 8
         rows = (torch.as_tensor(list(global_row_bases), dtype=torch.int64).repeat_interleave(G)
                 + torch.arange(G, dtype=torch.int64).repeat(P)).to(dev)
         if not self._merged_fresh:
             self.model.merge_adapters()
             self._merged_fresh = True
-        dec = self.model.new_decoder(B, Lmax + N, self.comm)
+        max_len = Lmax + N
+        if dev.type == "cuda":
+            max_len = (max_len + 127) // 128 * 128  # bucket the cache length so decoders and graphs are reused
+        dkey = (B, max_len)
+        dec = self._decoders.get(dkey)
+        if dec is None:
+            self._decoders.clear()
+            self._graphs.clear()
+            dec = self.model.new_decoder(B, max_len, self.comm)
+            self._decoders[dkey] = dec
         self.last_cache_bytes = dec.cache_bytes()
         logits = dec.prefill(ids, lens)
         dec.broadcast_groups(G)
         logits = logits.repeat_interleave(G, dim=0)
         eos = cfg.eos_token_id
         pad = eos if eos is not None else self.pad_token_id
-        out_tok, out_lp, comp_len = run_decode_loop(dec, self.sampler, logits, rows, N, temperature, top_p,
-                                                    eos, pad, self.early_exit_every)
+        if dev.type == "cuda" and self.use_cuda_graph and N > 2:
+            gkey = (B, max_len, temperature, top_p, eos, pad)
+            step = self._graphs.get(gkey)
+            if step is None:
+                step = GraphedDecodeStep(dec, self.sampler, B, temperature, top_p, eos, pad)
+                self._graphs[gkey] = step
+            out_tok, out_lp, comp_len = step.run(logits, rows, N, self.early_exit_every)
+        else:
+            out_tok, out_lp, comp_len = run_decode_loop(dec, self.sampler, logits, rows, N, temperature, top_p,
+                                                        eos, pad, self.early_exit_every)
+        self.d2h_bytes += out_tok.numel() * 8 + out_lp.numel() * 4 + comp_len.numel() * 8
         out_tok, out_lp, comp_len = out_tok.cpu(), out_lp.cpu(), comp_len.cpu()
         res = []
         for i, p in enumerate(prompts):
@@ -152,6 +177,7 @@ class LmPolicy(Policy):
         dev = self.device()
         if dev.type == "cuda":
             ids, start, targets = ids.pin_memory(), start.pin_memory(), targets.pin_memory()
+        self.h2d_bytes += (ids.numel() + start.numel() + targets.numel()) * 8
         ids, start, targets = (t.to(dev, non_blocking=True) for t in (ids, start, targets))
         inp = ids[:, :-1]
         mb = self.score_microbatch if self.score_microbatch > 0 else inp.shape[0]
@@ -188,3 +214,93 @@ def run_decode_loop(dec, sampler: GrpoSampler, logits, rows, N: int, temperature
             break
         logits = dec.decode(tok)
     return out_tok, out_lp, comp_len
+
+
+class GraphedDecodeStep:
+    """One decode step (sample -> bookkeeping -> model decode) captured as a CUDA
+    graph over static buffers, replayed once per generated token.  The draw
+    index is a device counter that the graph itself advances, so replays need
+    no host-side parameters and the host never synchronises inside the loop
+    (except for the optional every-k early-exit poll)."""
+
+    def __init__(self, dec, sampler: GrpoSampler, B: int, temperature, top_p, eos, pad):
+        self.dec, self.sampler = dec, sampler
+        self.B, self.temperature, self.top_p, self.eos, self.pad = B, temperature, top_p, eos, pad
+        self.graph = None
+        self.launches_per_replay = 0
+        self.N = 0
+
+    def _alloc(self, logits, rows, N):
+        dev = logits.device
+        B = self.B
+        self.N = N
+        self.logits = torch.empty_like(logits)
+        self.rows = rows.clone()
+        self.draw = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.finished = torch.zeros(B, dtype=torch.bool, device=dev)
+        self.comp_len = torch.zeros(B, dtype=torch.int64, device=dev)
+        self.out_tok = torch.full((B, N), self.pad, dtype=torch.int64, device=dev)
+        self.out_lp = torch.zeros((B, N), dtype=torch.float32, device=dev)
+        self.pad_t = torch.full((B,), self.pad, dtype=torch.int64, device=dev)
+
+    def _body(self):
+        tok, lp = self.sampler.sample(self.logits, self.rows, 0, self.temperature, self.top_p, draw_dev=self.draw)
+        tok = torch.where(self.finished, self.pad_t, tok)
+        col = self.draw.to(torch.int64).clamp(max=self.N - 1).view(1, 1).expand(self.B, 1)
+        self.out_tok.scatter_(1, col, tok[:, None])
+        self.out_lp.scatter_(1, col, torch.where(self.finished, torch.zeros_like(lp), lp)[:, None])
+        self.comp_len += (~self.finished).to(torch.int64)
+        if self.eos is not None:
+            self.finished |= tok == self.eos
+        self.logits.copy_(self.dec.decode(tok))
+        self.draw += 1
+
+    @torch.no_grad()
+    def run(self, logits, rows, N, early_exit_every=32):
+        from .ops import cuda as C
+        if self.graph is None or N != self.N:
+            self._alloc(logits, rows, N)
+            self.graph = None
+        self.logits.copy_(logits)
+        self.rows.copy_(rows)
+        self.draw.zero_()
+        self.finished.zero_()
+        self.comp_len.zero_()
+        self.out_tok.fill_(self.pad)
+        self.out_lp.zero_()
+        kv0 = self.dec.kv_len.clone()
+        if self.graph is None:
+            # one eager step warms every kernel (and lazy one-time allocations) before capture; its
+            # effects are rolled back so the captured graph starts from the same state
+            snap = (self.logits.clone(),)
+            self._body()
+            torch.cuda.synchronize()
+            self.dec.kv_len.copy_(kv0)
+            self.logits.copy_(snap[0])
+            self.draw.zero_()
+            self.finished.zero_()
+            self.comp_len.zero_()
+            self.out_tok.fill_(self.pad)
+            self.out_lp.zero_()
+            before = C.launches()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body()
+            self.launches_per_replay = C.launches() - before
+            self.graph = g
+        steps = 0
+        # N-1 full steps, then a final sample-only step handled eagerly below
+        for t in range(N - 1):
+            self.graph.replay()
+            steps += 1
+            if self.eos is not None and early_exit_every > 0 and (t + 1) % early_exit_every == 0 \
+                    and bool(self.finished.all()):
+                break
+        C.lib().add_launches(self.launches_per_replay * steps)
+        if steps == N - 1:
+            tok, lp = self.sampler.sample(self.logits, self.rows, N - 1, self.temperature, self.top_p)
+            tok = torch.where(self.finished, self.pad_t, tok)
+            self.out_tok[:, N - 1] = tok
+            self.out_lp[:, N - 1] = torch.where(self.finished, torch.zeros_like(lp), lp)
+            self.comp_len += (~self.finished).to(torch.int64)
+        return self.out_tok.clone(), self.out_lp.clone(), self.comp_len.clone()

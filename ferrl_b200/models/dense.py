@@ -163,6 +163,10 @@ class DenseLayer(nn.Module):
 
 def ops_cache_write(k_cache, v_cache, k, v, kv_len):
     """Write one token's K/V per row at that row's current length."""
+    if k.is_cuda and k.dtype == torch.bfloat16:
+        from ..ops import cuda as _c
+        _c.kv_append(k_cache, v_cache, k.contiguous(), v, kv_len)
+        return
     idx = kv_len.long()
     rows = torch.arange(k.shape[0], device=k.device)
     k_cache[rows, idx] = k

@@ -224,13 +224,11 @@ class FusedLoraLinear(nn.Module):
             return None, None
         r = self.rank
         A = torch.cat(list(self.lora_A), dim=0)  # [n*r, full_in]
-        cols = []
         offs = 0
         starts = []
         for o in self.out_sizes:
             starts.append(offs)
             offs += o
-        B = A.new_zeros(sum(self.out_sizes), r * len(self.adapted_idx))
         pieces = []
         for j, i in enumerate(self.adapted_idx):
             b = self.lora_B[j]
@@ -254,7 +252,6 @@ class FusedLoraLinear(nn.Module):
         if self.shard is not None and self.shard.kind == "row":
             per = self.full_in // self.shard.world
             A = A[:, self.shard.rank * per:(self.shard.rank + 1) * per]
-        del cols
         return A, B
 
     # --------------------------------------------------------------- forward
@@ -274,7 +271,11 @@ class FusedLoraLinear(nn.Module):
         if a is None:
             self.weight_merged = None
             return
-        self.weight_merged = ops.lora_merge(self.weight, a.detach(), b.detach())
+        new = ops.lora_merge(self.weight, a.detach(), b.detach())
+        if self.weight_merged is not None and self.weight_merged.shape == new.shape:
+            self.weight_merged.copy_(new)  # keep the address stable: captured decode graphs point at it
+        else:
+            self.weight_merged = new
 
     def merged_weight(self) -> torch.Tensor:
         a, b = self._stacks()

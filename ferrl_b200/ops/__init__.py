@@ -96,8 +96,9 @@ def embedding(ids, table, scale=1.0):
     return eager.embedding(ids, table, scale)
 
 
-def sample_top_p(logits, base_seed, global_row_base, draw, temperature, top_p):
-    return _cuda().sample_top_p(logits, base_seed, global_row_base, draw, temperature, top_p)
+def sample_top_p(logits, base_seed, global_rows, draw, temperature, top_p, draw_dev=None):
+    """``draw_dev`` (int32 device scalar) overrides ``draw`` so a captured CUDA graph can advance it."""
+    return _cuda().sample_top_p(logits, base_seed, global_rows, draw, temperature, top_p, draw_dev)
 
 
 def grpo_loss_fused(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w=None):

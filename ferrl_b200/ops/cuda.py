@@ -1,0 +1,403 @@
+"""CUDA side of ``ferrl_b200.ops``: loads the in-tree native library and wraps
+each sm_100a kernel as an autograd-aware function.
+
+bf16 is the production dtype: the tcgen05 GEMM, flash attention and decode
+attention accept bf16 only.  float32 CUDA tensors (a debugging configuration)
+run the eager restatement for those three ops and the native kernels for the
+rest.  A missing library raises ``ExtensionMissing`` - nothing falls back
+silently.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from . import eager
+
+_LIB = None
+_SO = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "_C.so")
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        from . import ExtensionMissing
+        if not os.path.exists(_SO):
+            raise ExtensionMissing(f"native library {_SO} is not built; run `python -m ferrl_b200._build`")
+        try:
+            torch.ops.load_library(_SO)
+        except OSError as e:
+            raise ExtensionMissing(f"cannot load {_SO}: {e}") from e
+        _LIB = torch.ops.ferrl_b200
+    return _LIB
+
+
+def launches() -> int:
+    return int(lib().launches())
+
+
+def kernel_status() -> int:
+    return int(lib().kernel_status())
+
+
+def _bf16(t):
+    return t is not None and t.dtype == torch.bfloat16
+
+
+# ----------------------------------------------------------------- GEMM
+def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0):
+    """``a [M,K] @ b[N,K]^T (+ a2 @ b2^T) (+ residual)`` on the tcgen05 kernel."""
+    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn)
+
+
+def _pad8(t, dim):
+    n = t.shape[dim]
+    if n % 8 == 0:
+        return t
+    pad = [0, 0] * t.dim()
+    pad[2 * (t.dim() - 1 - dim) + 1] = 8 - n % 8
+    return torch.nn.functional.pad(t, pad)
+
+
+class _LoraLinear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, wt, a_stack, b_stack):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        t = a16 = b16 = None
+        if a_stack is not None:
+            a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()   # [R, K]
+            b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()   # [N, R]
+            t = gemm(x2, a16)                                                  # [M, R]
+        y = gemm(x2, w, t, b16)
+        ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
+        ctx.x_shape = x.shape
+        ctx.x_grad = x.requires_grad
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, wt, a_stack, b_stack, t, a16, b16 = ctx.saved_tensors
+        N = w.shape[0]
+        dy2 = dy.reshape(-1, N)
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dx = da = db = None
+        u = None
+        if a_stack is not None:
+            u = gemm(dy2, b16.t().contiguous())                                # [M, R] = dy @ B
+        if ctx.x_grad:
+            wt_ = wt if wt is not None else w.t().contiguous()
+            if u is not None:
+                dx = gemm(dy2, wt_, u, a16.t().contiguous())
+            else:
+                dx = gemm(dy2, wt_)
+            dx = dx.view(ctx.x_shape)
+        if a_stack is not None:
+            R = a_stack.shape[0]
+            # adapter gradients: tall-skinny reductions over the token dimension
+            da = torch.matmul(u.t(), x2)[:R].float() if a_stack.requires_grad else None
+            db = torch.matmul(dy2.t(), t)[:, :R].float() if b_stack.requires_grad else None
+        return dx, None, None, da, db
+
+
+def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None):
+    if not (_bf16(x) and _bf16(w)) or bias is not None or w.requires_grad:
+        return eager.lora_linear(x, w, a_stack, b_stack, bias)
+    if x.shape[-1] % 8:
+        return eager.lora_linear(x, w, a_stack, b_stack, bias)
+    return _LoraLinear.apply(x, w, wt, a_stack, b_stack)
+
+
+def lora_merge(w, a_stack, b_stack):
+    if a_stack is None:
+        return w
+    return lib().lora_merge(w.contiguous(), a_stack.float().contiguous(), b_stack.float().contiguous())
+
+
+# ----------------------------------------------------------------- norms
+class _RmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, zc):
+        xc = x.contiguous()
+        y, _ = lib().rmsnorm(xc, None, w, None, eps, zc)
+        ctx.save_for_backward(xc, w)
+        ctx.eps, ctx.zc = eps, zc
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        return lib().rmsnorm_bwd(x, w, dy.contiguous(), ctx.eps, ctx.zc), None, None, None
+
+
+def rmsnorm(x, weight, eps, zero_centered=False):
+    if weight is not None and (weight.requires_grad or weight.dtype != x.dtype):
+        return eager.rmsnorm(x, weight, eps, zero_centered)
+    return _RmsNorm.apply(x, weight, eps, zero_centered)
+
+
+class _AddRmsNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, res, w, eps, zc):
+        y, h = lib().rmsnorm(x.contiguous(), res.contiguous(), w, None, eps, zc)
+        ctx.save_for_backward(h, w)
+        ctx.eps, ctx.zc = eps, zc
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        h, w = ctx.saved_tensors
+        g = lib().rmsnorm_bwd(h, w, dy.contiguous(), ctx.eps, ctx.zc)
+        if dh is not None:
+            g = g + dh
+        return g, g, None, None, None
+
+
+def add_rmsnorm(x, residual, weight, eps, zero_centered=False):
+    if weight is not None and (weight.requires_grad or weight.dtype != x.dtype):
+        return eager.add_rmsnorm(x, residual, weight, eps, zero_centered)
+    return _AddRmsNorm.apply(x, residual, weight, eps, zero_centered)
+
+
+def rmsnorm_gated(x, gate, weight, eps):
+    if torch.is_grad_enabled() and (x.requires_grad or gate.requires_grad or weight.requires_grad):
+        return eager.rmsnorm_gated(x, gate, weight, eps)
+    y, _ = lib().rmsnorm(x.contiguous(), None, weight.to(x.dtype), gate.contiguous(), eps, False)
+    return y
+
+
+class _QkNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, qw, kw, eps, cos, sin, pos, pos_div, zc):
+        B, S, Hq, D = q.shape
+        Hkv = k.shape[2]
+        ts = (lambda t: t.stride(1) if S > 1 else t.stride(0))  # token stride (a size-1 dim has an arbitrary stride)
+        q3 = q.reshape(B * S, Hq, D) if q.is_contiguous() else q.as_strided((B * S, Hq, D), (ts(q), D, 1), q.storage_offset())
+        k3 = k.reshape(B * S, Hkv, D) if k.is_contiguous() else k.as_strided((B * S, Hkv, D), (ts(k), D, 1), k.storage_offset())
+        qo, ko = lib().qk_norm_rope_fwd(q3, k3, qw, kw, cos, sin, pos, pos_div, eps, zc)
+        ctx.save_for_backward(q3, k3, qw, kw, cos, sin, pos)
+        ctx.meta = (B, S, Hq, Hkv, D, pos_div, eps, zc)
+        return qo.view(B, S, Hq, D), ko.view(B, S, Hkv, D)
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        q3, k3, qw, kw, cos, sin, pos = ctx.saved_tensors
+        B, S, Hq, Hkv, D, pos_div, eps, zc = ctx.meta
+        dqi = torch.empty(B * S, Hq, D, dtype=q3.dtype, device=q3.device)
+        dki = torch.empty(B * S, Hkv, D, dtype=k3.dtype, device=k3.device)
+        lib().qk_norm_rope_bwd(q3, k3, qw, kw, cos, sin, pos, pos_div, eps, zc, dq.contiguous().view(B * S, Hq, D),
+                               dk.contiguous().view(B * S, Hkv, D), dqi, dki)
+        return dqi.view(B, S, Hq, D), dki.view(B, S, Hkv, D), None, None, None, None, None, None, None, None
+
+
+def _strided_ok(t):
+    # [B,S,H,D] with packed heads and batch stride == S * token stride (so tokens form one strided 2-D matrix)
+    B, S, H, D = t.shape
+    return t.stride(3) == 1 and t.stride(2) == D and (B == 1 or S == 1 or t.stride(0) == S * t.stride(1))
+
+
+def qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered=False):
+    if (q_w is not None and q_w.requires_grad) or not (_strided_ok(q) and _strided_ok(k)):
+        return eager.qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered)
+    B, S = q.shape[:2]
+    if positions.dim() == 1:          # [S], shared by every batch row -> position of token t is pos[t % S]
+        pos = positions.repeat(B) if B > 1 else positions
+    else:
+        pos = positions.reshape(-1)
+    pos = pos.contiguous()
+    if pos.dtype not in (torch.int64, torch.int32):
+        pos = pos.long()
+    qw = None if q_w is None else q_w.to(q.dtype)
+    kw = None if k_w is None else k_w.to(k.dtype)
+    return _QkNormRope.apply(q, k, qw, kw, eps, cos.float(), sin.float(), pos, 1, zero_centered)
+
+
+# ------------------------------------------------------------- attention
+class _Flash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, causal, window, q_offset):
+        o, lse = lib().flash_fwd(q, k, v, scale, causal, window, q_offset)
+        ctx.save_for_backward(q, k, v, o, lse)
+        ctx.meta = (scale, causal, window, q_offset)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, o, lse = ctx.saved_tensors
+        dq, dk, dv = lib().flash_bwd(q, k, v, o, lse, do.contiguous(), *ctx.meta)
+        return dq, dk, dv, None, None, None, None
+
+
+def _packed(t):
+    return t if (t.stride(3) == 1 and t.stride(2) == t.shape[3]) else t.contiguous()
+
+
+def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None):
+    if not _bf16(q) or q.shape[-1] not in (64, 128, 256) or kv_len is not None:
+        return eager.attention(q, k, v, scale=scale, causal=causal, window=window, q_offset=q_offset, kv_len=kv_len)
+    return _Flash.apply(_packed(q), _packed(k), _packed(v), float(scale), bool(causal), int(window or 0), int(q_offset))
+
+
+def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0):
+    if not _bf16(q) or q.shape[-1] % 8 or q.shape[-1] > 256:
+        return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
+    return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),
+                             int(n_splits), None, 0)
+
+
+def kv_append(k_cache, v_cache, k, v, kv_len):
+    """Write one token's K/V per row at ``kv_len[b]`` (``k`` contiguous [B,Hkv,D], ``v`` may be a strided view)."""
+    B = k.shape[0]
+    lib().kv_append(k.reshape(B, -1), v.reshape(B, -1) if v.is_contiguous() else v.as_strided(
+        (B, v.shape[-2] * v.shape[-1]), (v.stride(0), 1), v.storage_offset()), k_cache, v_cache, kv_len)
+
+
+# ------------------------------------------------------------------ mlp
+_ACT = {"silu": 0, "gelu_pytorch_tanh": 1, "gelu_tanh": 1}
+
+
+class _Glu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu, act):
+        guc = gu.contiguous()
+        ctx.save_for_backward(guc)
+        ctx.act = act
+        return lib().glu_fwd(guc, act)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        return lib().glu_bwd(gu, dout.contiguous(), ctx.act), None
+
+
+def swiglu(gate_up, act="silu"):
+    if act not in _ACT:
+        return eager.swiglu(gate_up, act)
+    return _Glu.apply(gate_up, _ACT[act])
+
+
+def embedding(ids, table, scale=1.0):
+    if table.requires_grad:
+        return eager.embedding(ids, table, scale)
+    return lib().embedding(ids, table, float(scale))
+
+
+# -------------------------------------------------------------- logprob
+LOGPROB_CHUNK_BYTES = 1 << 30
+
+
+class _LogprobGather(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, hidden, head_w, head_wt, targets, temperature, softcap):
+        N, H = hidden.shape
+        V = head_w.shape[0]
+        chunk = max(128, min(N, (LOGPROB_CHUNK_BYTES // (2 * V)) // 128 * 128)) if N else 1
+        lp = torch.empty(N, dtype=torch.float32, device=hidden.device)
+        lse = torch.empty(N, dtype=torch.float32, device=hidden.device)
+        h = hidden.contiguous()
+        t = targets.contiguous()
+        for s in range(0, N, chunk):
+            logits = gemm(h[s:s + chunk], head_w)
+            a, b = lib().logprob_rows(logits, t[s:s + chunk], temperature, softcap)
+            lp[s:s + chunk] = a
+            lse[s:s + chunk] = b
+        ctx.save_for_backward(h, head_w, head_wt, t, lse)
+        ctx.meta = (temperature, softcap, chunk)
+        return lp
+
+    @staticmethod
+    def backward(ctx, dlp):
+        h, head_w, head_wt, t, lse = ctx.saved_tensors
+        temperature, softcap, chunk = ctx.meta
+        N = h.shape[0]
+        wt = head_wt if head_wt is not None else head_w.t().contiguous()
+        dh = torch.empty_like(h)
+        dlp = dlp.contiguous().float()
+        for s in range(0, N, chunk):
+            logits = gemm(h[s:s + chunk], head_w)
+            lib().logprob_rows_bwd(logits, t[s:s + chunk], lse[s:s + chunk], dlp[s:s + chunk], temperature, softcap)
+            dh[s:s + chunk] = gemm(logits, wt)
+        return dh, None, None, None, None, None
+
+
+def logprob_gather(hidden, head_w, targets, temperature=1.0, softcap=0.0, head_wt=None):
+    if not (_bf16(hidden) and _bf16(head_w)) or head_w.requires_grad or head_w.shape[0] % 8 or hidden.shape[-1] % 8:
+        return eager.logprob_gather(hidden, head_w, targets, temperature, softcap)
+    return _LogprobGather.apply(hidden, head_w, head_wt, targets.long(), float(temperature), float(softcap or 0.0))
+
+
+# -------------------------------------------------------------- sampling
+def _s64(x: int) -> int:
+    x &= (1 << 64) - 1
+    return x - (1 << 64) if x >= (1 << 63) else x
+
+
+def sample_top_p(logits, base_seed, global_rows, draw, temperature, top_p, draw_dev=None):
+    lg = logits if logits.stride(-1) == 1 else logits.contiguous()
+    return lib().sample_rows(lg, global_rows.long().contiguous(), _s64(int(base_seed)), draw_dev, int(draw),
+                             float(temperature), float(top_p) if top_p is not None else 0.0)
+
+
+# ----------------------------------------------------------------- loss
+class _GrpoLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logp, logp_old, logp_ref, adv, mask, tis_w, eps_lo, eps_hi, beta, seq_level, loss_type,
+                dapo_norm, scale):
+        G, L = logp.shape
+        want = logp.requires_grad
+        row_sum, row_cnt, dl = lib().grpo_loss_rows(logp.contiguous(), logp_old.contiguous(),
+                                                    None if logp_ref is None else logp_ref.contiguous(),
+                                                    adv.reshape(-1).float().contiguous(), mask.contiguous(),
+                                                    None if tis_w is None else tis_w.contiguous(), eps_lo, eps_hi,
+                                                    beta, seq_level, want)
+        if loss_type == "grpo":
+            row_scale = 1.0 / (row_cnt.clamp(min=1.0) * G)
+        elif loss_type == "dr_grpo":
+            row_scale = torch.full_like(row_cnt, 1.0 / (G * L))
+        else:
+            norm = row_cnt.sum().clamp(min=1.0) if dapo_norm is None else torch.full((), max(dapo_norm, 1.0),
+                                                                                    device=logp.device)
+            row_scale = torch.ones_like(row_cnt) / norm
+        row_scale = row_scale * scale
+        loss = -(row_sum * row_scale).sum()
+        if want:
+            ctx.save_for_backward(dl, row_scale)
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        dl, row_scale = ctx.saved_tensors
+        out = dl.clone()
+        lib().grpo_scale_rows(out, (-g * row_scale).contiguous())
+        return (out,) + (None,) * 12
+
+
+def grpo_loss(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w=None):
+    from ..grpo import ImportanceSamplingLevel, LossType
+    if logp.dtype != torch.float32:
+        from ..grpo import grpo_loss_eager
+        return grpo_loss_eager(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w)
+    return _GrpoLoss.apply(logp, logp_old.float(), None if logp_ref is None else logp_ref.float(), advantages,
+                           mask.float(), None if tis_w is None else tis_w.float(), float(cfg.clip_eps_low),
+                           float(cfg.clip_eps_high), float(cfg.beta),
+                           ImportanceSamplingLevel(cfg.is_level) is ImportanceSamplingLevel.SEQUENCE,
+                           LossType(cfg.loss_type).value, cfg.dapo_norm, float(cfg.scale))
+
+
+# ---------------------------------------------------------------- adamw
+def adamw_step(params, grads, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+               max_norm: float = 0.0, compute_norm: bool = False):
+    """Multi-tensor AdamW. With ``compute_norm`` the kernel also derives the global
+    gradient norm and clip factor on the device; returns the norm tensor."""
+    if not params:
+        return None
+    if any(p.dtype != torch.float32 for p in params):
+        return eager.adamw_step(params, grads, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                                weight_decay=weight_decay, step=step, grad_scale=grad_scale)
+    return lib().adamw_step(list(params), [g.contiguous() for g in grads], list(m), list(v), lr, beta1, beta2, eps,
+                            weight_decay, step, max_norm, grad_scale, compute_norm)

@@ -139,7 +139,7 @@ class GrpoSampler:
         return uniforms(self.base_seed, global_row_base, rows, draw)
 
     def sample(self, logits: torch.Tensor, global_rows, draw: int,
-               temperature: Optional[float] = None, top_p: Optional[float] = None):
+               temperature: Optional[float] = None, top_p: Optional[float] = None, draw_dev=None):
         """Sample one token per row of ``logits`` ``[R, V]``. ``global_rows`` is
         the first row's global index (rows are then consecutive) or an int64
         tensor ``[R]`` of global row indices."""
@@ -149,7 +149,7 @@ class GrpoSampler:
         if logits.is_cuda:
             from .ops import sample_top_p
             return sample_top_p(logits, self.base_seed, global_rows.to(logits.device), draw, t,
-                                validate_top_p(top_p))
+                                validate_top_p(top_p), draw_dev)
         u = uniforms_for_rows(self.base_seed, global_rows, draw)
         return sample_from_logits_eager(logits, u, t, top_p)
 
