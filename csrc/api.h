@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include "symm/symm.cuh"
+
 namespace ferrl {
 
 enum { kBF16 = 0, kF32 = 1 };
@@ -60,6 +62,25 @@ const char* grpo_loss_rows(const float* logp, const float* logp_old, const float
                            const float* mask, const float* tis, float* row_sum, float* row_cnt, float* dlogp, int G,
                            int L, float eps_lo, float eps_hi, float beta, int mode, cudaStream_t s);
 const char* grpo_scale_rows(float* dlogp, const float* row_scale, int G, int L, cudaStream_t s);
+
+// ---- data-parallel fused step and symmetric-heap collectives ----
+struct DpStepParams {
+  PeerTable grads, reduced, flags, scalars;  // per-rank copies of the symmetric buffers
+  int rank, world, barrier_world, own_lo, own_hi;
+  long long n;                               // flat length, padded to a multiple of 4*world
+  unsigned epoch; float pre_scale; float uncovered_local;
+  const AdamTensor* tab; const int* blk_tensor; const long long* blk_off; const long long* blk_flat;
+  int n_blocks, chunk;
+  float lr, b1, b2, eps, wd, bc1_inv, bc2_inv, max_norm;
+  double* block_partials;                    // local scratch, 2 doubles per block
+  float* out;                                // [norm, uncovered_total, stepped]
+  int* status; int* abort_word; unsigned long long limit_ns;
+};
+const char* dp_step(const DpStepParams& p, int num_sms, cudaStream_t s);
+int dp_step_grid(int num_sms);
+const char* symm_all_reduce(int dtype, const PeerTable& src, const PeerTable& flags, void* out, long long n, int rank,
+                            int world, unsigned epoch, unsigned long long limit_ns, int* status, int* abort_word,
+                            int num_sms, cudaStream_t s);
 
 // ---- decode attention ----
 struct DecodeAttnArgs {

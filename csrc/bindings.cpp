@@ -411,6 +411,104 @@ std::tuple<Tensor, Tensor> sample_rows(const Tensor& logits, const Tensor& globa
   return {tok, lp};
 }
 
+// ------------------------------------------------------------------ symmetric heap
+Tensor symm_alloc(int64_t nbytes) {
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaMalloc(&ptr, nbytes));
+  C10_CUDA_CHECK(cudaMemset(ptr, 0, nbytes));
+  int dev = c10::cuda::current_device();
+  return at::from_blob(ptr, {nbytes}, [](void* p) { cudaFree(p); },
+                       at::TensorOptions().dtype(at::kByte).device(at::kCUDA, dev));
+}
+
+Tensor symm_handle(const Tensor& buf) {
+  cudaIpcMemHandle_t h;
+  C10_CUDA_CHECK(cudaIpcGetMemHandle(&h, buf.data_ptr()));
+  Tensor out = at::empty({static_cast<long long>(sizeof(h))}, at::TensorOptions().dtype(at::kByte));
+  memcpy(out.data_ptr(), &h, sizeof(h));
+  return out;
+}
+
+int64_t symm_open(const Tensor& handle) {
+  TORCH_CHECK(!handle.is_cuda() && handle.numel() == static_cast<long long>(sizeof(cudaIpcMemHandle_t)), "symm_open: handle bytes");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle.data_ptr(), sizeof(h));
+  void* ptr = nullptr;
+  C10_CUDA_CHECK(cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess));
+  return reinterpret_cast<int64_t>(ptr);
+}
+
+void symm_close(int64_t ptr) { cudaIpcCloseMemHandle(reinterpret_cast<void*>(ptr)); }
+
+ferrl::PeerTable table_of(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() <= ferrl::kMaxRanks, "too many ranks");
+  ferrl::PeerTable t{};
+  for (size_t i = 0; i < ptrs.size(); ++i) t.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return t;
+}
+
+// Fused DP step; `tables` is a device uint8 blob holding [AdamTensor x n | blk_tensor | blk_off | blk_flat]
+// laid out by the caller (offsets in bytes), `out` a float32[3] device tensor.
+void dp_step(std::vector<int64_t> grads, std::vector<int64_t> reduced, std::vector<int64_t> flags,
+             std::vector<int64_t> scalars, int64_t rank, int64_t world, int64_t barrier_world, int64_t own_lo,
+             int64_t own_hi, int64_t n, int64_t epoch, double pre_scale, double uncovered_local, const Tensor& tables,
+             int64_t off_blk_tensor, int64_t off_blk_off, int64_t off_blk_flat, int64_t n_blocks, int64_t chunk,
+             double lr, double b1, double b2, double eps, double wd, int64_t step, double max_norm,
+             Tensor block_partials, Tensor out, Tensor abort_word, double limit_s) {
+  c10::cuda::CUDAGuard guard(out.device());
+  ferrl::DpStepParams p{};
+  p.grads = table_of(grads); p.reduced = table_of(reduced); p.flags = table_of(flags); p.scalars = table_of(scalars);
+  p.rank = rank; p.world = world; p.barrier_world = barrier_world; p.own_lo = own_lo; p.own_hi = own_hi;
+  p.n = n; p.epoch = static_cast<unsigned>(epoch); p.pre_scale = pre_scale; p.uncovered_local = uncovered_local;
+  uint8_t* d = tables.data_ptr<uint8_t>();
+  p.tab = reinterpret_cast<const ferrl::AdamTensor*>(d);
+  p.blk_tensor = reinterpret_cast<const int*>(d + off_blk_tensor);
+  p.blk_off = reinterpret_cast<const long long*>(d + off_blk_off);
+  p.blk_flat = reinterpret_cast<const long long*>(d + off_blk_flat);
+  p.n_blocks = n_blocks; p.chunk = chunk;
+  p.lr = lr; p.b1 = b1; p.b2 = b2; p.eps = eps; p.wd = wd;
+  p.bc1_inv = 1.f / (1.f - static_cast<float>(std::pow(b1, static_cast<double>(step))));
+  p.bc2_inv = 1.f / (1.f - static_cast<float>(std::pow(b2, static_cast<double>(step))));
+  p.max_norm = max_norm;
+  TORCH_CHECK(block_partials.scalar_type() == at::kDouble && block_partials.numel() >= 2 * ferrl::dp_step_grid(num_sms()), "dp_step: block_partials too small");
+  p.block_partials = block_partials.data_ptr<double>();
+  p.out = out.data_ptr<float>(); p.status = status_word(); p.abort_word = abort_word.data_ptr<int>();
+  p.limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
+  FERRL_CHECK(ferrl::dp_step(p, num_sms(), stream()));
+}
+
+// Packs the AdamW tensor table for dp_step / reuse; returns (device blob, off_blk_tensor, off_blk_off, off_blk_flat, n_blocks)
+std::tuple<Tensor, int64_t, int64_t, int64_t, int64_t> dp_tables(std::vector<Tensor> params, std::vector<Tensor> m,
+                                                                std::vector<Tensor> v, std::vector<int64_t> flat_off,
+                                                                int64_t chunk) {
+  const size_t n = params.size();
+  std::vector<ferrl::AdamTensor> tab(n);
+  std::vector<int> bt; std::vector<long long> bo, bf;
+  for (size_t i = 0; i < n; ++i) {
+    TORCH_CHECK(params[i].scalar_type() == at::kFloat && params[i].is_contiguous() && m[i].is_contiguous() && v[i].is_contiguous(), "dp_tables: float32 contiguous");
+    tab[i] = {params[i].data_ptr<float>(), nullptr, m[i].data_ptr<float>(), v[i].data_ptr<float>(), params[i].numel()};
+    for (long long o = 0; o < params[i].numel(); o += chunk) { bt.push_back(i); bo.push_back(o); bf.push_back(flat_off[i] + o); }
+  }
+  auto al = [](size_t x) { return (x + 15) & ~size_t(15); };
+  size_t o1 = al(n * sizeof(ferrl::AdamTensor)), o2 = al(o1 + bt.size() * 4), o3 = al(o2 + bo.size() * 8), tot = o3 + bf.size() * 8 + 16;
+  Tensor host = at::empty({static_cast<long long>(tot)}, at::TensorOptions().dtype(at::kByte));
+  uint8_t* h = host.data_ptr<uint8_t>();
+  memcpy(h, tab.data(), n * sizeof(ferrl::AdamTensor));
+  memcpy(h + o1, bt.data(), bt.size() * 4);
+  memcpy(h + o2, bo.data(), bo.size() * 8);
+  memcpy(h + o3, bf.data(), bf.size() * 8);
+  return {host.to(params[0].device()), static_cast<int64_t>(o1), static_cast<int64_t>(o2), static_cast<int64_t>(o3), static_cast<int64_t>(bt.size())};
+}
+
+void symm_all_reduce(std::vector<int64_t> src, std::vector<int64_t> flags, Tensor out, int64_t rank, int64_t world,
+                     int64_t epoch, double limit_s, Tensor abort_word) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous(), "symm_all_reduce: contiguous output");
+  FERRL_CHECK(ferrl::symm_all_reduce(dt(out), table_of(src), table_of(flags), out.data_ptr(), out.numel(), rank, world,
+                                     static_cast<unsigned>(epoch), static_cast<unsigned long long>(limit_s * 1e9),
+                                     status_word(), abort_word.data_ptr<int>(), num_sms(), stream()));
+}
+
 int64_t launches() { return ferrl::launch_count(); }
 void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 
@@ -438,6 +536,13 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);
   m.def("sample_rows(Tensor logits, Tensor global_rows, int seed, Tensor? draw_dev, int draw, float temperature, float top_p) -> (Tensor, Tensor)", &sample_rows);
+  m.def("symm_alloc(int nbytes) -> Tensor", &symm_alloc);
+  m.def("symm_handle(Tensor buf) -> Tensor", &symm_handle);
+  m.def("symm_open(Tensor handle) -> int", &symm_open);
+  m.def("symm_close(int ptr) -> ()", &symm_close);
+  m.def("dp_step(int[] grads, int[] reduced, int[] flags, int[] scalars, int rank, int world, int barrier_world, int own_lo, int own_hi, int n, int epoch, float pre_scale, float uncovered_local, Tensor tables, int off_blk_tensor, int off_blk_off, int off_blk_flat, int n_blocks, int chunk, float lr, float b1, float b2, float eps, float wd, int step, float max_norm, Tensor(a!) block_partials, Tensor(b!) out, Tensor(c!) abort_word, float limit_s) -> ()", &dp_step);
+  m.def("dp_tables(Tensor[] params, Tensor[] m, Tensor[] v, int[] flat_off, int chunk) -> (Tensor, int, int, int, int)", &dp_tables);
+  m.def("symm_all_reduce(int[] src, int[] flags, Tensor(a!) out, int rank, int world, int epoch, float limit_s, Tensor(b!) abort_word) -> ()", &symm_all_reduce);
   m.def("launches() -> int", &launches);
   m.def("add_launches(int n) -> ()", &add_launches);
 }

@@ -109,6 +109,8 @@ def finite_moments(values: Sequence[float]) -> FiniteMoments:
     scale = max(abs(v) for v in vals)
     if scale == 0.0:
         return FiniteMoments(n, 0.0, 0.0, 0.0)
+    if min(vals) == max(vals):  # degenerate group: exact mean, exactly zero spread
+        return FiniteMoments(n, 1.0, vals[0], 0.0)
     # Rewards that are O(1) keep scale == 1 so ordinary arithmetic is bit-equal to
     # the plain numpy ddof=1 computation.
     scale = scale if scale > 1e150 else 1.0

@@ -1,0 +1,139 @@
+"""Symmetric peer-memory heap over NVLink (one process per GPU).
+
+Each rank allocates the same buffers with ``cudaMalloc`` inside the native
+library, exports CUDA IPC handles, exchanges them through the bootstrap
+communicator (``Comm.all_gather_bytes``) and maps every peer's copy.  Kernels
+receive a table of per-rank pointers and read/write peers with plain loads and
+stores; ordering uses flag words in peer memory with bounded waits
+(``csrc/symm/symm.cuh``).  This is the data plane that replaces the reference's
+only collective, a blocking per-tensor ``ncclAllReduce``
+(``crates/ferrl/src/comm/nccl/real.rs:123-189``); NCCL (``TorchDistComm``)
+remains for bootstrap, host control scalars and as the measured baseline.
+
+A kernel that reports a peer-wait timeout leaves ``kernel_status() != 0``;
+``SymmHeap.check`` turns that into ``CommTimeout`` and poisons the heap so no
+further peer collective is attempted (the reference's NCCL path has no timeout
+at all, ``comm/nccl.rs:30-36``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..comm import Comm, CommPoisoned, CommTimeout
+
+FLAG_SLOTS = 8
+MAX_RANKS = 16
+_HEAPS: dict = {}
+
+
+@dataclass
+class SymmBuffer:
+    local: torch.Tensor        # uint8 view of this rank's copy
+    ptrs: list                 # device address of every rank's copy (index = rank)
+
+    def view(self, dtype, numel: Optional[int] = None) -> torch.Tensor:
+        t = self.local.view(dtype)
+        return t if numel is None else t[:numel]
+
+
+class SymmHeap:
+    def __init__(self, comm: Comm, device: torch.device, wait_limit_s: float = 20.0):
+        from ..ops import cuda as C
+        self.C = C
+        self.comm, self.device = comm, device
+        self.rank, self.world = comm.rank, comm.world_size
+        if self.world > MAX_RANKS:
+            raise ValueError(f"symmetric heap supports up to {MAX_RANKS} ranks")
+        self.wait_limit_s = wait_limit_s
+        self.epoch = 0
+        self.poisoned: Optional[str] = None
+        self._opened: list = []
+        with torch.cuda.device(device):
+            self.flags = self.alloc(FLAG_SLOTS * MAX_RANKS * 4)
+            self.abort_word = torch.zeros(1, dtype=torch.int32, device=device)
+        _HEAPS[id(comm)] = self
+
+    def alloc(self, nbytes: int) -> SymmBuffer:
+        nbytes = (nbytes + 255) // 256 * 256
+        lib = self.C.lib()
+        with torch.cuda.device(self.device):
+            local = lib.symm_alloc(nbytes)
+            handle = bytes(lib.symm_handle(local).tolist())
+        handles = self.comm.all_gather_bytes(handle) if self.world > 1 else [handle]
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(local.data_ptr())
+            else:
+                with torch.cuda.device(self.device):
+                    p = int(lib.symm_open(torch.tensor(list(h), dtype=torch.uint8)))
+                self._opened.append(p)
+                ptrs.append(p)
+        if self.world > 1:
+            self.comm.barrier()  # every rank has mapped every peer before anyone uses the buffer
+        return SymmBuffer(local, ptrs)
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+    def guard(self):
+        if self.poisoned is not None:
+            raise CommPoisoned(self.poisoned)
+
+    def check(self, what: str):
+        """Host-side status read after a peer kernel (synchronises the stream)."""
+        st = self.C.kernel_status()
+        if st != 0:
+            self.C.lib().reset_status()
+            self.poisoned = f"{what}: kernel reported status {st} (peer wait timed out)"
+            raise CommTimeout(self.poisoned)
+
+    def all_reduce_(self, buf: SymmBuffer, out: torch.Tensor) -> torch.Tensor:
+        """Sum ``buf`` (same dtype/numel as ``out``) over ranks into ``out``; one-shot, rank-ordered."""
+        self.guard()
+        self.C.lib().symm_all_reduce(buf.ptrs, self.flags.ptrs, out, self.rank, self.world, self.next_epoch(),
+                                     self.wait_limit_s, self.abort_word)
+        return out
+
+    def close(self):
+        lib = self.C.lib()
+        for p in self._opened:
+            lib.symm_close(p)
+        self._opened = []
+        _HEAPS.pop(id(self.comm), None)
+
+
+class SymmAllReducer:
+    """Reusable staging buffer for activation all-reduces under tensor parallelism."""
+
+    def __init__(self, heap: SymmHeap, max_bytes: int):
+        self.heap = heap
+        self.buf = heap.alloc(max_bytes)
+        self.max_bytes = max_bytes
+
+    def __call__(self, x: torch.Tensor) -> Optional[torch.Tensor]:
+        nbytes = x.numel() * x.element_size()
+        if nbytes > self.max_bytes or x.dtype not in (torch.bfloat16, torch.float32) or nbytes % 16:
+            return None
+        stage = self.buf.local[:nbytes].view(x.dtype).view(x.shape)
+        stage.copy_(x)
+        out = torch.empty_like(x, memory_format=torch.contiguous_format)
+        return self.heap.all_reduce_(SymmBuffer(self.buf.local[:nbytes], self.buf.ptrs), out)
+
+
+_REDUCERS: dict = {}
+
+
+def register_all_reducer(comm: Comm, reducer: SymmAllReducer) -> None:
+    _REDUCERS[id(comm)] = reducer
+
+
+def try_all_reduce(x: torch.Tensor, comm: Comm) -> Optional[torch.Tensor]:
+    """Peer-memory all-reduce when a reducer is registered for ``comm``; else ``None``
+    (caller falls back to the ``Comm`` seam)."""
+    r = _REDUCERS.get(id(comm))
+    return None if r is None else r(x)

@@ -7,7 +7,7 @@ per-group and detailed-group forms), ``sample.rs:38-43``, ``data.rs:59-230``.
 from __future__ import annotations
 
 import json
-import math
+import math as _math
 from dataclasses import dataclass
 from typing import Any, Callable, Generic, Hashable, Optional, Sequence, TypeVar
 
@@ -50,7 +50,7 @@ class RewardOutcome:
 
 def validate_reward_values(rewards: Sequence[float]) -> None:
     for r in rewards:
-        if not math.isfinite(r):
+        if not _math.isfinite(r):
             raise RewardError(f"reward function returned a non-finite reward {r!r}")
 
 

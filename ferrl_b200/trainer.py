@@ -449,19 +449,26 @@ class Trainer:
 
     def accumulate_step(self, live: list[LiveItem], window_tokens: float, beta: float, lr: float,
                         stats: WindowStats, agg: dict) -> None:
-        for p in self.params:
-            p.grad = None
+        if self.fused_dp_step is not None:
+            self.fused_dp_step.prepare_grads()   # .grad tensors are views of the peer-visible flat buffer
+        else:
+            for p in self.params:
+                p.grad = None
         for item in live:
             self._item_backward(item, window_tokens, beta, stats, agg)
         # a rank with no live item still joins the reduction with zeros
         for p in self.params:
             if p.grad is None and not live:
                 p.grad = torch.zeros_like(p)
-        missing, nonfinite = grad_coverage(self.params)
-        uncovered = float(len(missing) + len(nonfinite))
         self._phase("grad_reduce_optimizer")
         world = self.comm.world_size
-        if self.fused_dp_step is not None and world > 1 and not missing:
+        if self.fused_dp_step is not None:
+            missing = self.fused_dp_step.missing() if live else []
+            nonfinite = []                       # counted inside the kernel, world-wide
+        else:
+            missing, nonfinite = grad_coverage(self.params)
+        uncovered = float(len(missing) + len(nonfinite))
+        if self.fused_dp_step is not None:
             # fused peer-memory path: all-reduce + clip + AdamW in one pass
             self.opt.set_learning_rate(lr)
             res = self.fused_dp_step(self.opt, [p.grad for p in self.params], self.config.max_grad_norm, uncovered)
