@@ -289,7 +289,7 @@ const char* adamw_multi(const AdamTensor* tab_dev, const int* blk_tensor_dev, co
     sumsq_kernel<<<n_blocks, 256, 0, s>>>(tab_dev, blk_tensor_dev, blk_off_dev, sumsq_dev, chunk);
     count_launch();
   }
-  adamw_kernel<<<n_blocks, 256, 0, s>>>(tab_dev, blk_tensor_dev, blk_off_dev, sumsq_dev, chunk, lr, b1, b2, eps, wd,
+  adamw_kernel<<<n_blocks, 256, 0, s>>>(tab_dev, blk_tensor_dev, blk_off_dev, compute_norm ? sumsq_dev : nullptr, chunk, lr, b1, b2, eps, wd,
                                         bc1_inv, bc2_inv, max_norm, pre_scale, norm_out_dev);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "adamw launch failed";
