@@ -1,0 +1,167 @@
+"""Per-kernel timings at the headline model's shapes, against the measured roofline.
+
+    python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
+
+Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
+larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
+over the measured peaks in ``MEASURED_PEAKS.json`` (fallback 6.65 TB/s, 1.59 PFLOP/s when the
+file is absent).  Shapes follow Qwen3-8B: hidden 4096, 32q/8kv heads of 128, FFN 12288, vocab
+151936; decode batch 128, training micro-batch 16 x 1536 tokens.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["hbm_gbs"] * 1e9, d["bf16_tflops"] * 1e12, "measured"
+    return 6.65e12, 1.59e15, "fallback"
+
+
+class Timer:
+    def __init__(self, iters, flush_bytes=256 << 20):
+        self.iters = iters
+        self.flush = torch.empty(flush_bytes, dtype=torch.uint8, device="cuda")
+
+    def __call__(self, fn, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        ts = []
+        for _ in range(self.iters):
+            self.flush.zero_()                     # evict L2 (126 MB) between timed iterations
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ts.sort()
+        return ts[len(ts) // 2] * 1e-3            # median seconds
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--iters", type=int, default=15)
+    ap.add_argument("--json", default="")
+    args = ap.parse_args()
+    from ferrl_b200.ops import cuda as C
+    only = set(filter(None, args.only.split(",")))
+    want = lambda k: not only or k in only  # noqa: E731
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, flops_peak, src = peaks()
+    T = Timer(args.iters)
+    rows = []
+    bf = torch.bfloat16
+
+    def report(name, secs, bytes_=0, flops=0, note=""):
+        bw = bytes_ / secs if bytes_ else 0
+        fl = flops / secs if flops else 0
+        frac = max(bw / hbm, fl / flops_peak)
+        bound = "mem" if bw / hbm >= fl / flops_peak else "math"
+        rows.append({"kernel": name, "us": secs * 1e6, "GBps": bw / 1e9, "TFLOPs": fl / 1e12,
+                     f"frac_of_{src}": frac, "bound": bound, "note": note})
+        print(f"{name:46s} {secs * 1e6:10.1f} us  {bw / 1e9:8.0f} GB/s  {fl / 1e12:8.1f} TFLOP/s  "
+              f"{100 * frac:5.1f}% of {src} ({bound}) {note}", flush=True)
+
+    H, F, V, D, HQ, HKV = 4096, 12288, 151936, 128, 32, 8
+    if want("gemm"):
+        shapes = [("decode qkv", 128, 6144, H), ("decode o", 128, H, H), ("decode gate_up", 128, 2 * F, H),
+                  ("decode down", 128, H, F), ("decode lm_head", 128, V, H),
+                  ("train qkv", 24576, 6144, H), ("train o", 24576, H, H), ("train gate_up", 24576, 2 * F, H),
+                  ("train down", 24576, H, F), ("square 8192", 8192, 8192, 8192)]
+        for name, M, N, K in shapes:
+            a = torch.randn(M, K, device=dev, dtype=bf)
+            b = torch.randn(N, K, device=dev, dtype=bf) * 0.02
+            for bn in ([0] if M > 128 else [0, 64, 128]):
+                s = T(lambda: C.gemm(a, b, force_bn=bn))
+                report(f"gemm {name} M{M} N{N} K{K} bn{bn or 'auto'}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+            s = T(lambda: torch.matmul(a, b.t()))
+            report(f"  cuBLAS same shape (library reference)", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+            del a, b
+        M, N, K, R = 24576, 6144, H, 48
+        a = torch.randn(M, K, device=dev, dtype=bf)
+        b = torch.randn(N, K, device=dev, dtype=bf) * 0.02
+        a2, b2 = torch.randn(M, R, device=dev, dtype=bf), torch.randn(N, R, device=dev, dtype=bf)
+        s = T(lambda: C.gemm(a, b, a2, b2))
+        report("gemm train qkv + LoRA k-slab (R=48)", s, 2 * (M * K + N * K + M * N), 2 * M * N * (K + R))
+        del a, b, a2, b2
+    if want("attn"):
+        B, S = 16, 1536
+        q = torch.randn(B, S, HQ, D, device=dev, dtype=bf, requires_grad=True)
+        k = torch.randn(B, S, HKV, D, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(B, S, HKV, D, device=dev, dtype=bf, requires_grad=True)
+        fl = 4 * B * HQ * S * S * D / 2
+        with torch.no_grad():
+            s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True))
+        report(f"flash fwd B{B} S{S} causal", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        o = C.attention(q, k, v, scale=D ** -0.5, causal=True)
+        do = torch.randn_like(o)
+        s = T(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))
+        report(f"flash bwd B{B} S{S} causal", s, 0, 3.5 * fl, "7 matmuls / 2 of fwd's 2")
+        Bd, Smax = 128, 1536
+        qd = torch.randn(Bd, HQ, D, device=dev, dtype=bf)
+        kc = torch.randn(Bd, Smax, HKV, D, device=dev, dtype=bf)
+        vc = torch.randn(Bd, Smax, HKV, D, device=dev, dtype=bf)
+        lens = torch.full((Bd,), 832, device=dev, dtype=torch.int32)
+        s = T(lambda: C.decode_attention(qd, kc, vc, lens, scale=D ** -0.5))
+        report("decode attention B128 len832", s, 2 * Bd * 832 * HKV * D * 2, 4 * Bd * HQ * 832 * D)
+    if want("rows"):
+        x = torch.randn(24576, H, device=dev, dtype=bf)
+        r = torch.randn(24576, H, device=dev, dtype=bf)
+        w = torch.ones(H, device=dev, dtype=bf)
+        with torch.no_grad():
+            s = T(lambda: C.rmsnorm(x, w, 1e-6))
+            report("rmsnorm 24576x4096", s, 2 * x.numel() * 2)
+            s = T(lambda: C.add_rmsnorm(x, r, w, 1e-6))
+            report("add_rmsnorm 24576x4096", s, 4 * x.numel() * 2)
+            gu = torch.randn(24576, 2 * F, device=dev, dtype=bf)
+            s = T(lambda: C.swiglu(gu))
+            report("swiglu 24576x24576", s, 3 * 24576 * F * 2)
+            del gu
+            xd = torch.randn(128, H, device=dev, dtype=bf)
+            s = T(lambda: C.rmsnorm(xd, w, 1e-6))
+            report("rmsnorm decode 128x4096 (launch bound)", s, 2 * xd.numel() * 2)
+    if want("vocab"):
+        logits = torch.randn(128, V, device=dev, dtype=bf)
+        rows_ = torch.arange(128, device=dev)
+        s = T(lambda: C.sample_top_p(logits, 1, rows_, 0, 1.0, 0.95))
+        report("sample top-p 128 x 151936", s, logits.numel() * 2)
+        s = T(lambda: C.sample_top_p(logits, 1, rows_, 0, 1.0, None))
+        report("sample (no nucleus) 128 x 151936", s, logits.numel() * 2)
+        N = 4096
+        lg = torch.randn(N, V, device=dev, dtype=bf)
+        tg = torch.randint(0, V, (N,), device=dev)
+        s = T(lambda: C.lib().logprob_rows(lg, tg, 1.0, 0.0))
+        report("logprob rows 4096 x 151936", s, lg.numel() * 2)
+    if want("opt"):
+        shapes = [(16, 4096)] * 252 + [(4096, 16)] * 252
+        p = [torch.randn(s_, device=dev) for s_ in shapes]
+        g = [torch.randn(s_, device=dev) for s_ in shapes]
+        m = [torch.zeros(s_, device=dev) for s_ in shapes]
+        v = [torch.zeros(s_, device=dev) for s_ in shapes]
+        n = sum(t.numel() for t in p)
+        s = T(lambda: C.adamw_step(p, g, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1,
+                                   max_norm=1.0, compute_norm=True))
+        report(f"adamw + norm + clip, {len(p)} tensors {n / 1e6:.1f}M", s, n * 4 * 8)
+    if args.json:
+        with open(args.json, "w") as f:
+            json.dump({"peaks": {"hbm_Bps": hbm, "bf16_flops": flops_peak, "source": src}, "rows": rows}, f, indent=1)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -87,9 +87,12 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
                    float* __restrict__ lp_out, int V, float inv_t, float top_p) {
   __shared__ float red[32];
   __shared__ unsigned long long hist[256];
-  __shared__ unsigned long long scan[ST];
   __shared__ unsigned long long sh_u64[4];
   __shared__ unsigned int sh_u32[2];
+  // dynamic: 32 warp-private histograms of 256 u64 (64 KB); the first 8 KB double as the scan array later
+  extern __shared__ __align__(16) unsigned long long dyn[];
+  unsigned long long* whist = dyn + (threadIdx.x >> 5) * 256;
+  unsigned long long* scan = dyn;
   const long long row = blockIdx.x;
   const T* x = logits + row * ld;
   const int tid = threadIdx.x;
@@ -124,15 +127,35 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
     unsigned long long above = 0;
     for (int pass = 0; pass < 4; ++pass) {
       const int shift = 24 - 8 * pass;
-      for (int i = tid; i < 256; i += ST) hist[i] = 0;
+      for (int i = tid; i < 32 * 256; i += ST) dyn[i] = 0;
       __syncthreads();
-      for (int i = tid; i < V; i += ST) {
-        float e = e_of(i);
-        unsigned int key = __float_as_uint(e);
-        if (pass == 0 || (key >> (shift + 8)) == prefix) {
-          unsigned long long f = fix_of(e);
-          if (f) atomicAdd(&hist[(key >> shift) & 0xFF], f);
+      // Each warp fills its own histogram. Lanes that hit the same bucket are combined with
+      // match_any + two 32-bit warp reductions (mass < 2^40 split into 20-bit halves), and the
+      // group's lowest lane does a plain read-modify-write: no atomics, no cross-warp contention.
+      for (int i0 = 0; i0 < V; i0 += ST) {
+        const int i = i0 + tid;
+        unsigned int bucket = 0xFFFFFFFFu;
+        unsigned long long f = 0;
+        if (i < V) {
+          float e = e_of(i);
+          unsigned int key = __float_as_uint(e);
+          if (pass == 0 || (key >> (shift + 8)) == prefix) {
+            f = fix_of(e);
+            if (f) bucket = (key >> shift) & 0xFF;
+          }
         }
+        const unsigned int gm = __match_any_sync(0xffffffffu, bucket);
+        const unsigned int lo = __reduce_add_sync(gm, static_cast<unsigned int>(f & 0xFFFFFu));
+        const unsigned int hi = __reduce_add_sync(gm, static_cast<unsigned int>(f >> 20));
+        if (bucket != 0xFFFFFFFFu && (tid & 31) == (__ffs(gm) - 1))
+          whist[bucket] += (static_cast<unsigned long long>(hi) << 20) + lo;
+        __syncwarp();
+      }
+      __syncthreads();
+      if (tid < 256) {
+        unsigned long long t = 0;
+        for (int w = 0; w < 32; ++w) t += dyn[w * 256 + tid];
+        hist[tid] = t;
       }
       __syncthreads();
       if (tid == 0) {
@@ -170,6 +193,7 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
     float e = e_of(i);
     if (__float_as_uint(e) >= thresh_key) mine += fix_of(e);
   }
+  __syncthreads();
   scan[tid] = mine;
   __syncthreads();
   // Hillis-Steele inclusive scan (1024 entries, 10 steps)
@@ -252,11 +276,19 @@ const char* sample_rows(int dtype, const void* logits, long long ld, const long 
                         int rows, int V, float temperature, float top_p, cudaStream_t s) {
   if (rows == 0) return nullptr;
   float inv_t = 1.f / temperature;
+  constexpr size_t kDyn = 32 * 256 * sizeof(unsigned long long);
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(sample_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDyn));
+    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(kDyn));
+    attr = true;
+  }
   if (dtype == kF32)
-    sample_rows_kernel<float><<<rows, ST, 0, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
+    sample_rows_kernel<float><<<rows, ST, kDyn, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
                                                   draw_host, tok_out, lp_out, V, inv_t, top_p);
   else
-    sample_rows_kernel<__nv_bfloat16><<<rows, ST, 0, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
+    sample_rows_kernel<__nv_bfloat16><<<rows, ST, kDyn, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
                                                           seed, draw_dev, draw_host, tok_out, lp_out, V, inv_t, top_p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "sample_rows launch failed";
