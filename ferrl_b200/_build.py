@@ -21,6 +21,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 CSRC = os.path.join(ROOT, "csrc")
 BUILD = os.path.join(ROOT, "build")
 SO_PATH = os.path.join(ROOT, "ferrl_b200", "_C.so")
+LAUNCHER_SRC = os.path.join(CSRC, "native", "sandbox_launcher.cpp")
+LAUNCHER_BIN = os.path.join(ROOT, "ferrl_b200", "bin", "ferrl-sandbox-launch")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
@@ -51,6 +53,14 @@ def _run(cmd, log_path=None):
     return res
 
 
+def build_launcher(force: bool = False) -> str:
+    """Standalone host binary (no CUDA, no torch): the sandbox supervisor."""
+    os.makedirs(os.path.dirname(LAUNCHER_BIN), exist_ok=True)
+    if force or not os.path.exists(LAUNCHER_BIN) or os.path.getmtime(LAUNCHER_BIN) < os.path.getmtime(LAUNCHER_SRC):
+        _run(["g++", "-O2", "-std=c++17", "-o", LAUNCHER_BIN, LAUNCHER_SRC])
+    return LAUNCHER_BIN
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     import torch
     from torch.utils import cpp_extension as ce
@@ -58,7 +68,9 @@ def build(force: bool = False, verbose: bool = False) -> str:
     headers = glob.glob(os.path.join(CSRC, "**", "*.h"), recursive=True) + \
         glob.glob(os.path.join(CSRC, "**", "*.cuh"), recursive=True)
     cu = sorted(glob.glob(os.path.join(CSRC, "**", "*.cu"), recursive=True))
-    cpp = sorted(glob.glob(os.path.join(CSRC, "**", "*.cpp"), recursive=True))
+    cpp = sorted(p for p in glob.glob(os.path.join(CSRC, "**", "*.cpp"), recursive=True)
+                 if os.sep + "native" + os.sep not in p)   # csrc/native holds standalone host programs
+    build_launcher(force)
     nvcc = _nvcc()
     cuda_home = os.path.dirname(os.path.dirname(nvcc))
     inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{os.path.join(cuda_home, 'include')}"]

@@ -506,15 +506,24 @@ class Trainer:
         self._phase_end("grad_reduce_optimizer")
 
     # ---------------------------------------------------------------- window
-    def run_window(self, step: int, lr: float, beta: float) -> tuple[Metrics, int]:
+    def collect_window(self, step: int) -> list:
+        """Rollout + reward half of a window: ``[(accum_index, [CollectedGroup, ...]), ...]``."""
+        c = self.config
+        P = c.prompts_per_item
+        out = []
+        for j in range(c.grad_accum_steps):
+            sels = [self.select_prompt(step, j * P + q) for q in range(P)]
+            out.append((j, self.collect_groups(sels)))
+        return out
+
+    def run_window(self, step: int, lr: float, beta: float, collected: Optional[list] = None) -> tuple[Metrics, int]:
         c = self.config
         stats = WindowStats()
         live: list[LiveItem] = []
         all_groups: list[CollectedGroup] = []
-        P = c.prompts_per_item
-        for j in range(c.grad_accum_steps):
-            sels = [self.select_prompt(step, j * P + q) for q in range(P)]
-            groups = self.collect_groups(sels)
+        if collected is None:
+            collected = self.collect_window(step)
+        for j, groups in collected:
             all_groups += groups
             item = self.materialize(groups, beta, stats)
             if item is not None:
@@ -684,6 +693,62 @@ class Trainer:
         if self.comm.world_size > 1:
             flag = self.comm.all_reduce_scalar_sum(flag)
         return flag > 0
+
+    # ------------------------------------------------ separated collector / learner
+    def collect_to_ledger(self, step: int, writer) -> "object":
+        """Collector side: roll out and score window ``step`` and persist it; no update.
+        Under data parallelism every rank stages its shard and rank 0 commits the manifest
+        once all shards exist (reference trainer.rs:2211-2679, rollout_ledger.rs:676-1110)."""
+        import json as _json
+        from . import ledger as L
+        c = self.config
+        collected = self.collect_window(step)
+        ctl = L.LedgerControls(c.grad_accum_steps, c.prompts_per_item, c.group_size, c.max_new_tokens,
+                               c.reward_group_scope, c.scale_rewards, c.eos_token_id, c.truncation_masking,
+                               L.f64_bits(c.lr_at(step)), L.f64_bits(c.beta_at(step)))
+        groups = [L.LedgerGroup.from_collected(j, g) for j, gs in collected for g in gs]
+        tokens = sum(g.completion_tokens for _, gs in collected for g in gs)
+        st = L.LedgerStep(step, self.comm.rank, self.comm.world_size, ctl, tokens,
+                          sum(1 for _, gs in collected for g in gs if g.live), list(self.policy.sampler_state()), groups)
+        entry = self.comm.coordinate(lambda: writer.stage_step(st), "ledger shard write") \
+            if self.comm.world_size > 1 else writer.stage_step(st)
+        entries = [_json.loads(b.decode()) for b in self.comm.all_gather_bytes(_json.dumps(entry).encode())]
+        if self.is_writer:
+            writer.commit(entries)
+        if self.comm.world_size > 1:
+            self.comm.barrier()
+        return st
+
+    def train_from_ledger(self, record) -> Metrics:
+        """Learner side: run the update of a previously collected window (this rank's shard)."""
+        from . import ledger as L
+        c = self.config
+        if record.controls.group_size != c.group_size or record.controls.completion_width != c.max_new_tokens:
+            raise TrainerError("ledger step was collected under different group_size / max_new_tokens")
+        if record.world_size != self.comm.world_size or record.rank != self.comm.rank:
+            raise TrainerError("ledger shard belongs to a different rank/world")
+        by_item: dict = {}
+        for g in record.groups:
+            r = g.rollout()
+            sel = PromptSelection(g.prompt_index % len(self.samples), g.prompt_index, g.rollout_global_row_base)
+            cg = CollectedGroup(sel, self.samples[sel.sample_idx], list(g.prompt_token_ids), r, [], g.rewards(), [],
+                                g.advantages(), g.mask(), 0, int(sum(r.completion_lens)))
+            by_item.setdefault(g.accum_index, []).append(cg)
+        collected = sorted(by_item.items())
+        lr, beta = L.bits_f64(record.controls.effective_lr_bits), L.bits_f64(record.controls.effective_beta_bits)
+        dev = self.policy.device()
+        self._timer = PhaseTimer(dev)
+        self._probe = GpuMemoryProbe(False)
+        t0 = time.perf_counter()
+        m, local_tokens = self.run_window(record.step, lr, beta, collected)
+        m.phase_ms = self._timer.collect()
+        m.step_secs = time.perf_counter() - t0
+        m.tokens_per_sec = local_tokens / m.step_secs if m.step_secs > 0 else 0.0
+        self.policy.restore_sampler_state(bytes(record.post_rollout_sampler_state))
+        self.history.append(m)
+        if self.metrics_writer is not None:
+            self.metrics_writer.append(m)
+        return m
 
     # ---------------------------------------------------------- checkpoints
     def _has_checkpoint(self, step: int) -> bool:
