@@ -235,3 +235,56 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
 }
 
 }  // namespace ferrl
+
+// ------------------------------------------------------------------------------------------------
+// Allocation-free entry point (declared and documented in csrc/no_alloc.h).
+#include "../no_alloc.h"
+
+namespace {
+// Split-KV workspace that lives in the library image: callers that may not allocate use this
+// instead of a caller-provided buffer. In host code the name below is only a handle for
+// cudaGetSymbolAddress - it is not a device address and must never be handed to a kernel.
+static __device__ __align__(256) float g_static_decode_ws[FERRL_STATIC_WS_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* g_static_ws_addr[kMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int ferrl_decode_attn_static_ws(const void* q, const void* k_cache, const void* v_cache, const int* kv_len,
+                                           void* out, int B, int Hq, int Hkv, int D, long long seq_stride,
+                                           long long tok_stride, float scale, int window, int n_splits, void* stream) {
+  if (!q || !k_cache || !v_cache || !kv_len || !out || B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || n_splits < 1 ||
+      n_splits > 16 || (Hq % Hkv) || (Hq / Hkv) > 8 || (D % 8) || D > 256)
+    return FERRL_NOALLOC_BAD_ARGS;
+  if (B == 0) return FERRL_NOALLOC_OK;
+  const unsigned long long need =
+      n_splits > 1 ? static_cast<unsigned long long>(B) * Hq * n_splits * (D + 2) : 0ull;
+  if (need > FERRL_STATIC_WS_FLOATS) return FERRL_NOALLOC_TOO_LARGE;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FERRL_NOALLOC_CUDA_ERROR;
+  if (!g_static_ws_addr[dev]) {
+    // once per device, with that device current: turn the symbol into its device address
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_decode_ws) != cudaSuccess || !p)
+      return FERRL_NOALLOC_CUDA_ERROR;
+    g_static_ws_addr[dev] = p;
+  }
+  ferrl::DecodeAttnArgs a{};
+  a.q = q; a.k = k_cache; a.v = v_cache; a.kv_len = kv_len; a.block_table = nullptr; a.bt_stride = 0; a.page = 0;
+  a.out = out; a.workspace = n_splits > 1 ? g_static_ws_addr[dev] : nullptr;
+  a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.seq_stride = seq_stride; a.tok_stride = tok_stride;
+  a.scale = scale; a.window = window; a.n_splits = n_splits;
+  return ferrl::decode_attn(a, static_cast<cudaStream_t>(stream)) == nullptr ? FERRL_NOALLOC_OK
+                                                                             : FERRL_NOALLOC_CUDA_ERROR;
+}
+
+extern "C" const char* ferrl_noalloc_strerror(int code) {
+  switch (code) {
+    case FERRL_NOALLOC_OK: return "ok";
+    case FERRL_NOALLOC_TOO_LARGE:
+      return "B*Hq*n_splits*(D+2) exceeds the 4Mi-float static workspace; use fewer splits or a smaller batch";
+    case FERRL_NOALLOC_BAD_ARGS: return "null pointer or unsupported geometry (need Hq%Hkv==0, Hq/Hkv<=8, D%8==0, D<=256, 1<=n_splits<=16)";
+    case FERRL_NOALLOC_CUDA_ERROR: return "a CUDA call failed (device query, symbol address lookup or kernel launch)";
+    default: return "unknown code";
+  }
+}
