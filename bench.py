@@ -105,7 +105,7 @@ def build_trainer(args, comm, device):
     else:  # reduced geometry for bring-up only; never used for a reported number
         spec = DenseSpec(vocab_size=32768, hidden_size=1024, num_hidden_layers=4, num_attention_heads=8,
                          num_key_value_heads=2, head_dim=128, intermediate_size=3072, max_position_embeddings=max_pos)
-    model = DenseGradModel(spec, LoraSpec(16, 32.0), dtype=torch.bfloat16, device=device, remat=True)
+    model = DenseGradModel(spec, LoraSpec(16, 32.0), dtype=torch.bfloat16, device=device, remat=bool(args.remat))
     model.init_random(seed=1234, std=0.02)
     # non-zero B so the adapter path carries signal from the first step (same on every rank)
     g = torch.Generator().manual_seed(99)
@@ -147,7 +147,8 @@ def main():
     ap.add_argument("--max-new", type=int, default=1024)
     ap.add_argument("--prompt-lo", type=int, default=128)
     ap.add_argument("--prompt-hi", type=int, default=512)
-    ap.add_argument("--microbatch", type=int, default=16)
+    ap.add_argument("--microbatch", type=int, default=8, help="rows per scoring/backward micro-batch")
+    ap.add_argument("--remat", type=int, default=0, help="1 = recompute layer activations in backward (less memory)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--nccl-baseline", action="store_true", help="use per-tensor NCCL all-reduce instead of the fused DP step")
     args = ap.parse_args()
@@ -246,6 +247,8 @@ def main():
                     "d2h_bytes_per_step": (policy.d2h_bytes + 64) // args.steps},
             "gpu_launches": int(launches),
             "phase_ms_per_step": {k: round(v / args.steps, 2) for k, v in phase.items()},
+            "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+            "remat": bool(args.remat), "microbatch_rows": args.microbatch,
         }
         print(json.dumps(out))
     if world > 1:

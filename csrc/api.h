@@ -21,7 +21,10 @@ struct GemmArgs {
   int* status;                                                    // device status word (kStatus*)
   int num_sms;
   int force_bn;                                                   // 0 = heuristic
+  int split_k;                                                    // <= 1: none
+  float* partial;                                                 // [split_k, M, N] fp32 scratch when split_k > 1
 };
+void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out);
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 int gemm_pick_bn(int M, int N, int num_sms);
 

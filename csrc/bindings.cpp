@@ -64,7 +64,7 @@ void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(in
 
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
-            const optional<Tensor>& residual, bool out_f32, int64_t force_bn) {
+            const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
@@ -90,6 +90,17 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
   }
   a.status = status_word(); a.num_sms = num_sms(); a.force_bn = static_cast<int>(force_bn);
+  int bn = 0, split = 1;
+  ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split);
+  if (force_bn == 0) a.force_bn = bn;
+  if (force_split > 0) split = static_cast<int>(force_split);
+  else if (force_bn != 0) split = 1;
+  Tensor partial;
+  if (split > 1) {
+    partial = at::empty({split, a.M, a.N}, A.options().dtype(at::kFloat));
+    a.partial = partial.data_ptr<float>();
+    a.split_k = split;
+  }
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
   return out;
 }
@@ -515,7 +526,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn) -> Tensor", &gemm);
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split) -> Tensor", &gemm);
   m.def("kernel_status() -> int", &kernel_status);
   m.def("reset_status() -> ()", &reset_status);
   m.def("rmsnorm(Tensor x, Tensor? res, Tensor? w, Tensor? gate, float eps, bool zc) -> (Tensor, Tensor)", &rmsnorm);

@@ -41,6 +41,9 @@ struct GemmParams {
   long long ldo, ldr;
   int* status;          // device status word
   int group_m;
+  int split_k;          // > 1: each tile covers a slice of the k-tiles and writes fp32 partials
+  int kb_per_split;
+  float* partial;       // [split_k, M, N] fp32 when split_k > 1
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -150,7 +153,7 @@ template <int BN> struct Cfg {
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
+__device__ __forceinline__ void tile_coords_mn(int tile, int m_tiles, int n_tiles, int group_m, int& mi, int& ni) {
   int per_group = group_m * n_tiles;
   int g = tile / per_group;
   int first_m = g * group_m;
@@ -158,6 +161,13 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   int in = tile - g * per_group;
   mi = first_m + in % gsz;
   ni = in / gsz;
+}
+
+// tile index -> (k-split, m tile, n tile); splits of one output tile are adjacent so they share L2 lines
+__device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, int group_m, int split_k, int& ks,
+                                            int& mi, int& ni) {
+  ks = tile % split_k;
+  tile_coords_mn(tile / split_k, m_tiles, n_tiles, group_m, mi, ni);
 }
 
 // OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
@@ -180,7 +190,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int lane = threadIdx.x & 31;
   const int m_tiles = (p.M + BM - 1) / BM;
   const int n_tiles = (p.N + BN - 1) / BN;
-  const int total_tiles = m_tiles * n_tiles;
+  const int total_tiles = m_tiles * n_tiles * p.split_k;
   const int kb1 = (p.K + BK - 1) / BK;
   const int kb2 = (p.K2 + BK - 1) / BK;
   const int kb_total = kb1 + kb2;
@@ -215,9 +225,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, p.group_m, mi, ni);
-        for (int kb = 0; kb < kb_total; ++kb) {
+        int ks, mi, ni;
+        tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
             ok = false;
             break;
@@ -258,7 +269,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         acc_phase[acc] ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kb_total; ++kb) {
+        const int ks = tile % p.split_k;
+        const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
@@ -271,7 +284,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
             // advance 32 bytes (16 bf16) inside the 128-byte swizzle row: +2 in 16-byte units
-            umma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+            umma(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
           }
           umma_commit(&empty[stage]);  // frees the smem stage when these MMAs retire
           if (++stage == C::STAGES) {
@@ -288,8 +301,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     uint32_t acc_phase[2] = {0, 0};
     int it = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
-      int mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, p.group_m, mi, ni);
+      int ks, mi, ni;
+      tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       const int acc = it & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue)) break;
       acc_phase[acc] ^= 1;
@@ -302,6 +315,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c, r);
         tmem_ld_wait();
         const int col = ni * BN + c;
+        if (p.split_k > 1) {
+          // fp32 partial of this k-slice; residual and the output cast happen in the reduce kernel
+          if (row_ok && col < p.N) {
+            const int ncols = min(32, p.N - col);
+            float* op = p.partial + (static_cast<long long>(ks) * p.M + row) * p.N + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(op)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+              for (int e = 0; e < ncols; ++e) op[e] = __uint_as_float(r[e]);
+            }
+          }
+          continue;
+        }
         if (row_ok && col < p.N) {
           const int ncols = min(32, p.N - col);
           if (HAS_RES) {
@@ -367,6 +395,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   }
 }
 
+// out[r,c] = sum_s partial[s,r,c] (+ residual), summed in split order (deterministic)
+template <bool OUT_F32>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __restrict__ out, long long ldo,
+                                     const __nv_bfloat16* __restrict__ residual, long long ldr, int M, int N,
+                                     int split_k) {
+  const long long n4 = static_cast<long long>(M) * (N / 4);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n4;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / (N / 4));
+    const int col = static_cast<int>(i - static_cast<long long>(row) * (N / 4)) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < split_k; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partial + (static_cast<long long>(s) * M + row) * N + col);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (residual) {
+      const __nv_bfloat16* rp = residual + static_cast<long long>(row) * ldr + col;
+      acc.x += __bfloat162float(rp[0]); acc.y += __bfloat162float(rp[1]);
+      acc.z += __bfloat162float(rp[2]); acc.w += __bfloat162float(rp[3]);
+    }
+    if (OUT_F32) {
+      *reinterpret_cast<float4*>(static_cast<float*>(out) + static_cast<long long>(row) * ldo + col) = acc;
+    } else {
+      __nv_bfloat162 a = __floats2bfloat162_rn(acc.x, acc.y), b = __floats2bfloat162_rn(acc.z, acc.w);
+      uint2 o;
+      o.x = *reinterpret_cast<uint32_t*>(&a);
+      o.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + static_cast<long long>(row) * ldo + col) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -415,6 +475,13 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
   p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 16;
+  const int kb_total = (a.K + BK - 1) / BK + (a.K2 + BK - 1) / BK;
+  int split = a.split_k > 1 ? a.split_k : 1;
+  if (split > kb_total) split = kb_total;
+  p.kb_per_split = (kb_total + split - 1) / split;
+  p.split_k = (kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no empty slices
+  p.partial = a.partial;
+  if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   auto kern = gemm_kernel<BN, OUT_F32, HAS_RES>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -423,11 +490,20 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     attr_set = true;
   }
   int m_tiles = (a.M + BM - 1) / BM, n_tiles = (a.N + BN - 1) / BN;
-  int tiles = m_tiles * n_tiles;
+  int tiles = m_tiles * n_tiles * p.split_k;
   int grid = tiles < a.num_sms ? tiles : a.num_sms;
   if (grid < 1) return nullptr;
   kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
   count_launch();
+  if (p.split_k > 1) {
+    long long n4 = static_cast<long long>(a.M) * (a.N / 4);
+    int rb = static_cast<int>((n4 + 255) / 256 < 148 * 8 ? (n4 + 255) / 256 : 148 * 8);
+    if (OUT_F32)
+      splitk_reduce_kernel<true><<<rb, 256, 0, stream>>>(a.partial, a.out, a.ldo, p.residual, a.ldr, a.M, a.N, p.split_k);
+    else
+      splitk_reduce_kernel<false><<<rb, 256, 0, stream>>>(a.partial, a.out, a.ldo, p.residual, a.ldr, a.M, a.N, p.split_k);
+    count_launch();
+  }
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }
 
@@ -451,6 +527,34 @@ int gemm_pick_bn(int M, int N, int num_sms) {
     if (tiles >= num_sms || bn == 32) return bn;
   }
   return 32;
+}
+
+// Decode-shaped problems (one or two M tiles) are bound by how many bytes each SM has to pull
+// through its TMA path, not by HBM: pick the tile width and k-split that minimise the bytes of the
+// busiest SM (A slice + B slice per tile, times the number of waves) plus the cost of the reduce.
+void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out) {
+  const int m_tiles = (M + BM - 1) / BM;
+  *bn_out = gemm_pick_bn(M, N, num_sms);
+  *split_out = 1;
+  if (m_tiles > 2 || (N % 4)) return;
+  const int kb_total = (K + BK - 1) / BK + (K2 + BK - 1) / BK;
+  double best = 1e30;
+  const int cands[3] = {256, 128, 64};
+  for (int ci = 0; ci < 3; ++ci) {
+    const int bn = cands[ci];
+    if (N < bn) continue;
+    const int n_tiles = (N + bn - 1) / bn;
+    for (int split = 1; split <= 16 && split <= kb_total; ++split) {
+      const int per = (kb_total + split - 1) / split;
+      const int eff = (kb_total + per - 1) / per;
+      const long long tiles = static_cast<long long>(m_tiles) * n_tiles * eff;
+      const long long waves = (tiles + num_sms - 1) / num_sms;
+      double bytes = static_cast<double>(waves) * (BM + bn) * per * BK * 2.0;
+      double t = bytes / 64e9 + 2e-6 * waves;                      // ~64 GB/s per SM through TMA
+      if (eff > 1) t += 3e-6 + static_cast<double>(M) * N * 4.0 * (eff + 1) / 5e12;   // partial write + reduce
+      if (t < best) { best = t; *bn_out = bn; *split_out = eff; }
+    }
+  }
 }
 
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {

@@ -174,6 +174,187 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 }
 
+// Fast path for head_dim 64 / 128 / 256.  LPK = D/16 lanes cooperate on one key, each owning 16
+// channels: q (all `rep` heads) and the output accumulators live in registers, K and V rows are
+// read with two coalesced 16-byte loads per lane, and four keys per lane group are in flight at
+// once (no shared memory in the loop).  Every lane group keeps its own running (max, sum, out)
+// and the groups are merged once at the end: across groups by shuffle, across warps through
+// shared memory, across kv-splits through the workspace.
+template <int D, int REP>
+__global__ void __launch_bounds__(WARPS * 32)
+decode_attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                        const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
+                        const int* __restrict__ block_table, int bt_stride, int page,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
+                        long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  constexpr int LPK = D / 16;        // lanes per key
+  constexpr int KPW = 32 / LPK;      // keys per warp per step
+  constexpr int UNROLL = (REP >= 6) ? 2 : 4;   // key steps in flight (bounded by the register file)
+  extern __shared__ float sm[];
+  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, grp = lane / LPK;
+  const int d0 = sub * 16;
+
+  float qr[REP][16];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * REP + r) * D + d0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) qr[r][e] = __bfloat162float(qp[e]) * scale;
+  }
+  const int len = kv_len[b];
+  const int lo = (window > 0 && len > window) ? len - window : 0;
+  const int span = len - lo;
+  const int per = (span + n_splits - 1) / n_splits;
+  const int s0 = lo + split * per;
+  const int s1 = min(len, s0 + per);
+
+  float m_run[REP], l_run[REP], o[REP][16];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) o[r][e] = 0.f;
+  }
+
+  auto row_of = [&](int j) -> long long {
+    if (block_table) {
+      int pg = block_table[static_cast<long long>(b) * bt_stride + j / page];
+      return (static_cast<long long>(pg) * page + (j % page)) * tok_stride + hk * D + d0;
+    }
+    return static_cast<long long>(b) * seq_stride + static_cast<long long>(j) * tok_stride + hk * D + d0;
+  };
+
+  for (int base = s0 + (warp * KPW + grp); base < s1; base += WARPS * KPW * UNROLL) {
+    uint4 kraw[UNROLL][2], vraw[UNROLL][2];
+    bool live[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int j = base + u * WARPS * KPW;
+      live[u] = j < s1;
+      const long long row = live[u] ? row_of(j) : row_of(s0);
+      const uint4* kp = reinterpret_cast<const uint4*>(kc + row);
+      const uint4* vp = reinterpret_cast<const uint4*>(vc + row);
+      kraw[u][0] = kp[0]; kraw[u][1] = kp[1];
+      vraw[u][0] = vp[0]; vraw[u][1] = vp[1];
+    }
+    float sc[UNROLL][REP];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      float kf[16];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&kraw[u][0]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float2 f = __bfloat1622float2(h[e]);
+        kf[2 * e] = f.x;
+        kf[2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        float a = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) a += kf[e] * qr[r][e];
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        sc[u][r] = live[u] ? a : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float mx = m_run[r];
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) mx = fmaxf(mx, sc[u][r]);
+      const float corr = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mx);
+      m_run[r] = mx;
+      l_run[r] *= corr;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o[r][e] *= corr;
+#pragma unroll
+      for (int u = 0; u < UNROLL; ++u) {
+        const float pj = (sc[u][r] == -INFINITY) ? 0.f : __expf(sc[u][r] - mx);
+        sc[u][r] = pj;
+        l_run[r] += pj;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      float vf[16];
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&vraw[u][0]);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float2 f = __bfloat1622float2(h[e]);
+        vf[2 * e] = f.x;
+        vf[2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[r][e] += sc[u][r] * vf[e];
+    }
+  }
+
+  // merge the lane groups of this warp (same channels, different keys)
+#pragma unroll
+  for (int off = LPK; off < 32; off <<= 1) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m_run[r], off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l_run[r], off);
+      const float mn = fmaxf(m_run[r], m2);
+      const float c1 = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mn);
+      const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+      l_run[r] = l_run[r] * c1 + l2 * c2;
+      m_run[r] = mn;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, o[r][e], off);
+        o[r][e] = o[r][e] * c1 + o2 * c2;
+      }
+    }
+  }
+  // merge warps through shared memory
+  float* m_s = sm;                          // [WARPS][REP]
+  float* l_s = m_s + WARPS * REP;           // [WARPS][REP]
+  float* o_s = l_s + WARPS * REP;           // [WARPS][REP][D]
+  if (grp == 0) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      if (sub == 0) {
+        m_s[warp * REP + r] = m_run[r];
+        l_s[warp * REP + r] = l_run[r];
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o_s[(warp * REP + r) * D + d0 + e] = o[r][e];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D;
+    float m = -INFINITY;
+    for (int w = 0; w < WARPS; ++w) m = fmaxf(m, m_s[w * REP + r]);
+    float l = 0.f, acc = 0.f;
+    for (int w = 0; w < WARPS; ++w) {
+      const float mw = m_s[w * REP + r];
+      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+      l += l_s[w * REP + r] * c;
+      acc += o_s[(w * REP + r) * D + d] * c;
+    }
+    const long long head = static_cast<long long>(b) * Hq + hk * REP + r;
+    if (n_splits == 1) {
+      out[head * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      float* w_ = ws + (head * n_splits + split) * (D + 2);
+      w_[d] = acc;
+      if (d == 0) {
+        w_[D] = m;
+        w_[D + 1] = l;
+      }
+    }
+  }
+}
+
 __global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
                                       int n_splits) {
   const long long head = blockIdx.x;
@@ -212,20 +393,40 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
   if (rep > MAX_REP) return "decode_attn: more than 8 query heads per kv head";
   if (a.D % 8 || a.D > 256) return "decode_attn: head_dim must be a multiple of 8 and <= 256";
   if (a.n_splits > 1 && !a.workspace) return "decode_attn: workspace required for split-kv";
-  size_t smem = (static_cast<size_t>(rep) * a.D + 2 * WARPS * rep + static_cast<size_t>(WARPS) * rep * a.D) * 4;
-  auto kern = decode_attn_kernel;
-  if (smem > 48 * 1024) {
-    static bool set = false;
-    if (!set) {
-      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-      set = true;
-    }
-  }
   dim3 grid(a.B, a.Hkv, a.n_splits < 1 ? 1 : a.n_splits);
-  kern<<<grid, WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),
-                                      static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride,
-                                      a.page, static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.D,
-                                      a.seq_stride, a.tok_stride, a.scale, a.window, grid.z);
+  bool launched = false;
+#define FERRL_DECODE_FAST(DD, RR)                                                                                   \
+  if (!launched && a.D == DD && rep == RR) {                                                                          \
+    size_t fsm = (2 * WARPS * RR + static_cast<size_t>(WARPS) * RR * DD) * 4;                                         \
+    decode_attn_fast_kernel<DD, RR><<<grid, WARPS * 32, fsm, s>>>(                                                    \
+        static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
+        static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
+        static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.seq_stride, a.tok_stride, a.scale, a.window,  \
+        grid.z);                                                                                                      \
+    launched = true;                                                                                                  \
+  }
+  if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0) {
+    FERRL_DECODE_FAST(128, 4) FERRL_DECODE_FAST(128, 1) FERRL_DECODE_FAST(128, 2) FERRL_DECODE_FAST(128, 8)
+    FERRL_DECODE_FAST(64, 1) FERRL_DECODE_FAST(64, 2) FERRL_DECODE_FAST(64, 4) FERRL_DECODE_FAST(64, 8)
+    FERRL_DECODE_FAST(256, 1) FERRL_DECODE_FAST(256, 2) FERRL_DECODE_FAST(256, 4) FERRL_DECODE_FAST(256, 6)
+    FERRL_DECODE_FAST(256, 8)
+  }
+#undef FERRL_DECODE_FAST
+  if (!launched) {
+    size_t smem = (static_cast<size_t>(rep) * a.D + 2 * WARPS * rep + static_cast<size_t>(WARPS) * rep * a.D) * 4;
+    auto kern = decode_attn_kernel;
+    if (smem > 48 * 1024) {
+      static bool set = false;
+      if (!set) {
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        set = true;
+      }
+    }
+    kern<<<grid, WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),
+                                        static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride,
+                                        a.page, static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.D,
+                                        a.seq_stride, a.tok_stride, a.scale, a.window, grid.z);
+  }
   count_launch();
   if (grid.z > 1) {
     decode_combine_kernel<<<a.B * a.Hq, 128, 0, s>>>(a.workspace, static_cast<__nv_bfloat16*>(a.out), a.D, grid.z);

@@ -144,11 +144,18 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
             if (f) bucket = (key >> shift) & 0xFF;
           }
         }
-        const unsigned int gm = __match_any_sync(0xffffffffu, bucket);
-        const unsigned int lo = __reduce_add_sync(gm, static_cast<unsigned int>(f & 0xFFFFFu));
-        const unsigned int hi = __reduce_add_sync(gm, static_cast<unsigned int>(f >> 20));
-        if (bucket != 0xFFFFFFFFu && (tid & 31) == (__ffs(gm) - 1))
-          whist[bucket] += (static_cast<unsigned long long>(hi) << 20) + lo;
+        if (pass == 0) {
+          // leading exponent bits: a handful of distinct buckets per warp, so combine equal lanes first
+          const unsigned int gm = __match_any_sync(0xffffffffu, bucket);
+          const unsigned int lo = __reduce_add_sync(gm, static_cast<unsigned int>(f & 0xFFFFFu));
+          const unsigned int hi = __reduce_add_sync(gm, static_cast<unsigned int>(f >> 20));
+          if (bucket != 0xFFFFFFFFu && (tid & 31) == (__ffs(gm) - 1))
+            whist[bucket] += (static_cast<unsigned long long>(hi) << 20) + lo;
+        } else if (bucket != 0xFFFFFFFFu) {
+          // later digits are spread over the 256 buckets and only the selected prefix takes part:
+          // integer atomics on the warp-private histogram rarely collide (and stay order-independent)
+          atomicAdd(&whist[bucket], f);
+        }
         __syncwarp();
       }
       __syncthreads();

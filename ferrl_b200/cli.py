@@ -1,0 +1,221 @@
+"""Command line: ``python -m ferrl_b200.cli <verb> ...``.
+
+Verbs (reference ``crates/ferrl/src/bin/ferrl.rs:116-131``):
+
+    train             --config run.json                  GRPO/LoRA training run
+    score             (trimul-score) score external completions with the TriMul verifier
+    audit             (trimul-artifact) paired-block audit of a run's best candidate
+    report            (runreport) summarise a run directory's metrics and health
+    perf-gate         compare a candidate run's metrics stream against a baseline's
+    trimul-baseline   time the reference kernel to pin ``trimul.baseline.ns``
+    verifier-executor serve the dedicated-UID verifier socket
+
+The reference verb names are accepted as aliases.  Multi-GPU launches use one
+process per GPU (``torchrun`` or Slurm ``srun`` with ``FERRL_NCCL_RENDEZVOUS``);
+the communicator is opened from the environment.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+
+def _comm():
+    from .comm import NcclConfig, SoloComm, TorchDistComm
+    cfg = NcclConfig.from_env()
+    return SoloComm() if cfg is None or cfg.world_size == 1 else TorchDistComm.bootstrap(cfg)
+
+
+def cmd_train(args) -> int:
+    from .config import ConfigError, RunConfig
+    from .orchestration import run_cli_train_setup
+    try:
+        cfg = RunConfig.load(args.config)
+    except ConfigError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
+    comm = _comm()
+    if comm.world_size > 1 and cfg.tensor_parallel.enabled and cfg.distributed.enabled:
+        print("error: data-parallel and tensor-parallel launches cannot be combined", file=sys.stderr)
+        return 2
+    if cfg.tensor_parallel.enabled:
+        cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size = comm.rank, comm.world_size
+    out = run_cli_train_setup(cfg, comm, allow_dirty=args.allow_dirty)
+    if comm.rank == 0:
+        print(json.dumps({"run_dir": out.run_dir, "stop": out.stop, "steps": out.steps_run,
+                          "health": out.health.verdict,
+                          "eval_improvement": None if out.eval_report is None else out.eval_report.improvement(),
+                          "candidates": len(out.candidates)}))
+    return 0 if out.health.verdict != "fail" else 1
+
+
+def _trimul_reward(cfg):
+    from .orchestration import build_task
+    return build_task(cfg)[2]
+
+
+def cmd_score(args) -> int:
+    from .config import RunConfig
+    cfg = RunConfig.load(args.config)
+    if cfg.task != "trimul":
+        print("error: score needs a trimul run config", file=sys.stderr)
+        return 2
+    reward = _trimul_reward(cfg)
+    comps = []
+    for p in args.completion or []:
+        comps.append({"completion": open(p, encoding="utf-8").read(), "source_id": p})
+    for p in args.completions_jsonl or []:
+        for i, line in enumerate(open(p, encoding="utf-8")):
+            if line.strip():
+                d = json.loads(line)
+                d.setdefault("source_id", f"{p}:{i}")
+                comps.append(d)
+    if not comps:
+        print("error: no completions given", file=sys.stderr)
+        return 2
+    outs = reward.reward_group_detailed(None, [c["completion"] for c in comps])
+    with open(args.out, "w", encoding="utf-8") as f:
+        for c, o in zip(comps, outs):
+            f.write(json.dumps({"task": "trimul", "score_scheme": reward.profile.scheme, "run_id": args.run_id,
+                                "step": c.get("step", args.step), "prompt_index": c.get("prompt_index", args.prompt_index),
+                                "source_id": c["source_id"], "reward": o.reward, "reward_diagnostic": o.diagnostic,
+                                "reward_metadata": o.metadata, "completion_len_bytes": len(c["completion"].encode()),
+                                "completion": c["completion"]}, sort_keys=True) + "\n")
+    print(json.dumps({"scored": len(comps), "best": max(o.reward for o in outs), "out": args.out}))
+    return 0
+
+
+def cmd_audit(args) -> int:
+    from .artifact import publish_trimul_artifact
+    from .config import RunConfig
+    from .orchestration import load_and_rank_candidates
+    from .rewards.trimul import extract_submission
+    cands = load_and_rank_candidates(args.run_dir)
+    if not cands:
+        print("error: the run has no authenticated candidates", file=sys.stderr)
+        return 1
+    best = cands[0]
+    src = extract_submission(best.completion)
+    if src is None:
+        print("error: the best candidate contains no extractable submission", file=sys.stderr)
+        return 1
+    cfg = RunConfig.from_json(json.load(open(os.path.join(args.run_dir, "config.json"))))
+    reward = _trimul_reward(cfg)
+
+    def verify(source, seed):
+        import dataclasses
+        reward.cases = [dataclasses.replace(c, seed=seed) for c in reward.cases]
+        return reward.verify_submission(source).correct
+
+    def time_pair(source, first):
+        ev = reward.verify_submission(source)
+        ref = (cfg.trimul.get("baseline") or {}).get("ns") or float("nan")
+        return ref, ev.geomean_ns or float("nan")
+    man = publish_trimul_artifact(args.run_dir, args.out, src, best.reward, verify, time_pair,
+                                  run_health=args.run_health, source_inspection=args.source_inspection,
+                                  source_inspection_notes=args.source_inspection_notes)
+    print(json.dumps({"accepted": man.accepted, "wins": man.decision["observed_material_wins"], "out": args.out}))
+    return 0 if man.accepted else 1
+
+
+def cmd_report(args) -> int:
+    from . import telemetry as T
+    rd = T.RunDir.open(args.run_dir)
+    rows = T.read_metrics(rd.metrics_path) if os.path.exists(rd.metrics_path) else []
+    s = T.summarize(rows)
+    out = {"run_id": rd.run_id, "steps": s.steps, "reward_first": s.reward_first, "reward_last": s.reward_last,
+           "reward_best": s.reward_best, "mean_step_secs": s.mean_step_secs,
+           "mean_tokens_per_sec": s.mean_tokens_per_sec, "final_grad_norm": s.final_grad_norm,
+           "peak_mem_bytes": s.peak_mem_bytes, "healthy": s.healthy(), "anomalies": [str(a) for a in s.anomalies]}
+    if args.json:
+        print(json.dumps(out, sort_keys=True))
+    else:
+        print(f"run {rd.run_id}: {s.steps} steps, reward {s.reward_first:.4f} -> {s.reward_last:.4f} "
+              f"(best {s.reward_best:.4f}), {s.mean_step_secs:.3f} s/step, {s.mean_tokens_per_sec:.1f} tok/s")
+        for a in s.anomalies:
+            print(f"  anomaly: {a}")
+        if s.healthy():
+            print("  healthy")
+    return 0 if s.healthy() else 1
+
+
+def cmd_perf_gate(args) -> int:
+    from . import telemetry as T
+    base = T.read_metrics(os.path.join(args.baseline, T.RunDir.METRICS_FILE))
+    cand = T.read_metrics(os.path.join(args.candidate, T.RunDir.METRICS_FILE))
+    budget = T.RegressionBudget(max_mean_step_secs_ratio=args.max_step_ratio, warmup_steps=args.warmup_steps,
+                                require_cuda_memory=not args.no_memory)
+    rep = T.compare_metrics(base, cand, budget)
+    print(json.dumps({"passed": rep.passed, "failures": rep.failures, "baseline_mean_step_secs": rep.baseline_mean_step_secs,
+                      "candidate_mean_step_secs": rep.candidate_mean_step_secs}, sort_keys=True))
+    return 0 if rep.passed else 1
+
+
+def cmd_trimul_baseline(args) -> int:
+    from .config import RunConfig
+    cfg = RunConfig.load(args.config)
+    reward = _trimul_reward(cfg)
+    ref_path = os.path.join(cfg.trimul["eval_dir"], "reference_submission.py")
+    ev = reward.verify_submission(open(ref_path, encoding="utf-8").read())
+    print(json.dumps({"baseline_ns": ev.geomean_ns, "correct": ev.correct}))
+    return 0 if ev.correct and ev.geomean_ns else 1
+
+
+def cmd_verifier_executor(args) -> int:
+    from .sandbox import ApptainerSandbox
+    from .verifier_executor import serve_verifier_executor
+    os.makedirs(args.work_root, exist_ok=True)
+    serve_verifier_executor(args.socket, ApptainerSandbox(args.apptainer))
+    return 0
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="ferrl-b200")
+    sub = ap.add_subparsers(dest="verb", required=True)
+    p = sub.add_parser("train")
+    p.add_argument("--config", required=True)
+    p.add_argument("--allow-dirty", action="store_true")
+    p.set_defaults(fn=cmd_train)
+    p = sub.add_parser("score", aliases=["trimul-score"])
+    p.add_argument("--config", required=True)
+    p.add_argument("--completion", action="append")
+    p.add_argument("--completions-jsonl", action="append")
+    p.add_argument("--out", required=True)
+    p.add_argument("--run-id", default="external-rollout")
+    p.add_argument("--step", type=int, default=0)
+    p.add_argument("--prompt-index", type=int, default=0)
+    p.set_defaults(fn=cmd_score)
+    p = sub.add_parser("audit", aliases=["trimul-artifact"])
+    p.add_argument("--run-dir", required=True)
+    p.add_argument("--out", required=True)
+    p.add_argument("--run-health", default="ok")
+    p.add_argument("--source-inspection", default="not_performed")
+    p.add_argument("--source-inspection-notes", default="")
+    p.set_defaults(fn=cmd_audit)
+    p = sub.add_parser("report", aliases=["runreport"])
+    p.add_argument("run_dir")
+    p.add_argument("--json", action="store_true")
+    p.set_defaults(fn=cmd_report)
+    p = sub.add_parser("perf-gate")
+    p.add_argument("--baseline", required=True)
+    p.add_argument("--candidate", required=True)
+    p.add_argument("--max-step-ratio", type=float, default=1.10)
+    p.add_argument("--warmup-steps", type=int, default=0)
+    p.add_argument("--no-memory", action="store_true")
+    p.set_defaults(fn=cmd_perf_gate)
+    p = sub.add_parser("trimul-baseline")
+    p.add_argument("--config", required=True)
+    p.set_defaults(fn=cmd_trimul_baseline)
+    p = sub.add_parser("verifier-executor")
+    p.add_argument("--socket", default="/run/ferrl/verifier-executor.sock")
+    p.add_argument("--work-root", default="/var/lib/ferrl/verifier-executor")
+    p.add_argument("--apptainer", default="/usr/bin/apptainer")
+    p.set_defaults(fn=cmd_verifier_executor)
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -47,9 +47,10 @@ def _bf16(t):
 
 
 # ----------------------------------------------------------------- GEMM
-def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0):
-    """``a [M,K] @ b[N,K]^T (+ a2 @ b2^T) (+ residual)`` on the tcgen05 kernel."""
-    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn)
+def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0, force_split=0):
+    """``a [M,K] @ b[N,K]^T (+ a2 @ b2^T) (+ residual)`` on the tcgen05 kernel.
+    Tile width and k-split are planned from the shape unless forced."""
+    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn, force_split)
 
 
 def _pad8(t, dim):

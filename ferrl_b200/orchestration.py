@@ -1,0 +1,314 @@
+"""Run orchestration: from a validated ``RunConfig`` to a finished, provenance-bound run.
+
+Reference ``crates/ferrl/src/orchestration.rs``: launch manifest types
+``:82-470``; ``run_cli_train_setup`` ``:1094-1316`` (config / commit consensus,
+synchronised run id ``<task>-<unix secs>[-rankN]``, device preflight, task data);
+engine stages setup -> preflight -> launch -> train -> health -> eval ->
+candidates ``:1885-1896``; health policy ``:3202-3970``; authenticated candidate
+loading and ranking ``:4020-4560``.
+
+Stages here:
+
+1. ``setup``      build identity + config consensus, run id, device preflight,
+                  task data, policy load, EOS resolution and consensus.
+2. ``launch``     ``LaunchManifest`` (digests of config, policy, tokenizer,
+                  prompts; build identity; candidate signing key) ->
+                  ``RunDir.create`` -> immutable ``launch.json`` / ``config.json``.
+3. ``train``      ``Trainer.resume_latest`` then ``Trainer.train``.
+4. ``health``     ``telemetry.summarize`` + the configured run-health rules;
+                  a ``fail`` finding blocks publication.
+5. ``eval``       held-out base-vs-adapter evaluation -> ``eval-report.json``.
+6. ``candidates`` verify signatures against ``launch.json`` and rank.
+"""
+from __future__ import annotations
+
+import dataclasses
+import hashlib
+import json
+import os
+import time
+from dataclasses import dataclass, field
+from typing import Any, Optional, Sequence
+
+import torch
+
+from . import telemetry as T
+from .build_identity import BuildIdentity, require_clean, source_identity
+from .checkpoint import CheckpointBinding
+from .comm import Comm, SoloComm
+from .config import RunConfig, canonical_digest
+from .eval import EvalReport, evaluate
+from .hf import resolve_eos, validate_resolved_eos_consensus
+from .lm_policy import LmPolicy
+from .models.loader import LoaderOpts, load_auto_policy
+from .models.lora import BaseQuantization, DenseLoraTargets, LoraSpec
+from .policy import GenConfig
+from .rewards import (CountdownConfig, CountdownProblem, CountdownReward, MathProblem, MathReward, Sample, build_prompt,
+                      generate_dataset, math_prompt, read_jsonl, train_eval_split, train_eval_split_by_key)
+from .sampler import GrpoSampler
+from .trainer import RunStop, Trainer
+
+
+class OrchestrationError(RuntimeError):
+    pass
+
+
+@dataclass
+class LaunchManifest:
+    run_id: str
+    task: str
+    config_sha256: str
+    policy_sha256: str
+    tokenizer_sha256: str
+    samples_sha256: str
+    build: dict
+    world_size: int
+    topology: str
+    candidate_public_key: Optional[str]
+    launch_authentication: str
+    created_unix: int
+
+    def to_json(self) -> dict:
+        return dataclasses.asdict(self)
+
+    def digest(self) -> str:
+        return canonical_digest(self.to_json(), b"ferrl-b200/launch-manifest/v1")
+
+
+@dataclass
+class HealthFinding:
+    rule: str
+    action: str     # warn | fail
+    message: str
+
+
+@dataclass
+class HealthReport:
+    verdict: str    # ok | warn | fail
+    findings: list = field(default_factory=list)
+
+
+def evaluate_run_health(rows: Sequence[T.Metrics], rules: dict, candidates: Optional[Sequence] = None) -> HealthReport:
+    """Apply the configured ``run_health`` rules (``reward_collapse``, ``correctness_collapse``
+    ``{window, min, action}``; ``dropped_rows {max, action}``; ``grad_spike {factor, action}``;
+    ``telemetry_dark <action>``; ``source_dominance {max_fraction, action}``)."""
+    out = []
+    summ = T.summarize(rows)
+
+    def act(rule, default="warn"):
+        cfg = rules.get(rule)
+        if cfg is None:
+            return None
+        return cfg if isinstance(cfg, str) else cfg.get("action", default)
+    if not rows:
+        a = act("telemetry_dark") or "fail"
+        out.append(HealthFinding("telemetry_dark", a, "no metrics rows were recorded"))
+    for rule, attr in (("reward_collapse", "reward_mean"), ("correctness_collapse", "reward_mean")):
+        cfg = rules.get(rule)
+        if cfg and len(rows) >= int(cfg["window"]):
+            tail = [getattr(r, attr) for r in rows[-int(cfg["window"]):]]
+            if max(tail) < float(cfg["min"]):
+                out.append(HealthFinding(rule, cfg.get("action", "warn"),
+                                         f"{attr} stayed below {cfg['min']} for the last {cfg['window']} steps"))
+    cfg = rules.get("dropped_rows")
+    if cfg:
+        tot = sum(r.dropped_rows for r in rows)
+        if tot > int(cfg["max"]):
+            out.append(HealthFinding("dropped_rows", cfg.get("action", "warn"), f"{tot} rows dropped (max {cfg['max']})"))
+    cfg = rules.get("grad_spike")
+    if cfg:
+        norms = sorted(r.grad_norm for r in rows if r.grad_norm > 0)
+        if len(norms) >= 3:
+            med = norms[len(norms) // 2]
+            worst = max(norms)
+            if med > 0 and worst > float(cfg["factor"]) * med:
+                out.append(HealthFinding("grad_spike", cfg.get("action", "warn"),
+                                         f"grad_norm {worst:.3f} exceeds {cfg['factor']}x median {med:.3f}"))
+    cfg = rules.get("source_dominance")
+    if cfg and candidates:
+        by = {}
+        for c in candidates:
+            by[c.prompt_index] = by.get(c.prompt_index, 0) + 1
+        frac = max(by.values()) / len(candidates)
+        if frac > float(cfg["max_fraction"]):
+            out.append(HealthFinding("source_dominance", cfg.get("action", "warn"),
+                                     f"one prompt supplies {frac:.0%} of the candidates"))
+    for a in summ.anomalies:
+        if a.kind == "non_finite":
+            out.append(HealthFinding("non_finite", "fail", str(a)))
+    verdict = "fail" if any(f.action == "fail" for f in out) else ("warn" if out else "ok")
+    return HealthReport(verdict, out)
+
+
+def synchronized_run_id(task: str, comm: Comm, suffix_rank: bool = False) -> str:
+    """Rank 0's wall-clock second, shared with every rank."""
+    stamp = comm.broadcast_bytes(str(int(time.time())).encode() if comm.rank == 0 else None, 0).decode() \
+        if comm.world_size > 1 else str(int(time.time()))
+    rid = f"{task}-{stamp}"
+    return f"{rid}-rank{comm.rank}" if suffix_rank else rid
+
+
+def build_task(cfg: RunConfig):
+    """``(train_samples, eval_samples, reward_fn)`` for the configured task."""
+    d = cfg.data
+    if cfg.task == "countdown":
+        if d.path:
+            samples = read_jsonl(d.path, CountdownProblem.from_json)
+        else:
+            probs = generate_dataset(d.seed, d.train_n + d.eval_n, CountdownConfig())
+            samples = [Sample(build_prompt(p), p) for p in probs]
+        train, ev = train_eval_split_by_key(samples, d.eval_n, d.seed, lambda s: (s.target.numbers, s.target.target))
+        return train[:d.train_n] if d.train_n else train, ev, CountdownReward()
+    if cfg.task == "math":
+        if not d.path:
+            raise OrchestrationError("the math task needs data.path (a JSONL of {prompt, target:{answer}})")
+        samples = read_jsonl(d.path, MathProblem.from_json)
+        train, ev = train_eval_split(samples, d.eval_n, d.seed)
+        return train[:d.train_n] if d.train_n else train, ev, MathReward()
+    if cfg.task == "trimul":
+        from .rewards.trimul import TrimulCase, TrimulReward, TrimulRewardProfile
+        from .sandbox import ApptainerSandbox
+        from .verifier_executor import SameUidApptainerSandbox, VerifierExecutorSandbox, VerifierIsolationTier
+        t = cfg.trimul
+        for req in ("prompt_path", "image", "eval_dir"):
+            if not t.get(req):
+                raise OrchestrationError(f"trimul.{req} is required for the trimul task")
+        prompt = open(t["prompt_path"], encoding="utf-8").read()
+        tier = VerifierIsolationTier(t.get("verifier_isolation_tier", "same_uid_apptainer_v1"))
+        if tier is VerifierIsolationTier.DEDICATED_UID_SERVICE_V1:
+            sb = VerifierExecutorSandbox(t.get("verifier_executor_socket") or "/run/ferrl/verifier-executor.sock")
+        else:
+            sb = SameUidApptainerSandbox(ApptainerSandbox(t.get("verifier_apptainer_bin") or "apptainer"))
+        cases = [TrimulCase(**c) for c in t.get("cases", [])] or [TrimulCase(32, 1, 16, 16, int(t.get("secret_seed", 0)))]
+        reward = TrimulReward(sb, t["image"], t["eval_dir"], cases, scratch_root=t.get("scratch_root"),
+                              profile=TrimulRewardProfile(**t["reward"]) if t.get("reward") else None,
+                              baseline_ns=(t.get("baseline") or {}).get("ns"), wall_secs=float(t.get("wall_secs", 300)),
+                              scratch_max_bytes=int(t.get("scratch_max_bytes", 2 << 30)),
+                              parallelism=int(t.get("verifier_parallelism", 1)),
+                              extract_mode=t.get("submission_extract_mode") or "final_fence")
+        samples = [Sample(prompt, {"trimul": i}) for i in range(max(d.train_n, 1))]
+        return samples, samples[:max(d.eval_n, 0)], reward
+    raise OrchestrationError(f"unknown task {cfg.task!r}")
+
+
+_DTYPES = {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}
+
+
+@dataclass
+class TrainOutcome:
+    run_dir: str
+    run_id: str
+    stop: str
+    steps_run: int
+    health: HealthReport
+    eval_report: Optional[EvalReport]
+    candidates: list
+
+
+def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_dirty: bool = False,
+                        tokenizer=None, model_and_identity=None) -> TrainOutcome:
+    """The whole ``train`` verb. ``tokenizer`` / ``model_and_identity`` may be injected (tests,
+    synthetic runs); otherwise they are loaded from ``cfg.model_dir``."""
+    comm = comm or SoloComm()
+    T.init_tracing()
+    ident = source_identity()
+    require_clean(ident, allow_dirty)
+    comm.require_consensus(cfg.digest().encode(), "run config")
+    comm.require_consensus(ident.commit.encode(), "source commit")
+    topology = "tp" if cfg.tensor_parallel.enabled else "dp"
+    if comm.world_size > 1 and not (cfg.distributed.enabled or cfg.tensor_parallel.enabled):
+        raise OrchestrationError("a multi-rank launch needs distributed.enabled or tensor_parallel.enabled")
+    run_id = synchronized_run_id(cfg.task, comm)
+    device = cfg.device
+    if device.startswith("cuda"):
+        from .preflight import check_device, guard_first_kernel
+        idx = torch.cuda.current_device() if torch.cuda.is_available() else 0
+        check_device(idx)
+        guard_first_kernel()
+        device = f"cuda:{idx}"
+    train_samples, eval_samples, reward_fn = build_task(cfg)
+    # ---- policy
+    pc = cfg.policy
+    lora = LoraSpec(pc.lora_rank, pc.lora_alpha, DenseLoraTargets.parse(pc.lora_targets))
+    opts = LoaderOpts(dtype=_DTYPES[pc.base_dtype], device=device, lora=lora,
+                      quantization=BaseQuantization(pc.base_quantization), remat=pc.activation_checkpointing,
+                      tp=(cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size) if cfg.tensor_parallel.enabled else None,
+                      adapter_seed=pc.seed)
+    model, pident = model_and_identity or load_auto_policy(cfg.model_dir, opts)
+    if tokenizer is None:
+        from .tokenizer import HfTokenizer
+        tokenizer = HfTokenizer.from_file(cfg.model_dir)
+    if cfg.eos_selection != "disabled" and os.path.exists(os.path.join(cfg.model_dir, "config.json")):
+        cfg.trainer.eos_token_id = resolve_eos(cfg.model_dir, cfg.eos_selection, cfg.trainer.eos_token_id, tokenizer)
+    validate_resolved_eos_consensus(cfg.trainer.eos_token_id, comm)
+    policy = LmPolicy(model, GrpoSampler(pc.seed, cfg.trainer.temperature), comm if topology == "tp" else None,
+                      pad_token_id=cfg.trainer.eos_token_id or 0,
+                      score_microbatch=cfg.trainer.backward_microbatch_size)
+    # ---- launch manifest + run dir
+    samples_sha = hashlib.sha256("\n".join(s.key() for s in train_samples).encode()).hexdigest()
+    launch_sha_seed = hashlib.sha256((run_id + cfg.digest()).encode()).digest()
+    signer = None
+    if cfg.launch_authentication == "signed":
+        signer = T.CandidateSigner("", seed=None)
+    manifest = LaunchManifest(run_id, cfg.task, cfg.digest(), pident.digest(), tokenizer.digest(), samples_sha,
+                              ident.to_json(), comm.world_size, topology,
+                              signer.public_key_hex if signer else None, cfg.launch_authentication, int(time.time()))
+    if signer:
+        signer.launch_sha256 = manifest.digest()
+    del launch_sha_seed
+    comm.require_consensus(json.dumps({k: v for k, v in manifest.to_json().items()
+                                       if k not in ("candidate_public_key", "created_unix")}, sort_keys=True).encode(),
+                           "launch manifest")
+    run_dir = None
+    if comm.rank == 0:
+        run_dir = T.RunDir.create(cfg.out_dir, run_id)
+        run_dir.write_json_once(T.RunDir.LAUNCH_FILE, dict(manifest.to_json(), launch_sha256=manifest.digest()))
+        run_dir.write_json_once(T.RunDir.CONFIG_FILE, cfg.to_json())
+    comm.barrier() if comm.world_size > 1 else None
+    if run_dir is None:
+        run_dir = T.RunDir(os.path.join(cfg.out_dir, run_id), run_id)
+    binding = CheckpointBinding(pident.digest(), cfg.trainer.digest(), policy.lora_recipe())
+    cand_writer = T.CandidateWriter(run_dir.candidates_path, signer) if comm.rank == 0 or topology == "dp" else None
+    if cand_writer is not None and comm.rank != 0:
+        cand_writer = T.CandidateWriter(run_dir.candidates_path + f".rank{comm.rank}", signer)
+    fused = None
+    if topology == "dp" and comm.world_size > 1 and device.startswith("cuda"):
+        from .parallel.dp import FusedDpStep
+        fused = FusedDpStep.create(comm, policy.trainable_params(), torch.device(device))
+    trainer = Trainer(policy, tokenizer, reward_fn, train_samples, cfg.trainer, comm=comm, topology=topology,
+                      run_dir=run_dir, binding=binding, candidate_writer=cand_writer, fused_dp_step=fused)
+    with T.run_span(comm.rank, comm.world_size):
+        start = trainer.resume_latest()
+        stop = trainer.train(start)
+    # ---- health, eval, candidates (rank 0 owns publication)
+    rows = trainer.history
+    cands = T.read_candidates(run_dir.candidates_path) if comm.rank == 0 else []
+    health = evaluate_run_health(rows, cfg.run_health, cands)
+    report = None
+    if eval_samples and stop is RunStop.COMPLETED and health.verdict != "fail":
+        gen = GenConfig(cfg.trainer.group_size, cfg.trainer.max_new_tokens, cfg.trainer.temperature,
+                        cfg.trainer.eos_token_id)
+        report = evaluate(policy, reward_fn, tokenizer, eval_samples, gen)
+        if comm.rank == 0:
+            with open(run_dir.path(T.RunDir.EVAL_REPORT_FILE), "w") as f:
+                json.dump(report.to_json(), f, indent=2, sort_keys=True)
+    ranked = load_and_rank_candidates(run_dir.root) if comm.rank == 0 else []
+    return TrainOutcome(run_dir.root, run_id, stop.value, len(rows), health, report, ranked)
+
+
+def load_and_rank_candidates(run_root: str, require_signed: bool = True) -> list:
+    """Authenticated candidates of a run, best reward first (ties: earlier step, lower prompt index)."""
+    try:
+        launch = json.load(open(os.path.join(run_root, T.RunDir.LAUNCH_FILE)))
+    except (OSError, json.JSONDecodeError) as e:
+        raise OrchestrationError(f"cannot read launch.json of {run_root}: {e}") from e
+    key, lsha = launch.get("candidate_public_key"), launch.get("launch_sha256")
+    out = []
+    for rec in T.read_candidates(os.path.join(run_root, T.RunDir.CANDIDATES_FILE)):
+        if key:
+            T.verify_candidate(rec, key, lsha)
+        elif require_signed and launch.get("launch_authentication") == "signed":
+            raise OrchestrationError("run was launched as signed but carries no candidate key")
+        out.append(rec)
+    out.sort(key=lambda r: (-r.reward, r.step, r.prompt_index, r.group_index))
+    return out

