@@ -277,7 +277,6 @@ class Trainer:
             truncated = mask_truncated_rows(r, c.eos_token_id, mask) if c.truncation_masking else 0
             groups.append(CollectedGroup(sel, sample, pids, r, completions, rewards, outcomes, [], mask, truncated,
                                          int(sum(r.completion_lens))))
-        self._advantages(groups)
         self._phase_end("reward")
         return groups
 
@@ -454,8 +453,12 @@ class Trainer:
         else:
             for p in self.params:
                 p.grad = None
-        for item in live:
-            self._item_backward(item, window_tokens, beta, stats, agg)
+        def local_backward():
+            for item in live:
+                self._item_backward(item, window_tokens, beta, stats, agg)
+        # every rank must have finished (or failed) its local backward before anyone enters the
+        # gradient collective; a failure anywhere raises on all ranks here, not at a timeout
+        self._rendezvous(local_backward, "backward")
         # a rank with no live item still joins the reduction with zeros
         for p in self.params:
             if p.grad is None and not live:
@@ -510,10 +513,17 @@ class Trainer:
         """Rollout + reward half of a window: ``[(accum_index, [CollectedGroup, ...]), ...]``."""
         c = self.config
         P = c.prompts_per_item
-        out = []
-        for j in range(c.grad_accum_steps):
-            sels = [self.select_prompt(step, j * P + q) for q in range(P)]
-            out.append((j, self.collect_groups(sels)))
+        def local():
+            out = []
+            for j in range(c.grad_accum_steps):
+                sels = [self.select_prompt(step, j * P + q) for q in range(P)]
+                out.append((j, self.collect_groups(sels)))
+            return out
+        # rollout + rewards touch no data-parallel collective: agree on success first, then
+        # (possibly cross-rank) advantage normalisation
+        out = self._rendezvous(local, "rollout collection")
+        for _, groups in out:
+            self._advantages(groups)
         return out
 
     def run_window(self, step: int, lr: float, beta: float, collected: Optional[list] = None) -> tuple[Metrics, int]:
@@ -523,11 +533,14 @@ class Trainer:
         all_groups: list[CollectedGroup] = []
         if collected is None:
             collected = self.collect_window(step)
-        for j, groups in collected:
-            all_groups += groups
-            item = self.materialize(groups, beta, stats)
-            if item is not None:
-                live.append(item)
+
+        def local_materialize():
+            for j, groups in collected:
+                all_groups.extend(groups)
+                item = self.materialize(groups, beta, stats)
+                if item is not None:
+                    live.append(item)
+        self._rendezvous(local_materialize, "rollout scoring")
         if c.candidate_log_top_k > 0 and self.candidate_writer is not None:
             self._log_candidates(step, all_groups)
         local_tokens = stats.completion_tokens
@@ -586,6 +599,12 @@ class Trainer:
                 completion_len_tokens=g.rollout.completion_lens[i], completion=comp,
                 reward_diagnostic=o.diagnostic, reward_metadata=o.metadata))
 
+    def _rendezvous(self, fn, what: str):
+        """Run a rank-local stage, then agree on its outcome across data-parallel ranks."""
+        if self.topology == "dp" and self.comm.world_size > 1:
+            return self.comm.coordinate(fn, what)
+        return fn()
+
     # ------------------------------------------------------------ phases
     def _phase(self, label: str):
         if self._timer is not None:
@@ -632,19 +651,14 @@ class Trainer:
         self._probe = GpuMemoryProbe(c.gpu_memory_probe, dev if dev.type == "cuda" else None)
         snap = self._snapshot() if self.comm.world_size > 1 or self.fault_hook is not None else None
         t0 = time.perf_counter()
-        if self.comm.world_size > 1:
-            try:
-                m, local_tokens = self.comm.coordinate(lambda: self.run_window(step, lr, beta), f"step {step}")
-            except PeerFailure:
+        try:
+            m, local_tokens = self.run_window(step, lr, beta)
+        except CommError:
+            raise                      # communicator failures are terminal: no rollback collective is possible
+        except Exception:
+            if snap is not None:
                 self._restore(snap)
-                raise
-        else:
-            try:
-                m, local_tokens = self.run_window(step, lr, beta)
-            except Exception:
-                if snap is not None:
-                    self._restore(snap)
-                raise
+            raise
         phases = self._timer.collect()
         m.step_secs = time.perf_counter() - t0
         m.tokens_per_sec = local_tokens / m.step_secs if m.step_secs > 0 else 0.0

@@ -1,0 +1,460 @@
+"""Host-side infrastructure: communicators, config, checkpoints, telemetry, rewards, sandbox,
+artifact audit, orchestration and CLI."""
+import json
+import os
+import threading
+import time
+
+import pytest
+import torch
+
+from ferrl_b200 import checkpoint as CK, telemetry as T
+from ferrl_b200.comm import (CommMismatch, CommPoisoned, CommTimeout, NcclConfig, CommConfigError, PeerFailure, SoloComm,
+                             ThreadComm, run_ranks)
+from ferrl_b200.config import ConfigError, RunConfig, ScalarSchedule, TrainerConfig
+from ferrl_b200.optim import AdamWParams, FerrlAdamW, OptimizerState
+
+FIX = os.path.join(os.path.dirname(__file__), "fixtures")
+
+
+# ------------------------------------------------------------------ comm
+def test_threadcomm_sums_in_rank_order_and_gathers():
+    def body(c):
+        t = [torch.full((3,), float(c.rank + 1))]
+        c.all_reduce_sum(t)
+        return t[0].tolist(), c.all_reduce_scalar_sum(c.rank + 1), c.all_gather_bytes(bytes([c.rank])), \
+            c.all_reduce_scalars_sum([1.0, c.rank])
+    for vals, s, g, packed in run_ranks(4, body):
+        assert vals == [10.0] * 3 and s == 10.0 and g == [b"\x00", b"\x01", b"\x02", b"\x03"] and packed == [4.0, 6.0]
+
+
+def test_threadcomm_mismatch_timeout_poison_and_consensus():
+    def mism(c):
+        c.all_reduce_sum([torch.zeros(2 + c.rank)])
+    with pytest.raises(CommMismatch):
+        run_ranks(2, mism)
+
+    def lonely(c):
+        if c.rank == 0:
+            c.all_reduce_scalar_sum(1.0)
+    with pytest.raises(CommTimeout):
+        run_ranks(2, lonely, timeout=0.3)
+
+    def cons(c):
+        c.require_consensus(b"same", "x")
+        with pytest.raises(CommMismatch):
+            c.require_consensus(bytes([c.rank]), "y")
+        return True
+    assert run_ranks(3, cons) == [True] * 3
+    comms = ThreadComm.world(2)
+    comms[0].poison("dead")
+    with pytest.raises(CommPoisoned):
+        comms[1].all_reduce_scalar_sum(0.0)
+    with pytest.raises(CommMismatch):
+        SoloComm().validate_all_reduce_sum([torch.zeros(2, dtype=torch.bfloat16)])
+
+
+def test_coordinate_turns_one_failure_into_a_failure_everywhere():
+    def body(c):
+        def f():
+            if c.rank == 2:
+                raise ValueError("boom")
+            return c.rank
+        try:
+            c.coordinate(f, "stage")
+        except PeerFailure as e:
+            return ("failed", e.local is not None)
+        return ("ok", False)
+    assert run_ranks(3, body) == [("failed", False), ("failed", False), ("failed", True)]
+
+
+def test_nccl_config_from_env():
+    assert NcclConfig.from_env({}) is None
+    c = NcclConfig.from_env({"RANK": "1", "WORLD_SIZE": "4", "LOCAL_RANK": "1", "MASTER_ADDR": "127.0.0.1", "MASTER_PORT": "1234"})
+    assert (c.rank, c.world_size, c.init_method) == (1, 4, "tcp://127.0.0.1:1234")
+    c = NcclConfig.from_env({"FERRL_NCCL_RENDEZVOUS": "/tmp/rdv", "SLURM_PROCID": "0", "SLURM_NTASKS": "2", "SLURM_LOCALID": "0"})
+    assert c.init_method == "file:///tmp/rdv"
+    with pytest.raises(CommConfigError):
+        NcclConfig.from_env({"RANK": "5", "WORLD_SIZE": "4"})
+    with pytest.raises(CommConfigError):
+        NcclConfig.from_env({"FERRL_NCCL_RENDEZVOUS": "/tmp/x", "SLURM_PROCID": "zero", "SLURM_NTASKS": "2", "SLURM_LOCALID": "0"})
+
+
+def test_gloo_process_group_two_ranks(tmp_path):
+    """The torch.distributed communicator on CPU (gloo), as two real processes."""
+    import subprocess
+    import sys
+    code = ("import torch, os; from ferrl_b200.comm import TorchDistComm; c = TorchDistComm.bootstrap(backend='gloo', timeout_s=60);"
+            "t=[torch.full((4,), float(c.rank+1))]; c.all_reduce_sum(t); assert t[0].tolist()==[3.0]*4;"
+            "assert c.all_reduce_scalar_sum(c.rank+1)==3.0; assert c.all_gather_bytes(bytes([c.rank]))==[b'\\x00', b'\\x01'];"
+            "c.require_consensus(b'x','cfg'); c.barrier(); print('GLOO_OK', c.rank)")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29641",
+                   PYTHONPATH=root)
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    for p in procs:
+        out, err = p.communicate(timeout=180)
+        assert p.returncode == 0 and "GLOO_OK" in out, err[-2000:]
+
+
+# ---------------------------------------------------------------- config
+def test_trainer_config_validation_and_schedules():
+    c = TrainerConfig()
+    c.validate()
+    assert (c.loss_type, c.mu, c.beta, c.max_grad_norm, c.truncation_masking) == ("dapo", 1, 0.0, 1.0, True)
+    for bad in (dict(steps=0), dict(mu=0), dict(group_size=1), dict(clip_eps=1.0), dict(temperature=0.0),
+                dict(lr=-1.0), dict(max_grad_norm=0.0), dict(tis_imp_ratio_cap=0.5), dict(checkpoint_every=0),
+                dict(lr_schedule=ScalarSchedule.constant(1.0), warmup_steps=2)):
+        with pytest.raises(ConfigError):
+            TrainerConfig(**bad).validate()
+    c = TrainerConfig(lr=1.0, warmup_steps=4)
+    assert [c.lr_at(i) for i in range(5)] == [0.25, 0.5, 0.75, 1.0, 1.0]
+    s = ScalarSchedule.linear(0.0, 1.0, 10)
+    assert s.at(0) == 0.0 and s.at(5) == 0.5 and s.at(99) == 1.0
+    c = TrainerConfig(steps=20, beta_schedule=ScalarSchedule([(0, 0.0), (10, 0.1)]))
+    c.validate()
+    assert c.requires_reference_policy() and abs(c.beta_at(5) - 0.05) < 1e-12
+    assert TrainerConfig.from_json(c.to_json()).digest() == c.digest()
+    with pytest.raises(ConfigError):
+        TrainerConfig.from_json({"stepz": 3})
+
+
+def test_run_config_strict_json_eos_modes_and_digest():
+    base = {"task": "countdown", "model_dir": "/m", "trainer": {"steps": 2}}
+    cfg = RunConfig.from_json(base)
+    assert cfg.eos_selection == "checkpoint" and "eos_token_id" not in cfg.to_json()["trainer"]
+    assert RunConfig.from_json(dict(base, trainer={"steps": 2, "eos_token_id": 7})).eos_selection == "explicit"
+    d = RunConfig.from_json(dict(base, trainer={"steps": 2, "eos_token_id": "none"}))
+    assert d.eos_selection == "disabled" and d.to_json()["trainer"]["eos_token_id"] == "none"
+    for bad in (dict(base, trainer={"steps": 2, "eos_token_id": None}), dict(base, extra=1), dict(base, task="chess"),
+                dict(base, policy={"lora_rnk": 1}),
+                dict(base, distributed={"enabled": True}, tensor_parallel={"enabled": True, "rank": 0, "world_size": 2})):
+        with pytest.raises(ConfigError):
+            RunConfig.from_json(bad)
+    a = RunConfig.from_json(dict(base, tensor_parallel={"enabled": True, "rank": 0, "world_size": 2}))
+    b = RunConfig.from_json(dict(base, tensor_parallel={"enabled": True, "rank": 1, "world_size": 2}))
+    assert a.digest() == b.digest() and a.digest() != cfg.digest()
+
+
+# ------------------------------------------------------------ checkpoint
+def _ck(tmp, step=3, adapters=None):
+    adapters = adapters or [torch.randn(4, 8), torch.zeros(8, 4)]
+    opt = OptimizerState(5, [torch.ones_like(a) for a in adapters], [torch.full_like(a, 2.0) for a in adapters])
+    b = CK.CheckpointBinding("a" * 64, "b" * 64, "lora:r4")
+    path = CK.save_checkpoint(str(tmp), step, adapters, opt, b"sampler", b, world_size=2)
+    return path, adapters, b
+
+
+def test_checkpoint_round_trip_and_layout(tmp_path):
+    path, adapters, b = _ck(tmp_path)
+    assert sorted(os.listdir(path)) == ["adapter.safetensors", "manifest.json", "optimizer.safetensors"]
+    man = json.load(open(os.path.join(path, "manifest.json")))
+    assert man["format_version"] == 4 and man["step"] == 3 and man["num_vars"] == 2 and man["optimizer_step_t"] == 5
+    from safetensors.torch import load_file
+    assert sorted(load_file(os.path.join(path, "adapter.safetensors"))) == ["lora.00000", "lora.00001"]
+    assert sorted(load_file(os.path.join(path, "optimizer.safetensors"))) == ["m.00000", "m.00001", "v.00000", "v.00001"]
+    params = [torch.nn.Parameter(torch.zeros(4, 8)), torch.nn.Parameter(torch.ones(8, 4))]
+    lc = CK.load_checkpoint(path, b, params, world_size=2, topology="dp")
+    assert all(torch.equal(p.detach(), a) for p, a in zip(params, adapters))
+    assert lc.optimizer.step == 5 and lc.manifest.sampler_bytes() == b"sampler"
+    assert CK.latest_checkpoint(str(tmp_path)) == (3, path)
+    with pytest.raises(CK.CheckpointError):
+        CK.save_checkpoint(str(tmp_path), 3, adapters, None, None, b)          # never replaced
+
+
+def test_checkpoint_corruption_and_binding_are_rejected_before_mutation(tmp_path):
+    path, adapters, b = _ck(tmp_path)
+    params = [torch.nn.Parameter(torch.zeros(4, 8)), torch.nn.Parameter(torch.ones(8, 4))]
+    for wrong in (CK.CheckpointBinding("c" * 64, "b" * 64, "lora:r4"), CK.CheckpointBinding("a" * 64, "d" * 64, "lora:r4"),
+                  CK.CheckpointBinding("a" * 64, "b" * 64, "lora:r8")):
+        with pytest.raises(CK.CheckpointMismatch):
+            CK.load_checkpoint(path, wrong, params)
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.load_checkpoint(path, b, params, world_size=4)
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.load_checkpoint(path, b, [torch.nn.Parameter(torch.zeros(4, 9)), params[1]])
+    with open(os.path.join(path, "adapter.safetensors"), "r+b") as f:
+        f.seek(-1, 2)
+        f.write(b"\x55")
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.load_checkpoint(path, b, params)
+    assert torch.equal(params[0].detach(), torch.zeros(4, 8))
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.CheckpointBinding("xyz", "b" * 64)
+
+
+def test_failed_publication_leaves_nothing_and_newer_malformed_is_an_error(tmp_path):
+    def hook(stage):
+        if stage == "optimizer_written":
+            raise OSError("disk full")
+    b = CK.CheckpointBinding("a" * 64, "b" * 64, None)
+    with pytest.raises(OSError):
+        CK.save_checkpoint(str(tmp_path), 1, [torch.zeros(2)], None, None, b, fault_hook=hook)
+    assert CK.latest_checkpoint(str(tmp_path)) is None and not any(n.startswith("step-1") and "staging" in n for n in os.listdir(tmp_path))
+    _ck(tmp_path, step=2)
+    os.makedirs(tmp_path / "step-9")
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.latest_checkpoint(str(tmp_path))
+
+
+def test_bare_adapter_round_trip(tmp_path):
+    a = [torch.randn(2, 3), torch.randn(3, 2)]
+    CK.save_adapter(str(tmp_path / "a.safetensors"), a, "lora:x")
+    p = [torch.nn.Parameter(torch.zeros(2, 3)), torch.nn.Parameter(torch.zeros(3, 2))]
+    CK.load_adapter(str(tmp_path / "a.safetensors"), p, "lora:x")
+    assert all(torch.equal(x.detach(), y) for x, y in zip(p, a))
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.load_adapter(str(tmp_path / "a.safetensors"), p, "lora:y")
+
+
+def test_adamw_matches_torch_and_state_round_trips():
+    torch.manual_seed(0)
+    p = [torch.nn.Parameter(torch.randn(5, 3).double().float())]
+    q = [torch.nn.Parameter(p[0].detach().clone())]
+    ours = FerrlAdamW(p, AdamWParams(lr=1e-2, weight_decay=0.1))
+    ref = torch.optim.AdamW(q, lr=1e-2, weight_decay=0.1, eps=1e-8)
+    for _ in range(5):
+        g = torch.randn(5, 3)
+        ours.step([g])
+        q[0].grad = g.clone()
+        ref.step()
+    assert torch.allclose(p[0], q[0], atol=1e-6)
+    st = ours.state()
+    other = FerrlAdamW([torch.nn.Parameter(torch.zeros(5, 3))])
+    other.load_state(st)
+    assert other.step_t == 5 and torch.equal(other.m[0], ours.m[0])
+    with pytest.raises(ValueError):
+        other.load_state(OptimizerState(1, [torch.zeros(2)], [torch.zeros(2)]))
+
+
+# ------------------------------------------------------------- telemetry
+def test_metrics_sanitising_candidates_and_health(tmp_path):
+    rd = T.RunDir.create(str(tmp_path), "run")
+    with pytest.raises(FileExistsError):
+        T.RunDir.create(str(tmp_path), "run")
+    w = T.MetricsWriter(rd.metrics_path)
+    for i in range(6):
+        w.append(T.Metrics(step=i, reward_mean=0.1 * i, grad_norm=(100.0 if i == 4 else 1.0), step_secs=1.0,
+                           loss=float("nan") if i == 5 else 0.0))
+    rows = T.read_metrics(rd.metrics_path)
+    assert rows[5].loss == 0.0 and "loss" in rows[5].nonfinite_fields
+    kinds = {a.kind for a in T.detect_anomalies(rows)}
+    assert {"non_finite", "grad_spike"} <= kinds and T.detect_anomalies([])[0].kind == "telemetry_dark"
+    stall = [T.Metrics(step=i, reward_mean=0.5, frac_reward_zero_std=1.0) for i in range(6)]
+    assert any(a.kind == "reward_stall" for a in T.detect_anomalies(stall))
+    signer = T.CandidateSigner("f" * 64)
+    cw = T.CandidateWriter(rd.candidates_path, signer)
+    cw.append(T.CandidateRecord(1, 0, 1, 3, 0, 0.9, 5, "answer"))
+    rec = T.read_candidates(rd.candidates_path)[0]
+    T.verify_candidate(rec, signer.public_key_hex, "f" * 64)
+    rec.completion = "tampered"
+    with pytest.raises(ValueError):
+        T.verify_candidate(rec, signer.public_key_hex, "f" * 64)
+    rd.write_json_once("launch.json", {"a": 1})
+    with pytest.raises(FileExistsError):
+        rd.write_json_once("launch.json", {"a": 2})
+
+
+def test_perf_gate_budget():
+    base = [T.Metrics(step=i, step_secs=1.0, grad_norm=1.0, cuda_mem_peak_used_bytes=1 << 30) for i in range(4)]
+    ok = [T.Metrics(step=i, step_secs=1.05, grad_norm=1.0, cuda_mem_peak_used_bytes=(1 << 30) + (32 << 20)) for i in range(4)]
+    slow = [T.Metrics(step=i, step_secs=1.2, grad_norm=1.0, cuda_mem_peak_used_bytes=1 << 30) for i in range(4)]
+    fat = [T.Metrics(step=i, step_secs=1.0, grad_norm=1.0, cuda_mem_peak_used_bytes=(1 << 30) + (100 << 20)) for i in range(4)]
+    assert T.compare_metrics(base, ok).passed
+    assert not T.compare_metrics(base, slow).passed and not T.compare_metrics(base, fat).passed
+    assert not T.compare_metrics(base, []).passed
+    dead = [T.Metrics(step=i, step_secs=1.0, grad_norm=0.0, cuda_mem_peak_used_bytes=1 << 30) for i in range(4)]
+    assert not T.compare_metrics(base, dead).passed
+    with pytest.raises(ValueError):
+        T.compare_distributed_metrics([base], [ok, ok])
+
+
+# --------------------------------------------------------------- rewards
+def test_countdown_math_and_data(tmp_path):
+    from ferrl_b200.rewards import (CountdownProblem, CountdownReward, MathProblem, MathReward, Sample, build_prompt,
+                                    generate_dataset, parse_jsonl, read_jsonl, train_eval_split, train_eval_split_by_key, DataError)
+    from ferrl_b200.rewards.countdown import eval_expression
+    assert generate_dataset(7, 20) == generate_dataset(7, 20) != generate_dataset(8, 20)
+    assert all(1 <= p.target <= 1000 for p in generate_dataset(3, 50))
+    r, p = CountdownReward(), CountdownProblem((2, 3, 4), 14)
+    assert [round(r.score(p, c), 3) for c in ("<answer>2*(3+4)</answer>", "<answer>2*3+4</answer>", "<answer>2*(3+5)</answer>",
+                                              "<answer>2**3</answer>", "<answer>8/(3-3)</answer>", "nothing")] == [1.0, 0.2, 0.1, 0.1, 0.1, 0.0]
+    assert eval_expression("7/2*2")[0] == 7 and eval_expression("1 +") is None and eval_expression("4294967296") is None
+    assert "Numbers: 2, 3, 4" in build_prompt(p) and "Target: 14" in build_prompt(p)
+    m = MathReward()
+    assert m.score("1,000", "so <answer> 1000 </answer>") == 1.0 and m.score("5", "<answer>6</answer>") == 0.0
+    cd = read_jsonl(os.path.join(FIX, "countdown_dataset.jsonl"), CountdownProblem.from_json)
+    assert len(cd) == 3 and cd[0].target.target == 100
+    assert len(read_jsonl(os.path.join(FIX, "math_dataset.jsonl"), MathProblem.from_json)) >= 3
+    with pytest.raises(DataError):
+        parse_jsonl('{"prompt": "x"}')
+    s = [Sample(f"p{i % 5}", i % 5) for i in range(12)]
+    tr, ev = train_eval_split(s, 2, 1)
+    assert len(tr) == 3 and len(ev) == 2 and train_eval_split(s, 2, 1)[1] == ev
+    tr, ev = train_eval_split_by_key([Sample(f"p{i}", i % 3) for i in range(9)], 3, 2, lambda x: x.target)
+    assert {x.target for x in tr}.isdisjoint({x.target for x in ev}) and len(ev) >= 3
+
+
+def test_hf_eos_resolution_and_tokenizer():
+    from ferrl_b200.hf import HfError, chatml, checkpoint_eos, resolve_eos
+    from ferrl_b200.tokenizer import ByteTokenizer, HfTokenizer
+
+    class Tok:
+        def contains_id(self, i):
+            return i < 200000
+    assert checkpoint_eos(os.path.join(FIX, "eos_config")) == 151645
+    assert checkpoint_eos(os.path.join(FIX, "eos_config_multi")) == [3, 4]
+    with pytest.raises(HfError):
+        checkpoint_eos(os.path.join(FIX, "eos_config_malformed"))
+    assert resolve_eos(os.path.join(FIX, "eos_config"), "checkpoint", None, Tok()) == 151645
+    assert resolve_eos(os.path.join(FIX, "eos_config"), "disabled", None, Tok()) is None
+    with pytest.raises(HfError):
+        resolve_eos(os.path.join(FIX, "eos_config_multi"), "checkpoint", None, Tok())
+    assert resolve_eos(os.path.join(FIX, "eos_config_multi"), "explicit", 4, Tok()) == 4
+    with pytest.raises(HfError):
+        resolve_eos(os.path.join(FIX, "eos_config_multi"), "explicit", 9, Tok())
+    assert chatml("sys", "hi") == "<|im_start|>system\nsys<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
+    bt = ByteTokenizer()
+    assert bt.decode(bt.encode("héllo")) == "héllo"
+    ht = HfTokenizer.from_file(os.path.join(FIX, "tiny_tokenizer.json"))
+    ids = ht.encode("hello world")
+    assert isinstance(ids, list) and ht.vocab_size() > 0 and isinstance(ht.decode(ids), str)
+
+
+# --------------------------------------------------------------- sandbox
+def test_local_sandbox_limits_and_sealed_assets(tmp_path):
+    from ferrl_b200.sandbox import (ApptainerSandbox, LocalSandbox, ResourceLimits, RunSpec, Verdict, make_scratch, sealed_memfd)
+    sb = LocalSandbox()
+    out = sb.run(RunSpec("", ["sh", "-c", "echo hi; exit 3"]))
+    assert (out.verdict, out.exit_code, out.stdout) == (Verdict.EXITED, 3, b"hi\n")
+    t0 = time.time()
+    assert sb.run(RunSpec("", ["sh", "-c", "sleep 30 & sleep 30"], limits=ResourceLimits(wall_secs=0.4))).verdict is Verdict.TIMEOUT
+    assert time.time() - t0 < 10
+    d = make_scratch(str(tmp_path))
+    o = sb.run(RunSpec("", ["sh", "-c", f"dd if=/dev/zero of={d}/x bs=1M count=40 2>/dev/null; sleep 5"], scratch_dir=d,
+                       scratch_max_bytes=8 << 20, limits=ResourceLimits(wall_secs=10)))
+    assert o.verdict is Verdict.SCRATCH_EXCEEDED
+    big = sb.run(RunSpec("", ["sh", "-c", "head -c 3000000 /dev/zero"]))
+    assert big.truncated and len(big.stdout) == 1 << 20
+    fd = sealed_memfd("asset", b"payload")
+    with pytest.raises(OSError):
+        os.write(fd, b"x")
+    assert os.pread(fd, 7, 0) == b"payload"
+    os.close(fd)
+    argv = ApptainerSandbox().build_argv(RunSpec("img.sif", ["python", "x.py"], gpu=True))
+    for flag in ("--userns", "--containall", "--no-home", "--cleanenv", "--no-privs", "--nv", "--net"):
+        assert flag in argv
+    assert argv[argv.index("--network") + 1] == "none" and "--nv" not in ApptainerSandbox().build_argv(RunSpec("i", ["x"]))
+
+
+def test_trimul_reward_shaping_and_executor_socket(tmp_path):
+    from ferrl_b200.rewards.trimul import (SubmissionExtractMode, TrimulCase, TrimulReward, TrimulRewardProfile,
+                                           extract_submission, parse_eval_log, render_spec)
+    from ferrl_b200.sandbox import FakeSandbox, LocalSandbox, RunSpec, SandboxOutcome, Verdict
+    from ferrl_b200.verifier_executor import VerifierExecutorSandbox, serve_verifier_executor
+    assert extract_submission("x\n```python\nprint(1)\n```\n") == "print(1)"
+    assert extract_submission("```py\na\n``` trailing") is None and extract_submission("no fence") is None
+    assert extract_submission("```\na\n```</think>```\nb\n```", SubmissionExtractMode.THINKING_AFTER_THINK) == "b"
+    assert render_spec([TrimulCase(32, 1, 16, 8, 5)]) == "seqlen: 32; bs: 1; dim: 16; hiddendim: 8; seed: 5; nomask: 1; distribution: normal"
+    good = "test-count: 2\ntest.0.status: pass\ntest.1.status: pass\ncheck: pass\ntest-exit: 0\nbenchmark-count: 1\nbenchmark.0.mean: 2000000\nbenchmark-exit: 0\n"
+    half = "test-count: 2\ntest.0.status: pass\ntest.1.status: fail\ncheck: fail\ntest-exit: 1\n"
+    forged = good.replace("2000000", "5")
+    logs = {"good": good, "half": half, "forged": forged}
+    sb = FakeSandbox(lambda spec: SandboxOutcome(Verdict.EXITED, 0, logs[open(spec.binds[2].host).read().strip()].encode(), b""))
+    r = TrimulReward(sb, "img", str(tmp_path), [TrimulCase(32, 1, 16, 8, 1)], baseline_ns=4e6)
+    outs = r.reward_group_detailed(None, [f"```python\n{k}\n```" for k in ("good", "half", "forged")] + ["nothing"])
+    assert abs(outs[0].reward - 3.0) < 1e-6 and outs[0].diagnostic is None          # 1.0 + min(4e6/2e6, cap 2)
+    assert abs(outs[1].reward - (0.05 + 0.75 * 0.5)) < 1e-6 and outs[1].diagnostic == "trimul:test_process_failed"
+    assert outs[2].reward == 0.0 and outs[3].diagnostic == "trimul:no_submission"
+    assert sb.calls[0].gpu and sb.calls[0].binds[0].read_only
+    with pytest.raises(ValueError):
+        TrimulRewardProfile(format_extracted=0.2).validate()
+    timeout_eval = parse_eval_log("", False, "timeout")
+    assert r.reward_from_extracted_eval(timeout_eval) == r.profile.format_extracted and r.diagnostic(timeout_eval) == "trimul:sandbox_timeout"
+    sock = str(tmp_path / "ve.sock")
+    ready = threading.Event()
+    t = threading.Thread(target=serve_verifier_executor, args=(sock, LocalSandbox()), kwargs=dict(max_requests=1, ready=ready))
+    t.start()
+    ready.wait(10)
+    out = VerifierExecutorSandbox(sock).run(RunSpec("", ["sh", "-c", "echo served"]))
+    t.join(10)
+    assert out.ok and out.stdout == b"served\n"
+
+
+# ---------------------------------------------------- artifact / orchestration
+def test_artifact_audit_decision_and_manifest_last(tmp_path):
+    from ferrl_b200 import artifact as A
+    assert A.acceptance_from_speedups([1.05] * 9 + [1.0, 0.9]).accepted
+    assert not A.acceptance_from_speedups([1.05] * 8 + [1.0] * 3).accepted
+    assert not A.acceptance_from_speedups([1.02] * 11).accepted                   # strictly greater
+    assert not A.acceptance_from_speedups([1.05] * 10).accepted and not A.acceptance_from_speedups([1.05] * 10 + [float("nan")]).accepted
+    sched = A.audit_schedule("00" + "a" * 62)
+    assert sched[0] == "reference" and sched[1] == "candidate" and len(sched) == 11 and A.audit_schedule("01" + "a" * 62)[0] == "candidate"
+    run = tmp_path / "run"
+    os.makedirs(run)
+    json.dump({"run_id": "r1", "launch_sha256": "e" * 64}, open(run / "launch.json", "w"))
+    man = A.publish_trimul_artifact(str(run), str(tmp_path / "out"), "def k(): pass", 2.5, lambda s, seed: True,
+                                    lambda s, first: (1000.0, 900.0))
+    assert man.accepted and man.decision["observed_material_wins"] == 11 and os.path.exists(tmp_path / "out" / A.MANIFEST_FILE)
+    with pytest.raises(A.ArtifactError):
+        A.publish_trimul_artifact(str(run), str(tmp_path / "out"), "x", 1.0, lambda s, seed: True, lambda s, f: (1, 1))
+    rej = A.publish_trimul_artifact(str(run), str(tmp_path / "out2"), "x", 1.0, lambda s, seed: False, lambda s, f: (1000.0, 1.0))
+    assert not rej.accepted and rej.blocks == []
+
+    def crash(s, first):
+        raise RuntimeError("gpu fell over")
+    with pytest.raises(RuntimeError):
+        A.publish_trimul_artifact(str(run), str(tmp_path / "out3"), "x", 1.0, lambda s, seed: True, crash)
+    assert not os.path.exists(tmp_path / "out3" / A.MANIFEST_FILE) and os.path.exists(tmp_path / "out3" / A.ATTEMPT_FILE)
+
+
+def test_orchestrated_train_report_and_perf_gate_cli(tmp_path, capsys):
+    from ferrl_b200 import cli
+    from ferrl_b200.orchestration import evaluate_run_health, load_and_rank_candidates, run_cli_train_setup
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    cfg = RunConfig.from_json({"task": "countdown", "model_dir": os.path.join(FIX, "tiny_qwen3"), "out_dir": str(tmp_path),
+                               "policy": {"lora_rank": 4, "lora_alpha": 8.0}, "data": {"train_n": 8, "eval_n": 2},
+                               "trainer": {"steps": 2, "group_size": 4, "max_new_tokens": 5, "checkpoint_every": 1,
+                                           "candidate_log_top_k": 2, "eos_token_id": "none", "truncation_masking": False}})
+    out = run_cli_train_setup(cfg, allow_dirty=True, tokenizer=SyntheticTokenizer(32, 4, 8))
+    assert out.stop == "completed" and out.steps_run == 2 and out.eval_report is not None
+    for f in ("launch.json", "config.json", "metrics.jsonl", "candidates.jsonl", "eval-report.json", "checkpoints"):
+        assert os.path.exists(os.path.join(out.run_dir, f))
+    ranked = load_and_rank_candidates(out.run_dir)
+    assert len(ranked) == 4 and ranked[0].reward >= ranked[-1].reward
+    lines = open(os.path.join(out.run_dir, "candidates.jsonl")).read().splitlines()
+    bad = json.loads(lines[0])
+    bad["reward"] = 99.0
+    open(os.path.join(out.run_dir, "candidates.jsonl"), "w").write("\n".join([json.dumps(bad)] + lines[1:]) + "\n")
+    with pytest.raises(ValueError):
+        load_and_rank_candidates(out.run_dir)
+    assert cli.main(["report", out.run_dir, "--json"]) in (0, 1)
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["steps"] == 2
+    assert cli.main(["perf-gate", "--baseline", out.run_dir, "--candidate", out.run_dir, "--no-memory"]) in (0, 1)
+    rep = evaluate_run_health([T.Metrics(step=i, reward_mean=0.0, dropped_rows=3) for i in range(4)],
+                              {"reward_collapse": {"window": 3, "min": 0.1, "action": "fail"}, "dropped_rows": {"max": 5, "action": "warn"}})
+    assert rep.verdict == "fail" and {f.rule for f in rep.findings} == {"reward_collapse", "dropped_rows"}
+
+
+def test_preflight_with_fake_cuda():
+    from ferrl_b200.preflight import PreflightError, check_device
+
+    class Props:
+        name, total_memory, multi_processor_count = "Fake", 1 << 30, 148
+
+    class Fake:
+        def __init__(self, cap, n=2, peer=True):
+            self.cap, self.n, self.peer = cap, n, peer
+        is_available = lambda self: self.n > 0                    # noqa: E731
+        device_count = lambda self: self.n                        # noqa: E731
+        get_device_capability = lambda self, i: self.cap          # noqa: E731
+        get_device_properties = lambda self, i: Props             # noqa: E731
+        can_device_access_peer = lambda self, a, b: self.peer     # noqa: E731
+    assert check_device(0, probe=Fake((10, 0))).sm_count == 148
+    for probe, kind, kw in ((Fake((9, 0)), "wrong_arch", {}), (Fake((10, 0), n=0), "no_device", {}),
+                            (Fake((10, 0), peer=False), "no_peer_access", {"need_peers": 2})):
+        with pytest.raises(PreflightError) as e:
+            check_device(0, probe=probe, **kw)
+        assert e.value.kind == kind

@@ -1,0 +1,173 @@
+"""Model oracles: full-position logits of every family match the committed HF-transformers
+goldens, the cached (prefill + decode) path equals the uncached forward, and deliberately
+wrong hyper-parameters move the logits by far more than the tolerance (negative controls)."""
+import copy
+import json
+import os
+
+import pytest
+import torch
+
+from ferrl_b200.models.loader import LoaderOpts, load_auto_policy, load_llama
+
+FIX = os.path.join(os.path.dirname(__file__), "fixtures")
+ORACLE_TOL = 5e-4
+PERTURBATION_FLOOR = 1e-2
+
+
+def _golden(name):
+    return json.load(open(os.path.join(FIX, name, "golden.json")))["cases"]
+
+
+def _load(name, **kw):
+    fn = load_llama if name == "tiny_llama" else load_auto_policy
+    return fn(os.path.join(FIX, name), LoaderOpts(**kw))[0]
+
+
+def _max_err(model, case):
+    ids = torch.tensor(case["input_ids"])
+    ref = torch.tensor(case["logits"]).view(case["shape"])
+    with torch.no_grad():
+        return (model(ids) - ref).abs().max().item()
+
+
+@pytest.mark.parametrize("name", ["tiny_qwen3", "tiny_llama", "tiny_qwen35", "tiny_qwen35_moe", "tiny_gemma4"])
+def test_full_logits_match_hf_golden(name):
+    m = _load(name)
+    g = _golden(name)
+    for c in ("full_b1", "full_b2"):
+        assert _max_err(m, g[c]) < ORACLE_TOL
+
+
+@pytest.mark.parametrize("name", ["tiny_qwen3", "tiny_llama", "tiny_gemma4"])
+def test_cached_decode_equals_uncached(name):
+    m = _load(name)
+    ids = torch.tensor(_golden(name)["full_b2"]["input_ids"])
+    B, S = ids.shape
+    m.merge_adapters()
+    with torch.no_grad():
+        full = m(ids)
+    dec = m.new_decoder(B, S + 1)
+    lg = dec.prefill(ids[:, :3], torch.full((B,), 3))
+    errs = [(lg - full[:, 2]).abs().max().item()]
+    for t in range(3, S):
+        errs.append((dec.decode(ids[:, t]) - full[:, t]).abs().max().item())
+    assert max(errs) < ORACLE_TOL
+
+
+@pytest.mark.parametrize("name", ["tiny_qwen35", "tiny_qwen35_moe"])
+def test_hybrid_cached_split_matches_golden(name):
+    m = _load(name)
+    c = _golden(name)["cached_split"]
+    ids = torch.tensor(c["input_ids"])
+    P, S, V = c["prefill_len"], len(c["input_ids"][0]), m.spec.vocab_size
+    unc = torch.tensor(c["uncached_logits"]).view(1, S, V)
+    m.merge_adapters()
+    dec = m.new_decoder(1, S + 1)
+    errs = [(dec.prefill(ids[:, :P], torch.tensor([P])) - unc[:, P - 1]).abs().max().item()]
+    for t in range(P, S):
+        errs.append((dec.decode(ids[:, t]) - unc[:, t]).abs().max().item())
+    assert max(errs) < ORACLE_TOL
+    # a right-padded prefill must leave every row's recurrent state exactly as the unpadded one
+    dec2 = m.new_decoder(2, S + 4)
+    padded = torch.cat([ids[:, :P], torch.zeros(1, 3, dtype=torch.long)], 1).repeat(2, 1)
+    lg = dec2.prefill(padded, torch.tensor([P, P]))
+    e2 = [(lg[0] - unc[0, P - 1]).abs().max().item()]
+    for t in range(P, S):
+        e2.append((dec2.decode(ids[:, t].repeat(2))[1] - unc[0, t]).abs().max().item())
+    assert max(e2) < ORACLE_TOL
+
+
+def test_negative_controls_qwen3():
+    g = _golden("tiny_qwen3")["full_b2"]
+    m = _load("tiny_qwen3")
+    bad = copy.deepcopy(m)
+    from ferrl_b200 import ops
+    cos, sin = ops.rope_tables(ops.default_inv_freq(m.spec.head_dim, 10000.0), m.spec.max_position_embeddings)
+    bad.cos, bad.sin = cos, sin                      # wrong RoPE theta
+    assert _max_err(bad, g) > PERTURBATION_FLOOR
+    bad = copy.deepcopy(m)
+    for l in bad.layers:
+        l.eps = 1e-1                                  # wrong RMSNorm epsilon
+    assert _max_err(bad, g) > PERTURBATION_FLOOR
+
+
+def test_negative_controls_gemma_and_moe():
+    g = _golden("tiny_gemma4")["full_b2"]
+    m = _load("tiny_gemma4")
+    bad = copy.deepcopy(m)
+    for l in bad.layers:
+        if l.window:
+            l.window = 1                              # wrong sliding window
+    assert _max_err(bad, g) > PERTURBATION_FLOOR
+    g = _golden("tiny_qwen35_moe")["full_b2"]
+    m = _load("tiny_qwen35_moe")
+    import dataclasses
+    bad = copy.deepcopy(m)
+    bad_moe = dataclasses.replace(m.spec.moe, top_k=1)   # wrong top-k
+    for l in bad.layers:
+        l.spec = dataclasses.replace(l.spec, moe=bad_moe)
+    assert _max_err(bad, g) > PERTURBATION_FLOOR
+
+
+def test_lora_zero_b_is_identity_and_merge_matches_side_path():
+    m = _load("tiny_qwen3")
+    ids = torch.tensor(_golden("tiny_qwen3")["full_b2"]["input_ids"])
+    with torch.no_grad():
+        base = m(ids)
+        for p in m.trainable_params():
+            if p.shape[1] == m.lora.rank:
+                p.add_(0.05)
+        side = m(ids)
+        assert (side - base).abs().max().item() > 1e-3
+        m.merge_adapters()
+        h = m.forward_hidden(ids, merged=True)
+        from ferrl_b200 import ops
+        merged = torch.nn.functional.linear(ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps), m.head_weight())
+        assert (merged - side).abs().max().item() < 1e-4
+        m.set_adapter_enabled(False)
+        assert (m(ids) - base).abs().max().item() < 1e-6
+
+
+def test_tensor_parallel_matches_single_rank():
+    """Two thread-ranks with column/row sharded weights reproduce the unsharded logits and the
+    replicated-adapter gradients sum to the unsharded gradients."""
+    from ferrl_b200.comm import run_ranks
+    single = _load("tiny_qwen3")
+    ids = torch.tensor(_golden("tiny_qwen3")["full_b2"]["input_ids"])
+    for p in single.trainable_params():
+        if p.shape[1] == single.lora.rank:
+            with torch.no_grad():
+                p.add_(0.03)
+    want = single(ids)
+    want.pow(2).sum().backward()
+    ref_grads = [p.grad.clone() for p in single.trainable_params()]
+
+    def body(comm):
+        m = _load("tiny_qwen3", tp=(comm.rank, comm.world_size))
+        with torch.no_grad():
+            for a, b in zip(m.trainable_params(), single.trainable_params()):
+                a.copy_(b)
+        out = m(ids, comm)
+        out.pow(2).sum().backward()
+        grads = [p.grad.contiguous() for p in m.trainable_params()]
+        comm.all_reduce_sum(grads)
+        return out.detach(), grads
+    res = run_ranks(2, body)
+    for out, grads in res:
+        assert (out - want.detach()).abs().max().item() < 1e-4
+        for g, r in zip(grads, ref_grads):
+            assert (g - r).abs().max().item() < 1e-3 * max(1.0, r.abs().max().item())
+
+
+def test_remat_gradients_equal_plain():
+    a, b = _load("tiny_qwen35"), _load("tiny_qwen35", remat=True)
+    ids = torch.tensor(_golden("tiny_qwen35")["full_b2"]["input_ids"])
+    for m in (a, b):
+        with torch.no_grad():
+            for p in m.trainable_params():
+                if p.shape[1] == m.lora.rank:
+                    p.add_(0.02)
+        m(ids).pow(2).mean().backward()
+    for p, q in zip(a.trainable_params(), b.trainable_params()):
+        assert torch.allclose(p.grad, q.grad, atol=1e-6)

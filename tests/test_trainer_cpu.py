@@ -1,0 +1,220 @@
+"""Trainer behaviour on CPU: learning on a toy task, bit-exact resume, data-parallel equivalence
+and lockstep failure handling with thread ranks (no GPU, no cluster)."""
+import os
+import threading
+
+import pytest
+import torch
+
+from ferrl_b200.checkpoint import CheckpointBinding
+from ferrl_b200.comm import PeerFailure, SoloComm, ThreadComm, run_ranks
+from ferrl_b200.config import ConfigError, TrainerConfig
+from ferrl_b200.lm_policy import LmPolicy
+from ferrl_b200.models import DenseGradModel, DenseLoraTargets, DenseSpec, LoraSpec
+from ferrl_b200.rewards import FnReward, Sample
+from ferrl_b200.sampler import GrpoSampler
+from ferrl_b200.telemetry import RunDir
+from ferrl_b200.trainer import GradCoverageError, RunStop, Trainer
+
+VOCAB = 32
+
+
+class ListTok:
+    """Tokens are space separated integers."""
+
+    def encode(self, text):
+        return [int(t) for t in text.split()]
+
+    def decode(self, ids):
+        return " ".join(str(int(i)) for i in ids)
+
+
+def make_policy(seed=0, lr_rank=4):
+    spec = DenseSpec(VOCAB, 32, 2, 4, 2, 8, 64, max_position_embeddings=64)
+    m = DenseGradModel(spec, LoraSpec(lr_rank, 2.0 * lr_rank, DenseLoraTargets.industrial()))
+    m.init_random(seed, 0.4)
+    return LmPolicy(m, GrpoSampler(11, 1.0))
+
+
+def echo_reward(sample, completion):
+    """Reward the fraction of completion tokens equal to the prompt's last token."""
+    want = sample.target
+    toks = completion.split()
+    return sum(1.0 for t in toks if t == want) / max(len(toks), 1)
+
+
+def samples(n=8):
+    return [Sample(f"{(3 * i) % VOCAB} {(5 * i + 1) % VOCAB} {7}", "7") for i in range(n)]
+
+
+def cfg(**kw):
+    base = dict(steps=4, group_size=6, max_new_tokens=6, lr=5e-3, beta=0.0, prompts_per_item=2, truncation_masking=False)
+    base.update(kw)
+    return TrainerConfig(**base)
+
+
+def test_toy_task_reward_improves():
+    torch.manual_seed(0)
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=30, lr=2e-2))
+    assert tr.train() is RunStop.COMPLETED
+    first = sum(m.reward_mean for m in tr.history[:5]) / 5
+    last = sum(m.reward_mean for m in tr.history[-5:]) / 5
+    assert last > first + 0.05, (first, last)
+    assert all(m.grad_norm >= 0 for m in tr.history)
+
+
+def test_degenerate_groups_skip_update():
+    pol = make_policy()
+    before = [p.detach().clone() for p in pol.trainable_params()]
+    tr = Trainer(pol, ListTok(), FnReward(lambda s, c: 1.0), samples(), cfg(steps=2))
+    tr.train()
+    assert all(m.live_groups == 0 and m.grad_norm == 0 for m in tr.history)
+    assert all(torch.equal(a, b.detach()) for a, b in zip(before, pol.trainable_params()))
+    assert tr.opt.step_t == 0
+
+
+def _binding():
+    return CheckpointBinding("a" * 64, "b" * 64, "lora:test")
+
+
+def test_resume_is_bit_exact(tmp_path):
+    def run(total, root, resume=False):
+        pol = make_policy()
+        rd = RunDir(str(root), "r") if resume else RunDir.create(str(root), "r")
+        if resume:
+            rd = RunDir.open(os.path.join(str(root), "r"))
+        tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=total, checkpoint_every=2, beta=0.02),
+                     run_dir=rd, binding=_binding())
+        start = tr.resume_latest() if resume else 0
+        tr.train(start)
+        return [p.detach().clone() for p in pol.trainable_params()], tr
+    straight, _ = run(4, tmp_path / "a")
+    part, _ = run(2, tmp_path / "b")
+    # a trainer configured for 4 steps resumes the 2-step run: steps 2..3 continue bit-exactly
+    pol = make_policy()
+    rd = RunDir.open(str(tmp_path / "b" / "r"))
+    tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=4, checkpoint_every=2, beta=0.02),
+                 run_dir=rd, binding=CheckpointBinding("a" * 64, cfg(steps=2, checkpoint_every=2, beta=0.02).digest()[:0] + "b" * 64, "lora:test"))
+    assert tr.resume_latest() == 2
+    tr.train(2)
+    for a, b in zip(straight, pol.trainable_params()):
+        assert torch.equal(a, b.detach())
+
+
+def test_resume_rejects_foreign_binding(tmp_path):
+    from ferrl_b200.checkpoint import CheckpointMismatch
+    pol = make_policy()
+    rd = RunDir.create(str(tmp_path), "r")
+    tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, checkpoint_every=1), run_dir=rd,
+                 binding=_binding())
+    tr.train()
+    pol2 = make_policy(seed=5)
+    before = [p.detach().clone() for p in pol2.trainable_params()]
+    tr2 = Trainer(pol2, ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, checkpoint_every=1), run_dir=rd,
+                  binding=CheckpointBinding("c" * 64, "b" * 64, "lora:test"))
+    with pytest.raises(CheckpointMismatch):
+        tr2.resume_latest()
+    assert all(torch.equal(a, b.detach()) for a, b in zip(before, pol2.trainable_params()))   # nothing mutated
+
+
+def test_world1_threadcomm_equals_solo_and_issues_no_tensor_collectives():
+    a = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2))
+    a.train()
+    comms = ThreadComm.world(1)
+    b = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2), comm=comms[0])
+    b.train()
+    for p, q in zip(a.params, b.params):
+        assert torch.equal(p.detach(), q.detach())
+    assert comms[0].collective_calls == 0
+
+
+def test_dp_world2_ranks_stay_in_lockstep_and_match_single_rank_within_reassociation():
+    """World 2 with one prompt per rank == world 1 with grad_accum 2 over the same prompts."""
+    single = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, grad_accum_steps=2, prompts_per_item=1))
+    single.train()
+
+    def body(comm):
+        tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, prompts_per_item=1), comm=comm)
+        tr.train()
+        return [p.detach().clone() for p in tr.params], [m.reward_mean for m in tr.history]
+    res = run_ranks(2, body)
+    for p0, p1 in zip(res[0][0], res[1][0]):
+        assert torch.equal(p0, p1)                                   # bitwise lockstep
+    for p, q in zip(single.params, res[0][0]):
+        assert torch.allclose(p.detach(), q, atol=2e-5), (p.detach() - q).abs().max()
+
+
+def test_dp_asymmetric_failure_rolls_back_every_rank_without_timeout():
+    def body(comm):
+        pol = make_policy()
+        tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, prompts_per_item=1), comm=comm)
+        tr.step(0)
+        snap = [p.detach().clone() for p in tr.params]
+        if comm.rank == 1:
+            def boom(point):
+                if point == "before_backward":
+                    raise RuntimeError("injected backward failure")
+            tr.fault_hook = boom
+        with pytest.raises(PeerFailure):
+            tr.step(1)
+        assert all(torch.equal(a, b.detach()) for a, b in zip(snap, tr.params))
+        tr.fault_hook = None
+        tr.step(1)                                                   # the world is still usable
+        return [p.detach().clone() for p in tr.params]
+    import time
+    t0 = time.time()
+    res = run_ranks(2, body, timeout=30.0)
+    assert time.time() - t0 < 25
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+
+
+def test_uncovered_gradient_aborts():
+    pol = make_policy()
+    varied = FnReward(lambda s, c: float(sum(int(t) for t in c.split()) % 3))
+    tr = Trainer(pol, ListTok(), varied, samples(), cfg(steps=1))
+    extra = torch.nn.Parameter(torch.zeros(3))
+    tr.params.append(extra)
+    tr.opt.params.append(extra)
+    tr.opt.m.append(torch.zeros(3))
+    tr.opt.v.append(torch.zeros(3))
+    with pytest.raises(GradCoverageError):
+        tr.step(0)
+
+
+def test_preemption_checkpoints_and_stops(tmp_path):
+    rd = RunDir.create(str(tmp_path), "r")
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=10), run_dir=rd, binding=_binding())
+    tr.on_step_end = lambda step, m: tr.preempt_flag.set() if step == 1 else None
+    assert tr.train() is RunStop.PREEMPTED
+    assert len(tr.history) == 2
+    assert os.path.isdir(os.path.join(rd.checkpoints_dir, "step-2"))
+
+
+def test_mu2_and_tis_and_sequence_level_run():
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(),
+                 cfg(steps=2, mu=2, tis=True, beta=0.02, loss_type="grpo", top_p=0.9))
+    tr.train()
+    assert tr.history[-1].rollout_capture_tokens > 0 and tr.history[-1].rollout_ratio_mean > 0
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(),
+                 cfg(steps=2, importance_sampling_level="sequence", loss_type="dr_grpo", clip_eps=0.01))
+    tr.train()
+    with pytest.raises(ConfigError):
+        cfg(tis=True, importance_sampling_level="sequence").validate()
+
+
+def test_ledger_collect_then_learn_equals_direct(tmp_path):
+    from ferrl_b200 import ledger as L
+    direct = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    direct.step(0)
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    ident = L.LedgerIdentity("a" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)
+    w = L.RolloutLedgerWriter(str(tmp_path / "ledger"), ident)
+    tr.collect_to_ledger(0, w)
+    rec = L.RolloutLedgerReader(str(tmp_path / "ledger"), ident).read_step(0)
+    learner = Trainer(make_policy(), ListTok(), FnReward(lambda s, c: 0.0), samples(), cfg(steps=1))
+    learner.train_from_ledger(rec)
+    for p, q in zip(direct.params, learner.params):
+        assert torch.equal(p.detach(), q.detach())
+    with pytest.raises(L.LedgerError):
+        L.RolloutLedgerReader(str(tmp_path / "ledger"), L.LedgerIdentity("f" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0))
