@@ -23,6 +23,10 @@ struct GemmArgs {
   int force_bn;                                                   // 0 = heuristic
   int split_k;                                                    // <= 1: none
   float* partial;                                                 // [split_k, M, N] fp32 scratch when split_k > 1
+  // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu
+  int ar_world, ar_rank; unsigned ar_epoch; int ar_max_tiles; unsigned long long ar_limit_ns;
+  long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
+  PeerTable ar_stage, ar_outbuf, ar_flags;
 };
 void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out);
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);

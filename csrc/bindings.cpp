@@ -55,6 +55,13 @@ int* status_word() {
   return it->second.data_ptr<int>();
 }
 
+ferrl::PeerTable table_of_fwd(const std::vector<int64_t>& ptrs) {
+  TORCH_CHECK(ptrs.size() <= ferrl::kMaxRanks, "too many ranks");
+  ferrl::PeerTable t{};
+  for (size_t i = 0; i < ptrs.size(); ++i) t.ptr[i] = reinterpret_cast<void*>(ptrs[i]);
+  return t;
+}
+
 int64_t kernel_status() {
   int h = 0;
   C10_CUDA_CHECK(cudaMemcpy(&h, status_word(), sizeof(int), cudaMemcpyDeviceToHost));
@@ -101,6 +108,36 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     a.partial = partial.data_ptr<float>();
     a.split_k = split;
   }
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
+// Row-parallel projection fused with its tensor-parallel all-reduce:
+// out = sum_over_ranks(A_r B_r^T (+ A2 B2^T)) (+ residual), identical on every rank.
+Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
+                      const optional<Tensor>& residual, std::vector<int64_t> stage, std::vector<int64_t> outbuf,
+                      std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t epoch, int64_t max_tiles,
+                      int64_t stage_elems, int64_t out_elems, double limit_s) {
+  TORCH_CHECK(A.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_allreduce: bf16");
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1, "gemm_allreduce: shapes");
+  c10::cuda::CUDAGuard guard(A.device());
+  ferrl::GemmArgs a{};
+  a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
+  a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
+  if (A2.has_value() && A2->defined()) {
+    TORCH_CHECK(B2.has_value() && B2->defined() && A2->stride(1) == 1 && B2->stride(1) == 1, "gemm_allreduce: side operands");
+    a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
+  }
+  Tensor out = at::empty({a.M, a.N}, A.options());
+  a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = false;
+  if (residual.has_value() && residual->defined()) { a.residual = residual->data_ptr(); a.ldr = residual->stride(0); }
+  a.status = status_word(); a.num_sms = num_sms();
+  a.force_bn = (a.N >= 256 && static_cast<int64_t>((a.M + 127) / 128) * ((a.N + 255) / 256) >= num_sms()) ? 256 : 128;
+  if (a.N < 128) a.force_bn = 64;
+  a.ar_world = world; a.ar_rank = rank; a.ar_epoch = static_cast<unsigned>(epoch); a.ar_max_tiles = max_tiles;
+  a.ar_limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
+  a.ar_stage_elems = stage_elems; a.ar_out_elems = out_elems;
+  a.ar_stage = table_of_fwd(stage); a.ar_outbuf = table_of_fwd(outbuf); a.ar_flags = table_of_fwd(flags);
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
   return out;
 }
@@ -527,6 +564,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split) -> Tensor", &gemm);
+  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
   m.def("kernel_status() -> int", &kernel_status);
   m.def("reset_status() -> ()", &reset_status);
   m.def("rmsnorm(Tensor x, Tensor? res, Tensor? w, Tensor? gate, float eps, bool zc) -> (Tensor, Tensor)", &rmsnorm);

@@ -23,6 +23,7 @@
 
 #include "../api.h"
 #include "../common.cuh"
+#include "../symm/symm.cuh"
 
 namespace ferrl {
 
@@ -44,7 +45,65 @@ struct GemmParams {
   int split_k;          // > 1: each tile covers a slice of the k-tiles and writes fp32 partials
   int kb_per_split;
   float* partial;       // [split_k, M, N] fp32 when split_k > 1
+  // Fused all-reduce for tensor-parallel row-parallel projections, active when ar_world > 1.
+  // All NVLink traffic is posted stores.  Output tile t belongs to rank t % world:
+  //   1. every rank's epilogue writes its bf16 partial of tile t into the owner's staging buffer,
+  //      slot [t / world][rank], in a chunk-major layout (a warp store covers 512 contiguous bytes),
+  //      then releases ready[t][rank] in the owner's flags;
+  //   2. the owner waits for all ready flags, sums the slots in rank order (+ residual), writes the
+  //      tile into its own `out` and into every peer's `ar_outbuf`, and releases done[t] everywhere;
+  //   3. every rank copies the tiles it does not own from its local `ar_outbuf` into `out` as their
+  //      done flags arrive, between its own tiles where it can and in a final sweep for the rest.
+  int ar_world, ar_rank;
+  uint32_t ar_epoch;
+  PeerTable ar_stage, ar_outbuf, ar_flags;
+  int ar_max_tiles;
+  uint64_t ar_limit_ns;
 };
+
+// flag layout inside each rank's flag buffer: ready[tile][kMaxRanks] then done[tile]
+__device__ __forceinline__ uint32_t* ar_ready(const PeerTable& f, int rank_mem, int tile, int from) {
+  return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(tile) * kMaxRanks + from;
+}
+__device__ __forceinline__ uint32_t* ar_done(const PeerTable& f, int rank_mem, int max_tiles, int tile) {
+  return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * kMaxRanks + tile;
+}
+__device__ __forceinline__ bool flag_reached(const uint32_t* flag, uint32_t epoch) {
+  return static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0;   // epochs only grow; tolerates wrap-around
+}
+
+// Bounded spin on a flag word in local memory; one thread calls it.
+__device__ __forceinline__ bool ar_wait_flag(const uint32_t* flag, uint32_t epoch, uint64_t limit_ns, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!flag_reached(flag, epoch)) {
+    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) {
+      atomicCAS(status, kStatusOk, kStatusPeerWaitTimeout);
+      return false;
+    }
+  }
+  return true;
+}
+
+__device__ __forceinline__ uint4 pack8(const float* a) {
+  uint4 o;
+  uint32_t* op = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a[2 * e], a[2 * e + 1]);
+    op[e] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return o;
+}
+__device__ __forceinline__ void add8(float* a, const uint4& x) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float2 f = __bfloat1622float2(h[e]);
+    a[2 * e] += f.x;
+    a[2 * e + 1] += f.y;
+  }
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -74,14 +133,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait. Returns false when the CTA is aborting or the limit expired (and then
 // records `code`).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, uint64_t limit_ns = WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   uint64_t t0 = globaltimer_ns();
   uint32_t spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xff) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, kStatusOk, code);
         return false;
@@ -185,6 +244,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* acc_empty = acc_full + 2;          // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* epi_bar = acc_empty + 3;           // epilogue-group barrier (4 warps) of the all-reduce mode
+  volatile int* pull_ready = reinterpret_cast<volatile int*>(acc_empty + 4);
+  // a peer may enter the kernel later than this rank: every wait of the all-reduce mode allows for that skew
+  const uint64_t wait_limit = p.ar_world > 1 ? WAIT_LIMIT_NS + p.ar_limit_ns : WAIT_LIMIT_NS;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -204,6 +267,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(&acc_full[a], 1);
       mbar_init(&acc_empty[a], 4);
     }
+    mbar_init(epi_bar, 4);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -229,7 +293,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
         const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer, wait_limit)) {
             ok = false;
             break;
           }
@@ -265,14 +329,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
         const int acc = it & 1;
-        if (!mbar_wait(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) break;
+        if (!mbar_wait(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma, wait_limit)) break;
         acc_phase[acc] ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         const int ks = tile % p.split_k;
         const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma, wait_limit)) {
             ok = false;
             break;
           }
@@ -300,15 +364,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t acc_phase[2] = {0, 0};
     int it = 0;
+    // ---- all-reduce mode state
+    constexpr int CPR = BN / 8;                   // 16-byte chunks per tile row
+    const int et = threadIdx.x - 64;              // 0..127 within the epilogue group
+    const int out_tiles = m_tiles * n_tiles;
+    // tiles owned by peers, numbered densely so that the copies spread evenly over the CTAs
+    auto peer_tile = [&](int u) -> int {
+      const int g = u / (p.ar_world - 1), pos = u % (p.ar_world - 1);
+      return g * p.ar_world + (pos < p.ar_rank ? pos : pos + 1);
+    };
+    int pull_u = blockIdx.x;                      // next peer tile this CTA copies out of the local ar_outbuf
+    uint32_t epi_phase = 0;
+    auto epi_sync = [&]() -> bool {               // bounded barrier over the 4 epilogue warps
+      __syncwarp();
+      if (lane == 0) mbar_arrive(epi_bar);
+      const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit);
+      epi_phase ^= 1;
+      return ok && !*abort_flag;
+    };
+    auto copy_tile = [&](int t) {                 // local ar_outbuf -> out, one tile
+      const int tmi = t / n_tiles, tni = t % n_tiles;
+      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.ar_outbuf.ptr[p.ar_rank]);
+#pragma unroll 4
+      for (int i = et; i < BM * CPR; i += 128) {
+        const int rr = tmi * BM + i / CPR, cc = tni * BN + (i % CPR) * 8;
+        if (rr >= p.M || cc >= p.N) continue;
+        const uint4 x = *reinterpret_cast<const uint4*>(src + static_cast<long long>(rr) * p.N + cc);
+        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + cc) = x;
+      }
+    };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
       int ks, mi, ni;
       tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       const int acc = it & 1;
-      if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue)) break;
+      if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit)) break;
       acc_phase[acc] ^= 1;
       tc_fence_after();
       const int row = mi * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      const int out_tile = mi * n_tiles + ni;
+      __nv_bfloat16* ar_slot = nullptr;
+      if (p.ar_world > 1)
+        ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
+                  (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -327,6 +425,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             } else {
               for (int e = 0; e < ncols; ++e) op[e] = __uint_as_float(r[e]);
             }
+          }
+          continue;
+        }
+        if (p.ar_world > 1) {
+          // bf16 partial of this rank, pushed into the tile owner's staging slot; rows past M hold the
+          // zero fill of the TMA load, so no bounds test is needed inside the slot
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            float f8[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[v * 8 + e]);
+            reinterpret_cast<uint4*>(ar_slot)[(c / 8 + v) * BM + q * 32 + lane] = pack8(f8);
           }
           continue;
         }
@@ -383,7 +493,65 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
+      if (p.ar_world > 1) {
+        const int owner = out_tile % p.ar_world;
+        __threadfence_system();
+        if (!epi_sync()) break;
+        if (et == 0) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), p.ar_epoch);
+        if (owner == p.ar_rank) {
+          if (et == 0) {
+            bool ok = true;
+            for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
+              ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), p.ar_epoch, p.ar_limit_ns, p.status);
+            if (!ok) *abort_flag = 1;
+          }
+          if (!epi_sync()) break;
+          // sum the world slots of this tile in rank order; lanes walk along a row so that the stores
+          // to `out` and to the peers' buffers cover whole 128-byte lines
+          const uint4* slot0 = reinterpret_cast<const uint4*>(
+              static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
+              static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
+#pragma unroll 2
+          for (int i = et; i < BM * CPR; i += 128) {
+            const int rt = i / CPR, ch = i % CPR;
+            const int rr = mi * BM + rt, cc = ni * BN + ch * 8;
+            if (rr >= p.M || cc >= p.N) continue;
+            float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q2 = 0; q2 < p.ar_world; ++q2) add8(a8, slot0[q2 * (BM * CPR) + ch * BM + rt]);
+            if (HAS_RES) add8(a8, *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr) * p.ldr + cc));
+            const uint4 o = pack8(a8);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + cc) = o;
+            const long long off = static_cast<long long>(rr) * p.N + cc;
+            for (int q2 = 0; q2 < p.ar_world; ++q2)
+              if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
+          }
+          __threadfence_system();
+          if (!epi_sync()) break;
+          if (et == 0)
+            for (int q2 = 0; q2 < p.ar_world; ++q2)
+              if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), p.ar_epoch);
+        }
+        // between tiles: take one finished tile of a peer if its flag is already here
+        const int pt = peer_tile(pull_u);
+        if (et == 0)
+          *pull_ready = pt < out_tiles && flag_reached(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), p.ar_epoch);
+        if (!epi_sync()) break;
+        if (*pull_ready) {
+          copy_tile(pt);
+          pull_u += gridDim.x;
+        }
+      }
+    }
+    // final sweep: the tiles whose flags had not arrived yet
+    if (p.ar_world > 1 && !*abort_flag) {
+      for (int pt = peer_tile(pull_u); pt < out_tiles; pull_u += gridDim.x, pt = peer_tile(pull_u)) {
+        if (et == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), p.ar_epoch, p.ar_limit_ns,
+                                     p.status))
+          *abort_flag = 1;
+        if (!epi_sync()) break;
+        copy_tile(pt);
+      }
     }
   }
 
@@ -471,7 +639,7 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     tmA2 = tmA;
     tmB2 = tmB;
   }
-  GemmParams p;
+  GemmParams p{};
   p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
   p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 16;
@@ -482,6 +650,20 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.split_k = (kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no empty slices
   p.partial = a.partial;
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
+  p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
+  if (p.ar_world > 1) {
+    if (a.out_f32 || p.split_k > 1 || (a.N % 8) || a.ldo != a.N) return "fused all-reduce needs bf16 output, no split-k, N % 8 == 0, packed output";
+    const int out_tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+    if (out_tiles > a.ar_max_tiles) return "fused all-reduce: flag buffer too small for this many tiles";
+    const long long slots = static_cast<long long>((out_tiles + p.ar_world - 1) / p.ar_world) * p.ar_world;
+    if (slots * BM * BN > a.ar_stage_elems || static_cast<long long>(a.M) * a.N > a.ar_out_elems)
+      return "fused all-reduce: symmetric buffers too small for this output";
+    if (a.residual && ((a.ldr % 8) || (reinterpret_cast<uintptr_t>(a.residual) & 15)))
+      return "fused all-reduce: residual must be 16-byte aligned with ldr % 8 == 0";
+    if (a.ar_world > kMaxRanks || a.ar_rank < 0 || a.ar_rank >= a.ar_world) return "fused all-reduce: bad rank/world";
+    p.ar_rank = a.ar_rank; p.ar_epoch = a.ar_epoch; p.ar_stage = a.ar_stage; p.ar_outbuf = a.ar_outbuf;
+    p.ar_flags = a.ar_flags; p.ar_max_tiles = a.ar_max_tiles; p.ar_limit_ns = a.ar_limit_ns;
+  }
   auto kern = gemm_kernel<BN, OUT_F32, HAS_RES>;
   static bool attr_set = false;
   if (!attr_set) {

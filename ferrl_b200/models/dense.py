@@ -133,13 +133,10 @@ class DenseLayer(nn.Module):
             kv_out[0][:, :S].copy_(k)
             kv_out[1][:, :S].copy_(v)
         a = ops.attention(q, k, v, scale=self.scale, causal=True, softmax_fp32=True)
-        o = lin(self.o, a.reshape(B, S, self.hq * self.D))
-        o = reduce_from_tp(o, comm)
+        o = self.o.forward_reduce(a.reshape(B, S, self.hq * self.D), comm, merged)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
         x = copy_to_tp(x, comm)
-        d = lin(self.down, ops.swiglu(lin(self.gate_up, x), self.act))
-        d = reduce_from_tp(d, comm)
-        return h + d
+        return self.down.forward_reduce(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged, residual=h)
 
     # one-token forward against the cache (rollout; merged weights)
     def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm):
@@ -153,12 +150,10 @@ class DenseLayer(nn.Module):
         q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin, kv_len[:, None].long())
         ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
         a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_len + 1, scale=self.scale)
-        o = self.o.forward_merged(a.reshape(B, self.hq * self.D))
-        o = reduce_from_tp(o, comm)
+        o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
-        d = self.down.forward_merged(ops.swiglu(self.gate_up.forward_merged(x), self.act))
-        d = reduce_from_tp(d, comm)
-        return h + d
+        return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
+                                        residual=h)
 
 
 def ops_cache_write(k_cache, v_cache, k, v, kv_len):

@@ -259,6 +259,27 @@ class FusedLoraLinear(nn.Module):
         a, b = self._stacks()
         return ops.lora_linear(x, self.weight, a, b, wt=self.weight_t)
 
+    def forward_reduce(self, x: torch.Tensor, comm, merged: bool = False, residual=None) -> torch.Tensor:
+        """Row-parallel use: the projection, its tensor-parallel sum over ``comm`` and an
+        optional residual add.  On GPUs with a registered ``GemmAllReducer`` all three happen
+        in the GEMM kernel; otherwise the projection is followed by ``reduce_from_tp``."""
+        from ..parallel.tp import reduce_from_tp
+        if comm.world_size > 1 and x.is_cuda:
+            from ..parallel.symm import gemm_all_reducer
+            red = gemm_all_reducer(comm)
+            if red is not None:
+                from ..ops import cuda as _c
+                if merged:
+                    w = self.weight_merged if self.weight_merged is not None else self.weight
+                    y = _c.lora_linear_reduce(x, w, None, None, None, red, residual)
+                else:
+                    a, b = self._stacks()
+                    y = _c.lora_linear_reduce(x, self.weight, a, b, self.weight_t, red, residual)
+                if y is not None:
+                    return y
+        y = reduce_from_tp(self.forward_merged(x) if merged else self.forward(x), comm)
+        return y if residual is None else residual + y
+
     def forward_merged(self, x: torch.Tensor) -> torch.Tensor:
         """Rollout path over the merged snapshot (no adapter side path)."""
         w = self.weight_merged if self.weight_merged is not None else self.weight

@@ -106,6 +106,50 @@ class _LoraLinear(torch.autograd.Function):
         return dx, None, None, da, db
 
 
+class _LoraLinearReduce(torch.autograd.Function):
+    """Row-parallel projection whose tensor-parallel sum happens inside the GEMM kernel.
+    Backward is the local one: the cotangent of an all-reduced value is already replicated."""
+
+    @staticmethod
+    def forward(ctx, x, w, wt, a_stack, b_stack, residual, reducer):
+        K = x.shape[-1]
+        x2 = x.reshape(-1, K)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        t = a16 = b16 = None
+        if a_stack is not None:
+            a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()
+            b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()
+            t = gemm(x2, a16)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, w.shape[0])
+            if not res2.is_contiguous():
+                res2 = res2.contiguous()
+        y = reducer(x2, w, t, b16, res2)
+        ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
+        ctx.x_shape = x.shape
+        ctx.x_grad = x.requires_grad
+        ctx.res_grad = residual is not None and residual.requires_grad
+        return y.view(*x.shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, _, _, da, db = _LoraLinear.backward(ctx, dy)
+        return dx, None, None, da, db, (dy if ctx.res_grad else None), None
+
+
+def lora_linear_reduce(x, w, a_stack, b_stack, wt, reducer, residual=None):
+    """``all_reduce(x Wᵀ + (x Aᵀ) Bᵀ) (+ residual)`` in one kernel per rank; ``None`` when the
+    shapes do not fit the reducer's symmetric buffers (the caller then reduces separately)."""
+    if not (_bf16(x) and _bf16(w)) or w.requires_grad or x.shape[-1] % 8:
+        return None
+    rows = x.numel() // x.shape[-1]
+    if not reducer.fits(rows, w.shape[0]):
+        return None
+    return _LoraLinearReduce.apply(x, w, wt, a_stack, b_stack, residual, reducer)
+
+
 def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None):
     if not (_bf16(x) and _bf16(w)) or bias is not None or w.requires_grad:
         return eager.lora_linear(x, w, a_stack, b_stack, bias)

@@ -125,7 +125,64 @@ class SymmAllReducer:
         return self.heap.all_reduce_(SymmBuffer(self.buf.local[:nbytes], self.buf.ptrs), out)
 
 
+class GemmAllReducer:
+    """Buffers and epochs for the fused row-parallel GEMM -> all-reduce kernel.
+
+    ``y = sum_r (x_r W_rᵀ + t_r Bᵀ) (+ residual)`` comes out of ONE launch per rank: the
+    tcgen05 GEMM's epilogue pushes each partial tile into the tile owner's staging slot over
+    NVLink, the owner sums the slots in rank order and pushes the result to every peer
+    while the tensor cores are already on the next tiles (``csrc/gemm/tcgen05_gemm.cu``).
+    The reference issues the projection and then a blocking ``ncclAllReduce`` of the whole
+    activation (``crates/ferrl/src/tensor_parallel.rs:417-510``).
+
+    Every rank must call with the same shapes in the same order (true for lockstep
+    tensor-parallel forward passes); epochs advance once per call.
+    """
+
+    BM, BN_MAX, BN_MIN = 128, 256, 64
+
+    def __init__(self, heap: SymmHeap, max_rows: int, max_cols: int):
+        self.heap = heap
+        mt = (max_rows + self.BM - 1) // self.BM
+        self.max_tiles = mt * ((max_cols + self.BN_MIN - 1) // self.BN_MIN)
+        npad = (max_cols + self.BN_MAX - 1) // self.BN_MAX * self.BN_MAX
+        self.stage_elems = mt * self.BM * npad + heap.world * self.BM * self.BN_MAX
+        self.out_elems = max_rows * max_cols
+        self.stage = heap.alloc(self.stage_elems * 2)
+        self.outbuf = heap.alloc(self.out_elems * 2)
+        self.flags = heap.alloc(self.max_tiles * (MAX_RANKS + 1) * 4)
+        self.flags.local.zero_()
+        torch.cuda.synchronize(heap.device)
+        if heap.world > 1:
+            heap.comm.barrier()   # nobody signals into flags that are still being cleared
+        self.epoch = 0
+
+    def fits(self, rows: int, cols: int) -> bool:
+        mt = (rows + self.BM - 1) // self.BM
+        tiles = mt * ((cols + self.BN_MIN - 1) // self.BN_MIN)
+        npad = (cols + self.BN_MAX - 1) // self.BN_MAX * self.BN_MAX
+        return (cols % 8 == 0 and tiles <= self.max_tiles and rows * cols <= self.out_elems
+                and mt * self.BM * npad + self.heap.world * self.BM * self.BN_MAX <= self.stage_elems)
+
+    def __call__(self, a, b, a2=None, b2=None, residual=None) -> torch.Tensor:
+        self.heap.guard()
+        self.epoch += 1
+        h = self.heap
+        return h.C.lib().gemm_allreduce(a, b, a2, b2, residual, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
+                                        h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
+                                        self.out_elems, h.wait_limit_s)
+
+
 _REDUCERS: dict = {}
+_GEMM_REDUCERS: dict = {}
+
+
+def register_gemm_all_reducer(comm: Comm, reducer: GemmAllReducer) -> None:
+    _GEMM_REDUCERS[id(comm)] = reducer
+
+
+def gemm_all_reducer(comm: Comm) -> Optional[GemmAllReducer]:
+    return _GEMM_REDUCERS.get(id(comm))
 
 
 def register_all_reducer(comm: Comm, reducer: SymmAllReducer) -> None:

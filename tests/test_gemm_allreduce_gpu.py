@@ -1,0 +1,149 @@
+"""Fused row-parallel GEMM -> all-reduce kernel.
+
+On one GPU the peer is played by the host: its partial tiles, ready flags, reduced tiles and done
+flags are written before the launch, so the kernel under test never waits on another launch.  The
+check covers every byte the kernel must produce: its own output, the partial tiles and flags it
+pushes to the peer, and the reduced tiles it sends back.  The real two-process run lives in
+``multi_gpu_tp_worker.py``.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+BM, MAXR = 128, 16
+
+
+def _need_gpu(n=1):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} CUDA device(s)")
+
+
+def _chunk_major(tile):
+    """[128, BN] row-major tile -> staging layout [BN/8][128][8]."""
+    return tile.reshape(BM, -1, 8).permute(1, 0, 2).reshape(-1)
+
+
+def _tiles(M, N, BN):
+    return (M + BM - 1) // BM, (N + BN - 1) // BN
+
+
+def _pad_tile(full, mi, ni, BN):
+    t = torch.zeros(BM, BN, dtype=full.dtype, device=full.device)
+    src = full[mi * BM:(mi + 1) * BM, ni * BN:(ni + 1) * BN]
+    t[:src.shape[0], :src.shape[1]] = src
+    return t
+
+
+@pytest.mark.parametrize("M,N,K,rank,res,lora", [(300, 512, 256, 0, False, False), (300, 512, 256, 1, True, True),
+                                                  (128, 4096, 2048, 0, True, False)])
+def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
+    _need_gpu()
+    from ferrl_b200.comm import SoloComm
+    from ferrl_b200.ops import cuda as C
+    from ferrl_b200.parallel.symm import GemmAllReducer, SymmHeap
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(M + N + K + rank)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    peer = 1 - rank
+    a = [rnd(M, K).to(torch.bfloat16) for _ in range(2)]
+    b = [(rnd(N, K) / K ** 0.5).to(torch.bfloat16) for _ in range(2)]
+    t2 = [rnd(M, 16).to(torch.bfloat16) for _ in range(2)] if lora else [None, None]
+    b2 = (rnd(N, 16) * 0.1).to(torch.bfloat16) if lora else None
+    residual = rnd(M, N).to(torch.bfloat16) if res else None
+    part = []
+    for r in range(2):
+        p = a[r].float() @ b[r].float().t()
+        if lora:
+            p = p + t2[r].float() @ b2.float().t()
+        part.append(p.to(torch.bfloat16))
+    total = part[0].float() + part[1].float()
+    if res:
+        total = total + residual.float()
+    want = total.to(torch.bfloat16)
+
+    heap = SymmHeap(SoloComm(), dev, wait_limit_s=0.5)
+    red = GemmAllReducer(heap, M, N)
+    BN = 128                                   # the binding picks 128 for these (small) problems
+    mt, nt = _tiles(M, N, BN)
+    slot = BM * BN
+    mine = dict(stage=red.stage.local.view(torch.bfloat16), out=red.outbuf.local.view(torch.bfloat16),
+                flags=red.flags.local.view(torch.int32))
+    theirs = dict(stage=torch.zeros_like(mine["stage"]), out=torch.zeros_like(mine["out"]),
+                  flags=torch.zeros_like(mine["flags"]))
+    epoch = 7
+    done_base = red.max_tiles * MAXR
+    for t in range(mt * nt):
+        mi, ni = divmod(t, nt)
+        if t % 2 == rank:     # mine to reduce: the peer's partial is already in my staging slot
+            off = ((t // 2) * 2 + peer) * slot
+            mine["stage"][off:off + slot] = _chunk_major(_pad_tile(part[peer], mi, ni, BN))
+            mine["flags"][t * MAXR + peer] = epoch
+        else:                 # the peer's to reduce: its result is already in my output buffer
+            rows = slice(mi * BM, min(M, (mi + 1) * BM))
+            cols = slice(ni * BN, min(N, (ni + 1) * BN))
+            mine["out"][:M * N].view(M, N)[rows, cols] = want[rows, cols]
+            mine["flags"][done_base + t] = epoch
+    ptrs = lambda key: [(mine if r == rank else theirs)[key].data_ptr() for r in range(2)]
+    torch.cuda.synchronize()
+    y = C.lib().gemm_allreduce(a[rank], b[rank], t2[rank], b2, residual, ptrs("stage"), ptrs("out"), ptrs("flags"),
+                               rank, 2, epoch, red.max_tiles, red.stage_elems, red.out_elems, 0.5)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    tol = 0.02 * float(want.float().abs().max())
+    assert float((y.float() - want.float()).abs().max()) <= tol
+    peer_out = theirs["out"][:M * N].view(M, N)
+    for t in range(mt * nt):
+        mi, ni = divmod(t, nt)
+        rows = slice(mi * BM, min(M, (mi + 1) * BM))
+        cols = slice(ni * BN, min(N, (ni + 1) * BN))
+        if t % 2 == rank:
+            # reduced tile delivered to the peer, bit-identical to my own copy, and announced
+            assert torch.equal(peer_out[rows, cols], y[rows, cols])
+            assert int(theirs["flags"][done_base + t]) == epoch
+        else:
+            off = ((t // 2) * 2 + rank) * slot
+            got = theirs["stage"][off:off + slot].reshape(BN // 8, BM, 8).permute(1, 0, 2).reshape(BM, BN)
+            ref = _pad_tile(part[rank], mi, ni, BN)
+            assert float((got.float() - ref.float()).abs().max()) <= tol
+            assert int(theirs["flags"][t * MAXR + rank]) == epoch
+            assert torch.equal(y[rows, cols], want[rows, cols])     # copied verbatim from my output buffer
+
+
+def test_missing_peer_runs_out_without_hanging():
+    """No peer ever signals: the owner's wait must expire, the status word must say so and the
+    context must stay usable."""
+    _need_gpu()
+    from ferrl_b200.comm import SoloComm
+    from ferrl_b200.ops import cuda as C
+    from ferrl_b200.parallel.symm import GemmAllReducer, SymmHeap
+    dev = torch.device("cuda", 0)
+    heap = SymmHeap(SoloComm(), dev, wait_limit_s=0.3)
+    red = GemmAllReducer(heap, 256, 256)
+    a = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+    b = torch.randn(256, 128, device=dev).to(torch.bfloat16)
+    spare = {k: torch.zeros_like(getattr(red, k).local) for k in ("stage", "outbuf", "flags")}
+    ptrs = lambda k: [getattr(red, k).local.data_ptr(), spare[k].data_ptr()]
+    C.lib().gemm_allreduce(a, b, None, None, None, ptrs("stage"), ptrs("outbuf"), ptrs("flags"), 0, 2, 3,
+                           red.max_tiles, red.stage_elems, red.out_elems, 0.3)
+    torch.cuda.synchronize()
+    assert C.kernel_status() != 0
+    C.lib().reset_status()
+    y = C.gemm(a, b)                              # the same kernel family still runs
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    assert float((y.float() - a.float() @ b.float().t()).abs().max()) < 1.0
+
+
+def test_two_process_fused_tp():
+    _need_gpu(2)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "multi_gpu_tp_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "TP_FUSED_PASS" in res.stdout
