@@ -1,6 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
+    python bench_kernels.py --profile-case gemm|gemm_decode|decode_attn|sample|flash   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -51,13 +52,59 @@ class Timer:
         return ts[len(ts) // 2] * 1e-3            # median seconds
 
 
+def profile_case(name, C):
+    """A small fixed workload per kernel (inputs above the 126 MB L2, well under 2 GB on the
+    device, 2 warm-up + 3 measured launches) meant to be run under a profiler that replays
+    every launch many times."""
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    bf = torch.bfloat16
+    g = torch.Generator(device=dev).manual_seed(0)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g).to(bf)
+    if name == "gemm":
+        a, b = rnd(8192, 4096), rnd(8192, 4096)
+        fn = lambda: C.gemm(a, b)
+    elif name == "gemm_decode":
+        a, b = rnd(128, 4096), rnd(24576, 4096)
+        fn = lambda: C.gemm(a, b)
+    elif name == "decode_attn":
+        q, k, v = rnd(128, 32, 128), rnd(128, 1536, 8, 128), rnd(128, 1536, 8, 128)
+        lens = torch.full((128,), 832, device=dev, dtype=torch.int32)
+        fn = lambda: C.decode_attention(q, k, v, lens, scale=128 ** -0.5)
+    elif name == "sample":
+        logits = rnd(512, 151936)
+        rows = torch.arange(512, device=dev)
+        fn = lambda: C.sample_top_p(logits, 1, rows, 0, 1.0, 0.95)
+    elif name == "flash":
+        q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+        fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True)
+    else:
+        raise SystemExit(f"unknown profile case {name!r}")
+    evs = []
+    with torch.no_grad():
+        for i in range(5):
+            a_, b_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a_.record()
+            fn()
+            b_.record()
+            evs.append((a_, b_))
+    torch.cuda.synchronize()
+    print(f"profile case {name}: " + " ".join(f"{x.elapsed_time(y) * 1e3:.1f}us" for x, y in evs), flush=True)
+    if C.kernel_status() != 0:
+        raise SystemExit(f"kernel status {C.kernel_status()}")
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
     ap.add_argument("--iters", type=int, default=15)
     ap.add_argument("--json", default="")
+    ap.add_argument("--profile-case", default="", help="run one kernel a few times on a small case and exit")
     args = ap.parse_args()
     from ferrl_b200.ops import cuda as C
+    if args.profile_case:
+        return profile_case(args.profile_case, C)
     only = set(filter(None, args.only.split(",")))
     want = lambda k: not only or k in only  # noqa: E731
     dev = torch.device("cuda", 0)

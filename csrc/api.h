@@ -23,6 +23,8 @@ struct GemmArgs {
   int force_bn;                                                   // 0 = heuristic
   int split_k;                                                    // <= 1: none
   float* partial;                                                 // [split_k, M, N] fp32 scratch when split_k > 1
+  // grouped mode: B is [n_experts * N, K]; tile_expert[m tile] = expert (or -1: skip the tile)
+  const int* tile_expert; int n_experts;
   // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu
   int ar_world, ar_rank; unsigned ar_epoch; int ar_max_tiles; unsigned long long ar_limit_ns;
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
@@ -120,5 +122,17 @@ const char* logprob_rows_bwd(int dtype, void* logits, long long ld, const long l
 const char* sample_rows(int dtype, const void* logits, long long ld, const long long* global_rows,
                         unsigned long long seed, const int* draw_dev, int draw_host, long long* tok_out, float* lp_out,
                         int rows, int V, float temperature, float top_p, cudaStream_t s);
+
+// ---- mixture of experts (csrc/moe/moe.cu); all return nullptr on success
+const char* moe_route(const float* logits, long long ld, int T, int E, int k, bool renorm, float* probs, float* scores,
+                      int* idx, int* counts, cudaStream_t stream);
+const char* moe_plan(const int* idx, const int* counts, int n_pairs, int k, int E, int max_rows, int* row_of,
+                     int* token_of, int* tile_expert, int* seg_start, cudaStream_t stream);
+const char* moe_gather(const void* x, long long ldx, const int* token_of, const float* pair_w, const int* row_of,
+                       int n_pairs, float* row_scale, int rows, int H, void* xs, cudaStream_t stream);
+const char* moe_combine(const void* ys, const int* row_of, const float* w, int T, int k, int H, void* out,
+                        cudaStream_t stream);
+const char* moe_pair_dot(const void* dy, const void* ys, const int* row_of, int n_pairs, int k, int H, float* dw,
+                         cudaStream_t stream);
 
 }  // namespace ferrl

@@ -142,6 +142,100 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   return out;
 }
 
+// ---------------------------------------------------------------- mixture of experts
+// logits [T, E] fp32 -> (probs [T,E] f32, scores [T,k] f32, idx [T,k] i32, counts [E] i32)
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_route(const Tensor& logits, int64_t k, bool renorm) {
+  TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "moe_route: fp32 [T,E]");
+  c10::cuda::CUDAGuard guard(logits.device());
+  const int64_t T = logits.size(0), E = logits.size(1);
+  Tensor probs = at::empty({T, E}, logits.options());
+  Tensor scores = at::empty({T, k}, logits.options());
+  Tensor idx = at::empty({T, k}, logits.options().dtype(at::kInt));
+  Tensor counts = at::empty({E}, logits.options().dtype(at::kInt));
+  FERRL_CHECK(ferrl::moe_route(logits.data_ptr<float>(), logits.stride(0), T, E, k, renorm, probs.data_ptr<float>(),
+                               scores.data_ptr<float>(), idx.data_ptr<int>(), counts.data_ptr<int>(), stream()));
+  return {probs, scores, idx, counts};
+}
+
+// idx [T,k] i32, counts [E] -> (row_of [T*k], token_of [max_rows], tile_expert [max_rows/128], seg_start [E+1])
+std::tuple<Tensor, Tensor, Tensor, Tensor> moe_plan(const Tensor& idx, const Tensor& counts) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous(), "moe_plan: idx i32 [T,k]");
+  c10::cuda::CUDAGuard guard(idx.device());
+  const int64_t T = idx.size(0), k = idx.size(1), E = counts.size(0);
+  const int64_t pairs = T * k;
+  // every expert may waste up to 127 rows of padding, but never more rows than tiles it could fill
+  const int64_t max_rows = (pairs + std::min<int64_t>(E, pairs) * 127 + 127) / 128 * 128;
+  auto io = idx.options();
+  Tensor row_of = at::empty({pairs}, io);
+  Tensor token_of = at::full({std::max<int64_t>(max_rows, 128)}, -1, io);
+  Tensor tile_expert = at::full({std::max<int64_t>(max_rows / 128, 1)}, -1, io);
+  Tensor seg_start = at::zeros({E + 1}, io);
+  FERRL_CHECK(ferrl::moe_plan(idx.data_ptr<int>(), counts.data_ptr<int>(), pairs, k, E, max_rows, row_of.data_ptr<int>(),
+                              token_of.data_ptr<int>(), tile_expert.data_ptr<int>(), seg_start.data_ptr<int>(), stream()));
+  return {row_of, token_of, tile_expert, seg_start};
+}
+
+// xs[row] = (pair_w ? pair_w[pair of row] : 1) * x[token_of[row]]; padding rows are zero
+Tensor moe_gather(const Tensor& x, const Tensor& token_of, const optional<Tensor>& pair_w, const Tensor& row_of) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "moe_gather: bf16 [T,H]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = token_of.size(0), H = x.size(1);
+  Tensor xs = at::empty({rows, H}, x.options());
+  Tensor row_scale;
+  const float* pw = nullptr;
+  if (pair_w.has_value() && pair_w->defined()) {
+    TORCH_CHECK(pair_w->scalar_type() == at::kFloat && pair_w->is_contiguous() && pair_w->numel() == row_of.numel(), "moe_gather: pair weights f32 [T*k]");
+    row_scale = at::zeros({rows}, x.options().dtype(at::kFloat));
+    pw = pair_w->data_ptr<float>();
+  }
+  FERRL_CHECK(ferrl::moe_gather(x.data_ptr(), x.stride(0), token_of.data_ptr<int>(), pw, row_of.data_ptr<int>(),
+                                row_of.numel(), pw ? row_scale.data_ptr<float>() : nullptr, rows, H, xs.data_ptr(), stream()));
+  return xs;
+}
+
+// ys[rows, N] = xs[rows, K] x W[e(row)]^T with W [E, N, K]; rows sorted by expert in 128-row segments
+Tensor moe_grouped_gemm(const Tensor& xs, const Tensor& W, const Tensor& tile_expert) {
+  TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16, "moe_grouped_gemm: bf16");
+  TORCH_CHECK(xs.dim() == 2 && W.dim() == 3 && W.is_contiguous() && xs.is_contiguous() && xs.size(1) == W.size(2), "moe_grouped_gemm: xs [R,K], W [E,N,K]");
+  TORCH_CHECK(xs.size(0) % 128 == 0 && tile_expert.numel() * 128 >= xs.size(0) && tile_expert.scalar_type() == at::kInt, "moe_grouped_gemm: rows in 128-row tiles with one expert id each");
+  c10::cuda::CUDAGuard guard(xs.device());
+  ferrl::GemmArgs a{};
+  a.A = xs.data_ptr(); a.B = W.data_ptr(); a.lda = xs.stride(0); a.ldb = W.size(2);
+  a.M = xs.size(0); a.N = W.size(1); a.K = xs.size(1);
+  a.tile_expert = tile_expert.data_ptr<int>(); a.n_experts = W.size(0);
+  // rows of unused tiles are never written: start from zeros so padding stays finite downstream
+  Tensor out = at::zeros({a.M, a.N}, xs.options());
+  a.out = out.data_ptr(); a.ldo = a.N;
+  a.status = status_word(); a.num_sms = num_sms();
+  a.force_bn = a.N >= 256 ? 256 : (a.N >= 128 ? 128 : 64);
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
+// out[t] = sum_j w[t,j] * ys[row_of[t,j]]  (w undefined: plain sum)
+Tensor moe_combine(const Tensor& ys, const Tensor& row_of, const optional<Tensor>& w, int64_t T, int64_t k) {
+  TORCH_CHECK(ys.is_cuda() && ys.scalar_type() == at::kBFloat16 && ys.is_contiguous() && row_of.numel() == T * k, "moe_combine: shapes");
+  c10::cuda::CUDAGuard guard(ys.device());
+  Tensor out = at::empty({T, ys.size(1)}, ys.options());
+  const float* wp = nullptr;
+  if (w.has_value() && w->defined()) {
+    TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous() && w->numel() == T * k, "moe_combine: weights f32 [T,k]");
+    wp = w->data_ptr<float>();
+  }
+  FERRL_CHECK(ferrl::moe_combine(ys.data_ptr(), row_of.data_ptr<int>(), wp, T, k, ys.size(1), out.data_ptr(), stream()));
+  return out;
+}
+
+// dw[t,j] = <dy[t], ys[row_of[t,j]]>
+Tensor moe_pair_dot(const Tensor& dy, const Tensor& ys, const Tensor& row_of, int64_t k) {
+  TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && ys.is_contiguous() && dy.size(1) == ys.size(1), "moe_pair_dot: shapes");
+  c10::cuda::CUDAGuard guard(dy.device());
+  Tensor dw = at::empty({dy.size(0), k}, dy.options().dtype(at::kFloat));
+  FERRL_CHECK(ferrl::moe_pair_dot(dy.data_ptr(), ys.data_ptr(), row_of.data_ptr<int>(), row_of.numel(), k, dy.size(1),
+                                  dw.data_ptr<float>(), stream()));
+  return dw;
+}
+
 std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const optional<Tensor>& res, const optional<Tensor>& w,
                                    const optional<Tensor>& gate, double eps, bool zc) {
   TORCH_CHECK(x.is_cuda() && x.is_contiguous(), "rmsnorm: contiguous CUDA tensor required");
@@ -565,6 +659,12 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split) -> Tensor", &gemm);
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
+  m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
+  m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
+  m.def("moe_gather(Tensor x, Tensor token_of, Tensor? pair_w, Tensor row_of) -> Tensor", &moe_gather);
+  m.def("moe_grouped_gemm(Tensor xs, Tensor W, Tensor tile_expert) -> Tensor", &moe_grouped_gemm);
+  m.def("moe_combine(Tensor ys, Tensor row_of, Tensor? w, int T, int k) -> Tensor", &moe_combine);
+  m.def("moe_pair_dot(Tensor dy, Tensor ys, Tensor row_of, int k) -> Tensor", &moe_pair_dot);
   m.def("kernel_status() -> int", &kernel_status);
   m.def("reset_status() -> ()", &reset_status);
   m.def("rmsnorm(Tensor x, Tensor? res, Tensor? w, Tensor? gate, float eps, bool zc) -> (Tensor, Tensor)", &rmsnorm);

@@ -45,6 +45,9 @@ struct GemmParams {
   int split_k;          // > 1: each tile covers a slice of the k-tiles and writes fp32 partials
   int kb_per_split;
   float* partial;       // [split_k, M, N] fp32 when split_k > 1
+  // grouped (mixture-of-experts) mode: A rows are sorted by expert in 128-row aligned segments,
+  // B is [E * N, K]; tile_expert[mi] names the expert of m tile mi, or -1 for an unused tile.
+  const int* tile_expert;
   // Fused all-reduce for tensor-parallel row-parallel projections, active when ar_world > 1.
   // All NVLink traffic is posted stores.  Output tile t belongs to rank t % world:
   //   1. every rank's epilogue writes its bf16 partial of tile t into the owner's staging buffer,
@@ -291,6 +294,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int ks, mi, ni;
         tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        int b_row0 = ni * BN;
+        if (p.tile_expert) {
+          const int e = p.tile_expert[mi];
+          if (e < 0) continue;
+          b_row0 += e * p.N;
+        }
         const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer, wait_limit)) {
@@ -302,10 +311,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           mbar_expect_tx(&full[stage], C::STAGE_BYTES);
           if (kb < kb1) {
             tma_load_2d(sa, &tmA, &full[stage], kb * BK, mi * BM);
-            tma_load_2d(sb, &tmB, &full[stage], kb * BK, ni * BN);
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, b_row0);
           } else {
             tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, mi * BM);
-            tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, ni * BN);
+            tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, b_row0);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -327,8 +336,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t acc_phase[2] = {0, 0};
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-        const int acc = it & 1;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        if (p.tile_expert) {
+          int ks_, mi_, ni_;
+          tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks_, mi_, ni_);
+          if (p.tile_expert[mi_] < 0) continue;
+        }
+        const int acc = (it++) & 1;
         if (!mbar_wait(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma, wait_limit)) break;
         acc_phase[acc] ^= 1;
         tc_fence_after();
@@ -393,10 +407,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + cc) = x;
       }
     };
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int ks, mi, ni;
       tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
-      const int acc = it & 1;
+      if (p.tile_expert && p.tile_expert[mi] < 0) continue;
+      const int acc = (it++) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit)) break;
       acc_phase[acc] ^= 1;
       tc_fence_after();
@@ -631,7 +646,9 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   using C = Cfg<BN>;
   CUtensorMap tmA, tmB, tmA2, tmB2;
   if (!make_map(&tmA, a.A, a.M, a.K, a.lda, BM)) return "cuTensorMapEncodeTiled failed for A";
-  if (!make_map(&tmB, a.B, a.N, a.K, a.ldb, BN)) return "cuTensorMapEncodeTiled failed for B";
+  const long long b_rows = a.tile_expert ? static_cast<long long>(a.N) * (a.n_experts > 0 ? a.n_experts : 1) : a.N;
+  if (a.tile_expert && (a.K2 > 0 || a.split_k > 1 || a.ar_world > 1)) return "grouped mode takes no side operand, k-split or all-reduce";
+  if (!make_map(&tmB, a.B, b_rows, a.K, a.ldb, BN)) return "cuTensorMapEncodeTiled failed for B";
   if (a.K2 > 0) {
     if (!make_map(&tmA2, a.A2, a.M, a.K2, a.lda2, BM)) return "cuTensorMapEncodeTiled failed for A2";
     if (!make_map(&tmB2, a.B2, a.N, a.K2, a.ldb2, BN)) return "cuTensorMapEncodeTiled failed for B2";
@@ -649,6 +666,7 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.kb_per_split = (kb_total + split - 1) / split;
   p.split_k = (kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no empty slices
   p.partial = a.partial;
+  p.tile_expert = a.tile_expert;
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
   if (p.ar_world > 1) {

@@ -227,7 +227,10 @@ decode_attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     return static_cast<long long>(b) * seq_stride + static_cast<long long>(j) * tok_stride + hk * D + d0;
   };
 
-  for (int base = s0 + (warp * KPW + grp); base < s1; base += WARPS * KPW * UNROLL) {
+  // The trip count must be the same for every lane of a warp (the score reduction below shuffles
+  // across the full warp), so the loop runs on the warp's first key and lanes past the end idle.
+  for (int wbase = s0 + warp * KPW; wbase < s1; wbase += WARPS * KPW * UNROLL) {
+    const int base = wbase + grp;
     uint4 kraw[UNROLL][2], vraw[UNROLL][2];
     bool live[UNROLL];
 #pragma unroll

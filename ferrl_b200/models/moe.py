@@ -82,14 +82,30 @@ def moe_experts(x: torch.Tensor, indices: torch.Tensor, scores: torch.Tensor, ga
     return out
 
 
+def _device_moe(x2, router_w, gate_up, down, top_k, act, gate_up_t=None, down_t=None):
+    """Device-resident plan: router kernel, counting-sort dispatch into 128-row expert segments,
+    tcgen05 grouped GEMMs, deterministic combine (``csrc/moe/moe.cu``).  ``None`` when the
+    tensors are outside the kernels' domain."""
+    if x2.dtype != torch.bfloat16 or router_w.dtype != torch.bfloat16 or router_w.shape[0] > 1024 or top_k > 16:
+        return None
+    from .. import ops
+    from ..ops import cuda as C
+    logits = ops.lora_linear(x2, router_w, None, None).float()
+    scores, idx, counts, _ = C.moe_route(logits, top_k, True)
+    # the eager plan rounds the routing weights to the activation dtype before use
+    return C.moe_experts(x2, scores.to(x2.dtype), idx, counts, gate_up, down, act, gate_up_t, down_t)
+
+
 def sparse_moe_block(x: torch.Tensor, router_w, gate_up, down, top_k: int, shared=None, shared_gate_w=None,
                      act: str = "silu") -> torch.Tensor:
     """``x`` ``[..., H]``. ``shared`` is a callable shared-expert MLP, gated by
     ``sigmoid(x @ shared_gate_w^T)``."""
     shape = x.shape
     x2 = x.reshape(-1, shape[-1])
-    _, scores, idx = topk_router(x2, router_w, top_k)
-    y = moe_experts(x2, idx, scores.to(x2.dtype), gate_up, down, act)
+    y = _device_moe(x2, router_w, gate_up, down, top_k, act) if x2.is_cuda else None
+    if y is None:
+        _, scores, idx = topk_router(x2, router_w, top_k)
+        y = moe_experts(x2, idx, scores.to(x2.dtype), gate_up, down, act)
     if shared is not None:
         y = y + torch.sigmoid(F.linear(x2, shared_gate_w)) * shared(x2)
     return y.reshape(shape)

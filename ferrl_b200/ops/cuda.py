@@ -326,6 +326,90 @@ def swiglu(gate_up, act="silu"):
     return _Glu.apply(gate_up, _ACT[act])
 
 
+# ------------------------------------------------------------------ MoE
+class _MoeRoute(torch.autograd.Function):
+    """fp32 softmax over the router logits, top-k and renormalisation in one kernel; the
+    backward is the closed form of softmax -> gather -> normalise on the small [T, E] table."""
+
+    @staticmethod
+    def forward(ctx, logits, k, renorm):
+        probs, scores, idx, counts = lib().moe_route(logits.contiguous(), k, renorm)
+        ctx.save_for_backward(probs, scores, idx)
+        ctx.renorm = renorm
+        ctx.mark_non_differentiable(idx, counts)
+        return scores, idx, counts, probs.detach()
+
+    @staticmethod
+    def backward(ctx, ds, _di, _dc, _dp):
+        probs, scores, idx = ctx.saved_tensors
+        li = idx.long()
+        if ctx.renorm:
+            top = probs.gather(1, li).sum(-1, keepdim=True)
+            ds = (ds - (ds * scores).sum(-1, keepdim=True)) / top
+        dp = torch.zeros_like(probs).scatter_(1, li, ds)
+        return probs * (dp - (dp * probs).sum(-1, keepdim=True)), None, None
+
+
+def moe_route(logits_f32, k, renorm=True):
+    """``(scores [T,k] f32, idx [T,k] i32, counts [E] i32, probs [T,E] f32)``."""
+    return _MoeRoute.apply(logits_f32, int(k), bool(renorm))
+
+
+class _MoeExperts(torch.autograd.Function):
+    """Routed frozen experts: plan -> gather -> grouped GEMM -> SwiGLU -> grouped GEMM -> combine,
+    with no host synchronisation; gradients flow to the tokens and to the routing scores."""
+
+    @staticmethod
+    def forward(ctx, x, scores, idx, counts, gate_up, down, gate_up_t, down_t, act):
+        L = lib()
+        T, k = idx.shape
+        row_of, token_of, tile_expert, _ = L.moe_plan(idx.contiguous(), counts)
+        xs = L.moe_gather(x.contiguous(), token_of, None, row_of)
+        gu = L.moe_grouped_gemm(xs, gate_up, tile_expert)
+        del xs
+        h = L.glu_fwd(gu, act)
+        ys = L.moe_grouped_gemm(h, down, tile_expert)
+        del h
+        sc = scores.float().contiguous()
+        out = L.moe_combine(ys, row_of, sc, T, k)
+        ctx.save_for_backward(gu, ys, sc, row_of, token_of, tile_expert, gate_up, down, gate_up_t, down_t)
+        ctx.act, ctx.k = act, k
+        ctx.score_dtype = scores.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        L = lib()
+        gu, ys, sc, row_of, token_of, tile_expert, gate_up, down, gate_up_t, down_t = ctx.saved_tensors
+        dout = dout.contiguous()
+        T = dout.shape[0]
+        dsc = L.moe_pair_dot(dout, ys, row_of, ctx.k).to(ctx.score_dtype)
+        dys = L.moe_gather(dout, token_of, sc.view(-1), row_of)
+        if down_t is None:
+            down_t = down.transpose(1, 2).contiguous()
+        dh = L.moe_grouped_gemm(dys, down_t, tile_expert)
+        del dys
+        dgu = L.glu_bwd(gu, dh, ctx.act)
+        del dh
+        if gate_up_t is None:
+            gate_up_t = gate_up.transpose(1, 2).contiguous()
+        dxs = L.moe_grouped_gemm(dgu, gate_up_t, tile_expert)
+        dx = L.moe_combine(dxs, row_of, None, T, ctx.k)
+        return dx, dsc, None, None, None, None, None, None, None
+
+
+def moe_experts(x, scores, idx, counts, gate_up, down, act="silu", gate_up_t=None, down_t=None):
+    """``x`` ``[T,H]`` bf16; ``gate_up`` ``[E,2I,H]``, ``down`` ``[E,H,I]`` frozen bf16; optional
+    resident transposes for the backward GEMMs.  ``None`` when the shapes are outside the kernels'
+    domain (caller falls back to the eager plan)."""
+    if not (_bf16(x) and _bf16(gate_up) and _bf16(down)) or act not in _ACT or gate_up.requires_grad or down.requires_grad:
+        return None
+    H, I = x.shape[-1], down.shape[-1]
+    if H % 8 or I % 8 or not (gate_up.is_contiguous() and down.is_contiguous()):
+        return None
+    return _MoeExperts.apply(x, scores, idx, counts, gate_up, down, gate_up_t, down_t, _ACT[act])
+
+
 def embedding(ids, table, scale=1.0):
     if table.requires_grad:
         return eager.embedding(ids, table, scale)
