@@ -135,4 +135,15 @@ const char* moe_combine(const void* ys, const int* row_of, const float* w, int T
 const char* moe_pair_dot(const void* dy, const void* ys, const int* row_of, int n_pairs, int k, int H, float* dw,
                          cudaStream_t stream);
 
+// ---- GatedDeltaNet (csrc/kernels/gdn.cu)
+const char* gdn_conv_fwd(const void* x, long long ldx, const void* w, const void* left, int B, int L, int C, int K,
+                         bool act, void* y, cudaStream_t stream);
+const char* gdn_conv_bwd(const void* x, long long ldx, const void* w, const void* left, const void* dy, int B, int L,
+                         int C, int K, bool act, void* dx, cudaStream_t stream);
+const char* gdn_conv_step(const void* x, long long ldx, const void* w, void* state, int B, int C, int K, bool act,
+                          void* y, cudaStream_t stream);
+const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
+                            const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
+                            bool l2norm, float eps, void* out, cudaStream_t stream);
+
 }  // namespace ferrl

@@ -142,6 +142,68 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   return out;
 }
 
+// ---------------------------------------------------------------- GatedDeltaNet
+// x [B, L, C] bf16 (last dim contiguous, rows evenly strided), w [C, K], left [B, C, K-1] or none -> y [B, L, C]
+Tensor gdn_conv_fwd(const Tensor& x, const Tensor& w, const optional<Tensor>& left, bool act) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1 &&
+                  x.stride(0) == x.size(1) * x.stride(1), "gdn_conv_fwd: x bf16 [B,L,C] with uniform row stride");
+  TORCH_CHECK(w.scalar_type() == at::kBFloat16 && w.is_contiguous() && w.size(0) == x.size(2), "gdn_conv_fwd: w bf16 [C,K]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* lp = nullptr;
+  if (left.has_value() && left->defined()) {
+    TORCH_CHECK(left->scalar_type() == at::kBFloat16 && left->is_contiguous() && left->size(0) == x.size(0) &&
+                    left->size(1) == x.size(2) && left->size(2) == w.size(1) - 1, "gdn_conv_fwd: left bf16 [B,C,K-1]");
+    lp = left->data_ptr();
+  }
+  Tensor y = at::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  FERRL_CHECK(ferrl::gdn_conv_fwd(x.data_ptr(), x.stride(1), w.data_ptr(), lp, x.size(0), x.size(1), x.size(2), w.size(1),
+                                  act, y.data_ptr(), stream()));
+  return y;
+}
+
+Tensor gdn_conv_bwd(const Tensor& x, const Tensor& w, const optional<Tensor>& left, const Tensor& dy, bool act) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 3 && x.stride(2) == 1 &&
+                  x.stride(0) == x.size(1) * x.stride(1) && dy.is_contiguous() && dy.scalar_type() == at::kBFloat16,
+              "gdn_conv_bwd: shapes");
+  c10::cuda::CUDAGuard guard(x.device());
+  const void* lp = (left.has_value() && left->defined()) ? left->data_ptr() : nullptr;
+  Tensor dx = at::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  FERRL_CHECK(ferrl::gdn_conv_bwd(x.data_ptr(), x.stride(1), w.data_ptr(), lp, dy.data_ptr(), x.size(0), x.size(1),
+                                  x.size(2), w.size(1), act, dx.data_ptr(), stream()));
+  return dx;
+}
+
+// one token: x [B, C] (row stride free), state [B, C, K-1] updated in place -> y [B, C]
+Tensor gdn_conv_step(const Tensor& x, const Tensor& w, Tensor state, bool act) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "gdn_conv_step: x bf16 [B,C]");
+  TORCH_CHECK(state.scalar_type() == at::kBFloat16 && state.is_contiguous() && state.size(0) == x.size(0) &&
+                  state.size(1) == x.size(1) && state.size(2) == w.size(1) - 1 && w.is_contiguous(), "gdn_conv_step: state bf16 [B,C,K-1]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+  FERRL_CHECK(ferrl::gdn_conv_step(x.data_ptr(), x.stride(0), w.data_ptr(), state.data_ptr(), x.size(0), x.size(1),
+                                   w.size(1), act, y.data_ptr(), stream()));
+  return y;
+}
+
+// q,k [B, Hk*KD], v [B, Hv*VD] bf16 (row strides free), g,beta [B,Hv] f32, S [B,Hv,KD,VD] f32 in place -> o [B,Hv,VD]
+Tensor gdn_decode_step(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta, Tensor S,
+                       bool l2norm, double eps) {
+  TORCH_CHECK(S.is_cuda() && S.scalar_type() == at::kFloat && S.dim() == 4 && S.is_contiguous(), "gdn_decode_step: S f32 [B,Hv,KD,VD]");
+  const int64_t B = S.size(0), Hv = S.size(1), KD = S.size(2), VD = S.size(3);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+                  q.dim() == 2 && k.dim() == 2 && v.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1 && v.stride(1) == 1 &&
+                  q.size(0) == B && v.size(1) == Hv * VD && q.size(1) % KD == 0 && k.size(1) == q.size(1),
+              "gdn_decode_step: q,k [B,Hk*KD], v [B,Hv*VD] bf16");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && g.is_contiguous() && beta.is_contiguous() &&
+                  g.numel() == B * Hv && beta.numel() == B * Hv, "gdn_decode_step: g,beta f32 [B,Hv]");
+  c10::cuda::CUDAGuard guard(S.device());
+  Tensor out = at::empty({B, Hv, VD}, q.options());
+  FERRL_CHECK(ferrl::gdn_decode_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+                                     g.data_ptr<float>(), beta.data_ptr<float>(), S.data_ptr<float>(), B, q.size(1) / KD,
+                                     Hv, KD, VD, l2norm, static_cast<float>(eps), out.data_ptr(), stream()));
+  return out;
+}
+
 // ---------------------------------------------------------------- mixture of experts
 // logits [T, E] fp32 -> (probs [T,E] f32, scores [T,k] f32, idx [T,k] i32, counts [E] i32)
 std::tuple<Tensor, Tensor, Tensor, Tensor> moe_route(const Tensor& logits, int64_t k, bool renorm) {
@@ -659,6 +721,10 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split) -> Tensor", &gemm);
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
+  m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
+  m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
+  m.def("gdn_conv_step(Tensor x, Tensor w, Tensor(a!) state, bool act) -> Tensor", &gdn_conv_step);
+  m.def("gdn_decode_step(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor(a!) S, bool l2norm, float eps) -> Tensor", &gdn_decode_step);
   m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
   m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
   m.def("moe_gather(Tensor x, Tensor token_of, Tensor? pair_w, Tensor row_of) -> Tensor", &moe_gather);

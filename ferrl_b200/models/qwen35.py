@@ -244,7 +244,32 @@ class Qwen35Layer(nn.Module):
         p = f(self.inp, x)
         mixed, z, b, a = p.split([self.conv_dim, self.value_dim, self.vh, self.vh], dim=-1)
         left = None if state is None else state[0]
-        y, new_left = G.causal_depthwise_conv1d(mixed.transpose(1, 2), self.conv_w, left, activation=True)
+        fast = (x.is_cuda and mixed.dtype == torch.bfloat16 and not self.conv_w.requires_grad
+                and self.kd in (16, 32, 64, 128))
+        if fast and decode and state is not None and S_ == 1 and state[0].dtype == torch.bfloat16 \
+                and state[1].dtype == torch.float32 and state[0].is_contiguous() and state[1].is_contiguous():
+            # one-token path: two kernels, both states updated in place
+            from ..ops import cuda as C
+            y = C.gdn_conv_step(mixed[:, 0], self.conv_w, state[0], True)
+            beta = torch.sigmoid(b[:, 0].float())
+            g = -self.A_log.float().exp() * F.softplus(a[:, 0].float() + self.dt_bias.float())
+            core = C.gdn_decode_step(y[:, :self.key_dim], y[:, self.key_dim:2 * self.key_dim], y[:, 2 * self.key_dim:],
+                                     g, beta, state[1], True, 1e-6)
+            core = ops.rmsnorm_gated(core.reshape(-1, self.vd), z.reshape(-1, self.vd), self.gdn_norm, self.eps)
+            return f(self.out, core.reshape(B, S_, self.value_dim)), (state[0], state[1])
+        y = None
+        if fast:
+            from ..ops import cuda as C
+            y = C.gdn_conv(mixed, self.conv_w, left, True)
+        if y is not None:
+            K1 = self.conv_w.shape[-1] - 1
+            ctx = mixed if left is None else torch.cat([left.transpose(1, 2).to(mixed.dtype), mixed], dim=1)
+            if ctx.shape[1] < K1:
+                ctx = F.pad(ctx, (0, 0, K1 - ctx.shape[1], 0))
+            new_left = ctx[:, ctx.shape[1] - K1:].transpose(1, 2).detach()
+        else:
+            y, new_left = G.causal_depthwise_conv1d(mixed.transpose(1, 2), self.conv_w, left, activation=True)
+            y = y.transpose(1, 2)
         if valid is not None and state is not None:
             # conv context must be the last K-1 *real* inputs of every row
             K1 = self.conv_w.shape[-1] - 1
@@ -253,7 +278,6 @@ class Qwen35Layer(nn.Module):
             lens = valid.sum(1).long()
             idx = (lens[:, None] + torch.arange(K1, device=x.device)[None, :]).clamp(max=xx.shape[1] - 1)
             new_left = torch.gather(xx, 1, idx[:, :, None].expand(B, K1, self.conv_dim)).transpose(1, 2)
-        y = y.transpose(1, 2)
         q, k, v = y.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k = q.reshape(B, S_, self.kh, self.kd), k.reshape(B, S_, self.kh, self.kd)
         v = v.reshape(B, S_, self.vh, self.vd)

@@ -326,6 +326,42 @@ def swiglu(gate_up, act="silu"):
     return _Glu.apply(gate_up, _ACT[act])
 
 
+# ------------------------------------------------------------------ GatedDeltaNet
+class _GdnConv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, left, act):
+        ctx.save_for_backward(x, w, left)
+        ctx.act = act
+        return lib().gdn_conv_fwd(x, w, left, act)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, left = ctx.saved_tensors
+        return lib().gdn_conv_bwd(x, w, left, dy.contiguous(), ctx.act), None, None, None
+
+
+def gdn_conv(x, w, left=None, activation=True):
+    """Causal depthwise conv (+SiLU) over ``x`` ``[B, L, C]`` with frozen ``w`` ``[C, K]`` and
+    left context ``[B, C, K-1]``; ``None`` outside the kernel's domain."""
+    if not (_bf16(x) and _bf16(w)) or w.requires_grad or w.shape[-1] > 8 or x.dim() != 3:
+        return None
+    if x.stride(2) != 1 or x.stride(0) != x.shape[1] * x.stride(1):
+        x = x.contiguous()
+    if left is not None:
+        left = left.to(torch.bfloat16).contiguous()
+    return _GdnConv.apply(x, w.contiguous(), left, bool(activation))
+
+
+def gdn_conv_step(x, w, state, activation=True):
+    """One-token conv against ``state`` ``[B, C, K-1]`` (updated in place)."""
+    return lib().gdn_conv_step(x, w.contiguous(), state, bool(activation))
+
+
+def gdn_decode_step(q, k, v, g, beta, S, l2norm=True, eps=1e-6):
+    """Single-token gated delta rule; ``S`` ``[B,Hv,KD,VD]`` float32 is updated in place."""
+    return lib().gdn_decode_step(q, k, v, g.contiguous(), beta.contiguous(), S, bool(l2norm), float(eps))
+
+
 # ------------------------------------------------------------------ MoE
 class _MoeRoute(torch.autograd.Function):
     """fp32 softmax over the router logits, top-k and renormalisation in one kernel; the
