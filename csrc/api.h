@@ -4,6 +4,8 @@
 #include <cuda_runtime.h>
 #include <stddef.h>
 
+#include <cuda_bf16.h>
+
 #include "symm/symm.cuh"
 
 namespace ferrl {
@@ -145,5 +147,32 @@ const char* gdn_conv_step(const void* x, long long ldx, const void* w, void* sta
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                             const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
                             bool l2norm, float eps, void* out, cudaStream_t stream);
+
+// ---- expert parallelism over the symmetric heap (csrc/moe/ep.cu)
+struct EpDispatchParams {
+  const __nv_bfloat16* x; long long ldx;   // [T, H] rows to send
+  const int* idx;                          // [T*k] global expert of every (token, slot) pair
+  const float* pair_w;                     // optional per-pair scale applied while sending
+  int T, k, H, E, E_local, rank, world;
+  const int* my_counts;                    // [E] pairs per global expert on this rank
+  PeerTable counts_all;                    // int [world][E] on every rank
+  PeerTable xs;                            // bf16 [cap_rows][H] receive buffer on every rank
+  PeerTable flags; unsigned epoch; unsigned long long limit_ns; int* status; int* abort_word;
+  int cap_rows;
+  int* dest_row;                           // [T*k] row of each pair in its owner's buffer (out, or in when reuse_plan)
+  int* tile_expert;                        // [cap_rows/128] local expert of each received tile, -1 unused (out)
+  int* local_rows;                         // [1] padded rows in use on this rank (out)
+  int reuse_plan;                          // 1: skip count exchange and planning (backward pass)
+};
+struct EpCombineParams {
+  PeerTable ys;                            // bf16 [cap_rows][H] expert outputs on every rank
+  const int* idx; const int* dest_row; const float* w;   // w optional [T*k]
+  int T, k, H, E_local, rank, world;
+  PeerTable flags; unsigned epoch; unsigned long long limit_ns; int* status; int* abort_word;
+  __nv_bfloat16* out;                      // [T, H]
+  __nv_bfloat16* keep_rows;                // optional [T*k, H]: the pulled rows, for the routing-weight gradient
+};
+const char* ep_dispatch(const EpDispatchParams& p, int num_sms, cudaStream_t stream);
+const char* ep_combine(const EpCombineParams& p, int num_sms, cudaStream_t stream);
 
 }  // namespace ferrl

@@ -256,7 +256,7 @@ Tensor moe_gather(const Tensor& x, const Tensor& token_of, const optional<Tensor
 }
 
 // ys[rows, N] = xs[rows, K] x W[e(row)]^T with W [E, N, K]; rows sorted by expert in 128-row segments
-Tensor moe_grouped_gemm(const Tensor& xs, const Tensor& W, const Tensor& tile_expert) {
+Tensor moe_grouped_gemm(const Tensor& xs, const Tensor& W, const Tensor& tile_expert, const optional<Tensor>& out_buf) {
   TORCH_CHECK(xs.is_cuda() && xs.scalar_type() == at::kBFloat16 && W.scalar_type() == at::kBFloat16, "moe_grouped_gemm: bf16");
   TORCH_CHECK(xs.dim() == 2 && W.dim() == 3 && W.is_contiguous() && xs.is_contiguous() && xs.size(1) == W.size(2), "moe_grouped_gemm: xs [R,K], W [E,N,K]");
   TORCH_CHECK(xs.size(0) % 128 == 0 && tile_expert.numel() * 128 >= xs.size(0) && tile_expert.scalar_type() == at::kInt, "moe_grouped_gemm: rows in 128-row tiles with one expert id each");
@@ -266,11 +266,72 @@ Tensor moe_grouped_gemm(const Tensor& xs, const Tensor& W, const Tensor& tile_ex
   a.M = xs.size(0); a.N = W.size(1); a.K = xs.size(1);
   a.tile_expert = tile_expert.data_ptr<int>(); a.n_experts = W.size(0);
   // rows of unused tiles are never written: start from zeros so padding stays finite downstream
-  Tensor out = at::zeros({a.M, a.N}, xs.options());
+  Tensor out;
+  if (out_buf.has_value() && out_buf->defined()) {
+    TORCH_CHECK(out_buf->scalar_type() == at::kBFloat16 && out_buf->is_contiguous() && out_buf->dim() == 2 &&
+                    out_buf->size(0) == a.M && out_buf->size(1) == a.N, "moe_grouped_gemm: out buffer bf16 [R,N]");
+    out = *out_buf;
+  } else {
+    out = at::zeros({a.M, a.N}, xs.options());
+  }
   a.out = out.data_ptr(); a.ldo = a.N;
   a.status = status_word(); a.num_sms = num_sms();
   a.force_bn = a.N >= 256 ? 256 : (a.N >= 128 ? 128 : 64);
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
+// Expert-parallel dispatch: see csrc/moe/ep.cu.  dest_row / tile_expert / local_rows are outputs
+// unless reuse_plan (then dest_row is the forward plan).
+void ep_dispatch(const Tensor& x, const Tensor& idx, const optional<Tensor>& pair_w, const Tensor& counts,
+                 std::vector<int64_t> counts_all, std::vector<int64_t> xs, std::vector<int64_t> flags, int64_t rank,
+                 int64_t world, int64_t epoch, double limit_s, int64_t cap_rows, Tensor dest_row, Tensor tile_expert,
+                 Tensor local_rows, bool reuse_plan, Tensor abort_word) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "ep_dispatch: x bf16 [T,H]");
+  TORCH_CHECK(idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous() && idx.size(0) == x.size(0), "ep_dispatch: idx i32 [T,k]");
+  TORCH_CHECK(counts.scalar_type() == at::kInt && counts.is_contiguous(), "ep_dispatch: counts i32 [E]");
+  TORCH_CHECK(dest_row.scalar_type() == at::kInt && dest_row.numel() == idx.numel() && tile_expert.numel() * 128 >= cap_rows, "ep_dispatch: plan buffers");
+  c10::cuda::CUDAGuard guard(x.device());
+  ferrl::EpDispatchParams p{};
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x.data_ptr()); p.ldx = x.stride(0);
+  p.idx = idx.data_ptr<int>();
+  if (pair_w.has_value() && pair_w->defined()) {
+    TORCH_CHECK(pair_w->scalar_type() == at::kFloat && pair_w->is_contiguous() && pair_w->numel() == idx.numel(), "ep_dispatch: pair weights");
+    p.pair_w = pair_w->data_ptr<float>();
+  }
+  p.T = x.size(0); p.k = idx.size(1); p.H = x.size(1); p.E = counts.numel(); p.E_local = p.E / world;
+  p.rank = rank; p.world = world; p.my_counts = counts.data_ptr<int>();
+  p.counts_all = table_of_fwd(counts_all); p.xs = table_of_fwd(xs); p.flags = table_of_fwd(flags);
+  p.epoch = static_cast<unsigned>(epoch); p.limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
+  p.status = status_word(); p.abort_word = abort_word.data_ptr<int>(); p.cap_rows = cap_rows;
+  p.dest_row = dest_row.data_ptr<int>(); p.tile_expert = tile_expert.data_ptr<int>(); p.local_rows = local_rows.data_ptr<int>();
+  p.reuse_plan = reuse_plan ? 1 : 0;
+  FERRL_CHECK(ferrl::ep_dispatch(p, num_sms(), stream()));
+}
+
+// Expert-parallel combine: out[t] = sum_j w[t,j] * ys[owner(t,j)][dest_row[t,j]]
+Tensor ep_combine(std::vector<int64_t> ys, const Tensor& idx, const Tensor& dest_row, const optional<Tensor>& w,
+                  int64_t H, int64_t E_local, std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t epoch,
+                  double limit_s, const optional<Tensor>& keep_rows, Tensor abort_word) {
+  TORCH_CHECK(idx.is_cuda() && idx.scalar_type() == at::kInt && idx.dim() == 2 && idx.is_contiguous(), "ep_combine: idx i32 [T,k]");
+  c10::cuda::CUDAGuard guard(idx.device());
+  ferrl::EpCombineParams p{};
+  p.ys = table_of_fwd(ys); p.idx = idx.data_ptr<int>(); p.dest_row = dest_row.data_ptr<int>();
+  if (w.has_value() && w->defined()) {
+    TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous() && w->numel() == idx.numel(), "ep_combine: weights");
+    p.w = w->data_ptr<float>();
+  }
+  p.T = idx.size(0); p.k = idx.size(1); p.H = H; p.E_local = E_local; p.rank = rank; p.world = world;
+  p.flags = table_of_fwd(flags); p.epoch = static_cast<unsigned>(epoch);
+  p.limit_ns = static_cast<unsigned long long>(limit_s * 1e9); p.status = status_word();
+  p.abort_word = abort_word.data_ptr<int>();
+  Tensor out = at::empty({p.T, H}, idx.options().dtype(at::kBFloat16));
+  p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
+  if (keep_rows.has_value() && keep_rows->defined()) {
+    TORCH_CHECK(keep_rows->scalar_type() == at::kBFloat16 && keep_rows->is_contiguous() && keep_rows->numel() == idx.numel() * H, "ep_combine: keep_rows bf16 [T*k,H]");
+    p.keep_rows = reinterpret_cast<__nv_bfloat16*>(keep_rows->data_ptr());
+  }
+  FERRL_CHECK(ferrl::ep_combine(p, num_sms(), stream()));
   return out;
 }
 
@@ -728,7 +789,9 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
   m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
   m.def("moe_gather(Tensor x, Tensor token_of, Tensor? pair_w, Tensor row_of) -> Tensor", &moe_gather);
-  m.def("moe_grouped_gemm(Tensor xs, Tensor W, Tensor tile_expert) -> Tensor", &moe_grouped_gemm);
+  m.def("moe_grouped_gemm(Tensor xs, Tensor W, Tensor tile_expert, Tensor(a!)? out=None) -> Tensor(a!)", &moe_grouped_gemm);
+  m.def("ep_dispatch(Tensor x, Tensor idx, Tensor? pair_w, Tensor counts, int[] counts_all, int[] xs, int[] flags, int rank, int world, int epoch, float limit_s, int cap_rows, Tensor(a!) dest_row, Tensor(b!) tile_expert, Tensor(c!) local_rows, bool reuse_plan, Tensor(d!) abort_word) -> ()", &ep_dispatch);
+  m.def("ep_combine(int[] ys, Tensor idx, Tensor dest_row, Tensor? w, int H, int E_local, int[] flags, int rank, int world, int epoch, float limit_s, Tensor(a!)? keep_rows, Tensor(b!) abort_word) -> Tensor", &ep_combine);
   m.def("moe_combine(Tensor ys, Tensor row_of, Tensor? w, int T, int k) -> Tensor", &moe_combine);
   m.def("moe_pair_dot(Tensor dy, Tensor ys, Tensor row_of, int k) -> Tensor", &moe_pair_dot);
   m.def("kernel_status() -> int", &kernel_status);

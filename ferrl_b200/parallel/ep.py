@@ -29,7 +29,90 @@ class EpContext:
 
     rank: int
     world: int
-    all_to_all_rows: Callable
+    all_to_all_rows: Optional[Callable] = None
+    runtime: Optional["EpRuntime"] = None     # peer-memory data plane (GPUs)
+
+
+class EpRuntime:
+    """Symmetric receive buffers and epochs for the peer-memory dispatch/combine kernels
+    (``csrc/moe/ep.cu``).  ``capacity_factor`` bounds the rows one rank may receive relative to
+    a perfectly balanced routing; an overflow is detected on the device, identically on every
+    rank, and surfaces as an error from ``SymmHeap.check``."""
+
+    def __init__(self, heap, num_experts: int, hidden: int, max_tokens: int, top_k: int,
+                 capacity_factor: float = 2.0):
+        if num_experts % heap.world:
+            raise ValueError(f"{num_experts} experts do not split over {heap.world} ranks")
+        self.heap = heap
+        self.E, self.E_local, self.H = num_experts, num_experts // heap.world, hidden
+        pairs = max_tokens * top_k
+        factor = 1.0 if heap.world == 1 else capacity_factor
+        self.cap_rows = (int(pairs * factor) + self.E_local * 128 + 127) // 128 * 128
+        self.xs = heap.alloc(self.cap_rows * hidden * 2)
+        self.ys = heap.alloc(self.cap_rows * hidden * 2)
+        self.counts_all = heap.alloc(heap.world * num_experts * 4)
+
+    def view(self, buf) -> torch.Tensor:
+        return buf.local.view(torch.bfloat16)[:self.cap_rows * self.H].view(self.cap_rows, self.H)
+
+    def experts(self, x, scores, idx, counts, gate_up, down, act, gate_up_t=None, down_t=None):
+        from ..ops import cuda as C
+        return _EpExperts.apply(x, scores, idx, counts, gate_up, down, gate_up_t, down_t, C._ACT[act], self)
+
+
+class _EpExperts(torch.autograd.Function):
+    """Routed experts sharded over ranks: dispatch (push) -> local grouped GEMMs -> combine (pull).
+    The backward pass sends the weighted cotangents along the same plan."""
+
+    @staticmethod
+    def forward(ctx, x, scores, idx, counts, gate_up, down, gate_up_t, down_t, act, rt):
+        from ..ops import cuda as C
+        L, h = C.lib(), rt.heap
+        h.guard()
+        T, k = idx.shape
+        dev = x.device
+        dest_row = torch.empty(T * k, dtype=torch.int32, device=dev)
+        tile_expert = torch.full((rt.cap_rows // 128,), -1, dtype=torch.int32, device=dev)
+        local_rows = torch.zeros(1, dtype=torch.int32, device=dev)
+        xc = x.contiguous()
+        L.ep_dispatch(xc, idx, None, counts, rt.counts_all.ptrs, rt.xs.ptrs, h.flags.ptrs, h.rank, h.world,
+                      h.next_epoch(), h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, False, h.abort_word)
+        gu = L.moe_grouped_gemm(rt.view(rt.xs), gate_up, tile_expert)
+        hh = L.glu_fwd(gu, act)
+        L.moe_grouped_gemm(hh, down, tile_expert, rt.view(rt.ys))
+        del hh
+        sc = scores.float().contiguous()
+        need = x.requires_grad or scores.requires_grad
+        keep = torch.empty(T * k, x.shape[1], dtype=torch.bfloat16, device=dev) if need else None
+        out = L.ep_combine(rt.ys.ptrs, idx, dest_row, sc, x.shape[1], rt.E_local, h.flags.ptrs, h.rank, h.world,
+                           h.next_epoch(), h.wait_limit_s, keep, h.abort_word)
+        ctx.save_for_backward(gu, keep, sc, idx, counts, dest_row, tile_expert, local_rows, gate_up, down, gate_up_t, down_t)
+        ctx.act, ctx.rt, ctx.score_dtype = act, rt, scores.dtype
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops import cuda as C
+        L, rt = C.lib(), ctx.rt
+        h = rt.heap
+        gu, keep, sc, idx, counts, dest_row, tile_expert, local_rows, gate_up, down, gate_up_t, down_t = ctx.saved_tensors
+        T, k = idx.shape
+        dout = dout.contiguous()
+        ident = torch.arange(T * k, dtype=torch.int32, device=dout.device)
+        dsc = L.moe_pair_dot(dout, keep, ident, k).to(ctx.score_dtype)
+        L.ep_dispatch(dout, idx, sc.view(-1), counts, rt.counts_all.ptrs, rt.xs.ptrs, h.flags.ptrs, h.rank, h.world,
+                      h.next_epoch(), h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, True, h.abort_word)
+        if down_t is None:
+            down_t = down.transpose(1, 2).contiguous()
+        dh = L.moe_grouped_gemm(rt.view(rt.xs), down_t, tile_expert)
+        dgu = L.glu_bwd(gu, dh, ctx.act)
+        del dh
+        if gate_up_t is None:
+            gate_up_t = gate_up.transpose(1, 2).contiguous()
+        L.moe_grouped_gemm(dgu, gate_up_t, tile_expert, rt.view(rt.ys))
+        dx = L.ep_combine(rt.ys.ptrs, idx, dest_row, None, dout.shape[1], rt.E_local, h.flags.ptrs, h.rank, h.world,
+                          h.next_epoch(), h.wait_limit_s, None, h.abort_word)
+        return dx, dsc, None, None, None, None, None, None, None, None
 
 
 def install(ctx: Optional[EpContext]) -> None:
@@ -51,6 +134,15 @@ def sparse_moe(x, router_w, gate_up, down, top_k: int, shared, shared_gate_w, ac
     x2 = x.reshape(-1, shape[-1])
     E_local = gate_up.shape[0]
     E = E_local * ctx.world
+    if ctx.runtime is not None and x2.is_cuda and x2.dtype == torch.bfloat16 and router_w.dtype == torch.bfloat16:
+        from .. import ops
+        from ..ops import cuda as C
+        logits = ops.lora_linear(x2, router_w, None, None).float()
+        scores, idx, counts, _ = C.moe_route(logits, top_k, True)
+        out = ctx.runtime.experts(x2, scores.to(x2.dtype), idx, counts, gate_up, down, act)
+        if shared is not None:
+            out = out + torch.sigmoid(F.linear(x2, shared_gate_w)) * shared(x2)
+        return out.reshape(shape)
     _, scores, idx = M.topk_router(x2, router_w, top_k)
     plan = M.DispatchPlan.build(idx, E)
     xs = x2[plan.token]                                   # rows sorted by global expert => by destination rank

@@ -147,3 +147,13 @@ def test_two_process_fused_tp():
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "TP_FUSED_PASS" in res.stdout
+
+
+def test_two_process_expert_parallel():
+    _need_gpu(2)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29615", os.path.join(ROOT, "tests", "multi_gpu_ep_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "EP_PASS" in res.stdout

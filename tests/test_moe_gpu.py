@@ -87,3 +87,33 @@ def test_block_is_deterministic_and_matches_eager():
     # routing on bf16 logits can pick a different expert on near-ties; almost every row must agree
     err = (a.cpu().float() - ref).abs().amax(-1).flatten()
     assert float((err <= 0.05 * float(ref.abs().max())).float().mean()) > 0.97
+
+
+def test_expert_parallel_world1_equals_local_plan():
+    """With one rank the dispatch/combine kernels must reproduce the local plan exactly."""
+    from ferrl_b200.comm import SoloComm
+    from ferrl_b200.ops import cuda as C
+    from ferrl_b200.parallel.ep import EpRuntime
+    from ferrl_b200.parallel.symm import SymmHeap
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(21)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    T, E, k, H, I = 700, 16, 4, 256, 128
+    gate_up = (rnd(E, 2 * I, H) / H ** 0.5).to(torch.bfloat16)
+    down = (rnd(E, H, I) / I ** 0.5).to(torch.bfloat16)
+    scores, idx, counts, _ = C.moe_route(rnd(T, E), k, True)
+    dy = rnd(T, H).to(torch.bfloat16)
+    rt = EpRuntime(SymmHeap(SoloComm(), dev, wait_limit_s=1.0), E, H, T, k)
+    outs = []
+    for fn in (lambda x, s: C.moe_experts(x, s, idx, counts, gate_up, down, "silu"),
+               lambda x, s: rt.experts(x, s, idx, counts, gate_up, down, "silu")):
+        x = rnd(T, H).to(torch.bfloat16) if not outs else outs[0][3]
+        x = x.detach().clone().requires_grad_(True)
+        s = scores.detach().clone().requires_grad_(True)
+        y = fn(x, s)
+        y.backward(dy)
+        outs.append((y.detach(), x.grad, s.grad, x.detach()))
+    assert C.kernel_status() == 0
+    assert torch.equal(outs[0][0], outs[1][0])
+    assert torch.equal(outs[0][1], outs[1][1])
+    assert torch.equal(outs[0][2], outs[1][2])
