@@ -114,6 +114,8 @@ def build_trainer(args, comm, device):
             if p.shape[1] == 16:
                 p.copy_((torch.randn(p.shape, generator=g) * 0.01).to(p.device))
     policy = LmPolicy(model, GrpoSampler(args.seed, 1.0), score_microbatch=args.microbatch, early_exit_every=64)
+    if args.no_graph:
+        policy.use_cuda_graph = False
 
     class BernoulliVerifier(RewardFn):
         """Synthetic verifier: reward 1 with probability 1/2, a pure function of the completion text."""
@@ -150,6 +152,7 @@ def main():
     ap.add_argument("--microbatch", type=int, default=8, help="rows per scoring/backward micro-batch")
     ap.add_argument("--remat", type=int, default=0, help="1 = recompute layer activations in backward (less memory)")
     ap.add_argument("--seed", type=int, default=1234)
+    ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for per-kernel profiling)")
     ap.add_argument("--nccl-baseline", action="store_true", help="use per-tensor NCCL all-reduce instead of the fused DP step")
     args = ap.parse_args()
     if args.impl == "reference":

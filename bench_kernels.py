@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_decode|decode_attn|sample|flash   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_128|gemm_2cta_256|gemm_decode|decode_attn|sample|flash   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -64,6 +64,9 @@ def profile_case(name, C):
     if name == "gemm":
         a, b = rnd(8192, 4096), rnd(8192, 4096)
         fn = lambda: C.gemm(a, b)
+    elif name in ("gemm_2cta_128", "gemm_2cta_256"):
+        a, b = rnd(8192, 4096), rnd(8192, 4096)
+        fn = lambda: C.gemm(a, b, two_cta=int(name.rsplit("_", 1)[1]))
     elif name == "gemm_decode":
         a, b = rnd(128, 4096), rnd(24576, 4096)
         fn = lambda: C.gemm(a, b)

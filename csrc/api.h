@@ -25,6 +25,8 @@ struct GemmArgs {
   int force_bn;                                                   // 0 = heuristic
   int split_k;                                                    // <= 1: none
   float* partial;                                                 // [split_k, M, N] fp32 scratch when split_k > 1
+  // two-SM kernel (cluster of 2 CTAs, 256 x two_cta tiles): two_cta = 0 (off), 128 or 256
+  int two_cta; unsigned int* debug;
   // grouped mode: B is [n_experts * N, K]; tile_expert[m tile] = expert (or -1: skip the tile)
   const int* tile_expert; int n_experts;
   // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu

@@ -71,7 +71,8 @@ void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(in
 
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
-            const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split) {
+            const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split, int64_t two_cta,
+            const optional<Tensor>& debug) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
@@ -97,6 +98,13 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
   }
   a.status = status_word(); a.num_sms = num_sms(); a.force_bn = static_cast<int>(force_bn);
+  if (two_cta > 0 && !out_f32) {
+    TORCH_CHECK(two_cta == 128 || two_cta == 256, "gemm: two_cta must be 128 or 256");
+    a.two_cta = static_cast<int>(two_cta);
+    if (debug.has_value() && debug->defined()) a.debug = reinterpret_cast<unsigned int*>(debug->data_ptr<int>());
+    FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+    return out;
+  }
   int bn = 0, split = 1;
   ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split);
   if (force_bn == 0) a.force_bn = bn;
@@ -780,7 +788,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split) -> Tensor", &gemm);
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None) -> Tensor", &gemm);
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

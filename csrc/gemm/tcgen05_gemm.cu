@@ -707,6 +707,359 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   return cudaGetLastError() == cudaSuccess ? nullptr : "gemm kernel launch failed";
 }
 
+// =============================================================================================
+// Two-SM variant.  A cluster of two CTAs computes one 256 x BN tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and HALF of the B tile, so a
+// k-block costs 32 KB of shared-memory fill per SM instead of 48 KB for the same tensor work.
+// The one-SM kernel above is bound by that fill rate (about 64 B/clk/SM from L2) at ~70 % tensor
+// activity on large problems; halving B's share lifts the bound above the tensor pipe's rate.
+//
+//   CTA 0 (leader)                          CTA 1
+//   warp 0  TMA producer (own A, B half)    warp 0  TMA producer (own A, B half)
+//   warp 1  MMA issuer for the pair         warp 1  relay: own full[s] -> leader's peer_full[s]
+//   warps 2-5 epilogue of rows 0..127       warps 2-5 epilogue of rows 128..255
+//
+// Stage release and accumulator-ready signals reach both CTAs through tcgen05.commit with a
+// cluster multicast mask; the peer's epilogue warps release the accumulator with remote
+// mbarrier arrives.  TMA loads carry no cluster multicast.  All waits are bounded as above.
+template <int BN> struct Cfg2 {
+  static constexpr int A_BYTES = BM * BK * 2;
+  static constexpr int B_BYTES = (BN / 2) * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = (BN >= 256) ? 6 : 8;
+  static constexpr int TMEM_COLS = (2 * BN <= 256) ? 256 : 512;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 512 /*barriers*/;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait_cluster(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        atomicCAS(status, kStatusOk, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accum)
+      : "memory");
+}
+// arrive on the barrier at this shared-memory offset in every CTA of the mask when the MMAs retire
+__device__ __forceinline__ void umma_commit2(uint64_t* bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(cta_mask)
+               : "memory");
+}
+__host__ __device__ constexpr uint32_t make_idesc2(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) |
+         (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+template <int BN, bool HAS_RES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p,
+             unsigned int* debug) {
+  using C = Cfg2<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;                         // [STAGES] own TMA bytes
+  uint64_t* peer_full = bars + C::STAGES;        // [STAGES] leader only: the peer's stage has landed
+  uint64_t* empty = bars + 2 * C::STAGES;        // [STAGES] both CTAs: MMAs reading the stage retired
+  uint64_t* acc_full = bars + 3 * C::STAGES;     // [2] both CTAs
+  uint64_t* acc_empty = acc_full + 2;            // [2] leader only: 8 epilogue warps of the pair
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int cluster = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+  const int m_tiles = (p.M + 2 * BM - 1) / (2 * BM);
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int total_tiles = m_tiles * n_tiles;
+  const int kb1 = (p.K + BK - 1) / BK;
+  const int kb2 = (p.K2 + BK - 1) / BK;
+  const int kb_total = kb1 + kb2;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&peer_full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 8);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // both CTAs' barriers are initialised before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  if (debug && cluster == 0 && threadIdx.x == 0) debug[rank] = tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster; tile < total_tiles && ok; tile += num_clusters) {
+        int mi, ni;
+        tile_coords_mn(tile, m_tiles, n_tiles, p.group_m, mi, ni);
+        const int a_row = mi * 2 * BM + static_cast<int>(rank) * BM;
+        const int b_row = ni * BN + static_cast<int>(rank) * (BN / 2);
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * C::STAGE_BYTES;
+          uint8_t* sb = sa + C::A_BYTES;
+          mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+          if (kb < kb1) {
+            tma_load_2d(sa, &tmA, &full[stage], kb * BK, a_row);
+            tma_load_2d(sb, &tmB, &full[stage], kb * BK, b_row);
+          } else {
+            tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, a_row);
+            tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, b_row);
+          }
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 1) {
+      // ---------------------------------------------------------- relay (peer CTA)
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = cluster; tile < total_tiles && ok; tile += num_clusters) {
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_cluster(mapa_shared(smem_u32(&peer_full[stage]), 0));
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    } else if (lane == 0) {
+      // ---------------------------------------------------------- MMA issuer (leader CTA)
+      constexpr uint32_t idesc = make_idesc2(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int tile = cluster; tile < total_tiles && ok; tile += num_clusters) {
+        const int acc = (it++) & 1;
+        if (!mbar_wait_cluster(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) break;
+        acc_phase[acc] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < kb_total; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma) ||
+              !mbar_wait_cluster(&peer_full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + C::A_BYTES;
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma2(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit2(&empty[stage], 3);     // frees the stage in both CTAs when these MMAs retire
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit2(&acc_full[acc], 3);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps (both CTAs)
+    const int q = warp & 3;
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    for (int tile = cluster; tile < total_tiles; tile += num_clusters) {
+      int mi, ni;
+      tile_coords_mn(tile, m_tiles, n_tiles, p.group_m, mi, ni);
+      const int acc = (it++) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue)) break;
+      acc_phase[acc] ^= 1;
+      tc_fence_after();
+      const int row = mi * 2 * BM + static_cast<int>(rank) * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c, r);
+        tmem_ld_wait();
+        const int col = ni * BN + c;
+        if (row_ok && col < p.N) {
+          const int ncols = min(32, p.N - col);
+          if (HAS_RES) {
+            const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                uint4 x = reinterpret_cast<const uint4*>(rp)[v];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  float2 f = __bfloat1622float2(h[e]);
+                  r[v * 8 + 2 * e] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e]) + f.x);
+                  r[v * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(r[v * 8 + 2 * e + 1]) + f.y);
+                }
+              }
+            } else {
+              for (int e = 0; e < ncols; ++e)
+                r[e] = __float_as_uint(__uint_as_float(r[e]) + __bfloat162float(rp[e]));
+            }
+          }
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+          if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              float f8[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[v * 8 + e]);
+              reinterpret_cast<uint4*>(op)[v] = pack8(f8);
+            }
+          } else {
+            for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (rank == 0) mbar_arrive(&acc_empty[acc]);
+        else mbar_arrive_cluster(mapa_shared(smem_u32(&acc_empty[acc]), 0));
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();          // the peer may still signal into, or the leader's MMAs read from, this CTA
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+template <int BN, bool HAS_RES>
+const char* launch_2cta(const GemmArgs& a, cudaStream_t stream) {
+  using C = Cfg2<BN>;
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  if (!make_map(&tmA, a.A, a.M, a.K, a.lda, BM)) return "cuTensorMapEncodeTiled failed for A";
+  if (!make_map(&tmB, a.B, a.N, a.K, a.ldb, BN / 2)) return "cuTensorMapEncodeTiled failed for B";
+  if (a.K2 > 0) {
+    if (!make_map(&tmA2, a.A2, a.M, a.K2, a.lda2, BM)) return "cuTensorMapEncodeTiled failed for A2";
+    if (!make_map(&tmB2, a.B2, a.N, a.K2, a.ldb2, BN / 2)) return "cuTensorMapEncodeTiled failed for B2";
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
+  GemmParams p{};
+  p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
+  p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 8;
+  p.split_k = 1; p.ar_world = 1;
+  auto kern = gemm2_kernel<BN, HAS_RES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic smem) failed";
+    attr_set = true;
+  }
+  const int m_tiles = (a.M + 2 * BM - 1) / (2 * BM), n_tiles = (a.N + BN - 1) / BN;
+  const int tiles = m_tiles * n_tiles;
+  int clusters = tiles < a.num_sms / 2 ? tiles : a.num_sms / 2;
+  if (clusters < 1) return nullptr;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  unsigned int* dbg = a.debug;
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2, tmB2, p, dbg) != cudaSuccess) return "2-CTA gemm launch failed";
+  count_launch();
+  return nullptr;
+}
+
 template <int BN>
 const char* launch_flags(const GemmArgs& a, cudaStream_t stream) {
   if (a.out_f32) return a.residual ? launch_bn<BN, true, true>(a, stream) : launch_bn<BN, true, false>(a, stream);
@@ -766,6 +1119,11 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
     return "operand base addresses must be 16-byte aligned";
+  if (a.two_cta) {
+    if (a.out_f32 || a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "2-CTA gemm: bf16 output, no k-split, grouping or all-reduce";
+    if (a.two_cta == 128) return a.residual ? launch_2cta<128, true>(a, stream) : launch_2cta<128, false>(a, stream);
+    return a.residual ? launch_2cta<256, true>(a, stream) : launch_2cta<256, false>(a, stream);
+  }
   int bn = a.force_bn > 0 ? a.force_bn : gemm_pick_bn(a.M, a.N, a.num_sms);
   switch (bn) {
     case 256: return launch_flags<256>(a, stream);

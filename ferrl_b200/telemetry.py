@@ -521,6 +521,7 @@ class PhaseTimer:
 
     def start(self, label: str):
         if self.cuda:
+            self.torch.cuda.nvtx.range_push(label)      # lets a profiler filter launches by phase
             e = self.torch.cuda.Event(enable_timing=True)
             e.record()
             self.open[label] = e
@@ -532,6 +533,7 @@ class PhaseTimer:
         if self.cuda:
             e = self.torch.cuda.Event(enable_timing=True)
             e.record()
+            self.torch.cuda.nvtx.range_pop()
             self.pairs.append((label, s, e))
         else:
             self.ms[label] = self.ms.get(label, 0.0) + (time.perf_counter() - s) * 1e3

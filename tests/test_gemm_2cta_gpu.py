@@ -1,0 +1,45 @@
+"""Two-SM (cta_group::2) GEMM against fp32 matmul."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+WIDTHS = (128,)
+
+
+def _dev():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    return torch.device("cuda", 0)
+
+
+@pytest.mark.parametrize("bn", WIDTHS)
+@pytest.mark.parametrize("M,N,K,res,lora", [(256, 256, 64, False, False), (512, 512, 256, True, False),
+                                             (1000, 384, 520, False, True), (4096, 4096, 1024, True, True),
+                                             (300, 136, 72, True, False)])
+def test_two_cta_matches_fp32(bn, M, N, K, res, lora):
+    from ferrl_b200.ops import cuda as C
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    a = rnd(M, K).to(torch.bfloat16)
+    b = (rnd(N, K) / K ** 0.5).to(torch.bfloat16)
+    a2 = rnd(M, 16).to(torch.bfloat16) if lora else None
+    b2 = (rnd(N, 16) * 0.2).to(torch.bfloat16) if lora else None
+    r = rnd(M, N).to(torch.bfloat16) if res else None
+    dbg = torch.zeros(2, dtype=torch.int32, device=dev)
+    y = C.gemm(a, b, a2, b2, r, two_cta=bn, debug=dbg)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    want = a.float() @ b.float().t()
+    if lora:
+        want = want + a2.float() @ b2.float().t()
+    if res:
+        want = want + r.float()
+    print("tmem bases of the CTA pair:", dbg.tolist())
+    assert dbg[0].item() == dbg[1].item()
+    err = float((y.float() - want).abs().max())
+    assert err <= 0.02 * float(want.abs().max()), err
+    # same bits as the one-SM kernel (same k order, same rounding)
+    y1 = C.gemm(a, b, a2, b2, r, force_bn=128)
+    assert float((y.float() - y1.float()).abs().max()) <= 0.01 * float(want.abs().max())
