@@ -101,6 +101,7 @@ struct DecodeAttnArgs {
   const int* kv_len; const int* block_table; int bt_stride, page;
   void* out; float* workspace;
   int B, Hq, Hkv, D; long long seq_stride, tok_stride; float scale; int window, n_splits;
+  int no_pipe;   // 1: skip the shared-memory pipelined kernel (register-resident kernel instead)
 };
 const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s);
 size_t decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);

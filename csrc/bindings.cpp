@@ -98,7 +98,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
   }
   a.status = status_word(); a.num_sms = num_sms(); a.force_bn = static_cast<int>(force_bn);
-  if (two_cta > 0 && !out_f32) {
+  if (two_cta > 0 && !out_f32) {   // forced
     TORCH_CHECK(two_cta == 128 || two_cta == 256, "gemm: two_cta must be 128 or 256");
     a.two_cta = static_cast<int>(two_cta);
     if (debug.has_value() && debug->defined()) a.debug = reinterpret_cast<unsigned int*>(debug->data_ptr<int>());
@@ -110,6 +110,12 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
   if (force_bn == 0) a.force_bn = bn;
   if (force_split > 0) split = static_cast<int>(force_split);
   else if (force_bn != 0) split = 1;
+  if (split <= 1 && force_bn == 0 && two_cta == 0 && !out_f32 && a.M >= 1024 && a.N >= 512) {
+    // large problems: the two-SM kernel stages a third less per k-block and is not fill-bound
+    a.two_cta = 256;
+    FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+    return out;
+  }
   Tensor partial;
   if (split > 1) {
     partial = at::empty({split, a.M, a.N}, A.options().dtype(at::kFloat));
@@ -572,7 +578,7 @@ void grpo_scale_rows(Tensor dlogp, const Tensor& row_scale) {
 }
 
 Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& kv_len, double scale,
-                   int64_t window, int64_t n_splits, const optional<Tensor>& block_table, int64_t page) {
+                   int64_t window, int64_t n_splits, const optional<Tensor>& block_table, int64_t page, int64_t variant) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.dim() == 3, "decode_attn: q bf16 [B,Hq,D]");
   TORCH_CHECK(kc.scalar_type() == at::kBFloat16 && kc.is_contiguous() && vc.is_contiguous() && kc.dim() == 4, "decode_attn: caches bf16 [B,S,Hkv,D]");
   TORCH_CHECK(kv_len.scalar_type() == at::kInt && kv_len.is_contiguous(), "decode_attn: kv_len int32");
@@ -595,6 +601,7 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
     a.workspace = ws.data_ptr<float>();
   }
   a.out = out.data_ptr();
+  a.no_pipe = variant == 1 ? 1 : 0;
   FERRL_CHECK(ferrl::decode_attn(a, stream()));
   return out;
 }
@@ -788,7 +795,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None) -> Tensor", &gemm);
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
@@ -816,7 +823,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("adamw_step(Tensor[] params, Tensor[] grads, Tensor[] m, Tensor[] v, float lr, float b1, float b2, float eps, float wd, int step, float max_norm, float pre_scale, bool compute_norm) -> Tensor", &adamw_step);
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
-  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page) -> Tensor", &decode_attn);
+  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);

@@ -716,12 +716,14 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
 //
 //   CTA 0 (leader)                          CTA 1
 //   warp 0  TMA producer (own A, B half)    warp 0  TMA producer (own A, B half)
-//   warp 1  MMA issuer for the pair         warp 1  relay: own full[s] -> leader's peer_full[s]
+//   warp 1  MMA issuer for the pair         warp 1  (TMEM allocation only)
 //   warps 2-5 epilogue of rows 0..127       warps 2-5 epilogue of rows 128..255
 //
-// Stage release and accumulator-ready signals reach both CTAs through tcgen05.commit with a
-// cluster multicast mask; the peer's epilogue warps release the accumulator with remote
-// mbarrier arrives.  TMA loads carry no cluster multicast.  All waits are bounded as above.
+// Both producers' TMA loads (cta_group::2 form, no cluster multicast) complete their bytes on the
+// LEADER's full barrier, which therefore expects two stages' worth per phase.  Stage release and
+// accumulator-ready signals reach both CTAs through tcgen05.commit with a cluster multicast mask;
+// the peer's epilogue warps release the accumulator with remote mbarrier arrives.  All waits are
+// bounded as above.
 template <int BN> struct Cfg2 {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = (BN / 2) * BK * 2;
@@ -772,6 +774,14 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity
   }
   return true;
 }
+// TMA load whose completion is counted on a barrier that may live in the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t bar_cluster_addr,
+                                                 int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
 __device__ __forceinline__ void cluster_sync_all() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -804,8 +814,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
-  uint64_t* full = bars;                         // [STAGES] own TMA bytes
-  uint64_t* peer_full = bars + C::STAGES;        // [STAGES] leader only: the peer's stage has landed
+  uint64_t* full = bars;                         // [STAGES] leader only: both CTAs' TMA bytes of the stage
+  uint64_t* peer_full = bars + C::STAGES;        // [STAGES] unused (kept so the offsets match in both CTAs)
   uint64_t* empty = bars + 2 * C::STAGES;        // [STAGES] both CTAs: MMAs reading the stage retired
   uint64_t* acc_full = bars + 3 * C::STAGES;     // [2] both CTAs
   uint64_t* acc_empty = acc_full + 2;            // [2] leader only: 8 epilogue warps of the pair
@@ -867,13 +877,14 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           }
           uint8_t* sa = smem + stage * C::STAGE_BYTES;
           uint8_t* sb = sa + C::A_BYTES;
-          mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+          if (rank == 0) mbar_expect_tx(&full[stage], 2 * C::STAGE_BYTES);
+          const uint32_t bar = mapa_shared(smem_u32(&full[stage]), 0);
           if (kb < kb1) {
-            tma_load_2d(sa, &tmA, &full[stage], kb * BK, a_row);
-            tma_load_2d(sb, &tmB, &full[stage], kb * BK, b_row);
+            tma_load_2d_pair(sa, &tmA, bar, kb * BK, a_row);
+            tma_load_2d_pair(sb, &tmB, bar, kb * BK, b_row);
           } else {
-            tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, a_row);
-            tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, b_row);
+            tma_load_2d_pair(sa, &tmA2, bar, (kb - kb1) * BK, a_row);
+            tma_load_2d_pair(sb, &tmB2, bar, (kb - kb1) * BK, b_row);
           }
           if (++stage == C::STAGES) {
             stage = 0;
@@ -886,25 +897,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 1) {
-      // ---------------------------------------------------------- relay (peer CTA)
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = cluster; tile < total_tiles && ok; tile += num_clusters) {
-        for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
-            ok = false;
-            break;
-          }
-          mbar_arrive_cluster(mapa_shared(smem_u32(&peer_full[stage]), 0));
-          if (++stage == C::STAGES) {
-            stage = 0;
-            phase ^= 1;
-          }
-        }
-      }
-    } else if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       // ---------------------------------------------------------- MMA issuer (leader CTA)
       constexpr uint32_t idesc = make_idesc2(BN);
       int stage = 0;
@@ -919,8 +912,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < kb_total; ++kb) {
-          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma) ||
-              !mbar_wait_cluster(&peer_full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+          if (!mbar_wait_cluster(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
             ok = false;
             break;
           }

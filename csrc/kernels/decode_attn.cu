@@ -358,6 +358,231 @@ decode_attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
+// Shared-memory pipelined variant.  K/V rows stream through a ring of cp.async stages so the bytes
+// in flight per SM no longer depend on the register file: a CTA of 4 warps keeps 3 stages of
+// 32 keys (K and V) outstanding and three CTAs fit on an SM.  The math is the register-resident
+// scheme above, reading its 32-byte key slices from shared memory (a quarter-warp reads whole
+// 128-byte lines, so there are no bank conflicts).
+constexpr int PWARPS = 4;
+constexpr int PTK = 32;       // keys per stage
+constexpr int PSTAGES = 4;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc, bool valid) {
+  const uint32_t d = static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst));
+  const int n = valid ? 16 : 0;   // zero-fill when the key is past the end
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gsrc), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <int D, int REP>
+__global__ void __launch_bounds__(PWARPS * 32)
+decode_attn_pipe_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                        const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
+                        const int* __restrict__ block_table, int bt_stride, int page,
+                        __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
+                        long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  constexpr int LPK = D / 16;                 // lanes per key
+  constexpr int KPW = 32 / LPK;               // keys per warp per step
+  constexpr int STEPS = PTK / (PWARPS * KPW); // steps per stage
+  static_assert(STEPS >= 1, "tile too small for this head dim");
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int CHUNKS = PTK * ROW_BYTES / 16;          // 16-byte chunks per K (or V) tile
+  constexpr int STAGE_BYTES = 2 * PTK * ROW_BYTES;
+  extern __shared__ __align__(128) uint8_t psm[];
+  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane % LPK, grp = lane / LPK;
+  const int d0 = sub * 16;
+
+  float qr[REP][16];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * REP + r) * D + d0;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) qr[r][e] = __bfloat162float(qp[e]) * scale;
+  }
+  const int len = kv_len[b];
+  const int lo = (window > 0 && len > window) ? len - window : 0;
+  const int span = len - lo;
+  const int per = (span + n_splits - 1) / n_splits;
+  const int s0 = lo + split * per;
+  const int s1 = min(len, s0 + per);
+  const int n_tiles = s1 > s0 ? (s1 - s0 + PTK - 1) / PTK : 0;
+
+  auto row_of = [&](int j) -> long long {
+    if (block_table) {
+      int pg = block_table[static_cast<long long>(b) * bt_stride + j / page];
+      return (static_cast<long long>(pg) * page + (j % page)) * tok_stride + hk * D;
+    }
+    return static_cast<long long>(b) * seq_stride + static_cast<long long>(j) * tok_stride + hk * D;
+  };
+  auto issue = [&](int t) {
+    if (t < n_tiles) {
+      uint8_t* st = psm + (t % PSTAGES) * STAGE_BYTES;
+      const int j0 = s0 + t * PTK;
+      for (int c = threadIdx.x; c < CHUNKS; c += PWARPS * 32) {
+        const int key = c / (ROW_BYTES / 16), part = c % (ROW_BYTES / 16);
+        const int j = j0 + key;
+        const bool ok = j < s1;
+        const long long row = row_of(ok ? j : s0) + part * 8;
+        cp_async16(st + c * 16, kc + row, ok);
+        cp_async16(st + PTK * ROW_BYTES + c * 16, vc + row, ok);
+      }
+    }
+    cp_async_commit();     // one group per tile slot, empty past the end, so the wait count stays fixed
+  };
+
+  float m_run[REP], l_run[REP], o[REP][16];
+#pragma unroll
+  for (int r = 0; r < REP; ++r) {
+    m_run[r] = -INFINITY;
+    l_run[r] = 0.f;
+#pragma unroll
+    for (int e = 0; e < 16; ++e) o[r][e] = 0.f;
+  }
+
+#pragma unroll
+  for (int t = 0; t < PSTAGES - 1; ++t) issue(t);
+  for (int t = 0; t < n_tiles; ++t) {
+    cp_async_wait<PSTAGES - 2>();
+    __syncthreads();                 // tile t has landed for everyone; tile t-1's stage is free again
+    issue(t + PSTAGES - 1);
+    const uint8_t* st = psm + (t % PSTAGES) * STAGE_BYTES;
+    const int j0 = s0 + t * PTK;
+    float sc[STEPS][REP];
+#pragma unroll
+    for (int u = 0; u < STEPS; ++u) {
+      const int kt = u * (PWARPS * KPW) + warp * KPW + grp;
+      const bool live = j0 + kt < s1;
+      const uint4* kp = reinterpret_cast<const uint4*>(st + kt * ROW_BYTES + d0 * 2);
+      const uint4 k0 = kp[0], k1 = kp[1];
+      float kf[16];
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&k0);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&k1);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(h0[e]);
+        kf[2 * e] = f.x;
+        kf[2 * e + 1] = f.y;
+        f = __bfloat1622float2(h1[e]);
+        kf[8 + 2 * e] = f.x;
+        kf[8 + 2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r) {
+        float a = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) a += kf[e] * qr[r][e];
+#pragma unroll
+        for (int off = LPK / 2; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+        sc[u][r] = live ? a : -INFINITY;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      float mx = m_run[r];
+#pragma unroll
+      for (int u = 0; u < STEPS; ++u) mx = fmaxf(mx, sc[u][r]);
+      const float corr = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mx);
+      m_run[r] = mx;
+      l_run[r] *= corr;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o[r][e] *= corr;
+#pragma unroll
+      for (int u = 0; u < STEPS; ++u) {
+        const float pj = (sc[u][r] == -INFINITY) ? 0.f : __expf(sc[u][r] - mx);
+        sc[u][r] = pj;
+        l_run[r] += pj;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < STEPS; ++u) {
+      const int kt = u * (PWARPS * KPW) + warp * KPW + grp;
+      const uint4* vp = reinterpret_cast<const uint4*>(st + PTK * ROW_BYTES + kt * ROW_BYTES + d0 * 2);
+      const uint4 v0 = vp[0], v1 = vp[1];
+      float vf[16];
+      const __nv_bfloat162* h0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
+      const __nv_bfloat162* h1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float2 f = __bfloat1622float2(h0[e]);
+        vf[2 * e] = f.x;
+        vf[2 * e + 1] = f.y;
+        f = __bfloat1622float2(h1[e]);
+        vf[8 + 2 * e] = f.x;
+        vf[8 + 2 * e + 1] = f.y;
+      }
+#pragma unroll
+      for (int r = 0; r < REP; ++r)
+#pragma unroll
+        for (int e = 0; e < 16; ++e) o[r][e] += sc[u][r] * vf[e];
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();                   // the ring is reused below for the cross-warp merge
+
+  // merge the lane groups of this warp (same channels, different keys)
+#pragma unroll
+  for (int off = LPK; off < 32; off <<= 1) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m_run[r], off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l_run[r], off);
+      const float mn = fmaxf(m_run[r], m2);
+      const float c1 = (m_run[r] == -INFINITY) ? 0.f : __expf(m_run[r] - mn);
+      const float c2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+      l_run[r] = l_run[r] * c1 + l2 * c2;
+      m_run[r] = mn;
+#pragma unroll
+      for (int e = 0; e < 16; ++e) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, o[r][e], off);
+        o[r][e] = o[r][e] * c1 + o2 * c2;
+      }
+    }
+  }
+  float* m_s = reinterpret_cast<float*>(psm);   // [PWARPS][REP]
+  float* l_s = m_s + PWARPS * REP;              // [PWARPS][REP]
+  float* o_s = l_s + PWARPS * REP;              // [PWARPS][REP][D]
+  if (grp == 0) {
+#pragma unroll
+    for (int r = 0; r < REP; ++r) {
+      if (sub == 0) {
+        m_s[warp * REP + r] = m_run[r];
+        l_s[warp * REP + r] = l_run[r];
+      }
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o_s[(warp * REP + r) * D + d0 + e] = o[r][e];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D;
+    float m = -INFINITY;
+    for (int w = 0; w < PWARPS; ++w) m = fmaxf(m, m_s[w * REP + r]);
+    float l = 0.f, acc = 0.f;
+    for (int w = 0; w < PWARPS; ++w) {
+      const float mw = m_s[w * REP + r];
+      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+      l += l_s[w * REP + r] * c;
+      acc += o_s[(w * REP + r) * D + d] * c;
+    }
+    const long long head = static_cast<long long>(b) * Hq + hk * REP + r;
+    if (n_splits == 1) {
+      out[head * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      float* w_ = ws + (head * n_splits + split) * (D + 2);
+      w_[d] = acc;
+      if (d == 0) {
+        w_[D] = m;
+        w_[D + 1] = l;
+      }
+    }
+  }
+}
+
 __global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
                                       int n_splits) {
   const long long head = blockIdx.x;
@@ -408,6 +633,29 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
         grid.z);                                                                                                      \
     launched = true;                                                                                                  \
   }
+#define FERRL_DECODE_PIPE(DD, RR)                                                                                   \
+  if (!launched && a.D == DD && rep == RR && !a.no_pipe) {                                                            \
+    constexpr size_t psm_bytes = static_cast<size_t>(PSTAGES) * 2 * PTK * DD * 2;                                     \
+    auto pk = decode_attn_pipe_kernel<DD, RR>;                                                                        \
+    static bool pset = false;                                                                                         \
+    if (!pset) {                                                                                                      \
+      cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(psm_bytes));             \
+      pset = true;                                                                                                    \
+    }                                                                                                                 \
+    pk<<<grid, PWARPS * 32, psm_bytes, s>>>(                                                                          \
+        static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
+        static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
+        static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.seq_stride, a.tok_stride, a.scale, a.window,  \
+        grid.z);                                                                                                      \
+    launched = true;                                                                                                  \
+  }
+  if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.v) & 15) == 0) {
+    FERRL_DECODE_PIPE(128, 4) FERRL_DECODE_PIPE(128, 1) FERRL_DECODE_PIPE(128, 2) FERRL_DECODE_PIPE(128, 8)
+    FERRL_DECODE_PIPE(64, 1) FERRL_DECODE_PIPE(64, 2) FERRL_DECODE_PIPE(64, 4) FERRL_DECODE_PIPE(64, 8)
+    FERRL_DECODE_PIPE(256, 1) FERRL_DECODE_PIPE(256, 2) FERRL_DECODE_PIPE(256, 4)
+  }
+#undef FERRL_DECODE_PIPE
   if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0) {
     FERRL_DECODE_FAST(128, 4) FERRL_DECODE_FAST(128, 1) FERRL_DECODE_FAST(128, 2) FERRL_DECODE_FAST(128, 8)
     FERRL_DECODE_FAST(64, 1) FERRL_DECODE_FAST(64, 2) FERRL_DECODE_FAST(64, 4) FERRL_DECODE_FAST(64, 8)

@@ -139,7 +139,7 @@ class DenseLayer(nn.Module):
         return self.down.forward_reduce(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged, residual=h)
 
     # one-token forward against the cache (rollout; merged weights)
-    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm):
+    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None):
         B = h.shape[0]
         x = ops.rmsnorm(h, self.input_norm, self.eps)
         qkv = self.qkv.forward_merged(x)
@@ -147,9 +147,11 @@ class DenseLayer(nn.Module):
         q = q.reshape(B, 1, self.hq, self.D)
         k = k.reshape(B, 1, self.hkv, self.D)
         v = v.reshape(B, 1, self.hkv, self.D)
-        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin, kv_len[:, None].long())
+        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin,
+                                pos if pos is not None else kv_len[:, None].long())
         ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
-        a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_len + 1, scale=self.scale)
+        a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
+                                 scale=self.scale)
         o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
         return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
@@ -376,8 +378,10 @@ class DenseCachedDecoder:
         """Feed one token per row; returns next-token logits ``[B, V]`` float32."""
         m = self.m
         h = ops.embedding(tokens, m.embed)
+        kv_next = self.kv_len + 1                 # shared by every layer: computed once per token
+        pos = self.kv_len[:, None].long()
         for i, layer in enumerate(m.layers):
-            h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm)
+            h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos)
         self.kv_len += 1
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
         return ops.lora_linear(h, m.head_weight(), None, None).float()

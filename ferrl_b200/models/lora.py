@@ -255,9 +255,9 @@ class FusedLoraLinear(nn.Module):
         return A, B
 
     # --------------------------------------------------------------- forward
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         a, b = self._stacks()
-        return ops.lora_linear(x, self.weight, a, b, wt=self.weight_t)
+        return ops.lora_linear(x, self.weight, a, b, wt=self.weight_t, residual=residual)
 
     def forward_reduce(self, x: torch.Tensor, comm, merged: bool = False, residual=None) -> torch.Tensor:
         """Row-parallel use: the projection, its tensor-parallel sum over ``comm`` and an
@@ -277,13 +277,16 @@ class FusedLoraLinear(nn.Module):
                     y = _c.lora_linear_reduce(x, self.weight, a, b, self.weight_t, red, residual)
                 if y is not None:
                     return y
+        if comm.world_size == 1:
+            # no reduction to wait for: the residual rides in the GEMM epilogue
+            return self.forward_merged(x, residual) if merged else self.forward(x, residual)
         y = reduce_from_tp(self.forward_merged(x) if merged else self.forward(x), comm)
         return y if residual is None else residual + y
 
-    def forward_merged(self, x: torch.Tensor) -> torch.Tensor:
+    def forward_merged(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         """Rollout path over the merged snapshot (no adapter side path)."""
         w = self.weight_merged if self.weight_merged is not None else self.weight
-        return ops.lora_linear(x, w, None, None)
+        return ops.lora_linear(x, w, None, None, residual=residual)
 
     @torch.no_grad()
     def merge(self):

@@ -70,12 +70,13 @@ def swiglu(gate_up, act="silu"):
     return eager.swiglu(gate_up, act)
 
 
-def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None):
-    """``y = x Wᵀ + (x Aᵀ) Bᵀ``.  ``wt`` is the optional resident transpose of a
+def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None, residual=None):
+    """``y = x Wᵀ + (x Aᵀ) Bᵀ (+ residual)``.  ``wt`` is the optional resident transpose of a
     frozen ``w`` used by the backward GEMM so both passes read K-major tiles."""
     if _on_gpu(x):
-        return _cuda().lora_linear(x, w, a_stack, b_stack, wt, bias)
-    return eager.lora_linear(x, w, a_stack, b_stack, bias)
+        return _cuda().lora_linear(x, w, a_stack, b_stack, wt, bias, residual)
+    y = eager.lora_linear(x, w, a_stack, b_stack, bias)
+    return y if residual is None else residual + y
 
 
 def lora_merge(w, a_stack, b_stack):

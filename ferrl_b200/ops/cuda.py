@@ -65,7 +65,7 @@ def _pad8(t, dim):
 
 class _LoraLinear(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, wt, a_stack, b_stack):
+    def forward(ctx, x, w, wt, a_stack, b_stack, residual=None):
         K = x.shape[-1]
         x2 = x.reshape(-1, K)
         if not x2.is_contiguous():
@@ -75,10 +75,16 @@ class _LoraLinear(torch.autograd.Function):
             a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()   # [R, K]
             b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()   # [N, R]
             t = gemm(x2, a16)                                                  # [M, R]
-        y = gemm(x2, w, t, b16)
+        res2 = None
+        if residual is not None:
+            res2 = residual.reshape(-1, w.shape[0])
+            if res2.stride(-1) != 1:
+                res2 = res2.contiguous()
+        y = gemm(x2, w, t, b16, res2)
         ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
         ctx.x_shape = x.shape
         ctx.x_grad = x.requires_grad
+        ctx.res_grad = residual is not None and residual.requires_grad
         return y.view(*x.shape[:-1], w.shape[0])
 
     @staticmethod
@@ -104,7 +110,7 @@ class _LoraLinear(torch.autograd.Function):
             # adapter gradients: tall-skinny reductions over the token dimension
             da = torch.matmul(u.t(), x2)[:R].float() if a_stack.requires_grad else None
             db = torch.matmul(dy2.t(), t)[:, :R].float() if b_stack.requires_grad else None
-        return dx, None, None, da, db
+        return dx, None, None, da, db, (dy if getattr(ctx, "res_grad", False) else None)
 
 
 class _LoraLinearReduce(torch.autograd.Function):
@@ -136,8 +142,8 @@ class _LoraLinearReduce(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        dx, _, _, da, db = _LoraLinear.backward(ctx, dy)
-        return dx, None, None, da, db, (dy if ctx.res_grad else None), None
+        dx, _, _, da, db, dres = _LoraLinear.backward(ctx, dy)
+        return dx, None, None, da, db, dres, None
 
 
 def lora_linear_reduce(x, w, a_stack, b_stack, wt, reducer, residual=None):
@@ -151,12 +157,14 @@ def lora_linear_reduce(x, w, a_stack, b_stack, wt, reducer, residual=None):
     return _LoraLinearReduce.apply(x, w, wt, a_stack, b_stack, residual, reducer)
 
 
-def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None):
-    if not (_bf16(x) and _bf16(w)) or bias is not None or w.requires_grad:
-        return eager.lora_linear(x, w, a_stack, b_stack, bias)
-    if x.shape[-1] % 8:
-        return eager.lora_linear(x, w, a_stack, b_stack, bias)
-    return _LoraLinear.apply(x, w, wt, a_stack, b_stack)
+def lora_linear(x, w, a_stack, b_stack, wt=None, bias=None, residual=None):
+    """``x Wᵀ + (x Aᵀ) Bᵀ (+ residual)``; the residual add happens in the GEMM epilogue."""
+    if not (_bf16(x) and _bf16(w)) or bias is not None or w.requires_grad or x.shape[-1] % 8:
+        y = eager.lora_linear(x, w, a_stack, b_stack, bias)
+        return y if residual is None else residual + y
+    if residual is not None and residual.dtype != torch.bfloat16:
+        return residual + _LoraLinear.apply(x, w, wt, a_stack, b_stack)
+    return _LoraLinear.apply(x, w, wt, a_stack, b_stack, residual)
 
 
 def lora_merge(w, a_stack, b_stack):
@@ -289,11 +297,13 @@ def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None)
     return _Flash.apply(_packed(q), _packed(k), _packed(v), float(scale), bool(causal), int(window or 0), int(q_offset))
 
 
-def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0):
+def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0):
+    """``variant`` 0 picks the shared-memory pipelined kernel where it applies, 1 forces the
+    register-resident one (kept for head shapes the pipeline does not cover, and as a cross-check)."""
     if not _bf16(q) or q.shape[-1] % 8 or q.shape[-1] > 256:
         return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
     return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),
-                             int(n_splits), None, 0)
+                             int(n_splits), None, 0, int(variant))
 
 
 def kv_append(k_cache, v_cache, k, v, kv_len):

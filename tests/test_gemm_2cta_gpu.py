@@ -4,7 +4,7 @@ import torch
 
 pytestmark = pytest.mark.gpu
 
-WIDTHS = (128,)
+WIDTHS = (128, 256)
 
 
 def _dev():
@@ -41,5 +41,5 @@ def test_two_cta_matches_fp32(bn, M, N, K, res, lora):
     err = float((y.float() - want).abs().max())
     assert err <= 0.02 * float(want.abs().max()), err
     # same bits as the one-SM kernel (same k order, same rounding)
-    y1 = C.gemm(a, b, a2, b2, r, force_bn=128)
+    y1 = C.gemm(a, b, a2, b2, r, force_bn=128 if N >= 128 else 64)
     assert float((y.float() - y1.float()).abs().max()) <= 0.01 * float(want.abs().max())

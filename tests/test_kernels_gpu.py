@@ -156,8 +156,9 @@ def test_flash_attention_fwd_bwd(D, causal, window):
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 32, 8), (64, 4, 4), (256, 16, 2), (16, 4, 2)])
+@pytest.mark.parametrize("variant", [0, 1])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 4), (50, 2)])
-def test_decode_attention(D, Hq, Hkv, window, splits):
+def test_decode_attention(D, Hq, Hkv, window, splits, variant):
     from ferrl_b200.ops import cuda as C, eager as E
     dev = _dev()
     B, Smax = 5, 333
@@ -165,7 +166,7 @@ def test_decode_attention(D, Hq, Hkv, window, splits):
     kc = torch.randn(B, Smax, Hkv, D, device=dev).to(torch.bfloat16)
     vc = torch.randn(B, Smax, Hkv, D, device=dev).to(torch.bfloat16)
     lens = torch.tensor([1, 64, 65, 333, 200], device=dev, dtype=torch.int32)
-    out = C.decode_attention(q, kc, vc, lens, scale=1 / math.sqrt(D), window=window, n_splits=splits)
+    out = C.decode_attention(q, kc, vc, lens, scale=1 / math.sqrt(D), window=window, n_splits=splits, variant=variant)
     ref = E.decode_attention(q.float(), kc.float(), vc.float(), lens, scale=1 / math.sqrt(D), window=window)
     assert _rel(out, ref) < 2e-2
 
