@@ -139,6 +139,13 @@ def main():
             for bn in ([0] if M > 128 else [0, 64, 128]):
                 s = T(lambda: C.gemm(a, b, force_bn=bn))
                 report(f"gemm {name} M{M} N{N} K{K} bn{bn or 'auto'}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+            if M <= 128:
+                for bn, cl in ((128, 2), (128, 4), (128, 8), (256, 2), (64, 4)):
+                    s = T(lambda: C.gemm(a, b, force_bn=bn, cluster_k=cl))
+                    report(f"gemm {name} cluster split-k bn{bn} x{cl}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+            else:
+                s = T(lambda: C.gemm(a, b, two_cta=-1))
+                report(f"gemm {name} one-SM kernel", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
             s = T(lambda: torch.matmul(a, b.t()))
             report(f"  cuBLAS same shape (library reference)", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
             del a, b

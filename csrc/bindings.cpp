@@ -72,7 +72,7 @@ void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(in
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
             const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split, int64_t two_cta,
-            const optional<Tensor>& debug) {
+            const optional<Tensor>& debug, int64_t cluster_k) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
@@ -105,11 +105,23 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
     return out;
   }
-  int bn = 0, split = 1;
-  ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split);
+  int bn = 0, split = 1, cluster = 1;
+  ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split, &cluster);
+  if (cluster_k > 1) {                      // forced cluster split: force_bn names the tile width
+    TORCH_CHECK(force_bn > 0, "gemm: cluster_k needs force_bn");
+    a.cluster_k = static_cast<int>(cluster_k);
+    FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+    return out;
+  }
+  if (force_bn == 0 && force_split == 0 && cluster_k == 0 && cluster > 1) {
+    a.force_bn = bn;
+    a.cluster_k = cluster;
+    FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+    return out;
+  }
   if (force_bn == 0) a.force_bn = bn;
   if (force_split > 0) split = static_cast<int>(force_split);
-  else if (force_bn != 0) split = 1;
+  else if (force_bn != 0 || cluster > 1) split = 1;
   if (split <= 1 && force_bn == 0 && two_cta == 0 && !out_f32 && a.M >= 1024 && a.N >= 512) {
     // large problems: the two-SM kernel stages a third less per k-block and is not fill-bound
     a.two_cta = 256;
@@ -795,7 +807,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

@@ -1052,6 +1052,295 @@ const char* launch_2cta(const GemmArgs& a, cudaStream_t stream) {
   return nullptr;
 }
 
+// =============================================================================================
+// Cluster split-K variant for decode-shaped problems (one or two M tiles, long K).
+// A cluster of S CTAs shares one 128 x BN output tile: CTA r accumulates k-blocks
+// [r*kb/S, (r+1)*kb/S) in TMEM, then the partial sums are exchanged through distributed shared
+// memory as a reduce-scatter - CTA r receives every peer's partial of column slice r, adds the S
+// partials in rank order (its own in its place, so the order does not depend on who adds) and
+// writes that slice of the output.  One launch, no fp32 round trip through global memory, and the
+// result is bit-identical from run to run.  Non-persistent: one k-slice of one tile per CTA.
+template <int BN, int S> struct CfgK {
+  static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
+  static constexpr int SLICE = BN / S;                               // output columns owned by one CTA
+  static constexpr int SLOT_BYTES = BM * SLICE * 4;                  // one peer's fp32 partial of my slice
+  static constexpr int RED_BYTES = (S - 1) * SLOT_BYTES;
+  static constexpr int STAGES_FIT = (220 * 1024 - RED_BYTES - 1024 - 256) / STAGE_BYTES;
+  static constexpr int STAGES = STAGES_FIT > 8 ? 8 : STAGES_FIT;
+  static constexpr int TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RED_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ void st_cluster_f4(uint32_t cluster_addr, float4 v) {
+  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(cluster_addr), "f"(v.x), "f"(v.y), "f"(v.z),
+               "f"(v.w)
+               : "memory");
+}
+
+template <int BN, int S, bool OUT_F32, bool HAS_RES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                   const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p) {
+  using C = CfgK<BN, S>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* red = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);   // [S-1][BM][SLICE]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + C::RED_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* acc_full = bars + 2 * C::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int rank = static_cast<int>(cluster_ctarank());
+  const int tile = blockIdx.x / S;
+  const int n_tiles = (p.N + BN - 1) / BN;
+  const int mi = tile / n_tiles, ni = tile % n_tiles;
+  const int kb1 = (p.K + BK - 1) / BK;
+  const int kb2 = (p.K2 + BK - 1) / BK;
+  const int kb_total = kb1 + kb2;
+  const int kb_per = (kb_total + S - 1) / S;
+  const int kb_begin = min(kb_total, rank * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+        uint8_t* sb = sa + BM * BK * 2;
+        mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+        if (kb < kb1) {
+          tma_load_2d(sa, &tmA, &full[stage], kb * BK, mi * BM);
+          tma_load_2d(sb, &tmB, &full[stage], kb * BK, ni * BN);
+        } else {
+          tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, mi * BM);
+          tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, ni * BN);
+        }
+        if (++stage == C::STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int kb = kb_begin; kb < kb_end; ++kb) {
+        if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+        const uint32_t sb = sa + BM * BK * 2;
+        const uint64_t da = make_smem_desc(sa);
+        const uint64_t db = make_smem_desc(sb);
+#pragma unroll
+        for (int k = 0; k < BK / UMMA_K; ++k) umma(tmem_base, da + 2 * k, db + 2 * k, idesc, (kb > kb_begin || k > 0) ? 1u : 0u);
+        umma_commit(&empty[stage]);
+        if (++stage == C::STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (ok) umma_commit(acc_full);
+    }
+  }
+
+  // ---- exchange: every thread of the cluster passes the same two cluster barriers
+  const bool epi = warp >= 2;
+  const int q = warp & 3;
+  const int row_in = q * 32 + lane;                 // accumulator row held by this thread
+  const bool have = kb_end > kb_begin;              // a slice can be empty when kb_total < S
+  bool acc_ok = true;
+  if (epi) {
+    if (have) acc_ok = mbar_wait(acc_full, 0, abort_flag, p.status, kStatusWaitTimeoutEpilogue);
+    tc_fence_after();
+    // push my partial of every other CTA's column slice into that CTA's receive slot [my rank]
+    for (int dst = 0; dst < S; ++dst) {
+      if (dst == rank) continue;
+      const int slot = rank < dst ? rank : rank - 1;     // the receiver's slots skip its own rank
+      const uint32_t base = mapa_shared(smem_u32(red + (static_cast<size_t>(slot) * BM + row_in) * C::SLICE), dst);
+#pragma unroll 1
+      for (int c = 0; c < C::SLICE; c += 16) {
+        uint32_t r[16];
+        if (have && acc_ok) {
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + dst * C::SLICE + c)
+              : "memory");
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) r[e] = 0u;
+        }
+#pragma unroll
+        for (int v = 0; v < 4; ++v)
+          st_cluster_f4(base + (c + 4 * v) * 4, make_float4(__uint_as_float(r[4 * v]), __uint_as_float(r[4 * v + 1]),
+                                                            __uint_as_float(r[4 * v + 2]), __uint_as_float(r[4 * v + 3])));
+      }
+    }
+  }
+  cluster_sync_all();                                 // all partials have landed in their owners' slots
+  if (epi && acc_ok && !*abort_flag) {
+    const int row = mi * BM + row_in;
+    const int col0 = ni * BN + rank * C::SLICE;
+#pragma unroll 1
+    for (int c = 0; c < C::SLICE; c += 16) {
+      uint32_t r[16];
+      if (have) {
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+              "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+            : "r"(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + rank * C::SLICE + c)
+            : "memory");
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) r[e] = 0u;
+      }
+      float acc[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+      for (int src = 0; src < S; ++src) {            // rank order, my own partial in its place
+        if (src == rank) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc[e] += __uint_as_float(r[e]);
+        } else {
+          const int slot = src < rank ? src : src - 1;
+          const float4* sp = reinterpret_cast<const float4*>(red + (static_cast<size_t>(slot) * BM + row_in) * C::SLICE + c);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const float4 x = sp[v];
+            acc[4 * v] += x.x; acc[4 * v + 1] += x.y; acc[4 * v + 2] += x.z; acc[4 * v + 3] += x.w;
+          }
+        }
+      }
+      const int col = col0 + c;
+      if (row < p.M && col < p.N) {
+        const int ncols = min(16, p.N - col);
+        if (HAS_RES) {
+          const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
+          for (int e = 0; e < ncols; ++e) acc[e] += __bfloat162float(rp[e]);
+        }
+        if (OUT_F32) {
+          float* op = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+          if (ncols == 16 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v)
+              reinterpret_cast<float4*>(op)[v] = make_float4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+          } else {
+            for (int e = 0; e < ncols; ++e) op[e] = acc[e];
+          }
+        } else {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+          if (ncols == 16 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+            reinterpret_cast<uint4*>(op)[0] = pack8(acc);
+            reinterpret_cast<uint4*>(op)[1] = pack8(acc + 8);
+          } else {
+            for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(acc[e]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // nobody leaves while a peer may still read its slots' senders
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+template <int BN, int S, bool OUT_F32, bool HAS_RES>
+const char* launch_ksplit(const GemmArgs& a, cudaStream_t stream) {
+  using C = CfgK<BN, S>;
+  static_assert(C::STAGES >= 3, "not enough shared memory left for the pipeline");
+  static_assert(C::SLICE % 16 == 0, "column slice must be a multiple of 16");
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  if (!make_map(&tmA, a.A, a.M, a.K, a.lda, BM)) return "cuTensorMapEncodeTiled failed for A";
+  if (!make_map(&tmB, a.B, a.N, a.K, a.ldb, BN)) return "cuTensorMapEncodeTiled failed for B";
+  if (a.K2 > 0) {
+    if (!make_map(&tmA2, a.A2, a.M, a.K2, a.lda2, BM)) return "cuTensorMapEncodeTiled failed for A2";
+    if (!make_map(&tmB2, a.B2, a.N, a.K2, a.ldb2, BN)) return "cuTensorMapEncodeTiled failed for B2";
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
+  GemmParams p{};
+  p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
+  p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 1;
+  p.split_k = 1; p.ar_world = 1;
+  auto kern = gemm_ksplit_kernel<BN, S, OUT_F32, HAS_RES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic smem) failed";
+    attr_set = true;
+  }
+  const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(tiles * S);
+  cfg.blockDim = dim3(NUM_THREADS);
+  cfg.dynamicSmemBytes = C::SMEM_BYTES;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2, tmB2, p) != cudaSuccess) return "cluster split-k gemm launch failed";
+  count_launch();
+  return nullptr;
+}
+
+template <int BN, int S>
+const char* launch_ksplit_flags(const GemmArgs& a, cudaStream_t stream) {
+  if (a.out_f32) return a.residual ? launch_ksplit<BN, S, true, true>(a, stream) : launch_ksplit<BN, S, true, false>(a, stream);
+  return a.residual ? launch_ksplit<BN, S, false, true>(a, stream) : launch_ksplit<BN, S, false, false>(a, stream);
+}
+
 template <int BN>
 const char* launch_flags(const GemmArgs& a, cudaStream_t stream) {
   if (a.out_f32) return a.residual ? launch_bn<BN, true, true>(a, stream) : launch_bn<BN, true, false>(a, stream);
@@ -1075,12 +1364,15 @@ int gemm_pick_bn(int M, int N, int num_sms) {
 }
 
 // Decode-shaped problems (one or two M tiles) are bound by how many bytes each SM has to pull
-// through its TMA path, not by HBM: pick the tile width and k-split that minimise the bytes of the
-// busiest SM (A slice + B slice per tile, times the number of waves) plus the cost of the reduce.
-void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out) {
+// through its TMA path (about 64 GB/s per SM when the weights stream from HBM), not by HBM itself:
+// pick the tile width and the k-split that minimise the bytes of the busiest SM (A slice + B slice
+// per tile, times the number of waves).  Splits inside a cluster reduce through shared memory;
+// the global-memory split (fp32 partials + reduce kernel) is the fallback.
+void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out) {
   const int m_tiles = (M + BM - 1) / BM;
   *bn_out = gemm_pick_bn(M, N, num_sms);
   *split_out = 1;
+  *cluster_out = 1;
   if (m_tiles > 2 || (N % 4)) return;
   const int kb_total = (K + BK - 1) / BK + (K2 + BK - 1) / BK;
   double best = 1e30;
@@ -1095,9 +1387,21 @@ void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split
       const long long tiles = static_cast<long long>(m_tiles) * n_tiles * eff;
       const long long waves = (tiles + num_sms - 1) / num_sms;
       double bytes = static_cast<double>(waves) * (BM + bn) * per * BK * 2.0;
-      double t = bytes / 64e9 + 2e-6 * waves;                      // ~64 GB/s per SM through TMA
-      if (eff > 1) t += 3e-6 + static_cast<double>(M) * N * 4.0 * (eff + 1) / 5e12;   // partial write + reduce
-      if (t < best) { best = t; *bn_out = bn; *split_out = eff; }
+      double t = bytes / 64e9 + 2e-6 * waves;
+      if (eff > 1) t += 6e-6 + static_cast<double>(M) * N * 4.0 * (eff + 1) / 5e12;   // partial write + reduce launch
+      if (t < best) { best = t; *bn_out = bn; *split_out = eff; *cluster_out = 1; }
+    }
+    // cluster split: one CTA per k-slice, non-persistent
+    const int cl[3] = {2, 4, 8};
+    for (int k = 0; k < 3; ++k) {
+      const int S = cl[k];
+      const bool supported = (bn == 64 && S <= 4) || (bn == 128) || (bn == 256 && S == 2);
+      if (!supported || S > kb_total || (N % 16)) continue;
+      const int per = (kb_total + S - 1) / S;
+      const long long ctas = static_cast<long long>(m_tiles) * n_tiles * S;
+      const long long waves = (ctas + num_sms - 1) / num_sms;
+      double t = static_cast<double>(waves) * ((BM + bn) * static_cast<double>(per) * BK * 2.0 / 64e9 + 2.5e-6) + 1e-6;
+      if (t < best) { best = t; *bn_out = bn; *split_out = 1; *cluster_out = S; }
     }
   }
 }
@@ -1111,6 +1415,19 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
     return "operand base addresses must be 16-byte aligned";
+  if (a.cluster_k > 1) {
+    if (a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "cluster split-k gemm: no global k-split, grouping or all-reduce";
+    const int key = a.force_bn * 10 + a.cluster_k;
+    switch (key) {
+      case 642: return launch_ksplit_flags<64, 2>(a, stream);
+      case 644: return launch_ksplit_flags<64, 4>(a, stream);
+      case 1282: return launch_ksplit_flags<128, 2>(a, stream);
+      case 1284: return launch_ksplit_flags<128, 4>(a, stream);
+      case 1288: return launch_ksplit_flags<128, 8>(a, stream);
+      case 2562: return launch_ksplit_flags<256, 2>(a, stream);
+      default: return "cluster split-k gemm: unsupported (BN, cluster) pair";
+    }
+  }
   if (a.two_cta) {
     if (a.out_f32 || a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "2-CTA gemm: bf16 output, no k-split, grouping or all-reduce";
     if (a.two_cta == 128) return a.residual ? launch_2cta<128, true>(a, stream) : launch_2cta<128, false>(a, stream);

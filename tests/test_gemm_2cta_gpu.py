@@ -43,3 +43,46 @@ def test_two_cta_matches_fp32(bn, M, N, K, res, lora):
     # same bits as the one-SM kernel (same k order, same rounding)
     y1 = C.gemm(a, b, a2, b2, r, force_bn=128 if N >= 128 else 64)
     assert float((y.float() - y1.float()).abs().max()) <= 0.01 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("bn,S", [(64, 2), (64, 4), (128, 2), (128, 4), (128, 8), (256, 2)])
+@pytest.mark.parametrize("M,N,K,res,lora,f32", [(128, 512, 4096, False, False, False), (100, 1024, 1032, True, True, False),
+                                                 (256, 768, 192, True, False, True), (7, 256, 64, False, False, False)])
+def test_cluster_split_k(bn, S, M, N, K, res, lora, f32):
+    """Cluster split-k (partials reduced through distributed shared memory) against fp32 matmul,
+    including k-slices that come out empty and repeated calls (bitwise reproducible)."""
+    from ferrl_b200.ops import cuda as C
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(M + N + K + bn + S)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    a = rnd(M, K).to(torch.bfloat16)
+    b = (rnd(N, K) / K ** 0.5).to(torch.bfloat16)
+    a2 = rnd(M, 16).to(torch.bfloat16) if lora else None
+    b2 = (rnd(N, 16) * 0.2).to(torch.bfloat16) if lora else None
+    r = rnd(M, N).to(torch.bfloat16) if res else None
+    y = C.gemm(a, b, a2, b2, r, out_f32=f32, force_bn=bn, cluster_k=S)
+    y2 = C.gemm(a, b, a2, b2, r, out_f32=f32, force_bn=bn, cluster_k=S)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    want = a.float() @ b.float().t()
+    if lora:
+        want = want + a2.float() @ b2.float().t()
+    if res:
+        want = want + r.float()
+    assert float((y.float() - want).abs().max()) <= 0.02 * float(want.abs().max())
+    assert torch.equal(y, y2)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 6144, 4096), (128, 4096, 4096), (128, 24576, 4096), (128, 4096, 12288),
+                                   (128, 151936, 4096), (200, 4096, 4096)])
+def test_decode_shapes_planned(M, N, K):
+    from ferrl_b200.ops import cuda as C
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(N + K)
+    a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=dev, generator=g) / K ** 0.5).to(torch.bfloat16)
+    y = C.gemm(a, b)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    want = a.float() @ b.float().t()
+    assert float((y.float() - want).abs().max()) <= 0.02 * float(want.abs().max())
