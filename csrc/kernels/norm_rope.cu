@@ -87,6 +87,133 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ x, const T* __restrict_
   }
 }
 
+// ---- bf16 vector forms: each thread owns up to VMAX 16-byte chunks of the row and keeps them in
+// registers between the reduction and the scaling, so every byte is read once and all accesses
+// are 16 bytes wide.  Same arithmetic (and the same rounding points) as the scalar kernels above.
+constexpr int VMAX = 4;
+
+__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float2 t = __bfloat1622float2(h[e]);
+    f[2 * e] = t.x;
+    f[2 * e + 1] = t.y;
+  }
+}
+__device__ __forceinline__ uint4 pack8f(const float* f) {
+  uint4 o;
+  __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(f[2 * e], f[2 * e + 1]);
+  return o;
+}
+
+__global__ void rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res,
+                                   const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ gate,
+                                   __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, int H, float eps,
+                                   int zero_centered) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int chunks = H / 8;
+  float v[VMAX][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VMAX; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      unpack8(reinterpret_cast<const uint4*>(x + row * H)[c], v[k]);
+      if (res) {
+        float r[8];
+        unpack8(reinterpret_cast<const uint4*>(res + row * H)[c], r);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[k][e] += r[e];
+        const uint4 hv = pack8f(v[k]);          // the norm sees exactly what the residual stream holds
+        reinterpret_cast<uint4*>(h_out + row * H)[c] = hv;
+        unpack8(hv, v[k]);
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ss += v[k][e] * v[k][e];
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / H + eps);
+#pragma unroll
+  for (int k = 0; k < VMAX; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = v[k][e] * rstd;
+      if (w) {
+        float wv[8];
+        unpack8(reinterpret_cast<const uint4*>(w)[c], wv);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= zero_centered ? (1.f + wv[e]) : wv[e];
+      }
+      if (gate) {
+        float g[8];
+        unpack8(reinterpret_cast<const uint4*>(gate + row * H)[c], g);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o[e] *= g[e] / (1.f + __expf(-g[e]));
+      }
+      reinterpret_cast<uint4*>(y + row * H)[c] = pack8f(o);
+    }
+  }
+}
+
+__global__ void rmsnorm_bwd_vec_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ w,
+                                       const __nv_bfloat16* __restrict__ dy, __nv_bfloat16* __restrict__ dx, int H,
+                                       float eps, int zero_centered) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const int chunks = H / 8;
+  float xv[VMAX][8], gw[VMAX][8];      // x and w*dy
+  float ss = 0.f, dot = 0.f;
+#pragma unroll
+  for (int k = 0; k < VMAX; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      unpack8(reinterpret_cast<const uint4*>(x + row * H)[c], xv[k]);
+      unpack8(reinterpret_cast<const uint4*>(dy + row * H)[c], gw[k]);
+      float wv[8];
+      if (w) unpack8(reinterpret_cast<const uint4*>(w)[c], wv);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        float ww = w ? wv[e] : 1.f;
+        if (zero_centered) ww += 1.f;
+        gw[k][e] *= ww;
+        ss += xv[k][e] * xv[k][e];
+        dot += xv[k][e] * gw[k][e];
+      }
+    }
+  }
+  const float tot = block_sum(ss, red);
+  const float d = block_sum(dot, red);
+  const float rstd = rsqrtf(tot / H + eps);
+  const float cc = d * rstd * rstd / H;
+#pragma unroll
+  for (int k = 0; k < VMAX; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < chunks) {
+      float o[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = rstd * (gw[k][e] - xv[k][e] * cc);
+      reinterpret_cast<uint4*>(dx + row * H)[c] = pack8f(o);
+    }
+  }
+}
+
+static inline bool vec_ok(int H, const void* a, const void* b, const void* c, const void* d, const void* e, const void* f) {
+  auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return (H % 8) == 0 && H / 8 <= VMAX * 512 && al(a) && al(b) && al(c) && al(d) && al(e) && al(f);
+}
+static inline int vec_threads(int H) {
+  const int chunks = H / 8;
+  int t = (chunks + VMAX - 1) / VMAX;
+  t = (t + 31) / 32 * 32;
+  return t < 64 ? 64 : (t > 512 ? 512 : t);
+}
+
 // One warp per (token, head). D <= 512, D even. rot = 2*half <= D.
 template <typename T, bool BWD>
 __global__ void qk_norm_rope_kernel(const T* __restrict__ q_in, long long ld_q, const T* __restrict__ k_in,
@@ -215,6 +342,14 @@ template <typename T>
 static const char* rmsnorm_t(const void* x, const void* res, const void* w, const void* gate, void* y, void* h_out,
                              long long rows, int H, float eps, bool zc, cudaStream_t s) {
   if (rows == 0) return nullptr;
+  if (sizeof(T) == 2 && vec_ok(H, x, res, w, gate, y, h_out)) {
+    using B = __nv_bfloat16;
+    rmsnorm_vec_kernel<<<static_cast<unsigned>(rows), vec_threads(H), 0, s>>>(
+        static_cast<const B*>(x), static_cast<const B*>(res), static_cast<const B*>(w), static_cast<const B*>(gate),
+        static_cast<B*>(y), static_cast<B*>(h_out), H, eps, zc ? 1 : 0);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm launch failed";
+  }
   int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   rmsnorm_kernel<T><<<static_cast<unsigned>(rows), threads, 0, s>>>(
       static_cast<const T*>(x), static_cast<const T*>(res), static_cast<const T*>(w), static_cast<const T*>(gate),
@@ -233,6 +368,14 @@ template <typename T>
 static const char* rmsnorm_bwd_t(const void* x, const void* w, const void* dy, void* dx, long long rows, int H,
                                  float eps, bool zc, cudaStream_t s) {
   if (rows == 0) return nullptr;
+  if (sizeof(T) == 2 && vec_ok(H, x, w, dy, dx, nullptr, nullptr)) {
+    using B = __nv_bfloat16;
+    rmsnorm_bwd_vec_kernel<<<static_cast<unsigned>(rows), vec_threads(H), 0, s>>>(
+        static_cast<const B*>(x), static_cast<const B*>(w), static_cast<const B*>(dy), static_cast<B*>(dx), H, eps,
+        zc ? 1 : 0);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_bwd launch failed";
+  }
   int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
   rmsnorm_bwd_kernel<T><<<static_cast<unsigned>(rows), threads, 0, s>>>(
       static_cast<const T*>(x), static_cast<const T*>(w), static_cast<const T*>(dy), static_cast<T*>(dx), H, eps,
