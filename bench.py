@@ -243,7 +243,8 @@ def main():
                        "group_size": args.group, "seq_len": f"prompt U[{args.prompt_lo},{args.prompt_hi}] + {args.max_new} new",
                        "lora": "r16 all-linear", "top_p": 0.95, "parallelism": f"dp{comm.world_size}",
                        "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
-                       "dp_step": "nccl" if args.nccl_baseline or comm.world_size == 1 else "fused-peer-memory",
+                       "dp_step": ("single rank" if comm.world_size == 1 else
+                                   "nccl per tensor" if args.nccl_baseline else "fused-peer-memory"),
                        "tokens_counted": "completion tokens"},
             "clocks": clk,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": policy.h2d_bytes // args.steps,
