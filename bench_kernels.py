@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_128|gemm_2cta_256|gemm_decode|decode_attn|sample|flash   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|rmsnorm|swiglu|qk_norm_rope|logprob|moe_grouped|gdn_decode   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -81,6 +81,39 @@ def profile_case(name, C):
     elif name == "flash":
         q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
         fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True)
+    elif name == "rmsnorm":
+        x, r, w = rnd(24576, 4096), rnd(24576, 4096), torch.ones(4096, device=dev, dtype=bf)
+        fn = lambda: C.add_rmsnorm(x, r, w, 1e-6)
+    elif name == "swiglu":
+        gu = rnd(12288, 24576)
+        fn = lambda: C.swiglu(gu)
+    elif name == "qk_norm_rope":
+        from ferrl_b200 import ops
+        qq, kk = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128)
+        wq, wk = torch.ones(128, device=dev, dtype=bf), torch.ones(128, device=dev, dtype=bf)
+        cos, sin = ops.rope_tables(ops.default_inv_freq(128, 1e6), 2048)
+        cos, sin, pos = cos.to(dev), sin.to(dev), torch.arange(1536, device=dev)
+        fn = lambda: C.qk_norm_rope(qq, kk, wq, wk, 1e-6, cos, sin, pos)
+    elif name == "logprob":
+        lg = rnd(2048, 151936)
+        tg = torch.randint(0, 151936, (2048,), device=dev)
+        fn = lambda: C.lib().logprob_rows(lg, tg, 1.0, 0.0)
+    elif name == "gemm_lora":
+        a, b, a2, b2 = rnd(8192, 4096), rnd(6144, 4096), rnd(8192, 48), rnd(6144, 48)
+        fn = lambda: C.gemm(a, b, a2, b2)
+    elif name == "moe_grouped":
+        T_, E_, k_, H_, I_ = 8192, 64, 8, 2048, 768
+        x = rnd(T_, H_)
+        gate_up, down = rnd(E_, 2 * I_, H_), rnd(E_, H_, I_)
+        scores, idx, counts, _ = C.moe_route(torch.randn(T_, E_, device=dev, generator=g), k_, True)
+        fn = lambda: C.moe_experts(x, scores, idx, counts, gate_up, down, "silu")
+    elif name == "gdn_decode":
+        B_, Hk_, Hv_ = 128, 16, 32
+        qd, kd, vd = rnd(B_, Hk_ * 128), rnd(B_, Hk_ * 128), rnd(B_, Hv_ * 128)
+        gg = -torch.rand(B_, Hv_, device=dev)
+        bb = torch.rand(B_, Hv_, device=dev)
+        S = torch.zeros(B_, Hv_, 128, 128, device=dev)
+        fn = lambda: C.gdn_decode_step(qd, kd, vd, gg, bb, S, True, 1e-6)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     evs = []

@@ -149,6 +149,10 @@ const char* gdn_conv_bwd(const void* x, long long ldx, const void* w, const void
                          int C, int K, bool act, void* dx, cudaStream_t stream);
 const char* gdn_conv_step(const void* x, long long ldx, const void* w, void* state, int B, int C, int K, bool act,
                           void* y, cudaStream_t stream);
+const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long q_bs, long long q_ts, long long k_bs,
+                          long long k_ts, long long v_bs, long long v_ts, const float* g, const float* beta,
+                          const float* S0, float* S_out, void* out, int B, int T, int Hk, int Hv, int KD, int VD,
+                          bool l2norm, float eps, cudaStream_t stream);
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                             const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
                             bool l2norm, float eps, void* out, cudaStream_t stream);

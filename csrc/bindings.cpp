@@ -230,6 +230,34 @@ Tensor gdn_decode_step(const Tensor& q, const Tensor& k, const Tensor& v, const 
   return out;
 }
 
+// q,k [B,T,Hk,KD], v [B,T,Hv,VD] bf16 (head dims contiguous, token/batch strides free), g,beta [B,T,Hv] f32,
+// S0 [B,Hv,KD,VD] f32 or none -> (out [B,T,Hv,VD] bf16, S [B,Hv,KD,VD] f32)
+std::tuple<Tensor, Tensor> gdn_chunk_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g,
+                                         const Tensor& beta, const optional<Tensor>& S0, bool l2norm, double eps) {
+  TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
+                  v.scalar_type() == at::kBFloat16 && q.dim() == 4 && k.dim() == 4 && v.dim() == 4, "gdn_chunk_fwd: bf16 [B,T,H,D]");
+  const int64_t B = q.size(0), T = q.size(1), Hk = q.size(2), KD = q.size(3), Hv = v.size(2), VD = v.size(3);
+  auto packed = [](const Tensor& t) { return t.stride(3) == 1 && t.stride(2) == t.size(3); };
+  TORCH_CHECK(packed(q) && packed(k) && packed(v), "gdn_chunk_fwd: heads must be packed in the last two dims");
+  TORCH_CHECK(g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && g.is_contiguous() && beta.is_contiguous() &&
+                  g.numel() == B * T * Hv && beta.numel() == B * T * Hv, "gdn_chunk_fwd: g,beta f32 [B,T,Hv]");
+  c10::cuda::CUDAGuard guard(q.device());
+  const float* s0 = nullptr;
+  Tensor s0c;
+  if (S0.has_value() && S0->defined()) {
+    s0c = S0->to(at::kFloat).contiguous();
+    TORCH_CHECK(s0c.numel() == B * Hv * KD * VD, "gdn_chunk_fwd: state [B,Hv,KD,VD]");
+    s0 = s0c.data_ptr<float>();
+  }
+  Tensor out = at::empty({B, T, Hv, VD}, q.options());
+  Tensor S = at::empty({B, Hv, KD, VD}, q.options().dtype(at::kFloat));
+  FERRL_CHECK(ferrl::gdn_chunk_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), q.stride(1), k.stride(0),
+                                   k.stride(1), v.stride(0), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(), s0,
+                                   S.data_ptr<float>(), out.data_ptr(), B, T, Hk, Hv, KD, VD, l2norm,
+                                   static_cast<float>(eps), stream()));
+  return {out, S};
+}
+
 // ---------------------------------------------------------------- mixture of experts
 // logits [T, E] fp32 -> (probs [T,E] f32, scores [T,k] f32, idx [T,k] i32, counts [E] i32)
 std::tuple<Tensor, Tensor, Tensor, Tensor> moe_route(const Tensor& logits, int64_t k, bool renorm) {
@@ -812,6 +840,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
   m.def("gdn_conv_step(Tensor x, Tensor w, Tensor(a!) state, bool act) -> Tensor", &gdn_conv_step);
+  m.def("gdn_chunk_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0, bool l2norm, float eps) -> (Tensor, Tensor)", &gdn_chunk_fwd);
   m.def("gdn_decode_step(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor(a!) S, bool l2norm, float eps) -> Tensor", &gdn_decode_step);
   m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
   m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);

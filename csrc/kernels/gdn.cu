@@ -164,6 +164,282 @@ __global__ void gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ q, cons
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Chunked gated delta rule, forward (crates/ferrl/src/gdn.rs:451-556 composes it from ~40 tensor
+// ops per chunk).  One CTA per (batch row, value head) walks the sequence in chunks of 64 tokens
+// with the [128, 128] fp32 state resident in shared memory the whole time:
+//
+//   1. load q,k (L2-normalised, q scaled), v*beta, cumulative log-decay G, k*beta*exp(G)
+//   2. A = tril(beta_i exp(G_i-G_j) <k_i,k_j>, -1)
+//   3. (I + A) [u | w] = [v*beta | k*beta*exp(G)] by forward substitution, one column per thread
+//      held in registers (the unit-triangular solve the reference does in 8x8 blocks)
+//   4. v_new = u - w S
+//   5. P = tril(exp(G_i-G_j) <q_i,k_j>)
+//   6. o = (q exp(G)) S + P v_new
+//   7. S <- S exp(G_last) + (k exp(G_last-G))^T v_new
+//
+// All products are fp32 FMAs on register micro-tiles (4x4, 4x8, 8x8) fed from shared memory; the
+// arithmetic and its order inside a chunk are fixed, so results are bit-reproducible.
+constexpr int GC = 64;      // chunk length
+constexpr int GD = 128;     // key and value head dim of this kernel
+
+__global__ void __launch_bounds__(256, 1)
+gdn_chunk_fwd_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                     const __nv_bfloat16* __restrict__ v, long long q_bs, long long q_ts, long long k_bs,
+                     long long k_ts, long long v_bs, long long v_ts, const float* __restrict__ g,
+                     const float* __restrict__ beta, const float* __restrict__ S0, float* __restrict__ S_out,
+                     __nv_bfloat16* __restrict__ out, int T, int Hk, int Hv, int l2norm, float eps) {
+  extern __shared__ __align__(16) float gsm[];
+  float* S = gsm;                     // [GD][GD]
+  float* ks = S + GD * GD;            // [GC][GD]
+  float* qs = ks + GC * GD;           // [GC][GD]
+  float* us = qs + GC * GD;           // [GC][GD]  v*beta -> u -> v_new
+  float* ws = us + GC * GD;           // [GC][GD]  k*beta*exp(G) -> w
+  float* A = ws + GC * GD;            // [GC][GC]
+  float* Gc = A + GC * GC;            // [GC] cumulative log decay
+  float* bt = Gc + GC;                // [GC]
+  const int b = blockIdx.x / Hv, hv = blockIdx.x % Hv;
+  const int hk = hv / (Hv / Hk);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const long long bh = static_cast<long long>(b) * Hv + hv;
+  const float qscale = rsqrtf(static_cast<float>(GD));
+
+  for (int i = tid; i < GD * GD; i += 256) S[i] = S0 ? S0[bh * GD * GD + i] : 0.f;
+
+  for (int c0 = 0; c0 < T; c0 += GC) {
+    const int n = min(GC, T - c0);
+    __syncthreads();
+    // ---- 1. loads
+    if (tid < GC) {
+      const long long gi = (static_cast<long long>(b) * T + c0 + tid) * Hv + hv;
+      Gc[tid] = tid < n ? g[gi] : 0.f;
+      bt[tid] = tid < n ? beta[gi] : 0.f;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      float acc = 0.f;
+      for (int i = 0; i < GC; ++i) {
+        acc += Gc[i];
+        Gc[i] = acc;
+      }
+    }
+    for (int r = warp; r < GC; r += 8) {       // a warp per row, 4 channels per lane
+      float kv[4] = {0.f, 0.f, 0.f, 0.f}, qv[4] = {0.f, 0.f, 0.f, 0.f}, vv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (r < n) {
+        const __nv_bfloat16* kp = k + b * k_bs + (c0 + r) * k_ts + hk * GD + lane * 4;
+        const __nv_bfloat16* qp = q + b * q_bs + (c0 + r) * q_ts + hk * GD + lane * 4;
+        const __nv_bfloat16* vp = v + b * v_bs + (c0 + r) * v_ts + hv * GD + lane * 4;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          kv[e] = __bfloat162float(kp[e]);
+          qv[e] = __bfloat162float(qp[e]);
+          vv[e] = __bfloat162float(vp[e]);
+        }
+      }
+      float kn = 1.f, qn = 1.f;
+      if (l2norm) {
+        kn = rsqrtf(warp_sum(kv[0] * kv[0] + kv[1] * kv[1] + kv[2] * kv[2] + kv[3] * kv[3]) + eps);
+        qn = rsqrtf(warp_sum(qv[0] * qv[0] + qv[1] * qv[1] + qv[2] * qv[2] + qv[3] * qv[3]) + eps);
+      }
+      *reinterpret_cast<float4*>(ks + r * GD + lane * 4) = make_float4(kv[0] * kn, kv[1] * kn, kv[2] * kn, kv[3] * kn);
+      const float qm = qn * qscale;
+      *reinterpret_cast<float4*>(qs + r * GD + lane * 4) = make_float4(qv[0] * qm, qv[1] * qm, qv[2] * qm, qv[3] * qm);
+      *reinterpret_cast<float4*>(us + r * GD + lane * 4) = make_float4(vv[0], vv[1], vv[2], vv[3]);
+    }
+    __syncthreads();
+    for (int i = tid; i < GC * GD; i += 256) {
+      const int r = i / GD;
+      us[i] *= bt[r];
+      ws[i] = ks[i] * bt[r] * __expf(Gc[r]);
+    }
+    // ---- 2. A = strictly lower part of beta_i exp(G_i-G_j) <k_i,k_j>; 4x4 tile per thread
+    {
+      const int ti = tid / 16, tj = tid % 16;
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+      if (tj <= ti) {
+        for (int dd = 0; dd < GD; ++dd) {
+          const int d = (dd + lane) & (GD - 1);    // each lane starts at its own channel: no bank conflicts
+          float ka[4], kb[4];
+#pragma unroll
+          for (int a = 0; a < 4; ++a) {
+            ka[a] = ks[(4 * ti + a) * GD + d];
+            kb[a] = ks[(4 * tj + a) * GD + d];
+          }
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][c] += ka[a] * kb[c];
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int i = 4 * ti + a, j = 4 * tj + c;
+          A[i * GC + j] = (j < i) ? acc[a][c] * bt[i] * __expf(Gc[i] - Gc[j]) : 0.f;
+        }
+    }
+    __syncthreads();
+    // ---- 3. forward substitution; thread t owns column t of [u | w]
+    {
+      float* col = (tid < GD) ? (us + tid) : (ws + (tid - GD));
+      float x[GC];
+#pragma unroll
+      for (int i = 0; i < GC; ++i) x[i] = col[i * GD];
+#pragma unroll
+      for (int i = 1; i < GC; ++i) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < i; ++j) acc += A[i * GC + j] * x[j];
+        x[i] -= acc;
+      }
+#pragma unroll
+      for (int i = 0; i < GC; ++i) col[i * GD] = x[i];
+    }
+    __syncthreads();
+    // ---- 4. v_new = u - w S; 4 rows x 8 cols per thread
+    const int tr = tid / 16, tc = tid % 16;
+    {
+      float acc[4][8];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[a][c] = 0.f;
+      for (int d = 0; d < GD; ++d) {
+        const float4 s0 = *reinterpret_cast<const float4*>(S + d * GD + tc * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(S + d * GD + tc * 8 + 4);
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float wv = ws[(4 * tr + a) * GD + d];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[a][c] += wv * sv[c];
+        }
+      }
+      __syncthreads();     // everyone has finished reading ws/us of this phase's inputs before us changes
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) us[(4 * tr + a) * GD + tc * 8 + c] -= acc[a][c];
+    }
+    // ---- 5. P = lower (inclusive) part of exp(G_i-G_j) <q_i,k_j>, into A (L is no longer needed)
+    {
+      const int ti = tid / 16, tj = tid % 16;
+      float acc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[a][c] = 0.f;
+      if (tj <= ti) {
+        for (int dd = 0; dd < GD; ++dd) {
+          const int d = (dd + lane) & (GD - 1);
+          float qa[4], kb[4];
+#pragma unroll
+          for (int a = 0; a < 4; ++a) {
+            qa[a] = qs[(4 * ti + a) * GD + d];
+            kb[a] = ks[(4 * tj + a) * GD + d];
+          }
+#pragma unroll
+          for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[a][c] += qa[a] * kb[c];
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const int i = 4 * ti + a, j = 4 * tj + c;
+          A[i * GC + j] = (j <= i) ? acc[a][c] * __expf(Gc[i] - Gc[j]) : 0.f;
+        }
+    }
+    __syncthreads();
+    // ---- 6. o = (q exp(G)) S + P v_new
+    {
+      float acc[4][8];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[a][c] = 0.f;
+      float eg[4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a) eg[a] = __expf(Gc[4 * tr + a]);
+      for (int d = 0; d < GD; ++d) {
+        const float4 s0 = *reinterpret_cast<const float4*>(S + d * GD + tc * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(S + d * GD + tc * 8 + 4);
+        const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float qv = qs[(4 * tr + a) * GD + d] * eg[a];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[a][c] += qv * sv[c];
+        }
+      }
+      for (int j = 0; j < GC; ++j) {
+        const float4 u0 = *reinterpret_cast<const float4*>(us + j * GD + tc * 8);
+        const float4 u1 = *reinterpret_cast<const float4*>(us + j * GD + tc * 8 + 4);
+        const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+          const float pv = A[(4 * tr + a) * GC + j];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[a][c] += pv * uv[c];
+        }
+      }
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        const int r = 4 * tr + a;
+        if (r < n) {
+          uint4 o;
+          __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) oh[c] = __floats2bfloat162_rn(acc[a][2 * c], acc[a][2 * c + 1]);
+          *reinterpret_cast<uint4*>(out + ((static_cast<long long>(b) * T + c0 + r) * Hv + hv) * GD + tc * 8) = o;
+        }
+      }
+    }
+    __syncthreads();
+    // ---- 7. S <- S exp(G_last) + (k exp(G_last - G))^T v_new; 8x8 tile per thread
+    {
+      const float glast = Gc[GC - 1];
+      const float eglast = __expf(glast);
+      const int td = tid / 16, tcc = tid % 16;
+      float acc[8][8];
+#pragma unroll
+      for (int a = 0; a < 8; ++a) {
+        const float4 s0 = *reinterpret_cast<const float4*>(S + (8 * td + a) * GD + tcc * 8);
+        const float4 s1 = *reinterpret_cast<const float4*>(S + (8 * td + a) * GD + tcc * 8 + 4);
+        acc[a][0] = s0.x * eglast; acc[a][1] = s0.y * eglast; acc[a][2] = s0.z * eglast; acc[a][3] = s0.w * eglast;
+        acc[a][4] = s1.x * eglast; acc[a][5] = s1.y * eglast; acc[a][6] = s1.z * eglast; acc[a][7] = s1.w * eglast;
+      }
+      for (int i = 0; i < GC; ++i) {
+        const float dec = __expf(glast - Gc[i]);
+        const float4 k0 = *reinterpret_cast<const float4*>(ks + i * GD + td * 8);
+        const float4 k1 = *reinterpret_cast<const float4*>(ks + i * GD + td * 8 + 4);
+        const float4 u0 = *reinterpret_cast<const float4*>(us + i * GD + tcc * 8);
+        const float4 u1 = *reinterpret_cast<const float4*>(us + i * GD + tcc * 8 + 4);
+        const float kv[8] = {k0.x * dec, k0.y * dec, k0.z * dec, k0.w * dec, k1.x * dec, k1.y * dec, k1.z * dec, k1.w * dec};
+        const float uv[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+        for (int a = 0; a < 8; ++a)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[a][c] += kv[a] * uv[c];
+      }
+#pragma unroll
+      for (int a = 0; a < 8; ++a) {
+        *reinterpret_cast<float4*>(S + (8 * td + a) * GD + tcc * 8) = make_float4(acc[a][0], acc[a][1], acc[a][2], acc[a][3]);
+        *reinterpret_cast<float4*>(S + (8 * td + a) * GD + tcc * 8 + 4) = make_float4(acc[a][4], acc[a][5], acc[a][6], acc[a][7]);
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = tid; i < GD * GD; i += 256) S_out[bh * GD * GD + i] = S[i];
+}
+
 }  // namespace
 
 const char* gdn_conv_fwd(const void* x, long long ldx, const void* w, const void* left, int B, int L, int C, int K,
@@ -205,6 +481,29 @@ const char* gdn_conv_step(const void* x, long long ldx, const void* w, void* sta
                                                                 static_cast<__nv_bfloat16*>(y));
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_conv_step launch failed";
+}
+
+const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long q_bs, long long q_ts, long long k_bs,
+                          long long k_ts, long long v_bs, long long v_ts, const float* g, const float* beta,
+                          const float* S0, float* S_out, void* out, int B, int T, int Hk, int Hv, int KD, int VD,
+                          bool l2norm, float eps, cudaStream_t stream) {
+  if (KD != GD || VD != GD) return "gdn_chunk_fwd: key and value head dim must be 128";
+  if (Hk <= 0 || Hv % Hk) return "gdn_chunk_fwd: value heads must be a multiple of key heads";
+  if (B == 0 || T == 0) return nullptr;
+  constexpr size_t smem = (static_cast<size_t>(GD) * GD + 4 * GC * GD + GC * GC + 2 * GC) * sizeof(float);
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(gdn_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
+        cudaSuccess)
+      return "gdn_chunk_fwd: cannot reserve shared memory";
+    set = true;
+  }
+  gdn_chunk_fwd_kernel<<<B * Hv, 256, smem, stream>>>(
+      static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+      q_bs, q_ts, k_bs, k_ts, v_bs, v_ts, g, beta, S0, S_out, static_cast<__nv_bfloat16*>(out), T, Hk, Hv,
+      l2norm ? 1 : 0, eps);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_chunk_fwd launch failed";
 }
 
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,

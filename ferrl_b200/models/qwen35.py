@@ -281,15 +281,23 @@ class Qwen35Layer(nn.Module):
         q, k, v = y.split([self.key_dim, self.key_dim, self.value_dim], dim=-1)
         q, k = q.reshape(B, S_, self.kh, self.kd), k.reshape(B, S_, self.kh, self.kd)
         v = v.reshape(B, S_, self.vh, self.vd)
-        rep = self.vh // self.kh
-        if rep > 1:
-            q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
         beta = torch.sigmoid(b.float())
         g = -self.A_log.float().exp() * F.softplus(a.float() + self.dt_bias.float())
         if valid is not None:
             beta = beta * valid[:, :, None]
             g = g * valid[:, :, None]
         S0 = None if state is None else state[1]
+        if fast and not decode and not torch.is_grad_enabled() and self.kd == 128 and self.vd == 128:
+            # grad-free scoring and prefill: the whole chunked scan is one kernel with the state in shared memory
+            from ..ops import cuda as C
+            res = C.gdn_chunk_fwd(q, k, v, g, beta, S0, True, 1e-6)
+            if res is not None:
+                core, S1 = res
+                core = ops.rmsnorm_gated(core.reshape(-1, self.vd), z.reshape(-1, self.vd), self.gdn_norm, self.eps)
+                return f(self.out, core.reshape(B, S_, self.value_dim)), (new_left, S1)
+        rep = self.vh // self.kh
+        if rep > 1:
+            q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)
         if decode:
             core, S1 = G.gated_delta_rule_recurrent(q, k, v, g, beta, S0, use_qk_l2norm=True)
         else:

@@ -370,6 +370,17 @@ def gdn_conv_step(x, w, state, activation=True):
     return lib().gdn_conv_step(x, w.contiguous(), state, bool(activation))
 
 
+def gdn_chunk_fwd(q, k, v, g, beta, S0=None, l2norm=True, eps=1e-6):
+    """Chunked gated delta rule, forward only (no autograd): ``q,k`` ``[B,T,Hk,128]``, ``v``
+    ``[B,T,Hv,128]`` bf16, ``g,beta`` ``[B,T,Hv]`` f32 -> ``(out [B,T,Hv,128] bf16, S [B,Hv,128,128] f32)``;
+    ``None`` outside the kernel's domain."""
+    if not (_bf16(q) and _bf16(k) and _bf16(v)) or q.shape[-1] != 128 or v.shape[-1] != 128:
+        return None
+    fix = lambda t: t if (t.stride(3) == 1 and t.stride(2) == t.shape[3]) else t.contiguous()  # noqa: E731
+    return lib().gdn_chunk_fwd(fix(q), fix(k), fix(v), g.float().contiguous(), beta.float().contiguous(), S0,
+                               bool(l2norm), float(eps))
+
+
 def gdn_decode_step(q, k, v, g, beta, S, l2norm=True, eps=1e-6):
     """Single-token gated delta rule; ``S`` ``[B,Hv,KD,VD]`` float32 is updated in place."""
     return lib().gdn_decode_step(q, k, v, g.contiguous(), beta.contiguous(), S, bool(l2norm), float(eps))

@@ -71,3 +71,28 @@ def test_decode_step_matches_recurrent(B, Hk, Hv, KD, VD):
                                                     beta.view(B, 1, Hv), S_ref, use_qk_l2norm=True)
         assert float((o.float() - o_ref[:, 0]).abs().max()) <= 0.02 * float(o_ref.abs().max()) + 1e-3
         assert float((S - S_ref).abs().max()) <= 1e-4 * float(S_ref.abs().max()) + 1e-5
+
+
+@pytest.mark.parametrize("B,T,Hk,Hv,with_state", [(1, 64, 1, 1, False), (2, 150, 2, 4, True), (1, 7, 1, 2, True),
+                                                   (3, 257, 2, 2, False)])
+def test_chunk_scan_matches_recurrent(B, T, Hk, Hv, with_state):
+    """The chunked kernel (state in shared memory, 64-token chunks) against the token-by-token
+    fp32 recurrence, including a ragged last chunk and a carried-in state."""
+    from ferrl_b200.models import gdn as G
+    from ferrl_b200.ops import cuda as Cc
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(B * 1000 + T)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    q, k = rnd(B, T, Hk, 128).to(torch.bfloat16), rnd(B, T, Hk, 128).to(torch.bfloat16)
+    v = rnd(B, T, Hv, 128).to(torch.bfloat16)
+    gg = -torch.rand(B, T, Hv, device=dev, generator=g) * 0.5
+    beta = torch.rand(B, T, Hv, device=dev, generator=g)
+    S0 = rnd(B, Hv, 128, 128) * 0.05 if with_state else None
+    out, S = Cc.gdn_chunk_fwd(q, k, v, gg, beta, S0, True, 1e-6)
+    rep = Hv // Hk
+    qr, kr = q.float().repeat_interleave(rep, dim=2), k.float().repeat_interleave(rep, dim=2)
+    o_ref, S_ref = G.gated_delta_rule_recurrent(qr, kr, v.float(), gg, beta, S0, use_qk_l2norm=True)
+    assert float((out.float() - o_ref).abs().max()) <= 0.02 * float(o_ref.abs().max()) + 1e-3
+    assert float((S - S_ref).abs().max()) <= 2e-3 * float(S_ref.abs().max()) + 1e-4
+    out2, S2 = Cc.gdn_chunk_fwd(q, k, v, gg, beta, S0, True, 1e-6)
+    assert torch.equal(out, out2) and torch.equal(S, S2)
