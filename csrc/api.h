@@ -184,4 +184,10 @@ struct EpCombineParams {
 const char* ep_dispatch(const EpDispatchParams& p, int num_sms, cudaStream_t stream);
 const char* ep_combine(const EpCombineParams& p, int num_sms, cudaStream_t stream);
 
+// ---- adapter gradients out[R, C] = U^T X (csrc/kernels/lora_grad.cu)
+size_t lora_grad_workspace_floats(int R, int C, int n_splits);
+int lora_grad_splits(int M, int C, int num_sms);
+const char* lora_grad(const void* U, long long ldu, int R, const void* X, long long ldx, int C, int M, int n_splits,
+                      float* partial, int* counters, float* out, long long ldo, cudaStream_t stream);
+
 }  // namespace ferrl

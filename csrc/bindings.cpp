@@ -168,6 +168,27 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   return out;
 }
 
+// out[R, C] = U^T X, U [M, R] and X [M, C] bf16 (row strides free, last dim contiguous), fp32 result
+Tensor lora_grad(const Tensor& U, const Tensor& X) {
+  TORCH_CHECK(U.is_cuda() && U.scalar_type() == at::kBFloat16 && X.scalar_type() == at::kBFloat16 && U.dim() == 2 &&
+                  X.dim() == 2 && U.size(0) == X.size(0) && U.stride(1) == 1 && X.stride(1) == 1, "lora_grad: U [M,R], X [M,C] bf16");
+  c10::cuda::CUDAGuard guard(U.device());
+  const int64_t M = U.size(0), R = U.size(1), C = X.size(1);
+  Tensor out = at::empty({R, C}, U.options().dtype(at::kFloat));
+  if (M == 0) return out.zero_();
+  const int splits = ferrl::lora_grad_splits(M, C, num_sms());
+  Tensor partial = at::empty({static_cast<long long>(ferrl::lora_grad_workspace_floats(R, C, splits))}, out.options());
+  // per-device counters, zero between calls (the kernel resets the ones it used)
+  static std::vector<Tensor> counters(64);
+  const int dev = U.get_device();
+  const int64_t tiles = (C + 127) / 128;
+  if (!counters[dev].defined() || counters[dev].numel() < tiles)
+    counters[dev] = at::zeros({std::max<int64_t>(tiles, 4096)}, U.options().dtype(at::kInt));
+  FERRL_CHECK(ferrl::lora_grad(U.data_ptr(), U.stride(0), R, X.data_ptr(), X.stride(0), C, M, splits,
+                               partial.data_ptr<float>(), counters[dev].data_ptr<int>(), out.data_ptr<float>(), C, stream()));
+  return out;
+}
+
 // ---------------------------------------------------------------- GatedDeltaNet
 // x [B, L, C] bf16 (last dim contiguous, rows evenly strided), w [C, K], left [B, C, K-1] or none -> y [B, L, C]
 Tensor gdn_conv_fwd(const Tensor& x, const Tensor& w, const optional<Tensor>& left, bool act) {
@@ -837,6 +858,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
+  m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
   m.def("gdn_conv_step(Tensor x, Tensor w, Tensor(a!) state, bool act) -> Tensor", &gdn_conv_step);

@@ -322,6 +322,124 @@ __global__ void qk_norm_rope_kernel(const T* __restrict__ q_in, long long ld_q, 
   }
 }
 
+// bf16 vector form for D = 32*EPL (128 or 256): one warp per (token, head), EPL consecutive
+// channels per lane in one 8- or 16-byte access, rotation partners fetched with a warp shuffle
+// (partner lane = lane +- half/EPL).  Same arithmetic and rounding points as the kernel above.
+template <int EPL, bool BWD>
+__global__ void qk_norm_rope_vec_kernel(const __nv_bfloat16* __restrict__ q_in, long long ld_q,
+                                        const __nv_bfloat16* __restrict__ k_in, long long ld_k, long long ld_dq,
+                                        long long ld_dk, const __nv_bfloat16* __restrict__ qw,
+                                        const __nv_bfloat16* __restrict__ kw, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, const long long* __restrict__ pos,
+                                        const int* __restrict__ pos32, int pos_div, __nv_bfloat16* __restrict__ q_out,
+                                        __nv_bfloat16* __restrict__ k_out, const __nv_bfloat16* __restrict__ dq,
+                                        const __nv_bfloat16* __restrict__ dk, long long n_tok, int Hq, int Hkv, int half,
+                                        float eps, int zero_centered) {
+  constexpr int D = 32 * EPL;
+  const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = Hq + Hkv;
+  if (wid >= n_tok * heads) return;          // warp-uniform
+  const long long tok = wid / heads;
+  const int hh = static_cast<int>(wid % heads);
+  const bool is_q = hh < Hq;
+  const int h = is_q ? hh : hh - Hq;
+  const __nv_bfloat16* src = (is_q ? q_in + tok * ld_q : k_in + tok * ld_k) + h * D + lane * EPL;
+  const __nv_bfloat16* wv = is_q ? qw : kw;
+  const long long p = pos ? pos[tok / pos_div] : static_cast<long long>(pos32[tok / pos_div]);
+  const int rot = 2 * half;
+  const int i0 = lane * EPL;
+  const int shift = half / EPL;                                  // lanes between rotation partners
+  const bool in_rot = i0 < rot, lower = i0 < half;
+  const int partner = in_rot ? (lower ? lane + shift : lane - shift) : lane;
+
+  auto load = [&](const __nv_bfloat16* ptr, float* f) {
+    if (EPL == 4) {
+      const uint2 v = *reinterpret_cast<const uint2*>(ptr);
+      const __nv_bfloat162* hh2 = reinterpret_cast<const __nv_bfloat162*>(&v);
+      float2 a = __bfloat1622float2(hh2[0]), b = __bfloat1622float2(hh2[1]);
+      f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y;
+    } else {
+      unpack8(*reinterpret_cast<const uint4*>(ptr), f);
+    }
+  };
+  auto store = [&](__nv_bfloat16* ptr, const float* f) {
+    if (EPL == 4) {
+      uint2 v;
+      __nv_bfloat162* hh2 = reinterpret_cast<__nv_bfloat162*>(&v);
+      hh2[0] = __floats2bfloat162_rn(f[0], f[1]);
+      hh2[1] = __floats2bfloat162_rn(f[2], f[3]);
+      *reinterpret_cast<uint2*>(ptr) = v;
+    } else {
+      *reinterpret_cast<uint4*>(ptr) = pack8f(f);
+    }
+  };
+
+  float x[EPL], w[EPL], c[EPL], sn[EPL];
+  load(src, x);
+  float ss = 0.f;
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    ss += x[e] * x[e];
+    w[e] = 1.f;
+    c[e] = 1.f;
+    sn[e] = 0.f;
+  }
+  float rstd = 1.f;
+  if (wv) {
+    load(wv + i0, w);
+    if (zero_centered) {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) w[e] += 1.f;
+    }
+    rstd = rsqrtf(warp_sum(ss) / D + eps);
+  }
+  if (in_rot) {
+    const int f0 = lower ? i0 : i0 - half;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      c[e] = cos_t[p * half + f0 + e];
+      sn[e] = sin_t[p * half + f0 + e];
+    }
+  }
+  if (!BWD) {
+    float v[EPL], o[EPL];
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      v[e] = x[e] * rstd * w[e];
+      // the unfused form rounds the normalised value to bf16 before rotating it
+      if (in_rot) v[e] = __bfloat162float(__float2bfloat16_rn(v[e]));
+    }
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float u = __shfl_sync(0xffffffffu, v[e], partner);
+      o[e] = in_rot ? (lower ? v[e] * c[e] - u * sn[e] : v[e] * c[e] + u * sn[e]) : v[e];
+    }
+    store((is_q ? q_out + (tok * Hq + h) * D : k_out + (tok * Hkv + h) * D) + i0, o);
+  } else {
+    float g[EPL], dn[EPL];
+    load((is_q ? dq + (tok * Hq + h) * D : dk + (tok * Hkv + h) * D) + i0, g);
+    float dot = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPL; ++e) {
+      const float gj = __shfl_sync(0xffffffffu, g[e], partner);
+      dn[e] = in_rot ? (lower ? g[e] * c[e] + gj * sn[e] : g[e] * c[e] - gj * sn[e]) : g[e];
+      dot += x[e] * w[e] * dn[e];
+    }
+    __nv_bfloat16* dst = (is_q ? q_out + tok * ld_dq : k_out + tok * ld_dk) + h * D + i0;
+    float o[EPL];
+    if (wv) {
+      const float c2 = warp_sum(dot) * rstd * rstd / D;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[e] = rstd * (w[e] * dn[e] - x[e] * c2);
+    } else {
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) o[e] = dn[e];
+    }
+    store(dst, o);
+  }
+}
+
 // Decode: append this step's k (already normed+roped, [B,Hkv,D]) and v (view into qkv) to the cache
 // at each row's current length.
 template <typename T>
@@ -397,6 +515,25 @@ static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
   if (units == 0) return nullptr;
   int wpb = 8;
   long long blocks = (units + wpb - 1) / wpb;
+  if (sizeof(T) == 2 && (a.D == 128 || a.D == 256)) {
+    const int epl = a.D / 32;
+    auto al = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) % (2 * epl)) == 0 && (ld % epl) == 0; };
+    const bool ok = (a.half % epl) == 0 && al(a.q_in, a.ld_q) && al(a.k_in, a.ld_k) && al(a.q_out, a.backward ? a.ld_dq : epl) &&
+                    al(a.k_out, a.backward ? a.ld_dk : epl) && al(a.qw, epl) && al(a.kw, epl) && al(a.dq, epl) && al(a.dk, epl);
+    if (ok) {
+      using B = __nv_bfloat16;
+#define FERRL_QKV(EPLV)                                                                                             \
+  qk_norm_rope_vec_kernel<EPLV, BWD><<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(                             \
+      static_cast<const B*>(a.q_in), a.ld_q, static_cast<const B*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,               \
+      static_cast<const B*>(a.qw), static_cast<const B*>(a.kw), a.cos_t, a.sin_t, a.pos64, a.pos32, a.pos_div,      \
+      static_cast<B*>(a.q_out), static_cast<B*>(a.k_out), static_cast<const B*>(a.dq), static_cast<const B*>(a.dk), \
+      a.n_tok, a.Hq, a.Hkv, a.half, a.eps, a.zero_centered ? 1 : 0)
+      if (epl == 4) FERRL_QKV(4); else FERRL_QKV(8);
+#undef FERRL_QKV
+      count_launch();
+      return cudaGetLastError() == cudaSuccess ? nullptr : "qk_norm_rope launch failed";
+    }
+  }
   qk_norm_rope_kernel<T, BWD><<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const T*>(a.q_in), a.ld_q, static_cast<const T*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,
       static_cast<const T*>(a.qw),

@@ -65,6 +65,13 @@ def _pad8(t, dim):
     return torch.nn.functional.pad(t, pad)
 
 
+def _lora_grad(u, x):
+    """``uᵀ x`` in fp32 for ``u`` ``[M, R]`` (R a multiple of 8, <= 128) and ``x`` ``[M, C]`` bf16."""
+    if u.shape[1] > 128 or x.shape[1] % 8 or x.stride(0) % 8 or u.stride(0) % 8:
+        return torch.matmul(u.t().float(), x.float())
+    return lib().lora_grad(u, x)
+
+
 class _LoraLinear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, wt, a_stack, b_stack, residual=None):
@@ -110,8 +117,9 @@ class _LoraLinear(torch.autograd.Function):
         if a_stack is not None:
             R = a_stack.shape[0]
             # adapter gradients: tall-skinny reductions over the token dimension
-            da = torch.matmul(u.t(), x2)[:R].float() if a_stack.requires_grad else None
-            db = torch.matmul(dy2.t(), t)[:, :R].float() if b_stack.requires_grad else None
+            # adapter gradients: reductions over the token dimension (csrc/kernels/lora_grad.cu)
+            da = _lora_grad(u, x2)[:R] if a_stack.requires_grad else None
+            db = _lora_grad(t, dy2)[:R].t().contiguous() if b_stack.requires_grad else None
         return dx, None, None, da, db, (dy if getattr(ctx, "res_grad", False) else None)
 
 

@@ -320,3 +320,21 @@ def test_adamw_kernel_matches_eager():
     E.adamw_step(p2, g, m2, v2, grad_scale=1.0 / total, **kw)
     for a, b in zip(p, p2):
         assert (a - b).abs().max().item() < 1e-5
+
+
+@pytest.mark.parametrize("M,R,C", [(1000, 16, 4096), (12288, 48, 4096), (64, 8, 136), (5000, 96, 6144), (300, 128, 512),
+                                   (1, 16, 128)])
+def test_lora_grad_matches_fp32(M, R, C):
+    """Adapter-gradient kernel (token-dimension reduction on mma.sync) against fp32 matmul;
+    strided operands and repeated calls (the cross-CTA counters must reset themselves)."""
+    from ferrl_b200.ops import cuda as C_
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(M + R + C)
+    wide = torch.randn(M, C + 64, device=dev, generator=g).to(torch.bfloat16)
+    x = wide[:, 8:8 + C]
+    u = torch.randn(M, R, device=dev, generator=g).to(torch.bfloat16)
+    want = u.float().t() @ x.float()
+    for _ in range(3):
+        got = C_.lib().lora_grad(u, x)
+        assert float((got - want).abs().max()) <= 2e-3 * float(want.abs().max()) + 1e-3
+    assert torch.equal(got, C_.lib().lora_grad(u, x))
