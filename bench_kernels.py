@@ -208,12 +208,14 @@ def main():
         vc = torch.randn(Bd, Smax, HKV, D, device=dev, dtype=bf)
         lens = torch.full((Bd,), 832, device=dev, dtype=torch.int32)
         s = T(lambda: C.decode_attention(qd, kc, vc, lens, scale=D ** -0.5))
-        report("decode attention B128 len832 (smem pipeline)", s, 2 * Bd * 832 * HKV * D * 2, 4 * Bd * HQ * 832 * D)
+        report("decode attention B128 len832 (tensor-core pipeline)", s, 2 * Bd * 832 * HKV * D * 2, 4 * Bd * HQ * 832 * D)
+        s = T(lambda: C.decode_attention(qd, kc, vc, lens, scale=D ** -0.5, variant=2))
+        report("decode attention B128 len832 (scalar pipeline)", s, 2 * Bd * 832 * HKV * D * 2, 4 * Bd * HQ * 832 * D)
         s = T(lambda: C.decode_attention(qd, kc, vc, lens, scale=D ** -0.5, variant=1))
         report("decode attention B128 len832 (register kernel)", s, 2 * Bd * 832 * HKV * D * 2, 4 * Bd * HQ * 832 * D)
         lens2 = torch.full((Bd,), 1500, device=dev, dtype=torch.int32)
         s = T(lambda: C.decode_attention(qd, kc, vc, lens2, scale=D ** -0.5))
-        report("decode attention B128 len1500 (smem pipeline)", s, 2 * Bd * 1500 * HKV * D * 2, 4 * Bd * HQ * 1500 * D)
+        report("decode attention B128 len1500 (tensor-core pipeline)", s, 2 * Bd * 1500 * HKV * D * 2, 4 * Bd * HQ * 1500 * D)
     if want("rows"):
         x = torch.randn(24576, H, device=dev, dtype=bf)
         r = torch.randn(24576, H, device=dev, dtype=bf)

@@ -103,7 +103,7 @@ struct DecodeAttnArgs {
   const int* kv_len; const int* block_table; int bt_stride, page;
   void* out; float* workspace;
   int B, Hq, Hkv, D; long long seq_stride, tok_stride; float scale; int window, n_splits;
-  int no_pipe;   // 1: skip the shared-memory pipelined kernel (register-resident kernel instead)
+  int no_pipe;   // 0: tensor-core pipelined kernel; 2: scalar pipelined kernel; 1: register-resident kernel
 };
 const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s);
 size_t decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);

@@ -662,7 +662,7 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
     a.workspace = ws.data_ptr<float>();
   }
   a.out = out.data_ptr();
-  a.no_pipe = variant == 1 ? 1 : 0;
+  a.no_pipe = static_cast<int>(variant);
   FERRL_CHECK(ferrl::decode_attn(a, stream()));
   return out;
 }

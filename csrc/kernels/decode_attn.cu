@@ -583,6 +583,200 @@ decode_attn_pipe_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   }
 }
 
+// Tensor-core variant of the pipelined kernel.  The query heads that share a KV head are the M
+// dimension of the MMA (rows 0..REP-1 of a 16-row tile, the rest zero): scores S = Q K^T run on
+// mma.sync m16n8k16 with K fragments out of ldmatrix, P V on m16n8k8 with the P fragment taken
+// straight from the score accumulators and V fragments out of ldmatrix.trans.  Each warp owns 8 of
+// the 32 keys of a stage and keeps its own running max / sum / output; warps are merged at the end.
+// This removes the fp32 dot products from the CUDA cores, which bound the scalar kernel at ~57 %
+// of HBM bandwidth.  Shared-memory rows are XOR-swizzled by 16-byte chunk.
+__device__ __forceinline__ void mma_16816(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_1688(float* c, uint32_t a0, uint32_t a1, uint32_t b0) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(b0));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+
+template <int D, int REP>
+__global__ void __launch_bounds__(PWARPS * 32)
+decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                       const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
+                       const int* __restrict__ block_table, int bt_stride, int page,
+                       __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
+                       long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  static_assert(REP <= 8, "query heads of one KV head must fit rows 0..7 of the MMA tile");
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int CPR = ROW_BYTES / 16;                  // 16-byte chunks per row
+  constexpr int CHUNKS = PTK * CPR;
+  constexpr int STAGE_BYTES = 2 * PTK * ROW_BYTES;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;                            // output n-tiles
+  extern __shared__ __align__(128) uint8_t psm[];
+  const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  // Q fragments: rows g < REP are query heads hk*REP + g; a1 = a3 = 0 (rows 8..15 unused)
+  uint32_t qa0[KSTEPS], qa2[KSTEPS];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    qa0[ks] = 0u;
+    qa2[ks] = 0u;
+    if (g < REP) {
+      const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * REP + g) * D + ks * 16 + 2 * t;
+      qa0[ks] = *reinterpret_cast<const uint32_t*>(qp);
+      qa2[ks] = *reinterpret_cast<const uint32_t*>(qp + 8);
+    }
+  }
+  const int len = kv_len[b];
+  const int lo = (window > 0 && len > window) ? len - window : 0;
+  const int span = len - lo;
+  const int per = (span + n_splits - 1) / n_splits;
+  const int s0 = lo + split * per;
+  const int s1 = min(len, s0 + per);
+  const int n_tiles = s1 > s0 ? (s1 - s0 + PTK - 1) / PTK : 0;
+
+  auto row_of = [&](int j) -> long long {
+    if (block_table) {
+      int pg = block_table[static_cast<long long>(b) * bt_stride + j / page];
+      return (static_cast<long long>(pg) * page + (j % page)) * tok_stride + hk * D;
+    }
+    return static_cast<long long>(b) * seq_stride + static_cast<long long>(j) * tok_stride + hk * D;
+  };
+  auto issue = [&](int tt) {
+    if (tt < n_tiles) {
+      uint8_t* st = psm + (tt % PSTAGES) * STAGE_BYTES;
+      const int j0 = s0 + tt * PTK;
+      for (int c = threadIdx.x; c < CHUNKS; c += PWARPS * 32) {
+        const int key = c / CPR, part = c % CPR;
+        const int j = j0 + key;
+        const bool ok = j < s1;
+        const long long row = row_of(ok ? j : s0) + part * 8;
+        const int off = key * ROW_BYTES + ((part ^ (key & 7)) << 4);
+        cp_async16(st + off, kc + row, ok);
+        cp_async16(st + PTK * ROW_BYTES + off, vc + row, ok);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_run = -INFINITY, l_run = 0.f;     // row g of this warp's keys
+  float o[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+
+#pragma unroll
+  for (int tt = 0; tt < PSTAGES - 1; ++tt) issue(tt);
+  for (int tt = 0; tt < n_tiles; ++tt) {
+    cp_async_wait<PSTAGES - 2>();
+    __syncthreads();
+    issue(tt + PSTAGES - 1);
+    const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % PSTAGES) * STAGE_BYTES));
+    const uint32_t vt = kt + PTK * ROW_BYTES;
+    const int key0 = warp * 8;                        // this warp's 8 keys of the tile
+    const int j0 = s0 + tt * PTK + key0;
+    // ---- S = Q K^T for 8 keys
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+    const int lrow = key0 + (lane & 7), lmat = lane >> 3;
+#pragma unroll
+    for (int qd = 0; qd < KSTEPS / 2; ++qd) {
+      uint32_t b0, b1, b2, b3;
+      ldsm_x4(kt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), b0, b1, b2, b3);
+      mma_16816(sacc, qa0[2 * qd], 0u, qa2[2 * qd], 0u, b0, b1);
+      mma_16816(sacc, qa0[2 * qd + 1], 0u, qa2[2 * qd + 1], 0u, b2, b3);
+    }
+    // ---- online softmax on row g over keys (2t, 2t+1) of the 4 lanes sharing g
+    float sc0 = (j0 + 2 * t < s1) ? sacc[0] * scale : -INFINITY;
+    float sc1 = (j0 + 2 * t + 1 < s1) ? sacc[1] * scale : -INFINITY;
+    float mx = fmaxf(sc0, sc1);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m_run, mx);
+    const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+    const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
+    const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
+    float ps = p0 + p1;
+    ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+    ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+    l_run = l_run * corr + ps;
+    m_run = m_new;
+    __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
+    const uint32_t pa0 = *reinterpret_cast<uint32_t*>(&ph);
+    // ---- O = O * corr + P V
+#pragma unroll
+    for (int qd = 0; qd < NT / 4; ++qd) {
+      uint32_t v0, v1, v2, v3;
+      ldsm_x4_t(vt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), v0, v1, v2, v3);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        o[4 * qd + e][0] *= corr;
+        o[4 * qd + e][1] *= corr;
+      }
+      mma_1688(o[4 * qd + 0], pa0, 0u, v0);
+      mma_1688(o[4 * qd + 1], pa0, 0u, v1);
+      mma_1688(o[4 * qd + 2], pa0, 0u, v2);
+      mma_1688(o[4 * qd + 3], pa0, 0u, v3);
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge warps through shared memory (the ring is free now)
+  float* m_s = reinterpret_cast<float*>(psm);   // [PWARPS][REP]
+  float* l_s = m_s + PWARPS * REP;              // [PWARPS][REP]
+  float* o_s = l_s + PWARPS * REP;              // [PWARPS][REP][D]
+  if (g < REP) {
+    if (t == 0) {
+      m_s[warp * REP + g] = m_run;
+      l_s[warp * REP + g] = l_run;
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      o_s[(warp * REP + g) * D + n * 8 + 2 * t] = o[n][0];
+      o_s[(warp * REP + g) * D + n * 8 + 2 * t + 1] = o[n][1];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D;
+    float m = -INFINITY;
+    for (int w = 0; w < PWARPS; ++w) m = fmaxf(m, m_s[w * REP + r]);
+    float l = 0.f, acc = 0.f;
+    for (int w = 0; w < PWARPS; ++w) {
+      const float mw = m_s[w * REP + r];
+      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+      l += l_s[w * REP + r] * c;
+      acc += o_s[(w * REP + r) * D + d] * c;
+    }
+    const long long head = static_cast<long long>(b) * Hq + hk * REP + r;
+    if (n_splits == 1) {
+      out[head * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    } else {
+      float* w_ = ws + (head * n_splits + split) * (D + 2);
+      w_[d] = acc;
+      if (d == 0) {
+        w_[D] = m;
+        w_[D + 1] = l;
+      }
+    }
+  }
+}
+
 __global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
                                       int n_splits) {
   const long long head = blockIdx.x;
@@ -634,7 +828,7 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     launched = true;                                                                                                  \
   }
 #define FERRL_DECODE_PIPE(DD, RR)                                                                                   \
-  if (!launched && a.D == DD && rep == RR && !a.no_pipe) {                                                            \
+  if (!launched && a.D == DD && rep == RR && a.no_pipe != 1) {                                                            \
     constexpr size_t psm_bytes = static_cast<size_t>(PSTAGES) * 2 * PTK * DD * 2;                                     \
     auto pk = decode_attn_pipe_kernel<DD, RR>;                                                                        \
     static bool pset = false;                                                                                         \
@@ -649,6 +843,30 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
         grid.z);                                                                                                      \
     launched = true;                                                                                                  \
   }
+#define FERRL_DECODE_MMA(DD, RR)                                                                                    \
+  if (!launched && a.D == DD && rep == RR && a.no_pipe == 0) {                                                        \
+    constexpr size_t msm_bytes = static_cast<size_t>(PSTAGES) * 2 * PTK * DD * 2;                                     \
+    auto mk = decode_attn_mma_kernel<DD, RR>;                                                                         \
+    static bool mset = false;                                                                                         \
+    if (!mset) {                                                                                                      \
+      cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(msm_bytes));             \
+      mset = true;                                                                                                    \
+    }                                                                                                                 \
+    mk<<<grid, PWARPS * 32, msm_bytes, s>>>(                                                                          \
+        static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
+        static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
+        static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.seq_stride, a.tok_stride, a.scale, a.window,  \
+        grid.z);                                                                                                      \
+    launched = true;                                                                                                  \
+  }
+  if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(a.v) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.q) & 3) == 0) {
+    FERRL_DECODE_MMA(128, 4) FERRL_DECODE_MMA(128, 1) FERRL_DECODE_MMA(128, 2) FERRL_DECODE_MMA(128, 8)
+    FERRL_DECODE_MMA(64, 1) FERRL_DECODE_MMA(64, 2) FERRL_DECODE_MMA(64, 4) FERRL_DECODE_MMA(64, 8)
+    FERRL_DECODE_MMA(256, 1) FERRL_DECODE_MMA(256, 2) FERRL_DECODE_MMA(256, 4) FERRL_DECODE_MMA(256, 6)
+    FERRL_DECODE_MMA(256, 8)
+  }
+#undef FERRL_DECODE_MMA
   if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(a.v) & 15) == 0) {
     FERRL_DECODE_PIPE(128, 4) FERRL_DECODE_PIPE(128, 1) FERRL_DECODE_PIPE(128, 2) FERRL_DECODE_PIPE(128, 8)

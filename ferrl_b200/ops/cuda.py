@@ -308,8 +308,8 @@ def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None)
 
 
 def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0):
-    """``variant`` 0 picks the shared-memory pipelined kernel where it applies, 1 forces the
-    register-resident one (kept for head shapes the pipeline does not cover, and as a cross-check)."""
+    """``variant`` 0 picks the tensor-core pipelined kernel where it applies, 2 the scalar pipelined
+    one, 1 the register-resident one (both kept for uncovered head shapes and as cross-checks)."""
     if not _bf16(q) or q.shape[-1] % 8 or q.shape[-1] > 256:
         return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
     return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),

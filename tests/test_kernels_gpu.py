@@ -156,7 +156,7 @@ def test_flash_attention_fwd_bwd(D, causal, window):
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 32, 8), (64, 4, 4), (256, 16, 2), (16, 4, 2)])
-@pytest.mark.parametrize("variant", [0, 1])
+@pytest.mark.parametrize("variant", [0, 1, 2])
 @pytest.mark.parametrize("window,splits", [(0, 1), (0, 4), (50, 2)])
 def test_decode_attention(D, Hq, Hkv, window, splits, variant):
     from ferrl_b200.ops import cuda as C, eager as E
