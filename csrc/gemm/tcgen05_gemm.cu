@@ -210,7 +210,7 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 
 template <int BN> struct Cfg {
   static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
-  static constexpr int STAGES = (BN >= 256) ? 4 : (BN >= 128 ? 6 : 8);
+  static constexpr int STAGES = (BN >= 256) ? 4 : (BN > 128 ? 5 : (BN >= 128 ? 6 : 8));
   static constexpr int TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64 ? 64 : (2 * BN <= 128 ? 128 : (2 * BN <= 256 ? 256 : 512)));
   static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
@@ -431,7 +431,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.split_k > 1) {
           // fp32 partial of this k-slice; residual and the output cast happen in the reduce kernel
           if (row_ok && col < p.N) {
-            const int ncols = min(32, p.N - col);
+            const int ncols = min(min(32, BN - c), p.N - col);
             float* op = p.partial + (static_cast<long long>(ks) * p.M + row) * p.N + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
 #pragma unroll
@@ -456,7 +456,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           continue;
         }
         if (row_ok && col < p.N) {
-          const int ncols = min(32, p.N - col);
+          const int ncols = min(min(32, BN - c), p.N - col);
           if (HAS_RES) {
             const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
@@ -953,7 +953,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         tmem_ld_wait();
         const int col = ni * BN + c;
         if (row_ok && col < p.N) {
-          const int ncols = min(32, p.N - col);
+          const int ncols = min(min(32, BN - c), p.N - col);
           if (HAS_RES) {
             const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
@@ -1376,19 +1376,20 @@ void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split
   if (m_tiles > 2 || (N % 4)) return;
   const int kb_total = (K + BK - 1) / BK + (K2 + BK - 1) / BK;
   double best = 1e30;
-  const int cands[3] = {256, 128, 64};
-  for (int ci = 0; ci < 3; ++ci) {
+  const int cands[4] = {256, 176, 128, 64};   // 176 exists to fit N = 24576 onto 140 of 148 SMs in one wave
+  for (int ci = 0; ci < 4; ++ci) {
     const int bn = cands[ci];
     if (N < bn) continue;
     const int n_tiles = (N + bn - 1) / bn;
     for (int split = 1; split <= 16 && split <= kb_total; ++split) {
+      if (bn == 176 && split > 1) break;
       const int per = (kb_total + split - 1) / split;
       const int eff = (kb_total + per - 1) / per;
       const long long tiles = static_cast<long long>(m_tiles) * n_tiles * eff;
       const long long waves = (tiles + num_sms - 1) / num_sms;
       double bytes = static_cast<double>(waves) * (BM + bn) * per * BK * 2.0;
-      double t = bytes / 64e9 + 2e-6 * waves;
-      if (eff > 1) t += 6e-6 + static_cast<double>(M) * N * 4.0 * (eff + 1) / 5e12;   // partial write + reduce launch
+      double t = bytes / 64e9 + 7e-6;                                 // one prologue/drain for the persistent kernel
+      if (eff > 1) t += 8e-6 + static_cast<double>(M) * N * 4.0 * (eff + 1) / 5e12;   // partial write + reduce launch
       if (t < best) { best = t; *bn_out = bn; *split_out = eff; *cluster_out = 1; }
     }
     // cluster split: one CTA per k-slice, non-persistent
@@ -1400,7 +1401,9 @@ void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split
       const int per = (kb_total + S - 1) / S;
       const long long ctas = static_cast<long long>(m_tiles) * n_tiles * S;
       const long long waves = (ctas + num_sms - 1) / num_sms;
-      double t = static_cast<double>(waves) * ((BM + bn) * static_cast<double>(per) * BK * 2.0 / 64e9 + 2.5e-6) + 1e-6;
+      // measured: a cluster CTA pays ~9 us of prologue, exchange and drain per wave (one-tile CTAs
+      // cannot hide it behind the next tile the way the persistent kernel does)
+      double t = static_cast<double>(waves) * ((BM + bn) * static_cast<double>(per) * BK * 2.0 / 64e9 + 9e-6) + 1e-6;
       if (t < best) { best = t; *bn_out = bn; *split_out = 1; *cluster_out = S; }
     }
   }
@@ -1436,6 +1439,7 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   int bn = a.force_bn > 0 ? a.force_bn : gemm_pick_bn(a.M, a.N, a.num_sms);
   switch (bn) {
     case 256: return launch_flags<256>(a, stream);
+    case 176: return launch_flags<176>(a, stream);
     case 128: return launch_flags<128>(a, stream);
     case 64: return launch_flags<64>(a, stream);
     case 32: return launch_flags<32>(a, stream);

@@ -41,6 +41,36 @@ def main():
         heap.check("expert-parallel step")
         for a, b in zip(res[0], res[1]):
             assert torch.equal(a, b), (rep, float((a.float() - b.float()).abs().max()))
+    # timing at the hybrid-MoE benchmark's layer shape: 128 experts top-8, hidden 2048, expert FFN 768
+    if world in (2, 4, 8):
+        T2, E2, k2, H2, I2 = 8192, 128, 8, 2048, 768
+        rt2 = EpRuntime(heap, E2, H2, T2, k2, capacity_factor=2.0)
+        gu2 = (torch.randn(E2 // world, 2 * I2, H2, device=dev, generator=g) / H2 ** 0.5).to(torch.bfloat16)
+        dn2 = (torch.randn(E2 // world, H2, I2, device=dev, generator=g) / I2 ** 0.5).to(torch.bfloat16)
+        x2 = torch.randn(T2, H2, device=dev, generator=gl).to(torch.bfloat16)
+        sc2, idx2, cnt2, _ = C.moe_route(torch.randn(T2, E2, device=dev, generator=gl), k2, True)   # router logits N(0,1)
+
+        def run():
+            with torch.no_grad():
+                return rt2.experts(x2, sc2, idx2, cnt2, gu2, dn2, "silu")
+        for _ in range(3):
+            run()
+        torch.cuda.synchronize()
+        dist.barrier()
+        s_, e_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s_.record()
+        for _ in range(10):
+            run()
+        e_.record()
+        torch.cuda.synchronize()
+        heap.check("expert-parallel timing")
+        tt = torch.tensor([s_.elapsed_time(e_) / 10], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        if rank == 0:
+            sent = T2 * k2 * H2 * 2 * (world - 1) / world          # bytes a rank pushes out in dispatch (and pulls back in combine)
+            flops = 2 * T2 * k2 * H2 * 3 * I2                       # gate_up + down per routed row, per rank's tokens
+            print(f"EP_TIMING world={world} tokens/rank={T2} ms={float(tt):.4f} dispatch_bytes_out={sent / 1e6:.1f}MB "
+                  f"combine_bytes_in={sent / 1e6:.1f}MB expert_flops/rank={flops / 1e9:.1f}G")
     comm.barrier()
     if rank == 0:
         print("EP_PASS")
