@@ -58,6 +58,8 @@ struct QkNormRopeArgs {
   long long n_tok; int Hq, Hkv, D, half; float eps; bool zero_centered;
 };
 const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s);
+const char* kv_append_paged(const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
+                            const int* table, int bt_stride, int page, int batch, int HD, cudaStream_t s);
 const char* kv_append(int dtype, const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
                       int batch, int smax, int HD, cudaStream_t s);
 

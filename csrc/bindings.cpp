@@ -526,6 +526,17 @@ void kv_append(const Tensor& k, const Tensor& v, Tensor kc, Tensor vc, const Ten
                                kv_len.data_ptr<int>(), B, smax, HD, stream()));
 }
 
+void kv_append_paged(const Tensor& k, const Tensor& v, Tensor kc, Tensor vc, const Tensor& kv_len, const Tensor& table) {
+  // k [B, Hkv*D] contiguous, v [B, Hkv*D] row-strided view, pools [n_pages, page, Hkv, D], table [B, max_pages] i32
+  c10::cuda::CUDAGuard guard(k.device());
+  TORCH_CHECK(k.scalar_type() == at::kBFloat16 && k.is_contiguous() && v.stride(-1) == 1 && kc.is_contiguous() &&
+                  vc.is_contiguous() && kc.dim() == 4 && kv_len.scalar_type() == at::kInt && table.scalar_type() == at::kInt &&
+                  table.dim() == 2 && table.is_contiguous() && table.size(0) == k.size(0), "kv_append_paged: layout");
+  FERRL_CHECK(ferrl::kv_append_paged(k.data_ptr(), v.data_ptr(), v.stride(0), kc.data_ptr(), vc.data_ptr(),
+                                     kv_len.data_ptr<int>(), table.data_ptr<int>(), table.size(1), kc.size(1), k.size(0),
+                                     kc.size(2) * kc.size(3), stream()));
+}
+
 Tensor glu_fwd(const Tensor& gu, int64_t act) {
   TORCH_CHECK(gu.is_cuda() && gu.is_contiguous(), "glu: contiguous CUDA tensor");
   c10::cuda::CUDAGuard guard(gu.device());
@@ -879,6 +890,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("qk_norm_rope_fwd(Tensor q, Tensor k, Tensor? qw, Tensor? kw, Tensor cos, Tensor sin, Tensor pos, int pos_div, float eps, bool zc) -> (Tensor, Tensor)", &qk_norm_rope_fwd);
   m.def("qk_norm_rope_bwd(Tensor q, Tensor k, Tensor? qw, Tensor? kw, Tensor cos, Tensor sin, Tensor pos, int pos_div, float eps, bool zc, Tensor dq, Tensor dk, Tensor(a!) dq_in, Tensor(b!) dk_in) -> ()", &qk_norm_rope_bwd);
   m.def("kv_append(Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len) -> ()", &kv_append);
+  m.def("kv_append_paged(Tensor k, Tensor v, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len, Tensor table) -> ()", &kv_append_paged);
   m.def("glu_fwd(Tensor gu, int act) -> Tensor", &glu_fwd);
   m.def("glu_bwd(Tensor gu, Tensor dout, int act) -> Tensor", &glu_bwd);
   m.def("embedding(Tensor ids, Tensor table, float scale) -> Tensor", &embedding);

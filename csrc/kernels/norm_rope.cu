@@ -549,6 +549,37 @@ const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s) {
   return a.backward ? qknr_t<__nv_bfloat16, true>(a, s) : qknr_t<__nv_bfloat16, false>(a, s);
 }
 
+namespace {
+// Paged form: the caches are a pool [n_pages, page, Hkv*D]; row b's token t lives in page
+// table[b, t / page] at offset t % page.
+__global__ void kv_append_paged_kernel(const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v, long long ldv,
+                                       __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
+                                       const int* __restrict__ kv_len, const int* __restrict__ table, int bt_stride,
+                                       int page, int HD) {
+  const int b = blockIdx.x;
+  const int t = kv_len[b];
+  if (t / page >= bt_stride) return;   // row is full: drop rather than write out of bounds
+  const long long slot = static_cast<long long>(table[static_cast<long long>(b) * bt_stride + t / page]) * page + t % page;
+  for (int i = threadIdx.x; i < HD / 8; i += blockDim.x) {
+    reinterpret_cast<uint4*>(kc + slot * HD)[i] = reinterpret_cast<const uint4*>(k + static_cast<long long>(b) * HD)[i];
+    reinterpret_cast<uint4*>(vc + slot * HD)[i] = reinterpret_cast<const uint4*>(v + static_cast<long long>(b) * ldv)[i];
+  }
+}
+}  // namespace
+
+const char* kv_append_paged(const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
+                            const int* table, int bt_stride, int page, int batch, int HD, cudaStream_t s) {
+  if (batch == 0) return nullptr;
+  if ((HD % 8) || (ldv % 8) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
+      (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15))
+    return "kv_append_paged: 16-byte aligned rows required";
+  kv_append_paged_kernel<<<batch, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ldv,
+                                               static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, table,
+                                               bt_stride, page, HD);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "kv_append_paged launch failed";
+}
+
 const char* kv_append(int dtype, const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
                       int batch, int smax, int HD, cudaStream_t s) {
   if (batch == 0) return nullptr;

@@ -117,12 +117,15 @@ class LmPolicy(Policy):
         max_len = Lmax + N
         if dev.type == "cuda":
             max_len = (max_len + 127) // 128 * 128  # bucket the cache length so decoders and graphs are reused
-        dkey = (B, max_len)
+        dkey = (B, max_len, G)
         dec = self._decoders.get(dkey)
         if dec is None:
             self._decoders.clear()
             self._graphs.clear()
-            dec = self.model.new_decoder(B, max_len, self.comm)
+            try:
+                dec = self.model.new_decoder(B, max_len, self.comm, group=G)
+            except TypeError:       # model families whose decoder takes no group argument
+                dec = self.model.new_decoder(B, max_len, self.comm)
             self._decoders[dkey] = dec
         self.last_cache_bytes = dec.cache_bytes()
         logits = dec.prefill(ids, lens)

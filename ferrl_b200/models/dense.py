@@ -139,7 +139,7 @@ class DenseLayer(nn.Module):
         return self.down.forward_reduce(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged, residual=h)
 
     # one-token forward against the cache (rollout; merged weights)
-    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None):
+    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None, table=None):
         B = h.shape[0]
         x = ops.rmsnorm(h, self.input_norm, self.eps)
         qkv = self.qkv.forward_merged(x)
@@ -149,9 +149,15 @@ class DenseLayer(nn.Module):
         v = v.reshape(B, 1, self.hkv, self.D)
         q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin,
                                 pos if pos is not None else kv_len[:, None].long())
-        ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
-        a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
-                                 scale=self.scale)
+        if table is not None:
+            from ..ops import cuda as _c
+            _c.kv_append_paged(k_cache, v_cache, k[:, 0].contiguous(), v[:, 0], kv_len, table)
+            a = _c.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
+                                    scale=self.scale, block_table=table)
+        else:
+            ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
+            a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
+                                     scale=self.scale)
         o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
         return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
@@ -317,8 +323,17 @@ class DenseGradModel(nn.Module):
         return lp.view(B, L)
 
     # ------------------------------------------------------------- rollout
-    def new_decoder(self, batch: int, max_len: int, comm: Optional[Comm] = None) -> "DenseCachedDecoder":
-        return DenseCachedDecoder(self, batch, max_len, comm or SoloComm())
+    def new_decoder(self, batch: int, max_len: int, comm: Optional[Comm] = None, group: int = 1,
+                    paged: Optional[bool] = None) -> "DenseCachedDecoder":
+        """``group`` > 1 on a GPU selects the paged cache whose prompt pages are shared by the
+        ``group`` rows of a prompt (rows are prompt-major: row ``p*group + g``)."""
+        comm = comm or SoloComm()
+        if paged is None:
+            paged = (self.embed.is_cuda and self.dtype == torch.bfloat16 and group > 1 and batch % group == 0
+                     and self.spec.head_dim % 8 == 0)
+        if paged:
+            return DensePagedDecoder(self, batch, max_len, comm, group)
+        return DenseCachedDecoder(self, batch, max_len, comm)
 
 
 class DenseCachedDecoder:
@@ -382,6 +397,93 @@ class DenseCachedDecoder:
         pos = self.kv_len[:, None].long()
         for i, layer in enumerate(m.layers):
             h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos)
+        self.kv_len += 1
+        h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
+        return ops.lora_linear(h, m.head_weight(), None, None).float()
+
+
+class DensePagedDecoder(DenseCachedDecoder):
+    """Paged twin of ``DenseCachedDecoder`` for grouped rollouts.
+
+    K/V live in a per-layer pool ``[n_pages, PAGE, Hkv, D]`` addressed through one block table
+    ``[B, max_pages]`` shared by all layers.  The full pages of a prompt are stored once and
+    referenced by all ``group`` rows of that prompt, so decode attention reads them from HBM once
+    per group (the other rows hit L2) and prefill needs no per-row copy of the prompt; the
+    prompt's ragged tail and everything generated go to row-private pages.  The reference keeps
+    one contiguous cache per row (``crates/ferrl/src/dense.rs`` cached decoder)."""
+
+    PAGE = 64
+
+    def __init__(self, model: DenseGradModel, batch: int, max_len: int, comm: Comm, group: int):
+        self.m, self.comm = model, comm
+        spec = model.spec
+        if max_len > spec.max_position_embeddings:
+            raise ValueError("cache longer than the RoPE table")
+        if batch % group:
+            raise ValueError("batch must be a multiple of the group size")
+        dev, dt = model.embed.device, model.dtype
+        hkv, D, page = model.layers[0].hkv, spec.head_dim, self.PAGE
+        self.group, self.batch, self.max_len = group, batch, max_len
+        self.prompts = batch // group
+        self.pages_per_row = (max_len + page - 1) // page
+        self.shared_pages = self.prompts * self.pages_per_row          # upper bound: a prompt as long as the cache
+        n_pages = self.shared_pages + batch * self.pages_per_row
+        self.k = [torch.zeros(n_pages, page, hkv, D, dtype=dt, device=dev) for _ in model.layers]
+        self.v = [torch.zeros(n_pages, page, hkv, D, dtype=dt, device=dev) for _ in model.layers]
+        self.table = torch.zeros(batch, self.pages_per_row, dtype=torch.int32, device=dev)
+        self.kv_len = torch.zeros(batch, dtype=torch.int32, device=dev)
+
+    @torch.no_grad()
+    def prefill(self, ids: torch.Tensor, lens: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Prefill the ``P = batch // group`` prompts; afterwards every row ``p*group + g`` sees its
+        prompt (``broadcast_groups`` has nothing left to copy)."""
+        if rows is not None:
+            raise ValueError("the paged decoder prefills all prompts at once")
+        m, page, G = self.m, self.PAGE, self.group
+        P, L = ids.shape
+        if P != self.prompts:
+            raise ValueError(f"expected {self.prompts} prompts, got {P}")
+        dev = ids.device
+        hkv, D = self.k[0].shape[2], self.k[0].shape[3]
+        tmp = [(torch.empty(P, L, hkv, D, dtype=m.dtype, device=dev), torch.empty(P, L, hkv, D, dtype=m.dtype, device=dev))
+               for _ in m.layers]
+        h = m.forward_hidden(ids, self.comm, merged=True, kv_out=tmp, detached=True)
+        ppr = self.pages_per_row
+        full = (lens // page).to(torch.int64)                                  # shared (full) pages per prompt
+        # block table: shared page ids first, then the row's private pages
+        j = torch.arange(ppr, device=dev)[None, :]
+        p_of_row = torch.arange(P, device=dev).repeat_interleave(G)
+        full_r = full[p_of_row][:, None]
+        shared_id = p_of_row[:, None] * ppr + j
+        private_id = self.shared_pages + torch.arange(self.batch, device=dev)[:, None] * ppr + (j - full_r).clamp(min=0)
+        self.table.copy_(torch.where(j < full_r, shared_id, private_id).to(torch.int32))
+        # tail of every prompt (< PAGE tokens) goes to the first private page of each of its rows
+        tail_idx = (full[:, None] * page + torch.arange(page, device=dev)[None, :]).clamp(max=L - 1)     # [P, PAGE]
+        first_private = (self.shared_pages + torch.arange(self.batch, device=dev) * ppr).long()
+        Lp = min(L, ppr * page)
+        for i in range(len(m.layers)):
+            for pool, src in ((self.k[i], tmp[i][0]), (self.v[i], tmp[i][1])):
+                pool[:self.shared_pages].view(P, ppr * page, hkv, D)[:, :Lp] = src[:, :Lp]
+                tail = torch.gather(src, 1, tail_idx[:, :, None, None].expand(P, page, hkv, D))
+                pool[first_private] = tail.repeat_interleave(G, dim=0)
+        self.kv_len.copy_(lens.to(torch.int32).repeat_interleave(G))
+        last = h[torch.arange(P, device=dev), (lens - 1).long()]
+        last = ops.rmsnorm(last, m.final_norm, m.spec.rms_norm_eps)
+        return ops.lora_linear(last, m.head_weight(), None, None).float()
+
+    @torch.no_grad()
+    def broadcast_groups(self, group: int):
+        if group != self.group:
+            raise ValueError("group size differs from the one this cache was built for")
+
+    @torch.no_grad()
+    def decode(self, tokens: torch.Tensor) -> torch.Tensor:
+        m = self.m
+        h = ops.embedding(tokens, m.embed)
+        kv_next = self.kv_len + 1
+        pos = self.kv_len[:, None].long()
+        for i, layer in enumerate(m.layers):
+            h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos, self.table)
         self.kv_len += 1
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
         return ops.lora_linear(h, m.head_weight(), None, None).float()

@@ -307,13 +307,24 @@ def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None)
     return _Flash.apply(_packed(q), _packed(k), _packed(v), float(scale), bool(causal), int(window or 0), int(q_offset))
 
 
-def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0):
+def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0, block_table=None):
     """``variant`` 0 picks the tensor-core pipelined kernel where it applies, 2 the scalar pipelined
     one, 1 the register-resident one (both kept for uncovered head shapes and as cross-checks)."""
     if not _bf16(q) or q.shape[-1] % 8 or q.shape[-1] > 256:
         return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
+    if block_table is not None:
+        # paged pool [n_pages, page, Hkv, D]; row b's token t is in page block_table[b, t // page]
+        return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),
+                                 int(n_splits) or 1, block_table, k_cache.shape[1], int(variant))
     return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),
                              int(n_splits), None, 0, int(variant))
+
+
+def kv_append_paged(k_pool, v_pool, k, v, kv_len, table):
+    """Paged form of ``kv_append``: pools ``[n_pages, page, Hkv, D]``, ``table`` ``[B, max_pages]`` int32."""
+    B = k.shape[0]
+    lib().kv_append_paged(k.reshape(B, -1), v.reshape(B, -1) if v.is_contiguous() else v.as_strided(
+        (B, v.shape[-2] * v.shape[-1]), (v.stride(0), 1), v.storage_offset()), k_pool, v_pool, kv_len, table)
 
 
 def kv_append(k_cache, v_cache, k, v, kv_len):

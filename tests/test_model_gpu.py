@@ -101,3 +101,31 @@ def test_trainer_step_on_gpu():
     assert any(not torch.equal(a, b.detach()) for a, b in zip(before, tr.params))
     from ferrl_b200.ops import cuda as C
     assert C.launches() > 0 and C.kernel_status() == 0
+
+
+@pytest.mark.parametrize("lens", [[5, 64, 70, 129], [1, 1, 1, 1], [200, 63, 128, 65]])
+def test_paged_decoder_with_shared_prompt_pages_matches_contiguous(lens):
+    """Grouped rollout through the paged cache (prompt pages stored once per group, block table,
+    paged append and paged decode attention) must give the logits of the contiguous cache."""
+    _need_gpu()
+    _, gpu = _models()
+    gpu.merge_adapters()
+    P, G, steps = len(lens), 3, 5
+    L = max(lens)
+    gen = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, 1024, (P, L), generator=gen).cuda()
+    lens_t = torch.tensor(lens).cuda()
+    with torch.no_grad():
+        a = gpu.new_decoder(P * G, 256, group=G, paged=False)
+        b = gpu.new_decoder(P * G, 256, group=G, paged=True)
+        la = a.prefill(ids, lens_t)
+        a.broadcast_groups(G)
+        lb = b.prefill(ids, lens_t)
+        b.broadcast_groups(G)
+        assert torch.equal(la, lb)
+        assert torch.equal(a.kv_len, b.kv_len)
+        tok = torch.randint(0, 1024, (steps, P * G), generator=gen).cuda()
+        for s in range(steps):
+            xa, xb = a.decode(tok[s]), b.decode(tok[s])
+            assert float((xa - xb).abs().max()) <= 2e-2 * float(xa.abs().max()), s
+    assert b.cache_bytes() > 0
