@@ -142,7 +142,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=2)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch-baseline"],
+                    help="torch-baseline: the same trainer on PyTorch library kernels (eager ops, no CUDA graph, "
+                         "per-tensor NCCL all-reduce) - a stand-in for the reference's execution shape")
     ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "bringup"])
     ap.add_argument("--prompts", type=int, default=16)
     ap.add_argument("--group", type=int, default=8)
@@ -163,6 +165,14 @@ def main():
     import torch
     from ferrl_b200.comm import SoloComm, TorchDistComm
     from ferrl_b200.ops import cuda as C
+    if args.impl == "torch-baseline":
+        from ferrl_b200 import ops as _ops
+        _ops.use_library_kernels(True)
+        args.no_graph = True
+        args.nccl_baseline = True
+        # unfused attention keeps [rows, heads, S, S] fp32 scores: recompute per layer and take small micro-batches
+        args.remat = 1
+        args.microbatch = min(args.microbatch, 2)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:
@@ -236,7 +246,7 @@ def main():
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
             "data": "synthetic prompts (uniform random token ids), random-init weights, Bernoulli(0.5) rewards",
-            "impl": "ours",
+            "impl": args.impl,
             "config": {"model": "Qwen3-8B (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)" if args.model == "qwen3-8b"
                        else "bringup (NOT the named config)",
                        "global_batch": args.prompts * args.group * comm.world_size, "prompts_per_rank": args.prompts,

@@ -692,14 +692,20 @@ void fill_flash(ferrl::FlashArgs& a, const Tensor& q, const Tensor& k, const Ten
   a.scale = scale; a.causal = causal; a.window = window; a.q_offset = q_offset;
 }
 
+// variant: 0 = tcgen05 kernel where it applies (causal self-attention, head_dim 128), 1 = warp-level kernel
 std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
-                                     int64_t window, int64_t q_offset) {
+                                     int64_t window, int64_t q_offset, int64_t variant) {
   c10::cuda::CUDAGuard guard(q.device());
   ferrl::FlashArgs a{};
   fill_flash(a, q, k, v, scale, causal, window, q_offset);
   Tensor o = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
   Tensor lse = at::empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
+  if (variant == 0 && ferrl::flash_fwd_tc_supported(a)) {
+    Tensor vt = at::empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
+    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream()));
+    return {o, lse};
+  }
   FERRL_CHECK(ferrl::flash_fwd(a, stream()));
   return {o, lse};
 }
@@ -899,7 +905,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
-  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor)", &flash_fwd);
+  m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);

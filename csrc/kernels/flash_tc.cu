@@ -1,0 +1,346 @@
+// Causal flash-attention forward on the 5th-generation tensor cores (head_dim 128).
+//
+// One CTA owns 128 query rows of one head and walks the key/value sequence in tiles of 128 keys:
+//
+//   warp 0      TMA producer: Q once, then K tiles [128 keys x 128 dims] and V^T tiles
+//               [128 dims x 128 keys] into two-deep rings (128B swizzle, no cluster multicast)
+//   warp 1      one thread issues tcgen05.mma: S = Q K^T into a double-buffered TMEM accumulator
+//               (tile j+1's scores are computed while tile j's softmax runs), then O_j = P V
+//   warps 2-5   softmax: each thread owns one query row, reads its scores with tcgen05.ld (row max
+//               and row sum need no shuffles), writes P as bf16 into shared memory in the swizzled
+//               K-major layout the MMA reads, rescales its fp32 output row while the P V MMA runs,
+//               and adds the tile's P V from TMEM
+//
+// V is transposed once per call by a small kernel so that both MMAs read K-major operands written
+// by TMA.  The warp-level kernel in flash_attn.cu (mma.sync) reaches ~13 % of the measured bf16
+// peak on these shapes; it stays as the path for other head dims, windows and offsets, and its
+// backward consumes the log-sum-exp this kernel writes.  Reference: candle's flash-attn binding /
+// eager GQA attention (crates/ferrl/src/dense.rs attention path).
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../api.h"
+#include "../common.cuh"
+#include "../gemm/tc_common.cuh"
+
+namespace ferrl {
+namespace {
+
+using namespace tc;
+
+constexpr int FD = 128;                 // head dim
+constexpr int FT = 128;                 // query rows per CTA and keys per tile
+constexpr int ATOM = FT * 64 * 2;       // one [128 rows x 64 cols] swizzle atom: 16 KB
+constexpr int TILE = 2 * ATOM;          // [128 x 128] bf16 tile: 32 KB
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct FlashTcParams {
+  __nv_bfloat16* out; long long o_bs, o_ts;
+  float* lse;                           // [B, Hq, S] or null
+  int B, S, Hq, Hkv;
+  float scale;
+  int* status;
+};
+
+// vt[(b, hk, d), s] = v[b, s, hk, d]; zero for s in [S, S_pad)
+__global__ void transpose_v_kernel(const __nv_bfloat16* __restrict__ v, long long v_bs, long long v_ts,
+                                   __nv_bfloat16* __restrict__ vt, int S, int S_pad, int Hkv) {
+  __shared__ __nv_bfloat16 tile[64][FD + 2];
+  const int s0 = blockIdx.x * 64, hk = blockIdx.y, b = blockIdx.z;
+  for (int i = threadIdx.x; i < 64 * (FD / 2); i += blockDim.x) {
+    const int r = i / (FD / 2), c2 = i % (FD / 2);
+    __nv_bfloat162 val = __floats2bfloat162_rn(0.f, 0.f);
+    if (s0 + r < S) val = *reinterpret_cast<const __nv_bfloat162*>(v + b * v_bs + static_cast<long long>(s0 + r) * v_ts + hk * FD + 2 * c2);
+    tile[r][2 * c2] = val.x;
+    tile[r][2 * c2 + 1] = val.y;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < FD * 32; i += blockDim.x) {
+    const int d = i / 32, r2 = i % 32;
+    __nv_bfloat162 val;
+    val.x = tile[2 * r2][d];
+    val.y = tile[2 * r2 + 1][d];
+    *reinterpret_cast<__nv_bfloat162*>(vt + (static_cast<long long>(b) * Hkv + hk) * FD * S_pad + static_cast<long long>(d) * S_pad + s0 + 2 * r2) = val;
+  }
+}
+
+__global__ void __launch_bounds__(192, 1)
+flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmVt, FlashTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                    // 32 KB
+  uint8_t* sK = sQ + TILE;               // 2 x 32 KB
+  uint8_t* sV = sK + 2 * TILE;           // 2 x 32 KB
+  uint8_t* sP = sV + 2 * TILE;           // 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + TILE);
+  uint64_t* q_full = bars;               // [1]
+  uint64_t* k_full = bars + 1;           // [2]
+  uint64_t* k_empty = bars + 3;          // [2]
+  uint64_t* v_full = bars + 5;           // [2]
+  uint64_t* v_empty = bars + 7;          // [2]
+  uint64_t* s_full = bars + 9;           // [2]
+  uint64_t* s_empty = bars + 11;         // [2]
+  uint64_t* p_full = bars + 13;          // [1]
+  uint64_t* pv_full = bars + 14;         // [1]
+  uint64_t* pv_empty = bars + 15;        // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.S + FT - 1) / FT;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);     // longest rows first
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int hk = hq / (p.Hq / p.Hkv);
+  const int q0 = qt * FT;
+  const int n_kv = qt + 1;                                    // causal: tiles 0..qt
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    mbar_init(p_full, 4);
+    mbar_init(pv_full, 1);
+    mbar_init(pv_empty, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tPV = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      mbar_expect_tx(q_full, TILE);
+      tma_load_2d(sQ, &tmQ, q_full, hq * FD, b * p.S + q0);
+      tma_load_2d(sQ + ATOM, &tmQ, q_full, hq * FD + 64, b * p.S + q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_expect_tx(&k_full[st], TILE);
+        tma_load_2d(sK + st * TILE, &tmK, &k_full[st], hk * FD, b * p.S + j * FT);
+        tma_load_2d(sK + st * TILE + ATOM, &tmK, &k_full[st], hk * FD + 64, b * p.S + j * FT);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_expect_tx(&v_full[st], TILE);
+        tma_load_2d(sV + st * TILE, &tmVt, &v_full[st], j * FT, (b * p.Hkv + hk) * FD);
+        tma_load_2d(sV + st * TILE + ATOM, &tmVt, &v_full[st], j * FT + 64, (b * p.Hkv + hk) * FD);
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);   // let copies in flight land before shared memory goes away
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE);
+#pragma unroll
+        for (int ks = 0; ks < FD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * ATOM;
+          umma(tS[st], make_smem_desc(qa + off) + 2 * (ks & 3), make_smem_desc(ka + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusWaitTimeoutMma);
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(p_full, j & 1, abort_flag, p.status, kStatusWaitTimeoutMma) ||
+            !mbar_wait(&v_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma) ||
+            !mbar_wait(pv_empty, (j & 1) ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * TILE);
+#pragma unroll
+        for (int ks = 0; ks < FT / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * ATOM;
+          umma(tPV, make_smem_desc(pa + off) + 2 * (ks & 3), make_smem_desc(va + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(pv_full);
+        umma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- softmax + output (one row per thread)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                  // row inside the tile == TMEM lane
+    const int row = q0 + r;                       // query position
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const float c = p.scale * kLog2e;
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[FD];
+#pragma unroll
+    for (int i = 0; i < FD; ++i) o[i] = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * FT;
+      const int limit = min(p.S, (j == qt) ? row + 1 : p.S) - k0;     // keys [0, limit) of this tile are visible
+      // pass 1: row maximum
+      float mx = m_run;
+#pragma unroll 1
+      for (int cc = 0; cc < FT; cc += 32) {
+        uint32_t v[32];
+        tmem_ld32(tS[st] + lane_sel + cc, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e)
+          if (cc + e < limit) mx = fmaxf(mx, __uint_as_float(v[e]));
+      }
+      const float corr = (m_run == -INFINITY) ? 0.f : exp2f((m_run - mx) * c);
+      const float mc = (mx == -INFINITY) ? 0.f : mx * c;
+      // pass 2: probabilities -> bf16 -> swizzled K-major tile; row sum
+      float ps = 0.f;
+#pragma unroll 1
+      for (int cc = 0; cc < FT; cc += 32) {
+        uint32_t v[32];
+        tmem_ld32(tS[st] + lane_sel + cc, v);
+        tmem_ld_wait();
+        float pr[32];
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          pr[e] = (cc + e < limit) ? exp2f(__uint_as_float(v[e]) * c - mc) : 0.f;
+          ps += pr[e];
+        }
+        uint8_t* dst = sP + (cc >> 6) * ATOM + r * 128;
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 w;
+          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) wh[e] = __floats2bfloat162_rn(pr[ch * 8 + 2 * e], pr[ch * 8 + 2 * e + 1]);
+          const int chunk = ((cc & 63) >> 3) + ch;
+          *reinterpret_cast<uint4*>(dst + ((chunk ^ (r & 7)) << 4)) = w;
+        }
+      }
+      // scores of this buffer are consumed; P is written
+      tc_fence_before();
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(&s_empty[st]);
+        mbar_arrive(p_full);
+      }
+      l_run = l_run * corr + ps;
+      m_run = mx;
+      // rescale the running output while the tensor cores compute P V
+#pragma unroll
+      for (int i = 0; i < FD; ++i) o[i] *= corr;
+      if (!mbar_wait(pv_full, j & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      tc_fence_after();
+#pragma unroll
+      for (int cc = 0; cc < FD; cc += 32) {
+        uint32_t v[32];
+        tmem_ld32(tPV + lane_sel + cc, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[cc + e] += __uint_as_float(v[e]);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pv_empty);
+    }
+    if (ok && row < p.S) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = p.out + b * p.o_bs + static_cast<long long>(row) * p.o_ts + hq * FD;
+#pragma unroll
+      for (int ch = 0; ch < FD / 8; ++ch) {
+        uint4 w;
+        __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) wh[e] = __floats2bfloat162_rn(o[ch * 8 + 2 * e] * inv, o[ch * 8 + 2 * e + 1] * inv);
+        reinterpret_cast<uint4*>(orow)[ch] = w;
+      }
+      if (p.lse)
+        p.lse[(static_cast<long long>(b) * p.Hq + hq) * p.S + row] = (l_run > 0.f) ? m_run * p.scale + logf(l_run) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
+}  // namespace
+
+bool flash_fwd_tc_supported(const FlashArgs& a) {
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  return a.D == FD && a.causal && a.window == 0 && a.q_offset == 0 && a.Sq == a.Sk && a.Sq >= 1 && a.Hq % a.Hkv == 0 &&
+         a.q_bs == static_cast<long long>(a.Sq) * a.q_ts && a.k_bs == static_cast<long long>(a.Sk) * a.k_ts &&
+         (a.q_ts % 8) == 0 && (a.k_ts % 8) == 0 && (a.v_ts % 2) == 0 && (a.v_bs % 2) == 0 && (a.o_ts % 8) == 0 &&
+         (a.o_bs % 8) == 0 && al16(a.q) && al16(a.k) && al16(a.o) && (reinterpret_cast<uintptr_t>(a.v) & 3) == 0;
+}
+
+size_t flash_fwd_tc_workspace_elems(const FlashArgs& a) {
+  const long long s_pad = (a.Sk + 63) / 64 * 64;
+  return static_cast<size_t>(a.B) * a.Hkv * FD * s_pad;
+}
+
+// `vt_ws`: bf16 workspace of flash_fwd_tc_workspace_elems(a) elements, 16-byte aligned
+const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream) {
+  if (!flash_fwd_tc_supported(a)) return "flash_fwd_tc: unsupported arguments";
+  if (a.B == 0) return nullptr;
+  const int s_pad = (a.Sk + 63) / 64 * 64;
+  transpose_v_kernel<<<dim3(s_pad / 64, a.Hkv, a.B), 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(a.v), a.v_bs, a.v_ts,
+                                                                     static_cast<__nv_bfloat16*>(vt_ws), a.Sk, s_pad, a.Hkv);
+  count_launch();
+  CUtensorMap tmQ, tmK, tmVt;
+  if (!make_map_2d(&tmQ, a.q, static_cast<long long>(a.B) * a.Sq, static_cast<long long>(a.Hq) * FD, a.q_ts, FT))
+    return "flash_fwd_tc: tensor map for Q failed";
+  if (!make_map_2d(&tmK, a.k, static_cast<long long>(a.B) * a.Sk, static_cast<long long>(a.Hkv) * FD, a.k_ts, FT))
+    return "flash_fwd_tc: tensor map for K failed";
+  if (!make_map_2d(&tmVt, vt_ws, static_cast<long long>(a.B) * a.Hkv * FD, s_pad, s_pad, FT))
+    return "flash_fwd_tc: tensor map for V^T failed";
+  FlashTcParams p{};
+  p.out = static_cast<__nv_bfloat16*>(a.o); p.o_bs = a.o_bs; p.o_ts = a.o_ts; p.lse = a.lse;
+  p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status;
+  constexpr int smem = 6 * TILE + 1024 + 256;
+  static bool set = false;
+  if (!set) {
+    if (cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return "flash_fwd_tc: cannot reserve shared memory";
+    set = true;
+  }
+  dim3 grid((a.Sq + FT - 1) / FT, a.Hq, a.B);
+  flash_fwd_tc_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmVt, p);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "flash_fwd_tc launch failed";
+}
+
+}  // namespace ferrl

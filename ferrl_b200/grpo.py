@@ -291,7 +291,8 @@ def grpo_loss_eager(logp: torch.Tensor, logp_old: torch.Tensor, logp_ref: Option
 
 def grpo_loss(logp, logp_old, logp_ref, advantages, mask, cfg: LossConfig, tis_w=None) -> torch.Tensor:
     """Loss entry point used by the trainer: fused kernel on CUDA, eager on CPU."""
-    if logp.is_cuda:
+    from . import ops as _ops
+    if _ops.native(logp):
         from .ops import grpo_loss_fused
         return grpo_loss_fused(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w)
     return grpo_loss_eager(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w)

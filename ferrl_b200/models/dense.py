@@ -166,7 +166,7 @@ class DenseLayer(nn.Module):
 
 def ops_cache_write(k_cache, v_cache, k, v, kv_len):
     """Write one token's K/V per row at that row's current length."""
-    if k.is_cuda and k.dtype == torch.bfloat16:
+    if ops.native(k) and k.dtype == torch.bfloat16:
         from ..ops import cuda as _c
         _c.kv_append(k_cache, v_cache, k.contiguous(), v, kv_len)
         return
@@ -329,7 +329,7 @@ class DenseGradModel(nn.Module):
         ``group`` rows of a prompt (rows are prompt-major: row ``p*group + g``)."""
         comm = comm or SoloComm()
         if paged is None:
-            paged = (self.embed.is_cuda and self.dtype == torch.bfloat16 and group > 1 and batch % group == 0
+            paged = (ops.native(self.embed) and self.dtype == torch.bfloat16 and group > 1 and batch % group == 0
                      and self.spec.head_dim % 8 == 0)
         if paged:
             return DensePagedDecoder(self, batch, max_len, comm, group)

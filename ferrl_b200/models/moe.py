@@ -23,6 +23,11 @@ import torch
 import torch.nn.functional as F
 
 
+def ops_native(t):
+    from .. import ops
+    return ops.native(t)
+
+
 def topk_router(x: torch.Tensor, weight: torch.Tensor, top_k: int, renorm: bool = True):
     """``x`` ``[T, H]``, router ``weight`` ``[E, H]`` -> ``(probs [T,E] f32, scores [T,k] f32, indices [T,k])``."""
     logits = F.linear(x, weight)
@@ -102,7 +107,7 @@ def sparse_moe_block(x: torch.Tensor, router_w, gate_up, down, top_k: int, share
     ``sigmoid(x @ shared_gate_w^T)``."""
     shape = x.shape
     x2 = x.reshape(-1, shape[-1])
-    y = _device_moe(x2, router_w, gate_up, down, top_k, act) if x2.is_cuda else None
+    y = _device_moe(x2, router_w, gate_up, down, top_k, act) if ops_native(x2) else None
     if y is None:
         _, scores, idx = topk_router(x2, router_w, top_k)
         y = moe_experts(x2, idx, scores.to(x2.dtype), gate_up, down, act)

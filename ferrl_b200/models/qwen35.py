@@ -244,7 +244,7 @@ class Qwen35Layer(nn.Module):
         p = f(self.inp, x)
         mixed, z, b, a = p.split([self.conv_dim, self.value_dim, self.vh, self.vh], dim=-1)
         left = None if state is None else state[0]
-        fast = (x.is_cuda and mixed.dtype == torch.bfloat16 and not self.conv_w.requires_grad
+        fast = (ops.native(x) and mixed.dtype == torch.bfloat16 and not self.conv_w.requires_grad
                 and self.kd in (16, 32, 64, 128))
         if fast and decode and state is not None and S_ == 1 and state[0].dtype == torch.bfloat16 \
                 and state[1].dtype == torch.float32 and state[0].is_contiguous() and state[1].is_contiguous():

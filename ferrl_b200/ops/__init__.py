@@ -22,8 +22,24 @@ def _cuda():
     return _c
 
 
+_LIBRARY_BASELINE = False
+
+
+def use_library_kernels(flag: bool) -> None:
+    """Benchmark baseline switch: when set, CUDA tensors run the eager restatements in
+    ``ops.eager`` (PyTorch library kernels: cuBLAS GEMMs, unfused attention and norms) instead of
+    this package's kernels.  Never set implicitly; the product path leaves it off."""
+    global _LIBRARY_BASELINE
+    _LIBRARY_BASELINE = bool(flag)
+
+
+def native(*ts) -> bool:
+    """True when the hand-written kernels should handle these tensors."""
+    return not _LIBRARY_BASELINE and any(t is not None and t.is_cuda for t in ts)
+
+
 def _on_gpu(*ts) -> bool:
-    return any(t is not None and t.is_cuda for t in ts)
+    return native(*ts)
 
 
 def rmsnorm(x, weight, eps, zero_centered=False):
@@ -107,6 +123,6 @@ def grpo_loss_fused(logp, logp_old, logp_ref, advantages, mask, cfg, tis_w=None)
 
 
 def adamw_step(params, grads, m, v, **kw):
-    if params and params[0].is_cuda:
+    if params and native(params[0]):
         return _cuda().adamw_step(params, grads, m, v, **kw)
     return eager.adamw_step(params, grads, m, v, **kw)

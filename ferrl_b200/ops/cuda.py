@@ -284,8 +284,8 @@ def qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered=False):
 # ------------------------------------------------------------- attention
 class _Flash(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, q, k, v, scale, causal, window, q_offset):
-        o, lse = lib().flash_fwd(q, k, v, scale, causal, window, q_offset)
+    def forward(ctx, q, k, v, scale, causal, window, q_offset, variant=0):
+        o, lse = lib().flash_fwd(q, k, v, scale, causal, window, q_offset, variant)
         ctx.save_for_backward(q, k, v, o, lse)
         ctx.meta = (scale, causal, window, q_offset)
         return o
@@ -294,17 +294,20 @@ class _Flash(torch.autograd.Function):
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
         dq, dk, dv = lib().flash_bwd(q, k, v, o, lse, do.contiguous(), *ctx.meta)
-        return dq, dk, dv, None, None, None, None
+        return dq, dk, dv, None, None, None, None, None
 
 
 def _packed(t):
     return t if (t.stride(3) == 1 and t.stride(2) == t.shape[3]) else t.contiguous()
 
 
-def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None):
+def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None, variant=0):
+    """Flash attention.  Causal self-attention with head_dim 128 runs the tcgen05 forward
+    (``csrc/kernels/flash_tc.cu``); ``variant=1`` forces the warp-level kernel everywhere."""
     if not _bf16(q) or q.shape[-1] not in (64, 128, 256) or kv_len is not None:
         return eager.attention(q, k, v, scale=scale, causal=causal, window=window, q_offset=q_offset, kv_len=kv_len)
-    return _Flash.apply(_packed(q), _packed(k), _packed(v), float(scale), bool(causal), int(window or 0), int(q_offset))
+    return _Flash.apply(_packed(q), _packed(k), _packed(v), float(scale), bool(causal), int(window or 0), int(q_offset),
+                        int(variant))
 
 
 def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0, block_table=None):

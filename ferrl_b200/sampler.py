@@ -146,7 +146,8 @@ class GrpoSampler:
         t = self.temperature if temperature is None else validate_temperature(temperature)
         if isinstance(global_rows, int):
             global_rows = torch.arange(global_rows, global_rows + logits.shape[0])
-        if logits.is_cuda:
+        from . import ops as _ops
+        if _ops.native(logits):
             from .ops import sample_top_p
             return sample_top_p(logits, self.base_seed, global_rows.to(logits.device), draw, t,
                                 validate_top_p(top_p), draw_dev)

@@ -338,3 +338,31 @@ def test_lora_grad_matches_fp32(M, R, C):
         got = C_.lib().lora_grad(u, x)
         assert float((got - want).abs().max()) <= 2e-3 * float(want.abs().max()) + 1e-3
     assert torch.equal(got, C_.lib().lora_grad(u, x))
+
+
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 1, 2, 1), (2, 100, 4, 2), (1, 128, 2, 2), (2, 129, 8, 2), (1, 300, 4, 1),
+                                        (2, 1536, 8, 2)])
+def test_flash_forward_tcgen05(B, S, Hq, Hkv):
+    """Causal head-dim-128 forward on tcgen05 (TMA-fed Q K^T and P V with accumulators in TMEM)
+    against fp32 attention; the warp-level backward runs on the log-sum-exp it writes."""
+    from ferrl_b200.ops import cuda as C, eager as E
+    dev = _dev()
+    D = 128
+    g = torch.Generator(device=dev).manual_seed(B * 7 + S)
+    wide = torch.randn(B, S, (Hq + 2 * Hkv) * D, device=dev, generator=g).to(torch.bfloat16).requires_grad_(True)
+    q, k, v = wide.split([Hq * D, Hkv * D, Hkv * D], dim=-1)           # strided views, as the model passes them
+    q, k, v = q.reshape(B, S, Hq, D), k.reshape(B, S, Hkv, D), v.reshape(B, S, Hkv, D)
+    scale = 1 / math.sqrt(D)
+    o = C.attention(q, k, v, scale=scale, causal=True)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    o_warp = C.attention(q, k, v, scale=scale, causal=True, variant=1)
+    wf = wide.detach().float().requires_grad_(True)
+    qf, kf, vf = wf.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    ref = E.attention(qf.reshape(B, S, Hq, D), kf.reshape(B, S, Hkv, D), vf.reshape(B, S, Hkv, D), scale=scale, causal=True)
+    assert _rel(o, ref) < 2e-2
+    assert _rel(o, o_warp) < 2e-2
+    do = torch.randn_like(ref)
+    ref.backward(do)
+    o.backward(do.to(torch.bfloat16))
+    assert _rel(wide.grad, wf.grad) < 3e-2
