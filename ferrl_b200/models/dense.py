@@ -149,11 +149,22 @@ class DenseLayer(nn.Module):
         v = v.reshape(B, 1, self.hkv, self.D)
         q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin,
                                 pos if pos is not None else kv_len[:, None].long())
-        if table is not None:
+        if table is not None and ops.native(k_cache):
             from ..ops import cuda as _c
             _c.kv_append_paged(k_cache, v_cache, k[:, 0].contiguous(), v[:, 0], kv_len, table)
             a = _c.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
                                     scale=self.scale, block_table=table)
+        elif table is not None:
+            # eager restatement of the paged path (CPU tests of the block-table logic)
+            page = k_cache.shape[1]
+            t = kv_len.long()
+            rows = torch.arange(B, device=h.device)
+            slot_page = table[rows, t // page].long()
+            k_cache[slot_page, t % page] = k[:, 0]
+            v_cache[slot_page, t % page] = v[:, 0]
+            kc = k_cache[table.long()].reshape(B, -1, self.hkv, self.D)       # [B, max_pages*page, Hkv, D]
+            vc = v_cache[table.long()].reshape(B, -1, self.hkv, self.D)
+            a = ops.decode_attention(q[:, 0], kc, vc, kv_next if kv_next is not None else kv_len + 1, scale=self.scale)
         else:
             ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
             a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,

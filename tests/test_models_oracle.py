@@ -171,3 +171,35 @@ def test_remat_gradients_equal_plain():
         m(ids).pow(2).mean().backward()
     for p, q in zip(a.trainable_params(), b.trainable_params()):
         assert torch.allclose(p.grad, q.grad, atol=1e-6)
+
+
+def test_paged_decoder_block_table_matches_contiguous_cache():
+    """Block-table logic of the paged cache (shared full prompt pages, private tail and generated
+    pages) on CPU: logits equal the contiguous cache's for ragged prompts over several steps."""
+    import torch
+    from ferrl_b200.models import DenseGradModel, DenseSpec, LoraSpec
+    spec = DenseSpec(vocab_size=64, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=8, intermediate_size=64, max_position_embeddings=512)
+    m = DenseGradModel(spec, LoraSpec(4, 8.0), dtype=torch.float32)
+    m.init_random(3, 0.3)
+    m.merge_adapters()
+    lens = [5, 64, 70, 129, 1]
+    P, G, steps = len(lens), 3, 4
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 64, (P, max(lens)), generator=g)
+    lens_t = torch.tensor(lens)
+    with torch.no_grad():
+        a = m.new_decoder(P * G, 256, group=G, paged=False)
+        b = m.new_decoder(P * G, 256, group=G, paged=True)
+        la = a.prefill(ids, lens_t)
+        a.broadcast_groups(G)
+        lb = b.prefill(ids, lens_t)
+        b.broadcast_groups(G)
+        assert torch.allclose(la, lb)
+        tok = torch.randint(0, 64, (steps, P * G), generator=g)
+        for s in range(steps):
+            xa, xb = a.decode(tok[s]), b.decode(tok[s])
+            assert torch.allclose(xa, xb, atol=1e-5), s
+    # rows of one prompt share its full pages and nothing else
+    t = b.table
+    assert torch.equal(t[3 * G, :2], t[3 * G + 1, :2]) and t[3 * G, 2] != t[3 * G + 1, 2]
