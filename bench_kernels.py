@@ -81,6 +81,9 @@ def profile_case(name, C):
     elif name == "flash":
         q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
         fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True)
+    elif name == "flash_warp":
+        q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+        fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=1)
     elif name == "rmsnorm":
         x, r, w = rnd(24576, 4096), rnd(24576, 4096), torch.ones(4096, device=dev, dtype=bf)
         fn = lambda: C.add_rmsnorm(x, r, w, 1e-6)
@@ -173,7 +176,11 @@ def main():
                 s = T(lambda: C.gemm(a, b, force_bn=bn))
                 report(f"gemm {name} M{M} N{N} K{K} bn{bn or 'auto'}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
             if M <= 128:
-                for bn, cl in ((128, 2), (128, 4), (128, 8), (256, 2), (64, 4)):
+                s = T(lambda: C.gemm(a, b, stream_k=1))
+                report(f"gemm {name} stream-k", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+                s = T(lambda: C.gemm(a, b, stream_k=-1))
+                report(f"gemm {name} planner without stream-k", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+                for bn, cl in ((128, 2), (128, 4)):
                     s = T(lambda: C.gemm(a, b, force_bn=bn, cluster_k=cl))
                     report(f"gemm {name} cluster split-k bn{bn} x{cl}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
             else:
@@ -197,7 +204,10 @@ def main():
         fl = 4 * B * HQ * S * S * D / 2
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True))
-        report(f"flash fwd B{B} S{S} causal", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        report(f"flash fwd B{B} S{S} causal (tcgen05)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        with torch.no_grad():
+            s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=1))
+        report(f"flash fwd B{B} S{S} causal (warp-level mma.sync)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         o = C.attention(q, k, v, scale=D ** -0.5, causal=True)
         do = torch.randn_like(o)
         s = T(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))

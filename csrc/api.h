@@ -29,6 +29,8 @@ struct GemmArgs {
   int two_cta; unsigned int* debug;
   // cluster split-k kernel (decode shapes): cluster_k CTAs share one 128 x force_bn tile; 0/1 = off
   int cluster_k;
+  // stream-k kernel (decode shapes, M <= 128): equal unit ranges per SM, partial tiles fixed up through `sk_ws`
+  int stream_k; float* sk_ws; unsigned int* sk_flags; int sk_max_ctas;
   // grouped mode: B is [n_experts * N, K]; tile_expert[m tile] = expert (or -1: skip the tile)
   const int* tile_expert; int n_experts;
   // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu
@@ -36,7 +38,8 @@ struct GemmArgs {
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
   PeerTable ar_stage, ar_outbuf, ar_flags;
 };
-void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out);
+void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out,
+               double* est_out = nullptr);
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 int gemm_pick_bn(int M, int N, int num_sms);
 

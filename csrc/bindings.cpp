@@ -72,7 +72,7 @@ void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(in
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
             const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split, int64_t two_cta,
-            const optional<Tensor>& debug, int64_t cluster_k) {
+            const optional<Tensor>& debug, int64_t cluster_k, int64_t stream_k) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
@@ -106,7 +106,36 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     return out;
   }
   int bn = 0, split = 1, cluster = 1;
-  ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split, &cluster);
+  double est = 1e30;
+  ferrl::gemm_plan(a.M, a.N, a.K, a.K2, a.num_sms, &bn, &split, &cluster, &est);
+  {
+    // stream-k: equal unit ranges per SM (csrc/gemm/tcgen05_gemm.cu); workspace and epochs live per device
+    const bool eligible = a.M <= 128 && a.N >= 256 && (a.N % 4) == 0;
+    bool use_sk = stream_k > 0 && eligible;
+    if (stream_k == 0 && eligible && force_bn == 0 && force_split == 0 && cluster_k == 0 && two_cta == 0) {
+      const long long kb = (a.K + 63) / 64 + (a.K2 + 63) / 64;
+      const long long units = ((a.N + 255) / 256) * kb;
+      const long long per = (units + a.num_sms - 1) / a.num_sms;
+      const double t_sk = static_cast<double>(per) * (128 + 256) * 128.0 / 64e9 + 10e-6;
+      use_sk = units >= a.num_sms && t_sk < est;
+    }
+    TORCH_CHECK(stream_k <= 0 || eligible, "gemm: stream_k needs M <= 128, N >= 256, N % 4 == 0");
+    if (use_sk) {
+      static std::vector<Tensor> sk_ws(64), sk_flags(64);
+      const int dev = A.get_device();
+      const int max_ctas = 160;
+      if (!sk_ws[dev].defined()) {
+        sk_ws[dev] = at::empty({static_cast<long long>(max_ctas) * 2 * 128 * 256}, A.options().dtype(at::kFloat));
+        sk_flags[dev] = at::zeros({max_ctas * 2 + 2}, A.options().dtype(at::kInt));   // flags, launch counter, done counter
+      }
+      a.stream_k = 1;
+      a.sk_ws = sk_ws[dev].data_ptr<float>();
+      a.sk_flags = reinterpret_cast<unsigned int*>(sk_flags[dev].data_ptr<int>());
+      a.sk_max_ctas = max_ctas;
+      FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+      return out;
+    }
+  }
   if (cluster_k > 1) {                      // forced cluster split: force_bn names the tile width
     TORCH_CHECK(force_bn > 0, "gemm: cluster_k needs force_bn");
     a.cluster_k = static_cast<int>(cluster_k);
@@ -873,7 +902,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);

@@ -1341,6 +1341,376 @@ const char* launch_ksplit_flags(const GemmArgs& a, cudaStream_t stream) {
   return a.residual ? launch_ksplit<BN, S, false, true>(a, stream) : launch_ksplit<BN, S, false, false>(a, stream);
 }
 
+// =============================================================================================
+// Stream-K variant for decode-shaped problems (one M tile): the n_tiles x k_blocks work units are
+// dealt out as equal contiguous ranges, one per SM, so every SM streams the same number of weight
+// bytes whatever N and K are; a range may start or end in the middle of a tile.
+//
+//   * whole tiles inside a range take the ordinary epilogue;
+//   * a partial tile's fp32 accumulator is published row-major to a per-CTA workspace slot with a
+//     release flag (the first and the last segment of a range can be partial: two slots per CTA);
+//   * after its main loop, every contributor of a split tile waits for the others' flags and
+//     finishes a band of ROWS of that tile: it adds the partials in k order (lower CTA index =
+//     earlier k range, so the order is fixed), adds the residual and writes the output.
+//
+// Publishing never waits, so the waits cannot deadlock; they are bounded like all others.  One
+// persistent launch pays the prologue once (the cluster split-k kernel pays it per wave) and the
+// fix-up traffic stays in L2.  BN = 256 keeps the activation share of the fill at one third.
+constexpr int SK_BN = 256;
+
+struct StreamKParams {
+  float* ws;                 // [grid][2][BM][SK_BN] fp32 partial tiles
+  uint32_t* flags;           // [max_ctas][2] epochs, then [epoch word][done counter]
+  uint32_t* epoch_ptr;       // device-resident launch counter: the kernel advances it itself, so a
+  uint32_t* done_ptr;        //   captured CUDA graph can replay the launch (a host-side epoch would be baked in)
+  long long units;           // n_tiles * kb_total
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <bool OUT_F32, bool HAS_RES>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p,
+                    StreamKParams sk) {
+  constexpr int BN = SK_BN;
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + C::STAGES;
+  uint64_t* acc_full = bars + 2 * C::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  uint64_t* epi_bar = acc_empty + 3;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kb1 = (p.K + BK - 1) / BK;
+  const int kb2 = (p.K2 + BK - 1) / BK;
+  const int kb_total = kb1 + kb2;
+  const int G = gridDim.x;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(sk.epoch_ptr) + 1;   // this launch's flag value
+  auto range_lo = [&](int cta) -> long long { return static_cast<long long>(cta) * sk.units / G; };
+  const long long u_lo = range_lo(blockIdx.x), u_hi = range_lo(blockIdx.x + 1);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 4);
+    }
+    mbar_init(epi_bar, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(C::TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (long long u = u_lo; u < u_hi && ok; ++u) {
+        const int ni = static_cast<int>(u / kb_total), kb = static_cast<int>(u % kb_total);
+        if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
+          ok = false;
+          break;
+        }
+        uint8_t* sa = smem + stage * C::STAGE_BYTES;
+        uint8_t* sb = sa + BM * BK * 2;
+        mbar_expect_tx(&full[stage], C::STAGE_BYTES);
+        if (kb < kb1) {
+          tma_load_2d(sa, &tmA, &full[stage], kb * BK, 0);
+          tma_load_2d(sb, &tmB, &full[stage], kb * BK, ni * BN);
+        } else {
+          tma_load_2d(sa, &tmA2, &full[stage], (kb - kb1) * BK, 0);
+          tma_load_2d(sb, &tmB2, &full[stage], (kb - kb1) * BK, ni * BN);
+        }
+        if (++stage == C::STAGES) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) {
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc(BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      long long u = u_lo;
+      while (u < u_hi && ok) {
+        const long long tile_end = (u / kb_total + 1) * kb_total;
+        const long long seg_end = tile_end < u_hi ? tile_end : u_hi;
+        const int acc = (it++) & 1;
+        if (!mbar_wait(&acc_empty[acc], acc_phase[acc] ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) break;
+        acc_phase[acc] ^= 1;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (long long uu = u; uu < seg_end; ++uu) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * C::STAGE_BYTES);
+          const uint32_t sb = sa + BM * BK * 2;
+          const uint64_t da = make_smem_desc(sa);
+          const uint64_t db = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) umma(d_tmem, da + 2 * k, db + 2 * k, idesc, (uu > u || k > 0) ? 1u : 0u);
+          umma_commit(&empty[stage]);
+          if (++stage == C::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (ok) umma_commit(&acc_full[acc]);
+        u = seg_end;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue warps
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    uint32_t epi_phase = 0;
+    auto epi_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(epi_bar);
+      const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, p.status, kStatusWaitTimeoutEpilogue);
+      epi_phase ^= 1;
+      return ok && !*abort_flag;
+    };
+    int split_tile[2] = {-1, -1};          // tiles this CTA holds a partial of (slot 0: first segment, slot 1: last)
+    bool live = true;
+    long long u = u_lo;
+    const int row = q * 32 + lane;         // single M tile: accumulator row == output row
+    const bool row_ok = row < p.M;
+    while (u < u_hi) {
+      const int ni = static_cast<int>(u / kb_total);
+      const long long tile_begin = static_cast<long long>(ni) * kb_total, tile_end = tile_begin + kb_total;
+      const long long seg_end = tile_end < u_hi ? tile_end : u_hi;
+      const bool whole = (u == tile_begin) && (seg_end == tile_end);
+      const int acc = (it++) & 1;
+      if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue)) {
+        live = false;
+        break;
+      }
+      acc_phase[acc] ^= 1;
+      tc_fence_after();
+      const int slot = (u == u_lo) ? 0 : 1;
+      if (!whole) split_tile[slot] = ni;
+      float* part = sk.ws + ((static_cast<long long>(blockIdx.x) * 2 + slot) * BM + row) * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c, r);
+        tmem_ld_wait();
+        if (!whole) {
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            reinterpret_cast<uint4*>(part + c)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+          continue;
+        }
+        const int col = ni * BN + c;
+        if (row_ok && col < p.N) {
+          const int ncols = min(32, p.N - col);
+          if (HAS_RES) {
+            const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
+            for (int e = 0; e < ncols; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) + __bfloat162float(rp[e]));
+          }
+          if (OUT_F32) {
+            float* op = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                reinterpret_cast<uint4*>(op)[v] = make_uint4(r[4 * v], r[4 * v + 1], r[4 * v + 2], r[4 * v + 3]);
+            } else {
+              for (int e = 0; e < ncols; ++e) op[e] = __uint_as_float(r[e]);
+            }
+          } else {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col;
+            if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                float f8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) f8[e] = __uint_as_float(r[v * 8 + e]);
+                reinterpret_cast<uint4*>(op)[v] = pack8(f8);
+              }
+            } else {
+              for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[acc]);
+      if (!whole) {
+        __threadfence();
+        if (!epi_sync()) {
+          live = false;
+          break;
+        }
+        if (et == 0) st_release_gpu(sk.flags + blockIdx.x * 2 + slot, epoch);
+      }
+      u = seg_end;
+    }
+    // ---- fix-up: finish a band of rows of every tile this CTA holds a partial of
+    for (int sl = 0; sl < 2 && live; ++sl) {
+      const int ni = split_tile[sl];
+      if (ni < 0 || (sl == 1 && split_tile[0] == ni)) continue;
+      const long long tb = static_cast<long long>(ni) * kb_total, te = tb + kb_total;
+      // contributors: CTAs whose range intersects [tb, te)
+      int c_first = static_cast<int>((tb * G) / sk.units);
+      while (c_first > 0 && range_lo(c_first) > tb) --c_first;
+      while (range_lo(c_first + 1) <= tb) ++c_first;
+      int c_last = c_first;
+      while (c_last + 1 < G && range_lo(c_last + 1) < te) ++c_last;
+      const int n = c_last - c_first + 1, me = static_cast<int>(blockIdx.x) - c_first;
+      if (et == 0) {
+        const uint64_t t0 = globaltimer_ns();
+        for (int c = c_first; c <= c_last; ++c) {
+          const int cslot = (range_lo(c) >= tb) ? 0 : 1;     // the tile holds c's range start -> first segment
+          uint32_t spins = 0;
+          while (static_cast<int32_t>(ld_acquire_gpu(sk.flags + c * 2 + cslot) - epoch) < 0) {
+            if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > WAIT_LIMIT_NS) {
+              atomicCAS(p.status, kStatusOk, kStatusPeerWaitTimeout);
+              *abort_flag = 1;
+              break;
+            }
+          }
+          if (*abort_flag) break;
+        }
+      }
+      if (!epi_sync()) break;
+      const int rows_per = (BM + n - 1) / n;
+      const int r0 = me * rows_per, r1 = min(min(BM, p.M), r0 + rows_per);
+      constexpr int CH = BN / 4;           // float4 chunks per row
+      for (int i = et; i < (r1 - r0) * CH; i += 128) {
+        const int rr = r0 + i / CH, ch = i % CH;
+        const int col = ni * BN + ch * 4;
+        if (col >= p.N) continue;
+        float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int c = c_first; c <= c_last; ++c) {
+          const int cslot = (range_lo(c) >= tb) ? 0 : 1;
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(sk.ws + ((static_cast<long long>(c) * 2 + cslot) * BM + rr) * BN) + ch);
+          acc4.x += v.x; acc4.y += v.y; acc4.z += v.z; acc4.w += v.w;
+        }
+        float o4[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
+        const int ncols = min(4, p.N - col);
+        if (HAS_RES) {
+          const __nv_bfloat16* rp = p.residual + static_cast<long long>(rr) * p.ldr + col;
+          for (int e = 0; e < ncols; ++e) o4[e] += __bfloat162float(rp[e]);
+        }
+        if (OUT_F32) {
+          float* op = reinterpret_cast<float*>(p.out) + static_cast<long long>(rr) * p.ldo + col;
+          for (int e = 0; e < ncols; ++e) op[e] = o4[e];
+        } else {
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + col;
+          if (ncols == 4 && ((reinterpret_cast<uintptr_t>(op) & 7) == 0)) {
+            uint2 w;
+            __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+            wh[0] = __floats2bfloat162_rn(o4[0], o4[1]);
+            wh[1] = __floats2bfloat162_rn(o4[2], o4[3]);
+            *reinterpret_cast<uint2*>(op) = w;
+          } else {
+            for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(o4[e]);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    // the last CTA to get here advances the launch counter; everyone has finished reading flags by then
+    __threadfence();
+    if (atomicAdd(sk.done_ptr, 1u) == static_cast<uint32_t>(G - 1)) {
+      *sk.done_ptr = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(sk.epoch_ptr) = epoch;
+    }
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
+  }
+}
+
+template <bool OUT_F32, bool HAS_RES>
+const char* launch_streamk(const GemmArgs& a, cudaStream_t stream) {
+  constexpr int BN = SK_BN;
+  using C = Cfg<BN>;
+  if (a.M > BM) return "stream-k gemm: one M tile only";
+  if (!a.sk_ws || !a.sk_flags) return "stream-k gemm: workspace missing";
+  CUtensorMap tmA, tmB, tmA2, tmB2;
+  if (!make_map(&tmA, a.A, a.M, a.K, a.lda, BM)) return "cuTensorMapEncodeTiled failed for A";
+  if (!make_map(&tmB, a.B, a.N, a.K, a.ldb, BN)) return "cuTensorMapEncodeTiled failed for B";
+  if (a.K2 > 0) {
+    if (!make_map(&tmA2, a.A2, a.M, a.K2, a.lda2, BM)) return "cuTensorMapEncodeTiled failed for A2";
+    if (!make_map(&tmB2, a.B2, a.N, a.K2, a.ldb2, BN)) return "cuTensorMapEncodeTiled failed for B2";
+  } else {
+    tmA2 = tmA;
+    tmB2 = tmB;
+  }
+  GemmParams p{};
+  p.M = a.M; p.N = a.N; p.K = a.K; p.K2 = a.K2;
+  p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
+  p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 1; p.split_k = 1; p.ar_world = 1;
+  const int kb_total = (a.K + BK - 1) / BK + (a.K2 + BK - 1) / BK;
+  const int n_tiles = (a.N + BN - 1) / BN;
+  StreamKParams sk{};
+  sk.ws = a.sk_ws; sk.flags = a.sk_flags;
+  sk.epoch_ptr = a.sk_flags + 2 * a.sk_max_ctas;
+  sk.done_ptr = a.sk_flags + 2 * a.sk_max_ctas + 1;
+  sk.units = static_cast<long long>(n_tiles) * kb_total;
+  int grid = a.num_sms < a.sk_max_ctas ? a.num_sms : a.sk_max_ctas;
+  if (sk.units < grid) grid = static_cast<int>(sk.units);
+  if (grid < 1) return nullptr;
+  auto kern = gemm_streamk_kernel<OUT_F32, HAS_RES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
+      return "cudaFuncSetAttribute(max dynamic smem) failed";
+    attr_set = true;
+  }
+  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p, sk);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "stream-k gemm launch failed";
+}
+
 template <int BN>
 const char* launch_flags(const GemmArgs& a, cudaStream_t stream) {
   if (a.out_f32) return a.residual ? launch_bn<BN, true, true>(a, stream) : launch_bn<BN, true, false>(a, stream);
@@ -1368,11 +1738,12 @@ int gemm_pick_bn(int M, int N, int num_sms) {
 // pick the tile width and the k-split that minimise the bytes of the busiest SM (A slice + B slice
 // per tile, times the number of waves).  Splits inside a cluster reduce through shared memory;
 // the global-memory split (fp32 partials + reduce kernel) is the fallback.
-void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out) {
+void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out, double* est_out) {
   const int m_tiles = (M + BM - 1) / BM;
   *bn_out = gemm_pick_bn(M, N, num_sms);
   *split_out = 1;
   *cluster_out = 1;
+  if (est_out) *est_out = 1e30;
   if (m_tiles > 2 || (N % 4)) return;
   const int kb_total = (K + BK - 1) / BK + (K2 + BK - 1) / BK;
   double best = 1e30;
@@ -1407,6 +1778,7 @@ void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split
       if (t < best) { best = t; *bn_out = bn; *split_out = 1; *cluster_out = S; }
     }
   }
+  if (est_out) *est_out = best;
 }
 
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
@@ -1418,6 +1790,11 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
     return "operand base addresses must be 16-byte aligned";
+  if (a.stream_k) {
+    if (a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "stream-k gemm: no global k-split, grouping or all-reduce";
+    if (a.out_f32) return a.residual ? launch_streamk<true, true>(a, stream) : launch_streamk<true, false>(a, stream);
+    return a.residual ? launch_streamk<false, true>(a, stream) : launch_streamk<false, false>(a, stream);
+  }
   if (a.cluster_k > 1) {
     if (a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "cluster split-k gemm: no global k-split, grouping or all-reduce";
     const int key = a.force_bn * 10 + a.cluster_k;

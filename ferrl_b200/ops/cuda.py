@@ -48,12 +48,13 @@ def _bf16(t):
 
 # ----------------------------------------------------------------- GEMM
 def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0, force_split=0, two_cta=0, debug=None,
-         cluster_k=0):
+         cluster_k=0, stream_k=0):
     """``a [M,K] @ b[N,K]^T (+ a2 @ b2^T) (+ residual)`` on the tcgen05 kernel.
     Tile width and k-split are planned from the shape unless forced; ``two_cta`` (128 or 256)
     selects the two-SM kernel with 256 x ``two_cta`` tiles; ``cluster_k`` (with ``force_bn``) the
-    cluster split-k kernel (``-1`` keeps the planner away from it)."""
-    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn, force_split, two_cta, debug, cluster_k)
+    cluster split-k kernel (``-1`` keeps the planner away from it); ``stream_k`` 1 forces and -1
+    forbids the stream-k kernel for decode shapes (0: planner decides)."""
+    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn, force_split, two_cta, debug, cluster_k, stream_k)
 
 
 def _pad8(t, dim):

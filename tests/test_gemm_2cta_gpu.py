@@ -86,3 +86,48 @@ def test_decode_shapes_planned(M, N, K):
     assert C.kernel_status() == 0
     want = a.float() @ b.float().t()
     assert float((y.float() - want).abs().max()) <= 0.02 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("M,N,K,res,lora,f32", [(128, 6144, 4096, False, False, False), (128, 4096, 4096, True, False, False),
+                                                 (128, 24576, 4096, False, False, False), (100, 4096, 12288, True, True, False),
+                                                 (128, 151936, 4096, False, False, True), (7, 1000, 520, True, True, False),
+                                                 (128, 256, 64, False, False, False)])
+def test_stream_k(M, N, K, res, lora, f32):
+    """Stream-k decode GEMM (equal unit ranges per SM, partial tiles fixed up through L2) against
+    fp32 matmul; repeated launches must agree bit for bit (fixed summation order, self-advancing
+    launch counter)."""
+    from ferrl_b200.ops import cuda as C
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    a = rnd(M, K).to(torch.bfloat16)
+    b = (rnd(N, K) / K ** 0.5).to(torch.bfloat16)
+    a2 = rnd(M, 16).to(torch.bfloat16) if lora else None
+    b2 = (rnd(N, 16) * 0.2).to(torch.bfloat16) if lora else None
+    r = rnd(M, N).to(torch.bfloat16) if res else None
+    ys = [C.gemm(a, b, a2, b2, r, out_f32=f32, stream_k=1) for _ in range(3)]
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    want = a.float() @ b.float().t()
+    if lora:
+        want = want + a2.float() @ b2.float().t()
+    if res:
+        want = want + r.float()
+    assert float((ys[0].float() - want).abs().max()) <= 0.02 * float(want.abs().max())
+    assert torch.equal(ys[0], ys[1]) and torch.equal(ys[1], ys[2])
+    # replay inside a CUDA graph: the launch counter lives on the device
+    graph = torch.cuda.CUDAGraph()
+    static = torch.empty_like(ys[0])
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        static.copy_(C.gemm(a, b, a2, b2, r, out_f32=f32, stream_k=1))
+    torch.cuda.current_stream().wait_stream(s)
+    with torch.cuda.graph(graph):
+        static.copy_(C.gemm(a, b, a2, b2, r, out_f32=f32, stream_k=1))
+    for _ in range(3):
+        static.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(static, ys[0])
+    assert C.kernel_status() == 0
