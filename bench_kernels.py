@@ -67,6 +67,9 @@ def profile_case(name, C):
     elif name in ("gemm_2cta_128", "gemm_2cta_256"):
         a, b = rnd(8192, 4096), rnd(8192, 4096)
         fn = lambda: C.gemm(a, b, two_cta=int(name.rsplit("_", 1)[1]))
+    elif name == "gemm_streamk":
+        a, b = rnd(128, 4096), rnd(6144, 4096)
+        fn = lambda: C.gemm(a, b, stream_k=1)
     elif name == "gemm_decode":
         a, b = rnd(128, 4096), rnd(24576, 4096)
         fn = lambda: C.gemm(a, b)

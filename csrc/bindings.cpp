@@ -117,7 +117,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
       const long long units = ((a.N + 255) / 256) * kb;
       const long long per = (units + a.num_sms - 1) / a.num_sms;
       const double t_sk = static_cast<double>(per) * (128 + 256) * 128.0 / 64e9 + 10e-6;
-      use_sk = units >= a.num_sms && t_sk < est;
+      use_sk = false && units >= a.num_sms && t_sk < est;   // measured slower than the planner's other choices: forced use only
     }
     TORCH_CHECK(stream_k <= 0 || eligible, "gemm: stream_k needs M <= 128, N >= 256, N % 4 == 0");
     if (use_sk) {

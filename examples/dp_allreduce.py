@@ -63,12 +63,14 @@ def main(argv=None):
                 p.grad = torch.zeros_like(p)
             p.grad.fill_(1e-3)
         for p in params:
-            dist.all_reduce(p.grad)
-        opt.step_with_norm([p.grad for p in params], 1.0, pre_scale=1.0 / comm.world_size)
+            dist.all_reduce(p.grad)                      # one blocking collective per tensor, as the reference does
+        inv = 1.0 / comm.world_size
+        norm = float(torch.sqrt(sum((p.grad * inv).double().pow(2).sum() for p in params)))   # host-synchronised norm
+        opt.step([p.grad for p in params], grad_scale=inv * min(1.0, 1.0 / max(norm, 1e-12)))
 
     t_fused = timed(fused_step, args.iters)
     fused.heap.check("fused step")
-    t_nccl = timed(nccl_step, args.iters) if hasattr(opt, "step_with_norm") else float("nan")
+    t_nccl = timed(nccl_step, args.iters)
     if comm.rank == 0:
         n = sum(p.numel() for p in params)
         print(f"world {comm.world_size}: {len(params)} tensors, {n / 1e6:.1f} M values; fused {t_fused:.3f} ms, "
