@@ -30,7 +30,7 @@ struct GemmArgs {
   // cluster split-k kernel (decode shapes): cluster_k CTAs share one 128 x force_bn tile; 0/1 = off
   int cluster_k;
   // stream-k kernel (decode shapes, M <= 128): equal unit ranges per SM, partial tiles fixed up through `sk_ws`
-  int stream_k; float* sk_ws; unsigned int* sk_flags; int sk_max_ctas;
+  int stream_k; float* sk_ws; unsigned int* sk_flags; int sk_max_ctas; unsigned long long* sk_debug;
   // grouped mode: B is [n_experts * N, K]; tile_expert[m tile] = expert (or -1: skip the tile)
   const int* tile_expert; int n_experts;
   // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu

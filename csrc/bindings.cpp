@@ -132,6 +132,8 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
       a.sk_ws = sk_ws[dev].data_ptr<float>();
       a.sk_flags = reinterpret_cast<unsigned int*>(sk_flags[dev].data_ptr<int>());
       a.sk_max_ctas = max_ctas;
+      if (debug.has_value() && debug->defined() && debug->scalar_type() == at::kLong && debug->numel() >= 4 * max_ctas)
+        a.sk_debug = reinterpret_cast<unsigned long long*>(debug->data_ptr<int64_t>());
       FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
       return out;
     }

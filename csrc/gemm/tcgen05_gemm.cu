@@ -1364,6 +1364,7 @@ struct StreamKParams {
   uint32_t* epoch_ptr;       // device-resident launch counter: the kernel advances it itself, so a
   uint32_t* done_ptr;        //   captured CUDA graph can replay the launch (a host-side epoch would be baked in)
   long long units;           // n_tiles * kb_total
+  unsigned long long* debug; // optional [grid][4] globaltimer stamps: start, last publish, flags seen, end
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
@@ -1400,6 +1401,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   const int kb_total = kb1 + kb2;
   const int G = gridDim.x;
   const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(sk.epoch_ptr) + 1;   // this launch's flag value
+  if (sk.debug && threadIdx.x == 64) sk.debug[blockIdx.x * 4 + 0] = globaltimer_ns();
   auto range_lo = [&](int cta) -> long long { return static_cast<long long>(cta) * sk.units / G; };
   const long long u_lo = range_lo(blockIdx.x), u_hi = range_lo(blockIdx.x + 1);
 
@@ -1582,7 +1584,10 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           live = false;
           break;
         }
-        if (et == 0) st_release_gpu(sk.flags + blockIdx.x * 2 + slot, epoch);
+        if (et == 0) {
+          st_release_gpu(sk.flags + blockIdx.x * 2 + slot, epoch);
+          if (sk.debug) sk.debug[blockIdx.x * 4 + 1] = globaltimer_ns();
+        }
       }
       u = seg_end;
     }
@@ -1614,18 +1619,36 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
       }
       if (!epi_sync()) break;
+      if (sk.debug && et == 0) sk.debug[blockIdx.x * 4 + 2] = globaltimer_ns();
       const int rows_per = (BM + n - 1) / n;
       const int r0 = me * rows_per, r1 = min(min(BM, p.M), r0 + rows_per);
       constexpr int CH = BN / 4;           // float4 chunks per row
+      constexpr int MAXC = 16;             // contributors whose loads are kept in flight together
+      // slot of every contributor, one bit each (bit set: the tile is that CTA's last segment)
+      unsigned long long slot_bits = 0ull;
+      for (int c = c_first; c <= c_last && c - c_first < 64; ++c)
+        if (range_lo(c) < tb) slot_bits |= 1ull << (c - c_first);
       for (int i = et; i < (r1 - r0) * CH; i += 128) {
         const int rr = r0 + i / CH, ch = i % CH;
         const int col = ni * BN + ch * 4;
         if (col >= p.N) continue;
         float4 acc4 = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int c = c_first; c <= c_last; ++c) {
-          const int cslot = (range_lo(c) >= tb) ? 0 : 1;
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(sk.ws + ((static_cast<long long>(c) * 2 + cslot) * BM + rr) * BN) + ch);
-          acc4.x += v.x; acc4.y += v.y; acc4.z += v.z; acc4.w += v.w;
+        const float4* base = reinterpret_cast<const float4*>(sk.ws + static_cast<long long>(rr) * BN) + ch;
+        constexpr long long CTA_STRIDE4 = 2LL * BM * BN / 4, SLOT_STRIDE4 = static_cast<long long>(BM) * BN / 4;
+        for (int c0 = 0; c0 < n; c0 += MAXC) {
+          float4 v[MAXC];
+#pragma unroll
+          for (int k = 0; k < MAXC; ++k) {   // all loads first: the sum below must not serialise on L2 latency
+            const int ci = c0 + k;
+            if (ci < n)
+              v[k] = __ldcg(base + (c_first + ci) * CTA_STRIDE4 + ((slot_bits >> (ci & 63)) & 1ull) * SLOT_STRIDE4);
+          }
+#pragma unroll
+          for (int k = 0; k < MAXC; ++k) {   // contributor order == k order: fixed summation order
+            if (c0 + k < n) {
+              acc4.x += v[k].x; acc4.y += v[k].y; acc4.z += v[k].z; acc4.w += v[k].w;
+            }
+          }
         }
         float o4[4] = {acc4.x, acc4.y, acc4.z, acc4.w};
         const int ncols = min(4, p.N - col);
@@ -1654,6 +1677,7 @@ gemm_streamk_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
 
   tc_fence_before();
   __syncthreads();
+  if (sk.debug && threadIdx.x == 64) sk.debug[blockIdx.x * 4 + 3] = globaltimer_ns();
   if (threadIdx.x == 0) {
     // the last CTA to get here advances the launch counter; everyone has finished reading flags by then
     __threadfence();
@@ -1696,6 +1720,7 @@ const char* launch_streamk(const GemmArgs& a, cudaStream_t stream) {
   sk.epoch_ptr = a.sk_flags + 2 * a.sk_max_ctas;
   sk.done_ptr = a.sk_flags + 2 * a.sk_max_ctas + 1;
   sk.units = static_cast<long long>(n_tiles) * kb_total;
+  sk.debug = a.sk_debug;
   int grid = a.num_sms < a.sk_max_ctas ? a.num_sms : a.sk_max_ctas;
   if (sk.units < grid) grid = static_cast<int>(sk.units);
   if (grid < 1) return nullptr;
