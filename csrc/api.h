@@ -34,7 +34,7 @@ struct GemmArgs {
   // grouped mode: B is [n_experts * N, K]; tile_expert[m tile] = expert (or -1: skip the tile)
   const int* tile_expert; int n_experts;
   // fused GEMM -> all-reduce over the symmetric heap (ar_world > 1): see tcgen05_gemm.cu
-  int ar_world, ar_rank; unsigned ar_epoch; int ar_max_tiles; unsigned long long ar_limit_ns;
+  int ar_world, ar_rank; int ar_max_tiles; unsigned long long ar_limit_ns;
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
   PeerTable ar_stage, ar_outbuf, ar_flags;
 };

@@ -191,7 +191,7 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   a.status = status_word(); a.num_sms = num_sms();
   a.force_bn = (a.N >= 256 && static_cast<int64_t>((a.M + 127) / 128) * ((a.N + 255) / 256) >= num_sms()) ? 256 : 128;
   if (a.N < 128) a.force_bn = 64;
-  a.ar_world = world; a.ar_rank = rank; a.ar_epoch = static_cast<unsigned>(epoch); a.ar_max_tiles = max_tiles;
+  a.ar_world = world; a.ar_rank = rank; (void)epoch; a.ar_max_tiles = max_tiles;   // the call number lives on the device
   a.ar_limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
   a.ar_stage_elems = stage_elems; a.ar_out_elems = out_elems;
   a.ar_stage = table_of_fwd(stage); a.ar_outbuf = table_of_fwd(outbuf); a.ar_flags = table_of_fwd(flags);

@@ -58,7 +58,6 @@ struct GemmParams {
   //   3. every rank copies the tiles it does not own from its local `ar_outbuf` into `out` as their
   //      done flags arrive, between its own tiles where it can and in a final sweep for the rest.
   int ar_world, ar_rank;
-  uint32_t ar_epoch;
   PeerTable ar_stage, ar_outbuf, ar_flags;
   int ar_max_tiles;
   uint64_t ar_limit_ns;
@@ -251,6 +250,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   volatile int* pull_ready = reinterpret_cast<volatile int*>(acc_empty + 4);
   // a peer may enter the kernel later than this rank: every wait of the all-reduce mode allows for that skew
   const uint64_t wait_limit = p.ar_world > 1 ? WAIT_LIMIT_NS + p.ar_limit_ns : WAIT_LIMIT_NS;
+  // The call number lives in this rank's flag buffer and is advanced by the kernel itself (last CTA
+  // out), so a captured CUDA graph replays with fresh flag values; ranks call in lockstep, so their
+  // counters agree.
+  uint32_t* ar_epoch_word = nullptr;
+  uint32_t ar_epoch = 0;
+  if (p.ar_world > 1) {
+    ar_epoch_word = static_cast<uint32_t*>(p.ar_flags.ptr[p.ar_rank]) + static_cast<long long>(p.ar_max_tiles) * (kMaxRanks + 1);
+    ar_epoch = *reinterpret_cast<volatile uint32_t*>(ar_epoch_word) + 1;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -396,15 +404,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       epi_phase ^= 1;
       return ok && !*abort_flag;
     };
-    auto copy_tile = [&](int t) {                 // local ar_outbuf -> out, one tile
+    auto copy_tile = [&](int t) {                 // local ar_outbuf -> out, one tile, 8 chunks in flight per thread
       const int tmi = t / n_tiles, tni = t % n_tiles;
       const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.ar_outbuf.ptr[p.ar_rank]);
-#pragma unroll 4
-      for (int i = et; i < BM * CPR; i += 128) {
-        const int rr = tmi * BM + i / CPR, cc = tni * BN + (i % CPR) * 8;
-        if (rr >= p.M || cc >= p.N) continue;
-        const uint4 x = *reinterpret_cast<const uint4*>(src + static_cast<long long>(rr) * p.N + cc);
-        *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + cc) = x;
+      constexpr int UC = 8;
+      for (int i0 = et; i0 < BM * CPR; i0 += 128 * UC) {
+        uint4 x[UC];
+        long long so[UC];
+        bool ok[UC];
+#pragma unroll
+        for (int u = 0; u < UC; ++u) {
+          const int i = i0 + u * 128;
+          const int rr = tmi * BM + i / CPR, cc = tni * BN + (i % CPR) * 8;
+          ok[u] = i < BM * CPR && rr < p.M && cc < p.N;
+          so[u] = static_cast<long long>(rr) * p.ldo + cc;
+          if (ok[u]) x[u] = *reinterpret_cast<const uint4*>(src + static_cast<long long>(rr) * p.N + cc);
+        }
+#pragma unroll
+        for (int u = 0; u < UC; ++u)
+          if (ok[u]) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + so[u]) = x[u];
       }
     };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -513,12 +531,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int owner = out_tile % p.ar_world;
         __threadfence_system();
         if (!epi_sync()) break;
-        if (et == 0) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), p.ar_epoch);
+        if (et == 0) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
         if (owner == p.ar_rank) {
           if (et == 0) {
             bool ok = true;
             for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
-              ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), p.ar_epoch, p.ar_limit_ns, p.status);
+              ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), ar_epoch, p.ar_limit_ns, p.status);
             if (!ok) *abort_flag = 1;
           }
           if (!epi_sync()) break;
@@ -527,30 +545,60 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint4* slot0 = reinterpret_cast<const uint4*>(
               static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
               static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
-#pragma unroll 2
-          for (int i = et; i < BM * CPR; i += 128) {
-            const int rt = i / CPR, ch = i % CPR;
-            const int rr = mi * BM + rt, cc = ni * BN + ch * 8;
-            if (rr >= p.M || cc >= p.N) continue;
-            float a8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int q2 = 0; q2 < p.ar_world; ++q2) add8(a8, slot0[q2 * (BM * CPR) + ch * BM + rt]);
-            if (HAS_RES) add8(a8, *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr) * p.ldr + cc));
-            const uint4 o = pack8(a8);
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr) * p.ldo + cc) = o;
-            const long long off = static_cast<long long>(rr) * p.N + cc;
-            for (int q2 = 0; q2 < p.ar_world; ++q2)
-              if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
+          // U elements per round with every slot's load issued before the first add: the loop is bound
+          // by memory latency, not bandwidth, so loads in flight per thread are what sets its speed
+          constexpr int U = 4, WCH = 8;
+          for (int i0 = et; i0 < BM * CPR; i0 += 128 * U) {
+            float a8[U][8];
+            bool live[U];
+            int rr_[U], cc_[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int i = i0 + u * 128;
+              const int rt = i / CPR, ch = i % CPR;
+              rr_[u] = mi * BM + rt;
+              cc_[u] = ni * BN + ch * 8;
+              live[u] = i < BM * CPR && rr_[u] < p.M && cc_[u] < p.N;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) a8[u][e] = 0.f;
+            }
+            for (int w0 = 0; w0 < p.ar_world; w0 += WCH) {
+              uint4 x[U][WCH];
+#pragma unroll
+              for (int u = 0; u < U; ++u) {
+                const int i = i0 + u * 128;
+                const int rt = i / CPR, ch = i % CPR;
+#pragma unroll
+                for (int w = 0; w < WCH; ++w)
+                  if (live[u] && w0 + w < p.ar_world) x[u][w] = slot0[(w0 + w) * (BM * CPR) + ch * BM + rt];
+              }
+#pragma unroll
+              for (int u = 0; u < U; ++u)
+#pragma unroll
+                for (int w = 0; w < WCH; ++w)
+                  if (live[u] && w0 + w < p.ar_world) add8(a8[u], x[u][w]);      // rank order
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              if (!live[u]) continue;
+              if (HAS_RES) add8(a8[u], *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]));
+              const uint4 o = pack8(a8[u]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
+              const long long off = static_cast<long long>(rr_[u]) * p.N + cc_[u];
+              for (int q2 = 0; q2 < p.ar_world; ++q2)
+                if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
+            }
           }
           __threadfence_system();
           if (!epi_sync()) break;
           if (et == 0)
             for (int q2 = 0; q2 < p.ar_world; ++q2)
-              if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), p.ar_epoch);
+              if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), ar_epoch);
         }
         // between tiles: take one finished tile of a peer if its flag is already here
         const int pt = peer_tile(pull_u);
         if (et == 0)
-          *pull_ready = pt < out_tiles && flag_reached(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), p.ar_epoch);
+          *pull_ready = pt < out_tiles && flag_reached(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch);
         if (!epi_sync()) break;
         if (*pull_ready) {
           copy_tile(pt);
@@ -561,7 +609,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // final sweep: the tiles whose flags had not arrived yet
     if (p.ar_world > 1 && !*abort_flag) {
       for (int pt = peer_tile(pull_u); pt < out_tiles; pull_u += gridDim.x, pt = peer_tile(pull_u)) {
-        if (et == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), p.ar_epoch, p.ar_limit_ns,
+        if (et == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch, p.ar_limit_ns,
                                      p.status))
           *abort_flag = 1;
         if (!epi_sync()) break;
@@ -572,6 +620,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
+  if (p.ar_world > 1 && threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(ar_epoch_word + 1, 1u) == gridDim.x - 1) {   // last CTA out: next call uses the next number
+      ar_epoch_word[1] = 0u;
+      __threadfence();
+      *reinterpret_cast<volatile uint32_t*>(ar_epoch_word) = ar_epoch;
+    }
+  }
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(C::TMEM_COLS) : "memory");
@@ -679,7 +735,7 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     if (a.residual && ((a.ldr % 8) || (reinterpret_cast<uintptr_t>(a.residual) & 15)))
       return "fused all-reduce: residual must be 16-byte aligned with ldr % 8 == 0";
     if (a.ar_world > kMaxRanks || a.ar_rank < 0 || a.ar_rank >= a.ar_world) return "fused all-reduce: bad rank/world";
-    p.ar_rank = a.ar_rank; p.ar_epoch = a.ar_epoch; p.ar_stage = a.ar_stage; p.ar_outbuf = a.ar_outbuf;
+    p.ar_rank = a.ar_rank; p.ar_stage = a.ar_stage; p.ar_outbuf = a.ar_outbuf;
     p.ar_flags = a.ar_flags; p.ar_max_tiles = a.ar_max_tiles; p.ar_limit_ns = a.ar_limit_ns;
   }
   auto kern = gemm_kernel<BN, OUT_F32, HAS_RES>;

@@ -150,7 +150,8 @@ class GemmAllReducer:
         self.out_elems = max_rows * max_cols
         self.stage = heap.alloc(self.stage_elems * 2)
         self.outbuf = heap.alloc(self.out_elems * 2)
-        self.flags = heap.alloc(self.max_tiles * (MAX_RANKS + 1) * 4)
+        # ready[tile][rank] and done[tile] flags, then the device-resident call counter and its CTA counter
+        self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2) * 4)
         self.flags.local.zero_()
         torch.cuda.synchronize(heap.device)
         if heap.world > 1:

@@ -77,6 +77,7 @@ def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
                   flags=torch.zeros_like(mine["flags"]))
     epoch = 7
     done_base = red.max_tiles * MAXR
+    mine["flags"][red.max_tiles * (MAXR + 1)] = epoch - 1      # device-resident call counter: this call is number 7
     for t in range(mt * nt):
         mi, ni = divmod(t, nt)
         if t % 2 == rank:     # mine to reduce: the peer's partial is already in my staging slot
@@ -94,6 +95,7 @@ def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
                                rank, 2, epoch, red.max_tiles, red.stage_elems, red.out_elems, 0.5)
     torch.cuda.synchronize()
     assert C.kernel_status() == 0
+    assert int(mine["flags"][red.max_tiles * (MAXR + 1)]) == epoch      # the kernel advanced its own counter
     tol = 0.02 * float(want.float().abs().max())
     assert float((y.float() - want.float()).abs().max()) <= tol
     peer_out = theirs["out"][:M * N].view(M, N)
