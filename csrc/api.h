@@ -37,6 +37,7 @@ struct GemmArgs {
   int ar_world, ar_rank; int ar_max_tiles; unsigned long long ar_limit_ns;
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
   PeerTable ar_stage, ar_outbuf, ar_flags;
+  unsigned long long* ar_debug;
 };
 void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out,
                double* est_out = nullptr);

@@ -174,7 +174,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
 Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
                       const optional<Tensor>& residual, std::vector<int64_t> stage, std::vector<int64_t> outbuf,
                       std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t epoch, int64_t max_tiles,
-                      int64_t stage_elems, int64_t out_elems, double limit_s) {
+                      int64_t stage_elems, int64_t out_elems, double limit_s, const optional<Tensor>& debug) {
   TORCH_CHECK(A.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_allreduce: bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1, "gemm_allreduce: shapes");
   c10::cuda::CUDAGuard guard(A.device());
@@ -194,6 +194,8 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   a.ar_world = world; a.ar_rank = rank; (void)epoch; a.ar_max_tiles = max_tiles;   // the call number lives on the device
   a.ar_limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
   a.ar_stage_elems = stage_elems; a.ar_out_elems = out_elems;
+  if (debug.has_value() && debug->defined() && debug->scalar_type() == at::kLong && debug->numel() >= 160 * 16 * 4)
+    a.ar_debug = reinterpret_cast<unsigned long long*>(debug->data_ptr<int64_t>());
   a.ar_stage = table_of_fwd(stage); a.ar_outbuf = table_of_fwd(outbuf); a.ar_flags = table_of_fwd(flags);
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
   return out;
@@ -905,7 +907,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
-  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s) -> Tensor", &gemm_allreduce);
+  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

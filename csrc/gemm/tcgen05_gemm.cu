@@ -61,6 +61,7 @@ struct GemmParams {
   PeerTable ar_stage, ar_outbuf, ar_flags;
   int ar_max_tiles;
   uint64_t ar_limit_ns;
+  unsigned long long* ar_debug;   // optional [grid][16 tiles][4] globaltimer stamps of the exchange
 };
 
 // flag layout inside each rank's flag buffer: ready[tile][kMaxRanks] then done[tile]
@@ -232,7 +233,8 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 }
 
 // OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
-template <int BN, bool OUT_F32, bool HAS_RES>
+// AR: fused all-reduce mode (compiled separately so the plain kernel carries none of its registers).
+template <int BN, bool OUT_F32, bool HAS_RES, bool AR>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p) {
@@ -249,13 +251,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* epi_bar = acc_empty + 3;           // epilogue-group barrier (4 warps) of the all-reduce mode
   volatile int* pull_ready = reinterpret_cast<volatile int*>(acc_empty + 4);
   // a peer may enter the kernel later than this rank: every wait of the all-reduce mode allows for that skew
-  const uint64_t wait_limit = p.ar_world > 1 ? WAIT_LIMIT_NS + p.ar_limit_ns : WAIT_LIMIT_NS;
+  const uint64_t wait_limit = AR ? WAIT_LIMIT_NS + p.ar_limit_ns : WAIT_LIMIT_NS;
   // The call number lives in this rank's flag buffer and is advanced by the kernel itself (last CTA
   // out), so a captured CUDA graph replays with fresh flag values; ranks call in lockstep, so their
   // counters agree.
   uint32_t* ar_epoch_word = nullptr;
   uint32_t ar_epoch = 0;
-  if (p.ar_world > 1) {
+  if (AR) {
     ar_epoch_word = static_cast<uint32_t*>(p.ar_flags.ptr[p.ar_rank]) + static_cast<long long>(p.ar_max_tiles) * (kMaxRanks + 1);
     ar_epoch = *reinterpret_cast<volatile uint32_t*>(ar_epoch_word) + 1;
   }
@@ -437,7 +439,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool row_ok = row < p.M;
       const int out_tile = mi * n_tiles + ni;
       __nv_bfloat16* ar_slot = nullptr;
-      if (p.ar_world > 1)
+      if (AR)
         ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
                   (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
 #pragma unroll 1
@@ -461,7 +463,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           continue;
         }
-        if (p.ar_world > 1) {
+        if (AR) {
           // bf16 partial of this rank, pushed into the tile owner's staging slot; rows past M hold the
           // zero fill of the TMA load, so no bounds test is needed inside the slot
 #pragma unroll
@@ -527,16 +529,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
-      if (p.ar_world > 1) {
+      if (AR) {
         const int owner = out_tile % p.ar_world;
-        __threadfence_system();
+        if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 0] = globaltimer_ns();
+        // One system-scope release per tile, by one thread: the CTA-level barrier orders the other
+        // threads' stores before it (fences by all 128 threads would each wait for the NVLink
+        // acknowledgements).  My own slot of a tile I own is only read by this CTA: no flag needed.
         if (!epi_sync()) break;
-        if (et == 0) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
+        if (et == 0 && owner != p.ar_rank) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
+        if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 1] = globaltimer_ns();
         if (owner == p.ar_rank) {
           if (et == 0) {
             bool ok = true;
             for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
-              ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), ar_epoch, p.ar_limit_ns, p.status);
+              if (q2 != p.ar_rank)
+                ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), ar_epoch, p.ar_limit_ns, p.status);
             if (!ok) *abort_flag = 1;
           }
           if (!epi_sync()) break;
@@ -589,12 +596,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
             }
           }
-          __threadfence_system();
+          if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 2] = globaltimer_ns();
           if (!epi_sync()) break;
-          if (et == 0)
+          if (et == 0) {
+            __threadfence_system();
             for (int q2 = 0; q2 < p.ar_world; ++q2)
               if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), ar_epoch);
+          }
         }
+        if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 3] = globaltimer_ns();
         // between tiles: take one finished tile of a peer if its flag is already here
         const int pt = peer_tile(pull_u);
         if (et == 0)
@@ -607,7 +617,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     // final sweep: the tiles whose flags had not arrived yet
-    if (p.ar_world > 1 && !*abort_flag) {
+    if (AR && !*abort_flag) {
       for (int pt = peer_tile(pull_u); pt < out_tiles; pull_u += gridDim.x, pt = peer_tile(pull_u)) {
         if (et == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch, p.ar_limit_ns,
                                      p.status))
@@ -620,7 +630,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   tc_fence_before();
   __syncthreads();
-  if (p.ar_world > 1 && threadIdx.x == 0) {
+  if (AR && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(ar_epoch_word + 1, 1u) == gridDim.x - 1) {   // last CTA out: next call uses the next number
       ar_epoch_word[1] = 0u;
@@ -737,13 +747,18 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     if (a.ar_world > kMaxRanks || a.ar_rank < 0 || a.ar_rank >= a.ar_world) return "fused all-reduce: bad rank/world";
     p.ar_rank = a.ar_rank; p.ar_stage = a.ar_stage; p.ar_outbuf = a.ar_outbuf;
     p.ar_flags = a.ar_flags; p.ar_max_tiles = a.ar_max_tiles; p.ar_limit_ns = a.ar_limit_ns;
+    p.ar_debug = a.ar_debug;
   }
-  auto kern = gemm_kernel<BN, OUT_F32, HAS_RES>;
-  static bool attr_set = false;
-  if (!attr_set) {
+  constexpr bool kArOk = !OUT_F32 && (BN == 256 || BN == 128 || BN == 64);
+  if (p.ar_world > 1 && !kArOk) return "fused all-reduce: unsupported tile width or output type";
+  auto kern_plain = gemm_kernel<BN, OUT_F32, HAS_RES, false>;
+  auto kern_ar = gemm_kernel<BN, OUT_F32, HAS_RES, kArOk>;      // same as plain when the mode is not available
+  auto kern = p.ar_world > 1 ? kern_ar : kern_plain;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[p.ar_world > 1]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
       return "cudaFuncSetAttribute(max dynamic smem) failed";
-    attr_set = true;
+    attr_set[p.ar_world > 1] = true;
   }
   int m_tiles = (a.M + BM - 1) / BM, n_tiles = (a.N + BN - 1) / BN;
   int tiles = m_tiles * n_tiles * p.split_k;

@@ -165,13 +165,13 @@ class GemmAllReducer:
         return (cols % 8 == 0 and tiles <= self.max_tiles and rows * cols <= self.out_elems
                 and mt * self.BM * npad + self.heap.world * self.BM * self.BN_MAX <= self.stage_elems)
 
-    def __call__(self, a, b, a2=None, b2=None, residual=None) -> torch.Tensor:
+    def __call__(self, a, b, a2=None, b2=None, residual=None, debug=None) -> torch.Tensor:
         self.heap.guard()
         self.epoch += 1
         h = self.heap
         return h.C.lib().gemm_allreduce(a, b, a2, b2, residual, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
                                         h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
-                                        self.out_elems, h.wait_limit_s)
+                                        self.out_elems, h.wait_limit_s, debug)
 
 
 _REDUCERS: dict = {}
