@@ -235,7 +235,7 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 // OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
 // AR: fused all-reduce mode (compiled separately so the plain kernel carries none of its registers).
 template <int BN, bool OUT_F32, bool HAS_RES, bool AR>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(AR ? NUM_THREADS + 128 : NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, GemmParams p) {
   using C = Cfg<BN>;
@@ -250,6 +250,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   uint64_t* epi_bar = acc_empty + 3;           // epilogue-group barrier (4 warps) of the all-reduce mode
   volatile int* pull_ready = reinterpret_cast<volatile int*>(acc_empty + 4);
+  uint64_t* comm_bar = acc_empty + 5;          // communication-group barrier (4 warps), all-reduce mode
+  volatile int* drained = reinterpret_cast<volatile int*>(acc_empty + 6);   // tiles whose partial has left TMEM
   // a peer may enter the kernel later than this rank: every wait of the all-reduce mode allows for that skew
   const uint64_t wait_limit = AR ? WAIT_LIMIT_NS + p.ar_limit_ns : WAIT_LIMIT_NS;
   // The call number lives in this rank's flag buffer and is advanced by the kernel itself (last CTA
@@ -281,6 +283,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       mbar_init(&acc_empty[a], 4);
     }
     mbar_init(epi_bar, 4);
+    mbar_init(comm_bar, 4);
+    *drained = 0;
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -383,21 +387,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (ok) umma_commit(&acc_full[acc]);
       }
     }
-  } else {
+  } else if (warp < 6) {
     // ------------------------------------------------------------ epilogue warps
     const int q = warp & 3;  // TMEM lane quarter this warp may read
     uint32_t acc_phase[2] = {0, 0};
     int it = 0;
     // ---- all-reduce mode state
-    constexpr int CPR = BN / 8;                   // 16-byte chunks per tile row
     const int et = threadIdx.x - 64;              // 0..127 within the epilogue group
-    const int out_tiles = m_tiles * n_tiles;
-    // tiles owned by peers, numbered densely so that the copies spread evenly over the CTAs
-    auto peer_tile = [&](int u) -> int {
-      const int g = u / (p.ar_world - 1), pos = u % (p.ar_world - 1);
-      return g * p.ar_world + (pos < p.ar_rank ? pos : pos + 1);
-    };
-    int pull_u = blockIdx.x;                      // next peer tile this CTA copies out of the local ar_outbuf
     uint32_t epi_phase = 0;
     auto epi_sync = [&]() -> bool {               // bounded barrier over the 4 epilogue warps
       __syncwarp();
@@ -405,27 +401,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const bool ok = mbar_wait(epi_bar, epi_phase, abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit);
       epi_phase ^= 1;
       return ok && !*abort_flag;
-    };
-    auto copy_tile = [&](int t) {                 // local ar_outbuf -> out, one tile, 8 chunks in flight per thread
-      const int tmi = t / n_tiles, tni = t % n_tiles;
-      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.ar_outbuf.ptr[p.ar_rank]);
-      constexpr int UC = 8;
-      for (int i0 = et; i0 < BM * CPR; i0 += 128 * UC) {
-        uint4 x[UC];
-        long long so[UC];
-        bool ok[UC];
-#pragma unroll
-        for (int u = 0; u < UC; ++u) {
-          const int i = i0 + u * 128;
-          const int rr = tmi * BM + i / CPR, cc = tni * BN + (i % CPR) * 8;
-          ok[u] = i < BM * CPR && rr < p.M && cc < p.N;
-          so[u] = static_cast<long long>(rr) * p.ldo + cc;
-          if (ok[u]) x[u] = *reinterpret_cast<const uint4*>(src + static_cast<long long>(rr) * p.N + cc);
-        }
-#pragma unroll
-        for (int u = 0; u < UC; ++u)
-          if (ok[u]) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + so[u]) = x[u];
-      }
     };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int ks, mi, ni;
@@ -530,99 +505,156 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
       if (AR) {
+        // The exchange itself belongs to the communication warps below; here the tile is only
+        // announced.  One system-scope release per tile, by one thread: the barrier orders the other
+        // threads' stores before it.  A tile this rank owns is announced through shared memory.
         const int owner = out_tile % p.ar_world;
         if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 0] = globaltimer_ns();
-        // One system-scope release per tile, by one thread: the CTA-level barrier orders the other
-        // threads' stores before it (fences by all 128 threads would each wait for the NVLink
-        // acknowledgements).  My own slot of a tile I own is only read by this CTA: no flag needed.
         if (!epi_sync()) break;
-        if (et == 0 && owner != p.ar_rank) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
+        if (et == 0) {
+          if (owner != p.ar_rank) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
+          asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(drained))), "r"(it) : "memory");
+        }
         if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 1] = globaltimer_ns();
-        if (owner == p.ar_rank) {
-          if (et == 0) {
-            bool ok = true;
-            for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
-              if (q2 != p.ar_rank)
-                ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), ar_epoch, p.ar_limit_ns, p.status);
-            if (!ok) *abort_flag = 1;
+      }
+    }
+  } else if (AR) {
+    // ------------------------------------------------------------ communication warps (all-reduce mode only)
+    // They walk the same tile sequence as the epilogue, one or more tiles behind it, and never touch
+    // TMEM: waiting for peers, the owner's reduction, the pushes and the copies of the peers' tiles
+    // run beside the tensor cores instead of holding up the accumulator ring.
+    const int ct = threadIdx.x - 192;             // 0..127
+    constexpr int CPR = BN / 8;
+    const int out_tiles = m_tiles * n_tiles;
+    auto peer_tile = [&](int u) -> int {
+      const int g = u / (p.ar_world - 1), pos = u % (p.ar_world - 1);
+      return g * p.ar_world + (pos < p.ar_rank ? pos : pos + 1);
+    };
+    int pull_u = blockIdx.x;
+    uint32_t comm_phase = 0;
+    auto comm_sync = [&]() -> bool {
+      __syncwarp();
+      if (lane == 0) mbar_arrive(comm_bar);
+      const bool ok = mbar_wait(comm_bar, comm_phase, abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit);
+      comm_phase ^= 1;
+      return ok && !*abort_flag;
+    };
+    auto copy_tile = [&](int t) {                 // local ar_outbuf -> out, one tile, 8 chunks in flight per thread
+      const int tmi = t / n_tiles, tni = t % n_tiles;
+      const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.ar_outbuf.ptr[p.ar_rank]);
+      constexpr int UC = 8;
+      for (int i0 = ct; i0 < BM * CPR; i0 += 128 * UC) {
+        uint4 x[UC];
+        long long so[UC];
+        bool ok[UC];
+#pragma unroll
+        for (int u = 0; u < UC; ++u) {
+          const int i = i0 + u * 128;
+          const int rr = tmi * BM + i / CPR, cc = tni * BN + (i % CPR) * 8;
+          ok[u] = i < BM * CPR && rr < p.M && cc < p.N;
+          so[u] = static_cast<long long>(rr) * p.ldo + cc;
+          if (ok[u]) x[u] = *reinterpret_cast<const uint4*>(src + static_cast<long long>(rr) * p.N + cc);
+        }
+#pragma unroll
+        for (int u = 0; u < UC; ++u)
+          if (ok[u]) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + so[u]) = x[u];
+      }
+    };
+    int it = 0;
+    bool live_c = true;
+    for (int tile = blockIdx.x; tile < total_tiles && live_c; tile += gridDim.x) {
+      int ks, mi, ni;
+      tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+      ++it;
+      const int out_tile = mi * n_tiles + ni;
+      const int owner = out_tile % p.ar_world;
+      if (owner == p.ar_rank) {
+        if (ct == 0) {
+          // my own partial is in place once the epilogue has drained tile number `it`
+          const uint64_t t0 = globaltimer_ns();
+          uint32_t spins = 0;
+          bool ok = true;
+          while (*drained < it) {
+            if ((++spins & 0xff) == 0 && (*abort_flag || globaltimer_ns() - t0 > wait_limit)) { ok = false; break; }
           }
-          if (!epi_sync()) break;
-          // sum the world slots of this tile in rank order; lanes walk along a row so that the stores
-          // to `out` and to the peers' buffers cover whole 128-byte lines
-          const uint4* slot0 = reinterpret_cast<const uint4*>(
-              static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
-              static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
-          // U elements per round with every slot's load issued before the first add: the loop is bound
-          // by memory latency, not bandwidth, so loads in flight per thread are what sets its speed
-          constexpr int U = 4, WCH = 8;
-          for (int i0 = et; i0 < BM * CPR; i0 += 128 * U) {
-            float a8[U][8];
-            bool live[U];
-            int rr_[U], cc_[U];
+          asm volatile("fence.acq_rel.cta;" ::: "memory");
+          for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
+            if (q2 != p.ar_rank)
+              ok = ar_wait_flag(ar_ready(p.ar_flags, p.ar_rank, out_tile, q2), ar_epoch, p.ar_limit_ns, p.status);
+          if (!ok) *abort_flag = 1;
+        }
+        if (!comm_sync()) break;
+        const uint4* slot0 = reinterpret_cast<const uint4*>(
+            static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
+            static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
+        // U elements per round with every slot's load issued before the first add (latency-bound loop)
+        constexpr int U = 2, WCH = 8;
+        for (int i0 = ct; i0 < BM * CPR; i0 += 128 * U) {
+          float a8[U][8];
+          bool live[U];
+          int rr_[U], cc_[U];
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            const int i = i0 + u * 128;
+            const int rt = i / CPR, ch = i % CPR;
+            rr_[u] = mi * BM + rt;
+            cc_[u] = ni * BN + ch * 8;
+            live[u] = i < BM * CPR && rr_[u] < p.M && cc_[u] < p.N;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a8[u][e] = 0.f;
+          }
+          for (int w0 = 0; w0 < p.ar_world; w0 += WCH) {
+            uint4 x[U][WCH];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
               const int i = i0 + u * 128;
               const int rt = i / CPR, ch = i % CPR;
-              rr_[u] = mi * BM + rt;
-              cc_[u] = ni * BN + ch * 8;
-              live[u] = i < BM * CPR && rr_[u] < p.M && cc_[u] < p.N;
 #pragma unroll
-              for (int e = 0; e < 8; ++e) a8[u][e] = 0.f;
-            }
-            for (int w0 = 0; w0 < p.ar_world; w0 += WCH) {
-              uint4 x[U][WCH];
-#pragma unroll
-              for (int u = 0; u < U; ++u) {
-                const int i = i0 + u * 128;
-                const int rt = i / CPR, ch = i % CPR;
-#pragma unroll
-                for (int w = 0; w < WCH; ++w)
-                  if (live[u] && w0 + w < p.ar_world) x[u][w] = slot0[(w0 + w) * (BM * CPR) + ch * BM + rt];
-              }
-#pragma unroll
-              for (int u = 0; u < U; ++u)
-#pragma unroll
-                for (int w = 0; w < WCH; ++w)
-                  if (live[u] && w0 + w < p.ar_world) add8(a8[u], x[u][w]);      // rank order
+              for (int w = 0; w < WCH; ++w)
+                if (live[u] && w0 + w < p.ar_world) x[u][w] = slot0[(w0 + w) * (BM * CPR) + ch * BM + rt];
             }
 #pragma unroll
-            for (int u = 0; u < U; ++u) {
-              if (!live[u]) continue;
-              if (HAS_RES) add8(a8[u], *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]));
-              const uint4 o = pack8(a8[u]);
-              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
-              const long long off = static_cast<long long>(rr_[u]) * p.N + cc_[u];
-              for (int q2 = 0; q2 < p.ar_world; ++q2)
-                if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
-            }
+            for (int u = 0; u < U; ++u)
+#pragma unroll
+              for (int w = 0; w < WCH; ++w)
+                if (live[u] && w0 + w < p.ar_world) add8(a8[u], x[u][w]);      // rank order
           }
-          if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 2] = globaltimer_ns();
-          if (!epi_sync()) break;
-          if (et == 0) {
-            __threadfence_system();
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (!live[u]) continue;
+            if (HAS_RES) add8(a8[u], *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]));
+            const uint4 o = pack8(a8[u]);
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
+            const long long off = static_cast<long long>(rr_[u]) * p.N + cc_[u];
             for (int q2 = 0; q2 < p.ar_world; ++q2)
-              if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), ar_epoch);
+              if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
           }
         }
-        if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 3] = globaltimer_ns();
-        // between tiles: take one finished tile of a peer if its flag is already here
-        const int pt = peer_tile(pull_u);
-        if (et == 0)
-          *pull_ready = pt < out_tiles && flag_reached(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch);
-        if (!epi_sync()) break;
-        if (*pull_ready) {
-          copy_tile(pt);
-          pull_u += gridDim.x;
+        if (p.ar_debug && ct == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 2] = globaltimer_ns();
+        if (!comm_sync()) break;
+        if (ct == 0) {
+          __threadfence_system();
+          for (int q2 = 0; q2 < p.ar_world; ++q2)
+            if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), ar_epoch);
         }
+      }
+      if (p.ar_debug && ct == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 3] = globaltimer_ns();
+      // take one finished tile of a peer if its flag is already here
+      const int pt = peer_tile(pull_u);
+      if (ct == 0)
+        *pull_ready = pt < out_tiles && flag_reached(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch);
+      if (!comm_sync()) break;
+      if (*pull_ready) {
+        copy_tile(pt);
+        pull_u += gridDim.x;
       }
     }
     // final sweep: the tiles whose flags had not arrived yet
-    if (AR && !*abort_flag) {
+    if (!*abort_flag) {
       for (int pt = peer_tile(pull_u); pt < out_tiles; pull_u += gridDim.x, pt = peer_tile(pull_u)) {
-        if (et == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch, p.ar_limit_ns,
-                                     p.status))
+        if (ct == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch, p.ar_limit_ns, p.status))
           *abort_flag = 1;
-        if (!epi_sync()) break;
+        if (!comm_sync()) break;
         copy_tile(pt);
       }
     }
@@ -764,7 +796,7 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   int tiles = m_tiles * n_tiles * p.split_k;
   int grid = tiles < a.num_sms ? tiles : a.num_sms;
   if (grid < 1) return nullptr;
-  kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+  kern<<<grid, p.ar_world > 1 ? NUM_THREADS + 128 : NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
   count_launch();
   if (p.split_k > 1) {
     long long n4 = static_cast<long long>(a.M) * (a.N / 4);
