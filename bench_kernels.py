@@ -209,6 +209,9 @@ def main():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True))
         report(f"flash fwd B{B} S{S} causal (tcgen05)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         with torch.no_grad():
+            s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=2))
+        report(f"flash fwd B{B} S{S} causal (tcgen05, output in TMEM, lazy rescale)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=1))
         report(f"flash fwd B{B} S{S} causal (warp-level mma.sync)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         o = C.attention(q, k, v, scale=D ** -0.5, causal=True)

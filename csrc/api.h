@@ -129,7 +129,7 @@ const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
 // tcgen05 forward for causal self-attention with head_dim 128 (csrc/kernels/flash_tc.cu)
 bool flash_fwd_tc_supported(const FlashArgs& a);
 size_t flash_fwd_tc_workspace_elems(const FlashArgs& a);
-const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream);
+const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy = false);
 
 // ---- vocabulary rows ----
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,

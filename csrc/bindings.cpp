@@ -725,7 +725,8 @@ void fill_flash(ferrl::FlashArgs& a, const Tensor& q, const Tensor& k, const Ten
   a.scale = scale; a.causal = causal; a.window = window; a.q_offset = q_offset;
 }
 
-// variant: 0 = tcgen05 kernel where it applies (causal self-attention, head_dim 128), 1 = warp-level kernel
+// variant: 0 = tcgen05 kernel where it applies (causal self-attention, head_dim 128), 1 = warp-level kernel,
+// 2 = tcgen05 kernel with the output kept in TMEM and rescaled lazily
 std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Tensor& v, double scale, bool causal,
                                      int64_t window, int64_t q_offset, int64_t variant) {
   c10::cuda::CUDAGuard guard(q.device());
@@ -734,9 +735,9 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   Tensor o = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
   Tensor lse = at::empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
-  if (variant == 0 && ferrl::flash_fwd_tc_supported(a)) {
+  if ((variant == 0 || variant == 2) && ferrl::flash_fwd_tc_supported(a)) {
     Tensor vt = at::empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
-    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream()));
+    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 2));
     return {o, lse};
   }
   FERRL_CHECK(ferrl::flash_fwd(a, stream()));

@@ -612,8 +612,12 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
 }
 
+// Three stages of 32 keys (48 KB at head_dim 128) let four CTAs share an SM: 592 CTA slots take the
+// 1024 (row, kv-head) items of a 128-row batch in two waves instead of three.
+constexpr int MSTAGES = 3;
+
 template <int D, int REP>
-__global__ void __launch_bounds__(PWARPS * 32)
+__global__ void __launch_bounds__(PWARPS * 32, (D <= 128 && REP <= 4) ? 4 : 1)
 decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                        const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
                        const int* __restrict__ block_table, int bt_stride, int page,
@@ -660,7 +664,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   };
   auto issue = [&](int tt) {
     if (tt < n_tiles) {
-      uint8_t* st = psm + (tt % PSTAGES) * STAGE_BYTES;
+      uint8_t* st = psm + (tt % MSTAGES) * STAGE_BYTES;
       const int j0 = s0 + tt * PTK;
       for (int c = threadIdx.x; c < CHUNKS; c += PWARPS * 32) {
         const int key = c / CPR, part = c % CPR;
@@ -681,12 +685,12 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
   for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
 #pragma unroll
-  for (int tt = 0; tt < PSTAGES - 1; ++tt) issue(tt);
+  for (int tt = 0; tt < MSTAGES - 1; ++tt) issue(tt);
   for (int tt = 0; tt < n_tiles; ++tt) {
-    cp_async_wait<PSTAGES - 2>();
+    cp_async_wait<MSTAGES - 2>();
     __syncthreads();
-    issue(tt + PSTAGES - 1);
-    const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % PSTAGES) * STAGE_BYTES));
+    issue(tt + MSTAGES - 1);
+    const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % MSTAGES) * STAGE_BYTES));
     const uint32_t vt = kt + PTK * ROW_BYTES;
     const int key0 = warp * 8;                        // this warp's 8 keys of the tile
     const int j0 = s0 + tt * PTK + key0;
@@ -845,7 +849,7 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
   }
 #define FERRL_DECODE_MMA(DD, RR)                                                                                    \
   if (!launched && a.D == DD && rep == RR && a.no_pipe == 0) {                                                        \
-    constexpr size_t msm_bytes = static_cast<size_t>(PSTAGES) * 2 * PTK * DD * 2;                                     \
+    constexpr size_t msm_bytes = static_cast<size_t>(MSTAGES) * 2 * PTK * DD * 2;                                     \
     auto mk = decode_attn_mma_kernel<DD, RR>;                                                                         \
     static bool mset = false;                                                                                         \
     if (!mset) {                                                                                                      \

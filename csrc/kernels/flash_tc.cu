@@ -297,6 +297,264 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
+// Second form of the same kernel: the running output stays in TMEM (the P V MMAs accumulate into it
+// across tiles), a thread reads its score row once and keeps it in registers, P is double-buffered
+// and the output is rescaled lazily - only when the row maximum grew by more than 2^8 since the last
+// rescale.  Per tile a softmax thread then has one round of TMEM loads instead of three.
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__global__ void __launch_bounds__(192, 1)
+flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmVt, FlashTcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;                    // 32 KB
+  uint8_t* sK = sQ + TILE;               // 2 x 32 KB
+  uint8_t* sV = sK + 2 * TILE;           // 2 x 32 KB
+  uint8_t* sP = sV + 2 * TILE;           // 2 x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE);
+  uint64_t* q_full = bars;               // [1]
+  uint64_t* k_full = bars + 1;           // [2]
+  uint64_t* k_empty = bars + 3;          // [2]
+  uint64_t* v_full = bars + 5;           // [2]
+  uint64_t* v_empty = bars + 7;          // [2]
+  uint64_t* s_full = bars + 9;           // [2]
+  uint64_t* s_empty = bars + 11;         // [2]
+  uint64_t* p_full = bars + 13;          // [2] softmax wrote P[buf]
+  uint64_t* p_free = bars + 15;          // [2] the P V MMAs reading P[buf] have retired (O includes that tile)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qt = (p.S + FT - 1) / FT;
+  const int qt = n_qt - 1 - static_cast<int>(blockIdx.x);     // longest rows first
+  const int hq = blockIdx.y, b = blockIdx.z;
+  const int hk = hq / (p.Hq / p.Hkv);
+  const int q0 = qt * FT;
+  const int n_kv = qt + 1;                                    // causal: tiles 0..qt
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 4);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&p_full[i], 4);
+      mbar_init(&p_free[i], 1);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tO = tmem_base + 256;     // running output, accumulated by the P V MMAs across tiles
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      mbar_expect_tx(q_full, TILE);
+      tma_load_2d(sQ, &tmQ, q_full, hq * FD, b * p.S + q0);
+      tma_load_2d(sQ + ATOM, &tmQ, q_full, hq * FD + 64, b * p.S + q0);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_expect_tx(&k_full[st], TILE);
+        tma_load_2d(sK + st * TILE, &tmK, &k_full[st], hk * FD, b * p.S + j * FT);
+        tma_load_2d(sK + st * TILE + ATOM, &tmK, &k_full[st], hk * FD + 64, b * p.S + j * FT);
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
+        mbar_expect_tx(&v_full[st], TILE);
+        tma_load_2d(sV + st * TILE, &tmVt, &v_full[st], j * FT, (b * p.Hkv + hk) * FD);
+        tma_load_2d(sV + st * TILE + ATOM, &tmVt, &v_full[st], j * FT + 64, (b * p.Hkv + hk) * FD);
+      }
+      if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(10000);   // let copies in flight land before shared memory goes away
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ------------------------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      auto issue_qk = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+        tc_fence_after();
+        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE);
+#pragma unroll
+        for (int ks = 0; ks < FD / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * ATOM;
+          umma(tS[st], make_smem_desc(qa + off) + 2 * (ks & 3), make_smem_desc(ka + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+        return true;
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusWaitTimeoutMma);
+      if (ok) ok = issue_qk(0);
+      for (int j = 0; j < n_kv && ok; ++j) {
+        if (j + 1 < n_kv) ok = issue_qk(j + 1);
+        if (!ok) break;
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        const int pb = j & 1;
+        if (!mbar_wait(&p_full[pb], ph, abort_flag, p.status, kStatusWaitTimeoutMma) ||
+            !mbar_wait(&v_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t pa = smem_u32(sP + pb * TILE), va = smem_u32(sV + st * TILE);
+#pragma unroll
+        for (int ks = 0; ks < FT / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * ATOM;
+          umma(tO, make_smem_desc(pa + off) + 2 * (ks & 3), make_smem_desc(va + off) + 2 * (ks & 3), idesc, (j > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&p_free[pb]);
+        umma_commit(&v_empty[st]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------------- softmax + output (one row per thread)
+    const int q = warp & 3;
+    const int r = q * 32 + lane;                  // row inside the tile == TMEM lane
+    const int row = q0 + r;                       // query position
+    const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
+    const float c = p.scale * kLog2e;
+    float m_used = -INFINITY, l_run = 0.f;      // probabilities are taken relative to m_used
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(&s_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      tc_fence_after();
+      // the whole score row in registers: one round of TMEM loads, one wait
+      uint32_t sv[FT];
+      tmem_ld32(tS[st] + lane_sel + 0, sv + 0);
+      tmem_ld32(tS[st] + lane_sel + 32, sv + 32);
+      tmem_ld32(tS[st] + lane_sel + 64, sv + 64);
+      tmem_ld32(tS[st] + lane_sel + 96, sv + 96);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[st]);       // the next-but-one Q K^T may overwrite this buffer
+      const int k0 = j * FT;
+      const int limit = min(p.S, (j == qt) ? row + 1 : p.S) - k0;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int e = 0; e < FT; ++e)
+        if (e < limit) mx = fmaxf(mx, __uint_as_float(sv[e]));
+      const float m_new = fmaxf(m_used, mx);
+      // Lazy rescale: O (in TMEM) and l are only brought to the new maximum when it grew by more than
+      // 2^8 since the last rescale; smaller growth just makes the probabilities of this tile larger.
+      const bool need = (j > 0) && ((m_new - m_used) * c > 8.f);
+      if (j == 0) m_used = m_new;
+      if (__any_sync(0xffffffffu, need)) {
+        // O must contain every earlier tile before it is touched: wait for P V of tile j-1
+        if (!mbar_wait(&p_free[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+        tc_fence_after();
+        const float corr = need ? exp2f((m_used - m_new) * c) : 1.f;
+        if (need) {
+          m_used = m_new;
+          l_run *= corr;
+        }
+#pragma unroll 1
+        for (int cc = 0; cc < FD; cc += 32) {
+          uint32_t ov[32];
+          tmem_ld32(tO + lane_sel + cc, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) ov[e] = __float_as_uint(__uint_as_float(ov[e]) * corr);
+          tmem_st32(tO + lane_sel + cc, ov);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+      }
+      // P[j & 1] is free again once P V of tile j-2 has retired
+      const int pb = j & 1;
+      if (j >= 2 && !mbar_wait(&p_free[pb], ((j >> 1) - 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      const float mc = m_used * c;
+      float ps = 0.f;
+      uint8_t* prow = sP + pb * TILE + r * 128;
+#pragma unroll
+      for (int ch = 0; ch < FT / 8; ++ch) {
+        uint4 w;
+        __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int i0 = ch * 8 + 2 * e;
+          const float p0 = (i0 < limit) ? exp2f(__uint_as_float(sv[i0]) * c - mc) : 0.f;
+          const float p1 = (i0 + 1 < limit) ? exp2f(__uint_as_float(sv[i0 + 1]) * c - mc) : 0.f;
+          ps += p0 + p1;
+          wh[e] = __floats2bfloat162_rn(p0, p1);
+        }
+        *reinterpret_cast<uint4*>(prow + (ch >> 3) * ATOM + (((ch & 7) ^ (r & 7)) << 4)) = w;
+      }
+      l_run += ps;
+      fence_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[pb]);
+    }
+    // the last P V completes the output
+    if (ok && n_kv > 0 &&
+        !mbar_wait(&p_free[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue))
+      ok = false;
+    tc_fence_after();
+    if (ok && row < p.S) {
+      const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+      __nv_bfloat16* orow = p.out + b * p.o_bs + static_cast<long long>(row) * p.o_ts + hq * FD;
+#pragma unroll 1
+      for (int cc = 0; cc < FD; cc += 32) {
+        uint32_t ov[32];
+        tmem_ld32(tO + lane_sel + cc, ov);
+        tmem_ld_wait();
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          uint4 w;
+          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            wh[e] = __floats2bfloat162_rn(__uint_as_float(ov[ch * 8 + 2 * e]) * inv, __uint_as_float(ov[ch * 8 + 2 * e + 1]) * inv);
+          reinterpret_cast<uint4*>(orow + cc)[ch] = w;
+        }
+      }
+      if (p.lse)
+        p.lse[(static_cast<long long>(b) * p.Hq + hq) * p.S + row] = (l_run > 0.f) ? m_used * p.scale + logf(l_run) : -INFINITY;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+  }
+}
+
 }  // namespace
 
 bool flash_fwd_tc_supported(const FlashArgs& a) {
@@ -313,7 +571,7 @@ size_t flash_fwd_tc_workspace_elems(const FlashArgs& a) {
 }
 
 // `vt_ws`: bf16 workspace of flash_fwd_tc_workspace_elems(a) elements, 16-byte aligned
-const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream) {
+const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy) {
   if (!flash_fwd_tc_supported(a)) return "flash_fwd_tc: unsupported arguments";
   if (a.B == 0) return nullptr;
   const int s_pad = (a.Sk + 63) / 64 * 64;
@@ -330,15 +588,17 @@ const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStrea
   FlashTcParams p{};
   p.out = static_cast<__nv_bfloat16*>(a.o); p.o_bs = a.o_bs; p.o_ts = a.o_ts; p.lse = a.lse;
   p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status;
-  constexpr int smem = 6 * TILE + 1024 + 256;
+  constexpr int smem = 6 * TILE + 1024 + 256, smem2 = 7 * TILE + 1024 + 256;
   static bool set = false;
   if (!set) {
-    if (cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess)
       return "flash_fwd_tc: cannot reserve shared memory";
     set = true;
   }
   dim3 grid((a.Sq + FT - 1) / FT, a.Hq, a.B);
-  flash_fwd_tc_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmVt, p);
+  if (lazy) flash_fwd_tc2_kernel<<<grid, 192, smem2, stream>>>(tmQ, tmK, tmVt, p);
+  else flash_fwd_tc_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmVt, p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "flash_fwd_tc launch failed";
 }

@@ -342,7 +342,8 @@ def test_lora_grad_matches_fp32(M, R, C):
 
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 1, 2, 1), (2, 100, 4, 2), (1, 128, 2, 2), (2, 129, 8, 2), (1, 300, 4, 1),
                                         (2, 1536, 8, 2)])
-def test_flash_forward_tcgen05(B, S, Hq, Hkv):
+@pytest.mark.parametrize("variant", [0, 2])
+def test_flash_forward_tcgen05(B, S, Hq, Hkv, variant):
     """Causal head-dim-128 forward on tcgen05 (TMA-fed Q K^T and P V with accumulators in TMEM)
     against fp32 attention; the warp-level backward runs on the log-sum-exp it writes."""
     from ferrl_b200.ops import cuda as C, eager as E
@@ -353,7 +354,7 @@ def test_flash_forward_tcgen05(B, S, Hq, Hkv):
     q, k, v = wide.split([Hq * D, Hkv * D, Hkv * D], dim=-1)           # strided views, as the model passes them
     q, k, v = q.reshape(B, S, Hq, D), k.reshape(B, S, Hkv, D), v.reshape(B, S, Hkv, D)
     scale = 1 / math.sqrt(D)
-    o = C.attention(q, k, v, scale=scale, causal=True)
+    o = C.attention(q, k, v, scale=scale, causal=True, variant=variant)
     torch.cuda.synchronize()
     assert C.kernel_status() == 0
     o_warp = C.attention(q, k, v, scale=scale, causal=True, variant=1)
