@@ -24,6 +24,9 @@ SO_PATH = os.path.join(ROOT, "ferrl_b200", "_C.so")
 LAUNCHER_SRC = os.path.join(CSRC, "native", "sandbox_launcher.cpp")
 LAUNCHER_BIN = os.path.join(ROOT, "ferrl_b200", "bin", "ferrl-sandbox-launch")
 
+IO_SRC = os.path.join(CSRC, "native", "st_reader.cpp")
+IO_LIB = os.path.join(ROOT, "ferrl_b200", "bin", "libferrl_io.so")
+
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "--use_fast_math", "-Xcompiler", "-fPIC", "-Xptxas", "-v", "--expt-relaxed-constexpr"]
 
@@ -61,6 +64,14 @@ def build_launcher(force: bool = False) -> str:
     return LAUNCHER_BIN
 
 
+def build_io(force: bool = False) -> str:
+    """Host-only shared library (no CUDA, no torch): the safetensors range reader."""
+    os.makedirs(os.path.dirname(IO_LIB), exist_ok=True)
+    if force or not os.path.exists(IO_LIB) or os.path.getmtime(IO_LIB) < os.path.getmtime(IO_SRC):
+        _run(["g++", "-O2", "-std=c++17", "-shared", "-fPIC", "-pthread", "-o", IO_LIB, IO_SRC])
+    return IO_LIB
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     import torch
     from torch.utils import cpp_extension as ce
@@ -71,6 +82,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     cpp = sorted(p for p in glob.glob(os.path.join(CSRC, "**", "*.cpp"), recursive=True)
                  if os.sep + "native" + os.sep not in p)   # csrc/native holds standalone host programs
     build_launcher(force)
+    build_io(force)
     nvcc = _nvcc()
     cuda_home = os.path.dirname(os.path.dirname(nvcc))
     inc = [f"-I{p}" for p in ce.include_paths()] + [f"-I{os.path.join(cuda_home, 'include')}"]
@@ -107,6 +119,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
         _run(link)
         with open(stamp, "w") as f:
             f.write(want)
+    keep = {os.path.basename(o) for o in objs}
+    for name in os.listdir(BUILD):   # objects of earlier source versions
+        base = name[:-4] if name.endswith(".log") else name
+        if base.endswith(".o") and base not in keep:
+            os.remove(os.path.join(BUILD, name))
     return SO_PATH
 
 

@@ -6,8 +6,9 @@ dispatch on ``config.json``'s ``model_type`` into Qwen3 / Qwen3.5 / Gemma 4
 ``:987-1010`` (Llama is library-only); a frozen-policy digest over config and
 weight bytes ``:269-307`` that checkpoints bind to.  Rank-local streaming reads
 only the bytes of this rank's shard (``sharded_safetensors.rs:644-750``); here
-that is done by the native range reader in ``ferrl_b200.native`` when built,
-else by ``safetensors`` slicing, which also touches only the requested rows.
+that is done by the native range reader (``ferrl_b200.native.SafetensorsFile``:
+threaded positional reads into pinned host memory); ``safetensors`` slicing is the
+fallback when the helper library cannot be built.
 """
 from __future__ import annotations
 
@@ -50,12 +51,30 @@ class PolicyLoadIdentity:
         return h.hexdigest()
 
 
+class _SafeOpenFile:
+    """The ``safetensors`` library behind the same three calls as the native reader."""
+
+    def __init__(self, handle):
+        self.h = handle
+
+    def keys(self):
+        return list(self.h.keys())
+
+    def get(self, name):
+        return self.h.get_tensor(name)
+
+    def rows(self, name, start, n):
+        return self.h.get_slice(name)[start:start + n]
+
+    def cols(self, name, start, n):
+        return self.h.get_slice(name)[:, start:start + n]
+
+
 class TensorSource:
     """Name -> tensor access over one or many safetensors files, with row/column
     range reads so a TP rank never materialises a full matrix."""
 
-    def __init__(self, model_dir: str):
-        from safetensors import safe_open
+    def __init__(self, model_dir: str, native: bool = True):
         self.dir = model_dir
         idx = os.path.join(model_dir, "model.safetensors.index.json")
         if os.path.exists(idx):
@@ -65,9 +84,20 @@ class TensorSource:
         else:
             self.files = ["model.safetensors"]
             self.weight_map = None
-        self._open = {f: safe_open(os.path.join(model_dir, f), framework="pt") for f in self.files}
+        self._open = {f: self._open_file(os.path.join(model_dir, f), native) for f in self.files}
         if self.weight_map is None:
             self.weight_map = {k: "model.safetensors" for k in self._open["model.safetensors"].keys()}
+
+    @staticmethod
+    def _open_file(path: str, native: bool):
+        if native:
+            try:
+                from ..native import SafetensorsFile
+                return SafetensorsFile(path)
+            except (OSError, RuntimeError):   # helper library missing and no compiler: library fallback
+                pass
+        from safetensors import safe_open
+        return _SafeOpenFile(safe_open(path, framework="pt"))
 
     def names(self):
         return list(self.weight_map.keys())
@@ -76,13 +106,13 @@ class TensorSource:
         return name in self.weight_map
 
     def get(self, name: str) -> torch.Tensor:
-        return self._open[self.weight_map[name]].get_tensor(name)
+        return self._open[self.weight_map[name]].get(name)
 
     def rows(self, name: str, start: int, n: int) -> torch.Tensor:
-        return self._open[self.weight_map[name]].get_slice(name)[start:start + n]
+        return self._open[self.weight_map[name]].rows(name, start, n)
 
     def cols(self, name: str, start: int, n: int) -> torch.Tensor:
-        return self._open[self.weight_map[name]].get_slice(name)[:, start:start + n]
+        return self._open[self.weight_map[name]].cols(name, start, n)
 
     def files_sha256(self) -> str:
         h = hashlib.sha256()
