@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|rmsnorm|swiglu|qk_norm_rope|logprob|moe_grouped|gdn_decode   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc2|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -120,6 +120,18 @@ def profile_case(name, C):
         bb = torch.rand(B_, Hv_, device=dev)
         S = torch.zeros(B_, Hv_, 128, 128, device=dev)
         fn = lambda: C.gdn_decode_step(qd, kd, vd, gg, bb, S, True, 1e-6)
+    elif name == "gdn_chunk":
+        B_, T_, Hk_, Hv_ = 8, 1536, 16, 32
+        qc, kc_, vc_ = rnd(B_, T_, Hk_, 128), rnd(B_, T_, Hk_, 128), rnd(B_, T_, Hv_, 128)
+        gc = -torch.rand(B_, T_, Hv_, device=dev)
+        bc = torch.rand(B_, T_, Hv_, device=dev)
+        fn = lambda: C.gdn_chunk_fwd(qc, kc_, vc_, gc, bc)
+    elif name == "lora_grad":
+        u, xx = rnd(24576, 48), rnd(24576, 4096)
+        fn = lambda: C.lib().lora_grad(u, xx)
+    elif name == "flash_tc2":
+        q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+        fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=2)
     else:
         raise SystemExit(f"unknown profile case {name!r}")
     evs = []
@@ -199,6 +211,46 @@ def main():
         s = T(lambda: C.gemm(a, b, a2, b2))
         report("gemm train qkv + LoRA k-slab (R=48)", s, 2 * (M * K + N * K + M * N), 2 * M * N * (K + R))
         del a, b, a2, b2
+    if want("chain"):
+        # The four projections of a decode step over LAYERS distinct weight sets, back to back in one
+        # CUDA graph: what a decode step's GEMMs cost with the L2 state a real step leaves (clean
+        # weight lines of the previous layer, no dirty flush buffer).  Inputs (LAYERS x 444 MB) are
+        # far larger than L2, so no flush between iterations.
+        LAYERS, Bd = 8, 128
+        ws = [[torch.randn(n, k, device=dev, dtype=bf) * 0.02 for n, k in ((6144, H), (H, H), (2 * F, H), (H, F))]
+              for _ in range(LAYERS)]
+        x = torch.randn(Bd, H, device=dev, dtype=bf)
+        xo = torch.randn(Bd, H, device=dev, dtype=bf)
+        xf = torch.randn(Bd, F, device=dev, dtype=bf)
+        wbytes = sum(w.numel() * 2 for w in ws[0])
+
+        def chain(mm):
+            for wq, wo, wg, wd in ws:
+                mm(x, wq)
+                mm(xo, wo)
+                mm(x, wg)
+                mm(xf, wd)
+
+        for label, mm in (("tcgen05 planner", lambda a, b: C.gemm(a, b)),
+                          ("cuBLAS (library reference)", lambda a, b: torch.matmul(a, b.t()))):
+            chain(mm)
+            torch.cuda.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                chain(mm)
+            for _ in range(3):
+                gr.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            for _ in range(args.iters):
+                gr.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            s = e0.elapsed_time(e1) * 1e-3 / (args.iters * LAYERS)
+            report(f"decode GEMM chain per layer B{Bd}, {label}", s, wbytes, 2 * Bd * wbytes / 2,
+                   f"{LAYERS} layers per graph, inputs > L2")
+        del ws
     if want("attn"):
         B, S = 16, 1536
         q = torch.randn(B, S, HQ, D, device=dev, dtype=bf, requires_grad=True)
