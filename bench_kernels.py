@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc2|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -129,6 +129,11 @@ def profile_case(name, C):
     elif name == "lora_grad":
         u, xx = rnd(24576, 48), rnd(24576, 4096)
         fn = lambda: C.lib().lora_grad(u, xx)
+    elif name == "flash_bwd":
+        q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+        dd = rnd(8, 1536, 32, 128)
+        o_, lse_ = C.lib().flash_fwd(q, k, v, 128 ** -0.5, True, 0, 0, 1)
+        fn = lambda: C.lib().flash_bwd(q, k, v, o_, lse_, dd, 128 ** -0.5, True, 0, 0, 0)
     elif name == "flash_tc2":
         q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
         fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=2)
@@ -269,7 +274,11 @@ def main():
         o = C.attention(q, k, v, scale=D ** -0.5, causal=True)
         do = torch.randn_like(o)
         s = T(lambda: torch.autograd.grad(o, (q, k, v), do, retain_graph=True))
-        report(f"flash bwd B{B} S{S} causal", s, 0, 3.5 * fl, "7 matmuls / 2 of fwd's 2")
+        report(f"flash bwd B{B} S{S} causal (tcgen05, dQ + dK/dV kernels)", s, 0, 2.5 * fl, "5 matmuls of the algorithm counted (the two kernels run 7)")
+        with torch.no_grad():
+            o2, lse2 = C.lib().flash_fwd(q, k, v, D ** -0.5, True, 0, 0, 1)
+            s = T(lambda: C.lib().flash_bwd(q, k, v, o2, lse2, do, D ** -0.5, True, 0, 0, 1))
+        report(f"flash bwd B{B} S{S} causal (warp-level mma.sync)", s, 0, 2.5 * fl, "5 matmuls")
         Bd, Smax = 128, 1536
         qd = torch.randn(Bd, HQ, D, device=dev, dtype=bf)
         kc = torch.randn(Bd, Smax, HKV, D, device=dev, dtype=bf)

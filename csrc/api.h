@@ -130,6 +130,9 @@ const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
 bool flash_fwd_tc_supported(const FlashArgs& a);
 size_t flash_fwd_tc_workspace_elems(const FlashArgs& a);
 const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy = false);
+// tcgen05 backward for the same domain (csrc/kernels/flash_bwd_tc.cu); desc_mode is a diagnostic switch
+bool flash_bwd_tc_supported(const FlashArgs& a);
+const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream, int desc_mode = 0);
 
 // ---- vocabulary rows ----
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,

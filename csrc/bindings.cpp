@@ -746,7 +746,7 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
 
 std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                                              const Tensor& lse, const Tensor& d_o, double scale, bool causal,
-                                             int64_t window, int64_t q_offset) {
+                                             int64_t window, int64_t q_offset, int64_t variant) {
   c10::cuda::CUDAGuard guard(q.device());
   ferrl::FlashArgs a{};
   fill_flash(a, q, k, v, scale, causal, window, q_offset);
@@ -761,6 +761,11 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   a.dk = dk.data_ptr(); a.dk_bs = dk.stride(0); a.dk_ts = dk.stride(1);
   a.dv = dv.data_ptr(); a.dv_bs = dv.stride(0); a.dv_ts = dv.stride(1);
   a.delta = delta.data_ptr<float>();
+  // variant 0: tcgen05 kernels where they apply; 1: warp-level kernels; 3: tcgen05 with the diagnostic descriptor mode
+  if (variant != 1 && ferrl::flash_bwd_tc_supported(a)) {
+    FERRL_CHECK(ferrl::flash_bwd_tc(a, status_word(), stream(), variant == 3 ? 1 : 0));
+    return {dq, dk, dv};
+  }
   FERRL_CHECK(ferrl::flash_bwd(a, stream()));
   return {dq, dk, dv};
 }
@@ -940,7 +945,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
-  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);
   m.def("sample_rows(Tensor logits, Tensor global_rows, int seed, Tensor? draw_dev, int draw, float temperature, float top_p) -> (Tensor, Tensor)", &sample_rows);

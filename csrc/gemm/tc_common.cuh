@@ -53,6 +53,12 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   }
   return true;
 }
+// The same wait taken by a whole warp, with one answer for all its lanes: warp-collective
+// instructions (tcgen05.ld/st, __syncwarp) may follow either outcome without divergence.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  const bool r = mbar_wait(bar, parity, abort_flag, status, code);
+  return __all_sync(0xffffffffu, r);
+}
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -450,7 +450,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
       const uint32_t ph = (j >> 1) & 1;
-      if (!mbar_wait(&s_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       tc_fence_after();
       // the whole score row in registers: one round of TMEM loads, one wait
       uint32_t sv[FT];
@@ -475,7 +475,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (j == 0) m_used = m_new;
       if (__any_sync(0xffffffffu, need)) {
         // O must contain every earlier tile before it is touched: wait for P V of tile j-1
-        if (!mbar_wait(&p_free[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+        if (!mbar_wait_warp(&p_free[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
         tc_fence_after();
         const float corr = need ? exp2f((m_used - m_new) * c) : 1.f;
         if (need) {
@@ -496,7 +496,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       // P[j & 1] is free again once P V of tile j-2 has retired
       const int pb = j & 1;
-      if (j >= 2 && !mbar_wait(&p_free[pb], ((j >> 1) - 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
+      if (j >= 2 && !mbar_wait_warp(&p_free[pb], ((j >> 1) - 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       const float mc = m_used * c;
       float ps = 0.f;
       uint8_t* prow = sP + pb * TILE + r * 128;
@@ -521,28 +521,31 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
     // the last P V completes the output
     if (ok && n_kv > 0 &&
-        !mbar_wait(&p_free[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue))
+        !mbar_wait_warp(&p_free[(n_kv - 1) & 1], ((n_kv - 1) >> 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue))
       ok = false;
     tc_fence_after();
-    if (ok && row < p.S) {
+    if (ok) {      // warp-uniform: the TMEM loads are warp-collective, only the stores are per row
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       __nv_bfloat16* orow = p.out + b * p.o_bs + static_cast<long long>(row) * p.o_ts + hq * FD;
 #pragma unroll 1
       for (int cc = 0; cc < FD; cc += 32) {
         uint32_t ov[32];
+        __syncwarp();   // lanes that skipped the stores rejoin before the collective load
         tmem_ld32(tO + lane_sel + cc, ov);
         tmem_ld_wait();
+        if (row < p.S) {
 #pragma unroll
-        for (int ch = 0; ch < 4; ++ch) {
-          uint4 w;
-          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+          for (int ch = 0; ch < 4; ++ch) {
+            uint4 w;
+            __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
 #pragma unroll
-          for (int e = 0; e < 4; ++e)
-            wh[e] = __floats2bfloat162_rn(__uint_as_float(ov[ch * 8 + 2 * e]) * inv, __uint_as_float(ov[ch * 8 + 2 * e + 1]) * inv);
-          reinterpret_cast<uint4*>(orow + cc)[ch] = w;
+            for (int e = 0; e < 4; ++e)
+              wh[e] = __floats2bfloat162_rn(__uint_as_float(ov[ch * 8 + 2 * e]) * inv, __uint_as_float(ov[ch * 8 + 2 * e + 1]) * inv);
+            reinterpret_cast<uint4*>(orow + cc)[ch] = w;
+          }
         }
       }
-      if (p.lse)
+      if (p.lse && row < p.S)
         p.lse[(static_cast<long long>(b) * p.Hq + hq) * p.S + row] = (l_run > 0.f) ? m_used * p.scale + logf(l_run) : -INFINITY;
     }
   }

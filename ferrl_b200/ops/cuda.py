@@ -288,7 +288,7 @@ class _Flash(torch.autograd.Function):
     def forward(ctx, q, k, v, scale, causal, window, q_offset, variant=0):
         o, lse = lib().flash_fwd(q, k, v, scale, causal, window, q_offset, variant)
         ctx.save_for_backward(q, k, v, o, lse)
-        ctx.meta = (scale, causal, window, q_offset)
+        ctx.meta = (scale, causal, window, q_offset, 1 if variant == 1 else 0)
         return o
 
     @staticmethod

@@ -367,3 +367,38 @@ def test_flash_forward_tcgen05(B, S, Hq, Hkv, variant):
     ref.backward(do)
     o.backward(do.to(torch.bfloat16))
     assert _rel(wide.grad, wf.grad) < 3e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 64, 2, 2), (1, 128, 4, 1), (2, 200, 4, 2), (1, 333, 8, 2), (2, 1536, 8, 2)])
+def test_flash_backward_tcgen05(B, S, Hq, Hkv):
+    """Causal head-dim-128 backward on tcgen05 (dQ kernel and dK/dV kernel, operands read through
+    K-major and MN-major descriptors) against fp32 autograd and against the warp-level kernels."""
+    from ferrl_b200.ops import cuda as C, eager as E
+    dev = _dev()
+    D = 128
+    g = torch.Generator(device=dev).manual_seed(B * 11 + S)
+    q = torch.randn(B, S, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
+    do = torch.randn(B, S, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+    scale = 1 / math.sqrt(D)
+    o, lse = C.lib().flash_fwd(q, k, v, scale, True, 0, 0, 1)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    E.attention(qf, kf, vf, scale=scale, causal=True).backward(do.float())
+    ref = (qf.grad, kf.grad, vf.grad)
+    warp = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 1)
+    got = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 0)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    errs = [_rel(a, b) for a, b in zip(got, ref)]
+    if max(errs) >= 3e-2:   # say whether the exchanged descriptor offsets would have matched
+        alt = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 3)
+        alt_errs = [_rel(a, b) for a, b in zip(alt, ref)]
+        raise AssertionError(f"dq/dk/dv rel err {errs}; with exchanged offsets {alt_errs}; "
+                             f"warp-level {[_rel(a, b) for a, b in zip(warp, ref)]}")
+    for a, b in zip(got, warp):
+        assert _rel(a, b) < 3e-2
+    again = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 0)
+    for a, b in zip(got, again):
+        assert torch.equal(a, b)       # fixed summation order
