@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc1|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -134,7 +134,10 @@ def profile_case(name, C):
         dd = rnd(8, 1536, 32, 128)
         o_, lse_ = C.lib().flash_fwd(q, k, v, 128 ** -0.5, True, 0, 0, 1)
         fn = lambda: C.lib().flash_bwd(q, k, v, o_, lse_, dd, 128 ** -0.5, True, 0, 0, 0)
-    elif name == "flash_tc2":
+    elif name == "flash_tc2":   # the default form (output accumulated in TMEM); "flash_tc1" is the first form
+        q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+        fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=0)
+    elif name == "flash_tc1":
         q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
         fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=2)
     else:
@@ -237,6 +240,8 @@ def main():
                 mm(xf, wd)
 
         for label, mm in (("tcgen05 planner", lambda a, b: C.gemm(a, b)),
+                          ("tcgen05 planner, weights prefetched under the previous kernel (dependent launch)",
+                           lambda a, b: C.gemm(a, b, static_b=True)),
                           ("cuBLAS (library reference)", lambda a, b: torch.matmul(a, b.t()))):
             chain(mm)
             torch.cuda.synchronize()
@@ -264,10 +269,10 @@ def main():
         fl = 4 * B * HQ * S * S * D / 2
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True))
-        report(f"flash fwd B{B} S{S} causal (tcgen05)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        report(f"flash fwd B{B} S{S} causal (tcgen05, output in TMEM, lazy rescale)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=2))
-        report(f"flash fwd B{B} S{S} causal (tcgen05, output in TMEM, lazy rescale)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        report(f"flash fwd B{B} S{S} causal (tcgen05, first form: output in registers)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=1))
         report(f"flash fwd B{B} S{S} causal (warp-level mma.sync)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)

@@ -38,6 +38,9 @@ struct GemmArgs {
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
   PeerTable ar_stage, ar_outbuf, ar_flags;
   unsigned long long* ar_debug;
+  // launch as a programmatic dependent of the stream predecessor: weights are prefetched before the
+  // dependency wait (only where B is never written by an earlier kernel of the same stream)
+  int pdl;
 };
 void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out,
                double* est_out = nullptr);
@@ -123,6 +126,7 @@ struct FlashArgs {
   // backward only
   const void* d_o; void* dq; void* dk; void* dv; float* delta;
   long long do_bs, do_ts, dq_bs, dq_ts, dk_bs, dk_ts, dv_bs, dv_ts;
+  unsigned long long* debug;   // optional time stamps (tcgen05 backward), else null
 };
 const char* flash_fwd(const FlashArgs& a, cudaStream_t s);
 const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
@@ -130,9 +134,10 @@ const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
 bool flash_fwd_tc_supported(const FlashArgs& a);
 size_t flash_fwd_tc_workspace_elems(const FlashArgs& a);
 const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy = false);
-// tcgen05 backward for the same domain (csrc/kernels/flash_bwd_tc.cu); desc_mode is a diagnostic switch
+// tcgen05 backward for the same domain (csrc/kernels/flash_bwd_tc.cu)
 bool flash_bwd_tc_supported(const FlashArgs& a);
-const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream, int desc_mode = 0);
+size_t flash_bwd_tc_scratch_floats(const FlashArgs& a);   // size of a.delta for flash_bwd_tc
+const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream);
 
 // ---- vocabulary rows ----
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,

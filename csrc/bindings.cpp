@@ -72,7 +72,7 @@ void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(in
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
             const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split, int64_t two_cta,
-            const optional<Tensor>& debug, int64_t cluster_k, int64_t stream_k) {
+            const optional<Tensor>& debug, int64_t cluster_k, int64_t stream_k, bool static_b) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "gemm: CUDA tensors required");
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
@@ -98,6 +98,9 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
     a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
   }
   a.status = status_word(); a.num_sms = num_sms(); a.force_bn = static_cast<int>(force_bn);
+  // static_b: B (and B2) are weights that no kernel earlier in the stream writes, so a decode-shaped
+  // call may start streaming them before its predecessor has finished (programmatic dependent launch)
+  a.pdl = (static_b && a.M <= 256) ? 1 : 0;
   if (two_cta > 0 && !out_f32) {   // forced
     TORCH_CHECK(two_cta == 128 || two_cta == 256, "gemm: two_cta must be 128 or 256");
     a.two_cta = static_cast<int>(two_cta);
@@ -737,7 +740,7 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
   if ((variant == 0 || variant == 2) && ferrl::flash_fwd_tc_supported(a)) {
     Tensor vt = at::empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
-    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 2));
+    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 0));   // 0: output in TMEM (default); 2: first form
     return {o, lse};
   }
   FERRL_CHECK(ferrl::flash_fwd(a, stream()));
@@ -746,7 +749,8 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
 
 std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& o,
                                              const Tensor& lse, const Tensor& d_o, double scale, bool causal,
-                                             int64_t window, int64_t q_offset, int64_t variant) {
+                                             int64_t window, int64_t q_offset, int64_t variant,
+                                             const optional<Tensor>& debug) {
   c10::cuda::CUDAGuard guard(q.device());
   ferrl::FlashArgs a{};
   fill_flash(a, q, k, v, scale, causal, window, q_offset);
@@ -761,9 +765,15 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   a.dk = dk.data_ptr(); a.dk_bs = dk.stride(0); a.dk_ts = dk.stride(1);
   a.dv = dv.data_ptr(); a.dv_bs = dv.stride(0); a.dv_ts = dv.stride(1);
   a.delta = delta.data_ptr<float>();
-  // variant 0: tcgen05 kernels where they apply; 1: warp-level kernels; 3: tcgen05 with the diagnostic descriptor mode
+  if (debug.has_value() && debug->defined()) {
+    TORCH_CHECK(debug->scalar_type() == at::kLong && debug->is_contiguous() && debug->numel() >= 1024, "flash_bwd: debug int64[>=1024]");
+    a.debug = reinterpret_cast<unsigned long long*>(debug->data_ptr<int64_t>());
+  }
+  // variant 0: tcgen05 kernels where they apply; 1: warp-level kernels
   if (variant != 1 && ferrl::flash_bwd_tc_supported(a)) {
-    FERRL_CHECK(ferrl::flash_bwd_tc(a, status_word(), stream(), variant == 3 ? 1 : 0));
+    Tensor stats = at::empty({static_cast<long long>(ferrl::flash_bwd_tc_scratch_floats(a))}, lse.options());
+    a.delta = stats.data_ptr<float>();
+    FERRL_CHECK(ferrl::flash_bwd_tc(a, status_word(), stream()));
     return {dq, dk, dv};
   }
   FERRL_CHECK(ferrl::flash_bwd(a, stream()));
@@ -912,7 +922,7 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 }  // namespace
 
 TORCH_LIBRARY(ferrl_b200, m) {
-  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
+  m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0, bool static_b=False) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
@@ -945,7 +955,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
-  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0, Tensor? debug=None) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);
   m.def("sample_rows(Tensor logits, Tensor global_rows, int seed, Tensor? draw_dev, int draw, float temperature, float top_p) -> (Tensor, Tensor)", &sample_rows);

@@ -59,6 +59,13 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
+// Programmatic dependent launch.  A kernel launched with launch_pdl() may begin while its stream
+// predecessor is still running, once every CTA of the predecessor has executed pdl_trigger() (or
+// exited); it must execute pdl_wait() before it touches anything the predecessor writes, and before
+// it writes anything the predecessor reads.  Both instructions are no-ops in an ordinary launch.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 template <typename T> __device__ __forceinline__ float to_f(T v);
 template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -67,6 +74,24 @@ template <> __device__ __forceinline__ float from_f<float>(float v) { return v; 
 template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
 #endif  // __CUDACC__
+
+#ifdef __CUDACC__
+// Launch `kern` so that it may overlap the tail of its stream predecessor (see pdl_wait()).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
 
 // Count of kernel launches issued by this library (host side, for benchmarks).
 void count_launch(int n = 1);

@@ -75,6 +75,24 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
   d |= static_cast<uint64_t>(2) << 61;
   return d;
 }
+// The same descriptor `bytes` further into shared memory.  Only the address field (low word)
+// changes and it cannot carry, so this is one 32-bit add: the single MMA-issuing thread must not
+// spend more instructions per MMA than the MMA takes to execute.
+__device__ __forceinline__ uint64_t desc_adv(uint64_t d, uint32_t bytes) {
+  return (d & 0xFFFFFFFF00000000ull) | static_cast<uint64_t>(static_cast<uint32_t>(d) + (bytes >> 4));
+}
+// MN-major operand tile written by TMA as [rows x 64-col atoms], 128B swizzle: the contraction index
+// is the row (8-row groups 1024 bytes apart = stride offset), the 64-element column groups are
+// `atom_bytes` apart (leading offset).
+__device__ __forceinline__ uint64_t make_smem_desc_mn(uint32_t smem_addr, uint32_t atom_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>(atom_bytes >> 4) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
@@ -88,6 +106,20 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t desc_a, uint64_t 
 }
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// One lane of a converged warp.  The MMA warps keep all 32 lanes in the loop (waits, descriptor
+// arithmetic) and let the elected lane issue: the operands of tcgen05.mma live in uniform registers,
+// and only code that the whole warp executes can compute them there.  Issued from inside an
+// `if (lane == 0)` region every operand is first moved from a vector register, which costs more
+// than a 128x64 MMA takes to execute.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

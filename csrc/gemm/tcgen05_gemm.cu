@@ -62,6 +62,11 @@ struct GemmParams {
   int ar_max_tiles;
   uint64_t ar_limit_ns;
   unsigned long long* ar_debug;   // optional [grid][16 tiles][4] globaltimer stamps of the exchange
+  // Launched as a programmatic dependent: the producer fills its ring with the weight (B) halves of
+  // its first k-blocks, which no earlier kernel writes, before it waits for the stream predecessor;
+  // only then does it fetch the activation (A) halves.  Everything else in the kernel is ordered
+  // behind those loads by the pipeline's barriers.
+  int pdl;
 };
 
 // flag layout inside each rank's flag buffer: ready[tile][kMaxRanks] then done[tile]
@@ -272,6 +277,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const int kb1 = (p.K + BK - 1) / BK;
   const int kb2 = (p.K2 + BK - 1) / BK;
   const int kb_total = kb1 + kb2;
+  if (threadIdx.x == 0) pdl_trigger();   // a dependent kernel may start its own prologue now
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -305,6 +311,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      int pre = 0;          // k-blocks of the first tile whose loads were issued around the dependency wait
+      if (p.pdl && static_cast<int>(blockIdx.x) < total_tiles) {
+        int ks, mi, ni;
+        tile_coords(blockIdx.x, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
+        pre = min(C::STAGES, kb_end - kb_begin);
+        for (int i = 0; i < pre; ++i) {           // first pass over the ring: every stage is free
+          const int kb = kb_begin + i;
+          uint8_t* sb = smem + i * C::STAGE_BYTES + BM * BK * 2;
+          mbar_expect_tx(&full[i], C::STAGE_BYTES);
+          if (kb < kb1) tma_load_2d(sb, &tmB, &full[i], kb * BK, ni * BN);
+          else tma_load_2d(sb, &tmB2, &full[i], (kb - kb1) * BK, ni * BN);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) {
+          const int kb = kb_begin + i;
+          uint8_t* sa = smem + i * C::STAGE_BYTES;
+          if (kb < kb1) tma_load_2d(sa, &tmA, &full[i], kb * BK, mi * BM);
+          else tma_load_2d(sa, &tmA2, &full[i], (kb - kb1) * BK, mi * BM);
+        }
+        if (pre == C::STAGES) phase = 1; else stage = pre;
+      }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int ks, mi, ni;
         tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
@@ -314,7 +342,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           if (e < 0) continue;
           b_row0 += e * p.N;
         }
-        const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
+        int kb_begin = ks * p.kb_per_split;
+        const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
+        if (tile == static_cast<int>(blockIdx.x)) kb_begin += pre;
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer, wait_limit)) {
             ok = false;
@@ -796,7 +826,13 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   int tiles = m_tiles * n_tiles * p.split_k;
   int grid = tiles < a.num_sms ? tiles : a.num_sms;
   if (grid < 1) return nullptr;
-  kern<<<grid, p.ar_world > 1 ? NUM_THREADS + 128 : NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+  p.pdl = (a.pdl && p.ar_world <= 1 && !p.tile_expert && p.split_k == 1) ? 1 : 0;
+  if (p.pdl) {
+    if (launch_pdl(kern, dim3(grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, tmA, tmB, tmA2, tmB2, p) != cudaSuccess)
+      return "gemm launch (programmatic dependent) failed";
+  } else {
+    kern<<<grid, p.ar_world > 1 ? NUM_THREADS + 128 : NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p);
+  }
   count_launch();
   if (p.split_k > 1) {
     long long n4 = static_cast<long long>(a.M) * (a.N / 4);
@@ -1206,6 +1242,7 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int kb_total = kb1 + kb2;
   const int kb_per = (kb_total + S - 1) / S;
   const int kb_begin = min(kb_total, rank * kb_per), kb_end = min(kb_total, kb_begin + kb_per);
+  if (threadIdx.x == 0) pdl_trigger();   // a dependent kernel may start its own prologue now
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < C::STAGES; ++s) {
@@ -1232,7 +1269,26 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int kb = kb_begin; kb < kb_end; ++kb) {
+      int pre = 0;
+      if (p.pdl) {
+        pre = min(C::STAGES, kb_end - kb_begin);
+        for (int i = 0; i < pre; ++i) {           // first pass over the ring: every stage is free
+          const int kb = kb_begin + i;
+          uint8_t* sb = smem + i * C::STAGE_BYTES + BM * BK * 2;
+          mbar_expect_tx(&full[i], C::STAGE_BYTES);
+          if (kb < kb1) tma_load_2d(sb, &tmB, &full[i], kb * BK, ni * BN);
+          else tma_load_2d(sb, &tmB2, &full[i], (kb - kb1) * BK, ni * BN);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i) {
+          const int kb = kb_begin + i;
+          uint8_t* sa = smem + i * C::STAGE_BYTES;
+          if (kb < kb1) tma_load_2d(sa, &tmA, &full[i], kb * BK, mi * BM);
+          else tma_load_2d(sa, &tmA2, &full[i], (kb - kb1) * BK, mi * BM);
+        }
+        if (pre == C::STAGES) phase = 1; else stage = pre;
+      }
+      for (int kb = kb_begin + pre; kb < kb_end; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) {
           ok = false;
           break;
@@ -1426,13 +1482,16 @@ const char* launch_ksplit(const GemmArgs& a, cudaStream_t stream) {
   cfg.blockDim = dim3(NUM_THREADS);
   cfg.dynamicSmemBytes = C::SMEM_BYTES;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = S;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  p.pdl = a.pdl ? 1 : 0;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = p.pdl ? 2 : 1;
   if (cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmA2, tmB2, p) != cudaSuccess) return "cluster split-k gemm launch failed";
   count_launch();
   return nullptr;

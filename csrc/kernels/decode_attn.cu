@@ -29,6 +29,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const int* __restrict__ block_table, int bt_stride, int page, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ ws, int Hq, int Hkv, int D, long long seq_stride, long long tok_stride,
                    float scale, int window, int n_splits) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   extern __shared__ float sm[];
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int rep = Hq / Hkv;
@@ -187,6 +188,7 @@ decode_attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int bt_stride, int page,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                         long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   constexpr int LPK = D / 16;        // lanes per key
   constexpr int KPW = 32 / LPK;      // keys per warp per step
   constexpr int UNROLL = (REP >= 6) ? 2 : 4;   // key steps in flight (bounded by the register file)
@@ -384,6 +386,7 @@ decode_attn_pipe_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         const int* __restrict__ block_table, int bt_stride, int page,
                         __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                         long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   constexpr int LPK = D / 16;                 // lanes per key
   constexpr int KPW = 32 / LPK;               // keys per warp per step
   constexpr int STEPS = PTK / (PWARPS * KPW); // steps per stage
@@ -623,6 +626,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        const int* __restrict__ block_table, int bt_stride, int page,
                        __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                        long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   static_assert(REP <= 8, "query heads of one KV head must fit rows 0..7 of the MMA tile");
   constexpr int ROW_BYTES = D * 2;
   constexpr int CPR = ROW_BYTES / 16;                  // 16-byte chunks per row
@@ -783,6 +787,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
 __global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
                                       int n_splits) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   const long long head = blockIdx.x;
   const float* base = ws + head * n_splits * (D + 2);
   float m = -INFINITY;

@@ -121,7 +121,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tS0 = tmem_base, tS1 = tmem_base + 128;
   const uint32_t tPV = tmem_base + 256;
 
   if (warp == 0) {
@@ -156,11 +156,12 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE);
+        const uint64_t dq = make_smem_desc(smem_u32(sQ)), dk = make_smem_desc(smem_u32(sK + st * TILE));
+        const uint32_t ts = st ? tS1 : tS0;
 #pragma unroll
         for (int ks = 0; ks < FD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * ATOM;
-          umma(tS[st], make_smem_desc(qa + off) + 2 * (ks & 3), make_smem_desc(ka + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * ATOM + (ks & 3) * 32;
+          umma(ts, desc_adv(dq, off), desc_adv(dk, off), idesc, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
         umma_commit(&k_empty[st]);
@@ -180,11 +181,11 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           break;
         }
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP), va = smem_u32(sV + st * TILE);
+        const uint64_t dp = make_smem_desc(smem_u32(sP)), dvt = make_smem_desc(smem_u32(sV + st * TILE));
 #pragma unroll
         for (int ks = 0; ks < FT / 16; ++ks) {
           const uint32_t off = (ks >> 2) * ATOM;
-          umma(tPV, make_smem_desc(pa + off) + 2 * (ks & 3), make_smem_desc(va + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+          umma(tPV, desc_adv(dp, off + (ks & 3) * 32), desc_adv(dvt, off + (ks & 3) * 32), idesc, ks > 0 ? 1u : 0u);
         }
         umma_commit(pv_full);
         umma_commit(&v_empty[st]);
@@ -214,7 +215,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll 1
       for (int cc = 0; cc < FT; cc += 32) {
         uint32_t v[32];
-        tmem_ld32(tS[st] + lane_sel + cc, v);
+        tmem_ld32((st ? tS1 : tS0) + lane_sel + cc, v);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 32; ++e)
@@ -227,7 +228,7 @@ flash_fwd_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll 1
       for (int cc = 0; cc < FT; cc += 32) {
         uint32_t v[32];
-        tmem_ld32(tS[st] + lane_sel + cc, v);
+        tmem_ld32((st ? tS1 : tS0) + lane_sel + cc, v);
         tmem_ld_wait();
         float pr[32];
 #pragma unroll
@@ -369,7 +370,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tS0 = tmem_base, tS1 = tmem_base + 128;
   const uint32_t tO = tmem_base + 256;     // running output, accumulated by the P V MMAs across tiles
 
   if (warp == 0) {
@@ -404,11 +405,12 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
         if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
         tc_fence_after();
-        const uint32_t qa = smem_u32(sQ), ka = smem_u32(sK + st * TILE);
+        const uint64_t dq = make_smem_desc(smem_u32(sQ)), dk = make_smem_desc(smem_u32(sK + st * TILE));
+        const uint32_t ts = st ? tS1 : tS0;
 #pragma unroll
         for (int ks = 0; ks < FD / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * ATOM;
-          umma(tS[st], make_smem_desc(qa + off) + 2 * (ks & 3), make_smem_desc(ka + off) + 2 * (ks & 3), idesc, ks > 0 ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * ATOM + (ks & 3) * 32;
+          umma(ts, desc_adv(dq, off), desc_adv(dk, off), idesc, ks > 0 ? 1u : 0u);
         }
         umma_commit(&s_full[st]);
         umma_commit(&k_empty[st]);
@@ -428,11 +430,11 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           break;
         }
         tc_fence_after();
-        const uint32_t pa = smem_u32(sP + pb * TILE), va = smem_u32(sV + st * TILE);
+        const uint64_t dp = make_smem_desc(smem_u32(sP + pb * TILE)), dvt = make_smem_desc(smem_u32(sV + st * TILE));
 #pragma unroll
         for (int ks = 0; ks < FT / 16; ++ks) {
           const uint32_t off = (ks >> 2) * ATOM;
-          umma(tO, make_smem_desc(pa + off) + 2 * (ks & 3), make_smem_desc(va + off) + 2 * (ks & 3), idesc, (j > 0 || ks > 0) ? 1u : 0u);
+          umma(tO, desc_adv(dp, off + (ks & 3) * 32), desc_adv(dvt, off + (ks & 3) * 32), idesc, (j > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&p_free[pb]);
         umma_commit(&v_empty[st]);
@@ -454,10 +456,10 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       tc_fence_after();
       // the whole score row in registers: one round of TMEM loads, one wait
       uint32_t sv[FT];
-      tmem_ld32(tS[st] + lane_sel + 0, sv + 0);
-      tmem_ld32(tS[st] + lane_sel + 32, sv + 32);
-      tmem_ld32(tS[st] + lane_sel + 64, sv + 64);
-      tmem_ld32(tS[st] + lane_sel + 96, sv + 96);
+      tmem_ld32((st ? tS1 : tS0) + lane_sel + 0, sv + 0);
+      tmem_ld32((st ? tS1 : tS0) + lane_sel + 32, sv + 32);
+      tmem_ld32((st ? tS1 : tS0) + lane_sel + 64, sv + 64);
+      tmem_ld32((st ? tS1 : tS0) + lane_sel + 96, sv + 96);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();

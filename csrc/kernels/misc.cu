@@ -33,6 +33,7 @@ __device__ __forceinline__ float act_grad(float g, int act) {
 // gate_up [rows, 2F] laid out [gate | up] -> out [rows, F]
 template <typename T>
 __global__ void glu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, int act) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   long long n = rows * F;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -46,6 +47,7 @@ __global__ void glu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ out, lo
 // bf16 vector forms: 8 elements per thread per step, 16-byte loads and stores; F % 8 == 0
 __global__ void glu_fwd_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long rows,
                                    int F, int act) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   const int chunks = F / 8;
   const long long n = rows * chunks;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;

@@ -26,6 +26,7 @@ template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ res, const T* __restrict__ w,
                                const T* __restrict__ gate, T* __restrict__ y, T* __restrict__ h_out, int H, float eps,
                                int zero_centered) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const T* xr = x + row * H;
@@ -113,6 +114,7 @@ __global__ void rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ gate,
                                    __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, int H, float eps,
                                    int zero_centered) {
+  pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int chunks = H / 8;

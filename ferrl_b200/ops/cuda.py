@@ -48,13 +48,17 @@ def _bf16(t):
 
 # ----------------------------------------------------------------- GEMM
 def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0, force_split=0, two_cta=0, debug=None,
-         cluster_k=0, stream_k=0):
+         cluster_k=0, stream_k=0, static_b=False):
     """``a [M,K] @ b[N,K]^T (+ a2 @ b2^T) (+ residual)`` on the tcgen05 kernel.
     Tile width and k-split are planned from the shape unless forced; ``two_cta`` (128 or 256)
     selects the two-SM kernel with 256 x ``two_cta`` tiles; ``cluster_k`` (with ``force_bn``) the
     cluster split-k kernel (``-1`` keeps the planner away from it); ``stream_k`` 1 forces and -1
-    forbids the stream-k kernel for decode shapes (0: planner decides)."""
-    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn, force_split, two_cta, debug, cluster_k, stream_k)
+    forbids the stream-k kernel for decode shapes (0: planner decides).  ``static_b``: ``b`` is a
+    weight that no kernel earlier in the stream writes; a decode-shaped call (M <= 256) is then
+    launched as a programmatic dependent and streams its first weight tiles while the previous
+    kernel is still running."""
+    return lib().gemm(a, b, a2, b2, residual, out_f32, force_bn, force_split, two_cta, debug, cluster_k, stream_k,
+                      bool(static_b))
 
 
 def _pad8(t, dim):
@@ -90,7 +94,7 @@ class _LoraLinear(torch.autograd.Function):
             res2 = residual.reshape(-1, w.shape[0])
             if res2.stride(-1) != 1:
                 res2 = res2.contiguous()
-        y = gemm(x2, w, t, b16, res2)
+        y = gemm(x2, w, t, b16, res2, static_b=a_stack is None)   # no adapter slab: a frozen (or merged) weight
         ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
         ctx.x_shape = x.shape
         ctx.x_grad = x.requires_grad

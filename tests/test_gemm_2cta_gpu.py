@@ -131,3 +131,42 @@ def test_stream_k(M, N, K, res, lora, f32):
         torch.cuda.synchronize()
         assert torch.equal(static, ys[0])
     assert C.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 6144, 4096), (128, 4096, 12288), (64, 24576, 4096), (7, 512, 192)])
+def test_gemm_dependent_launch_orders_activations(M, N, K):
+    """`static_b=True` launches a decode-shaped GEMM as a programmatic dependent: its weight tiles
+    stream while the previous kernel runs, the activation tiles only after it has finished.  The
+    activations are rewritten by the kernel just before every call, eagerly and in a replayed graph."""
+    from ferrl_b200.ops import cuda as C
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(M + N)
+    w = (torch.randn(N, K, device=dev, generator=g) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    a = torch.empty_like(x)
+
+    def step(scale):
+        torch.mul(x, scale, out=a)                 # the predecessor writes the activations
+        y = C.gemm(a, w, static_b=True)
+        return y
+
+    for i in range(6):
+        sc = 1.0 + 0.25 * i
+        y = step(sc)
+        ref = (x.float() * sc).to(torch.bfloat16).float() @ w.float().t()
+        assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2, i
+    assert C.kernel_status() == 0
+    sc_t = torch.ones((), device=dev)
+    torch.cuda.synchronize()
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        torch.mul(x, sc_t, out=a)
+        yg = C.gemm(a, w, static_b=True)
+        yg2 = C.gemm(yg[:, :K].contiguous() if N >= K else a, w, static_b=True)   # GEMM after GEMM-fed kernel
+    for i in range(4):
+        sc_t.fill_(0.5 + i)
+        gr.replay()
+        torch.cuda.synchronize()
+        ref = (x.float() * (0.5 + i)).to(torch.bfloat16).float() @ w.float().t()
+        assert ((yg.float() - ref).norm() / ref.norm()).item() < 1e-2, i
+    assert C.kernel_status() == 0

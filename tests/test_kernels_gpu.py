@@ -392,11 +392,7 @@ def test_flash_backward_tcgen05(B, S, Hq, Hkv):
     torch.cuda.synchronize()
     assert C.kernel_status() == 0
     errs = [_rel(a, b) for a, b in zip(got, ref)]
-    if max(errs) >= 3e-2:   # say whether the exchanged descriptor offsets would have matched
-        alt = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 3)
-        alt_errs = [_rel(a, b) for a, b in zip(alt, ref)]
-        raise AssertionError(f"dq/dk/dv rel err {errs}; with exchanged offsets {alt_errs}; "
-                             f"warp-level {[_rel(a, b) for a, b in zip(warp, ref)]}")
+    assert max(errs) < 3e-2, f"dq/dk/dv rel err {errs}; warp-level {[_rel(a, b) for a, b in zip(warp, ref)]}"
     for a, b in zip(got, warp):
         assert _rel(a, b) < 3e-2
     again = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 0)
