@@ -134,7 +134,7 @@ def profile_case(name, C):
         dd = rnd(8, 1536, 32, 128)
         o_, lse_ = C.lib().flash_fwd(q, k, v, 128 ** -0.5, True, 0, 0, 1)
         fn = lambda: C.lib().flash_bwd(q, k, v, o_, lse_, dd, 128 ** -0.5, True, 0, 0, 0)
-    elif name == "flash_tc2":   # the default form (output accumulated in TMEM); "flash_tc1" is the first form
+    elif name == "flash_tc2":   # the default form (output and P in TMEM); "flash_tc1" is the first form
         q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
         fn = lambda: C.attention(q, k, v, scale=128 ** -0.5, causal=True, variant=0)
     elif name == "flash_tc1":
@@ -219,6 +219,18 @@ def main():
         s = T(lambda: C.gemm(a, b, a2, b2))
         report("gemm train qkv + LoRA k-slab (R=48)", s, 2 * (M * K + N * K + M * N), 2 * M * N * (K + R))
         del a, b, a2, b2
+    if want("slab"):
+        # cost of the adapter k-slab as a function of its width (the k-block is 64 wide whatever R is)
+        M, N, K = 24576, 6144, H
+        a = torch.randn(M, K, device=dev, dtype=bf)
+        b = torch.randn(N, K, device=dev, dtype=bf) * 0.02
+        s = T(lambda: C.gemm(a, b))
+        report("gemm train qkv, no slab", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
+        for R in (16, 48, 64):
+            a2, b2 = torch.randn(M, R, device=dev, dtype=bf), torch.randn(N, R, device=dev, dtype=bf)
+            s = T(lambda: C.gemm(a, b, a2, b2))
+            report(f"gemm train qkv + LoRA k-slab R={R}", s, 2 * (M * K + N * K + M * N), 2 * M * N * (K + R))
+        del a, b, a2, b2
     if want("chain"):
         # The four projections of a decode step over LAYERS distinct weight sets, back to back in one
         # CUDA graph: what a decode step's GEMMs cost with the L2 state a real step leaves (clean
@@ -269,10 +281,13 @@ def main():
         fl = 4 * B * HQ * S * S * D / 2
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True))
-        report(f"flash fwd B{B} S{S} causal (tcgen05, output in TMEM, lazy rescale)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        report(f"flash fwd B{B} S{S} causal (tcgen05, output and P in TMEM, lazy rescale)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=2))
         report(f"flash fwd B{B} S{S} causal (tcgen05, first form: output in registers)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
+        with torch.no_grad():
+            s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=3))
+        report(f"flash fwd B{B} S{S} causal (tcgen05, output in TMEM, P through shared memory)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)
         with torch.no_grad():
             s = T(lambda: C.attention(q, k, v, scale=D ** -0.5, causal=True, variant=1))
         report(f"flash fwd B{B} S{S} causal (warp-level mma.sync)", s, 2 * B * S * (2 * HQ + 2 * HKV) * D, fl)

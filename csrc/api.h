@@ -133,7 +133,7 @@ const char* flash_bwd(const FlashArgs& a, cudaStream_t s);
 // tcgen05 forward for causal self-attention with head_dim 128 (csrc/kernels/flash_tc.cu)
 bool flash_fwd_tc_supported(const FlashArgs& a);
 size_t flash_fwd_tc_workspace_elems(const FlashArgs& a);
-const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy = false);
+const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, int form = 1);
 // tcgen05 backward for the same domain (csrc/kernels/flash_bwd_tc.cu)
 bool flash_bwd_tc_supported(const FlashArgs& a);
 size_t flash_bwd_tc_scratch_floats(const FlashArgs& a);   // size of a.delta for flash_bwd_tc

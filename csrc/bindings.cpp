@@ -738,9 +738,10 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   Tensor o = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
   Tensor lse = at::empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
-  if ((variant == 0 || variant == 2) && ferrl::flash_fwd_tc_supported(a)) {
+  if ((variant == 0 || variant == 2 || variant == 3) && ferrl::flash_fwd_tc_supported(a)) {
     Tensor vt = at::empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
-    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 0));   // 0: output in TMEM (default); 2: first form
+    // variant 0: output and P in TMEM (default); 3: output in TMEM, P through shared memory; 2: first form (output in registers)
+    FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 0 ? 2 : (variant == 3 ? 1 : 0)));
     return {o, lse};
   }
   FERRL_CHECK(ferrl::flash_fwd(a, stream()));

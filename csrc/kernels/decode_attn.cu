@@ -30,6 +30,7 @@ decode_attn_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    float* __restrict__ ws, int Hq, int Hkv, int D, long long seq_stride, long long tok_stride,
                    float scale, int window, int n_splits) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   extern __shared__ float sm[];
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int rep = Hq / Hkv;
@@ -189,6 +190,7 @@ decode_attn_fast_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                         long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   constexpr int LPK = D / 16;        // lanes per key
   constexpr int KPW = 32 / LPK;      // keys per warp per step
   constexpr int UNROLL = (REP >= 6) ? 2 : 4;   // key steps in flight (bounded by the register file)
@@ -387,6 +389,7 @@ decode_attn_pipe_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
                         __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                         long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   constexpr int LPK = D / 16;                 // lanes per key
   constexpr int KPW = 32 / LPK;               // keys per warp per step
   constexpr int STEPS = PTK / (PWARPS * KPW); // steps per stage
@@ -627,6 +630,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
                        long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   static_assert(REP <= 8, "query heads of one KV head must fit rows 0..7 of the MMA tile");
   constexpr int ROW_BYTES = D * 2;
   constexpr int CPR = ROW_BYTES / 16;                  // 16-byte chunks per row
@@ -788,6 +792,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 __global__ void decode_combine_kernel(const float* __restrict__ ws, __nv_bfloat16* __restrict__ out, int D,
                                       int n_splits) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   const long long head = blockIdx.x;
   const float* base = ws + head * n_splits * (D + 2);
   float m = -INFINITY;
@@ -861,7 +866,7 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
       cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(msm_bytes));             \
       mset = true;                                                                                                    \
     }                                                                                                                 \
-    mk<<<grid, PWARPS * 32, msm_bytes, s>>>(                                                                          \
+    launch_pdl(mk, grid, dim3(PWARPS * 32), msm_bytes, s,                                                             \
         static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
         static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
         static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.seq_stride, a.tok_stride, a.scale, a.window,  \
@@ -907,7 +912,8 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
   }
   count_launch();
   if (grid.z > 1) {
-    decode_combine_kernel<<<a.B * a.Hq, 128, 0, s>>>(a.workspace, static_cast<__nv_bfloat16*>(a.out), a.D, grid.z);
+    launch_pdl(decode_combine_kernel, dim3(a.B * a.Hq), dim3(128), 0, s, a.workspace, static_cast<__nv_bfloat16*>(a.out), a.D,
+               static_cast<int>(grid.z));
     count_launch();
   }
   return cudaGetLastError() == cudaSuccess ? nullptr : "decode_attn launch failed";

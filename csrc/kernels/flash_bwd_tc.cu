@@ -44,7 +44,7 @@ constexpr int ATOM128 = FT * 64 * 2;       // [128 rows x 64 cols] swizzle atom:
 constexpr int TILE128 = 2 * ATOM128;       // [128 x 128] bf16: 32 KB
 constexpr int ATOM64 = QH * 64 * 2;        // [64 rows x 64 cols]: 8 KB
 constexpr int TILE64 = 2 * ATOM64;         // [64 x 128] bf16: 16 KB
-constexpr int NST = 3;                     // Q/dO ring depth of the dK/dV kernel
+constexpr int NST = 4;                     // Q/dO ring depth of the dK/dV kernel
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kBMajorMN = 1u << 16;   // instruction descriptor: B operand is MN-major
 constexpr int BWD_THREADS = 320;
@@ -353,8 +353,14 @@ __global__ void __launch_bounds__(BWD_THREADS, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_constant__ CUtensorMap tmV,
                      const __grid_constant__ CUtensorMap tmQ64, const __grid_constant__ CUtensorMap tmdO64,
                      FlashBwdTcParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // The four-deep Q/dO ring leaves no room for alignment slack: the dynamic shared memory is declared
+  // 1024-byte aligned (the swizzled tiles need it) and the kernel refuses to run if it is not.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0) atomicCAS(p.status, kStatusOk, kStatusBadShape);
+    return;
+  }
   uint8_t* sK = smem;                       // 32 KB, resident
   uint8_t* sV = sK + TILE128;               // 32 KB, resident
   uint8_t* sQ = sV + TILE128;               // NST x 16 KB
@@ -655,7 +661,7 @@ const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream) {
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_bs = a.dv_bs; p.dv_ts = a.dv_ts;
   p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status; p.debug = a.debug;
   constexpr int smem_dq = 7 * TILE128 + 1024 + 256;
-  constexpr int smem_dkv = 2 * TILE128 + 2 * NST * TILE64 + 2 * ATOM128 + NST * QH * 8 + 1024 + 256;
+  constexpr int smem_dkv = 2 * TILE128 + 2 * NST * TILE64 + 2 * ATOM128 + NST * QH * 8 + 256;
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq) != cudaSuccess ||

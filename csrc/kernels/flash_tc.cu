@@ -315,6 +315,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// tcgen05.mma with the A operand in tensor memory (row i in lane i, two bf16 per 32-bit column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accum)
+      : "memory");
+}
+
+// PT: P stays in tensor memory (written with tcgen05.st as packed bf16, read by the P V MMAs as their
+// A operand), so it costs neither shared-memory writes nor shared-memory read bandwidth.
+template <bool PT>
 __global__ void __launch_bounds__(192, 1)
 flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmVt, FlashTcParams p) {
@@ -323,8 +336,8 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sQ = smem;                    // 32 KB
   uint8_t* sK = sQ + TILE;               // 2 x 32 KB
   uint8_t* sV = sK + 2 * TILE;           // 2 x 32 KB
-  uint8_t* sP = sV + 2 * TILE;           // 2 x 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + 2 * TILE);
+  uint8_t* sP = sV + 2 * TILE;           // 2 x 32 KB (absent when P stays in tensor memory)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + (PT ? 0 : 2 * TILE));
   uint64_t* q_full = bars;               // [1]
   uint64_t* k_full = bars + 1;           // [2]
   uint64_t* k_empty = bars + 3;          // [2]
@@ -372,6 +385,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tS1 = tmem_base + 128;
   const uint32_t tO = tmem_base + 256;     // running output, accumulated by the P V MMAs across tiles
+  const uint32_t tP0 = tmem_base + 384;    // PT: two P buffers of 64 columns (128 keys as bf16 pairs)
 
   if (warp == 0) {
     if (lane == 0) {
@@ -396,17 +410,18 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ------------------------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      auto issue_qk = [&](int j) -> bool {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
-        if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
-        tc_fence_after();
-        const uint64_t dq = make_smem_desc(smem_u32(sQ)), dk = make_smem_desc(smem_u32(sK + st * TILE));
-        const uint32_t ts = st ? tS1 : tS0;
+    // ------------------------------------------------------------------ MMA warp: all lanes walk the loop, one issues
+    constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+    const uint64_t dq = make_smem_desc(smem_u32(sQ));
+    auto issue_qk = [&](int j) -> bool {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait_warp(&k_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+      if (!mbar_wait_warp(&s_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutMma)) return false;
+      tc_fence_after();
+      const uint64_t dk = make_smem_desc(smem_u32(sK + st * TILE));
+      const uint32_t ts = st ? tS1 : tS0;
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < FD / 16; ++ks) {
           const uint32_t off = (ks >> 2) * ATOM + (ks & 3) * 32;
@@ -414,31 +429,37 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
         umma_commit(&s_full[st]);
         umma_commit(&k_empty[st]);
-        return true;
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag, p.status, kStatusWaitTimeoutMma);
-      if (ok) ok = issue_qk(0);
-      for (int j = 0; j < n_kv && ok; ++j) {
-        if (j + 1 < n_kv) ok = issue_qk(j + 1);
-        if (!ok) break;
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        const int pb = j & 1;
-        if (!mbar_wait(&p_full[pb], ph, abort_flag, p.status, kStatusWaitTimeoutMma) ||
-            !mbar_wait(&v_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) {
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint64_t dp = make_smem_desc(smem_u32(sP + pb * TILE)), dvt = make_smem_desc(smem_u32(sV + st * TILE));
+      }
+      __syncwarp();
+      return true;
+    };
+    bool ok = mbar_wait_warp(q_full, 0, abort_flag, p.status, kStatusWaitTimeoutMma);
+    if (ok) ok = issue_qk(0);
+    for (int j = 0; j < n_kv && ok; ++j) {
+      if (j + 1 < n_kv) ok = issue_qk(j + 1);
+      if (!ok) break;
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      const int pb = j & 1;
+      if (!mbar_wait_warp(&p_full[pb], ph, abort_flag, p.status, kStatusWaitTimeoutMma) ||
+          !mbar_wait_warp(&v_full[st], ph, abort_flag, p.status, kStatusWaitTimeoutMma)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const uint64_t dp = make_smem_desc(smem_u32(sP + pb * TILE)), dvt = make_smem_desc(smem_u32(sV + st * TILE));
+      const uint32_t acc0 = j > 0 ? 1u : 0u;
+      if (elect_one()) {
 #pragma unroll
         for (int ks = 0; ks < FT / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * ATOM;
-          umma(tO, desc_adv(dp, off + (ks & 3) * 32), desc_adv(dvt, off + (ks & 3) * 32), idesc, (j > 0 || ks > 0) ? 1u : 0u);
+          const uint32_t off = (ks >> 2) * ATOM + (ks & 3) * 32;
+          if (PT) umma_ts(tO, tP0 + pb * 64 + ks * 8, desc_adv(dvt, off), idesc, ks > 0 ? 1u : acc0);
+          else umma(tO, desc_adv(dp, off), desc_adv(dvt, off), idesc, ks > 0 ? 1u : acc0);
         }
         umma_commit(&p_free[pb]);
         umma_commit(&v_empty[st]);
       }
+      __syncwarp();
     }
   } else {
     // -------------------------------------------------------------------- softmax + output (one row per thread)
@@ -448,6 +469,7 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const uint32_t lane_sel = static_cast<uint32_t>(q * 32) << 16;
     const float c = p.scale * kLog2e;
     float m_used = -INFINITY, l_run = 0.f;      // probabilities are taken relative to m_used
+    const bool rows_ok = __all_sync(0xffffffffu, row < p.S);
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
@@ -466,10 +488,19 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (lane == 0) mbar_arrive(&s_empty[st]);       // the next-but-one Q K^T may overwrite this buffer
       const int k0 = j * FT;
       const int limit = min(p.S, (j == qt) ? row + 1 : p.S) - k0;
-      float mx = -INFINITY;
+      // tiles strictly below the diagonal need no mask (warp-uniform test); four independent chains
+      // for the maximum and for the sum, a single warp per scheduler has no other way to hide latency
+      const bool full = (j < qt) && rows_ok;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (full) {
 #pragma unroll
-      for (int e = 0; e < FT; ++e)
-        if (e < limit) mx = fmaxf(mx, __uint_as_float(sv[e]));
+        for (int e = 0; e < FT; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+      } else {
+#pragma unroll
+        for (int e = 0; e < FT; ++e)
+          if (e < limit) mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(sv[e]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       const float m_new = fmaxf(m_used, mx);
       // Lazy rescale: O (in TMEM) and l are only brought to the new maximum when it grew by more than
       // 2^8 since the last rescale; smaller growth just makes the probabilities of this tile larger.
@@ -501,23 +532,55 @@ flash_fwd_tc2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (j >= 2 && !mbar_wait_warp(&p_free[pb], ((j >> 1) - 1) & 1, abort_flag, p.status, kStatusWaitTimeoutEpilogue)) { ok = false; break; }
       const float mc = m_used * c;
       float ps = 0.f;
-      uint8_t* prow = sP + pb * TILE + r * 128;
+      if (PT) {
+        // packed in place: word i0/2 replaces a score that has already been consumed
+        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+        if (full) {
 #pragma unroll
-      for (int ch = 0; ch < FT / 8; ++ch) {
-        uint4 w;
-        __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+          for (int i0 = 0; i0 < FT; i0 += 2) {
+            const float p0 = exp2f(__uint_as_float(sv[i0]) * c - mc);
+            const float p1 = exp2f(__uint_as_float(sv[i0 + 1]) * c - mc);
+            ps4[(i0 >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            sv[i0 >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int i0 = ch * 8 + 2 * e;
-          const float p0 = (i0 < limit) ? exp2f(__uint_as_float(sv[i0]) * c - mc) : 0.f;
-          const float p1 = (i0 + 1 < limit) ? exp2f(__uint_as_float(sv[i0 + 1]) * c - mc) : 0.f;
-          ps += p0 + p1;
-          wh[e] = __floats2bfloat162_rn(p0, p1);
+          for (int i0 = 0; i0 < FT; i0 += 2) {
+            const float p0 = (i0 < limit) ? exp2f(__uint_as_float(sv[i0]) * c - mc) : 0.f;
+            const float p1 = (i0 + 1 < limit) ? exp2f(__uint_as_float(sv[i0 + 1]) * c - mc) : 0.f;
+            ps4[(i0 >> 1) & 3] += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            sv[i0 >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
-        *reinterpret_cast<uint4*>(prow + (ch >> 3) * ATOM + (((ch & 7) ^ (r & 7)) << 4)) = w;
+        ps = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+        l_run += ps;
+        tmem_st32(tP0 + pb * 64 + lane_sel, sv);
+        tmem_st32(tP0 + pb * 64 + lane_sel + 32, sv + 32);
+        tmem_st_wait();
+        tc_fence_before();
+      } else {
+        uint8_t* prow = sP + pb * TILE + r * 128;
+        float ps4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int ch = 0; ch < FT / 8; ++ch) {
+          uint4 w;
+          __nv_bfloat162* wh = reinterpret_cast<__nv_bfloat162*>(&w);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int i0 = ch * 8 + 2 * e;
+            const float p0 = (full || i0 < limit) ? exp2f(__uint_as_float(sv[i0]) * c - mc) : 0.f;
+            const float p1 = (full || i0 + 1 < limit) ? exp2f(__uint_as_float(sv[i0 + 1]) * c - mc) : 0.f;
+            ps4[e] += p0 + p1;
+            wh[e] = __floats2bfloat162_rn(p0, p1);
+          }
+          *reinterpret_cast<uint4*>(prow + (ch >> 3) * ATOM + (((ch & 7) ^ (r & 7)) << 4)) = w;
+        }
+        ps = (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
+        l_run += ps;
+        fence_async_smem();
       }
-      l_run += ps;
-      fence_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[pb]);
     }
@@ -576,7 +639,7 @@ size_t flash_fwd_tc_workspace_elems(const FlashArgs& a) {
 }
 
 // `vt_ws`: bf16 workspace of flash_fwd_tc_workspace_elems(a) elements, 16-byte aligned
-const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, bool lazy) {
+const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStream_t stream, int form) {
   if (!flash_fwd_tc_supported(a)) return "flash_fwd_tc: unsupported arguments";
   if (a.B == 0) return nullptr;
   const int s_pad = (a.Sk + 63) / 64 * 64;
@@ -593,16 +656,19 @@ const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStrea
   FlashTcParams p{};
   p.out = static_cast<__nv_bfloat16*>(a.o); p.o_bs = a.o_bs; p.o_ts = a.o_ts; p.lse = a.lse;
   p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status;
-  constexpr int smem = 6 * TILE + 1024 + 256, smem2 = 7 * TILE + 1024 + 256;
+  constexpr int smem = 6 * TILE + 1024 + 256, smem2 = 7 * TILE + 1024 + 256, smem3 = 5 * TILE + 1024 + 256;
   static bool set = false;
   if (!set) {
     if (cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd_tc2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess)
+        cudaFuncSetAttribute(flash_fwd_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess ||
+        cudaFuncSetAttribute(flash_fwd_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3) != cudaSuccess)
       return "flash_fwd_tc: cannot reserve shared memory";
     set = true;
   }
   dim3 grid((a.Sq + FT - 1) / FT, a.Hq, a.B);
-  if (lazy) flash_fwd_tc2_kernel<<<grid, 192, smem2, stream>>>(tmQ, tmK, tmVt, p);
+  // form 0: output in registers; 1: output in TMEM, P through shared memory; 2: output and P in TMEM
+  if (form == 2) flash_fwd_tc2_kernel<true><<<grid, 192, smem3, stream>>>(tmQ, tmK, tmVt, p);
+  else if (form == 1) flash_fwd_tc2_kernel<false><<<grid, 192, smem2, stream>>>(tmQ, tmK, tmVt, p);
   else flash_fwd_tc_kernel<<<grid, 192, smem, stream>>>(tmQ, tmK, tmVt, p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "flash_fwd_tc launch failed";

@@ -34,6 +34,7 @@ __device__ __forceinline__ float act_grad(float g, int act) {
 template <typename T>
 __global__ void glu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ out, long long rows, int F, int act) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   long long n = rows * F;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
        i += static_cast<long long>(gridDim.x) * blockDim.x) {
@@ -48,6 +49,7 @@ __global__ void glu_fwd_kernel(const T* __restrict__ gu, T* __restrict__ out, lo
 __global__ void glu_fwd_vec_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, long long rows,
                                    int F, int act) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   const int chunks = F / 8;
   const long long n = rows * chunks;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -302,7 +304,7 @@ const char* glu(int dtype, bool backward, const void* gu, const void* dout, void
       glu_bwd_vec_kernel<<<vgrid, 256, 0, s>>>(static_cast<const B*>(gu), static_cast<const B*>(dout), static_cast<B*>(out),
                                                rows, F, act);
     else
-      glu_fwd_vec_kernel<<<vgrid, 256, 0, s>>>(static_cast<const B*>(gu), static_cast<B*>(out), rows, F, act);
+      launch_pdl(glu_fwd_vec_kernel, dim3(vgrid), dim3(256), 0, s, static_cast<const B*>(gu), static_cast<B*>(out), rows, F, act);
   } else {
     using B = __nv_bfloat16;
     if (backward)

@@ -27,6 +27,7 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const T* __restrict__ re
                                const T* __restrict__ gate, T* __restrict__ y, T* __restrict__ h_out, int H, float eps,
                                int zero_centered) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const T* xr = x + row * H;
@@ -115,6 +116,7 @@ __global__ void rmsnorm_vec_kernel(const __nv_bfloat16* __restrict__ x, const __
                                    __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, int H, float eps,
                                    int zero_centered) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   __shared__ float red[32];
   const long long row = blockIdx.x;
   const int chunks = H / 8;
@@ -337,6 +339,8 @@ __global__ void qk_norm_rope_vec_kernel(const __nv_bfloat16* __restrict__ q_in, 
                                         __nv_bfloat16* __restrict__ k_out, const __nv_bfloat16* __restrict__ dq,
                                         const __nv_bfloat16* __restrict__ dk, long long n_tok, int Hq, int Hkv, int half,
                                         float eps, int zero_centered) {
+  pdl_trigger();
+  pdl_wait();      // may be launched as a programmatic dependent: nothing is read before the predecessor is done
   constexpr int D = 32 * EPL;
   const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
@@ -447,6 +451,8 @@ __global__ void qk_norm_rope_vec_kernel(const __nv_bfloat16* __restrict__ q_in, 
 template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, long long ldv, T* __restrict__ kc,
                                  T* __restrict__ vc, const int* __restrict__ kv_len, int smax, int HD) {
+  pdl_trigger();
+  pdl_wait();      // may be launched as a programmatic dependent: nothing is read before the predecessor is done
   const int b = blockIdx.x;
   const long long slot = static_cast<long long>(b) * smax + kv_len[b];
   if (kv_len[b] >= smax) return;  // cache full: drop rather than write out of bounds
@@ -464,9 +470,9 @@ static const char* rmsnorm_t(const void* x, const void* res, const void* w, cons
   if (rows == 0) return nullptr;
   if (sizeof(T) == 2 && vec_ok(H, x, res, w, gate, y, h_out)) {
     using B = __nv_bfloat16;
-    rmsnorm_vec_kernel<<<static_cast<unsigned>(rows), vec_threads(H), 0, s>>>(
-        static_cast<const B*>(x), static_cast<const B*>(res), static_cast<const B*>(w), static_cast<const B*>(gate),
-        static_cast<B*>(y), static_cast<B*>(h_out), H, eps, zc ? 1 : 0);
+    launch_pdl(rmsnorm_vec_kernel, dim3(static_cast<unsigned>(rows)), dim3(vec_threads(H)), 0, s,
+               static_cast<const B*>(x), static_cast<const B*>(res), static_cast<const B*>(w), static_cast<const B*>(gate),
+               static_cast<B*>(y), static_cast<B*>(h_out), H, eps, zc ? 1 : 0);
     count_launch();
     return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm launch failed";
   }
@@ -525,7 +531,7 @@ static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
     if (ok) {
       using B = __nv_bfloat16;
 #define FERRL_QKV(EPLV)                                                                                             \
-  qk_norm_rope_vec_kernel<EPLV, BWD><<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(                             \
+  launch_pdl(qk_norm_rope_vec_kernel<EPLV, BWD>, dim3(static_cast<unsigned>(blocks)), dim3(wpb * 32), 0, s,          \
       static_cast<const B*>(a.q_in), a.ld_q, static_cast<const B*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,               \
       static_cast<const B*>(a.qw), static_cast<const B*>(a.kw), a.cos_t, a.sin_t, a.pos64, a.pos32, a.pos_div,      \
       static_cast<B*>(a.q_out), static_cast<B*>(a.k_out), static_cast<const B*>(a.dq), static_cast<const B*>(a.dk), \
@@ -558,6 +564,8 @@ __global__ void kv_append_paged_kernel(const __nv_bfloat16* __restrict__ k, cons
                                        __nv_bfloat16* __restrict__ kc, __nv_bfloat16* __restrict__ vc,
                                        const int* __restrict__ kv_len, const int* __restrict__ table, int bt_stride,
                                        int page, int HD) {
+  pdl_trigger();
+  pdl_wait();      // may be launched as a programmatic dependent: nothing is read before the predecessor is done
   const int b = blockIdx.x;
   const int t = kv_len[b];
   if (t / page >= bt_stride) return;   // row is full: drop rather than write out of bounds
@@ -575,9 +583,9 @@ const char* kv_append_paged(const void* k, const void* v, long long ldv, void* k
   if ((HD % 8) || (ldv % 8) || (reinterpret_cast<uintptr_t>(k) & 15) || (reinterpret_cast<uintptr_t>(v) & 15) ||
       (reinterpret_cast<uintptr_t>(kc) & 15) || (reinterpret_cast<uintptr_t>(vc) & 15))
     return "kv_append_paged: 16-byte aligned rows required";
-  kv_append_paged_kernel<<<batch, 128, 0, s>>>(static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ldv,
-                                               static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, table,
-                                               bt_stride, page, HD);
+  launch_pdl(kv_append_paged_kernel, dim3(batch), dim3(128), 0, s, static_cast<const __nv_bfloat16*>(k),
+             static_cast<const __nv_bfloat16*>(v), ldv, static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, table,
+             bt_stride, page, HD);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "kv_append_paged launch failed";
 }
@@ -589,9 +597,9 @@ const char* kv_append(int dtype, const void* k, const void* v, long long ldv, vo
     kv_append_kernel<float><<<batch, 256, 0, s>>>(static_cast<const float*>(k), static_cast<const float*>(v), ldv,
                                                   static_cast<float*>(kc), static_cast<float*>(vc), kv_len, smax, HD);
   else
-    kv_append_kernel<__nv_bfloat16><<<batch, 256, 0, s>>>(
-        static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ldv,
-        static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, smax, HD);
+    launch_pdl(kv_append_kernel<__nv_bfloat16>, dim3(batch), dim3(256), 0, s,
+               static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), ldv,
+               static_cast<__nv_bfloat16*>(kc), static_cast<__nv_bfloat16*>(vc), kv_len, smax, HD);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "kv_append launch failed";
 }

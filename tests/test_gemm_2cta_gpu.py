@@ -170,3 +170,47 @@ def test_gemm_dependent_launch_orders_activations(M, N, K):
         ref = (x.float() * (0.5 + i)).to(torch.bfloat16).float() @ w.float().t()
         assert ((yg.float() - ref).norm() / ref.norm()).item() < 1e-2, i
     assert C.kernel_status() == 0
+
+
+def test_dependent_launch_chain_matches_reference():
+    """A decode-layer-like chain (RMSNorm -> projection -> GLU -> projection with residual) in which
+    every kernel is a programmatic dependent of the one before it, replayed from a CUDA graph with
+    fresh inputs, against the same chain in fp32."""
+    from ferrl_b200.ops import cuda as C
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(5)
+    Bt, H, F = 128, 1024, 2048
+    x = torch.randn(Bt, H, device=dev, generator=g).to(torch.bfloat16)
+    wn = (1 + 0.1 * torch.randn(H, device=dev, generator=g)).to(torch.bfloat16)
+    w1 = (torch.randn(2 * F, H, device=dev, generator=g) * 0.03).to(torch.bfloat16)
+    w2 = (torch.randn(H, F, device=dev, generator=g) * 0.03).to(torch.bfloat16)
+
+    def chain(inp):
+        h = C.rmsnorm(inp, wn, 1e-6)
+        gu = C.gemm(h, w1, static_b=True)
+        a = C.swiglu(gu)
+        return C.gemm(a, w2, residual=inp, static_b=True)
+
+    def ref(inp):
+        xf = inp.float()
+        h = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-6) * wn.float()).to(torch.bfloat16).float()
+        gu = (h @ w1.float().t()).to(torch.bfloat16).float()
+        a = (torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]).to(torch.bfloat16).float()
+        return xf + a @ w2.float().t()
+
+    with torch.no_grad():
+        y = chain(x)
+        r = ref(x)
+        assert ((y.float() - r).norm() / r.norm()).item() < 2e-2
+        xin = x.clone()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            yg = chain(xin)
+        for i in range(5):
+            xin.copy_(torch.randn(Bt, H, device=dev, generator=g).to(torch.bfloat16))
+            gr.replay()
+            torch.cuda.synchronize()
+            r = ref(xin)
+            assert ((yg.float() - r).norm() / r.norm()).item() < 2e-2, i
+    assert C.kernel_status() == 0

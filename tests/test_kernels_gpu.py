@@ -342,7 +342,7 @@ def test_lora_grad_matches_fp32(M, R, C):
 
 @pytest.mark.parametrize("B,S,Hq,Hkv", [(1, 1, 2, 1), (2, 100, 4, 2), (1, 128, 2, 2), (2, 129, 8, 2), (1, 300, 4, 1),
                                         (2, 1536, 8, 2)])
-@pytest.mark.parametrize("variant", [0, 2])
+@pytest.mark.parametrize("variant", [0, 2, 3])
 def test_flash_forward_tcgen05(B, S, Hq, Hkv, variant):
     """Causal head-dim-128 forward on tcgen05 (TMA-fed Q K^T and P V with accumulators in TMEM)
     against fp32 attention; the warp-level backward runs on the log-sum-exp it writes."""
