@@ -237,7 +237,13 @@ class GraphedDecodeStep:
         dev = logits.device
         B = self.B
         self.N = N
-        self.logits = torch.empty_like(logits)
+        # logits stay in the head GEMM's dtype inside the loop where the decoder offers that (the
+        # sampler upcasts element by element, so the draw is the same as from an fp32 copy)
+        self._decode = getattr(self.dec, "decode_native", None) or self.dec.decode
+        dt = logits.dtype
+        if self._decode is not self.dec.decode and logits.is_cuda:
+            dt = self.dec.m.head_weight().dtype
+        self.logits = torch.empty(logits.shape, dtype=dt, device=dev)
         self.rows = rows.clone()
         self.draw = torch.zeros(1, dtype=torch.int32, device=dev)
         self.finished = torch.zeros(B, dtype=torch.bool, device=dev)
@@ -255,7 +261,7 @@ class GraphedDecodeStep:
         self.comp_len += (~self.finished).to(torch.int64)
         if self.eos is not None:
             self.finished |= tok == self.eos
-        self.logits.copy_(self.dec.decode(tok))
+        self.logits.copy_(self._decode(tok))
         self.draw += 1
 
     @torch.no_grad()

@@ -402,6 +402,12 @@ class DenseCachedDecoder:
     @torch.no_grad()
     def decode(self, tokens: torch.Tensor) -> torch.Tensor:
         """Feed one token per row; returns next-token logits ``[B, V]`` float32."""
+        return self.decode_native(tokens).float()
+
+    @torch.no_grad()
+    def decode_native(self, tokens: torch.Tensor) -> torch.Tensor:
+        """``decode`` with the logits left in the head GEMM's output dtype (bf16 for a bf16 model): the
+        device sampler reads them as they are, which saves the fp32 copy of ``[B, V]`` every token."""
         m = self.m
         h = ops.embedding(tokens, m.embed)
         kv_next = self.kv_len + 1                 # shared by every layer: computed once per token
@@ -410,7 +416,7 @@ class DenseCachedDecoder:
             h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos)
         self.kv_len += 1
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
-        return ops.lora_linear(h, m.head_weight(), None, None).float()
+        return ops.lora_linear(h, m.head_weight(), None, None)
 
 
 class DensePagedDecoder(DenseCachedDecoder):
@@ -488,7 +494,7 @@ class DensePagedDecoder(DenseCachedDecoder):
             raise ValueError("group size differs from the one this cache was built for")
 
     @torch.no_grad()
-    def decode(self, tokens: torch.Tensor) -> torch.Tensor:
+    def decode_native(self, tokens: torch.Tensor) -> torch.Tensor:
         m = self.m
         h = ops.embedding(tokens, m.embed)
         kv_next = self.kv_len + 1
@@ -497,4 +503,4 @@ class DensePagedDecoder(DenseCachedDecoder):
             h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos, self.table)
         self.kv_len += 1
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
-        return ops.lora_linear(h, m.head_weight(), None, None).float()
+        return ops.lora_linear(h, m.head_weight(), None, None)
