@@ -63,6 +63,11 @@ struct QkNormRopeArgs {
   long long ld_dq, ld_dk;       // backward: token strides of the two gradient destinations
   const void* dq; const void* dk;                       // backward inputs (contiguous)
   long long n_tok; int Hq, Hkv, D, half; float eps; bool zero_centered;
+  // decode (forward, one token per row, vector kernel only): when kc is set the rotated K row and
+  // the V row of token t go straight to cache row kv_len[t] of sequence t (k_out is not written):
+  // dense caches [B, smax, Hkv, D], or pools [n_pages, page, Hkv, D] behind table[t, kv_len / page]
+  void* kc; void* vc; const void* v_in; long long ld_v;
+  const int* kv_len; const int* table; int bt_stride, page, smax;
 };
 const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s);
 const char* kv_append_paged(const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,

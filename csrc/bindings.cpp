@@ -537,6 +537,35 @@ std::tuple<Tensor, Tensor> qk_norm_rope_fwd(const Tensor& q, const Tensor& k, co
   return {qo, ko};
 }
 
+// Decode form: one token per row; the rotated keys and the values go straight into the KV cache
+// (dense [B, Smax, Hkv, D], or a paged pool [n_pages, page, Hkv, D] behind `table`), only q is returned.
+Tensor qk_norm_rope_append(const Tensor& q, const Tensor& k, const Tensor& v, const optional<Tensor>& qw,
+                           const optional<Tensor>& kw, const Tensor& cos_t, const Tensor& sin_t, const Tensor& pos,
+                           double eps, bool zc, Tensor kc, Tensor vc, const Tensor& kv_len, const optional<Tensor>& table) {
+  c10::cuda::CUDAGuard guard(q.device());
+  ferrl::QkNormRopeArgs a{};
+  fill_qknr(a, q, k, qw, kw, cos_t, sin_t, pos, 1, eps, zc);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 && v.dim() == 3 && v.sizes() == k.sizes() &&
+                  v.stride(2) == 1 && v.stride(1) == v.size(2) && kc.is_contiguous() && vc.is_contiguous() &&
+                  kc.dim() == 4 && kc.sizes() == vc.sizes() && kc.size(2) == k.size(1) && kc.size(3) == k.size(2) &&
+                  kv_len.scalar_type() == at::kInt && kv_len.is_contiguous() && kv_len.numel() == q.size(0),
+              "qk_norm_rope_append: layout");
+  Tensor qo = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  a.backward = false; a.q_out = qo.data_ptr(); a.k_out = nullptr;
+  a.kc = kc.data_ptr(); a.vc = vc.data_ptr(); a.v_in = v.data_ptr(); a.ld_v = v.stride(0);
+  a.kv_len = kv_len.data_ptr<int>();
+  if (table.has_value() && table->defined()) {
+    TORCH_CHECK(table->scalar_type() == at::kInt && table->dim() == 2 && table->stride(1) == 1 && table->size(0) == q.size(0),
+                "qk_norm_rope_append: table int32 [B, pages]");
+    a.table = table->data_ptr<int>(); a.bt_stride = table->stride(0); a.page = kc.size(1);
+  } else {
+    TORCH_CHECK(kc.size(0) == q.size(0), "qk_norm_rope_append: dense cache [B, Smax, Hkv, D]");
+    a.smax = kc.size(1);
+  }
+  FERRL_CHECK(ferrl::qk_norm_rope(a, stream()));
+  return qo;
+}
+
 // d(q_in), d(k_in) written into dq_in / dk_in (views with packed heads, any token stride)
 void qk_norm_rope_bwd(const Tensor& q, const Tensor& k, const optional<Tensor>& qw, const optional<Tensor>& kw,
                       const Tensor& cos_t, const Tensor& sin_t, const Tensor& pos, int64_t pos_div, double eps, bool zc,
@@ -955,6 +984,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
+  m.def("qk_norm_rope_append(Tensor q, Tensor k, Tensor v, Tensor? qw, Tensor? kw, Tensor cos_t, Tensor sin_t, Tensor pos, float eps, bool zc, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len, Tensor? table) -> Tensor", &qk_norm_rope_append);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0, Tensor? debug=None) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);

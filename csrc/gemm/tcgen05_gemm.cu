@@ -617,12 +617,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const uint4* slot0 = reinterpret_cast<const uint4*>(
             static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
             static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
-        // U elements per round with every slot's load issued before the first add (latency-bound loop)
-        constexpr int U = 2, WCH = 8;
+        // U elements per round; the residual and WCH slots of each are requested before the first add
+        // (the loop is bound by the latency of these loads, so what counts is how many are in flight)
+        constexpr int U = 4, WCH = 4;
         for (int i0 = ct; i0 < BM * CPR; i0 += 128 * U) {
           float a8[U][8];
           bool live[U];
           int rr_[U], cc_[U];
+          uint4 resv[U];
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             const int i = i0 + u * 128;
@@ -630,6 +632,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             rr_[u] = mi * BM + rt;
             cc_[u] = ni * BN + ch * 8;
             live[u] = i < BM * CPR && rr_[u] < p.M && cc_[u] < p.N;
+            resv[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (HAS_RES && live[u]) resv[u] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]);
 #pragma unroll
             for (int e = 0; e < 8; ++e) a8[u][e] = 0.f;
           }
@@ -652,7 +656,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
           for (int u = 0; u < U; ++u) {
             if (!live[u]) continue;
-            if (HAS_RES) add8(a8[u], *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]));
+            if (HAS_RES) add8(a8[u], resv[u]);
             const uint4 o = pack8(a8[u]);
             *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
             const long long off = static_cast<long long>(rr_[u]) * p.N + cc_[u];
@@ -663,7 +667,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.ar_debug && ct == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 2] = globaltimer_ns();
         if (!comm_sync()) break;
         if (ct == 0) {
-          __threadfence_system();
+          // the release store orders this thread's view (which includes the other threads' pushes,
+          // through the barrier above) before the flag; a separate sequentially-consistent system
+          // fence in front of it cost 60 us per tile while the epilogue warps were pushing too
           for (int q2 = 0; q2 < p.ar_world; ++q2)
             if (q2 != p.ar_rank) st_release_sys(ar_done(p.ar_flags, q2, p.ar_max_tiles, out_tile), ar_epoch);
         }

@@ -149,11 +149,24 @@ size_t lora_grad_workspace_floats(int R, int C, int n_splits) {
 }
 
 int lora_grad_splits(int M, int C, int num_sms) {
+  // Two CTAs fit on an SM.  The token split is chosen so that the grid fills whole waves of
+  // 2 * num_sms CTAs: a grid of 1.08 waves takes as long as one of two.
   const int col_tiles = (C + LG_COLS - 1) / LG_COLS;
-  int s = (2 * num_sms + col_tiles - 1) / col_tiles;          // two CTAs per SM
-  const int max_s = (M + 4 * LG_ROWS - 1) / (4 * LG_ROWS);    // at least four stages per CTA
-  s = std::max(1, std::min(s, max_s));
-  return std::min(s, 64);
+  const int slots = 2 * num_sms;
+  const int max_s = std::min(64, std::max(1, (M + 4 * LG_ROWS - 1) / (4 * LG_ROWS)));   // at least four stages per CTA
+  int best = 1;
+  double best_eff = 0.0;
+  for (int s = 1; s <= max_s; ++s) {
+    const long long ctas = static_cast<long long>(col_tiles) * s;
+    const long long waves = (ctas + slots - 1) / slots;
+    const double eff = static_cast<double>(ctas) / static_cast<double>(waves * slots);
+    if (eff > best_eff + 1e-9) {
+      best_eff = eff;
+      best = s;
+    }
+    if (eff >= 0.93 && ctas >= slots / 2) return s;      // smallest split that fills its waves
+  }
+  return best;
 }
 
 const char* lora_grad(const void* U, long long ldu, int R, const void* X, long long ldx, int C, int M, int n_splits,

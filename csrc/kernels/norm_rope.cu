@@ -338,7 +338,10 @@ __global__ void qk_norm_rope_vec_kernel(const __nv_bfloat16* __restrict__ q_in, 
                                         const int* __restrict__ pos32, int pos_div, __nv_bfloat16* __restrict__ q_out,
                                         __nv_bfloat16* __restrict__ k_out, const __nv_bfloat16* __restrict__ dq,
                                         const __nv_bfloat16* __restrict__ dk, long long n_tok, int Hq, int Hkv, int half,
-                                        float eps, int zero_centered) {
+                                        float eps, int zero_centered, __nv_bfloat16* __restrict__ kc,
+                                        __nv_bfloat16* __restrict__ vc, const __nv_bfloat16* __restrict__ v_in, long long ld_v,
+                                        const int* __restrict__ kv_len, const int* __restrict__ table, int bt_stride, int page,
+                                        int smax) {
   pdl_trigger();
   pdl_wait();      // may be launched as a programmatic dependent: nothing is read before the predecessor is done
   constexpr int D = 32 * EPL;
@@ -421,7 +424,19 @@ __global__ void qk_norm_rope_vec_kernel(const __nv_bfloat16* __restrict__ q_in, 
       const float u = __shfl_sync(0xffffffffu, v[e], partner);
       o[e] = in_rot ? (lower ? v[e] * c[e] - u * sn[e] : v[e] * c[e] + u * sn[e]) : v[e];
     }
-    store((is_q ? q_out + (tok * Hq + h) * D : k_out + (tok * Hkv + h) * D) + i0, o);
+    if (!is_q && kc) {
+      // decode: the key goes to its cache row, and the value row of the same head is copied along
+      const int t = kv_len[tok];
+      const long long slot = table ? static_cast<long long>(table[tok * bt_stride + t / page]) * page + t % page
+                                   : tok * smax + t;
+      const long long off = (slot * Hkv + h) * D + i0;
+      store(kc + off, o);
+      float vv[EPL];
+      load(v_in + tok * ld_v + h * D + i0, vv);
+      store(vc + off, vv);
+    } else {
+      store((is_q ? q_out + (tok * Hq + h) * D : k_out + (tok * Hkv + h) * D) + i0, o);
+    }
   } else {
     float g[EPL], dn[EPL];
     load((is_q ? dq + (tok * Hq + h) * D : dk + (tok * Hkv + h) * D) + i0, g);
@@ -527,7 +542,8 @@ static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
     const int epl = a.D / 32;
     auto al = [&](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) % (2 * epl)) == 0 && (ld % epl) == 0; };
     const bool ok = (a.half % epl) == 0 && al(a.q_in, a.ld_q) && al(a.k_in, a.ld_k) && al(a.q_out, a.backward ? a.ld_dq : epl) &&
-                    al(a.k_out, a.backward ? a.ld_dk : epl) && al(a.qw, epl) && al(a.kw, epl) && al(a.dq, epl) && al(a.dk, epl);
+                    al(a.k_out, a.backward ? a.ld_dk : epl) && al(a.qw, epl) && al(a.kw, epl) && al(a.dq, epl) && al(a.dk, epl) &&
+                    (!a.kc || (!BWD && al(a.kc, epl) && al(a.vc, epl) && al(a.v_in, a.ld_v) && a.kv_len));
     if (ok) {
       using B = __nv_bfloat16;
 #define FERRL_QKV(EPLV)                                                                                             \
@@ -535,13 +551,15 @@ static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
       static_cast<const B*>(a.q_in), a.ld_q, static_cast<const B*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,               \
       static_cast<const B*>(a.qw), static_cast<const B*>(a.kw), a.cos_t, a.sin_t, a.pos64, a.pos32, a.pos_div,      \
       static_cast<B*>(a.q_out), static_cast<B*>(a.k_out), static_cast<const B*>(a.dq), static_cast<const B*>(a.dk), \
-      a.n_tok, a.Hq, a.Hkv, a.half, a.eps, a.zero_centered ? 1 : 0)
+      a.n_tok, a.Hq, a.Hkv, a.half, a.eps, a.zero_centered ? 1 : 0, static_cast<B*>(a.kc), static_cast<B*>(a.vc),      \
+      static_cast<const B*>(a.v_in), a.ld_v, a.kv_len, a.table, a.bt_stride, a.page, a.smax)
       if (epl == 4) FERRL_QKV(4); else FERRL_QKV(8);
 #undef FERRL_QKV
       count_launch();
       return cudaGetLastError() == cudaSuccess ? nullptr : "qk_norm_rope launch failed";
     }
   }
+  if (a.kc) return "qk_norm_rope: the fused cache append needs bf16 heads of 128 or 256 and aligned rows";
   qk_norm_rope_kernel<T, BWD><<<static_cast<unsigned>(blocks), wpb * 32, 0, s>>>(
       static_cast<const T*>(a.q_in), a.ld_q, static_cast<const T*>(a.k_in), a.ld_k, a.ld_dq, a.ld_dk,
       static_cast<const T*>(a.qw),

@@ -144,6 +144,19 @@ class DenseLayer(nn.Module):
         x = ops.rmsnorm(h, self.input_norm, self.eps)
         qkv = self.qkv.forward_merged(x)
         q, k, v = qkv.split([self.hq * self.D, self.hkv * self.D, self.hkv * self.D], dim=-1)
+        if ops.native(qkv) and cos.dtype == torch.float32 and (table is not None or k_cache.dim() == 4):
+            # one kernel: QK-norm, RoPE and the cache write of this token's K and V
+            from ..ops import cuda as _c
+            qr = _c.qk_norm_rope_append(q.unflatten(-1, (self.hq, self.D)), k.unflatten(-1, (self.hkv, self.D)),
+                                        v.unflatten(-1, (self.hkv, self.D)), self.q_norm, self.k_norm, self.eps, cos, sin,
+                                        pos if pos is not None else kv_len[:, None].long(), k_cache, v_cache, kv_len, table)
+            if qr is not None:
+                a = _c.decode_attention(qr, k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
+                                        scale=self.scale, block_table=table)
+                o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
+                x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
+                return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
+                                                residual=h)
         q = q.reshape(B, 1, self.hq, self.D)
         k = k.reshape(B, 1, self.hkv, self.D)
         v = v.reshape(B, 1, self.hkv, self.D)

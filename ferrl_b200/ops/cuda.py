@@ -286,6 +286,27 @@ def qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered=False):
     return _QkNormRope.apply(q, k, qw, kw, eps, cos.float(), sin.float(), pos, 1, zero_centered)
 
 
+def qk_norm_rope_append(q, k, v, q_w, k_w, eps, cos, sin, positions, k_cache, v_cache, kv_len, table=None,
+                        zero_centered=False):
+    """Decode form of ``qk_norm_rope`` fused with the KV-cache write: ``q, k, v`` ``[B, H, D]`` (one
+    token per row, views into the fused projection are fine), the rotated keys and the values go to
+    cache row ``kv_len[b]`` (dense ``[B, Smax, Hkv, D]`` caches, or paged pools behind ``table``).
+    Returns the rotated ``q`` ``[B, Hq, D]``, or ``None`` outside the kernel's domain."""
+    D = q.shape[-1]
+    if not (_bf16(q) and _bf16(k) and _bf16(v) and _bf16(k_cache)) or D not in (128, 256) or kv_len.dtype != torch.int32:
+        return None
+    if (q_w is not None and q_w.dtype != q.dtype) or (k_w is not None and k_w.dtype != k.dtype):
+        return None
+    for t in (q, k, v):
+        if t.dim() != 3 or t.stride(2) != 1 or t.stride(1) != D or t.stride(0) % 8:
+            return None
+    pos = positions.reshape(-1)
+    if pos.dtype not in (torch.int64, torch.int32):
+        pos = pos.long()
+    return lib().qk_norm_rope_append(q, k, v, q_w, k_w, cos, sin, pos.contiguous(), float(eps), bool(zero_centered),
+                                     k_cache, v_cache, kv_len, table)
+
+
 # ------------------------------------------------------------- attention
 class _Flash(torch.autograd.Function):
     @staticmethod
