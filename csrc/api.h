@@ -41,6 +41,8 @@ struct GemmArgs {
   // launch as a programmatic dependent of the stream predecessor: weights are prefetched before the
   // dependency wait (only where B is never written by an earlier kernel of the same stream)
   int pdl;
+  // GLU epilogue: B rows interleaved in groups of 16 (8 gate, 8 up); out is [M, N/2]; 1 SiLU, 2 tanh-GELU
+  int glu_act;
 };
 void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out,
                double* est_out = nullptr);

@@ -172,6 +172,31 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
   return out;
 }
 
+// act(x Wg^T) * (x Wu^T) in one kernel: W holds the gate and up rows interleaved in groups of 16
+// (8 gate rows, then the 8 up rows of the same features); returns [M, N/2].
+Tensor gemm_glu(const Tensor& A, const Tensor& B, int64_t act, bool static_b) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 &&
+                  A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1,
+              "gemm_glu: A [M,K], B [N,K] bf16, K-major");
+  TORCH_CHECK((B.size(0) % 16) == 0 && (act == 0 || act == 1), "gemm_glu: N a multiple of 16, act 0 (silu) or 1 (tanh-gelu)");
+  c10::cuda::CUDAGuard guard(A.device());
+  ferrl::GemmArgs a{};
+  a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
+  a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
+  Tensor out = at::empty({A.size(0), B.size(0) / 2}, A.options());
+  a.out = out.data_ptr(); a.ldo = out.stride(0);
+  a.status = status_word(); a.num_sms = num_sms();
+  a.glu_act = static_cast<int>(act) + 1;
+  a.pdl = (static_b && a.M <= 256) ? 1 : 0;
+  int bn = 0, split = 1, cluster = 1;
+  ferrl::gemm_plan(a.M, a.N, a.K, 0, a.num_sms, &bn, &split, &cluster, nullptr);
+  if (split > 1 || cluster > 1 || bn == 32) bn = 128;      // the epilogue needs whole tiles in one CTA
+  a.force_bn = bn;
+  if (a.M == 0) return out;
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
 // Row-parallel projection fused with its tensor-parallel all-reduce:
 // out = sum_over_ranks(A_r B_r^T (+ A2 B2^T)) (+ residual), identical on every rank.
 Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
@@ -984,6 +1009,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
+  m.def("gemm_glu(Tensor A, Tensor B, int act, bool static_b=False) -> Tensor", &gemm_glu);
   m.def("qk_norm_rope_append(Tensor q, Tensor k, Tensor v, Tensor? qw, Tensor? kw, Tensor cos_t, Tensor sin_t, Tensor pos, float eps, bool zc, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len, Tensor? table) -> Tensor", &qk_norm_rope_append);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0, Tensor? debug=None) -> (Tensor, Tensor, Tensor)", &flash_bwd);

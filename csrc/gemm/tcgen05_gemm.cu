@@ -67,6 +67,10 @@ struct GemmParams {
   // only then does it fetch the activation (A) halves.  Everything else in the kernel is ordered
   // behind those loads by the pipeline's barriers.
   int pdl;
+  // Gated-linear-unit epilogue (one-SM kernel, bf16 output, no k-split): the N rows of B come in groups
+  // of 16, eight gate rows followed by the eight up rows of the same features, and the kernel writes
+  // act(gate) * up, N / 2 columns per row.  1 = SiLU, 2 = tanh-GELU.
+  int glu_act;
 };
 
 // flag layout inside each rank's flag buffer: ready[tile][kMaxRanks] then done[tile]
@@ -510,6 +514,27 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             } else {
               for (int e = 0; e < ncols; ++e) op[e] = __uint_as_float(r[e]);
             }
+          } else if (p.glu_act) {
+            __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + (col >> 1);
+#pragma unroll
+            for (int g16 = 0; g16 < 2; ++g16) {
+              if (g16 * 16 < ncols) {
+                float o8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                  const float gate = __uint_as_float(r[g16 * 16 + e]), up = __uint_as_float(r[g16 * 16 + 8 + e]);
+                  float a;
+                  if (p.glu_act == 1) {
+                    a = gate / (1.f + __expf(-gate));
+                  } else {
+                    const float t = tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate));
+                    a = 0.5f * gate * (1.f + t);
+                  }
+                  o8[e] = a * up;
+                }
+                *reinterpret_cast<uint4*>(op + g16 * 8) = pack8(o8);
+              }
+            }
           } else {
             __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(row) * p.ldo + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(op) & 15) == 0)) {
@@ -801,6 +826,7 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.split_k = (kb_total + p.kb_per_split - 1) / p.kb_per_split;   // no empty slices
   p.partial = a.partial;
   p.tile_expert = a.tile_expert;
+  p.glu_act = a.glu_act;
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
   if (p.ar_world > 1) {
@@ -1983,6 +2009,11 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
     return "operand base addresses must be 16-byte aligned";
+  if (a.glu_act) {
+    if (a.stream_k || a.cluster_k > 1 || a.two_cta || a.split_k > 1 || a.out_f32 || a.residual || a.ar_world > 1 || a.tile_expert ||
+        (a.N % 16) || (a.ldo % 8))
+      return "gemm with GLU epilogue: one-SM kernel, bf16 output, no split, residual or grouping; N a multiple of 16";
+  }
   if (a.stream_k) {
     if (a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "stream-k gemm: no global k-split, grouping or all-reduce";
     if (a.out_f32) return a.residual ? launch_streamk<true, true>(a, stream) : launch_streamk<true, false>(a, stream);

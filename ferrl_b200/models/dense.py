@@ -93,6 +93,7 @@ class DenseLayer(nn.Module):
                                  full_in=hq * D, **kw)
         self.gate_up = FusedLoraLinear(H, [F // w, F // w], ("gate", "up"), (t.mlp_gate, t.mlp_up), lora,
                                        shard=col, full_out_sizes=[F, F], **kw)
+        self.gate_up.enable_glu_layout()      # rollout snapshot interleaved for the GEMM's GLU epilogue
         self.down = FusedLoraLinear(F // w, [H], ("down",), (t.mlp_down,), lora, shard=row, full_in=F, **kw)
         mk = (lambda n: nn.Parameter(torch.ones(n, dtype=dtype, device=device))) if trainable_base else None
         for name, n in (("input_norm", H), ("post_norm", H)) + ((("q_norm", D), ("k_norm", D)) if spec.qk_norm else ()):
@@ -136,7 +137,8 @@ class DenseLayer(nn.Module):
         o = self.o.forward_reduce(a.reshape(B, S, self.hq * self.D), comm, merged)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
         x = copy_to_tp(x, comm)
-        return self.down.forward_reduce(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged, residual=h)
+        mid = self.gate_up.forward_merged_glu(x, self.act) if merged else ops.swiglu(self.gate_up(x), self.act)
+        return self.down.forward_reduce(mid, comm, merged, residual=h)
 
     # one-token forward against the cache (rollout; merged weights)
     def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None, table=None):
@@ -155,7 +157,7 @@ class DenseLayer(nn.Module):
                                         scale=self.scale, block_table=table)
                 o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
                 x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
-                return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
+                return self.down.forward_reduce(self.gate_up.forward_merged_glu(x, self.act), comm, merged=True,
                                                 residual=h)
         q = q.reshape(B, 1, self.hq, self.D)
         k = k.reshape(B, 1, self.hkv, self.D)
@@ -184,7 +186,7 @@ class DenseLayer(nn.Module):
                                      scale=self.scale)
         o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
-        return self.down.forward_reduce(ops.swiglu(self.gate_up.forward_merged(x), self.act), comm, merged=True,
+        return self.down.forward_reduce(self.gate_up.forward_merged_glu(x, self.act), comm, merged=True,
                                         residual=h)
 
 

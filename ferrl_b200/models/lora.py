@@ -286,7 +286,47 @@ class FusedLoraLinear(nn.Module):
     def forward_merged(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         """Rollout path over the merged snapshot (no adapter side path)."""
         w = self.weight_merged if self.weight_merged is not None else self.weight
-        return ops.lora_linear(x, w, None, None, residual=residual)
+        y = ops.lora_linear(x, w, None, None, residual=None if self._glu_rows() is not None else residual)
+        if self._glu_rows() is not None:      # snapshot rows are interleaved for the fused GLU: undo it for plain use
+            y = y.index_select(-1, self._glu_inverse)
+            if residual is not None:
+                y = residual + y
+        return y
+
+    # ------------------------------------------------------------ gate/up projections
+    def enable_glu_layout(self):
+        """For a fused [gate | up] projection: keep the merged snapshot with its rows interleaved in
+        groups of 16 (8 gate rows, then the 8 up rows of the same features), the layout the GEMM's
+        GLU epilogue reads, so that rollout computes ``act(gate) * up`` inside the projection.
+        Takes effect at the next ``merge()`` on a bf16 CUDA weight; a plain snapshot otherwise."""
+        self._glu_requested = True
+
+    def _glu_rows(self):
+        """Row permutation of the interleaved snapshot, or ``None`` when the snapshot is plain."""
+        if not getattr(self, "_glu_active", False) or self.weight_merged is None:
+            return None
+        return self._glu_perm
+
+    def _glu_prepare(self) -> bool:
+        w = self.weight
+        ok = getattr(self, "_glu_requested", False) and w.is_cuda and w.dtype == torch.bfloat16 and \
+            w.shape[0] % 16 == 0 and (w.shape[0] // 2) % 8 == 0
+        if ok and (getattr(self, "_glu_perm", None) is None or self._glu_perm.device != w.device):
+            half = w.shape[0] // 2
+            g = torch.arange(half, device=w.device).view(-1, 8)
+            self._glu_perm = torch.stack([g, g + half], dim=1).reshape(-1)          # [8 gate, 8 up, 8 gate, ...]
+            self._glu_inverse = torch.argsort(self._glu_perm)
+        self._glu_active = bool(ok)
+        return self._glu_active
+
+    def forward_merged_glu(self, x: torch.Tensor, act: str) -> torch.Tensor:
+        """``act(x Wg^T) * (x Wu^T)`` over the merged snapshot; one kernel where the snapshot is
+        interleaved, projection + GLU kernel otherwise."""
+        if self._glu_rows() is not None and ops.native(x) and x.dtype == torch.bfloat16 and act in ("silu", "gelu_pytorch_tanh",
+                                                                                                    "gelu_tanh"):
+            from ..ops import cuda as _c
+            return _c.gemm_glu(x, self.weight_merged, act)
+        return ops.swiglu(self.forward_merged(x), act)
 
     @torch.no_grad()
     def merge(self):
@@ -294,8 +334,11 @@ class FusedLoraLinear(nn.Module):
         a, b = self._stacks()
         if a is None:
             self.weight_merged = None
+            self._glu_active = False
             return
         new = ops.lora_merge(self.weight, a.detach(), b.detach())
+        if self._glu_prepare():
+            new = new.index_select(0, self._glu_perm)
         if self.weight_merged is not None and self.weight_merged.shape == new.shape:
             self.weight_merged.copy_(new)  # keep the address stable: captured decode graphs point at it
         else:

@@ -61,6 +61,16 @@ def gemm(a, b, a2=None, b2=None, residual=None, out_f32=False, force_bn=0, force
                       bool(static_b))
 
 
+def gemm_glu(x, w_interleaved, act="silu"):
+    """``act(x Wg^T) * (x Wu^T)`` with ``w_interleaved`` ``[2F, K]`` holding gate and up rows in groups of
+    16 (8 gate, 8 up): the GLU runs in the GEMM epilogue (``[..., F]`` out, no ``[..., 2F]`` round trip)."""
+    x2 = x.reshape(-1, x.shape[-1])
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = lib().gemm_glu(x2, w_interleaved, _ACT[act], True)
+    return y.view(*x.shape[:-1], w_interleaved.shape[0] // 2)
+
+
 def _pad8(t, dim):
     n = t.shape[dim]
     if n % 8 == 0:

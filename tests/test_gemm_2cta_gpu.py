@@ -214,3 +214,55 @@ def test_dependent_launch_chain_matches_reference():
             r = ref(xin)
             assert ((yg.float() - r).norm() / r.norm()).item() < 2e-2, i
     assert C.kernel_status() == 0
+
+
+@pytest.mark.parametrize("M,F,K,act", [(128, 12288, 4096, "silu"), (7, 88, 192, "silu"), (300, 1024, 512, "gelu_tanh"),
+                                         (2048, 2048, 1024, "silu")])
+def test_gemm_glu_epilogue(M, F, K, act):
+    """Projection with the GLU in its epilogue (gate/up rows interleaved in groups of 16) against
+    act(x Wg^T) * (x Wu^T) in fp32."""
+    from ferrl_b200.ops import cuda as C
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(F + M)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * F, K, device=dev, generator=g) * (2.0 / K ** 0.5)).to(torch.bfloat16)
+    idx = torch.arange(F, device=dev).view(-1, 8)
+    perm = torch.stack([idx, idx + F], dim=1).reshape(-1)
+    y = C.gemm_glu(x, w.index_select(0, perm).contiguous(), act)
+    gu = x.float() @ w.float().t()
+    gate, up = gu[:, :F], gu[:, F:]
+    a = torch.nn.functional.silu(gate) if act == "silu" else torch.nn.functional.gelu(gate, approximate="tanh")
+    ref = a * up
+    assert y.shape == (M, F)
+    assert ((y.float() - ref).norm() / ref.norm()).item() < 1e-2
+    assert C.kernel_status() == 0
+
+
+def test_fused_linear_glu_layout_matches_plain_snapshot():
+    """A gate/up projection whose merged snapshot is kept interleaved gives the same rollout
+    activations as projection + GLU kernel on the plain snapshot, and still serves plain calls."""
+    from ferrl_b200.models.lora import FusedLoraLinear, LoraSpec
+    from ferrl_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(3)
+    H, F = 512, 1024
+    mk = lambda: FusedLoraLinear(H, [F, F], ("gate", "up"), (True, True), LoraSpec(rank=8, alpha=16.0),  # noqa: E731
+                                 dtype=torch.bfloat16, device=dev)
+    a, b = mk(), mk()
+    w = (torch.randn(2 * F, H, device=dev) * 0.05).to(torch.bfloat16)
+    for m in (a, b):
+        m.set_weight(w)
+    for pa, pb in zip(list(a.lora_A) + list(a.lora_B), list(b.lora_A) + list(b.lora_B)):
+        v = torch.randn_like(pa) * 0.05
+        pa.data.copy_(v)
+        pb.data.copy_(v)
+    b.enable_glu_layout()
+    a.merge()
+    b.merge()
+    x = torch.randn(64, H, device=dev).to(torch.bfloat16)
+    with torch.no_grad():
+        ref = ops.swiglu(a.forward_merged(x), "silu")
+        got = b.forward_merged_glu(x, "silu")
+        plain = b.forward_merged(x)
+    assert ((got.float() - ref.float()).norm() / ref.float().norm()).item() < 1e-2
+    assert torch.equal(plain, a.forward_merged(x))
