@@ -153,7 +153,10 @@ __device__ __forceinline__ uint64_t mix64(uint64_t z) {
 
 constexpr int ST = 1024;  // threads per row
 
-template <typename T>
+// VEC (16-bit logits, V a multiple of 8, 16-byte aligned rows): a thread takes 8 consecutive logits
+// per 16-byte load, so every pass keeps eight times the bytes in flight; the passes are bound by
+// L2 latency and the histograms and integer sums do not depend on the element order.
+template <typename T, bool VEC>
 __global__ void __launch_bounds__(ST)
 sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* __restrict__ global_rows,
                    uint64_t seed, const int* __restrict__ draw_dev, int draw_host, long long* __restrict__ tok_out,
@@ -171,22 +174,41 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   const int tid = threadIdx.x;
   const float FIX = 1099511627776.f;  // 2^40
 
-  // Every pass over the row is bound by L2 latency, not bandwidth: loads are issued four at a time
-  // (four coalesced warp accesses in flight per thread) before anything consumes them.
-  constexpr int UL = 4;
-  auto load_batch = [&](int i0, float* v) {
+  // Every pass over the row is bound by L2 latency, not bandwidth: a thread issues UL loads (of one
+  // element, or of a group of eight) before anything consumes them.
+  constexpr int EPT = VEC ? 8 : 1;          // elements per load
+  constexpr int UL = VEC ? 2 : 4;           // loads in flight per thread
+  constexpr int NV = UL * EPT;
+  const int Vg = V / EPT;                   // groups in the row (VEC: V % 8 == 0)
+  auto load_group = [&](int g, float* v) {  // group g -> EPT values (-inf past the end)
+    if (VEC) {
+      if (g < Vg) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(x) + static_cast<long long>(g) * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
-    for (int u = 0; u < UL; ++u) {
-      const int i = i0 + u * ST;
-      v[u] = i < V ? to_f(x[i]) : -INFINITY;
+        for (int k = 0; k < 4; ++k) {
+          const float2 f = __bfloat1622float2(h[k]);
+          v[2 * k] = f.x;
+          v[2 * k + 1] = f.y;
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v[k] = -INFINITY;
+      }
+    } else {
+      v[0] = g < V ? to_f(x[g]) : -INFINITY;
     }
   };
+  auto load_batch = [&](int g0, float* v) {
+#pragma unroll
+    for (int u = 0; u < UL; ++u) load_group(g0 + u * ST, v + u * EPT);
+  };
   float m = -INFINITY;
-  for (int i0 = tid; i0 < V; i0 += UL * ST) {
-    float v[UL];
+  for (int i0 = tid; i0 < Vg; i0 += UL * ST) {
+    float v[NV];
     load_batch(i0, v);
 #pragma unroll
-    for (int u = 0; u < UL; ++u) m = fmaxf(m, v[u]);
+    for (int u = 0; u < NV; ++u) m = fmaxf(m, v[u]);
   }
   m = block_max(m, red);
 
@@ -194,49 +216,62 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   auto e_val = [&](float xv) -> float { return __expf((xv - m) * inv_t); };   // exp(-inf) = 0 for padding lanes
   auto fix_of = [&](float e) -> unsigned long long { return static_cast<unsigned long long>(e * FIX); };
 
-  // total mass
+  // Radix keys.  For 16-bit logits the order of the probabilities is the order of the logits, so the
+  // nucleus cut is found on the sortable 16-bit pattern of the logit itself: two 8-bit passes instead
+  // of four over the fp32 probability, and the first histogram also yields the total mass.
+  constexpr bool K16 = sizeof(T) == 2;
+  constexpr int N_PASS = K16 ? 2 : 4;
+  auto key_of = [&](float xv, float e) -> unsigned int {
+    if (K16) {
+      const unsigned int u = __float_as_uint(xv) >> 16;
+      return (u & 0x8000u) ? (~u & 0xFFFFu) : (u | 0x8000u);
+    }
+    return __float_as_uint(e);
+  };
+  const bool nucleus = top_p > 0.f && top_p < 1.f;
+
+  // total mass (taken from the first histogram instead when that is built anyway)
   if (tid == 0) sh_u64[0] = 0;
   __syncthreads();
-  {
+  if (!(K16 && nucleus)) {
     unsigned long long part = 0;
-    for (int i0 = tid; i0 < V; i0 += UL * ST) {
-      float v[UL];
+    for (int i0 = tid; i0 < Vg; i0 += UL * ST) {
+      float v[NV];
       load_batch(i0, v);
 #pragma unroll
-      for (int u = 0; u < UL; ++u) part += fix_of(e_val(v[u]));
+      for (int u = 0; u < NV; ++u) part += fix_of(e_val(v[u]));
     }
     // warp-level integer reduction, then one atomic per warp
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     if ((tid & 31) == 0) atomicAdd(&sh_u64[0], part);
   }
   __syncthreads();
-  const unsigned long long Z = sh_u64[0];
+  unsigned long long Z = sh_u64[0];
 
   unsigned int thresh_key = 0;          // keep everything
   unsigned long long kept_mass = Z;
-  if (top_p > 0.f && top_p < 1.f) {
-    const unsigned long long target =
+  if (nucleus) {
+    unsigned long long target =
         static_cast<unsigned long long>(static_cast<double>(Z) * static_cast<double>(top_p));
     unsigned int prefix = 0;
     unsigned long long above = 0;
-    for (int pass = 0; pass < 4; ++pass) {
-      const int shift = 24 - 8 * pass;
+    for (int pass = 0; pass < N_PASS; ++pass) {
+      const int shift = 8 * (N_PASS - 1 - pass);
       for (int i = tid; i < 32 * 256; i += ST) dyn[i] = 0;
       __syncthreads();
       // Each warp fills its own histogram. Lanes that hit the same bucket are combined with
       // match_any + two 32-bit warp reductions (mass < 2^40 split into 20-bit halves), and the
       // group's lowest lane does a plain read-modify-write: no atomics, no cross-warp contention.
-      for (int ib = 0; ib < V; ib += UL * ST) {
-        float xv[UL];
+      for (int ib = 0; ib < Vg; ib += UL * ST) {
+        float xv[NV];
         load_batch(ib + tid, xv);
 #pragma unroll
-        for (int u = 0; u < UL; ++u) {
-          const int i = ib + u * ST + tid;
+        for (int u = 0; u < NV; ++u) {
           unsigned int bucket = 0xFFFFFFFFu;
           unsigned long long f = 0;
-          if (i < V) {
+          {                                  // lanes past the end hold -inf: zero mass, no bucket
             float e = e_val(xv[u]);
-            unsigned int key = __float_as_uint(e);
+            unsigned int key = key_of(xv[u], e);
             if (pass == 0 || (key >> (shift + 8)) == prefix) {
               f = fix_of(e);
               if (f) bucket = (key >> shift) & 0xFF;
@@ -265,10 +300,17 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
       }
       __syncthreads();
       if (tid == 0) {
+        if (K16 && pass == 0) {          // the first histogram covers every element: its sum is the total mass
+          unsigned long long z = 0;
+          for (int b = 0; b < 256; ++b) z += hist[b];
+          sh_u64[0] = z;
+          sh_u64[3] = static_cast<unsigned long long>(static_cast<double>(z) * static_cast<double>(top_p));
+        }
+        const unsigned long long target_ = (K16 && pass == 0) ? sh_u64[3] : target;
         unsigned long long cum = above;
         int b = 255;
         for (; b > 0; --b) {
-          if (hist[b] > 0 && cum + hist[b] >= target) break;
+          if (hist[b] > 0 && cum + hist[b] >= target_) break;
           cum += hist[b];
         }
         sh_u64[1] = cum;                 // mass strictly above the chosen bucket
@@ -279,6 +321,10 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
       above = sh_u64[1];
       kept_mass = sh_u64[2];
       prefix = sh_u32[0];
+      if (K16 && pass == 0) {
+        Z = sh_u64[0];
+        target = sh_u64[3];
+      }
       __syncthreads();
     }
     thresh_key = prefix;
@@ -292,12 +338,17 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   const unsigned long long target = (kept_mass >> 24) * u24 + (((kept_mass & 0xFFFFFFull) * u24) >> 24);
 
   // contiguous chunk per thread, block scan of chunk masses, then the owning thread walks its chunk
-  const int chunk = (V + ST - 1) / ST;
-  const int c0 = tid * chunk, c1 = min(V, c0 + chunk);
+  const int chunk = (Vg + ST - 1) / ST;                 // groups per thread
+  const int c0 = tid * chunk, c1 = min(Vg, c0 + chunk);
   unsigned long long mine = 0;
-  for (int i = c0; i < c1; ++i) {
-    float e = e_of(i);
-    if (__float_as_uint(e) >= thresh_key) mine += fix_of(e);
+  for (int g = c0; g < c1; ++g) {
+    float xg[EPT];
+    load_group(g, xg);
+#pragma unroll
+    for (int k = 0; k < EPT; ++k) {
+      const float e = e_val(xg[k]);
+      if (key_of(xg[k], e) >= thresh_key) mine += fix_of(e);
+    }
   }
   __syncthreads();
   scan[tid] = mine;
@@ -314,14 +365,20 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   __syncthreads();
   if (mine > 0 && target >= excl && target < incl) {
     unsigned long long cum = excl;
-    int pick = c1 - 1;
-    for (int i = c0; i < c1; ++i) {
-      float e = e_of(i);
-      if (__float_as_uint(e) >= thresh_key) {
-        cum += fix_of(e);
-        if (cum > target) {
-          pick = i;
-          break;
+    int pick = c1 * EPT - 1;
+    bool found = false;
+    for (int g = c0; g < c1 && !found; ++g) {
+      float xg[EPT];
+      load_group(g, xg);
+#pragma unroll
+      for (int k = 0; k < EPT; ++k) {
+        const float e = e_val(xg[k]);
+        if (!found && key_of(xg[k], e) >= thresh_key) {
+          cum += fix_of(e);
+          if (cum > target) {
+            pick = g * EPT + k;
+            found = true;
+          }
         }
       }
     }
@@ -391,17 +448,22 @@ const char* sample_rows(int dtype, const void* logits, long long ld, const long 
   constexpr size_t kDyn = 32 * 256 * sizeof(unsigned long long);
   static bool attr = false;
   if (!attr) {
-    cudaFuncSetAttribute(sample_rows_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDyn));
-    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaFuncSetAttribute(sample_rows_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDyn));
+    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         static_cast<int>(kDyn));
+    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(kDyn));
     attr = true;
   }
   if (dtype == kF32)
-    sample_rows_kernel<float><<<rows, ST, kDyn, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
-                                                  draw_host, tok_out, lp_out, V, inv_t, top_p);
+    sample_rows_kernel<float, false><<<rows, ST, kDyn, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
+                                                         draw_host, tok_out, lp_out, V, inv_t, top_p);
+  else if ((V % 8) == 0 && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0)
+    sample_rows_kernel<__nv_bfloat16, true><<<rows, ST, kDyn, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
+                                                                seed, draw_dev, draw_host, tok_out, lp_out, V, inv_t, top_p);
   else
-    sample_rows_kernel<__nv_bfloat16><<<rows, ST, kDyn, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
-                                                          seed, draw_dev, draw_host, tok_out, lp_out, V, inv_t, top_p);
+    sample_rows_kernel<__nv_bfloat16, false><<<rows, ST, kDyn, s>>>(static_cast<const __nv_bfloat16*>(logits), ld, global_rows,
+                                                                 seed, draw_dev, draw_host, tok_out, lp_out, V, inv_t, top_p);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "sample_rows launch failed";
 }

@@ -251,12 +251,13 @@ def test_logprob_gather_fwd_bwd(softcap):
     assert _rel(h.grad, hf.grad) < 4e-2
 
 
+@pytest.mark.parametrize("V", [3001, 4096])      # scalar loads / 16-byte vector loads
 @pytest.mark.parametrize("top_p", [None, 0.9, 0.3])
-def test_sampling_matches_host_oracle(top_p):
+def test_sampling_matches_host_oracle(top_p, V):
     from ferrl_b200.ops import cuda as C
     from ferrl_b200.sampler import sample_from_logits_eager, uniforms_for_rows
     dev = _dev()
-    R, V = 64, 3001
+    R = 64
     logits = (torch.randn(R, V, device=dev) * 3).to(torch.bfloat16)
     rows = torch.arange(100, 100 + R, device=dev)
     agree, n = 0, 0
