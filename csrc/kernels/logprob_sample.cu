@@ -165,9 +165,9 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   __shared__ unsigned long long hist[256];
   __shared__ unsigned long long sh_u64[4];
   __shared__ unsigned int sh_u32[2];
-  // dynamic: 32 warp-private histograms of 256 u64 (64 KB); the first 8 KB double as the scan array later
+  // dynamic (96 KB): 32 warp-private histograms of three planes of 256 u32; the first 8 KB double as the
+  // scan array afterwards
   extern __shared__ __align__(16) unsigned long long dyn[];
-  unsigned long long* whist = dyn + (threadIdx.x >> 5) * 256;
   unsigned long long* scan = dyn;
   const long long row = blockIdx.x;
   const T* x = logits + row * ld;
@@ -257,45 +257,55 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
     unsigned long long above = 0;
     for (int pass = 0; pass < N_PASS; ++pass) {
       const int shift = 8 * (N_PASS - 1 - pass);
-      for (int i = tid; i < 32 * 256; i += ST) dyn[i] = 0;
+      for (int i = tid; i < 32 * 3 * 128; i += ST) dyn[i] = 0;     // 32 warps x 3 planes of 256 u32
       __syncthreads();
-      // Each warp fills its own histogram. Lanes that hit the same bucket are combined with
-      // match_any + two 32-bit warp reductions (mass < 2^40 split into 20-bit halves), and the
-      // group's lowest lane does a plain read-modify-write: no atomics, no cross-warp contention.
-      for (int ib = 0; ib < Vg; ib += UL * ST) {
-        float xv[NV];
-        load_batch(ib + tid, xv);
+      // Each warp fills its own histogram with native 32-bit shared atomics on 14/13/13-bit pieces of the
+      // fixed-point mass (a 64-bit shared atomic is a compare-and-swap loop; integer sums stay
+      // order-independent).  A thread first adds up runs of equal buckets in registers: in the first
+      // pass the digit is the sign and the high exponent bits, so runs are long and atomics few.
+      {
+        unsigned int* planes = reinterpret_cast<unsigned int*>(dyn) + (threadIdx.x >> 5) * 3 * 256;
+        unsigned int cb = 0xFFFFFFFFu;
+        unsigned long long cf = 0;
+        auto flush = [&]() {
+          if (cb != 0xFFFFFFFFu && cf) {
+            atomicAdd(&planes[cb], static_cast<unsigned int>(cf & 0x3FFFu));
+            atomicAdd(&planes[256 + cb], static_cast<unsigned int>((cf >> 14) & 0x1FFFu));
+            atomicAdd(&planes[512 + cb], static_cast<unsigned int>(cf >> 27));
+          }
+        };
+        for (int ib = 0; ib < Vg; ib += UL * ST) {
+          float xv[NV];
+          load_batch(ib + tid, xv);
 #pragma unroll
-        for (int u = 0; u < NV; ++u) {
-          unsigned int bucket = 0xFFFFFFFFu;
-          unsigned long long f = 0;
-          {                                  // lanes past the end hold -inf: zero mass, no bucket
-            float e = e_val(xv[u]);
-            unsigned int key = key_of(xv[u], e);
+          for (int u = 0; u < NV; ++u) {
+            const float e = e_val(xv[u]);          // lanes past the end hold -inf: zero mass, no bucket
+            const unsigned int key = key_of(xv[u], e);
             if (pass == 0 || (key >> (shift + 8)) == prefix) {
-              f = fix_of(e);
-              if (f) bucket = (key >> shift) & 0xFF;
+              const unsigned long long f = fix_of(e);
+              if (f) {
+                const unsigned int bucket = (key >> shift) & 0xFF;
+                if (bucket == cb) {
+                  cf += f;
+                } else {
+                  flush();
+                  cb = bucket;
+                  cf = f;
+                }
+              }
             }
           }
-          if (pass == 0) {
-            // leading exponent bits: a handful of distinct buckets per warp, so combine equal lanes first
-            const unsigned int gm = __match_any_sync(0xffffffffu, bucket);
-            const unsigned int lo = __reduce_add_sync(gm, static_cast<unsigned int>(f & 0xFFFFFu));
-            const unsigned int hi = __reduce_add_sync(gm, static_cast<unsigned int>(f >> 20));
-            if (bucket != 0xFFFFFFFFu && (tid & 31) == (__ffs(gm) - 1))
-              whist[bucket] += (static_cast<unsigned long long>(hi) << 20) + lo;
-          } else if (bucket != 0xFFFFFFFFu) {
-            // later digits are spread over the 256 buckets and only the selected prefix takes part:
-            // integer atomics on the warp-private histogram rarely collide (and stay order-independent)
-            atomicAdd(&whist[bucket], f);
-          }
-          __syncwarp();
         }
+        flush();
       }
       __syncthreads();
       if (tid < 256) {
         unsigned long long t = 0;
-        for (int w = 0; w < 32; ++w) t += dyn[w * 256 + tid];
+        const unsigned int* planes = reinterpret_cast<const unsigned int*>(dyn);
+        for (int w = 0; w < 32; ++w)
+          t += static_cast<unsigned long long>(planes[(w * 3) * 256 + tid]) +
+               (static_cast<unsigned long long>(planes[(w * 3 + 1) * 256 + tid]) << 14) +
+               (static_cast<unsigned long long>(planes[(w * 3 + 2) * 256 + tid]) << 27);
         hist[tid] = t;
       }
       __syncthreads();
@@ -445,7 +455,7 @@ const char* sample_rows(int dtype, const void* logits, long long ld, const long 
                         int rows, int V, float temperature, float top_p, cudaStream_t s) {
   if (rows == 0) return nullptr;
   float inv_t = 1.f / temperature;
-  constexpr size_t kDyn = 32 * 256 * sizeof(unsigned long long);
+  constexpr size_t kDyn = 32 * 3 * 128 * sizeof(unsigned long long);   // 96 KB: see the histogram passes
   static bool attr = false;
   if (!attr) {
     cudaFuncSetAttribute(sample_rows_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDyn));
