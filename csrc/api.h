@@ -43,7 +43,15 @@ struct GemmArgs {
   int pdl;
   // GLU epilogue: B rows interleaved in groups of 16 (8 gate, 8 up); out is [M, N/2]; 1 SiLU, 2 tanh-GELU
   int glu_act;
+  // RMSNorm folded around the projection (one-SM and cluster split-k kernels, bf16 output):
+  // ss_in [ss_parts, ss_ld] fp32 partial row sums of squares of A's rows (rows are scaled by
+  // rsqrt(sum * ss_inv_k + ss_eps) in the epilogue); ss_out [parts, ss_ld] receives the partial row sums
+  // of squares of the stored output, parts = gemm_ss_parts()
+  const float* ss_in; int ss_parts; long long ss_ld; float ss_inv_k, ss_eps;
+  float* ss_out;
 };
+// number of partial rows ss_out needs for a call that would run with tile width bn and cluster size (1: none)
+inline int gemm_ss_parts(int N, int bn, int cluster) { return ((N + bn - 1) / bn) * (cluster > 1 ? cluster : 1); }
 void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split_out, int* cluster_out,
                double* est_out = nullptr);
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);
@@ -72,6 +80,7 @@ struct QkNormRopeArgs {
   const int* kv_len; const int* table; int bt_stride, page, smax;
 };
 const char* qk_norm_rope(const QkNormRopeArgs& a, cudaStream_t s);
+const char* row_sumsq(const void* x, long long ld, float* ss, int rows, int H, cudaStream_t s);   // bf16 rows
 const char* kv_append_paged(const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
                             const int* table, int bt_stride, int page, int batch, int HD, cudaStream_t s);
 const char* kv_append(int dtype, const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,

@@ -197,6 +197,67 @@ Tensor gemm_glu(const Tensor& A, const Tensor& B, int64_t act, bool static_b) {
   return out;
 }
 
+// Projection with an RMSNorm folded around it (decode chain).  `ss_in` [parts, M]: partial row sums of
+// squares of A's rows; the rows of the result are scaled by rsqrt(sum / K + eps) (the norm weight must
+// already be folded into B's columns).  `want_ss`: also return the partial row sums of squares of the
+// stored output [parts', M] for the next projection.  glu_act: -1 none, 0 SiLU, 1 tanh-GELU (B interleaved).
+std::tuple<Tensor, Tensor> gemm_norm(const Tensor& A, const Tensor& B, const optional<Tensor>& residual,
+                                     const optional<Tensor>& ss_in, double eps, int64_t glu_act, bool want_ss, bool static_b) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 &&
+                  A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1,
+              "gemm_norm: A [M,K], B [N,K] bf16, K-major");
+  TORCH_CHECK(glu_act >= -1 && glu_act <= 1 && (glu_act < 0 || (B.size(0) % 16) == 0), "gemm_norm: glu_act");
+  TORCH_CHECK(glu_act < 0 || !(residual.has_value() && residual->defined()), "gemm_norm: no residual with the GLU epilogue");
+  c10::cuda::CUDAGuard guard(A.device());
+  ferrl::GemmArgs a{};
+  a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
+  a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
+  const int64_t n_out = glu_act >= 0 ? B.size(0) / 2 : B.size(0);
+  Tensor out = at::empty({A.size(0), n_out}, A.options());
+  a.out = out.data_ptr(); a.ldo = out.stride(0);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == a.M &&
+                    residual->size(1) == a.N && residual->stride(1) == 1, "gemm_norm: residual bf16 [M,N]");
+    a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
+  }
+  a.status = status_word(); a.num_sms = num_sms();
+  a.glu_act = glu_act >= 0 ? static_cast<int>(glu_act) + 1 : 0;
+  a.pdl = (static_b && a.M <= 256) ? 1 : 0;
+  if (ss_in.has_value() && ss_in->defined()) {
+    TORCH_CHECK(ss_in->scalar_type() == at::kFloat && ss_in->dim() == 2 && ss_in->is_contiguous() && ss_in->size(1) == a.M,
+                "gemm_norm: ss_in float32 [parts, M]");
+    a.ss_in = ss_in->data_ptr<float>(); a.ss_parts = ss_in->size(0); a.ss_ld = a.M;
+    a.ss_inv_k = 1.0f / static_cast<float>(a.K); a.ss_eps = static_cast<float>(eps);
+  }
+  int bn = 0, split = 1, cluster = 1;
+  ferrl::gemm_plan(a.M, a.N, a.K, 0, a.num_sms, &bn, &split, &cluster, nullptr);
+  if (glu_act >= 0 || cluster <= 1) {
+    if (split > 1 || cluster > 1 || bn == 32) bn = 128;      // whole tiles in one CTA
+    cluster = 1;
+  }
+  a.force_bn = bn;
+  a.cluster_k = cluster > 1 ? cluster : 0;
+  Tensor ss_out;
+  if (want_ss) {
+    TORCH_CHECK(glu_act < 0, "gemm_norm: no row statistics behind the GLU epilogue");
+    ss_out = at::empty({ferrl::gemm_ss_parts(a.N, bn, cluster), static_cast<long long>(a.M)}, A.options().dtype(at::kFloat));
+    a.ss_out = ss_out.data_ptr<float>(); a.ss_ld = a.M;
+  } else {
+    ss_out = at::empty({0}, A.options().dtype(at::kFloat));
+  }
+  if (a.M == 0) return {out, ss_out};
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return {out, ss_out};
+}
+
+Tensor row_sumsq(const Tensor& x) {
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "row_sumsq: bf16 [M,H]");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor ss = at::empty({1, x.size(0)}, x.options().dtype(at::kFloat));
+  FERRL_CHECK(ferrl::row_sumsq(x.data_ptr(), x.stride(0), ss.data_ptr<float>(), x.size(0), x.size(1), stream()));
+  return ss;
+}
+
 // Row-parallel projection fused with its tensor-parallel all-reduce:
 // out = sum_over_ranks(A_r B_r^T (+ A2 B2^T)) (+ residual), identical on every rank.
 Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
@@ -1009,6 +1070,8 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
   m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
+  m.def("gemm_norm(Tensor A, Tensor B, Tensor? residual, Tensor? ss_in, float eps, int glu_act, bool want_ss, bool static_b=True) -> (Tensor, Tensor)", &gemm_norm);
+  m.def("row_sumsq(Tensor x) -> Tensor", &row_sumsq);
   m.def("gemm_glu(Tensor A, Tensor B, int act, bool static_b=False) -> Tensor", &gemm_glu);
   m.def("qk_norm_rope_append(Tensor q, Tensor k, Tensor v, Tensor? qw, Tensor? kw, Tensor cos_t, Tensor sin_t, Tensor pos, float eps, bool zc, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len, Tensor? table) -> Tensor", &qk_norm_rope_append);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);

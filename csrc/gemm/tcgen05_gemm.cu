@@ -71,6 +71,13 @@ struct GemmParams {
   // of 16, eight gate rows followed by the eight up rows of the same features, and the kernel writes
   // act(gate) * up, N / 2 columns per row.  1 = SiLU, 2 = tanh-GELU.
   int glu_act;
+  // RMSNorm folded around the projection (decode): with ss_in the accumulator rows are scaled by
+  // rstd[row] = rsqrt(sum_t ss_in[t][row] * ss_inv_k + ss_eps) (the norm weight lives in B's columns);
+  // with ss_out the epilogue writes, per output row, the sum of squares of the values it stored to
+  // ss_out[part][row] (part = column tile, or column tile x cluster rank), summed by the consumer in
+  // part order: no atomics, so the normalisation stays bit-reproducible.
+  const float* ss_in; int ss_parts; long long ss_ld; float ss_inv_k, ss_eps;
+  float* ss_out;
 };
 
 // flag layout inside each rank's flag buffer: ready[tile][kMaxRanks] then done[tile]
@@ -447,6 +454,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int row = mi * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
       const int out_tile = mi * n_tiles + ni;
+      float rstd = 1.f, ssq = 0.f;
+      if (p.ss_in && row_ok) {
+        float sacc = 0.f;
+        for (int t = 0; t < p.ss_parts; ++t) sacc += p.ss_in[t * p.ss_ld + row];
+        rstd = rsqrtf(sacc * p.ss_inv_k + p.ss_eps);
+      }
       __nv_bfloat16* ar_slot = nullptr;
       if (AR)
         ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
@@ -486,6 +499,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (row_ok && col < p.N) {
           const int ncols = min(min(32, BN - c), p.N - col);
+          if (p.ss_in) {
+#pragma unroll
+            for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * rstd);
+          }
           if (HAS_RES) {
             const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
@@ -547,15 +564,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                   __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[v * 8 + 2 * e]),
                                                           __uint_as_float(r[v * 8 + 2 * e + 1]));
                   xp[e] = *reinterpret_cast<uint32_t*>(&h);
+                  if (p.ss_out) {
+                    const float2 hf = __bfloat1622float2(h);
+                    ssq += hf.x * hf.x + hf.y * hf.y;
+                  }
                 }
                 reinterpret_cast<uint4*>(op)[v] = x;
               }
             } else {
-              for (int e = 0; e < ncols; ++e) op[e] = __float2bfloat16_rn(__uint_as_float(r[e]));
+              for (int e = 0; e < ncols; ++e) {
+                const __nv_bfloat16 hb = __float2bfloat16_rn(__uint_as_float(r[e]));
+                op[e] = hb;
+                if (p.ss_out) ssq += __bfloat162float(hb) * __bfloat162float(hb);
+              }
             }
           }
         }
       }
+      if (p.ss_out && row_ok) p.ss_out[ni * p.ss_ld + row] = ssq;
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
@@ -827,6 +853,8 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.partial = a.partial;
   p.tile_expert = a.tile_expert;
   p.glu_act = a.glu_act;
+  p.ss_in = a.ss_in; p.ss_parts = a.ss_parts; p.ss_ld = a.ss_ld; p.ss_inv_k = a.ss_inv_k; p.ss_eps = a.ss_eps;
+  p.ss_out = a.ss_out;
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
   if (p.ar_world > 1) {
@@ -1409,9 +1437,16 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
     }
   }
   cluster_sync_all();                                 // all partials have landed in their owners' slots
+  float ssq = 0.f;
   if (epi && acc_ok && !*abort_flag) {
     const int row = mi * BM + row_in;
     const int col0 = ni * BN + rank * C::SLICE;
+    float rstd = 1.f;
+    if (p.ss_in && row < p.M) {
+      float sacc = 0.f;
+      for (int t = 0; t < p.ss_parts; ++t) sacc += p.ss_in[t * p.ss_ld + row];
+      rstd = rsqrtf(sacc * p.ss_inv_k + p.ss_eps);
+    }
 #pragma unroll 1
     for (int c = 0; c < C::SLICE; c += 16) {
       uint32_t r[16];
@@ -1447,9 +1482,19 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       const int col = col0 + c;
       if (row < p.M && col < p.N) {
         const int ncols = min(16, p.N - col);
+        if (p.ss_in) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc[e] *= rstd;
+        }
         if (HAS_RES) {
           const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
           for (int e = 0; e < ncols; ++e) acc[e] += __bfloat162float(rp[e]);
+        }
+        if (p.ss_out && !OUT_F32) {
+          for (int e = 0; e < ncols; ++e) {
+            const float hv = __bfloat162float(__float2bfloat16_rn(acc[e]));
+            ssq += hv * hv;
+          }
         }
         if (OUT_F32) {
           float* op = reinterpret_cast<float*>(p.out) + static_cast<long long>(row) * p.ldo + col;
@@ -1472,6 +1517,8 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
       }
     }
   }
+  if (epi && acc_ok && !*abort_flag && p.ss_out && (mi * BM + row_in) < p.M)
+    p.ss_out[(static_cast<long long>(ni) * S + rank) * p.ss_ld + mi * BM + row_in] = ssq;
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();                                 // nobody leaves while a peer may still read its slots' senders
@@ -1501,6 +1548,8 @@ const char* launch_ksplit(const GemmArgs& a, cudaStream_t stream) {
   p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 1;
   p.split_k = 1; p.ar_world = 1;
+  p.ss_in = a.ss_in; p.ss_parts = a.ss_parts; p.ss_ld = a.ss_ld; p.ss_inv_k = a.ss_inv_k; p.ss_eps = a.ss_eps;
+  p.ss_out = a.ss_out;
   auto kern = gemm_ksplit_kernel<BN, S, OUT_F32, HAS_RES>;
   static bool attr_set = false;
   if (!attr_set) {
@@ -2009,6 +2058,10 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
   if ((reinterpret_cast<uintptr_t>(a.A) & 15) || (reinterpret_cast<uintptr_t>(a.B) & 15) ||
       (a.K2 > 0 && ((reinterpret_cast<uintptr_t>(a.A2) & 15) || (reinterpret_cast<uintptr_t>(a.B2) & 15))))
     return "operand base addresses must be 16-byte aligned";
+  if (a.ss_in || a.ss_out) {
+    if (a.stream_k || a.two_cta || a.split_k > 1 || a.out_f32 || a.ar_world > 1 || a.tile_expert)
+      return "gemm with folded RMSNorm: one-SM or cluster split-k kernel, bf16 output, no global split or grouping";
+  }
   if (a.glu_act) {
     if (a.stream_k || a.cluster_k > 1 || a.two_cta || a.split_k > 1 || a.out_f32 || a.residual || a.ar_world > 1 || a.tile_expert ||
         (a.N % 16) || (a.ldo % 8))

@@ -595,6 +595,37 @@ __global__ void kv_append_paged_kernel(const __nv_bfloat16* __restrict__ k, cons
 }
 }  // namespace
 
+// ss[row] = sum of squares of a bf16 row (one warp per row): the first link of the chain of folded
+// RMSNorms in the decode loop, whose later links come out of the projections' epilogues.
+__global__ void row_sumsq_kernel(const __nv_bfloat16* __restrict__ x, long long ld, float* __restrict__ ss, int rows, int H) {
+  pdl_trigger();
+  pdl_wait();
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const __nv_bfloat16* xr = x + row * ld;
+  float acc = 0.f;
+  for (int i = lane * 8; i < H; i += 256) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(xr + i);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const float2 f = __bfloat1622float2(h[k]);
+      acc += f.x * f.x + f.y * f.y;
+    }
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) ss[row] = acc;
+}
+
+const char* row_sumsq(const void* x, long long ld, float* ss, int rows, int H, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  if ((H % 8) || (ld % 8) || (reinterpret_cast<uintptr_t>(x) & 15)) return "row_sumsq: bf16 rows of a multiple of 8, 16-byte aligned";
+  launch_pdl(row_sumsq_kernel, dim3((rows + 7) / 8), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(x), ld, ss, rows, H);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "row_sumsq launch failed";
+}
+
 const char* kv_append_paged(const void* k, const void* v, long long ldv, void* kc, void* vc, const int* kv_len,
                             const int* table, int bt_stride, int page, int batch, int HD, cudaStream_t s) {
   if (batch == 0) return nullptr;

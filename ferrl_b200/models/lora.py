@@ -172,6 +172,7 @@ class FusedLoraLinear(nn.Module):
             self.register_buffer("weight", w, persistent=False)
         self.register_buffer("weight_t", None, persistent=False)
         self.register_buffer("weight_merged", None, persistent=False)
+        self.weight_decode = None               # see enable_decode_fold()
         self._q = None
         self.scale = lora.scale if lora is not None else 0.0
         self.rank = lora.rank if lora is not None else 0
@@ -212,6 +213,7 @@ class FusedLoraLinear(nn.Module):
         if self.keep_transpose:
             self.weight_t = self.weight.t().contiguous()
         self.weight_merged = None
+        self.weight_decode = None
 
     # ------------------------------------------------------------- adapters
     def has_adapters(self) -> bool:
@@ -319,6 +321,40 @@ class FusedLoraLinear(nn.Module):
         self._glu_active = bool(ok)
         return self._glu_active
 
+    def enable_decode_fold(self, norm_weight, zero_centered: bool = False, glu: bool = False):
+        """Keep a second rollout snapshot ``weight_decode`` whose columns carry the weight of the
+        RMSNorm in front of this projection (and whose rows are interleaved for the GLU epilogue when
+        ``glu``): the decode chain then applies the norm as a per-row scale in the GEMM epilogue
+        (``ops.cuda.gemm_norm``) and needs no normalisation kernel.  Built by ``merge()`` on bf16
+        CUDA weights."""
+        self._fold_src = [norm_weight]          # in a list: not registered as this module's parameter
+        self._fold_zc = bool(zero_centered)
+        self._fold_glu = bool(glu)
+
+    @torch.no_grad()
+    def _refresh_decode_snapshot(self, plain: torch.Tensor):
+        """``plain``: the merged (or frozen) weight in its natural row order."""
+        src = getattr(self, "_fold_src", None)
+        if src is None or not plain.is_cuda or plain.dtype != torch.bfloat16:
+            self.weight_decode = None
+            return
+        scale = src[0].detach().float()
+        if self._fold_zc:
+            scale = scale + 1.0
+        wd = (plain.float() * scale[None, :]).to(plain.dtype)
+        if self._fold_glu:
+            half = plain.shape[0] // 2
+            if plain.shape[0] % 16 or half % 8:
+                self.weight_decode = None
+                return
+            g = torch.arange(half, device=plain.device).view(-1, 8)
+            wd = wd.index_select(0, torch.stack([g, g + half], dim=1).reshape(-1))
+        cur = getattr(self, "weight_decode", None)
+        if cur is not None and cur.shape == wd.shape:
+            cur.copy_(wd)                        # stable address for captured decode graphs
+        else:
+            self.weight_decode = wd
+
     def forward_merged_glu(self, x: torch.Tensor, act: str) -> torch.Tensor:
         """``act(x Wg^T) * (x Wu^T)`` over the merged snapshot; one kernel where the snapshot is
         interleaved, projection + GLU kernel otherwise."""
@@ -335,8 +371,10 @@ class FusedLoraLinear(nn.Module):
         if a is None:
             self.weight_merged = None
             self._glu_active = False
+            self._refresh_decode_snapshot(self.weight)
             return
         new = ops.lora_merge(self.weight, a.detach(), b.detach())
+        self._refresh_decode_snapshot(new)
         if self._glu_prepare():
             new = new.index_select(0, self._glu_perm)
         if self.weight_merged is not None and self.weight_merged.shape == new.shape:

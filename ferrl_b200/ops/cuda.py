@@ -71,6 +71,21 @@ def gemm_glu(x, w_interleaved, act="silu"):
     return y.view(*x.shape[:-1], w_interleaved.shape[0] // 2)
 
 
+def gemm_norm(x, w, residual=None, ss_in=None, eps=1e-6, glu_act=None, want_ss=False):
+    """Decode-chain projection with an RMSNorm folded around it: with ``ss_in`` ``[parts, M]`` (partial row
+    sums of squares of ``x``) the result rows are scaled by ``rsqrt(sum / K + eps)`` in the epilogue (the
+    norm weight must already be folded into ``w``'s columns); ``want_ss`` also returns the partial row sums
+    of squares of the stored output for the next projection; ``glu_act`` runs the GLU in the epilogue
+    (``w`` interleaved as for ``gemm_glu``).  ``x`` ``[M, K]``; returns ``(y, ss_or_None)``."""
+    y, ss = lib().gemm_norm(x, w, residual, ss_in, float(eps), -1 if glu_act is None else _ACT[glu_act], bool(want_ss), True)
+    return y, (ss if want_ss else None)
+
+
+def row_sumsq(x):
+    """``[1, M]`` float32 sums of squares of the bf16 rows of ``x`` ``[M, H]``."""
+    return lib().row_sumsq(x)
+
+
 def _pad8(t, dim):
     n = t.shape[dim]
     if n % 8 == 0:

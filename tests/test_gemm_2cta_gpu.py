@@ -266,3 +266,47 @@ def test_fused_linear_glu_layout_matches_plain_snapshot():
         plain = b.forward_merged(x)
     assert ((got.float() - ref.float()).norm() / ref.float().norm()).item() < 1e-2
     assert torch.equal(plain, a.forward_merged(x))
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 6144, 4096), (128, 4096, 12288), (96, 4096, 4096), (128, 1024, 512), (300, 2048, 1024)])
+def test_gemm_folded_rmsnorm_chain(M, N, K):
+    """RMSNorm folded around projections: the producer's epilogue writes partial row sums of squares of
+    what it stores, the consumer scales its rows by the resulting rstd and reads weights that carry
+    the norm weight, against rmsnorm + matmul in fp32."""
+    from ferrl_b200.ops import cuda as C
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device=dev).manual_seed(M + N + K)
+    eps = 1e-6
+    a = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w1 = (torch.randn(N, K, device=dev, generator=g) / K ** 0.5).to(torch.bfloat16)
+    res = torch.randn(M, N, device=dev, generator=g).to(torch.bfloat16)
+    # producer: h = res + a w1^T, with row statistics
+    h, ss = C.gemm_norm(a, w1, res, None, 0.0, None, True)
+    h_ref = res.float() + a.float() @ w1.float().t()
+    assert ((h.float() - h_ref).norm() / h_ref.norm()).item() < 1e-2
+    assert ss.dim() == 2 and ss.shape[1] == M
+    ss_ref = h.float().pow(2).sum(-1)
+    assert ((ss.sum(0) - ss_ref).abs() / ss_ref).max().item() < 1e-4
+    assert torch.equal(ss, C.gemm_norm(a, w1, res, None, 0.0, None, True)[1])       # fixed order
+    # consumer: y = rmsnorm(h, wn) w2^T through the folded weight
+    wn = (1 + 0.2 * torch.randn(N, device=dev, generator=g)).to(torch.bfloat16)
+    w2 = (torch.randn(512, N, device=dev, generator=g) / N ** 0.5).to(torch.bfloat16)
+    folded = (w2.float() * wn.float()[None, :]).to(torch.bfloat16)
+    y, none = C.gemm_norm(h, folded, None, ss, eps)
+    assert none is None
+    hf = h.float()
+    xn = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * wn.float()
+    y_ref = xn @ w2.float().t()
+    assert ((y.float() - y_ref).norm() / y_ref.norm()).item() < 1.5e-2
+    # consumer with the GLU epilogue
+    F = 256
+    wg = (torch.randn(2 * F, N, device=dev, generator=g) / N ** 0.5).to(torch.bfloat16)
+    idx = torch.arange(F, device=dev).view(-1, 8)
+    perm = torch.stack([idx, idx + F], dim=1).reshape(-1)
+    wgf = (wg.float() * wn.float()[None, :]).to(torch.bfloat16).index_select(0, perm).contiguous()
+    z, _ = C.gemm_norm(h, wgf, None, ss, eps, "silu")
+    gu = xn @ wg.float().t()
+    z_ref = torch.nn.functional.silu(gu[:, :F]) * gu[:, F:]
+    assert ((z.float() - z_ref).norm() / z_ref.norm()).item() < 2e-2
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
