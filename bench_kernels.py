@@ -351,6 +351,19 @@ def main():
         s = T(lambda: C.adamw_step(p, g, m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.0, step=1,
                                    max_norm=1.0, compute_norm=True))
         report(f"adamw + norm + clip, {len(p)} tensors {n / 1e6:.1f}M", s, n * 4 * 8)
+        from ferrl_b200.grpo import LossConfig, grpo_loss
+        G, L = 128, 1024
+        lp = (-torch.rand(G, L, device=dev)).requires_grad_(True)
+        lo, lr_ = lp.detach() + 0.1 * torch.randn(G, L, device=dev), lp.detach() + 0.1 * torch.randn(G, L, device=dev)
+        adv, mask = torch.randn(G, device=dev), (torch.rand(G, L, device=dev) > 0.2).float()
+        cfg = LossConfig(0.2, 0.28, 0.04)
+
+        def loss_fb():
+            lp.grad = None
+            grpo_loss(lp, lo, lr_, adv, mask, cfg).backward()
+
+        s = T(loss_fb)
+        report(f"GRPO loss forward + backward {G} x {L} (one kernel + row scaling)", s, G * L * 4 * 6)
     if args.json:
         with open(args.json, "w") as f:
             json.dump({"peaks": {"hbm_Bps": hbm, "bf16_flops": flops_peak, "source": src}, "rows": rows}, f, indent=1)
