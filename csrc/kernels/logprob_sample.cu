@@ -212,7 +212,6 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
   }
   m = block_max(m, red);
 
-  auto e_of = [&](int i) -> float { return __expf((to_f(x[i]) - m) * inv_t); };
   auto e_val = [&](float xv) -> float { return __expf((xv - m) * inv_t); };   // exp(-inf) = 0 for padding lanes
   auto fix_of = [&](float e) -> unsigned long long { return static_cast<unsigned long long>(e * FIX); };
 

@@ -309,14 +309,19 @@ class FusedLoraLinear(nn.Module):
             return None
         return self._glu_perm
 
+    @staticmethod
+    def glu_row_order(half: int, device=None) -> torch.Tensor:
+        """Row order of an interleaved [gate | up] weight: groups of 16 rows, the 8 gate rows of features
+        ``8q .. 8q+7`` followed by their 8 up rows (``half`` = number of features, a multiple of 8)."""
+        g = torch.arange(half, device=device).view(-1, 8)
+        return torch.stack([g, g + half], dim=1).reshape(-1)
+
     def _glu_prepare(self) -> bool:
         w = self.weight
         ok = getattr(self, "_glu_requested", False) and w.is_cuda and w.dtype == torch.bfloat16 and \
             w.shape[0] % 16 == 0 and (w.shape[0] // 2) % 8 == 0
         if ok and (getattr(self, "_glu_perm", None) is None or self._glu_perm.device != w.device):
-            half = w.shape[0] // 2
-            g = torch.arange(half, device=w.device).view(-1, 8)
-            self._glu_perm = torch.stack([g, g + half], dim=1).reshape(-1)          # [8 gate, 8 up, 8 gate, ...]
+            self._glu_perm = self.glu_row_order(w.shape[0] // 2, w.device)
             self._glu_inverse = torch.argsort(self._glu_perm)
         self._glu_active = bool(ok)
         return self._glu_active
@@ -347,8 +352,7 @@ class FusedLoraLinear(nn.Module):
             if plain.shape[0] % 16 or half % 8:
                 self.weight_decode = None
                 return
-            g = torch.arange(half, device=plain.device).view(-1, 8)
-            wd = wd.index_select(0, torch.stack([g, g + half], dim=1).reshape(-1))
+            wd = wd.index_select(0, self.glu_row_order(half, plain.device))
         cur = getattr(self, "weight_decode", None)
         if cur is not None and cur.shape == wd.shape:
             cur.copy_(wd)                        # stable address for captured decode graphs

@@ -458,3 +458,21 @@ def test_preflight_with_fake_cuda():
         with pytest.raises(PreflightError) as e:
             check_device(0, probe=probe, **kw)
         assert e.value.kind == kind
+
+
+def test_glu_row_order_interleaves_gate_and_up():
+    """Interleaved [gate | up] layout read by the GEMM's GLU epilogue: 8 gate rows, then the 8 up rows
+    of the same features; applying it to a weight and splitting 16-row groups recovers both halves."""
+    import torch
+    from ferrl_b200.models.lora import FusedLoraLinear
+    F = 24
+    perm = FusedLoraLinear.glu_row_order(F)
+    assert perm.tolist()[:16] == list(range(8)) + list(range(F, F + 8))
+    assert sorted(perm.tolist()) == list(range(2 * F))
+    w = torch.arange(2 * F * 3, dtype=torch.float32).view(2 * F, 3)
+    wi = w.index_select(0, perm).view(-1, 2, 8, 3)
+    assert torch.equal(wi[:, 0].reshape(F, 3), w[:F]) and torch.equal(wi[:, 1].reshape(F, 3), w[F:])
+    x = torch.randn(5, 3)
+    y = x @ w.index_select(0, perm).t()
+    inv = torch.argsort(perm)
+    assert torch.allclose(y.index_select(-1, inv), x @ w.t())
