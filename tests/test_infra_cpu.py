@@ -476,3 +476,40 @@ def test_glu_row_order_interleaves_gate_and_up():
     y = x @ w.index_select(0, perm).t()
     inv = torch.argsort(perm)
     assert torch.allclose(y.index_select(-1, inv), x @ w.t())
+
+
+def test_gloo_rank_leaves_between_steps_is_detected(tmp_path):
+    """Failure detection without a GPU: rank 1 completes a step and exits; rank 0's next collective ends
+    with a typed communication error after the short process-group timeout, and the communicator stays
+    poisoned so that no later step can run on half a job."""
+    import subprocess
+    import sys
+    code = (
+        "import sys, torch\n"
+        "from ferrl_b200.comm import TorchDistComm, CommError, CommPoisoned\n"
+        "c = TorchDistComm.bootstrap(backend='gloo', timeout_s=4)\n"
+        "t = [torch.ones(2)]; c.all_reduce_sum(t); assert t[0].tolist() == [2.0, 2.0]\n"
+        "c.barrier()\n"
+        "if c.rank == 1:\n"
+        "    print('LEFT', flush=True); sys.exit(0)\n"
+        "try:\n"
+        "    c.all_reduce_sum([torch.ones(2)])\n"
+        "    print('NO_ERROR', flush=True); sys.exit(3)\n"
+        "except CommError as e:\n"
+        "    print('DETECTED', type(e).__name__, flush=True)\n"
+        "try:\n"
+        "    c.barrier()\n"
+        "    print('NOT_POISONED', flush=True); sys.exit(4)\n"
+        "except CommPoisoned:\n"
+        "    print('POISONED', flush=True)\n"
+        "import os; os._exit(0)\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), MASTER_ADDR="127.0.0.1", MASTER_PORT="29643",
+                   PYTHONPATH=root)
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True))
+    outs = [p.communicate(timeout=180) for p in procs]
+    assert "LEFT" in outs[1][0]
+    assert procs[0].returncode == 0, outs[0][1][-2000:]
+    assert "DETECTED" in outs[0][0] and "POISONED" in outs[0][0], outs[0][0] + outs[0][1][-1500:]
