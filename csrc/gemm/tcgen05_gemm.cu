@@ -250,6 +250,20 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
 
 // OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
 // AR: fused all-reduce mode (compiled separately so the plain kernel carries none of its registers).
+// rstd of one row from the partial sums of squares its producer wrote (summed in part order, 16 loads in
+// flight at a time: the epilogue threads call this while the main loop is still running)
+__device__ __forceinline__ float row_rstd(const float* __restrict__ ss, int parts, long long ld, int row, float inv_k, float eps) {
+  float sacc = 0.f;
+  for (int t0 = 0; t0 < parts; t0 += 16) {
+    float v[16];
+#pragma unroll
+    for (int k = 0; k < 16; ++k) v[k] = (t0 + k < parts) ? ss[(t0 + k) * ld + row] : 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) sacc += v[k];
+  }
+  return rsqrtf(sacc * inv_k + eps);
+}
+
 template <int BN, bool OUT_F32, bool HAS_RES, bool AR>
 __global__ void __launch_bounds__(AR ? NUM_THREADS + 128 : NUM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -447,19 +461,20 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int ks, mi, ni;
       tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       if (p.tile_expert && p.tile_expert[mi] < 0) continue;
+      const int row = mi * BM + q * 32 + lane;
+      const bool row_ok = row < p.M;
+      float rstd = 1.f, ssq = 0.f;
+      if (p.ss_in) {
+        // gathered while the main loop runs; the statistics come from the stream predecessor, and this
+        // thread is not ordered behind the producer warp's dependency wait yet
+        if (p.pdl) pdl_wait();
+        if (row_ok) rstd = row_rstd(p.ss_in, p.ss_parts, p.ss_ld, row, p.ss_inv_k, p.ss_eps);
+      }
       const int acc = (it++) & 1;
       if (!mbar_wait(&acc_full[acc], acc_phase[acc], abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit)) break;
       acc_phase[acc] ^= 1;
       tc_fence_after();
-      const int row = mi * BM + q * 32 + lane;
-      const bool row_ok = row < p.M;
       const int out_tile = mi * n_tiles + ni;
-      float rstd = 1.f, ssq = 0.f;
-      if (p.ss_in && row_ok) {
-        float sacc = 0.f;
-        for (int t = 0; t < p.ss_parts; ++t) sacc += p.ss_in[t * p.ss_ld + row];
-        rstd = rsqrtf(sacc * p.ss_inv_k + p.ss_eps);
-      }
       __nv_bfloat16* ar_slot = nullptr;
       if (AR)
         ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
@@ -1406,6 +1421,12 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   const int row_in = q * 32 + lane;                 // accumulator row held by this thread
   const bool have = kb_end > kb_begin;              // a slice can be empty when kb_total < S
   bool acc_ok = true;
+  float rstd = 1.f;
+  if (epi && p.ss_in) {
+    // gathered while the main loop runs (see row_rstd); the statistics come from the stream predecessor
+    if (p.pdl) pdl_wait();
+    if (mi * BM + row_in < p.M) rstd = row_rstd(p.ss_in, p.ss_parts, p.ss_ld, mi * BM + row_in, p.ss_inv_k, p.ss_eps);
+  }
   if (epi) {
     if (have) acc_ok = mbar_wait(acc_full, 0, abort_flag, p.status, kStatusWaitTimeoutEpilogue);
     tc_fence_after();
@@ -1441,12 +1462,7 @@ gemm_ksplit_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constan
   if (epi && acc_ok && !*abort_flag) {
     const int row = mi * BM + row_in;
     const int col0 = ni * BN + rank * C::SLICE;
-    float rstd = 1.f;
-    if (p.ss_in && row < p.M) {
-      float sacc = 0.f;
-      for (int t = 0; t < p.ss_parts; ++t) sacc += p.ss_in[t * p.ss_ld + row];
-      rstd = rsqrtf(sacc * p.ss_inv_k + p.ss_eps);
-    }
+
 #pragma unroll 1
     for (int c = 0; c < C::SLICE; c += 16) {
       uint32_t r[16];

@@ -221,8 +221,9 @@ class DenseLayer(nn.Module):
 
 
 # Opt-in (FERRL_DECODE_FOLD=1): on the Qwen3-8B benchmark the folded chain launches 37 % fewer kernels
-# per decode step but is not faster (the consumers' epilogues gather up to 128 partial sums per row),
-# and its snapshots cost 9 GB, so the default decode step keeps the two RMSNorm kernels per layer.
+# per decode step and shortens rollout by 1.5 %, but its extra snapshots (9 GB) slow the training
+# phases of the same step by more than that, so the default decode step keeps the two RMSNorm
+# kernels per layer.
 _DECODE_FOLD = os.environ.get("FERRL_DECODE_FOLD", "0") == "1"
 
 
