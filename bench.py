@@ -262,6 +262,8 @@ def main():
             "gpu_launches": int(launches),
             "phase_ms_per_step": {k: round(v / args.steps, 2) for k, v in phase.items()},
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+            "peak_reserved_gb": round(torch.cuda.max_memory_reserved() / 2 ** 30, 1),
+            "alloc_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),
             "remat": bool(args.remat), "microbatch_rows": args.microbatch,
         }
         print(json.dumps(out))
