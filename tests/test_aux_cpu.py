@@ -1,0 +1,169 @@
+"""CPU tests of the smaller seams: rematerialisation, build identity, evaluation, discovery SDK."""
+import os
+import subprocess
+
+import pytest
+import torch
+
+FIX = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fixtures")
+
+
+def test_remat_segment_matches_plain_autograd():
+    from ferrl_b200.remat import RematTape, remat_segment
+    torch.manual_seed(0)
+    w1 = torch.randn(6, 6, requires_grad=True)
+    w2 = torch.randn(6, 6, requires_grad=True)
+    frozen = torch.randn(6, 6)
+    x = torch.randn(4, 6, requires_grad=True)
+
+    def seg(h):
+        return torch.tanh(h @ w1) @ frozen + torch.sin(h @ w2)
+
+    ref = seg(seg(x)).pow(2).sum()
+    gref = torch.autograd.grad(ref, (x, w1, w2))
+    calls = []
+
+    def counted(h):
+        calls.append(1)
+        return seg(h)
+
+    tape = RematTape()
+    h = remat_segment(counted, tape.capture(x), (w1, w2, frozen))
+    y = remat_segment(counted, tape.capture(h), (w1, w2, frozen)).pow(2).sum()
+    got = torch.autograd.grad(y, (x, w1, w2))
+    assert torch.allclose(y, ref)
+    for a, b in zip(got, gref):
+        assert torch.allclose(a, b, atol=1e-6)
+    assert len(calls) == 4                      # two forwards, two replays in the backward
+    assert tape.bytes_held() == 2 * 4 * 6 * 4
+    with torch.no_grad():
+        assert torch.equal(remat_segment(seg, x, (w1, w2)), seg(x))
+    # a cotangent transform is applied to the segment's input gradient only
+    y2 = remat_segment(seg, x, (w1,), cot_transform=lambda g: 2 * g).sum()
+    gx, gw = torch.autograd.grad(y2, (x, w1))
+    px, pw = torch.autograd.grad(seg(x).sum(), (x, w1))
+    assert torch.allclose(gx, 2 * px, atol=1e-6) and torch.allclose(gw, pw, atol=1e-6)
+
+
+def test_build_identity_tracks_commit_and_dirt(tmp_path, monkeypatch):
+    from ferrl_b200.build_identity import BuildIdentityError, require_clean, source_identity
+    monkeypatch.delenv("FERRL_B200_ALLOW_DIRTY", raising=False)
+    nogit = source_identity(str(tmp_path))
+    assert nogit.commit == "unknown" and nogit.dirty
+    with pytest.raises(BuildIdentityError):
+        require_clean(nogit)
+    require_clean(nogit, allow_dirty=True)
+    repo = tmp_path / "r"
+    repo.mkdir()
+    env = dict(os.environ, GIT_AUTHOR_NAME="t", GIT_AUTHOR_EMAIL="t@t", GIT_COMMITTER_NAME="t", GIT_COMMITTER_EMAIL="t@t")
+    run = lambda *a: subprocess.run(["git", *a], cwd=repo, env=env, check=True, capture_output=True)  # noqa: E731
+    run("init", "-q")
+    (repo / "f.txt").write_text("a")
+    run("add", "f.txt")
+    run("commit", "-q", "-m", "one")
+    clean = source_identity(str(repo))
+    assert len(clean.commit) == 40 and not clean.dirty and clean.to_json() == {"git_commit": clean.commit, "git_dirty": False}
+    require_clean(clean)
+    (repo / "f.txt").write_text("b")
+    dirty = source_identity(str(repo))
+    assert dirty.commit == clean.commit and dirty.dirty
+    with pytest.raises(BuildIdentityError):
+        require_clean(dirty)
+    monkeypatch.setenv("FERRL_B200_ALLOW_DIRTY", "1")
+    require_clean(dirty)
+
+
+def _digit_fraction(sample, completion):
+    """Fraction of the completion's characters that are digits (any deterministic function will do)."""
+    return sum(ch.isdigit() for ch in completion) / max(1, len(completion))
+
+
+def test_discovery_sdk_runs_a_task_and_publishes_outcome_last(tmp_path):
+    """The narrow entry point: a task (samples + reward) and a config in, a run directory with ranked
+    candidates, a health verdict, an eval comparison and a manifest-last outcome file out."""
+    import json
+    from ferrl_b200.config import TrainerConfig
+    from ferrl_b200.discovery import Discovery, DiscoveryConfig, DiscoveryTask
+    from ferrl_b200.rewards import FnReward, Sample
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    samples = [Sample(f"make {i} from 1 2 3", None) for i in range(6)]
+    tr = TrainerConfig(steps=2, group_size=4, max_new_tokens=5, checkpoint_every=1, eos_token_id=None,
+                       truncation_masking=False)
+    cfg = (DiscoveryConfig.Builder(os.path.join(FIX, "tiny_qwen3")).out_dir(str(tmp_path)).trainer(tr).lora(4, 8.0)
+           .candidate_top_k(3).build())
+    with pytest.raises(ValueError):
+        DiscoveryConfig.Builder("x").candidate_top_k(0).build()
+    task = DiscoveryTask("digits", samples[:4], FnReward(_digit_fraction), samples[4:])
+    out = Discovery(task, cfg, tokenizer=SyntheticTokenizer(32, 4, 8)).run()
+    assert out.stop == "completed" and out.steps_run == 2 and 1 <= len(out.best) <= 3
+    assert all(a.reward >= b.reward for a, b in zip(out.best, out.best[1:]))
+    assert out.eval_improvement is not None
+    path = os.path.join(out.run_dir, "discovery-outcome.json")
+    assert os.path.exists(path) and not os.path.exists(path + ".tmp")
+    js = json.load(open(path))
+    assert js["steps_run"] == 2 and js["health_verdict"] == out.health_verdict and len(js["best"]) == len(out.best)
+    import ferrl_b200.orchestration as orch
+    assert orch.build_task.__name__ == "build_task"          # the task hook is restored after the run
+
+
+def test_evaluate_compares_base_and_adapter_and_restores_state():
+    from ferrl_b200.eval import EvalError, evaluate
+    from ferrl_b200.policy import GenConfig
+    from ferrl_b200.rewards import Sample
+
+    class Tok:
+        def encode(self, s):
+            return [ord(c) % 7 for c in s]
+
+        def decode(self, ids):
+            return "".join(str(int(i)) for i in ids)
+
+    class FakeRollout:
+        def __init__(self, rows):
+            self.rows = rows
+
+        def __len__(self):
+            return len(self.rows)
+
+        def completion(self, i):
+            return self.rows[i]
+
+    class FakePolicy:
+        def __init__(self):
+            self.enabled, self.state, self.calls = True, 7, []
+
+        def sampler_state(self):
+            return self.state
+
+        def restore_sampler_state(self, s):
+            self.state = s
+
+        def adapter_enabled(self):
+            return self.enabled
+
+        def set_adapter_enabled(self, on):
+            self.enabled = on
+
+        def generate_batch(self, prompts, gen, bases):
+            self.state += 1
+            self.calls.append((self.enabled, tuple(bases)))
+            tok = 9 if self.enabled else 0          # the "adapter" emits the digit the reward likes
+            return [FakeRollout([[tok] * 3 for _ in range(gen.group_size)]) for _ in prompts]
+
+    class Nine:
+        def reward_group(self, sample, comps):
+            return [c.count("9") / len(c) for c in comps]
+
+    pol = FakePolicy()
+    pol.enabled = False
+    samples = [Sample(f"p{i}", None) for i in range(5)]
+    rep = evaluate(pol, Nine(), Tok(), samples, GenConfig(group_size=2, max_new_tokens=3), batch_prompts=2)
+    assert rep.base_reward_mean == 0.0 and rep.adapter_reward_mean == 1.0 and rep.improvement() == 1.0 and len(rep.per_prompt) == 5
+    assert rep.to_json()["improvement"] == 1.0 and rep.n_prompts == 5 and rep.group_size == 2
+    assert pol.enabled is False and pol.state == 7                       # adapter switch and sampler rolled back
+    assert [c[0] for c in pol.calls] == [False] * 3 + [True] * 3           # paired: same row bases for both passes
+    assert [c[1] for c in pol.calls[:3]] == [c[1] for c in pol.calls[3:]]
+    with pytest.raises(EvalError):
+        evaluate(pol, Nine(), Tok(), [], GenConfig(group_size=2, max_new_tokens=3))
+    with pytest.raises(EvalError):
+        evaluate(pol, Nine(), Tok(), samples, GenConfig(group_size=0, max_new_tokens=3))
