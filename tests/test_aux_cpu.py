@@ -167,3 +167,57 @@ def test_evaluate_compares_base_and_adapter_and_restores_state():
         evaluate(pol, Nine(), Tok(), [], GenConfig(group_size=2, max_new_tokens=3))
     with pytest.raises(EvalError):
         evaluate(pol, Nine(), Tok(), samples, GenConfig(group_size=0, max_new_tokens=3))
+
+
+_EP_WORKER = r'''
+import os, sys, torch
+import torch.distributed as dist
+from ferrl_b200.models import moe as M
+from ferrl_b200.parallel import ep
+dist.init_process_group("gloo", init_method="env://")
+rank, world = dist.get_rank(), dist.get_world_size()
+torch.manual_seed(11)                                   # every rank builds the same full problem
+T, H, I, E, k = 37, 16, 24, 8, 2
+x = torch.randn(T, H)
+router = torch.randn(E, H)
+gate_up = torch.randn(E, 2 * I, H) * 0.2
+down = torch.randn(E, H, I) * 0.2
+x_local = x[rank::world].clone().requires_grad_(True)    # each rank routes its own tokens
+El = E // world
+
+def a2a(rows, per_rank, expert_counts):
+    send = [int(v) for v in per_rank.tolist()]
+    recv_n = torch.zeros(world, dtype=torch.long)
+    dist.all_to_all_single(recv_n, torch.tensor(send, dtype=torch.long))
+    recv = rows.new_empty((int(recv_n.sum()), rows.shape[1]))
+    dist.all_to_all_single(recv, rows.contiguous(), [int(v) for v in recv_n.tolist()], send)
+    rec = None
+    if expert_counts is not None:
+        rec = torch.zeros(world, El, dtype=torch.long)
+        dist.all_to_all_single(rec, expert_counts.contiguous().long())
+    return recv, recv_n, rec
+
+ep.install(ep.EpContext(rank, world, all_to_all_rows=a2a))
+y = ep.sparse_moe(x_local, router, gate_up[rank * El:(rank + 1) * El], down[rank * El:(rank + 1) * El], k, None, None)
+ep.install(None)
+ref = M.sparse_moe_block(x[rank::world], router, gate_up, down, k)
+err = (y - ref).abs().max().item()
+assert err < 1e-4, err
+print("EP_OK", rank, err, flush=True)
+dist.destroy_process_group()
+'''
+
+
+def test_expert_parallel_host_path_two_gloo_ranks():
+    """Experts sharded over two CPU ranks (dispatch and combine through gloo all-to-all) give the same
+    block output as one rank holding every expert."""
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", MASTER_ADDR="127.0.0.1", MASTER_PORT="29647", PYTHONPATH=root)
+        procs.append(subprocess.Popen([sys.executable, "-c", _EP_WORKER], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.PIPE, text=True))
+    for p in procs:
+        out, err = p.communicate(timeout=240)
+        assert p.returncode == 0 and "EP_OK" in out, err[-2500:]
