@@ -221,3 +221,24 @@ def test_expert_parallel_host_path_two_gloo_ranks():
     for p in procs:
         out, err = p.communicate(timeout=240)
         assert p.returncode == 0 and "EP_OK" in out, err[-2500:]
+
+
+def test_examples_run_end_to_end_on_cpu(tmp_path):
+    """Every CPU example runs as a user would start it; the run report reads what the trainer wrote."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+    def run(*args):
+        r = subprocess.run([sys.executable, *args], cwd=root, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        return r.stdout
+
+    out = run("examples/countdown_grpo.py", "--steps", "2", "--out", str(tmp_path))
+    assert "COMPLETED" in out
+    runs = [d for d in os.listdir(tmp_path) if os.path.isdir(tmp_path / d)]
+    assert len(runs) == 1
+    report = run("examples/runreport.py", str(tmp_path / runs[0]))
+    assert "2 steps" in report
+    assert "reward per step" in run("examples/minimal_task.py")
+    assert "step 0" in run("examples/countdown_grpo_qwen35.py", "--steps", "1", "--moe")

@@ -218,3 +218,45 @@ def test_ledger_collect_then_learn_equals_direct(tmp_path):
         assert torch.equal(p.detach(), q.detach())
     with pytest.raises(L.LedgerError):
         L.RolloutLedgerReader(str(tmp_path / "ledger"), L.LedgerIdentity("f" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0))
+
+
+_GLOO_DP_WORKER = r"""
+import hashlib, os, sys
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, os.path.join(sys.argv[1], "tests"))
+import torch
+import test_trainer_cpu as T
+from ferrl_b200.comm import TorchDistComm
+from ferrl_b200.rewards import FnReward
+from ferrl_b200.trainer import Trainer
+
+comm = TorchDistComm.bootstrap(backend="gloo", timeout_s=120.0)
+tr = Trainer(T.make_policy(), T.ListTok(), FnReward(T.echo_reward), T.samples(),
+             T.cfg(steps=2, prompts_per_item=1), comm=comm)
+tr.train()
+digest = hashlib.sha256(b"".join(p.detach().numpy().tobytes() for p in tr.params)).digest()
+comm.require_consensus(digest, "adapters after two steps")
+assert any(m.grad_norm > 0 for m in tr.history), [m.grad_norm for m in tr.history]
+if comm.rank == 0:
+    torch.save([p.detach().clone() for p in tr.params], sys.argv[2])
+comm.barrier()
+"""
+
+
+def test_dp_two_gloo_processes_match_single_rank(tmp_path):
+    """The same equivalence with real processes: two gloo ranks under the launcher end in
+    consensus on non-trivial gradients and match the one-rank run with two accumulation steps."""
+    import subprocess
+    import sys
+    script = tmp_path / "worker.py"
+    script.write_text(_GLOO_DP_WORKER)
+    out = tmp_path / "params.pt"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29671", str(script), root, str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    single = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, grad_accum_steps=2, prompts_per_item=1))
+    single.train()
+    got = torch.load(out)
+    for p, q in zip(single.params, got):
+        assert torch.allclose(p.detach(), q, atol=2e-5), (p.detach() - q).abs().max()
