@@ -260,3 +260,86 @@ def test_dp_two_gloo_processes_match_single_rank(tmp_path):
     got = torch.load(out)
     for p, q in zip(single.params, got):
         assert torch.allclose(p.detach(), q, atol=2e-5), (p.detach() - q).abs().max()
+
+
+def test_ledger_two_ranks_stage_shards_rank0_commits_and_learners_match_direct(tmp_path):
+    """Collector and learner separated under data parallelism: each rank stages its own shard,
+    rank 0 publishes one manifest covering both, and two learners that replay their shards end
+    with the same adapters as two ranks that trained directly."""
+    import json
+    from ferrl_b200 import ledger as L
+    ident = L.LedgerIdentity("a" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)
+    led = str(tmp_path / "ledger")
+
+    def direct(comm):
+        tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1, prompts_per_item=1), comm=comm)
+        tr.step(0)
+        return [p.detach().clone() for p in tr.params]
+
+    def collect(comm):
+        tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1, prompts_per_item=1), comm=comm)
+        w = L.RolloutLedgerWriter(led, ident, rank=comm.rank, world_size=comm.world_size)
+        st = tr.collect_to_ledger(0, w)
+        return st.rank, [g.prompt_index for g in st.groups]
+
+    def learn(comm):
+        rec = L.RolloutLedgerReader(led, ident).read_step(0, rank=comm.rank)
+        tr = Trainer(make_policy(), ListTok(), FnReward(lambda s, c: 0.0), samples(), cfg(steps=1, prompts_per_item=1), comm=comm)
+        tr.train_from_ledger(rec)
+        return [p.detach().clone() for p in tr.params]
+
+    want = run_ranks(2, direct)
+    shards = run_ranks(2, collect)
+    assert [s[0] for s in shards] == [0, 1]
+    assert set(shards[0][1]).isdisjoint(shards[1][1])               # ranks drew different prompts
+    man = json.load(open(os.path.join(led, "manifest.json")))
+    assert man["world_size"] == 2 and sorted((e["step"], e["rank"]) for e in man["steps"]) == [(0, 0), (0, 1)]
+    got = run_ranks(2, learn)
+    for r in range(2):
+        for p, q in zip(want[r], got[r]):
+            assert torch.equal(p, q)
+    # a learner of the wrong rank refuses the shard
+    rec1 = L.RolloutLedgerReader(led, ident).read_step(0, rank=1)
+    solo = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1, prompts_per_item=1))
+    with pytest.raises(Exception, match="different rank/world"):
+        solo.train_from_ledger(rec1)
+
+
+def test_ledger_rejects_tampering_replacement_and_malformed_steps(tmp_path):
+    from ferrl_b200 import ledger as L
+    ident = L.LedgerIdentity("a" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)
+    led = str(tmp_path / "ledger")
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    w = L.RolloutLedgerWriter(led, ident)
+    st = tr.collect_to_ledger(0, w)
+    with pytest.raises(L.LedgerError, match="never replaced"):
+        w.stage_step(st)
+    with pytest.raises(L.LedgerError, match="no shard"):
+        L.RolloutLedgerReader(led, ident).read_step(3)
+    # controls of the learner must agree with the collector's (schedules excepted)
+    import dataclasses
+    other = dataclasses.replace(st.controls, group_size=st.controls.group_size + 1)
+    with pytest.raises(L.LedgerError, match="group_size"):
+        L.RolloutLedgerReader(led, ident, controls=other).read_step(0)
+    sched = dataclasses.replace(st.controls, effective_lr_bits=L.f64_bits(123.0))
+    assert L.RolloutLedgerReader(led, ident, controls=sched).read_step(0).step == 0
+    # structural validation
+    bad = L.LedgerStep.from_json(st.to_json())
+    bad.groups[0].token_ids[0][0] ^= 1
+    with pytest.raises(L.LedgerError, match="start with its prompt"):
+        bad.validate()
+    bad = L.LedgerStep.from_json(st.to_json())
+    bad.groups[0].completion_lens[0] = st.controls.completion_width + 1
+    with pytest.raises(L.LedgerError, match="out of range"):
+        bad.validate()
+    with pytest.raises(L.LedgerError, match="malformed"):
+        L.LedgerStep.from_json({"step": 0})
+    # a flipped byte in the shard file is caught by its recorded digest
+    p = w.step_path(0, 0)
+    raw = bytearray(open(p, "rb").read())
+    raw[len(raw) // 2] ^= 1
+    open(p, "wb").write(bytes(raw))
+    with pytest.raises(L.LedgerError, match="SHA-256"):
+        L.RolloutLedgerReader(led, ident).read_step(0)
+    assert L.bits_f32(L.f32_bits(-0.0)) == 0.0 and L.f32_bits(-0.0) != L.f32_bits(0.0)
+    assert L.bits_f64(L.f64_bits(1e-300)) == 1e-300
