@@ -3,18 +3,29 @@
 Reference ``crates/ferrl/src/rollout_ledger.rs`` (format v6 ``:19``): a window's
 collection - prompt tokens, sampled tokens, completion lengths, behaviour
 log-probs, rewards, advantages, loss masks, the controls it was collected under
-(group size, width, reward scope, EOS, lr/beta of that step) and the sampler
-state to hand to the next collector - is written as one step record under an
-identity (trainer-config / policy / adapter / optimizer / sampler digests,
-source step).  A reader refuses a ledger whose identity or controls differ
-from the learner's expectations (``:1427-1890``).  Floats are stored as bit
-patterns so a replay is bit-exact.
+(group size, width, reward scope, EOS, TIS cap, lr/beta of that step) and the
+sampler state to hand to the next collector - is one published artifact under an
+identity (trainer-config / policy / tensor-schema / adapter / optimizer / sampler
+/ lineage digests, source step).  A reader refuses a window whose identity or
+controls differ from the learner's expectations (``:1427-1890``).  Floats are
+stored as bit patterns so a replay is bit-exact.
 
-Layout: ``<dir>/manifest.json`` (format, identity, list of step files with
-their SHA-256) and ``<dir>/step-<N>-rank<R>.json``.  Files are written to a
-temp name, fsynced and renamed; the manifest is rewritten last.  Under data
-parallelism every rank writes its own shard file and rank 0 commits the
-manifest after all ranks report success.
+Layout (file names as in the reference, ``:21-24``, ``:1903``, ``:1985``)::
+
+    <root>/step-<step:020>/window.json                 one-rank payload
+    <root>/step-<step:020>/rank-<rank:05>.window.json  one payload per rank (distributed)
+    <root>/step-<step:020>/.ferrl-ledger-owner         who staged a distributed window
+    <root>/step-<step:020>/manifest.json               commit marker, linked last
+
+A window is staged in a hidden sibling directory (``.tmp-step-...``): payloads
+are created exclusively and fsynced, the manifest (identity, payload names,
+lengths and SHA-256; for a distributed window also world size, controls and the
+window totals) is written last.  Publication claims the final directory with
+``mkdir`` - an existing window is never replaced - hard-links the payloads and
+then the manifest, and syncs the directories.  A reader treats a directory
+without ``manifest.json`` as absent.  Under data parallelism rank 0 creates the
+stage, every rank writes its shard into it, and rank 0 commits once all ranks
+report success or removes the stage when any rank failed (``:676-1110``).
 """
 from __future__ import annotations
 
@@ -31,6 +42,18 @@ from .policy import Rollout
 
 LEDGER_FORMAT = 6
 MANIFEST = "manifest.json"
+PAYLOAD = "window.json"
+OWNER_FILE = ".ferrl-ledger-owner"
+DISTRIBUTED_KIND = "distributed_rollout_ledger"
+_ZERO_DIGEST = "0" * 64
+
+
+def step_dir_name(step: int) -> str:
+    return f"step-{step:020d}"
+
+
+def shard_payload_name(rank: int) -> str:
+    return f"rank-{rank:05d}.window.json"
 
 
 class LedgerError(RuntimeError):
@@ -62,6 +85,16 @@ class LedgerIdentity:
     sampler_sha256: str
     source_step: int
     optimizer_step: int
+    tensor_schema_sha256: str = _ZERO_DIGEST
+    lineage_sha256: str = _ZERO_DIGEST
+
+    def validate(self) -> None:
+        for k, v in asdict(self).items():
+            if k.endswith("_sha256"):
+                if not (isinstance(v, str) and len(v) == 64 and all(c in "0123456789abcdef" for c in v)):
+                    raise LedgerError(f"ledger identity field {k} is not a lowercase SHA-256 hex digest")
+        if self.source_step < 0 or self.optimizer_step < 0:
+            raise LedgerError("ledger identity steps must be non-negative")
 
 
 @dataclass
@@ -76,6 +109,7 @@ class LedgerControls:
     truncation_masking: bool
     effective_lr_bits: int
     effective_beta_bits: int
+    tis_imp_ratio_cap_bits: Optional[int] = None
 
 
 @dataclass
@@ -166,88 +200,282 @@ class LedgerStep:
                             raise LedgerError("behaviour log-probs must be finite and non-positive")
 
 
-def _write_json_atomic(path: str, obj) -> str:
-    tmp = path + ".tmp"
-    data = json.dumps(obj, sort_keys=True).encode()
-    with open(tmp, "wb") as f:
-        f.write(data)
-        f.flush()
-        os.fsync(f.fileno())
-    os.rename(tmp, path)
-    return hashlib.sha256(data).hexdigest()
+
+
+# ------------------------------------------------------------------ durable file helpers
+def _write_new_synced(path: str, data: bytes) -> None:
+    """Create ``path`` exclusively (never overwrite), write and fsync."""
+    fd = os.open(path, os.O_WRONLY | os.O_CREAT | os.O_EXCL, 0o644)
+    try:
+        with os.fdopen(fd, "wb") as f:
+            f.write(data)
+            f.flush()
+            os.fsync(f.fileno())
+    except BaseException:
+        try:
+            os.unlink(path)
+        except OSError:
+            pass
+        raise
+
+
+def _sync_dir(path: str) -> None:
+    fd = os.open(path or ".", os.O_RDONLY)
+    try:
+        os.fsync(fd)
+    finally:
+        os.close(fd)
+
+
+def _remove_tree(path: str) -> None:
+    """Remove a staging directory created by this module (flat: files only)."""
+    try:
+        for name in os.listdir(path):
+            os.unlink(os.path.join(path, name))
+        os.rmdir(path)
+    except FileNotFoundError:
+        pass
+
+
+def _payload_bytes(st: "LedgerStep") -> bytes:
+    return json.dumps(st.to_json(), sort_keys=True).encode()
+
+
+def _entry(name: str, data: bytes, rank: Optional[int] = None) -> dict:
+    e = {"payload_file": name, "payload_len": len(data), "payload_sha256": hashlib.sha256(data).hexdigest()}
+    if rank is not None:
+        e = {"rank": rank, **e}
+    return e
+
+
+@dataclass
+class DistributedStage:
+    """A hidden staging directory of one distributed window (created by rank 0)."""
+    path: str
+    final_dir: str
+    owner: bytes
+    step: int
+    world_size: int
 
 
 class RolloutLedgerWriter:
-    def __init__(self, directory: str, identity: LedgerIdentity, *, rank: int = 0, world_size: int = 1):
+    """Writer bound to one learner pre-state identity (one window: ``identity.source_step``)."""
+
+    def __init__(self, directory: str, identity: LedgerIdentity, *, rank: int = 0, world_size: int = 1,
+                 fault_hook=None):
+        identity.validate()
         self.dir, self.identity, self.rank, self.world = directory, identity, rank, world_size
+        self.fault_hook = fault_hook            # tests: called with a stage name before each publication stage
         os.makedirs(directory, exist_ok=True)
-        self.entries: list = []
-        mp = os.path.join(directory, MANIFEST)
-        if os.path.exists(mp):
-            man = json.load(open(mp))
-            if man.get("identity") != asdict(identity):
-                raise LedgerError("an existing ledger in this directory belongs to a different identity")
-            self.entries = man.get("steps", [])
+
+    # -- paths
+    def step_dir(self, step: int) -> str:
+        return os.path.join(self.dir, step_dir_name(step))
 
     def step_path(self, step: int, rank: int) -> str:
-        return os.path.join(self.dir, f"step-{step:08d}-rank{rank}.json")
+        name = PAYLOAD if self.world == 1 else shard_payload_name(rank)
+        return os.path.join(self.step_dir(step), name)
 
-    def stage_step(self, st: LedgerStep) -> dict:
-        """Write this rank's shard file; returns its manifest entry."""
+    def stage_path(self, step: int, nonce: int) -> str:
+        kind = "distributed" if self.world > 1 else "local"
+        return os.path.join(self.dir, f".tmp-{step_dir_name(step)}-{kind}-{nonce & (2 ** 64 - 1):016x}")
+
+    def _fault(self, where: str) -> None:
+        if self.fault_hook is not None:
+            self.fault_hook(where)
+
+    def _check_step(self, st: LedgerStep) -> None:
         st.validate()
-        if st.rank != self.rank or st.world_size != self.world:
-            raise LedgerError("ledger step rank/world does not match the writer")
-        p = self.step_path(st.step, st.rank)
-        if os.path.exists(p):
-            raise LedgerError(f"{p} already exists; ledger steps are never replaced")
-        sha = _write_json_atomic(p, st.to_json())
-        return {"step": st.step, "rank": st.rank, "file": os.path.basename(p), "sha256": sha}
+        if st.step != self.identity.source_step:
+            raise LedgerError(f"payload step {st.step} does not match identity source_step {self.identity.source_step}")
+        if os.path.exists(os.path.join(self.step_dir(st.step), MANIFEST)):
+            raise LedgerError(f"{self.step_dir(st.step)} already exists; ledger windows are never replaced")
 
-    def commit(self, entries: Sequence[dict]) -> None:
-        """Rank 0: publish the manifest covering ``entries`` (all ranks' shards of one step)."""
-        self.entries = list(self.entries) + list(entries)
-        _write_json_atomic(os.path.join(self.dir, MANIFEST),
-                           {"format": LEDGER_FORMAT, "identity": asdict(self.identity), "world_size": self.world,
-                            "steps": self.entries})
+    def _publish(self, stage: str, final_dir: str, names: Sequence[str]) -> None:
+        """Claim ``final_dir``, link payloads, link the manifest last, sync."""
+        try:
+            os.mkdir(final_dir)                                   # atomic claim
+        except FileExistsError:
+            if os.path.exists(os.path.join(final_dir, MANIFEST)):
+                raise LedgerError(f"{final_dir} already exists; ledger windows are never replaced") from None
+            raise LedgerError(f"{final_dir} exists without a manifest (an interrupted or concurrent publication); "
+                              "it is not reader-visible and must be removed before this window can be written") from None
+        try:
+            for name in names:
+                os.link(os.path.join(stage, name), os.path.join(final_dir, name))
+            self._fault("before_manifest_link")
+            _sync_dir(final_dir)
+            os.link(os.path.join(stage, MANIFEST), os.path.join(final_dir, MANIFEST))
+        except BaseException:
+            _remove_tree(final_dir)                               # nothing reader-visible was committed
+            raise
+        _sync_dir(final_dir)
+        _sync_dir(self.dir)
+        _remove_tree(stage)
+        _sync_dir(self.dir)
 
-    def write_step(self, st: LedgerStep) -> None:
-        """World-1 convenience: stage and commit."""
-        self.commit([self.stage_step(st)])
+    # -- one rank
+    def write_step(self, st: LedgerStep) -> str:
+        """Stage and publish a complete one-rank window; returns the window directory."""
+        if self.world != 1 or st.world_size != 1 or st.rank != 0:
+            raise LedgerError("write_step publishes one-rank windows; use the distributed stage for more ranks")
+        self._check_step(st)
+        stage = self.stage_path(st.step, int.from_bytes(os.urandom(8), "little"))
+        os.mkdir(stage)
+        try:
+            data = _payload_bytes(st)
+            _write_new_synced(os.path.join(stage, PAYLOAD), data)
+            man = {"format_version": LEDGER_FORMAT, "identity": asdict(self.identity), **_entry(PAYLOAD, data)}
+            _write_new_synced(os.path.join(stage, MANIFEST), json.dumps(man, sort_keys=True).encode())
+            _sync_dir(stage)
+            self._publish(stage, self.step_dir(st.step), [PAYLOAD])
+        except BaseException:
+            _remove_tree(stage)
+            raise
+        return self.step_dir(st.step)
+
+    # -- several ranks
+    def create_distributed_stage(self, step: int, nonce: int) -> DistributedStage:
+        """Rank 0: make the hidden stage all ranks write their shard into."""
+        if self.world <= 1:
+            raise LedgerError("distributed ledger staging requires world_size > 1")
+        if step != self.identity.source_step:
+            raise LedgerError(f"distributed stage step {step} does not match identity source_step "
+                              f"{self.identity.source_step}")
+        if os.path.exists(os.path.join(self.step_dir(step), MANIFEST)):
+            raise LedgerError(f"{self.step_dir(step)} already exists; ledger windows are never replaced")
+        path = self.stage_path(step, nonce)
+        os.mkdir(path)
+        owner = f"{os.getpid()}:{nonce & (2 ** 64 - 1):016x}".encode()
+        _write_new_synced(os.path.join(path, OWNER_FILE), owner)
+        _sync_dir(path)
+        _sync_dir(self.dir)
+        return DistributedStage(path, self.step_dir(step), owner, step, self.world)
+
+    def open_distributed_stage(self, step: int, nonce: int) -> DistributedStage:
+        """Other ranks: the stage rank 0 created under the agreed nonce."""
+        path = self.stage_path(step, nonce)
+        try:
+            owner = open(os.path.join(path, OWNER_FILE), "rb").read()
+        except OSError as e:
+            raise LedgerError(f"distributed stage {path} is not visible on this rank: {e}") from e
+        return DistributedStage(path, self.step_dir(step), owner, step, self.world)
+
+    def write_distributed_shard(self, stage: DistributedStage, st: LedgerStep) -> dict:
+        """Write and sync this rank's immutable payload into ``stage``; returns its manifest entry."""
+        st.validate()
+        if st.world_size != self.world or st.rank != self.rank or not 0 <= st.rank < st.world_size:
+            raise LedgerError(f"distributed shard has invalid rank {st.rank}/world {st.world_size} for this writer")
+        if st.step != stage.step:
+            raise LedgerError(f"payload step {st.step} does not match the stage's step {stage.step}")
+        data = _payload_bytes(st)
+        self._fault("before_shard_write")
+        _write_new_synced(os.path.join(stage.path, shard_payload_name(st.rank)), data)
+        return _entry(shard_payload_name(st.rank), data, rank=st.rank)
+
+    def abort_distributed_stage(self, stage: DistributedStage) -> None:
+        """Rank 0, after every rank reported that it stopped writing: drop the uncommitted stage."""
+        try:
+            owner = open(os.path.join(stage.path, OWNER_FILE), "rb").read()
+        except FileNotFoundError:
+            return
+        if owner != stage.owner:
+            raise LedgerError(f"stage {stage.path} changed owner; refusing to remove it")
+        _remove_tree(stage.path)
+        _sync_dir(self.dir)
+
+    def commit_distributed_stage(self, stage: DistributedStage) -> str:
+        """Rank 0: validate the shards against one another, write the manifest and publish."""
+        shards, steps = [], []
+        for r in range(stage.world_size):
+            p = os.path.join(stage.path, shard_payload_name(r))
+            try:
+                data = open(p, "rb").read()
+            except OSError as e:
+                raise LedgerError(f"distributed stage is missing the shard of rank {r}: {e}") from e
+            st = LedgerStep.from_json(json.loads(data))
+            st.validate()
+            if st.rank != r or st.world_size != stage.world_size or st.step != stage.step:
+                raise LedgerError(f"shard {p} declares rank {st.rank}/world {st.world_size}/step {st.step}")
+            shards.append(_entry(shard_payload_name(r), data, rank=r))
+            steps.append(st)
+        first = asdict(steps[0].controls)
+        for st in steps[1:]:
+            if asdict(st.controls) != first:
+                raise LedgerError(f"rank {st.rank} collected under different controls than rank 0")
+        seen: set = set()
+        for st in steps:
+            for g in st.groups:
+                key = (g.accum_index, g.rollout_global_row_base)
+                if key in seen:
+                    raise LedgerError(f"two shards claim rollout rows starting at {g.rollout_global_row_base}")
+                seen.add(key)
+        man = {"format_version": LEDGER_FORMAT, "kind": DISTRIBUTED_KIND, "identity": asdict(self.identity),
+               "step": stage.step, "world_size": stage.world_size, "controls": first,
+               "window_tokens": sum(st.window_tokens for st in steps),
+               "live_items": sum(st.live_items for st in steps), "shards": shards}
+        _write_new_synced(os.path.join(stage.path, MANIFEST), json.dumps(man, sort_keys=True).encode())
+        _sync_dir(stage.path)
+        self._publish(stage.path, stage.final_dir, [OWNER_FILE] + [s["payload_file"] for s in shards])
+        return stage.final_dir
 
 
 class RolloutLedgerReader:
     def __init__(self, directory: str, expected: Optional[LedgerIdentity] = None, controls: Optional[LedgerControls] = None):
         self.dir = directory
-        mp = os.path.join(directory, MANIFEST)
-        try:
-            man = json.load(open(mp))
-        except (OSError, json.JSONDecodeError) as e:
-            raise LedgerError(f"cannot read ledger manifest {mp}: {e}") from e
-        if man.get("format") != LEDGER_FORMAT:
-            raise LedgerError(f"unsupported ledger format {man.get('format')}")
-        self.identity = LedgerIdentity(**man["identity"])
-        if expected is not None and asdict(expected) != asdict(self.identity):
-            diff = [k for k, v in asdict(expected).items() if asdict(self.identity).get(k) != v]
-            raise LedgerError(f"ledger identity differs from the learner's expectation in {diff}")
-        self.world = int(man.get("world_size", 1))
-        self.entries = man["steps"]
+        if not os.path.isdir(directory):
+            raise LedgerError(f"ledger root {directory} does not exist")
+        self.expected = expected
         self.expected_controls = controls
 
     def steps(self) -> list:
-        return sorted({e["step"] for e in self.entries})
+        """Published windows (directories that carry their commit marker)."""
+        out = []
+        for name in os.listdir(self.dir):
+            if name.startswith("step-") and os.path.isfile(os.path.join(self.dir, name, MANIFEST)):
+                try:
+                    out.append(int(name[5:]))
+                except ValueError:
+                    continue
+        return sorted(out)
 
-    def read_step(self, step: int, rank: int = 0) -> LedgerStep:
-        ent = next((e for e in self.entries if e["step"] == step and e["rank"] == rank), None)
-        if ent is None:
-            raise LedgerError(f"ledger has no shard for step {step} rank {rank}")
-        p = os.path.join(self.dir, ent["file"])
+    def _manifest(self, step: int) -> tuple:
+        d = os.path.join(self.dir, step_dir_name(step))
+        mp = os.path.join(d, MANIFEST)
+        try:
+            man = json.load(open(mp))
+        except FileNotFoundError:
+            raise LedgerError(f"ledger has no published window for step {step}") from None
+        except (OSError, json.JSONDecodeError) as e:
+            raise LedgerError(f"cannot read ledger manifest {mp}: {e}") from e
+        if man.get("format_version") != LEDGER_FORMAT:
+            raise LedgerError(f"unsupported ledger format {man.get('format_version')}")
+        try:
+            ident = LedgerIdentity(**man["identity"])
+        except (KeyError, TypeError) as e:
+            raise LedgerError(f"malformed ledger identity in {mp}: {e}") from e
+        if self.expected is not None and asdict(self.expected) != asdict(ident):
+            diff = [k for k, v in asdict(self.expected).items() if asdict(ident).get(k) != v]
+            raise LedgerError(f"ledger identity differs from the learner's expectation in {diff}")
+        if ident.source_step != step:
+            raise LedgerError(f"window in {d} was collected for step {ident.source_step}")
+        return d, man, ident
+
+    def identity(self, step: int) -> LedgerIdentity:
+        return self._manifest(step)[2]
+
+    def _payload(self, d: str, ent: dict) -> "LedgerStep":
+        p = os.path.join(d, ent["payload_file"])
         try:
             data = open(p, "rb").read()
         except OSError as e:
             raise LedgerError(f"cannot read {p}: {e}") from e
-        if hashlib.sha256(data).hexdigest() != ent["sha256"]:
-            raise LedgerError(f"{p} does not match its recorded SHA-256")
-        st = LedgerStep.from_json(json.loads(data))
+        if len(data) != ent["payload_len"] or hashlib.sha256(data).hexdigest() != ent["payload_sha256"]:
+            raise LedgerError(f"{p} does not match its recorded length and SHA-256")
+        try:
+            st = LedgerStep.from_json(json.loads(data))
+        except json.JSONDecodeError as e:
+            raise LedgerError(f"{p} is not valid JSON: {e}") from e
         st.validate()
         if self.expected_controls is not None:
             want, got = asdict(self.expected_controls), asdict(st.controls)
@@ -255,3 +483,41 @@ class RolloutLedgerReader:
             if bad:
                 raise LedgerError(f"ledger controls differ from the learner's in {bad}")
         return st
+
+    def world_size(self, step: int) -> int:
+        man = self._manifest(step)[1]
+        return int(man["world_size"]) if man.get("kind") == DISTRIBUTED_KIND else 1
+
+    def read_step(self, step: int, rank: int = 0) -> LedgerStep:
+        """The window of ``step`` (one-rank ledger) or ``rank``'s shard of it (distributed ledger)."""
+        d, man, _ = self._manifest(step)
+        if man.get("kind") == DISTRIBUTED_KIND:
+            ent = next((e for e in man["shards"] if e["rank"] == rank), None)
+            if ent is None:
+                raise LedgerError(f"ledger has no shard for step {step} rank {rank}")
+            st = self._payload(d, ent)
+            if st.rank != rank or st.world_size != man["world_size"] or st.step != step:
+                raise LedgerError(f"shard of rank {rank} declares rank {st.rank}/world {st.world_size}/step {st.step}")
+            if asdict(st.controls) != man["controls"]:
+                raise LedgerError(f"shard of rank {rank} disagrees with the manifest's controls")
+            return st
+        if rank != 0:
+            raise LedgerError(f"ledger has no shard for step {step} rank {rank}")
+        st = self._payload(d, man)
+        if st.step != step or st.world_size != 1:
+            raise LedgerError(f"window in {d} declares step {st.step}/world {st.world_size}")
+        return st
+
+    def read_distributed_step(self, step: int) -> list:
+        """Every rank's shard of a distributed window, in rank order, with the totals checked."""
+        d, man, _ = self._manifest(step)
+        if man.get("kind") != DISTRIBUTED_KIND:
+            raise LedgerError(f"window of step {step} is not a distributed ledger")
+        ranks = sorted(e["rank"] for e in man["shards"])
+        if ranks != list(range(int(man["world_size"]))):
+            raise LedgerError(f"distributed manifest lists ranks {ranks} for world {man['world_size']}")
+        shards = [self.read_step(step, r) for r in ranks]
+        if sum(s.window_tokens for s in shards) != man["window_tokens"] or \
+                sum(s.live_items for s in shards) != man["live_items"]:
+            raise LedgerError("distributed manifest totals do not match its shards")
+        return shards

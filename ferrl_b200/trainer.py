@@ -713,24 +713,39 @@ class Trainer:
         """Collector side: roll out and score window ``step`` and persist it; no update.
         Under data parallelism every rank stages its shard and rank 0 commits the manifest
         once all shards exist (reference trainer.rs:2211-2679, rollout_ledger.rs:676-1110)."""
-        import json as _json
         from . import ledger as L
         c = self.config
         collected = self.collect_window(step)
+        cap = L.f64_bits(c.tis_imp_ratio_cap) if c.tis else None
         ctl = L.LedgerControls(c.grad_accum_steps, c.prompts_per_item, c.group_size, c.max_new_tokens,
                                c.reward_group_scope, c.scale_rewards, c.eos_token_id, c.truncation_masking,
-                               L.f64_bits(c.lr_at(step)), L.f64_bits(c.beta_at(step)))
+                               L.f64_bits(c.lr_at(step)), L.f64_bits(c.beta_at(step)), cap)
         groups = [L.LedgerGroup.from_collected(j, g) for j, gs in collected for g in gs]
         tokens = sum(g.completion_tokens for _, gs in collected for g in gs)
         st = L.LedgerStep(step, self.comm.rank, self.comm.world_size, ctl, tokens,
                           sum(1 for _, gs in collected for g in gs if g.live), list(self.policy.sampler_state()), groups)
-        entry = self.comm.coordinate(lambda: writer.stage_step(st), "ledger shard write") \
-            if self.comm.world_size > 1 else writer.stage_step(st)
-        entries = [_json.loads(b.decode()) for b in self.comm.all_gather_bytes(_json.dumps(entry).encode())]
-        if self.is_writer:
-            writer.commit(entries)
-        if self.comm.world_size > 1:
-            self.comm.barrier()
+        if self.comm.world_size == 1:
+            writer.write_step(st)
+            return st
+        # rank 0 draws the stage nonce and creates the hidden stage; every rank writes its shard
+        # into it; the outcome of each phase is agreed before anyone moves on, and the stage is
+        # removed only after all ranks have stopped writing.
+        import os as _os
+        nonce = int.from_bytes(self.comm.broadcast_bytes(_os.urandom(8) if self.is_writer else None), "little")
+        stage = self.comm.coordinate(lambda: writer.create_distributed_stage(step, nonce) if self.is_writer else None,
+                                     "ledger stage creation")
+        try:
+            if not self.is_writer:
+                stage = self.comm.coordinate(lambda: writer.open_distributed_stage(step, nonce), "ledger stage open")
+            else:
+                self.comm.coordinate(lambda: None, "ledger stage open")
+            self.comm.coordinate(lambda: writer.write_distributed_shard(stage, st), "ledger shard write")
+            self.comm.coordinate(lambda: writer.commit_distributed_stage(stage) if self.is_writer else None,
+                                 "ledger commit")
+        except PeerFailure:
+            if self.is_writer and stage is not None:
+                writer.abort_distributed_stage(stage)
+            raise
         return st
 
     def train_from_ledger(self, record) -> Metrics:
@@ -741,6 +756,8 @@ class Trainer:
             raise TrainerError("ledger step was collected under different group_size / max_new_tokens")
         if record.world_size != self.comm.world_size or record.rank != self.comm.rank:
             raise TrainerError("ledger shard belongs to a different rank/world")
+        if record.controls.tis_imp_ratio_cap_bits != (L.f64_bits(c.tis_imp_ratio_cap) if c.tis else None):
+            raise TrainerError("ledger step was collected under a different truncated-importance-sampling cap")
         by_item: dict = {}
         for g in record.groups:
             r = g.rollout()

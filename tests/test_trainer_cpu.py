@@ -217,7 +217,8 @@ def test_ledger_collect_then_learn_equals_direct(tmp_path):
     for p, q in zip(direct.params, learner.params):
         assert torch.equal(p.detach(), q.detach())
     with pytest.raises(L.LedgerError):
-        L.RolloutLedgerReader(str(tmp_path / "ledger"), L.LedgerIdentity("f" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0))
+        L.RolloutLedgerReader(str(tmp_path / "ledger"),
+                              L.LedgerIdentity("f" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)).read_step(0)
 
 
 _GLOO_DP_WORKER = r"""
@@ -292,8 +293,15 @@ def test_ledger_two_ranks_stage_shards_rank0_commits_and_learners_match_direct(t
     shards = run_ranks(2, collect)
     assert [s[0] for s in shards] == [0, 1]
     assert set(shards[0][1]).isdisjoint(shards[1][1])               # ranks drew different prompts
-    man = json.load(open(os.path.join(led, "manifest.json")))
-    assert man["world_size"] == 2 and sorted((e["step"], e["rank"]) for e in man["steps"]) == [(0, 0), (0, 1)]
+    win = os.path.join(led, L.step_dir_name(0))
+    assert sorted(os.listdir(led)) == [L.step_dir_name(0)]           # the hidden stage is gone
+    assert sorted(os.listdir(win)) == [".ferrl-ledger-owner", "manifest.json", "rank-00000.window.json",
+                                       "rank-00001.window.json"]
+    man = json.load(open(os.path.join(win, "manifest.json")))
+    assert man["kind"] == "distributed_rollout_ledger" and man["world_size"] == 2
+    assert [e["rank"] for e in man["shards"]] == [0, 1]
+    both = L.RolloutLedgerReader(led, ident).read_distributed_step(0)
+    assert sum(s.window_tokens for s in both) == man["window_tokens"]
     got = run_ranks(2, learn)
     for r in range(2):
         for p, q in zip(want[r], got[r]):
@@ -306,18 +314,24 @@ def test_ledger_two_ranks_stage_shards_rank0_commits_and_learners_match_direct(t
 
 
 def test_ledger_rejects_tampering_replacement_and_malformed_steps(tmp_path):
+    import dataclasses
     from ferrl_b200 import ledger as L
     ident = L.LedgerIdentity("a" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)
     led = str(tmp_path / "ledger")
     tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
     w = L.RolloutLedgerWriter(led, ident)
     st = tr.collect_to_ledger(0, w)
+    assert sorted(os.listdir(os.path.join(led, L.step_dir_name(0)))) == ["manifest.json", "window.json"]
+    assert L.RolloutLedgerReader(led, ident).steps() == [0]
     with pytest.raises(L.LedgerError, match="never replaced"):
-        w.stage_step(st)
-    with pytest.raises(L.LedgerError, match="no shard"):
+        w.write_step(st)
+    with pytest.raises(L.LedgerError, match="no published window"):
         L.RolloutLedgerReader(led, ident).read_step(3)
+    with pytest.raises(L.LedgerError, match="source_step"):
+        L.RolloutLedgerWriter(str(tmp_path / "other"), dataclasses.replace(ident, source_step=5)).write_step(st)
+    with pytest.raises(L.LedgerError, match="lowercase SHA-256"):
+        L.RolloutLedgerWriter(str(tmp_path / "other"), dataclasses.replace(ident, policy_sha256="XYZ"))
     # controls of the learner must agree with the collector's (schedules excepted)
-    import dataclasses
     other = dataclasses.replace(st.controls, group_size=st.controls.group_size + 1)
     with pytest.raises(L.LedgerError, match="group_size"):
         L.RolloutLedgerReader(led, ident, controls=other).read_step(0)
@@ -336,6 +350,7 @@ def test_ledger_rejects_tampering_replacement_and_malformed_steps(tmp_path):
         L.LedgerStep.from_json({"step": 0})
     # a flipped byte in the shard file is caught by its recorded digest
     p = w.step_path(0, 0)
+    assert p.endswith(os.path.join(L.step_dir_name(0), "window.json"))
     raw = bytearray(open(p, "rb").read())
     raw[len(raw) // 2] ^= 1
     open(p, "wb").write(bytes(raw))
@@ -343,3 +358,44 @@ def test_ledger_rejects_tampering_replacement_and_malformed_steps(tmp_path):
         L.RolloutLedgerReader(led, ident).read_step(0)
     assert L.bits_f32(L.f32_bits(-0.0)) == 0.0 and L.f32_bits(-0.0) != L.f32_bits(0.0)
     assert L.bits_f64(L.f64_bits(1e-300)) == 1e-300
+
+
+def test_ledger_interrupted_publication_is_invisible_and_failed_shard_aborts_every_rank(tmp_path):
+    from ferrl_b200 import ledger as L
+    ident = L.LedgerIdentity("a" * 64, "b" * 64, "c" * 64, "d" * 64, "e" * 64, 0, 0)
+    led = str(tmp_path / "one")
+
+    def die(where):
+        if where == "before_manifest_link":
+            raise OSError("disk went away")
+    tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    with pytest.raises(OSError, match="disk went away"):
+        tr.collect_to_ledger(0, L.RolloutLedgerWriter(led, ident, fault_hook=die))
+    assert os.listdir(led) == []                                     # no stage, no claimed directory
+    assert L.RolloutLedgerReader(led, ident).steps() == []
+    # a directory without its commit marker is not a window
+    os.mkdir(os.path.join(led, L.step_dir_name(0)))
+    open(os.path.join(led, L.step_dir_name(0), "window.json"), "w").write("{}")
+    assert L.RolloutLedgerReader(led, ident).steps() == []
+    with pytest.raises(L.LedgerError, match="no published window"):
+        L.RolloutLedgerReader(led, ident).read_step(0)
+    tr2 = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    with pytest.raises(L.LedgerError, match="without a manifest"):
+        tr2.collect_to_ledger(0, L.RolloutLedgerWriter(led, ident))
+
+    # two ranks: rank 1 cannot write its shard -> both ranks raise, nothing is published, the stage is removed
+    led2 = str(tmp_path / "two")
+
+    def body(comm):
+        def hook(where):
+            if where == "before_shard_write" and comm.rank == 1:
+                raise OSError("quota exceeded")
+        t = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1, prompts_per_item=1), comm=comm)
+        w = L.RolloutLedgerWriter(led2, ident, rank=comm.rank, world_size=comm.world_size, fault_hook=hook)
+        try:
+            t.collect_to_ledger(0, w)
+        except PeerFailure as e:
+            return "local" if e.local is not None else "peer"
+        return "published"
+    assert run_ranks(2, body) == ["peer", "local"]
+    assert os.listdir(led2) == []
