@@ -206,9 +206,10 @@ class TrainOutcome:
 
 
 def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_dirty: bool = False,
-                        tokenizer=None, model_and_identity=None) -> TrainOutcome:
+                        tokenizer=None, model_and_identity=None, preemption_flag=None) -> TrainOutcome:
     """The whole ``train`` verb. ``tokenizer`` / ``model_and_identity`` may be injected (tests,
-    synthetic runs); otherwise they are loaded from ``cfg.model_dir``."""
+    synthetic runs); otherwise they are loaded from ``cfg.model_dir``.  ``preemption_flag`` is a
+    ``threading.Event`` the caller sets to stop cooperatively after the step in flight."""
     comm = comm or SoloComm()
     T.init_tracing()
     ident = source_identity()
@@ -277,6 +278,8 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
         fused = FusedDpStep.create(comm, policy.trainable_params(), torch.device(device))
     trainer = Trainer(policy, tokenizer, reward_fn, train_samples, cfg.trainer, comm=comm, topology=topology,
                       run_dir=run_dir, binding=binding, candidate_writer=cand_writer, fused_dp_step=fused)
+    if preemption_flag is not None:
+        trainer.with_preemption_flag(preemption_flag)
     with T.run_span(comm.rank, comm.world_size):
         start = trainer.resume_latest()
         stop = trainer.train(start)

@@ -242,3 +242,124 @@ def test_examples_run_end_to_end_on_cpu(tmp_path):
     assert "2 steps" in report
     assert "reward per step" in run("examples/minimal_task.py")
     assert "step 0" in run("examples/countdown_grpo_qwen35.py", "--steps", "1", "--moe")
+
+
+def _discovery_setup(tmp_path, verify, **task_kw):
+    from ferrl_b200.config import TrainerConfig
+    from ferrl_b200 import discovery as D
+    from ferrl_b200.rewards import FnReward, Sample
+    samples = [Sample(f"make {i} from 1 2 3", None) for i in range(6)]
+    tr = TrainerConfig(steps=2, group_size=4, max_new_tokens=5, checkpoint_every=1, eos_token_id=None,
+                       truncation_masking=False)
+    contract = D.MetricContract("digit share", "fraction", D.HIGHER_IS_BETTER, 0.25, 0.05)
+    task = D.DiscoveryTask("digits", samples[:4], FnReward(_digit_fraction), samples[4:], version=2,
+                           metric_contract=contract, verify_candidate=verify, **task_kw)
+    b = (D.DiscoveryConfig.Builder(os.path.join(FIX, "tiny_qwen3")).out_dir(str(tmp_path / "runs")).trainer(tr)
+         .lora(4, 8.0).candidate_top_k(4).artifact_output(str(tmp_path / "bundle")))
+    return D, task, contract, b
+
+
+def test_discovery_verified_outcome_publishes_bundle_manifest_last(tmp_path):
+    import json
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    seen = []
+
+    def verify(cand):
+        seen.append(cand)
+        score = 0.25 + 0.1 * (len(seen) == 2) + 0.2 * (len(seen) == 3)      # third candidate is strongest
+        if len(seen) == 1:
+            return D.CandidateVerification.rejected("does not parse")
+        return D.CandidateVerification.measured(D.FinalEvidence(True, D.MetricReport.of(contract, score),
+                                                                {"program": cand.completion}, {"trials": 3}))
+    D, task, contract, b = _discovery_setup(tmp_path, verify)
+    out = D.Discovery(task, b.build(), tokenizer=SyntheticTokenizer(32, 4, 8)).run()
+    assert out.kind == "verified" and out.artifact is not None and len(seen) >= 3
+    assert all(len(c.provenance_sha256) == 64 for c in seen)
+    assert [c.search_reward for c in seen] == sorted((c.search_reward for c in seen), reverse=True)
+    art = out.artifact
+    assert sorted(os.listdir(art.output)) == sorted(D.ARTIFACT_FILES + (D.ARTIFACT_MANIFEST_FILE,))
+    man = D.verify_artifact_bundle(art.output)
+    assert man["contract"] == "ferrl.discovery-artifact.v1" and man["task"] == {"name": "digits", "version": 2}
+    assert man["candidate_sha256"] == seen[2].provenance_sha256 and abs(art.metric.candidate - 0.45) < 1e-12
+    assert json.load(open(art.payload_path)) == {"program": seen[2].completion}
+    ev = json.load(open(art.verification_evidence_path))
+    assert ev["held_out_correct"] is True and ev["evidence"] == {"trials": 3}
+    assert json.load(open(os.path.join(art.output, "launch.json")))["launch_sha256"] == man["launch_sha256"]
+    assert json.load(open(os.path.join(out.run_dir, "discovery-outcome.json")))["kind"] == "verified"
+    # a tampered file is caught; a second run refuses to overwrite the bundle before loading anything
+    with open(art.payload_path, "a") as f:
+        f.write(" ")
+    with pytest.raises(D.DiscoveryError, match="does not match the manifest"):
+        D.verify_artifact_bundle(art.output)
+    with pytest.raises(D.InvalidConfiguration, match="already exists"):
+        D.Discovery(task, b.build(), tokenizer=SyntheticTokenizer(32, 4, 8)).run()
+
+
+def test_discovery_no_win_reasons_preemption_and_validation(tmp_path):
+    import threading
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    D, task, contract, b = _discovery_setup(tmp_path, None)
+    tok = SyntheticTokenizer(32, 4, 8)
+
+    def outcome(verify, sub):
+        t = D.DiscoveryTask(task.name, task.samples, task.reward_fn, task.eval_samples, 2, contract, verify)
+        cfg = b.out_dir(str(tmp_path / sub)).artifact_output(str(tmp_path / (sub + "-bundle"))).build()
+        return D.Discovery(t, cfg, tokenizer=tok).run(), str(tmp_path / (sub + "-bundle"))
+
+    out, bundle = outcome(lambda c: D.CandidateVerification.rejected(" "), "rej")
+    assert out.kind == "no_win" and out.no_win.reason == D.NO_WIN_CANDIDATES_REJECTED
+    assert out.no_win.detail == "candidate rejected without task detail" and not os.path.exists(bundle)
+    out, _ = outcome(lambda c: D.CandidateVerification.measured(
+        D.FinalEvidence(False, D.MetricReport.of(contract, 0.9), {}, {})), "wrong")
+    assert out.no_win.reason == D.NO_WIN_HELD_OUT_INCORRECT
+    # exactly at the margin is not a win: the improvement must strictly exceed it
+    out, _ = outcome(lambda c: D.CandidateVerification.measured(
+        D.FinalEvidence(True, D.MetricReport.of(contract, 0.25 + 0.05), {}, {})), "margin")
+    assert out.no_win.reason == D.NO_WIN_NO_MATERIAL_METRIC_WIN and out.no_win.candidates_checked >= 1
+    # evidence measured under another contract is an error, and so is a crashing verifier
+    other = D.MetricContract("digit share", "fraction", D.HIGHER_IS_BETTER, 0.0, 0.05)
+    with pytest.raises(D.InvalidFinalEvidence, match="launch-frozen"):
+        outcome(lambda c: D.CandidateVerification.measured(D.FinalEvidence(True, D.MetricReport.of(other, 1.0), {}, {})), "c2")
+    with pytest.raises(D.TaskVerificationError, match="sandbox died"):
+        outcome(lambda c: (_ for _ in ()).throw(RuntimeError("sandbox died")), "crash")
+    # cooperative preemption: stops after the step in flight, checkpoints, verifies nothing
+    flag = threading.Event()
+    flag.set()
+    called = []
+    t = D.DiscoveryTask(task.name, task.samples, task.reward_fn, task.eval_samples, 2, contract,
+                        lambda c: called.append(c))
+    cfg = b.out_dir(str(tmp_path / "pre")).artifact_output(str(tmp_path / "pre-bundle")).preemption_flag(flag).build()
+    out = D.Discovery(t, cfg, tokenizer=tok).run()
+    assert out.kind == "preempted" and out.steps_run == 1 and not called and not os.path.exists(cfg.artifact_output)
+    assert os.path.isdir(os.path.join(out.run_dir, "checkpoints"))
+    # validation before anything is loaded
+    with pytest.raises(D.InvalidConfiguration, match="contain"):
+        b.out_dir(str(tmp_path / "a" / "runs")).artifact_output(str(tmp_path / "a")).build()
+    with pytest.raises(D.InvalidConfiguration, match="task name"):
+        D.TaskIdentity("Has Space")
+    with pytest.raises(D.InvalidFinalEvidence):
+        D.MetricContract(" padded", "s", D.LOWER_IS_BETTER, 1.0, 0.0).validate()
+    with pytest.raises(D.InvalidFinalEvidence):
+        D.MetricContract("t", "s", D.LOWER_IS_BETTER, 1.0, -0.1).validate()
+    low = D.MetricContract("latency", "us", D.LOWER_IS_BETTER, 100.0, 2.0)
+    assert D.MetricReport.of(low, 97.0).is_material_win() and not D.MetricReport.of(low, 98.0).is_material_win()
+    assert D.metric_is_stronger(D.MetricReport.of(low, 90.0), D.MetricReport.of(low, 95.0))
+
+
+def test_discovery_bundle_publication_failure_leaves_nothing(tmp_path):
+    from ferrl_b200 import discovery as D
+    from ferrl_b200.telemetry import CandidateRecord
+    rec = CandidateRecord(1, 0, 1, 3, 2, 0.5, 4, "1 2 3 4")
+    contract = D.MetricContract("m", "u", D.HIGHER_IS_BETTER, 0.0, 0.0)
+    ev = D.FinalEvidence(True, D.MetricReport.of(contract, 1.0), {"x": 1}, {})
+
+    def die(where):
+        raise OSError("no space left")
+    out = str(tmp_path / "bundle")
+    with pytest.raises(OSError):
+        D.publish_verified_artifact(out, D.TaskIdentity("t"), "run", b'{"launch_sha256": "ab"}', b"{}", rec, ev, fault_hook=die)
+    assert os.listdir(tmp_path) == []
+    art = D.publish_verified_artifact(out, D.TaskIdentity("t"), "run", b'{"launch_sha256": "ab"}', b"{}", rec, ev)
+    assert D.verify_artifact_bundle(art.output)["candidate_sha256"] == rec.digest()
+    with pytest.raises(D.InvalidConfiguration, match="already exists"):
+        D.publish_verified_artifact(out, D.TaskIdentity("t"), "run", b"{}", b"{}", rec, ev)
