@@ -44,6 +44,8 @@ def cmd_train(args) -> int:
         cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size = comm.rank, comm.world_size
     out = run_cli_train_setup(cfg, comm, allow_dirty=args.allow_dirty)
     if comm.rank == 0:
+        if out.health.findings:
+            print(out.health.render(), file=sys.stderr, end="")
         print(json.dumps({"run_dir": out.run_dir, "stop": out.stop, "steps": out.steps_run,
                           "health": out.health.verdict,
                           "eval_improvement": None if out.eval_report is None else out.eval_report.improvement(),

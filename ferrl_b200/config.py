@@ -352,6 +352,8 @@ class RunConfig:
             _require(not self.distributed.enabled,
                      "data-parallel and tensor-parallel launches cannot be combined")
         self.trainer.validate()
+        from .run_health import validate_run_health
+        validate_run_health(self.run_health, self.trainer)
 
     def to_json(self, *, for_consensus: bool = False) -> dict:
         t = self.trainer.to_json()

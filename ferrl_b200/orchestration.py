@@ -43,6 +43,7 @@ from .lm_policy import LmPolicy
 from .models.loader import LoaderOpts, load_auto_policy
 from .models.lora import BaseQuantization, DenseLoraTargets, LoraSpec
 from .policy import GenConfig
+from .run_health import HealthFinding, HealthReport, evaluate_run_health  # noqa: F401
 from .rewards import (CountdownConfig, CountdownProblem, CountdownReward, MathProblem, MathReward, Sample, build_prompt,
                       generate_dataset, math_prompt, read_jsonl, train_eval_split, train_eval_split_by_key)
 from .sampler import GrpoSampler
@@ -73,71 +74,6 @@ class LaunchManifest:
 
     def digest(self) -> str:
         return canonical_digest(self.to_json(), b"ferrl-b200/launch-manifest/v1")
-
-
-@dataclass
-class HealthFinding:
-    rule: str
-    action: str     # warn | fail
-    message: str
-
-
-@dataclass
-class HealthReport:
-    verdict: str    # ok | warn | fail
-    findings: list = field(default_factory=list)
-
-
-def evaluate_run_health(rows: Sequence[T.Metrics], rules: dict, candidates: Optional[Sequence] = None) -> HealthReport:
-    """Apply the configured ``run_health`` rules (``reward_collapse``, ``correctness_collapse``
-    ``{window, min, action}``; ``dropped_rows {max, action}``; ``grad_spike {factor, action}``;
-    ``telemetry_dark <action>``; ``source_dominance {max_fraction, action}``)."""
-    out = []
-    summ = T.summarize(rows)
-
-    def act(rule, default="warn"):
-        cfg = rules.get(rule)
-        if cfg is None:
-            return None
-        return cfg if isinstance(cfg, str) else cfg.get("action", default)
-    if not rows:
-        a = act("telemetry_dark") or "fail"
-        out.append(HealthFinding("telemetry_dark", a, "no metrics rows were recorded"))
-    for rule, attr in (("reward_collapse", "reward_mean"), ("correctness_collapse", "reward_mean")):
-        cfg = rules.get(rule)
-        if cfg and len(rows) >= int(cfg["window"]):
-            tail = [getattr(r, attr) for r in rows[-int(cfg["window"]):]]
-            if max(tail) < float(cfg["min"]):
-                out.append(HealthFinding(rule, cfg.get("action", "warn"),
-                                         f"{attr} stayed below {cfg['min']} for the last {cfg['window']} steps"))
-    cfg = rules.get("dropped_rows")
-    if cfg:
-        tot = sum(r.dropped_rows for r in rows)
-        if tot > int(cfg["max"]):
-            out.append(HealthFinding("dropped_rows", cfg.get("action", "warn"), f"{tot} rows dropped (max {cfg['max']})"))
-    cfg = rules.get("grad_spike")
-    if cfg:
-        norms = sorted(r.grad_norm for r in rows if r.grad_norm > 0)
-        if len(norms) >= 3:
-            med = norms[len(norms) // 2]
-            worst = max(norms)
-            if med > 0 and worst > float(cfg["factor"]) * med:
-                out.append(HealthFinding("grad_spike", cfg.get("action", "warn"),
-                                         f"grad_norm {worst:.3f} exceeds {cfg['factor']}x median {med:.3f}"))
-    cfg = rules.get("source_dominance")
-    if cfg and candidates:
-        by = {}
-        for c in candidates:
-            by[c.prompt_index] = by.get(c.prompt_index, 0) + 1
-        frac = max(by.values()) / len(candidates)
-        if frac > float(cfg["max_fraction"]):
-            out.append(HealthFinding("source_dominance", cfg.get("action", "warn"),
-                                     f"one prompt supplies {frac:.0%} of the candidates"))
-    for a in summ.anomalies:
-        if a.kind == "non_finite":
-            out.append(HealthFinding("non_finite", "fail", str(a)))
-    verdict = "fail" if any(f.action == "fail" for f in out) else ("warn" if out else "ok")
-    return HealthReport(verdict, out)
 
 
 def synchronized_run_id(task: str, comm: Comm, suffix_rank: bool = False) -> str:
@@ -286,7 +222,8 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     # ---- health, eval, candidates (rank 0 owns publication)
     rows = trainer.history
     cands = T.read_candidates(run_dir.candidates_path) if comm.rank == 0 else []
-    health = evaluate_run_health(rows, cfg.run_health, cands)
+    health = evaluate_run_health(rows, cfg.run_health, cands, group_size=cfg.trainer.group_size,
+                                 prompt_groups_per_step=cfg.trainer.grad_accum_steps * cfg.trainer.prompts_per_item)
     report = None
     if eval_samples and stop is RunStop.COMPLETED and health.verdict != "fail":
         gen = GenConfig(cfg.trainer.group_size, cfg.trainer.max_new_tokens, cfg.trainer.temperature,

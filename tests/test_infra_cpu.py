@@ -513,3 +513,80 @@ def test_gloo_rank_leaves_between_steps_is_detected(tmp_path):
     assert "LEFT" in outs[1][0]
     assert procs[0].returncode == 0, outs[0][1][-2000:]
     assert "DETECTED" in outs[0][0] and "POISONED" in outs[0][0], outs[0][0] + outs[0][1][-1500:]
+
+
+def test_run_health_policy_rules_coverage_and_validation():
+    from ferrl_b200 import run_health as H
+    from ferrl_b200 import telemetry as T
+    from ferrl_b200.config import ConfigError, TrainerConfig
+
+    def rows(n, **kw):
+        return [T.Metrics(step=i, reward_mean=0.5, grad_norm=1.0, rollout_capture_tokens=8, **kw) for i in range(n)]
+
+    def cand(step, prompt, g, md):
+        return T.CandidateRecord(step, 0, 1, prompt, g, 0.0, 3, "x", reward_metadata=md)
+
+    # trailing-window MEAN, and a window that has not filled yet is reported rather than passed
+    r = rows(4)
+    r[-1].reward_mean = 0.0
+    rule = {"reward_collapse": {"window": 2, "min": 0.3, "action": "warn"}}
+    rep = H.evaluate_run_health(r, rule)
+    assert rep.verdict == "warn" and "0.250000" in rep.findings[0].message
+    assert H.evaluate_run_health(rows(4), rule).verdict == "ok"
+    assert "only 1 metric rows" in H.evaluate_run_health(rows(1), rule).findings[0].message
+    # gradient spike against the median of the positive norms; zero-gradient steps do not drag the median
+    g = rows(6)
+    g[0].grad_norm, g[3].grad_norm = 0.0, 9.0
+    rep = H.evaluate_run_health(g, {"grad_spike": {"factor": 5.0, "action": "fail"}})
+    assert rep.is_fail() and "at step 3 was 9.00x" in rep.findings[0].message and rep.render().startswith("run health policy - FAIL")
+    assert H.evaluate_run_health(g, {"grad_spike": {"factor": 9.0, "action": "fail"}}).verdict == "ok"
+    # dark telemetry: every step captured nothing
+    dark = [T.Metrics(step=i, reward_mean=0.5) for i in range(3)]
+    assert H.evaluate_run_health(dark, {"telemetry_dark": "warn"}).findings[0].rule == "telemetry_dark"
+    assert H.evaluate_run_health(rows(3), {"telemetry_dark": "warn"}).verdict == "ok"
+    # a non-finite metric always fails
+    bad = rows(2)
+    bad[1].loss = float("nan")
+    assert H.evaluate_run_health(bad, {}).findings[0].rule == "non_finite"
+
+    # candidate-based rules: full coverage of (prompt groups per step) x (group size) is required
+    cc = {"correctness_collapse": {"window": 2, "min": 0.5, "action": "fail"}}
+    full = [cand(s, p, g, {"correct": (s == 0), "source_sha256": "aa" if g else "bb"})
+            for s in range(2) for p in (10 + s, 20 + s) for g in range(2)]
+    kw = dict(group_size=2, prompt_groups_per_step=2)
+    assert H.evaluate_run_health(rows(2), cc, full, **kw).verdict == "ok"                      # 4/8 = 0.5, not below
+    worse = [cand(c.step, c.prompt_index, c.group_index, {"correct": False}) if i == 0 else c for i, c in enumerate(full)]
+    assert "3/8 = 0.375" in H.evaluate_run_health(rows(2), cc, worse, **kw).findings[0].message
+    assert "unavailable" in H.evaluate_run_health(rows(2), cc, None, **kw).findings[0].message
+    assert "is empty" in H.evaluate_run_health(rows(2), cc, [], **kw).findings[0].message
+    assert "missing rows for trailing metric steps 1" in \
+        H.evaluate_run_health(rows(2), cc, [c for c in full if c.step == 0], **kw).findings[0].message
+    assert "lacks full group coverage for trailing metric steps 1" in \
+        H.evaluate_run_health(rows(2), cc, full[:-1], **kw).findings[0].message
+    nometa = [cand(c.step, c.prompt_index, c.group_index, None) for c in full]
+    assert "no candidate correctness metadata" in H.evaluate_run_health(rows(2), cc, nometa, **kw).findings[0].message
+    tri = T.CandidateRecord(0, 0, 1, 1, 0, 0.0, 3, "x", reward_metadata={"task": "trimul", "submission_extracted": False})
+    assert H.candidate_correctness(tri) is False and H.candidate_source_bucket(tri) == H.UNKNOWN_SOURCE
+    sd = {"source_dominance": {"max_fraction": 0.5, "action": "warn"}}
+    assert H.evaluate_run_health(rows(2), sd, full, **kw).verdict == "ok"                      # aa and bb split 4/4
+    mono = [cand(c.step, c.prompt_index, c.group_index, {"source_sha256": "aa"}) for c in full]
+    assert "dominant candidate source aa covered 8/8" in H.evaluate_run_health(rows(2), sd, mono, **kw).findings[0].message
+
+    # validation
+    t = TrainerConfig(steps=4, group_size=4, candidate_log_top_k=4)
+    H.validate_run_health({"reward_collapse": {"window": 4, "min": 0.0, "action": "fail"}, "telemetry_dark": "warn", **cc, **sd}, t)
+    for bad_rules, msg in (
+            ({"reward_collapse": {"window": 5, "min": 0.0, "action": "fail"}}, "must be <= trainer.steps"),
+            ({"reward_collapse": {"window": 0, "min": 0.0, "action": "fail"}}, "window must be >= 1"),
+            ({"reward_collapse": {"window": 1, "min": 0.0, "action": "stop"}}, "reserved"),
+            ({"reward_collapse": {"window": 1, "min": 0.0}}, "exactly the fields"),
+            ({"correctness_collapse": {"window": 1, "min": 1.5, "action": "warn"}}, r"in \[0, 1\]"),
+            ({"grad_spike": {"factor": 0.0, "action": "warn"}}, "factor must be finite and > 0"),
+            ({"source_dominance": {"max_fraction": 2.0, "action": "warn"}}, "max_fraction"),
+            ({"dropped_rows": {"max": -1, "action": "warn"}}, "non-negative"),
+            ({"telemetry_dark": "stop"}, "reserved"),
+            ({"surprise": 1}, "unknown field")):
+        with pytest.raises(ConfigError, match=msg):
+            H.validate_run_health(bad_rules, t)
+    with pytest.raises(ConfigError, match="candidate_log_top_k >= trainer.group_size"):
+        H.validate_run_health(sd, TrainerConfig(steps=4, group_size=4, candidate_log_top_k=2))
