@@ -102,10 +102,11 @@ def build_task(cfg: RunConfig):
         train, ev = train_eval_split(samples, d.eval_n, d.seed)
         return train[:d.train_n] if d.train_n else train, ev, MathReward()
     if cfg.task == "trimul":
-        from .rewards.trimul import TrimulCase, TrimulReward, TrimulRewardProfile
+        from .rewards.trimul import TrimulCase, TrimulReward, TrimulRewardProfile, default_eval_dir
         from .sandbox import ApptainerSandbox
         from .verifier_executor import SameUidApptainerSandbox, VerifierExecutorSandbox, VerifierIsolationTier
-        t = cfg.trimul
+        t = dict(cfg.trimul)
+        t.setdefault("eval_dir", default_eval_dir())
         for req in ("prompt_path", "image", "eval_dir"):
             if not t.get(req):
                 raise OrchestrationError(f"trimul.{req} is required for the trimul task")

@@ -10,10 +10,12 @@ the speed term ``baseline_ns / geomean_ns`` ``:1879-1893``; diagnostics strings
 candidate and the case spec travel as sealed in-memory files ``:697-840`` and
 the evaluation runs through a verifier sandbox tier (``verifier_executor``).
 
-The GPUMODE evaluation bundle (reference.py / eval.py / task.yml) is not part
-of this repository; its directory is configuration (``eval_dir``) and is bound
-read-only into the sandbox.  The driver's log protocol is the ``key: value``
-line format parsed by ``parse_eval_log``.
+The evaluation driver ships with the package (``trimul_eval/ferrl_eval.py``,
+counterpart of the reference's ``trimul_eval_driver.py``): its directory is the
+default ``eval_dir`` (``default_eval_dir()``) and is bound read-only into the
+sandbox at ``/eval``; another bundle that speaks the same protocol can be
+configured instead.  The driver's grade log is the ``key: value`` line format
+parsed by ``parse_eval_log``.
 """
 from __future__ import annotations
 
@@ -33,6 +35,14 @@ RUNNABLE_REWARD = 0.05
 PARTIAL_CORRECTNESS_REWARD = 0.75
 CORRECTNESS_REWARD = 1.0
 SPEED_REWARD_CAP = 2.0
+EVAL_DRIVER_FILE = "ferrl_eval.py"
+
+
+def default_eval_dir() -> str:
+    """Directory of the packaged evaluation driver."""
+    return os.path.join(os.path.dirname(os.path.abspath(__file__)), "trimul_eval")
+
+
 MIN_PLAUSIBLE_NS = 1000.0      # a "benchmark" faster than a microsecond is a glitch or a forged grade
 
 
