@@ -159,7 +159,8 @@ def cmd_trimul_baseline(args) -> int:
     from .config import RunConfig
     cfg = RunConfig.load(args.config)
     reward = _trimul_reward(cfg)
-    ref_path = os.path.join(cfg.trimul["eval_dir"], "reference_submission.py")
+    from .rewards.trimul import default_eval_dir
+    ref_path = os.path.join(cfg.trimul.get("eval_dir") or default_eval_dir(), "reference_submission.py")
     ev = reward.verify_submission(open(ref_path, encoding="utf-8").read())
     print(json.dumps({"baseline_ns": ev.geomean_ns, "correct": ev.correct}))
     return 0 if ev.correct and ev.geomean_ns else 1

@@ -61,6 +61,12 @@ def test_correct_submission_passes_and_is_timed_and_cannot_forge_the_grade_log(t
     assert sb.calls[0].binds[0].host == default_eval_dir() and sb.calls[0].command[-1] == "/eval/ferrl_eval.py"
 
 
+def test_packaged_reference_submission_is_correct(tmp_path):
+    src = open(os.path.join(default_eval_dir(), "reference_submission.py")).read()
+    r, ev = grade(tmp_path, src, bench=False)
+    assert r.returncode == 0 and ev.correct and not ev.has_benchmark_section
+
+
 def test_wrong_results_shapes_exceptions_and_import_failures_are_graded(tmp_path):
     wrong = GOOD.replace('@ w["to_out.weight"].t()', '@ w["to_out.weight"].t() * 1.2')
     r, ev = grade(tmp_path, wrong)
