@@ -27,7 +27,7 @@ import shutil
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
-from ..sandbox import Bind, ResourceLimits, RunSpec, Sandbox, SandboxOutcome, Verdict, make_scratch, sealed_memfd
+from ..sandbox import Bind, ProtectedOutput, ResourceLimits, RunSpec, Sandbox, SandboxOutcome, Verdict, make_scratch, sealed_memfd
 from . import RewardError, RewardOutcome
 
 FORMAT_EXTRACTED_REWARD = 0.02
@@ -36,6 +36,7 @@ PARTIAL_CORRECTNESS_REWARD = 0.75
 CORRECTNESS_REWARD = 1.0
 SPEED_REWARD_CAP = 2.0
 EVAL_DRIVER_FILE = "ferrl_eval.py"
+GRADE_SOCKET = "grade.sock"
 
 
 def default_eval_dir() -> str:
@@ -207,7 +208,8 @@ class TrimulReward:
                ("FERRL_BENCH_SPEC", "/sealed/benchmarks.txt"), ("FERRL_SCRATCH", "/scratch")]
         return RunSpec(self.image, list(self.driver), binds=binds, workdir="/scratch", env=env, gpu=self.gpu,
                        limits=ResourceLimits(wall_secs=self.wall_secs), scratch_dir=scratch,
-                       scratch_max_bytes=self.scratch_max)
+                       scratch_max_bytes=self.scratch_max,
+                       protected_output=ProtectedOutput(os.path.join(scratch, GRADE_SOCKET), "/scratch/" + GRADE_SOCKET))
 
     def run_eval(self, submission: str) -> TrimulEval:
         scratch = make_scratch(self.scratch_root)
@@ -224,7 +226,10 @@ class TrimulReward:
                 os.close(fd)
             shutil.rmtree(scratch, ignore_errors=True)
         ok = out.verdict is Verdict.EXITED
-        return parse_eval_log(out.stdout.decode(errors="replace"), ok, out.verdict.value)
+        # the grade is what arrived on the protected socket; standard output is only the fallback of
+        # sandboxes that do not offer the channel (scripted doubles)
+        log = out.protected_output if out.protected_output is not None else out.stdout
+        return parse_eval_log(log.decode(errors="replace"), ok, out.verdict.value)
 
     # --------------------------------------------------------------- reward
     def speed_value(self, geomean_ns: Optional[float]) -> float:

@@ -26,7 +26,9 @@ benchmark case, default 5), ``FERRL_EVAL_CALL_TIMEOUT`` (seconds per request, de
 Output (standard output, ``key: value`` lines): ``test-count``, ``test.<i>.spec``,
 ``test.<i>.status`` (``pass`` | ``fail`` | ``timeout``), ``test.<i>.error``, ``check``
 (``pass`` | ``fail``), ``test-exit``, ``benchmark-count``, ``benchmark.<i>.runs`` / ``.mean`` /
-``.std`` / ``.best`` / ``.worst`` (nanoseconds), ``benchmark-exit``, ``timing-metric``.
+``.std`` / ``.best`` / ``.worst`` (nanoseconds), ``benchmark-exit``, ``timing-metric``.  With
+``FERRL_GRADE_SOCKET`` set, the same lines also go to that Unix socket - the protected channel the
+host reads the grade from - which the parent connects before the payload process exists.
 """
 import json
 import math
@@ -484,9 +486,22 @@ def main(argv=None):
     except OSError:
         pass
     out = os.fdopen(os.dup(1), "w", buffering=1)
+    grade = None
+    path = os.environ.pop("FERRL_GRADE_SOCKET", None)
+    if path:
+        # the protected channel: connected before any candidate code exists in this sandbox; the
+        # host stops listening after this one connection, so the grade cannot come from anyone else
+        grade = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        try:
+            grade.connect(path)
+        except OSError as e:
+            out.write(f"infrastructure-error: cannot reach the grade socket: {one_line(e)}\n")
+            return 2
 
     def log(line):
         out.write(line + "\n")
+        if grade is not None:
+            grade.sendall((line + "\n").encode())
     try:
         tests = parse_spec(open(os.environ["FERRL_TEST_SPEC"]).read())
         bench_path = os.environ.get("FERRL_BENCH_SPEC")

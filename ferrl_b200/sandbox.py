@@ -6,7 +6,9 @@ Reference ``crates/ferrl/src/sandbox.rs``: ``RunSpec`` ``:254-343`` and
 --no-mount home,cwd,hostfs,bind-paths --no-privs --drop-caps all``, ``--nv``
 only on request, ``--net --network none``); a host-side wall-clock supervisor
 that kills the whole process tree ``:1009-1205``; a scratch byte-cap monitor
-``:1216-1484``; 1 MiB capture cap ``:841``; sealed in-memory assets
+``:1216-1484``; 1 MiB capture cap ``:841``; a protected output socket on which
+the in-sandbox verifier returns its grade, so that nothing the candidate prints
+can pass for one ``:598-1007``; sealed in-memory assets
 (``crates/ferrl/src/trimul.rs:697-840``).
 
 The OS-level part - new session, rlimits before exec, wall clock, scratch byte
@@ -23,8 +25,10 @@ import enum
 import fcntl
 import os
 import shutil
+import socket
 import subprocess
 import tempfile
+import threading
 from dataclasses import dataclass, field
 from typing import Callable, Optional, Sequence
 
@@ -61,6 +65,19 @@ class Bind:
 
 
 @dataclass
+class ProtectedOutput:
+    """A Unix socket the host listens on and the in-sandbox verifier connects to once to hand
+    back its result.  ``host_socket`` must lie beneath the host side of exactly one read-write
+    bind and ``sandbox_socket`` at the same relative path beneath that bind's container side."""
+    host_socket: str
+    sandbox_socket: str
+    max_bytes: int = CAPTURE_CAP
+
+
+PROTECTED_OUTPUT_ENV = "FERRL_GRADE_SOCKET"
+
+
+@dataclass
 class RunSpec:
     image: str
     command: list
@@ -73,6 +90,7 @@ class RunSpec:
     scratch_dir: Optional[str] = None
     scratch_max_bytes: Optional[int] = None
     stdin_bytes: Optional[bytes] = None
+    protected_output: Optional[ProtectedOutput] = None
 
 
 class Verdict(str, enum.Enum):
@@ -90,10 +108,111 @@ class SandboxOutcome:
     stdout: bytes
     stderr: bytes
     truncated: bool = False
+    protected_output: Optional[bytes] = None     # what arrived on the protected socket (None: nothing connected)
 
     @property
     def ok(self) -> bool:
         return self.verdict is Verdict.EXITED and self.exit_code == 0
+
+
+def _normal_absolute(path: str) -> bool:
+    return os.path.isabs(path) and all(c not in (".", "..") for c in path.split("/")) and "//" not in path.rstrip("/")
+
+
+def validate_protected_output_mapping(spec: RunSpec) -> Optional[tuple]:
+    """``(bind_index, relative_path)`` of the read-write bind the protected socket travels through."""
+    po = spec.protected_output
+    if po is None:
+        return None
+    for label, p in (("protected output host socket", po.host_socket),
+                     ("protected output sandbox socket", po.sandbox_socket)):
+        if not _normal_absolute(p):
+            raise SandboxError(f"{label} must be an absolute path without '.' or '..': {p}")
+    found = []
+    for i, b in enumerate(spec.binds):
+        if b.read_only or not (_normal_absolute(b.host) and _normal_absolute(b.container)):
+            continue
+        h, c = b.host.rstrip("/") + "/", b.container.rstrip("/") + "/"
+        if (po.host_socket + "/").startswith(h) and (po.sandbox_socket + "/").startswith(c):
+            rh, rc = po.host_socket[len(h):], po.sandbox_socket[len(c):]
+            if rh == rc:
+                found.append((i, rh))
+    if not found:
+        raise SandboxError("protected output socket does not map through a read-write bind")
+    if len(found) > 1:
+        raise SandboxError("protected output socket maps through more than one read-write bind")
+    if not found[0][1]:
+        raise SandboxError("protected output socket must name a file beneath its read-write bind")
+    return found[0]
+
+
+class _ProtectedListener:
+    """Accepts ONE connection on the host socket, removes the socket's name at once so no second
+    party can connect, and reads until end of stream or the byte cap."""
+
+    def __init__(self, po: ProtectedOutput):
+        self.po, self.data, self.truncated = po, None, False
+        if os.path.lexists(po.host_socket):
+            raise SandboxError(f"protected output socket path already exists: {po.host_socket}")
+        self.sock = socket.socket(socket.AF_UNIX, socket.SOCK_STREAM)
+        old = os.umask(0o077)
+        try:
+            self.sock.bind(po.host_socket)
+        finally:
+            os.umask(old)
+        self.sock.listen(1)
+        self.sock.settimeout(0.2)
+        self.stop = threading.Event()
+        self.thread = threading.Thread(target=self._serve, daemon=True)
+        self.thread.start()
+
+    def _unlink(self):
+        try:
+            os.unlink(self.po.host_socket)
+        except OSError:
+            pass
+
+    def _serve(self):
+        conn = None
+        while not self.stop.is_set():
+            try:
+                conn, _ = self.sock.accept()
+                break
+            except socket.timeout:
+                continue
+            except OSError:
+                return
+        self._unlink()
+        if conn is None:
+            return
+        buf = bytearray()
+        conn.settimeout(0.2)
+        with conn:
+            while True:
+                try:
+                    chunk = conn.recv(1 << 16)
+                except socket.timeout:
+                    if self.stop.is_set():
+                        break
+                    continue
+                except OSError:
+                    break
+                if not chunk:
+                    break
+                buf += chunk
+                if len(buf) > self.po.max_bytes:
+                    self.truncated = True
+                    del buf[self.po.max_bytes:]
+                    break
+        self.data = bytes(buf)
+
+    def finish(self) -> Optional[bytes]:
+        """Call after the sandboxed process has ended."""
+        self.stop.set()
+        self.thread.join(5)
+        self.sock.close()
+        self._unlink()
+        return self.data
 
 
 def sealed_memfd(name: str, data: bytes) -> int:
@@ -174,7 +293,19 @@ class _SupervisedSandbox(Sandbox):
     def run(self, spec: RunSpec) -> SandboxOutcome:
         if not spec.command:
             raise SandboxError("empty command")
+        validate_protected_output_mapping(spec)
         argv = _supervisor_argv(spec) + ["--"] + self._payload_argv(spec)
+        listener = _ProtectedListener(spec.protected_output) if spec.protected_output is not None else None
+        try:
+            out = self._run(spec, argv)
+        finally:
+            got = listener.finish() if listener is not None else None
+        if listener is not None:
+            out.protected_output = got if got is not None else b""     # asked for and silent: an empty grade
+            out.truncated = out.truncated or listener.truncated
+        return out
+
+    def _run(self, spec: RunSpec, argv: list) -> SandboxOutcome:
         try:
             # generous outer timeout: the supervisor enforces the real limit and always returns
             res = subprocess.run(argv, input=spec.stdin_bytes, capture_output=True, env=self._env(spec),
@@ -205,6 +336,8 @@ class ApptainerSandbox(_SupervisedSandbox):
             a += ["--bind", b.render()]
         for k, v in spec.env:
             a += ["--env", f"{k}={v}"]
+        if spec.protected_output is not None:
+            a += ["--env", f"{PROTECTED_OUTPUT_ENV}={spec.protected_output.sandbox_socket}"]
         a += [spec.image, self.shell, "-c", _in_container_script(spec)]
         return a
 
@@ -219,12 +352,27 @@ class LocalSandbox(_SupervisedSandbox):
     wall clock, scratch cap and group kill, a scrubbed environment and its own cwd.
     For tests and trusted verifiers only."""
 
+    @staticmethod
+    def _host_path(spec: RunSpec, value: str) -> str:
+        """Without a container a bind is only a name: a path beneath a bind's container side is
+        rewritten to the same path beneath its host side (longest container prefix first)."""
+        for b in sorted(spec.binds, key=lambda b: -len(b.container)):
+            c = b.container.rstrip("/")
+            if value == c or value.startswith(c + "/"):
+                return b.host.rstrip("/") + value[len(c):]
+        return value
+
     def _payload_argv(self, spec: RunSpec) -> list:
-        return ["/bin/sh", "-c", f"cd {spec.workdir if os.path.isdir(spec.workdir) else '/'} && " + _in_container_script(spec)]
+        import dataclasses
+        wd = self._host_path(spec, spec.workdir)
+        local = dataclasses.replace(spec, command=[self._host_path(spec, c) for c in spec.command])
+        return ["/bin/sh", "-c", f"cd {wd if os.path.isdir(wd) else '/'} && " + _in_container_script(local)]
 
     def _env(self, spec: RunSpec) -> dict:
         env = super()._env(spec)
-        env.update({k: v for k, v in spec.env})
+        env.update({k: self._host_path(spec, v) for k, v in spec.env})
+        if spec.protected_output is not None:
+            env[PROTECTED_OUTPUT_ENV] = spec.protected_output.host_socket     # no container: host paths are the paths
         return env
 
 

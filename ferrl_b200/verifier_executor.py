@@ -26,7 +26,7 @@ import struct
 from dataclasses import dataclass
 from typing import Optional
 
-from .sandbox import (ApptainerSandbox, Bind, NetworkPolicy, ResourceLimits, RunSpec, Sandbox, SandboxError,
+from .sandbox import (ApptainerSandbox, Bind, NetworkPolicy, ProtectedOutput, ResourceLimits, RunSpec, Sandbox, SandboxError,
                       SandboxOutcome, Verdict)
 
 
@@ -84,6 +84,8 @@ def _spec_from_json(blob: bytes, fds: list) -> RunSpec:
             b.host = f"/proc/{os.getpid()}/fd/{by_name[base]}"
     lim = ResourceLimits(**d.pop("limits"))
     d.pop("stdin_bytes", None)
+    po = d.pop("protected_output", None)
+    d["protected_output"] = ProtectedOutput(**po) if po else None
     return RunSpec(binds=binds, limits=lim, network=NetworkPolicy(d.pop("network")),
                    env=[tuple(e) for e in d.pop("env")], **d)
 
@@ -133,8 +135,10 @@ class VerifierExecutorSandbox(Sandbox):
             except OSError as e:
                 return SandboxOutcome(Verdict.LAUNCH_FAILED, 126, b"", f"verifier executor: {e}".encode())
         d = json.loads(body.decode())
+        po = d.get("protected_output")
         return SandboxOutcome(Verdict(d["verdict"]), int(d["exit_code"]), base64.b64decode(d["stdout"]),
-                              base64.b64decode(d["stderr"]), bool(d.get("truncated")))
+                              base64.b64decode(d["stderr"]), bool(d.get("truncated")),
+                              None if po is None else base64.b64decode(po))
 
 
 def serve_verifier_executor(socket_path: str, inner: Sandbox, *, max_requests: Optional[int] = None,
@@ -168,6 +172,8 @@ def serve_verifier_executor(socket_path: str, inner: Sandbox, *, max_requests: O
                 _send_msg(conn, json.dumps({"verdict": out.verdict.value, "exit_code": out.exit_code,
                                             "stdout": base64.b64encode(out.stdout).decode(),
                                             "stderr": base64.b64encode(out.stderr).decode(),
-                                            "truncated": out.truncated}).encode())
+                                            "truncated": out.truncated,
+                                            "protected_output": None if out.protected_output is None
+                                            else base64.b64encode(out.protected_output).decode()}).encode())
             served += 1
     return served

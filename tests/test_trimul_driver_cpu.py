@@ -136,3 +136,26 @@ def test_wire_format_rejects_inconsistent_lengths():
     assert torch.equal(x, x2) and not torch.equal(x, E.generate_case({"seqlen": 6, "bs": 1, "dim": 8, "hiddendim": 4, "seed": 1, "nomask": False, "distribution": "normal"}, salt=1)[0])
     out = E.reference_trimul(x, mask, w, cfg)
     assert out.shape == x.shape and E.check_output(out.clone(), out) is None and "shape" in E.check_output(out[:, :2], out)
+
+
+def test_reward_end_to_end_through_the_supervised_sandbox_and_protected_socket(tmp_path):
+    """Completion -> extraction -> sealed files -> supervisor -> driver -> grade over the protected
+    socket -> shaped reward.  No container here: bind names are translated to host paths."""
+    from ferrl_b200.sandbox import LocalSandbox
+    seen = []
+
+    class Spy(LocalSandbox):
+        def run(self, spec):
+            out = super().run(spec)
+            seen.append((spec, out))
+            return out
+    rew = TrimulReward(Spy(), "", default_eval_dir(), CASES[:1], scratch_root=str(tmp_path), gpu=False,
+                       driver=(sys.executable, "-I", "/eval/ferrl_eval.py"), baseline_ns=1e12, wall_secs=240)
+    cheat = "print('check: pass')\ndef custom_kernel(data):\n    return data[0] * 0\n"
+    outs = rew.reward_group_detailed(None, [f"```python\n{GOOD}\n```", f"```python\n{cheat}\n```"])
+    assert abs(outs[0].reward - 3.0) < 1e-6 and outs[0].diagnostic is None          # correct + capped speed term
+    assert outs[1].reward == pytest.approx(rew.profile.runnable) and outs[1].diagnostic is not None
+    spec, out = seen[0]
+    assert out.protected_output is not None and b"check: pass" in out.protected_output
+    assert spec.protected_output.sandbox_socket == "/scratch/grade.sock"
+    assert os.listdir(tmp_path) == []                                  # scratch (and its socket) removed
