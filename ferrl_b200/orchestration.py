@@ -233,23 +233,68 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
         if comm.rank == 0:
             with open(run_dir.path(T.RunDir.EVAL_REPORT_FILE), "w") as f:
                 json.dump(report.to_json(), f, indent=2, sort_keys=True)
-    ranked = load_and_rank_candidates(run_dir.root) if comm.rank == 0 else []
+    ranked = load_and_rank_candidates(run_dir.root, steps=cfg.trainer.steps, group_size=cfg.trainer.group_size,
+                                      max_new_tokens=cfg.trainer.max_new_tokens, rank=0,
+                                      world_size=comm.world_size) if comm.rank == 0 else []
     return TrainOutcome(run_dir.root, run_id, stop.value, len(rows), health, report, ranked)
 
 
-def load_and_rank_candidates(run_root: str, require_signed: bool = True) -> list:
-    """Authenticated candidates of a run, best reward first (ties: earlier step, lower prompt index)."""
+def load_and_rank_candidates(run_root: str, require_signed: bool = True, *, steps: Optional[int] = None,
+                             group_size: Optional[int] = None, max_new_tokens: Optional[int] = None,
+                             rank: Optional[int] = None, world_size: Optional[int] = None,
+                             require_complete: bool = False) -> list:
+    """Authenticated candidates of a run, best reward first (ties: earlier step, lower prompt index,
+    lower group index).  Every row must be newline-terminated, non-blank, signed for this launch
+    and - when the launch bounds are given - lie inside them: ``step < steps``, ``group_index <
+    group_size``, ``1 <= completion_len_tokens <= max_new_tokens``, the active rank/world; no two
+    rows may claim one ``(step, prompt_index, group_index)``; ``require_complete`` demands exactly
+    ``steps * group_size`` rows (reference orchestration.rs:4020-4180)."""
     try:
         launch = json.load(open(os.path.join(run_root, T.RunDir.LAUNCH_FILE)))
     except (OSError, json.JSONDecodeError) as e:
         raise OrchestrationError(f"cannot read launch.json of {run_root}: {e}") from e
     key, lsha = launch.get("candidate_public_key"), launch.get("launch_sha256")
-    out = []
-    for rec in T.read_candidates(os.path.join(run_root, T.RunDir.CANDIDATES_FILE)):
+    path = os.path.join(run_root, T.RunDir.CANDIDATES_FILE)
+    if not os.path.exists(path):
+        if require_complete:
+            raise OrchestrationError("candidate ledger is missing")
+        return []
+    raw = open(path, "rb").read()
+    if raw and not raw.endswith(b"\n"):
+        raise OrchestrationError(f"candidate ledger {path} has an unterminated final row")
+    try:
+        text = raw.decode("utf-8")
+    except UnicodeDecodeError as e:
+        raise OrchestrationError(f"candidate ledger {path} is not UTF-8: {e}") from e
+    out, seen = [], set()
+    for n, line in enumerate(text.split("\n")[:-1] if text else [], 1):
+        if not line.strip():
+            raise OrchestrationError(f"candidate ledger {path} contains blank row {n}")
+        try:
+            rec = T.CandidateRecord(**json.loads(line))
+        except (TypeError, json.JSONDecodeError) as e:
+            raise OrchestrationError(f"candidate ledger {path} row {n} is malformed: {e}") from e
         if key:
-            T.verify_candidate(rec, key, lsha)
+            try:
+                T.verify_candidate(rec, key, lsha)
+            except ValueError as e:
+                raise OrchestrationError(f"candidate ledger {path} row {n} failed launch authentication: {e}") from e
         elif require_signed and launch.get("launch_authentication") == "signed":
             raise OrchestrationError("run was launched as signed but carries no candidate key")
+        if (rank is not None and rec.rank != rank) or (world_size is not None and rec.world_size != world_size):
+            raise OrchestrationError(f"candidate ledger {path} row {n} rank/world disagree with active execution topology")
+        if (steps is not None and rec.step >= steps) or (group_size is not None and rec.group_index >= group_size) \
+                or rec.step < 0 or rec.group_index < 0:
+            raise OrchestrationError(f"candidate ledger {path} row {n} coordinates exceed the launch config")
+        if max_new_tokens is not None and not 1 <= rec.completion_len_tokens <= max_new_tokens:
+            raise OrchestrationError(f"candidate ledger {path} row {n} completion length {rec.completion_len_tokens} "
+                                     f"is outside the launch-bound range 1..={max_new_tokens}")
+        pos = (rec.step, rec.prompt_index, rec.group_index)
+        if pos in seen:
+            raise OrchestrationError(f"candidate ledger {path} row {n} duplicates a training position")
+        seen.add(pos)
         out.append(rec)
+    if require_complete and steps is not None and group_size is not None and len(out) != steps * group_size:
+        raise OrchestrationError(f"candidate ledger has {len(out)} rows, expected complete logging of {steps * group_size}")
     out.sort(key=lambda r: (-r.reward, r.step, r.prompt_index, r.group_index))
     return out

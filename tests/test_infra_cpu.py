@@ -425,11 +425,29 @@ def test_orchestrated_train_report_and_perf_gate_cli(tmp_path, capsys):
         assert os.path.exists(os.path.join(out.run_dir, f))
     ranked = load_and_rank_candidates(out.run_dir)
     assert len(ranked) == 4 and ranked[0].reward >= ranked[-1].reward
-    lines = open(os.path.join(out.run_dir, "candidates.jsonl")).read().splitlines()
+    from ferrl_b200.orchestration import OrchestrationError
+    cpath = os.path.join(out.run_dir, "candidates.jsonl")
+    good_text = open(cpath).read()
+    lines = good_text.splitlines()
+    bounds = dict(steps=2, group_size=4, max_new_tokens=5, rank=0, world_size=1)
+    assert len(load_and_rank_candidates(out.run_dir, **bounds)) == 4
+    for kw, msg in ((dict(bounds, steps=1), "coordinates exceed the launch config"),
+                    (dict(bounds, max_new_tokens=1), "outside the launch-bound range"),
+                    (dict(bounds, world_size=2), "rank/world disagree"),
+                    (dict(bounds, require_complete=True), "expected complete logging of 8")):
+        with pytest.raises(OrchestrationError, match=msg):
+            load_and_rank_candidates(out.run_dir, **kw)
+    for text, msg in ((good_text + lines[0] + "\n", "duplicates a training position"),
+                      (good_text.rstrip("\n"), "unterminated final row"),
+                      (lines[0] + "\n\n" + "\n".join(lines[1:]) + "\n", "blank row 2"),
+                      (good_text + "{not json\n", "malformed")):
+        open(cpath, "w").write(text)
+        with pytest.raises(OrchestrationError, match=msg):
+            load_and_rank_candidates(out.run_dir)
     bad = json.loads(lines[0])
     bad["reward"] = 99.0
-    open(os.path.join(out.run_dir, "candidates.jsonl"), "w").write("\n".join([json.dumps(bad)] + lines[1:]) + "\n")
-    with pytest.raises(ValueError):
+    open(cpath, "w").write("\n".join([json.dumps(bad)] + lines[1:]) + "\n")
+    with pytest.raises(OrchestrationError, match="failed launch authentication"):
         load_and_rank_candidates(out.run_dir)
     assert cli.main(["report", out.run_dir, "--json"]) in (0, 1)
     assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["steps"] == 2
