@@ -652,3 +652,20 @@ def test_protected_output_socket_mapping_single_connection_cap_and_executor(tmp_
     out = VerifierExecutorSandbox(sock).run(spec(send + "s.close()\n"))
     t.join(10)
     assert out.ok and out.protected_output == b"grade: 1\n"
+
+
+def test_preflight_driver_compat_and_error_translation():
+    from ferrl_b200.preflight import PreflightError, check_driver_compat, translate_cuda_error
+    assert check_driver_compat(12090) == (12, 9) and check_driver_compat(13000) == (13, 0)
+    for v, kind in ((12040, "driver_too_old"), (11080, "driver_too_old"), (0, "no_driver"), (None, "no_driver")):
+        with pytest.raises(PreflightError) as e:
+            check_driver_compat(v)
+        assert e.value.kind == kind
+    cases = {"CUDA error: no kernel image is available for execution on the device": "wrong_arch",
+             "the provided PTX was compiled with an unsupported toolchain.": "driver_too_old",
+             "CUDA driver version is insufficient for CUDA runtime version": "driver_too_old",
+             "peer access is not supported between these two devices": "no_peer_access",
+             "CUDA out of memory. Tried to allocate 2.00 GiB": "out_of_memory"}
+    for msg, kind in cases.items():
+        assert translate_cuda_error(msg).kind == kind
+    assert translate_cuda_error("an illegal memory access was encountered") is None
