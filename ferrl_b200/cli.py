@@ -123,35 +123,97 @@ def cmd_audit(args) -> int:
 
 
 def cmd_report(args) -> int:
+    """One-glance summary of a finished run (a run directory or a ``metrics.jsonl``).  ``--config``
+    applies that run configuration's ``run_health`` policy; ``--strict`` exits 2 when the summary
+    flags anomalies or the policy has findings (otherwise: 0 healthy, 1 not)."""
     from . import telemetry as T
-    rd = T.RunDir.open(args.run_dir)
-    rows = T.read_metrics(rd.metrics_path) if os.path.exists(rd.metrics_path) else []
+    from .run_health import evaluate_run_health
+    if os.path.isfile(args.run_dir):
+        run_id, rows, cands = os.path.basename(os.path.dirname(os.path.abspath(args.run_dir))), T.read_metrics(args.run_dir), None
+    else:
+        rd = T.RunDir.open(args.run_dir)
+        run_id = rd.run_id
+        rows = T.read_metrics(rd.metrics_path) if os.path.exists(rd.metrics_path) else []
+        cands = T.read_candidates(rd.candidates_path) if os.path.exists(rd.candidates_path) else None
     s = T.summarize(rows)
-    out = {"run_id": rd.run_id, "steps": s.steps, "reward_first": s.reward_first, "reward_last": s.reward_last,
+    out = {"run_id": run_id, "steps": s.steps, "reward_first": s.reward_first, "reward_last": s.reward_last,
            "reward_best": s.reward_best, "mean_step_secs": s.mean_step_secs,
            "mean_tokens_per_sec": s.mean_tokens_per_sec, "final_grad_norm": s.final_grad_norm,
            "peak_mem_bytes": s.peak_mem_bytes, "healthy": s.healthy(), "anomalies": [str(a) for a in s.anomalies]}
+    policy = None
+    if args.config:
+        from .config import ConfigError, RunConfig
+        try:
+            cfg = RunConfig.load(args.config)
+        except ConfigError as e:
+            print(f"error: {e}", file=sys.stderr)
+            return 2
+        policy = evaluate_run_health(rows, cfg.run_health, cands, group_size=cfg.trainer.group_size,
+                                     prompt_groups_per_step=cfg.trainer.grad_accum_steps * cfg.trainer.prompts_per_item)
+        out["run_health"] = {"verdict": policy.verdict,
+                             "findings": [{"rule": f.rule, "action": f.action, "message": f.message} for f in policy.findings]}
     if args.json:
         print(json.dumps(out, sort_keys=True))
     else:
-        print(f"run {rd.run_id}: {s.steps} steps, reward {s.reward_first:.4f} -> {s.reward_last:.4f} "
+        print(f"run {run_id}: {s.steps} steps, reward {s.reward_first:.4f} -> {s.reward_last:.4f} "
               f"(best {s.reward_best:.4f}), {s.mean_step_secs:.3f} s/step, {s.mean_tokens_per_sec:.1f} tok/s")
         for a in s.anomalies:
             print(f"  anomaly: {a}")
         if s.healthy():
             print("  healthy")
-    return 0 if s.healthy() else 1
+        if policy is not None:
+            print(policy.render(), end="")
+    flagged = bool(s.anomalies) or (policy is not None and bool(policy.findings))
+    if args.strict and flagged:
+        return 2
+    return 0 if s.healthy() and not (policy is not None and policy.is_fail()) else 1
+
+
+def _metrics_of(path: str):
+    from . import telemetry as T
+    p = path if os.path.isfile(path) else os.path.join(path, T.RunDir.METRICS_FILE)
+    return T.read_metrics(p)
 
 
 def cmd_perf_gate(args) -> int:
+    """Compare two finished runs; several ``--baseline`` / ``--candidate`` paths are the ranks of one
+    data-parallel job and need ``--distributed-world-max`` (gate the job as a whole: slowest rank,
+    largest peak) with ``--distributed-world-size`` equal to the number of paths given."""
     from . import telemetry as T
-    base = T.read_metrics(os.path.join(args.baseline, T.RunDir.METRICS_FILE))
-    cand = T.read_metrics(os.path.join(args.candidate, T.RunDir.METRICS_FILE))
-    budget = T.RegressionBudget(max_mean_step_secs_ratio=args.max_step_ratio, warmup_steps=args.warmup_steps,
-                                require_cuda_memory=not args.no_memory)
-    rep = T.compare_metrics(base, cand, budget)
-    print(json.dumps({"passed": rep.passed, "failures": rep.failures, "baseline_mean_step_secs": rep.baseline_mean_step_secs,
-                      "candidate_mean_step_secs": rep.candidate_mean_step_secs}, sort_keys=True))
+    ratio = 1.0 + args.max_step_secs_regression_pct / 100.0 if args.max_step_ratio is None else args.max_step_ratio
+    budget = T.RegressionBudget(
+        require_timing=not args.skip_step_time_check, require_cuda_memory=not (args.skip_memory_check or args.no_memory),
+        allow_health_warnings=args.allow_health_warnings, warmup_steps=args.warmup_steps,
+        min_positive_grad_steps=args.min_positive_grad_steps, max_mean_step_secs_ratio=ratio,
+        max_mean_step_secs_abs_slack=args.step_secs_slack,
+        max_cuda_peak_used_ratio=1.0 + args.max_peak_mem_regression_pct / 100.0,
+        max_cuda_peak_used_abs_slack_bytes=args.peak_mem_slack_bytes,
+        max_final_grad_norm_rel_drift=args.max_final_grad_norm_rel_drift)
+    many = len(args.baseline) > 1 or len(args.candidate) > 1
+    if many and not args.distributed_world_max:
+        print("error: several --baseline/--candidate paths are the ranks of one job; pass --distributed-world-max",
+              file=sys.stderr)
+        return 2
+    if args.distributed_world_max:
+        n = args.distributed_world_size
+        if n is None or n != len(args.baseline) or n != len(args.candidate):
+            print("error: --distributed-world-max needs --distributed-world-size equal to the number of --baseline "
+                  "and of --candidate paths", file=sys.stderr)
+            return 2
+        rep = T.compare_world_max_metrics([_metrics_of(p) for p in args.baseline],
+                                          [_metrics_of(p) for p in args.candidate], budget)
+    else:
+        rep = T.compare_metrics(_metrics_of(args.baseline[0]), _metrics_of(args.candidate[0]), budget)
+    out = {"passed": rep.passed, "failures": rep.failures, "baseline_mean_step_secs": rep.baseline_mean_step_secs,
+           "candidate_mean_step_secs": rep.candidate_mean_step_secs, "baseline_peak_bytes": rep.baseline_peak_bytes,
+           "candidate_peak_bytes": rep.candidate_peak_bytes}
+    if args.json:
+        print(json.dumps(out, sort_keys=True))
+    else:
+        print(f"perf gate - {'PASS' if rep.passed else 'FAIL'}: step {rep.baseline_mean_step_secs:.4f} s -> "
+              f"{rep.candidate_mean_step_secs:.4f} s, peak {rep.baseline_peak_bytes} B -> {rep.candidate_peak_bytes} B")
+        for f in rep.failures:
+            print(f"  {f}")
     return 0 if rep.passed else 1
 
 
@@ -170,7 +232,8 @@ def cmd_verifier_executor(args) -> int:
     from .sandbox import ApptainerSandbox
     from .verifier_executor import serve_verifier_executor
     os.makedirs(args.work_root, exist_ok=True)
-    serve_verifier_executor(args.socket, ApptainerSandbox(args.apptainer))
+    serve_verifier_executor(args.socket, ApptainerSandbox(args.apptainer), client_uid=args.client_uid,
+                            socket_mode=args.socket_mode)
     return 0
 
 
@@ -198,15 +261,29 @@ def main(argv=None) -> int:
     p.add_argument("--source-inspection-notes", default="")
     p.set_defaults(fn=cmd_audit)
     p = sub.add_parser("report", aliases=["runreport"])
-    p.add_argument("run_dir")
+    p.add_argument("run_dir", help="a run directory or a metrics.jsonl file")
+    p.add_argument("--config", help="run configuration whose run_health policy is applied")
     p.add_argument("--json", action="store_true")
+    p.add_argument("--strict", action="store_true", help="exit 2 on any anomaly or policy finding")
     p.set_defaults(fn=cmd_report)
     p = sub.add_parser("perf-gate")
-    p.add_argument("--baseline", required=True)
-    p.add_argument("--candidate", required=True)
-    p.add_argument("--max-step-ratio", type=float, default=1.10)
+    p.add_argument("--baseline", required=True, action="append")
+    p.add_argument("--candidate", required=True, action="append")
+    p.add_argument("--distributed-world-max", action="store_true")
+    p.add_argument("--distributed-world-size", type=int)
+    p.add_argument("--max-peak-mem-regression-pct", type=float, default=0.0)
+    p.add_argument("--peak-mem-slack-bytes", type=int, default=64 * 1024 * 1024)
+    p.add_argument("--max-step-secs-regression-pct", type=float, default=10.0)
+    p.add_argument("--step-secs-slack", type=float, default=0.0)
+    p.add_argument("--min-positive-grad-steps", type=int, default=1)
+    p.add_argument("--max-final-grad-norm-rel-drift", type=float)
+    p.add_argument("--skip-memory-check", action="store_true")
+    p.add_argument("--skip-step-time-check", action="store_true")
+    p.add_argument("--allow-health-warnings", action="store_true")
+    p.add_argument("--json", action="store_true")
+    p.add_argument("--max-step-ratio", type=float, help="alternative to --max-step-secs-regression-pct: a ratio")
     p.add_argument("--warmup-steps", type=int, default=0)
-    p.add_argument("--no-memory", action="store_true")
+    p.add_argument("--no-memory", action="store_true", help="same as --skip-memory-check")
     p.set_defaults(fn=cmd_perf_gate)
     p = sub.add_parser("trimul-baseline")
     p.add_argument("--config", required=True)
@@ -215,6 +292,8 @@ def main(argv=None) -> int:
     p.add_argument("--socket", default="/run/ferrl/verifier-executor.sock")
     p.add_argument("--work-root", default="/var/lib/ferrl/verifier-executor")
     p.add_argument("--apptainer", default="/usr/bin/apptainer")
+    p.add_argument("--client-uid", type=int, required=True, help="the only UID whose requests are served")
+    p.add_argument("--socket-mode", type=lambda v: int(v, 8), default=0o660)
     p.set_defaults(fn=cmd_verifier_executor)
     args = ap.parse_args(argv)
     return args.fn(args)

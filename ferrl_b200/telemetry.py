@@ -477,6 +477,63 @@ def compare_distributed_metrics(baselines: Sequence[Sequence[Metrics]], candidat
     return [compare_metrics(b, c, budget) for b, c in zip(baselines, candidates)]
 
 
+def aggregate_world_rows(stream: str, ranks: Sequence[Sequence[Metrics]], budget: RegressionBudget,
+                         failures: list) -> list:
+    """One row per step for a whole data-parallel job: the slowest rank's ``step_secs``, the largest
+    peak memory, summed tokens and dropped rows, rank 0's update statistics.  Every rank must have
+    logged the same steps; missing timing or memory telemetry on ANY rank is a failure."""
+    if not ranks or not ranks[0]:
+        failures.append(f"{stream} metrics stream is empty")
+        return []
+    n = len(ranks[0])
+    for r, rows in enumerate(ranks):
+        if len(rows) != n:
+            failures.append(f"{stream} rank {r} logged {len(rows)} steps, rank 0 logged {n}")
+    n = min(len(rows) for rows in ranks)
+    if n == 0:
+        failures.append(f"{stream} metrics stream is empty")
+        return []
+    flat = [m for rows in ranks for m in rows]
+    if budget.require_timing and any(not math.isfinite(m.step_secs) or m.step_secs <= 0 for m in flat):
+        failures.append(f"{stream}: step timing is missing on at least one rank")
+    if budget.require_cuda_memory and any(m.cuda_mem_peak_used_bytes == 0 for m in flat):
+        failures.append(f"{stream}: CUDA memory telemetry is missing on at least one rank")
+    out = []
+    for i in range(n):
+        row = [rows[i] for rows in ranks]
+        if any(m.step != row[0].step for m in row):
+            failures.append(f"{stream} row {i}: ranks disagree on the step index {[m.step for m in row]}")
+        agg = dataclasses.replace(row[0])
+        agg.step_secs = max(m.step_secs for m in row)
+        agg.cuda_mem_peak_used_bytes = max(m.cuda_mem_peak_used_bytes for m in row)
+        agg.dropped_rows = sum(m.dropped_rows for m in row)
+        agg.tokens_per_sec = sum(m.tokens_per_sec for m in row)
+        agg.reward_mean = sum(m.reward_mean for m in row) / len(row)
+        out.append(agg)
+    return out
+
+
+def compare_world_max_metrics(baseline_ranks: Sequence[Sequence[Metrics]], candidate_ranks: Sequence[Sequence[Metrics]],
+                              budget: Optional[RegressionBudget] = None) -> RegressionReport:
+    """Gate a multi-rank run as ONE job: per-rank health must not differ, then the world rows
+    (``aggregate_world_rows``) are compared like a single stream."""
+    b = budget or RegressionBudget()
+    fails: list = []
+    if len(baseline_ranks) != len(candidate_ranks):
+        fails.append(f"baseline has {len(baseline_ranks)} ranks, candidate has {len(candidate_ranks)}")
+    elif not b.allow_health_warnings:
+        for r, (br, cr) in enumerate(zip(baseline_ranks, candidate_ranks)):
+            ba, ca = [str(a) for a in detect_anomalies(br)], [str(a) for a in detect_anomalies(cr)]
+            if ba != ca:
+                fails.append(f"rank {r}: health findings differ ({len(ba)} in baseline, {len(ca)} in candidate)")
+    base = aggregate_world_rows("baseline", baseline_ranks, b, fails)
+    cand = aggregate_world_rows("candidate", candidate_ranks, b, fails)
+    rep = compare_metrics(base, cand, b)
+    rep.failures = fails + [f for f in rep.failures if f not in fails]
+    rep.passed = not rep.failures
+    return rep
+
+
 # ------------------------------------------------------- device probes
 def cuda_memory_snapshot(device=None) -> Optional[tuple[int, int]]:
     """``(used_bytes, total_bytes)`` from the driver, or ``None`` without a GPU."""

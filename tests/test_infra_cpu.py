@@ -669,3 +669,78 @@ def test_preflight_driver_compat_and_error_translation():
     for msg, kind in cases.items():
         assert translate_cuda_error(msg).kind == kind
     assert translate_cuda_error("an illegal memory access was encountered") is None
+
+
+def test_cli_report_policy_strict_and_world_max_perf_gate(tmp_path, capsys):
+    import ferrl_b200.cli as cli
+    from ferrl_b200 import telemetry as T
+
+    def write(path, rows):
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        w = T.MetricsWriter(path)
+        for m in rows:
+            w.append(m)
+
+    def rows(secs, peak=1 << 30, n=3):
+        return [T.Metrics(step=i, reward_mean=0.4, grad_norm=1.0, step_secs=secs, tokens_per_sec=10.0,
+                          cuda_mem_peak_used_bytes=peak, rollout_capture_tokens=4) for i in range(n)]
+    b0, b1 = str(tmp_path / "b/r0/metrics.jsonl"), str(tmp_path / "b/r1/metrics.jsonl")
+    c0, c1 = str(tmp_path / "c/r0/metrics.jsonl"), str(tmp_path / "c/r1/metrics.jsonl")
+    write(b0, rows(1.0)), write(b1, rows(1.0)), write(c0, rows(1.0)), write(c1, rows(1.3))
+    # rank 0 alone looks fine; the job as a whole is 30 % slower because rank 1 is
+    assert cli.main(["perf-gate", "--baseline", b0, "--candidate", c0, "--json"]) == 0
+    capsys.readouterr()
+    args = ["perf-gate", "--baseline", b0, "--baseline", b1, "--candidate", c0, "--candidate", c1]
+    assert cli.main(args) == 2                                          # several paths need the world-max mode
+    assert cli.main(args + ["--distributed-world-max", "--distributed-world-size", "3"]) == 2
+    capsys.readouterr()
+    assert cli.main(args + ["--distributed-world-max", "--distributed-world-size", "2", "--json"]) == 1
+    rep = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert rep["candidate_mean_step_secs"] == pytest.approx(1.3) and "exceeds budget" in rep["failures"][0]
+    assert cli.main(args + ["--distributed-world-max", "--distributed-world-size", "2",
+                            "--max-step-secs-regression-pct", "40"]) == 0
+    # memory: the largest rank peak counts, within slack
+    write(str(tmp_path / "m/r1/metrics.jsonl"), rows(1.0, peak=(1 << 30) + (200 << 20)))
+    assert cli.main(["perf-gate", "--baseline", b0, "--baseline", b1, "--candidate", c0, "--candidate",
+                     str(tmp_path / "m/r1/metrics.jsonl"), "--distributed-world-max", "--distributed-world-size", "2"]) == 1
+    # a rank that logged fewer steps is a failure of its own
+    write(str(tmp_path / "s/r1/metrics.jsonl"), rows(1.0, n=2))
+    r = T.compare_world_max_metrics([T.read_metrics(b0), T.read_metrics(b1)],
+                                    [T.read_metrics(c0), T.read_metrics(str(tmp_path / "s/r1/metrics.jsonl"))])
+    assert not r.passed and any("logged 2 steps" in f for f in r.failures)
+    capsys.readouterr()
+    # report: a metrics file is accepted; the configured policy is applied; --strict exits 2 on findings
+    cfgp = tmp_path / "run.json"
+    cfgp.write_text(json.dumps({"task": "countdown", "model_dir": "x", "trainer": {"steps": 3, "group_size": 4},
+                                "run_health": {"reward_collapse": {"window": 2, "min": 0.9, "action": "warn"}}}))
+    assert cli.main(["report", b0, "--json"]) == 0
+    assert json.loads(capsys.readouterr().out.strip().splitlines()[-1])["steps"] == 3
+    assert cli.main(["report", b0, "--config", str(cfgp), "--json"]) == 0           # a warning is not a failure
+    js = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert js["run_health"]["verdict"] == "warn" and js["run_health"]["findings"][0]["rule"] == "reward_collapse"
+    assert cli.main(["report", b0, "--config", str(cfgp), "--strict"]) == 2
+    assert "run health policy - WARN" in capsys.readouterr().out
+
+
+def test_verifier_executor_serves_only_the_configured_client_uid(tmp_path):
+    from ferrl_b200.sandbox import LocalSandbox, RunSpec, Verdict
+    from ferrl_b200.verifier_executor import VerifierExecutorSandbox, serve_verifier_executor
+    sock = str(tmp_path / "ve.sock")
+
+    def serve(uid, n):
+        ready = threading.Event()
+        t = threading.Thread(target=serve_verifier_executor, args=(sock, LocalSandbox()),
+                             kwargs=dict(max_requests=n, ready=ready, client_uid=uid, socket_mode=0o600))
+        t.daemon = True
+        t.start()
+        ready.wait(10)
+        return t
+    t = serve(os.getuid(), 1)
+    assert (os.stat(sock).st_mode & 0o777) == 0o600
+    out = VerifierExecutorSandbox(sock).run(RunSpec("", ["sh", "-c", "echo mine"]))
+    t.join(10)
+    assert out.ok and out.stdout == b"mine\n"
+    # a service configured for another UID hangs up on us without running anything
+    t = serve(os.getuid() + 12345, 1)
+    out = VerifierExecutorSandbox(sock, timeout=5).run(RunSpec("", ["sh", "-c", "echo intruder"]))
+    assert out.verdict is Verdict.LAUNCH_FAILED and out.stdout == b""
