@@ -58,13 +58,57 @@ def _trimul_reward(cfg):
     return build_task(cfg)[2]
 
 
+LLAMA_CPP_EOT = "[end of text]"
+
+
+def normalize_completion(raw: str, mode: str) -> tuple:
+    """``(text, changed)``.  ``llama-cpp``: drop the ``[end of text]`` marker llama.cpp's CLI appends
+    (and the whitespace around it), leaving one trailing newline."""
+    if mode == "llama-cpp":
+        stripped = raw.rstrip()
+        if stripped.endswith(LLAMA_CPP_EOT):
+            text = stripped[:-len(LLAMA_CPP_EOT)].rstrip() + "\n"
+            return text, text != raw
+    return raw, False
+
+
+def read_verified_prompt_copy(path: str) -> bytes:
+    """The prompt copy of a run directory, checked against the ``prompt.sha256`` beside it."""
+    import hashlib
+    data = open(path, "rb").read()
+    hash_path = os.path.join(os.path.dirname(os.path.abspath(path)), "prompt.sha256")
+    try:
+        expected = (open(hash_path).read().split() or [""])[0]
+    except OSError as e:
+        raise ValueError(f"read {hash_path}: {e}") from e
+    actual = hashlib.sha256(data).hexdigest()
+    if expected != actual:
+        raise ValueError(f"prompt copy hash mismatch: {hash_path} records {expected or '<empty>'}, but {path} "
+                         f"hashes to {actual}")
+    return data
+
+
 def cmd_score(args) -> int:
+    """Score external TriMul completions once with the shaped reward, on hidden cases re-keyed with
+    ``--score-secret-seed`` (which must differ from the training seed)."""
+    import hashlib
     from .config import RunConfig
+    from .rewards.trimul import TRIMUL_CASE_SEED_MAX
     cfg = RunConfig.load(args.config)
     if cfg.task != "trimul":
-        print("error: score needs a trimul run config", file=sys.stderr)
+        print("error: trimul-score requires a config with task \"trimul\"", file=sys.stderr)
         return 2
-    reward = _trimul_reward(cfg)
+    if not 0 <= args.score_secret_seed <= TRIMUL_CASE_SEED_MAX:
+        print(f"error: trimul-score requires --score-secret-seed between 0 and {TRIMUL_CASE_SEED_MAX}", file=sys.stderr)
+        return 2
+    if args.score_secret_seed == int(cfg.trimul.get("secret_seed", 0)):
+        print("error: trimul-score requires --score-secret-seed to differ from trimul.secret_seed", file=sys.stderr)
+        return 2
+    try:
+        prompt = read_verified_prompt_copy(args.prompt_copy)
+    except (OSError, ValueError) as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 2
     comps = []
     for p in args.completion or []:
         comps.append({"completion": open(p, encoding="utf-8").read(), "source_id": p})
@@ -72,20 +116,52 @@ def cmd_score(args) -> int:
         for i, line in enumerate(open(p, encoding="utf-8")):
             if line.strip():
                 d = json.loads(line)
+                if not isinstance(d.get("completion"), str):
+                    print(f"error: {p}:{i} has no completion string", file=sys.stderr)
+                    return 2
                 d.setdefault("source_id", f"{p}:{i}")
                 comps.append(d)
     if not comps:
-        print("error: no completions given", file=sys.stderr)
+        print("error: trimul-score requires at least one --completion or --completions-jsonl row", file=sys.stderr)
         return 2
-    outs = reward.reward_group_detailed(None, [c["completion"] for c in comps])
-    with open(args.out, "w", encoding="utf-8") as f:
-        for c, o in zip(comps, outs):
-            f.write(json.dumps({"task": "trimul", "score_scheme": reward.profile.scheme, "run_id": args.run_id,
-                                "step": c.get("step", args.step), "prompt_index": c.get("prompt_index", args.prompt_index),
-                                "source_id": c["source_id"], "reward": o.reward, "reward_diagnostic": o.diagnostic,
-                                "reward_metadata": o.metadata, "completion_len_bytes": len(c["completion"].encode()),
-                                "completion": c["completion"]}, sort_keys=True) + "\n")
-    print(json.dumps({"scored": len(comps), "best": max(o.reward for o in outs), "out": args.out}))
+    if os.path.lexists(args.out):
+        print(f"error: {args.out} already exists; scores are never overwritten", file=sys.stderr)
+        return 2
+    normalized = [normalize_completion(c["completion"], args.completion_normalization) for c in comps]
+    reward = _trimul_reward(cfg).with_secret_seed(args.score_secret_seed)
+    outs = reward.reward_group_detailed(None, [t for t, _ in normalized])
+    if len(outs) != len(comps):
+        print(f"error: trimul scoring returned {len(outs)} outcomes for {len(comps)} completions", file=sys.stderr)
+        return 1
+    config_sha = hashlib.sha256(open(args.config, "rb").read()).hexdigest()
+    diagnostics: dict = {}
+    with open(args.out, "x", encoding="utf-8") as f:
+        for i, (c, (text, changed), o) in enumerate(zip(comps, normalized, outs)):
+            if o.diagnostic:
+                diagnostics[o.diagnostic] = diagnostics.get(o.diagnostic, 0) + 1
+            meta = c.get("metadata")
+            if args.completion_normalization != "none":
+                meta = dict(meta or {}, completion_normalization={
+                    "mode": args.completion_normalization, "changed": changed,
+                    "raw_len_bytes": len(c["completion"].encode()),
+                    "raw_sha256": hashlib.sha256(c["completion"].encode()).hexdigest()})
+            f.write(json.dumps({
+                "task": "trimul", "score_scheme": reward.profile.scheme, "run_id": args.run_id,
+                "step": c.get("step", args.step), "rank": c.get("rank", args.rank),
+                "world_size": c.get("world_size", args.world_size),
+                "prompt_index": c.get("prompt_index", args.prompt_index), "group_index": c.get("group_index", i),
+                "reward": o.reward, "reward_diagnostic": o.diagnostic, "reward_metadata": o.metadata,
+                "input_metadata": meta, "input_reward_metadata": c.get("reward_metadata"),
+                "completion_len_tokens": c.get("completion_len_tokens"), "completion_len_bytes": len(text.encode()),
+                "completion": text,
+                "external_score": {"model_family": args.model_family, "checkpoint": args.checkpoint,
+                                   "tokenizer": args.tokenizer, "source_label": args.source_label,
+                                   "source_id": c["source_id"], "source_index": i,
+                                   "score_secret_seed": args.score_secret_seed, "used_training_secret_seed": False,
+                                   "prompt_sha256": hashlib.sha256(prompt).hexdigest(), "config_sha256": config_sha},
+            }, sort_keys=True) + "\n")
+    print(json.dumps({"scored": len(comps), "positive": sum(1 for o in outs if o.reward > 0),
+                      "best": max(o.reward for o in outs), "diagnostics": diagnostics, "out": args.out}, sort_keys=True))
     return 0
 
 
@@ -246,12 +322,21 @@ def main(argv=None) -> int:
     p.set_defaults(fn=cmd_train)
     p = sub.add_parser("score", aliases=["trimul-score"])
     p.add_argument("--config", required=True)
+    p.add_argument("--prompt-copy", required=True, help="prompt.txt of a run directory (prompt.sha256 beside it)")
     p.add_argument("--completion", action="append")
     p.add_argument("--completions-jsonl", action="append")
+    p.add_argument("--completion-normalization", choices=["none", "llama-cpp"], default="none")
     p.add_argument("--out", required=True)
+    p.add_argument("--score-secret-seed", type=int, required=True)
     p.add_argument("--run-id", default="external-rollout")
+    p.add_argument("--source-label", default="external")
     p.add_argument("--step", type=int, default=0)
     p.add_argument("--prompt-index", type=int, default=0)
+    p.add_argument("--rank", type=int, default=0)
+    p.add_argument("--world-size", type=int, default=1)
+    p.add_argument("--model-family", default="external")
+    p.add_argument("--checkpoint")
+    p.add_argument("--tokenizer")
     p.set_defaults(fn=cmd_score)
     p = sub.add_parser("audit", aliases=["trimul-artifact"])
     p.add_argument("--run-dir", required=True)

@@ -37,6 +37,7 @@ CORRECTNESS_REWARD = 1.0
 SPEED_REWARD_CAP = 2.0
 EVAL_DRIVER_FILE = "ferrl_eval.py"
 GRADE_SOCKET = "grade.sock"
+TRIMUL_CASE_SEED_MAX = (1 << 32) - 1
 
 
 def default_eval_dir() -> str:
@@ -194,6 +195,17 @@ class TrimulReward:
         self.baseline_ns, self.extract_mode = baseline_ns, SubmissionExtractMode(extract_mode)
         self.scratch_root, self.wall_secs, self.scratch_max = scratch_root, wall_secs, scratch_max_bytes
         self.parallelism, self.gpu, self.driver = max(1, parallelism), gpu, list(driver)
+
+    def with_secret_seed(self, seed: int) -> "TrimulReward":
+        """Re-key every hidden case: case ``i`` gets ``seed + i`` (mod 2^32), so external scoring and
+        audits never replay the inputs a policy was trained against."""
+        import dataclasses
+        if not 0 <= int(seed) <= TRIMUL_CASE_SEED_MAX:
+            raise RewardError(f"secret seed must be between 0 and {TRIMUL_CASE_SEED_MAX}")
+        self.cases = [dataclasses.replace(c, seed=(int(seed) + i) & TRIMUL_CASE_SEED_MAX) for i, c in enumerate(self.cases)]
+        self.benchmark_cases = [dataclasses.replace(c, seed=(int(seed) + 7919 + i) & TRIMUL_CASE_SEED_MAX)
+                                for i, c in enumerate(self.benchmark_cases)]
+        return self
 
     def with_baseline_ns(self, ns: float) -> "TrimulReward":
         self.baseline_ns = float(ns)

@@ -744,3 +744,53 @@ def test_verifier_executor_serves_only_the_configured_client_uid(tmp_path):
     t = serve(os.getuid() + 12345, 1)
     out = VerifierExecutorSandbox(sock, timeout=5).run(RunSpec("", ["sh", "-c", "echo intruder"]))
     assert out.verdict is Verdict.LAUNCH_FAILED and out.stdout == b""
+
+
+def test_cli_trimul_score_prompt_copy_secret_seed_normalization_and_records(tmp_path, capsys, monkeypatch):
+    import hashlib
+    import ferrl_b200.cli as cli
+    from ferrl_b200.rewards.trimul import TrimulCase, TrimulReward
+    from ferrl_b200.sandbox import FakeSandbox, SandboxOutcome, Verdict
+    good = "test-count: 1\ntest.0.status: pass\ncheck: pass\ntest-exit: 0\nbenchmark-count: 1\nbenchmark.0.mean: 2000000\nbenchmark-exit: 0\n"
+    specs = []
+
+    def fake(spec):
+        specs.append(open(spec.binds[3].host).read())                 # the sealed test spec
+        return SandboxOutcome(Verdict.EXITED, 0, good.encode(), b"")
+    reward = TrimulReward(FakeSandbox(fake), "img", str(tmp_path), [TrimulCase(32, 1, 16, 8, 11), TrimulCase(64, 1, 16, 8, 11)],
+                          baseline_ns=4e6)
+    monkeypatch.setattr(cli, "_trimul_reward", lambda cfg: reward)
+    prompt = tmp_path / "prompt.txt"
+    prompt.write_text("write a kernel")
+    (tmp_path / "prompt.sha256").write_text(hashlib.sha256(b"write a kernel").hexdigest() + "\n")
+    cfgp = tmp_path / "run.json"
+    cfgp.write_text(json.dumps({"task": "trimul", "model_dir": "x", "trainer": {"steps": 1, "group_size": 2},
+                                "trimul": {"secret_seed": 11, "prompt_path": str(prompt), "image": "img"}}))
+    comp = tmp_path / "c.txt"
+    comp.write_text("```python\nprint(1)\n```\n [end of text]\n")
+    jl = tmp_path / "c.jsonl"
+    jl.write_text(json.dumps({"completion": "no code here", "step": 3, "group_index": 5, "metadata": {"k": 1}}) + "\n")
+    base = ["score", "--config", str(cfgp), "--prompt-copy", str(prompt), "--completion", str(comp),
+            "--completions-jsonl", str(jl), "--completion-normalization", "llama-cpp", "--model-family", "qwen3"]
+    out = str(tmp_path / "scores.jsonl")
+    assert cli.main(base + ["--out", out, "--score-secret-seed", "11"]) == 2          # the training seed is refused
+    assert "differ from trimul.secret_seed" in capsys.readouterr().err
+    assert cli.main(base + ["--out", out, "--score-secret-seed", str(1 << 32)]) == 2
+    (tmp_path / "prompt.sha256").write_text("0" * 64 + "\n")
+    assert cli.main(base + ["--out", out, "--score-secret-seed", "77"]) == 2
+    assert "prompt copy hash mismatch" in capsys.readouterr().err and not specs
+    (tmp_path / "prompt.sha256").write_text(hashlib.sha256(b"write a kernel").hexdigest() + "\n")
+    assert cli.main(base + ["--out", out, "--score-secret-seed", "77"]) == 0
+    summary = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert summary["scored"] == 2 and summary["positive"] == 1 and summary["diagnostics"] == {"trimul:no_submission": 1}
+    assert "seed: 77;" in specs[0] and "seed: 78;" in specs[0] and "seed: 11;" not in specs[0]
+    recs = [json.loads(line) for line in open(out)]
+    assert recs[0]["completion"] == "```python\nprint(1)\n```\n" and abs(recs[0]["reward"] - 3.0) < 1e-6
+    assert recs[0]["input_metadata"]["completion_normalization"] == {
+        "mode": "llama-cpp", "changed": True, "raw_len_bytes": len(comp.read_text().encode()),
+        "raw_sha256": hashlib.sha256(comp.read_text().encode()).hexdigest()}
+    assert recs[0]["external_score"]["score_secret_seed"] == 77 and recs[0]["external_score"]["model_family"] == "qwen3"
+    assert recs[1]["step"] == 3 and recs[1]["group_index"] == 5 and recs[1]["reward"] == 0.0
+    assert recs[1]["input_metadata"]["k"] == 1 and recs[1]["input_metadata"]["completion_normalization"]["changed"] is False
+    assert cli.main(base + ["--out", out, "--score-secret-seed", "77"]) == 2          # never overwritten
+    assert cli.normalize_completion("abc [end of text]", "none") == ("abc [end of text]", False)
