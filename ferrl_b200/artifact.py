@@ -136,7 +136,11 @@ def publish_trimul_artifact(run_root: str, out_dir: str, candidate_source: str, 
             ref_ns, cand_ns = time_pair(candidate_source, first)
             blocks.append(AuditBlock(i, first, float(ref_ns), float(cand_ns)))
     decision = acceptance_from_speedups([b.paired_speedup for b in blocks])
-    accepted = correct and decision.accepted
+    if source_inspection not in ("clean", "suspicious", "not_performed"):
+        raise ArtifactError(f"source_inspection must be clean, suspicious or not_performed, got {source_inspection!r}")
+    # an operator who found the candidate probing processes, descriptors, the environment, the
+    # network or paths outside its inputs vetoes it whatever the timings say (artifact.rs:1682)
+    accepted = correct and decision.accepted and source_inspection != "suspicious"
     man = ArtifactManifest(ARTIFACT_CONTRACT_VERSION, aid, str(launch.get("run_id")), csha, float(candidate_reward),
                            correct, [dict(asdict(b), paired_speedup=b.paired_speedup) for b in blocks],
                            asdict(decision), accepted, run_health, source_inspection, source_inspection_notes,
@@ -156,7 +160,15 @@ def publish_trimul_artifact(run_root: str, out_dir: str, candidate_source: str, 
 
 def artifact_report(m: ArtifactManifest) -> str:
     verdict = "accepted_artifact" if m.accepted else "rejected_candidate"
-    lines = [f"# TriMul artifact audit: {verdict}", "", f"- run: `{m.run_id}`", f"- audit id: `{m.audit_id}`",
+    if m.accepted:
+        reason = "accepted: at least nine of eleven same-device pairs exceed the 2% material margin"
+    elif m.source_inspection == "suspicious":
+        reason = "rejected: source inspection found process/file/env/network/path probing"
+    elif not m.correct_on_secret_cases:
+        reason = "rejected: the candidate is not correct on the audit's secret-seed cases"
+    else:
+        reason = "rejected: paired audit did not establish nine material wins out of eleven"
+    lines = [f"# TriMul artifact audit: {verdict}", "", reason, "", f"- run: `{m.run_id}`", f"- audit id: `{m.audit_id}`",
              f"- candidate sha256: `{m.candidate_sha256}`", f"- training reward: {m.candidate_reward:.4f}",
              f"- correct on secret-seed cases: {m.correct_on_secret_cases}",
              f"- material wins: {m.decision['observed_material_wins']} of {m.decision['paired_blocks']} "

@@ -165,36 +165,72 @@ def cmd_score(args) -> int:
     return 0
 
 
+SOURCE_INSPECTION_RESULTS = ("clean", "suspicious", "not_performed")
+
+
 def cmd_audit(args) -> int:
-    from .artifact import publish_trimul_artifact
+    """Extract one launch-bound candidate row (``--candidate-sha256``, default: the best-ranked one)
+    and audit it: correctness on re-keyed secret cases, then 11 paired blocks in which the
+    packaged baseline submission and the candidate are both run, in the block's scheduled order,
+    on the one device named by ``--audit-cuda-visible-device``."""
+    from .artifact import ArtifactError, publish_trimul_artifact
     from .config import RunConfig
-    from .orchestration import load_and_rank_candidates
-    from .rewards.trimul import extract_submission
-    cands = load_and_rank_candidates(args.run_dir)
+    from .orchestration import OrchestrationError, load_and_rank_candidates
+    from .rewards.trimul import default_eval_dir, extract_submission
+    if os.path.lexists(args.out):
+        print(f"error: {args.out} already exists; an audit claims a new output directory", file=sys.stderr)
+        return 2
+    try:
+        cands = load_and_rank_candidates(args.run_dir)
+    except OrchestrationError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
     if not cands:
         print("error: the run has no authenticated candidates", file=sys.stderr)
         return 1
-    best = cands[0]
-    src = extract_submission(best.completion)
-    if src is None:
-        print("error: the best candidate contains no extractable submission", file=sys.stderr)
-        return 1
+    if args.candidate_sha256:
+        match = [c for c in cands if c.record_sha256 == args.candidate_sha256]
+        if not match:
+            print(f"error: no candidate row with record_sha256 {args.candidate_sha256}", file=sys.stderr)
+            return 1
+        best = match[0]
+    else:
+        best = cands[0]
     cfg = RunConfig.from_json(json.load(open(os.path.join(args.run_dir, "config.json"))))
+    if args.audit_verifier_executor_socket:
+        cfg.trimul["verifier_isolation_tier"] = "dedicated_uid_service_v1"
+        cfg.trimul["verifier_executor_socket"] = args.audit_verifier_executor_socket
+    if args.audit_cuda_visible_device is not None:
+        os.environ["CUDA_VISIBLE_DEVICES"] = args.audit_cuda_visible_device
     reward = _trimul_reward(cfg)
+    src = extract_submission(best.completion, reward.extract_mode)
+    if src is None:
+        print("error: the candidate contains no extractable submission", file=sys.stderr)
+        return 1
+    ref_src = open(os.path.join(cfg.trimul.get("eval_dir") or default_eval_dir(), "reference_submission.py"),
+                   encoding="utf-8").read()
 
     def verify(source, seed):
-        import dataclasses
-        reward.cases = [dataclasses.replace(c, seed=seed) for c in reward.cases]
-        return reward.verify_submission(source).correct
+        return reward.with_secret_seed(seed).verify_submission(source).correct
 
     def time_pair(source, first):
-        ev = reward.verify_submission(source)
-        ref = (cfg.trimul.get("baseline") or {}).get("ns") or float("nan")
-        return ref, ev.geomean_ns or float("nan")
-    man = publish_trimul_artifact(args.run_dir, args.out, src, best.reward, verify, time_pair,
-                                  run_health=args.run_health, source_inspection=args.source_inspection,
-                                  source_inspection_notes=args.source_inspection_notes)
-    print(json.dumps({"accepted": man.accepted, "wins": man.decision["observed_material_wins"], "out": args.out}))
+        order = [("reference", ref_src), ("candidate", source)]
+        if first == "candidate":
+            order.reverse()
+        ns = {}
+        for name, code in order:
+            ev = reward.verify_submission(code)
+            ns[name] = ev.geomean_ns if (ev.correct and ev.geomean_ns and not ev.implausible()) else float("nan")
+        return ns["reference"], ns["candidate"]
+    try:
+        man = publish_trimul_artifact(args.run_dir, args.out, src, best.reward, verify, time_pair,
+                                      run_health=args.run_health, source_inspection=args.source_inspection,
+                                      source_inspection_notes=args.source_inspection_notes)
+    except ArtifactError as e:
+        print(f"error: {e}", file=sys.stderr)
+        return 1
+    print(json.dumps({"accepted": man.accepted, "wins": man.decision["observed_material_wins"],
+                      "candidate_record_sha256": best.record_sha256, "out": args.out}))
     return 0 if man.accepted else 1
 
 
@@ -340,9 +376,12 @@ def main(argv=None) -> int:
     p.set_defaults(fn=cmd_score)
     p = sub.add_parser("audit", aliases=["trimul-artifact"])
     p.add_argument("--run-dir", required=True)
+    p.add_argument("--candidate-sha256", help="record_sha256 of one row of candidates.jsonl (default: the best-ranked row)")
     p.add_argument("--out", required=True)
+    p.add_argument("--audit-verifier-executor-socket")
+    p.add_argument("--audit-cuda-visible-device")
     p.add_argument("--run-health", default="ok")
-    p.add_argument("--source-inspection", default="not_performed")
+    p.add_argument("--source-inspection", default="not_performed", choices=SOURCE_INSPECTION_RESULTS)
     p.add_argument("--source-inspection-notes", default="")
     p.set_defaults(fn=cmd_audit)
     p = sub.add_parser("report", aliases=["runreport"])

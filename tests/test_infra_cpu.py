@@ -794,3 +794,55 @@ def test_cli_trimul_score_prompt_copy_secret_seed_normalization_and_records(tmp_
     assert recs[1]["input_metadata"]["k"] == 1 and recs[1]["input_metadata"]["completion_normalization"]["changed"] is False
     assert cli.main(base + ["--out", out, "--score-secret-seed", "77"]) == 2          # never overwritten
     assert cli.normalize_completion("abc [end of text]", "none") == ("abc [end of text]", False)
+
+
+def test_cli_audit_pairs_reference_and_candidate_per_block_and_honours_inspection(tmp_path, capsys, monkeypatch):
+    import ferrl_b200.cli as cli
+    from ferrl_b200 import telemetry as T
+    from ferrl_b200.artifact import audit_schedule
+    from ferrl_b200.rewards.trimul import TrimulCase, TrimulReward
+    from ferrl_b200.sandbox import FakeSandbox, SandboxOutcome, Verdict
+    run = tmp_path / "run"
+    run.mkdir()
+    signer = T.CandidateSigner("ab" * 32)
+    (run / "launch.json").write_text(json.dumps({"run_id": "r1", "launch_sha256": "ab" * 32,
+                                                 "candidate_public_key": signer.public_key_hex,
+                                                 "launch_authentication": "signed"}))
+    (run / "config.json").write_text(json.dumps({"task": "trimul", "model_dir": "x", "trainer": {"steps": 2, "group_size": 2},
+                                                 "trimul": {"secret_seed": 5, "prompt_path": "p", "image": "img"}}))
+    w = T.CandidateWriter(str(run / "candidates.jsonl"), signer)
+    w.append(T.CandidateRecord(0, 0, 1, 0, 0, 2.5, 9, "```python\n# FAST\n```"))
+    w.append(T.CandidateRecord(1, 0, 1, 1, 1, 1.0, 9, "```python\n# SLOW\n```"))
+    slow_sha = [c for c in T.read_candidates(str(run / "candidates.jsonl")) if "SLOW" in c.completion][0].record_sha256
+    order = []
+
+    def fake(spec):
+        code = open(spec.binds[2].host).read()
+        who = "fast" if "FAST" in code else "slow" if "SLOW" in code else "reference"
+        order.append(who)
+        ns = {"fast": 1000000, "slow": 2100000, "reference": 2000000}[who]
+        log = f"test-count: 1\ntest.0.status: pass\ncheck: pass\ntest-exit: 0\nbenchmark-count: 1\nbenchmark.0.mean: {ns}\nbenchmark-exit: 0\n"
+        return SandboxOutcome(Verdict.EXITED, 0, log.encode(), b"")
+    monkeypatch.setattr(cli, "_trimul_reward", lambda cfg: TrimulReward(FakeSandbox(fake), "img", str(tmp_path),
+                                                                         [TrimulCase(32, 1, 16, 8, 5)]))
+    out = tmp_path / "audit-fast"
+    assert cli.main(["audit", "--run-dir", str(run), "--out", str(out), "--source-inspection", "clean",
+                     "--audit-cuda-visible-device", "0"]) == 0
+    res = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert res["accepted"] and res["wins"] == 11
+    man = json.load(open(out / "artifact-manifest.json"))
+    sched = audit_schedule(man["audit_id"])
+    pairs = [tuple(order[1 + 2 * i: 3 + 2 * i]) for i in range(11)]                # order[0] is the correctness re-check
+    assert order[0] == "fast" and all(p == (("reference", "fast") if f == "reference" else ("fast", "reference"))
+                                      for p, f in zip(pairs, sched))
+    assert all(abs(b["paired_speedup"] - 2.0) < 1e-9 for b in man["blocks"])
+    assert "accepted: at least nine of eleven" in open(out / "artifact-report.md").read()
+    assert cli.main(["audit", "--run-dir", str(run), "--out", str(out)]) == 2      # the output is never reused
+    # a named row: the slower candidate loses every pair
+    assert cli.main(["audit", "--run-dir", str(run), "--candidate-sha256", slow_sha, "--out", str(tmp_path / "audit-slow")]) == 1
+    assert json.load(open(tmp_path / "audit-slow" / "artifact-manifest.json"))["decision"]["observed_material_wins"] == 0
+    assert cli.main(["audit", "--run-dir", str(run), "--candidate-sha256", "00" * 32, "--out", str(tmp_path / "x")]) == 1
+    # a suspicious source inspection vetoes a candidate that wins every pair
+    assert cli.main(["audit", "--run-dir", str(run), "--out", str(tmp_path / "audit-sus"), "--source-inspection", "suspicious",
+                     "--source-inspection-notes", "reads /proc/self/environ"]) == 1
+    assert "rejected: source inspection found" in open(tmp_path / "audit-sus" / "artifact-report.md").read()
