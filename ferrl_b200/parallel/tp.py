@@ -13,8 +13,8 @@ The two autograd operators are the classic pair:
 * ``reduce_from_tp``  forward sum-all-reduce, backward identity
 
 On GPUs ``reduce_from_tp`` is not issued as a separate collective: the
-row-parallel projection calls the fused GEMM→all-reduce kernel
-(``csrc/tp``), which pushes partial tiles over NVLink while later tiles are
+row-parallel projection calls the all-reduce mode of the GEMM kernel
+(``csrc/gemm/tcgen05_gemm.cu``), which pushes partial tiles over NVLink while later tiles are
 still on the tensor cores.  The functions here are the CPU/``Comm`` form used
 by lockstep tests and as the NCCL baseline.
 """

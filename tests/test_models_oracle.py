@@ -203,3 +203,80 @@ def test_paged_decoder_block_table_matches_contiguous_cache():
     # rows of one prompt share its full pages and nothing else
     t = b.table
     assert torch.equal(t[3 * G, :2], t[3 * G + 1, :2]) and t[3 * G, 2] != t[3 * G + 1, 2]
+
+
+def make_ckpt(d):
+    """A random Gemma 4 checkpoint in HF naming with 4 query / 2 kv heads, so that it shards over two ranks."""
+    from safetensors.torch import save_file
+    cfg = json.load(open(os.path.join(FIX, "tiny_gemma4", "config.json")))
+    t = cfg["text_config"]
+    t.update(num_attention_heads=4, num_key_value_heads=2, num_global_key_value_heads=2, hidden_size=16, intermediate_size=32)
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    g = torch.Generator().manual_seed(5)
+    H, F, D, GD, V = 16, 32, t["head_dim"], t["global_head_dim"], t["vocab_size"]
+    rnd = lambda *s: torch.randn(*s, generator=g) * 0.2
+    w = {"model.embed_tokens.weight": rnd(V, H), "model.norm.weight": 1 + 0.1 * rnd(H)}
+    for i, kind in enumerate(t["layer_types"]):
+        b = f"model.layers.{i}."
+        d_ = D if kind == "sliding_attention" else GD
+        hkv = 2
+        w[b + "self_attn.q_proj.weight"] = rnd(4 * d_, H)
+        w[b + "self_attn.k_proj.weight"] = rnd(hkv * d_, H)
+        if kind == "sliding_attention" or not t["attention_k_eq_v"]:
+            w[b + "self_attn.v_proj.weight"] = rnd(hkv * d_, H)
+        w[b + "self_attn.o_proj.weight"] = rnd(H, 4 * d_)
+        w[b + "mlp.gate_proj.weight"] = rnd(F, H); w[b + "mlp.up_proj.weight"] = rnd(F, H); w[b + "mlp.down_proj.weight"] = rnd(H, F)
+        for n in ("input_layernorm", "post_attention_layernorm", "pre_feedforward_layernorm", "post_feedforward_layernorm"):
+            w[b + n + ".weight"] = 1 + 0.1 * rnd(H)
+        w[b + "self_attn.q_norm.weight"] = 1 + 0.1 * rnd(d_); w[b + "self_attn.k_norm.weight"] = 1 + 0.1 * rnd(d_)
+        w[b + "layer_scalar"] = torch.tensor([0.7 + 0.1 * i])
+    save_file(w, os.path.join(d, "model.safetensors"))
+    return t
+
+
+@pytest.mark.parametrize("remat", [False, True])
+def test_gemma4_tensor_parallel_training_matches_single_rank(tmp_path, remat):
+    """Gemma 4 is the family the reference trains tensor-parallel (with activation checkpointing):
+    two thread ranks that stream only their own rows/columns of a checkpoint reproduce the
+    unsharded logits, and their replicated-adapter gradients sum to the unsharded gradients."""
+    from ferrl_b200.comm import run_ranks
+    d = str(tmp_path)
+    t = make_ckpt(d)
+    ids = torch.randint(0, t["vocab_size"], (2, 10), generator=torch.Generator().manual_seed(1))
+    single = load_auto_policy(d, LoaderOpts())[0]
+    for p in single.trainable_params():
+        if p.shape[1] == single.lora.rank:
+            with torch.no_grad():
+                p.add_(0.03)
+    want = single(ids)
+    want.pow(2).sum().backward()
+    ref = [p.grad.clone() for p in single.trainable_params()]
+
+    def body(comm):
+        m = load_auto_policy(d, LoaderOpts(tp=(comm.rank, comm.world_size), remat=remat))[0]
+        assert m.layers[0].qkv.weight.shape[0] * 2 == single.layers[0].qkv.weight.shape[0]      # a real shard
+        with torch.no_grad():
+            for a, b in zip(m.trainable_params(), single.trainable_params()):
+                a.copy_(b)
+        out = m(ids, comm)
+        out.pow(2).sum().backward()
+        grads = [p.grad.contiguous() for p in m.trainable_params()]
+        comm.all_reduce_sum(grads)
+        return out.detach(), grads
+    for out, grads in run_ranks(2, body, timeout=120):
+        assert (out - want.detach()).abs().max().item() < 1e-4
+        for g, r in zip(grads, ref):
+            assert (g - r).abs().max().item() < 1e-3 * max(1.0, r.abs().max().item())
+
+
+def test_tensor_parallel_plan_divides_evenly_or_refuses():
+    from ferrl_b200.comm import CommConfigError
+    from ferrl_b200.parallel.tp import TensorParallelPlan
+    p = TensorParallelPlan.new(1, 4, 32, 8, 12288)
+    assert (p.local_heads, p.local_kv_heads, p.local_intermediate) == (8, 2, 3072)
+    s = p.shard(4096)
+    assert (s.start, s.len, s.end) == (1024, 1024, 2048)
+    for args, msg in (((0, 3, 32, 8, 12288), "attention heads"), ((0, 16, 32, 8, 12288), "kv heads"),
+                      ((0, 5, 40, 40, 12288), "intermediate size"), ((4, 4, 32, 8, 12288), "outside world")):
+        with pytest.raises(CommConfigError, match=msg):
+            TensorParallelPlan.new(*args)
