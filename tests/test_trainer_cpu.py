@@ -399,3 +399,33 @@ def test_ledger_interrupted_publication_is_invisible_and_failed_shard_aborts_eve
         return "published"
     assert run_ranks(2, body) == ["peer", "local"]
     assert os.listdir(led2) == []
+
+
+def test_tensor_parallel_trainer_ranks_identical_and_match_single_rank():
+    """Topology "tp": both ranks hold half of every projection, roll out the SAME prompts through the
+    sharded model, and apply the same update; the result equals one-rank training up to the
+    reassociation of the row-parallel sums."""
+    from ferrl_b200.models.loader import LoaderOpts, load_auto_policy
+    fix = os.path.join(os.path.dirname(__file__), "fixtures", "tiny_qwen3")
+
+    def policy(tp=None, comm=None):
+        m = load_auto_policy(fix, LoaderOpts(tp=tp) if tp else LoaderOpts())[0]
+        return LmPolicy(m, GrpoSampler(11, 1.0), comm)
+    single = Trainer(policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2))
+    single.train()
+    assert any(m.grad_norm > 0 for m in single.history)
+
+    def body(comm):
+        tr = Trainer(policy((comm.rank, comm.world_size), comm), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2),
+                     comm=comm, topology="tp")
+        tr.train()
+        return [p.detach().clone() for p in tr.params], [(m.reward_mean, m.completion_len_max) for m in tr.history]
+    res = run_ranks(2, body, timeout=120)
+    assert res[0][1] == res[1][1] == [(m.reward_mean, m.completion_len_max) for m in single.history]
+    for a, b in zip(res[0][0], res[1][0]):
+        assert torch.equal(a, b)
+    for p, q in zip(single.params, res[0][0]):
+        assert torch.allclose(p.detach(), q, atol=2e-5)
+    with pytest.raises(Exception, match="need a data-parallel launch"):
+        Trainer(policy(), ListTok(), FnReward(echo_reward), samples(),
+                cfg(steps=1, reward_group_scope="distributed_same_prompt", group_size=2), topology="tp")
