@@ -205,9 +205,12 @@ class _WriterLock:
 def save_checkpoint(checkpoints_dir: str, step: int, adapters: Sequence[torch.Tensor],
                     optimizer: Optional[OptimizerState], sampler_state: Optional[bytes],
                     binding: CheckpointBinding, *, world_size: int = 1, topology: str = "dp",
-                    fault_hook=None) -> str:
+                    fault_hook=None, continuation: Optional[dict] = None) -> str:
     """Stage, fsync, publish atomically.  ``fault_hook(stage_name)`` lets tests
-    inject host-side failures between stages."""
+    inject host-side failures between stages.  ``continuation`` (the JSON form of a
+    ``ledger.LedgerContinuation``) marks the checkpoint as the post-state of a separated
+    collector/learner chain: it is bound into the manifest and, like every checkpoint here,
+    never replaces an existing ``step-N`` (reference checkpoint.rs:1631)."""
     os.makedirs(checkpoints_dir, exist_ok=True)
     final = step_dir(checkpoints_dir, step)
     if os.path.exists(final):
@@ -250,7 +253,8 @@ def save_checkpoint(checkpoints_dir: str, step: int, adapters: Sequence[torch.Te
                                      optimizer.step if optimizer else None,
                                      len(optimizer.m) if optimizer else None,
                                      list(sampler) if sampler_state is not None else None,
-                                     binding.lora_recipe, world_size, topology, ident)
+                                     binding.lora_recipe, world_size, topology, ident,
+                                     dict(continuation) if continuation is not None else None)
             mp = os.path.join(stage, MANIFEST_FILE)
             with open(mp, "w", encoding="utf-8") as f:
                 json.dump(man.to_json(), f, sort_keys=True)
@@ -353,6 +357,31 @@ def load_checkpoint(path: str, binding: Optional[CheckpointBinding], params: Seq
         for p, t in zip(params, lc.adapters):
             p.copy_(t.to(p.dtype))
     return lc
+
+
+def latest_rollout_ledger_continuation(checkpoints_dir: str) -> Optional[tuple[int, str, dict]]:
+    """Highest ``step-N`` whose manifest carries a rollout-ledger continuation:
+    ``(step, path, continuation)``.  Ordinary checkpoints are skipped, so the two kinds are
+    discovered separately."""
+    if not os.path.isdir(checkpoints_dir):
+        return None
+    best = None
+    for name in os.listdir(checkpoints_dir):
+        m = _STEP_RE.match(name)
+        if not m:
+            continue
+        path = os.path.join(checkpoints_dir, name)
+        if not os.path.exists(os.path.join(path, MANIFEST_FILE)):
+            continue
+        man = read_manifest(path)
+        c = man.rollout_ledger_continuation
+        if c is None:
+            continue
+        if c.get("kind") != "rollout_ledger":
+            raise CheckpointMismatch(f"{path} carries a continuation of unknown kind {c.get('kind')!r}")
+        if best is None or int(m.group(1)) > best[0]:
+            best = (int(m.group(1)), path, c)
+    return best
 
 
 def latest_checkpoint(checkpoints_dir: str) -> Optional[tuple[int, str]]:

@@ -464,6 +464,12 @@ class RolloutLedgerReader:
     def identity(self, step: int) -> LedgerIdentity:
         return self._manifest(step)[2]
 
+    def consumed_ledger_sha256(self, step: int) -> str:
+        """SHA-256 of the window's commit marker (which itself records every payload's digest): the
+        value a learner binds into its continuation as "the ledger I consumed"."""
+        self._manifest(step)
+        return hashlib.sha256(open(os.path.join(self.dir, step_dir_name(step), MANIFEST), "rb").read()).hexdigest()
+
     def _payload(self, d: str, ent: dict) -> "LedgerStep":
         p = os.path.join(d, ent["payload_file"])
         try:
@@ -521,3 +527,85 @@ class RolloutLedgerReader:
                 sum(s.live_items for s in shards) != man["live_items"]:
             raise LedgerError("distributed manifest totals do not match its shards")
         return shards
+
+
+# ------------------------------------------------------------------ lineage: collector <-> learner chain
+CONTINUATION_FORMAT = 3
+CONTINUATION_KIND = "rollout_ledger"
+CONTINUATION_TP_LAYOUT = "tensor_parallel.communicator_rank_ascending.v1"
+ROOT_LINEAGE = hashlib.sha256(b"ferrl.rollout-ledger.lineage-root.v1").hexdigest()
+
+
+def _tensor_bytes(t: torch.Tensor) -> bytes:
+    t = t.detach().contiguous().cpu()
+    return t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""
+
+
+def state_digests(params: Sequence[torch.Tensor], optimizer, sampler_state: bytes, lora_recipe: Optional[str]) -> dict:
+    """Digests of the learner's mutable state: ordered tensor schema, adapter values, Adam moments
+    (independent of the step counter) and the opaque sampler state."""
+    from .checkpoint import domain_sha256, tensor_schema_sha256
+    ps = [p.detach() for p in params]
+    return {
+        "tensor_schema_sha256": tensor_schema_sha256(ps, lora_recipe),
+        "adapter_sha256": domain_sha256("ferrl.rollout-ledger.adapter.v1", [_tensor_bytes(p) for p in ps]),
+        "optimizer_sha256": domain_sha256("ferrl.rollout-ledger.optimizer.v1",
+                                          [_tensor_bytes(t) for pair in zip(optimizer.m, optimizer.v) for t in pair]),
+        "sampler_sha256": domain_sha256("ferrl.rollout-ledger.sampler.v1", [bytes(sampler_state)]),
+    }
+
+
+def lineage_sha256(parent_lineage: str, consumed_ledger_sha256: str, completed_step: int, post_state: dict) -> str:
+    """The chain link a learner produces by consuming one window: binds the parent link, the exact
+    ledger bytes consumed, the step completed and the state that resulted."""
+    from .checkpoint import domain_sha256
+    return domain_sha256("ferrl.rollout-ledger.lineage.v1",
+                         [parent_lineage.encode(), consumed_ledger_sha256.encode(), str(int(completed_step)).encode()] +
+                         [post_state[k].encode() for k in ("tensor_schema_sha256", "adapter_sha256", "optimizer_sha256",
+                                                           "sampler_sha256")])
+
+
+@dataclass
+class LedgerContinuation:
+    """What a learner hands to the next collector (and stores in its continuation checkpoint)."""
+    completed_step: int
+    policy_sha256: str
+    trainer_config_sha256: str
+    tensor_schema_sha256: str
+    adapter_sha256: str
+    optimizer_sha256: str
+    sampler_sha256: str
+    parent_lineage_sha256: str
+    consumed_ledger_sha256: str
+    lineage_sha256: str
+    world_size: int = 1
+    tensor_parallel_world_size: int = 1
+    tensor_parallel_layout: str = CONTINUATION_TP_LAYOUT
+    format_version: int = CONTINUATION_FORMAT
+    kind: str = CONTINUATION_KIND
+
+    def to_json(self) -> dict:
+        return asdict(self)
+
+    @staticmethod
+    def from_json(d: dict) -> "LedgerContinuation":
+        try:
+            c = LedgerContinuation(**d)
+        except TypeError as e:
+            raise LedgerError(f"malformed rollout-ledger continuation: {e}") from e
+        if c.kind != CONTINUATION_KIND:
+            raise LedgerError(f"continuation kind {c.kind!r} is not {CONTINUATION_KIND!r}")
+        if not 1 <= c.format_version <= CONTINUATION_FORMAT:
+            raise LedgerError(f"unsupported continuation format {c.format_version}")
+        return c
+
+    def verify(self) -> None:
+        want = lineage_sha256(self.parent_lineage_sha256, self.consumed_ledger_sha256, self.completed_step, asdict(self))
+        if want != self.lineage_sha256:
+            raise LedgerError("continuation lineage does not follow from its parent, consumed ledger and state")
+
+    def next_identity(self, optimizer_step: int) -> LedgerIdentity:
+        """Identity of the window the next collector must write on top of this state."""
+        return LedgerIdentity(self.trainer_config_sha256, self.policy_sha256, self.adapter_sha256, self.optimizer_sha256,
+                              self.sampler_sha256, self.completed_step, optimizer_step, self.tensor_schema_sha256,
+                              self.lineage_sha256)

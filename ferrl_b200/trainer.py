@@ -781,6 +781,70 @@ class Trainer:
             self.metrics_writer.append(m)
         return m
 
+    # ------------------------------------------------ collector / learner chain
+    def learner_semantic_config_sha256(self) -> str:
+        """Digest of the trainer configuration without the operational fields (run horizon, checkpoint
+        cadence, candidate logging, memory probing) that do not change one learner update."""
+        from .config import canonical_digest
+        d = self.config.to_json()
+        for k in ("steps", "checkpoint_every", "candidate_log_top_k", "gpu_memory_probe"):
+            d.pop(k, None)
+        return canonical_digest(d, b"ferrl-b200/trainer-config-learner/v1")
+
+    def ledger_identity(self, step: int, lineage: Optional[str] = None):
+        """The identity a window collected NOW, for ``step``, must carry: digests of this trainer's
+        configuration, frozen policy, adapter values, optimizer moments and sampler state."""
+        from . import ledger as L
+        dg = L.state_digests(self.params, self.opt, self.policy.sampler_state(), self.policy.lora_recipe())
+        policy = self.binding.frozen_policy_sha256 if self.binding is not None else "0" * 64
+        return L.LedgerIdentity(self.learner_semantic_config_sha256(), policy, dg["adapter_sha256"], dg["optimizer_sha256"],
+                                dg["sampler_sha256"], step, self.opt.step_t, dg["tensor_schema_sha256"],
+                                lineage or L.ROOT_LINEAGE)
+
+    def collect_window_to(self, ledger_root: str, step: int, lineage: Optional[str] = None):
+        """Collector: write window ``step`` under the identity of the current state."""
+        from . import ledger as L
+        w = L.RolloutLedgerWriter(ledger_root, self.ledger_identity(step, lineage), rank=self.comm.rank,
+                                  world_size=self.comm.world_size)
+        return self.collect_to_ledger(step, w)
+
+    def learn_window_from(self, ledger_root: str, step: int, lineage: Optional[str] = None):
+        """Learner: consume window ``step`` only if it was collected from exactly this state (identity
+        and controls are checked before anything is mutated), apply the update and return the
+        ``LedgerContinuation`` that the next collector builds on.  With a run directory the
+        post-update state is also published as a no-replace continuation checkpoint."""
+        from . import ledger as L
+        lineage = lineage or L.ROOT_LINEAGE
+        c = self.config
+        want = self.ledger_identity(step, lineage)
+        ctl = L.LedgerControls(c.grad_accum_steps, c.prompts_per_item, c.group_size, c.max_new_tokens,
+                               c.reward_group_scope, c.scale_rewards, c.eos_token_id, c.truncation_masking, 0, 0,
+                               L.f64_bits(c.tis_imp_ratio_cap) if c.tis else None)
+        reader = L.RolloutLedgerReader(ledger_root, want, ctl)
+        record = reader.read_step(step, rank=self.comm.rank)
+        consumed = reader.consumed_ledger_sha256(step)
+        self.train_from_ledger(record)
+        post = L.state_digests(self.params, self.opt, self.policy.sampler_state(), self.policy.lora_recipe())
+        cont = L.LedgerContinuation(step + 1, want.policy_sha256, want.trainer_config_sha256, post["tensor_schema_sha256"],
+                                    post["adapter_sha256"], post["optimizer_sha256"], post["sampler_sha256"], lineage,
+                                    consumed, L.lineage_sha256(lineage, consumed, step + 1, post),
+                                    world_size=self.comm.world_size if self.topology == "dp" else 1,
+                                    tensor_parallel_world_size=self.comm.world_size if self.topology == "tp" else 1)
+        if self.comm.world_size > 1:
+            self.comm.require_consensus(cont.lineage_sha256.encode(), "rollout-ledger continuation lineage")
+        if self.run_dir is not None and self.binding is not None:
+            def write():
+                if self.is_writer:
+                    save_checkpoint(self.run_dir.checkpoints_dir, step + 1, [p.detach() for p in self.params],
+                                    self.opt.state(), self.policy.sampler_state(), self.binding,
+                                    world_size=self.comm.world_size, topology=self.topology,
+                                    continuation=cont.to_json())
+            if self.comm.world_size > 1:
+                self.comm.coordinate(write, "continuation checkpoint write")
+            else:
+                write()
+        return cont
+
     # ---------------------------------------------------------- checkpoints
     def _has_checkpoint(self, step: int) -> bool:
         import os

@@ -429,3 +429,54 @@ def test_tensor_parallel_trainer_ranks_identical_and_match_single_rank():
     with pytest.raises(Exception, match="need a data-parallel launch"):
         Trainer(policy(), ListTok(), FnReward(echo_reward), samples(),
                 cfg(steps=1, reward_group_scope="distributed_same_prompt", group_size=2), topology="tp")
+
+
+def test_collector_learner_chain_is_bit_exact_and_refuses_stale_or_foreign_windows(tmp_path):
+    """Two windows through the separated path: collect from the learner's exact state, learn, hand
+    the continuation's lineage to the next collector.  The chain ends where direct training ends,
+    each link verifies, and a window collected from any other state is refused before mutation."""
+    from ferrl_b200 import ledger as L
+    from ferrl_b200.checkpoint import latest_checkpoint, latest_rollout_ledger_continuation
+    direct = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2))
+    direct.step(0)
+    direct.step(1)
+    led = str(tmp_path / "ledger")
+    rd = RunDir.create(str(tmp_path / "runs"), "chain")
+    collector = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2))
+    learner = Trainer(make_policy(), ListTok(), FnReward(lambda s, c: 0.0), samples(), cfg(steps=7, checkpoint_every=1),
+                      run_dir=rd, binding=_binding())
+    collector.binding = _binding()
+    assert learner.ledger_identity(0) == collector.ledger_identity(0)          # operational fields do not enter
+    collector.collect_window_to(led, 0)
+    c0 = learner.learn_window_from(led, 0)
+    c0.verify()
+    assert c0.parent_lineage_sha256 == L.ROOT_LINEAGE and c0.completed_step == 1
+    # the collector adopts the learner's post-state (here: by applying the same window), then continues the chain
+    collector.learn_window_from(led, 0)
+    assert collector.ledger_identity(1, c0.lineage_sha256) == c0.next_identity(learner.opt.step_t)
+    collector.collect_window_to(led, 1, c0.lineage_sha256)
+    c1 = learner.learn_window_from(led, 1, c0.lineage_sha256)
+    c1.verify()
+    assert c1.parent_lineage_sha256 == c0.lineage_sha256 and c1.consumed_ledger_sha256 != c0.consumed_ledger_sha256
+    for p, q in zip(direct.params, learner.params):
+        assert torch.equal(p.detach(), q.detach())
+    # continuation checkpoints are discovered separately and carry the chain link
+    step, path, cont = latest_rollout_ledger_continuation(rd.checkpoints_dir)
+    assert step == 2 and L.LedgerContinuation.from_json(cont).lineage_sha256 == c1.lineage_sha256
+    assert latest_checkpoint(rd.checkpoints_dir)[0] == 2
+    tampered = L.LedgerContinuation.from_json(dict(cont, consumed_ledger_sha256="0" * 64))
+    with pytest.raises(L.LedgerError, match="does not follow"):
+        tampered.verify()
+    # a learner in any other state must not consume window 1, nor window 0 under a foreign lineage
+    stale = Trainer(make_policy(seed=3), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2))
+    stale.binding = _binding()
+    before = [p.detach().clone() for p in stale.params]
+    with pytest.raises(L.LedgerError, match="adapter_sha256"):
+        stale.learn_window_from(led, 1, c0.lineage_sha256)
+    with pytest.raises(L.LedgerError, match="lineage_sha256"):
+        stale.learn_window_from(led, 0, c0.lineage_sha256)
+    other_cfg = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, clip_eps=0.3))
+    other_cfg.binding = _binding()
+    with pytest.raises(L.LedgerError, match="trainer_config_sha256"):
+        other_cfg.learn_window_from(led, 0)
+    assert all(torch.equal(a, b.detach()) for a, b in zip(before, stale.params))
