@@ -198,6 +198,11 @@ class Trainer:
         self.params = policy.trainable_params()
         if not self.params:
             raise TrainerError("the policy exposes no trainable tensors")
+        uses_kl = config.beta > 0 or config.beta_schedule is not None
+        if uses_kl and policy.lora_recipe() == "full_ft":
+            # the KL reference is "this model with its adapters switched off"; with every base tensor
+            # trainable there is no frozen reference left, and the penalty would silently be zero
+            raise TrainerError("a KL penalty (beta > 0) needs a frozen reference policy; full fine-tuning has none")
         self.opt = FerrlAdamW(self.params, AdamWParams(config.lr, config.adam_beta1, config.adam_beta2, adam_eps,
                                                        config.weight_decay))
         self.fused_dp_step = fused_dp_step
