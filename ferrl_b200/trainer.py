@@ -727,10 +727,14 @@ class Trainer:
                                L.f64_bits(c.lr_at(step)), L.f64_bits(c.beta_at(step)), cap)
         groups = [L.LedgerGroup.from_collected(j, g) for j, gs in collected for g in gs]
         tokens = sum(g.completion_tokens for _, gs in collected for g in gs)
-        st = L.LedgerStep(step, self.comm.rank, self.comm.world_size, ctl, tokens,
+        st = L.LedgerStep(step, self.dp_rank, self.dp_world, ctl, tokens,
                           sum(1 for _, gs in collected for g in gs if g.live), list(self.policy.sampler_state()), groups)
         if self.comm.world_size == 1:
             writer.write_step(st)
+            return st
+        if self.topology == "tp":
+            # every tensor-parallel rank holds the same window: it is one artifact, written by rank 0
+            self.comm.coordinate(lambda: writer.write_step(st) if self.is_writer else None, "ledger write")
             return st
         # rank 0 draws the stage nonce and creates the hidden stage; every rank writes its shard
         # into it; the outcome of each phase is agreed before anyone moves on, and the stage is
@@ -759,7 +763,7 @@ class Trainer:
         c = self.config
         if record.controls.group_size != c.group_size or record.controls.completion_width != c.max_new_tokens:
             raise TrainerError("ledger step was collected under different group_size / max_new_tokens")
-        if record.world_size != self.comm.world_size or record.rank != self.comm.rank:
+        if record.world_size != self.dp_world or record.rank != self.dp_rank:
             raise TrainerError("ledger shard belongs to a different rank/world")
         if record.controls.tis_imp_ratio_cap_bits != (L.f64_bits(c.tis_imp_ratio_cap) if c.tis else None):
             raise TrainerError("ledger step was collected under a different truncated-importance-sampling cap")
@@ -809,8 +813,8 @@ class Trainer:
     def collect_window_to(self, ledger_root: str, step: int, lineage: Optional[str] = None):
         """Collector: write window ``step`` under the identity of the current state."""
         from . import ledger as L
-        w = L.RolloutLedgerWriter(ledger_root, self.ledger_identity(step, lineage), rank=self.comm.rank,
-                                  world_size=self.comm.world_size)
+        w = L.RolloutLedgerWriter(ledger_root, self.ledger_identity(step, lineage), rank=self.dp_rank,
+                                  world_size=self.dp_world)
         return self.collect_to_ledger(step, w)
 
     def learn_window_from(self, ledger_root: str, step: int, lineage: Optional[str] = None):
@@ -826,7 +830,7 @@ class Trainer:
                                c.reward_group_scope, c.scale_rewards, c.eos_token_id, c.truncation_masking, 0, 0,
                                L.f64_bits(c.tis_imp_ratio_cap) if c.tis else None)
         reader = L.RolloutLedgerReader(ledger_root, want, ctl)
-        record = reader.read_step(step, rank=self.comm.rank)
+        record = reader.read_step(step, rank=self.dp_rank)
         consumed = reader.consumed_ledger_sha256(step)
         self.train_from_ledger(record)
         post = L.state_digests(self.params, self.opt, self.policy.sampler_state(), self.policy.lora_recipe())

@@ -120,3 +120,50 @@ def test_rank0_writes_the_only_checkpoint_and_dp_resume_is_bit_exact(tmp_path):
     for r in range(2):
         for p, q in zip(straight[r][1], resumed[r][1]):
             assert torch.equal(p, q)
+
+
+def test_tensor_parallel_ledger_run_equals_direct_run_and_topology_mismatch_is_refused(tmp_path):
+    fix = os.path.join(FIX, "tiny_qwen3")
+    led = str(tmp_path / "ledger")
+    binding = CheckpointBinding("a" * 64, "b" * 64, None)
+
+    def tp_trainer(comm, **kw):
+        m = load_auto_policy(fix, LoaderOpts(tp=(comm.rank, comm.world_size)))[0]
+        pol = LmPolicy(m, GrpoSampler(11, 1.0), comm)
+        b = CheckpointBinding(binding.frozen_policy_sha256, binding.trainer_config_sha256, pol.lora_recipe())
+        return Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=2, checkpoint_every=1), comm=comm,
+                       topology="tp", binding=b, **kw)
+
+    def direct(comm):
+        tr = tp_trainer(comm)
+        tr.step(0)
+        tr.step(1)
+        return [p.detach().clone() for p in tr.params]
+
+    def separated(comm):
+        if comm.rank == 0:
+            RunDir.create(str(tmp_path / "runs"), "r")
+        comm.barrier()
+        collector, learner = tp_trainer(comm), tp_trainer(comm, run_dir=RunDir.open(str(tmp_path / "runs" / "r")))
+        collector.collect_window_to(led, 0)
+        c0 = learner.learn_window_from(led, 0)
+        collector.learn_window_from(led, 0)
+        collector.collect_window_to(led, 1, c0.lineage_sha256)
+        c1 = learner.learn_window_from(led, 1, c0.lineage_sha256)
+        return [p.detach().clone() for p in learner.params], (c1.tensor_parallel_world_size, c1.world_size, c1.lineage_sha256)
+    want = run_ranks(2, direct, timeout=120)
+    got = run_ranks(2, separated, timeout=120)
+    assert got[0][1] == got[1][1] and got[0][1][:2] == (2, 1)
+    for r in range(2):
+        for p, q in zip(want[r], got[r][0]):
+            assert torch.equal(p, q)
+    # the continuation checkpoint was written for a tensor-parallel world of two: a data-parallel
+    # resume of it is refused before anything is touched
+    from ferrl_b200.checkpoint import CheckpointMismatch, latest_checkpoint, prepare_checkpoint
+    step, path = latest_checkpoint(str(tmp_path / "runs" / "r" / "checkpoints"))
+    assert step == 2
+    with pytest.raises(CheckpointMismatch, match="topology"):
+        prepare_checkpoint(path, None, world_size=2, topology="dp")
+    with pytest.raises(CheckpointMismatch, match="world size"):
+        prepare_checkpoint(path, None, world_size=4, topology="tp")
+    assert prepare_checkpoint(path, None, world_size=2, topology="tp").manifest.rollout_ledger_continuation["kind"] == "rollout_ledger"
