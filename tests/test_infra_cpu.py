@@ -846,3 +846,26 @@ def test_cli_audit_pairs_reference_and_candidate_per_block_and_honours_inspectio
     assert cli.main(["audit", "--run-dir", str(run), "--out", str(tmp_path / "audit-sus"), "--source-inspection", "suspicious",
                      "--source-inspection-notes", "reads /proc/self/environ"]) == 1
     assert "rejected: source inspection found" in open(tmp_path / "audit-sus" / "artifact-report.md").read()
+
+
+def test_cli_trimul_baseline_times_the_packaged_reference_submission(tmp_path, capsys, monkeypatch):
+    import ferrl_b200.cli as cli
+    from ferrl_b200.rewards.trimul import TrimulCase, TrimulReward, default_eval_dir
+    from ferrl_b200.sandbox import FakeSandbox, SandboxOutcome, Verdict
+    seen = []
+
+    def fake(spec):
+        seen.append(open(spec.binds[2].host).read())
+        log = "test-count: 1\ntest.0.status: pass\ncheck: pass\ntest-exit: 0\nbenchmark-count: 2\nbenchmark.0.mean: 1000000\nbenchmark.1.mean: 4000000\nbenchmark-exit: 0\n"
+        return SandboxOutcome(Verdict.EXITED, 0, log.encode(), b"")
+    monkeypatch.setattr(cli, "_trimul_reward", lambda cfg: TrimulReward(FakeSandbox(fake), "img", default_eval_dir(),
+                                                                         [TrimulCase(32, 1, 16, 8, 5)]))
+    cfgp = tmp_path / "run.json"
+    cfgp.write_text(json.dumps({"task": "trimul", "model_dir": "x", "trainer": {"steps": 1, "group_size": 2},
+                                "trimul": {"prompt_path": "p", "image": "img"}}))
+    assert cli.main(["trimul-baseline", "--config", str(cfgp)]) == 0
+    out = json.loads(capsys.readouterr().out.strip().splitlines()[-1])
+    assert out["correct"] and out["baseline_ns"] == pytest.approx(2000000.0)       # geometric mean of the cases
+    assert seen[0] == open(os.path.join(default_eval_dir(), "reference_submission.py")).read()
+    with pytest.raises(SystemExit):
+        cli.main(["verifier-executor", "--socket", str(tmp_path / "s.sock")])      # --client-uid is mandatory
