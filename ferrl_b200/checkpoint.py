@@ -38,7 +38,10 @@ from .optim import OptimizerState
 ADAPTER_FILE = "adapter.safetensors"
 OPTIMIZER_FILE = "optimizer.safetensors"
 MANIFEST_FILE = "manifest.json"
-LOCK_SUFFIX = ".lock"
+LOCK_SUFFIX = ".writer-lock"                   # reference checkpoint.rs WRITER_LOCK_SUFFIX
+TOPOLOGY_FILE = "topology.json"                # readable copy of what trainer_config_sha256 also binds
+ORDINARY_KIND = "ordinary"
+_DOMAIN = "ferrl.ordinary-checkpoint."         # digest domains of the reference (checkpoint.rs:447-540)
 FORMAT_VERSION = 4
 MIN_READ_VERSION = 4
 _STEP_RE = re.compile(r"^step-(\d+)$")
@@ -86,11 +89,70 @@ def moment_key(kind: str, i: int) -> str:
     return f"{kind}.{i:05d}"
 
 
+_CANDLE_DTYPE = {torch.float32: "f32", torch.float64: "f64", torch.bfloat16: "bf16", torch.float16: "f16",
+                 torch.uint8: "u8", torch.int64: "i64", torch.int32: "i32", torch.int16: "i16"}
+
+
+def _compact_json(obj) -> bytes:
+    """The byte form ``serde_json::to_vec`` produces: no whitespace, keys in insertion order,
+    UTF-8 written raw."""
+    return json.dumps(obj, separators=(",", ":"), ensure_ascii=False).encode("utf-8")
+
+
+def _dtype_name(dt: torch.dtype) -> str:
+    try:
+        return _CANDLE_DTYPE[dt]
+    except KeyError:
+        raise CheckpointMismatch(f"dtype {dt} has no checkpoint schema name") from None
+
+
 def tensor_schema_sha256(tensors: Sequence[torch.Tensor], lora_recipe: Optional[str]) -> str:
-    fields = [(lora_recipe or "").encode()]
-    for t in tensors:
-        fields.append(json.dumps([list(t.shape), str(t.dtype)]).encode())
-    return domain_sha256("ferrl.checkpoint.tensor-schema.v1", fields)
+    """Digest of ``(recipe, [(key, dims, dtype), ...])`` as compact JSON (reference
+    checkpoint.rs ``tensor_schema_sha256``): shape-aliased recipes get different identities."""
+    schema = [[var_key(i), [int(d) for d in t.shape], _dtype_name(t.dtype)] for i, t in enumerate(tensors)]
+    return domain_sha256(_DOMAIN + "tensor-schema.v1", [_compact_json([lora_recipe, schema])])
+
+
+def adapter_payload_sha256(data: bytes) -> str:
+    return domain_sha256(_DOMAIN + "adapter.v1", [data])
+
+
+def optimizer_payload_sha256(step_t: int, data: bytes) -> str:
+    """The Adam bias-correction counter is bound into the optimizer digest, so an edited
+    ``optimizer_step_t`` cannot pass verification."""
+    if not 0 <= int(step_t) < 1 << 64:
+        raise CheckpointMismatch("optimizer step_t does not fit the checkpoint's u64 identity")
+    return domain_sha256(_DOMAIN + "optimizer.v1", [struct.pack("<Q", int(step_t)), data])
+
+
+def sampler_payload_sha256(data: bytes) -> str:
+    return domain_sha256(_DOMAIN + "sampler.v1", [data])
+
+
+def state_envelope_sha256(format_version: int, kind: str, step: int, num_vars: int, lora_recipe: Optional[str],
+                          optimizer_step_t: int, optimizer_num_vars: int, ident: dict) -> str:
+    """Root digest over version/kind, step, counts, recipe, the two immutable identities and every
+    mutable payload digest, in the reference's field order (checkpoint.rs ``OrdinaryCheckpointEnvelope``)."""
+    env = {"format_version": int(format_version), "kind": kind, "step": int(step), "num_vars": int(num_vars),
+           "lora_recipe": lora_recipe, "optimizer_step_t": int(optimizer_step_t),
+           "optimizer_num_vars": int(optimizer_num_vars)}
+    for k in ("frozen_policy_sha256", "trainer_config_sha256", "tensor_schema_sha256", "adapter_sha256",
+              "optimizer_sha256", "sampler_sha256"):
+        env[k] = ident[k]
+    return domain_sha256(_DOMAIN + "state-envelope.v1", [_compact_json(env)])
+
+
+def bound_trainer_config_sha256(trainer_config_sha256: str, world_size: int, topology: str) -> str:
+    """The manifest's ``trainer_config_sha256`` covers the learner-semantic config AND the topology
+    (the reference's manifest has no world/topology fields and rejects unknown ones): this is the
+    caller's config digest extended by world size and topology name."""
+    return domain_sha256(_DOMAIN + "trainer-config-topology.v1",
+                         [trainer_config_sha256.encode(), topology.encode(), struct.pack("<Q", int(world_size))])
+
+
+def _read_bytes(path: str) -> bytes:
+    with open(path, "rb") as f:
+        return f.read()
 
 
 def _file_sha256(path: str) -> str:
@@ -136,6 +198,9 @@ def _load_tensors(path: str) -> dict:
 
 @dataclass
 class CheckpointManifest:
+    """Field set of the reference's ``CheckpointManifest`` (checkpoint.rs:370-412), which rejects
+    unknown fields; world size and topology are therefore not manifest fields (see
+    ``bound_trainer_config_sha256`` and the ``topology.json`` side file)."""
     format_version: int
     step: int
     num_vars: int
@@ -143,13 +208,15 @@ class CheckpointManifest:
     optimizer_num_vars: Optional[int] = None
     sampler_state: Optional[list] = None      # bytes as a list of ints (JSON friendly)
     lora_recipe: Optional[str] = None
-    world_size: int = 1
-    topology: str = "dp"
-    ordinary_checkpoint: Optional[dict] = None
     rollout_ledger_continuation: Optional[dict] = None
+    ordinary_checkpoint: Optional[dict] = None
+    world_size: int = 1                       # from topology.json, not serialised into manifest.json
+    topology: str = "dp"
 
     FIELDS = ("format_version", "step", "num_vars", "optimizer_step_t", "optimizer_num_vars", "sampler_state",
-              "lora_recipe", "world_size", "topology", "ordinary_checkpoint", "rollout_ledger_continuation")
+              "lora_recipe", "rollout_ledger_continuation", "ordinary_checkpoint")
+    IDENTITY_FIELDS = ("kind", "frozen_policy_sha256", "trainer_config_sha256", "tensor_schema_sha256",
+                       "adapter_sha256", "optimizer_sha256", "sampler_sha256", "state_envelope_sha256")
 
     def to_json(self) -> dict:
         return {k: getattr(self, k) for k in self.FIELDS}
@@ -164,6 +231,15 @@ class CheckpointManifest:
         for req in ("format_version", "step", "num_vars"):
             if req not in d:
                 raise CheckpointMismatch(f"manifest is missing {req}")
+        for k in ("format_version", "step", "num_vars"):
+            if not isinstance(d[k], int) or isinstance(d[k], bool) or d[k] < 0:
+                raise CheckpointMismatch(f"manifest field {k} must be a non-negative integer")
+        ident = d.get("ordinary_checkpoint")
+        if ident is not None:
+            if not isinstance(ident, dict) or set(ident) != set(CheckpointManifest.IDENTITY_FIELDS):
+                raise CheckpointMismatch("ordinary_checkpoint identity has missing or unknown fields")
+            for k in CheckpointManifest.IDENTITY_FIELDS[1:]:
+                _validate_sha(k, ident[k])
         return CheckpointManifest(**d)
 
     def sampler_bytes(self) -> Optional[bytes]:
@@ -235,26 +311,28 @@ def save_checkpoint(checkpoints_dir: str, step: int, adapters: Sequence[torch.Te
             if fault_hook:
                 fault_hook("optimizer_written")
             sampler = sampler_state or b""
+            step_t = optimizer.step if optimizer else 0
+            n_opt = len(optimizer.m) if optimizer else 0
             ident = {
-                "kind": "ordinary",
+                "kind": ORDINARY_KIND,
                 "frozen_policy_sha256": binding.frozen_policy_sha256,
-                "trainer_config_sha256": binding.trainer_config_sha256,
+                "trainer_config_sha256": bound_trainer_config_sha256(binding.trainer_config_sha256, world_size, topology),
                 "tensor_schema_sha256": tensor_schema_sha256(adapters, binding.lora_recipe),
-                "adapter_sha256": _file_sha256(ap),
-                "optimizer_sha256": _file_sha256(op),
-                "sampler_sha256": domain_sha256("ferrl.checkpoint.sampler.v1", [sampler]),
+                "adapter_sha256": adapter_payload_sha256(_read_bytes(ap)),
+                "optimizer_sha256": optimizer_payload_sha256(step_t, _read_bytes(op)),
+                "sampler_sha256": sampler_payload_sha256(sampler),
             }
-            ident["state_envelope_sha256"] = domain_sha256(
-                "ferrl.checkpoint.state-envelope.v1",
-                [str(step).encode(), str(optimizer.step if optimizer else 0).encode(),
-                 ident["adapter_sha256"].encode(), ident["optimizer_sha256"].encode(),
-                 ident["sampler_sha256"].encode(), str(world_size).encode(), topology.encode()])
-            man = CheckpointManifest(FORMAT_VERSION, step, len(adapters),
-                                     optimizer.step if optimizer else None,
-                                     len(optimizer.m) if optimizer else None,
+            ident["state_envelope_sha256"] = state_envelope_sha256(
+                FORMAT_VERSION, ORDINARY_KIND, step, len(adapters), binding.lora_recipe, step_t, n_opt, ident)
+            man = CheckpointManifest(FORMAT_VERSION, step, len(adapters), step_t, n_opt,
                                      list(sampler) if sampler_state is not None else None,
-                                     binding.lora_recipe, world_size, topology, ident,
-                                     dict(continuation) if continuation is not None else None)
+                                     binding.lora_recipe,
+                                     dict(continuation) if continuation is not None else None, ident)
+            tp = os.path.join(stage, TOPOLOGY_FILE)
+            with open(tp, "w", encoding="utf-8") as f:
+                json.dump({"world_size": int(world_size), "topology": topology}, f, sort_keys=True)
+                f.flush()
+                os.fsync(f.fileno())
             mp = os.path.join(stage, MANIFEST_FILE)
             with open(mp, "w", encoding="utf-8") as f:
                 json.dump(man.to_json(), f, sort_keys=True)
@@ -279,45 +357,66 @@ def read_manifest(path: str) -> CheckpointManifest:
     mp = os.path.join(path, MANIFEST_FILE)
     try:
         with open(mp, encoding="utf-8") as f:
-            return CheckpointManifest.from_json(json.load(f))
+            man = CheckpointManifest.from_json(json.load(f))
     except FileNotFoundError:
         raise CheckpointMismatch(f"{path} has no manifest (incomplete checkpoint)") from None
     except json.JSONDecodeError as e:
         raise CheckpointMismatch(f"{mp} is not valid JSON: {e}") from e
     except TypeError as e:
         raise CheckpointMismatch(f"{mp} is malformed: {e}") from e
+    tp = os.path.join(path, TOPOLOGY_FILE)
+    if os.path.exists(tp):
+        try:
+            with open(tp, encoding="utf-8") as f:
+                t = json.load(f)
+            man.world_size, man.topology = int(t["world_size"]), str(t["topology"])
+        except (ValueError, KeyError, TypeError) as e:
+            raise CheckpointMismatch(f"{tp} is malformed: {e}") from e
+    return man
 
 
 def prepare_checkpoint(path: str, binding: Optional[CheckpointBinding], expected_shapes: Optional[Sequence] = None,
                        *, world_size: Optional[int] = None, topology: Optional[str] = None) -> LoadedCheckpoint:
-    """Read and verify everything; touches no live state."""
+    """Read and verify everything; touches no live state.  Order: version and kind, the state
+    envelope (so an edited step / counter / count field fails before any payload is read), payload
+    digests, binding, topology, tensor keys + schema + shapes (adapters and both Adam moments)."""
     man = read_manifest(path)
     if not (MIN_READ_VERSION <= man.format_version <= FORMAT_VERSION):
         raise CheckpointMismatch(f"unsupported checkpoint format {man.format_version}")
     ident = man.ordinary_checkpoint
     if ident is None:
         raise CheckpointMismatch("manifest carries no checkpoint identity")
+    if ident.get("kind") != ORDINARY_KIND:
+        raise CheckpointMismatch(f"checkpoint kind {ident.get('kind')!r} is not {ORDINARY_KIND!r}")
+    if man.optimizer_step_t is None or man.optimizer_num_vars is None:
+        raise CheckpointMismatch("ordinary checkpoint is missing optimizer_step_t / optimizer_num_vars")
+    if state_envelope_sha256(man.format_version, ident["kind"], man.step, man.num_vars, man.lora_recipe,
+                             man.optimizer_step_t, man.optimizer_num_vars, ident) != ident["state_envelope_sha256"]:
+        raise CheckpointMismatch("ordinary checkpoint state-envelope digest mismatch")
     ap, op = os.path.join(path, ADAPTER_FILE), os.path.join(path, OPTIMIZER_FILE)
-    for p, key in ((ap, "adapter_sha256"), (op, "optimizer_sha256")):
+    for p in (ap, op):
         if not os.path.exists(p):
             raise CheckpointMismatch(f"missing payload {p}")
-        if _file_sha256(p) != ident.get(key):
-            raise CheckpointMismatch(f"{os.path.basename(p)} does not match its recorded SHA-256")
+    if adapter_payload_sha256(_read_bytes(ap)) != ident["adapter_sha256"]:
+        raise CheckpointMismatch(f"{ADAPTER_FILE} does not match its recorded SHA-256")
+    if optimizer_payload_sha256(man.optimizer_step_t, _read_bytes(op)) != ident["optimizer_sha256"]:
+        raise CheckpointMismatch(f"{OPTIMIZER_FILE} (with its step counter) does not match its recorded SHA-256")
     sampler = man.sampler_bytes() or b""
-    if domain_sha256("ferrl.checkpoint.sampler.v1", [sampler]) != ident.get("sampler_sha256"):
+    if sampler_payload_sha256(sampler) != ident["sampler_sha256"]:
         raise CheckpointMismatch("sampler state does not match its recorded digest")
-    if binding is not None:
-        if ident.get("frozen_policy_sha256") != binding.frozen_policy_sha256:
-            raise CheckpointMismatch("checkpoint was written for a different frozen policy")
-        if ident.get("trainer_config_sha256") != binding.trainer_config_sha256:
-            raise CheckpointMismatch("checkpoint was written under a different trainer config")
-        if man.lora_recipe != binding.lora_recipe:
-            raise CheckpointMismatch(f"checkpoint LoRA recipe {man.lora_recipe!r} differs from "
-                                     f"the live recipe {binding.lora_recipe!r}")
     if world_size is not None and man.world_size != world_size:
         raise CheckpointMismatch(f"checkpoint world size {man.world_size} differs from the live world {world_size}")
     if topology is not None and man.topology != topology:
         raise CheckpointMismatch(f"checkpoint topology {man.topology!r} differs from {topology!r}")
+    if binding is not None:
+        if ident["frozen_policy_sha256"] != binding.frozen_policy_sha256:
+            raise CheckpointMismatch("checkpoint was written for a different frozen policy")
+        if ident["trainer_config_sha256"] != bound_trainer_config_sha256(binding.trainer_config_sha256,
+                                                                        man.world_size, man.topology):
+            raise CheckpointMismatch("checkpoint was written under a different trainer config or topology")
+        if man.lora_recipe != binding.lora_recipe:
+            raise CheckpointMismatch(f"checkpoint LoRA recipe {man.lora_recipe!r} differs from "
+                                     f"the live recipe {binding.lora_recipe!r}")
     at = _load_tensors(ap)
     adapters = []
     for i in range(man.num_vars):
@@ -327,7 +426,7 @@ def prepare_checkpoint(path: str, binding: Optional[CheckpointBinding], expected
         adapters.append(at[k])
     if len(at) != man.num_vars:
         raise CheckpointMismatch("adapter payload has unexpected extra tensors")
-    if tensor_schema_sha256(adapters, man.lora_recipe) != ident.get("tensor_schema_sha256"):
+    if tensor_schema_sha256(adapters, man.lora_recipe) != ident["tensor_schema_sha256"]:
         raise CheckpointMismatch("tensor schema digest mismatch")
     if expected_shapes is not None:
         if len(expected_shapes) != len(adapters):
@@ -336,16 +435,24 @@ def prepare_checkpoint(path: str, binding: Optional[CheckpointBinding], expected
             if tuple(t.shape) != tuple(s):
                 raise CheckpointMismatch(f"tensor {i} shape {tuple(t.shape)} differs from live {tuple(s)}")
     opt = None
-    if man.optimizer_num_vars is not None:
-        ot = _load_tensors(op)
+    ot = _load_tensors(op)
+    n_opt = man.optimizer_num_vars
+    if len(ot) != 2 * n_opt:
+        raise CheckpointMismatch(f"optimizer payload holds {len(ot)} tensors, manifest promises {2 * n_opt}")
+    if n_opt not in (0, man.num_vars):
+        raise CheckpointMismatch(f"optimizer covers {n_opt} tensors, the adapter has {man.num_vars}")
+    if n_opt:
         m, v = [], []
-        for i in range(man.optimizer_num_vars):
+        for i in range(n_opt):
             for kind, dst in (("m", m), ("v", v)):
                 k = moment_key(kind, i)
                 if k not in ot:
                     raise CheckpointMismatch(f"optimizer payload is missing {k}")
+                if tuple(ot[k].shape) != tuple(adapters[i].shape):
+                    raise CheckpointMismatch(f"optimizer tensor {k} shape {tuple(ot[k].shape)} differs from "
+                                             f"its adapter tensor {tuple(adapters[i].shape)}")
                 dst.append(ot[k])
-        opt = OptimizerState(int(man.optimizer_step_t or 0), m, v)
+        opt = OptimizerState(int(man.optimizer_step_t), m, v)
     return LoadedCheckpoint(man, adapters, opt, path)
 
 
@@ -385,7 +492,9 @@ def latest_rollout_ledger_continuation(checkpoints_dir: str) -> Optional[tuple[i
 
 
 def latest_checkpoint(checkpoints_dir: str) -> Optional[tuple[int, str]]:
-    """Highest complete ``step-N``; a newer malformed final directory is an error."""
+    """Highest complete ordinary ``step-N``; a newer malformed final directory is an error.
+    Directories whose manifest carries a rollout-ledger continuation belong to the separated
+    collector/learner chain and are discovered by ``latest_rollout_ledger_continuation`` only."""
     if not os.path.isdir(checkpoints_dir):
         return None
     steps = []
@@ -393,14 +502,15 @@ def latest_checkpoint(checkpoints_dir: str) -> Optional[tuple[int, str]]:
         m = _STEP_RE.match(name)
         if m and os.path.isdir(os.path.join(checkpoints_dir, name)):
             steps.append(int(m.group(1)))
-    if not steps:
-        return None
-    best = max(steps)
-    path = step_dir(checkpoints_dir, best)
-    man = read_manifest(path)  # raises CheckpointMismatch if the newest is malformed
-    if man.step != best:
-        raise CheckpointMismatch(f"{path} manifest records step {man.step}")
-    return best, path
+    for best in sorted(steps, reverse=True):
+        path = step_dir(checkpoints_dir, best)
+        man = read_manifest(path)  # raises CheckpointMismatch if the newest is malformed
+        if man.rollout_ledger_continuation is not None:
+            continue
+        if man.step != best:
+            raise CheckpointMismatch(f"{path} manifest records step {man.step}")
+        return best, path
+    return None
 
 
 def save_adapter(path: str, adapters: Sequence[torch.Tensor], lora_recipe: Optional[str] = None) -> None:

@@ -464,17 +464,23 @@ class Trainer:
         # every rank must have finished (or failed) its local backward before anyone enters the
         # gradient collective; a failure anywhere raises on all ranks here, not at a timeout
         self._rendezvous(local_backward, "backward")
-        # a rank with no live item still joins the reduction with zeros
-        for p in self.params:
-            if p.grad is None and not live:
-                p.grad = torch.zeros_like(p)
         self._phase("grad_reduce_optimizer")
         world = self.comm.world_size
         if self.fused_dp_step is not None:
             missing = self.fused_dp_step.missing() if live else []
             nonfinite = []                       # counted inside the kernel, world-wide
         else:
+            # a rank with live items but an absent gradient is a coverage failure; a rank with no live
+            # item simply contributes zeros.  Either way every slot is materialised with zeros so that
+            # all ranks enter the same tensor collective with the same shapes, and the failure is
+            # reported through the uncovered count on every rank (reference trainer.rs
+            # materialize_zero_grad_slots + reduce_accumulated_grads).
             missing, nonfinite = grad_coverage(self.params)
+            if not live:
+                missing = []
+            for p in self.params:
+                if p.grad is None:
+                    p.grad = torch.zeros_like(p)
         uncovered = float(len(missing) + len(nonfinite))
         if self.fused_dp_step is not None:
             # fused peer-memory path: all-reduce + clip + AdamW in one pass
@@ -490,8 +496,7 @@ class Trainer:
                 self.policy.on_params_updated()
             return
         if world > 1:
-            if not missing:
-                self.comm.all_reduce_sum([p.grad for p in self.params])
+            self.comm.all_reduce_sum([p.grad for p in self.params])
             uncovered = self.comm.all_reduce_scalar_sum(uncovered)
         if uncovered > 0:
             raise GradCoverageError(

@@ -159,8 +159,10 @@ def test_tensor_parallel_ledger_run_equals_direct_run_and_topology_mismatch_is_r
             assert torch.equal(p, q)
     # the continuation checkpoint was written for a tensor-parallel world of two: a data-parallel
     # resume of it is refused before anything is touched
-    from ferrl_b200.checkpoint import CheckpointMismatch, latest_checkpoint, prepare_checkpoint
-    step, path = latest_checkpoint(str(tmp_path / "runs" / "r" / "checkpoints"))
+    from ferrl_b200.checkpoint import (CheckpointMismatch, latest_checkpoint, latest_rollout_ledger_continuation,
+                                       prepare_checkpoint)
+    assert latest_checkpoint(str(tmp_path / "runs" / "r" / "checkpoints")) is None
+    step, path, _ = latest_rollout_ledger_continuation(str(tmp_path / "runs" / "r" / "checkpoints"))
     assert step == 2
     with pytest.raises(CheckpointMismatch, match="topology"):
         prepare_checkpoint(path, None, world_size=2, topology="dp")

@@ -150,8 +150,11 @@ def _ck(tmp, step=3, adapters=None):
 
 def test_checkpoint_round_trip_and_layout(tmp_path):
     path, adapters, b = _ck(tmp_path)
-    assert sorted(os.listdir(path)) == ["adapter.safetensors", "manifest.json", "optimizer.safetensors"]
+    assert sorted(os.listdir(path)) == ["adapter.safetensors", "manifest.json", "optimizer.safetensors", "topology.json"]
     man = json.load(open(os.path.join(path, "manifest.json")))
+    # exactly the reference manifest's field set (its decoder rejects unknown fields)
+    assert sorted(man) == sorted(["format_version", "step", "num_vars", "optimizer_step_t", "optimizer_num_vars",
+                                  "sampler_state", "lora_recipe", "rollout_ledger_continuation", "ordinary_checkpoint"])
     assert man["format_version"] == 4 and man["step"] == 3 and man["num_vars"] == 2 and man["optimizer_step_t"] == 5
     from safetensors.torch import load_file
     assert sorted(load_file(os.path.join(path, "adapter.safetensors"))) == ["lora.00000", "lora.00001"]
@@ -184,6 +187,96 @@ def test_checkpoint_corruption_and_binding_are_rejected_before_mutation(tmp_path
     assert torch.equal(params[0].detach(), torch.zeros(4, 8))
     with pytest.raises(CK.CheckpointMismatch):
         CK.CheckpointBinding("xyz", "b" * 64)
+
+
+def _ref_domain(domain, fields):
+    """Independent restatement of the reference's length-prefixed, domain-separated SHA-256
+    (crates/ferrl/src/checkpoint.rs:447-456)."""
+    import hashlib
+    import struct
+    h = hashlib.sha256()
+    h.update(struct.pack("<Q", len(domain)) + domain.encode())
+    for f in fields:
+        h.update(struct.pack("<Q", len(f)) + f)
+    return h.hexdigest()
+
+
+def test_checkpoint_identity_follows_the_reference_formulas(tmp_path):
+    """Golden manifest: every digest of the identity block recomputed from the reference's
+    formulas (domains ferrl.ordinary-checkpoint.*, step_t bound into the optimizer digest, schema
+    as JSON of (recipe, [(key, dims, dtype)]), envelope as the struct's compact JSON)."""
+    import struct
+    path, adapters, b = _ck(tmp_path)
+    man = json.load(open(os.path.join(path, "manifest.json")))
+    ident = man["ordinary_checkpoint"]
+    raw_a = open(os.path.join(path, "adapter.safetensors"), "rb").read()
+    raw_o = open(os.path.join(path, "optimizer.safetensors"), "rb").read()
+    assert ident["kind"] == "ordinary"
+    assert ident["adapter_sha256"] == _ref_domain("ferrl.ordinary-checkpoint.adapter.v1", [raw_a])
+    assert ident["optimizer_sha256"] == _ref_domain("ferrl.ordinary-checkpoint.optimizer.v1", [struct.pack("<Q", 5), raw_o])
+    assert ident["sampler_sha256"] == _ref_domain("ferrl.ordinary-checkpoint.sampler.v1", [b"sampler"])
+    schema = '["lora:r4",[["lora.00000",[4,8],"f32"],["lora.00001",[8,4],"f32"]]]'
+    assert ident["tensor_schema_sha256"] == _ref_domain("ferrl.ordinary-checkpoint.tensor-schema.v1", [schema.encode()])
+    env = ('{"format_version":4,"kind":"ordinary","step":3,"num_vars":2,"lora_recipe":"lora:r4","optimizer_step_t":5,'
+           '"optimizer_num_vars":2,"frozen_policy_sha256":"%s","trainer_config_sha256":"%s","tensor_schema_sha256":"%s",'
+           '"adapter_sha256":"%s","optimizer_sha256":"%s","sampler_sha256":"%s"}'
+           % ("a" * 64, ident["trainer_config_sha256"], ident["tensor_schema_sha256"], ident["adapter_sha256"],
+              ident["optimizer_sha256"], ident["sampler_sha256"]))
+    assert ident["state_envelope_sha256"] == _ref_domain("ferrl.ordinary-checkpoint.state-envelope.v1", [env.encode()])
+    # world size and topology live inside trainer_config_sha256, not in manifest fields
+    assert ident["trainer_config_sha256"] == CK.bound_trainer_config_sha256("b" * 64, 2, "dp") != "b" * 64
+    assert CK.LOCK_SUFFIX == ".writer-lock"
+
+
+def test_checkpoint_tampered_counters_kind_and_optimizer_payload_are_rejected(tmp_path):
+    path, adapters, b = _ck(tmp_path)
+    mp = os.path.join(path, "manifest.json")
+    good = json.load(open(mp))
+    params = [torch.nn.Parameter(torch.zeros(4, 8)), torch.nn.Parameter(torch.ones(8, 4))]
+
+    def rewrite(mut):
+        man = json.loads(json.dumps(good))
+        mut(man)
+        json.dump(man, open(mp, "w"))
+    for mut in (lambda m: m.__setitem__("optimizer_step_t", 6),          # wrong Adam bias correction on resume
+                lambda m: m.__setitem__("optimizer_num_vars", 1),
+                lambda m: m.__setitem__("num_vars", 1),
+                lambda m: m.__setitem__("step", 4),
+                lambda m: m["ordinary_checkpoint"].__setitem__("kind", "rollout_ledger"),
+                lambda m: m.__setitem__("world_size", 2)):                # not a manifest field
+        rewrite(mut)
+        with pytest.raises(CK.CheckpointMismatch):
+            CK.load_checkpoint(path, b, params)
+        assert torch.equal(params[0].detach(), torch.zeros(4, 8))
+    rewrite(lambda m: None)
+    CK.load_checkpoint(path, b, params, world_size=2, topology="dp")
+    # an edited topology side file no longer matches what trainer_config_sha256 binds
+    json.dump({"world_size": 4, "topology": "dp"}, open(os.path.join(path, "topology.json"), "w"))
+    with pytest.raises(CK.CheckpointMismatch):
+        CK.load_checkpoint(path, b, params)
+    json.dump({"world_size": 2, "topology": "dp"}, open(os.path.join(path, "topology.json"), "w"))
+    # optimizer payload with an extra tensor / a moment of the wrong shape (digests re-sealed by an attacker
+    # who cannot be told from a writer bug): refused by the key and shape checks
+    from safetensors.torch import load_file, save_file
+    op = os.path.join(path, "optimizer.safetensors")
+    ot = load_file(op)
+    for bad in ({**ot, "m.00002": torch.zeros(1)}, {**ot, "v.00001": torch.zeros(3, 3)}):
+        save_file(bad, op)
+        man = json.loads(json.dumps(good))
+        ident = man["ordinary_checkpoint"]
+        ident["optimizer_sha256"] = CK.optimizer_payload_sha256(5, open(op, "rb").read())
+        ident["state_envelope_sha256"] = CK.state_envelope_sha256(4, "ordinary", 3, 2, "lora:r4", 5, 2, ident)
+        json.dump(man, open(mp, "w"))
+        with pytest.raises(CK.CheckpointMismatch):
+            CK.load_checkpoint(path, b, params)
+
+
+def test_latest_checkpoint_skips_ledger_continuations(tmp_path):
+    path, adapters, b = _ck(tmp_path, step=2)
+    opt = OptimizerState(5, [torch.ones_like(a) for a in adapters], [torch.full_like(a, 2.0) for a in adapters])
+    CK.save_checkpoint(str(tmp_path), 7, adapters, opt, b"s", b, continuation={"kind": "rollout_ledger", "completed_step": 7})
+    assert CK.latest_checkpoint(str(tmp_path)) == (2, path)
+    assert CK.latest_rollout_ledger_continuation(str(tmp_path))[0] == 7
 
 
 def test_failed_publication_leaves_nothing_and_newer_malformed_is_an_error(tmp_path):

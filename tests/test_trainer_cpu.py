@@ -182,6 +182,33 @@ def test_uncovered_gradient_aborts():
         tr.step(0)
 
 
+def test_dp_one_rank_drops_a_gradient_and_every_rank_raises_coverage_error():
+    """A rank whose backward left one trainable tensor without a gradient still enters the same
+    tensor all-reduce as its peers (the slot is zero-filled) and the failure surfaces as a
+    GradCoverageError on every rank, not as mismatched collectives (reference trainer.rs
+    materialize_zero_grad_slots + reduce_accumulated_grads)."""
+    varied = FnReward(lambda s, c: float(sum(int(t) for t in c.split()) % 3))
+
+    def body(comm):
+        pol = make_policy()
+        tr = Trainer(pol, ListTok(), varied, samples(), cfg(steps=1, prompts_per_item=1), comm=comm)
+        if comm.rank == 1:
+            real = pol.backward
+
+            def lossy(loss):
+                real(loss)
+                tr.params[0].grad = None
+            pol.backward = lossy
+        with pytest.raises(GradCoverageError):
+            tr.step(0)
+        return comm.collective_calls
+    import time
+    t0 = time.time()
+    calls = run_ranks(2, body, timeout=30.0)
+    assert time.time() - t0 < 25
+    assert calls[0] == calls[1]          # both ranks issued the same sequence of collectives
+
+
 def test_preemption_checkpoints_and_stops(tmp_path):
     rd = RunDir.create(str(tmp_path), "r")
     tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=10), run_dir=rd, binding=_binding())
@@ -463,7 +490,7 @@ def test_collector_learner_chain_is_bit_exact_and_refuses_stale_or_foreign_windo
     # continuation checkpoints are discovered separately and carry the chain link
     step, path, cont = latest_rollout_ledger_continuation(rd.checkpoints_dir)
     assert step == 2 and L.LedgerContinuation.from_json(cont).lineage_sha256 == c1.lineage_sha256
-    assert latest_checkpoint(rd.checkpoints_dir)[0] == 2
+    assert latest_checkpoint(rd.checkpoints_dir) is None      # ordinary discovery never picks a continuation
     tampered = L.LedgerContinuation.from_json(dict(cont, consumed_ledger_sha256="0" * 64))
     with pytest.raises(L.LedgerError, match="does not follow"):
         tampered.verify()
