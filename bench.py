@@ -218,11 +218,14 @@ def main():
     launches = C.launches() - l0
     clk = clocks.stop()
     ms = e0.elapsed_time(e1)
-    vals = comm.all_gather_bytes(json.dumps({"ms": ms, "tok": tokens_local}).encode())
+    vals = comm.all_gather_bytes(json.dumps({"ms": ms, "tok": tokens_local, "rollout_ms": phase.get("rollout", 0.0)}).encode())
     vals = [json.loads(v.decode()) for v in vals]
     ms_max = max(v["ms"] for v in vals)
     tok_total = sum(v["tok"] for v in vals)
     value = tok_total / (ms_max / 1e3)
+    # decode throughput: completion tokens of all ranks over the slowest rank's rollout phase (prefill included)
+    rollout_ms_max = max(v["rollout_ms"] for v in vals)
+    decode_tok_s = tok_total / (rollout_ms_max / 1e3) if rollout_ms_max > 0 else None
 
     # end-to-end pass: host wall clock, explicit H2D/D2H accounting
     policy.h2d_bytes = policy.d2h_bytes = 0
@@ -259,6 +262,8 @@ def main():
             "clocks": clk,
             "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": policy.h2d_bytes // args.steps,
                     "d2h_bytes_per_step": (policy.d2h_bytes + 64) // args.steps},
+            "decode_tok_s": decode_tok_s,
+            "rollout_ms_per_token": round(rollout_ms_max / args.steps / args.max_new, 4),   # one decode step of the whole batch
             "gpu_launches": int(launches),
             "phase_ms_per_step": {k: round(v / args.steps, 2) for k, v in phase.items()},
             "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),

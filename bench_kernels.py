@@ -199,6 +199,8 @@ def main():
                 s = T(lambda: C.gemm(a, b, force_bn=bn))
                 report(f"gemm {name} M{M} N{N} K{K} bn{bn or 'auto'}", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
             if M <= 128:
+                s = T(lambda: C.lib().decode_gemm(a, b, None, -1, 0, False))
+                report(f"gemm {name} resident-activation cluster kernel", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
                 s = T(lambda: C.gemm(a, b, stream_k=1))
                 report(f"gemm {name} stream-k", s, 2 * (M * K + N * K + M * N), 2 * M * N * K)
                 s = T(lambda: C.gemm(a, b, stream_k=-1))
@@ -251,9 +253,15 @@ def main():
                 mm(x, wg)
                 mm(xf, wd)
 
+        def planner_pdl(a, b):
+            return C.gemm(a, b, static_b=True)
+
         for label, mm in (("tcgen05 planner", lambda a, b: C.gemm(a, b)),
-                          ("tcgen05 planner, weights prefetched under the previous kernel (dependent launch)",
-                           lambda a, b: C.gemm(a, b, static_b=True)),
+                          ("tcgen05 planner, weights prefetched under the previous kernel (dependent launch)", planner_pdl),
+                          ("tcgen05 resident-activation cluster kernel (dependent launch)",
+                           lambda a, b: C.lib().decode_gemm(a, b, None, -1, 0, True)),
+                          ("tcgen05 resident-activation cluster kernel, no dependent launch",
+                           lambda a, b: C.lib().decode_gemm(a, b, None, -1, 0, False)),
                           ("cuBLAS (library reference)", lambda a, b: torch.matmul(a, b.t()))):
             chain(mm)
             torch.cuda.synchronize()

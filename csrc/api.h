@@ -57,6 +57,24 @@ void gemm_plan(int M, int N, int K, int K2, int num_sms, int* bn_out, int* split
 const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream);
 int gemm_pick_bn(int M, int N, int num_sms);
 
+// ---- decode projection with resident activations (csrc/gemm/decode_gemm.cu): M <= 128, bf16 out ----
+struct DecodeGemmArgs {
+  const void* A; const void* B;            // bf16, K-major: A [M, K] activations, B [N, K] weights
+  long long lda, ldb;
+  int M, N, K;
+  void* out; long long ldo;                // bf16 [M, N], or [M, N/2] with the GLU epilogue
+  const void* residual; long long ldr;     // optional bf16 [M, N]
+  int glu_act;                             // 0 none, 1 SiLU, 2 tanh-GELU (B rows interleaved in groups of 16: 8 gate, 8 up)
+  float* partial;                          // fp32 [groups, M, N] scratch, needed when decode_gemm_groups(K) > 1
+  int* status;                             // device status word (kStatus*)
+  int pdl;                                 // programmatic dependent launch: B is never written by an earlier kernel
+  int max_clusters;                        // 0 = as many as the device holds
+  unsigned long long* debug;               // optional [64]: time stamps of one epilogue warp (development aid)
+};
+bool decode_gemm_supported(int M, int N, int K, bool glu);
+int decode_gemm_groups(int K);
+const char* decode_gemm(const DecodeGemmArgs& a, cudaStream_t stream);
+
 // ---- norms / rope ----
 const char* rmsnorm(int dtype, const void* x, const void* res, const void* w, const void* gate, void* y, void* h_out,
                     long long rows, int H, float eps, bool zero_centered, cudaStream_t s);
@@ -129,6 +147,9 @@ struct DecodeAttnArgs {
   void* out; float* workspace;
   int B, Hq, Hkv, D; long long seq_stride, tok_stride; float scale; int window, n_splits;
   int no_pipe;   // 0: tensor-core pipelined kernel; 2: scalar pipelined kernel; 1: register-resident kernel
+  // shared-prefix mode (paged cache, rows in groups of `group` that share their first prefix_len[b / group]
+  // keys): those keys are streamed once per group; workspace: B * Hq * prefix_splits * (D + 2) floats
+  const int* prefix_len; int group; int prefix_splits;
 };
 const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s);
 size_t decode_attn_workspace_bytes(int B, int Hq, int D, int n_splits);

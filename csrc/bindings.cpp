@@ -7,6 +7,7 @@
 #include <torch/library.h>
 
 #include <atomic>
+#include <cstdlib>
 #include <mutex>
 #include <unordered_map>
 #include <vector>
@@ -69,6 +70,56 @@ int64_t kernel_status() {
 }
 void reset_status() { C10_CUDA_CHECK(cudaMemsetAsync(status_word(), 0, sizeof(int), stream())); }
 
+// Decode projections (M <= 128) with the activation tile resident in tensor memory
+// (csrc/gemm/decode_gemm.cu).  Opt-in: measured inside a decode layer it is slower than the planner's
+// choices (its per-tile exchange between the CTAs of a cluster takes about 2 us), so weights (static_b)
+// take it only with FERRL_DECODE_GEMM=1 or set_decode_gemm(true).
+bool g_decode_gemm = [] {
+  const char* e = std::getenv("FERRL_DECODE_GEMM");
+  return e && e[0] == '1';
+}();
+void set_decode_gemm(bool on) { g_decode_gemm = on; }
+
+// glu_act: -1 none, 0 SiLU, 1 tanh-GELU (B rows interleaved in groups of 16: 8 gate rows, 8 up rows)
+Tensor decode_gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& residual, int64_t glu_act, int64_t max_clusters,
+                   bool static_b, const optional<Tensor>& debug = optional<Tensor>()) {
+  TORCH_CHECK(A.is_cuda() && B.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16 &&
+                  A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1,
+              "decode_gemm: A [M,K], B [N,K] bf16, K-major");
+  TORCH_CHECK(glu_act >= -1 && glu_act <= 1, "decode_gemm: glu_act -1, 0 or 1");
+  const int M = A.size(0), N = B.size(0), K = A.size(1);
+  TORCH_CHECK(ferrl::decode_gemm_supported(M, N, K, glu_act >= 0),
+              "decode_gemm: needs 1 <= M <= 128, N a multiple of 64, K a multiple of 8 and >= 512 (no k groups with GLU)");
+  c10::cuda::CUDAGuard guard(A.device());
+  ferrl::DecodeGemmArgs a{};
+  a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
+  a.M = M; a.N = N; a.K = K;
+  Tensor out = at::empty({A.size(0), glu_act >= 0 ? B.size(0) / 2 : B.size(0)}, A.options());
+  a.out = out.data_ptr(); a.ldo = out.stride(0);
+  if (residual.has_value() && residual->defined()) {
+    TORCH_CHECK(glu_act < 0, "decode_gemm: no residual with the GLU epilogue");
+    TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == M &&
+                    residual->size(1) == N && residual->stride(1) == 1, "decode_gemm: residual bf16 [M,N]");
+    a.residual = residual->data_ptr(); a.ldr = residual->stride(0);
+  }
+  a.glu_act = glu_act >= 0 ? static_cast<int>(glu_act) + 1 : 0;
+  Tensor partial;
+  const int groups = ferrl::decode_gemm_groups(K);
+  if (groups > 1) {
+    partial = at::empty({groups, A.size(0), B.size(0)}, A.options().dtype(at::kFloat));
+    a.partial = partial.data_ptr<float>();
+  }
+  a.status = status_word();
+  a.pdl = static_b ? 1 : 0;
+  a.max_clusters = static_cast<int>(max_clusters);
+  if (debug.has_value() && debug->defined()) {
+    TORCH_CHECK(debug->scalar_type() == at::kLong && debug->numel() >= 64 && debug->is_cuda(), "decode_gemm: debug int64[64]");
+    a.debug = reinterpret_cast<unsigned long long*>(debug->data_ptr<int64_t>());
+  }
+  FERRL_CHECK(ferrl::decode_gemm(a, stream()));
+  return out;
+}
+
 // out[M,N] = A[M,K] B[N,K]^T (+ A2 B2^T) (+ residual)
 Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
             const optional<Tensor>& residual, bool out_f32, int64_t force_bn, int64_t force_split, int64_t two_cta,
@@ -77,6 +128,10 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm: operands must be bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1), "gemm: A [M,K], B [N,K]");
   TORCH_CHECK(A.stride(1) == 1 && B.stride(1) == 1, "gemm: operands must be K-major");
+  if (g_decode_gemm && static_b && !out_f32 && !(A2.has_value() && A2->defined()) && force_bn == 0 && force_split == 0 &&
+      two_cta <= 0 && cluster_k == 0 && stream_k == 0 && B.size(0) <= 32768 &&
+      ferrl::decode_gemm_supported(A.size(0), B.size(0), A.size(1), false))
+    return decode_gemm(A, B, residual, -1, 0, true);
   c10::cuda::CUDAGuard guard(A.device());
   ferrl::GemmArgs a{};
   a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
@@ -179,6 +234,8 @@ Tensor gemm_glu(const Tensor& A, const Tensor& B, int64_t act, bool static_b) {
                   A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1,
               "gemm_glu: A [M,K], B [N,K] bf16, K-major");
   TORCH_CHECK((B.size(0) % 16) == 0 && (act == 0 || act == 1), "gemm_glu: N a multiple of 16, act 0 (silu) or 1 (tanh-gelu)");
+  if (g_decode_gemm && static_b && ferrl::decode_gemm_supported(A.size(0), B.size(0), A.size(1), true))
+    return decode_gemm(A, B, optional<Tensor>(), act, 0, true);
   c10::cuda::CUDAGuard guard(A.device());
   ferrl::GemmArgs a{};
   a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
@@ -801,7 +858,8 @@ void grpo_scale_rows(Tensor dlogp, const Tensor& row_scale) {
 }
 
 Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Tensor& kv_len, double scale,
-                   int64_t window, int64_t n_splits, const optional<Tensor>& block_table, int64_t page, int64_t variant) {
+                   int64_t window, int64_t n_splits, const optional<Tensor>& block_table, int64_t page, int64_t variant,
+                   const optional<Tensor>& prefix_len, int64_t group, int64_t prefix_splits) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && q.is_contiguous() && q.dim() == 3, "decode_attn: q bf16 [B,Hq,D]");
   TORCH_CHECK(kc.scalar_type() == at::kBFloat16 && kc.is_contiguous() && vc.is_contiguous() && kc.dim() == 4, "decode_attn: caches bf16 [B,S,Hkv,D]");
   TORCH_CHECK(kv_len.scalar_type() == at::kInt && kv_len.is_contiguous(), "decode_attn: kv_len int32");
@@ -818,7 +876,15 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
   a.n_splits = n_splits > 0 ? n_splits : ferrl::decode_attn_pick_splits(a.B, a.Hkv, kc.size(1), num_sms());
   Tensor out = at::empty_like(q);
   Tensor ws;
-  if (a.n_splits > 1) {
+  if (prefix_len.has_value() && prefix_len->defined()) {
+    TORCH_CHECK(prefix_len->scalar_type() == at::kInt && prefix_len->is_contiguous() && group >= 1 &&
+                    prefix_len->numel() * group == a.B, "decode_attn: prefix_len int32 [B / group]");
+    a.prefix_len = prefix_len->data_ptr<int>(); a.group = static_cast<int>(group);
+    a.prefix_splits = static_cast<int>(prefix_splits);
+    a.n_splits = 1;
+    ws = at::empty({static_cast<long long>(a.B) * a.Hq * a.prefix_splits * (a.D + 2)}, q.options().dtype(at::kFloat));
+    a.workspace = ws.data_ptr<float>();
+  } else if (a.n_splits > 1) {
     ws = at::empty({static_cast<long long>(ferrl::decode_attn_workspace_bytes(a.B, a.Hq, a.D, a.n_splits) / 4)},
                    q.options().dtype(at::kFloat));
     a.workspace = ws.data_ptr<float>();
@@ -1039,6 +1105,8 @@ void add_launches(int64_t n) { ferrl::count_launch(static_cast<int>(n)); }
 
 TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0, bool static_b=False) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
+  m.def("decode_gemm(Tensor A, Tensor B, Tensor? residual=None, int glu_act=-1, int max_clusters=0, bool static_b=False, Tensor? debug=None) -> Tensor", &decode_gemm);
+  m.def("set_decode_gemm(bool on) -> ()", &set_decode_gemm);
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
@@ -1069,7 +1137,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("adamw_step(Tensor[] params, Tensor[] grads, Tensor[] m, Tensor[] v, float lr, float b1, float b2, float eps, float wd, int step, float max_norm, float pre_scale, bool compute_norm) -> Tensor", &adamw_step);
   m.def("grpo_loss_rows(Tensor logp, Tensor logp_old, Tensor? logp_ref, Tensor adv, Tensor mask, Tensor? tis, float eps_lo, float eps_hi, float beta, bool seq_level, bool want_grad) -> (Tensor, Tensor, Tensor)", &grpo_loss_rows);
   m.def("grpo_scale_rows(Tensor(a!) dlogp, Tensor row_scale) -> ()", &grpo_scale_rows);
-  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0) -> Tensor", &decode_attn);
+  m.def("decode_attn(Tensor q, Tensor kc, Tensor vc, Tensor kv_len, float scale, int window, int n_splits, Tensor? block_table, int page, int variant=0, Tensor? prefix_len=None, int group=1, int prefix_splits=1) -> Tensor", &decode_attn);
   m.def("gemm_norm(Tensor A, Tensor B, Tensor? residual, Tensor? ss_in, float eps, int glu_act, bool want_ss, bool static_b=True) -> (Tensor, Tensor)", &gemm_norm);
   m.def("row_sumsq(Tensor x) -> Tensor", &row_sumsq);
   m.def("gemm_glu(Tensor A, Tensor B, int act, bool static_b=False) -> Tensor", &gemm_glu);

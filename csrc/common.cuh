@@ -93,6 +93,30 @@ inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
 }
 #endif
 
+// cudaFuncSetAttribute values are per device: a flag that remembers "already set" must be kept per
+// device too, or a process that drives a second GPU launches there without the opt-in.  This is a
+// once-per-(call site, device) guard; devices beyond kMaxDevices simply set the attribute every time.
+constexpr int kMaxDevices = 64;
+struct PerDeviceOnce {
+  unsigned char done[kMaxDevices] = {};   // written with the same value by any racing thread
+  // Returns the current device's slot index, or -1 when it cannot be cached.
+  static int slot() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+    return dev;
+  }
+};
+// `expr` evaluates to true when every attribute call succeeded.  Evaluates to false on failure.
+#define FERRL_ONCE_PER_DEVICE(expr)                                                         \
+  ([&]() -> bool {                                                                          \
+    static ::ferrl::PerDeviceOnce once_;                                                    \
+    const int slot_ = ::ferrl::PerDeviceOnce::slot();                                       \
+    if (slot_ >= 0 && once_.done[slot_]) return true;                                       \
+    if (!(expr)) return false;                                                              \
+    if (slot_ >= 0) once_.done[slot_] = 1;                                                  \
+    return true;                                                                            \
+  }())
+
 // Count of kernel launches issued by this library (host side, for benchmarks).
 void count_launch(int n = 1);
 long long launch_count();

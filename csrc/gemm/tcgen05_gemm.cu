@@ -891,12 +891,10 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   auto kern_plain = gemm_kernel<BN, OUT_F32, HAS_RES, false>;
   auto kern_ar = gemm_kernel<BN, OUT_F32, HAS_RES, kArOk>;      // same as plain when the mode is not available
   auto kern = p.ar_world > 1 ? kern_ar : kern_plain;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[p.ar_world > 1]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic smem) failed";
-    attr_set[p.ar_world > 1] = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(
+          cudaFuncSetAttribute(kern_plain, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) == cudaSuccess &&
+          cudaFuncSetAttribute(kern_ar, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) == cudaSuccess))
+    return "cudaFuncSetAttribute(max dynamic smem) failed";
   int m_tiles = (a.M + BM - 1) / BM, n_tiles = (a.N + BN - 1) / BN;
   int tiles = m_tiles * n_tiles * p.split_k;
   int grid = tiles < a.num_sms ? tiles : a.num_sms;
@@ -1238,12 +1236,9 @@ const char* launch_2cta(const GemmArgs& a, cudaStream_t stream) {
   p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 8;
   p.split_k = 1; p.ar_world = 1;
   auto kern = gemm2_kernel<BN, HAS_RES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic smem) failed";
-    attr_set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) ==
+                             cudaSuccess))
+    return "cudaFuncSetAttribute(max dynamic smem) failed";
   const int m_tiles = (a.M + 2 * BM - 1) / (2 * BM), n_tiles = (a.N + BN - 1) / BN;
   const int tiles = m_tiles * n_tiles;
   int clusters = tiles < a.num_sms / 2 ? tiles : a.num_sms / 2;
@@ -1567,12 +1562,9 @@ const char* launch_ksplit(const GemmArgs& a, cudaStream_t stream) {
   p.ss_in = a.ss_in; p.ss_parts = a.ss_parts; p.ss_ld = a.ss_ld; p.ss_inv_k = a.ss_inv_k; p.ss_eps = a.ss_eps;
   p.ss_out = a.ss_out;
   auto kern = gemm_ksplit_kernel<BN, S, OUT_F32, HAS_RES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic smem) failed";
-    attr_set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) ==
+                             cudaSuccess))
+    return "cudaFuncSetAttribute(max dynamic smem) failed";
   const int tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(tiles * S);
@@ -1984,12 +1976,9 @@ const char* launch_streamk(const GemmArgs& a, cudaStream_t stream) {
   if (sk.units < grid) grid = static_cast<int>(sk.units);
   if (grid < 1) return nullptr;
   auto kern = gemm_streamk_kernel<OUT_F32, HAS_RES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
-      return "cudaFuncSetAttribute(max dynamic smem) failed";
-    attr_set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) ==
+                             cudaSuccess))
+    return "cudaFuncSetAttribute(max dynamic smem) failed";
   kern<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, tmA2, tmB2, p, sk);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "stream-k gemm launch failed";

@@ -628,9 +628,14 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        const __nv_bfloat16* __restrict__ vc, const int* __restrict__ kv_len,
                        const int* __restrict__ block_table, int bt_stride, int page,
                        __nv_bfloat16* __restrict__ out, float* __restrict__ ws, int Hq, int Hkv,
-                       long long seq_stride, long long tok_stride, float scale, int window, int n_splits) {
+                       long long seq_stride, long long tok_stride, float scale, int window, int n_splits,
+                       const int* __restrict__ kv_start, int kv_start_div, int ws_off, int ws_total) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
-  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
+  // Launched as a programmatic dependent itself: nothing is read before the predecessor is done.  In
+  // shared-prefix mode the predecessor is the group kernel, which only produces the prefix partials
+  // that the final merge below reads (and which lets this kernel start only after ITS predecessor has
+  // finished): the wait moves down to the merge and the two kernels run side by side.
+  if (ws_total == 0) pdl_wait();
   static_assert(REP <= 8, "query heads of one KV head must fit rows 0..7 of the MMA tile");
   constexpr int ROW_BYTES = D * 2;
   constexpr int CPR = ROW_BYTES / 16;                  // 16-byte chunks per row
@@ -656,8 +661,10 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
   }
   const int len = kv_len[b];
-  const int lo = (window > 0 && len > window) ? len - window : 0;
-  const int span = len - lo;
+  int lo = (window > 0 && len > window) ? len - window : 0;
+  // keys below kv_start[b / kv_start_div] belong to a prefix that another kernel covers (see the group kernel)
+  if (kv_start) lo = max(lo, kv_start[b / kv_start_div]);
+  const int span = max(len - lo, 0);
   const int per = (span + n_splits - 1) / n_splits;
   const int s0 = lo + split * per;
   const int s1 = min(len, s0 + per);
@@ -764,6 +771,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
   }
   __syncthreads();
+  if (ws_total > 0) pdl_wait();    // the prefix partials in slots [0, ws_off) are complete from here on
   for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
     const int r = i / D, d = i - r * D;
     float m = -INFINITY;
@@ -776,7 +784,21 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
       acc += o_s[(w * REP + r) * D + d] * c;
     }
     const long long head = static_cast<long long>(b) * Hq + hk * REP + r;
-    if (n_splits == 1) {
+    if (ws_total > 0) {
+      // shared-prefix mode: merge my keys with the prefix partials and write the final row
+      const float* base = ws + head * ws_total * (D + 2);
+      float mm = m;
+      for (int sp = 0; sp < ws_off; ++sp) mm = fmaxf(mm, base[sp * (D + 2) + D]);
+      const float c0 = (m == -INFINITY) ? 0.f : __expf(m - mm);
+      float lt = l * c0, ot = acc * c0;
+      for (int sp = 0; sp < ws_off; ++sp) {
+        const float ms = base[sp * (D + 2) + D];
+        const float c = (ms == -INFINITY) ? 0.f : __expf(ms - mm);
+        lt += base[sp * (D + 2) + D + 1] * c;
+        ot += base[sp * (D + 2) + d] * c;
+      }
+      out[head * D + d] = __float2bfloat16_rn((lt > 0.f && len > 0) ? ot / lt : 0.f);   // a retired row (length 0) stays zero
+    } else if (n_splits == 1) {
       out[head * D + d] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     } else {
       float* w_ = ws + (head * n_splits + split) * (D + 2);
@@ -785,6 +807,217 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         w_[D] = m;
         w_[D + 1] = l;
       }
+    }
+  }
+}
+
+// Shared-prefix form for grouped rollouts.  The G rows of a group (one prompt, G completions) share
+// the prompt's full pages, so the keys [0, prefix_len[group]) are the same memory for all of them: one
+// CTA per (group, KV head, split) streams those keys ONCE and applies them to all G * REP query rows
+// of the group (two 16-row MMA tiles for G = 8, REP = 4) instead of G CTAs streaming them G times.
+// The rest of every row ([prefix_len, kv_len)) is covered by decode_attn_mma_kernel with kv_start =
+// prefix_len, launched right behind this kernel and running beside it; it reads the (o, m, l) partials
+// written here only in its last step, where it merges them with its own and writes the final rows.
+// Query row r of the tile is batch row group * G + r / REP, head hk * REP + r % REP.
+// One CTA of this kernel owns an SM (32 query rows of accumulators), so its own ring must hold the bytes in
+// flight that four co-resident CTAs provide in the per-row kernel: eight stages of 32 keys.
+constexpr int GSTAGES = 8;
+
+template <int D, int REP, int G>
+__global__ void __launch_bounds__(PWARPS * 32, 1)
+decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                         const __nv_bfloat16* __restrict__ vc, const int* __restrict__ prefix_len,
+                         const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int page,
+                         float* __restrict__ ws, int Hq, int Hkv, long long tok_stride, float scale, int n_splits,
+                         int ws_total) {
+  // wait first, then let the per-row kernel start: when it runs, everything before this kernel is complete
+  pdl_wait();
+  pdl_trigger();
+  constexpr int QR = REP * G;                          // query rows sharing the keys
+  static_assert(QR % 16 == 0 && QR <= 32, "group kernel: G * REP must be 16 or 32");
+  constexpr int RT = QR / 16;                          // 16-row MMA tiles
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int CPR = ROW_BYTES / 16;
+  constexpr int CHUNKS = PTK * CPR;
+  constexpr int STAGE_BYTES = 2 * PTK * ROW_BYTES;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;
+  extern __shared__ __align__(128) uint8_t psm[];
+  const int gi = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+
+  int pre = prefix_len[gi];
+  {
+    // a group whose rows have all been retired (attention length 0) reads nothing
+    int live = 0;
+    for (int r = 0; r < G; ++r) live |= kv_len[gi * G + r];
+    if (live == 0) pre = 0;
+  }
+  const int per = (pre + n_splits - 1) / n_splits;
+  const int s0 = split * per;
+  const int s1 = min(pre, s0 + per);
+  const int n_tiles = s1 > s0 ? (s1 - s0 + PTK - 1) / PTK : 0;
+  const int b0 = gi * G;                               // the group's first row: its table names the shared pages
+
+  // Q fragments of the RT row tiles: rows rt*16 + g (a0, a2) and rt*16 + g + 8 (a1, a3)
+  uint32_t qa[RT][KSTEPS][4];
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rt * 16 + g + 8 * hh;
+      const __nv_bfloat16* qp = q + (static_cast<long long>(b0 + r / REP) * Hq + hk * REP + r % REP) * D + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        qa[rt][ks][hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16);
+        qa[rt][ks][2 + hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8);
+      }
+    }
+  }
+
+  auto row_of = [&](int j) -> long long {
+    const int pg = block_table[static_cast<long long>(b0) * bt_stride + j / page];
+    return (static_cast<long long>(pg) * page + (j % page)) * tok_stride + hk * D;
+  };
+  auto issue = [&](int tt) {
+    if (tt < n_tiles) {
+      uint8_t* st = psm + (tt % GSTAGES) * STAGE_BYTES;
+      const int j0 = s0 + tt * PTK;
+      for (int c = threadIdx.x; c < CHUNKS; c += PWARPS * 32) {
+        const int key = c / CPR, part = c % CPR;
+        const int j = j0 + key;
+        const bool ok = j < s1;
+        const long long row = row_of(ok ? j : s0) + part * 8;
+        const int off = key * ROW_BYTES + ((part ^ (key & 7)) << 4);
+        cp_async16(st + off, kc + row, ok);
+        cp_async16(st + PTK * ROW_BYTES + off, vc + row, ok);
+      }
+    }
+    cp_async_commit();
+  };
+
+  float m_run[RT][2], l_run[RT][2];
+  float o[RT][NT][4];
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt) {
+    m_run[rt][0] = m_run[rt][1] = -INFINITY;
+    l_run[rt][0] = l_run[rt][1] = 0.f;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[rt][n][0] = o[rt][n][1] = o[rt][n][2] = o[rt][n][3] = 0.f;
+  }
+
+#pragma unroll
+  for (int tt = 0; tt < GSTAGES - 1; ++tt) issue(tt);
+  for (int tt = 0; tt < n_tiles; ++tt) {
+    cp_async_wait<GSTAGES - 2>();
+    __syncthreads();
+    issue(tt + GSTAGES - 1);
+    const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % GSTAGES) * STAGE_BYTES));
+    const uint32_t vt = kt + PTK * ROW_BYTES;
+    const int key0 = warp * 8;
+    const int j0 = s0 + tt * PTK + key0;
+    const int lrow = key0 + (lane & 7), lmat = lane >> 3;
+    float sacc[RT][4];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) sacc[rt][0] = sacc[rt][1] = sacc[rt][2] = sacc[rt][3] = 0.f;
+#pragma unroll
+    for (int qd = 0; qd < KSTEPS / 2; ++qd) {
+      uint32_t b0_, b1_, b2_, b3_;
+      ldsm_x4(kt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), b0_, b1_, b2_, b3_);
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+        mma_16816(sacc[rt], qa[rt][2 * qd][0], qa[rt][2 * qd][1], qa[rt][2 * qd][2], qa[rt][2 * qd][3], b0_, b1_);
+        mma_16816(sacc[rt], qa[rt][2 * qd + 1][0], qa[rt][2 * qd + 1][1], qa[rt][2 * qd + 1][2], qa[rt][2 * qd + 1][3], b2_, b3_);
+      }
+    }
+    const bool v0 = j0 + 2 * t < s1, v1 = j0 + 2 * t + 1 < s1;
+    uint32_t pa[RT][2];
+    float corr[RT][2];
+#pragma unroll
+    for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float sc0 = v0 ? sacc[rt][2 * hh] * scale : -INFINITY;
+        const float sc1 = v1 ? sacc[rt][2 * hh + 1] * scale : -INFINITY;
+        float mx = fmaxf(sc0, sc1);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[rt][hh], mx);
+        const float cr = (m_run[rt][hh] == -INFINITY) ? 0.f : __expf(m_run[rt][hh] - m_new);
+        const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
+        const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run[rt][hh] = l_run[rt][hh] * cr + ps;
+        m_run[rt][hh] = m_new;
+        corr[rt][hh] = cr;
+        __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
+        pa[rt][hh] = *reinterpret_cast<uint32_t*>(&ph);
+      }
+    }
+#pragma unroll
+    for (int qd = 0; qd < NT / 4; ++qd) {
+      uint32_t w0, w1, w2, w3;
+      ldsm_x4_t(vt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), w0, w1, w2, w3);
+#pragma unroll
+      for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[rt][4 * qd + e][0] *= corr[rt][0];
+          o[rt][4 * qd + e][1] *= corr[rt][0];
+          o[rt][4 * qd + e][2] *= corr[rt][1];
+          o[rt][4 * qd + e][3] *= corr[rt][1];
+        }
+        mma_1688(o[rt][4 * qd + 0], pa[rt][0], pa[rt][1], w0);
+        mma_1688(o[rt][4 * qd + 1], pa[rt][0], pa[rt][1], w1);
+        mma_1688(o[rt][4 * qd + 2], pa[rt][0], pa[rt][1], w2);
+        mma_1688(o[rt][4 * qd + 3], pa[rt][0], pa[rt][1], w3);
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();
+
+  // merge the four warps (each saw different keys) through shared memory
+  float* m_s = reinterpret_cast<float*>(psm);   // [PWARPS][QR]
+  float* l_s = m_s + PWARPS * QR;               // [PWARPS][QR]
+  float* o_s = l_s + PWARPS * QR;               // [PWARPS][QR][D]
+#pragma unroll
+  for (int rt = 0; rt < RT; ++rt) {
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rt * 16 + g + 8 * hh;
+      if (t == 0) {
+        m_s[warp * QR + r] = m_run[rt][hh];
+        l_s[warp * QR + r] = l_run[rt][hh];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o_s[(warp * QR + r) * D + n * 8 + 2 * t] = o[rt][n][2 * hh];
+        o_s[(warp * QR + r) * D + n * 8 + 2 * t + 1] = o[rt][n][2 * hh + 1];
+      }
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < QR * D; i += blockDim.x) {
+    const int r = i / D, d = i - r * D;
+    float m = -INFINITY;
+    for (int w = 0; w < PWARPS; ++w) m = fmaxf(m, m_s[w * QR + r]);
+    float l = 0.f, acc = 0.f;
+    for (int w = 0; w < PWARPS; ++w) {
+      const float mw = m_s[w * QR + r];
+      const float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+      l += l_s[w * QR + r] * c;
+      acc += o_s[(w * QR + r) * D + d] * c;
+    }
+    const long long head = static_cast<long long>(b0 + r / REP) * Hq + hk * REP + r % REP;
+    float* w_ = ws + (head * ws_total + split) * (D + 2);
+    w_[d] = acc;
+    if (d == 0) {
+      w_[D] = m;
+      w_[D + 1] = l;
     }
   }
 }
@@ -831,8 +1064,42 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
   if (a.n_splits > 1 && !a.workspace) return "decode_attn: workspace required for split-kv";
   dim3 grid(a.B, a.Hkv, a.n_splits < 1 ? 1 : a.n_splits);
   bool launched = false;
+  // shared-prefix mode (grouped rollouts over a paged cache): see decode_attn_group_kernel
+  const int* kv_start = nullptr;
+  int kv_start_div = 1, ws_off = 0, ws_total = 0;
+  if (a.prefix_len) {
+    const int G = a.group;
+    if (!a.block_table || !a.workspace || a.window > 0 || a.no_pipe != 0 || grid.z != 1 || G < 1 || (a.B % G) ||
+        a.prefix_splits < 1 || a.prefix_splits > 8)
+      return "decode_attn: shared-prefix mode needs a paged cache, a workspace, no window, one private split, 1..8 prefix splits";
+    if ((a.tok_stride % 8) || (reinterpret_cast<uintptr_t>(a.k) & 15) || (reinterpret_cast<uintptr_t>(a.v) & 15) ||
+        (reinterpret_cast<uintptr_t>(a.q) & 3))
+      return "decode_attn: shared-prefix mode needs 16-byte aligned caches";
+    kv_start = a.prefix_len; kv_start_div = G; ws_off = a.prefix_splits; ws_total = a.prefix_splits;
+    bool ok = false;
+#define FERRL_DECODE_GROUP(DD, RR, GG)                                                                                \
+  if (!ok && a.D == DD && rep == RR && G == GG) {                                                                     \
+    constexpr size_t ring = static_cast<size_t>(GSTAGES) * 2 * PTK * DD * 2;                                          \
+    constexpr size_t merge = (2 * PWARPS * RR * GG + static_cast<size_t>(PWARPS) * RR * GG * DD) * 4;                 \
+    constexpr size_t gsm = ring > merge ? ring : merge;                                                               \
+    auto gk = decode_attn_group_kernel<DD, RR, GG>;                                                                   \
+    if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                                                    static_cast<int>(gsm)) == cudaSuccess))                           \
+      return "decode_attn: cannot reserve shared memory";                                                             \
+    launch_pdl(gk, dim3(a.B / GG, a.Hkv, a.prefix_splits), dim3(PWARPS * 32), gsm, s,                                 \
+               static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                        \
+               static_cast<const __nv_bfloat16*>(a.v), a.prefix_len, a.kv_len, a.block_table, a.bt_stride, a.page,    \
+               a.workspace, a.Hq, a.Hkv, a.tok_stride, a.scale, a.prefix_splits, ws_total);                           \
+    ok = true;                                                                                                        \
+  }
+    FERRL_DECODE_GROUP(128, 4, 8) FERRL_DECODE_GROUP(128, 4, 4) FERRL_DECODE_GROUP(128, 8, 4) FERRL_DECODE_GROUP(128, 8, 2)
+    FERRL_DECODE_GROUP(128, 2, 8) FERRL_DECODE_GROUP(64, 4, 8) FERRL_DECODE_GROUP(64, 4, 4) FERRL_DECODE_GROUP(128, 2, 16)
+#undef FERRL_DECODE_GROUP
+    if (!ok) return "decode_attn: shared-prefix mode has no kernel for this (head_dim, heads per kv head, group) triple";
+    count_launch();
+  }
 #define FERRL_DECODE_FAST(DD, RR)                                                                                   \
-  if (!launched && a.D == DD && rep == RR) {                                                                          \
+  if (!launched && a.D == DD && rep == RR && !kv_start) {                                                                          \
     size_t fsm = (2 * WARPS * RR + static_cast<size_t>(WARPS) * RR * DD) * 4;                                         \
     decode_attn_fast_kernel<DD, RR><<<grid, WARPS * 32, fsm, s>>>(                                                    \
         static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
@@ -842,14 +1109,12 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     launched = true;                                                                                                  \
   }
 #define FERRL_DECODE_PIPE(DD, RR)                                                                                   \
-  if (!launched && a.D == DD && rep == RR && a.no_pipe != 1) {                                                            \
+  if (!launched && a.D == DD && rep == RR && a.no_pipe != 1 && !kv_start) {                                                            \
     constexpr size_t psm_bytes = static_cast<size_t>(PSTAGES) * 2 * PTK * DD * 2;                                     \
     auto pk = decode_attn_pipe_kernel<DD, RR>;                                                                        \
-    static bool pset = false;                                                                                         \
-    if (!pset) {                                                                                                      \
-      cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(psm_bytes));             \
-      pset = true;                                                                                                    \
-    }                                                                                                                 \
+    if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                                                    static_cast<int>(psm_bytes)) == cudaSuccess))                     \
+      return "decode_attn: cannot reserve shared memory";                                                             \
     pk<<<grid, PWARPS * 32, psm_bytes, s>>>(                                                                          \
         static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
         static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
@@ -861,16 +1126,14 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
   if (!launched && a.D == DD && rep == RR && a.no_pipe == 0) {                                                        \
     constexpr size_t msm_bytes = static_cast<size_t>(MSTAGES) * 2 * PTK * DD * 2;                                     \
     auto mk = decode_attn_mma_kernel<DD, RR>;                                                                         \
-    static bool mset = false;                                                                                         \
-    if (!mset) {                                                                                                      \
-      cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(msm_bytes));             \
-      mset = true;                                                                                                    \
-    }                                                                                                                 \
+    if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
+                                                    static_cast<int>(msm_bytes)) == cudaSuccess))                     \
+      return "decode_attn: cannot reserve shared memory";                                                             \
     launch_pdl(mk, grid, dim3(PWARPS * 32), msm_bytes, s,                                                             \
         static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \
         static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride, a.page,                         \
         static_cast<__nv_bfloat16*>(a.out), a.workspace, a.Hq, a.Hkv, a.seq_stride, a.tok_stride, a.scale, a.window,  \
-        grid.z);                                                                                                      \
+        grid.z, kv_start, kv_start_div, ws_off, ws_total);                                                            \
     launched = true;                                                                                                  \
   }
   if ((a.tok_stride % 8) == 0 && (a.seq_stride % 8) == 0 && (reinterpret_cast<uintptr_t>(a.k) & 15) == 0 &&
@@ -895,15 +1158,14 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     FERRL_DECODE_FAST(256, 8)
   }
 #undef FERRL_DECODE_FAST
+  if (!launched && kv_start) return "decode_attn: shared-prefix mode found no tensor-core kernel for the private part";
   if (!launched) {
     size_t smem = (static_cast<size_t>(rep) * a.D + 2 * WARPS * rep + static_cast<size_t>(WARPS) * rep * a.D) * 4;
     auto kern = decode_attn_kernel;
     if (smem > 48 * 1024) {
-      static bool set = false;
-      if (!set) {
-        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
-        set = true;
-      }
+      if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024) ==
+                                 cudaSuccess))
+        return "decode_attn: cannot reserve shared memory";
     }
     kern<<<grid, WARPS * 32, smem, s>>>(static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),
                                         static_cast<const __nv_bfloat16*>(a.v), a.kv_len, a.block_table, a.bt_stride,
@@ -923,6 +1185,8 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
 
 // ------------------------------------------------------------------------------------------------
 // Allocation-free entry point (declared and documented in csrc/no_alloc.h).
+#include <atomic>
+
 #include "../no_alloc.h"
 
 namespace {
@@ -931,15 +1195,17 @@ namespace {
 // cudaGetSymbolAddress - it is not a device address and must never be handed to a kernel.
 static __device__ __align__(256) float g_static_decode_ws[FERRL_STATIC_WS_FLOATS];
 
-constexpr int kMaxDevices = 64;
-float* g_static_ws_addr[kMaxDevices] = {nullptr};
+constexpr int kMaxDevices = FERRL_NOALLOC_MAX_DEVICES;
+// Written once per device with the same value by whichever host thread gets there first.
+std::atomic<float*> g_static_ws_addr[kMaxDevices];
 }  // namespace
 
 extern "C" int ferrl_decode_attn_static_ws(const void* q, const void* k_cache, const void* v_cache, const int* kv_len,
                                            void* out, int B, int Hq, int Hkv, int D, long long seq_stride,
                                            long long tok_stride, float scale, int window, int n_splits, void* stream) {
   if (!q || !k_cache || !v_cache || !kv_len || !out || B < 0 || Hq <= 0 || Hkv <= 0 || D <= 0 || n_splits < 1 ||
-      n_splits > 16 || (Hq % Hkv) || (Hq / Hkv) > 8 || (D % 8) || D > 256)
+      n_splits > 16 || (Hq % Hkv) || (Hq / Hkv) > 8 || (D % 8) || D > 256 || window < 0 || seq_stride < 0 ||
+      tok_stride < static_cast<long long>(Hkv) * D)
     return FERRL_NOALLOC_BAD_ARGS;
   if (B == 0) return FERRL_NOALLOC_OK;
   const unsigned long long need =
@@ -947,16 +1213,16 @@ extern "C" int ferrl_decode_attn_static_ws(const void* q, const void* k_cache, c
   if (need > FERRL_STATIC_WS_FLOATS) return FERRL_NOALLOC_TOO_LARGE;
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return FERRL_NOALLOC_CUDA_ERROR;
-  if (!g_static_ws_addr[dev]) {
+  float* ws = g_static_ws_addr[dev].load(std::memory_order_acquire);
+  if (!ws) {
     // once per device, with that device current: turn the symbol into its device address
-    float* p = nullptr;
-    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_decode_ws) != cudaSuccess || !p)
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&ws), g_static_decode_ws) != cudaSuccess || !ws)
       return FERRL_NOALLOC_CUDA_ERROR;
-    g_static_ws_addr[dev] = p;
+    g_static_ws_addr[dev].store(ws, std::memory_order_release);
   }
   ferrl::DecodeAttnArgs a{};
   a.q = q; a.k = k_cache; a.v = v_cache; a.kv_len = kv_len; a.block_table = nullptr; a.bt_stride = 0; a.page = 0;
-  a.out = out; a.workspace = n_splits > 1 ? g_static_ws_addr[dev] : nullptr;
+  a.out = out; a.workspace = n_splits > 1 ? ws : nullptr;
   a.B = B; a.Hq = Hq; a.Hkv = Hkv; a.D = D; a.seq_stride = seq_stride; a.tok_stride = tok_stride;
   a.scale = scale; a.window = window; a.n_splits = n_splits;
   return ferrl::decode_attn(a, static_cast<cudaStream_t>(stream)) == nullptr ? FERRL_NOALLOC_OK
@@ -968,8 +1234,12 @@ extern "C" const char* ferrl_noalloc_strerror(int code) {
     case FERRL_NOALLOC_OK: return "ok";
     case FERRL_NOALLOC_TOO_LARGE:
       return "B*Hq*n_splits*(D+2) exceeds the 4Mi-float static workspace; use fewer splits or a smaller batch";
-    case FERRL_NOALLOC_BAD_ARGS: return "null pointer or unsupported geometry (need Hq%Hkv==0, Hq/Hkv<=8, D%8==0, D<=256, 1<=n_splits<=16)";
-    case FERRL_NOALLOC_CUDA_ERROR: return "a CUDA call failed (device query, symbol address lookup or kernel launch)";
+    case FERRL_NOALLOC_BAD_ARGS:
+      return "null pointer or unsupported geometry (need Hq%Hkv==0, Hq/Hkv<=8, D%8==0, D<=256, 1<=n_splits<=16, "
+             "window>=0, seq_stride>=0, tok_stride>=Hkv*D)";
+    case FERRL_NOALLOC_CUDA_ERROR:
+      return "a CUDA call failed (device query, symbol address lookup or kernel launch), or the current device's "
+             "ordinal is FERRL_NOALLOC_MAX_DEVICES or higher";
     default: return "unknown code";
   }
 }

@@ -662,13 +662,10 @@ const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream) {
   p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status; p.debug = a.debug;
   constexpr int smem_dq = 7 * TILE128 + 1024 + 256;
   constexpr int smem_dkv = 2 * TILE128 + 2 * NST * TILE64 + 2 * ATOM128 + NST * QH * 8 + 256;
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv) != cudaSuccess)
-      return "flash_bwd_tc: cannot reserve shared memory";
-    set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(
+          cudaFuncSetAttribute(flash_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dq) == cudaSuccess &&
+          cudaFuncSetAttribute(flash_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_dkv) == cudaSuccess))
+    return "flash_bwd_tc: cannot reserve shared memory";
   const int n_t = (a.Sq + FT - 1) / FT;
   flash_bwd_dq_kernel<<<dim3(n_t, a.Hq, a.B), BWD_THREADS, smem_dq, stream>>>(tmQ, tmK, tmV, tmdO, p);
   count_launch();

@@ -657,14 +657,11 @@ const char* flash_fwd_tc(const FlashArgs& a, void* vt_ws, int* status, cudaStrea
   p.out = static_cast<__nv_bfloat16*>(a.o); p.o_bs = a.o_bs; p.o_ts = a.o_ts; p.lse = a.lse;
   p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status;
   constexpr int smem = 6 * TILE + 1024 + 256, smem2 = 7 * TILE + 1024 + 256, smem3 = 5 * TILE + 1024 + 256;
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) != cudaSuccess ||
-        cudaFuncSetAttribute(flash_fwd_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3) != cudaSuccess)
-      return "flash_fwd_tc: cannot reserve shared memory";
-    set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(
+          cudaFuncSetAttribute(flash_fwd_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+          cudaFuncSetAttribute(flash_fwd_tc2_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem2) == cudaSuccess &&
+          cudaFuncSetAttribute(flash_fwd_tc2_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem3) == cudaSuccess))
+    return "flash_fwd_tc: cannot reserve shared memory";
   dim3 grid((a.Sq + FT - 1) / FT, a.Hq, a.B);
   // form 0: output in registers; 1: output in TMEM, P through shared memory; 2: output and P in TMEM
   if (form == 2) flash_fwd_tc2_kernel<true><<<grid, 192, smem3, stream>>>(tmQ, tmK, tmVt, p);

@@ -491,13 +491,9 @@ const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long
   if (Hk <= 0 || Hv % Hk) return "gdn_chunk_fwd: value heads must be a multiple of key heads";
   if (B == 0 || T == 0) return nullptr;
   constexpr size_t smem = (static_cast<size_t>(GD) * GD + 4 * GC * GD + GC * GC + 2 * GC) * sizeof(float);
-  static bool set = false;
-  if (!set) {
-    if (cudaFuncSetAttribute(gdn_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) !=
-        cudaSuccess)
-      return "gdn_chunk_fwd: cannot reserve shared memory";
-    set = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(gdn_chunk_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                  static_cast<int>(smem)) == cudaSuccess))
+    return "gdn_chunk_fwd: cannot reserve shared memory";
   gdn_chunk_fwd_kernel<<<B * Hv, 256, smem, stream>>>(
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
       q_bs, q_ts, k_bs, k_ts, v_bs, v_ts, g, beta, S0, S_out, static_cast<__nv_bfloat16*>(out), T, Hk, Hv,

@@ -455,15 +455,14 @@ const char* sample_rows(int dtype, const void* logits, long long ld, const long 
   if (rows == 0) return nullptr;
   float inv_t = 1.f / temperature;
   constexpr size_t kDyn = 32 * 3 * 128 * sizeof(unsigned long long);   // 96 KB: see the histogram passes
-  static bool attr = false;
-  if (!attr) {
-    cudaFuncSetAttribute(sample_rows_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kDyn));
-    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(kDyn));
-    cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         static_cast<int>(kDyn));
-    attr = true;
-  }
+  if (!FERRL_ONCE_PER_DEVICE(
+          cudaFuncSetAttribute(sample_rows_kernel<float, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kDyn)) == cudaSuccess &&
+          cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kDyn)) == cudaSuccess &&
+          cudaFuncSetAttribute(sample_rows_kernel<__nv_bfloat16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(kDyn)) == cudaSuccess))
+    return "sample_rows: cannot reserve shared memory";
   if (dtype == kF32)
     sample_rows_kernel<float, false><<<rows, ST, kDyn, s>>>(static_cast<const float*>(logits), ld, global_rows, seed, draw_dev,
                                                          draw_host, tok_out, lp_out, V, inv_t, top_p);

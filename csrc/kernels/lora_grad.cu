@@ -182,11 +182,9 @@ const char* lora_grad(const void* U, long long ldu, int R, const void* X, long l
   constexpr int smem = LG_STAGES * 2 * LG_TILE_BYTES;
 #define FERRL_LG(RTV)                                                                                                 \
   case RTV: {                                                                                                         \
-    static bool set = false;                                                                                          \
-    if (!set) {                                                                                                       \
-      cudaFuncSetAttribute(lora_grad_kernel<RTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                 \
-      set = true;                                                                                                     \
-    }                                                                                                                 \
+    if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(lora_grad_kernel<RTV>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                    smem) == cudaSuccess))                                            \
+      return "lora_grad: cannot reserve shared memory";                                                               \
     lora_grad_kernel<RTV><<<grid, 128, smem, stream>>>(static_cast<const __nv_bfloat16*>(U), ldu, R,                  \
                                                        static_cast<const __nv_bfloat16*>(X), ldx, C, M, rows_per_split, \
                                                        partial, counters, out, ldo);                                  \

@@ -24,6 +24,11 @@
 //    it.  The kernels overwrite every slot they later read, so nothing has to be cleared between
 //    calls - but two calls that overlap on the GPU (different streams, no ordering between them)
 //    race on it.  Order them on one stream or with events.
+//  * The address cache is indexed by device ordinal and holds FERRL_NOALLOC_MAX_DEVICES entries; a
+//    call made with a higher ordinal current returns FERRL_NOALLOC_CUDA_ERROR.  Host threads may
+//    make their first calls concurrently.
+//  * Rejected with FERRL_NOALLOC_BAD_ARGS: a negative `window` or `seq_stride`, and a
+//    `tok_stride` smaller than Hkv * D (tokens would overlap).
 //  * Shapes follow the regular op: q [B,Hq,D] bf16 contiguous; k_cache / v_cache bf16 with
 //    `seq_stride` elements between sequences and `tok_stride` between tokens, heads packed
 //    [Hkv,D]; kv_len int32 [B]; out [B,Hq,D] bf16.  D % 8 == 0, D <= 256, Hq/Hkv <= 8.
@@ -34,12 +39,13 @@ extern "C" {
 #endif
 
 #define FERRL_STATIC_WS_FLOATS (4u * 1024u * 1024u)
+#define FERRL_NOALLOC_MAX_DEVICES 64
 
 enum {
   FERRL_NOALLOC_OK = 0,
   FERRL_NOALLOC_TOO_LARGE = 1,   /* workspace need exceeds FERRL_STATIC_WS_FLOATS */
-  FERRL_NOALLOC_BAD_ARGS = 2,    /* null pointer, bad head geometry, n_splits out of [1,16] */
-  FERRL_NOALLOC_CUDA_ERROR = 3,  /* cudaGetDevice / cudaGetSymbolAddress / launch failed */
+  FERRL_NOALLOC_BAD_ARGS = 2,    /* null pointer, bad head geometry or strides, negative window, n_splits out of [1,16] */
+  FERRL_NOALLOC_CUDA_ERROR = 3,  /* cudaGetDevice / cudaGetSymbolAddress / launch failed, or device ordinal >= 64 */
 };
 
 /* `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream). */

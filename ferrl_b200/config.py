@@ -271,6 +271,16 @@ class TensorParallelCfg:
 
 
 @dataclass
+class ExpertParallelCfg:
+    """Experts of a sparse-MoE policy sharded over the data-parallel ranks (rank r owns experts
+    ``[r*E/world, (r+1)*E/world)``); tokens travel to their experts and back through the
+    dispatch/combine kernels.  Requires ``distributed.enabled`` (every rank still rolls out its
+    own prompts) and an adapter recipe that leaves the routed experts frozen."""
+    enabled: bool = False
+    capacity_factor: float = 2.0
+
+
+@dataclass
 class RunConfig:
     task: str = "countdown"
     model_dir: str = ""
@@ -281,6 +291,7 @@ class RunConfig:
     data: DataCfg = field(default_factory=DataCfg)
     distributed: DistributedCfg = field(default_factory=DistributedCfg)
     tensor_parallel: TensorParallelCfg = field(default_factory=TensorParallelCfg)
+    expert_parallel: ExpertParallelCfg = field(default_factory=ExpertParallelCfg)
     trimul: dict = field(default_factory=dict)
     run_health: dict = field(default_factory=dict)
     trainer: TrainerConfig = field(default_factory=TrainerConfig)
@@ -291,7 +302,7 @@ class RunConfig:
     @staticmethod
     def from_json(d: dict) -> "RunConfig":
         _strict(d, {"task", "model_dir", "device", "out_dir", "launch_authentication", "policy", "data",
-                    "distributed", "tensor_parallel", "trimul", "run_health", "trainer"}, "run config")
+                    "distributed", "tensor_parallel", "expert_parallel", "trimul", "run_health", "trainer"}, "run config")
         for req in ("task", "model_dir", "trainer"):
             _require(req in d, f"run config is missing required field {req!r}")
         t = dict(d["trainer"]) if isinstance(d["trainer"], dict) else d["trainer"]
@@ -321,6 +332,7 @@ class RunConfig:
                         policy=block(PolicyCfg, "policy"), data=block(DataCfg, "data"),
                         distributed=block(DistributedCfg, "distributed"),
                         tensor_parallel=block(TensorParallelCfg, "tensor_parallel"),
+                        expert_parallel=block(ExpertParallelCfg, "expert_parallel"),
                         trimul=dict(d.get("trimul", {})), run_health=dict(d.get("run_health", {})),
                         trainer=TrainerConfig.from_json(t), eos_selection=eos_sel)
         cfg.validate()
@@ -351,6 +363,10 @@ class RunConfig:
                      "tensor_parallel needs world_size >= 2 and 0 <= rank < world_size")
             _require(not self.distributed.enabled,
                      "data-parallel and tensor-parallel launches cannot be combined")
+        if self.expert_parallel.enabled:
+            _require(self.distributed.enabled and not tp.enabled,
+                     "expert_parallel shards experts over data-parallel ranks: it needs distributed.enabled and no tensor_parallel")
+            _require(self.expert_parallel.capacity_factor >= 1.0, "expert_parallel.capacity_factor must be >= 1")
         self.trainer.validate()
         from .run_health import validate_run_health
         validate_run_health(self.run_health, self.trainer)
@@ -367,7 +383,8 @@ class RunConfig:
         return {"task": self.task, "model_dir": self.model_dir, "device": self.device, "out_dir": self.out_dir,
                 "launch_authentication": self.launch_authentication, "policy": dataclasses.asdict(self.policy),
                 "data": dataclasses.asdict(self.data), "distributed": dataclasses.asdict(self.distributed),
-                "tensor_parallel": tp, "trimul": self.trimul, "run_health": self.run_health, "trainer": t}
+                "tensor_parallel": tp, "trimul": self.trimul, "run_health": self.run_health, "trainer": t,
+                **({"expert_parallel": dataclasses.asdict(self.expert_parallel)} if self.expert_parallel.enabled else {})}
 
     def digest(self) -> str:
         return canonical_digest(self.to_json(for_consensus=True), b"ferrl-b200/run-config/v1")

@@ -215,7 +215,11 @@ def run_decode_loop(dec, sampler: GrpoSampler, logits, rows, N: int, temperature
             break
         if eos is not None and early_exit_every > 0 and (t + 1) % early_exit_every == 0 and bool(finished.all()):
             break
-        logits = dec.decode(tok)
+        # rows that have emitted EOS are retired: their attention reads no KV from here on
+        if eos is not None and getattr(dec, "supports_retirement", False):
+            logits = dec.decode(tok, ~finished)
+        else:
+            logits = dec.decode(tok)
     return out_tok, out_lp, comp_len
 
 
@@ -251,6 +255,7 @@ class GraphedDecodeStep:
         self.out_tok = torch.full((B, N), self.pad, dtype=torch.int64, device=dev)
         self.out_lp = torch.zeros((B, N), dtype=torch.float32, device=dev)
         self.pad_t = torch.full((B,), self.pad, dtype=torch.int64, device=dev)
+        self.kv_tokens_read = torch.zeros((), dtype=torch.int64, device=dev)   # per layer, summed over steps
 
     def _body(self):
         tok, lp = self.sampler.sample(self.logits, self.rows, 0, self.temperature, self.top_p, draw_dev=self.draw)
@@ -261,7 +266,12 @@ class GraphedDecodeStep:
         self.comp_len += (~self.finished).to(torch.int64)
         if self.eos is not None:
             self.finished |= tok == self.eos
-        self.logits.copy_(self._decode(tok))
+        if self.eos is not None and getattr(self.dec, "supports_retirement", False):
+            # retired rows stay in the fixed-shape batch but attend to nothing (see _step_lengths)
+            self.kv_tokens_read += self.dec.kv_tokens_read(~self.finished).to(torch.int64)
+            self.logits.copy_(self._decode(tok, ~self.finished))
+        else:
+            self.logits.copy_(self._decode(tok))
         self.draw += 1
 
     @torch.no_grad()
@@ -277,6 +287,7 @@ class GraphedDecodeStep:
         self.comp_len.zero_()
         self.out_tok.fill_(self.pad)
         self.out_lp.zero_()
+        self.kv_tokens_read.zero_()
         kv0 = self.dec.kv_len.clone()
         if self.graph is None:
             # one eager step warms every kernel (and lazy one-time allocations) before capture; its
@@ -291,6 +302,7 @@ class GraphedDecodeStep:
             self.comp_len.zero_()
             self.out_tok.fill_(self.pad)
             self.out_lp.zero_()
+            self.kv_tokens_read.zero_()
             before = C.launches()
             g = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g):

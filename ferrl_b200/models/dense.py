@@ -142,7 +142,7 @@ class DenseLayer(nn.Module):
         return self.down.forward_reduce(mid, comm, merged, residual=h)
 
     # one-token forward against the cache (rollout; merged weights)
-    def decode_fused(self, h, ss, kv_len, cos, sin, k_cache, v_cache, kv_next, pos, table=None):
+    def decode_fused(self, h, ss, kv_len, cos, sin, k_cache, v_cache, kv_next, pos, table=None, prefix=None):
         """One decode step of the layer in six kernels.  The two RMSNorms are folded around the
         projections: ``ss`` ``[parts, B]`` holds partial row sums of squares of ``h`` (written by the
         epilogue of the projection that produced ``h``), the QKV and gate/up projections scale their
@@ -164,14 +164,14 @@ class DenseLayer(nn.Module):
             else:
                 ops_cache_write(k_cache, v_cache, k4[:, 0], v.reshape(B, self.hkv, self.D), kv_len)
             qr = q4[:, 0]
-        a = _c.decode_attention(qr, k_cache, v_cache, kv_next, scale=self.scale, block_table=table)
+        a = _c.decode_attention(qr, k_cache, v_cache, kv_next, scale=self.scale, block_table=table, **_prefix_kw(prefix))
         wo = self.o.weight_merged if self.o.weight_merged is not None else self.o.weight
         h2, ss2 = _c.gemm_norm(a.reshape(B, self.hq * self.D), wo, h, None, 0.0, None, True)
         mid, _ = _c.gemm_norm(h2, self.gate_up.weight_decode, None, ss2, self.eps, self.act)
         wd = self.down.weight_merged if self.down.weight_merged is not None else self.down.weight
         return _c.gemm_norm(mid, wd, h2, None, 0.0, None, True)
 
-    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None, table=None):
+    def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm: Comm, kv_next=None, pos=None, table=None, prefix=None):
         B = h.shape[0]
         x = ops.rmsnorm(h, self.input_norm, self.eps)
         qkv = self.qkv.forward_merged(x)
@@ -184,7 +184,7 @@ class DenseLayer(nn.Module):
                                         pos if pos is not None else kv_len[:, None].long(), k_cache, v_cache, kv_len, table)
             if qr is not None:
                 a = _c.decode_attention(qr, k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
-                                        scale=self.scale, block_table=table)
+                                        scale=self.scale, block_table=table, **_prefix_kw(prefix))
                 o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, merged=True)
                 x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
                 return self.down.forward_reduce(self.gate_up.forward_merged_glu(x, self.act), comm, merged=True,
@@ -198,7 +198,7 @@ class DenseLayer(nn.Module):
             from ..ops import cuda as _c
             _c.kv_append_paged(k_cache, v_cache, k[:, 0].contiguous(), v[:, 0], kv_len, table)
             a = _c.decode_attention(q[:, 0], k_cache, v_cache, kv_next if kv_next is not None else kv_len + 1,
-                                    scale=self.scale, block_table=table)
+                                    scale=self.scale, block_table=table, **_prefix_kw(prefix))
         elif table is not None:
             # eager restatement of the paged path (CPU tests of the block-table logic)
             page = k_cache.shape[1]
@@ -218,6 +218,12 @@ class DenseLayer(nn.Module):
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps)
         return self.down.forward_reduce(self.gate_up.forward_merged_glu(x, self.act), comm, merged=True,
                                         residual=h)
+
+
+def _prefix_kw(prefix) -> dict:
+    """``prefix = (prefix_len [P] int32, group)`` of a paged grouped cache -> keyword arguments of
+    ``decode_attention`` (empty when the cache has no shared prefix)."""
+    return {} if prefix is None else {"prefix_len": prefix[0], "group": prefix[1]}
 
 
 # Opt-in (FERRL_DECODE_FOLD=1): on the Qwen3-8B benchmark the folded chain launches 37 % fewer kernels
@@ -467,18 +473,37 @@ class DenseCachedDecoder:
             self.v[i].copy_(self.v[i][src])
         self.kv_len.copy_(self.kv_len[src])
 
-    @torch.no_grad()
-    def decode(self, tokens: torch.Tensor) -> torch.Tensor:
-        """Feed one token per row; returns next-token logits ``[B, V]`` float32."""
-        return self.decode_native(tokens).float()
+    supports_retirement = True      # ``decode(tokens, active)``: see ``_step_lengths``
+
+    def _step_lengths(self, active: Optional[torch.Tensor]):
+        """Attention length of every row for this token and the length increment afterwards.
+        A retired row (``active[b]`` false: it has emitted EOS) attends to nothing, so the decode
+        attention kernels read none of its KV, and its cache length stays frozen (its pad token is
+        written over the same slot every step).  The reference drops such rows from the batch
+        (lm_policy.rs:736-743); here the batch keeps its shape, so a captured CUDA graph stays valid,
+        and the projections, whose cost is the weight stream, do not care about the row count."""
+        if active is None:
+            return self.kv_len + 1, None
+        inc = active.to(torch.int32)
+        return (self.kv_len + 1) * inc, inc
+
+    def kv_tokens_read(self, active: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Tokens of KV that the next ``decode`` call's attention reads per layer (sum of the lengths
+        handed to the kernel): the quantity row retirement shrinks."""
+        return self._step_lengths(active)[0].sum()
 
     @torch.no_grad()
-    def decode_native(self, tokens: torch.Tensor) -> torch.Tensor:
+    def decode(self, tokens: torch.Tensor, active: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Feed one token per row; returns next-token logits ``[B, V]`` float32."""
+        return self.decode_native(tokens, active).float()
+
+    @torch.no_grad()
+    def decode_native(self, tokens: torch.Tensor, active: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``decode`` with the logits left in the head GEMM's output dtype (bf16 for a bf16 model): the
         device sampler reads them as they are, which saves the fp32 copy of ``[B, V]`` every token."""
         m = self.m
         h = ops.embedding(tokens, m.embed)
-        kv_next = self.kv_len + 1                 # shared by every layer: computed once per token
+        kv_next, inc = self._step_lengths(active)  # shared by every layer: computed once per token
         pos = self.kv_len[:, None].long()
         if _decode_fused_ok(m.layers, h, self.comm) and m.cos.dtype == torch.float32:
             from ..ops import cuda as _c
@@ -488,7 +513,7 @@ class DenseCachedDecoder:
         else:
             for i, layer in enumerate(m.layers):
                 h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos)
-        self.kv_len += 1
+        self.kv_len += 1 if inc is None else inc
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
         return ops.lora_linear(h, m.head_weight(), None, None)
 
@@ -523,6 +548,14 @@ class DensePagedDecoder(DenseCachedDecoder):
         self.v = [torch.zeros(n_pages, page, hkv, D, dtype=dt, device=dev) for _ in model.layers]
         self.table = torch.zeros(batch, self.pages_per_row, dtype=torch.int32, device=dev)
         self.kv_len = torch.zeros(batch, dtype=torch.int32, device=dev)
+        # tokens of each prompt that live in shared pages: decode attention streams them once per group
+        self.prefix_len = torch.zeros(self.prompts, dtype=torch.int32, device=dev)
+        from ..ops import cuda as _c
+        self.share_prefix = (os.environ.get("FERRL_PREFIX_ATTN", "1") != "0" and ops.native(self.k[0])
+                             and _c.prefix_attention_supported(D, model.layers[0].hq // hkv, group))
+
+    def _prefix(self):
+        return (self.prefix_len, self.group) if self.share_prefix else None
 
     @torch.no_grad()
     def prefill(self, ids: torch.Tensor, lens: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -548,6 +581,7 @@ class DensePagedDecoder(DenseCachedDecoder):
         shared_id = p_of_row[:, None] * ppr + j
         private_id = self.shared_pages + torch.arange(self.batch, device=dev)[:, None] * ppr + (j - full_r).clamp(min=0)
         self.table.copy_(torch.where(j < full_r, shared_id, private_id).to(torch.int32))
+        self.prefix_len.copy_((full * page).to(torch.int32))
         # tail of every prompt (< PAGE tokens) goes to the first private page of each of its rows
         tail_idx = (full[:, None] * page + torch.arange(page, device=dev)[None, :]).clamp(max=L - 1)     # [P, PAGE]
         first_private = (self.shared_pages + torch.arange(self.batch, device=dev) * ppr).long()
@@ -568,19 +602,21 @@ class DensePagedDecoder(DenseCachedDecoder):
             raise ValueError("group size differs from the one this cache was built for")
 
     @torch.no_grad()
-    def decode_native(self, tokens: torch.Tensor) -> torch.Tensor:
+    def decode_native(self, tokens: torch.Tensor, active: Optional[torch.Tensor] = None) -> torch.Tensor:
         m = self.m
         h = ops.embedding(tokens, m.embed)
-        kv_next = self.kv_len + 1
+        kv_next, inc = self._step_lengths(active)
         pos = self.kv_len[:, None].long()
         if _decode_fused_ok(m.layers, h, self.comm) and m.cos.dtype == torch.float32:
             from ..ops import cuda as _c
             ss = _c.row_sumsq(h)
             for i, layer in enumerate(m.layers):
-                h, ss = layer.decode_fused(h, ss, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], kv_next, pos, self.table)
+                h, ss = layer.decode_fused(h, ss, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], kv_next, pos, self.table,
+                                            self._prefix())
         else:
             for i, layer in enumerate(m.layers):
-                h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos, self.table)
-        self.kv_len += 1
+                h = layer.decode(h, self.kv_len, m.cos, m.sin, self.k[i], self.v[i], self.comm, kv_next, pos, self.table,
+                                 self._prefix())
+        self.kv_len += 1 if inc is None else inc
         h = ops.rmsnorm(h, m.final_norm, m.spec.rms_norm_eps)
         return ops.lora_linear(h, m.head_weight(), None, None)

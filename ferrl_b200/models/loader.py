@@ -33,6 +33,7 @@ class LoaderOpts:
     quantization: BaseQuantization = BaseQuantization.NONE
     remat: bool = False
     tp: Optional[tuple[int, int]] = None  # (rank, world)
+    ep: Optional[tuple[int, int]] = None  # (rank, world): expert parallelism, sparse-MoE families only
     full_ft: bool = False
     adapter_seed: int = 0
     max_position_embeddings: Optional[int] = None

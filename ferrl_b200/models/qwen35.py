@@ -153,7 +153,7 @@ class _Mlp(nn.Module):
 
 class Qwen35Layer(nn.Module):
     def __init__(self, spec: Qwen35Spec, kind: str, lora: Optional[LoraSpec], tg: Qwen35LoraTargets, dtype, device,
-                 keep_transpose, quant, trainable_base=False):
+                 keep_transpose, quant, trainable_base=False, ep_world: int = 1):
         super().__init__()
         self.spec, self.kind = spec, kind
         H, D = spec.hidden_size, spec.head_dim
@@ -197,8 +197,9 @@ class Qwen35Layer(nn.Module):
             self.mlp = None
             self.shared = _Mlp(H, m.shared_intermediate, lora, tg, kw, spec.activation) if m.shared_intermediate else None
             reg("router", torch.zeros(m.num_experts, H, dtype=dtype, device=device))
-            reg("experts_gate_up", torch.zeros(m.num_experts, 2 * m.moe_intermediate, H, dtype=dtype, device=device))
-            reg("experts_down", torch.zeros(m.num_experts, H, m.moe_intermediate, dtype=dtype, device=device))
+            e_local = m.num_experts // ep_world          # expert parallelism: this rank's contiguous block of experts
+            reg("experts_gate_up", torch.zeros(e_local, 2 * m.moe_intermediate, H, dtype=dtype, device=device))
+            reg("experts_down", torch.zeros(e_local, H, m.moe_intermediate, dtype=dtype, device=device))
             reg("shared_gate", torch.zeros(1, H, dtype=dtype, device=device))
         self.eps = spec.rms_norm_eps
 
@@ -328,10 +329,21 @@ class Qwen35Layer(nn.Module):
 class Qwen35GradModel(nn.Module):
     def __init__(self, spec: Qwen35Spec, lora: Optional[LoraSpec] = None, targets: Optional[Qwen35LoraTargets] = None, *,
                  dtype=torch.float32, device=None, keep_transpose: Optional[bool] = None,
-                 quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False, full_ft: bool = False):
+                 quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False, full_ft: bool = False,
+                 ep: Optional[tuple] = None):
+        """``ep = (rank, world)``: hold only this rank's ``E / world`` routed experts (expert
+        parallelism, see ``ferrl_b200.parallel.ep``); everything else is replicated."""
         super().__init__()
         spec.validate()
         self.spec, self.lora, self.remat, self.full_ft, self.dtype = spec, lora, remat, full_ft, dtype
+        self.ep = ep if ep is not None and ep[1] > 1 else None
+        if self.ep is not None:
+            if spec.moe is None:
+                raise ValueError("expert parallelism needs a sparse-MoE model")
+            if spec.moe.num_experts % self.ep[1] or not 0 <= self.ep[0] < self.ep[1]:
+                raise ValueError(f"{spec.moe.num_experts} experts do not split over expert-parallel world {self.ep[1]}")
+            if full_ft:
+                raise ValueError("expert parallelism keeps the routed experts frozen: not available with full fine-tuning")
         self.targets = targets or Qwen35LoraTargets()
         dev = torch.device(device) if device is not None else torch.device("cpu")
         if keep_transpose is None:
@@ -352,7 +364,8 @@ class Qwen35GradModel(nn.Module):
             self.register_buffer("lm_head", torch.zeros_like(emb), persistent=False)
         self.register_buffer("head_t", None, persistent=False)
         self.layers = nn.ModuleList([Qwen35Layer(spec, k, None if full_ft else lora, self.targets, dtype, dev,
-                                                 keep_transpose, quant, full_ft) for k in spec.layer_types])
+                                                 keep_transpose, quant, full_ft,
+                                                 ep_world=self.ep[1] if self.ep else 1) for k in spec.layer_types])
         cos, sin = ops.rope_tables(ops.default_inv_freq(spec.rot_dim, spec.rope_theta), spec.max_position_embeddings)
         self.register_buffer("cos", cos.to(dev), persistent=False)
         self.register_buffer("sin", sin.to(dev), persistent=False)
@@ -400,7 +413,7 @@ class Qwen35GradModel(nn.Module):
         self.embed.copy_(rnd(self.embed.shape))
         if self.lm_head is not None:
             self.lm_head.copy_(rnd(self.lm_head.shape))
-        for l in self.layers:
+        for li, l in enumerate(self.layers):
             for p in l.projections():
                 p.set_weight(rnd(p.weight.shape))
                 p.init_adapters(g)
@@ -409,10 +422,27 @@ class Qwen35GradModel(nn.Module):
                 l.A_log.copy_(torch.log(torch.rand(l.A_log.shape, generator=g) * 15 + 1).to(dev))
             if self.spec.moe is not None:
                 l.router.copy_(rnd(l.router.shape, 1.0))          # N(0,1) router logits scale with the input norm
-                l.experts_gate_up.copy_(rnd(l.experts_gate_up.shape))
-                l.experts_down.copy_(rnd(l.experts_down.shape))
+                self._init_experts(l, li, seed, std, rnd)
                 l.shared_gate.copy_(rnd(l.shared_gate.shape))
         self.refresh_head()
+
+    def _init_experts(self, l, li: int, seed: int, std: float, rnd):
+        """Random experts.  Each expert's values are a pure function of (seed, layer, expert), drawn on
+        the parameter's device, so an expert-parallel rank generates exactly its own block and the
+        world as a whole holds the same experts as a single rank would."""
+        E = self.spec.moe.num_experts
+        if self.ep is None and l.experts_gate_up.device.type == "cpu":
+            l.experts_gate_up.copy_(rnd(l.experts_gate_up.shape))
+            l.experts_down.copy_(rnd(l.experts_down.shape))
+            return
+        e_local = l.experts_gate_up.shape[0]
+        first = (self.ep[0] * e_local) if self.ep else 0
+        dev = l.experts_gate_up.device
+        for j in range(e_local):
+            gg = torch.Generator(device=dev).manual_seed((seed * 1000003 + li * 4099 + first + j) & 0x7fffffff)
+            l.experts_gate_up[j].copy_((torch.randn(l.experts_gate_up.shape[1:], generator=gg, device=dev) * std).to(self.dtype))
+            l.experts_down[j].copy_((torch.randn(l.experts_down.shape[1:], generator=gg, device=dev) * std).to(self.dtype))
+        del E
 
     # ------------------------------------------------------------- forward
     def forward_hidden(self, ids, comm: Optional[Comm] = None, merged=False, detached=False):
@@ -554,15 +584,17 @@ def load_qwen35_weights(model: Qwen35GradModel, src) -> None:
             l.mlp.down.set_weight(to(src.get(b + "mlp.down_proj.weight")))
         else:
             l.router.copy_(to(src.get(b + "mlp.gate.weight")))
+            e_local = l.experts_gate_up.shape[0]
+            first = model.ep[0] * e_local if model.ep else 0      # expert parallelism: read this rank's experts only
             if src.has(b + "mlp.experts.gate_up_proj"):        # fused 3-D layout
-                l.experts_gate_up.copy_(to(src.get(b + "mlp.experts.gate_up_proj")))
-                l.experts_down.copy_(to(src.get(b + "mlp.experts.down_proj")))
+                l.experts_gate_up.copy_(to(src.get(b + "mlp.experts.gate_up_proj")[first:first + e_local]))
+                l.experts_down.copy_(to(src.get(b + "mlp.experts.down_proj")[first:first + e_local]))
             else:                                               # one tensor per expert and projection
-                for e in range(spec.moe.num_experts):
-                    eb = f"{b}mlp.experts.{e}."
-                    l.experts_gate_up[e].copy_(to(torch.cat([src.get(eb + "gate_proj.weight"),
+                for j in range(e_local):
+                    eb = f"{b}mlp.experts.{first + j}."
+                    l.experts_gate_up[j].copy_(to(torch.cat([src.get(eb + "gate_proj.weight"),
                                                              src.get(eb + "up_proj.weight")], 0)))
-                    l.experts_down[e].copy_(to(src.get(eb + "down_proj.weight")))
+                    l.experts_down[j].copy_(to(src.get(eb + "down_proj.weight")))
             l.shared_gate.copy_(to(src.get(b + "mlp.shared_expert_gate.weight")))
             if l.shared is not None:
                 l.shared.gate_up.set_weight(to(torch.cat([src.get(b + "mlp.shared_expert.gate_proj.weight"),
@@ -580,7 +612,7 @@ def load_qwen35(model_dir: str, opts):
     if opts.tp is not None:
         raise ValueError("tensor parallelism is not supported for the Qwen3.5 family")
     model = Qwen35GradModel(spec, None if opts.full_ft else opts.lora, dtype=opts.dtype, device=opts.device,
-                            quant=opts.quantization, remat=opts.remat, full_ft=opts.full_ft)
+                            quant=opts.quantization, remat=opts.remat, full_ft=opts.full_ft, ep=opts.ep)
     src = TensorSource(model_dir)
     load_qwen35_weights(model, src)
     g = torch.Generator().manual_seed(opts.adapter_seed)

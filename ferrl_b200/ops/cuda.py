@@ -361,11 +361,30 @@ def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, kv_len=None,
                         int(variant))
 
 
-def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0, block_table=None):
+_PREFIX_SHAPES = {(128, 4, 8), (128, 4, 4), (128, 8, 4), (128, 8, 2), (128, 2, 8), (64, 4, 8), (64, 4, 4), (128, 2, 16)}
+
+
+def prefix_attention_supported(head_dim: int, q_per_kv: int, group: int) -> bool:
+    """Whether ``decode_attention(..., prefix_len=...)`` has a kernel for this (head_dim, query heads
+    per KV head, rows per group) triple."""
+    return (head_dim, q_per_kv, group) in _PREFIX_SHAPES
+
+
+def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0, variant=0, block_table=None,
+                     prefix_len=None, group=1, prefix_splits=0):
     """``variant`` 0 picks the tensor-core pipelined kernel where it applies, 2 the scalar pipelined
-    one, 1 the register-resident one (both kept for uncovered head shapes and as cross-checks)."""
+    one, 1 the register-resident one (both kept for uncovered head shapes and as cross-checks).
+    ``prefix_len`` ``[B / group]`` int32 (paged cache only): the first ``prefix_len[b // group]`` keys of
+    row ``b`` are shared by the ``group`` rows of its group (same pages in ``block_table``); they are
+    streamed once per group by a kernel that applies them to all the group's queries, each row's
+    remaining keys by the per-row kernel, and a combine kernel merges the two partial results."""
     if not _bf16(q) or q.shape[-1] % 8 or q.shape[-1] > 256:
         return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
+    if block_table is not None and prefix_len is not None and not window:
+        B = q.shape[0]
+        ps = int(prefix_splits) or max(1, min(4, 296 // max(1, (B // group) * k_cache.shape[2])))   # about two CTAs per SM
+        return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), 0, 1, block_table,
+                                 k_cache.shape[1], 0, prefix_len, int(group), ps)
     if block_table is not None:
         # paged pool [n_pages, page, Hkv, D]; row b's token t is in page block_table[b, t // page]
         return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), int(window or 0),

@@ -156,6 +156,7 @@ def decode_attention(q, k_cache, v_cache, kv_len, *, scale: float, window: int =
     scores = torch.einsum("bhd,bshd->bhs", q.float(), kf) * scale
     scores = scores.masked_fill(~allowed[:, None, :], float("-inf"))
     p = torch.softmax(scores, dim=-1)
+    p = torch.where(allowed.any(dim=1)[:, None, None], p, torch.zeros_like(p))   # a row with no keys attends to nothing
     return torch.einsum("bhs,bshd->bhd", p, vf).to(q.dtype)
 
 

@@ -143,10 +143,13 @@ class TrainOutcome:
 
 
 def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_dirty: bool = False,
-                        tokenizer=None, model_and_identity=None, preemption_flag=None) -> TrainOutcome:
+                        tokenizer=None, model_and_identity=None, preemption_flag=None,
+                        heap_factory=None) -> TrainOutcome:
     """The whole ``train`` verb. ``tokenizer`` / ``model_and_identity`` may be injected (tests,
     synthetic runs); otherwise they are loaded from ``cfg.model_dir``.  ``preemption_flag`` is a
-    ``threading.Event`` the caller sets to stop cooperatively after the step in flight."""
+    ``threading.Event`` the caller sets to stop cooperatively after the step in flight.
+    ``heap_factory(comm, device, wait_limit_s)`` replaces the symmetric heap (tests run the
+    tensor-/expert-parallel wiring against a fake on CPU)."""
     comm = comm or SoloComm()
     T.init_tracing()
     ident = source_identity()
@@ -168,9 +171,11 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     # ---- policy
     pc = cfg.policy
     lora = LoraSpec(pc.lora_rank, pc.lora_alpha, DenseLoraTargets.parse(pc.lora_targets))
+    ep_on = cfg.expert_parallel.enabled and comm.world_size > 1
     opts = LoaderOpts(dtype=_DTYPES[pc.base_dtype], device=device, lora=lora,
                       quantization=BaseQuantization(pc.base_quantization), remat=pc.activation_checkpointing,
                       tp=(cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size) if cfg.tensor_parallel.enabled else None,
+                      ep=(comm.rank, comm.world_size) if ep_on else None,
                       adapter_seed=pc.seed)
     model, pident = model_and_identity or load_auto_policy(cfg.model_dir, opts)
     if tokenizer is None:
@@ -182,6 +187,11 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     policy = LmPolicy(model, GrpoSampler(pc.seed, cfg.trainer.temperature), comm if topology == "tp" else None,
                       pad_token_id=cfg.trainer.eos_token_id or 0,
                       score_microbatch=cfg.trainer.backward_microbatch_size)
+    parallel_rt = build_parallel_runtime(cfg, comm, device, model, topology, heap_factory=heap_factory)
+    if ep_on:
+        # dispatch and combine are collectives: every rank must issue the same number of model calls,
+        # so no rank leaves the decode loop early and no rank skips a degenerate group on its own
+        policy.early_exit_every = 0
     # ---- launch manifest + run dir
     samples_sha = hashlib.sha256("\n".join(s.key() for s in train_samples).encode()).hexdigest()
     launch_sha_seed = hashlib.sha256((run_id + cfg.digest()).encode()).digest()
@@ -214,12 +224,18 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
         from .parallel.dp import FusedDpStep
         fused = FusedDpStep.create(comm, policy.trainable_params(), torch.device(device))
     trainer = Trainer(policy, tokenizer, reward_fn, train_samples, cfg.trainer, comm=comm, topology=topology,
-                      run_dir=run_dir, binding=binding, candidate_writer=cand_writer, fused_dp_step=fused)
+                      run_dir=run_dir, binding=binding, candidate_writer=cand_writer, fused_dp_step=fused,
+                      parallel_runtime=parallel_rt, lockstep_model_calls=ep_on)
     if preemption_flag is not None:
         trainer.with_preemption_flag(preemption_flag)
-    with T.run_span(comm.rank, comm.world_size):
-        start = trainer.resume_latest()
-        stop = trainer.train(start)
+    try:
+        with T.run_span(comm.rank, comm.world_size):
+            start = trainer.resume_latest()
+            stop = trainer.train(start)
+    except BaseException:
+        if parallel_rt is not None:
+            parallel_rt.close()
+        raise
     # ---- health, eval, candidates (rank 0 owns publication)
     rows = trainer.history
     cands = T.read_candidates(run_dir.candidates_path) if comm.rank == 0 else []
@@ -236,7 +252,37 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     ranked = load_and_rank_candidates(run_dir.root, steps=cfg.trainer.steps, group_size=cfg.trainer.group_size,
                                       max_new_tokens=cfg.trainer.max_new_tokens, rank=0,
                                       world_size=comm.world_size) if comm.rank == 0 else []
+    if parallel_rt is not None:
+        parallel_rt.close()
     return TrainOutcome(run_dir.root, run_id, stop.value, len(rows), health, report, ranked)
+
+
+def build_parallel_runtime(cfg: RunConfig, comm: Comm, device: str, model, topology: str, heap_factory=None):
+    """The peer-memory data plane of a tensor- or expert-parallel launch (``None`` otherwise): a
+    symmetric heap, the fused GEMM -> all-reduce and activation all-reduce registered for the
+    tensor-parallel communicator, and the expert-parallel dispatch/combine runtime.  Buffer sizes come
+    from the largest forward call the trainer makes (scoring micro-batch rows x longest sequence)."""
+    tp_on = topology == "tp" and comm.world_size > 1
+    ep_on = cfg.expert_parallel.enabled and comm.world_size > 1
+    if not (tp_on or ep_on):
+        return None
+    from .parallel.runtime import ParallelRuntime
+    spec = model.spec
+    t = cfg.trainer
+    rows_per_call = t.backward_microbatch_size if t.backward_microbatch_size > 0 else t.prompts_per_item * t.group_size
+    tokens_cap = min(int(getattr(spec, "max_position_embeddings", 4096)), t.max_new_tokens + 2048)
+    max_rows = min(max(rows_per_call, t.prompts_per_item * t.group_size) * tokens_cap, 1 << 16)
+    ep = None
+    if ep_on:
+        moe = getattr(spec, "moe", None)
+        if moe is None:
+            raise OrchestrationError("expert_parallel.enabled needs a sparse-MoE policy")
+        if moe.num_experts % comm.world_size:
+            raise OrchestrationError(f"{moe.num_experts} experts do not split over {comm.world_size} ranks")
+        ep = {"num_experts": moe.num_experts, "hidden": spec.hidden_size, "max_tokens": max_rows, "top_k": moe.top_k,
+              "capacity_factor": cfg.expert_parallel.capacity_factor}
+    return ParallelRuntime.create(comm, device, tensor_parallel=tp_on, hidden=spec.hidden_size, max_rows=max_rows,
+                                  expert_parallel=ep, heap_factory=heap_factory)
 
 
 def load_and_rank_candidates(run_root: str, require_signed: bool = True, *, steps: Optional[int] = None,

@@ -153,7 +153,8 @@ class GemmAllReducer:
         # ready[tile][rank] and done[tile] flags, then the device-resident call counter and its CTA counter
         self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2) * 4)
         self.flags.local.zero_()
-        torch.cuda.synchronize(heap.device)
+        if torch.device(heap.device).type == "cuda":
+            torch.cuda.synchronize(heap.device)
         if heap.world > 1:
             heap.comm.barrier()   # nobody signals into flags that are still being cleared
         self.epoch = 0

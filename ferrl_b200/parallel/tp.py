@@ -98,11 +98,10 @@ def all_reduce_sum_value(x: torch.Tensor, comm: Comm) -> torch.Tensor:
     ``Comm`` seam (f32/f64 gate) and cast back."""
     if comm.world_size == 1:
         return x
-    if x.is_cuda:
-        from . import symm
-        fused = symm.try_all_reduce(x, comm)
-        if fused is not None:
-            return fused
+    from . import symm
+    fused = symm.try_all_reduce(x, comm)      # None unless a peer-memory reducer is registered for this communicator
+    if fused is not None:
+        return fused
     staged = x.detach().to(torch.float32).contiguous().clone()
     comm.all_reduce_sum([staged])
     return staged.to(x.dtype)

@@ -175,8 +175,15 @@ class Trainer:
                  config: TrainerConfig, *, comm: Optional[Comm] = None, topology: str = "dp",
                  run_dir: Optional[RunDir] = None, binding: Optional[CheckpointBinding] = None,
                  candidate_writer: Optional[CandidateWriter] = None, adam_eps: float = 1e-8,
-                 fused_dp_step=None):
+                 fused_dp_step=None, parallel_runtime=None, lockstep_model_calls: bool = False):
+        """``parallel_runtime``: the launch's peer-memory data plane (``parallel.runtime.ParallelRuntime``);
+        its status word is checked once per step, before the optimizer.  ``lockstep_model_calls``:
+        every rank issues the same number of model calls per window (expert parallelism: dispatch and
+        combine are collectives), so locally degenerate groups are scored and trained with their zero
+        advantages instead of being skipped."""
         config.validate()
+        self.parallel_runtime = parallel_runtime
+        self.lockstep_model_calls = bool(lockstep_model_calls)
         self.config = config
         self.policy = policy
         self.tokenizer = tokenizer
@@ -346,7 +353,7 @@ class Trainer:
             stats.completion_tokens += g.completion_tokens
             stats.completion_len_max = max(stats.completion_len_max, max(g.rollout.completion_lens))
             stats.dropped_rows += grpo.zero_mask_rows(g.mask.tolist()) if g.truncated else 0
-        live = [g for g in groups if g.live or beta > 0.0]
+        live = [g for g in groups if g.live or beta > 0.0 or self.lockstep_model_calls]
         stats.live_groups += len(live)
         if not live:
             return None
@@ -464,6 +471,11 @@ class Trainer:
         # every rank must have finished (or failed) its local backward before anyone enters the
         # gradient collective; a failure anywhere raises on all ranks here, not at a timeout
         self._rendezvous(local_backward, "backward")
+        if self.parallel_runtime is not None:
+            # a bounded peer wait that ran out inside a fused tensor-/expert-parallel kernel leaves a
+            # status word behind: raise CommTimeout here, before the optimizer touches anything
+            self._rendezvous(lambda: self.parallel_runtime.check("tensor-/expert-parallel kernels of this step"),
+                             "peer-memory status")
         self._phase("grad_reduce_optimizer")
         world = self.comm.world_size
         if self.fused_dp_step is not None:
@@ -563,6 +575,10 @@ class Trainer:
             for e in range(c.mu):
                 agg["epoch"] = e
                 self.accumulate_step(live, window_tokens, beta, lr, stats, agg)
+        elif self.parallel_runtime is not None:
+            # no update this window: the rollout and scoring kernels still ran over peer memory
+            self._rendezvous(lambda: self.parallel_runtime.check("tensor-/expert-parallel kernels of this step"),
+                             "peer-memory status")
         return self._build_metrics(step, lr, beta, stats, agg), local_tokens
 
     def _build_metrics(self, step, lr, beta, stats: WindowStats, agg: dict) -> Metrics:

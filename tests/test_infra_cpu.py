@@ -962,3 +962,99 @@ def test_cli_trimul_baseline_times_the_packaged_reference_submission(tmp_path, c
     assert seen[0] == open(os.path.join(default_eval_dir(), "reference_submission.py")).read()
     with pytest.raises(SystemExit):
         cli.main(["verifier-executor", "--socket", str(tmp_path / "s.sock")])      # --client-uid is mandatory
+
+
+class _FakeHeap:
+    """Stands in for the symmetric heap on CPU ranks: buffers are plain host tensors, the one-shot
+    all-reduce goes through the rank's communicator, and the status word can be made to report a
+    peer wait that ran out."""
+
+    def __init__(self, comm, device, wait_limit_s):
+        from ferrl_b200.parallel.symm import SymmBuffer
+        self._SymmBuffer = SymmBuffer
+        self.comm, self.device = comm, torch.device("cpu")
+        self.rank, self.world = comm.rank, comm.world_size
+        self.wait_limit_s, self.poisoned = wait_limit_s, None
+        self.reduces = self.checks = 0
+        self.fail_check = False
+
+    def alloc(self, nbytes):
+        return self._SymmBuffer(torch.zeros((nbytes + 255) // 256 * 256, dtype=torch.uint8), [0] * self.world)
+
+    def guard(self):
+        pass
+
+    def all_reduce_(self, buf, out):
+        self.reduces += 1
+        staged = buf.local.view(out.dtype)[:out.numel()].view(out.shape).to(torch.float32).clone()
+        self.comm.all_reduce_sum([staged])
+        out.copy_(staged.to(out.dtype))
+        return out
+
+    def check(self, what):
+        self.checks += 1
+        if self.fail_check:
+            from ferrl_b200.comm import CommTimeout
+            self.poisoned = what
+            raise CommTimeout(f"{what}: kernel reported status 4 (peer wait timed out)")
+
+    def close(self):
+        pass
+
+
+def _tp_cfg(tmp_path, rank, **trainer):
+    t = {"steps": 2, "group_size": 4, "max_new_tokens": 4, "eos_token_id": "none", "truncation_masking": False,
+         "prompts_per_item": 1}
+    t.update(trainer)
+    return RunConfig.from_json({"task": "countdown", "model_dir": os.path.join(FIX, "tiny_qwen3"), "out_dir": str(tmp_path),
+                                "launch_authentication": "unsigned_development",
+                                "policy": {"lora_rank": 4, "lora_alpha": 8.0}, "data": {"train_n": 8, "eval_n": 0},
+                                "tensor_parallel": {"enabled": True, "rank": rank, "world_size": 2}, "trainer": t})
+
+
+def test_train_verb_with_tensor_parallel_reaches_the_registered_peer_memory_reducer(tmp_path):
+    """``tensor_parallel.enabled`` makes the train verb build the peer-memory runtime and register its
+    reducers for the tensor-parallel communicator: every row-parallel reduction of rollout, scoring and
+    backward goes through them (here a fake heap on two thread ranks), the status word is checked once
+    per step, and the result equals the run over the plain ``Comm`` seam."""
+    from ferrl_b200.comm import run_ranks
+    from ferrl_b200.orchestration import run_cli_train_setup
+    from ferrl_b200.parallel import symm
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    heaps = {}
+
+    def factory(comm, device, limit):
+        heaps[comm.rank] = _FakeHeap(comm, device, limit)
+        return heaps[comm.rank]
+
+    def body(comm, use_fake):
+        out = run_cli_train_setup(_tp_cfg(tmp_path / ("fake" if use_fake else "seam"), comm.rank), comm, allow_dirty=True,
+                                  tokenizer=SyntheticTokenizer(32, 4, 8), heap_factory=factory if use_fake else None)
+        assert symm.gemm_all_reducer(comm) is None and symm._REDUCERS.get(id(comm)) is None    # closed with the run
+        rows = [json.loads(l) for l in open(os.path.join(out.run_dir, "metrics.jsonl"))] if comm.rank == 0 else []
+        return out.steps_run, [(r["loss"], r["grad_norm"]) for r in rows]
+    fake = run_ranks(2, lambda c: body(c, True), timeout=120)
+    assert fake[0][0] == 2
+    for r in (0, 1):
+        assert heaps[r].reduces > 0 and heaps[r].checks == 2          # one status check per optimizer step
+    assert heaps[0].reduces == heaps[1].reduces
+    seam = run_ranks(2, lambda c: body(c, False), timeout=120)
+    assert seam[0][1] == fake[0][1]                                   # same sums, same order: identical metrics
+
+
+def test_train_verb_turns_a_peer_wait_timeout_into_comm_timeout_on_every_rank(tmp_path):
+    from ferrl_b200.comm import CommError, run_ranks
+    from ferrl_b200.orchestration import run_cli_train_setup
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+
+    def factory(comm, device, limit):
+        h = _FakeHeap(comm, device, limit)
+        h.fail_check = comm.rank == 1          # only rank 1's kernel gave up on its peer
+        return h
+
+    def body(comm):
+        with pytest.raises(CommError):
+            run_cli_train_setup(_tp_cfg(tmp_path, comm.rank), comm, allow_dirty=True,
+                                tokenizer=SyntheticTokenizer(32, 4, 8), heap_factory=factory)
+        return True
+    assert run_ranks(2, body, timeout=120) == [True, True]

@@ -280,3 +280,32 @@ def test_tensor_parallel_plan_divides_evenly_or_refuses():
                       ((0, 5, 40, 40, 12288), "intermediate size"), ((4, 4, 32, 8, 12288), "outside world")):
         with pytest.raises(CommConfigError, match=msg):
             TensorParallelPlan.new(*args)
+
+
+def test_retired_rows_read_no_kv_and_live_rows_are_unchanged():
+    """Rows that have emitted EOS stay in the fixed-shape decode batch but attend to nothing: the
+    lengths handed to decode attention drop to zero for them and their cache length freezes, while
+    the live rows' logits are bit-identical to a run without retirement (reference retires rows in
+    lm_policy.rs:736-743)."""
+    from ferrl_b200.models import DenseGradModel, DenseSpec
+    spec = DenseSpec(vocab_size=97, hidden_size=32, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                     head_dim=8, intermediate_size=64, max_position_embeddings=64)
+    m = DenseGradModel(spec, None, dtype=torch.float32)
+    m.init_random(3, 0.2)
+    m.merge_adapters()
+    B, L = 4, 6
+    ids = torch.randint(0, 97, (B, L), generator=torch.Generator().manual_seed(1))
+    lens = torch.tensor([6, 4, 5, 6])
+    a, b = m.new_decoder(B, 32), m.new_decoder(B, 32)
+    a.prefill(ids, lens)
+    b.prefill(ids, lens)
+    active = torch.tensor([True, False, True, False])
+    tok = torch.tensor([3, 0, 5, 0])
+    before = b.kv_len.clone()
+    assert int(b.kv_tokens_read(active)) == int(((before + 1) * active).sum()) < int(a.kv_tokens_read())
+    for _ in range(3):
+        la = a.decode(tok)
+        lb = b.decode(tok, active)
+        assert torch.equal(la[active], lb[active])
+        assert torch.isfinite(lb).all()
+    assert torch.equal(b.kv_len[active], before[active] + 3) and torch.equal(b.kv_len[~active], before[~active])

@@ -55,11 +55,14 @@ def test_static_workspace_entry_matches_regular_op_twice():
         out = torch.empty_like(q)
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated(dev)
+        free_before = torch.cuda.mem_get_info(dev)[0]      # a raw cudaMalloc would show here, not in torch's counter
         rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D,
                 kc.stride(0), kc.stride(1), scale, 0, splits, stream)
         assert rc == 0, err(rc)
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated(dev) == before   # nothing came from torch's allocator
+        if call == 1:   # the first call on a device may load kernel images lazily; the second must not move the heap
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         ref = C.decode_attention(q, kc, vc, lens, scale=scale, n_splits=splits)
         # same kernels, same split boundaries: the tolerance is the one the other decode tests use
         rel = ((out.float() - ref.float()).norm() / ref.float().norm()).item()
@@ -75,10 +78,15 @@ def test_static_workspace_entry_rejects_oversize_and_bad_args():
     t = torch.zeros(16, device=dev, dtype=torch.bfloat16)
     lens = torch.zeros(1, device=dev, dtype=torch.int32)
     # 4096 * 32 * 16 * 130 floats is far beyond the 4 Mi-float array: refused before any launch
-    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 4096, 32, 8, 128, 0, 0, 1.0, 0, 16, None)
+    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 4096, 32, 8, 128, 0, 1024, 1.0, 0, 16, None)
     assert rc == 1 and b"exceeds" in err(rc)
-    rc = fn(None, t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 1, 4, 4, 128, 0, 0, 1.0, 0, 2, None)
+    rc = fn(None, t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 1, 4, 4, 128, 0, 512, 1.0, 0, 2, None)
     assert rc == 2
-    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 1, 4, 4, 100, 0, 0, 1.0, 0, 2, None)
+    rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 1, 4, 4, 100, 0, 400, 1.0, 0, 2, None)
     assert rc == 2
+    # overlapping tokens (tok_stride < Hkv*D), a negative sequence stride and a negative window are refused
+    for seq_stride, tok_stride, window in ((0, 511, 0), (-1, 512, 0), (0, 512, -1)):
+        rc = fn(t.data_ptr(), t.data_ptr(), t.data_ptr(), lens.data_ptr(), t.data_ptr(), 1, 4, 4, 128,
+                seq_stride, tok_stride, 1.0, window, 2, None)
+        assert rc == 2 and b"tok_stride" in err(rc)
     torch.cuda.synchronize()
