@@ -631,11 +631,7 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                        long long seq_stride, long long tok_stride, float scale, int window, int n_splits,
                        const int* __restrict__ kv_start, int kv_start_div, int ws_off, int ws_total) {
   pdl_trigger();   // a dependent GEMM may start streaming its weights while this kernel runs
-  // Launched as a programmatic dependent itself: nothing is read before the predecessor is done.  In
-  // shared-prefix mode the predecessor is the group kernel, which only produces the prefix partials
-  // that the final merge below reads (and which lets this kernel start only after ITS predecessor has
-  // finished): the wait moves down to the merge and the two kernels run side by side.
-  if (ws_total == 0) pdl_wait();
+  pdl_wait();      // launched as a programmatic dependent itself: nothing is read before the predecessor is done
   static_assert(REP <= 8, "query heads of one KV head must fit rows 0..7 of the MMA tile");
   constexpr int ROW_BYTES = D * 2;
   constexpr int CPR = ROW_BYTES / 16;                  // 16-byte chunks per row
@@ -771,7 +767,6 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
   }
   __syncthreads();
-  if (ws_total > 0) pdl_wait();    // the prefix partials in slots [0, ws_off) are complete from here on
   for (int i = threadIdx.x; i < REP * D; i += blockDim.x) {
     const int r = i / D, d = i - r * D;
     float m = -INFINITY;
@@ -816,26 +811,24 @@ decode_attn_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 // CTA per (group, KV head, split) streams those keys ONCE and applies them to all G * REP query rows
 // of the group (two 16-row MMA tiles for G = 8, REP = 4) instead of G CTAs streaming them G times.
 // The rest of every row ([prefix_len, kv_len)) is covered by decode_attn_mma_kernel with kv_start =
-// prefix_len, launched right behind this kernel and running beside it; it reads the (o, m, l) partials
-// written here only in its last step, where it merges them with its own and writes the final rows.
+// prefix_len, launched right behind this kernel as its programmatic dependent; in its last step it merges
+// the (o, m, l) partials written here with its own and writes the final rows (no combine kernel).
 // Query row r of the tile is batch row group * G + r / REP, head hk * REP + r % REP.
-// One CTA of this kernel owns an SM (32 query rows of accumulators), so its own ring must hold the bytes in
-// flight that four co-resident CTAs provide in the per-row kernel: eight stages of 32 keys.
-constexpr int GSTAGES = 8;
+// Eight warps for 32 query rows: warp w takes keys 8 (w & 3) .. +7 of every 32-key tile for the 16-row MMA tile
+// w >> 2, so two warps share each scheduler and two CTAs (four ring stages each) fit an SM.
+constexpr int GSTAGES = 4;
 
 template <int D, int REP, int G>
-__global__ void __launch_bounds__(PWARPS * 32, 1)
+__global__ void __launch_bounds__(PWARPS * 32 * (REP * G / 16), 2)
 decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
                          const __nv_bfloat16* __restrict__ vc, const int* __restrict__ prefix_len,
                          const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int page,
                          float* __restrict__ ws, int Hq, int Hkv, long long tok_stride, float scale, int n_splits,
                          int ws_total) {
-  // wait first, then let the per-row kernel start: when it runs, everything before this kernel is complete
+  pdl_trigger();   // the per-row kernel may take its place on the SMs; it waits for this kernel before it reads anything
   pdl_wait();
-  pdl_trigger();
   constexpr int QR = REP * G;                          // query rows sharing the keys
   static_assert(QR % 16 == 0 && QR <= 32, "group kernel: G * REP must be 16 or 32");
-  constexpr int RT = QR / 16;                          // 16-row MMA tiles
   constexpr int ROW_BYTES = D * 2;
   constexpr int CPR = ROW_BYTES / 16;
   constexpr int CHUNKS = PTK * CPR;
@@ -845,6 +838,7 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   extern __shared__ __align__(128) uint8_t psm[];
   const int gi = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kq = warp & 3, rt = warp >> 2;             // key octet of the tile, 16-row tile of the queries
   const int g = lane >> 2, t = lane & 3;
 
   int pre = prefix_len[gi];
@@ -860,19 +854,16 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   const int n_tiles = s1 > s0 ? (s1 - s0 + PTK - 1) / PTK : 0;
   const int b0 = gi * G;                               // the group's first row: its table names the shared pages
 
-  // Q fragments of the RT row tiles: rows rt*16 + g (a0, a2) and rt*16 + g + 8 (a1, a3)
-  uint32_t qa[RT][KSTEPS][4];
+  // Q fragments of my row tile: rows rt*16 + g (a0, a2) and rt*16 + g + 8 (a1, a3)
+  uint32_t qa[KSTEPS][4];
 #pragma unroll
-  for (int rt = 0; rt < RT; ++rt) {
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = rt * 16 + g + 8 * hh;
+    const __nv_bfloat16* qp = q + (static_cast<long long>(b0 + r / REP) * Hq + hk * REP + r % REP) * D + 2 * t;
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int r = rt * 16 + g + 8 * hh;
-      const __nv_bfloat16* qp = q + (static_cast<long long>(b0 + r / REP) * Hq + hk * REP + r % REP) * D + 2 * t;
-#pragma unroll
-      for (int ks = 0; ks < KSTEPS; ++ks) {
-        qa[rt][ks][hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16);
-        qa[rt][ks][2 + hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8);
-      }
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      qa[ks][hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16);
+      qa[ks][2 + hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8);
     }
   }
 
@@ -884,7 +875,7 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     if (tt < n_tiles) {
       uint8_t* st = psm + (tt % GSTAGES) * STAGE_BYTES;
       const int j0 = s0 + tt * PTK;
-      for (int c = threadIdx.x; c < CHUNKS; c += PWARPS * 32) {
+      for (int c = threadIdx.x; c < CHUNKS; c += blockDim.x) {
         const int key = c / CPR, part = c % CPR;
         const int j = j0 + key;
         const bool ok = j < s1;
@@ -897,15 +888,10 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     cp_async_commit();
   };
 
-  float m_run[RT][2], l_run[RT][2];
-  float o[RT][NT][4];
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o[NT][4];
 #pragma unroll
-  for (int rt = 0; rt < RT; ++rt) {
-    m_run[rt][0] = m_run[rt][1] = -INFINITY;
-    l_run[rt][0] = l_run[rt][1] = 0.f;
-#pragma unroll
-    for (int n = 0; n < NT; ++n) o[rt][n][0] = o[rt][n][1] = o[rt][n][2] = o[rt][n][3] = 0.f;
-  }
+  for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
 
 #pragma unroll
   for (int tt = 0; tt < GSTAGES - 1; ++tt) issue(tt);
@@ -915,89 +901,75 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     issue(tt + GSTAGES - 1);
     const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % GSTAGES) * STAGE_BYTES));
     const uint32_t vt = kt + PTK * ROW_BYTES;
-    const int key0 = warp * 8;
+    const int key0 = kq * 8;
     const int j0 = s0 + tt * PTK + key0;
     const int lrow = key0 + (lane & 7), lmat = lane >> 3;
-    float sacc[RT][4];
-#pragma unroll
-    for (int rt = 0; rt < RT; ++rt) sacc[rt][0] = sacc[rt][1] = sacc[rt][2] = sacc[rt][3] = 0.f;
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int qd = 0; qd < KSTEPS / 2; ++qd) {
       uint32_t b0_, b1_, b2_, b3_;
       ldsm_x4(kt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), b0_, b1_, b2_, b3_);
-#pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-        mma_16816(sacc[rt], qa[rt][2 * qd][0], qa[rt][2 * qd][1], qa[rt][2 * qd][2], qa[rt][2 * qd][3], b0_, b1_);
-        mma_16816(sacc[rt], qa[rt][2 * qd + 1][0], qa[rt][2 * qd + 1][1], qa[rt][2 * qd + 1][2], qa[rt][2 * qd + 1][3], b2_, b3_);
-      }
+      mma_16816(sacc, qa[2 * qd][0], qa[2 * qd][1], qa[2 * qd][2], qa[2 * qd][3], b0_, b1_);
+      mma_16816(sacc, qa[2 * qd + 1][0], qa[2 * qd + 1][1], qa[2 * qd + 1][2], qa[2 * qd + 1][3], b2_, b3_);
     }
     const bool v0 = j0 + 2 * t < s1, v1 = j0 + 2 * t + 1 < s1;
-    uint32_t pa[RT][2];
-    float corr[RT][2];
+    uint32_t pa[2];
+    float corr[2];
 #pragma unroll
-    for (int rt = 0; rt < RT; ++rt) {
-#pragma unroll
-      for (int hh = 0; hh < 2; ++hh) {
-        const float sc0 = v0 ? sacc[rt][2 * hh] * scale : -INFINITY;
-        const float sc1 = v1 ? sacc[rt][2 * hh + 1] * scale : -INFINITY;
-        float mx = fmaxf(sc0, sc1);
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_run[rt][hh], mx);
-        const float cr = (m_run[rt][hh] == -INFINITY) ? 0.f : __expf(m_run[rt][hh] - m_new);
-        const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
-        const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
-        float ps = p0 + p1;
-        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
-        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
-        l_run[rt][hh] = l_run[rt][hh] * cr + ps;
-        m_run[rt][hh] = m_new;
-        corr[rt][hh] = cr;
-        __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
-        pa[rt][hh] = *reinterpret_cast<uint32_t*>(&ph);
-      }
+    for (int hh = 0; hh < 2; ++hh) {
+      const float sc0 = v0 ? sacc[2 * hh] * scale : -INFINITY;
+      const float sc1 = v1 ? sacc[2 * hh + 1] * scale : -INFINITY;
+      float mx = fmaxf(sc0, sc1);
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run[hh], mx);
+      const float cr = (m_run[hh] == -INFINITY) ? 0.f : __expf(m_run[hh] - m_new);
+      const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
+      const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
+      float ps = p0 + p1;
+      ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+      ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+      l_run[hh] = l_run[hh] * cr + ps;
+      m_run[hh] = m_new;
+      corr[hh] = cr;
+      __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
+      pa[hh] = *reinterpret_cast<uint32_t*>(&ph);
     }
 #pragma unroll
     for (int qd = 0; qd < NT / 4; ++qd) {
       uint32_t w0, w1, w2, w3;
       ldsm_x4_t(vt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), w0, w1, w2, w3);
 #pragma unroll
-      for (int rt = 0; rt < RT; ++rt) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          o[rt][4 * qd + e][0] *= corr[rt][0];
-          o[rt][4 * qd + e][1] *= corr[rt][0];
-          o[rt][4 * qd + e][2] *= corr[rt][1];
-          o[rt][4 * qd + e][3] *= corr[rt][1];
-        }
-        mma_1688(o[rt][4 * qd + 0], pa[rt][0], pa[rt][1], w0);
-        mma_1688(o[rt][4 * qd + 1], pa[rt][0], pa[rt][1], w1);
-        mma_1688(o[rt][4 * qd + 2], pa[rt][0], pa[rt][1], w2);
-        mma_1688(o[rt][4 * qd + 3], pa[rt][0], pa[rt][1], w3);
+      for (int e = 0; e < 4; ++e) {
+        o[4 * qd + e][0] *= corr[0];
+        o[4 * qd + e][1] *= corr[0];
+        o[4 * qd + e][2] *= corr[1];
+        o[4 * qd + e][3] *= corr[1];
       }
+      mma_1688(o[4 * qd + 0], pa[0], pa[1], w0);
+      mma_1688(o[4 * qd + 1], pa[0], pa[1], w1);
+      mma_1688(o[4 * qd + 2], pa[0], pa[1], w2);
+      mma_1688(o[4 * qd + 3], pa[0], pa[1], w3);
     }
   }
   cp_async_wait<0>();
   __syncthreads();
 
-  // merge the four warps (each saw different keys) through shared memory
-  float* m_s = reinterpret_cast<float*>(psm);   // [PWARPS][QR]
-  float* l_s = m_s + PWARPS * QR;               // [PWARPS][QR]
-  float* o_s = l_s + PWARPS * QR;               // [PWARPS][QR][D]
+  // merge the four key octets of every row through shared memory
+  float* m_s = reinterpret_cast<float*>(psm);   // [4][QR]
+  float* l_s = m_s + PWARPS * QR;               // [4][QR]
+  float* o_s = l_s + PWARPS * QR;               // [4][QR][D]
 #pragma unroll
-  for (int rt = 0; rt < RT; ++rt) {
+  for (int hh = 0; hh < 2; ++hh) {
+    const int r = rt * 16 + g + 8 * hh;
+    if (t == 0) {
+      m_s[kq * QR + r] = m_run[hh];
+      l_s[kq * QR + r] = l_run[hh];
+    }
 #pragma unroll
-    for (int hh = 0; hh < 2; ++hh) {
-      const int r = rt * 16 + g + 8 * hh;
-      if (t == 0) {
-        m_s[warp * QR + r] = m_run[rt][hh];
-        l_s[warp * QR + r] = l_run[rt][hh];
-      }
-#pragma unroll
-      for (int n = 0; n < NT; ++n) {
-        o_s[(warp * QR + r) * D + n * 8 + 2 * t] = o[rt][n][2 * hh];
-        o_s[(warp * QR + r) * D + n * 8 + 2 * t + 1] = o[rt][n][2 * hh + 1];
-      }
+    for (int n = 0; n < NT; ++n) {
+      o_s[(kq * QR + r) * D + n * 8 + 2 * t] = o[n][2 * hh];
+      o_s[(kq * QR + r) * D + n * 8 + 2 * t + 1] = o[n][2 * hh + 1];
     }
   }
   __syncthreads();
@@ -1018,6 +990,301 @@ decode_attn_group_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
     if (d == 0) {
       w_[D] = m;
       w_[D + 1] = l;
+    }
+  }
+}
+
+// Whole-group form (D = 128, REP = 4, G = 8): one CTA per (group, KV head) does the shared prefix AND the
+// private keys of the group's eight rows, so nothing crosses a kernel boundary (no workspace, no second
+// launch, no dependency edge).
+//   phase 1: the prefix keys stream once through a CTA-wide ring; all 32 query rows of the group (8 rows x 4
+//            heads, two 16-row MMA tiles) are applied to them as in decode_attn_group_kernel; the four key
+//            octets are merged into one (o, m, l) per query row in shared memory.
+//   phase 2: warp w owns row w of the group: it streams that row's private keys [prefix_len, kv_len) through
+//            its own 3-stage ring of 16 keys (no CTA-wide barrier in the loop), its 4 query heads being rows
+//            0..3 of the MMA tile, then merges with the prefix partial of those heads and writes the row.
+// Eight warps with 16 KB in flight each keep 128 KB of loads outstanding per SM.
+constexpr int FSTAGES = 3;       // per-warp ring stages
+constexpr int FKEYS = 16;        // keys per per-warp stage
+
+__global__ void __launch_bounds__(256, 1)
+decode_attn_group_fused_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kc,
+                               const __nv_bfloat16* __restrict__ vc, const int* __restrict__ prefix_len,
+                               const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int page,
+                               __nv_bfloat16* __restrict__ out, int Hq, int Hkv, long long tok_stride, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  constexpr int D = 128, REP = 4, G = 8, QR = 32;
+  constexpr int ROW_BYTES = D * 2;
+  constexpr int CPR = ROW_BYTES / 16;
+  constexpr int KSTEPS = D / 16;
+  constexpr int NT = D / 8;
+  constexpr int P1_STAGE = 2 * PTK * ROW_BYTES;            // 16 KB
+  constexpr int W_STAGE = 2 * FKEYS * ROW_BYTES;           // 8 KB
+  constexpr int RING_BYTES = 8 * FSTAGES * W_STAGE;        // 192 KB (phase 1 uses its first GSTAGES * 16 KB)
+  extern __shared__ __align__(128) uint8_t psm[];
+  float* pre_m = reinterpret_cast<float*>(psm + RING_BYTES);   // [32]
+  float* pre_l = pre_m + QR;                                    // [32]
+  float* pre_o = pre_l + QR;                                    // [32][128]
+  const int gi = blockIdx.x, hk = blockIdx.y;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int b0 = gi * G;
+
+  int pre = prefix_len[gi];
+  {
+    int live = 0;
+    for (int r = 0; r < G; ++r) live |= kv_len[b0 + r];
+    if (live == 0) pre = 0;
+  }
+
+  // ------------------------------------------------------------------ phase 1: shared prefix
+  {
+    const int kq = warp & 3, rt = warp >> 2;
+    const int n_tiles = (pre + PTK - 1) / PTK;
+    uint32_t qa[KSTEPS][4];
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rt * 16 + g + 8 * hh;
+      const __nv_bfloat16* qp = q + (static_cast<long long>(b0 + r / REP) * Hq + hk * REP + r % REP) * D + 2 * t;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        qa[ks][hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16);
+        qa[ks][2 + hh] = *reinterpret_cast<const uint32_t*>(qp + ks * 16 + 8);
+      }
+    }
+    auto issue = [&](int tt) {
+      if (tt < n_tiles) {
+        uint8_t* st = psm + (tt % GSTAGES) * P1_STAGE;
+        const int j0 = tt * PTK;
+        for (int c = threadIdx.x; c < PTK * CPR; c += 256) {
+          const int key = c / CPR, part = c % CPR;
+          const int j = j0 + key;
+          const bool ok = j < pre;
+          const int jj = ok ? j : 0;
+          const int pg = block_table[static_cast<long long>(b0) * bt_stride + jj / page];
+          const long long row = (static_cast<long long>(pg) * page + (jj % page)) * tok_stride + hk * D + part * 8;
+          const int off = key * ROW_BYTES + ((part ^ (key & 7)) << 4);
+          cp_async16(st + off, kc + row, ok);
+          cp_async16(st + PTK * ROW_BYTES + off, vc + row, ok);
+        }
+      }
+      cp_async_commit();
+    };
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+#pragma unroll
+    for (int tt = 0; tt < GSTAGES - 1; ++tt) issue(tt);
+    for (int tt = 0; tt < n_tiles; ++tt) {
+      cp_async_wait<GSTAGES - 2>();
+      __syncthreads();
+      issue(tt + GSTAGES - 1);
+      const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(psm + (tt % GSTAGES) * P1_STAGE));
+      const uint32_t vt = kt + PTK * ROW_BYTES;
+      const int key0 = kq * 8;
+      const int j0 = tt * PTK + key0;
+      const int lrow = key0 + (lane & 7), lmat = lane >> 3;
+      float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int qd = 0; qd < KSTEPS / 2; ++qd) {
+        uint32_t b0_, b1_, b2_, b3_;
+        ldsm_x4(kt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), b0_, b1_, b2_, b3_);
+        mma_16816(sacc, qa[2 * qd][0], qa[2 * qd][1], qa[2 * qd][2], qa[2 * qd][3], b0_, b1_);
+        mma_16816(sacc, qa[2 * qd + 1][0], qa[2 * qd + 1][1], qa[2 * qd + 1][2], qa[2 * qd + 1][3], b2_, b3_);
+      }
+      const bool v0 = j0 + 2 * t < pre, v1 = j0 + 2 * t + 1 < pre;
+      uint32_t pa[2];
+      float corr[2];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh) {
+        const float sc0 = v0 ? sacc[2 * hh] * scale : -INFINITY;
+        const float sc1 = v1 ? sacc[2 * hh + 1] * scale : -INFINITY;
+        float mx = fmaxf(sc0, sc1);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run[hh], mx);
+        const float cr = (m_run[hh] == -INFINITY) ? 0.f : __expf(m_run[hh] - m_new);
+        const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
+        const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run[hh] = l_run[hh] * cr + ps;
+        m_run[hh] = m_new;
+        corr[hh] = cr;
+        __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
+        pa[hh] = *reinterpret_cast<uint32_t*>(&ph);
+      }
+#pragma unroll
+      for (int qd = 0; qd < NT / 4; ++qd) {
+        uint32_t w0, w1, w2, w3;
+        ldsm_x4_t(vt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), w0, w1, w2, w3);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          o[4 * qd + e][0] *= corr[0];
+          o[4 * qd + e][1] *= corr[0];
+          o[4 * qd + e][2] *= corr[1];
+          o[4 * qd + e][3] *= corr[1];
+        }
+        mma_1688(o[4 * qd + 0], pa[0], pa[1], w0);
+        mma_1688(o[4 * qd + 1], pa[0], pa[1], w1);
+        mma_1688(o[4 * qd + 2], pa[0], pa[1], w2);
+        mma_1688(o[4 * qd + 3], pa[0], pa[1], w3);
+      }
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+    // merge the four key octets of every query row: ring memory is free now
+    float* m_s = reinterpret_cast<float*>(psm);   // [4][32]
+    float* l_s = m_s + 4 * QR;
+    float* o_s = l_s + 4 * QR;                    // [4][32][128]
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+      const int r = rt * 16 + g + 8 * hh;
+      if (t == 0) {
+        m_s[kq * QR + r] = m_run[hh];
+        l_s[kq * QR + r] = l_run[hh];
+      }
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        o_s[(kq * QR + r) * D + n * 8 + 2 * t] = o[n][2 * hh];
+        o_s[(kq * QR + r) * D + n * 8 + 2 * t + 1] = o[n][2 * hh + 1];
+      }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < QR * D; i += 256) {
+      const int r = i / D, d = i - r * D;
+      float m = -INFINITY;
+      for (int w = 0; w < 4; ++w) m = fmaxf(m, m_s[w * QR + r]);
+      float l = 0.f, acc = 0.f;
+      for (int w = 0; w < 4; ++w) {
+        const float mw = m_s[w * QR + r];
+        const float c = (mw == -INFINITY) ? 0.f : __expf(mw - m);
+        l += l_s[w * QR + r] * c;
+        acc += o_s[(w * QR + r) * D + d] * c;
+      }
+      pre_o[r * D + d] = acc;
+      if (d == 0) {
+        pre_m[r] = m;
+        pre_l[r] = l;
+      }
+    }
+    __syncthreads();
+  }
+
+  // ------------------------------------------------------------------ phase 2: warp w = row w of the group
+  {
+    const int b = b0 + warp;
+    const int len = kv_len[b];
+    const int lo = min(pre, len);
+    const int n_tiles = len > lo ? (len - lo + FKEYS - 1) / FKEYS : 0;
+    uint8_t* ring = psm + warp * (FSTAGES * W_STAGE);
+    uint32_t qa0[KSTEPS], qa2[KSTEPS];
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      qa0[ks] = 0u;
+      qa2[ks] = 0u;
+      if (g < REP) {
+        const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * REP + g) * D + ks * 16 + 2 * t;
+        qa0[ks] = *reinterpret_cast<const uint32_t*>(qp);
+        qa2[ks] = *reinterpret_cast<const uint32_t*>(qp + 8);
+      }
+    }
+    auto issue = [&](int tt) {
+      if (tt < n_tiles) {
+        uint8_t* st = ring + (tt % FSTAGES) * W_STAGE;
+        const int j0 = lo + tt * FKEYS;
+        for (int c = lane; c < FKEYS * CPR; c += 32) {
+          const int key = c / CPR, part = c % CPR;
+          const int j = j0 + key;
+          const bool ok = j < len;
+          const int jj = ok ? j : lo;
+          const int pg = block_table[static_cast<long long>(b) * bt_stride + jj / page];
+          const long long row = (static_cast<long long>(pg) * page + (jj % page)) * tok_stride + hk * D + part * 8;
+          const int off = key * ROW_BYTES + ((part ^ (key & 7)) << 4);
+          cp_async16(st + off, kc + row, ok);
+          cp_async16(st + FKEYS * ROW_BYTES + off, vc + row, ok);
+        }
+      }
+      cp_async_commit();
+    };
+    float m_run = -INFINITY, l_run = 0.f;
+    float o[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+#pragma unroll
+    for (int tt = 0; tt < FSTAGES - 1; ++tt) issue(tt);
+    for (int tt = 0; tt < n_tiles; ++tt) {
+      cp_async_wait<FSTAGES - 2>();
+      __syncwarp();
+      issue(tt + FSTAGES - 1);
+      const uint32_t kt = static_cast<uint32_t>(__cvta_generic_to_shared(ring + (tt % FSTAGES) * W_STAGE));
+      const uint32_t vt = kt + FKEYS * ROW_BYTES;
+#pragma unroll
+      for (int oct = 0; oct < FKEYS / 8; ++oct) {
+        const int key0 = oct * 8;
+        const int j0 = lo + tt * FKEYS + key0;
+        const int lrow = key0 + (lane & 7), lmat = lane >> 3;
+        float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int qd = 0; qd < KSTEPS / 2; ++qd) {
+          uint32_t b0_, b1_, b2_, b3_;
+          ldsm_x4(kt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), b0_, b1_, b2_, b3_);
+          mma_16816(sacc, qa0[2 * qd], 0u, qa2[2 * qd], 0u, b0_, b1_);
+          mma_16816(sacc, qa0[2 * qd + 1], 0u, qa2[2 * qd + 1], 0u, b2_, b3_);
+        }
+        const float sc0 = (j0 + 2 * t < len) ? sacc[0] * scale : -INFINITY;
+        const float sc1 = (j0 + 2 * t + 1 < len) ? sacc[1] * scale : -INFINITY;
+        float mx = fmaxf(sc0, sc1);
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = (m_run == -INFINITY) ? 0.f : __expf(m_run - m_new);
+        const float p0 = (sc0 == -INFINITY) ? 0.f : __expf(sc0 - m_new);
+        const float p1 = (sc1 == -INFINITY) ? 0.f : __expf(sc1 - m_new);
+        float ps = p0 + p1;
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = l_run * corr + ps;
+        m_run = m_new;
+        __nv_bfloat162 ph = __floats2bfloat162_rn(p0, p1);
+        const uint32_t pa0 = *reinterpret_cast<uint32_t*>(&ph);
+#pragma unroll
+        for (int qd = 0; qd < NT / 4; ++qd) {
+          uint32_t w0, w1, w2, w3;
+          ldsm_x4_t(vt + lrow * ROW_BYTES + (((4 * qd + lmat) ^ (lrow & 7)) << 4), w0, w1, w2, w3);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            o[4 * qd + e][0] *= corr;
+            o[4 * qd + e][1] *= corr;
+          }
+          mma_1688(o[4 * qd + 0], pa0, 0u, w0);
+          mma_1688(o[4 * qd + 1], pa0, 0u, w1);
+          mma_1688(o[4 * qd + 2], pa0, 0u, w2);
+          mma_1688(o[4 * qd + 3], pa0, 0u, w3);
+        }
+      }
+    }
+    cp_async_wait<0>();
+    // merge with the prefix partial of query row warp * 4 + g and write the row's 4 heads
+    if (g < REP) {
+      const int r = warp * REP + g;
+      const float mp = pre_m[r], lp = pre_l[r];
+      const float mm = fmaxf(m_run, mp);
+      const float c0 = (m_run == -INFINITY) ? 0.f : __expf(m_run - mm);
+      const float c1 = (mp == -INFINITY) ? 0.f : __expf(mp - mm);
+      const float lt = l_run * c0 + lp * c1;
+      const float inv = (lt > 0.f && len > 0) ? 1.f / lt : 0.f;           // a retired row (length 0) stays zero
+      __nv_bfloat16* op = out + (static_cast<long long>(b) * Hq + hk * REP + g) * D;
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {
+        const int d = n * 8 + 2 * t;
+        const float x0 = (o[n][0] * c0 + pre_o[r * D + d] * c1) * inv;
+        const float x1 = (o[n][1] * c0 + pre_o[r * D + d + 1] * c1) * inv;
+        *reinterpret_cast<__nv_bfloat162*>(op + d) = __floats2bfloat162_rn(x0, x1);
+      }
     }
   }
 }
@@ -1075,6 +1342,19 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     if ((a.tok_stride % 8) || (reinterpret_cast<uintptr_t>(a.k) & 15) || (reinterpret_cast<uintptr_t>(a.v) & 15) ||
         (reinterpret_cast<uintptr_t>(a.q) & 3))
       return "decode_attn: shared-prefix mode needs 16-byte aligned caches";
+    if (a.D == 128 && rep == 4 && G == 8 && a.prefix_splits == 1) {
+      // whole-group kernel: prefix and private keys in one launch, no workspace
+      constexpr size_t fsm = static_cast<size_t>(8) * FSTAGES * 2 * FKEYS * 128 * 2 + (2 * 32 + 32 * 128) * 4;
+      auto fk = decode_attn_group_fused_kernel;
+      if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(fk, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                      static_cast<int>(fsm)) == cudaSuccess))
+        return "decode_attn: cannot reserve shared memory";
+      launch_pdl(fk, dim3(a.B / 8, a.Hkv), dim3(256), fsm, s, static_cast<const __nv_bfloat16*>(a.q),
+                 static_cast<const __nv_bfloat16*>(a.k), static_cast<const __nv_bfloat16*>(a.v), a.prefix_len, a.kv_len,
+                 a.block_table, a.bt_stride, a.page, static_cast<__nv_bfloat16*>(a.out), a.Hq, a.Hkv, a.tok_stride, a.scale);
+      count_launch();
+      return cudaGetLastError() == cudaSuccess ? nullptr : "decode_attn launch failed";
+    }
     kv_start = a.prefix_len; kv_start_div = G; ws_off = a.prefix_splits; ws_total = a.prefix_splits;
     bool ok = false;
 #define FERRL_DECODE_GROUP(DD, RR, GG)                                                                                \
@@ -1084,9 +1364,11 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     constexpr size_t gsm = ring > merge ? ring : merge;                                                               \
     auto gk = decode_attn_group_kernel<DD, RR, GG>;                                                                   \
     if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(gk, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                                                    static_cast<int>(gsm)) == cudaSuccess))                           \
+                                                    static_cast<int>(gsm)) == cudaSuccess &&                          \
+                               cudaFuncSetAttribute(gk, cudaFuncAttributePreferredSharedMemoryCarveout,               \
+                                                    cudaSharedmemCarveoutMaxShared) == cudaSuccess))                  \
       return "decode_attn: cannot reserve shared memory";                                                             \
-    launch_pdl(gk, dim3(a.B / GG, a.Hkv, a.prefix_splits), dim3(PWARPS * 32), gsm, s,                                 \
+    launch_pdl(gk, dim3(a.B / GG, a.Hkv, a.prefix_splits), dim3(PWARPS * 32 * (RR * GG / 16)), gsm, s,                                 \
                static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                        \
                static_cast<const __nv_bfloat16*>(a.v), a.prefix_len, a.kv_len, a.block_table, a.bt_stride, a.page,    \
                a.workspace, a.Hq, a.Hkv, a.tok_stride, a.scale, a.prefix_splits, ws_total);                           \
@@ -1127,7 +1409,9 @@ const char* decode_attn(const DecodeAttnArgs& a, cudaStream_t s) {
     constexpr size_t msm_bytes = static_cast<size_t>(MSTAGES) * 2 * PTK * DD * 2;                                     \
     auto mk = decode_attn_mma_kernel<DD, RR>;                                                                         \
     if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(mk, cudaFuncAttributeMaxDynamicSharedMemorySize,                  \
-                                                    static_cast<int>(msm_bytes)) == cudaSuccess))                     \
+                                                    static_cast<int>(msm_bytes)) == cudaSuccess &&                    \
+                               cudaFuncSetAttribute(mk, cudaFuncAttributePreferredSharedMemoryCarveout,               \
+                                                    cudaSharedmemCarveoutMaxShared) == cudaSuccess))                  \
       return "decode_attn: cannot reserve shared memory";                                                             \
     launch_pdl(mk, grid, dim3(PWARPS * 32), msm_bytes, s,                                                             \
         static_cast<const __nv_bfloat16*>(a.q), static_cast<const __nv_bfloat16*>(a.k),                               \

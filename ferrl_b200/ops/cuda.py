@@ -382,7 +382,12 @@ def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0, n_splits=0
         return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
     if block_table is not None and prefix_len is not None and not window:
         B = q.shape[0]
-        ps = int(prefix_splits) or max(1, min(4, 296 // max(1, (B // group) * k_cache.shape[2])))   # about two CTAs per SM
+        if int(prefix_splits):
+            ps = int(prefix_splits)
+        elif (q.shape[-1], q.shape[1] // k_cache.shape[2], group) == (128, 4, 8):
+            ps = 1          # the whole-group kernel: prefix and private keys in one launch
+        else:
+            ps = max(1, min(4, 296 // max(1, (B // group) * k_cache.shape[2])))   # about two prefix CTAs per SM
         return lib().decode_attn(q.contiguous(), k_cache, v_cache, kv_len.to(torch.int32), float(scale), 0, 1, block_table,
                                  k_cache.shape[1], 0, prefix_len, int(group), ps)
     if block_table is not None:
