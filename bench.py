@@ -166,13 +166,16 @@ def main():
     from ferrl_b200.comm import SoloComm, TorchDistComm
     from ferrl_b200.ops import cuda as C
     if args.impl == "torch-baseline":
+        # stand-in comparator (the reference itself cannot be built here): the same trainer and models on
+        # library kernels - cuBLAS GEMMs with the LoRA side path as separate matmuls, PyTorch SDPA for
+        # scoring/backward, flash-attn's KV-cache kernel for decode, eager norms / RoPE / GLU / log-softmax,
+        # host-seeded eager sampler, no CUDA graph, no paged cache, one NCCL all-reduce per gradient tensor
         from ferrl_b200 import ops as _ops
         _ops.use_library_kernels(True)
         args.no_graph = True
         args.nccl_baseline = True
-        # unfused attention keeps [rows, heads, S, S] fp32 scores: recompute per layer and take small micro-batches
-        args.remat = 1
-        args.microbatch = min(args.microbatch, 2)
+        args.remat = 1          # eager ops keep fp32 intermediates alive: recompute per layer
+        args.microbatch = min(args.microbatch, 4)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if world > 1:

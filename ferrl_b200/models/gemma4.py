@@ -191,23 +191,34 @@ class Gemma4Layer(nn.Module):
             kv_out[0][:, :S].copy_(k)
             kv_out[1][:, :S].copy_(v)
         a = ops.attention(q, k, v, scale=1.0, causal=True, window=self.window, softmax_fp32=True)
-        o = reduce_from_tp(lin(self.o, a.reshape(B, S, self.hq * self.D)), comm)
+        # row-parallel projection and its tensor-parallel sum: one fused GEMM -> all-reduce kernel where a
+        # reducer is registered for ``comm`` (the residual joins after the post-norm, so none rides along)
+        o = self.o.forward_reduce(a.reshape(B, S, self.hq * self.D), comm, merged)
         return h + ops.rmsnorm(o, self.post_attn_norm, self.eps)
 
     def mlp_half(self, h, comm, merged=False):
         lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
         x = copy_to_tp(ops.rmsnorm(h, self.pre_ffn_norm, self.eps), comm)
-        d = reduce_from_tp(lin(self.down, ops.swiglu(lin(self.gate_up, x), self.act)), comm)
+        d = self.down.forward_reduce(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged)
         return (h + ops.rmsnorm(d, self.post_ffn_norm, self.eps)) * self.layer_scalar
 
     def decode(self, h, kv_len, cos, sin, k_cache, v_cache, comm):
+        """One token against the cache.  A sliding layer's cache is a ring of ``window`` slots (token ``p``
+        lives in slot ``p % window``): the new token overwrites the one that just left the window and
+        attention runs over the ``min(p + 1, window)`` occupied slots - keys carry their RoPE phase, so the
+        slot order does not matter.  Full-attention layers keep the whole sequence."""
         B = h.shape[0]
         lin = lambda m, z: m.forward_merged(z)  # noqa: E731
         x = ops.rmsnorm(h, self.input_norm, self.eps).unsqueeze(1)
         q, k, v = self._qkv(x, kv_len[:, None].long(), cos, sin, lin)
-        ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
-        a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_len + 1, scale=1.0, window=self.window)
-        o = reduce_from_tp(lin(self.o, a.reshape(B, self.hq * self.D)), comm)
+        slots = k_cache.shape[1]
+        if self.window and slots <= self.window:
+            ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len % slots)
+            a = ops.decode_attention(q[:, 0], k_cache, v_cache, (kv_len + 1).clamp(max=slots), scale=1.0)
+        else:
+            ops_cache_write(k_cache, v_cache, k[:, 0], v[:, 0], kv_len)
+            a = ops.decode_attention(q[:, 0], k_cache, v_cache, kv_len + 1, scale=1.0, window=self.window)
+        o = self.o.forward_reduce(a.reshape(B, self.hq * self.D), comm, True)
         h = h + ops.rmsnorm(o, self.post_attn_norm, self.eps)
         return self.mlp_half(h, comm, merged=True)
 
@@ -325,26 +336,28 @@ class Gemma4GradModel(nn.Module):
 
 
 class Gemma4CachedDecoder:
-    """Cached rollout twin. Sliding layers read only the last ``sliding_window`` keys (the
-    decode kernel never touches older ones); ``retained_bytes`` reports what a windowed cache
-    actually needs to keep, as the reference's cache telemetry does (gemma4.rs:2960-2977)."""
+    """Cached rollout twin with windowed retention: a sliding layer keeps only the last
+    ``sliding_window`` tokens of every row, in a ring of that many slots, so its cache does not grow
+    with the sequence (reference gemma4.rs:2327-2394); full-attention layers keep ``max_len`` tokens.
+    ``retained_bytes`` is what is actually allocated, as the reference's cache telemetry reports
+    (gemma4.rs:2960-2977); ``dense_bytes`` is what a cache without retention would take."""
 
     def __init__(self, model: Gemma4GradModel, batch: int, max_len: int, comm: Comm):
         self.m, self.comm, self.batch, self.max_len = model, comm, batch, max_len
         dev, dt = model.embed.device, model.dtype
-        self.k = [torch.zeros(batch, max_len, l.hkv, l.D, dtype=dt, device=dev) for l in model.layers]
-        self.v = [torch.zeros(batch, max_len, l.hkv, l.D, dtype=dt, device=dev) for l in model.layers]
+        self.slots = [min(max_len, l.window) if l.window else max_len for l in model.layers]
+        self.k = [torch.zeros(batch, n, l.hkv, l.D, dtype=dt, device=dev) for l, n in zip(model.layers, self.slots)]
+        self.v = [torch.zeros(batch, n, l.hkv, l.D, dtype=dt, device=dev) for l, n in zip(model.layers, self.slots)]
         self.kv_len = torch.zeros(batch, dtype=torch.int32, device=dev)
 
     def cache_bytes(self):
         return sum(t.numel() * t.element_size() for t in self.k + self.v)
 
     def retained_bytes(self):
-        tot = 0
-        for l, k in zip(self.m.layers, self.k):
-            keep = min(self.max_len, l.window) if l.window else self.max_len
-            tot += 2 * k.shape[0] * keep * k.shape[2] * k.shape[3] * k.element_size()
-        return tot
+        return self.cache_bytes()
+
+    def dense_bytes(self):
+        return sum(2 * k.shape[0] * self.max_len * k.shape[2] * k.shape[3] * k.element_size() for k in self.k)
 
     @torch.no_grad()
     def prefill(self, ids, lens, rows=None):
@@ -354,9 +367,18 @@ class Gemma4CachedDecoder:
         tmp = [(torch.empty(P, L, l.hkv, l.D, dtype=m.dtype, device=ids.device),
                 torch.empty(P, L, l.hkv, l.D, dtype=m.dtype, device=ids.device)) for l in m.layers]
         h = m.forward_hidden(ids, self.comm, merged=True, kv_out=tmp, detached=True)
-        for i in range(len(m.layers)):
-            self.k[i][rows, :L] = tmp[i][0]
-            self.v[i][rows, :L] = tmp[i][1]
+        lens64 = lens.to(ids.device).long()
+        for i, n in enumerate(self.slots):
+            if n >= L:
+                self.k[i][rows, :L] = tmp[i][0]
+                self.v[i][rows, :L] = tmp[i][1]
+                continue
+            # ring: slot s of a row holds its newest token p < len with p % n == s
+            s_idx = torch.arange(n, device=ids.device)[None, :]
+            pos = (s_idx + n * ((lens64[:, None] - 1 - s_idx).clamp(min=0) // n)).clamp(max=L - 1)     # [P, n]
+            gi = pos[:, :, None, None].expand(P, n, tmp[i][0].shape[2], tmp[i][0].shape[3])
+            self.k[i][rows] = torch.gather(tmp[i][0], 1, gi)
+            self.v[i][rows] = torch.gather(tmp[i][1], 1, gi)
         self.kv_len[rows] = lens.to(torch.int32)
         last = h[torch.arange(P, device=ids.device), (lens - 1).long()]
         last = ops.rmsnorm(last, m.final_norm, m.spec.rms_norm_eps)

@@ -26,9 +26,10 @@ _LIBRARY_BASELINE = False
 
 
 def use_library_kernels(flag: bool) -> None:
-    """Benchmark baseline switch: when set, CUDA tensors run the eager restatements in
-    ``ops.eager`` (PyTorch library kernels: cuBLAS GEMMs, unfused attention and norms) instead of
-    this package's kernels.  Never set implicitly; the product path leaves it off."""
+    """Benchmark baseline switch: when set, CUDA tensors run on library kernels instead of this
+    package's: the eager restatements in ``ops.eager`` (cuBLAS GEMMs, unfused norms, RoPE, GLU,
+    log-softmax), PyTorch's fused SDPA for full-sequence attention and flash-attn's KV-cache kernel
+    for decode.  Never set implicitly; the product path leaves it off."""
     global _LIBRARY_BASELINE
     _LIBRARY_BASELINE = bool(flag)
 
@@ -66,7 +67,28 @@ def qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered=False):
     return eager.qk_norm_rope(q, k, q_w, k_w, eps, cos, sin, positions, zero_centered)
 
 
+def _library_attention(q, k, v, scale, causal):
+    """Benchmark baseline: PyTorch's fused SDPA (GQA-native flash kernel) on ``[B,S,H,D]`` tensors."""
+    import torch.nn.functional as F
+    o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal,
+                                       scale=scale, enable_gqa=True)
+    return o.transpose(1, 2).contiguous()
+
+
+def _library_decode_attention(q, k_cache, v_cache, kv_len, scale):
+    """Benchmark baseline: flash-attn's KV-cache decode kernel (``None`` when the package is missing)."""
+    try:
+        from flash_attn import flash_attn_with_kvcache
+    except ImportError:
+        return None
+    import torch
+    return flash_attn_with_kvcache(q[:, None], k_cache, v_cache, cache_seqlens=kv_len.to(torch.int32),
+                                   softmax_scale=scale, causal=True)[:, 0]
+
+
 def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, softmax_fp32=True, kv_len=None):
+    if _LIBRARY_BASELINE and q.is_cuda and not window and not q_offset and kv_len is None and q.dtype != __import__("torch").float32:
+        return _library_attention(q, k, v, scale, causal)
     if _on_gpu(q):
         return _cuda().attention(q, k, v, scale=scale, causal=causal, window=window,
                                  q_offset=q_offset, kv_len=kv_len)
@@ -75,6 +97,10 @@ def attention(q, k, v, *, scale, causal=True, window=0, q_offset=0, softmax_fp32
 
 
 def decode_attention(q, k_cache, v_cache, kv_len, *, scale, window=0):
+    if _LIBRARY_BASELINE and q.is_cuda and not window and k_cache.dim() == 4:
+        out = _library_decode_attention(q, k_cache, v_cache, kv_len, scale)
+        if out is not None:
+            return out
     if _on_gpu(q):
         return _cuda().decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)
     return eager.decode_attention(q, k_cache, v_cache, kv_len, scale=scale, window=window)

@@ -309,6 +309,23 @@ class CandidateWriter:
         d = {k: v for k, v in dataclasses.asdict(rec).items() if v is not None}
         _append_line(self.path, json.dumps(d, sort_keys=True))
 
+    def mark(self) -> int:
+        """Current end of the ledger: what ``rollback`` cuts back to."""
+        try:
+            return os.path.getsize(self.path)
+        except OSError:
+            return 0
+
+    def rollback(self, mark: int) -> None:
+        """Drop every row appended since ``mark`` (a failed window must leave no candidate rows behind:
+        its completions belong to a policy state that was rolled back; reference trainer.rs:7819)."""
+        if not os.path.exists(self.path) or os.path.getsize(self.path) <= mark:
+            return
+        with open(self.path, "r+b") as f:
+            f.truncate(mark)
+            f.flush()
+            os.fsync(f.fileno())
+
 
 def read_candidates(path: str) -> list[CandidateRecord]:
     out = []

@@ -648,7 +648,34 @@ class Trainer:
 
     # ------------------------------------------------------------ rollback
     def _snapshot(self):
-        return ([p.detach().clone() for p in self.params], self.opt.state(), self.policy.sampler_state())
+        """Pre-window copy of adapters, Adam moments and sampler state for rollback (reference
+        trainer.rs:5120-5290).  The copies live in three persistent buffer lists refilled with one
+        multi-tensor copy each (three launches per step instead of one clone per tensor)."""
+        cur = [p.detach() for p in self.params]
+        bufs = getattr(self, "_snap_bufs", None)
+        if bufs is None or len(bufs[0]) != len(cur) or any(b.shape != c.shape or b.device != c.device
+                                                          for b, c in zip(bufs[0], cur)):
+            bufs = ([torch.empty_like(c) for c in cur], [torch.empty_like(t) for t in self.opt.m],
+                    [torch.empty_like(t) for t in self.opt.v])
+            self._snap_bufs = bufs
+        with torch.no_grad():
+            if cur:
+                torch._foreach_copy_(bufs[0], cur)
+                torch._foreach_copy_(bufs[1], list(self.opt.m))
+                torch._foreach_copy_(bufs[2], list(self.opt.v))
+        return (bufs[0], OptimizerState(self.opt.step_t, bufs[1], bufs[2]), self.policy.sampler_state())
+
+    def check_replicated_adapters(self) -> None:
+        """Tensor parallelism keeps every adapter replicated: all ranks must hold bit-identical values,
+        or their gradients (summed over the group) update diverging copies.  The reference proves it by
+        all-reducing every adapter value on each backward (gemma4.rs:157-274); here each rank reduces its
+        adapters to two float64 moments per tensor on the device and the ranks compare one digest."""
+        if self.topology != "tp" or self.comm.world_size == 1 or not self.params:
+            return
+        with torch.no_grad():
+            flat = [p.detach().double() for p in self.params]
+            fp = torch.stack([t.sum() for t in flat] + [(t * t).sum() for t in flat]).cpu()
+        self.comm.require_consensus(fp.numpy().tobytes(), "replicated adapter values")
 
     def _restore(self, snap) -> None:
         try:
@@ -675,13 +702,17 @@ class Trainer:
         dev = self.policy.device()
         self._timer = PhaseTimer(dev)
         self._probe = GpuMemoryProbe(c.gpu_memory_probe, dev if dev.type == "cuda" else None)
+        self.check_replicated_adapters()
         snap = self._snapshot() if self.comm.world_size > 1 or self.fault_hook is not None else None
+        cand_mark = self.candidate_writer.mark() if self.candidate_writer is not None else None
         t0 = time.perf_counter()
         try:
             m, local_tokens = self.run_window(step, lr, beta)
         except CommError:
             raise                      # communicator failures are terminal: no rollback collective is possible
         except Exception:
+            if cand_mark is not None:
+                self.candidate_writer.rollback(cand_mark)   # the window's candidate rows go with its state
             if snap is not None:
                 self._restore(snap)
             raise

@@ -309,3 +309,34 @@ def test_retired_rows_read_no_kv_and_live_rows_are_unchanged():
         assert torch.equal(la[active], lb[active])
         assert torch.isfinite(lb).all()
     assert torch.equal(b.kv_len[active], before[active] + 3) and torch.equal(b.kv_len[~active], before[~active])
+
+
+def test_gemma_sliding_layers_retain_only_their_window_and_decode_matches_uncached():
+    """Sliding-attention layers keep a ring of ``sliding_window`` slots instead of the whole sequence
+    (reference gemma4.rs:2327-2394): the cache of those layers does not grow with ``max_len``, and a
+    ragged-prefill + long decode through the ring reproduces the uncached forward exactly."""
+    model = _load("tiny_gemma4")
+    model.merge_adapters()
+    W = model.spec.sliding_window
+    sliding = [l.window > 0 for l in model.layers]
+    assert any(sliding) and not all(sliding)
+    dec = model.new_decoder(2, 24)
+    for s, n in zip(sliding, dec.slots):
+        assert n == (W if s else 24)
+    assert dec.retained_bytes() < dec.dense_bytes()
+    g = torch.Generator().manual_seed(0)
+    V = model.spec.vocab_size
+    ids = torch.randint(0, V, (2, 16), generator=g)
+    lens = torch.tensor([7, 2])                          # one prompt longer than the window, one shorter
+    prompt = ids[:, :7].clone()
+    logits = dec.prefill(prompt, lens)
+    seqs = [ids[0, :7].tolist(), ids[1, :2].tolist()]
+    for step in range(9):
+        for b in range(2):
+            with torch.no_grad():
+                ref = model(torch.tensor([seqs[b]]))[0, -1]
+            assert torch.allclose(logits[b], ref, atol=2e-4), (step, b, float((logits[b] - ref).abs().max()))
+        nxt = torch.tensor([int(ids[0, 7 + step]), int(ids[1, 2 + step])])
+        for b in range(2):
+            seqs[b].append(int(nxt[b]))
+        logits = dec.decode(nxt)

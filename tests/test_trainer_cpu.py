@@ -507,3 +507,48 @@ def test_collector_learner_chain_is_bit_exact_and_refuses_stale_or_foreign_windo
     with pytest.raises(L.LedgerError, match="trainer_config_sha256"):
         other_cfg.learn_window_from(led, 0)
     assert all(torch.equal(a, b.detach()) for a, b in zip(before, stale.params))
+
+
+def test_tensor_parallel_ranks_with_diverged_adapters_are_refused_before_the_step():
+    """Under tensor parallelism the adapters are replicated; a rank whose copy has drifted is caught by
+    the per-step digest comparison on every rank, before any rollout or update runs (reference
+    gemma4.rs:157-274 all-reduces every adapter value for the same purpose)."""
+    from ferrl_b200.comm import CommMismatch
+
+    def body(comm):
+        pol = make_policy()
+        tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=1), comm=comm, topology="tp")
+        tr.check_replicated_adapters()                       # identical copies pass
+        if comm.rank == 1:
+            with torch.no_grad():
+                tr.params[0].view(-1)[0] += 1e-3
+        before = [p.detach().clone() for p in tr.params]
+        with pytest.raises(CommMismatch, match="replicated adapter"):
+            tr.step(0)
+        assert all(torch.equal(a, b.detach()) for a, b in zip(before, tr.params))
+        return True
+    assert run_ranks(2, body, timeout=30.0) == [True, True]
+
+
+def test_failed_window_leaves_no_candidate_rows(tmp_path):
+    """Candidate rows logged by a window that later fails are cut from the ledger together with the
+    rollback of adapters, Adam state and sampler (reference trainer.rs:7819)."""
+    from ferrl_b200.telemetry import CandidateWriter, read_candidates
+    path = str(tmp_path / "candidates.jsonl")
+    varied = FnReward(lambda s, c: float(sum(int(t) for t in c.split()) % 3))
+    tr = Trainer(make_policy(), ListTok(), varied, samples(), cfg(steps=3, candidate_log_top_k=2),
+                 candidate_writer=CandidateWriter(path))
+    tr.step(0)
+    kept = read_candidates(path)
+    assert len(kept) == 2 and all(r.step == 0 for r in kept)
+
+    def boom(point):
+        if point == "before_optimizer":
+            raise RuntimeError("injected optimizer failure")
+    tr.fault_hook = boom
+    with pytest.raises(RuntimeError):
+        tr.step(1)
+    assert [r.step for r in read_candidates(path)] == [0, 0]          # step 1's rows are gone
+    tr.fault_hook = None
+    tr.step(1)
+    assert [r.step for r in read_candidates(path)] == [0, 0, 1, 1]
