@@ -1,6 +1,9 @@
 """Worker for the two-process fused data-parallel test (launched by torchrun, one rank per GPU)."""
-import math
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run as a script from any directory
+import math
 
 import torch
 

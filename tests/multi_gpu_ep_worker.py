@@ -1,7 +1,10 @@
 """Worker for the multi-process expert-parallel test (torchrun, one rank per GPU): experts sharded
 over ranks through the peer-memory dispatch/combine kernels must give every rank the result of the
 local plan over all experts, forward and backward, on repeated calls."""
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run as a script from any directory
 
 import torch
 import torch.distributed as dist

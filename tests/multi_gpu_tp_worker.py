@@ -6,8 +6,11 @@
    equal the ones with a separate all-reduce.
 Prints device timings of fused vs. GEMM + NCCL all-reduce for one training-shaped problem.
 """
-import hashlib
+import os
 import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))   # run as a script from any directory
+import hashlib
 
 import torch
 import torch.distributed as dist
@@ -88,9 +91,10 @@ def main():
     from ferrl_b200.models.dense import DenseGradModel, DenseSpec
     from ferrl_b200.models.lora import LoraSpec
     from ferrl_b200.parallel.tp import TensorParallelPlan
-    spec = DenseSpec(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
-                     num_key_value_heads=2, head_dim=64, intermediate_size=512)
-    plan = TensorParallelPlan.new(rank, world, 4, 2, 512)
+    hq, hkv = max(4, world), max(2, world)          # heads divide evenly over 2, 4 and 8 ranks
+    spec = DenseSpec(vocab_size=512, hidden_size=256, num_hidden_layers=2, num_attention_heads=hq,
+                     num_key_value_heads=hkv, head_dim=64, intermediate_size=512)
+    plan = TensorParallelPlan.new(rank, world, hq, hkv, 512)
     ids = torch.randint(0, spec.vocab_size, (2, 64), device=dev, generator=torch.Generator(device=dev).manual_seed(3))
     outs = []
     for fused_on in (False, True):

@@ -93,11 +93,12 @@ def test_peer_wait_times_out_without_hanging():
     assert float(y.sum()) == 16.0
 
 
-def test_two_process_dp_step_and_all_reduce():
-    _need_gpu(2)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_process_dp_step_and_all_reduce(world):
+    _need_gpu(world)
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29611", os.path.join(ROOT, "tests", "multi_gpu_dp_worker.py")]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29650 + world), os.path.join(ROOT, "tests", "multi_gpu_dp_worker.py")]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "DP_STEP_PASS" in res.stdout

@@ -141,21 +141,26 @@ def test_missing_peer_runs_out_without_hanging():
     assert float((y.float() - a.float() @ b.float().t()).abs().max()) < 1.0
 
 
-def test_two_process_fused_tp():
-    _need_gpu(2)
+def _torchrun(worker, world, port, marker, timeout=900):
+    """One rank per GPU; NVLS off: a rank that fails between kernels must not leave multicast bindings behind."""
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29613", os.path.join(ROOT, "tests", "multi_gpu_tp_worker.py")]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(port), os.path.join(ROOT, "tests", worker)]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    assert "TP_FUSED_PASS" in res.stdout
+    assert marker in res.stdout
+    return res.stdout
 
 
-def test_two_process_expert_parallel():
-    _need_gpu(2)
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29615", os.path.join(ROOT, "tests", "multi_gpu_ep_worker.py")]
-    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
-    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
-    assert "EP_PASS" in res.stdout
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_process_fused_tp(world):
+    _need_gpu(world)
+    out = _torchrun("multi_gpu_tp_worker.py", world, 29613 + world, "TP_FUSED_PASS")
+    print("\n".join(l for l in out.splitlines() if l.startswith("TP_TIMING")))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_process_expert_parallel(world):
+    _need_gpu(world)
+    out = _torchrun("multi_gpu_ep_worker.py", world, 29633 + world, "EP_PASS")
+    print("\n".join(l for l in out.splitlines() if l.startswith("EP_TIMING")))

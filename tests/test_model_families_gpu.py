@@ -42,7 +42,12 @@ def _build(name, dtype, device, remat=False):
                           num_key_value_heads=2, head_dim=128, global_head_dim=128, num_global_key_value_heads=2,
                           intermediate_size=512, layer_types=["sliding_attention"] * 5 + ["full_attention"],
                           sliding_window=16, max_position_embeddings=256)
-        return Gemma4GradModel(spec, lora, **kw)
+        m = Gemma4GradModel(spec, lora, **kw)
+        with torch.no_grad():           # scores are q.k without 1/sqrt(d): keep them of order ten, as trained norms do
+            for l in m.layers:
+                l.q_norm.fill_(0.3)
+                l.k_norm.fill_(0.3)
+        return m
     cfg = {"vocab_size": 1024, "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 4,
            "num_key_value_heads": 2, "intermediate_size": 512, "max_position_embeddings": 256, "rms_norm_eps": 1e-5,
            "rope_theta": 10000.0, "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
@@ -78,28 +83,50 @@ def _pair(name, remat=False):
     return cpu, gpu
 
 
-def _close(got, ref, atol, rtol, frac=1.0):
-    """|got - ref| <= atol + rtol |ref| for at least ``frac`` of the elements."""
-    ok = (got - ref).abs() <= atol + rtol * ref.abs()
-    return float(ok.float().mean()) >= frac, float((got - ref).abs().max())
+def _rel(a, b):
+    return float((a - b).norm() / b.norm().clamp(min=1e-12))
+
+
+class _eager_bf16:
+    """Run the same CUDA bf16 model through PyTorch's own kernels (the library-baseline switch): the
+    yardstick for what bf16 storage with fp32 arithmetic costs on this model, independent of our kernels."""
+
+    def __enter__(self):
+        from ferrl_b200 import ops
+        ops.use_library_kernels(True)
+
+    def __exit__(self, *exc):
+        from ferrl_b200 import ops
+        ops.use_library_kernels(False)
+        return False
+
+
+def _check_against_yardstick(kernel, eager, ref, what, slack=1.6, floor=4e-3):
+    """The kernel path must be about as close to the fp32 reference as PyTorch's bf16 path is (within
+    ``slack``, plus a small floor), in norm and in the worst element; and the two bf16 paths must agree
+    with each other far better than either agrees with a wrong model."""
+    rk, re_ = _rel(kernel, ref), _rel(eager, ref)
+    assert rk <= slack * re_ + floor, (what, "norm", rk, re_)
+    mk, me = float((kernel - ref).abs().max()), float((eager - ref).abs().max())
+    assert mk <= 2.5 * me + 10 * floor * float(ref.abs().max()), (what, "max", mk, me)
 
 
 @pytest.mark.parametrize("name", FAMILIES)
 def test_family_logits_on_gpu_match_cpu_fp32(name):
     _need_gpu()
+    from ferrl_b200.ops import cuda as C
     cpu, gpu = _pair(name)
     ids = torch.randint(0, 1024, (2, 40), generator=torch.Generator().manual_seed(1))
+    before = C.launches()
     with torch.no_grad():
         ref = cpu(ids)
         got = gpu(ids.cuda()).float().cpu()
-    # a routed-expert tie that falls the other way in bf16 moves one token's logits: allow 1 % of the
-    # elements of the sparse model to be off, none for the others
-    ok, err = _close(got, ref, 3e-2, 3e-2, 0.99 if name == "hybrid_moe" else 1.0)
-    assert ok, err
-    # negative control: the comparison is able to see a wrong model
-    with torch.no_grad():
+        assert C.launches() > before                      # this package's kernels ran
+        with _eager_bf16():
+            yard = gpu(ids.cuda()).float().cpu()
         wrong = cpu(torch.roll(ids, 1, dims=1))
-    assert not _close(got, wrong, 3e-2, 3e-2, 0.9)[0]
+    _check_against_yardstick(got, yard, ref, name)
+    assert _rel(got, ref) < 0.25 * _rel(wrong, ref)       # negative control: a wrong model is far away
 
 
 @pytest.mark.parametrize("name", FAMILIES)
@@ -111,19 +138,21 @@ def test_family_token_logprobs_and_adapter_grads_on_gpu_match_cpu(name, remat):
     ids = torch.randint(0, 1024, (3, 48), generator=g)
     start = torch.tensor([5, 9, 2])
     targets = torch.randint(0, 1024, (3, 24), generator=g)
-    lp_c = cpu.token_logprobs(ids, start, targets, 1.0)
-    lp_g = gpu.token_logprobs(ids.cuda(), start.cuda(), targets.cuda(), 1.0)
-    ok, err = _close(lp_g.float().cpu(), lp_c.detach(), 4e-2, 1e-2, 0.98 if name == "hybrid_moe" else 1.0)
-    assert ok, err
     w = torch.randn(3, 24, generator=g)
-    (lp_c * w).sum().backward()
-    (lp_g * w.cuda()).sum().backward()
-    num = den = 0.0
-    for a, b in zip(cpu.trainable_params(), gpu.trainable_params()):
-        assert b.grad is not None and torch.isfinite(b.grad).all()
-        num += float((a.grad - b.grad.float().cpu()).pow(2).sum())
-        den += float(a.grad.pow(2).sum())
-    assert den > 0 and (num / den) ** 0.5 < (0.12 if name == "hybrid_moe" else 0.06), (num / den) ** 0.5
+
+    def run(model, dev):
+        for p in model.trainable_params():
+            p.grad = None
+        lp = model.token_logprobs(ids.to(dev), start.to(dev), targets.to(dev), 1.0)
+        (lp * w.to(dev)).sum().backward()
+        return lp.detach().float().cpu(), torch.cat([p.grad.float().cpu().reshape(-1) for p in model.trainable_params()])
+    lp_ref, g_ref = run(cpu, "cpu")
+    lp_k, g_k = run(gpu, "cuda")
+    with _eager_bf16():
+        lp_e, g_e = run(gpu, "cuda")
+    assert torch.isfinite(g_k).all()
+    _check_against_yardstick(lp_k, lp_e, lp_ref, name + " logprobs")
+    _check_against_yardstick(g_k, g_e, g_ref, name + " adapter grads", slack=2.0, floor=1e-2)
 
 
 @pytest.mark.parametrize("name", FAMILIES)
@@ -132,14 +161,22 @@ def test_family_cached_decode_on_gpu_matches_full_forward(name):
     _, gpu = _pair(name)
     gpu.merge_adapters()
     ids = torch.randint(0, 1024, (4, 36), generator=torch.Generator().manual_seed(4)).cuda()
-    with torch.no_grad():
+
+    def run():
         full = gpu(ids).float()
         dec = gpu.new_decoder(4, 64)
-        lg = dec.prefill(ids[:, :11], torch.full((4,), 11, device="cuda"))
-        oks = [_close(lg.float(), full[:, 10], 4e-2, 3e-2, 0.98 if name == "hybrid_moe" else 1.0)]
+        outs = [dec.prefill(ids[:, :11], torch.full((4,), 11, device="cuda")).float()]
         for t in range(11, 36):
-            oks.append(_close(dec.decode(ids[:, t]).float(), full[:, t], 4e-2, 3e-2, 0.98 if name == "hybrid_moe" else 1.0))
-    assert all(o for o, _ in oks), max(e for _, e in oks)
+            outs.append(dec.decode(ids[:, t]).float())
+        return full[:, 10:], torch.stack(outs, 1)
+    with torch.no_grad():
+        full_k, dec_k = run()
+        with _eager_bf16():
+            full_e, dec_e = run()
+    # cached decode vs full forward of the same path: as consistent as PyTorch's own bf16 path is
+    rk, re_ = _rel(dec_k, full_k), _rel(dec_e, full_e)
+    assert rk <= 1.6 * re_ + 1e-2, (name, rk, re_)
+    assert _rel(dec_k, full_e) < 0.2                      # and the two paths describe the same model
 
 
 def test_graphed_decode_retires_finished_rows_and_leaves_live_rows_bit_identical():
