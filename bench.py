@@ -89,31 +89,92 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# ---------------------------------------------------------------------------------------------
+# Benchmark configurations.  "qwen3-dp" is the headline (default); the other three time the
+# remaining model families / parallel layouts at their named geometries (random weights).
+CONFIGS = {
+    "qwen3-dp": dict(label="Qwen3-8B (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)", lora="r16 all-linear",
+                     prompts=16, group=8, max_new=1024, prompt_lo=128, prompt_hi=512, microbatch=8, remat=0, beta=0.0,
+                     parallelism="dp", rank_lora=16),
+    "gemma-tp": dict(label="Gemma-style dense (62L, h5376, 32q/16kv, d128, GeGLU 21504, vocab262144, window 1024 at 5:1)",
+                     lora="r16 attention+MLP", prompts=64, group=8, max_new=2048, prompt_lo=256, prompt_hi=256, microbatch=2,
+                     remat=1, beta=0.0, parallelism="tp", rank_lora=16),
+    "moe-ep": dict(label="Qwen3.5-style hybrid MoE (48L, h2048, GDN:GQA 3:1, 16q/2kv d256, GDN 16x128, 128 experts top-8 "
+                         "ffn768 + shared, vocab151936)", lora="r8 attention+shared expert", prompts=16, group=8, max_new=1024,
+                   prompt_lo=512, prompt_hi=512, microbatch=4, remat=1, beta=0.0, parallelism="ep", rank_lora=8),
+    "hybrid27b-dp": dict(label="Qwen3.6-27B-class dense hybrid (64L, h5120, GDN:GQA 3:1, 24q/4kv d256, ffn17408, vocab151936)",
+                         lora="r32 all-linear", prompts=4, group=16, max_new=4096, prompt_lo=1024, prompt_hi=1024, microbatch=1,
+                         remat=1, beta=0.04, parallelism="dp", rank_lora=32),
+}
+
+
+def _build_model(args, comm, device):
+    import torch
+    from ferrl_b200.models import DenseGradModel, DenseSpec, LoraSpec, qwen3_8b_spec
+    cfg = CONFIGS[args.config]
+    max_pos = (args.prompt_hi + args.max_new + 127) // 128 * 128 + 128
+    lora = LoraSpec(cfg["rank_lora"], 2.0 * cfg["rank_lora"])
+    kw = dict(dtype=torch.bfloat16, device=device, remat=bool(args.remat))
+    if args.config == "qwen3-dp":
+        if args.model == "qwen3-8b":
+            spec = qwen3_8b_spec(max_pos)
+        else:  # reduced geometry for bring-up only; never used for a reported number
+            spec = DenseSpec(vocab_size=32768, hidden_size=1024, num_hidden_layers=4, num_attention_heads=8,
+                             num_key_value_heads=2, head_dim=128, intermediate_size=3072, max_position_embeddings=max_pos)
+        return DenseGradModel(spec, lora, **kw), spec
+    small = args.model == "bringup"
+    if args.config == "gemma-tp":
+        from ferrl_b200.models.gemma4 import Gemma4GradModel, Gemma4Spec
+        from ferrl_b200.parallel.tp import TensorParallelPlan
+        L = 6 if small else 62
+        spec = Gemma4Spec(vocab_size=8192 if small else 262144, hidden_size=512 if small else 5376, num_hidden_layers=L,
+                          num_attention_heads=32, num_key_value_heads=16, head_dim=128, global_head_dim=128,
+                          num_global_key_value_heads=16, intermediate_size=2048 if small else 21504,
+                          layer_types=["full_attention" if i % 6 == 5 else "sliding_attention" for i in range(L)],
+                          sliding_window=1024, max_position_embeddings=max_pos)
+        tp = TensorParallelPlan.new(comm.rank, comm.world_size, 32, 16, spec.intermediate_size) if comm.world_size > 1 else None
+        # the frozen base is kept once (no resident transpose): 27B parameters leave no room for a second copy
+        return Gemma4GradModel(spec, lora, tp=tp, keep_transpose=False, **kw), spec
+    from ferrl_b200.models.qwen35 import MoeDims, Qwen35GradModel, Qwen35LoraTargets, Qwen35Spec
+    if args.config == "moe-ep":
+        L = 4 if small else 48
+        spec = Qwen35Spec(vocab_size=8192 if small else 151936, hidden_size=512 if small else 2048, num_hidden_layers=L,
+                          num_attention_heads=16, num_key_value_heads=2, head_dim=256, intermediate_size=768,
+                          layer_types=["full_attention" if i % 4 == 3 else "linear_attention" for i in range(L)],
+                          max_position_embeddings=max_pos, lin_k_heads=16, lin_v_heads=16, lin_k_dim=128, lin_v_dim=128,
+                          moe=MoeDims(16 if small else 128, 8, 768, 768))
+        ep = (comm.rank, comm.world_size) if comm.world_size > 1 else None
+        return Qwen35GradModel(spec, lora, Qwen35LoraTargets("qkvo", "gud", ""), ep=ep, **kw), spec
+    L = 4 if small else 64
+    spec = Qwen35Spec(vocab_size=8192 if small else 151936, hidden_size=512 if small else 5120, num_hidden_layers=L,
+                      num_attention_heads=24, num_key_value_heads=4, head_dim=256, intermediate_size=1024 if small else 17408,
+                      layer_types=["full_attention" if i % 4 == 3 else "linear_attention" for i in range(L)],
+                      max_position_embeddings=max_pos, lin_k_heads=16, lin_v_heads=48, lin_k_dim=128, lin_v_dim=128)
+    return Qwen35GradModel(spec, lora, Qwen35LoraTargets("qkvo", "gud", "io"), keep_transpose=False, **kw), spec
+
+
 def build_trainer(args, comm, device):
     import torch
     from ferrl_b200.config import TrainerConfig
     from ferrl_b200.lm_policy import LmPolicy
-    from ferrl_b200.models import DenseGradModel, DenseSpec, LoraSpec, qwen3_8b_spec
     from ferrl_b200.rewards import RewardFn, Sample
     from ferrl_b200.sampler import GrpoSampler
     from ferrl_b200.tokenizer import SyntheticTokenizer
     from ferrl_b200.trainer import Trainer
 
-    max_pos = (args.prompt_hi + args.max_new + 127) // 128 * 128 + 128
-    if args.model == "qwen3-8b":
-        spec = qwen3_8b_spec(max_pos)
-    else:  # reduced geometry for bring-up only; never used for a reported number
-        spec = DenseSpec(vocab_size=32768, hidden_size=1024, num_hidden_layers=4, num_attention_heads=8,
-                         num_key_value_heads=2, head_dim=128, intermediate_size=3072, max_position_embeddings=max_pos)
-    model = DenseGradModel(spec, LoraSpec(16, 32.0), dtype=torch.bfloat16, device=device, remat=bool(args.remat))
+    cfg = CONFIGS[args.config]
+    model, spec = _build_model(args, comm, device)
     model.init_random(seed=1234, std=0.02)
     # non-zero B so the adapter path carries signal from the first step (same on every rank)
     g = torch.Generator().manual_seed(99)
+    r = cfg["rank_lora"]
     with torch.no_grad():
         for p in model.trainable_params():
-            if p.shape[1] == 16:
+            if p.shape[1] == r:
                 p.copy_((torch.randn(p.shape, generator=g) * 0.01).to(p.device))
-    policy = LmPolicy(model, GrpoSampler(args.seed, 1.0), score_microbatch=args.microbatch, early_exit_every=64)
+    topology = "tp" if cfg["parallelism"] == "tp" and comm.world_size > 1 else "dp"
+    policy = LmPolicy(model, GrpoSampler(args.seed, 1.0), comm if topology == "tp" else None,
+                      score_microbatch=args.microbatch, early_exit_every=0 if cfg["parallelism"] == "ep" else 64)
     if args.no_graph:
         policy.use_cuda_graph = False
 
@@ -125,15 +186,27 @@ def build_trainer(args, comm, device):
 
     tok = SyntheticTokenizer(spec.vocab_size, args.prompt_lo, args.prompt_hi)
     samples = [Sample(f"synthetic prompt #{i}", i) for i in range(4096)]
-    cfg = TrainerConfig(steps=10 ** 6, group_size=args.group, max_new_tokens=args.max_new, temperature=1.0, mu=1,
-                        beta=0.0, clip_eps=0.2, lr=1e-5, max_grad_norm=1.0, truncation_masking=False,
-                        loss_type="dapo", grad_accum_steps=1, prompts_per_item=args.prompts,
-                        backward_microbatch_size=args.microbatch, eos_token_id=spec.vocab_size - 1, top_p=0.95)
+    tcfg = TrainerConfig(steps=10 ** 6, group_size=args.group, max_new_tokens=args.max_new, temperature=1.0, mu=1,
+                         beta=cfg["beta"], clip_eps=0.2, lr=1e-5, max_grad_norm=1.0, truncation_masking=False,
+                         loss_type="dapo", grad_accum_steps=1, prompts_per_item=args.prompts,
+                         backward_microbatch_size=args.microbatch, eos_token_id=spec.vocab_size - 1, top_p=0.95)
     fused = None
-    if comm.world_size > 1 and not args.nccl_baseline:
-        from ferrl_b200.parallel.dp import FusedDpStep
-        fused = FusedDpStep.create(comm, policy.trainable_params(), device)
-    trainer = Trainer(policy, tok, BernoulliVerifier(), samples, cfg, comm=comm, fused_dp_step=fused)
+    runtime = None
+    if comm.world_size > 1:
+        from ferrl_b200.parallel.runtime import ParallelRuntime
+        rows = args.microbatch * (args.prompt_hi + args.max_new)
+        if topology == "tp":
+            runtime = ParallelRuntime.create(comm, device, tensor_parallel=True, hidden=spec.hidden_size,
+                                             max_rows=max(rows, args.prompts * args.group))
+        elif cfg["parallelism"] == "ep":
+            runtime = ParallelRuntime.create(comm, device, expert_parallel={
+                "num_experts": spec.moe.num_experts, "hidden": spec.hidden_size, "top_k": spec.moe.top_k,
+                "max_tokens": max(rows, args.prompts * args.group, args.prompts * args.prompt_hi), "capacity_factor": 2.0})
+        if topology == "dp" and not args.nccl_baseline:
+            from ferrl_b200.parallel.dp import FusedDpStep
+            fused = FusedDpStep.create(comm, policy.trainable_params(), device)
+    trainer = Trainer(policy, tok, BernoulliVerifier(), samples, tcfg, comm=comm, topology=topology, fused_dp_step=fused,
+                      parallel_runtime=runtime, lockstep_model_calls=cfg["parallelism"] == "ep" and comm.world_size > 1)
     return trainer, policy, spec
 
 
@@ -145,18 +218,25 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch-baseline"],
                     help="torch-baseline: the same trainer on PyTorch library kernels (eager ops, no CUDA graph, "
                          "per-tensor NCCL all-reduce) - a stand-in for the reference's execution shape")
-    ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "bringup"])
-    ap.add_argument("--prompts", type=int, default=16)
-    ap.add_argument("--group", type=int, default=8)
-    ap.add_argument("--max-new", type=int, default=1024)
-    ap.add_argument("--prompt-lo", type=int, default=128)
-    ap.add_argument("--prompt-hi", type=int, default=512)
-    ap.add_argument("--microbatch", type=int, default=8, help="rows per scoring/backward micro-batch")
-    ap.add_argument("--remat", type=int, default=0, help="1 = recompute layer activations in backward (less memory)")
+    ap.add_argument("--config", default="qwen3-dp", choices=sorted(CONFIGS),
+                    help="qwen3-dp: the headline benchmark (default); gemma-tp / moe-ep / hybrid27b-dp: the other model "
+                         "families at their named geometries (tensor-parallel, expert-parallel, data-parallel with a KL reference)")
+    ap.add_argument("--model", default="qwen3-8b", choices=["qwen3-8b", "bringup"],
+                    help="bringup: a reduced geometry of the chosen config, for plumbing checks only")
+    ap.add_argument("--prompts", type=int, default=None, help="prompts per rank (per tensor-parallel group for gemma-tp)")
+    ap.add_argument("--group", type=int, default=None)
+    ap.add_argument("--max-new", type=int, default=None)
+    ap.add_argument("--prompt-lo", type=int, default=None)
+    ap.add_argument("--prompt-hi", type=int, default=None)
+    ap.add_argument("--microbatch", type=int, default=None, help="rows per scoring/backward micro-batch")
+    ap.add_argument("--remat", type=int, default=None, help="1 = recompute layer activations in backward (less memory)")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for per-kernel profiling)")
     ap.add_argument("--nccl-baseline", action="store_true", help="use per-tensor NCCL all-reduce instead of the fused DP step")
     args = ap.parse_args()
+    for k in ("prompts", "group", "max_new", "prompt_lo", "prompt_hi", "microbatch", "remat"):
+        if getattr(args, k) is None:
+            setattr(args, k, CONFIGS[args.config][k])
     if args.impl == "reference":
         return reference_arm(args)
     if args.warmup < 3:
@@ -224,7 +304,8 @@ def main():
     vals = comm.all_gather_bytes(json.dumps({"ms": ms, "tok": tokens_local, "rollout_ms": phase.get("rollout", 0.0)}).encode())
     vals = [json.loads(v.decode()) for v in vals]
     ms_max = max(v["ms"] for v in vals)
-    tok_total = sum(v["tok"] for v in vals)
+    shared_batch = CONFIGS[args.config]["parallelism"] == "tp"      # tensor-parallel ranks work on ONE batch together
+    tok_total = vals[0]["tok"] if shared_batch else sum(v["tok"] for v in vals)
     value = tok_total / (ms_max / 1e3)
     # decode throughput: completion tokens of all ranks over the slowest rank's rollout phase (prefill included)
     rollout_ms_max = max(v["rollout_ms"] for v in vals)
@@ -243,21 +324,25 @@ def main():
     barrier()
     wall = time.perf_counter() - t0
     vals2 = [json.loads(v.decode()) for v in comm.all_gather_bytes(json.dumps({"s": wall, "tok": tok2}).encode())]
-    e2e = sum(v["tok"] for v in vals2) / max(v["s"] for v in vals2)
+    e2e = (vals2[0]["tok"] if shared_batch else sum(v["tok"] for v in vals2)) / max(v["s"] for v in vals2)
 
     if rank == 0:
         out = {
-            "metric": "GRPO step tok/s (rollout+score+update) Qwen3-8B LoRA", "value": value, "unit": "tokens/s",
+            "metric": "GRPO step tok/s (rollout+score+update) " + ("Qwen3-8B LoRA" if args.config == "qwen3-dp" else args.config + " LoRA"),
+            "value": value, "unit": "tokens/s",
             "n_gpus": comm.world_size, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_max / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / BASELINE_VALUE) if BASELINE_VALUE else None, "dtype": "bf16",
             "data": "synthetic prompts (uniform random token ids), random-init weights, Bernoulli(0.5) rewards",
             "impl": args.impl,
-            "config": {"model": "Qwen3-8B (36L, h4096, 32q/8kv, d128, ffn12288, vocab151936)" if args.model == "qwen3-8b"
-                       else "bringup (NOT the named config)",
-                       "global_batch": args.prompts * args.group * comm.world_size, "prompts_per_rank": args.prompts,
+            "config": {"name": args.config,
+                       "model": CONFIGS[args.config]["label"] if args.model == "qwen3-8b" else "bringup (NOT the named config)",
+                       "global_batch": args.prompts * args.group * (1 if CONFIGS[args.config]["parallelism"] == "tp" else comm.world_size),
+                       "prompts_per_rank": args.prompts,
                        "group_size": args.group, "seq_len": f"prompt U[{args.prompt_lo},{args.prompt_hi}] + {args.max_new} new",
-                       "lora": "r16 all-linear", "top_p": 0.95, "parallelism": f"dp{comm.world_size}",
+                       "lora": CONFIGS[args.config]["lora"], "top_p": 0.95,
+                       "parallelism": f"{CONFIGS[args.config]['parallelism']}{comm.world_size}",
+                       "kl_beta": CONFIGS[args.config]["beta"],
                        "l2_policy": "inputs larger than L2 (16 GB of weights stream every step)",
                        "dp_step": ("single rank" if comm.world_size == 1 else
                                    "nccl per tensor" if args.nccl_baseline else "fused-peer-memory"),

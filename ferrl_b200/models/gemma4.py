@@ -290,6 +290,9 @@ class Gemma4GradModel(nn.Module):
         g = torch.Generator().manual_seed(seed)
         dev = self.embed.device
         rnd = lambda shape: (torch.randn(shape, generator=g) * std).to(self.dtype).to(dev)  # noqa: E731
+        if dev.type == "cuda":          # device-side generation for the large synthetic benchmarks
+            gg = torch.Generator(device=dev).manual_seed(seed)
+            rnd = lambda shape: (torch.randn(shape, generator=gg, device=dev, dtype=torch.float32) * std).to(self.dtype)  # noqa: E731
         self.embed.copy_(rnd(self.embed.shape))
         for l in self.layers:
             for p in l.projections():

@@ -410,6 +410,11 @@ class Qwen35GradModel(nn.Module):
 
         def rnd(shape, s=std):
             return (torch.randn(shape, generator=g) * s).to(self.dtype).to(dev)
+        if dev.type == "cuda":
+            gg = torch.Generator(device=dev).manual_seed(seed)
+
+            def rnd(shape, s=std):  # noqa: F811 - device-side generation for the large synthetic benchmarks
+                return (torch.randn(shape, generator=gg, device=dev, dtype=torch.float32) * s).to(self.dtype)
         self.embed.copy_(rnd(self.embed.shape))
         if self.lm_head is not None:
             self.lm_head.copy_(rnd(self.lm_head.shape))

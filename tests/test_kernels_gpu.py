@@ -14,6 +14,9 @@ def _dev():
     return torch.device("cuda")
 
 
+from _numerics import close as _close   # norm ratio AND an elementwise bound
+
+
 def _rel(a, b):
     return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
 
@@ -33,9 +36,9 @@ def test_gemm_matches_fp32(M, N, K, bn):
     torch.cuda.synchronize()
     assert C.kernel_status() == 0
     ref = a.float() @ b.float().t()
-    assert _rel(out, ref) < 6e-3
+    _close(out, ref, 6e-3)
     out32 = C.gemm(a, b, out_f32=True, force_bn=bn)
-    assert _rel(out32, ref) < 1e-5 * math.sqrt(K) + 1e-6
+    _close(out32, ref, 1e-5 * math.sqrt(K) + 1e-6)
 
 
 def test_gemm_lora_slab_and_residual():
@@ -51,7 +54,7 @@ def test_gemm_lora_slab_and_residual():
     out = C.gemm(a, b, a2, b2, res)
     ref = a.float() @ b.float().t() + a2.float() @ b2.float().t() + res.float()
     assert C.kernel_status() == 0
-    assert _rel(out, ref) < 6e-3
+    _close(out, ref, 6e-3)
 
 
 @pytest.mark.parametrize("M,N,K,split", [(128, 4096, 4096, 4), (128, 6144, 4096, 0), (100, 512, 12288, 8), (256, 4096, 1024, 3)])
@@ -65,10 +68,10 @@ def test_gemm_split_k(M, N, K, split):
     out = C.gemm(a, b, residual=res, force_split=split)
     assert C.kernel_status() == 0
     ref = a.float() @ b.float().t() + res.float()
-    assert _rel(out, ref) < 6e-3
+    _close(out, ref, 6e-3)
     assert torch.equal(out, C.gemm(a, b, residual=res, force_split=split))   # deterministic reduce order
     out32 = C.gemm(a, b, out_f32=True, force_split=split)
-    assert _rel(out32, a.float() @ b.float().t()) < 2e-3
+    _close(out32, a.float() @ b.float().t(), 2e-3)
 
 
 def test_gemm_deterministic():
@@ -91,19 +94,20 @@ def test_rmsnorm_family(dtype, H):
     for zc in (False, True):
         y = C.rmsnorm(x, w, 1e-6, zc)
         ref = E.rmsnorm(x.detach().float(), w.float(), 1e-6, zc)
-        assert _rel(y, ref) < tol
+        _close(y, ref, tol)
     y, h = C.add_rmsnorm(x, r, w, 1e-6)
     yr, hr = E.add_rmsnorm(x.detach().float(), r.float(), w.float(), 1e-6)
-    assert _rel(y, yr) < tol and _rel(h, hr) < tol
+    _close(y, yr, tol)
+    _close(h, hr, tol)
     # backward
     xf = x.detach().float().requires_grad_(True)
     dy = torch.randn(33, H, device=dev)
     E.rmsnorm(xf, w.float(), 1e-6).backward(dy)
     C.rmsnorm(x, w, 1e-6).backward(dy.to(dtype))
-    assert _rel(x.grad, xf.grad) < tol
+    _close(x.grad, xf.grad, tol)
     gate = torch.randn(33, H, device=dev).to(dtype)
     with torch.no_grad():
-        assert _rel(C.rmsnorm_gated(x, gate, w, 1e-6), E.rmsnorm_gated(x.float(), gate.float(), w.float(), 1e-6)) < tol
+        _close(C.rmsnorm_gated(x, gate, w, 1e-6), E.rmsnorm_gated(x.float(), gate.float(), w.float(), 1e-6), tol)
 
 
 @pytest.mark.parametrize("D,half,norm", [(128, 64, True), (128, 64, False), (256, 32, True), (64, 32, True)])
@@ -124,12 +128,13 @@ def test_qk_norm_rope_fwd_bwd(D, half, norm):
     q, k = run(C.qk_norm_rope, qkv)
     ref_in = qkv.detach().float().requires_grad_(True)
     qr, kr = run(E.qk_norm_rope, ref_in)
-    assert _rel(q, qr) < 2e-2 and _rel(k, kr) < 2e-2
+    _close(q, qr, 2e-2)
+    _close(k, kr, 2e-2)
     gq, gk = torch.randn_like(qr), torch.randn_like(kr)
     (qr * gq).sum().backward(retain_graph=True)
     (kr * gk).sum().backward()
     ((q.float() * gq).sum() + (k.float() * gk).sum()).backward()
-    assert _rel(qkv.grad, ref_in.grad) < 3e-2
+    _close(qkv.grad, ref_in.grad, 3e-2)
 
 
 @pytest.mark.parametrize("D", [64, 128, 256])
@@ -146,13 +151,13 @@ def test_flash_attention_fwd_bwd(D, causal, window):
     o = C.attention(q, k, v, scale=scale, causal=causal, window=window)
     qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
     ref = E.attention(qf, kf, vf, scale=scale, causal=causal, window=window)
-    assert _rel(o, ref) < 2e-2
+    _close(o, ref, 2e-2)
     do = torch.randn_like(ref)
     ref.backward(do)
     o.backward(do.to(torch.bfloat16))
-    assert _rel(q.grad, qf.grad) < 3e-2
-    assert _rel(k.grad, kf.grad) < 3e-2
-    assert _rel(v.grad, vf.grad) < 3e-2
+    _close(q.grad, qf.grad, 3e-2)
+    _close(k.grad, kf.grad, 3e-2)
+    _close(v.grad, vf.grad, 3e-2)
 
 
 @pytest.mark.parametrize("D,Hq,Hkv", [(128, 32, 8), (64, 4, 4), (256, 16, 2), (16, 4, 2)])
@@ -168,7 +173,7 @@ def test_decode_attention(D, Hq, Hkv, window, splits, variant):
     lens = torch.tensor([1, 64, 65, 333, 200], device=dev, dtype=torch.int32)
     out = C.decode_attention(q, kc, vc, lens, scale=1 / math.sqrt(D), window=window, n_splits=splits, variant=variant)
     ref = E.decode_attention(q.float(), kc.float(), vc.float(), lens, scale=1 / math.sqrt(D), window=window)
-    assert _rel(out, ref) < 2e-2
+    _close(out, ref, 2e-2)
 
 
 def test_kv_append():
@@ -194,11 +199,11 @@ def test_glu(act):
     y = C.swiglu(gu, act)
     gf = gu.detach().float().requires_grad_(True)
     yr = E.swiglu(gf, act)
-    assert _rel(y, yr) < 1e-2
+    _close(y, yr, 1e-2)
     d = torch.randn_like(yr)
     yr.backward(d)
     y.backward(d.to(torch.bfloat16))
-    assert _rel(gu.grad, gf.grad) < 2e-2
+    _close(gu.grad, gf.grad, 2e-2)
 
 
 def test_embedding_and_merge():
@@ -209,7 +214,7 @@ def test_embedding_and_merge():
     assert torch.equal(C.embedding(ids, table), E.embedding(ids, table))
     w = torch.randn(96, 128, device=dev).to(torch.bfloat16)
     a, b = torch.randn(16, 128, device=dev), torch.randn(96, 16, device=dev) * 0.1
-    assert _rel(C.lora_merge(w, a, b), E.lora_merge(w, a, b).float()) < 1e-2
+    _close(C.lora_merge(w, a, b), E.lora_merge(w, a, b).float(), 1e-2)
 
 
 def test_lora_linear_fwd_bwd():
@@ -224,13 +229,13 @@ def test_lora_linear_fwd_bwd():
     xf = x.detach().float().requires_grad_(True)
     af, bf = a.detach().clone().requires_grad_(True), b.detach().clone().requires_grad_(True)
     yr = E.lora_linear(xf, w.float(), af, bf)
-    assert _rel(y, yr) < 1e-2
+    _close(y, yr, 1e-2)
     d = torch.randn_like(yr)
     yr.backward(d)
     y.backward(d.to(torch.bfloat16))
-    assert _rel(x.grad, xf.grad) < 2e-2
-    assert _rel(a.grad, af.grad) < 3e-2
-    assert _rel(b.grad, bf.grad) < 3e-2
+    _close(x.grad, xf.grad, 2e-2)
+    _close(a.grad, af.grad, 3e-2)
+    _close(b.grad, bf.grad, 3e-2)
 
 
 @pytest.mark.parametrize("softcap", [0.0, 30.0])
@@ -248,7 +253,7 @@ def test_logprob_gather_fwd_bwd(softcap):
     d = torch.randn_like(ref)
     ref.backward(d)
     lp.backward(d)
-    assert _rel(h.grad, hf.grad) < 4e-2
+    _close(h.grad, hf.grad, 4e-2)
 
 
 @pytest.mark.parametrize("V", [3001, 4096])      # scalar loads / 16-byte vector loads
@@ -362,12 +367,12 @@ def test_flash_forward_tcgen05(B, S, Hq, Hkv, variant):
     wf = wide.detach().float().requires_grad_(True)
     qf, kf, vf = wf.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
     ref = E.attention(qf.reshape(B, S, Hq, D), kf.reshape(B, S, Hkv, D), vf.reshape(B, S, Hkv, D), scale=scale, causal=True)
-    assert _rel(o, ref) < 2e-2
-    assert _rel(o, o_warp) < 2e-2
+    _close(o, ref, 2e-2)
+    _close(o, o_warp, 2e-2)
     do = torch.randn_like(ref)
     ref.backward(do)
     o.backward(do.to(torch.bfloat16))
-    assert _rel(wide.grad, wf.grad) < 3e-2
+    _close(wide.grad, wf.grad, 3e-2)
 
 
 @pytest.mark.gpu
@@ -395,7 +400,7 @@ def test_flash_backward_tcgen05(B, S, Hq, Hkv):
     errs = [_rel(a, b) for a, b in zip(got, ref)]
     assert max(errs) < 3e-2, f"dq/dk/dv rel err {errs}; warp-level {[_rel(a, b) for a, b in zip(warp, ref)]}"
     for a, b in zip(got, warp):
-        assert _rel(a, b) < 3e-2
+        _close(a, b, 3e-2)
     again = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 0)
     for a, b in zip(got, again):
         assert torch.equal(a, b)       # fixed summation order
