@@ -202,9 +202,10 @@ def build_trainer(args, comm, device):
             runtime = ParallelRuntime.create(comm, device, expert_parallel={
                 "num_experts": spec.moe.num_experts, "hidden": spec.hidden_size, "top_k": spec.moe.top_k,
                 "max_tokens": max(rows, args.prompts * args.group, args.prompts * args.prompt_hi), "capacity_factor": 2.0})
-        if topology == "dp" and not args.nccl_baseline:
-            from ferrl_b200.parallel.dp import FusedDpStep
-            fused = FusedDpStep.create(comm, policy.trainable_params(), device)
+    if topology == "dp" and not args.nccl_baseline:
+        # one kernel for reduce (a no-op at world 1), clip and AdamW at every world size
+        from ferrl_b200.parallel.dp import FusedDpStep
+        fused = FusedDpStep.create(comm, policy.trainable_params(), device)
     trainer = Trainer(policy, tok, BernoulliVerifier(), samples, tcfg, comm=comm, topology=topology, fused_dp_step=fused,
                       parallel_runtime=runtime, lockstep_model_calls=cfg["parallelism"] == "ep" and comm.world_size > 1)
     return trainer, policy, spec

@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc1|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc1|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk|gdn_tc_fwd|gdn_tc_bwd   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -126,6 +126,20 @@ def profile_case(name, C):
         gc = -torch.rand(B_, T_, Hv_, device=dev)
         bc = torch.rand(B_, T_, Hv_, device=dev)
         fn = lambda: C.gdn_chunk_fwd(qc, kc_, vc_, gc, bc)
+    elif name in ("gdn_tc_fwd", "gdn_tc_bwd"):
+        B_, T_, Hk_, Hv_ = 4, 1024, 16, 32
+        f32 = lambda *sh: torch.randn(*sh, device=dev, generator=g)  # noqa: E731
+        qn = torch.nn.functional.normalize(f32(B_, T_, Hk_, 128), dim=-1) * 128 ** -0.5
+        kn = torch.nn.functional.normalize(f32(B_, T_, Hk_, 128), dim=-1)
+        vv = f32(B_, T_, Hv_, 128)
+        gc = -torch.rand(B_, T_, Hv_, device=dev) * 0.3
+        bc = torch.rand(B_, T_, Hv_, device=dev)
+        if name == "gdn_tc_fwd":
+            fn = lambda: C.lib().gdn_tc_fwd(qn, kn, vv, gc, bc, None)
+        else:
+            saved_ = C.lib().gdn_tc_fwd(qn, kn, vv, gc, bc, None)[2:]
+            dO_ = f32(B_, T_, Hv_, 128)
+            fn = lambda: C.lib().gdn_tc_bwd(qn, kn, vv, bc, *saved_, dO_, None)
     elif name == "lora_grad":
         u, xx = rnd(24576, 48), rnd(24576, 4096)
         fn = lambda: C.lib().lora_grad(u, xx)
@@ -221,6 +235,39 @@ def main():
         s = T(lambda: C.gemm(a, b, a2, b2))
         report("gemm train qkv + LoRA k-slab (R=48)", s, 2 * (M * K + N * K + M * N), 2 * M * N * (K + R))
         del a, b, a2, b2
+    if want("gdn"):
+        from ferrl_b200.models import gdn as G
+        B_, T_, Hk_, Hv_ = 8, 1536, 16, 32
+        qc, kc_, vc_ = (torch.randn(B_, T_, h, 128, device=dev, dtype=bf) for h in (Hk_, Hk_, Hv_))
+        gc = -torch.rand(B_, T_, Hv_, device=dev) * 0.3
+        bc = torch.rand(B_, T_, Hv_, device=dev)
+        fl = B_ * Hv_ * (T_ // 64) * 2 * (64 * 64 * 128 * 2 + 64 * 128 * 64 * 3 + 64 * 128 * 128 * 3)
+        with torch.no_grad():
+            s = T(lambda: C.gdn_chunk_fwd(qc, kc_, vc_, gc, bc))
+            report("gdn chunk scan fwd B8 T1536 Hv32, CUDA-core kernel", s, 0, fl)
+            s = T(lambda: C.gdn_chunk_tc(qc, kc_, vc_, gc, bc))
+            report("gdn chunk fwd B8 T1536 Hv32, tensor-core kernels (incl. l2norm, casts)", s, 0, fl)
+            qn = torch.nn.functional.normalize(qc.float(), dim=-1) * 128 ** -0.5
+            kn = torch.nn.functional.normalize(kc_.float(), dim=-1)
+            vf = vc_.float()
+            s = T(lambda: C.lib().gdn_tc_fwd(qn, kn, vf, gc, bc, None))
+            report("gdn chunk fwd B8 T1536 Hv32, tensor-core kernels only", s, 0, fl)
+        saved = C.lib().gdn_tc_fwd(qn, kn, vf, gc, bc, None)[2:]
+        dO_ = torch.randn_like(vf)
+        s = T(lambda: C.lib().gdn_tc_bwd(qn, kn, vf, bc, *saved, dO_, None))
+        report("gdn chunk bwd B8 T1536 Hv32, tensor-core kernels only", s, 0, 3 * fl)
+        del saved
+
+        def train(fn_):
+            leaves = [t.clone().requires_grad_() for t in (qc, kc_, vc_)]
+            o, _ = fn_(*leaves)
+            o.backward(torch.ones_like(o))
+        rep_ = Hv_ // Hk_
+        s = T(lambda: train(lambda a, b_, c: C.gdn_chunk_tc(a, b_, c, gc, bc)))
+        report("gdn chunk fwd+bwd B8 T1536 Hv32, tensor-core kernels via autograd", s, 0, 4 * fl)
+        s = T(lambda: train(lambda a, b_, c: G.gated_delta_rule_chunked(a.repeat_interleave(rep_, 2), b_.repeat_interleave(rep_, 2),
+                                                                        c, gc, bc, None, use_qk_l2norm=True)))
+        report("gdn chunk fwd+bwd B8 T1536 Hv32, eager chunk loop (the former training path)", s, 0, 4 * fl)
     if want("slab"):
         # cost of the adapter k-slab as a function of its width (the k-block is 64 wide whatever R is)
         M, N, K = 24576, 6144, H

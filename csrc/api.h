@@ -49,6 +49,14 @@ struct GemmArgs {
   // of squares of the stored output, parts = gemm_ss_parts()
   const float* ss_in; int ss_parts; long long ss_ld; float ss_inv_k, ss_eps;
   float* ss_out;
+  // language-model head without a logits tensor (tile width 256; two_cta 256 or the one-SM kernel):
+  // every accumulator value x becomes the scored logit z = softcap(x) * lp_inv_t.
+  // lp_mode 1: out is not written; lp_ws [ceil(N/256), M] float2 receives per row and column tile the running
+  //            (max, sum exp(z - max)), lp_tl [M] the z of the target column (lp_targets int64, vocabulary index);
+  // lp_mode 2: out (bf16) receives lp_coef[row] * (exp(z - lp_lse[row]) - [col == target]) * dz/dx.
+  // B may be a slice of the vocabulary starting at row lp_col0.
+  int lp_mode; const long long* lp_targets; float lp_inv_t, lp_cap; long long lp_col0;
+  float* lp_ws; float* lp_tl; const float* lp_lse; const float* lp_coef;
 };
 // number of partial rows ss_out needs for a call that would run with tile width bn and cluster size (1: none)
 inline int gemm_ss_parts(int N, int bn, int cluster) { return ((N + bn - 1) / bn) * (cluster > 1 ? cluster : 1); }
@@ -80,6 +88,9 @@ const char* rmsnorm(int dtype, const void* x, const void* res, const void* w, co
                     long long rows, int H, float eps, bool zero_centered, cudaStream_t s);
 const char* rmsnorm_bwd(int dtype, const void* x, const void* w, const void* dy, void* dx, long long rows, int H,
                         float eps, bool zero_centered, cudaStream_t s);
+// gated form y = rmsnorm(x) * w * silu(gate): gradients of x and gate for a frozen weight
+const char* rmsnorm_gated_bwd(int dtype, const void* x, const void* gate, const void* w, const void* dy, void* dx,
+                              void* dg, long long rows, int H, float eps, cudaStream_t s);
 struct QkNormRopeArgs {
   int dtype; bool backward;
   const void* q_in; long long ld_q;                     // [n_tok, Hq*D] rows with token stride ld_q (may be a view
@@ -177,6 +188,8 @@ size_t flash_bwd_tc_scratch_floats(const FlashArgs& a);   // size of a.delta for
 const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream);
 
 // ---- vocabulary rows ----
+// finish of the head GEMM's log-prob epilogue (GemmArgs::lp_mode 1): ws [n_tiles, M] float2, tl [M]
+const char* logprob_finalize(const float* ws, const float* tl, int n_tiles, int M, float* lp, float* lse, cudaStream_t s);
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,
                          long long rows, int V, float temperature, float softcap, cudaStream_t s);
 const char* logprob_rows_bwd(int dtype, void* logits, long long ld, const long long* targets, const float* lse,
@@ -211,6 +224,20 @@ const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                             const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
                             bool l2norm, float eps, void* out, cudaStream_t stream);
+
+// ---- chunked gated delta rule on tensor cores, forward and backward (csrc/kernels/gdn_tc.cu)
+// All tensors fp32 and contiguous: q,k [B,T,Hk,128] (already L2-normalised, q scaled), v/out/dO/dq/dk/dv
+// [B,T,Hv,128], g/beta/dG/dbeta [B,T,Hv]; per-chunk tensors (n = T / 64 chunks) Gc [B,Hv,n,64], gl [B,Hv,n],
+// Tm [B,Hv,n,64,64], U/Wn/Kd/Vn/X0/dVn [B,Hv,n,64,128], Sin/Y0/dSout [B,Hv,n,128,128]; states [B,Hv,128,128].
+// T must be a multiple of 64 (at most 65536).  S0 and dS_final may be null.
+const char* gdn_tc_forward(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* S0,
+                           int B, int T, int Hk, int Hv, float* Gc, float* gl, float* Tm, float* U, float* Wn, float* Kd,
+                           float* out, float* S_out, float* Sin, float* Vn, cudaStream_t stream);
+const char* gdn_tc_backward(const float* q, const float* k, const float* v, const float* beta, const float* Gc, const float* gl,
+                            const float* Tm, const float* Wn, const float* Kd, const float* Vn, const float* Sin,
+                            const float* dO, const float* dS_final, int B, int T, int Hk, int Hv, float* X0, float* Y0,
+                            float* dVn, float* dSout, float* dq, float* dk, float* dv, float* dbeta, float* dG, float* dS0,
+                            cudaStream_t stream);
 
 // ---- expert parallelism over the symmetric heap (csrc/moe/ep.cu)
 struct EpDispatchParams {

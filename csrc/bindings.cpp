@@ -432,6 +432,75 @@ Tensor gdn_decode_step(const Tensor& q, const Tensor& k, const Tensor& v, const 
 
 // q,k [B,T,Hk,KD], v [B,T,Hv,VD] bf16 (head dims contiguous, token/batch strides free), g,beta [B,T,Hv] f32,
 // S0 [B,Hv,KD,VD] f32 or none -> (out [B,T,Hv,VD] bf16, S [B,Hv,KD,VD] f32)
+static void gdn_tc_check(const Tensor& t, const char* what) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kFloat && t.is_contiguous(), "gdn_tc: ", what, " must be contiguous fp32 on the GPU");
+}
+
+// Tensor-core chunked gated delta rule. Returns (out, S_final, Gc, gl, Tm, Wn, Kd, Vn, Sin); everything after
+// S_final feeds gdn_tc_bwd.
+std::vector<Tensor> gdn_tc_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g, const Tensor& beta,
+                               const optional<Tensor>& S0) {
+  gdn_tc_check(q, "q"); gdn_tc_check(k, "k"); gdn_tc_check(v, "v"); gdn_tc_check(g, "g"); gdn_tc_check(beta, "beta");
+  TORCH_CHECK(q.dim() == 4 && k.sizes() == q.sizes() && v.dim() == 4 && q.size(3) == 128 && v.size(3) == 128 &&
+                  v.size(0) == q.size(0) && v.size(1) == q.size(1), "gdn_tc_fwd: q,k [B,T,Hk,128], v [B,T,Hv,128]");
+  const int64_t B = q.size(0), T = q.size(1), Hk = q.size(2), Hv = v.size(2);
+  TORCH_CHECK(T % 64 == 0 && Hv % Hk == 0, "gdn_tc_fwd: T must be a multiple of 64 and Hv a multiple of Hk");
+  TORCH_CHECK(g.numel() == B * T * Hv && beta.numel() == B * T * Hv, "gdn_tc_fwd: g,beta [B,T,Hv]");
+  const float* s0 = nullptr;
+  if (S0.has_value()) {
+    gdn_tc_check(*S0, "S0");
+    TORCH_CHECK(S0->numel() == B * Hv * 128 * 128, "gdn_tc_fwd: S0 [B,Hv,128,128]");
+    s0 = S0->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  const int64_t n = T / 64;
+  auto opt = q.options();
+  Tensor out = at::empty({B, T, Hv, 128}, opt), S_out = at::empty({B, Hv, 128, 128}, opt);
+  Tensor Gc = at::empty({B, Hv, n, 64}, opt), gl = at::empty({B, Hv, n}, opt), Tm = at::empty({B, Hv, n, 64, 64}, opt);
+  Tensor U = at::empty({B, Hv, n, 64, 128}, opt), Wn = at::empty({B, Hv, n, 64, 128}, opt), Kd = at::empty({B, Hv, n, 64, 128}, opt);
+  Tensor Vn = at::empty({B, Hv, n, 64, 128}, opt), Sin = at::empty({B, Hv, n, 128, 128}, opt);
+  FERRL_CHECK(ferrl::gdn_tc_forward(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(),
+                                    beta.data_ptr<float>(), s0, B, T, Hk, Hv, Gc.data_ptr<float>(), gl.data_ptr<float>(),
+                                    Tm.data_ptr<float>(), U.data_ptr<float>(), Wn.data_ptr<float>(), Kd.data_ptr<float>(),
+                                    out.data_ptr<float>(), S_out.data_ptr<float>(), Sin.data_ptr<float>(), Vn.data_ptr<float>(),
+                                    stream()));
+  return {out, S_out, Gc, gl, Tm, Wn, Kd, Vn, Sin};
+}
+
+// Returns (dq [B,T,Hv,128] per value head, dk likewise, dv, dbeta, dG, dS0); dG is the gradient of the
+// in-chunk cumulative log decay (the caller's reverse cumulative sum inside each chunk gives dg).
+std::vector<Tensor> gdn_tc_bwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& beta, const Tensor& Gc,
+                               const Tensor& gl, const Tensor& Tm, const Tensor& Wn, const Tensor& Kd, const Tensor& Vn,
+                               const Tensor& Sin, const Tensor& dO, const optional<Tensor>& dS_final) {
+  gdn_tc_check(q, "q"); gdn_tc_check(k, "k"); gdn_tc_check(v, "v"); gdn_tc_check(beta, "beta"); gdn_tc_check(Gc, "Gc");
+  gdn_tc_check(gl, "gl"); gdn_tc_check(Tm, "Tm"); gdn_tc_check(Wn, "Wn"); gdn_tc_check(Kd, "Kd"); gdn_tc_check(Vn, "Vn");
+  gdn_tc_check(Sin, "Sin"); gdn_tc_check(dO, "dO");
+  const int64_t B = q.size(0), T = q.size(1), Hk = q.size(2), Hv = v.size(2), n = T / 64;
+  TORCH_CHECK(T % 64 == 0 && dO.sizes() == v.sizes() && Vn.numel() == B * Hv * n * 64 * 128 &&
+                  Sin.numel() == B * Hv * n * 128 * 128 && Tm.numel() == B * Hv * n * 64 * 64 && Wn.numel() == Vn.numel() &&
+                  Kd.numel() == Vn.numel() && Gc.numel() == B * Hv * n * 64 && gl.numel() == B * Hv * n &&
+                  beta.numel() == B * T * Hv,
+              "gdn_tc_bwd: saved tensors do not match the inputs");
+  const float* dsf = nullptr;
+  if (dS_final.has_value()) {
+    gdn_tc_check(*dS_final, "dS_final");
+    TORCH_CHECK(dS_final->numel() == B * Hv * 128 * 128, "gdn_tc_bwd: dS_final [B,Hv,128,128]");
+    dsf = dS_final->data_ptr<float>();
+  }
+  c10::cuda::CUDAGuard guard(q.device());
+  auto opt = q.options();
+  Tensor X0 = at::empty_like(Vn), Y0 = at::empty_like(Sin), dVn = at::empty_like(Vn), dSout = at::empty_like(Sin);
+  Tensor dq = at::empty({B, T, Hv, 128}, opt), dk = at::empty({B, T, Hv, 128}, opt), dv = at::empty_like(v);
+  Tensor dbeta = at::empty({B, T, Hv}, opt), dG = at::empty({B, T, Hv}, opt), dS0 = at::empty({B, Hv, 128, 128}, opt);
+  FERRL_CHECK(ferrl::gdn_tc_backward(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), beta.data_ptr<float>(),
+                                     Gc.data_ptr<float>(), gl.data_ptr<float>(), Tm.data_ptr<float>(), Wn.data_ptr<float>(),
+                                     Kd.data_ptr<float>(), Vn.data_ptr<float>(), Sin.data_ptr<float>(), dO.data_ptr<float>(), dsf,
+                                     B, T, Hk, Hv, X0.data_ptr<float>(), Y0.data_ptr<float>(), dVn.data_ptr<float>(),
+                                     dSout.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv.data_ptr<float>(),
+                                     dbeta.data_ptr<float>(), dG.data_ptr<float>(), dS0.data_ptr<float>(), stream()));
+  return {dq, dk, dv, dbeta, dG, dS0};
+}
+
 std::tuple<Tensor, Tensor> gdn_chunk_fwd(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& g,
                                          const Tensor& beta, const optional<Tensor>& S0, bool l2norm, double eps) {
   TORCH_CHECK(q.is_cuda() && q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 &&
@@ -641,6 +710,19 @@ Tensor rmsnorm_bwd(const Tensor& x, const optional<Tensor>& w, const Tensor& dy,
   FERRL_CHECK(ferrl::rmsnorm_bwd(dt(x), x.data_ptr(), optr(w), dy.data_ptr(), dx.data_ptr(), x.numel() / H, H,
                                  static_cast<float>(eps), zc, stream()));
   return dx;
+}
+
+std::tuple<Tensor, Tensor> rmsnorm_gated_bwd(const Tensor& x, const Tensor& gate, const Tensor& w, const Tensor& dy, double eps) {
+  TORCH_CHECK(x.is_cuda() && x.is_contiguous() && gate.is_contiguous() && dy.is_contiguous() && w.is_contiguous() &&
+                  dy.sizes() == x.sizes() && gate.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type() &&
+                  gate.scalar_type() == x.scalar_type() && w.scalar_type() == x.scalar_type() && w.numel() == x.size(-1),
+              "rmsnorm_gated_bwd: x, gate, dy of one shape and dtype, w [H]");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int H = x.size(-1);
+  Tensor dx = at::empty_like(x), dg = at::empty_like(x);
+  FERRL_CHECK(ferrl::rmsnorm_gated_bwd(dt(x), x.data_ptr(), gate.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(),
+                                       dg.data_ptr(), x.numel() / H, H, static_cast<float>(eps), stream()));
+  return {dx, dg};
 }
 
 void fill_qknr(ferrl::QkNormRopeArgs& a, const Tensor& q, const Tensor& k, const optional<Tensor>& qw,
@@ -962,6 +1044,59 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   return {dq, dk, dv};
 }
 
+static void lp_head_common(ferrl::GemmArgs& a, const Tensor& hidden, const Tensor& w, const Tensor& targets, double temperature,
+                           double softcap, const char* what) {
+  TORCH_CHECK(hidden.is_cuda() && hidden.scalar_type() == at::kBFloat16 && w.scalar_type() == at::kBFloat16 && hidden.dim() == 2 &&
+                  w.dim() == 2 && hidden.size(1) == w.size(1) && hidden.stride(1) == 1 && w.stride(1) == 1,
+              what, ": hidden [M,H] and weight [V,H] bf16, K-major");
+  TORCH_CHECK(targets.scalar_type() == at::kLong && targets.is_contiguous() && targets.numel() == hidden.size(0), what, ": targets int64 [M]");
+  a.A = hidden.data_ptr(); a.B = w.data_ptr(); a.lda = hidden.stride(0); a.ldb = w.stride(0);
+  a.M = hidden.size(0); a.N = w.size(0); a.K = hidden.size(1);
+  a.status = status_word(); a.num_sms = num_sms();
+  a.lp_targets = reinterpret_cast<const long long*>(targets.data_ptr<int64_t>());
+  a.lp_inv_t = static_cast<float>(1.0 / temperature);
+  a.lp_cap = static_cast<float>(softcap);
+  // the two-SM kernel for training-sized row counts, the one-SM kernel (256-wide tiles) below that
+  if (a.M >= 1024 && a.N >= 512) a.two_cta = 256; else a.force_bn = 256;
+}
+
+// log_softmax(softcap(h W^T) / T)[target] per row with the row statistics taken in the head GEMM's epilogue:
+// no [M, V] tensor exists at any point.  Returns (lp [M], lse [M]) in fp32.
+std::tuple<Tensor, Tensor> logprob_head_fwd(const Tensor& hidden, const Tensor& w, const Tensor& targets, double temperature,
+                                            double softcap) {
+  ferrl::GemmArgs a{};
+  lp_head_common(a, hidden, w, targets, temperature, softcap, "logprob_head_fwd");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  const int n_tiles = (a.N + 255) / 256;
+  auto f32 = hidden.options().dtype(at::kFloat);
+  Tensor ws = at::empty({n_tiles, a.M, 2}, f32), tl = at::zeros({a.M}, f32);
+  Tensor lp = at::empty({a.M}, f32), lse = at::empty({a.M}, f32);
+  if (a.M == 0) return {lp, lse};
+  a.lp_mode = 1; a.lp_ws = ws.data_ptr<float>(); a.lp_tl = tl.data_ptr<float>(); a.ldo = a.N;
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  FERRL_CHECK(ferrl::logprob_finalize(ws.data_ptr<float>(), tl.data_ptr<float>(), n_tiles, a.M, lp.data_ptr<float>(),
+                                      lse.data_ptr<float>(), stream()));
+  return {lp, lse};
+}
+
+// Gradient of sum_rows coef[row] * (-lp[row]) with respect to the raw logits of the vocabulary slice `w`
+// ([Vc, H] rows col0 .. col0+Vc of the head), written as bf16 [M, Vc]: the softmax is recomputed in the
+// GEMM epilogue from the saved lse.
+Tensor logprob_head_dlogits(const Tensor& hidden, const Tensor& w, const Tensor& targets, const Tensor& lse, const Tensor& coef,
+                            double temperature, double softcap, int64_t col0) {
+  ferrl::GemmArgs a{};
+  lp_head_common(a, hidden, w, targets, temperature, softcap, "logprob_head_dlogits");
+  TORCH_CHECK(lse.scalar_type() == at::kFloat && coef.scalar_type() == at::kFloat && lse.is_contiguous() && coef.is_contiguous() &&
+                  lse.numel() == a.M && coef.numel() == a.M, "logprob_head_dlogits: lse, coef fp32 [M]");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  Tensor out = at::empty({a.M, a.N}, hidden.options());
+  if (a.M == 0) return out;
+  a.lp_mode = 2; a.lp_lse = lse.data_ptr<float>(); a.lp_coef = coef.data_ptr<float>(); a.lp_col0 = col0;
+  a.out = out.data_ptr(); a.ldo = a.N;
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
 std::tuple<Tensor, Tensor> logprob_rows(const Tensor& logits, const Tensor& targets, double temperature, double softcap) {
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && targets.scalar_type() == at::kLong &&
                   targets.is_contiguous() && targets.numel() == logits.size(0), "logprob_rows: args");
@@ -1113,6 +1248,9 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
   m.def("gdn_conv_step(Tensor x, Tensor w, Tensor(a!) state, bool act) -> Tensor", &gdn_conv_step);
   m.def("gdn_chunk_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0, bool l2norm, float eps) -> (Tensor, Tensor)", &gdn_chunk_fwd);
+  m.def("rmsnorm_gated_bwd(Tensor x, Tensor gate, Tensor w, Tensor dy, float eps) -> (Tensor, Tensor)", &rmsnorm_gated_bwd);
+  m.def("gdn_tc_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0) -> Tensor[]", &gdn_tc_fwd);
+  m.def("gdn_tc_bwd(Tensor q, Tensor k, Tensor v, Tensor beta, Tensor Gc, Tensor gl, Tensor Tm, Tensor Wn, Tensor Kd, Tensor Vn, Tensor Sin, Tensor dO, Tensor? dS_final) -> Tensor[]", &gdn_tc_bwd);
   m.def("gdn_decode_step(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor(a!) S, bool l2norm, float eps) -> Tensor", &gdn_decode_step);
   m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
   m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);
@@ -1144,6 +1282,8 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("qk_norm_rope_append(Tensor q, Tensor k, Tensor v, Tensor? qw, Tensor? kw, Tensor cos_t, Tensor sin_t, Tensor pos, float eps, bool zc, Tensor(a!) kc, Tensor(b!) vc, Tensor kv_len, Tensor? table) -> Tensor", &qk_norm_rope_append);
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0, Tensor? debug=None) -> (Tensor, Tensor, Tensor)", &flash_bwd);
+  m.def("logprob_head_fwd(Tensor hidden, Tensor w, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_head_fwd);
+  m.def("logprob_head_dlogits(Tensor hidden, Tensor w, Tensor targets, Tensor lse, Tensor coef, float temperature, float softcap, int col0) -> Tensor", &logprob_head_dlogits);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);
   m.def("sample_rows(Tensor logits, Tensor global_rows, int seed, Tensor? draw_dev, int draw, float temperature, float top_p) -> (Tensor, Tensor)", &sample_rows);

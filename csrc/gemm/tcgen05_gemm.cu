@@ -71,6 +71,21 @@ struct GemmParams {
   // of 16, eight gate rows followed by the eight up rows of the same features, and the kernel writes
   // act(gate) * up, N / 2 columns per row.  1 = SiLU, 2 = tanh-GELU.
   int glu_act;
+  // Language-model head without a logits tensor (one-SM kernel with 256-wide tiles and the two-SM kernel).
+  // Every accumulator value is first turned into the scored logit z = softcap(x) / T.
+  //   lp_mode 1: nothing is stored to `out`; per row and column tile the epilogue writes the running
+  //              (max, sum exp(z - max)) to lp_ws[tile][row], and the z of the target column to lp_tl[row];
+  //   lp_mode 2: `out` receives d z-loss / d x = lp_coef[row] * (exp(z - lp_lse[row]) - [col == target]) *
+  //              dz/dx as bf16 (the caller multiplies by the weight again for the hidden-state gradient).
+  // B may be a slice of the vocabulary: lp_col0 is the vocabulary index of its first row.
+  int lp_mode;
+  const long long* lp_targets;
+  float lp_inv_t, lp_cap;
+  long long lp_col0;
+  float2* lp_ws;
+  float* lp_tl;
+  const float* lp_lse;
+  const float* lp_coef;
   // RMSNorm folded around the projection (decode): with ss_in the accumulator rows are scaled by
   // rstd[row] = rsqrt(sum_t ss_in[t][row] * ss_inv_k + ss_eps) (the norm weight lives in B's columns);
   // with ss_out the epilogue writes, per output row, the sum of squares of the values it stored to
@@ -223,6 +238,64 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ---- log-prob epilogue (see GemmParams::lp_mode): per-thread state of one output row
+struct LpRow {
+  float m, s, tl, lse, coef;
+  long long tgt;       // target column relative to this call's first column (may be out of range)
+  bool hit;
+};
+__device__ __forceinline__ void lp_begin(const GemmParams& p, int row, bool row_ok, LpRow& st) {
+  st.m = -INFINITY; st.s = 0.f; st.tl = 0.f; st.hit = false; st.lse = 0.f; st.coef = 0.f; st.tgt = -1;
+  if (!row_ok) return;
+  st.tgt = p.lp_targets[row] - p.lp_col0;
+  if (p.lp_mode == 2) {
+    st.lse = p.lp_lse[row];
+    st.coef = p.lp_coef[row];
+  }
+}
+// r holds 32 accumulator columns starting at column `col`; the first `ncols` are inside the matrix.
+__device__ __forceinline__ void lp_chunk(const GemmParams& p, uint32_t* r, int col, int ncols, LpRow& st) {
+  const float cap = p.lp_cap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+  if (p.lp_mode == 1) {
+    float cm = -INFINITY;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      float z = __uint_as_float(r[e]);
+      if (cap > 0.f) z = cap * tanhf(z * inv_cap);
+      z *= p.lp_inv_t;
+      if (e >= ncols) z = -INFINITY;
+      if (col + e == st.tgt) { st.tl = z; st.hit = true; }
+      r[e] = __float_as_uint(z);
+      cm = fmaxf(cm, z);
+    }
+    const float nm = fmaxf(st.m, cm);
+    float add = 0.f;
+#pragma unroll
+    for (int e = 0; e < 32; ++e) add += __expf(__uint_as_float(r[e]) - nm);
+    st.s = st.s * __expf(st.m - nm) + add;
+    st.m = nm;
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      const float x = __uint_as_float(r[e]);
+      float z = x, dz = p.lp_inv_t;
+      if (cap > 0.f) {
+        const float t = tanhf(x * inv_cap);
+        z = cap * t;
+        dz *= 1.f - t * t;
+      }
+      z *= p.lp_inv_t;
+      const float pr = __expf(z - st.lse) - ((col + e == st.tgt) ? 1.f : 0.f);
+      r[e] = __float_as_uint(st.coef * pr * dz);
+    }
+  }
+}
+__device__ __forceinline__ void lp_end(const GemmParams& p, int row, bool row_ok, int ni, const LpRow& st) {
+  if (p.lp_mode != 1 || !row_ok) return;
+  p.lp_ws[static_cast<long long>(ni) * p.M + row] = make_float2(st.m, st.s);
+  if (st.hit) p.lp_tl[row] = st.tl;
+}
 
 template <int BN> struct Cfg {
   static constexpr int STAGE_BYTES = (BM + BN) * BK * 2;
@@ -479,12 +552,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       if (AR)
         ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
                   (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
+      LpRow lp;
+      if (p.lp_mode) lp_begin(p, row, row_ok, lp);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
         tmem_ld32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * BN + c, r);
         tmem_ld_wait();
         const int col = ni * BN + c;
+        if (p.lp_mode) {
+          if (!(row_ok && col < p.N)) continue;
+          lp_chunk(p, r, col, min(min(32, BN - c), p.N - col), lp);
+          if (p.lp_mode == 1) continue;
+        }
         if (p.split_k > 1) {
           // fp32 partial of this k-slice; residual and the output cast happen in the reduce kernel
           if (row_ok && col < p.N) {
@@ -597,6 +677,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
       if (p.ss_out && row_ok) p.ss_out[ni * p.ss_ld + row] = ssq;
+      if (p.lp_mode) lp_end(p, row, row_ok, ni, lp);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
@@ -870,6 +951,10 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
   p.glu_act = a.glu_act;
   p.ss_in = a.ss_in; p.ss_parts = a.ss_parts; p.ss_ld = a.ss_ld; p.ss_inv_k = a.ss_inv_k; p.ss_eps = a.ss_eps;
   p.ss_out = a.ss_out;
+  p.lp_mode = a.lp_mode; p.lp_targets = a.lp_targets; p.lp_inv_t = a.lp_inv_t; p.lp_cap = a.lp_cap; p.lp_col0 = a.lp_col0;
+  p.lp_ws = reinterpret_cast<float2*>(a.lp_ws); p.lp_tl = a.lp_tl; p.lp_lse = a.lp_lse; p.lp_coef = a.lp_coef;
+  if (p.lp_mode && (p.split_k > 1 || a.ar_world > 1 || a.tile_expert || a.glu_act || a.ss_in || a.ss_out || OUT_F32 || HAS_RES || BN != 256))
+    return "log-prob epilogue: plain bf16 call with 256-wide tiles only";
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
   if (p.ar_world > 1) {
@@ -1158,6 +1243,8 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
       tc_fence_after();
       const int row = mi * 2 * BM + static_cast<int>(rank) * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
+      LpRow lp;
+      if (p.lp_mode) lp_begin(p, row, row_ok, lp);
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
@@ -1166,6 +1253,10 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
         const int col = ni * BN + c;
         if (row_ok && col < p.N) {
           const int ncols = min(min(32, BN - c), p.N - col);
+          if (p.lp_mode) {
+            lp_chunk(p, r, col, ncols, lp);
+            if (p.lp_mode == 1) continue;
+          }
           if (HAS_RES) {
             const __nv_bfloat16* rp = p.residual + static_cast<long long>(row) * p.ldr + col;
             if (ncols == 32 && ((reinterpret_cast<uintptr_t>(rp) & 15) == 0)) {
@@ -1199,6 +1290,7 @@ gemm2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CU
           }
         }
       }
+      if (p.lp_mode) lp_end(p, row, row_ok, ni, lp);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) {
@@ -1235,6 +1327,9 @@ const char* launch_2cta(const GemmArgs& a, cudaStream_t stream) {
   p.out = a.out; p.residual = reinterpret_cast<const __nv_bfloat16*>(a.residual);
   p.ldo = a.ldo; p.ldr = a.ldr; p.status = a.status; p.group_m = 8;
   p.split_k = 1; p.ar_world = 1;
+  p.lp_mode = a.lp_mode; p.lp_targets = a.lp_targets; p.lp_inv_t = a.lp_inv_t; p.lp_cap = a.lp_cap; p.lp_col0 = a.lp_col0;
+  p.lp_ws = reinterpret_cast<float2*>(a.lp_ws); p.lp_tl = a.lp_tl; p.lp_lse = a.lp_lse; p.lp_coef = a.lp_coef;
+  if (p.lp_mode && (HAS_RES || BN != 256)) return "log-prob epilogue: plain bf16 call with 256-wide tiles only";
   auto kern = gemm2_kernel<BN, HAS_RES>;
   if (!FERRL_ONCE_PER_DEVICE(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) ==
                              cudaSuccess))
@@ -2071,6 +2166,11 @@ const char* gemm_bf16(const GemmArgs& a, cudaStream_t stream) {
     if (a.stream_k || a.cluster_k > 1 || a.two_cta || a.split_k > 1 || a.out_f32 || a.residual || a.ar_world > 1 || a.tile_expert ||
         (a.N % 16) || (a.ldo % 8))
       return "gemm with GLU epilogue: one-SM kernel, bf16 output, no split, residual or grouping; N a multiple of 16";
+  }
+  if (a.lp_mode) {
+    if (a.stream_k || a.cluster_k > 1 || a.out_f32 || a.residual || a.K2 > 0 || !a.lp_targets ||
+        (a.lp_mode == 1 && (!a.lp_ws || !a.lp_tl)) || (a.lp_mode == 2 && (!a.lp_lse || !a.lp_coef || !a.out)))
+      return "log-prob epilogue: plain call (no side operand, residual or fp32 output) with its buffers set";
   }
   if (a.stream_k) {
     if (a.split_k > 1 || a.tile_expert || a.ar_world > 1) return "stream-k gemm: no global k-split, grouping or all-reduce";

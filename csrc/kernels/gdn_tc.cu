@@ -14,18 +14,21 @@
 // q and k arrive L2-normalised (q also scaled by 1/sqrt(dk)); those elementwise steps and their
 // derivatives stay with the caller.
 //
-// Four kernels, all matrix products on the tensor cores (wmma m16n16k8, tf32 operands, fp32
-// accumulation; operands are read as fp32 from shared or straight from global memory):
-//   gdn_prep_kernel      one CTA per (chunk, head): G, T (forward substitution), U, W
-//   gdn_scan_fwd_kernel  one CTA per head, chunks in order, state resident in shared memory: Vn, O, S'
-//   gdn_scan_bwd_kernel  one CTA per head, chunks in reverse, dS resident: dVn and the dS recursion
-//   gdn_chunk_bwd_kernel one CTA per (chunk, head): everything that does not cross chunks - dq, dk, dv,
-//                        dbeta and dG (the caller turns dG into dg with a reverse cumulative sum)
-// The two scans are the only sequential parts; the forward saves the entering state and Vn of every
-// chunk when a backward will follow.
+// All matrix products run on the tensor cores (wmma m16n16k8, tf32 operands, fp32 accumulation).  Only the
+// two products per chunk that carry the state are sequential; everything else is one CTA per (chunk, head):
+//   gdn_prep_kernel       G, T (forward substitution), U, Wn = -W, Kd = diag(gamma_C / gamma) K
+//   gdn_scan_kernel<fwd>  one CTA per (head, slice of the value columns), chunks in order, state in shared
+//                         memory: Vn = U + Wn S and S' = gamma_C S + Kd^T Vn; saves the entering state of each chunk
+//   gdn_out_kernel        O of a chunk from its saved entering state
+//   gdn_bwd_prep_kernel   X0 = P^T dO and Y0 = (gamma Q)^T dO
+//   gdn_scan_kernel<bwd>  chunks in reverse: dVn = X0 + Kd dS', dS = gamma_C dS' + Y0 + Wn^T dVn
+//   gdn_chunk_bwd_kernel  everything that does not cross chunks: dq, dk, dv, dbeta and dG (the caller turns
+//                         dG into dg with a reverse cumulative sum inside each chunk)
 #include <cuda_runtime.h>
 #include <mma.h>
 #include <stdint.h>
+
+#include <type_traits>
 
 #include "../api.h"
 #include "../common.cuh"
@@ -50,6 +53,7 @@ __device__ __forceinline__ void mm(float* Cm, int ldc, const float* A, long long
     wm::fragment<wm::accumulator, 16, 16, 8, float> c;
     if (ACC) wm::load_matrix_sync(c, Cm + i * 16 * ldc + j * 16, ldc, wm::mem_row_major);
     else wm::fill_fragment(c, 0.f);
+#pragma unroll 4
     for (int k = 0; k < K; k += 8) {
       if (!AT && !BT) {
         wm::fragment<wm::matrix_a, 16, 16, 8, wm::precision::tf32, wm::row_major> a;
@@ -112,15 +116,62 @@ __device__ __forceinline__ long long ch_off(const GdnDims& d, int b, int hv, int
 }
 
 // ---------------------------------------------------------------------------------------------
-// prep: G, T, U, W of one chunk.  Shared: three [64, 64] matrices and two vectors.
+// Shared-memory tiles carry a padded leading dimension so that the tensor-core fragment loads spread
+// over the banks: an operand read "row by 4 columns" (A row-major, B column-major) wants ld = 4 mod 32,
+// one read "4 rows by column" (B row-major, A column-major) wants ld = 8 mod 32.
+constexpr int LD4 = GD + 4;     // 132
+constexpr int LD8 = GD + 8;     // 136
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// rows x cols floats (cols a multiple of 4) from global (row stride lds) into shared (row stride ldd), whole CTA
+__device__ __forceinline__ void tile_async(float* dst, int ldd, const float* src, long long lds, int rows, int cols) {
+  const int c4 = cols >> 2;
+  for (int e = threadIdx.x; e < rows * c4; e += blockDim.x) {
+    const int r = e / c4, x = e - r * c4;
+    cp_async16(dst + r * ldd + x * 4, src + r * lds + x * 4);
+  }
+}
+
+// one 16x16 accumulator tile: c += op(A)[16, K] * op(B)[K, 16], k loop unrolled so the fragment loads overlap.
+// A points at the tile's first row (AT: first column of the stored [K, M] matrix), B likewise.
+template <int K, bool AT, bool BT>
+__device__ __forceinline__ void tile_mma(wm::fragment<wm::accumulator, 16, 16, 8, float>& c, const float* A, int lda,
+                                         const float* Bm, int ldb) {
+  using FA = typename std::conditional<AT, wm::fragment<wm::matrix_a, 16, 16, 8, wm::precision::tf32, wm::col_major>,
+                                       wm::fragment<wm::matrix_a, 16, 16, 8, wm::precision::tf32, wm::row_major>>::type;
+  using FB = typename std::conditional<BT, wm::fragment<wm::matrix_b, 16, 16, 8, wm::precision::tf32, wm::col_major>,
+                                       wm::fragment<wm::matrix_b, 16, 16, 8, wm::precision::tf32, wm::row_major>>::type;
+#pragma unroll
+  for (int k = 0; k < K; k += 8) {
+    FA a;
+    FB b;
+    wm::load_matrix_sync(a, AT ? A + k * lda : A + k, lda);
+    wm::load_matrix_sync(b, BT ? Bm + k : Bm + k * ldb, ldb);
+#pragma unroll
+    for (int e = 0; e < a.num_elements; ++e) a.x[e] = wm::__float_to_tf32(a.x[e]);
+#pragma unroll
+    for (int e = 0; e < b.num_elements; ++e) b.x[e] = wm::__float_to_tf32(b.x[e]);
+    wm::mma_sync(c, a, b, c);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// prep: per chunk G, T, U, Wn = -W, Kd = diag(exp(G_C - G)) K and gl = G_C.
+// Shared: three [64, 64] matrices and two vectors.
 __global__ void __launch_bounds__(256)
 gdn_prep_kernel(const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ g,
-                const float* __restrict__ beta, GdnDims d, float* __restrict__ Gc, float* __restrict__ Tm,
-                float* __restrict__ U, float* __restrict__ W) {
+                const float* __restrict__ beta, GdnDims d, float* __restrict__ Gc, float* __restrict__ gl,
+                float* __restrict__ Tm, float* __restrict__ U, float* __restrict__ Wn, float* __restrict__ Kd) {
   extern __shared__ __align__(128) float sm[];
   float* Y1 = sm;                  // K K^T, then A
   float* Y2 = Y1 + GC * GC;        // T
-  float* Y3 = Y2 + GC * GC;        // T diag(beta), then T diag(gamma beta)
+  float* Y3 = Y2 + GC * GC;        // T diag(beta), then -T diag(gamma beta)
   float* Gs = Y3 + GC * GC;
   float* bs = Gs + GC;
   const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
@@ -129,20 +180,34 @@ gdn_prep_kernel(const float* __restrict__ k, const float* __restrict__ v, const 
   const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
   const float* kg = k + qk_off(d, b, c * GC, hk);
   const float* vg = v + v_off(d, b, c * GC, hv);
+  const long long co = ch_off(d, b, hv, c);
   if (tid < GC) bs[tid] = beta[(static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv];
-  if (tid == 0) {
-    float acc = 0.f;
-    for (int i = 0; i < GC; ++i) {
-      acc += g[(static_cast<long long>(b) * d.T + c * GC + i) * d.Hv + hv];
-      Gs[i] = acc;
+  if (tid < 32) {                  // inclusive scan of 64 log decays by one warp
+    const long long o = (static_cast<long long>(b) * d.T + c * GC) * d.Hv + hv;
+    float a0 = g[o + static_cast<long long>(2 * tid) * d.Hv], a1 = g[o + static_cast<long long>(2 * tid + 1) * d.Hv];
+    float sum = a0 + a1;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const float t = __shfl_up_sync(0xffffffffu, sum, off);
+      if (tid >= off) sum += t;
     }
+    Gs[2 * tid + 1] = sum;
+    Gs[2 * tid] = sum - a1;
   }
   mm<false, true, false>(Y1, GC, kg, ldk, kg, ldk, GC, GC, GD);
   __syncthreads();
+  const float glast = Gs[GC - 1];
   for (int e = tid; e < GC * GC; e += 256) {
     const int i = e / GC, j = e - i * GC;
     Y1[e] = (i > j) ? bs[i] * Y1[e] * __expf(Gs[i] - Gs[j]) : 0.f;
     Y2[e] = (i == j) ? 1.f : 0.f;
+  }
+  // Kd = diag(exp(G_C - G)) K, straight from global to global
+  for (int e = tid; e < GC * GD / 4; e += 256) {
+    const int i = e / (GD / 4), x = e - i * (GD / 4);
+    float4 t = reinterpret_cast<const float4*>(kg + i * ldk)[x];
+    const float f = __expf(glast - Gs[i]);
+    reinterpret_cast<float4*>(Kd + co * GC * GD)[e] = make_float4(t.x * f, t.y * f, t.z * f, t.w * f);
   }
   __syncthreads();
   // T = (I + A)^-1 by forward substitution: row i of T is e_i - sum_{j<i} A[i][j] T[j][:]
@@ -154,164 +219,254 @@ gdn_prep_kernel(const float* __restrict__ k, const float* __restrict__ v, const 
     }
     __syncthreads();
   }
-  const long long co = ch_off(d, b, hv, c);
   for (int e = tid; e < GC * GC; e += 256) {
     const int j = e % GC;
     Tm[co * GC * GC + e] = Y2[e];
     Y3[e] = Y2[e] * bs[j];
   }
   if (tid < GC) Gc[co * GC + tid] = Gs[tid];
+  if (tid == 0) gl[co] = glast;
   __syncthreads();
   mm<false, false, false>(U + co * GC * GD, GD, Y3, GC, vg, ldv, GC, GD, GC);
   __syncthreads();
   for (int e = tid; e < GC * GC; e += 256) {
     const int j = e % GC;
-    Y3[e] = Y2[e] * bs[j] * __expf(Gs[j]);
+    Y3[e] = -Y2[e] * bs[j] * __expf(Gs[j]);
   }
   __syncthreads();
-  mm<false, false, false>(W + co * GC * GD, GD, Y3, GC, kg, ldk, GC, GD, GC);
+  mm<false, false, false>(Wn + co * GC * GD, GD, Y3, GC, kg, ldk, GC, GD, GC);
 }
 
 // ---------------------------------------------------------------------------------------------
-// forward scan: one CTA per (head, batch), state in shared memory.
-// Shared: S [128,128], Qs, Ks, Ws, Us [64,128] each, P [64,64], Gs [64].
+// The two scans.  The state's value columns never mix (Vn[:, j] and S'[:, j] depend on S[:, j] only), so a CTA
+// owns DV of the 128 value columns of one head and walks the chunks with two products per chunk:
+//   forward   Vn  = U  + Wn S              S' = gamma_C S   + Kd^T Vn
+//   backward  dVn = X0 + Kd dS'            dS = gamma_C dS' + Y0 + Wn^T dVn      (chunks in reverse)
+// Both have the form  V = V0 + A1 R;  R = g R + R0 + A2^T V  with per-chunk [64,128] matrices A1, A2, a
+// [64, DV] start V0 and (backward only) a [128, DV] addend R0.  A1, A2 and V0 of the next chunk are fetched with
+// cp.async while the current chunk computes; everything elementwise was folded into the per-chunk kernels.
+template <int DV>
+struct ScanSmem {
+  static constexpr int LS = DV + 8;                                   // B row-major operands: 8 mod 32
+  static constexpr int R = GD * LS, A1 = 2 * GC * LD4, A2 = 2 * GC * LD8, V = 2 * GC * LS;
+  static constexpr size_t BYTES = static_cast<size_t>(R + A1 + A2 + V) * sizeof(float);
+};
+
+template <int DV, bool BWD>
 __global__ void __launch_bounds__(256, 1)
-gdn_scan_fwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
-                    const float* __restrict__ U, const float* __restrict__ W, const float* __restrict__ S0, GdnDims d,
-                    float* __restrict__ out, float* __restrict__ S_out, float* __restrict__ Sin, float* __restrict__ Vn) {
+gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forward) / Kd (backward)
+                const float* __restrict__ A2g,    // [.., n, 64, 128]: Kd (forward) / Wn (backward)
+                const float* __restrict__ V0g,    // [.., n, 64, 128]: U (forward) / X0 (backward)
+                const float* __restrict__ R0g,    // backward: Y0 [.., n, 128, 128]; forward: null
+                const float* __restrict__ gl,     // [.., n] last cumulative log decay of every chunk
+                const float* __restrict__ Rinit,  // [.., 128, 128] initial state (S0 / dS_final) or null
+                int n, int n_slices,
+                float* __restrict__ Vout,         // [.., n, 64, 128]: Vn / dVn
+                float* __restrict__ Rchunks,      // [.., n, 128, 128]: forward Sin[c] = state entering chunk c;
+                                                  //                    backward dSout[c] = gradient of the state leaving c
+                float* __restrict__ Rfinal) {     // [.., 128, 128]: S after the last chunk / dS0 (may be null)
+  using SM = ScanSmem<DV>;
+  constexpr int LS = SM::LS;
   extern __shared__ __align__(128) float sm[];
-  float* S = sm;
-  float* Qs = S + GD * GD;
-  float* Ks = Qs + GC * GD;
-  float* Ws = Ks + GC * GD;
-  float* Us = Ws + GC * GD;
-  float* P = Us + GC * GD;
-  float* Gs = P + GC * GC;
-  const int hv = blockIdx.x, b = blockIdx.y;
-  const int hk = hv / (d.Hv / d.Hk);
-  const int tid = threadIdx.x;
-  const long long bh = static_cast<long long>(b) * d.Hv + hv;
-  for (int e = tid; e < GD * GD; e += 256) S[e] = S0 ? S0[bh * GD * GD + e] : 0.f;
-  for (int c = 0; c < d.n; ++c) {
-    const long long co = ch_off(d, b, hv, c);
-    __syncthreads();
-    for (int e = tid; e < GC * GD / 4; e += 256) {
-      const int i = e / (GD / 4), x = e - i * (GD / 4);
-      reinterpret_cast<float4*>(Qs)[e] = reinterpret_cast<const float4*>(q + qk_off(d, b, c * GC + i, hk))[x];
-      reinterpret_cast<float4*>(Ks)[e] = reinterpret_cast<const float4*>(k + qk_off(d, b, c * GC + i, hk))[x];
-      float4 w = reinterpret_cast<const float4*>(W + co * GC * GD)[e];
-      reinterpret_cast<float4*>(Ws)[e] = make_float4(-w.x, -w.y, -w.z, -w.w);
-      reinterpret_cast<float4*>(Us)[e] = reinterpret_cast<const float4*>(U + co * GC * GD)[e];
-    }
-    if (tid < GC) Gs[tid] = Gc[co * GC + tid];
-    if (Sin)
-      for (int e = tid; e < GD * GD / 4; e += 256)
-        reinterpret_cast<float4*>(Sin + co * GD * GD)[e] = reinterpret_cast<const float4*>(S)[e];
-    __syncthreads();
-    mm<false, false, true>(Us, GD, Ws, GD, S, GD, GC, GD, GD);        // Vn = U - W S
-    mm<false, true, false>(P, GC, Qs, GD, Ks, GD, GC, GC, GD);         // Q K^T
-    __syncthreads();
-    if (Vn)
-      for (int e = tid; e < GC * GD / 4; e += 256)
-        reinterpret_cast<float4*>(Vn + co * GC * GD)[e] = reinterpret_cast<const float4*>(Us)[e];
-    for (int e = tid; e < GC * GC; e += 256) {
-      const int i = e / GC, j = e - i * GC;
-      P[e] = (i >= j) ? P[e] * __expf(Gs[i] - Gs[j]) : 0.f;
-    }
-    for (int e = tid; e < GC * GD; e += 256) Qs[e] *= __expf(Gs[e / GD]);
-    __syncthreads();
-    mm<false, false, false>(Ws, GD, Qs, GD, S, GD, GC, GD, GD);        // O = (gamma Q) S ...
-    __syncthreads();
-    mm<false, false, true>(Ws, GD, P, GC, Us, GD, GC, GD, GC);          // ... + P Vn
-    __syncthreads();
-    for (int e = tid; e < GC * GD / 4; e += 256) {
-      const int i = e / (GD / 4), x = e - i * (GD / 4);
-      reinterpret_cast<float4*>(out + v_off(d, b, c * GC + i, hv))[x] = reinterpret_cast<const float4*>(Ws)[e];
-    }
-    const float glast = Gs[GC - 1];
-    const float eg = __expf(glast);
-    for (int e = tid; e < GD * GD; e += 256) S[e] *= eg;
-    for (int e = tid; e < GC * GD; e += 256) Ks[e] *= __expf(glast - Gs[e / GD]);
-    __syncthreads();
-    mm<true, false, true>(S, GD, Ks, GD, Us, GD, GD, GD, GC);           // S += (K decayed)^T Vn
+  float* Rs = sm;
+  float* A1s = Rs + SM::R;
+  float* A2s = A1s + SM::A1;
+  float* Vs = A2s + SM::A2;
+  __shared__ float gls[1024];
+  const int slice = blockIdx.x % n_slices;
+  const long long bh = blockIdx.x / n_slices + static_cast<long long>(blockIdx.y) * (gridDim.x / n_slices);
+  const int col0 = slice * DV;
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long cbase = bh * n;
+  for (int e = tid; e < n; e += 256) gls[e] = gl[cbase + e];
+  for (int e = tid; e < GD * DV; e += 256) {
+    const int r = e / DV, x = e - r * DV;
+    Rs[r * LS + x] = Rinit ? Rinit[bh * GD * GD + r * GD + col0 + x] : 0.f;
   }
+  auto fetch = [&](int c, int buf) {
+    const long long co = cbase + c;
+    tile_async(A1s + buf * GC * LD4, LD4, A1g + co * GC * GD, GD, GC, GD);
+    tile_async(A2s + buf * GC * LD8, LD8, A2g + co * GC * GD, GD, GC, GD);
+    tile_async(Vs + buf * GC * LS, LS, V0g + co * GC * GD + col0, GD, GC, DV);
+    cp_async_commit();
+  };
+  const int first = BWD ? n - 1 : 0, step = BWD ? -1 : 1;
+  fetch(first, 0);
   __syncthreads();
-  for (int e = tid; e < GD * GD; e += 256) S_out[bh * GD * GD + e] = S[e];
+  {  // the state as the first chunk sees it
+    float* dst = Rchunks + (cbase + first) * GD * GD;
+    for (int e = tid; e < GD * DV; e += 256) {
+      const int r = e / DV, x = e - r * DV;
+      dst[r * GD + col0 + x] = Rs[r * LS + x];
+    }
+  }
+  constexpr int TN = DV / 16;
+  for (int i = 0; i < n; ++i) {
+    const int c = first + i * step, buf = i & 1;
+    cp_async_wait_all();
+    __syncthreads();                        // this chunk's tiles have landed; the other buffer and Rs are free
+    if (i + 1 < n) fetch(c + step, buf ^ 1);
+    const float* a1 = A1s + buf * GC * LD4;
+    const float* a2 = A2s + buf * GC * LD8;
+    float* vs = Vs + buf * GC * LS;
+    const long long co = cbase + c;
+    // V = V0 + A1 R    [64, DV], K = 128
+    for (int t = warp; t < (GC / 16) * TN; t += 8) {
+      const int ti = t / TN, tj = t - ti * TN;
+      wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+      wm::load_matrix_sync(acc, vs + ti * 16 * LS + tj * 16, LS, wm::mem_row_major);
+      tile_mma<GD, false, false>(acc, a1 + ti * 16 * LD4, LD4, Rs + tj * 16, LS);
+      wm::store_matrix_sync(vs + ti * 16 * LS + tj * 16, acc, LS, wm::mem_row_major);
+      wm::store_matrix_sync(Vout + co * GC * GD + ti * 16 * GD + col0 + tj * 16, acc, GD, wm::mem_row_major);
+    }
+    __syncthreads();
+    // R = g R (+ R0) + A2^T V    [128, DV], K = 64
+    const float eg = __expf(gls[c]);
+    const bool last = i + 1 == n;
+    float* rdst = last ? Rfinal : Rchunks + (cbase + c + step) * GD * GD;
+    for (int t = warp; t < (GD / 16) * TN; t += 8) {
+      const int ti = t / TN, tj = t - ti * TN;
+      wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+      wm::load_matrix_sync(acc, Rs + ti * 16 * LS + tj * 16, LS, wm::mem_row_major);
+      if (BWD) {
+        wm::fragment<wm::accumulator, 16, 16, 8, float> add;
+        wm::load_matrix_sync(add, R0g + co * GD * GD + ti * 16 * GD + col0 + tj * 16, GD, wm::mem_row_major);
+#pragma unroll
+        for (int e = 0; e < acc.num_elements; ++e) acc.x[e] = acc.x[e] * eg + add.x[e];
+      } else {
+#pragma unroll
+        for (int e = 0; e < acc.num_elements; ++e) acc.x[e] *= eg;
+      }
+      tile_mma<GC, true, false>(acc, a2 + ti * 16, LD8, vs + tj * 16, LS);
+      wm::store_matrix_sync(Rs + ti * 16 * LS + tj * 16, acc, LS, wm::mem_row_major);
+      if (rdst) wm::store_matrix_sync(rdst + ti * 16 * GD + col0 + tj * 16, acc, GD, wm::mem_row_major);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward scan: chunks in reverse, dS in shared memory.
-//   dVn = P^T dO + Kdec dS',   dS = gamma_C dS' + (gamma Q)^T dO - W^T dVn
-// Writes dVn and the dS' of every chunk (gradient of the state leaving it) for the chunk kernel.
+// output of one chunk from the saved entering state:  O = diag(gamma) Q Sin + tril(Q K^T o D) Vn
+// Shared: Q, K [64, 132]; Sin [128, 136]; Vn [64, 136]; P [64, 68]; G [64].
+constexpr int LP = GC + 4;      // 68
+constexpr size_t kOutSmem = (2 * GC * LD4 + GD * LD8 + GC * LD8 + GC * LP + GC) * sizeof(float);
+
 __global__ void __launch_bounds__(256, 1)
-gdn_scan_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
-                    const float* __restrict__ W, const float* __restrict__ dO, const float* __restrict__ dS_final, GdnDims d,
-                    float* __restrict__ dVn, float* __restrict__ dSout, float* __restrict__ dS0) {
+gdn_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
+               const float* __restrict__ Sin, const float* __restrict__ Vn, GdnDims d, float* __restrict__ out) {
   extern __shared__ __align__(128) float sm[];
-  float* dS = sm;
-  float* Qs = dS + GD * GD;
-  float* Ks = Qs + GC * GD;
-  float* Os = Ks + GC * GD;
-  float* X = Os + GC * GD;
-  float* P = X + GC * GD;
-  float* Gs = P + GC * GC;
-  const int hv = blockIdx.x, b = blockIdx.y;
+  float* Qs = sm;
+  float* Ks = Qs + GC * LD4;
+  float* Ss = Ks + GC * LD4;
+  float* Vs = Ss + GD * LD8;
+  float* P = Vs + GC * LD8;
+  float* Gs = P + GC * LP;
+  const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int hk = hv / (d.Hv / d.Hk);
-  const int tid = threadIdx.x;
-  const long long bh = static_cast<long long>(b) * d.Hv + hv;
-  for (int e = tid; e < GD * GD; e += 256) dS[e] = dS_final ? dS_final[bh * GD * GD + e] : 0.f;
-  for (int c = d.n - 1; c >= 0; --c) {
-    const long long co = ch_off(d, b, hv, c);
-    __syncthreads();
-    for (int e = tid; e < GC * GD / 4; e += 256) {
-      const int i = e / (GD / 4), x = e - i * (GD / 4);
-      reinterpret_cast<float4*>(Qs)[e] = reinterpret_cast<const float4*>(q + qk_off(d, b, c * GC + i, hk))[x];
-      reinterpret_cast<float4*>(Ks)[e] = reinterpret_cast<const float4*>(k + qk_off(d, b, c * GC + i, hk))[x];
-      reinterpret_cast<float4*>(Os)[e] = reinterpret_cast<const float4*>(dO + v_off(d, b, c * GC + i, hv))[x];
-    }
-    if (tid < GC) Gs[tid] = Gc[co * GC + tid];
-    for (int e = tid; e < GD * GD / 4; e += 256)
-      reinterpret_cast<float4*>(dSout + co * GD * GD)[e] = reinterpret_cast<const float4*>(dS)[e];
-    __syncthreads();
-    mm<false, true, false>(P, GC, Qs, GD, Ks, GD, GC, GC, GD);
-    __syncthreads();
-    const float glast = Gs[GC - 1];
-    for (int e = tid; e < GC * GC; e += 256) {
-      const int i = e / GC, j = e - i * GC;
-      P[e] = (i >= j) ? P[e] * __expf(Gs[i] - Gs[j]) : 0.f;
-    }
-    for (int e = tid; e < GC * GD; e += 256) Ks[e] *= __expf(glast - Gs[e / GD]);
-    __syncthreads();
-    mm<true, false, false>(X, GD, P, GC, Os, GD, GC, GD, GC);          // P^T dO
-    __syncthreads();
-    mm<false, false, true>(X, GD, Ks, GD, dS, GD, GC, GD, GD);          // + Kdec dS'
-    __syncthreads();
-    for (int e = tid; e < GC * GD / 4; e += 256)
-      reinterpret_cast<float4*>(dVn + co * GC * GD)[e] = reinterpret_cast<const float4*>(X)[e];
-    const float eg = __expf(glast);
-    for (int e = tid; e < GD * GD; e += 256) dS[e] *= eg;
-    for (int e = tid; e < GC * GD; e += 256) Qs[e] *= __expf(Gs[e / GD]);
-    for (int e = tid; e < GC * GD / 4; e += 256) {                      // Ks <- -W
-      float4 w = reinterpret_cast<const float4*>(W + co * GC * GD)[e];
-      reinterpret_cast<float4*>(Ks)[e] = make_float4(-w.x, -w.y, -w.z, -w.w);
-    }
-    __syncthreads();
-    mm<true, false, true>(dS, GD, Qs, GD, Os, GD, GD, GD, GC);          // + (gamma Q)^T dO
-    __syncthreads();
-    mm<true, false, true>(dS, GD, Ks, GD, X, GD, GD, GD, GC);           // - W^T dVn
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
+  const long long co = ch_off(d, b, hv, c);
+  tile_async(Qs, LD4, q + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(Ks, LD4, k + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  cp_async_commit();
+  tile_async(Ss, LD8, Sin + co * GD * GD, GD, GD, GD);
+  tile_async(Vs, LD8, Vn + co * GC * GD, GD, GC, GD);
+  cp_async_commit();
+  if (tid < GC) Gs[tid] = Gc[co * GC + tid];
+  asm volatile("cp.async.wait_group 1;" ::: "memory");
+  __syncthreads();
+  for (int t = warp; t < 16; t += 8) {                 // P = Q K^T
+    const int ti = t >> 2, tj = t & 3;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GD, false, true>(acc, Qs + ti * 16 * LD4, LD4, Ks + tj * 16 * LD4, LD4);
+    wm::store_matrix_sync(P + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
   }
   __syncthreads();
-  if (dS0)
-    for (int e = tid; e < GD * GD; e += 256) dS0[bh * GD * GD + e] = dS[e];
+  for (int e = tid; e < GC * GC; e += 256) {
+    const int i = e / GC, j = e - i * GC;
+    P[i * LP + j] = (i >= j) ? P[i * LP + j] * __expf(Gs[i] - Gs[j]) : 0.f;
+  }
+  for (int e = tid; e < GC * GD; e += 256) {
+    const int i = e / GD, x = e - i * GD;
+    Qs[i * LD4 + x] *= __expf(Gs[i]);
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  float* og = out + v_off(d, b, c * GC, hv);
+  for (int t = warp; t < 32; t += 8) {                 // O = (gamma Q) Sin + P Vn
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GD, false, false>(acc, Qs + ti * 16 * LD4, LD4, Ss + tj * 16, LD8);
+    tile_mma<GC, false, false>(acc, P + ti * 16 * LP, LP, Vs + tj * 16, LD8);
+    wm::store_matrix_sync(og + static_cast<long long>(ti) * 16 * ldv + tj * 16, acc, static_cast<unsigned>(ldv), wm::mem_row_major);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward, chunk-local inputs of the reverse scan:  X0 = P^T dO  [64,128],  Y0 = (gamma Q)^T dO  [128,128]
+// Shared: Q, K [64, 132]; dO [64, 136]; P [64, 72]; G [64].
+constexpr int LP8 = GC + 8;     // 72
+constexpr size_t kBwdPrepSmem = (2 * GC * LD4 + GC * LD8 + GC * LP8 + GC) * sizeof(float);
+
+__global__ void __launch_bounds__(256, 1)
+gdn_bwd_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
+                    const float* __restrict__ dO, GdnDims d, float* __restrict__ X0, float* __restrict__ Y0) {
+  extern __shared__ __align__(128) float sm[];
+  float* Qs = sm;
+  float* Ks = Qs + GC * LD4;
+  float* Os = Ks + GC * LD4;
+  float* P = Os + GC * LD8;
+  float* Gs = P + GC * LP8;
+  const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  const int hk = hv / (d.Hv / d.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
+  const long long co = ch_off(d, b, hv, c);
+  tile_async(Qs, LD4, q + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(Ks, LD4, k + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(Os, LD8, dO + v_off(d, b, c * GC, hv), ldv, GC, GD);
+  cp_async_commit();
+  if (tid < GC) Gs[tid] = Gc[co * GC + tid];
+  cp_async_wait_all();
+  __syncthreads();
+  for (int t = warp; t < 16; t += 8) {
+    const int ti = t >> 2, tj = t & 3;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GD, false, true>(acc, Qs + ti * 16 * LD4, LD4, Ks + tj * 16 * LD4, LD4);
+    wm::store_matrix_sync(P + ti * 16 * LP8 + tj * 16, acc, LP8, wm::mem_row_major);
+  }
+  __syncthreads();
+  for (int e = tid; e < GC * GC; e += 256) {
+    const int i = e / GC, j = e - i * GC;
+    P[i * LP8 + j] = (i >= j) ? P[i * LP8 + j] * __expf(Gs[i] - Gs[j]) : 0.f;
+  }
+  for (int e = tid; e < GC * GD; e += 256) {
+    const int i = e / GD, x = e - i * GD;
+    Qs[i * LD4 + x] *= __expf(Gs[i]);
+  }
+  __syncthreads();
+  for (int t = warp; t < 32; t += 8) {                 // X0 = P^T dO
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, true, false>(acc, P + ti * 16, LP8, Os + tj * 16, LD8);
+    wm::store_matrix_sync(X0 + co * GC * GD + ti * 16 * GD + tj * 16, acc, GD, wm::mem_row_major);
+  }
+  for (int t = warp; t < 64; t += 8) {                 // Y0 = (gamma Q)^T dO
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, true, false>(acc, Qs + ti * 16, LD4, Os + tj * 16, LD8);
+    wm::store_matrix_sync(Y0 + co * GD * GD + ti * 16 * GD + tj * 16, acc, GD, wm::mem_row_major);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
 // everything of the backward that stays inside a chunk.  Shared: E1, E2, E3 [64,128]; Y1, Y2, Y3
 // [64,64]; vectors.  Operands that are plain inputs (q, k, v, dO, Vn, dVn, T, Sin, dSout) are read
 // by the tensor-core loads straight from global memory.
-__device__ __forceinline__ float block_sum256(float v, float* red) {
-  return block_sum(v, red);
-}
 
 __global__ void __launch_bounds__(256, 1)
 gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
@@ -330,7 +485,8 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
   float* bs = Gs + GC;            // [64]
   float* dGs = bs + GC;           // [64] accumulates dG
   float* dbs = dGs + GC;          // [64] accumulates dbeta
-  float* red = dbs + GC;          // [32]
+  float* Rv = dbs + GC;           // [64]
+  float* red = Rv + GC;           // [32]
   const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int hk = hv / (d.Hv / d.Hk);
   const int tid = threadIdx.x;
@@ -394,10 +550,14 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
     for (int x = 0; x < GD; ++x) t += kg[tid * ldk + x] * E2[tid * GD + x];
     const float r = __expf(glast - Gs[tid]) * t;
     dGs[tid] -= r;
-    red[0] = 0.f;                      // (re)used below
-    atomicAdd(&dGs[GC - 1], r);
+    Rv[tid] = r;
   }
   __syncthreads();
+  if (tid == 0) {
+    float t = 0.f;
+    for (int i = 0; i < GC; ++i) t += Rv[i];
+    dGs[GC - 1] += t;
+  }
   for (int e = tid; e < GC * GD; e += 256) E2[e] *= __expf(glast - Gs[e / GD]);
   __syncthreads();
   mm<true, false, true>(E2, GD, Y1, GC, qg, ldk, GC, GD, GC);
@@ -405,7 +565,7 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
   {
     float part = 0.f;
     for (int e = tid; e < GD * GD; e += 256) part += Sg[e] * dSg[e];
-    const float tot = block_sum256(part, red);
+    const float tot = block_sum(part, red);
     if (tid == 0) dGs[GC - 1] += __expf(glast) * tot;
   }
   __syncthreads();
@@ -444,13 +604,13 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
   mm<true, false, false>(Y2, GC, Tg, GC, Y1, GC, GC, GC, GC);
   __syncthreads();
   mm<false, true, false>(Y3, GC, Y2, GC, Tg, GC, GC, GC, GC);
-  mm<false, true, false>(Y2, GC, kg, ldk, kg, ldk, GC, GC, GD);        // K K^T
+  mm<false, true, false>(Y1, GC, kg, ldk, kg, ldk, GC, GC, GD);        // K K^T (dT is no longer needed)
   __syncthreads();
   for (int e = tid; e < GC * GC; e += 256) {
     const int i = e / GC, j = e - i * GC;
     const float dad = (i > j) ? -Y3[e] * __expf(Gs[i] - Gs[j]) : 0.f;
+    Y2[e] = dad * bs[i] * Y1[e];       // M_A = dA o A
     Y1[e] = dad;                       // dA o D
-    Y2[e] = dad * bs[i] * Y2[e];       // M_A = dA o A
   }
   __syncthreads();
   if (tid < GC) {
@@ -462,10 +622,7 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
     // gamma in W: sum_x d(gamma Kb)[i][x] * gamma_i beta_i K[i][x]
     float t = 0.f;
     for (int x = 0; x < GD; ++x) t += E1[tid * GD + x] * kg[tid * ldk + x];
-    const float eg = __expf(Gs[tid]);
-    dGs[tid] += rs - cs + eg * bs[tid] * t;
-    // beta in M_A: A_ij = beta_i (K K^T o D)_ij  ->  dbeta_i += sum_j dA_ij A_ij / beta_i
-    dbs[tid] += (bs[tid] != 0.f) ? rs / bs[tid] : 0.f;
+    dGs[tid] += rs - cs + __expf(Gs[tid]) * bs[tid] * t;
   }
   __syncthreads();
   // ---- 8. dKb = (dA o D) K + gamma o d(gamma Kb)
@@ -498,43 +655,70 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
 }
 
 constexpr size_t kPrepSmem = (3 * GC * GC + 2 * GC) * sizeof(float);
-constexpr size_t kScanSmem = (GD * GD + 4 * GC * GD + GC * GC + GC) * sizeof(float);
-constexpr size_t kChunkBwdSmem = (3 * GC * GD + 3 * GC * GC + 4 * GC + 32) * sizeof(float);
+constexpr size_t kChunkBwdSmem = (3 * GC * GD + 3 * GC * GC + 5 * GC + 32) * sizeof(float);
+
+template <bool BWD>
+const char* launch_scan(const float* A1, const float* A2, const float* V0, const float* R0, const float* gl, const float* Rinit,
+                        int B, int Hv, int n, float* Vout, float* Rchunks, float* Rfinal, cudaStream_t stream) {
+  if (n > 1024) return "gdn_tc: at most 1024 chunks (65536 tokens) per sequence";
+  int dev = 0, sms = 148;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  // narrower column slices when the heads alone would leave SMs idle
+  const bool narrow = static_cast<long long>(B) * Hv * 2 < sms;
+  if (!FERRL_ONCE_PER_DEVICE(
+          cudaFuncSetAttribute(gdn_scan_kernel<64, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(ScanSmem<64>::BYTES)) == cudaSuccess &&
+          cudaFuncSetAttribute(gdn_scan_kernel<32, BWD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               static_cast<int>(ScanSmem<32>::BYTES)) == cudaSuccess))
+    return "gdn_tc: cannot reserve shared memory";
+  if (narrow)
+    gdn_scan_kernel<32, BWD><<<dim3(Hv * 4, B), 256, ScanSmem<32>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 4, Vout, Rchunks,
+                                                                                    Rfinal);
+  else
+    gdn_scan_kernel<64, BWD><<<dim3(Hv * 2, B), 256, ScanSmem<64>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 2, Vout, Rchunks,
+                                                                                    Rfinal);
+  count_launch();
+  return nullptr;
+}
 
 }  // namespace
 
 const char* gdn_tc_forward(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* S0,
-                           int B, int T, int Hk, int Hv, float* Gc, float* Tm, float* U, float* W, float* out,
-                           float* S_out, float* Sin, float* Vn, cudaStream_t stream) {
+                           int B, int T, int Hk, int Hv, float* Gc, float* gl, float* Tm, float* U, float* Wn, float* Kd,
+                           float* out, float* S_out, float* Sin, float* Vn, cudaStream_t stream) {
   if (T % GC) return "gdn_tc: the sequence length must be a multiple of 64 (pad with beta = 0, g = 0)";
   if (Hk <= 0 || Hv % Hk) return "gdn_tc: value heads must be a multiple of key heads";
   if (B == 0 || T == 0) return nullptr;
   GdnDims d{B, T, Hk, Hv, T / GC};
   if (!FERRL_ONCE_PER_DEVICE(
           cudaFuncSetAttribute(gdn_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kPrepSmem)) == cudaSuccess &&
-          cudaFuncSetAttribute(gdn_scan_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kScanSmem)) == cudaSuccess))
+          cudaFuncSetAttribute(gdn_out_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kOutSmem)) == cudaSuccess))
     return "gdn_tc: cannot reserve shared memory";
-  gdn_prep_kernel<<<dim3(d.n, Hv, B), 256, kPrepSmem, stream>>>(k, v, g, beta, d, Gc, Tm, U, W);
+  gdn_prep_kernel<<<dim3(d.n, Hv, B), 256, kPrepSmem, stream>>>(k, v, g, beta, d, Gc, gl, Tm, U, Wn, Kd);
   count_launch();
-  gdn_scan_fwd_kernel<<<dim3(Hv, B), 256, kScanSmem, stream>>>(q, k, Gc, U, W, S0, d, out, S_out, Sin, Vn);
+  if (const char* e = launch_scan<false>(Wn, Kd, U, nullptr, gl, S0, B, Hv, d.n, Vn, Sin, S_out, stream)) return e;
+  gdn_out_kernel<<<dim3(d.n, Hv, B), 256, kOutSmem, stream>>>(q, k, Gc, Sin, Vn, d, out);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_tc forward launch failed";
 }
 
-const char* gdn_tc_backward(const float* q, const float* k, const float* v, const float* beta, const float* Gc,
-                            const float* Tm, const float* W, const float* Vn, const float* Sin, const float* dO,
-                            const float* dS_final, int B, int T, int Hk, int Hv, float* dVn, float* dSout, float* dq,
-                            float* dk, float* dv, float* dbeta, float* dG, float* dS0, cudaStream_t stream) {
+const char* gdn_tc_backward(const float* q, const float* k, const float* v, const float* beta, const float* Gc, const float* gl,
+                            const float* Tm, const float* Wn, const float* Kd, const float* Vn, const float* Sin,
+                            const float* dO, const float* dS_final, int B, int T, int Hk, int Hv, float* X0, float* Y0,
+                            float* dVn, float* dSout, float* dq, float* dk, float* dv, float* dbeta, float* dG, float* dS0,
+                            cudaStream_t stream) {
   if (T % GC) return "gdn_tc: the sequence length must be a multiple of 64";
   if (Hk <= 0 || Hv % Hk) return "gdn_tc: value heads must be a multiple of key heads";
   if (B == 0 || T == 0) return nullptr;
   GdnDims d{B, T, Hk, Hv, T / GC};
   if (!FERRL_ONCE_PER_DEVICE(
-          cudaFuncSetAttribute(gdn_scan_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kScanSmem)) == cudaSuccess &&
+          cudaFuncSetAttribute(gdn_bwd_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdPrepSmem)) == cudaSuccess &&
           cudaFuncSetAttribute(gdn_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kChunkBwdSmem)) == cudaSuccess))
     return "gdn_tc: cannot reserve shared memory";
-  gdn_scan_bwd_kernel<<<dim3(Hv, B), 256, kScanSmem, stream>>>(q, k, Gc, W, dO, dS_final, d, dVn, dSout, dS0);
+  gdn_bwd_prep_kernel<<<dim3(d.n, Hv, B), 256, kBwdPrepSmem, stream>>>(q, k, Gc, dO, d, X0, Y0);
   count_launch();
+  if (const char* e = launch_scan<true>(Kd, Wn, X0, Y0, gl, dS_final, B, Hv, d.n, dVn, dSout, dS0, stream)) return e;
   gdn_chunk_bwd_kernel<<<dim3(d.n, Hv, B), 256, kChunkBwdSmem, stream>>>(q, k, v, beta, Gc, Tm, Vn, dVn, Sin, dSout, dO, d, dq,
                                                                          dk, dv, dbeta, dG);
   count_launch();

@@ -414,6 +414,31 @@ sample_rows_kernel(const T* __restrict__ logits, long long ld, const long long* 
 
 }  // namespace
 
+// Combine the per-tile (max, sum exp) pairs of the head GEMM's log-prob epilogue: lse = log sum exp over the
+// vocabulary, lp = target logit - lse.  One thread per row; the tile-major layout keeps the reads coalesced.
+__global__ void logprob_finalize_kernel(const float2* __restrict__ ws, const float* __restrict__ tl, int n_tiles, int M,
+                                        float* __restrict__ lp, float* __restrict__ lse) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY;
+  for (int t = 0; t < n_tiles; ++t) m = fmaxf(m, ws[static_cast<long long>(t) * M + row].x);
+  float s = 0.f;
+  for (int t = 0; t < n_tiles; ++t) {
+    const float2 v = ws[static_cast<long long>(t) * M + row];
+    s += v.y * __expf(v.x - m);
+  }
+  const float l = m + __logf(s);
+  lse[row] = l;
+  lp[row] = tl[row] - l;
+}
+
+const char* logprob_finalize(const float* ws, const float* tl, int n_tiles, int M, float* lp, float* lse, cudaStream_t s) {
+  if (M == 0) return nullptr;
+  logprob_finalize_kernel<<<(M + 127) / 128, 128, 0, s>>>(reinterpret_cast<const float2*>(ws), tl, n_tiles, M, lp, lse);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "logprob_finalize launch failed";
+}
+
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,
                          long long rows, int V, float temperature, float softcap, cudaStream_t s) {
   if (rows == 0) return nullptr;

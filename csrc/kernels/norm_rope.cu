@@ -531,6 +531,56 @@ const char* rmsnorm_bwd(int dtype, const void* x, const void* w, const void* dy,
                        : rmsnorm_bwd_t<__nv_bfloat16>(x, w, dy, dx, rows, H, eps, zero_centered, s);
 }
 
+// Gated RMSNorm backward with a frozen weight: y = x * rstd * w * silu(g).
+//   a_i = dy_i w_i silu(g_i);  dx_i = rstd (a_i - x_i rstd^2 mean_j(a_j x_j));  dg_i = dy_i x_i rstd w_i silu'(g_i)
+// One warp per row (rows are GatedDeltaNet value heads, H = 128), several rows per CTA.
+template <typename T>
+__global__ void rmsnorm_gated_bwd_kernel(const T* __restrict__ x, const T* __restrict__ gate, const T* __restrict__ w,
+                                         const T* __restrict__ dy, T* __restrict__ dx, T* __restrict__ dg, long long rows,
+                                         int H, float eps) {
+  const long long row = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const T* xr = x + row * H;
+  const T* gr = gate + row * H;
+  const T* yr = dy + row * H;
+  float ss = 0.f, dot = 0.f;
+  for (int i = lane; i < H; i += 32) {
+    const float v = to_f(xr[i]), g = to_f(gr[i]);
+    const float sg = 1.f / (1.f + __expf(-g));
+    ss += v * v;
+    dot += v * to_f(yr[i]) * to_f(w[i]) * g * sg;
+  }
+  ss = warp_sum(ss);
+  dot = warp_sum(dot);
+  const float rstd = rsqrtf(ss / H + eps);
+  const float c = dot * rstd * rstd / H;
+  for (int i = lane; i < H; i += 32) {
+    const float v = to_f(xr[i]), g = to_f(gr[i]), d = to_f(yr[i]) * to_f(w[i]);
+    const float sg = 1.f / (1.f + __expf(-g));
+    dx[row * H + i] = from_f<T>(rstd * (d * g * sg - v * c));
+    dg[row * H + i] = from_f<T>(d * v * rstd * sg * (1.f + g * (1.f - sg)));
+  }
+}
+
+template <typename T>
+static const char* rmsnorm_gated_bwd_t(const void* x, const void* gate, const void* w, const void* dy, void* dx, void* dg,
+                                       long long rows, int H, float eps, cudaStream_t s) {
+  if (rows == 0) return nullptr;
+  const int warps = 8;
+  rmsnorm_gated_bwd_kernel<T><<<static_cast<unsigned>((rows + warps - 1) / warps), warps * 32, 0, s>>>(
+      static_cast<const T*>(x), static_cast<const T*>(gate), static_cast<const T*>(w), static_cast<const T*>(dy),
+      static_cast<T*>(dx), static_cast<T*>(dg), rows, H, eps);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "rmsnorm_gated_bwd launch failed";
+}
+
+const char* rmsnorm_gated_bwd(int dtype, const void* x, const void* gate, const void* w, const void* dy, void* dx,
+                              void* dg, long long rows, int H, float eps, cudaStream_t s) {
+  return dtype == kF32 ? rmsnorm_gated_bwd_t<float>(x, gate, w, dy, dx, dg, rows, H, eps, s)
+                       : rmsnorm_gated_bwd_t<__nv_bfloat16>(x, gate, w, dy, dx, dg, rows, H, eps, s);
+}
+
 template <typename T, bool BWD>
 static const char* qknr_t(const QkNormRopeArgs& a, cudaStream_t s) {
   if (a.D > 512 || (a.D & 1) || 2 * a.half > a.D) return "qk_norm_rope: head_dim must be even, <= 512, rot <= D";

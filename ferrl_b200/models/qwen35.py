@@ -296,6 +296,14 @@ class Qwen35Layer(nn.Module):
                 core, S1 = res
                 core = ops.rmsnorm_gated(core.reshape(-1, self.vd), z.reshape(-1, self.vd), self.gdn_norm, self.eps)
                 return f(self.out, core.reshape(B, S_, self.value_dim)), (new_left, S1)
+        if fast and not decode and self.kd == 128 and self.vd == 128:
+            # training: tensor-core chunk kernels with a hand-written backward
+            from ..ops import cuda as C
+            res = C.gdn_chunk_tc(q, k, v, g, beta, S0, 1e-6)
+            if res is not None:
+                core, S1 = res
+                core = ops.rmsnorm_gated(core.reshape(-1, self.vd), z.reshape(-1, self.vd), self.gdn_norm, self.eps)
+                return f(self.out, core.reshape(B, S_, self.value_dim)), (new_left, S1)
         rep = self.vh // self.kh
         if rep > 1:
             q, k = q.repeat_interleave(rep, dim=2), k.repeat_interleave(rep, dim=2)

@@ -13,6 +13,7 @@ import os
 from typing import Optional
 
 import torch
+import torch.nn.functional as F
 
 from . import eager
 
@@ -258,10 +259,28 @@ def add_rmsnorm(x, residual, weight, eps, zero_centered=False):
     return _AddRmsNorm.apply(x, residual, weight, eps, zero_centered)
 
 
+class _RmsNormGated(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, gate, w, eps):
+        y, _ = lib().rmsnorm(x, None, w, gate, eps, False)
+        ctx.save_for_backward(x, gate, w)
+        ctx.eps = eps
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, gate, w = ctx.saved_tensors
+        dx, dg = lib().rmsnorm_gated_bwd(x, gate, w, dy.contiguous(), ctx.eps)
+        return dx, dg, None, None
+
+
 def rmsnorm_gated(x, gate, weight, eps):
-    if torch.is_grad_enabled() and (x.requires_grad or gate.requires_grad or weight.requires_grad):
+    if weight.requires_grad or gate.dtype != x.dtype:
         return eager.rmsnorm_gated(x, gate, weight, eps)
-    y, _ = lib().rmsnorm(x.contiguous(), None, weight.to(x.dtype), gate.contiguous(), eps, False)
+    w = weight.to(x.dtype).contiguous()
+    if torch.is_grad_enabled() and (x.requires_grad or gate.requires_grad):
+        return _RmsNormGated.apply(x.contiguous(), gate.contiguous(), w, eps)
+    y, _ = lib().rmsnorm(x.contiguous(), None, w, gate.contiguous(), eps, False)
     return y
 
 
@@ -478,6 +497,54 @@ def gdn_chunk_fwd(q, k, v, g, beta, S0=None, l2norm=True, eps=1e-6):
                                bool(l2norm), float(eps))
 
 
+class _GdnTc(torch.autograd.Function):
+    """Tensor-core chunked gated delta rule with its hand-written backward (``csrc/kernels/gdn_tc.cu``)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, g, beta, S0):
+        out, S1, *saved = lib().gdn_tc_fwd(q, k, v, g, beta, S0)
+        if any(ctx.needs_input_grad):
+            ctx.save_for_backward(q, k, v, beta, *saved)
+        ctx.set_materialize_grads(False)
+        return out, S1
+
+    @staticmethod
+    def backward(ctx, dO, dS1):
+        q, k, v, beta, Gc, gl, Tm, Wn, Kd, Vn, Sin = ctx.saved_tensors
+        dO = torch.zeros_like(v) if dO is None else dO.contiguous()
+        dq, dk, dv, dbeta, dG, dS0 = lib().gdn_tc_bwd(q, k, v, beta, Gc, gl, Tm, Wn, Kd, Vn, Sin, dO,
+                                                      None if dS1 is None else dS1.contiguous())
+        B, T, Hv, D = dq.shape
+        Hk = q.shape[2]
+        if Hv != Hk:      # several value heads share one key head
+            dq = dq.view(B, T, Hk, Hv // Hk, D).sum(3)
+            dk = dk.view(B, T, Hk, Hv // Hk, D).sum(3)
+        # dG is the gradient of the cumulative log decay inside each chunk: g_j reaches every G_i with i >= j
+        dg = dG.view(B, T // 64, 64, Hv).flip(2).cumsum(2).flip(2).reshape(B, T, Hv)
+        return dq, dk, dv, dg, dbeta, (dS0 if ctx.needs_input_grad[5] else None)
+
+
+def gdn_chunk_tc(q, k, v, g, beta, S0=None, eps=1e-6):
+    """Chunked gated delta rule on the tensor cores with autograd: ``q,k`` ``[B,T,Hk,128]`` (raw; they are
+    L2-normalised here and q is scaled by 1/sqrt(128)), ``v`` ``[B,T,Hv,128]``, ``g,beta`` ``[B,T,Hv]``, ``S0``
+    ``[B,Hv,128,128]`` f32 -> ``(out [B,T,Hv,128] in v's dtype, S [B,Hv,128,128] f32)``; ``None`` outside the
+    kernels' domain (head dims other than 128)."""
+    if q.shape[-1] != 128 or v.shape[-1] != 128 or v.shape[2] % q.shape[2]:
+        return None
+    T = q.shape[1]
+    qf = eager.l2norm(q.float(), eps) * (128 ** -0.5)
+    kf = eager.l2norm(k.float(), eps)
+    vf, gf, bf = v.float(), g.float(), beta.float()
+    pad = (-T) % 64
+    if pad:
+        # beta = 0 and g = 0 leave the state untouched on the padded tokens
+        qf, kf, vf = (F.pad(t, (0, 0, 0, 0, 0, pad)) for t in (qf, kf, vf))
+        gf, bf = F.pad(gf, (0, 0, 0, pad)), F.pad(bf, (0, 0, 0, pad))
+    out, S1 = _GdnTc.apply(qf.contiguous(), kf.contiguous(), vf.contiguous(), gf.contiguous(), bf.contiguous(),
+                           None if S0 is None else S0.float().contiguous())
+    return out[:, :T].to(v.dtype), S1
+
+
 def gdn_decode_step(q, k, v, g, beta, S, l2norm=True, eps=1e-6):
     """Single-token gated delta rule; ``S`` ``[B,Hv,KD,VD]`` float32 is updated in place."""
     return lib().gdn_decode_step(q, k, v, g.contiguous(), beta.contiguous(), S, bool(l2norm), float(eps))
@@ -578,36 +645,35 @@ LOGPROB_CHUNK_BYTES = 1 << 30
 
 
 class _LogprobGather(torch.autograd.Function):
+    """``log_softmax(softcap(h Wᵀ) / T)[target]`` with the row statistics taken in the head GEMM's epilogue
+    (``csrc/gemm/tcgen05_gemm.cu``, ``lp_mode``): the forward allocates nothing of vocabulary width.  The
+    backward recomputes the logits tile by tile and writes the softmax gradient straight from the epilogue,
+    one bounded row chunk at a time, then multiplies by the weight again.  Reference: the chunked
+    log-softmax gather of crates/ferrl/src/model.rs:523-559, which materialises ``[chunk, V]`` logits."""
+
     @staticmethod
     def forward(ctx, hidden, head_w, head_wt, targets, temperature, softcap):
-        N, H = hidden.shape
-        V = head_w.shape[0]
-        chunk = max(128, min(N, (LOGPROB_CHUNK_BYTES // (2 * V)) // 128 * 128)) if N else 1
-        lp = torch.empty(N, dtype=torch.float32, device=hidden.device)
-        lse = torch.empty(N, dtype=torch.float32, device=hidden.device)
         h = hidden.contiguous()
         t = targets.contiguous()
-        for s in range(0, N, chunk):
-            logits = gemm(h[s:s + chunk], head_w)
-            a, b = lib().logprob_rows(logits, t[s:s + chunk], temperature, softcap)
-            lp[s:s + chunk] = a
-            lse[s:s + chunk] = b
+        lp, lse = lib().logprob_head_fwd(h, head_w, t, temperature, softcap)
         ctx.save_for_backward(h, head_w, head_wt, t, lse)
-        ctx.meta = (temperature, softcap, chunk)
+        ctx.meta = (temperature, softcap)
         return lp
 
     @staticmethod
     def backward(ctx, dlp):
         h, head_w, head_wt, t, lse = ctx.saved_tensors
-        temperature, softcap, chunk = ctx.meta
-        N = h.shape[0]
+        temperature, softcap = ctx.meta
+        N, V = h.shape[0], head_w.shape[0]
+        chunk = max(256, min(N, (LOGPROB_CHUNK_BYTES // (2 * V)) // 256 * 256)) if N else 1
         wt = head_wt if head_wt is not None else head_w.t().contiguous()
         dh = torch.empty_like(h)
-        dlp = dlp.contiguous().float()
+        coef = (-dlp).contiguous().float()
         for s in range(0, N, chunk):
-            logits = gemm(h[s:s + chunk], head_w)
-            lib().logprob_rows_bwd(logits, t[s:s + chunk], lse[s:s + chunk], dlp[s:s + chunk], temperature, softcap)
-            dh[s:s + chunk] = gemm(logits, wt)
+            dl = lib().logprob_head_dlogits(h[s:s + chunk], head_w, t[s:s + chunk], lse[s:s + chunk], coef[s:s + chunk],
+                                            temperature, softcap, 0)
+            dh[s:s + chunk] = gemm(dl, wt)
+            del dl
         return dh, None, None, None, None, None
 
 

@@ -220,7 +220,7 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     if cand_writer is not None and comm.rank != 0:
         cand_writer = T.CandidateWriter(run_dir.candidates_path + f".rank{comm.rank}", signer)
     fused = None
-    if topology == "dp" and comm.world_size > 1 and device.startswith("cuda"):
+    if topology == "dp" and device.startswith("cuda"):
         from .parallel.dp import FusedDpStep
         fused = FusedDpStep.create(comm, policy.trainable_params(), torch.device(device))
     trainer = Trainer(policy, tokenizer, reward_fn, train_samples, cfg.trainer, comm=comm, topology=topology,

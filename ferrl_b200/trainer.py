@@ -60,6 +60,11 @@ class RunStop(enum.Enum):
     PREEMPTED = "preempted"
 
 
+# a rank whose backward raised enters the fused data-parallel step with this "uncovered" count (exact in
+# float32, far above any real tensor count) so that every rank learns of it from the kernel's world-wide sum
+PEER_FAILED_COUNT = float(2 ** 20)
+
+
 class TrainerError(RuntimeError):
     pass
 
@@ -469,8 +474,20 @@ class Trainer:
             for item in live:
                 self._item_backward(item, window_tokens, beta, stats, agg)
         # every rank must have finished (or failed) its local backward before anyone enters the
-        # gradient collective; a failure anywhere raises on all ranks here, not at a timeout
-        self._rendezvous(local_backward, "backward")
+        # gradient collective; a failure anywhere raises on all ranks here, not at a timeout.
+        # The fused peer-memory step already sums an "uncovered" count over the world on the device and
+        # skips the update when it is non-zero, so there a failed backward rides on that count and the
+        # healthy step has no rendezvous of its own.
+        backward_error = None
+        if self.fused_dp_step is not None and self.parallel_runtime is None and self._deferred_agreement():
+            try:
+                local_backward()
+            except CommError:
+                raise
+            except Exception as e:  # noqa: BLE001 - reported to every rank through the fused step's count
+                backward_error = e
+        else:
+            self._rendezvous(local_backward, "backward")
         if self.parallel_runtime is not None:
             # a bounded peer wait that ran out inside a fused tensor-/expert-parallel kernel leaves a
             # status word behind: raise CommTimeout here, before the optimizer touches anything
@@ -497,8 +514,14 @@ class Trainer:
         if self.fused_dp_step is not None:
             # fused peer-memory path: all-reduce + clip + AdamW in one pass
             self.opt.set_learning_rate(lr)
+            if backward_error is not None:
+                uncovered = PEER_FAILED_COUNT
             res = self.fused_dp_step(self.opt, [p.grad for p in self.params], self.config.max_grad_norm, uncovered)
             agg["grad_norm"] = res.grad_norm
+            if backward_error is not None:
+                raise PeerFailure(f"backward failed on this rank: {backward_error!r}", local=backward_error)
+            if res.uncovered >= PEER_FAILED_COUNT:
+                raise PeerFailure("backward failed on a peer rank", local=None)
             if res.uncovered > 0:
                 raise GradCoverageError(f"{int(res.uncovered)} trainable tensor(s) uncovered or non-finite "
                                         "somewhere in the world")
@@ -531,8 +554,9 @@ class Trainer:
         self._phase_end("grad_reduce_optimizer")
 
     # ---------------------------------------------------------------- window
-    def collect_window(self, step: int) -> list:
-        """Rollout + reward half of a window: ``[(accum_index, [CollectedGroup, ...]), ...]``."""
+    def collect_window(self, step: int, defer_agreement: bool = False) -> list:
+        """Rollout + reward half of a window: ``[(accum_index, [CollectedGroup, ...]), ...]``.
+        ``defer_agreement``: the caller's next exchange reports a failure of this stage (``run_window``)."""
         c = self.config
         P = c.prompts_per_item
         def local():
@@ -541,9 +565,15 @@ class Trainer:
                 sels = [self.select_prompt(step, j * P + q) for q in range(P)]
                 out.append((j, self.collect_groups(sels)))
             return out
-        # rollout + rewards touch no data-parallel collective: agree on success first, then
-        # (possibly cross-rank) advantage normalisation
-        out = self._rendezvous(local, "rollout collection")
+        # rollout + rewards touch no data-parallel collective.  With rank-local advantages nothing
+        # between here and the window-size exchange needs the peers, so a failure is carried to that
+        # exchange instead of a rendezvous of its own; cross-rank normalisation needs agreement first.
+        if defer_agreement and self._deferred_agreement():
+            out = self._stage(local, "rollout collection")
+            if out is None:
+                return []
+        else:
+            out = self._rendezvous(local, "rollout collection")
         for _, groups in out:
             self._advantages(groups)
         return out
@@ -553,8 +583,9 @@ class Trainer:
         stats = WindowStats()
         live: list[LiveItem] = []
         all_groups: list[CollectedGroup] = []
+        self._pending_failure = None
         if collected is None:
-            collected = self.collect_window(step)
+            collected = self.collect_window(step, defer_agreement=True)
 
         def local_materialize():
             for j, groups in collected:
@@ -562,12 +593,28 @@ class Trainer:
                 item = self.materialize(groups, beta, stats)
                 if item is not None:
                     live.append(item)
-        self._rendezvous(local_materialize, "rollout scoring")
-        if c.candidate_log_top_k > 0 and self.candidate_writer is not None:
-            self._log_candidates(step, all_groups)
-        local_tokens = stats.completion_tokens
-        window_tokens, n_live = self.comm.all_reduce_scalars_sum([float(local_tokens), float(len(live))]) \
-            if self.topology == "dp" else (float(local_tokens), float(len(live)))
+        if self._deferred_agreement():
+            # one exchange carries the window size, the live-item count and whether any rank failed in
+            # the rollout or scoring stage: a healthy step has no other rendezvous before its backward
+            self._stage(local_materialize, "rollout scoring")
+            failed = self._pending_failure
+            self._pending_failure = None
+            local_tokens = stats.completion_tokens
+            window_tokens, n_live, failures = self.comm.all_reduce_scalars_sum(
+                [float(local_tokens), float(len(live)), 0.0 if failed is None else 1.0])
+            if failures > 0:
+                if failed is not None:
+                    raise PeerFailure(f"{failed[0]} failed on this rank: {failed[1]!r}", local=failed[1])
+                raise PeerFailure(f"rollout or scoring failed on {int(failures)} peer rank(s)", local=None)
+            if c.candidate_log_top_k > 0 and self.candidate_writer is not None:
+                self._log_candidates(step, all_groups)
+        else:
+            self._rendezvous(local_materialize, "rollout scoring")
+            if c.candidate_log_top_k > 0 and self.candidate_writer is not None:
+                self._log_candidates(step, all_groups)
+            local_tokens = stats.completion_tokens
+            window_tokens, n_live = self.comm.all_reduce_scalars_sum([float(local_tokens), float(len(live))]) \
+                if self.topology == "dp" else (float(local_tokens), float(len(live)))
         window_tokens = max(window_tokens, 1.0)
         agg = {"kl": 0.0, "clip_low": 0.0, "clip_high": 0.0, "tokens": 0.0, "loss": 0.0, "grad_norm": 0.0,
                "stepped": False, "epoch": 0}
@@ -630,6 +677,27 @@ class Trainer:
         if self.topology == "dp" and self.comm.world_size > 1:
             return self.comm.coordinate(fn, what)
         return fn()
+
+    _pending_failure = None
+
+    def _deferred_agreement(self) -> bool:
+        """True when the rollout and scoring stages need no rendezvous of their own: plain data
+        parallelism (no lockstep model calls) with rank-local advantage normalisation."""
+        return (self.topology == "dp" and self.comm.world_size > 1 and not self.lockstep_model_calls
+                and (self.config.reward_group_scope == RewardGroupScope.LOCAL or self.dp_world == 1))
+
+    def _stage(self, fn, what: str):
+        """Run a rank-local stage whose outcome the ranks agree on at the window's next exchange; after
+        a failure the later stages of this rank are skipped (``None``) until that exchange."""
+        if self._pending_failure is not None:
+            return None
+        try:
+            return fn()
+        except CommError:
+            raise
+        except Exception as e:  # noqa: BLE001 - reported to every rank at the next exchange
+            self._pending_failure = (what, e)
+            return None
 
     # ------------------------------------------------------------ phases
     def _phase(self, label: str):

@@ -41,6 +41,17 @@ def main():
                      grad_scale=min(1.0, 1.0 / norm))
         for a, b in zip(params, ref_p):
             assert (a.detach() - b).abs().max().item() < 2e-5
+    # a rank whose backward failed enters the same kernel with a large uncovered count: nobody steps,
+    # every rank reads the count (this is how the trainer agrees on a backward failure without a
+    # rendezvous of its own)
+    before = [p.detach().clone() for p in params]
+    fused.prepare_grads()
+    for p in params:
+        p.grad.add_(1.0)
+    res = fused(opt, None, 1.0, float(2 ** 20) if rank == world - 1 else 0.0, pre_scale=1.0 / world)
+    assert not res.stepped and res.uncovered >= 2 ** 20, res
+    for a, b in zip(params, before):
+        assert torch.equal(a.detach(), b)
     # ranks must hold bit-identical parameters
     import hashlib
     digest = hashlib.sha256(b"".join(p.detach().cpu().numpy().tobytes() for p in params)).digest()

@@ -169,6 +169,38 @@ def test_dp_asymmetric_failure_rolls_back_every_rank_without_timeout():
         assert torch.equal(a, b)
 
 
+def test_dp_rollout_failure_is_reported_at_the_window_exchange_and_a_healthy_step_has_one_rendezvous():
+    """Rollout and scoring have no rendezvous of their own under plain data parallelism: a failure there
+    reaches every rank through the window-size exchange, and a healthy step enters exactly one status
+    rendezvous (after backward)."""
+    def body(comm):
+        pol = make_policy()
+        tr = Trainer(pol, ListTok(), FnReward(echo_reward), samples(), cfg(steps=3, prompts_per_item=1), comm=comm)
+        coordinated = []
+        orig = comm.coordinate
+        comm.coordinate = lambda fn, what="": (coordinated.append(what), orig(fn, what))[1]
+        tr.step(0)
+        snap = [p.detach().clone() for p in tr.params]
+        if comm.rank == 1:
+            def boom(point):
+                if point == "before_generate":
+                    raise RuntimeError("injected rollout failure")
+            tr.fault_hook = boom
+        with pytest.raises(PeerFailure) as ei:
+            tr.step(1)
+        assert (ei.value.local is not None) == (comm.rank == 1)
+        assert all(torch.equal(a, b.detach()) for a, b in zip(snap, tr.params))
+        tr.fault_hook = None
+        del coordinated[:]
+        m = tr.step(1)
+        assert m.live_groups > 0
+        return list(coordinated), [p.detach().clone() for p in tr.params]
+    res = run_ranks(2, body, timeout=30.0)
+    assert res[0][0] == ["backward"] and res[1][0] == ["backward"]
+    for a, b in zip(res[0][1], res[1][1]):
+        assert torch.equal(a, b)
+
+
 def test_uncovered_gradient_aborts():
     pol = make_policy()
     varied = FnReward(lambda s, c: float(sum(int(t) for t in c.split()) % 3))
