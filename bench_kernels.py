@@ -354,6 +354,22 @@ def main():
             o2, lse2 = C.lib().flash_fwd(q, k, v, D ** -0.5, True, 0, 0, 1)
             s = T(lambda: C.lib().flash_bwd(q, k, v, o2, lse2, do, D ** -0.5, True, 0, 0, 1))
         report(f"flash bwd B{B} S{S} causal (warp-level mma.sync)", s, 0, 2.5 * fl, "5 matmuls")
+        with torch.no_grad():
+            W_ = 1024
+            flw = 4 * B * HQ * D * (S * W_ - W_ * W_ / 2)          # visible (query, key) pairs with a 1024-key window
+            s = T(lambda: C.attention(q, k, v, scale=1.0 / 16, causal=True, window=W_))
+            report(f"flash fwd B{B} S{S} window {W_} (tcgen05, third form)", s, 0, flw)
+            s = T(lambda: C.attention(q, k, v, scale=1.0 / 16, causal=True, window=W_, variant=1))
+            report(f"flash fwd B{B} S{S} window {W_} (warp-level mma.sync)", s, 0, flw)
+            q2 = torch.randn(B, S, 16, 256, device=dev, dtype=bf)
+            k2 = torch.randn(B, S, 2, 256, device=dev, dtype=bf)
+            v2 = torch.randn(B, S, 2, 256, device=dev, dtype=bf)
+            fl2 = 4 * B * 16 * S * S * 256 / 2
+            s = T(lambda: C.attention(q2, k2, v2, scale=1.0 / 16, causal=True))
+            report(f"flash fwd B{B} S{S} 16q/2kv head_dim 256 (tcgen05, third form, 64-key tiles)", s, 0, fl2)
+            s = T(lambda: C.attention(q2, k2, v2, scale=1.0 / 16, causal=True, variant=1))
+            report(f"flash fwd B{B} S{S} 16q/2kv head_dim 256 (warp-level mma.sync)", s, 0, fl2)
+            del q2, k2, v2
         Bd, Smax = 128, 1536
         qd = torch.randn(Bd, HQ, D, device=dev, dtype=bf)
         kc = torch.randn(Bd, Smax, HKV, D, device=dev, dtype=bf)

@@ -228,7 +228,8 @@ const char* gdn_decode_step(const void* q, const void* k, const void* v, long lo
 // ---- chunked gated delta rule on tensor cores, forward and backward (csrc/kernels/gdn_tc.cu)
 // All tensors fp32 and contiguous: q,k [B,T,Hk,128] (already L2-normalised, q scaled), v/out/dO/dq/dk/dv
 // [B,T,Hv,128], g/beta/dG/dbeta [B,T,Hv]; per-chunk tensors (n = T / 64 chunks) Gc [B,Hv,n,64], gl [B,Hv,n],
-// Tm [B,Hv,n,64,64], U/Wn/Kd/Vn/X0/dVn [B,Hv,n,64,128], Sin/Y0/dSout [B,Hv,n,128,128]; states [B,Hv,128,128].
+// Tm [B,Hv,n,64,64], U/Wn/Kd/Vn/X0/dVn/dW [B,Hv,n,64,128], Sin/Y0/dSout [B,Hv,n,128,128], dGpart [2,B,T,Hv];
+// states [B,Hv,128,128].
 // T must be a multiple of 64 (at most 65536).  S0 and dS_final may be null.
 const char* gdn_tc_forward(const float* q, const float* k, const float* v, const float* g, const float* beta, const float* S0,
                            int B, int T, int Hk, int Hv, float* Gc, float* gl, float* Tm, float* U, float* Wn, float* Kd,
@@ -236,8 +237,8 @@ const char* gdn_tc_forward(const float* q, const float* k, const float* v, const
 const char* gdn_tc_backward(const float* q, const float* k, const float* v, const float* beta, const float* Gc, const float* gl,
                             const float* Tm, const float* Wn, const float* Kd, const float* Vn, const float* Sin,
                             const float* dO, const float* dS_final, int B, int T, int Hk, int Hv, float* X0, float* Y0,
-                            float* dVn, float* dSout, float* dq, float* dk, float* dv, float* dbeta, float* dG, float* dS0,
-                            cudaStream_t stream);
+                            float* dVn, float* dSout, float* dW, float* dGpart, float* dq, float* dk, float* dv, float* dbeta,
+                            float* dG, float* dS0, cudaStream_t stream);
 
 // ---- expert parallelism over the symmetric heap (csrc/moe/ep.cu)
 struct EpDispatchParams {

@@ -56,6 +56,60 @@ int* status_word() {
   return it->second.data_ptr<int>();
 }
 
+// ---- canary mode (a test aid): every output the bindings allocate sits between two 512-byte pads filled with a
+// pattern; check_canaries() counts pad bytes that changed since allocation, over all outputs made since the last
+// check, and forgets them.  A kernel that stores outside its output is caught without any device-side tool.
+std::atomic<bool> g_canary{false};
+std::mutex g_canary_mu;
+std::vector<std::pair<Tensor, int64_t>> g_canary_bufs;      // (raw byte buffer, payload bytes)
+constexpr int64_t kCanaryPad = 512;
+constexpr int kCanaryByte = 0xA5;
+
+Tensor canary_alloc(at::IntArrayRef sizes, const at::TensorOptions& opt, bool zero) {
+  int64_t numel = 1;
+  for (auto d : sizes) numel *= d;
+  const int64_t esz = static_cast<int64_t>(c10::elementSize(c10::typeMetaToScalarType(opt.dtype())));
+  const int64_t nbytes = (numel * esz + 15) / 16 * 16;
+  Tensor raw = at::empty({nbytes + 2 * kCanaryPad}, opt.dtype(at::kByte));
+  raw.slice(0, 0, kCanaryPad).fill_(kCanaryByte);
+  raw.slice(0, kCanaryPad + numel * esz, nbytes + 2 * kCanaryPad).fill_(kCanaryByte);
+  Tensor out = raw.slice(0, kCanaryPad, kCanaryPad + numel * esz).view(c10::typeMetaToScalarType(opt.dtype())).view(sizes);
+  if (zero) out.zero_();
+  std::lock_guard<std::mutex> g(g_canary_mu);
+  g_canary_bufs.emplace_back(raw, numel * esz);
+  return out;
+}
+// not while a CUDA graph is being captured: the pad fills would only run at replay
+bool canary_on() {
+  if (!g_canary.load()) return false;
+  cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+  return cudaStreamIsCapturing(c10::cuda::getCurrentCUDAStream().stream(), &st) == cudaSuccess && st == cudaStreamCaptureStatusNone;
+}
+Tensor out_empty(at::IntArrayRef sizes, const at::TensorOptions& opt) {
+  return canary_on() && opt.device().is_cuda() ? canary_alloc(sizes, opt, false) : at::empty(sizes, opt);
+}
+Tensor out_zeros(at::IntArrayRef sizes, const at::TensorOptions& opt) {
+  return canary_on() && opt.device().is_cuda() ? canary_alloc(sizes, opt, true) : at::zeros(sizes, opt);
+}
+Tensor out_empty_like(const Tensor& t) {
+  return canary_on() && t.is_cuda() && t.is_contiguous() ? canary_alloc(t.sizes(), t.options(), false) : at::empty_like(t);
+}
+void set_canary(bool on) { g_canary.store(on); }
+int64_t check_canaries() {
+  std::vector<std::pair<Tensor, int64_t>> bufs;
+  {
+    std::lock_guard<std::mutex> g(g_canary_mu);
+    bufs.swap(g_canary_bufs);
+  }
+  int64_t bad = 0;
+  for (auto& b : bufs) {
+    const Tensor& raw = b.first;
+    bad += raw.slice(0, 0, kCanaryPad).ne(kCanaryByte).sum().item<int64_t>();
+    bad += raw.slice(0, kCanaryPad + b.second, raw.size(0)).ne(kCanaryByte).sum().item<int64_t>();
+  }
+  return bad;
+}
+
 ferrl::PeerTable table_of_fwd(const std::vector<int64_t>& ptrs) {
   TORCH_CHECK(ptrs.size() <= ferrl::kMaxRanks, "too many ranks");
   ferrl::PeerTable t{};
@@ -94,7 +148,7 @@ Tensor decode_gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& res
   ferrl::DecodeGemmArgs a{};
   a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
   a.M = M; a.N = N; a.K = K;
-  Tensor out = at::empty({A.size(0), glu_act >= 0 ? B.size(0) / 2 : B.size(0)}, A.options());
+  Tensor out = out_empty({A.size(0), glu_act >= 0 ? B.size(0) / 2 : B.size(0)}, A.options());
   a.out = out.data_ptr(); a.ldo = out.stride(0);
   if (residual.has_value() && residual->defined()) {
     TORCH_CHECK(glu_act < 0, "decode_gemm: no residual with the GLU epilogue");
@@ -106,7 +160,7 @@ Tensor decode_gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& res
   Tensor partial;
   const int groups = ferrl::decode_gemm_groups(K);
   if (groups > 1) {
-    partial = at::empty({groups, A.size(0), B.size(0)}, A.options().dtype(at::kFloat));
+    partial = out_empty({groups, A.size(0), B.size(0)}, A.options().dtype(at::kFloat));
     a.partial = partial.data_ptr<float>();
   }
   a.status = status_word();
@@ -144,7 +198,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
                 "gemm: side operand shapes");
     a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
   }
-  Tensor out = at::empty({a.M, a.N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
+  Tensor out = out_empty({a.M, a.N}, A.options().dtype(out_f32 ? at::kFloat : at::kBFloat16));
   a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = out_f32;
   if (residual.has_value() && residual->defined()) {
     TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == a.M &&
@@ -183,8 +237,8 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
       const int dev = A.get_device();
       const int max_ctas = 160;
       if (!sk_ws[dev].defined()) {
-        sk_ws[dev] = at::empty({static_cast<long long>(max_ctas) * 2 * 128 * 256}, A.options().dtype(at::kFloat));
-        sk_flags[dev] = at::zeros({max_ctas * 2 + 2}, A.options().dtype(at::kInt));   // flags, launch counter, done counter
+        sk_ws[dev] = out_empty({static_cast<long long>(max_ctas) * 2 * 128 * 256}, A.options().dtype(at::kFloat));
+        sk_flags[dev] = out_zeros({max_ctas * 2 + 2}, A.options().dtype(at::kInt));   // flags, launch counter, done counter
       }
       a.stream_k = 1;
       a.sk_ws = sk_ws[dev].data_ptr<float>();
@@ -219,7 +273,7 @@ Tensor gemm(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const 
   }
   Tensor partial;
   if (split > 1) {
-    partial = at::empty({split, a.M, a.N}, A.options().dtype(at::kFloat));
+    partial = out_empty({split, a.M, a.N}, A.options().dtype(at::kFloat));
     a.partial = partial.data_ptr<float>();
     a.split_k = split;
   }
@@ -240,7 +294,7 @@ Tensor gemm_glu(const Tensor& A, const Tensor& B, int64_t act, bool static_b) {
   ferrl::GemmArgs a{};
   a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
   a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
-  Tensor out = at::empty({A.size(0), B.size(0) / 2}, A.options());
+  Tensor out = out_empty({A.size(0), B.size(0) / 2}, A.options());
   a.out = out.data_ptr(); a.ldo = out.stride(0);
   a.status = status_word(); a.num_sms = num_sms();
   a.glu_act = static_cast<int>(act) + 1;
@@ -270,7 +324,7 @@ std::tuple<Tensor, Tensor> gemm_norm(const Tensor& A, const Tensor& B, const opt
   a.A = A.data_ptr(); a.B = B.data_ptr(); a.lda = A.stride(0); a.ldb = B.stride(0);
   a.M = A.size(0); a.N = B.size(0); a.K = A.size(1);
   const int64_t n_out = glu_act >= 0 ? B.size(0) / 2 : B.size(0);
-  Tensor out = at::empty({A.size(0), n_out}, A.options());
+  Tensor out = out_empty({A.size(0), n_out}, A.options());
   a.out = out.data_ptr(); a.ldo = out.stride(0);
   if (residual.has_value() && residual->defined()) {
     TORCH_CHECK(residual->scalar_type() == at::kBFloat16 && residual->dim() == 2 && residual->size(0) == a.M &&
@@ -297,10 +351,10 @@ std::tuple<Tensor, Tensor> gemm_norm(const Tensor& A, const Tensor& B, const opt
   Tensor ss_out;
   if (want_ss) {
     TORCH_CHECK(glu_act < 0, "gemm_norm: no row statistics behind the GLU epilogue");
-    ss_out = at::empty({ferrl::gemm_ss_parts(a.N, bn, cluster), static_cast<long long>(a.M)}, A.options().dtype(at::kFloat));
+    ss_out = out_empty({ferrl::gemm_ss_parts(a.N, bn, cluster), static_cast<long long>(a.M)}, A.options().dtype(at::kFloat));
     a.ss_out = ss_out.data_ptr<float>(); a.ss_ld = a.M;
   } else {
-    ss_out = at::empty({0}, A.options().dtype(at::kFloat));
+    ss_out = out_empty({0}, A.options().dtype(at::kFloat));
   }
   if (a.M == 0) return {out, ss_out};
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
@@ -310,7 +364,7 @@ std::tuple<Tensor, Tensor> gemm_norm(const Tensor& A, const Tensor& B, const opt
 Tensor row_sumsq(const Tensor& x) {
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "row_sumsq: bf16 [M,H]");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor ss = at::empty({1, x.size(0)}, x.options().dtype(at::kFloat));
+  Tensor ss = out_empty({1, x.size(0)}, x.options().dtype(at::kFloat));
   FERRL_CHECK(ferrl::row_sumsq(x.data_ptr(), x.stride(0), ss.data_ptr<float>(), x.size(0), x.size(1), stream()));
   return ss;
 }
@@ -331,7 +385,7 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
     TORCH_CHECK(B2.has_value() && B2->defined() && A2->stride(1) == 1 && B2->stride(1) == 1, "gemm_allreduce: side operands");
     a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
   }
-  Tensor out = at::empty({a.M, a.N}, A.options());
+  Tensor out = out_empty({a.M, a.N}, A.options());
   a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = false;
   if (residual.has_value() && residual->defined()) { a.residual = residual->data_ptr(); a.ldr = residual->stride(0); }
   a.status = status_word(); a.num_sms = num_sms();
@@ -353,16 +407,16 @@ Tensor lora_grad(const Tensor& U, const Tensor& X) {
                   X.dim() == 2 && U.size(0) == X.size(0) && U.stride(1) == 1 && X.stride(1) == 1, "lora_grad: U [M,R], X [M,C] bf16");
   c10::cuda::CUDAGuard guard(U.device());
   const int64_t M = U.size(0), R = U.size(1), C = X.size(1);
-  Tensor out = at::empty({R, C}, U.options().dtype(at::kFloat));
+  Tensor out = out_empty({R, C}, U.options().dtype(at::kFloat));
   if (M == 0) return out.zero_();
   const int splits = ferrl::lora_grad_splits(M, C, num_sms());
-  Tensor partial = at::empty({static_cast<long long>(ferrl::lora_grad_workspace_floats(R, C, splits))}, out.options());
+  Tensor partial = out_empty({static_cast<long long>(ferrl::lora_grad_workspace_floats(R, C, splits))}, out.options());
   // per-device counters, zero between calls (the kernel resets the ones it used)
   static std::vector<Tensor> counters(64);
   const int dev = U.get_device();
   const int64_t tiles = (C + 127) / 128;
   if (!counters[dev].defined() || counters[dev].numel() < tiles)
-    counters[dev] = at::zeros({std::max<int64_t>(tiles, 4096)}, U.options().dtype(at::kInt));
+    counters[dev] = out_zeros({std::max<int64_t>(tiles, 4096)}, U.options().dtype(at::kInt));
   FERRL_CHECK(ferrl::lora_grad(U.data_ptr(), U.stride(0), R, X.data_ptr(), X.stride(0), C, M, splits,
                                partial.data_ptr<float>(), counters[dev].data_ptr<int>(), out.data_ptr<float>(), C, stream()));
   return out;
@@ -381,7 +435,7 @@ Tensor gdn_conv_fwd(const Tensor& x, const Tensor& w, const optional<Tensor>& le
                     left->size(1) == x.size(2) && left->size(2) == w.size(1) - 1, "gdn_conv_fwd: left bf16 [B,C,K-1]");
     lp = left->data_ptr();
   }
-  Tensor y = at::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  Tensor y = out_empty({x.size(0), x.size(1), x.size(2)}, x.options());
   FERRL_CHECK(ferrl::gdn_conv_fwd(x.data_ptr(), x.stride(1), w.data_ptr(), lp, x.size(0), x.size(1), x.size(2), w.size(1),
                                   act, y.data_ptr(), stream()));
   return y;
@@ -393,7 +447,7 @@ Tensor gdn_conv_bwd(const Tensor& x, const Tensor& w, const optional<Tensor>& le
               "gdn_conv_bwd: shapes");
   c10::cuda::CUDAGuard guard(x.device());
   const void* lp = (left.has_value() && left->defined()) ? left->data_ptr() : nullptr;
-  Tensor dx = at::empty({x.size(0), x.size(1), x.size(2)}, x.options());
+  Tensor dx = out_empty({x.size(0), x.size(1), x.size(2)}, x.options());
   FERRL_CHECK(ferrl::gdn_conv_bwd(x.data_ptr(), x.stride(1), w.data_ptr(), lp, dy.data_ptr(), x.size(0), x.size(1),
                                   x.size(2), w.size(1), act, dx.data_ptr(), stream()));
   return dx;
@@ -405,7 +459,7 @@ Tensor gdn_conv_step(const Tensor& x, const Tensor& w, Tensor state, bool act) {
   TORCH_CHECK(state.scalar_type() == at::kBFloat16 && state.is_contiguous() && state.size(0) == x.size(0) &&
                   state.size(1) == x.size(1) && state.size(2) == w.size(1) - 1 && w.is_contiguous(), "gdn_conv_step: state bf16 [B,C,K-1]");
   c10::cuda::CUDAGuard guard(x.device());
-  Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+  Tensor y = out_empty({x.size(0), x.size(1)}, x.options());
   FERRL_CHECK(ferrl::gdn_conv_step(x.data_ptr(), x.stride(0), w.data_ptr(), state.data_ptr(), x.size(0), x.size(1),
                                    w.size(1), act, y.data_ptr(), stream()));
   return y;
@@ -423,7 +477,7 @@ Tensor gdn_decode_step(const Tensor& q, const Tensor& k, const Tensor& v, const 
   TORCH_CHECK(g.scalar_type() == at::kFloat && beta.scalar_type() == at::kFloat && g.is_contiguous() && beta.is_contiguous() &&
                   g.numel() == B * Hv && beta.numel() == B * Hv, "gdn_decode_step: g,beta f32 [B,Hv]");
   c10::cuda::CUDAGuard guard(S.device());
-  Tensor out = at::empty({B, Hv, VD}, q.options());
+  Tensor out = out_empty({B, Hv, VD}, q.options());
   FERRL_CHECK(ferrl::gdn_decode_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
                                      g.data_ptr<float>(), beta.data_ptr<float>(), S.data_ptr<float>(), B, q.size(1) / KD,
                                      Hv, KD, VD, l2norm, static_cast<float>(eps), out.data_ptr(), stream()));
@@ -455,10 +509,10 @@ std::vector<Tensor> gdn_tc_fwd(const Tensor& q, const Tensor& k, const Tensor& v
   c10::cuda::CUDAGuard guard(q.device());
   const int64_t n = T / 64;
   auto opt = q.options();
-  Tensor out = at::empty({B, T, Hv, 128}, opt), S_out = at::empty({B, Hv, 128, 128}, opt);
-  Tensor Gc = at::empty({B, Hv, n, 64}, opt), gl = at::empty({B, Hv, n}, opt), Tm = at::empty({B, Hv, n, 64, 64}, opt);
-  Tensor U = at::empty({B, Hv, n, 64, 128}, opt), Wn = at::empty({B, Hv, n, 64, 128}, opt), Kd = at::empty({B, Hv, n, 64, 128}, opt);
-  Tensor Vn = at::empty({B, Hv, n, 64, 128}, opt), Sin = at::empty({B, Hv, n, 128, 128}, opt);
+  Tensor out = out_empty({B, T, Hv, 128}, opt), S_out = out_empty({B, Hv, 128, 128}, opt);
+  Tensor Gc = out_empty({B, Hv, n, 64}, opt), gl = out_empty({B, Hv, n}, opt), Tm = out_empty({B, Hv, n, 64, 64}, opt);
+  Tensor U = out_empty({B, Hv, n, 64, 128}, opt), Wn = out_empty({B, Hv, n, 64, 128}, opt), Kd = out_empty({B, Hv, n, 64, 128}, opt);
+  Tensor Vn = out_empty({B, Hv, n, 64, 128}, opt), Sin = out_empty({B, Hv, n, 128, 128}, opt);
   FERRL_CHECK(ferrl::gdn_tc_forward(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr<float>(),
                                     beta.data_ptr<float>(), s0, B, T, Hk, Hv, Gc.data_ptr<float>(), gl.data_ptr<float>(),
                                     Tm.data_ptr<float>(), U.data_ptr<float>(), Wn.data_ptr<float>(), Kd.data_ptr<float>(),
@@ -489,14 +543,16 @@ std::vector<Tensor> gdn_tc_bwd(const Tensor& q, const Tensor& k, const Tensor& v
   }
   c10::cuda::CUDAGuard guard(q.device());
   auto opt = q.options();
-  Tensor X0 = at::empty_like(Vn), Y0 = at::empty_like(Sin), dVn = at::empty_like(Vn), dSout = at::empty_like(Sin);
-  Tensor dq = at::empty({B, T, Hv, 128}, opt), dk = at::empty({B, T, Hv, 128}, opt), dv = at::empty_like(v);
-  Tensor dbeta = at::empty({B, T, Hv}, opt), dG = at::empty({B, T, Hv}, opt), dS0 = at::empty({B, Hv, 128, 128}, opt);
+  Tensor X0 = out_empty_like(Vn), Y0 = out_empty_like(Sin), dVn = out_empty_like(Vn), dSout = out_empty_like(Sin);
+  Tensor dW = out_empty_like(Vn), dGpart = out_empty({2, B, T, Hv}, opt);
+  Tensor dq = out_empty({B, T, Hv, 128}, opt), dk = out_empty({B, T, Hv, 128}, opt), dv = out_empty_like(v);
+  Tensor dbeta = out_empty({B, T, Hv}, opt), dG = out_empty({B, T, Hv}, opt), dS0 = out_empty({B, Hv, 128, 128}, opt);
   FERRL_CHECK(ferrl::gdn_tc_backward(q.data_ptr<float>(), k.data_ptr<float>(), v.data_ptr<float>(), beta.data_ptr<float>(),
                                      Gc.data_ptr<float>(), gl.data_ptr<float>(), Tm.data_ptr<float>(), Wn.data_ptr<float>(),
                                      Kd.data_ptr<float>(), Vn.data_ptr<float>(), Sin.data_ptr<float>(), dO.data_ptr<float>(), dsf,
                                      B, T, Hk, Hv, X0.data_ptr<float>(), Y0.data_ptr<float>(), dVn.data_ptr<float>(),
-                                     dSout.data_ptr<float>(), dq.data_ptr<float>(), dk.data_ptr<float>(), dv.data_ptr<float>(),
+                                     dSout.data_ptr<float>(), dW.data_ptr<float>(), dGpart.data_ptr<float>(), dq.data_ptr<float>(),
+                                     dk.data_ptr<float>(), dv.data_ptr<float>(),
                                      dbeta.data_ptr<float>(), dG.data_ptr<float>(), dS0.data_ptr<float>(), stream()));
   return {dq, dk, dv, dbeta, dG, dS0};
 }
@@ -518,8 +574,8 @@ std::tuple<Tensor, Tensor> gdn_chunk_fwd(const Tensor& q, const Tensor& k, const
     TORCH_CHECK(s0c.numel() == B * Hv * KD * VD, "gdn_chunk_fwd: state [B,Hv,KD,VD]");
     s0 = s0c.data_ptr<float>();
   }
-  Tensor out = at::empty({B, T, Hv, VD}, q.options());
-  Tensor S = at::empty({B, Hv, KD, VD}, q.options().dtype(at::kFloat));
+  Tensor out = out_empty({B, T, Hv, VD}, q.options());
+  Tensor S = out_empty({B, Hv, KD, VD}, q.options().dtype(at::kFloat));
   FERRL_CHECK(ferrl::gdn_chunk_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), q.stride(1), k.stride(0),
                                    k.stride(1), v.stride(0), v.stride(1), g.data_ptr<float>(), beta.data_ptr<float>(), s0,
                                    S.data_ptr<float>(), out.data_ptr(), B, T, Hk, Hv, KD, VD, l2norm,
@@ -533,10 +589,10 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> moe_route(const Tensor& logits, int64
   TORCH_CHECK(logits.is_cuda() && logits.scalar_type() == at::kFloat && logits.dim() == 2 && logits.stride(1) == 1, "moe_route: fp32 [T,E]");
   c10::cuda::CUDAGuard guard(logits.device());
   const int64_t T = logits.size(0), E = logits.size(1);
-  Tensor probs = at::empty({T, E}, logits.options());
-  Tensor scores = at::empty({T, k}, logits.options());
-  Tensor idx = at::empty({T, k}, logits.options().dtype(at::kInt));
-  Tensor counts = at::empty({E}, logits.options().dtype(at::kInt));
+  Tensor probs = out_empty({T, E}, logits.options());
+  Tensor scores = out_empty({T, k}, logits.options());
+  Tensor idx = out_empty({T, k}, logits.options().dtype(at::kInt));
+  Tensor counts = out_empty({E}, logits.options().dtype(at::kInt));
   FERRL_CHECK(ferrl::moe_route(logits.data_ptr<float>(), logits.stride(0), T, E, k, renorm, probs.data_ptr<float>(),
                                scores.data_ptr<float>(), idx.data_ptr<int>(), counts.data_ptr<int>(), stream()));
   return {probs, scores, idx, counts};
@@ -551,10 +607,10 @@ std::tuple<Tensor, Tensor, Tensor, Tensor> moe_plan(const Tensor& idx, const Ten
   // every expert may waste up to 127 rows of padding, but never more rows than tiles it could fill
   const int64_t max_rows = (pairs + std::min<int64_t>(E, pairs) * 127 + 127) / 128 * 128;
   auto io = idx.options();
-  Tensor row_of = at::empty({pairs}, io);
+  Tensor row_of = out_empty({pairs}, io);
   Tensor token_of = at::full({std::max<int64_t>(max_rows, 128)}, -1, io);
   Tensor tile_expert = at::full({std::max<int64_t>(max_rows / 128, 1)}, -1, io);
-  Tensor seg_start = at::zeros({E + 1}, io);
+  Tensor seg_start = out_zeros({E + 1}, io);
   FERRL_CHECK(ferrl::moe_plan(idx.data_ptr<int>(), counts.data_ptr<int>(), pairs, k, E, max_rows, row_of.data_ptr<int>(),
                               token_of.data_ptr<int>(), tile_expert.data_ptr<int>(), seg_start.data_ptr<int>(), stream()));
   return {row_of, token_of, tile_expert, seg_start};
@@ -565,12 +621,12 @@ Tensor moe_gather(const Tensor& x, const Tensor& token_of, const optional<Tensor
   TORCH_CHECK(x.is_cuda() && x.scalar_type() == at::kBFloat16 && x.dim() == 2 && x.stride(1) == 1, "moe_gather: bf16 [T,H]");
   c10::cuda::CUDAGuard guard(x.device());
   const int64_t rows = token_of.size(0), H = x.size(1);
-  Tensor xs = at::empty({rows, H}, x.options());
+  Tensor xs = out_empty({rows, H}, x.options());
   Tensor row_scale;
   const float* pw = nullptr;
   if (pair_w.has_value() && pair_w->defined()) {
     TORCH_CHECK(pair_w->scalar_type() == at::kFloat && pair_w->is_contiguous() && pair_w->numel() == row_of.numel(), "moe_gather: pair weights f32 [T*k]");
-    row_scale = at::zeros({rows}, x.options().dtype(at::kFloat));
+    row_scale = out_zeros({rows}, x.options().dtype(at::kFloat));
     pw = pair_w->data_ptr<float>();
   }
   FERRL_CHECK(ferrl::moe_gather(x.data_ptr(), x.stride(0), token_of.data_ptr<int>(), pw, row_of.data_ptr<int>(),
@@ -595,7 +651,7 @@ Tensor moe_grouped_gemm(const Tensor& xs, const Tensor& W, const Tensor& tile_ex
                     out_buf->size(0) == a.M && out_buf->size(1) == a.N, "moe_grouped_gemm: out buffer bf16 [R,N]");
     out = *out_buf;
   } else {
-    out = at::zeros({a.M, a.N}, xs.options());
+    out = out_zeros({a.M, a.N}, xs.options());
   }
   a.out = out.data_ptr(); a.ldo = a.N;
   a.status = status_word(); a.num_sms = num_sms();
@@ -648,7 +704,7 @@ Tensor ep_combine(std::vector<int64_t> ys, const Tensor& idx, const Tensor& dest
   p.flags = table_of_fwd(flags); p.epoch = static_cast<unsigned>(epoch);
   p.limit_ns = static_cast<unsigned long long>(limit_s * 1e9); p.status = status_word();
   p.abort_word = abort_word.data_ptr<int>();
-  Tensor out = at::empty({p.T, H}, idx.options().dtype(at::kBFloat16));
+  Tensor out = out_empty({p.T, H}, idx.options().dtype(at::kBFloat16));
   p.out = reinterpret_cast<__nv_bfloat16*>(out.data_ptr());
   if (keep_rows.has_value() && keep_rows->defined()) {
     TORCH_CHECK(keep_rows->scalar_type() == at::kBFloat16 && keep_rows->is_contiguous() && keep_rows->numel() == idx.numel() * H, "ep_combine: keep_rows bf16 [T*k,H]");
@@ -662,7 +718,7 @@ Tensor ep_combine(std::vector<int64_t> ys, const Tensor& idx, const Tensor& dest
 Tensor moe_combine(const Tensor& ys, const Tensor& row_of, const optional<Tensor>& w, int64_t T, int64_t k) {
   TORCH_CHECK(ys.is_cuda() && ys.scalar_type() == at::kBFloat16 && ys.is_contiguous() && row_of.numel() == T * k, "moe_combine: shapes");
   c10::cuda::CUDAGuard guard(ys.device());
-  Tensor out = at::empty({T, ys.size(1)}, ys.options());
+  Tensor out = out_empty({T, ys.size(1)}, ys.options());
   const float* wp = nullptr;
   if (w.has_value() && w->defined()) {
     TORCH_CHECK(w->scalar_type() == at::kFloat && w->is_contiguous() && w->numel() == T * k, "moe_combine: weights f32 [T,k]");
@@ -676,7 +732,7 @@ Tensor moe_combine(const Tensor& ys, const Tensor& row_of, const optional<Tensor
 Tensor moe_pair_dot(const Tensor& dy, const Tensor& ys, const Tensor& row_of, int64_t k) {
   TORCH_CHECK(dy.is_cuda() && dy.scalar_type() == at::kBFloat16 && dy.is_contiguous() && ys.is_contiguous() && dy.size(1) == ys.size(1), "moe_pair_dot: shapes");
   c10::cuda::CUDAGuard guard(dy.device());
-  Tensor dw = at::empty({dy.size(0), k}, dy.options().dtype(at::kFloat));
+  Tensor dw = out_empty({dy.size(0), k}, dy.options().dtype(at::kFloat));
   FERRL_CHECK(ferrl::moe_pair_dot(dy.data_ptr(), ys.data_ptr(), row_of.data_ptr<int>(), row_of.numel(), k, dy.size(1),
                                   dw.data_ptr<float>(), stream()));
   return dw;
@@ -688,11 +744,11 @@ std::tuple<Tensor, Tensor> rmsnorm(const Tensor& x, const optional<Tensor>& res,
   c10::cuda::CUDAGuard guard(x.device());
   const int H = x.size(-1);
   const long long rows = x.numel() / H;
-  Tensor y = at::empty_like(x);
+  Tensor y = out_empty_like(x);
   Tensor h;
   if (res.has_value() && res->defined()) {
     TORCH_CHECK(res->is_contiguous() && res->sizes() == x.sizes() && res->scalar_type() == x.scalar_type(), "rmsnorm: residual");
-    h = at::empty_like(x);
+    h = out_empty_like(x);
   }
   if (w.has_value() && w->defined()) TORCH_CHECK(w->scalar_type() == x.scalar_type() && w->numel() == H && w->is_contiguous(), "rmsnorm: weight");
   if (gate.has_value() && gate->defined()) TORCH_CHECK(gate->is_contiguous() && gate->sizes() == x.sizes() && gate->scalar_type() == x.scalar_type(), "rmsnorm: gate");
@@ -706,7 +762,7 @@ Tensor rmsnorm_bwd(const Tensor& x, const optional<Tensor>& w, const Tensor& dy,
                   dy.scalar_type() == x.scalar_type(), "rmsnorm_bwd: shapes");
   c10::cuda::CUDAGuard guard(x.device());
   const int H = x.size(-1);
-  Tensor dx = at::empty_like(x);
+  Tensor dx = out_empty_like(x);
   FERRL_CHECK(ferrl::rmsnorm_bwd(dt(x), x.data_ptr(), optr(w), dy.data_ptr(), dx.data_ptr(), x.numel() / H, H,
                                  static_cast<float>(eps), zc, stream()));
   return dx;
@@ -719,7 +775,7 @@ std::tuple<Tensor, Tensor> rmsnorm_gated_bwd(const Tensor& x, const Tensor& gate
               "rmsnorm_gated_bwd: x, gate, dy of one shape and dtype, w [H]");
   c10::cuda::CUDAGuard guard(x.device());
   const int H = x.size(-1);
-  Tensor dx = at::empty_like(x), dg = at::empty_like(x);
+  Tensor dx = out_empty_like(x), dg = out_empty_like(x);
   FERRL_CHECK(ferrl::rmsnorm_gated_bwd(dt(x), x.data_ptr(), gate.data_ptr(), w.data_ptr(), dy.data_ptr(), dx.data_ptr(),
                                        dg.data_ptr(), x.numel() / H, H, static_cast<float>(eps), stream()));
   return {dx, dg};
@@ -755,8 +811,8 @@ std::tuple<Tensor, Tensor> qk_norm_rope_fwd(const Tensor& q, const Tensor& k, co
   c10::cuda::CUDAGuard guard(q.device());
   ferrl::QkNormRopeArgs a{};
   fill_qknr(a, q, k, qw, kw, cos_t, sin_t, pos, pos_div, eps, zc);
-  Tensor qo = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
-  Tensor ko = at::empty({k.size(0), k.size(1), k.size(2)}, k.options());
+  Tensor qo = out_empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor ko = out_empty({k.size(0), k.size(1), k.size(2)}, k.options());
   a.backward = false; a.q_out = qo.data_ptr(); a.k_out = ko.data_ptr();
   FERRL_CHECK(ferrl::qk_norm_rope(a, stream()));
   return {qo, ko};
@@ -775,7 +831,7 @@ Tensor qk_norm_rope_append(const Tensor& q, const Tensor& k, const Tensor& v, co
                   kc.dim() == 4 && kc.sizes() == vc.sizes() && kc.size(2) == k.size(1) && kc.size(3) == k.size(2) &&
                   kv_len.scalar_type() == at::kInt && kv_len.is_contiguous() && kv_len.numel() == q.size(0),
               "qk_norm_rope_append: layout");
-  Tensor qo = at::empty({q.size(0), q.size(1), q.size(2)}, q.options());
+  Tensor qo = out_empty({q.size(0), q.size(1), q.size(2)}, q.options());
   a.backward = false; a.q_out = qo.data_ptr(); a.k_out = nullptr;
   a.kc = kc.data_ptr(); a.vc = vc.data_ptr(); a.v_in = v.data_ptr(); a.ld_v = v.stride(0);
   a.kv_len = kv_len.data_ptr<int>();
@@ -833,7 +889,7 @@ Tensor glu_fwd(const Tensor& gu, int64_t act) {
   const int F = gu.size(-1) / 2;
   auto sizes = gu.sizes().vec();
   sizes.back() = F;
-  Tensor out = at::empty(sizes, gu.options());
+  Tensor out = out_empty(sizes, gu.options());
   FERRL_CHECK(ferrl::glu(dt(gu), false, gu.data_ptr(), nullptr, out.data_ptr(), gu.numel() / (2 * F), F, act, stream()));
   return out;
 }
@@ -842,7 +898,7 @@ Tensor glu_bwd(const Tensor& gu, const Tensor& dout, int64_t act) {
   TORCH_CHECK(gu.is_contiguous() && dout.is_contiguous(), "glu_bwd: contiguous");
   c10::cuda::CUDAGuard guard(gu.device());
   const int F = gu.size(-1) / 2;
-  Tensor dgu = at::empty_like(gu);
+  Tensor dgu = out_empty_like(gu);
   FERRL_CHECK(ferrl::glu(dt(gu), true, gu.data_ptr(), dout.data_ptr(), dgu.data_ptr(), gu.numel() / (2 * F), F, act, stream()));
   return dgu;
 }
@@ -853,7 +909,7 @@ Tensor embedding(const Tensor& ids, const Tensor& table, double scale) {
   Tensor idc = ids.contiguous();
   auto sizes = idc.sizes().vec();
   sizes.push_back(table.size(1));
-  Tensor out = at::empty(sizes, table.options());
+  Tensor out = out_empty(sizes, table.options());
   FERRL_CHECK(ferrl::embedding(dt(table), reinterpret_cast<long long*>(idc.data_ptr<int64_t>()), table.data_ptr(), out.data_ptr(), idc.numel(),
                                table.size(1), table.size(0), static_cast<float>(scale), stream()));
   return out;
@@ -864,7 +920,7 @@ Tensor lora_merge(const Tensor& w, const Tensor& a, const Tensor& b) {
                   b.scalar_type() == at::kFloat && a.size(1) == w.size(1) && b.size(0) == w.size(0) &&
                   a.size(0) == b.size(1), "lora_merge: shapes");
   c10::cuda::CUDAGuard guard(w.device());
-  Tensor out = at::empty_like(w);
+  Tensor out = out_empty_like(w);
   FERRL_CHECK(ferrl::lora_merge(dt(w), w.data_ptr(), a.data_ptr<float>(), b.data_ptr<float>(), out.data_ptr(),
                                 w.size(0), w.size(1), a.size(0), stream()));
   return out;
@@ -877,7 +933,7 @@ Tensor adamw_step(std::vector<Tensor> params, std::vector<Tensor> grads, std::ve
                   double pre_scale, bool compute_norm) {
   const size_t n = params.size();
   TORCH_CHECK(grads.size() == n && m.size() == n && v.size() == n, "adamw: list sizes");
-  Tensor norm = at::zeros({1}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, c10::cuda::current_device()));
+  Tensor norm = out_zeros({1}, at::TensorOptions().dtype(at::kFloat).device(at::kCUDA, c10::cuda::current_device()));
   if (n == 0) return norm;
   c10::cuda::CUDAGuard guard(params[0].device());
   const int chunk = 1 << 16;
@@ -897,12 +953,12 @@ Tensor adamw_step(std::vector<Tensor> params, std::vector<Tensor> grads, std::ve
   }
   const size_t tab_b = n * sizeof(ferrl::AdamTensor), bt_b = blk_t.size() * sizeof(int), bo_b = blk_o.size() * sizeof(long long);
   const size_t off1 = (tab_b + 15) & ~size_t(15), off2 = (off1 + bt_b + 15) & ~size_t(15), total = off2 + bo_b + 16;
-  Tensor host = at::empty({static_cast<long long>(total)}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
+  Tensor host = out_empty({static_cast<long long>(total)}, at::TensorOptions().dtype(at::kByte).pinned_memory(true));
   memcpy(host.data_ptr<uint8_t>(), tab.data(), tab_b);
   memcpy(host.data_ptr<uint8_t>() + off1, blk_t.data(), bt_b);
   memcpy(host.data_ptr<uint8_t>() + off2, blk_o.data(), bo_b);
   Tensor dev = host.to(params[0].device(), /*non_blocking=*/true);
-  Tensor sumsq = at::zeros({1}, norm.options().dtype(at::kDouble));
+  Tensor sumsq = out_zeros({1}, norm.options().dtype(at::kDouble));
   uint8_t* d = dev.data_ptr<uint8_t>();
   const float bc1 = 1.f / (1.f - static_cast<float>(std::pow(b1, static_cast<double>(step))));
   const float bc2 = 1.f / (1.f - static_cast<float>(std::pow(b2, static_cast<double>(step))));
@@ -922,8 +978,8 @@ std::tuple<Tensor, Tensor, Tensor> grpo_loss_rows(const Tensor& logp, const Tens
                   mask.is_contiguous() && adv.is_contiguous() && logp.dim() == 2, "grpo_loss: float32 [G,L] tensors");
   c10::cuda::CUDAGuard guard(logp.device());
   const int G = logp.size(0), L = logp.size(1);
-  Tensor row_sum = at::empty({G}, logp.options()), row_cnt = at::empty({G}, logp.options());
-  Tensor dl = want_grad ? at::empty_like(logp) : Tensor();
+  Tensor row_sum = out_empty({G}, logp.options()), row_cnt = out_empty({G}, logp.options());
+  Tensor dl = want_grad ? out_empty_like(logp) : Tensor();
   int mode = (seq_level ? 1 : 0) | (logp_ref.has_value() && logp_ref->defined() ? 2 : 0) |
              (tis.has_value() && tis->defined() ? 4 : 0);
   FERRL_CHECK(ferrl::grpo_loss_rows(logp.data_ptr<float>(), logp_old.data_ptr<float>(),
@@ -956,7 +1012,7 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
   }
   a.scale = scale; a.window = window;
   a.n_splits = n_splits > 0 ? n_splits : ferrl::decode_attn_pick_splits(a.B, a.Hkv, kc.size(1), num_sms());
-  Tensor out = at::empty_like(q);
+  Tensor out = out_empty_like(q);
   Tensor ws;
   if (prefix_len.has_value() && prefix_len->defined()) {
     TORCH_CHECK(prefix_len->scalar_type() == at::kInt && prefix_len->is_contiguous() && group >= 1 &&
@@ -964,10 +1020,10 @@ Tensor decode_attn(const Tensor& q, const Tensor& kc, const Tensor& vc, const Te
     a.prefix_len = prefix_len->data_ptr<int>(); a.group = static_cast<int>(group);
     a.prefix_splits = static_cast<int>(prefix_splits);
     a.n_splits = 1;
-    ws = at::empty({static_cast<long long>(a.B) * a.Hq * a.prefix_splits * (a.D + 2)}, q.options().dtype(at::kFloat));
+    ws = out_empty({static_cast<long long>(a.B) * a.Hq * a.prefix_splits * (a.D + 2)}, q.options().dtype(at::kFloat));
     a.workspace = ws.data_ptr<float>();
   } else if (a.n_splits > 1) {
-    ws = at::empty({static_cast<long long>(ferrl::decode_attn_workspace_bytes(a.B, a.Hq, a.D, a.n_splits) / 4)},
+    ws = out_empty({static_cast<long long>(ferrl::decode_attn_workspace_bytes(a.B, a.Hq, a.D, a.n_splits) / 4)},
                    q.options().dtype(at::kFloat));
     a.workspace = ws.data_ptr<float>();
   }
@@ -998,11 +1054,11 @@ std::tuple<Tensor, Tensor> flash_fwd(const Tensor& q, const Tensor& k, const Ten
   c10::cuda::CUDAGuard guard(q.device());
   ferrl::FlashArgs a{};
   fill_flash(a, q, k, v, scale, causal, window, q_offset);
-  Tensor o = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
-  Tensor lse = at::empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
+  Tensor o = out_empty({a.B, a.Sq, a.Hq, a.D}, q.options());
+  Tensor lse = out_empty({a.B, a.Hq, a.Sq}, q.options().dtype(at::kFloat));
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
   if ((variant == 0 || variant == 2 || variant == 3) && ferrl::flash_fwd_tc_supported(a)) {
-    Tensor vt = at::empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
+    Tensor vt = out_empty({static_cast<long long>(ferrl::flash_fwd_tc_workspace_elems(a))}, q.options());
     // variant 0: output and P in TMEM (default); 3: output in TMEM, P through shared memory; 2: first form (output in registers)
     FERRL_CHECK(ferrl::flash_fwd_tc(a, vt.data_ptr(), status_word(), stream(), variant == 0 ? 2 : (variant == 3 ? 1 : 0)));
     return {o, lse};
@@ -1019,10 +1075,10 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   ferrl::FlashArgs a{};
   fill_flash(a, q, k, v, scale, causal, window, q_offset);
   TORCH_CHECK(o.is_contiguous() && d_o.is_contiguous() && lse.is_contiguous(), "flash_bwd: o, do, lse contiguous");
-  Tensor dq = at::empty({a.B, a.Sq, a.Hq, a.D}, q.options());
-  Tensor dk = at::empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
-  Tensor dv = at::empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
-  Tensor delta = at::empty({a.B, a.Hq, a.Sq}, lse.options());
+  Tensor dq = out_empty({a.B, a.Sq, a.Hq, a.D}, q.options());
+  Tensor dk = out_empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
+  Tensor dv = out_empty({a.B, a.Sk, a.Hkv, a.D}, q.options());
+  Tensor delta = out_empty({a.B, a.Hq, a.Sq}, lse.options());
   a.o = o.data_ptr(); a.o_bs = o.stride(0); a.o_ts = o.stride(1); a.lse = lse.data_ptr<float>();
   a.d_o = d_o.data_ptr(); a.do_bs = d_o.stride(0); a.do_ts = d_o.stride(1);
   a.dq = dq.data_ptr(); a.dq_bs = dq.stride(0); a.dq_ts = dq.stride(1);
@@ -1035,7 +1091,7 @@ std::tuple<Tensor, Tensor, Tensor> flash_bwd(const Tensor& q, const Tensor& k, c
   }
   // variant 0: tcgen05 kernels where they apply; 1: warp-level kernels
   if (variant != 1 && ferrl::flash_bwd_tc_supported(a)) {
-    Tensor stats = at::empty({static_cast<long long>(ferrl::flash_bwd_tc_scratch_floats(a))}, lse.options());
+    Tensor stats = out_empty({static_cast<long long>(ferrl::flash_bwd_tc_scratch_floats(a))}, lse.options());
     a.delta = stats.data_ptr<float>();
     FERRL_CHECK(ferrl::flash_bwd_tc(a, status_word(), stream()));
     return {dq, dk, dv};
@@ -1069,8 +1125,8 @@ std::tuple<Tensor, Tensor> logprob_head_fwd(const Tensor& hidden, const Tensor& 
   c10::cuda::CUDAGuard guard(hidden.device());
   const int n_tiles = (a.N + 255) / 256;
   auto f32 = hidden.options().dtype(at::kFloat);
-  Tensor ws = at::empty({n_tiles, a.M, 2}, f32), tl = at::zeros({a.M}, f32);
-  Tensor lp = at::empty({a.M}, f32), lse = at::empty({a.M}, f32);
+  Tensor ws = out_empty({n_tiles, a.M, 2}, f32), tl = out_zeros({a.M}, f32);
+  Tensor lp = out_empty({a.M}, f32), lse = out_empty({a.M}, f32);
   if (a.M == 0) return {lp, lse};
   a.lp_mode = 1; a.lp_ws = ws.data_ptr<float>(); a.lp_tl = tl.data_ptr<float>(); a.ldo = a.N;
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
@@ -1089,7 +1145,7 @@ Tensor logprob_head_dlogits(const Tensor& hidden, const Tensor& w, const Tensor&
   TORCH_CHECK(lse.scalar_type() == at::kFloat && coef.scalar_type() == at::kFloat && lse.is_contiguous() && coef.is_contiguous() &&
                   lse.numel() == a.M && coef.numel() == a.M, "logprob_head_dlogits: lse, coef fp32 [M]");
   c10::cuda::CUDAGuard guard(hidden.device());
-  Tensor out = at::empty({a.M, a.N}, hidden.options());
+  Tensor out = out_empty({a.M, a.N}, hidden.options());
   if (a.M == 0) return out;
   a.lp_mode = 2; a.lp_lse = lse.data_ptr<float>(); a.lp_coef = coef.data_ptr<float>(); a.lp_col0 = col0;
   a.out = out.data_ptr(); a.ldo = a.N;
@@ -1101,7 +1157,7 @@ std::tuple<Tensor, Tensor> logprob_rows(const Tensor& logits, const Tensor& targ
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && targets.scalar_type() == at::kLong &&
                   targets.is_contiguous() && targets.numel() == logits.size(0), "logprob_rows: args");
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor lp = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat)), lse = at::empty_like(lp);
+  Tensor lp = out_empty({logits.size(0)}, logits.options().dtype(at::kFloat)), lse = out_empty_like(lp);
   FERRL_CHECK(ferrl::logprob_rows(dt(logits), logits.data_ptr(), logits.stride(0), reinterpret_cast<long long*>(targets.data_ptr<int64_t>()),
                                   lp.data_ptr<float>(), lse.data_ptr<float>(), logits.size(0), logits.size(1),
                                   temperature, softcap, stream()));
@@ -1122,8 +1178,8 @@ std::tuple<Tensor, Tensor> sample_rows(const Tensor& logits, const Tensor& globa
   TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1 && global_rows.scalar_type() == at::kLong &&
                   global_rows.is_contiguous() && global_rows.numel() == logits.size(0), "sample_rows: args");
   c10::cuda::CUDAGuard guard(logits.device());
-  Tensor tok = at::empty({logits.size(0)}, logits.options().dtype(at::kLong));
-  Tensor lp = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  Tensor tok = out_empty({logits.size(0)}, logits.options().dtype(at::kLong));
+  Tensor lp = out_empty({logits.size(0)}, logits.options().dtype(at::kFloat));
   const int* dd = nullptr;
   if (draw_dev.has_value() && draw_dev->defined()) {
     TORCH_CHECK(draw_dev->scalar_type() == at::kInt, "sample_rows: draw counter int32");
@@ -1148,7 +1204,7 @@ Tensor symm_alloc(int64_t nbytes) {
 Tensor symm_handle(const Tensor& buf) {
   cudaIpcMemHandle_t h;
   C10_CUDA_CHECK(cudaIpcGetMemHandle(&h, buf.data_ptr()));
-  Tensor out = at::empty({static_cast<long long>(sizeof(h))}, at::TensorOptions().dtype(at::kByte));
+  Tensor out = out_empty({static_cast<long long>(sizeof(h))}, at::TensorOptions().dtype(at::kByte));
   memcpy(out.data_ptr(), &h, sizeof(h));
   return out;
 }
@@ -1215,7 +1271,7 @@ std::tuple<Tensor, int64_t, int64_t, int64_t, int64_t> dp_tables(std::vector<Ten
   }
   auto al = [](size_t x) { return (x + 15) & ~size_t(15); };
   size_t o1 = al(n * sizeof(ferrl::AdamTensor)), o2 = al(o1 + bt.size() * 4), o3 = al(o2 + bo.size() * 8), tot = o3 + bf.size() * 8 + 16;
-  Tensor host = at::empty({static_cast<long long>(tot)}, at::TensorOptions().dtype(at::kByte));
+  Tensor host = out_empty({static_cast<long long>(tot)}, at::TensorOptions().dtype(at::kByte));
   uint8_t* h = host.data_ptr<uint8_t>();
   memcpy(h, tab.data(), n * sizeof(ferrl::AdamTensor));
   memcpy(h + o1, bt.data(), bt.size() * 4);
@@ -1248,6 +1304,8 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);
   m.def("gdn_conv_step(Tensor x, Tensor w, Tensor(a!) state, bool act) -> Tensor", &gdn_conv_step);
   m.def("gdn_chunk_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0, bool l2norm, float eps) -> (Tensor, Tensor)", &gdn_chunk_fwd);
+  m.def("set_canary(bool on) -> ()", &set_canary);
+  m.def("check_canaries() -> int", &check_canaries);
   m.def("rmsnorm_gated_bwd(Tensor x, Tensor gate, Tensor w, Tensor dy, float eps) -> (Tensor, Tensor)", &rmsnorm_gated_bwd);
   m.def("gdn_tc_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0) -> Tensor[]", &gdn_tc_fwd);
   m.def("gdn_tc_bwd(Tensor q, Tensor k, Tensor v, Tensor beta, Tensor Gc, Tensor gl, Tensor Tm, Tensor Wn, Tensor Kd, Tensor Vn, Tensor Sin, Tensor dO, Tensor? dS_final) -> Tensor[]", &gdn_tc_bwd);

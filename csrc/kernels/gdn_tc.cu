@@ -22,8 +22,9 @@
 //   gdn_out_kernel        O of a chunk from its saved entering state
 //   gdn_bwd_prep_kernel   X0 = P^T dO and Y0 = (gamma Q)^T dO
 //   gdn_scan_kernel<bwd>  chunks in reverse: dVn = X0 + Kd dS', dS = gamma_C dS' + Y0 + Wn^T dVn
-//   gdn_chunk_bwd_kernel  everything that does not cross chunks: dq, dk, dv, dbeta and dG (the caller turns
-//                         dG into dg with a reverse cumulative sum inside each chunk)
+//   gdn_bwd_state_kernel  the chunk-local products with the saved states: dW, the state parts of dq, dk and dG
+//   gdn_bwd_intra_kernel  everything else inside a chunk: dq, dk, dv, dbeta and dG (the caller turns dG into dg
+//                         with a reverse cumulative sum inside each chunk)
 #include <cuda_runtime.h>
 #include <mma.h>
 #include <stdint.h>
@@ -163,24 +164,32 @@ __device__ __forceinline__ void tile_mma(wm::fragment<wm::accumulator, 16, 16, 8
 
 // ---------------------------------------------------------------------------------------------
 // prep: per chunk G, T, U, Wn = -W, Kd = diag(exp(G_C - G)) K and gl = G_C.
-// Shared: three [64, 64] matrices and two vectors.
-__global__ void __launch_bounds__(256)
+// T = (I + A)^-1 with A strictly lower triangular: column c of T depends on A and on that column's own
+// earlier rows only, so thread c solves its column in registers (fully unrolled, four partial sums per row
+// to shorten the dependent chain) with no synchronisation at all.
+// Shared: A / scaled T [64, 68], T [64, 68], K [64, 132], V [64, 136], two vectors.
+constexpr size_t kPrepSmem = (2 * GC * (GC + 4) + GC * (GD + 4) + GC * (GD + 8) + 2 * GC) * sizeof(float);
+
+__global__ void __launch_bounds__(256, 2)
 gdn_prep_kernel(const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ g,
                 const float* __restrict__ beta, GdnDims d, float* __restrict__ Gc, float* __restrict__ gl,
                 float* __restrict__ Tm, float* __restrict__ U, float* __restrict__ Wn, float* __restrict__ Kd) {
+  constexpr int LY = GC + 4;
   extern __shared__ __align__(128) float sm[];
-  float* Y1 = sm;                  // K K^T, then A
-  float* Y2 = Y1 + GC * GC;        // T
-  float* Y3 = Y2 + GC * GC;        // T diag(beta), then -T diag(gamma beta)
-  float* Gs = Y3 + GC * GC;
+  float* Y1 = sm;                  // K K^T, then A, then T diag(beta), then -T diag(gamma beta)
+  float* Y2 = Y1 + GC * LY;        // T
+  float* Ks = Y2 + GC * LY;        // [64, 132]
+  float* Vs = Ks + GC * LD4;       // [64, 136]
+  float* Gs = Vs + GC * LD8;
   float* bs = Gs + GC;
   const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
   const int hk = hv / (d.Hv / d.Hk);
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5;
   const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
-  const float* kg = k + qk_off(d, b, c * GC, hk);
-  const float* vg = v + v_off(d, b, c * GC, hv);
   const long long co = ch_off(d, b, hv, c);
+  tile_async(Ks, LD4, k + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(Vs, LD8, v + v_off(d, b, c * GC, hv), ldv, GC, GD);
+  cp_async_commit();
   if (tid < GC) bs[tid] = beta[(static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv];
   if (tid < 32) {                  // inclusive scan of 64 log decays by one warp
     const long long o = (static_cast<long long>(b) * d.T + c * GC) * d.Hv + hv;
@@ -194,47 +203,79 @@ gdn_prep_kernel(const float* __restrict__ k, const float* __restrict__ v, const 
     Gs[2 * tid + 1] = sum;
     Gs[2 * tid] = sum - a1;
   }
-  mm<false, true, false>(Y1, GC, kg, ldk, kg, ldk, GC, GC, GD);
+  cp_async_wait_all();
+  __syncthreads();
+  for (int t = warp; t < 16; t += 8) {                 // K K^T
+    const int ti = t >> 2, tj = t & 3;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GD, false, true>(acc, Ks + ti * 16 * LD4, LD4, Ks + tj * 16 * LD4, LD4);
+    wm::store_matrix_sync(Y1 + ti * 16 * LY + tj * 16, acc, LY, wm::mem_row_major);
+  }
   __syncthreads();
   const float glast = Gs[GC - 1];
   for (int e = tid; e < GC * GC; e += 256) {
     const int i = e / GC, j = e - i * GC;
-    Y1[e] = (i > j) ? bs[i] * Y1[e] * __expf(Gs[i] - Gs[j]) : 0.f;
-    Y2[e] = (i == j) ? 1.f : 0.f;
+    Y1[i * LY + j] = (i > j) ? bs[i] * Y1[i * LY + j] * __expf(Gs[i] - Gs[j]) : 0.f;
   }
-  // Kd = diag(exp(G_C - G)) K, straight from global to global
+  // Kd = diag(exp(G_C - G)) K
   for (int e = tid; e < GC * GD / 4; e += 256) {
     const int i = e / (GD / 4), x = e - i * (GD / 4);
-    float4 t = reinterpret_cast<const float4*>(kg + i * ldk)[x];
+    const float4 t = *reinterpret_cast<const float4*>(Ks + i * LD4 + x * 4);
     const float f = __expf(glast - Gs[i]);
     reinterpret_cast<float4*>(Kd + co * GC * GD)[e] = make_float4(t.x * f, t.y * f, t.z * f, t.w * f);
   }
   __syncthreads();
-  // T = (I + A)^-1 by forward substitution: row i of T is e_i - sum_{j<i} A[i][j] T[j][:]
-  for (int i = 1; i < GC; ++i) {
-    if (tid < GC) {
-      float acc = (tid == i) ? 1.f : 0.f;
-      for (int j = 0; j < i; ++j) acc -= Y1[i * GC + j] * Y2[j * GC + tid];
-      Y2[i * GC + tid] = acc;
+  if (tid < GC) {
+    // column tid of T: t[i] = [i == tid] - sum_{j<i} A[i][j] t[j]; rows above the diagonal stay zero
+    float t[GC];
+#pragma unroll
+    for (int i = 0; i < GC; ++i) {
+      float a0 = (i == tid) ? 1.f : 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+      for (int j = 0; j + 3 < i; j += 4) {
+        const float4 a = *reinterpret_cast<const float4*>(Y1 + i * LY + j);
+        a0 -= a.x * t[j];
+        a1 -= a.y * t[j + 1];
+        a2 -= a.z * t[j + 2];
+        a3 -= a.w * t[j + 3];
+      }
+#pragma unroll
+      for (int j = i & ~3; j < i; ++j) a0 -= Y1[i * LY + j] * t[j];
+      t[i] = (a0 + a1) + (a2 + a3);
+      Y2[i * LY + tid] = t[i];
     }
-    __syncthreads();
   }
+  __syncthreads();
   for (int e = tid; e < GC * GC; e += 256) {
-    const int j = e % GC;
-    Tm[co * GC * GC + e] = Y2[e];
-    Y3[e] = Y2[e] * bs[j];
+    const int i = e / GC, j = e - i * GC;
+    const float tv = Y2[i * LY + j];
+    Tm[co * GC * GC + e] = tv;
+    Y1[i * LY + j] = tv * bs[j];
   }
   if (tid < GC) Gc[co * GC + tid] = Gs[tid];
   if (tid == 0) gl[co] = glast;
   __syncthreads();
-  mm<false, false, false>(U + co * GC * GD, GD, Y3, GC, vg, ldv, GC, GD, GC);
-  __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
-    const int j = e % GC;
-    Y3[e] = -Y2[e] * bs[j] * __expf(Gs[j]);
+  for (int t = warp; t < 32; t += 8) {                 // U = T diag(beta) V
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, false, false>(acc, Y1 + ti * 16 * LY, LY, Vs + tj * 16, LD8);
+    wm::store_matrix_sync(U + co * GC * GD + ti * 16 * GD + tj * 16, acc, GD, wm::mem_row_major);
   }
   __syncthreads();
-  mm<false, false, false>(Wn + co * GC * GD, GD, Y3, GC, kg, ldk, GC, GD, GC);
+  for (int e = tid; e < GC * GC; e += 256) {
+    const int i = e / GC, j = e - i * GC;
+    Y1[i * LY + j] = -Y2[i * LY + j] * bs[j] * __expf(Gs[j]);
+  }
+  __syncthreads();
+  for (int t = warp; t < 32; t += 8) {                 // Wn = -T diag(gamma beta) K
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, false, false>(acc, Y1 + ti * 16 * LY, LY, Ks + tj * 16, LD4);
+    wm::store_matrix_sync(Wn + co * GC * GD + ti * 16 * GD + tj * 16, acc, GD, wm::mem_row_major);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -323,7 +364,7 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
     // R = g R (+ R0) + A2^T V    [128, DV], K = 64
     const float eg = __expf(gls[c]);
     const bool last = i + 1 == n;
-    float* rdst = last ? Rfinal : Rchunks + (cbase + c + step) * GD * GD;
+    float* rdst = last ? (Rfinal ? Rfinal + bh * GD * GD : nullptr) : Rchunks + (cbase + c + step) * GD * GD;
     for (int t = warp; t < (GD / 16) * TN; t += 8) {
       const int ti = t / TN, tj = t - ti * TN;
       wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
@@ -464,188 +505,302 @@ gdn_bwd_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, co
 }
 
 // ---------------------------------------------------------------------------------------------
-// everything of the backward that stays inside a chunk.  Shared: E1, E2, E3 [64,128]; Y1, Y2, Y3
-// [64,64]; vectors.  Operands that are plain inputs (q, k, v, dO, Vn, dVn, T, Sin, dSout) are read
-// by the tensor-core loads straight from global memory.
+// Backward, the part of a chunk that touches the states.  One CTA per (chunk, half of the key dims):
+//   E1 = dO Sin^T    -> dq  = gamma o E1          (the chunk kernel adds (dP o D) K),  dG += gamma <Q, E1>
+//   dW = -dVn Sin^T  -> global
+//   E2 = Vn dS'^T    -> dk  = (gamma_C / gamma) o E2 (the chunk kernel adds the rest), R = <K, that>:
+//                       dG -= R, dG[last] += sum R;   dG[last] += gamma_C <Sin, dS'>
+// Shared: one half state [64 key dims, 132], one [64, 132] operand tile, one [64, 68] result, vectors.
+constexpr size_t kBwdStateSmem = (2 * GC * LD4 + GC * LP + 3 * GC + 32) * sizeof(float);
 
-__global__ void __launch_bounds__(256, 1)
-gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
-                     const float* __restrict__ beta, const float* __restrict__ Gc, const float* __restrict__ Tm,
+__global__ void __launch_bounds__(256, 2)
+gdn_bwd_state_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
                      const float* __restrict__ Vn, const float* __restrict__ dVn, const float* __restrict__ Sin,
                      const float* __restrict__ dSout, const float* __restrict__ dO, GdnDims d, float* __restrict__ dq,
-                     float* __restrict__ dk, float* __restrict__ dv, float* __restrict__ dbeta, float* __restrict__ dG) {
+                     float* __restrict__ dk, float* __restrict__ dW, float* __restrict__ dGpart) {
   extern __shared__ __align__(128) float sm[];
-  float* E1 = sm;
-  float* E2 = E1 + GC * GD;
-  float* E3 = E2 + GC * GD;
-  float* Y1 = E3 + GC * GD;
-  float* Y2 = Y1 + GC * GC;
-  float* Y3 = Y2 + GC * GC;
-  float* Gs = Y3 + GC * GC;       // [64]
-  float* bs = Gs + GC;            // [64]
-  float* dGs = bs + GC;           // [64] accumulates dG
-  float* dbs = dGs + GC;          // [64] accumulates dbeta
-  float* Rv = dbs + GC;           // [64]
-  float* red = Rv + GC;           // [32]
-  const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  float* Sh = sm;                    // [64, LD4] rows = key dims of this half, cols = value dims
+  float* X = Sh + GC * LD4;          // [64, LD4] dO, then dVn, then Vn
+  float* E = X + GC * LD4;           // [64, LP]
+  float* Gs = E + GC * LP;
+  float* dGs = Gs + GC;
+  float* Rv = dGs + GC;
+  float* red = Rv + GC;
+  const int c = blockIdx.x >> 1, half = blockIdx.x & 1, hv = blockIdx.y, b = blockIdx.z;
   const int hk = hv / (d.Hv / d.Hk);
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
   const long long co = ch_off(d, b, hv, c);
-  const float* qg = q + qk_off(d, b, c * GC, hk);
-  const float* kg = k + qk_off(d, b, c * GC, hk);
-  const float* vg = v + v_off(d, b, c * GC, hv);
-  const float* og = dO + v_off(d, b, c * GC, hv);
-  const float* Tg = Tm + co * GC * GC;
-  const float* Vng = Vn + co * GC * GD;
-  const float* dVng = dVn + co * GC * GD;
-  const float* Sg = Sin + co * GD * GD;
-  const float* dSg = dSout + co * GD * GD;
+  const int kc0 = half * GC;                                          // first key dim of this half
+  const float* qg = q + qk_off(d, b, c * GC, hk) + kc0;
+  const float* kg = k + qk_off(d, b, c * GC, hk) + kc0;
+  const float* Sg = Sin + co * GD * GD + static_cast<long long>(kc0) * GD;
+  const float* dSg = dSout + co * GD * GD + static_cast<long long>(kc0) * GD;
+  tile_async(Sh, LD4, Sg, GD, GC, GD);
+  tile_async(X, LD4, dO + v_off(d, b, c * GC, hv), ldv, GC, GD);
+  cp_async_commit();
   if (tid < GC) {
     Gs[tid] = Gc[co * GC + tid];
-    bs[tid] = beta[(static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv];
     dGs[tid] = 0.f;
-    dbs[tid] = 0.f;
   }
+  cp_async_wait_all();
   __syncthreads();
   const float glast = Gs[GC - 1];
-
-  // ---- 1. dQ = gamma o (dO Sin^T) + (dP o D) K;  dG from gamma in O and from D in P
-  mm<false, true, false>(E1, GD, og, ldv, Sg, GD, GC, GD, GD);         // dO Sin^T            [64, dk]
-  mm<false, true, false>(Y1, GC, og, ldv, Vng, GD, GC, GC, GD);        // dO Vn^T  = dP       [64, 64]
-  mm<false, true, false>(Y2, GC, qg, ldk, kg, ldk, GC, GC, GD);        // Q K^T
-  __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
-    const int i = e / GC, j = e - i * GC;
-    const float dpd = (i >= j) ? Y1[e] * __expf(Gs[i] - Gs[j]) : 0.f;
-    Y1[e] = dpd;                       // dP o D
-    Y2[e] = dpd * Y2[e];               // M_P = dP o D o (Q K^T)
-  }
-  __syncthreads();
-  if (tid < GC) {                      // row sums minus column sums of M_P, and the gamma-in-O term
-    float rs = 0.f, cs = 0.f;
-    for (int j = 0; j < GC; ++j) {
-      rs += Y2[tid * GC + j];
-      cs += Y2[j * GC + tid];
+  auto product = [&](bool negate_to_dW) {                              // [64, 64] = X Sh^T, K = 128
+    for (int t = warp; t < 16; t += 8) {
+      const int ti = t >> 2, tj = t & 3;
+      wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+      wm::fill_fragment(acc, 0.f);
+      tile_mma<GD, false, true>(acc, X + ti * 16 * LD4, LD4, Sh + tj * 16 * LD4, LD4);
+      if (negate_to_dW) {
+#pragma unroll
+        for (int e = 0; e < acc.num_elements; ++e) acc.x[e] = -acc.x[e];
+        wm::store_matrix_sync(dW + co * GC * GD + ti * 16 * GD + kc0 + tj * 16, acc, GD, wm::mem_row_major);
+      } else {
+        wm::store_matrix_sync(E + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
+      }
     }
-    const float eg = __expf(Gs[tid]);
-    float t = 0.f;
-    for (int x = 0; x < GD; ++x) t += qg[tid * ldk + x] * E1[tid * GD + x];
-    dGs[tid] += rs - cs + eg * t;
+  };
+  // row i of E scaled by f(i) goes to dst[i][kc0 + x]; returns through dots[i] the scaled row's dot with src[i]
+  auto scale_rows = [&](float* dst, const float* src, bool by_gamma, float* dots) {
+    for (int i = warp * 8; i < warp * 8 + 8; ++i) {
+      const float f = by_gamma ? __expf(Gs[i]) : __expf(glast - Gs[i]);
+      const float e0 = f * E[i * LP + lane], e1 = f * E[i * LP + lane + 32];
+      float* drow = dst + v_off(d, b, c * GC + i, hv) + kc0;
+      drow[lane] = e0;
+      drow[lane + 32] = e1;
+      float dot = e0 * src[i * ldk + lane] + e1 * src[i * ldk + lane + 32];
+      dot = warp_sum(dot);
+      if (lane == 0) dots[i] = dot;
+    }
+  };
+  product(false);                                                      // E1 = dO Sin^T
+  __syncthreads();
+  scale_rows(dq, qg, true, Rv);
+  __syncthreads();
+  if (tid < GC) dGs[tid] += Rv[tid];
+  tile_async(X, LD4, dVn + co * GC * GD, GD, GC, GD);
+  cp_async_commit();
+  cp_async_wait_all();
+  __syncthreads();
+  product(true);                                                       // dW = -dVn Sin^T
+  {                                                                    // gamma_C <Sin, dS'> over this half
+    float part = 0.f;
+    for (int e = tid; e < GC * GD / 4; e += 256) {
+      const int r = e / (GD / 4), x = e - r * (GD / 4);
+      const float4 a = *reinterpret_cast<const float4*>(Sh + r * LD4 + x * 4);
+      const float4 g4 = reinterpret_cast<const float4*>(dSg + static_cast<long long>(r) * GD)[x];
+      part += a.x * g4.x + a.y * g4.y + a.z * g4.z + a.w * g4.w;
+    }
+    const float tot = block_sum(part, red);
+    if (tid == 0) dGs[GC - 1] += __expf(glast) * tot;
   }
   __syncthreads();
-  for (int e = tid; e < GC * GD; e += 256) E1[e] *= __expf(Gs[e / GD]);
+  tile_async(Sh, LD4, dSg, GD, GC, GD);
+  tile_async(X, LD4, Vn + co * GC * GD, GD, GC, GD);
+  cp_async_commit();
+  cp_async_wait_all();
   __syncthreads();
-  mm<false, false, true>(E1, GD, Y1, GC, kg, ldk, GC, GD, GC);
+  product(false);                                                      // E2 = Vn dS'^T
   __syncthreads();
-  for (int e = tid; e < GC * GD / 4; e += 256) {
-    const int i = e / (GD / 4), x = e - i * (GD / 4);
-    reinterpret_cast<float4*>(dq + v_off(d, b, c * GC + i, hv))[x] = reinterpret_cast<const float4*>(E1)[e];
-  }
-  // ---- 2. dK (first part) = (dP o D)^T Q + (gamma_C / gamma) o (Vn dS'^T); dG from the decayed K in S'
-  mm<false, true, false>(E2, GD, Vng, GD, dSg, GD, GC, GD, GD);        // Vn dS'^T             [64, dk]
+  scale_rows(dk, kg, false, Rv);
   __syncthreads();
-  if (tid < GC) {
-    float t = 0.f;
-    for (int x = 0; x < GD; ++x) t += kg[tid * ldk + x] * E2[tid * GD + x];
-    const float r = __expf(glast - Gs[tid]) * t;
-    dGs[tid] -= r;
-    Rv[tid] = r;
-  }
+  if (tid < GC) dGs[tid] -= Rv[tid];
   __syncthreads();
   if (tid == 0) {
     float t = 0.f;
     for (int i = 0; i < GC; ++i) t += Rv[i];
     dGs[GC - 1] += t;
   }
-  for (int e = tid; e < GC * GD; e += 256) E2[e] *= __expf(glast - Gs[e / GD]);
   __syncthreads();
-  mm<true, false, true>(E2, GD, Y1, GC, qg, ldk, GC, GD, GC);
-  // ---- gamma_C <Sin, dS'> goes to dG of the last row
-  {
-    float part = 0.f;
-    for (int e = tid; e < GD * GD; e += 256) part += Sg[e] * dSg[e];
-    const float tot = block_sum(part, red);
-    if (tid == 0) dGs[GC - 1] += __expf(glast) * tot;
-  }
-  __syncthreads();
-  // ---- 3. dW = -dVn Sin^T
-  mm<false, true, false>(E3, GD, dVng, GD, Sg, GD, GC, GD, GD);
-  __syncthreads();
-  for (int e = tid; e < GC * GD; e += 256) E3[e] = -E3[e];
-  __syncthreads();
-  // ---- 4. dT = (dVn V^T) diag(beta) + (dW K^T) diag(gamma beta)
-  mm<false, true, false>(Y1, GC, dVng, GD, vg, ldv, GC, GC, GD);
-  mm<false, true, false>(Y2, GC, E3, GD, kg, ldk, GC, GC, GD);
-  __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
-    const int j = e % GC;
-    Y1[e] = bs[j] * (Y1[e] + __expf(Gs[j]) * Y2[e]);
-  }
-  __syncthreads();
-  // ---- 5. dVb = T^T dVn -> dV, dbeta
-  mm<true, false, false>(E1, GD, Tg, GC, dVng, GD, GC, GD, GC);
-  __syncthreads();
+  if (tid < GC)
+    dGpart[(static_cast<long long>(half) * d.B * d.T + static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv] = dGs[tid];
+}
+
+// ---------------------------------------------------------------------------------------------
+// Backward, everything inside a chunk that does not touch the states.  With Z1 = dVn V^T, Z2 = dW K^T:
+//   dP o D = tril(dO Vn^T) o D;   dq += (dP o D) K;   dk += (dP o D)^T Q
+//   dT = (Z1 + Z2 diag(gamma)) diag(beta);   dA o D = -tril(T^T dT T^T, -1) o D;   Ab = diag(beta) (dA o D)
+//   dv = (T diag(beta))^T dVn;   dk += Ab K + Ab^T K + (T diag(gamma beta))^T dW
+//   dbeta_i = sum_k T_ki (Z1_ki + gamma_i Z2_ki) + sum_j (dA o D)_ij (K K^T)_ij
+//   dG_i  += rowsum - colsum of (dP o D) o (Q K^T) and of Ab o (K K^T), + gamma_i beta_i sum_k T_ki Z2_ki
+// The products Tᵀ dVn and Tᵀ dW never exist as tiles: their row dots are column sums over T o Z, and their
+// contributions to dv and dk are products with pre-scaled copies of T.
+// Shared: five [64, 132] tiles (Q, K, dO, Vn, dk accumulator; later V, K, dVn, dW), three [64, 68], vectors.
+constexpr size_t kBwdIntraSmem = (5 * GC * LD4 + 3 * GC * LP + 6 * GC) * sizeof(float);
+constexpr int kIntraThreads = 512;
+
+__global__ void __launch_bounds__(kIntraThreads, 1)
+gdn_bwd_intra_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+                     const float* __restrict__ beta, const float* __restrict__ Gc, const float* __restrict__ Tm,
+                     const float* __restrict__ Vn, const float* __restrict__ dVn, const float* __restrict__ dW,
+                     const float* __restrict__ dO, const float* __restrict__ dGpart, GdnDims d, float* __restrict__ dq,
+                     float* __restrict__ dk, float* __restrict__ dv, float* __restrict__ dbeta, float* __restrict__ dG) {
+  extern __shared__ __align__(128) float sm[];
+  float* tQ = sm;                     // Q, later V
+  float* tK = tQ + GC * LD4;          // K
+  float* tO = tK + GC * LD4;          // dO, later dVn
+  float* tV = tO + GC * LD4;          // Vn, later dW
+  float* tD = tV + GC * LD4;          // dk accumulator
+  float* Y1 = tD + GC * LD4;
+  float* Y2 = Y1 + GC * LP;
+  float* Y3 = Y2 + GC * LP;
+  float* Gs = Y3 + GC * LP;
+  float* bs = Gs + GC;
+  float* dGs = bs + GC;
+  float* dbs = dGs + GC;
+  float* s1 = dbs + GC;
+  float* s2 = s1 + GC;
+  constexpr int NW = kIntraThreads / 32;
+  const int c = blockIdx.x, hv = blockIdx.y, b = blockIdx.z;
+  const int hk = hv / (d.Hv / d.Hk);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const long long ldk = static_cast<long long>(d.Hk) * GD, ldv = static_cast<long long>(d.Hv) * GD;
+  const long long co = ch_off(d, b, hv, c);
+  const long long vo = v_off(d, b, c * GC, hv);
+  tile_async(tQ, LD4, q + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(tK, LD4, k + qk_off(d, b, c * GC, hk), ldk, GC, GD);
+  tile_async(tO, LD4, dO + vo, ldv, GC, GD);
+  tile_async(tV, LD4, Vn + co * GC * GD, GD, GC, GD);
+  cp_async_commit();
   if (tid < GC) {
-    float t = 0.f;
-    for (int x = 0; x < GD; ++x) t += E1[tid * GD + x] * vg[tid * ldv + x];
-    dbs[tid] += t;
+    const long long o = (static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv;
+    Gs[tid] = Gc[co * GC + tid];
+    bs[tid] = beta[o];
+    dGs[tid] = dGpart[o] + dGpart[static_cast<long long>(d.B) * d.T * d.Hv + o];
+    dbs[tid] = 0.f;
   }
-  for (int e = tid; e < GC * GD / 4; e += 256) {
-    const int i = e / (GD / 4), x = e - i * (GD / 4);
-    float4 t = reinterpret_cast<const float4*>(E1)[e];
-    const float bi = bs[i];
-    reinterpret_cast<float4*>(dv + v_off(d, b, c * GC + i, hv))[x] = make_float4(t.x * bi, t.y * bi, t.z * bi, t.w * bi);
-  }
+  cp_async_wait_all();
   __syncthreads();
-  // ---- 6. d(gamma Kb) = T^T dW
-  mm<true, false, false>(E1, GD, Tg, GC, E3, GD, GC, GD, GC);
-  // ---- 7. dA = -tril_strict(T^T dT T^T), taken with D; dG from D in A
-  mm<true, false, false>(Y2, GC, Tg, GC, Y1, GC, GC, GC, GC);
+  // [64, 64] = A B^T with A, B [64, 128] tiles
+  auto abt = [&](float* Y, const float* A, const float* Bt, int t0) {
+    for (int t = warp - t0; t < 16 && t >= 0; t += NW) {
+      const int ti = t >> 2, tj = t & 3;
+      wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+      wm::fill_fragment(acc, 0.f);
+      tile_mma<GD, false, true>(acc, A + ti * 16 * LD4, LD4, Bt + tj * 16 * LD4, LD4);
+      wm::store_matrix_sync(Y + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
+    }
+  };
+  // ---- dP o D and its dG term
+  abt(Y1, tO, tV, 0);                                                  // dO Vn^T   (warps 0..15 take one tile each)
   __syncthreads();
-  mm<false, true, false>(Y3, GC, Y2, GC, Tg, GC, GC, GC, GC);
-  mm<false, true, false>(Y1, GC, kg, ldk, kg, ldk, GC, GC, GD);        // K K^T (dT is no longer needed)
+  abt(Y2, tQ, tK, 0);                                                  // Q K^T
   __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
+  for (int e = tid; e < GC * GC; e += kIntraThreads) {
     const int i = e / GC, j = e - i * GC;
-    const float dad = (i > j) ? -Y3[e] * __expf(Gs[i] - Gs[j]) : 0.f;
-    Y2[e] = dad * bs[i] * Y1[e];       // M_A = dA o A
-    Y1[e] = dad;                       // dA o D
+    const float dpd = (i >= j) ? Y1[i * LP + j] * __expf(Gs[i] - Gs[j]) : 0.f;
+    Y1[i * LP + j] = dpd;
+    Y2[i * LP + j] *= dpd;
   }
   __syncthreads();
   if (tid < GC) {
     float rs = 0.f, cs = 0.f;
     for (int j = 0; j < GC; ++j) {
-      rs += Y2[tid * GC + j];
-      cs += Y2[j * GC + tid];
+      rs += Y2[tid * LP + j];
+      cs += Y2[j * LP + tid];
     }
-    // gamma in W: sum_x d(gamma Kb)[i][x] * gamma_i beta_i K[i][x]
-    float t = 0.f;
-    for (int x = 0; x < GD; ++x) t += E1[tid * GD + x] * kg[tid * ldk + x];
-    dGs[tid] += rs - cs + __expf(Gs[tid]) * bs[tid] * t;
+    dGs[tid] += rs - cs;
+  }
+  // ---- dq = dq(state part) + (dP o D) K;  dk accumulator = dk(state part) + (dP o D)^T Q
+  for (int t = warp; t < 64; t += NW) {
+    const int which = t >> 5, tt = t & 31, ti = tt >> 3, tj = tt & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    float* gsrc = (which ? dk : dq) + vo + static_cast<long long>(ti) * 16 * ldv + tj * 16;
+    wm::load_matrix_sync(acc, gsrc, static_cast<unsigned>(ldv), wm::mem_row_major);
+    if (which == 0) {
+      tile_mma<GC, false, false>(acc, Y1 + ti * 16 * LP, LP, tK + tj * 16, LD4);
+      wm::store_matrix_sync(gsrc, acc, static_cast<unsigned>(ldv), wm::mem_row_major);
+    } else {
+      tile_mma<GC, true, false>(acc, Y1 + ti * 16, LP, tQ + tj * 16, LD4);
+      wm::store_matrix_sync(tD + ti * 16 * LD4 + tj * 16, acc, LD4, wm::mem_row_major);
+    }
   }
   __syncthreads();
-  // ---- 8. dKb = (dA o D) K + gamma o d(gamma Kb)
-  for (int e = tid; e < GC * GD; e += 256) E1[e] *= __expf(Gs[e / GD]);
+  // ---- second set of operands: V, dVn, dW, T
+  tile_async(tQ, LD4, v + vo, ldv, GC, GD);
+  tile_async(tO, LD4, dVn + co * GC * GD, GD, GC, GD);
+  tile_async(tV, LD4, dW + co * GC * GD, GD, GC, GD);
+  tile_async(Y3, LP, Tm + co * GC * GC, GC, GC, GC);
+  cp_async_commit();
+  cp_async_wait_all();
   __syncthreads();
-  mm<false, false, true>(E1, GD, Y1, GC, kg, ldk, GC, GD, GC);
+  abt(Y2, tO, tQ, 0);                                                  // Z1 = dVn V^T
+  __syncthreads();
+  abt(Y1, tV, tK, 0);                                                  // Z2 = dW K^T
+  __syncthreads();
+  if (tid < GC) {                                                      // column sums of T o Z1, T o Z2
+    float a1 = 0.f, a2 = 0.f;
+    for (int kk = 0; kk < GC; ++kk) {
+      const float t = Y3[kk * LP + tid];
+      a1 += t * Y2[kk * LP + tid];
+      a2 += t * Y1[kk * LP + tid];
+    }
+    const float eg = __expf(Gs[tid]);
+    dbs[tid] += a1 + eg * a2;
+    dGs[tid] += eg * bs[tid] * a2;
+  }
+  __syncthreads();
+  for (int e = tid; e < GC * GC; e += kIntraThreads) {                 // dT
+    const int i = e / GC, j = e - i * GC;
+    Y1[i * LP + j] = bs[j] * (Y2[i * LP + j] + __expf(Gs[j]) * Y1[i * LP + j]);
+  }
+  __syncthreads();
+  // ---- dA = -tril(T^T dT T^T, -1)
+  for (int t = warp; t < 16; t += NW) {                                // Y2 = T^T dT
+    const int ti = t >> 2, tj = t & 3;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, true, false>(acc, Y3 + ti * 16, LP, Y1 + tj * 16, LP);
+    wm::store_matrix_sync(Y2 + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
+  }
+  __syncthreads();
+  for (int t = warp; t < 16; t += NW) {                                // Y1 = Y2 T^T
+    const int ti = t >> 2, tj = t & 3;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, false, true>(acc, Y2 + ti * 16 * LP, LP, Y3 + tj * 16 * LP, LP);
+    wm::store_matrix_sync(Y1 + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
+  }
+  __syncthreads();
+  abt(Y2, tK, tK, 0);                                                  // K K^T
+  __syncthreads();
+  for (int e = tid; e < GC * GC; e += kIntraThreads) {
+    const int i = e / GC, j = e - i * GC;
+    const float dad = (i > j) ? -Y1[i * LP + j] * __expf(Gs[i] - Gs[j]) : 0.f;
+    Y2[i * LP + j] *= dad;                                             // (dA o D) o (K K^T)
+    Y1[i * LP + j] = dad * bs[i];                                      // Ab = diag(beta) (dA o D)
+  }
   __syncthreads();
   if (tid < GC) {
-    float t = 0.f;
-    for (int x = 0; x < GD; ++x) t += E1[tid * GD + x] * kg[tid * ldk + x];
-    dbs[tid] += t;
+    float rs = 0.f, cs = 0.f;
+    for (int j = 0; j < GC; ++j) {
+      rs += Y2[tid * LP + j];
+      cs += bs[j] * Y2[j * LP + tid];
+    }
+    dbs[tid] += rs;
+    dGs[tid] += bs[tid] * rs - cs;
   }
-  // ---- 9. dK (second part) = ((dA o D) with rows scaled by beta)^T K;  dK = E2 + beta o dKb
-  for (int e = tid; e < GC * GC; e += 256) Y1[e] *= bs[e / GC];
+  for (int e = tid; e < GC * GC; e += kIntraThreads) Y3[(e / GC) * LP + (e % GC)] *= bs[e % GC];     // T diag(beta)
   __syncthreads();
-  mm<true, false, true>(E2, GD, Y1, GC, kg, ldk, GC, GD, GC);
+  for (int t = warp; t < 32; t += NW) {                                // dv = (T diag(beta))^T dVn
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::fill_fragment(acc, 0.f);
+    tile_mma<GC, true, false>(acc, Y3 + ti * 16, LP, tO + tj * 16, LD4);
+    wm::store_matrix_sync(dv + vo + static_cast<long long>(ti) * 16 * ldv + tj * 16, acc, static_cast<unsigned>(ldv), wm::mem_row_major);
+  }
   __syncthreads();
-  for (int e = tid; e < GC * GD / 4; e += 256) {
-    const int i = e / (GD / 4), x = e - i * (GD / 4);
-    const float4 a = reinterpret_cast<const float4*>(E2)[e], t = reinterpret_cast<const float4*>(E1)[e];
-    const float bi = bs[i];
-    reinterpret_cast<float4*>(dk + v_off(d, b, c * GC + i, hv))[x] =
-        make_float4(a.x + bi * t.x, a.y + bi * t.y, a.z + bi * t.z, a.w + bi * t.w);
+  for (int e = tid; e < GC * GC; e += kIntraThreads) Y3[(e / GC) * LP + (e % GC)] *= __expf(Gs[e % GC]);   // T diag(gamma beta)
+  __syncthreads();
+  for (int t = warp; t < 32; t += NW) {                                // dk = acc + Ab K + Ab^T K + (T diag(gamma beta))^T dW
+    const int ti = t >> 3, tj = t & 7;
+    wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
+    wm::load_matrix_sync(acc, tD + ti * 16 * LD4 + tj * 16, LD4, wm::mem_row_major);
+    tile_mma<GC, false, false>(acc, Y1 + ti * 16 * LP, LP, tK + tj * 16, LD4);
+    tile_mma<GC, true, false>(acc, Y1 + ti * 16, LP, tK + tj * 16, LD4);
+    tile_mma<GC, true, false>(acc, Y3 + ti * 16, LP, tV + tj * 16, LD4);
+    wm::store_matrix_sync(dk + vo + static_cast<long long>(ti) * 16 * ldv + tj * 16, acc, static_cast<unsigned>(ldv), wm::mem_row_major);
   }
   if (tid < GC) {
     const long long o = (static_cast<long long>(b) * d.T + c * GC + tid) * d.Hv + hv;
@@ -654,8 +809,6 @@ gdn_chunk_bwd_kernel(const float* __restrict__ q, const float* __restrict__ k, c
   }
 }
 
-constexpr size_t kPrepSmem = (3 * GC * GC + 2 * GC) * sizeof(float);
-constexpr size_t kChunkBwdSmem = (3 * GC * GD + 3 * GC * GC + 5 * GC + 32) * sizeof(float);
 
 template <bool BWD>
 const char* launch_scan(const float* A1, const float* A2, const float* V0, const float* R0, const float* gl, const float* Rinit,
@@ -706,21 +859,24 @@ const char* gdn_tc_forward(const float* q, const float* k, const float* v, const
 const char* gdn_tc_backward(const float* q, const float* k, const float* v, const float* beta, const float* Gc, const float* gl,
                             const float* Tm, const float* Wn, const float* Kd, const float* Vn, const float* Sin,
                             const float* dO, const float* dS_final, int B, int T, int Hk, int Hv, float* X0, float* Y0,
-                            float* dVn, float* dSout, float* dq, float* dk, float* dv, float* dbeta, float* dG, float* dS0,
-                            cudaStream_t stream) {
+                            float* dVn, float* dSout, float* dW, float* dGpart, float* dq, float* dk, float* dv, float* dbeta,
+                            float* dG, float* dS0, cudaStream_t stream) {
   if (T % GC) return "gdn_tc: the sequence length must be a multiple of 64";
   if (Hk <= 0 || Hv % Hk) return "gdn_tc: value heads must be a multiple of key heads";
   if (B == 0 || T == 0) return nullptr;
   GdnDims d{B, T, Hk, Hv, T / GC};
   if (!FERRL_ONCE_PER_DEVICE(
           cudaFuncSetAttribute(gdn_bwd_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdPrepSmem)) == cudaSuccess &&
-          cudaFuncSetAttribute(gdn_chunk_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kChunkBwdSmem)) == cudaSuccess))
+          cudaFuncSetAttribute(gdn_bwd_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdStateSmem)) == cudaSuccess &&
+          cudaFuncSetAttribute(gdn_bwd_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdIntraSmem)) == cudaSuccess))
     return "gdn_tc: cannot reserve shared memory";
   gdn_bwd_prep_kernel<<<dim3(d.n, Hv, B), 256, kBwdPrepSmem, stream>>>(q, k, Gc, dO, d, X0, Y0);
   count_launch();
   if (const char* e = launch_scan<true>(Kd, Wn, X0, Y0, gl, dS_final, B, Hv, d.n, dVn, dSout, dS0, stream)) return e;
-  gdn_chunk_bwd_kernel<<<dim3(d.n, Hv, B), 256, kChunkBwdSmem, stream>>>(q, k, v, beta, Gc, Tm, Vn, dVn, Sin, dSout, dO, d, dq,
-                                                                         dk, dv, dbeta, dG);
+  gdn_bwd_state_kernel<<<dim3(d.n * 2, Hv, B), 256, kBwdStateSmem, stream>>>(q, k, Gc, Vn, dVn, Sin, dSout, dO, d, dq, dk, dW, dGpart);
+  count_launch();
+  gdn_bwd_intra_kernel<<<dim3(d.n, Hv, B), kIntraThreads, kBwdIntraSmem, stream>>>(q, k, v, beta, Gc, Tm, Vn, dVn, dW, dO, dGpart, d,
+                                                                                 dq, dk, dv, dbeta, dG);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_tc backward launch failed";
 }

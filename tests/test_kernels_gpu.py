@@ -404,3 +404,25 @@ def test_flash_backward_tcgen05(B, S, Hq, Hkv):
     again = C.lib().flash_bwd(q, k, v, o, lse, do, scale, True, 0, 0, 0)
     for a, b in zip(got, again):
         assert torch.equal(a, b)       # fixed summation order
+
+
+@pytest.mark.no_canary
+def test_canary_pads_catch_a_store_outside_an_output():
+    """The test aid itself: one byte changed in the pad after an output is reported, and forgotten after the check."""
+    from ferrl_b200.ops import cuda as C
+    lib = C.lib()
+    lib.set_canary(True)
+    try:
+        x = torch.randn(8, 256, device="cuda").bfloat16()
+        y, _ = lib.rmsnorm(x, None, torch.ones(256, device="cuda").bfloat16(), None, 1e-6, False)
+        assert lib.check_canaries() == 0
+        y, _ = lib.rmsnorm(x, None, torch.ones(256, device="cuda").bfloat16(), None, 1e-6, False)
+        raw = torch.empty(0, dtype=torch.uint8, device="cuda").set_(y.untyped_storage())
+        end = y.storage_offset() * y.element_size() + y.numel() * y.element_size()
+        raw[end + 3] = 0                  # inside the allocation (the pad), outside the output
+        torch.cuda.synchronize()
+        assert lib.check_canaries() == 1
+        assert lib.check_canaries() == 0
+    finally:
+        lib.set_canary(False)
+        lib.check_canaries()

@@ -38,6 +38,7 @@ def test_head_logprob_matches_eager(N, H, V, temperature, softcap):
     assert ((hs.grad.float() - hr.grad).abs() <= tol).float().mean().item() > 0.999
 
 
+@pytest.mark.no_canary
 def test_head_logprob_forward_allocates_nothing_of_vocabulary_width():
     from ferrl_b200.ops import cuda as C
     N, H, V = 4096, 256, 32768
@@ -55,6 +56,7 @@ def test_head_logprob_forward_allocates_nothing_of_vocabulary_width():
     assert peak < 16 * 2 ** 20, peak
 
 
+@pytest.mark.no_canary
 def test_head_logprob_backward_is_bounded_by_the_row_chunk(monkeypatch):
     from ferrl_b200.ops import cuda as C
     N, H, V = 4096, 256, 32768
