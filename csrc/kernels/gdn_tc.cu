@@ -140,7 +140,9 @@ __device__ __forceinline__ void tile_async(float* dst, int ldd, const float* src
 }
 
 // one 16x16 accumulator tile: c += op(A)[16, K] * op(B)[K, 16], k loop unrolled so the fragment loads overlap.
-// A points at the tile's first row (AT: first column of the stored [K, M] matrix), B likewise.
+// A points at the tile's first row (AT: first column of the stored [K, M] matrix), B likewise.  The fp32 operands
+// go to the tensor cores as they are: the tf32 path reads the top 19 bits (truncation instead of the
+// round-to-nearest conversion, which would cost as many instructions as the loads themselves).
 template <int K, bool AT, bool BT>
 __device__ __forceinline__ void tile_mma(wm::fragment<wm::accumulator, 16, 16, 8, float>& c, const float* A, int lda,
                                          const float* Bm, int ldb) {
@@ -154,10 +156,6 @@ __device__ __forceinline__ void tile_mma(wm::fragment<wm::accumulator, 16, 16, 8
     FB b;
     wm::load_matrix_sync(a, AT ? A + k * lda : A + k, lda);
     wm::load_matrix_sync(b, BT ? Bm + k : Bm + k * ldb, ldb);
-#pragma unroll
-    for (int e = 0; e < a.num_elements; ++e) a.x[e] = wm::__float_to_tf32(a.x[e]);
-#pragma unroll
-    for (int e = 0; e < b.num_elements; ++e) b.x[e] = wm::__float_to_tf32(b.x[e]);
     wm::mma_sync(c, a, b, c);
   }
 }
@@ -293,8 +291,10 @@ struct ScanSmem {
   static constexpr size_t BYTES = static_cast<size_t>(R + A1 + A2 + V) * sizeof(float);
 };
 
+constexpr int kScanThreads = 512;
+
 template <int DV, bool BWD>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(kScanThreads, 1)
 gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forward) / Kd (backward)
                 const float* __restrict__ A2g,    // [.., n, 64, 128]: Kd (forward) / Wn (backward)
                 const float* __restrict__ V0g,    // [.., n, 64, 128]: U (forward) / X0 (backward)
@@ -319,8 +319,8 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
   const int col0 = slice * DV;
   const int tid = threadIdx.x, warp = tid >> 5;
   const long long cbase = bh * n;
-  for (int e = tid; e < n; e += 256) gls[e] = gl[cbase + e];
-  for (int e = tid; e < GD * DV; e += 256) {
+  for (int e = tid; e < n; e += kScanThreads) gls[e] = gl[cbase + e];
+  for (int e = tid; e < GD * DV; e += kScanThreads) {
     const int r = e / DV, x = e - r * DV;
     Rs[r * LS + x] = Rinit ? Rinit[bh * GD * GD + r * GD + col0 + x] : 0.f;
   }
@@ -336,7 +336,7 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
   __syncthreads();
   {  // the state as the first chunk sees it
     float* dst = Rchunks + (cbase + first) * GD * GD;
-    for (int e = tid; e < GD * DV; e += 256) {
+    for (int e = tid; e < GD * DV; e += kScanThreads) {
       const int r = e / DV, x = e - r * DV;
       dst[r * GD + col0 + x] = Rs[r * LS + x];
     }
@@ -352,7 +352,7 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
     float* vs = Vs + buf * GC * LS;
     const long long co = cbase + c;
     // V = V0 + A1 R    [64, DV], K = 128
-    for (int t = warp; t < (GC / 16) * TN; t += 8) {
+    for (int t = warp; t < (GC / 16) * TN; t += kScanThreads / 32) {
       const int ti = t / TN, tj = t - ti * TN;
       wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
       wm::load_matrix_sync(acc, vs + ti * 16 * LS + tj * 16, LS, wm::mem_row_major);
@@ -365,7 +365,7 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
     const float eg = __expf(gls[c]);
     const bool last = i + 1 == n;
     float* rdst = last ? (Rfinal ? Rfinal + bh * GD * GD : nullptr) : Rchunks + (cbase + c + step) * GD * GD;
-    for (int t = warp; t < (GD / 16) * TN; t += 8) {
+    for (int t = warp; t < (GD / 16) * TN; t += kScanThreads / 32) {
       const int ti = t / TN, tj = t - ti * TN;
       wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
       wm::load_matrix_sync(acc, Rs + ti * 16 * LS + tj * 16, LS, wm::mem_row_major);
@@ -391,7 +391,7 @@ gdn_scan_kernel(const float* __restrict__ A1g,    // [.., n, 64, 128]: Wn (forwa
 constexpr int LP = GC + 4;      // 68
 constexpr size_t kOutSmem = (2 * GC * LD4 + GD * LD8 + GC * LD8 + GC * LP + GC) * sizeof(float);
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 gdn_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
                const float* __restrict__ Sin, const float* __restrict__ Vn, GdnDims d, float* __restrict__ out) {
   extern __shared__ __align__(128) float sm[];
@@ -415,7 +415,7 @@ gdn_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const f
   if (tid < GC) Gs[tid] = Gc[co * GC + tid];
   asm volatile("cp.async.wait_group 1;" ::: "memory");
   __syncthreads();
-  for (int t = warp; t < 16; t += 8) {                 // P = Q K^T
+  for (int t = warp; t < 16; t += 16) {                 // P = Q K^T
     const int ti = t >> 2, tj = t & 3;
     wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
     wm::fill_fragment(acc, 0.f);
@@ -423,18 +423,18 @@ gdn_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const f
     wm::store_matrix_sync(P + ti * 16 * LP + tj * 16, acc, LP, wm::mem_row_major);
   }
   __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
+  for (int e = tid; e < GC * GC; e += 512) {
     const int i = e / GC, j = e - i * GC;
     P[i * LP + j] = (i >= j) ? P[i * LP + j] * __expf(Gs[i] - Gs[j]) : 0.f;
   }
-  for (int e = tid; e < GC * GD; e += 256) {
+  for (int e = tid; e < GC * GD; e += 512) {
     const int i = e / GD, x = e - i * GD;
     Qs[i * LD4 + x] *= __expf(Gs[i]);
   }
   cp_async_wait_all();
   __syncthreads();
   float* og = out + v_off(d, b, c * GC, hv);
-  for (int t = warp; t < 32; t += 8) {                 // O = (gamma Q) Sin + P Vn
+  for (int t = warp; t < 32; t += 16) {                 // O = (gamma Q) Sin + P Vn
     const int ti = t >> 3, tj = t & 7;
     wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
     wm::fill_fragment(acc, 0.f);
@@ -450,7 +450,7 @@ gdn_out_kernel(const float* __restrict__ q, const float* __restrict__ k, const f
 constexpr int LP8 = GC + 8;     // 72
 constexpr size_t kBwdPrepSmem = (2 * GC * LD4 + GC * LD8 + GC * LP8 + GC) * sizeof(float);
 
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 gdn_bwd_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ Gc,
                     const float* __restrict__ dO, GdnDims d, float* __restrict__ X0, float* __restrict__ Y0) {
   extern __shared__ __align__(128) float sm[];
@@ -471,7 +471,7 @@ gdn_bwd_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, co
   if (tid < GC) Gs[tid] = Gc[co * GC + tid];
   cp_async_wait_all();
   __syncthreads();
-  for (int t = warp; t < 16; t += 8) {
+  for (int t = warp; t < 16; t += 16) {
     const int ti = t >> 2, tj = t & 3;
     wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
     wm::fill_fragment(acc, 0.f);
@@ -479,23 +479,23 @@ gdn_bwd_prep_kernel(const float* __restrict__ q, const float* __restrict__ k, co
     wm::store_matrix_sync(P + ti * 16 * LP8 + tj * 16, acc, LP8, wm::mem_row_major);
   }
   __syncthreads();
-  for (int e = tid; e < GC * GC; e += 256) {
+  for (int e = tid; e < GC * GC; e += 512) {
     const int i = e / GC, j = e - i * GC;
     P[i * LP8 + j] = (i >= j) ? P[i * LP8 + j] * __expf(Gs[i] - Gs[j]) : 0.f;
   }
-  for (int e = tid; e < GC * GD; e += 256) {
+  for (int e = tid; e < GC * GD; e += 512) {
     const int i = e / GD, x = e - i * GD;
     Qs[i * LD4 + x] *= __expf(Gs[i]);
   }
   __syncthreads();
-  for (int t = warp; t < 32; t += 8) {                 // X0 = P^T dO
+  for (int t = warp; t < 32; t += 16) {                 // X0 = P^T dO
     const int ti = t >> 3, tj = t & 7;
     wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
     wm::fill_fragment(acc, 0.f);
     tile_mma<GC, true, false>(acc, P + ti * 16, LP8, Os + tj * 16, LD8);
     wm::store_matrix_sync(X0 + co * GC * GD + ti * 16 * GD + tj * 16, acc, GD, wm::mem_row_major);
   }
-  for (int t = warp; t < 64; t += 8) {                 // Y0 = (gamma Q)^T dO
+  for (int t = warp; t < 64; t += 16) {                 // Y0 = (gamma Q)^T dO
     const int ti = t >> 3, tj = t & 7;
     wm::fragment<wm::accumulator, 16, 16, 8, float> acc;
     wm::fill_fragment(acc, 0.f);
@@ -826,10 +826,10 @@ const char* launch_scan(const float* A1, const float* A2, const float* V0, const
                                static_cast<int>(ScanSmem<32>::BYTES)) == cudaSuccess))
     return "gdn_tc: cannot reserve shared memory";
   if (narrow)
-    gdn_scan_kernel<32, BWD><<<dim3(Hv * 4, B), 256, ScanSmem<32>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 4, Vout, Rchunks,
+    gdn_scan_kernel<32, BWD><<<dim3(Hv * 4, B), kScanThreads, ScanSmem<32>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 4, Vout, Rchunks,
                                                                                     Rfinal);
   else
-    gdn_scan_kernel<64, BWD><<<dim3(Hv * 2, B), 256, ScanSmem<64>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 2, Vout, Rchunks,
+    gdn_scan_kernel<64, BWD><<<dim3(Hv * 2, B), kScanThreads, ScanSmem<64>::BYTES, stream>>>(A1, A2, V0, R0, gl, Rinit, n, 2, Vout, Rchunks,
                                                                                     Rfinal);
   count_launch();
   return nullptr;
@@ -851,7 +851,7 @@ const char* gdn_tc_forward(const float* q, const float* k, const float* v, const
   gdn_prep_kernel<<<dim3(d.n, Hv, B), 256, kPrepSmem, stream>>>(k, v, g, beta, d, Gc, gl, Tm, U, Wn, Kd);
   count_launch();
   if (const char* e = launch_scan<false>(Wn, Kd, U, nullptr, gl, S0, B, Hv, d.n, Vn, Sin, S_out, stream)) return e;
-  gdn_out_kernel<<<dim3(d.n, Hv, B), 256, kOutSmem, stream>>>(q, k, Gc, Sin, Vn, d, out);
+  gdn_out_kernel<<<dim3(d.n, Hv, B), 512, kOutSmem, stream>>>(q, k, Gc, Sin, Vn, d, out);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_tc forward launch failed";
 }
@@ -870,7 +870,7 @@ const char* gdn_tc_backward(const float* q, const float* k, const float* v, cons
           cudaFuncSetAttribute(gdn_bwd_state_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdStateSmem)) == cudaSuccess &&
           cudaFuncSetAttribute(gdn_bwd_intra_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kBwdIntraSmem)) == cudaSuccess))
     return "gdn_tc: cannot reserve shared memory";
-  gdn_bwd_prep_kernel<<<dim3(d.n, Hv, B), 256, kBwdPrepSmem, stream>>>(q, k, Gc, dO, d, X0, Y0);
+  gdn_bwd_prep_kernel<<<dim3(d.n, Hv, B), 512, kBwdPrepSmem, stream>>>(q, k, Gc, dO, d, X0, Y0);
   count_launch();
   if (const char* e = launch_scan<true>(Kd, Wn, X0, Y0, gl, dS_final, B, Hv, d.n, dVn, dSout, dS0, stream)) return e;
   gdn_bwd_state_kernel<<<dim3(d.n * 2, Hv, B), 256, kBwdStateSmem, stream>>>(q, k, Gc, Vn, dVn, Sin, dSout, dO, d, dq, dk, dW, dGpart);
