@@ -247,10 +247,34 @@ def _harden_payload(keep_fd):
     scratch = os.environ.get("FERRL_SCRATCH")
     if scratch and os.path.isdir(scratch):
         os.chdir(scratch)
+    return _install_syscall_filter()
+
+
+def _install_syscall_filter():
+    """Last hardening step: the seccomp deny list of ``syscall_filter.py`` (the file next to this one; loaded
+    by path because the interpreter runs isolated).  Returns the kernel's evidence, or a record that says why
+    the filter is absent (``FERRL_EVAL_SECCOMP=0``, another architecture)."""
+    if os.environ.get("FERRL_EVAL_SECCOMP", "1") == "0":
+        return {"seccomp_policy": None, "reason": "disabled by FERRL_EVAL_SECCOMP=0"}
+    import importlib.util
+    import platform
+    if platform.machine() != "x86_64" or not sys.platform.startswith("linux"):
+        return {"seccomp_policy": None, "reason": f"no policy for {sys.platform}/{platform.machine()}"}
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "syscall_filter.py")
+    spec = importlib.util.spec_from_file_location("ferrl_syscall_filter", path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod.install()
 
 
 def payload_main(fd):
-    _harden_payload(fd)
+    try:
+        hardening = _harden_payload(fd)
+    except BaseException as e:  # noqa: BLE001 - a payload that could not be confined must not run candidate code
+        sock = socket.socket(fileno=fd)
+        send_msg(sock, pack_bundle("error", meta={"error": one_line(f"payload hardening failed: {type(e).__name__}: {e}"),
+                                                  "infrastructure": True}))
+        return
     sock = socket.socket(fileno=fd)
     import importlib.machinery
     import importlib.util
@@ -263,7 +287,7 @@ def payload_main(fd):
         sys.dont_write_bytecode = True
         loader.exec_module(mod)
         kernel = getattr(mod, "custom_kernel")
-        send_msg(sock, pack_bundle("ready"))
+        send_msg(sock, pack_bundle("ready", meta={"hardening": hardening}))
     except BaseException as e:  # noqa: BLE001 - reported to the parent as a candidate failure
         send_msg(sock, pack_bundle("error", meta={"error": one_line(f"import failed: {type(e).__name__}: {e}")}))
         return
@@ -316,7 +340,14 @@ class CandidateSession:
         kind, meta, _ = self._recv(max(call_timeout, 60.0))
         if kind != "ready":
             self.close()
+            if isinstance(meta, dict) and meta.get("infrastructure"):
+                raise RuntimeError(meta.get("error", "payload hardening failed"))      # not the candidate's fault
             raise CandidateFailure(meta.get("error", "payload did not start") if isinstance(meta, dict) else "payload did not start")
+        self.hardening = meta.get("hardening") if isinstance(meta, dict) else None
+        h = self.hardening
+        if isinstance(h, dict) and h.get("seccomp_policy") is not None and (h.get("seccomp_mode") != 2 or h.get("no_new_privs") != 1):
+            self.close()
+            raise RuntimeError(f"payload reports an inactive syscall filter: {h}")
 
     def _recv(self, timeout):
         msg = recv_msg(self.sock, time.monotonic() + timeout)
@@ -402,9 +433,13 @@ class CandidateSession:
 
 def _session(log, call_timeout):
     try:
-        return CandidateSession(call_timeout), None
+        session = CandidateSession(call_timeout)
     except CandidateFailure as e:
         return None, e
+    h = session.hardening if isinstance(session.hardening, dict) else {}
+    log("payload-hardening: " + one_line(json.dumps({k: h.get(k) for k in ("seccomp_policy", "seccomp_mode", "seccomp_filters",
+                                                                          "no_new_privs", "reason") if k in h}, sort_keys=True)))
+    return session, None
 
 
 def run_tests(log, cases, call_timeout):
