@@ -49,18 +49,27 @@ def test_token_logprobs_and_grads_match_cpu(remat):
     ids = torch.randint(0, 1024, (3, 40))
     start = torch.tensor([9, 14, 19])
     targets = torch.randint(0, 1024, (3, 16))
-    lp_c = cpu.token_logprobs(ids, start, targets, 1.0)
-    lp_g = gpu.token_logprobs(ids.cuda(), start.cuda(), targets.cuda(), 1.0)
-    assert (lp_c - lp_g.cpu()).abs().max().item() < 0.15
+    from test_model_families_gpu import _check_against_yardstick, _eager_bf16
     w = torch.randn(3, 16)
-    (lp_c * w).sum().backward()
-    (lp_g * w.cuda()).sum().backward()
-    num = den = 0.0
-    for a, b in zip(cpu.trainable_params(), gpu.trainable_params()):
-        assert b.grad is not None and torch.isfinite(b.grad).all()
-        num += float((a.grad - b.grad.cpu()).pow(2).sum())
-        den += float(a.grad.pow(2).sum())
-    assert (num / den) ** 0.5 < 0.08
+
+    def run(model, dev):
+        for p in model.trainable_params():
+            p.grad = None
+        lp = model.token_logprobs(ids.to(dev), start.to(dev), targets.to(dev), 1.0)
+        (lp * w.to(dev)).sum().backward()
+        for p in model.trainable_params():
+            assert p.grad is not None and torch.isfinite(p.grad).all()
+        return lp.detach().float().cpu(), torch.cat([p.grad.float().cpu().reshape(-1) for p in model.trainable_params()])
+    lp_c, g_c = run(cpu, "cpu")
+    lp_g, g_g = run(gpu, "cuda")
+    with _eager_bf16():
+        lp_e, g_e = run(gpu, "cuda")
+    # The yardstick is PyTorch's own bf16 evaluation of the same GPU model: bf16 activations carry 8 bits of
+    # mantissa through two layers and a 1024-way softmax, so neither path can match fp32 to better than a few
+    # 1e-2 in log-prob; what the kernels owe is to be as close to fp32 as the library's bf16 path is.
+    _check_against_yardstick(lp_g, lp_e, lp_c, "dense logprobs")
+    _check_against_yardstick(g_g, g_e, g_c, "dense adapter grads", slack=2.0, floor=1e-2)
+    assert (lp_c - lp_g).abs().max().item() < 0.15          # and an absolute ceiling on top
 
 
 def test_cached_decode_matches_full_forward_on_gpu():

@@ -70,6 +70,33 @@ def test_static_workspace_entry_matches_regular_op_twice():
         assert torch.equal(out, ref)
 
 
+def test_static_workspace_entry_on_the_second_device_before_the_first():
+    """Kernel attributes (shared-memory opt-in for head dim 256) and the workspace address are kept per
+    device: the first call of the process goes to device 1 with head dim 256, then the same to device 0."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs two CUDA devices")
+    from ferrl_b200.ops import cuda as C
+    fn, err = _entry()
+    B, Smax, Hq, Hkv, D, splits = 4, 300, 8, 2, 256, 2
+    scale = 1.0 / math.sqrt(D)
+    for index in (1, 0):
+        dev = torch.device("cuda", index)
+        with torch.cuda.device(dev):
+            g = torch.Generator(device=dev).manual_seed(3 + index)
+            q = torch.randn(B, Hq, D, device=dev, generator=g).to(torch.bfloat16)
+            kc = torch.randn(B, Smax, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
+            vc = torch.randn(B, Smax, Hkv, D, device=dev, generator=g).to(torch.bfloat16)
+            lens = torch.tensor([300, 7, 129, 64], device=dev, dtype=torch.int32)
+            out = torch.empty_like(q)
+            stream = torch.cuda.current_stream(dev).cuda_stream
+            rc = fn(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), lens.data_ptr(), out.data_ptr(), B, Hq, Hkv, D,
+                    kc.stride(0), kc.stride(1), scale, 0, splits, stream)
+            assert rc == 0, err(rc)
+            torch.cuda.synchronize(dev)
+            ref = C.decode_attention(q, kc, vc, lens, scale=scale, n_splits=splits)
+            assert torch.equal(out, ref), index
+
+
 def test_static_workspace_entry_rejects_oversize_and_bad_args():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
