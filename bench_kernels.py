@@ -1,7 +1,7 @@
 """Per-kernel timings at the headline model's shapes, against the measured roofline.
 
     python bench_kernels.py [--only gemm,attn,...] [--iters 20] [--json out.json]
-    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc1|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk|gdn_tc_fwd|gdn_tc_bwd   # small, for a profiler
+    python bench_kernels.py --profile-case gemm|gemm_2cta_256|gemm_lora|gemm_decode|decode_attn|sample|flash|flash_tc1|flash_tc2|flash_bwd|rmsnorm|swiglu|qk_norm_rope|logprob|lora_grad|moe_grouped|gdn_decode|gdn_chunk|gdn_tc_fwd|gdn_tc_bwd|flash_tc3_d256|flash_tc3_window|decode_attn_group|logprob_head   # small, for a profiler
 
 Every kernel is timed with CUDA events on the launching stream after warm-up, with a buffer
 larger than L2 written between iterations (cold L2), and reported as achieved bytes/s or FLOP/s
@@ -140,6 +140,32 @@ def profile_case(name, C):
             saved_ = C.lib().gdn_tc_fwd(qn, kn, vv, gc, bc, None)[2:]
             dO_ = f32(B_, T_, Hv_, 128)
             fn = lambda: C.lib().gdn_tc_bwd(qn, kn, vv, bc, *saved_, dO_, None)
+    elif name in ("flash_tc3_d256", "flash_tc3_window"):
+        if name == "flash_tc3_d256":
+            q, k, v = rnd(8, 1536, 16, 256), rnd(8, 1536, 2, 256), rnd(8, 1536, 2, 256)
+            fn = lambda: C.attention(q, k, v, scale=1.0 / 16, causal=True)
+        else:
+            q, k, v = rnd(8, 1536, 32, 128), rnd(8, 1536, 8, 128), rnd(8, 1536, 8, 128)
+            fn = lambda: C.attention(q, k, v, scale=1.0 / 16, causal=True, window=1024)
+    elif name == "decode_attn_group":
+        # 16 groups of 8 rows, 448 shared prompt tokens (7 pages of 64) + 384 private tokens per row, Qwen3-8B heads
+        P_, G_, page_, ppr_ = 16, 8, 64, 14
+        B_ = P_ * G_
+        n_pages = (P_ + B_) * ppr_
+        kp, vp = rnd(n_pages, page_, 8, 128), rnd(n_pages, page_, 8, 128)
+        qd = rnd(B_, 32, 128)
+        jj = torch.arange(ppr_, device=dev)[None, :]
+        grp = torch.arange(P_, device=dev).repeat_interleave(G_)
+        shared = grp[:, None] * ppr_ + jj
+        private = P_ * ppr_ + torch.arange(B_, device=dev)[:, None] * ppr_ + (jj - 7).clamp(min=0)
+        table = torch.where(jj < 7, shared, private).to(torch.int32).contiguous()
+        prefix = torch.full((P_,), 7 * page_, device=dev, dtype=torch.int32)
+        lens = torch.full((B_,), 832, device=dev, dtype=torch.int32)
+        fn = lambda: C.decode_attention(qd, kp, vp, lens, scale=128 ** -0.5, block_table=table, prefix_len=prefix, group=G_)
+    elif name == "logprob_head":
+        hh, ww = rnd(4096, 4096), rnd(32768, 4096) * 0.02
+        tg = torch.randint(0, 32768, (4096,), device=dev)
+        fn = lambda: C.lib().logprob_head_fwd(hh, ww, tg, 1.0, 0.0)
     elif name == "lora_grad":
         u, xx = rnd(24576, 48), rnd(24576, 4096)
         fn = lambda: C.lib().lora_grad(u, xx)
