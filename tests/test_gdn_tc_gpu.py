@@ -24,7 +24,9 @@ def _rel(a, b):
     return ((a.double() - b.double()).norm() / b.double().norm().clamp_min(1e-12)).item()
 
 
-@pytest.mark.parametrize("B,T,Hk,Hv,with_state", [(2, 128, 2, 2, False), (1, 130, 1, 2, True), (2, 64, 2, 4, True)])
+# the last case has enough (batch, head) pairs for the 64-column scan slices; the others take the 32-column ones
+@pytest.mark.parametrize("B,T,Hk,Hv,with_state", [(2, 128, 2, 2, False), (1, 130, 1, 2, True), (2, 64, 2, 4, True),
+                                                   (2, 192, 20, 40, True)])
 def test_gdn_tc_matches_recurrence_with_grads(B, T, Hk, Hv, with_state):
     from ferrl_b200.ops import cuda as C, eager
     dev = torch.device("cuda")
@@ -58,7 +60,7 @@ def test_gdn_tc_matches_recurrence_with_grads(B, T, Hk, Hv, with_state):
         assert _rel(a, r) < 1e-2, (name, _rel(a, r))
 
 
-def test_gdn_tc_forward_only_saves_nothing():
+def test_gdn_tc_forward_without_grad_matches_the_scan_kernel():
     from ferrl_b200.ops import cuda as C
     dev = torch.device("cuda")
     torch.manual_seed(0)
