@@ -14,6 +14,7 @@ The reference reduces after every row-parallel projection with a blocking NCCL a
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Callable, Optional
 
@@ -48,6 +49,17 @@ def gloo_all_to_all_rows(comm: Comm):
     return a2a
 
 
+class _FirstOf:
+    """An activation all-reducer that tries ``first`` and falls back to ``second`` for inputs it declines."""
+
+    def __init__(self, first, second):
+        self.first, self.second = first, second
+
+    def __call__(self, x):
+        y = self.first(x)
+        return y if y is not None else self.second(x)
+
+
 @dataclass
 class ParallelRuntime:
     comm: Comm
@@ -60,7 +72,7 @@ class ParallelRuntime:
     @classmethod
     def create(cls, comm: Comm, device, *, tensor_parallel: bool = False, hidden: int = 0, max_rows: int = 0,
                expert_parallel: Optional[dict] = None, heap_factory: Optional[Callable] = None,
-               wait_limit_s: float = 20.0) -> "ParallelRuntime":
+               wait_limit_s: float = 20.0, nvls: Optional[bool] = None) -> "ParallelRuntime":
         """``max_rows``: most activation rows (tokens) one forward call carries; ``hidden``: model width.
         ``expert_parallel``: ``{num_experts, hidden, max_tokens, top_k, capacity_factor}``."""
         from . import ep as EP
@@ -73,10 +85,21 @@ class ParallelRuntime:
         if tensor_parallel and comm.world_size > 1 and rt.heap is not None:
             rows = max(int(max_rows), 128)
             rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden))
-            rt.all_reducer = symm.SymmAllReducer(rt.heap, rows * int(hidden) * 4)
+            plain = symm.SymmAllReducer(rt.heap, rows * int(hidden) * 4)
+            rt.all_reducer = plain
+            how = "peer-memory"
+            if (os.environ.get("FERRL_NVLS") == "1" if nvls is None else nvls) and on_gpu:
+                # in-switch reduction for the activations; shapes it does not take fall back to peer loads
+                from .nvls import NvlsAllReducer, NvlsUnavailable
+                try:
+                    fast = NvlsAllReducer(rt.heap, rows * int(hidden) * 4)
+                    rt.all_reducer = _FirstOf(fast, plain)
+                    how = "NVLS multimem"
+                except NvlsUnavailable as e:
+                    rt.notes.append(f"nvls unavailable: {e}")
             symm.register_gemm_all_reducer(comm, rt.gemm_reducer)
             symm.register_all_reducer(comm, rt.all_reducer)
-            rt.notes.append("tp: fused gemm->all-reduce + peer-memory activation all-reduce")
+            rt.notes.append(f"tp: fused gemm->all-reduce + {how} activation all-reduce")
         if expert_parallel is not None and comm.world_size > 1:
             e = expert_parallel
             runtime = None

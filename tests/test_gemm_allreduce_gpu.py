@@ -164,3 +164,16 @@ def test_multi_process_expert_parallel(world):
     _need_gpu(world)
     out = _torchrun("multi_gpu_ep_worker.py", world, 29633 + world, "EP_PASS")
     print("\n".join(l for l in out.splitlines() if l.startswith("EP_TIMING")))
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_multi_process_nvls_all_reduce(world):
+    """In-switch all-reduce (multimem) against the peer-load form; passes with a note where the box has no multicast."""
+    _need_gpu(world)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", PYTHONPATH=ROOT)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29653 + world), os.path.join(ROOT, "tests", "multi_gpu_nvls_worker.py")]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    assert "NVLS_PASS" in res.stdout or "NVLS_UNAVAILABLE" in res.stdout
+    print("\n".join(l for l in res.stdout.splitlines() if l.startswith("NVLS_")))
