@@ -226,9 +226,17 @@ const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long
                           long long k_ts, long long v_bs, long long v_ts, const float* g, const float* beta,
                           const float* S0, float* S_out, void* out, int B, int T, int Hk, int Hv, int KD, int VD,
                           bool l2norm, float eps, cudaStream_t stream);
+// Optional gate inputs straight from the input projection (decode): a, b bf16 [B, Hv] with row strides lda, ldb,
+// A_log and dt_bias fp32 [Hv]; the kernel then forms g = -exp(A_log) softplus(a + dt_bias) and beta = sigmoid(b)
+// itself and ignores `g` / `beta`.
+struct GdnRawGates {
+  const __nv_bfloat16* a; long long lda;
+  const __nv_bfloat16* b; long long ldb;
+  const float* A_log; const float* dt_bias;
+};
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                             const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
-                            bool l2norm, float eps, void* out, cudaStream_t stream);
+                            bool l2norm, float eps, void* out, cudaStream_t stream, const GdnRawGates* raw_gates = nullptr);
 
 // ---- chunked gated delta rule on tensor cores, forward and backward (csrc/kernels/gdn_tc.cu)
 // All tensors fp32 and contiguous: q,k [B,T,Hk,128] (already L2-normalised, q scaled), v/out/dO/dq/dk/dv

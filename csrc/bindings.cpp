@@ -484,6 +484,32 @@ Tensor gdn_decode_step(const Tensor& q, const Tensor& k, const Tensor& v, const 
   return out;
 }
 
+// Same step with the gates taken from the input projection: a, b bf16 [B, Hv] (row strides free), A_log and
+// dt_bias f32 [Hv]; g and beta are formed inside the kernel.
+Tensor gdn_decode_step_raw(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& a, const Tensor& b,
+                           const Tensor& A_log, const Tensor& dt_bias, Tensor S, bool l2norm, double eps) {
+  TORCH_CHECK(S.is_cuda() && S.scalar_type() == at::kFloat && S.dim() == 4 && S.is_contiguous(), "gdn_decode_step_raw: S f32 [B,Hv,KD,VD]");
+  const int64_t B = S.size(0), Hv = S.size(1), KD = S.size(2), VD = S.size(3);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 && k.scalar_type() == at::kBFloat16 && v.scalar_type() == at::kBFloat16 &&
+                  q.dim() == 2 && k.dim() == 2 && v.dim() == 2 && q.stride(1) == 1 && k.stride(1) == 1 && v.stride(1) == 1 &&
+                  q.size(0) == B && v.size(1) == Hv * VD && q.size(1) % KD == 0 && k.size(1) == q.size(1),
+              "gdn_decode_step_raw: q,k [B,Hk*KD], v [B,Hv*VD] bf16");
+  TORCH_CHECK(a.scalar_type() == at::kBFloat16 && b.scalar_type() == at::kBFloat16 && a.dim() == 2 && b.dim() == 2 &&
+                  a.size(0) == B && b.size(0) == B && a.size(1) == Hv && b.size(1) == Hv && a.stride(1) == 1 && b.stride(1) == 1,
+              "gdn_decode_step_raw: a,b bf16 [B,Hv]");
+  TORCH_CHECK(A_log.scalar_type() == at::kFloat && dt_bias.scalar_type() == at::kFloat && A_log.is_contiguous() &&
+                  dt_bias.is_contiguous() && A_log.numel() == Hv && dt_bias.numel() == Hv, "gdn_decode_step_raw: A_log, dt_bias f32 [Hv]");
+  c10::cuda::CUDAGuard guard(S.device());
+  Tensor out = out_empty({B, Hv, VD}, q.options());
+  ferrl::GdnRawGates raw{reinterpret_cast<const __nv_bfloat16*>(a.data_ptr()), a.stride(0),
+                         reinterpret_cast<const __nv_bfloat16*>(b.data_ptr()), b.stride(0), A_log.data_ptr<float>(),
+                         dt_bias.data_ptr<float>()};
+  FERRL_CHECK(ferrl::gdn_decode_step(q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), k.stride(0), v.stride(0), nullptr,
+                                     nullptr, S.data_ptr<float>(), B, q.size(1) / KD, Hv, KD, VD, l2norm, static_cast<float>(eps),
+                                     out.data_ptr(), stream(), &raw));
+  return out;
+}
+
 // q,k [B,T,Hk,KD], v [B,T,Hv,VD] bf16 (head dims contiguous, token/batch strides free), g,beta [B,T,Hv] f32,
 // S0 [B,Hv,KD,VD] f32 or none -> (out [B,T,Hv,VD] bf16, S [B,Hv,KD,VD] f32)
 static void gdn_tc_check(const Tensor& t, const char* what) {
@@ -1321,6 +1347,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("rmsnorm_gated_bwd(Tensor x, Tensor gate, Tensor w, Tensor dy, float eps) -> (Tensor, Tensor)", &rmsnorm_gated_bwd);
   m.def("gdn_tc_fwd(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor? S0) -> Tensor[]", &gdn_tc_fwd);
   m.def("gdn_tc_bwd(Tensor q, Tensor k, Tensor v, Tensor beta, Tensor Gc, Tensor gl, Tensor Tm, Tensor Wn, Tensor Kd, Tensor Vn, Tensor Sin, Tensor dO, Tensor? dS_final) -> Tensor[]", &gdn_tc_bwd);
+  m.def("gdn_decode_step_raw(Tensor q, Tensor k, Tensor v, Tensor a, Tensor b, Tensor A_log, Tensor dt_bias, Tensor(a!) S, bool l2norm, float eps) -> Tensor", &gdn_decode_step_raw);
   m.def("gdn_decode_step(Tensor q, Tensor k, Tensor v, Tensor g, Tensor beta, Tensor(a!) S, bool l2norm, float eps) -> Tensor", &gdn_decode_step);
   m.def("moe_route(Tensor logits, int k, bool renorm) -> (Tensor, Tensor, Tensor, Tensor)", &moe_route);
   m.def("moe_plan(Tensor idx, Tensor counts) -> (Tensor, Tensor, Tensor, Tensor)", &moe_plan);

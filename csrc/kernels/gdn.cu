@@ -119,7 +119,7 @@ __global__ void gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ q, cons
                                        const __nv_bfloat16* __restrict__ v, long long ldq, long long ldk, long long ldv,
                                        const float* __restrict__ g, const float* __restrict__ beta,
                                        float* __restrict__ S, int Hk, int Hv, int VD, int l2norm, float eps,
-                                       __nv_bfloat16* __restrict__ out) {
+                                       __nv_bfloat16* __restrict__ out, GdnRawGates raw) {
   __shared__ float qs[KD], ks[KD], red[32];
   const int b = blockIdx.x / Hv, hv = blockIdx.x % Hv;
   const int hk = hv / (Hv / Hk);
@@ -141,8 +141,17 @@ __global__ void gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ q, cons
   __syncthreads();
   const float qscale = qn * rsqrtf(static_cast<float>(KD));
   const long long bh = static_cast<long long>(b) * Hv + hv;
-  const float eg = __expf(g[bh]);
-  const float bt = beta[bh];
+  float eg, bt;
+  if (raw.a) {
+    // gates from the projection output: g = -exp(A_log) softplus(a + dt_bias), beta = sigmoid(b)
+    const float x = __bfloat162float(raw.a[static_cast<long long>(b) * raw.lda + hv]) + raw.dt_bias[hv];
+    const float sp = x > 20.f ? x : log1pf(__expf(x));
+    eg = __expf(-__expf(raw.A_log[hv]) * sp);
+    bt = 1.f / (1.f + __expf(-__bfloat162float(raw.b[static_cast<long long>(b) * raw.ldb + hv])));
+  } else {
+    eg = __expf(g[bh]);
+    bt = beta[bh];
+  }
   for (int j = tid; j < VD; j += blockDim.x) {
     float* Sc = S + bh * KD * VD + j;
     float col[KD];
@@ -504,14 +513,18 @@ const char* gdn_chunk_fwd(const void* q, const void* k, const void* v, long long
 
 const char* gdn_decode_step(const void* q, const void* k, const void* v, long long ldq, long long ldk, long long ldv,
                             const float* g, const float* beta, float* S, int B, int Hk, int Hv, int KD, int VD,
-                            bool l2norm, float eps, void* out, cudaStream_t stream) {
+                            bool l2norm, float eps, void* out, cudaStream_t stream, const GdnRawGates* raw_gates) {
   if (Hk <= 0 || Hv % Hk) return "gdn_decode_step: value heads must be a multiple of key heads";
+  GdnRawGates raw{};
+  if (raw_gates) raw = *raw_gates;
+  if (!raw.a && (!g || !beta)) return "gdn_decode_step: either g and beta or the raw gate inputs are needed";
+  if (raw.a && (!raw.b || !raw.A_log || !raw.dt_bias)) return "gdn_decode_step: incomplete raw gate inputs";
   if (B == 0) return nullptr;
   const int threads = std::min(256, (VD + 31) / 32 * 32);
 #define FERRL_GDN_STEP(KDV)                                                                                        \
   gdn_decode_step_kernel<KDV><<<B * Hv, threads, 0, stream>>>(                                                     \
       static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v), \
-      ldq, ldk, ldv, g, beta, S, Hk, Hv, VD, l2norm ? 1 : 0, eps, static_cast<__nv_bfloat16*>(out))
+      ldq, ldk, ldv, g, beta, S, Hk, Hv, VD, l2norm ? 1 : 0, eps, static_cast<__nv_bfloat16*>(out), raw)
   switch (KD) {
     case 16: FERRL_GDN_STEP(16); break;
     case 32: FERRL_GDN_STEP(32); break;

@@ -252,10 +252,14 @@ class Qwen35Layer(nn.Module):
             # one-token path: two kernels, both states updated in place
             from ..ops import cuda as C
             y = C.gdn_conv_step(mixed[:, 0], self.conv_w, state[0], True)
-            beta = torch.sigmoid(b[:, 0].float())
-            g = -self.A_log.float().exp() * F.softplus(a[:, 0].float() + self.dt_bias.float())
-            core = C.gdn_decode_step(y[:, :self.key_dim], y[:, self.key_dim:2 * self.key_dim], y[:, 2 * self.key_dim:],
-                                     g, beta, state[1], True, 1e-6)
+            if self.A_log.dtype == torch.float32 and self.dt_bias.dtype == torch.float32:
+                core = C.gdn_decode_step_raw(y[:, :self.key_dim], y[:, self.key_dim:2 * self.key_dim], y[:, 2 * self.key_dim:],
+                                             a[:, 0], b[:, 0], self.A_log, self.dt_bias, state[1], True, 1e-6)
+            else:
+                beta = torch.sigmoid(b[:, 0].float())
+                g = -self.A_log.float().exp() * F.softplus(a[:, 0].float() + self.dt_bias.float())
+                core = C.gdn_decode_step(y[:, :self.key_dim], y[:, self.key_dim:2 * self.key_dim], y[:, 2 * self.key_dim:],
+                                         g, beta, state[1], True, 1e-6)
             core = ops.rmsnorm_gated(core.reshape(-1, self.vd), z.reshape(-1, self.vd), self.gdn_norm, self.eps)
             return f(self.out, core.reshape(B, S_, self.value_dim)), (state[0], state[1])
         y = None

@@ -550,6 +550,12 @@ def gdn_decode_step(q, k, v, g, beta, S, l2norm=True, eps=1e-6):
     return lib().gdn_decode_step(q, k, v, g.contiguous(), beta.contiguous(), S, bool(l2norm), float(eps))
 
 
+def gdn_decode_step_raw(q, k, v, a, b, A_log, dt_bias, S, l2norm=True, eps=1e-6):
+    """The same step with the gates formed in the kernel from the projection's ``a`` and ``b`` columns
+    (``g = -exp(A_log) softplus(a + dt_bias)``, ``beta = sigmoid(b)``): ten small launches fewer per layer."""
+    return lib().gdn_decode_step_raw(q, k, v, a, b, A_log, dt_bias, S, bool(l2norm), float(eps))
+
+
 # ------------------------------------------------------------------ MoE
 class _MoeRoute(torch.autograd.Function):
     """fp32 softmax over the router logits, top-k and renormalisation in one kernel; the

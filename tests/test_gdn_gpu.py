@@ -73,6 +73,32 @@ def test_decode_step_matches_recurrent(B, Hk, Hv, KD, VD):
         assert float((S - S_ref).abs().max()) <= 1e-4 * float(S_ref.abs().max()) + 1e-5
 
 
+def test_decode_step_with_gates_formed_in_the_kernel():
+    """``gdn_decode_step_raw`` (g and beta from the projection's a / b columns, strided views) equals the step fed
+    with gates computed by PyTorch."""
+    import torch.nn.functional as F
+    from ferrl_b200.ops import cuda as Cc
+    dev = _dev()
+    g = torch.Generator(device=dev).manual_seed(5)
+    B, Hk, Hv, KD, VD = 5, 2, 4, 128, 128
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    S1 = rnd(B, Hv, KD, VD) * 0.1
+    S2 = S1.clone()
+    A_log = torch.log(torch.rand(Hv, device=dev, generator=g) * 15 + 1)
+    dt_bias = rnd(Hv)
+    for step in range(3):
+        q, k = rnd(B, Hk * KD).to(torch.bfloat16), rnd(B, Hk * KD).to(torch.bfloat16)
+        v = rnd(B, Hv * VD).to(torch.bfloat16)
+        ab = (rnd(B, 2 * Hv + 3) * 3).to(torch.bfloat16)           # a and b as column slices of a wider row
+        a, b = ab[:, 1:1 + Hv], ab[:, 1 + Hv:1 + 2 * Hv]
+        gg = -A_log.exp() * F.softplus(a.float() + dt_bias)
+        beta = torch.sigmoid(b.float())
+        o1 = Cc.gdn_decode_step(q, k, v, gg, beta, S1, True, 1e-6)
+        o2 = Cc.gdn_decode_step_raw(q, k, v, a, b, A_log, dt_bias, S2, True, 1e-6)
+        assert float((o1.float() - o2.float()).abs().max()) <= 0.01 * float(o1.float().abs().max()) + 1e-3
+        assert float((S1 - S2).abs().max()) <= 1e-4 * float(S1.abs().max()) + 1e-5
+
+
 @pytest.mark.parametrize("B,T,Hk,Hv,with_state", [(1, 64, 1, 1, False), (2, 150, 2, 4, True), (1, 7, 1, 2, True),
                                                    (3, 257, 2, 2, False)])
 def test_chunk_scan_matches_recurrent(B, T, Hk, Hv, with_state):
