@@ -66,7 +66,17 @@ nvls_all_reduce_kernel(uint4* mc, const uint4* __restrict__ local, PeerTable fla
   const long long per = n16 / world, lo = per * rank;
   const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
-  for (long long i = lo + tid; i < lo + per; i += nthreads) {
+  // four requests in flight per thread: the round trip through the switch is long
+  constexpr int U = 4;
+  long long i = lo + tid;
+  for (; i + (U - 1) * nthreads < lo + per; i += U * nthreads) {
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = mc_ld_reduce<T>(mc + i + u * nthreads);
+#pragma unroll
+    for (int u = 0; u < U; ++u) mc_st(mc + i + u * nthreads, v[u]);
+  }
+  for (; i < lo + per; i += nthreads) {
     const uint4 v = mc_ld_reduce<T>(mc + i);
     mc_st(mc + i, v);
   }
@@ -79,7 +89,7 @@ nvls_all_reduce_kernel(uint4* mc, const uint4* __restrict__ local, PeerTable fla
   }
   grid.sync();
   if (*reinterpret_cast<volatile int*>(abort_word)) return;
-  for (long long i = tid; i < n16; i += nthreads) out[i] = local[i];
+  for (long long j = tid; j < n16; j += nthreads) out[j] = local[j];
 }
 
 }  // namespace
@@ -103,7 +113,7 @@ const char* nvls_all_reduce(int dtype, void* mc, const void* local, const PeerTa
   void* fn = dtype == kF32 ? reinterpret_cast<void*>(nvls_all_reduce_kernel<float>)
                            : reinterpret_cast<void*>(nvls_all_reduce_kernel<__nv_bfloat16>);
   // a small grid: the switch does the arithmetic, the SMs only issue 16-byte requests
-  long long want = (n16 / world + 511) / 512;
+  long long want = (n16 + 2047) / 2048;
   int grid = static_cast<int>(want < 1 ? 1 : (want > num_sms ? num_sms : want));
   if (cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(512), args, 0, s) != cudaSuccess)
     return "nvls_all_reduce: cooperative launch failed";
