@@ -387,6 +387,11 @@ def main():
             report(f"flash fwd B{B} S{S} window {W_} (tcgen05, third form)", s, 0, flw)
             s = T(lambda: C.attention(q, k, v, scale=1.0 / 16, causal=True, window=W_, variant=1))
             report(f"flash fwd B{B} S{S} window {W_} (warp-level mma.sync)", s, 0, flw)
+            ow, lsew = C.lib().flash_fwd(q, k, v, 1.0 / 16, True, W_, 0, 0)
+            s = T(lambda: C.lib().flash_bwd(q, k, v, ow, lsew, do, 1.0 / 16, True, W_, 0, 0, None))
+            report(f"flash bwd B{B} S{S} window {W_} (tcgen05, dQ + dK/dV kernels)", s, 0, 2.5 * flw, "5 matmuls")
+            s = T(lambda: C.lib().flash_bwd(q, k, v, ow, lsew, do, 1.0 / 16, True, W_, 0, 1, None))
+            report(f"flash bwd B{B} S{S} window {W_} (warp-level mma.sync)", s, 0, 2.5 * flw, "5 matmuls")
             q2 = torch.randn(B, S, 16, 256, device=dev, dtype=bf)
             k2 = torch.randn(B, S, 2, 256, device=dev, dtype=bf)
             v2 = torch.randn(B, S, 2, 256, device=dev, dtype=bf)

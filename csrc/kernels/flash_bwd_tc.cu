@@ -1,4 +1,4 @@
-// Causal flash-attention backward on the 5th-generation tensor cores (head_dim 128).
+// Causal flash-attention backward on the 5th-generation tensor cores (head_dim 128, optional sliding window).
 //
 // Two kernels, both deterministic (no floating-point atomics; every accumulator lives in TMEM and is
 // summed in a fixed order):
@@ -13,6 +13,10 @@
 //                           S^T = K Q_i^T, dP^T = V dO_i^T
 //                           P^T, dS^T written to shared memory as K-major A operands
 //                           dV += P^T dO_i,  dK += dS^T Q_i        (accumulated in TMEM across tiles and heads)
+//
+// With a window of w keys (query i sees keys (i - w, i]) the dQ kernel starts at the first key tile any of its
+// rows sees and the dK/dV kernel stops at the last query tile that still has one of its keys in the window; only
+// tiles cut by the diagonal or by the window's lower edge take the masked path.
 //
 // Every operand is a natural-layout tile written by TMA with the 128-byte swizzle (no cluster
 // multicast).  Where the contraction runs over the tile's row index (dS K_j, P^T dO, dS^T Q) the
@@ -57,6 +61,7 @@ struct FlashBwdTcParams {
   __nv_bfloat16* dv; long long dv_bs, dv_ts;
   int B, S, Hq, Hkv;
   float scale;
+  int window;            // 0: plain causal; w > 0: query i sees keys (i - w, i]
   int* status;
   unsigned long long* debug;   // optional globaltimer stamps of CTA (0,0,0) of the dQ kernel: [step][8]
 };
@@ -132,7 +137,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int hq = blockIdx.y, b = blockIdx.z;
   const int hk = hq / (p.Hq / p.Hkv);
   const int q0 = qt * FT;
-  const int n_kv = qt + 1;
+  const int j_lo = p.window > 0 ? max(0, q0 - p.window + 1) / FT : 0;   // first key tile any row of this CTA sees
+  const int n_kv = qt + 1 - j_lo;                                        // steps j = 0 .. n_kv-1 walk key tiles j_lo + j
   unsigned long long* dbg = (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.debug : nullptr;
 
   if (threadIdx.x == 0) {
@@ -174,12 +180,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const uint32_t ph = (j / KRING) & 1;
         if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
         mbar_expect_tx(&k_full[st], TILE128);
-        tma_load_2d(sK + st * TILE128, &tmK, &k_full[st], hk * FD, b * p.S + j * FT);
-        tma_load_2d(sK + st * TILE128 + ATOM128, &tmK, &k_full[st], hk * FD + 64, b * p.S + j * FT);
+        tma_load_2d(sK + st * TILE128, &tmK, &k_full[st], hk * FD, b * p.S + (j_lo + j) * FT);
+        tma_load_2d(sK + st * TILE128 + ATOM128, &tmK, &k_full[st], hk * FD + 64, b * p.S + (j_lo + j) * FT);
         if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer)) break;
         mbar_expect_tx(v_full, TILE128);
-        tma_load_2d(sV, &tmV, v_full, hk * FD, b * p.S + j * FT);
-        tma_load_2d(sV + ATOM128, &tmV, v_full, hk * FD + 64, b * p.S + j * FT);
+        tma_load_2d(sV, &tmV, v_full, hk * FD, b * p.S + (j_lo + j) * FT);
+        tma_load_2d(sV + ATOM128, &tmV, v_full, hk * FD + 64, b * p.S + (j_lo + j) * FT);
       }
       if (*abort_flag) {
         for (int i = 0; i < 64; ++i) __nanosleep(10000);   // let copies in flight land before shared memory goes away
@@ -282,7 +288,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       if (stamp) dbg[j * 12 + 1] = globaltimer_ns();
       // dS without the softmax scale (it is applied once to dQ at the end), packed to bf16 in place
       uint32_t w[32];
-      if (j < qt && rows_ok) {               // warp-uniform: a tile strictly below the diagonal needs no mask
+      const int ja = j_lo + j;                // key tile of this step
+      // warp-uniform: a tile strictly below the diagonal and above the window's lower edge needs no mask
+      if (ja < qt && rows_ok && (p.window == 0 || q0 + FT - p.window <= ja * FT + half * 64)) {
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           const float d0 = exp2f(__uint_as_float(sv[2 * e]) * c - lse_c) * (__uint_as_float(dv[2 * e]) - dlt);
@@ -290,14 +298,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           w[e] = pack_bf16(d0, d1);
         }
       } else {
-        const int k0 = j * FT + half * 64;
-        int nvalid = row < p.S ? (j == qt ? row - k0 + 1 : 64) : 0;     // keys k0 .. k0+nvalid-1 are at or before the query
+        const int k0 = ja * FT + half * 64;
+        int nvalid = row < p.S ? (ja == qt ? row - k0 + 1 : 64) : 0;    // keys k0 .. k0+nvalid-1 are at or before the query
         nvalid = max(0, min(64, nvalid));
+        const int lo = p.window > 0 ? row - p.window + 1 - k0 : -(1 << 30);   // keys below k0+lo have left the window
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
           float d0 = 0.f, d1 = 0.f;
-          if (2 * e < nvalid) d0 = exp2f(__uint_as_float(sv[2 * e]) * c - lse_c) * (__uint_as_float(dv[2 * e]) - dlt);
-          if (2 * e + 1 < nvalid) d1 = exp2f(__uint_as_float(sv[2 * e + 1]) * c - lse_c) * (__uint_as_float(dv[2 * e + 1]) - dlt);
+          if (2 * e < nvalid && 2 * e >= lo) d0 = exp2f(__uint_as_float(sv[2 * e]) * c - lse_c) * (__uint_as_float(dv[2 * e]) - dlt);
+          if (2 * e + 1 < nvalid && 2 * e + 1 >= lo) d1 = exp2f(__uint_as_float(sv[2 * e + 1]) * c - lse_c) * (__uint_as_float(dv[2 * e + 1]) - dlt);
           w[e] = pack_bf16(d0, d1);
         }
       }
@@ -387,7 +396,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
   const int G = p.Hq / p.Hkv;
   const int n64 = (p.S + QH - 1) / QH;
   const int i_lo = 2 * kt;                                     // first 64-row query tile that can see these keys
-  const int cnt = n64 - i_lo;                                  // query tiles per head (>= 1)
+  // last 64-row query tile that still has one of these keys inside its window
+  const int i_hi = p.window > 0 ? min(n64 - 1, (kt * FT + FT - 1 + p.window - 1) / QH) : n64 - 1;
+  const int cnt = i_hi - i_lo + 1;                             // query tiles per head (>= 1)
   const int T = G * cnt;
   unsigned long long* dbg = (p.debug && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) ? p.debug + 512 : nullptr;
 
@@ -534,7 +545,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
       if (stamp) dbg[t * 12 + 1] = globaltimer_ns();
       // P^T and dS^T (without the softmax scale: it is applied once to dK at the end) as packed bf16
       uint32_t pw[16], dw[16];
-      if (qbase >= kt * FT + FT - 1 && qbase + 32 <= p.S) {     // warp-uniform: every query is real and at or after every key
+      // warp-uniform: every query is real, at or after every key, and no key has left any query's window
+      if (qbase >= kt * FT + FT - 1 && qbase + 32 <= p.S && (p.window == 0 || qbase + 31 - kt * FT < p.window)) {
 #pragma unroll
         for (int e2 = 0; e2 < 16; ++e2) {
           const float4 s4 = *reinterpret_cast<const float4*>(st_row + 2 * e2);     // {lse, delta} of two queries (broadcast read)
@@ -549,11 +561,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmK, const __grid_const
           const float4 s4 = *reinterpret_cast<const float4*>(st_row + 2 * e2);
           const int q = qbase + 2 * e2;
           float p0 = 0.f, p1 = 0.f, d0 = 0.f, d1 = 0.f;
-          if (q < p.S && key <= q) {
+          if (q < p.S && key <= q && (p.window == 0 || q - key < p.window)) {
             p0 = exp2f(__uint_as_float(sv[2 * e2]) * c - s4.x);
             d0 = p0 * (__uint_as_float(dv[2 * e2]) - s4.y);
           }
-          if (q + 1 < p.S && key <= q + 1) {
+          if (q + 1 < p.S && key <= q + 1 && (p.window == 0 || q + 1 - key < p.window)) {
             p1 = exp2f(__uint_as_float(sv[2 * e2 + 1]) * c - s4.z);
             d1 = p1 * (__uint_as_float(dv[2 * e2 + 1]) - s4.w);
           }
@@ -625,7 +637,7 @@ size_t flash_bwd_tc_scratch_floats(const FlashArgs& a) {
 
 bool flash_bwd_tc_supported(const FlashArgs& a) {
   auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-  return a.D == FD && a.causal && a.window == 0 && a.q_offset == 0 && a.Sq == a.Sk && a.Sq >= 1 && a.Hq % a.Hkv == 0 &&
+  return a.D == FD && a.causal && a.window >= 0 && a.q_offset == 0 && a.Sq == a.Sk && a.Sq >= 1 && a.Hq % a.Hkv == 0 &&
          a.q_bs == static_cast<long long>(a.Sq) * a.q_ts && a.k_bs == static_cast<long long>(a.Sk) * a.k_ts &&
          a.v_bs == static_cast<long long>(a.Sk) * a.v_ts && a.do_bs == static_cast<long long>(a.Sq) * a.do_ts &&
          (a.q_ts % 8) == 0 && (a.k_ts % 8) == 0 && (a.v_ts % 8) == 0 && (a.do_ts % 8) == 0 && (a.o_ts % 4) == 0 &&
@@ -659,7 +671,7 @@ const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream) {
   p.dq = static_cast<__nv_bfloat16*>(a.dq); p.dq_bs = a.dq_bs; p.dq_ts = a.dq_ts;
   p.dk = static_cast<__nv_bfloat16*>(a.dk); p.dk_bs = a.dk_bs; p.dk_ts = a.dk_ts;
   p.dv = static_cast<__nv_bfloat16*>(a.dv); p.dv_bs = a.dv_bs; p.dv_ts = a.dv_ts;
-  p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.status = status; p.debug = a.debug;
+  p.B = a.B; p.S = a.Sq; p.Hq = a.Hq; p.Hkv = a.Hkv; p.scale = a.scale; p.window = a.window; p.status = status; p.debug = a.debug;
   constexpr int smem_dq = 7 * TILE128 + 1024 + 256;
   constexpr int smem_dkv = 2 * TILE128 + 2 * NST * TILE64 + 2 * ATOM128 + NST * QH * 8 + 256;
   if (!FERRL_ONCE_PER_DEVICE(

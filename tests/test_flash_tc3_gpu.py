@@ -40,7 +40,10 @@ def test_tcgen05_flash_window_and_head_dim_256(B, S, Hq, Hkv, D, window, scale):
     close(out.float(), warp.float(), 1.2e-2)
 
 
-@pytest.mark.parametrize("S,Hq,Hkv,D,window", [(300, 4, 2, 128, 100), (333, 4, 1, 256, 0)])
+# head dim 128 with a window runs the tcgen05 backward kernels too (window masks in both of them);
+# head dim 256 takes the warp-level backward
+@pytest.mark.parametrize("S,Hq,Hkv,D,window", [(300, 4, 2, 128, 100), (333, 4, 1, 256, 0), (1536, 8, 4, 128, 1024),
+                                               (257, 4, 4, 128, 64), (200, 4, 2, 128, 4096), (700, 6, 2, 128, 129)])
 def test_backward_through_the_tcgen05_forward(S, Hq, Hkv, D, window):
     from ferrl_b200.ops import cuda as C, eager
     scale = D ** -0.5
@@ -53,3 +56,9 @@ def test_backward_through_the_tcgen05_forward(S, Hq, Hkv, D, window):
     eager.attention(*refs, scale=scale, causal=True, window=window).backward(do.float())
     for a, r in zip(leaves, refs):
         close(a.grad.float(), r.grad, 2e-2)
+    if D == 128:        # and the two backward implementations agree with each other
+        o2, lse2 = C.lib().flash_fwd(q, k, v, scale, True, window, 0, 1)
+        warp = C.lib().flash_bwd(q, k, v, o2, lse2, do.contiguous(), scale, True, window, 0, 1, None)
+        for a, w in zip(leaves, warp):
+            close(a.grad.float(), w.float(), 2e-2)
+        assert C.kernel_status() == 0
