@@ -38,6 +38,8 @@ struct GemmArgs {
   long long ar_stage_elems, ar_out_elems;                         // capacity of the symmetric staging / output buffers (bf16 elements)
   PeerTable ar_stage, ar_outbuf, ar_flags;
   unsigned long long* ar_debug;
+  // in-switch variant: multicast addresses of ar_stage / ar_outbuf (both or none), see GemmParams in tcgen05_gemm.cu
+  void* ar_mc_stage; void* ar_mc_outbuf;
   // launch as a programmatic dependent of the stream predecessor: weights are prefetched before the
   // dependency wait (only where B is never written by an earlier kernel of the same stream)
   int pdl;

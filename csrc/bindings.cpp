@@ -374,7 +374,8 @@ Tensor row_sumsq(const Tensor& x) {
 Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2,
                       const optional<Tensor>& residual, std::vector<int64_t> stage, std::vector<int64_t> outbuf,
                       std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t epoch, int64_t max_tiles,
-                      int64_t stage_elems, int64_t out_elems, double limit_s, const optional<Tensor>& debug) {
+                      int64_t stage_elems, int64_t out_elems, double limit_s, const optional<Tensor>& debug, int64_t mc_stage,
+                      int64_t mc_outbuf) {
   TORCH_CHECK(A.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_allreduce: bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1, "gemm_allreduce: shapes");
   c10::cuda::CUDAGuard guard(A.device());
@@ -397,6 +398,7 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   if (debug.has_value() && debug->defined() && debug->scalar_type() == at::kLong && debug->numel() >= 160 * 16 * 4)
     a.ar_debug = reinterpret_cast<unsigned long long*>(debug->data_ptr<int64_t>());
   a.ar_stage = table_of_fwd(stage); a.ar_outbuf = table_of_fwd(outbuf); a.ar_flags = table_of_fwd(flags);
+  a.ar_mc_stage = reinterpret_cast<void*>(mc_stage); a.ar_mc_outbuf = reinterpret_cast<void*>(mc_outbuf);
   FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
   return out;
 }
@@ -1336,7 +1338,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0, bool static_b=False) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("decode_gemm(Tensor A, Tensor B, Tensor? residual=None, int glu_act=-1, int max_clusters=0, bool static_b=False, Tensor? debug=None) -> Tensor", &decode_gemm);
   m.def("set_decode_gemm(bool on) -> ()", &set_decode_gemm);
-  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None) -> Tensor", &gemm_allreduce);
+  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None, int mc_stage=0, int mc_outbuf=0) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

@@ -62,6 +62,12 @@ struct GemmParams {
   int ar_max_tiles;
   uint64_t ar_limit_ns;
   unsigned long long* ar_debug;   // optional [grid][16 tiles][4] globaltimer stamps of the exchange
+  // In-switch variant (both non-null): `ar_stage` and `ar_outbuf` are bound to NVSwitch multicast objects and these
+  // are their multicast addresses.  Every rank then stores its partial of tile t in its OWN staging copy, slot t;
+  // the owner reads the sum of all copies with `multimem.ld_reduce` (the switch adds), and one `multimem.st` per
+  // chunk puts the reduced tile into every rank's receive buffer.  Flags, epochs and the copy-out are unchanged.
+  void* ar_mc_stage;
+  void* ar_mc_outbuf;
   // Launched as a programmatic dependent: the producer fills its ring with the weight (B) halves of
   // its first k-blocks, which no earlier kernel writes, before it waits for the stream predecessor;
   // only then does it fetch the activation (A) halves.  Everything else in the kernel is ordered
@@ -128,6 +134,18 @@ __device__ __forceinline__ uint4 pack8(const float* a) {
     op[e] = *reinterpret_cast<uint32_t*>(&h);
   }
   return o;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st16(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
 }
 __device__ __forceinline__ void add8(float* a, const uint4& x) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&x);
@@ -550,8 +568,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int out_tile = mi * n_tiles + ni;
       __nv_bfloat16* ar_slot = nullptr;
       if (AR)
-        ar_slot = static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
-                  (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
+        ar_slot = p.ar_mc_stage
+                      ? static_cast<__nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) + static_cast<long long>(out_tile) * (BM * BN)
+                      : static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
+                            (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
       LpRow lp;
       if (p.lp_mode) lp_begin(p, row, row_ok, lp);
 #pragma unroll 1
@@ -689,6 +709,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 0] = globaltimer_ns();
         if (!epi_sync()) break;
         if (et == 0) {
+          // in-switch variant: the partial sits in local memory and is read through the switch, by this
+          // rank's communication warps too, so it has to be performed at system scope first
+          if (p.ar_mc_stage) __threadfence_system();
           if (owner != p.ar_rank) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
           asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(drained))), "r"(it) : "memory");
         }
@@ -767,6 +790,46 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // U elements per round; the residual and WCH slots of each are requested before the first add
         // (the loop is bound by the latency of these loads, so what counts is how many are in flight)
         constexpr int U = 4, WCH = 4;
+        if (p.ar_mc_stage) {
+          // the switch forms the sum over all ranks' copies of slot `out_tile`; U requests in flight per thread
+          const uint4* mc_tile = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.ar_mc_stage) +
+                                                                static_cast<long long>(out_tile) * (BM * BN));
+          __nv_bfloat16* mc_out = static_cast<__nv_bfloat16*>(p.ar_mc_outbuf);
+          for (int i0 = ct; i0 < BM * CPR; i0 += 128 * U) {
+            uint4 x[U], resv[U];
+            bool live[U];
+            int rr_[U], cc_[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              const int i = i0 + u * 128;
+              const int rt = i / CPR, ch = i % CPR;
+              rr_[u] = mi * BM + rt;
+              cc_[u] = ni * BN + ch * 8;
+              live[u] = i < BM * CPR && rr_[u] < p.M && cc_[u] < p.N;
+              resv[u] = make_uint4(0u, 0u, 0u, 0u);
+              x[u] = make_uint4(0u, 0u, 0u, 0u);
+              if (live[u]) {
+                x[u] = multimem_ld_reduce_bf16(mc_tile + ch * BM + rt);
+                if (HAS_RES) resv[u] = *reinterpret_cast<const uint4*>(p.residual + static_cast<long long>(rr_[u]) * p.ldr + cc_[u]);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              if (!live[u]) continue;
+              uint4 o = x[u];
+              if (HAS_RES) {
+                float a8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) a8[e] = 0.f;
+                add8(a8, x[u]);
+                add8(a8, resv[u]);
+                o = pack8(a8);
+              }
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
+              multimem_st16(mc_out + static_cast<long long>(rr_[u]) * p.N + cc_[u], o);     // every rank's receive buffer at once
+            }
+          }
+        } else
         for (int i0 = ct; i0 < BM * CPR; i0 += 128 * U) {
           float a8[U][8];
           bool live[U];
@@ -970,6 +1033,13 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     p.ar_rank = a.ar_rank; p.ar_stage = a.ar_stage; p.ar_outbuf = a.ar_outbuf;
     p.ar_flags = a.ar_flags; p.ar_max_tiles = a.ar_max_tiles; p.ar_limit_ns = a.ar_limit_ns;
     p.ar_debug = a.ar_debug;
+    if ((a.ar_mc_stage != nullptr) != (a.ar_mc_outbuf != nullptr)) return "fused all-reduce: both multicast addresses or none";
+    if (a.ar_mc_stage) {
+      if (static_cast<long long>(out_tiles) * BM * BN > a.ar_stage_elems) return "fused all-reduce: staging buffer too small for one slot per tile";
+      if ((reinterpret_cast<uintptr_t>(a.ar_mc_stage) & 15) || (reinterpret_cast<uintptr_t>(a.ar_mc_outbuf) & 15))
+        return "fused all-reduce: multicast addresses must be 16-byte aligned";
+    }
+    p.ar_mc_stage = a.ar_mc_stage; p.ar_mc_outbuf = a.ar_mc_outbuf;
   }
   constexpr bool kArOk = !OUT_F32 && (BN == 256 || BN == 128 || BN == 64);
   if (p.ar_world > 1 && !kArOk) return "fused all-reduce: unsupported tile width or output type";

@@ -26,6 +26,34 @@ class NvlsUnavailable(RuntimeError):
     """No multicast address for this group (no NVSwitch, no driver support, or not one process per GPU)."""
 
 
+def alloc_multicast(heap: SymmHeap, nbytes: int, group=None):
+    """A symmetric buffer bound to an NVSwitch multicast object: ``(SymmBuffer, multicast address, handle)``.
+    Collective over the process group; raises ``NvlsUnavailable`` on every rank if any rank has no address."""
+    import torch.distributed as dist
+    from .symm import SymmBuffer
+    try:
+        import torch.distributed._symmetric_memory as symm_mem
+    except ImportError as e:  # pragma: no cover - depends on the torch build
+        raise NvlsUnavailable(f"torch has no symmetric-memory module: {e}") from e
+    if not dist.is_initialized():
+        raise NvlsUnavailable("torch.distributed is not initialised")
+    group = group if group is not None else dist.group.WORLD
+    nbytes = (int(nbytes) + 255) // 256 * 256
+    failure, mc, buf, handle, ptrs = None, 0, None, None, []
+    try:
+        with torch.cuda.device(heap.device):
+            buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=heap.device)
+            handle = symm_mem.rendezvous(buf, group)
+        mc = int(getattr(handle, "multicast_ptr", 0) or 0)
+        ptrs = [int(p) for p in handle.buffer_ptrs]
+    except Exception as e:  # noqa: BLE001 - any allocation / rendezvous failure means "not available here"
+        failure = e
+    ok = heap.comm.all_reduce_scalar_sum(1.0 if mc and len(ptrs) == heap.world else 0.0)
+    if ok != heap.world:
+        raise NvlsUnavailable(f"no multicast address on {heap.world - int(ok)} rank(s)" + (f": {failure}" if failure is not None else ""))
+    return SymmBuffer(buf, ptrs), mc, handle
+
+
 class NvlsAllReducer:
     def __init__(self, heap: SymmHeap, max_bytes: int, group=None):
         import torch.distributed as dist

@@ -84,19 +84,23 @@ class ParallelRuntime:
             rt.heap = (heap_factory or symm.SymmHeap)(comm, dev, wait_limit_s)
         if tensor_parallel and comm.world_size > 1 and rt.heap is not None:
             rows = max(int(max_rows), 128)
-            rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden))
             plain = symm.SymmAllReducer(rt.heap, rows * int(hidden) * 4)
             rt.all_reducer = plain
             how = "peer-memory"
             if (os.environ.get("FERRL_NVLS") == "1" if nvls is None else nvls) and on_gpu:
-                # in-switch reduction for the activations; shapes it does not take fall back to peer loads
+                # in-switch reduction, in the fused projection kernel and for the plain activation all-reduce
+                # (inputs the latter does not take fall back to peer loads)
                 from .nvls import NvlsAllReducer, NvlsUnavailable
                 try:
+                    rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden), nvls=True)
                     fast = NvlsAllReducer(rt.heap, rows * int(hidden) * 4)
                     rt.all_reducer = _FirstOf(fast, plain)
                     how = "NVLS multimem"
                 except NvlsUnavailable as e:
+                    rt.gemm_reducer = None
                     rt.notes.append(f"nvls unavailable: {e}")
+            if rt.gemm_reducer is None:
+                rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden))
             symm.register_gemm_all_reducer(comm, rt.gemm_reducer)
             symm.register_all_reducer(comm, rt.all_reducer)
             rt.notes.append(f"tp: fused gemm->all-reduce + {how} activation all-reduce")

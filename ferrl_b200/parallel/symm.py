@@ -141,15 +141,24 @@ class GemmAllReducer:
 
     BM, BN_MAX, BN_MIN = 128, 256, 64
 
-    def __init__(self, heap: SymmHeap, max_rows: int, max_cols: int):
+    def __init__(self, heap: SymmHeap, max_rows: int, max_cols: int, nvls: bool = False):
+        """``nvls``: staging and receive buffers bound to NVSwitch multicast objects; the tile owner then reads the
+        sum of all ranks' partials with ``multimem.ld_reduce`` and broadcasts the reduced tile with ``multimem.st``
+        (raises ``parallel.nvls.NvlsUnavailable`` on every rank where the group has no multicast address)."""
         self.heap = heap
         mt = (max_rows + self.BM - 1) // self.BM
         self.max_tiles = mt * ((max_cols + self.BN_MIN - 1) // self.BN_MIN)
         npad = (max_cols + self.BN_MAX - 1) // self.BN_MAX * self.BN_MAX
         self.stage_elems = mt * self.BM * npad + heap.world * self.BM * self.BN_MAX
         self.out_elems = max_rows * max_cols
-        self.stage = heap.alloc(self.stage_elems * 2)
-        self.outbuf = heap.alloc(self.out_elems * 2)
+        self.mc_stage = self.mc_outbuf = 0
+        if nvls:
+            from .nvls import alloc_multicast
+            self.stage, self.mc_stage, self._h1 = alloc_multicast(heap, self.stage_elems * 2)
+            self.outbuf, self.mc_outbuf, self._h2 = alloc_multicast(heap, self.out_elems * 2)
+        else:
+            self.stage = heap.alloc(self.stage_elems * 2)
+            self.outbuf = heap.alloc(self.out_elems * 2)
         # ready[tile][rank] and done[tile] flags, then the device-resident call counter and its CTA counter
         self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2) * 4)
         self.flags.local.zero_()
@@ -172,7 +181,7 @@ class GemmAllReducer:
         h = self.heap
         return h.C.lib().gemm_allreduce(a, b, a2, b2, residual, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
                                         h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
-                                        self.out_elems, h.wait_limit_s, debug)
+                                        self.out_elems, h.wait_limit_s, debug, self.mc_stage, self.mc_outbuf)
 
 
 _REDUCERS: dict = {}

@@ -36,11 +36,7 @@ def _time(fn, iters=10):
     return float(t)
 
 
-def main():
-    comm = TorchDistComm.bootstrap(timeout_s=120.0)
-    dev, world, rank = comm.device, comm.world_size, comm.rank
-    heap = SymmHeap(comm, dev, wait_limit_s=20.0)
-    red = GemmAllReducer(heap, 8192, 4096)
+def _check_reducer(comm, heap, red, dev, world, rank, what):
     for i, (M, N, K, use_res, use_lora) in enumerate([(300, 512, 256, False, False), (1000, 4096, 1024, True, True),
                                                       (128, 4096, 2048, True, False), (8192, 4096, 2048, True, True),
                                                       (300, 512, 256, True, False)]):
@@ -67,7 +63,41 @@ def main():
             err = float((y.float() - want).abs().max())
             assert err <= 0.02 * float(want.abs().max()), (M, N, K, rep, err)
             digest = hashlib.sha256(y.cpu().view(torch.int16).numpy().tobytes()).digest()
-            comm.require_consensus(digest, f"fused all-reduce output {M}x{N}x{K} rep {rep}")
+            comm.require_consensus(digest, f"{what} output {M}x{N}x{K} rep {rep}")
+
+
+def _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl):
+    """The in-switch form of the same kernel (FERRL_TEST_NVLS=1): same checks, its own timing line.  No rank
+    leaves this function before all have finished with the multicast-bound buffers."""
+    from ferrl_b200.parallel.nvls import NvlsUnavailable
+    try:
+        red = GemmAllReducer(heap, 8192, 4096, nvls=True)
+    except NvlsUnavailable as e:
+        if rank == 0:
+            print(f"TP_NVLS_UNAVAILABLE {e}")
+        return
+    failed = None
+    try:
+        _check_reducer(comm, heap, red, dev, world, rank, "in-switch fused all-reduce")
+        t = _time(lambda: red(a, b, None, None, res))
+        heap.check("in-switch timing")
+        if rank == 0:
+            print(f"TP_NVLS_TIMING world={world} M={a.shape[0]} N={b.shape[0]} K={a.shape[1]} fused_nvls_ms={t:.4f} gemm_nccl_ms={t_nccl:.4f}")
+    except BaseException as e:  # noqa: BLE001
+        failed = f"{type(e).__name__}: {e}"
+    torch.cuda.synchronize()
+    flags = comm.all_gather_bytes((failed or "").encode())
+    assert not any(flags), [f.decode() for f in flags if f]
+    if rank == 0:
+        print("TP_NVLS_PASS")
+
+
+def main():
+    comm = TorchDistComm.bootstrap(timeout_s=120.0)
+    dev, world, rank = comm.device, comm.world_size, comm.rank
+    heap = SymmHeap(comm, dev, wait_limit_s=20.0)
+    red = GemmAllReducer(heap, 8192, 4096)
+    _check_reducer(comm, heap, red, dev, world, rank, "fused all-reduce")
 
     # timing: training-shaped row-parallel projection, fused vs. GEMM followed by NCCL
     M, N, K = 8192, 4096, 12288 // world
@@ -86,6 +116,8 @@ def main():
     if rank == 0:
         print(f"TP_TIMING world={world} M={M} N={N} K={K} fused_ms={t_fused:.4f} gemm_nccl_ms={t_nccl:.4f} "
               f"gemm_only_ms={t_gemm:.4f}")
+    if os.environ.get("FERRL_TEST_NVLS") == "1":
+        _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl)
 
     # model-level equivalence: tensor-parallel layers with and without the fused kernel
     from ferrl_b200.models.dense import DenseGradModel, DenseSpec
