@@ -709,9 +709,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 0] = globaltimer_ns();
         if (!epi_sync()) break;
         if (et == 0) {
-          // in-switch variant: the partial sits in local memory and is read through the switch, by this
-          // rank's communication warps too, so it has to be performed at system scope first
-          if (p.ar_mc_stage) __threadfence_system();
+          // in-switch variant: the partial sits in local memory and is read through the switch.  For a peer's
+          // tile the system-scope release below orders it; for a tile of this rank the hand-over to the
+          // communication warps is only CTA-scoped, so the partial is made visible device-wide first
+          if (p.ar_mc_stage && owner == p.ar_rank) __threadfence();
           if (owner != p.ar_rank) st_release_sys(ar_ready(p.ar_flags, owner, out_tile, p.ar_rank), ar_epoch);
           asm volatile("st.release.cta.shared::cta.u32 [%0], %1;" ::"r"(smem_u32(const_cast<int*>(drained))), "r"(it) : "memory");
         }
@@ -792,6 +793,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         constexpr int U = 4, WCH = 4;
         if (p.ar_mc_stage) {
           // the switch forms the sum over all ranks' copies of slot `out_tile`; U requests in flight per thread
+          // (more would spill: the epilogue warps of this kernel set the register budget)
           const uint4* mc_tile = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.ar_mc_stage) +
                                                                 static_cast<long long>(out_tile) * (BM * BN));
           __nv_bfloat16* mc_out = static_cast<__nv_bfloat16*>(p.ar_mc_outbuf);
