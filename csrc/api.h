@@ -196,6 +196,8 @@ const char* flash_bwd_tc(const FlashArgs& a, int* status, cudaStream_t stream);
 
 // ---- vocabulary rows ----
 // finish of the head GEMM's log-prob epilogue (GemmArgs::lp_mode 1): ws [n_tiles, M] float2, tl [M]
+// the same combine for one vocabulary shard: stats [M, 3] = (max, sum exp(z - max), target logit or 0)
+const char* logprob_shard_stats(const float* ws, const float* tl, int n_tiles, int M, float* stats, cudaStream_t s);
 const char* logprob_finalize(const float* ws, const float* tl, int n_tiles, int M, float* lp, float* lse, cudaStream_t s);
 const char* logprob_rows(int dtype, const void* logits, long long ld, const long long* targets, float* lp, float* lse,
                          long long rows, int V, float temperature, float softcap, cudaStream_t s);

@@ -1163,6 +1163,23 @@ std::tuple<Tensor, Tensor> logprob_head_fwd(const Tensor& hidden, const Tensor& 
   return {lp, lse};
 }
 
+// One vocabulary shard of the head (rows col0 .. col0 + Vs of the full head): per row (max, sum exp(z - max), target
+// logit or 0 when the target lies in another shard), fp32 [M, 3].  The caller merges the shards' partials.
+Tensor logprob_head_shard_stats(const Tensor& hidden, const Tensor& w, const Tensor& targets, double temperature, double softcap,
+                                int64_t col0) {
+  ferrl::GemmArgs a{};
+  lp_head_common(a, hidden, w, targets, temperature, softcap, "logprob_head_shard_stats");
+  c10::cuda::CUDAGuard guard(hidden.device());
+  const int n_tiles = (a.N + 255) / 256;
+  auto f32 = hidden.options().dtype(at::kFloat);
+  Tensor ws = out_empty({n_tiles, a.M, 2}, f32), tl = out_zeros({a.M}, f32), stats = out_empty({a.M, 3}, f32);
+  if (a.M == 0) return stats;
+  a.lp_mode = 1; a.lp_ws = ws.data_ptr<float>(); a.lp_tl = tl.data_ptr<float>(); a.ldo = a.N; a.lp_col0 = col0;
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  FERRL_CHECK(ferrl::logprob_shard_stats(ws.data_ptr<float>(), tl.data_ptr<float>(), n_tiles, a.M, stats.data_ptr<float>(), stream()));
+  return stats;
+}
+
 // Gradient of sum_rows coef[row] * (-lp[row]) with respect to the raw logits of the vocabulary slice `w`
 // ([Vc, H] rows col0 .. col0+Vc of the head), written as bf16 [M, Vc]: the softmax is recomputed in the
 // GEMM epilogue from the saved lse.
@@ -1382,6 +1399,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("flash_fwd(Tensor q, Tensor k, Tensor v, float scale, bool causal, int window, int q_offset, int variant=0) -> (Tensor, Tensor)", &flash_fwd);
   m.def("flash_bwd(Tensor q, Tensor k, Tensor v, Tensor o, Tensor lse, Tensor d_o, float scale, bool causal, int window, int q_offset, int variant=0, Tensor? debug=None) -> (Tensor, Tensor, Tensor)", &flash_bwd);
   m.def("logprob_head_fwd(Tensor hidden, Tensor w, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_head_fwd);
+  m.def("logprob_head_shard_stats(Tensor hidden, Tensor w, Tensor targets, float temperature, float softcap, int col0) -> Tensor", &logprob_head_shard_stats);
   m.def("logprob_head_dlogits(Tensor hidden, Tensor w, Tensor targets, Tensor lse, Tensor coef, float temperature, float softcap, int col0) -> Tensor", &logprob_head_dlogits);
   m.def("logprob_rows(Tensor logits, Tensor targets, float temperature, float softcap) -> (Tensor, Tensor)", &logprob_rows);
   m.def("logprob_rows_bwd(Tensor(a!) logits, Tensor targets, Tensor lse, Tensor dlp, float temperature, float softcap) -> ()", &logprob_rows_bwd);

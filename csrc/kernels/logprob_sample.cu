@@ -432,6 +432,31 @@ __global__ void logprob_finalize_kernel(const float2* __restrict__ ws, const flo
   lp[row] = tl[row] - l;
 }
 
+// Vocabulary-sharded form: the same combine, but the result stays a partial (max, sum exp, target logit) per row,
+// to be merged with the other shards' partials (tensor-parallel head).  stats [M, 3].
+__global__ void logprob_shard_stats_kernel(const float2* __restrict__ ws, const float* __restrict__ tl, int n_tiles, int M,
+                                           float* __restrict__ stats) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= M) return;
+  float m = -INFINITY;
+  for (int t = 0; t < n_tiles; ++t) m = fmaxf(m, ws[static_cast<long long>(t) * M + row].x);
+  float s = 0.f;
+  for (int t = 0; t < n_tiles; ++t) {
+    const float2 v = ws[static_cast<long long>(t) * M + row];
+    s += v.y * __expf(v.x - m);
+  }
+  stats[3 * row] = m;
+  stats[3 * row + 1] = s;
+  stats[3 * row + 2] = tl[row];
+}
+
+const char* logprob_shard_stats(const float* ws, const float* tl, int n_tiles, int M, float* stats, cudaStream_t s) {
+  if (M == 0) return nullptr;
+  logprob_shard_stats_kernel<<<(M + 127) / 128, 128, 0, s>>>(reinterpret_cast<const float2*>(ws), tl, n_tiles, M, stats);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? nullptr : "logprob_shard_stats launch failed";
+}
+
 const char* logprob_finalize(const float* ws, const float* tl, int n_tiles, int M, float* lp, float* lse, cudaStream_t s) {
   if (M == 0) return nullptr;
   logprob_finalize_kernel<<<(M + 127) / 128, 128, 0, s>>>(reinterpret_cast<const float2*>(ws), tl, n_tiles, M, lp, lse);

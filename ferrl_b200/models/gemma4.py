@@ -331,6 +331,14 @@ class Gemma4GradModel(nn.Module):
         idx = (win_start.view(B, 1).long() + torch.arange(L, device=ids.device)[None, :]).clamp(max=ids.shape[1] - 1)
         hw = torch.gather(h, 1, idx[:, :, None].expand(B, L, h.shape[-1]))
         hw = ops.rmsnorm(hw, self.final_norm, self.spec.rms_norm_eps)
+        if comm is not None and comm.world_size > 1 and self.tp is not None and not self.full_ft:
+            # tensor parallelism: every rank scores 1 / world of the (tied, replicated) vocabulary and the ranks
+            # exchange three floats per row instead of each evaluating the whole 262144-row head
+            from ..parallel.tp import sharded_logprob_gather
+            lp = sharded_logprob_gather(hw.reshape(B * L, -1), self.embed, targets.reshape(-1), temperature,
+                                        self.spec.final_logit_softcapping, comm)
+            if lp is not None:
+                return lp.view(B, L)
         return ops.logprob_gather(hw.reshape(B * L, -1), self.embed, targets.reshape(-1), temperature,
                                   self.spec.final_logit_softcapping, head_wt=self.head_t).view(B, L)
 

@@ -144,8 +144,30 @@ def main():
     assert float((outs[0][0] - outs[1][0]).abs().max()) < 0.05 * float(outs[0][0].abs().max())
     for g0, g1 in zip(outs[0][1], outs[1][1]):
         assert float((g0 - g1).abs().max()) <= 0.08 * float(g0.abs().max()) + 1e-6
+    # vocabulary-sharded log-prob head: each rank scores 1 / world of the vocabulary in the head GEMM's epilogue
+    from ferrl_b200.parallel.tp import sharded_logprob_gather
+    gen = torch.Generator(device=dev).manual_seed(23)
+    Nr, Hh, Vv = 700, 256, 1024 * world
+    hh = (torch.randn(Nr, Hh, device=dev, generator=gen) * 0.7).to(torch.bfloat16)
+    ww = (torch.randn(Vv, Hh, device=dev, generator=gen) * 0.05).to(torch.bfloat16)
+    tt = torch.randint(0, Vv, (Nr,), device=dev, generator=gen)
+    dlp = torch.randn(Nr, device=dev, generator=gen)
+    for cap, temp in ((0.0, 1.0), (30.0, 0.7)):
+        h1 = hh.clone().requires_grad_()
+        lp1 = sharded_logprob_gather(h1, ww, tt, temp, cap, comm)
+        assert lp1 is not None
+        lp1.backward(dlp)
+        h2 = hh.clone().requires_grad_()
+        lp2 = C.logprob_gather(h2, ww, tt, temp, cap)
+        lp2.backward(dlp)
+        heap.check("sharded head")
+        assert float((lp1 - lp2).abs().max()) < 2e-3 * max(1.0, float(lp2.abs().max())), float((lp1 - lp2).abs().max())
+        rel = float((h1.grad.float() - h2.grad.float()).norm() / h2.grad.float().norm())
+        assert rel < 1.5e-2, rel
+        comm.require_consensus(hashlib.sha256(lp1.detach().cpu().numpy().tobytes()).digest(), "sharded head log-probs")
     comm.barrier()
     if rank == 0:
+        print("TP_SHARDED_HEAD_PASS")
         print("TP_FUSED_PASS")
     dist.destroy_process_group()
 

@@ -363,3 +363,35 @@ def test_discovery_bundle_publication_failure_leaves_nothing(tmp_path):
     assert D.verify_artifact_bundle(art.output)["candidate_sha256"] == rec.digest()
     with pytest.raises(D.InvalidConfiguration, match="already exists"):
         D.publish_verified_artifact(out, D.TaskIdentity("t"), "run", b"{}", b"{}", rec, ev)
+
+
+@pytest.mark.parametrize("world,softcap,temperature", [(2, 0.0, 1.0), (4, 30.0, 0.7)])
+def test_vocabulary_sharded_logprob_head_equals_the_full_head_on_thread_ranks(world, softcap, temperature):
+    """Each tensor-parallel rank scores 1 / world of the vocabulary; values and hidden-state gradients must equal
+    the unsharded log-softmax gather, identically on every rank."""
+    import torch
+    from ferrl_b200.comm import run_ranks
+    from ferrl_b200.ops import eager
+    from ferrl_b200.parallel.tp import sharded_logprob_gather
+    g = torch.Generator().manual_seed(3)
+    N, H, V = 37, 24, 64 * world
+    h0 = torch.randn(N, H, generator=g)
+    w = torch.randn(V, H, generator=g) * 0.5
+    t = torch.randint(0, V, (N,), generator=g)
+    dlp = torch.randn(N, generator=g)
+    hr = h0.clone().requires_grad_()
+    ref = eager.logprob_gather(hr, w, t, temperature, softcap)
+    ref.backward(dlp)
+
+    def body(comm):
+        h = h0.clone().requires_grad_()
+        lp = sharded_logprob_gather(h, w, t, temperature, softcap, comm)
+        assert lp is not None
+        lp.backward(dlp)
+        return lp.detach(), h.grad
+    outs = run_ranks(world, body, timeout=60)
+    for lp, grad in outs:
+        assert torch.allclose(lp, ref.detach(), atol=2e-5, rtol=1e-5)
+        assert torch.allclose(grad, hr.grad, atol=2e-5, rtol=1e-4)
+        assert torch.equal(lp, outs[0][0]) and torch.equal(grad, outs[0][1])      # every rank holds the same bits
+    assert sharded_logprob_gather(h0, w[:V - 1], t.clamp(max=V - 2), 1.0, 0.0, type("C", (), {"world_size": world, "rank": 0})()) is None

@@ -1058,3 +1058,26 @@ def test_train_verb_turns_a_peer_wait_timeout_into_comm_timeout_on_every_rank(tm
                                 tokenizer=SyntheticTokenizer(32, 4, 8), heap_factory=factory)
         return True
     assert run_ranks(2, body, timeout=120) == [True, True]
+
+
+def test_parallel_runtime_ignores_the_in_switch_request_off_gpu_and_composes_reducers():
+    """``nvls=True`` only takes effect for CUDA ranks; on CPU ranks the runtime keeps the plain reducers.  The
+    composed reducer hands an input to its second member when the first declines it."""
+    from ferrl_b200.comm import run_ranks
+    from ferrl_b200.parallel.runtime import ParallelRuntime, _FirstOf
+
+    def body(comm):
+        rt = ParallelRuntime.create(comm, "cpu", tensor_parallel=True, hidden=64, max_rows=8,
+                                    heap_factory=lambda c, d, l: _FakeHeap(c, d, l), nvls=True)
+        kind = type(rt.all_reducer).__name__
+        notes = list(rt.notes)
+        rt.close()
+        return kind, notes
+    for kind, notes in run_ranks(2, body, timeout=60):
+        assert kind == "SymmAllReducer" and any("peer-memory" in n for n in notes)
+    calls = []
+    first = lambda x: (calls.append("first"), None if x.numel() % 2 else x + 1)[1]    # noqa: E731
+    second = lambda x: (calls.append("second"), x + 2)[1]                              # noqa: E731
+    both = _FirstOf(first, second)
+    assert torch.equal(both(torch.zeros(4)), torch.ones(4)) and calls == ["first"]
+    assert torch.equal(both(torch.zeros(3)), torch.full((3,), 2.0)) and calls == ["first", "first", "second"]
