@@ -144,9 +144,12 @@ __global__ void __launch_bounds__(512) dp_step_kernel(DpStepParams p) {
   }
 }
 
-// One-shot sum all-reduce of a symmetric buffer (bf16 or fp32), used for tensor-parallel
-// activations: barrier, every rank reads all peers' copies of its output range in rank order,
-// barrier. Deterministic and identical on every rank.
+// Sum all-reduce of a symmetric buffer (bf16 or fp32), used for tensor-parallel activations.  Deterministic and
+// identical on every rank (every element is summed once, in rank order, by one rank).
+//   world <= 2  one shot: barrier, every rank reads all peers' copies of the whole range, barrier;
+//   world  > 2  two shots: rank r sums slice r of all copies and stores the result into slice r of EVERY copy
+//               (in place: nobody else reads slice r), barrier, every rank copies its now complete local buffer
+//               out.  Per rank 2 (world-1)/world n elements cross NVLink instead of (world-1) n.
 template <typename T>
 __global__ void __launch_bounds__(512) symm_all_reduce_kernel(PeerTable src, PeerTable flags, T* __restrict__ out,
                                                              long long n, int rank, int world, uint32_t epoch,
@@ -161,8 +164,14 @@ __global__ void __launch_bounds__(512) symm_all_reduce_kernel(PeerTable src, Pee
   if (*reinterpret_cast<volatile int*>(abort_word)) return;
   constexpr int VEC = 16 / sizeof(T);
   const long long nv = n / VEC;
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nv;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool two_shot = world > 2;
+  // the 16-byte units this rank sums: everything (one shot) or its slice (two shots; the last rank takes the remainder)
+  const long long per = two_shot ? nv / world : nv;
+  const long long lo = two_shot ? per * rank : 0;
+  const long long hi = two_shot ? (rank == world - 1 ? nv : lo + per) : nv;
+  for (long long i = lo + tid; i < hi; i += nthreads) {
     float acc[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
@@ -176,20 +185,38 @@ __global__ void __launch_bounds__(512) symm_all_reduce_kernel(PeerTable src, Pee
     T* ov = reinterpret_cast<T*>(&o);
 #pragma unroll
     for (int e = 0; e < VEC; ++e) ov[e] = from_f<T>(acc[e]);
-    reinterpret_cast<uint4*>(out)[i] = o;
+    if (two_shot) {
+      for (int q = 0; q < world; ++q) reinterpret_cast<uint4*>(src.ptr[q])[i] = o;
+    } else {
+      reinterpret_cast<uint4*>(out)[i] = o;
+    }
   }
-  for (long long i = nv * VEC + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    float acc = 0.f;
-    for (int q = 0; q < world; ++q) acc += to_f(static_cast<const T*>(src.ptr[q])[i]);
-    out[i] = from_f<T>(acc);
+  // the tail that does not fill a 16-byte unit: rank 0's job in the two-shot form
+  if (!two_shot || rank == 0) {
+    for (long long i = nv * VEC + tid; i < n; i += nthreads) {
+      float acc = 0.f;
+      for (int q = 0; q < world; ++q) acc += to_f(static_cast<const T*>(src.ptr[q])[i]);
+      if (two_shot) {
+        for (int q = 0; q < world; ++q) static_cast<T*>(src.ptr[q])[i] = from_f<T>(acc);
+      } else {
+        out[i] = from_f<T>(acc);
+      }
+    }
   }
   grid.sync();
-  // trailing barrier: nobody may overwrite its source buffer until every peer has read it
+  // trailing barrier: one shot - nobody may overwrite its source buffer until every peer has read it;
+  // two shots - every slice has been reduced and stored into this rank's copy
   if (blockIdx.x == 0 && threadIdx.x == 0) {
     bool ok = peer_barrier(flags, 3, rank, world, epoch, limit_ns, status);
     if (!ok) *abort_word = 1;
+    __threadfence();
   }
+  if (!two_shot) return;
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(abort_word)) return;
+  const T* mine = static_cast<const T*>(src.ptr[rank]);
+  for (long long i = tid; i < nv; i += nthreads) reinterpret_cast<uint4*>(out)[i] = reinterpret_cast<const uint4*>(mine)[i];
+  for (long long i = nv * VEC + tid; i < n; i += nthreads) out[i] = mine[i];
 }
 
 }  // namespace
