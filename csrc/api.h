@@ -152,6 +152,12 @@ int dp_step_grid(int num_sms);
 const char* symm_all_reduce(int dtype, const PeerTable& src, const PeerTable& flags, void* out, long long n, int rank,
                             int world, unsigned epoch, unsigned long long limit_ns, int* status, int* abort_word,
                             int num_sms, cudaStream_t s);
+// The halves of that all-reduce for sequence-sharded tensor parallelism: which = 0 reduce-scatter (src: every rank's
+// full partial [world * n_shard], out: this rank's summed slice [n_shard]); 1 all-gather (src: every rank's shard,
+// out: all rows [world * n_shard]).
+const char* symm_row_collective(int which, int dtype, const PeerTable& src, const PeerTable& flags, void* out, long long n_shard,
+                                int rank, int world, unsigned epoch, unsigned long long limit_ns, int* status, int* abort_word,
+                                int num_sms, cudaStream_t s);
 // NVLS form (csrc/symm/nvls_all_reduce.cu): `mc` is the multicast address of the symmetric buffer whose local
 // copy is `local`; in place in the buffer, then copied to `out`.  nbytes a multiple of 16 * world.
 const char* nvls_all_reduce(int dtype, void* mc, const void* local, const PeerTable& flags, void* out, long long nbytes, int rank,

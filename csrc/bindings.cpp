@@ -1334,6 +1334,16 @@ void symm_all_reduce(std::vector<int64_t> src, std::vector<int64_t> flags, Tenso
                                      status_word(), abort_word.data_ptr<int>(), num_sms(), stream()));
 }
 
+void symm_row_collective(int64_t which, std::vector<int64_t> src, std::vector<int64_t> flags, Tensor out, int64_t n_shard, int64_t rank,
+                         int64_t world, int64_t epoch, double limit_s, Tensor abort_word) {
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(out.is_contiguous() && (which == 0 ? out.numel() == n_shard : out.numel() == n_shard * world),
+              "symm_row_collective: contiguous output of n_shard (reduce-scatter) or world * n_shard (all-gather) elements");
+  FERRL_CHECK(ferrl::symm_row_collective(static_cast<int>(which), dt(out), table_of(src), table_of(flags), out.data_ptr(), n_shard, rank,
+                                         world, static_cast<unsigned>(epoch), static_cast<unsigned long long>(limit_s * 1e9),
+                                         status_word(), abort_word.data_ptr<int>(), num_sms(), stream()));
+}
+
 void nvls_all_reduce(int64_t mc_ptr, Tensor local, std::vector<int64_t> flags, Tensor out, int64_t rank, int64_t world,
                      int64_t epoch, double limit_s, Tensor abort_word) {
   c10::cuda::CUDAGuard guard(out.device());
@@ -1410,6 +1420,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("symm_close(int ptr) -> ()", &symm_close);
   m.def("dp_step(int[] grads, int[] reduced, int[] flags, int[] scalars, int rank, int world, int barrier_world, int own_lo, int own_hi, int n, int epoch, float pre_scale, float uncovered_local, Tensor tables, int off_blk_tensor, int off_blk_off, int off_blk_flat, int n_blocks, int chunk, float lr, float b1, float b2, float eps, float wd, int step, float max_norm, Tensor(a!) block_partials, Tensor(b!) out, Tensor(c!) abort_word, float limit_s) -> ()", &dp_step);
   m.def("dp_tables(Tensor[] params, Tensor[] m, Tensor[] v, int[] flat_off, int chunk) -> (Tensor, int, int, int, int)", &dp_tables);
+  m.def("symm_row_collective(int which, int[] src, int[] flags, Tensor(a!) out, int n_shard, int rank, int world, int epoch, float limit_s, Tensor(b!) abort_word) -> ()", &symm_row_collective);
   m.def("nvls_all_reduce(int mc_ptr, Tensor local, int[] flags, Tensor(a!) out, int rank, int world, int epoch, float limit_s, Tensor(b!) abort_word) -> ()", &nvls_all_reduce);
   m.def("symm_all_reduce(int[] src, int[] flags, Tensor(a!) out, int rank, int world, int epoch, float limit_s, Tensor(b!) abort_word) -> ()", &symm_all_reduce);
   m.def("launches() -> int", &launches);

@@ -219,6 +219,88 @@ __global__ void __launch_bounds__(512) symm_all_reduce_kernel(PeerTable src, Pee
   for (long long i = nv * VEC + tid; i < n; i += nthreads) out[i] = mine[i];
 }
 
+// The two halves of the all-reduce as collectives of their own, for sequence-sharded tensor parallelism (the
+// residual stream holds 1 / world of the token rows between a row-parallel projection and the next column-parallel
+// one).  Rows are contiguous, so a shard is a contiguous range of n_shard elements.
+//   reduce-scatter: src[q] holds rank q's full partial [world * n_shard]; rank r sums slice r over q (rank order)
+//                   into `out` [n_shard].  Leading barrier: all partials staged; trailing: all slices read.
+//   all-gather:     src[q] holds rank q's shard [n_shard]; every rank copies all shards into `out` [world * n_shard].
+template <typename T>
+__global__ void __launch_bounds__(512) symm_reduce_scatter_kernel(PeerTable src, PeerTable flags, T* __restrict__ out,
+                                                                 long long n_shard, int rank, int world, uint32_t epoch,
+                                                                 uint64_t limit_ns, int* status, int* abort_word) {
+  cg::grid_group grid = cg::this_grid();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    bool ok = peer_barrier(flags, 6, rank, world, epoch, limit_ns, status);
+    *abort_word = ok ? 0 : 1;
+    __threadfence();
+  }
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(abort_word)) return;
+  constexpr int VEC = 16 / sizeof(T);
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const long long base = n_shard * rank;                       // first element of this rank's slice in every partial
+  const bool vec = (n_shard % VEC) == 0;                       // then every slice starts on a 16-byte boundary
+  const long long nv = vec ? n_shard / VEC : 0;
+  for (long long i = tid; i < nv; i += nthreads) {
+    float acc[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
+    for (int q = 0; q < world; ++q) {
+      uint4 raw = reinterpret_cast<const uint4*>(static_cast<const T*>(src.ptr[q]) + base)[i];
+      const T* v = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e) acc[e] += to_f(v[e]);
+    }
+    uint4 o;
+    T* ov = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) ov[e] = from_f<T>(acc[e]);
+    reinterpret_cast<uint4*>(out)[i] = o;
+  }
+  for (long long i = nv * VEC + tid; i < n_shard; i += nthreads) {
+    float acc = 0.f;
+    for (int q = 0; q < world; ++q) acc += to_f(static_cast<const T*>(src.ptr[q])[base + i]);
+    out[i] = from_f<T>(acc);
+  }
+  grid.sync();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    bool ok = peer_barrier(flags, 7, rank, world, epoch, limit_ns, status);
+    if (!ok) *abort_word = 1;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512) symm_all_gather_kernel(PeerTable src, PeerTable flags, T* __restrict__ out,
+                                                             long long n_shard, int rank, int world, uint32_t epoch,
+                                                             uint64_t limit_ns, int* status, int* abort_word) {
+  cg::grid_group grid = cg::this_grid();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    bool ok = peer_barrier(flags, 6, rank, world, epoch, limit_ns, status);
+    *abort_word = ok ? 0 : 1;
+    __threadfence();
+  }
+  grid.sync();
+  if (*reinterpret_cast<volatile int*>(abort_word)) return;
+  constexpr int VEC = 16 / sizeof(T);
+  const long long tid = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long nthreads = static_cast<long long>(gridDim.x) * blockDim.x;
+  const bool vec = (n_shard % VEC) == 0;
+  const long long nv = vec ? n_shard / VEC : 0;
+  for (int q = 0; q < world; ++q) {
+    const T* from = static_cast<const T*>(src.ptr[q]);
+    T* to = out + n_shard * q;
+    for (long long i = tid; i < nv; i += nthreads) reinterpret_cast<uint4*>(to)[i] = reinterpret_cast<const uint4*>(from)[i];
+    for (long long i = nv * VEC + tid; i < n_shard; i += nthreads) to[i] = from[i];
+  }
+  grid.sync();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    bool ok = peer_barrier(flags, 7, rank, world, epoch, limit_ns, status);
+    if (!ok) *abort_word = 1;
+  }
+}
+
 }  // namespace
 
 const char* dp_step(const DpStepParams& p, int num_sms, cudaStream_t s) {
@@ -252,6 +334,28 @@ const char* symm_all_reduce(int dtype, const PeerTable& src, const PeerTable& fl
                            : reinterpret_cast<void*>(symm_all_reduce_kernel<__nv_bfloat16>);
   if (cudaLaunchCooperativeKernel(fn, dim3(grid), dim3(512), args, 0, s) != cudaSuccess)
     return "symm_all_reduce: cooperative launch failed";
+  count_launch();
+  return nullptr;
+}
+
+// which: 0 reduce-scatter (src = full partials, out = this rank's slice), 1 all-gather (src = shards, out = all rows)
+const char* symm_row_collective(int which, int dtype, const PeerTable& src, const PeerTable& flags, void* out, long long n_shard,
+                                int rank, int world, unsigned epoch, unsigned long long limit_ns, int* status, int* abort_word,
+                                int num_sms, cudaStream_t s) {
+  if (world < 1 || world > kMaxRanks) return "symm_row_collective: world size out of range";
+  if (n_shard == 0) return nullptr;
+  if ((n_shard * (dtype == kF32 ? 4 : 2)) % 16 == 0 && (reinterpret_cast<uintptr_t>(out) & 15)) return "symm_row_collective: output must be 16-byte aligned";
+  PeerTable a = src, f = flags;
+  uint32_t ep = epoch;
+  uint64_t lim = limit_ns;
+  void* args[] = {&a, &f, &out, &n_shard, &rank, &world, &ep, &lim, &status, &abort_word};
+  void* fn;
+  if (which == 0)
+    fn = dtype == kF32 ? reinterpret_cast<void*>(symm_reduce_scatter_kernel<float>) : reinterpret_cast<void*>(symm_reduce_scatter_kernel<__nv_bfloat16>);
+  else
+    fn = dtype == kF32 ? reinterpret_cast<void*>(symm_all_gather_kernel<float>) : reinterpret_cast<void*>(symm_all_gather_kernel<__nv_bfloat16>);
+  if (cudaLaunchCooperativeKernel(fn, dim3(num_sms), dim3(512), args, 0, s) != cudaSuccess)
+    return "symm_row_collective: cooperative launch failed";
   count_launch();
   return nullptr;
 }

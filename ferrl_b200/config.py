@@ -268,6 +268,9 @@ class TensorParallelCfg:
     enabled: bool = False
     rank: int = 0
     world_size: int = 1
+    # addition: keep the residual stream sharded over the token rows between the projections (reduce-scatter after
+    # the row-parallel ones, all-gather in front of the column-parallel ones); model families that support it
+    sequence_parallel: bool = False
 
 
 @dataclass

@@ -196,6 +196,23 @@ class Gemma4Layer(nn.Module):
         o = self.o.forward_reduce(a.reshape(B, S, self.hq * self.D), comm, merged)
         return h + ops.rmsnorm(o, self.post_attn_norm, self.eps)
 
+    # ---- sequence-sharded forms: ``hs`` holds this rank's block of the flattened [B * S, H] token rows
+    def attn_half_sp(self, hs, B, S, positions, cos, sin, comm, merged=False):
+        from ..parallel import sp
+        lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
+        x = sp.gather_rows_tp(ops.rmsnorm(hs, self.input_norm, self.eps), comm).view(B, S, -1)
+        q, k, v = self._qkv(x, positions, cos, sin, lin)
+        a = ops.attention(q, k, v, scale=1.0, causal=True, window=self.window, softmax_fp32=True)
+        o = sp.scatter_rows_sum(lin(self.o, a.reshape(B * S, self.hq * self.D)), comm)      # this rank's rows of the sum
+        return hs + ops.rmsnorm(o, self.post_attn_norm, self.eps)
+
+    def mlp_half_sp(self, hs, comm, merged=False):
+        from ..parallel import sp
+        lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
+        x = sp.gather_rows_tp(ops.rmsnorm(hs, self.pre_ffn_norm, self.eps), comm)
+        d = sp.scatter_rows_sum(lin(self.down, ops.swiglu(lin(self.gate_up, x), self.act)), comm)
+        return (hs + ops.rmsnorm(d, self.post_ffn_norm, self.eps)) * self.layer_scalar
+
     def mlp_half(self, h, comm, merged=False):
         lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
         x = copy_to_tp(ops.rmsnorm(h, self.pre_ffn_norm, self.eps), comm)
@@ -226,10 +243,13 @@ class Gemma4Layer(nn.Module):
 class Gemma4GradModel(nn.Module):
     def __init__(self, spec: Gemma4Spec, lora: Optional[LoraSpec] = None, *, dtype=torch.float32, device=None,
                  tp: Optional[TensorParallelPlan] = None, keep_transpose: Optional[bool] = None,
-                 quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False, full_ft: bool = False):
+                 quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False, full_ft: bool = False,
+                 sequence_parallel: bool = False):
         super().__init__()
         spec.validate()
         self.spec, self.lora, self.tp, self.remat, self.full_ft, self.dtype = spec, lora, tp, remat, full_ft, dtype
+        # training / scoring forward with the residual stream sharded over the token rows (``parallel/sp.py``)
+        self.sequence_parallel = bool(sequence_parallel)
         dev = torch.device(device) if device is not None else torch.device("cpu")
         if keep_transpose is None:
             keep_transpose = dev.type == "cuda" and not full_ft
@@ -306,6 +326,19 @@ class Gemma4GradModel(nn.Module):
         positions = torch.arange(S, device=ids.device)
         h = ops.embedding(ids, self.embed, self.embed_scale)
         use_remat = self.remat and torch.is_grad_enabled() and not detached
+        if self.sequence_parallel and comm.world_size > 1 and kv_out is None and (B * S) % comm.world_size == 0:
+            from ..parallel import sp
+            hs = sp.shard_rows(h.reshape(B * S, -1), comm)
+            for layer in self.layers:
+                cos, sin = self._tables(layer)
+                params = layer.adapter_params() if not self.full_ft else list(layer.parameters())
+                if use_remat:
+                    hs = remat_segment(lambda x, l=layer, c=cos, s=sin: l.attn_half_sp(x, B, S, positions, c, s, comm, merged), hs, params)
+                    hs = remat_segment(lambda x, l=layer: l.mlp_half_sp(x, comm, merged), hs, params)
+                else:
+                    hs = layer.attn_half_sp(hs, B, S, positions, cos, sin, comm, merged)
+                    hs = layer.mlp_half_sp(hs, comm, merged)
+            return sp.gather_rows_replicated(hs, comm).view(B, S, -1)
         for i, layer in enumerate(self.layers):
             cos, sin = self._tables(layer)
             params = layer.adapter_params() if not self.full_ft else list(layer.parameters())

@@ -178,6 +178,10 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
                       ep=(comm.rank, comm.world_size) if ep_on else None,
                       adapter_seed=pc.seed)
     model, pident = model_and_identity or load_auto_policy(cfg.model_dir, opts)
+    if cfg.tensor_parallel.enabled and cfg.tensor_parallel.sequence_parallel:
+        if not hasattr(model, "sequence_parallel"):
+            raise OrchestrationError("tensor_parallel.sequence_parallel is not supported by this model family")
+        model.sequence_parallel = True
     if tokenizer is None:
         from .tokenizer import HfTokenizer
         tokenizer = HfTokenizer.from_file(cfg.model_dir)

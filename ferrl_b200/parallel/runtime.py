@@ -67,6 +67,7 @@ class ParallelRuntime:
     gemm_reducer: Optional[object] = None
     all_reducer: Optional[object] = None
     ep_context: Optional[object] = None
+    row_collectives: Optional[object] = None
     notes: list = field(default_factory=list)
 
     @classmethod
@@ -103,6 +104,11 @@ class ParallelRuntime:
                 rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden))
             symm.register_gemm_all_reducer(comm, rt.gemm_reducer)
             symm.register_all_reducer(comm, rt.all_reducer)
+            if on_gpu:
+                # reduce-scatter / all-gather over the token rows for sequence-sharded models (parallel/sp.py)
+                from . import sp
+                rt.row_collectives = sp.RowCollectives(rt.heap, rows * int(hidden) * 4)
+                sp.register_row_collectives(comm, rt.row_collectives)
             rt.notes.append(f"tp: fused gemm->all-reduce + {how} activation all-reduce")
         if expert_parallel is not None and comm.world_size > 1:
             e = expert_parallel
@@ -129,5 +135,8 @@ class ParallelRuntime:
             EP.install(None)
         symm._GEMM_REDUCERS.pop(id(self.comm), None)
         symm._REDUCERS.pop(id(self.comm), None)
+        if self.row_collectives is not None:
+            from . import sp
+            sp.register_row_collectives(self.comm, None)
         if self.heap is not None and hasattr(self.heap, "close"):
             self.heap.close()

@@ -92,6 +92,58 @@ def _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl):
         print("TP_NVLS_PASS")
 
 
+def _sequence_parallel_checks(comm, heap, dev, world, rank):
+    """Row collectives over the symmetric heap against the Comm seam, and a Gemma-style stack with the residual
+    stream sharded over the token rows against the replicated layout (outputs and adapter gradients)."""
+    from ferrl_b200.models.gemma4 import Gemma4GradModel, Gemma4Spec
+    from ferrl_b200.models.lora import LoraSpec
+    from ferrl_b200.parallel import sp
+    from ferrl_b200.parallel.tp import TensorParallelPlan
+    rc = sp.RowCollectives(heap, 4096 * 512 * 4)
+    for it, (rows, cols, dtype) in enumerate([(64 * world, 512, torch.bfloat16), (3 * world, 37, torch.float32), (4096, 256, torch.bfloat16)]):
+        gen = torch.Generator(device=dev).manual_seed(900 + 10 * it + rank)
+        x = torch.randn(rows, cols, device=dev, generator=gen).to(dtype)
+        got = rc.reduce_scatter(x)
+        heap.check("reduce-scatter")
+        want = sp._reduce_scatter_value(x, comm)                      # no collectives registered yet: Comm seam
+        tol = (2.0 ** -7 if dtype == torch.bfloat16 else 1e-5) * max(1.0, float(want.float().abs().max()))
+        assert got is not None and float((got.float() - want.float()).abs().max()) <= tol
+        shard = got
+        full = rc.all_gather(shard)
+        heap.check("all-gather")
+        assert full is not None and torch.equal(full, sp._all_gather_value(shard, comm))
+    sp.register_row_collectives(comm, rc)
+    hq = max(4, world)
+    spec = Gemma4Spec(vocab_size=512 * world, hidden_size=256, num_hidden_layers=2, num_attention_heads=hq, num_key_value_heads=hq,
+                      head_dim=64, global_head_dim=64, num_global_key_value_heads=hq, intermediate_size=512,
+                      layer_types=["sliding_attention", "full_attention"], sliding_window=32, max_position_embeddings=128)
+    plan = TensorParallelPlan.new(rank, world, hq, hq, 512)
+    ids = torch.randint(0, spec.vocab_size, (2, 16 * world), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+    outs = []
+    for seq_par in (False, True):
+        model = Gemma4GradModel(spec, LoraSpec(rank=8, alpha=16.0), dtype=torch.bfloat16, device=dev, tp=plan,
+                                sequence_parallel=seq_par)
+        model.init_random(seed=21)
+        with torch.no_grad():
+            for l in model.layers:          # scores are q.k without 1/sqrt(d): keep them of order ten, as trained norms do
+                l.q_norm.fill_(0.3)
+                l.k_norm.fill_(0.3)
+            for i, q in enumerate(model.trainable_params()):
+                q.copy_(torch.randn(q.shape, device=dev, generator=torch.Generator(device=dev).manual_seed(70 + i)) * 0.05)
+        h = model.forward_hidden(ids, comm)
+        h.float().pow(2).mean().backward()
+        outs.append((h.detach().float(), [q.grad.detach().float().clone() for q in model.trainable_params()]))
+    heap.check("sequence-parallel model")
+    sp.register_row_collectives(comm, None)
+    ref, got = outs
+    assert float((ref[0] - got[0]).abs().max()) < 0.05 * float(ref[0].abs().max()), float((ref[0] - got[0]).abs().max())
+    for g0, g1 in zip(ref[1], got[1]):
+        assert float((g0 - g1).abs().max()) <= 0.08 * float(g0.abs().max()) + 1e-6
+    comm.barrier()
+    if rank == 0:
+        print("TP_SEQUENCE_PARALLEL_PASS")
+
+
 def main():
     comm = TorchDistComm.bootstrap(timeout_s=120.0)
     dev, world, rank = comm.device, comm.world_size, comm.rank
@@ -168,6 +220,8 @@ def main():
     comm.barrier()
     if rank == 0:
         print("TP_SHARDED_HEAD_PASS")
+    _sequence_parallel_checks(comm, heap, dev, world, rank)
+    if rank == 0:
         print("TP_FUSED_PASS")
     dist.destroy_process_group()
 

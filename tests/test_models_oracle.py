@@ -234,8 +234,9 @@ def make_ckpt(d):
     return t
 
 
+@pytest.mark.parametrize("sequence_parallel", [False, True])
 @pytest.mark.parametrize("remat", [False, True])
-def test_gemma4_tensor_parallel_training_matches_single_rank(tmp_path, remat):
+def test_gemma4_tensor_parallel_training_matches_single_rank(tmp_path, remat, sequence_parallel):
     """Gemma 4 is the family the reference trains tensor-parallel (with activation checkpointing):
     two thread ranks that stream only their own rows/columns of a checkpoint reproduce the
     unsharded logits, and their replicated-adapter gradients sum to the unsharded gradients."""
@@ -255,6 +256,7 @@ def test_gemma4_tensor_parallel_training_matches_single_rank(tmp_path, remat):
     def body(comm):
         m = load_auto_policy(d, LoaderOpts(tp=(comm.rank, comm.world_size), remat=remat))[0]
         assert m.layers[0].qkv.weight.shape[0] * 2 == single.layers[0].qkv.weight.shape[0]      # a real shard
+        m.sequence_parallel = sequence_parallel          # residual stream sharded over the token rows between projections
         with torch.no_grad():
             for a, b in zip(m.trainable_params(), single.trainable_params()):
                 a.copy_(b)
