@@ -40,6 +40,9 @@ struct GemmArgs {
   unsigned long long* ar_debug;
   // in-switch variant: multicast addresses of ar_stage / ar_outbuf (both or none), see GemmParams in tcgen05_gemm.cu
   void* ar_mc_stage; void* ar_mc_outbuf;
+  // reduce-scatter form: rank r keeps rows [r M/world, (r+1) M/world) of the sum in `out` [M/world, N] and nothing is sent back
+  // (M a multiple of world x 128, no residual, peer-load staging only)
+  int ar_scatter;
   // launch as a programmatic dependent of the stream predecessor: weights are prefetched before the
   // dependency wait (only where B is never written by an earlier kernel of the same stream)
   int pdl;

@@ -375,7 +375,7 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
                       const optional<Tensor>& residual, std::vector<int64_t> stage, std::vector<int64_t> outbuf,
                       std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t epoch, int64_t max_tiles,
                       int64_t stage_elems, int64_t out_elems, double limit_s, const optional<Tensor>& debug, int64_t mc_stage,
-                      int64_t mc_outbuf) {
+                      int64_t mc_outbuf, bool scatter) {
   TORCH_CHECK(A.is_cuda() && A.scalar_type() == at::kBFloat16 && B.scalar_type() == at::kBFloat16, "gemm_allreduce: bf16");
   TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.size(1) == B.size(1) && A.stride(1) == 1 && B.stride(1) == 1, "gemm_allreduce: shapes");
   c10::cuda::CUDAGuard guard(A.device());
@@ -386,7 +386,10 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
     TORCH_CHECK(B2.has_value() && B2->defined() && A2->stride(1) == 1 && B2->stride(1) == 1, "gemm_allreduce: side operands");
     a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
   }
-  Tensor out = out_empty({a.M, a.N}, A.options());
+  // reduce-scatter form: this rank's M / world rows of the sum
+  TORCH_CHECK(!scatter || (world > 1 && a.M % (world * 128) == 0), "gemm_allreduce: the reduce-scatter form needs rows % (world x 128) == 0");
+  Tensor out = out_empty({scatter ? a.M / world : a.M, a.N}, A.options());
+  a.ar_scatter = scatter ? 1 : 0;
   a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = false;
   if (residual.has_value() && residual->defined()) { a.residual = residual->data_ptr(); a.ldr = residual->stride(0); }
   a.status = status_word(); a.num_sms = num_sms();
@@ -1365,7 +1368,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("gemm(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, bool out_f32, int force_bn, int force_split, int two_cta=0, Tensor? debug=None, int cluster_k=0, int stream_k=0, bool static_b=False) -> Tensor", &gemm);  // two_cta: 0 auto, -1 never, 128/256 forced
   m.def("decode_gemm(Tensor A, Tensor B, Tensor? residual=None, int glu_act=-1, int max_clusters=0, bool static_b=False, Tensor? debug=None) -> Tensor", &decode_gemm);
   m.def("set_decode_gemm(bool on) -> ()", &set_decode_gemm);
-  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None, int mc_stage=0, int mc_outbuf=0) -> Tensor", &gemm_allreduce);
+  m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None, int mc_stage=0, int mc_outbuf=0, bool scatter=False) -> Tensor", &gemm_allreduce);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

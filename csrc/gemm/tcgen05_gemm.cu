@@ -68,6 +68,13 @@ struct GemmParams {
   // chunk puts the reduced tile into every rank's receive buffer.  Flags, epochs and the copy-out are unchanged.
   void* ar_mc_stage;
   void* ar_mc_outbuf;
+  // Reduce-scatter form (ar_scatter != 0, M a multiple of ar_world x BM): the owner of a tile is the rank that keeps
+  // its rows, step 2 ends with the store into the owner's `out` [M / ar_world, N], and step 3 does not exist.  Each
+  // rank walks the row blocks starting with its successor's and ending with its own, so the peers' partials of a tile
+  // are in place when its owner reaches it.  Nothing flows back to the senders tile by tile; instead every rank's last
+  // CTA publishes fin[rank] = call number on all peers, and a rank waits for fin >= previous call on its peers before
+  // its first push of a call (both forms do: a sender may otherwise run ahead into staging slots still being summed).
+  int ar_scatter;
   // Launched as a programmatic dependent: the producer fills its ring with the weight (B) halves of
   // its first k-blocks, which no earlier kernel writes, before it waits for the stream predecessor;
   // only then does it fetch the activation (A) halves.  Everything else in the kernel is ordered
@@ -107,6 +114,9 @@ __device__ __forceinline__ uint32_t* ar_ready(const PeerTable& f, int rank_mem, 
 }
 __device__ __forceinline__ uint32_t* ar_done(const PeerTable& f, int rank_mem, int max_tiles, int tile) {
   return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * kMaxRanks + tile;
+}
+__device__ __forceinline__ uint32_t* ar_fin(const PeerTable& f, int rank_mem, int max_tiles, int from) {
+  return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * (kMaxRanks + 1) + 2 + from;
 }
 __device__ __forceinline__ bool flag_reached(const uint32_t* flag, uint32_t epoch) {
   return static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0;   // epochs only grow; tolerates wrap-around
@@ -339,6 +349,38 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   tile_coords_mn(tile / split_k, m_tiles, n_tiles, group_m, mi, ni);
 }
 
+// Tile order of the fused collective forms.  All-reduce: the plain order.  Reduce-scatter: row block by row block,
+// the successor's first and this rank's own last (the plain order inside a block).
+template <bool AR>
+__device__ __forceinline__ void tile_coords_ar(int ar_scatter, int ar_rank, int ar_world, int tile, int m_tiles, int n_tiles,
+                                               int group_m, int split_k, int& ks, int& mi, int& ni) {
+  if (AR && ar_scatter) {
+    const int mt_per = m_tiles / ar_world, per = mt_per * n_tiles;
+    const int blk = tile / per;
+    int owner = ar_rank + 1 + blk;
+    if (owner >= ar_world) owner -= ar_world;
+    int ml;
+    tile_coords_mn(tile - blk * per, mt_per, n_tiles, group_m, ml, ni);
+    mi = owner * mt_per + ml;
+    ks = 0;
+  } else {
+    tile_coords(tile, m_tiles, n_tiles, group_m, split_k, ks, mi, ni);
+  }
+}
+// owner of an output tile and the first staging slot of its group of ar_world slots in the owner's buffer
+__device__ __forceinline__ void ar_owner_slot(int ar_scatter, int ar_world, int m_tiles, int n_tiles, int mi, int ni,
+                                              int& owner, long long& slot0) {
+  if (ar_scatter) {
+    const int mt_per = m_tiles / ar_world;
+    owner = mi / mt_per;
+    slot0 = (static_cast<long long>(mi - owner * mt_per) * n_tiles + ni) * ar_world;
+  } else {
+    const int out_tile = mi * n_tiles + ni;
+    owner = out_tile % ar_world;
+    slot0 = static_cast<long long>(out_tile / ar_world) * ar_world;
+  }
+}
+
 // OUT_F32: write fp32 instead of bf16.  HAS_RES: add a bf16 residual tile before the store.
 // AR: fused all-reduce mode (compiled separately so the plain kernel carries none of its registers).
 // rstd of one row from the partial sums of squares its producer wrote (summed in part order, 16 loads in
@@ -430,7 +472,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int pre = 0;          // k-blocks of the first tile whose loads were issued around the dependency wait
       if (p.pdl && static_cast<int>(blockIdx.x) < total_tiles) {
         int ks, mi, ni;
-        tile_coords(blockIdx.x, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, blockIdx.x, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
         const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
         pre = min(C::STAGES, kb_end - kb_begin);
         for (int i = 0; i < pre; ++i) {           // first pass over the ring: every stage is free
@@ -451,7 +493,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int ks, mi, ni;
-        tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
         int b_row0 = ni * BN;
         if (p.tile_expert) {
           const int e = p.tile_expert[mi];
@@ -499,7 +541,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         if (p.tile_expert) {
           int ks_, mi_, ni_;
-          tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks_, mi_, ni_);
+          tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks_, mi_, ni_);
           if (p.tile_expert[mi_] < 0) continue;
         }
         const int acc = (it++) & 1;
@@ -550,7 +592,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int ks, mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+      tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       if (p.tile_expert && p.tile_expert[mi] < 0) continue;
       const int row = mi * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -567,11 +609,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const int out_tile = mi * n_tiles + ni;
       __nv_bfloat16* ar_slot = nullptr;
-      if (AR)
+      int owner = 0;
+      if (AR) {
+        long long slot0;
+        ar_owner_slot(p.ar_scatter, p.ar_world, m_tiles, n_tiles, mi, ni, owner, slot0);
         ar_slot = p.ar_mc_stage
                       ? static_cast<__nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) + static_cast<long long>(out_tile) * (BM * BN)
-                      : static_cast<__nv_bfloat16*>(p.ar_stage.ptr[out_tile % p.ar_world]) +
-                            (static_cast<long long>(out_tile / p.ar_world) * p.ar_world + p.ar_rank) * (BM * BN);
+                      : static_cast<__nv_bfloat16*>(p.ar_stage.ptr[owner]) + (slot0 + p.ar_rank) * (BM * BN);
+        if (it == 1) {
+          // first push of this call: every peer must have left the previous call, or its staging slots may still be read
+          if (et == 0) {
+            bool ok = true;
+            for (int q2 = 0; q2 < p.ar_world && ok; ++q2)
+              if (q2 != p.ar_rank)
+                ok = ar_wait_flag(ar_fin(p.ar_flags, p.ar_rank, p.ar_max_tiles, q2), ar_epoch - 1, p.ar_limit_ns, p.status);
+            if (!ok) *abort_flag = 1;
+          }
+          if (!epi_sync()) break;
+        }
+      }
       LpRow lp;
       if (p.lp_mode) lp_begin(p, row, row_ok, lp);
 #pragma unroll 1
@@ -705,7 +761,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // The exchange itself belongs to the communication warps below; here the tile is only
         // announced.  One system-scope release per tile, by one thread: the barrier orders the other
         // threads' stores before it.  A tile this rank owns is announced through shared memory.
-        const int owner = out_tile % p.ar_world;
         if (p.ar_debug && et == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 0] = globaltimer_ns();
         if (!epi_sync()) break;
         if (et == 0) {
@@ -765,10 +820,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     bool live_c = true;
     for (int tile = blockIdx.x; tile < total_tiles && live_c; tile += gridDim.x) {
       int ks, mi, ni;
-      tile_coords(tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+      tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       ++it;
       const int out_tile = mi * n_tiles + ni;
-      const int owner = out_tile % p.ar_world;
+      int owner;
+      long long slot_first;
+      ar_owner_slot(p.ar_scatter, p.ar_world, m_tiles, n_tiles, mi, ni, owner, slot_first);
+      const int row_shift = p.ar_scatter ? p.ar_rank * (m_tiles / p.ar_world) * BM : 0;   // `out` holds this rank's rows only
       if (owner == p.ar_rank) {
         if (ct == 0) {
           // my own partial is in place once the epilogue has drained tile number `it`
@@ -786,8 +844,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (!comm_sync()) break;
         const uint4* slot0 = reinterpret_cast<const uint4*>(
-            static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) +
-            static_cast<long long>(out_tile / p.ar_world) * p.ar_world * (BM * BN));
+            static_cast<const __nv_bfloat16*>(p.ar_stage.ptr[p.ar_rank]) + slot_first * (BM * BN));
         // U elements per round; the residual and WCH slots of each are requested before the first add
         // (the loop is bound by the latency of these loads, so what counts is how many are in flight)
         constexpr int U = 4, WCH = 4;
@@ -870,13 +927,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (!live[u]) continue;
             if (HAS_RES) add8(a8[u], resv[u]);
             const uint4 o = pack8(a8[u]);
-            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u]) * p.ldo + cc_[u]) = o;
+            *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + static_cast<long long>(rr_[u] - row_shift) * p.ldo + cc_[u]) = o;
+            if (p.ar_scatter) continue;
             const long long off = static_cast<long long>(rr_[u]) * p.N + cc_[u];
             for (int q2 = 0; q2 < p.ar_world; ++q2)
               if (q2 != p.ar_rank) *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.ar_outbuf.ptr[q2]) + off) = o;
           }
         }
         if (p.ar_debug && ct == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 2] = globaltimer_ns();
+        if (p.ar_scatter) continue;
         if (!comm_sync()) break;
         if (ct == 0) {
           // the release store orders this thread's view (which includes the other threads' pushes,
@@ -887,6 +946,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
       }
       if (p.ar_debug && ct == 0) p.ar_debug[(blockIdx.x * 16 + min(it - 1, 15)) * 4 + 3] = globaltimer_ns();
+      if (p.ar_scatter) continue;
       // take one finished tile of a peer if its flag is already here
       const int pt = peer_tile(pull_u);
       if (ct == 0)
@@ -898,7 +958,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
     }
     // final sweep: the tiles whose flags had not arrived yet
-    if (!*abort_flag) {
+    if (!*abort_flag && !p.ar_scatter) {
       for (int pt = peer_tile(pull_u); pt < out_tiles; pull_u += gridDim.x, pt = peer_tile(pull_u)) {
         if (ct == 0 && !ar_wait_flag(ar_done(p.ar_flags, p.ar_rank, p.ar_max_tiles, pt), ar_epoch, p.ar_limit_ns, p.status))
           *abort_flag = 1;
@@ -915,6 +975,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (atomicAdd(ar_epoch_word + 1, 1u) == gridDim.x - 1) {   // last CTA out: next call uses the next number
       ar_epoch_word[1] = 0u;
       __threadfence();
+      // every read of this rank's staging slots is over: peers may push the next call's partials
+      for (int q2 = 0; q2 < p.ar_world; ++q2)
+        if (q2 != p.ar_rank) st_release_sys(ar_fin(p.ar_flags, q2, p.ar_max_tiles, p.ar_rank), ar_epoch);
       *reinterpret_cast<volatile uint32_t*>(ar_epoch_word) = ar_epoch;
     }
   }
@@ -1042,6 +1105,11 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
         return "fused all-reduce: multicast addresses must be 16-byte aligned";
     }
     p.ar_mc_stage = a.ar_mc_stage; p.ar_mc_outbuf = a.ar_mc_outbuf;
+    if (a.ar_scatter) {
+      if (a.M % (p.ar_world * BM) || a.residual || a.ar_mc_stage)
+        return "fused reduce-scatter: M must be a multiple of world x 128; no residual, no multicast staging";
+      p.ar_scatter = 1;
+    }
   }
   constexpr bool kArOk = !OUT_F32 && (BN == 256 || BN == 128 || BN == 64);
   if (p.ar_world > 1 && !kArOk) return "fused all-reduce: unsupported tile width or output type";

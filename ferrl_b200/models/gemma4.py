@@ -203,14 +203,14 @@ class Gemma4Layer(nn.Module):
         x = sp.gather_rows_tp(ops.rmsnorm(hs, self.input_norm, self.eps), comm).view(B, S, -1)
         q, k, v = self._qkv(x, positions, cos, sin, lin)
         a = ops.attention(q, k, v, scale=1.0, causal=True, window=self.window, softmax_fp32=True)
-        o = sp.scatter_rows_sum(lin(self.o, a.reshape(B * S, self.hq * self.D)), comm)      # this rank's rows of the sum
+        o = self.o.forward_reduce_scatter(a.reshape(B * S, self.hq * self.D), comm, merged)   # this rank's rows of the sum
         return hs + ops.rmsnorm(o, self.post_attn_norm, self.eps)
 
     def mlp_half_sp(self, hs, comm, merged=False):
         from ..parallel import sp
         lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
         x = sp.gather_rows_tp(ops.rmsnorm(hs, self.pre_ffn_norm, self.eps), comm)
-        d = sp.scatter_rows_sum(lin(self.down, ops.swiglu(lin(self.gate_up, x), self.act)), comm)
+        d = self.down.forward_reduce_scatter(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged)
         return (hs + ops.rmsnorm(d, self.post_ffn_norm, self.eps)) * self.layer_scalar
 
     def mlp_half(self, h, comm, merged=False):

@@ -285,6 +285,27 @@ class FusedLoraLinear(nn.Module):
         y = reduce_from_tp(self.forward_merged(x) if merged else self.forward(x), comm)
         return y if residual is None else residual + y
 
+    def forward_reduce_scatter(self, x: torch.Tensor, comm, merged: bool = False) -> torch.Tensor:
+        """Row-parallel use under sequence sharding: ``x`` is ``[rows, in_local]`` and the result is this rank's
+        ``rows / world`` rows of the tensor-parallel sum.  On GPUs with a registered ``GemmAllReducer`` the sum and
+        the scatter happen in the GEMM kernel; otherwise the projection is followed by ``scatter_rows_sum``."""
+        from ..parallel import sp
+        if comm.world_size > 1 and x.is_cuda and x.dim() == 2:
+            from ..parallel.symm import gemm_all_reducer
+            red = gemm_all_reducer(comm)
+            if red is not None:
+                from ..ops import cuda as _c
+                gather = lambda g: sp.all_gather_rows_value(g, comm)  # noqa: E731
+                if merged:
+                    w = self.weight_merged if self.weight_merged is not None else self.weight
+                    y = _c.lora_linear_reduce_scatter(x, w, None, None, None, red, gather)
+                else:
+                    a, b = self._stacks()
+                    y = _c.lora_linear_reduce_scatter(x, self.weight, a, b, self.weight_t, red, gather)
+                if y is not None:
+                    return y
+        return sp.scatter_rows_sum(self.forward_merged(x) if merged else self.forward(x), comm)
+
     def forward_merged(self, x: torch.Tensor, residual=None) -> torch.Tensor:
         """Rollout path over the merged snapshot (no adapter side path)."""
         w = self.weight_merged if self.weight_merged is not None else self.weight

@@ -187,6 +187,46 @@ class _LoraLinearReduce(torch.autograd.Function):
         return dx, None, None, da, db, dres, None
 
 
+class _LoraLinearReduceScatter(torch.autograd.Function):
+    """Row-parallel projection whose tensor-parallel sum is reduce-scattered over the token rows inside the GEMM
+    kernel: the result is this rank's ``rows / world`` rows.  Backward all-gathers the row shards of the cotangent
+    (``gather``: shard -> all rows) and then runs the local backward of the projection."""
+
+    @staticmethod
+    def forward(ctx, x, w, wt, a_stack, b_stack, reducer, gather):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        t = a16 = b16 = None
+        if a_stack is not None:
+            a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()
+            b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()
+            t = gemm(x2, a16)
+        y = reducer.reduce_scatter(x2, w, t, b16)
+        ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
+        ctx.x_shape = x.shape
+        ctx.x_grad = x.requires_grad
+        ctx.res_grad = False
+        ctx.gather = gather
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        dx, _, _, da, db, _ = _LoraLinear.backward(ctx, ctx.gather(dy.contiguous()))
+        return dx, None, None, da, db, None, None
+
+
+def lora_linear_reduce_scatter(x, w, a_stack, b_stack, wt, reducer, gather):
+    """This rank's rows of ``sum_r (x_r W_rᵀ + (x_r A_rᵀ) Bᵀ)``, ``[rows / world, out]``, in one kernel per rank;
+    ``None`` when the shapes do not fit (the caller then projects and reduce-scatters separately)."""
+    if not (_bf16(x) and _bf16(w)) or w.requires_grad or x.shape[-1] % 8:
+        return None
+    rows = x.numel() // x.shape[-1]
+    if not reducer.fits_scatter(rows, w.shape[0]):
+        return None
+    return _LoraLinearReduceScatter.apply(x, w, wt, a_stack, b_stack, reducer, gather)
+
+
 def lora_linear_reduce(x, w, a_stack, b_stack, wt, reducer, residual=None):
     """``all_reduce(x Wᵀ + (x Aᵀ) Bᵀ) (+ residual)`` in one kernel per rank; ``None`` when the
     shapes do not fit the reducer's symmetric buffers (the caller then reduces separately)."""

@@ -160,6 +160,11 @@ class _ShardRows(torch.autograd.Function):
         return _all_gather_value(g.contiguous(), ctx.comm), None
 
 
+def all_gather_rows_value(x: torch.Tensor, comm: Comm) -> torch.Tensor:
+    """All ranks' row shards of ``x`` in rank order, outside autograd (used by backward passes)."""
+    return _all_gather_value(x, comm)
+
+
 def gather_rows_tp(x, comm):
     return x if comm.world_size == 1 else _GatherTP.apply(x, comm)
 

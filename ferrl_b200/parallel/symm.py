@@ -159,8 +159,9 @@ class GemmAllReducer:
         else:
             self.stage = heap.alloc(self.stage_elems * 2)
             self.outbuf = heap.alloc(self.out_elems * 2)
-        # ready[tile][rank] and done[tile] flags, then the device-resident call counter and its CTA counter
-        self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2) * 4)
+        # ready[tile][rank] and done[tile] flags, the device-resident call counter and its CTA counter, then
+        # fin[rank]: the last call each peer has left (a sender waits for it before it reuses the staging slots)
+        self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2 + MAX_RANKS) * 4)
         self.flags.local.zero_()
         if torch.device(heap.device).type == "cuda":
             torch.cuda.synchronize(heap.device)
@@ -182,6 +183,21 @@ class GemmAllReducer:
         return h.C.lib().gemm_allreduce(a, b, a2, b2, residual, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
                                         h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
                                         self.out_elems, h.wait_limit_s, debug, self.mc_stage, self.mc_outbuf)
+
+    def fits_scatter(self, rows: int, cols: int) -> bool:
+        """The reduce-scatter form: whole 128-row tiles per rank, peer-load staging."""
+        return self.mc_stage == 0 and rows % (self.heap.world * self.BM) == 0 and self.fits(rows, cols)
+
+    def reduce_scatter(self, a, b, a2=None, b2=None) -> torch.Tensor:
+        """Rows ``[rank * M / world, (rank + 1) * M / world)`` of ``sum_r (a_r b_rᵀ + a2_r b2ᵀ)``: the same kernel
+        with the tile owner chosen by row block; the owner keeps the summed tile and nothing is sent back, so the
+        launch moves ``(world - 1) / world`` of the partial once instead of twice."""
+        self.heap.guard()
+        self.epoch += 1
+        h = self.heap
+        return h.C.lib().gemm_allreduce(a, b, a2, b2, None, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
+                                        h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
+                                        self.out_elems, h.wait_limit_s, None, 0, 0, True)
 
 
 _REDUCERS: dict = {}

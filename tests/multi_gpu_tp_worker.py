@@ -66,6 +66,36 @@ def _check_reducer(comm, heap, red, dev, world, rank, what):
             comm.require_consensus(digest, f"{what} output {M}x{N}x{K} rep {rep}")
 
 
+def _check_reduce_scatter(comm, heap, red, dev, world, rank):
+    """Reduce-scatter form of the fused kernel: this rank's rows must equal, bit for bit, the same rows of the
+    all-reduce form (both sum the partials in rank order), also when the two forms alternate back to back."""
+    for i, (M, N, K, use_lora) in enumerate([(world * 128, 512, 256, False), (world * 512, 4096, 1024, True),
+                                             (8192, 4096, 2048, True)]):
+        gen = torch.Generator(device=dev).manual_seed(101 + i)
+        b2 = (torch.randn(N, 16, device=dev, generator=gen) * 0.1).to(torch.bfloat16) if use_lora else None
+        mine = None
+        for r in range(world):
+            a = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+            b = (torch.randn(N, K, device=dev, generator=gen) / K ** 0.5).to(torch.bfloat16)
+            t2 = torch.randn(M, 16, device=dev, generator=gen).to(torch.bfloat16) if use_lora else None
+            if r == rank:
+                mine = (a, b, t2)
+        assert red.fits_scatter(M, N)
+        n = M // world
+        for rep in range(4):
+            full = red(mine[0], mine[1], mine[2], b2, None)
+            part = red.reduce_scatter(mine[0], mine[1], mine[2], b2)
+            part2 = red.reduce_scatter(mine[0], mine[1], mine[2], b2)
+            torch.cuda.synchronize()
+            heap.check("fused gemm reduce-scatter")
+            assert part.shape == (n, N)
+            assert torch.equal(part, full[rank * n:(rank + 1) * n]), (M, N, K, rep)
+            assert torch.equal(part2, part), (M, N, K, rep)
+    comm.barrier()
+    if rank == 0:
+        print("TP_REDUCE_SCATTER_PASS")
+
+
 def _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl):
     """The in-switch form of the same kernel (FERRL_TEST_NVLS=1): same checks, its own timing line.  No rank
     leaves this function before all have finished with the multicast-bound buffers."""
@@ -165,6 +195,19 @@ def main():
     t_nccl = _time(unfused)
     t_gemm = _time(lambda: C.gemm(a, b, None, None, res))
     heap.check("timing")
+    _check_reduce_scatter(comm, heap, red, dev, world, rank)
+    t_rs = _time(lambda: red.reduce_scatter(a, b))
+    t_ar = _time(lambda: red(a, b))
+    rs_out = torch.empty(M // world, N, device=dev, dtype=torch.bfloat16)
+
+    def unfused_rs():
+        dist.reduce_scatter_tensor(rs_out, C.gemm(a, b))
+        return rs_out
+    t_rs_nccl = _time(unfused_rs)
+    heap.check("reduce-scatter timing")
+    if rank == 0:
+        print(f"TP_RS_TIMING world={world} M={M} N={N} K={K} fused_reduce_scatter_ms={t_rs:.4f} fused_all_reduce_ms={t_ar:.4f} "
+              f"gemm_nccl_reduce_scatter_ms={t_rs_nccl:.4f}")
     if rank == 0:
         print(f"TP_TIMING world={world} M={M} N={N} K={K} fused_ms={t_fused:.4f} gemm_nccl_ms={t_nccl:.4f} "
               f"gemm_only_ms={t_gemm:.4f}")
