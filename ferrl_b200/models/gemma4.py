@@ -169,8 +169,10 @@ class Gemma4Layer(nn.Module):
         return out
 
     def _qkv(self, x, positions, cos, sin, lin):
-        B, S, _ = x.shape
-        p = lin(self.qkv, x)
+        return self._split_qkv(lin(self.qkv, x), positions, cos, sin)
+
+    def _split_qkv(self, p, positions, cos, sin):
+        B, S, _ = p.shape
         if self.k_eq_v:
             q, k = p.split([self.hq * self.D, self.hkv * self.D], dim=-1)
             v_raw = k
@@ -198,19 +200,16 @@ class Gemma4Layer(nn.Module):
 
     # ---- sequence-sharded forms: ``hs`` holds this rank's block of the flattened [B * S, H] token rows
     def attn_half_sp(self, hs, B, S, positions, cos, sin, comm, merged=False):
-        from ..parallel import sp
-        lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
-        x = sp.gather_rows_tp(ops.rmsnorm(hs, self.input_norm, self.eps), comm).view(B, S, -1)
-        q, k, v = self._qkv(x, positions, cos, sin, lin)
+        # the column-parallel projection gathers the normalised rows; its backward reduce-scatters inside the GEMM
+        p = self.qkv.forward_gathered(ops.rmsnorm(hs, self.input_norm, self.eps), comm, merged).view(B, S, -1)
+        q, k, v = self._split_qkv(p, positions, cos, sin)
         a = ops.attention(q, k, v, scale=1.0, causal=True, window=self.window, softmax_fp32=True)
         o = self.o.forward_reduce_scatter(a.reshape(B * S, self.hq * self.D), comm, merged)   # this rank's rows of the sum
         return hs + ops.rmsnorm(o, self.post_attn_norm, self.eps)
 
     def mlp_half_sp(self, hs, comm, merged=False):
-        from ..parallel import sp
-        lin = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
-        x = sp.gather_rows_tp(ops.rmsnorm(hs, self.pre_ffn_norm, self.eps), comm)
-        d = self.down.forward_reduce_scatter(ops.swiglu(lin(self.gate_up, x), self.act), comm, merged)
+        gu = self.gate_up.forward_gathered(ops.rmsnorm(hs, self.pre_ffn_norm, self.eps), comm, merged)
+        d = self.down.forward_reduce_scatter(ops.swiglu(gu, self.act), comm, merged)
         return (hs + ops.rmsnorm(d, self.post_ffn_norm, self.eps)) * self.layer_scalar
 
     def mlp_half(self, h, comm, merged=False):

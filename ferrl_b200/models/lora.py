@@ -285,6 +285,28 @@ class FusedLoraLinear(nn.Module):
         y = reduce_from_tp(self.forward_merged(x) if merged else self.forward(x), comm)
         return y if residual is None else residual + y
 
+    def forward_gathered(self, xs: torch.Tensor, comm, merged: bool = False) -> torch.Tensor:
+        """Column-parallel use under sequence sharding: ``xs`` is this rank's ``[rows / world, in]`` block of the
+        input and the result covers all rows.  On GPUs the gather runs over the symmetric heap and the backward's
+        reduce-scatter of the input gradient happens inside its GEMM."""
+        from ..parallel import sp
+        if comm.world_size > 1 and xs.is_cuda and xs.dim() == 2:
+            from ..parallel.symm import gemm_all_reducer
+            from ..ops import cuda as _c
+            gather = lambda z: sp.all_gather_rows_value(z, comm)            # noqa: E731
+            scatter = lambda z: sp.reduce_scatter_rows_value(z, comm)       # noqa: E731
+            if merged:
+                w = self.weight_merged if self.weight_merged is not None else self.weight
+                y = None if self._glu_rows() is not None else \
+                    _c.gather_lora_linear(xs, w, None, None, None, gather, scatter, gemm_all_reducer(comm))
+            else:
+                a, b = self._stacks()
+                y = _c.gather_lora_linear(xs, self.weight, a, b, self.weight_t, gather, scatter, gemm_all_reducer(comm))
+            if y is not None:
+                return y
+        x = sp.gather_rows_tp(xs, comm)
+        return self.forward_merged(x) if merged else self.forward(x)
+
     def forward_reduce_scatter(self, x: torch.Tensor, comm, merged: bool = False) -> torch.Tensor:
         """Row-parallel use under sequence sharding: ``x`` is ``[rows, in_local]`` and the result is this rank's
         ``rows / world`` rows of the tensor-parallel sum.  On GPUs with a registered ``GemmAllReducer`` the sum and

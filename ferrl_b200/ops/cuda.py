@@ -216,6 +216,57 @@ class _LoraLinearReduceScatter(torch.autograd.Function):
         return dx, None, None, da, db, None, None
 
 
+class _GatherLoraLinear(torch.autograd.Function):
+    """Column-parallel projection of an all-gathered row shard: ``y = gather(xs) Wᵀ + (gather(xs) Aᵀ) Bᵀ``.
+    Backward: the input gradient of rank r is ``dy_r W_r + (dy_r B_r) A``, and the shard of ``xs`` wants the sum of
+    those over the ranks for its own rows: one fused GEMM -> reduce-scatter launch (the cotangent path of the
+    reference's column-parallel layers sums full activations, ``crates/ferrl/src/gemma4.rs:2136-2169``)."""
+
+    @staticmethod
+    def forward(ctx, xs, w, wt, a_stack, b_stack, gather, scatter_sum, reducer):
+        x2 = gather(xs.reshape(-1, xs.shape[-1]).contiguous())
+        t = a16 = b16 = None
+        if a_stack is not None:
+            a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()
+            b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()
+            t = gemm(x2, a16)
+        y = gemm(x2, w, t, b16, None, static_b=a_stack is None)
+        ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
+        ctx.x_grad = xs.requires_grad
+        ctx.scatter_sum, ctx.reducer = scatter_sum, reducer
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w, wt, a_stack, b_stack, t, a16, b16 = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w.shape[0])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dxs = da = db = None
+        u = gemm(dy2, b16.t().contiguous()) if a_stack is not None else None
+        if ctx.x_grad:
+            wt_ = wt if wt is not None else w.t().contiguous()
+            a16t = a16.t().contiguous() if u is not None else None
+            red = ctx.reducer
+            if red is not None and red.fits_scatter(dy2.shape[0], wt_.shape[0]):
+                dxs = red.reduce_scatter(dy2, wt_, u, a16t)
+            else:
+                dxs = ctx.scatter_sum(gemm(dy2, wt_, u, a16t))
+        if a_stack is not None:
+            R = a_stack.shape[0]
+            da = _lora_grad(u, x2)[:R] if a_stack.requires_grad else None
+            db = _lora_grad(t, dy2)[:R].t().contiguous() if b_stack.requires_grad else None
+        return dxs, None, None, da, db, None, None, None
+
+
+def gather_lora_linear(xs, w, a_stack, b_stack, wt, gather, scatter_sum, reducer):
+    """``lora_linear(all_gather_rows(xs))`` for a ``[rows / world, in]`` shard, with the reduce-scatter of the input
+    gradient fused into its GEMM; ``None`` when the operands are not the bf16 frozen-weight case."""
+    if not (_bf16(xs) and _bf16(w)) or w.requires_grad or xs.shape[-1] % 8 or xs.dim() != 2:
+        return None
+    return _GatherLoraLinear.apply(xs, w, wt, a_stack, b_stack, gather, scatter_sum, reducer)
+
+
 def lora_linear_reduce_scatter(x, w, a_stack, b_stack, wt, reducer, gather):
     """This rank's rows of ``sum_r (x_r W_rᵀ + (x_r A_rᵀ) Bᵀ)``, ``[rows / world, out]``, in one kernel per rank;
     ``None`` when the shapes do not fit (the caller then projects and reduce-scatters separately)."""

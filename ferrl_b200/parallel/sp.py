@@ -165,6 +165,11 @@ def all_gather_rows_value(x: torch.Tensor, comm: Comm) -> torch.Tensor:
     return _all_gather_value(x, comm)
 
 
+def reduce_scatter_rows_value(x: torch.Tensor, comm: Comm) -> torch.Tensor:
+    """This rank's rows of the sum of ``x`` over the ranks, outside autograd (used by backward passes)."""
+    return _reduce_scatter_value(x, comm)
+
+
 def gather_rows_tp(x, comm):
     return x if comm.world_size == 1 else _GatherTP.apply(x, comm)
 

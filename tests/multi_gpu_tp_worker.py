@@ -122,7 +122,7 @@ def _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl):
         print("TP_NVLS_PASS")
 
 
-def _sequence_parallel_checks(comm, heap, dev, world, rank):
+def _sequence_parallel_checks(comm, heap, red, dev, world, rank):
     """Row collectives over the symmetric heap against the Comm seam, and a Gemma-style stack with the residual
     stream sharded over the token rows against the replicated layout (outputs and adapter gradients)."""
     from ferrl_b200.models.gemma4 import Gemma4GradModel, Gemma4Spec
@@ -146,10 +146,18 @@ def _sequence_parallel_checks(comm, heap, dev, world, rank):
     hq = max(4, world)
     spec = Gemma4Spec(vocab_size=512 * world, hidden_size=256, num_hidden_layers=2, num_attention_heads=hq, num_key_value_heads=hq,
                       head_dim=64, global_head_dim=64, num_global_key_value_heads=hq, intermediate_size=512,
-                      layer_types=["sliding_attention", "full_attention"], sliding_window=32, max_position_embeddings=128)
+                      layer_types=["sliding_attention", "full_attention"], sliding_window=32, max_position_embeddings=128 * world)
     plan = TensorParallelPlan.new(rank, world, hq, hq, 512)
-    ids = torch.randint(0, spec.vocab_size, (2, 16 * world), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
+    # 128 x world token rows: whole tiles per rank, so the sharded layers run the fused GEMM -> reduce-scatter
+    ids = torch.randint(0, spec.vocab_size, (2, 64 * world), device=dev, generator=torch.Generator(device=dev).manual_seed(5))
     outs = []
+    fused_calls = [0]
+    plain_rs = red.reduce_scatter
+
+    def counted(*a, **k):
+        fused_calls[0] += 1
+        return plain_rs(*a, **k)
+    red.reduce_scatter = counted
     for seq_par in (False, True):
         model = Gemma4GradModel(spec, LoraSpec(rank=8, alpha=16.0), dtype=torch.bfloat16, device=dev, tp=plan,
                                 sequence_parallel=seq_par)
@@ -164,6 +172,9 @@ def _sequence_parallel_checks(comm, heap, dev, world, rank):
         h.float().pow(2).mean().backward()
         outs.append((h.detach().float(), [q.grad.detach().float().clone() for q in model.trainable_params()]))
     heap.check("sequence-parallel model")
+    red.reduce_scatter = plain_rs
+    # per layer: o and down forward, qkv and gate_up backward
+    assert fused_calls[0] >= 4 * spec.num_hidden_layers, fused_calls[0]
     sp.register_row_collectives(comm, None)
     ref, got = outs
     assert float((ref[0] - got[0]).abs().max()) < 0.05 * float(ref[0].abs().max()), float((ref[0] - got[0]).abs().max())
@@ -263,7 +274,7 @@ def main():
     comm.barrier()
     if rank == 0:
         print("TP_SHARDED_HEAD_PASS")
-    _sequence_parallel_checks(comm, heap, dev, world, rank)
+    _sequence_parallel_checks(comm, heap, red, dev, world, rank)
     if rank == 0:
         print("TP_FUSED_PASS")
     dist.destroy_process_group()
