@@ -134,7 +134,8 @@ def _build_model(args, comm, device):
                           sliding_window=1024, max_position_embeddings=max_pos)
         tp = TensorParallelPlan.new(comm.rank, comm.world_size, 32, 16, spec.intermediate_size) if comm.world_size > 1 else None
         # the frozen base is kept once (no resident transpose): 27B parameters leave no room for a second copy
-        return Gemma4GradModel(spec, lora, tp=tp, keep_transpose=False, **kw), spec
+        return Gemma4GradModel(spec, lora, tp=tp, keep_transpose=False,
+                               sequence_parallel=bool(args.sequence_parallel and tp is not None), **kw), spec
     from ferrl_b200.models.qwen35 import MoeDims, Qwen35GradModel, Qwen35LoraTargets, Qwen35Spec
     if args.config == "moe-ep":
         L = 4 if small else 48
@@ -197,7 +198,8 @@ def build_trainer(args, comm, device):
         rows = args.microbatch * (args.prompt_hi + args.max_new)
         if topology == "tp":
             runtime = ParallelRuntime.create(comm, device, tensor_parallel=True, hidden=spec.hidden_size,
-                                             max_rows=max(rows, args.prompts * args.group))
+                                             max_rows=max(rows, args.prompts * args.group),
+                                             sequence_parallel=args.sequence_parallel)
         elif cfg["parallelism"] == "ep":
             runtime = ParallelRuntime.create(comm, device, expert_parallel={
                 "num_experts": spec.moe.num_experts, "hidden": spec.hidden_size, "top_k": spec.moe.top_k,
@@ -231,6 +233,8 @@ def main():
     ap.add_argument("--prompt-hi", type=int, default=None)
     ap.add_argument("--microbatch", type=int, default=None, help="rows per scoring/backward micro-batch")
     ap.add_argument("--remat", type=int, default=None, help="1 = recompute layer activations in backward (less memory)")
+    ap.add_argument("--sequence-parallel", action="store_true",
+                    help="gemma-tp: keep the residual stream sharded over the token rows between the projections")
     ap.add_argument("--seed", type=int, default=1234)
     ap.add_argument("--no-graph", action="store_true", help="run decode steps eagerly (for per-kernel profiling)")
     ap.add_argument("--nccl-baseline", action="store_true", help="use per-tensor NCCL all-reduce instead of the fused DP step")

@@ -43,6 +43,11 @@ struct GemmArgs {
   // reduce-scatter form: rank r keeps rows [r M/world, (r+1) M/world) of the sum in `out` [M/world, N] and nothing is sent back
   // (M a multiple of world x 128, no residual, peer-load staging only)
   int ar_scatter;
+  // all-gather -> GEMM (ar_gather != 0, with ar_world / ar_rank / ar_flags / ar_max_tiles / ar_limit_ns): A is this rank's
+  // gather buffer ag_src.ptr[ar_rank], [M, K] packed, of which only its own M / world rows are filled; the kernel's
+  // communication warps pull the other rows from the peers' buffers while the tensor cores work on the rows in place
+  int ar_gather;
+  PeerTable ag_src;
   // launch as a programmatic dependent of the stream predecessor: weights are prefetched before the
   // dependency wait (only where B is never written by an earlier kernel of the same stream)
   int pdl;

@@ -406,6 +406,36 @@ Tensor gemm_allreduce(const Tensor& A, const Tensor& B, const optional<Tensor>& 
   return out;
 }
 
+// Column-parallel projection fused with the all-gather of its sequence-sharded input: `src` are every rank's gather
+// buffers ([M, K] bf16, packed; this rank has filled its own M / world rows of src[rank]); out = gathered A B^T (+ A2 B2^T).
+// After the call src[rank] holds all M rows.
+Tensor gemm_allgather(const Tensor& B, const optional<Tensor>& A2, const optional<Tensor>& B2, std::vector<int64_t> src,
+                      std::vector<int64_t> flags, int64_t rank, int64_t world, int64_t max_tiles, int64_t M, int64_t K,
+                      double limit_s) {
+  TORCH_CHECK(B.is_cuda() && B.scalar_type() == at::kBFloat16 && B.dim() == 2 && B.size(1) == K && B.stride(1) == 1, "gemm_allgather: B bf16 [N, K]");
+  TORCH_CHECK(world > 1 && M % (world * 128) == 0 && K % 8 == 0, "gemm_allgather: rows % (world x 128) == 0 and K % 8 == 0");
+  c10::cuda::CUDAGuard guard(B.device());
+  ferrl::GemmArgs a{};
+  a.ag_src = table_of_fwd(src);
+  a.A = a.ag_src.ptr[rank]; a.B = B.data_ptr(); a.lda = K; a.ldb = B.stride(0);
+  a.M = M; a.N = B.size(0); a.K = K;
+  if (A2.has_value() && A2->defined()) {
+    TORCH_CHECK(B2.has_value() && B2->defined() && A2->stride(1) == 1 && B2->stride(1) == 1 && A2->size(0) == M &&
+                    A2->scalar_type() == at::kBFloat16 && B2->scalar_type() == at::kBFloat16, "gemm_allgather: side operands");
+    a.A2 = A2->data_ptr(); a.B2 = B2->data_ptr(); a.lda2 = A2->stride(0); a.ldb2 = B2->stride(0); a.K2 = A2->size(1);
+  }
+  Tensor out = out_empty({a.M, a.N}, B.options());
+  a.out = out.data_ptr(); a.ldo = a.N; a.out_f32 = false;
+  a.status = status_word(); a.num_sms = num_sms();
+  a.force_bn = (a.N >= 256 && static_cast<int64_t>((a.M + 127) / 128) * ((a.N + 255) / 256) >= num_sms()) ? 256 : 128;
+  if (a.N < 128) a.force_bn = 64;
+  a.ar_world = world; a.ar_rank = rank; a.ar_max_tiles = max_tiles; a.ar_gather = 1;
+  a.ar_limit_ns = static_cast<unsigned long long>(limit_s * 1e9);
+  a.ar_flags = table_of_fwd(flags);
+  FERRL_CHECK(ferrl::gemm_bf16(a, stream()));
+  return out;
+}
+
 // out[R, C] = U^T X, U [M, R] and X [M, C] bf16 (row strides free, last dim contiguous), fp32 result
 Tensor lora_grad(const Tensor& U, const Tensor& X) {
   TORCH_CHECK(U.is_cuda() && U.scalar_type() == at::kBFloat16 && X.scalar_type() == at::kBFloat16 && U.dim() == 2 &&
@@ -1369,6 +1399,7 @@ TORCH_LIBRARY(ferrl_b200, m) {
   m.def("decode_gemm(Tensor A, Tensor B, Tensor? residual=None, int glu_act=-1, int max_clusters=0, bool static_b=False, Tensor? debug=None) -> Tensor", &decode_gemm);
   m.def("set_decode_gemm(bool on) -> ()", &set_decode_gemm);
   m.def("gemm_allreduce(Tensor A, Tensor B, Tensor? A2, Tensor? B2, Tensor? residual, int[] stage, int[] outbuf, int[] flags, int rank, int world, int epoch, int max_tiles, int stage_elems, int out_elems, float limit_s, Tensor? debug=None, int mc_stage=0, int mc_outbuf=0, bool scatter=False) -> Tensor", &gemm_allreduce);
+  m.def("gemm_allgather(Tensor B, Tensor? A2, Tensor? B2, int[] src, int[] flags, int rank, int world, int max_tiles, int M, int K, float limit_s) -> Tensor", &gemm_allgather);
   m.def("lora_grad(Tensor U, Tensor X) -> Tensor", &lora_grad);
   m.def("gdn_conv_fwd(Tensor x, Tensor w, Tensor? left, bool act) -> Tensor", &gdn_conv_fwd);
   m.def("gdn_conv_bwd(Tensor x, Tensor w, Tensor? left, Tensor dy, bool act) -> Tensor", &gdn_conv_bwd);

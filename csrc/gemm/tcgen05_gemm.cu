@@ -75,6 +75,16 @@ struct GemmParams {
   // CTA publishes fin[rank] = call number on all peers, and a rank waits for fin >= previous call on its peers before
   // its first push of a call (both forms do: a sender may otherwise run ahead into staging slots still being summed).
   int ar_scatter;
+  // All-gather -> GEMM (ar_gather != 0, M a multiple of ar_world x BM, A packed): A is this rank's gather buffer, of
+  // which the caller filled this rank's M / ar_world rows.  CTA 0 tells every peer that the rows are in place
+  // (agr[rank] = call number); the communication warps pull the peers' rows, 128 rows x 256 columns per unit and unit
+  // by unit over all CTAs, into the local buffer and count arrived[m tile] up; the TMA producer loads a tile of
+  // foreign rows only once its count is complete.  The tile sequence starts with this rank's own rows and continues
+  // with the successors' in the order the units are pulled.  The output is the plain [M, N] one of this rank.
+  // The caller alternates between two gather buffers: a peer may rewrite its rows for the call after next only after
+  // this rank has published that call's number, i.e. has finished pulling for this one.
+  int ar_gather;
+  PeerTable ag_src;
   // Launched as a programmatic dependent: the producer fills its ring with the weight (B) halves of
   // its first k-blocks, which no earlier kernel writes, before it waits for the stream predecessor;
   // only then does it fetch the activation (A) halves.  Everything else in the kernel is ordered
@@ -118,6 +128,14 @@ __device__ __forceinline__ uint32_t* ar_done(const PeerTable& f, int rank_mem, i
 __device__ __forceinline__ uint32_t* ar_fin(const PeerTable& f, int rank_mem, int max_tiles, int from) {
   return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * (kMaxRanks + 1) + 2 + from;
 }
+__device__ __forceinline__ uint32_t* ar_agr(const PeerTable& f, int rank_mem, int max_tiles, int from) {
+  return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * (kMaxRanks + 1) + 2 + kMaxRanks + from;
+}
+constexpr int kMaxGatherMTiles = 1024;
+constexpr int kGatherUnitCols = 256;
+__device__ __forceinline__ uint32_t* ar_arrived(const PeerTable& f, int rank_mem, int max_tiles) {
+  return static_cast<uint32_t*>(f.ptr[rank_mem]) + static_cast<long long>(max_tiles) * (kMaxRanks + 1) + 2 + 2 * kMaxRanks;
+}
 __device__ __forceinline__ bool flag_reached(const uint32_t* flag, uint32_t epoch) {
   return static_cast<int32_t>(ld_acquire_sys(flag) - epoch) >= 0;   // epochs only grow; tolerates wrap-around
 }
@@ -133,6 +151,21 @@ __device__ __forceinline__ bool ar_wait_flag(const uint32_t* flag, uint32_t epoc
     }
   }
   return true;
+}
+
+// Bounded spin until a device-scope counter in local memory has reached `want`; one thread calls it.
+__device__ __forceinline__ bool ar_wait_count(const uint32_t* ctr, uint32_t want, uint64_t limit_ns, int* status) {
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  for (;;) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(ctr) : "memory");
+    if (v >= want) return true;
+    if ((++spins & 0x3f) == 0 && globaltimer_ns() - t0 > limit_ns) {
+      atomicCAS(status, kStatusOk, kStatusPeerWaitTimeout);
+      return false;
+    }
+  }
 }
 
 __device__ __forceinline__ uint4 pack8(const float* a) {
@@ -349,15 +382,16 @@ __device__ __forceinline__ void tile_coords(int tile, int m_tiles, int n_tiles, 
   tile_coords_mn(tile / split_k, m_tiles, n_tiles, group_m, mi, ni);
 }
 
-// Tile order of the fused collective forms.  All-reduce: the plain order.  Reduce-scatter: row block by row block,
-// the successor's first and this rank's own last (the plain order inside a block).
+// Tile order of the fused collective forms.  All-reduce: the plain order.  Reduce-scatter (1): row block by row block,
+// the successor's first and this rank's own last (the plain order inside a block).  All-gather (2): this rank's own
+// block first, then the successors'.
 template <bool AR>
 __device__ __forceinline__ void tile_coords_ar(int ar_scatter, int ar_rank, int ar_world, int tile, int m_tiles, int n_tiles,
                                                int group_m, int split_k, int& ks, int& mi, int& ni) {
   if (AR && ar_scatter) {
     const int mt_per = m_tiles / ar_world, per = mt_per * n_tiles;
     const int blk = tile / per;
-    int owner = ar_rank + 1 + blk;
+    int owner = ar_rank + blk + (ar_scatter == 2 ? 0 : 1);      // 2: gather order, own rows first
     if (owner >= ar_world) owner -= ar_world;
     int ml;
     tile_coords_mn(tile - blk * per, mt_per, n_tiles, group_m, ml, ni);
@@ -425,6 +459,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (AR) {
     ar_epoch_word = static_cast<uint32_t*>(p.ar_flags.ptr[p.ar_rank]) + static_cast<long long>(p.ar_max_tiles) * (kMaxRanks + 1);
     ar_epoch = *reinterpret_cast<volatile uint32_t*>(ar_epoch_word) + 1;
+    if (p.ar_gather && blockIdx.x == 0 && threadIdx.x == 0)     // this rank's rows were written before the launch
+      for (int q2 = 0; q2 < p.ar_world; ++q2)
+        if (q2 != p.ar_rank) st_release_sys(ar_agr(p.ar_flags, q2, p.ar_max_tiles, p.ar_rank), ar_epoch);
   }
 
   const int warp = threadIdx.x >> 5;
@@ -472,7 +509,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int pre = 0;          // k-blocks of the first tile whose loads were issued around the dependency wait
       if (p.pdl && static_cast<int>(blockIdx.x) < total_tiles) {
         int ks, mi, ni;
-        tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, blockIdx.x, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        tile_coords_ar<AR>(p.ar_gather ? 2 : p.ar_scatter, p.ar_rank, p.ar_world, blockIdx.x, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
         const int kb_begin = ks * p.kb_per_split, kb_end = min(kb_total, kb_begin + p.kb_per_split);
         pre = min(C::STAGES, kb_end - kb_begin);
         for (int i = 0; i < pre; ++i) {           // first pass over the ring: every stage is free
@@ -493,7 +530,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         int ks, mi, ni;
-        tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+        tile_coords_ar<AR>(p.ar_gather ? 2 : p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
         int b_row0 = ni * BN;
         if (p.tile_expert) {
           const int e = p.tile_expert[mi];
@@ -503,6 +540,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         int kb_begin = ks * p.kb_per_split;
         const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
         if (tile == static_cast<int>(blockIdx.x)) kb_begin += pre;
+        if (AR && p.ar_gather && mi / (m_tiles / p.ar_world) != p.ar_rank) {
+          // rows of a peer: all their column units must have landed in the local buffer (generic-proxy stores of
+          // other CTAs, read here through the async proxy)
+          const uint32_t units = (p.K + kGatherUnitCols - 1) / kGatherUnitCols;
+          if (!ar_wait_count(ar_arrived(p.ar_flags, p.ar_rank, p.ar_max_tiles) + mi, units, wait_limit, p.status)) {
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = kb_begin; kb < kb_end; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.status, kStatusWaitTimeoutProducer, wait_limit)) {
             ok = false;
@@ -541,7 +589,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         if (p.tile_expert) {
           int ks_, mi_, ni_;
-          tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks_, mi_, ni_);
+          tile_coords_ar<AR>(p.ar_gather ? 2 : p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks_, mi_, ni_);
           if (p.tile_expert[mi_] < 0) continue;
         }
         const int acc = (it++) & 1;
@@ -592,7 +640,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     };
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
       int ks, mi, ni;
-      tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+      tile_coords_ar<AR>(p.ar_gather ? 2 : p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       if (p.tile_expert && p.tile_expert[mi] < 0) continue;
       const int row = mi * BM + q * 32 + lane;
       const bool row_ok = row < p.M;
@@ -610,7 +658,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       const int out_tile = mi * n_tiles + ni;
       __nv_bfloat16* ar_slot = nullptr;
       int owner = 0;
-      if (AR) {
+      if (AR && !p.ar_gather) {
         long long slot0;
         ar_owner_slot(p.ar_scatter, p.ar_world, m_tiles, n_tiles, mi, ni, owner, slot0);
         ar_slot = p.ar_mc_stage
@@ -656,7 +704,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           continue;
         }
-        if (AR) {
+        if (AR && !p.ar_gather) {
           // bf16 partial of this rank, pushed into the tile owner's staging slot; rows past M hold the
           // zero fill of the TMA load, so no bounds test is needed inside the slot
 #pragma unroll
@@ -757,7 +805,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[acc]);   // TMEM is free again: the MMA warp moves on while we talk to peers
-      if (AR) {
+      if (AR && !p.ar_gather) {
         // The exchange itself belongs to the communication warps below; here the tile is only
         // announced.  One system-scope release per tile, by one thread: the barrier orders the other
         // threads' stores before it.  A tile this rank owns is announced through shared memory.
@@ -780,6 +828,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // TMEM: waiting for peers, the owner's reduction, the pushes and the copies of the peers' tiles
     // run beside the tensor cores instead of holding up the accumulator ring.
     const int ct = threadIdx.x - 192;             // 0..127
+    if (p.ar_gather) {
+      // ---- all-gather -> GEMM: pull the peers' rows of A into the local buffer, in the order the tiles need them
+      const int mt_per = m_tiles / p.ar_world;
+      const int kch = (p.K + kGatherUnitCols - 1) / kGatherUnitCols;
+      const int units = (p.ar_world - 1) * mt_per * kch;
+      uint32_t* arrived = ar_arrived(p.ar_flags, p.ar_rank, p.ar_max_tiles);
+      __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(p.ag_src.ptr[p.ar_rank]);
+      uint32_t gphase = 0, seen = 0;
+      auto gsync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(comm_bar);
+        const bool ok = mbar_wait(comm_bar, gphase, abort_flag, p.status, kStatusWaitTimeoutEpilogue, wait_limit);
+        gphase ^= 1;
+        return ok && !*abort_flag;
+      };
+      for (int u = blockIdx.x; u < units; u += gridDim.x) {
+        const int kc = u % kch, mt = (u / kch) % mt_per, blk = u / (kch * mt_per) + 1;
+        int src = p.ar_rank + blk;
+        if (src >= p.ar_world) src -= p.ar_world;
+        if (ct == 0 && !((seen >> src) & 1u) &&
+            !ar_wait_flag(ar_agr(p.ar_flags, p.ar_rank, p.ar_max_tiles, src), ar_epoch, wait_limit, p.status))
+          *abort_flag = 1;
+        seen |= 1u << src;
+        if (!gsync()) break;
+        const int mi = src * mt_per + mt;
+        const int c0 = kc * kGatherUnitCols;
+        const int nc8 = min(kGatherUnitCols, p.K - c0) >> 3;          // 16-byte pieces per row of this unit
+        const int total = BM * nc8;
+        const __nv_bfloat16* from = static_cast<const __nv_bfloat16*>(p.ag_src.ptr[src]);
+        constexpr int UG = 8;
+        for (int i0 = ct; i0 < total; i0 += 128 * UG) {
+          uint4 x[UG];
+          long long off[UG];
+#pragma unroll
+          for (int v = 0; v < UG; ++v) {
+            const int i = i0 + v * 128;
+            off[v] = -1;
+            if (i < total) {
+              off[v] = (static_cast<long long>(mi) * BM + i / nc8) * p.K + c0 + (i % nc8) * 8;
+              x[v] = *reinterpret_cast<const uint4*>(from + off[v]);
+            }
+          }
+#pragma unroll
+          for (int v = 0; v < UG; ++v)
+            if (off[v] >= 0) *reinterpret_cast<uint4*>(dst + off[v]) = x[v];
+        }
+        __threadfence();
+        asm volatile("fence.proxy.async.global;" ::: "memory");
+        if (!gsync()) break;
+        if (ct == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(arrived + mi) : "memory");
+      }
+    } else {
     constexpr int CPR = BN / 8;
     const int out_tiles = m_tiles * n_tiles;
     auto peer_tile = [&](int u) -> int {
@@ -820,7 +920,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     bool live_c = true;
     for (int tile = blockIdx.x; tile < total_tiles && live_c; tile += gridDim.x) {
       int ks, mi, ni;
-      tile_coords_ar<AR>(p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
+      tile_coords_ar<AR>(p.ar_gather ? 2 : p.ar_scatter, p.ar_rank, p.ar_world, tile, m_tiles, n_tiles, p.group_m, p.split_k, ks, mi, ni);
       ++it;
       const int out_tile = mi * n_tiles + ni;
       int owner;
@@ -966,6 +1066,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         copy_tile(pt);
       }
     }
+    }   // all-reduce / reduce-scatter forms
   }
 
   tc_fence_before();
@@ -975,6 +1076,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if (atomicAdd(ar_epoch_word + 1, 1u) == gridDim.x - 1) {   // last CTA out: next call uses the next number
       ar_epoch_word[1] = 0u;
       __threadfence();
+      if (p.ar_gather) {          // arrival counts back to zero for the next call
+        uint32_t* arrived = ar_arrived(p.ar_flags, p.ar_rank, p.ar_max_tiles);
+        for (int i = 0; i < m_tiles; ++i) arrived[i] = 0u;
+        __threadfence();
+      }
       // every read of this rank's staging slots is over: peers may push the next call's partials
       for (int q2 = 0; q2 < p.ar_world; ++q2)
         if (q2 != p.ar_rank) st_release_sys(ar_fin(p.ar_flags, q2, p.ar_max_tiles, p.ar_rank), ar_epoch);
@@ -1085,7 +1191,14 @@ const char* launch_bn(const GemmArgs& a, cudaStream_t stream) {
     return "log-prob epilogue: plain bf16 call with 256-wide tiles only";
   if (p.split_k > 1 && (!a.partial || (a.N % 4))) return "split-k needs a partial buffer and N % 4 == 0";
   p.ar_world = a.ar_world > 1 ? a.ar_world : 1;
-  if (p.ar_world > 1) {
+  if (a.ar_gather) {
+    if (p.ar_world < 2 || a.ar_world > kMaxRanks || a.ar_rank < 0 || a.ar_rank >= a.ar_world) return "all-gather GEMM: bad rank/world";
+    if (a.M % (p.ar_world * BM) || a.M / BM > kMaxGatherMTiles || (a.K % 8) || a.lda != a.K || p.split_k > 1 || a.out_f32 ||
+        a.A != a.ag_src.ptr[a.ar_rank])
+      return "all-gather GEMM: M a multiple of world x 128 (at most 1024 row tiles), packed bf16 A in this rank's gather buffer, no split-k";
+    p.ar_rank = a.ar_rank; p.ar_flags = a.ar_flags; p.ar_max_tiles = a.ar_max_tiles; p.ar_limit_ns = a.ar_limit_ns;
+    p.ar_gather = 1; p.ag_src = a.ag_src;
+  } else if (p.ar_world > 1) {
     if (a.out_f32 || p.split_k > 1 || (a.N % 8) || a.ldo != a.N) return "fused all-reduce needs bf16 output, no split-k, N % 8 == 0, packed output";
     const int out_tiles = ((a.M + BM - 1) / BM) * ((a.N + BN - 1) / BN);
     if (out_tiles > a.ar_max_tiles) return "fused all-reduce: flag buffer too small for this many tiles";

@@ -224,13 +224,23 @@ class _GatherLoraLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, xs, w, wt, a_stack, b_stack, gather, scatter_sum, reducer):
-        x2 = gather(xs.reshape(-1, xs.shape[-1]).contiguous())
+        xs2 = xs.reshape(-1, xs.shape[-1]).contiguous()
         t = a16 = b16 = None
         if a_stack is not None:
             a16 = _pad8(a_stack.detach().to(torch.bfloat16), 0).contiguous()
             b16 = _pad8(b_stack.detach().to(torch.bfloat16), 1).contiguous()
-            t = gemm(x2, a16)
-        y = gemm(x2, w, t, b16, None, static_b=a_stack is None)
+        if reducer is not None and reducer.fits_gather(xs2.shape[0] * reducer.heap.world, xs2.shape[1]):
+            # one launch gathers and projects; the rank-r factor of the adapter path is gathered from its row shards
+            if a_stack is not None:
+                t = gather(gemm(xs2, a16))
+            y, x2 = reducer.gather_gemm(xs2, w, t, b16)
+            if a_stack is not None and ctx.needs_input_grad[3]:
+                x2 = x2.clone()             # the buffer is reused two calls later; the adapter gradient wants these rows
+        else:
+            x2 = gather(xs2)
+            if a_stack is not None:
+                t = gemm(x2, a16)
+            y = gemm(x2, w, t, b16, None, static_b=a_stack is None)
         ctx.save_for_backward(x2, w, wt, a_stack, b_stack, t, a16, b16)
         ctx.x_grad = xs.requires_grad
         ctx.scatter_sum, ctx.reducer = scatter_sum, reducer

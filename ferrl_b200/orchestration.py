@@ -286,7 +286,8 @@ def build_parallel_runtime(cfg: RunConfig, comm: Comm, device: str, model, topol
         ep = {"num_experts": moe.num_experts, "hidden": spec.hidden_size, "max_tokens": max_rows, "top_k": moe.top_k,
               "capacity_factor": cfg.expert_parallel.capacity_factor}
     return ParallelRuntime.create(comm, device, tensor_parallel=tp_on, hidden=spec.hidden_size, max_rows=max_rows,
-                                  expert_parallel=ep, heap_factory=heap_factory)
+                                  expert_parallel=ep, heap_factory=heap_factory,
+                                  sequence_parallel=bool(tp_on and cfg.tensor_parallel.sequence_parallel))
 
 
 def load_and_rank_candidates(run_root: str, require_signed: bool = True, *, steps: Optional[int] = None,

@@ -73,8 +73,9 @@ class ParallelRuntime:
     @classmethod
     def create(cls, comm: Comm, device, *, tensor_parallel: bool = False, hidden: int = 0, max_rows: int = 0,
                expert_parallel: Optional[dict] = None, heap_factory: Optional[Callable] = None,
-               wait_limit_s: float = 20.0, nvls: Optional[bool] = None) -> "ParallelRuntime":
+               wait_limit_s: float = 20.0, nvls: Optional[bool] = None, sequence_parallel: bool = False) -> "ParallelRuntime":
         """``max_rows``: most activation rows (tokens) one forward call carries; ``hidden``: model width.
+        ``sequence_parallel``: also allocate the input buffers of the fused all-gather -> GEMM kernel.
         ``expert_parallel``: ``{num_experts, hidden, max_tokens, top_k, capacity_factor}``."""
         from . import ep as EP
         from . import symm
@@ -85,6 +86,7 @@ class ParallelRuntime:
             rt.heap = (heap_factory or symm.SymmHeap)(comm, dev, wait_limit_s)
         if tensor_parallel and comm.world_size > 1 and rt.heap is not None:
             rows = max(int(max_rows), 128)
+            gcols = int(hidden) if sequence_parallel and on_gpu else 0
             plain = symm.SymmAllReducer(rt.heap, rows * int(hidden) * 4)
             rt.all_reducer = plain
             how = "peer-memory"
@@ -93,7 +95,7 @@ class ParallelRuntime:
                 # (inputs the latter does not take fall back to peer loads)
                 from .nvls import NvlsAllReducer, NvlsUnavailable
                 try:
-                    rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden), nvls=True)
+                    rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden), nvls=True, gather_cols=gcols)
                     fast = NvlsAllReducer(rt.heap, rows * int(hidden) * 4)
                     rt.all_reducer = _FirstOf(fast, plain)
                     how = "NVLS multimem"
@@ -101,7 +103,7 @@ class ParallelRuntime:
                     rt.gemm_reducer = None
                     rt.notes.append(f"nvls unavailable: {e}")
             if rt.gemm_reducer is None:
-                rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden))
+                rt.gemm_reducer = symm.GemmAllReducer(rt.heap, rows, int(hidden), gather_cols=gcols)
             symm.register_gemm_all_reducer(comm, rt.gemm_reducer)
             symm.register_all_reducer(comm, rt.all_reducer)
             if on_gpu:

@@ -141,7 +141,9 @@ class GemmAllReducer:
 
     BM, BN_MAX, BN_MIN = 128, 256, 64
 
-    def __init__(self, heap: SymmHeap, max_rows: int, max_cols: int, nvls: bool = False):
+    GATHER_MAX_ROW_TILES = 1024
+
+    def __init__(self, heap: SymmHeap, max_rows: int, max_cols: int, nvls: bool = False, gather_cols: int = 0):
         """``nvls``: staging and receive buffers bound to NVSwitch multicast objects; the tile owner then reads the
         sum of all ranks' partials with ``multimem.ld_reduce`` and broadcasts the reduced tile with ``multimem.st``
         (raises ``parallel.nvls.NvlsUnavailable`` on every rank where the group has no multicast address)."""
@@ -161,7 +163,12 @@ class GemmAllReducer:
             self.outbuf = heap.alloc(self.out_elems * 2)
         # ready[tile][rank] and done[tile] flags, the device-resident call counter and its CTA counter, then
         # fin[rank]: the last call each peer has left (a sender waits for it before it reuses the staging slots)
-        self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2 + MAX_RANKS) * 4)
+        # then, for the all-gather form, agr[rank] (call number whose rows that peer has in place) and arrived[row tile]
+        self.flags = heap.alloc((self.max_tiles * (MAX_RANKS + 1) + 2 + 2 * MAX_RANKS + self.GATHER_MAX_ROW_TILES) * 4)
+        # all-gather -> GEMM: two [max_rows, gather_cols] input buffers used alternately (see gather_gemm)
+        self.gather_elems = max_rows * gather_cols
+        self.gather_bufs = [heap.alloc(self.gather_elems * 2) for _ in range(2)] if gather_cols > 0 else []
+        self.gather_calls = 0
         self.flags.local.zero_()
         if torch.device(heap.device).type == "cuda":
             torch.cuda.synchronize(heap.device)
@@ -183,6 +190,32 @@ class GemmAllReducer:
         return h.C.lib().gemm_allreduce(a, b, a2, b2, residual, self.stage.ptrs, self.outbuf.ptrs, self.flags.ptrs,
                                         h.rank, h.world, self.epoch, self.max_tiles, self.stage_elems,
                                         self.out_elems, h.wait_limit_s, debug, self.mc_stage, self.mc_outbuf)
+
+    def fits_gather(self, rows: int, k: int) -> bool:
+        """The all-gather form: whole 128-row tiles per rank, the gathered input fits one of the two buffers."""
+        return (bool(self.gather_bufs) and rows % (self.heap.world * self.BM) == 0 and k % 8 == 0
+                and rows // self.BM <= self.GATHER_MAX_ROW_TILES and rows * k <= self.gather_elems)
+
+    def gather_gemm(self, xs: torch.Tensor, b: torch.Tensor, a2=None, b2=None):
+        """``(all_gather_rows(xs) bᵀ + a2 b2ᵀ, all_gather_rows(xs))`` for this rank's ``[rows / world, k]`` block
+        ``xs``: one launch whose communication warps pull the peers' blocks into a local buffer while the tensor cores
+        start on the rows already here; a tile of foreign rows is loaded once its rows have arrived.  The second
+        result is a view of that buffer: it is overwritten by the call after next, copy it to keep it.
+
+        Two buffers alternate: a peer rewrites its block of a buffer two calls later, and it cannot finish the call
+        in between before this rank has entered it, i.e. has finished pulling for this one."""
+        h = self.heap
+        h.guard()
+        n, k = xs.shape
+        rows = n * h.world
+        buf = self.gather_bufs[self.gather_calls & 1]
+        self.gather_calls += 1
+        self.epoch += 1
+        full = buf.local[:rows * k * 2].view(torch.bfloat16).view(rows, k)
+        full[h.rank * n:(h.rank + 1) * n].copy_(xs)
+        y = h.C.lib().gemm_allgather(b, a2, b2, buf.ptrs, self.flags.ptrs, h.rank, h.world, self.max_tiles, rows, k,
+                                     h.wait_limit_s)
+        return y, full
 
     def fits_scatter(self, rows: int, cols: int) -> bool:
         """The reduce-scatter form: whole 128-row tiles per rank, peer-load staging."""

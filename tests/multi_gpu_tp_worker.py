@@ -96,6 +96,48 @@ def _check_reduce_scatter(comm, heap, red, dev, world, rank):
         print("TP_REDUCE_SCATTER_PASS")
 
 
+def _check_gather_gemm(comm, heap, dev, world, rank):
+    """All-gather -> GEMM in one launch against gather-then-GEMM: fresh inputs every call (a tile loaded before its rows
+    arrived would show the previous call's data), shapes whose K is and is not a multiple of the 256-column pull unit."""
+    red = GemmAllReducer(heap, 8192, 4096, gather_cols=5376)
+    for i, (M, N, K, use_lora) in enumerate([(world * 128, 512, 256, False), (world * 512, 1024, 264, True),
+                                             (world * 1024, 2048, 5376, True), (8192, 4096, 2048, False)]):
+        assert red.fits_gather(M, K)
+        n = M // world
+        for rep in range(4):
+            gen = torch.Generator(device=dev).manual_seed(4000 + 100 * i + rep)
+            x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)          # same on every rank
+            b = (torch.randn(N, K, device=dev, generator=torch.Generator(device=dev).manual_seed(77 + rank)) / K ** 0.5).to(torch.bfloat16)
+            t2 = torch.randn(M, 16, device=dev, generator=gen).to(torch.bfloat16) if use_lora else None
+            b2 = (torch.randn(N, 16, device=dev, generator=gen) * 0.1).to(torch.bfloat16) if use_lora else None
+            y, full = red.gather_gemm(x[rank * n:(rank + 1) * n].contiguous(), b, t2, b2)
+            torch.cuda.synchronize()
+            heap.check("fused all-gather gemm")
+            assert torch.equal(full, x), (M, N, K, rep)
+            want = C.gemm(x, b, t2, b2)
+            err = float((y.float() - want.float()).abs().max())
+            assert err <= 2.0 ** -7 * float(want.float().abs().max()), (M, N, K, rep, err)
+    M, K, N = 8192, 4096, 12288 // world
+    x = torch.randn(M, K, device=dev).to(torch.bfloat16)
+    b = (torch.randn(N, K, device=dev) / K ** 0.5).to(torch.bfloat16)
+    n = M // world
+    xs = x[rank * n:(rank + 1) * n].contiguous()
+    t_fused = _time(lambda: red.gather_gemm(xs, b))
+    full = torch.empty(M, K, device=dev, dtype=torch.bfloat16)
+
+    def unfused():
+        dist.all_gather_into_tensor(full, xs)
+        return C.gemm(full, b)
+    t_nccl = _time(unfused)
+    t_gemm = _time(lambda: C.gemm(x, b))
+    heap.check("all-gather gemm timing")
+    comm.barrier()
+    if rank == 0:
+        print(f"TP_AG_TIMING world={world} M={M} N={N} K={K} fused_all_gather_gemm_ms={t_fused:.4f} "
+              f"nccl_all_gather_gemm_ms={t_nccl:.4f} gemm_only_ms={t_gemm:.4f}")
+        print("TP_ALL_GATHER_GEMM_PASS")
+
+
 def _nvls_variant(comm, heap, dev, world, rank, a, b, res, t_nccl):
     """The in-switch form of the same kernel (FERRL_TEST_NVLS=1): same checks, its own timing line.  No rank
     leaves this function before all have finished with the multicast-bound buffers."""
@@ -173,8 +215,8 @@ def _sequence_parallel_checks(comm, heap, red, dev, world, rank):
         outs.append((h.detach().float(), [q.grad.detach().float().clone() for q in model.trainable_params()]))
     heap.check("sequence-parallel model")
     red.reduce_scatter = plain_rs
-    # per layer: o and down forward, qkv and gate_up backward
-    assert fused_calls[0] >= 4 * spec.num_hidden_layers, fused_calls[0]
+    # per layer: o and down forward, qkv and gate_up backward (the first layer's qkv input, the frozen embedding, wants no gradient)
+    assert fused_calls[0] >= 4 * spec.num_hidden_layers - 1, fused_calls[0]
     sp.register_row_collectives(comm, None)
     ref, got = outs
     assert float((ref[0] - got[0]).abs().max()) < 0.05 * float(ref[0].abs().max()), float((ref[0] - got[0]).abs().max())
@@ -189,7 +231,7 @@ def main():
     comm = TorchDistComm.bootstrap(timeout_s=120.0)
     dev, world, rank = comm.device, comm.world_size, comm.rank
     heap = SymmHeap(comm, dev, wait_limit_s=20.0)
-    red = GemmAllReducer(heap, 8192, 4096)
+    red = GemmAllReducer(heap, 8192, 4096, gather_cols=256)    # gather buffers for the small sequence-sharded model below
     _check_reducer(comm, heap, red, dev, world, rank, "fused all-reduce")
 
     # timing: training-shaped row-parallel projection, fused vs. GEMM followed by NCCL
@@ -275,6 +317,7 @@ def main():
     if rank == 0:
         print("TP_SHARDED_HEAD_PASS")
     _sequence_parallel_checks(comm, heap, red, dev, world, rank)
+    _check_gather_gemm(comm, heap, dev, world, rank)
     if rank == 0:
         print("TP_FUSED_PASS")
     dist.destroy_process_group()
