@@ -294,6 +294,13 @@ def main():
         s = T(lambda: train(lambda a, b_, c: G.gated_delta_rule_chunked(a.repeat_interleave(rep_, 2), b_.repeat_interleave(rep_, 2),
                                                                         c, gc, bc, None, use_qk_l2norm=True)))
         report("gdn chunk fwd+bwd B8 T1536 Hv32, eager chunk loop (the former training path)", s, 0, 4 * fl)
+        # one decode token: the 128 x 128 fp32 state of every (row, value head) is read and written once
+        for Bd, Hkd, Hvd in ((64, 16, 48), (128, 16, 16)):
+            qd, kd, vd = (torch.randn(Bd, h * 128, device=dev, dtype=bf) for h in (Hkd, Hkd, Hvd))
+            gg, bb = -torch.rand(Bd, Hvd, device=dev), torch.rand(Bd, Hvd, device=dev)
+            Sd = torch.randn(Bd, Hvd, 128, 128, device=dev) * 0.05
+            s = T(lambda: C.gdn_decode_step(qd, kd, vd, gg, bb, Sd, True, 1e-6))
+            report(f"gdn decode step B{Bd} Hv{Hvd} (state in registers, 16-byte accesses)", s, 2 * Sd.numel() * 4, 0)
     if want("slab"):
         # cost of the adapter k-slab as a function of its width (the k-block is 64 wide whatever R is)
         M, N, K = 24576, 6144, H

@@ -173,6 +173,97 @@ __global__ void gdn_decode_step_kernel(const __nv_bfloat16* __restrict__ q, cons
   }
 }
 
+// The same step for KD x VD states that divide over 256 threads: thread (row group, column group) keeps RPT rows x 4
+// columns of S in registers (16 x float4 at 128 x 128), so every load and store is a 16-byte access of a 512-byte row
+// and all of a CTA's 64 KB are in flight at once; the two dot products (S^T k and S^T q) are finished across the row
+// groups through shared memory in a fixed order.  (One column per thread, as above, needs KD registers per thread and
+// spills at KD = 128.)
+template <int KD, int VD>
+__global__ void __launch_bounds__(256)
+gdn_decode_step_tile_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k,
+                            const __nv_bfloat16* __restrict__ v, long long ldq, long long ldk, long long ldv,
+                            const float* __restrict__ g, const float* __restrict__ beta, float* __restrict__ S, int Hk,
+                            int Hv, int l2norm, float eps, __nv_bfloat16* __restrict__ out, GdnRawGates raw) {
+  constexpr int CG = VD / 4, RG = 256 / CG, RPT = KD / RG;
+  static_assert(VD % 4 == 0 && 256 % CG == 0 && KD % RG == 0 && RPT >= 1, "state does not divide over 256 threads");
+  __shared__ float qs[KD], ks[KD], red[32];
+  __shared__ __align__(16) float part[RG][VD];
+  const int b = blockIdx.x / Hv, hv = blockIdx.x % Hv;
+  const int hk = hv / (Hv / Hk);
+  const int tid = threadIdx.x;
+  const int cg = tid % CG, rg = tid / CG;
+  const long long bh = static_cast<long long>(b) * Hv + hv;
+  // the state does not depend on anything computed here: request it first
+  float4* Sp = reinterpret_cast<float4*>(S + bh * KD * VD) + static_cast<long long>(rg) * RPT * CG + cg;
+  float4 col[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) col[i] = Sp[i * CG];
+  float qq = 0.f, kk = 0.f;
+  for (int i = tid; i < KD; i += 256) {
+    const float qv = __bfloat162float(q[static_cast<long long>(b) * ldq + hk * KD + i]);
+    const float kv = __bfloat162float(k[static_cast<long long>(b) * ldk + hk * KD + i]);
+    qs[i] = qv;
+    ks[i] = kv;
+    qq += qv * qv;
+    kk += kv * kv;
+  }
+  float qn = 1.f, kn = 1.f;
+  if (l2norm) {
+    qn = rsqrtf(block_sum(qq, red) + eps);
+    kn = rsqrtf(block_sum(kk, red) + eps);
+  }
+  __syncthreads();
+  const float qscale = qn * rsqrtf(static_cast<float>(KD));
+  float eg, bt;
+  if (raw.a) {
+    const float x = __bfloat162float(raw.a[static_cast<long long>(b) * raw.lda + hv]) + raw.dt_bias[hv];
+    const float sp = x > 20.f ? x : log1pf(__expf(x));
+    eg = __expf(-__expf(raw.A_log[hv]) * sp);
+    bt = 1.f / (1.f + __expf(-__bfloat162float(raw.b[static_cast<long long>(b) * raw.ldb + hv])));
+  } else {
+    eg = __expf(g[bh]);
+    bt = beta[bh];
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const float kx = ks[rg * RPT + i] * kn;
+    col[i].x *= eg; col[i].y *= eg; col[i].z *= eg; col[i].w *= eg;
+    acc.x += col[i].x * kx; acc.y += col[i].y * kx; acc.z += col[i].z * kx; acc.w += col[i].w * kx;
+  }
+  *reinterpret_cast<float4*>(&part[rg][cg * 4]) = acc;
+  __syncthreads();
+  float4 kv = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int r = 0; r < RG; ++r) {
+    const float4 t = *reinterpret_cast<const float4*>(&part[r][cg * 4]);
+    kv.x += t.x; kv.y += t.y; kv.z += t.z; kv.w += t.w;
+  }
+  const __nv_bfloat16* vp = v + static_cast<long long>(b) * ldv + hv * VD + cg * 4;
+  float4 delta;
+  delta.x = (__bfloat162float(vp[0]) - kv.x) * bt;
+  delta.y = (__bfloat162float(vp[1]) - kv.y) * bt;
+  delta.z = (__bfloat162float(vp[2]) - kv.z) * bt;
+  delta.w = (__bfloat162float(vp[3]) - kv.w) * bt;
+  acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const float kx = ks[rg * RPT + i] * kn, qx = qs[rg * RPT + i] * qscale;
+    col[i].x += kx * delta.x; col[i].y += kx * delta.y; col[i].z += kx * delta.z; col[i].w += kx * delta.w;
+    acc.x += col[i].x * qx; acc.y += col[i].y * qx; acc.z += col[i].z * qx; acc.w += col[i].w * qx;
+    Sp[i * CG] = col[i];
+  }
+  __syncthreads();                       // every thread has read the first sums
+  *reinterpret_cast<float4*>(&part[rg][cg * 4]) = acc;
+  __syncthreads();
+  if (tid < VD) {
+    float o = 0.f;
+#pragma unroll
+    for (int r = 0; r < RG; ++r) o += part[r][tid];
+    out[bh * VD + tid] = __float2bfloat16_rn(o);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // Chunked gated delta rule, forward (crates/ferrl/src/gdn.rs:451-556 composes it from ~40 tensor
 // ops per chunk).  One CTA per (batch row, value head) walks the sequence in chunks of 64 tokens
@@ -520,6 +611,13 @@ const char* gdn_decode_step(const void* q, const void* k, const void* v, long lo
   if (!raw.a && (!g || !beta)) return "gdn_decode_step: either g and beta or the raw gate inputs are needed";
   if (raw.a && (!raw.b || !raw.A_log || !raw.dt_bias)) return "gdn_decode_step: incomplete raw gate inputs";
   if (B == 0) return nullptr;
+  if (KD == 128 && VD == 128) {
+    gdn_decode_step_tile_kernel<128, 128><<<B * Hv, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(q), static_cast<const __nv_bfloat16*>(k), static_cast<const __nv_bfloat16*>(v),
+        ldq, ldk, ldv, g, beta, S, Hk, Hv, l2norm ? 1 : 0, eps, static_cast<__nv_bfloat16*>(out), raw);
+    count_launch();
+    return cudaGetLastError() == cudaSuccess ? nullptr : "gdn_decode_step launch failed";
+  }
   const int threads = std::min(256, (VD + 31) / 32 * 32);
 #define FERRL_GDN_STEP(KDV)                                                                                        \
   gdn_decode_step_kernel<KDV><<<B * Hv, threads, 0, stream>>>(                                                     \
