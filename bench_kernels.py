@@ -301,6 +301,40 @@ def main():
             Sd = torch.randn(Bd, Hvd, 128, 128, device=dev) * 0.05
             s = T(lambda: C.gdn_decode_step(qd, kd, vd, gg, bb, Sd, True, 1e-6))
             report(f"gdn decode step B{Bd} Hv{Hvd} (state in registers, 16-byte accesses)", s, 2 * Sd.numel() * 4, 0)
+    if "hybrid_decode" in only:
+        # one decode step of a 4-layer slice (3 GatedDeltaNet layers + 1 attention layer + final norm and head) of the two
+        # hybrid geometries, replayed from a CUDA graph at cache length prompt + 2048; only on request (builds a model)
+        from ferrl_b200.models.lora import LoraSpec
+        from ferrl_b200.models.qwen35 import MoeDims, Qwen35GradModel, Qwen35LoraTargets, Qwen35Spec
+        kinds = ["full_attention" if i % 4 == 3 else "linear_attention" for i in range(4)]
+        for label, Bd, Pd, Gd, kw, lora, tg in (
+                ("27B-class dense hybrid, 64 rows", 64, 1024, 16,
+                 dict(hidden_size=5120, num_attention_heads=24, num_key_value_heads=4, intermediate_size=17408, lin_v_heads=48),
+                 LoraSpec(rank=32, alpha=64.0), Qwen35LoraTargets("qkvo", "gud", "io")),
+                ("hybrid MoE 128 experts top-8, 128 rows", 128, 512, 8,
+                 dict(hidden_size=2048, num_attention_heads=16, num_key_value_heads=2, intermediate_size=768, lin_v_heads=16,
+                      moe=MoeDims(128, 8, 768, 768)),
+                 LoraSpec(rank=8, alpha=16.0), Qwen35LoraTargets("qkvo", "gud", ""))):
+            spec = Qwen35Spec(vocab_size=V, num_hidden_layers=4, head_dim=256, layer_types=kinds, max_position_embeddings=6144,
+                              lin_k_heads=16, lin_k_dim=128, lin_v_dim=128, **kw)
+            model = Qwen35GradModel(spec, lora, tg, keep_transpose=False, dtype=bf, device=dev)
+            model.init_random(seed=1)
+            model.merge_adapters()
+            dec = model.new_decoder(Bd, Pd + 3072, None)
+            with torch.no_grad():
+                dec.prefill(torch.randint(0, 1000, (Bd // Gd, Pd), device=dev), torch.full((Bd // Gd,), Pd, device=dev))
+                dec.broadcast_groups(Gd)
+                dec.kv_len += 2048
+                tok = torch.randint(0, 1000, (Bd,), device=dev)
+                for _ in range(3):
+                    dec.decode(tok)
+                torch.cuda.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    dec.decode(tok)
+                s = T(graph.replay)
+            report(f"decode step, 4-layer slice: {label}", s, 0, 0)
+            del graph, dec, model
     if want("slab"):
         # cost of the adapter k-slab as a function of its width (the k-block is 64 wide whatever R is)
         M, N, K = 24576, 6144, H

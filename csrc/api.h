@@ -280,7 +280,7 @@ struct EpDispatchParams {
   const int* my_counts;                    // [E] pairs per global expert on this rank
   PeerTable counts_all;                    // int [world][E] on every rank
   PeerTable xs;                            // bf16 [cap_rows][H] receive buffer on every rank
-  PeerTable flags; unsigned epoch; unsigned long long limit_ns; int* status; int* abort_word;
+  PeerTable flags; unsigned epoch; unsigned long long limit_ns; int* status; int* abort_word;   // epoch: unused, the call number lives in `flags`
   int cap_rows;
   int* dest_row;                           // [T*k] row of each pair in its owner's buffer (out, or in when reuse_plan)
   int* tile_expert;                        // [cap_rows/128] local expert of each received tile, -1 unused (out)

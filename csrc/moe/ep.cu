@@ -32,7 +32,13 @@ namespace ferrl {
 namespace {
 
 constexpr int kSeg = 128;
-constexpr int kSlotCounts = 4, kSlotPushed = 5, kSlotExperts = 6;
+// The flag buffer belongs to the expert-parallel runtime alone: three barrier slots, then the call number.  The
+// number lives on the device and each kernel advances it when it is through with its barriers, so a captured CUDA
+// graph (the decode step) replays with fresh flag values; ranks call in lockstep, so their numbers agree.
+constexpr int kSlotCounts = 0, kSlotPushed = 1, kSlotExperts = 2, kCallWord = 3 * kMaxRanks;
+__device__ __forceinline__ volatile uint32_t* ep_call_word(const PeerTable& flags, int rank) {
+  return static_cast<volatile uint32_t*>(flags.ptr[rank]) + kCallWord;
+}
 
 __device__ __forceinline__ int pad_seg(int n) { return (n + kSeg - 1) / kSeg * kSeg; }
 
@@ -41,6 +47,8 @@ __global__ void __launch_bounds__(512) ep_dispatch_kernel(EpDispatchParams p) {
   __shared__ int s_base, s_off, s_running, s_warp[16];
   volatile int* abort_word = p.abort_word;
   const int n_pairs = p.T * p.k;
+  uint32_t epoch = 0;                              // used by thread 0 of block 0 only
+  if (blockIdx.x == 0 && threadIdx.x == 0) epoch = *ep_call_word(p.flags, p.rank) + 1;
 
   if (!p.reuse_plan) {
     // ---- phase 0: publish my per-expert counts to every rank, wait for everyone's
@@ -52,7 +60,7 @@ __global__ void __launch_bounds__(512) ep_dispatch_kernel(EpDispatchParams p) {
       __threadfence_system();
       __syncthreads();
       if (threadIdx.x == 0) {
-        const bool ok = peer_barrier(p.flags, kSlotCounts, p.rank, p.world, p.epoch, p.limit_ns, p.status);
+        const bool ok = peer_barrier(p.flags, kSlotCounts, p.rank, p.world, epoch, p.limit_ns, p.status);
         *abort_word = ok ? 0 : 1;
         __threadfence();
       }
@@ -140,8 +148,9 @@ __global__ void __launch_bounds__(512) ep_dispatch_kernel(EpDispatchParams p) {
   __threadfence_system();
   grid.sync();
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    const bool ok = peer_barrier(p.flags, kSlotPushed, p.rank, p.world, p.epoch, p.limit_ns, p.status);
+    const bool ok = peer_barrier(p.flags, kSlotPushed, p.rank, p.world, epoch, p.limit_ns, p.status);
     if (!ok) *abort_word = 1;
+    *ep_call_word(p.flags, p.rank) = epoch;
   }
 }
 
@@ -149,8 +158,10 @@ __global__ void __launch_bounds__(512) ep_combine_kernel(EpCombineParams p) {
   cg::grid_group grid = cg::this_grid();
   volatile int* abort_word = p.abort_word;
   if (blockIdx.x == 0 && threadIdx.x == 0) {
-    const bool ok = peer_barrier(p.flags, kSlotExperts, p.rank, p.world, p.epoch, p.limit_ns, p.status);
+    const uint32_t epoch = *ep_call_word(p.flags, p.rank) + 1;
+    const bool ok = peer_barrier(p.flags, kSlotExperts, p.rank, p.world, epoch, p.limit_ns, p.status);
     *abort_word = ok ? 0 : 1;
+    *ep_call_word(p.flags, p.rank) = epoch;
     __threadfence();
   }
   grid.sync();

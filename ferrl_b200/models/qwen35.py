@@ -143,9 +143,11 @@ class _Mlp(nn.Module):
         self.down = FusedLoraLinear(inter, [hidden], ("down",), ("d" in tg.mlp,), lora, **kw)
         self.act = act
 
-    def forward(self, x, merged=False):
-        f = (lambda m, z: m.forward_merged(z)) if merged else (lambda m, z: m(z))
-        return f(self.down, ops.swiglu(f(self.gate_up, x), self.act))
+    def forward(self, x, merged=False, residual=None):
+        """``residual`` (the layer's stream) is added in the down projection's GEMM epilogue."""
+        if merged:
+            return self.down.forward_merged(ops.swiglu(self.gate_up.forward_merged(x), self.act), residual)
+        return self.down(ops.swiglu(self.gate_up(x), self.act), residual)
 
     def projections(self):
         return (self.gate_up, self.down)
@@ -335,6 +337,8 @@ class Qwen35Layer(nn.Module):
         else:
             o, new_state = self._gdn(x, merged, cache, valid, decode)
         x, h = ops.add_rmsnorm(o, h, self.post_norm, self.eps, True)
+        if self.spec.moe is None:
+            return self.mlp(x, merged, residual=h), new_state
         return h + self._ffn(x, merged), new_state
 
 

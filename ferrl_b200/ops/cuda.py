@@ -696,10 +696,15 @@ class _MoeExperts(torch.autograd.Function):
         T, k = idx.shape
         row_of, token_of, tile_expert, _ = L.moe_plan(idx.contiguous(), counts)
         xs = L.moe_gather(x.contiguous(), token_of, None, row_of)
-        gu = L.moe_grouped_gemm(xs, gate_up, tile_expert)
+        # rows of unused tiles are never written and never read back (the combine reads routed rows only); the
+        # zero fill of the outputs is kept for training, where the padded rows are saved for the backward pass
+        train = any(ctx.needs_input_grad)
+        o1 = None if train else torch.empty(xs.shape[0], gate_up.shape[1], dtype=xs.dtype, device=xs.device)
+        gu = L.moe_grouped_gemm(xs, gate_up, tile_expert, o1)
         del xs
         h = L.glu_fwd(gu, act)
-        ys = L.moe_grouped_gemm(h, down, tile_expert)
+        o2 = None if train else torch.empty(h.shape[0], down.shape[1], dtype=h.dtype, device=h.device)
+        ys = L.moe_grouped_gemm(h, down, tile_expert, o2)
         del h
         sc = scores.float().contiguous()
         out = L.moe_combine(ys, row_of, sc, T, k)

@@ -51,6 +51,15 @@ class EpRuntime:
         self.xs = heap.alloc(self.cap_rows * hidden * 2)
         self.ys = heap.alloc(self.cap_rows * hidden * 2)
         self.counts_all = heap.alloc(heap.world * num_experts * 4)
+        # barrier flags of the two kernels and their device-resident call number (the kernels advance it themselves, so
+        # the decode step can be captured in a CUDA graph and replayed)
+        from .symm import MAX_RANKS
+        self.flags = heap.alloc((3 * MAX_RANKS + 4) * 4)
+        self.flags.local.zero_()
+        if torch.device(heap.device).type == "cuda":
+            torch.cuda.synchronize(heap.device)
+        if heap.world > 1:
+            heap.comm.barrier()     # nobody signals into flags that are still being cleared
 
     def view(self, buf) -> torch.Tensor:
         return buf.local.view(torch.bfloat16)[:self.cap_rows * self.H].view(self.cap_rows, self.H)
@@ -75,17 +84,19 @@ class _EpExperts(torch.autograd.Function):
         tile_expert = torch.full((rt.cap_rows // 128,), -1, dtype=torch.int32, device=dev)
         local_rows = torch.zeros(1, dtype=torch.int32, device=dev)
         xc = x.contiguous()
-        L.ep_dispatch(xc, idx, None, counts, rt.counts_all.ptrs, rt.xs.ptrs, h.flags.ptrs, h.rank, h.world,
-                      h.next_epoch(), h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, False, h.abort_word)
-        gu = L.moe_grouped_gemm(rt.view(rt.xs), gate_up, tile_expert)
+        L.ep_dispatch(xc, idx, None, counts, rt.counts_all.ptrs, rt.xs.ptrs, rt.flags.ptrs, h.rank, h.world,
+                      0, h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, False, h.abort_word)
+        need = x.requires_grad or scores.requires_grad
+        # unused tiles are never written nor read back; the zero fill is kept where the rows are saved for backward
+        o1 = None if need else torch.empty(rt.cap_rows, gate_up.shape[1], dtype=torch.bfloat16, device=dev)
+        gu = L.moe_grouped_gemm(rt.view(rt.xs), gate_up, tile_expert, o1)
         hh = L.glu_fwd(gu, act)
         L.moe_grouped_gemm(hh, down, tile_expert, rt.view(rt.ys))
         del hh
         sc = scores.float().contiguous()
-        need = x.requires_grad or scores.requires_grad
         keep = torch.empty(T * k, x.shape[1], dtype=torch.bfloat16, device=dev) if need else None
-        out = L.ep_combine(rt.ys.ptrs, idx, dest_row, sc, x.shape[1], rt.E_local, h.flags.ptrs, h.rank, h.world,
-                           h.next_epoch(), h.wait_limit_s, keep, h.abort_word)
+        out = L.ep_combine(rt.ys.ptrs, idx, dest_row, sc, x.shape[1], rt.E_local, rt.flags.ptrs, h.rank, h.world,
+                           0, h.wait_limit_s, keep, h.abort_word)
         ctx.save_for_backward(gu, keep, sc, idx, counts, dest_row, tile_expert, local_rows, gate_up, down, gate_up_t, down_t)
         ctx.act, ctx.rt, ctx.score_dtype = act, rt, scores.dtype
         return out
@@ -100,8 +111,8 @@ class _EpExperts(torch.autograd.Function):
         dout = dout.contiguous()
         ident = torch.arange(T * k, dtype=torch.int32, device=dout.device)
         dsc = L.moe_pair_dot(dout, keep, ident, k).to(ctx.score_dtype)
-        L.ep_dispatch(dout, idx, sc.view(-1), counts, rt.counts_all.ptrs, rt.xs.ptrs, h.flags.ptrs, h.rank, h.world,
-                      h.next_epoch(), h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, True, h.abort_word)
+        L.ep_dispatch(dout, idx, sc.view(-1), counts, rt.counts_all.ptrs, rt.xs.ptrs, rt.flags.ptrs, h.rank, h.world,
+                      0, h.wait_limit_s, rt.cap_rows, dest_row, tile_expert, local_rows, True, h.abort_word)
         if down_t is None:
             down_t = down.transpose(1, 2).contiguous()
         dh = L.moe_grouped_gemm(rt.view(rt.xs), down_t, tile_expert)
@@ -110,8 +121,8 @@ class _EpExperts(torch.autograd.Function):
         if gate_up_t is None:
             gate_up_t = gate_up.transpose(1, 2).contiguous()
         L.moe_grouped_gemm(dgu, gate_up_t, tile_expert, rt.view(rt.ys))
-        dx = L.ep_combine(rt.ys.ptrs, idx, dest_row, None, dout.shape[1], rt.E_local, h.flags.ptrs, h.rank, h.world,
-                          h.next_epoch(), h.wait_limit_s, None, h.abort_word)
+        dx = L.ep_combine(rt.ys.ptrs, idx, dest_row, None, dout.shape[1], rt.E_local, rt.flags.ptrs, h.rank, h.world,
+                          0, h.wait_limit_s, None, h.abort_word)
         return dx, dsc, None, None, None, None, None, None, None, None
 
 

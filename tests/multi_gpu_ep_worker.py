@@ -44,6 +44,35 @@ def main():
         heap.check("expert-parallel step")
         for a, b in zip(res[0], res[1]):
             assert torch.equal(a, b), (rep, float((a.float() - b.float()).abs().max()))
+    # the decode step is replayed from a CUDA graph: the kernels' barriers must use a fresh call number on every
+    # replay (it lives on the device), so replays with new inputs must keep matching the local plan
+    Td = 128
+    xs_ = torch.zeros(Td, H, device=dev, dtype=torch.bfloat16)
+    lg_ = torch.zeros(Td, E, device=dev)
+    gu_l, dn_l = gate_up[lo:hi].contiguous(), down[lo:hi].contiguous()
+
+    def step():
+        with torch.no_grad():
+            sc_, idx_, cnt_, _ = C.moe_route(lg_, k, True)
+            return rt.experts(xs_, sc_, idx_, cnt_, gu_l, dn_l, "silu")
+    step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        y_static = step()
+    for rep in range(4):
+        xs_.copy_(torch.randn(Td, H, device=dev, generator=gl).to(torch.bfloat16))
+        lg_.copy_(torch.randn(Td, E, device=dev, generator=gl))
+        graph.replay()
+        with torch.no_grad():
+            sc_, idx_, cnt_, _ = C.moe_route(lg_, k, True)
+            want = C.moe_experts(xs_, sc_, idx_, cnt_, gate_up, down, "silu")
+        torch.cuda.synchronize()
+        heap.check("expert-parallel graph replay")
+        assert torch.equal(y_static, want), (rep, float((y_static.float() - want.float()).abs().max()))
+    comm.barrier()
+    if rank == 0:
+        print("EP_GRAPH_REPLAY_PASS")
     # timing at the hybrid-MoE benchmark's layer shape: 128 experts top-8, hidden 2048, expert FFN 768
     if world in (2, 4, 8):
         T2, E2, k2, H2, I2 = 8192, 128, 8, 2048, 768

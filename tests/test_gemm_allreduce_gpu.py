@@ -165,7 +165,8 @@ def test_multi_process_fused_tp(world):
 def test_multi_process_expert_parallel(world):
     _need_gpu(world)
     out = _torchrun("multi_gpu_ep_worker.py", world, 29633 + world, "EP_PASS")
-    print("\n".join(l for l in out.splitlines() if l.startswith("EP_TIMING")))
+    print("\n".join(l for l in out.splitlines() if l.startswith("EP_")))
+    assert "EP_GRAPH_REPLAY_PASS" in out
 
 
 @pytest.mark.parametrize("world", [int(w) for w in os.environ.get("FERRL_TEST_NVLS_WORLDS", "2").split(",")])
