@@ -68,12 +68,51 @@ class LaunchManifest:
     candidate_public_key: Optional[str]
     launch_authentication: str
     created_unix: int
+    evaluation_samples_sha256: Optional[str] = None
 
     def to_json(self) -> dict:
         return dataclasses.asdict(self)
 
     def digest(self) -> str:
         return canonical_digest(self.to_json(), b"ferrl-b200/launch-manifest/v1")
+
+
+def exact_execution_samples(samples) -> bytes:
+    """The ordered samples as the JSON bytes whose SHA-256 the ranks must agree on.  The bytes must survive a parse
+    and re-serialisation unchanged (no NaN, no value that only ``repr`` can express), so that a run can be rebuilt
+    from them (reference: ``exact_execution_samples``, crates/ferrl/src/orchestration.rs:587-597)."""
+    blob = ("[" + ",".join(s.key() for s in samples) + "]").encode()
+
+    def reject(constant):
+        raise OrchestrationError(f"samples contain {constant}, which strict JSON cannot carry")
+    parsed = json.loads(blob.decode(), parse_constant=reject)
+    if len(parsed) != len(samples) or any(set(p) != {"prompt", "target"} for p in parsed):
+        raise OrchestrationError("samples do not round-trip through JSON")
+    return blob
+
+
+def preflight_prompt_tokenization(samples, kind: str, tokenizer) -> None:
+    """A prompt that encodes to no tokens would silently become an empty model input
+    (crates/ferrl/src/orchestration.rs:599-613)."""
+    for index, sample in enumerate(samples):
+        if len(tokenizer.encode(sample.prompt)) == 0:
+            raise OrchestrationError(f"{kind} prompt at index {index} encoded to zero tokens with the loaded tokenizer")
+
+
+def preflight_samples(train_samples, eval_samples, tokenizer, comm: Comm) -> tuple[str, str]:
+    """The preflight stage of the engine (crates/ferrl/src/orchestration.rs:2027-2082): exact sample bytes and the
+    tokenizer check run locally, a failure on any rank stops all of them together, then the ranks must agree on both
+    digests.  Returns ``(training_sha256, evaluation_sha256)``."""
+    def local():
+        tb = exact_execution_samples(train_samples)
+        eb = exact_execution_samples(eval_samples)
+        preflight_prompt_tokenization(train_samples, "ordered training samples", tokenizer)
+        preflight_prompt_tokenization(eval_samples, "ordered held-out samples", tokenizer)
+        return hashlib.sha256(tb).hexdigest(), hashlib.sha256(eb).hexdigest()
+    train_sha, eval_sha = comm.coordinate(local, "exact sample reconstruction and tokenizer preflight")
+    comm.require_consensus(train_sha.encode(), "ordered training samples")
+    comm.require_consensus(eval_sha.encode(), "ordered held-out samples")
+    return train_sha, eval_sha
 
 
 def synchronized_run_id(task: str, comm: Comm, suffix_rank: bool = False) -> str:
@@ -197,14 +236,15 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
         # so no rank leaves the decode loop early and no rank skips a degenerate group on its own
         policy.early_exit_every = 0
     # ---- launch manifest + run dir
-    samples_sha = hashlib.sha256("\n".join(s.key() for s in train_samples).encode()).hexdigest()
+    samples_sha, eval_samples_sha = preflight_samples(train_samples, eval_samples, tokenizer, comm)
     launch_sha_seed = hashlib.sha256((run_id + cfg.digest()).encode()).digest()
     signer = None
     if cfg.launch_authentication == "signed":
         signer = T.CandidateSigner("", seed=None)
     manifest = LaunchManifest(run_id, cfg.task, cfg.digest(), pident.digest(), tokenizer.digest(), samples_sha,
                               ident.to_json(), comm.world_size, topology,
-                              signer.public_key_hex if signer else None, cfg.launch_authentication, int(time.time()))
+                              signer.public_key_hex if signer else None, cfg.launch_authentication, int(time.time()),
+                              eval_samples_sha)
     if signer:
         signer.launch_sha256 = manifest.digest()
     del launch_sha_seed

@@ -1081,3 +1081,47 @@ def test_parallel_runtime_ignores_the_in_switch_request_off_gpu_and_composes_red
     both = _FirstOf(first, second)
     assert torch.equal(both(torch.zeros(4)), torch.ones(4)) and calls == ["first"]
     assert torch.equal(both(torch.zeros(3)), torch.full((3,), 2.0)) and calls == ["first", "first", "second"]
+
+
+def test_preflight_stage_checks_samples_and_tokenization():
+    """Engine preflight (reference: crates/ferrl/src/orchestration.rs:2027-2082 and its unit tests at :6139-6168):
+    exact sample bytes, a prompt that encodes to nothing is refused on every rank, ranks must hold the same samples."""
+    from ferrl_b200.comm import CommMismatch, PeerFailure, SoloComm, run_ranks
+    from ferrl_b200.orchestration import (OrchestrationError, exact_execution_samples, preflight_prompt_tokenization,
+                                          preflight_samples)
+    from ferrl_b200.rewards import Sample
+
+    class OneToken:
+        def encode(self, text):
+            return [1]
+
+    class Empty:
+        def encode(self, text):
+            return []
+
+    samples = [Sample("alpha", (1, 2)), Sample("beta", {"k": [3, 4]})]
+    blob = exact_execution_samples(samples)
+    assert json.loads(blob.decode()) == [{"prompt": "alpha", "target": [1, 2]}, {"prompt": "beta", "target": {"k": [3, 4]}}]
+    with pytest.raises(OrchestrationError, match="strict JSON cannot carry"):
+        exact_execution_samples([Sample("x", float("nan"))])
+    preflight_prompt_tokenization([Sample("", None), Sample("", None)], "ordered held-out samples", OneToken())
+    with pytest.raises(OrchestrationError, match="ordered training samples prompt at index 0 encoded to zero tokens"):
+        preflight_prompt_tokenization([Sample("", None)], "ordered training samples", Empty())
+    a, b = preflight_samples(samples, samples[:1], OneToken(), SoloComm())
+    assert len(a) == 64 and len(b) == 64 and a != b
+
+    def rank_fn(comm):
+        # rank 1's tokenizer yields nothing: both ranks must stop with the coordinated failure
+        try:
+            preflight_samples(samples, [], Empty() if comm.rank == 1 else OneToken(), comm)
+        except PeerFailure as e:
+            first = "local" if e.local is not None else "peer"
+        else:
+            first = "none"
+        # rank 1 holds different samples: consensus on the digest fails on both
+        try:
+            preflight_samples(samples if comm.rank == 0 else samples[::-1], [], OneToken(), comm)
+        except CommMismatch:
+            return first, "mismatch"
+        return first, "agreed"
+    assert run_ranks(2, rank_fn) == [("peer", "mismatch"), ("local", "mismatch")]
