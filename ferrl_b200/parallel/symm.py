@@ -77,6 +77,12 @@ class SymmHeap:
         return SymmBuffer(local, ptrs)
 
     def next_epoch(self) -> int:
+        """The next call number of the host-numbered kernels (all-reduce, row collectives, the data-parallel step).
+        A CUDA graph would replay such a launch with the number it was captured with, and its barriers would find
+        every flag already there; kernels meant for capture keep their call number on the device instead (the fused
+        GEMM collectives, the expert-parallel dispatch and combine)."""
+        if torch.device(self.device).type == "cuda" and torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("a host-numbered peer-memory collective cannot be captured in a CUDA graph")
         self.epoch += 1
         return self.epoch
 

@@ -78,6 +78,8 @@ def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
     epoch = 7
     done_base = red.max_tiles * MAXR
     mine["flags"][red.max_tiles * (MAXR + 1)] = epoch - 1      # device-resident call counter: this call is number 7
+    fin_base = red.max_tiles * (MAXR + 1) + 2
+    mine["flags"][fin_base + peer] = epoch - 1                  # the peer has left the previous call
     for t in range(mt * nt):
         mi, ni = divmod(t, nt)
         if t % 2 == rank:     # mine to reduce: the peer's partial is already in my staging slot
@@ -96,6 +98,7 @@ def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
     torch.cuda.synchronize()
     assert C.kernel_status() == 0
     assert int(mine["flags"][red.max_tiles * (MAXR + 1)]) == epoch      # the kernel advanced its own counter
+    assert int(theirs["flags"][fin_base + rank]) == epoch               # and told the peer that it has left this call
     tol = 0.02 * float(want.float().abs().max())
     assert float((y.float() - want.float()).abs().max()) <= tol
     peer_out = theirs["out"][:M * N].view(M, N)
@@ -114,6 +117,109 @@ def test_rank_against_host_played_peer(M, N, K, rank, res, lora):
             assert float((got.float() - ref.float()).abs().max()) <= tol
             assert int(theirs["flags"][t * MAXR + rank]) == epoch
             assert torch.equal(y[rows, cols], want[rows, cols])     # copied verbatim from my output buffer
+
+
+@pytest.mark.parametrize("rank,lora", [(0, False), (1, True)])
+def test_reduce_scatter_form_against_host_played_peer(rank, lora):
+    """Reduce-scatter form: this rank keeps its own row block of the sum, pushes its partials of the peer's block
+    and sends nothing back."""
+    _need_gpu()
+    from ferrl_b200.comm import SoloComm
+    from ferrl_b200.ops import cuda as C
+    from ferrl_b200.parallel.symm import GemmAllReducer, SymmHeap
+    dev = torch.device("cuda", 0)
+    M, N, K, BN = 512, 512, 256, 128
+    g = torch.Generator(device=dev).manual_seed(91 + rank)
+    rnd = lambda *s: torch.randn(*s, device=dev, generator=g)
+    peer = 1 - rank
+    a = [rnd(M, K).to(torch.bfloat16) for _ in range(2)]
+    b = [(rnd(N, K) / K ** 0.5).to(torch.bfloat16) for _ in range(2)]
+    t2 = [rnd(M, 16).to(torch.bfloat16) for _ in range(2)] if lora else [None, None]
+    b2 = (rnd(N, 16) * 0.1).to(torch.bfloat16) if lora else None
+    part = []
+    for r in range(2):
+        p = a[r].float() @ b[r].float().t()
+        if lora:
+            p = p + t2[r].float() @ b2.float().t()
+        part.append(p.to(torch.bfloat16))
+    want = (part[0].float() + part[1].float()).to(torch.bfloat16)
+    heap = SymmHeap(SoloComm(), dev, wait_limit_s=0.5)
+    red = GemmAllReducer(heap, M, N)
+    mt, nt = _tiles(M, N, BN)
+    mt_per, slot = mt // 2, BM * BN
+    mine = dict(stage=red.stage.local.view(torch.bfloat16), flags=red.flags.local.view(torch.int32))
+    theirs = dict(stage=torch.zeros_like(mine["stage"]), flags=torch.zeros_like(mine["flags"]))
+    spare_out = torch.zeros_like(red.outbuf.local)
+    epoch = 5
+    ctr = red.max_tiles * (MAXR + 1)
+    mine["flags"][ctr] = epoch - 1
+    mine["flags"][ctr + 2 + peer] = epoch - 1
+    local_slot = lambda mi, ni, owner, frm: (((mi - owner * mt_per) * nt + ni) * 2 + frm) * slot
+    for mi in range(rank * mt_per, (rank + 1) * mt_per):          # my row block: the peer's partials are already here
+        for ni in range(nt):
+            off = local_slot(mi, ni, rank, peer)
+            mine["stage"][off:off + slot] = _chunk_major(_pad_tile(part[peer], mi, ni, BN))
+            mine["flags"][(mi * nt + ni) * MAXR + peer] = epoch
+    ptrs = lambda key: [(mine if r == rank else theirs)[key].data_ptr() for r in range(2)]
+    outs = [red.outbuf.local.data_ptr() if r == rank else spare_out.data_ptr() for r in range(2)]
+    torch.cuda.synchronize()
+    y = C.lib().gemm_allreduce(a[rank], b[rank], t2[rank], b2, None, ptrs("stage"), outs, ptrs("flags"), rank, 2, epoch,
+                               red.max_tiles, red.stage_elems, red.out_elems, 0.5, None, 0, 0, True)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    n = M // 2
+    tol = 0.02 * float(want.float().abs().max())
+    assert y.shape == (n, N)
+    assert float((y.float() - want[rank * n:(rank + 1) * n].float()).abs().max()) <= tol
+    for mi in range(peer * mt_per, (peer + 1) * mt_per):          # the peer's row block: my partials and their flags
+        for ni in range(nt):
+            off = local_slot(mi, ni, peer, rank)
+            got = theirs["stage"][off:off + slot].reshape(BN // 8, BM, 8).permute(1, 0, 2).reshape(BM, BN)
+            assert float((got.float() - _pad_tile(part[rank], mi, ni, BN).float()).abs().max()) <= tol
+            assert int(theirs["flags"][(mi * nt + ni) * MAXR + rank]) == epoch
+    assert int(mine["flags"][ctr]) == epoch and int(theirs["flags"][ctr + 2 + rank]) == epoch
+    assert not bool(spare_out.any())                               # nothing is sent back in this form
+
+
+@pytest.mark.parametrize("rank,K", [(0, 256), (1, 264)])
+def test_all_gather_form_against_host_played_peer(rank, K):
+    """All-gather form: the peer's rows sit in its buffer (here: a second local buffer) with its "rows in place" flag
+    set; the kernel pulls them into this rank's buffer and multiplies all rows."""
+    _need_gpu()
+    from ferrl_b200.comm import SoloComm
+    from ferrl_b200.ops import cuda as C
+    from ferrl_b200.parallel.symm import GemmAllReducer, SymmHeap
+    dev = torch.device("cuda", 0)
+    M, N = 512, 384
+    g = torch.Generator(device=dev).manual_seed(17 + rank)
+    x = torch.randn(M, K, device=dev, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, device=dev, generator=g) / K ** 0.5).to(torch.bfloat16)
+    peer, n = 1 - rank, M // 2
+    heap = SymmHeap(SoloComm(), dev, wait_limit_s=0.5)
+    red = GemmAllReducer(heap, M, N, gather_cols=K)
+    mine_buf = red.gather_bufs[0].local[:M * K * 2].view(torch.bfloat16).view(M, K)
+    mine_buf.zero_()
+    mine_buf[rank * n:(rank + 1) * n] = x[rank * n:(rank + 1) * n]
+    their_buf = torch.zeros(M, K, device=dev, dtype=torch.bfloat16)
+    their_buf[peer * n:(peer + 1) * n] = x[peer * n:(peer + 1) * n]
+    flags = red.flags.local.view(torch.int32)
+    their_flags = torch.zeros_like(flags)
+    epoch = 9
+    ctr = red.max_tiles * (MAXR + 1)
+    agr, arrived = ctr + 2 + MAXR, ctr + 2 + 2 * MAXR
+    flags[ctr] = epoch - 1
+    flags[agr + peer] = epoch                                      # the peer's rows are in place
+    bufs = [mine_buf.data_ptr() if r == rank else their_buf.data_ptr() for r in range(2)]
+    fl = [flags.data_ptr() if r == rank else their_flags.data_ptr() for r in range(2)]
+    torch.cuda.synchronize()
+    y = C.lib().gemm_allgather(w, None, None, bufs, fl, rank, 2, red.max_tiles, M, K, 0.5)
+    torch.cuda.synchronize()
+    assert C.kernel_status() == 0
+    assert torch.equal(mine_buf, x)
+    ref = x.float() @ w.float().t()
+    assert float((y.float() - ref).abs().max()) <= 0.02 * float(ref.abs().max())
+    assert int(flags[ctr]) == epoch and int(their_flags[agr + rank]) == epoch
+    assert not bool(flags[arrived:arrived + M // BM].any())         # arrival counts are back to zero for the next call
 
 
 def test_missing_peer_runs_out_without_hanging():
