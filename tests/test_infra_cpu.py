@@ -1125,3 +1125,43 @@ def test_preflight_stage_checks_samples_and_tokenization():
             return first, "mismatch"
         return first, "agreed"
     assert run_ranks(2, rank_fn) == [("peer", "mismatch"), ("local", "mismatch")]
+
+
+def test_sequence_parallel_key_reaches_the_model_or_is_refused(tmp_path):
+    """``tensor_parallel.sequence_parallel`` is part of the strict schema; a family whose layers have no
+    sequence-sharded form refuses it on every rank; the Gemma family trains with it over two thread ranks and ends
+    with the same metrics as the replicated layout (same sums in the same rank order)."""
+    from ferrl_b200.comm import run_ranks
+    from ferrl_b200.orchestration import OrchestrationError, run_cli_train_setup
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+
+    from test_models_oracle import make_ckpt
+    gemma_dir = tmp_path / "gemma_ckpt"
+    gemma_dir.mkdir()
+    make_ckpt(str(gemma_dir))                    # 4 query / 2 kv heads: shards over two ranks
+
+    def cfg(root, rank, model, on):
+        c = _tp_cfg(root, rank)
+        c.model_dir = str(gemma_dir) if model == "gemma" else os.path.join(FIX, model)
+        c.tensor_parallel.sequence_parallel = on
+        return c
+    assert RunConfig.from_json(cfg(tmp_path, 0, "gemma", True).to_json()).tensor_parallel.sequence_parallel is True
+    with pytest.raises(Exception, match="sequence_paralel"):
+        RunConfig.from_json({"task": "countdown", "model_dir": "x", "trainer": {"steps": 1},
+                             "tensor_parallel": {"sequence_paralel": True}})
+
+    def refused(comm):
+        with pytest.raises(OrchestrationError, match="sequence_parallel is not supported"):
+            run_cli_train_setup(cfg(tmp_path / "dense", comm.rank, "tiny_qwen3", True), comm, allow_dirty=True,
+                                tokenizer=SyntheticTokenizer(32, 4, 8))
+        return True
+    assert run_ranks(2, refused, timeout=120) == [True, True]
+
+    def train(comm, on):
+        out = run_cli_train_setup(cfg(tmp_path / ("sp" if on else "tp"), comm.rank, "gemma", on), comm, allow_dirty=True,
+                                  tokenizer=SyntheticTokenizer(16, 4, 8))      # the checkpoint's vocabulary has 16 entries
+        rows = [json.loads(l) for l in open(os.path.join(out.run_dir, "metrics.jsonl"))] if comm.rank == 0 else []
+        return out.steps_run, [(round(r["loss"], 5), round(r["grad_norm"], 4)) for r in rows]
+    sharded = run_ranks(2, lambda c: train(c, True), timeout=180)
+    plain = run_ranks(2, lambda c: train(c, False), timeout=180)
+    assert sharded[0][0] == 2 and sharded[0][1] == plain[0][1]
