@@ -51,6 +51,9 @@ class SymmHeap:
         self.epoch = 0
         self.poisoned: Optional[str] = None
         self._opened: list = []
+        # every allocation lives as long as the heap: peers keep their mappings of it until close(), and memory that
+        # was freed and handed out again under the same handle cannot be mapped a second time
+        self._allocations: list = []
         with torch.cuda.device(device):
             self.flags = self.alloc(FLAG_SLOTS * MAX_RANKS * 4)
             self.abort_word = torch.zeros(1, dtype=torch.int32, device=device)
@@ -74,6 +77,7 @@ class SymmHeap:
                 ptrs.append(p)
         if self.world > 1:
             self.comm.barrier()  # every rank has mapped every peer before anyone uses the buffer
+        self._allocations.append(local)
         return SymmBuffer(local, ptrs)
 
     def next_epoch(self) -> int:
@@ -110,6 +114,7 @@ class SymmHeap:
         for p in self._opened:
             lib.symm_close(p)
         self._opened = []
+        self._allocations = []
         _HEAPS.pop(id(self.comm), None)
 
 
