@@ -242,6 +242,17 @@ def test_examples_run_end_to_end_on_cpu(tmp_path):
     assert "2 steps" in report
     assert "reward per step" in run("examples/minimal_task.py")
     assert "step 0" in run("examples/countdown_grpo_qwen35.py", "--steps", "1", "--moe")
+    # two gloo ranks as one tensor-parallel group, replicated and sequence-sharded residual stream: the same
+    # adapters come out of both layouts (the collectives sum in rank order either way)
+    digests = []
+    for port, extra in ((29821, ()), (29822, ("--sequence-parallel",))):
+        out = run("-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
+                  "--master-port", str(port), "examples/gemma_tensor_parallel.py", "--steps", "2", "--out",
+                  str(tmp_path / f"tp{port}"), *extra)
+        line = [l for l in out.splitlines() if "all ranks hold identical adapters" in l]
+        assert line and "step 1" in out, out[-1500:]
+        digests.append(line[0].split()[-1])
+    assert digests[0] == digests[1]
 
 
 def _discovery_setup(tmp_path, verify, **task_kw):
