@@ -141,6 +141,23 @@ class DenseLayer(nn.Module):
         mid = self.gate_up.forward_merged_glu(x, self.act) if merged else ops.swiglu(self.gate_up(x), self.act)
         return self.down.forward_reduce(mid, comm, merged, residual=h)
 
+    def forward_sp(self, hs, B, S, positions, cos, sin, comm: Comm, merged: bool = False):
+        """Sequence-sharded form: ``hs`` holds this rank's block of the flattened ``[B * S, H]`` token rows.  The
+        column-parallel projections gather the normalised rows (their backward reduce-scatters inside its GEMM),
+        the row-parallel ones keep this rank's rows of the tensor-parallel sum; norms and residual adds run on the
+        shard."""
+        p = self.qkv.forward_gathered(ops.rmsnorm(hs, self.input_norm, self.eps), comm, merged).view(B, S, -1)
+        q, k, v = p.split([self.hq * self.D, self.hkv * self.D, self.hkv * self.D], dim=-1)
+        q = q.reshape(B, S, self.hq, self.D)
+        k = k.reshape(B, S, self.hkv, self.D)
+        v = v.reshape(B, S, self.hkv, self.D)
+        q, k = ops.qk_norm_rope(q, k, self.q_norm, self.k_norm, self.eps, cos, sin, positions)
+        a = ops.attention(q, k, v, scale=self.scale, causal=True, softmax_fp32=True)
+        o = self.o.forward_reduce_scatter(a.reshape(B * S, self.hq * self.D), comm, merged)
+        x, hs = ops.add_rmsnorm(o, hs, self.post_norm, self.eps)
+        mid = ops.swiglu(self.gate_up.forward_gathered(x, comm, merged), self.act)
+        return hs + self.down.forward_reduce_scatter(mid, comm, merged)
+
     # one-token forward against the cache (rollout; merged weights)
     def decode_fused(self, h, ss, kv_len, cos, sin, k_cache, v_cache, kv_next, pos, table=None, prefix=None):
         """One decode step of the layer in six kernels.  The two RMSNorms are folded around the
@@ -262,7 +279,7 @@ class DenseGradModel(nn.Module):
     def __init__(self, spec: DenseSpec, lora: Optional[LoraSpec] = None, *, dtype=torch.float32,
                  device=None, tp: Optional[TensorParallelPlan] = None, keep_transpose: Optional[bool] = None,
                  quant: BaseQuantization = BaseQuantization.NONE, remat: bool = False,
-                 full_ft: bool = False):
+                 full_ft: bool = False, sequence_parallel: bool = False):
         super().__init__()
         spec.validate()
         if tp is not None and (tp.num_heads != spec.num_attention_heads or tp.num_kv_heads != spec.num_key_value_heads):
@@ -270,6 +287,8 @@ class DenseGradModel(nn.Module):
         self.spec = spec
         self.lora = lora
         self.tp = tp
+        # tensor parallelism with the residual stream sharded over the token rows (training and scoring passes)
+        self.sequence_parallel = bool(sequence_parallel)
         self.remat = remat
         self.full_ft = full_ft
         dev = torch.device(device) if device is not None else torch.device("cpu")
@@ -376,6 +395,16 @@ class DenseGradModel(nn.Module):
             raise ValueError(f"sequence length {S} exceeds max_position_embeddings {self.cos.shape[0]}")
         positions = torch.arange(S, device=ids.device)
         h = ops.embedding(ids, self.embed)
+        if self.sequence_parallel and comm.world_size > 1 and kv_out is None and (B * S) % comm.world_size == 0:
+            from ..parallel import sp
+            hs = sp.shard_rows(h.reshape(B * S, -1), comm)
+            for layer in self.layers:
+                fn = (lambda x, layer=layer: layer.forward_sp(x, B, S, positions, self.cos, self.sin, comm, merged))
+                if self.remat and torch.is_grad_enabled() and not detached:
+                    hs = remat_segment(fn, hs, layer.adapter_params() if not self.full_ft else list(layer.parameters()), None)
+                else:
+                    hs = fn(hs)
+            return sp.gather_rows_replicated(hs, comm).view(B, S, -1)
         cot = (lambda g: g)  # boundary cotangents are already reduced by copy_to_tp's backward
         for i, layer in enumerate(self.layers):
             kv = None if kv_out is None else kv_out[i]

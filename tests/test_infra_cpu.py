@@ -1128,9 +1128,9 @@ def test_preflight_stage_checks_samples_and_tokenization():
 
 
 def test_sequence_parallel_key_reaches_the_model_or_is_refused(tmp_path):
-    """``tensor_parallel.sequence_parallel`` is part of the strict schema; a family whose layers have no
-    sequence-sharded form refuses it on every rank; the Gemma family trains with it over two thread ranks and ends
-    with the same metrics as the replicated layout (same sums in the same rank order)."""
+    """``tensor_parallel.sequence_parallel`` is part of the strict schema; a policy without a sequence-sharded form
+    refuses it on every rank; the Gemma and dense families train with it over two thread ranks and end with the
+    same metrics as the replicated layout (same sums in the same rank order)."""
     from ferrl_b200.comm import run_ranks
     from ferrl_b200.orchestration import OrchestrationError, run_cli_train_setup
     from ferrl_b200.tokenizer import SyntheticTokenizer
@@ -1151,17 +1151,22 @@ def test_sequence_parallel_key_reaches_the_model_or_is_refused(tmp_path):
                              "tensor_parallel": {"sequence_paralel": True}})
 
     def refused(comm):
+        # a policy object without the sequence-sharded form (here: the attribute removed from a loaded model)
+        from ferrl_b200.models.loader import LoaderOpts, load_auto_policy
+        model, ident = load_auto_policy(os.path.join(FIX, "tiny_qwen3"), LoaderOpts(tp=(comm.rank, comm.world_size)))
+        del model.sequence_parallel
         with pytest.raises(OrchestrationError, match="sequence_parallel is not supported"):
-            run_cli_train_setup(cfg(tmp_path / "dense", comm.rank, "tiny_qwen3", True), comm, allow_dirty=True,
-                                tokenizer=SyntheticTokenizer(32, 4, 8))
+            run_cli_train_setup(cfg(tmp_path / "other", comm.rank, "tiny_qwen3", True), comm, allow_dirty=True,
+                                tokenizer=SyntheticTokenizer(32, 4, 8), model_and_identity=(model, ident))
         return True
     assert run_ranks(2, refused, timeout=120) == [True, True]
 
-    def train(comm, on):
-        out = run_cli_train_setup(cfg(tmp_path / ("sp" if on else "tp"), comm.rank, "gemma", on), comm, allow_dirty=True,
-                                  tokenizer=SyntheticTokenizer(16, 4, 8))      # the checkpoint's vocabulary has 16 entries
+    def train(comm, on, model):
+        out = run_cli_train_setup(cfg(tmp_path / (model + ("_sp" if on else "_tp")), comm.rank, model, on), comm, allow_dirty=True,
+                                  tokenizer=SyntheticTokenizer(16, 4, 8))      # the smaller vocabulary has 16 entries
         rows = [json.loads(l) for l in open(os.path.join(out.run_dir, "metrics.jsonl"))] if comm.rank == 0 else []
         return out.steps_run, [(round(r["loss"], 5), round(r["grad_norm"], 4)) for r in rows]
-    sharded = run_ranks(2, lambda c: train(c, True), timeout=180)
-    plain = run_ranks(2, lambda c: train(c, False), timeout=180)
-    assert sharded[0][0] == 2 and sharded[0][1] == plain[0][1]
+    for model in ("gemma", "tiny_qwen3"):
+        sharded = run_ranks(2, lambda c: train(c, True, model), timeout=180)
+        plain = run_ranks(2, lambda c: train(c, False, model), timeout=180)
+        assert sharded[0][0] == 2 and sharded[0][1] == plain[0][1]

@@ -129,9 +129,11 @@ def test_lora_zero_b_is_identity_and_merge_matches_side_path():
         assert (m(ids) - base).abs().max().item() < 1e-6
 
 
-def test_tensor_parallel_matches_single_rank():
+@pytest.mark.parametrize("sequence_parallel,remat", [(False, False), (True, False), (True, True)])
+def test_tensor_parallel_matches_single_rank(sequence_parallel, remat):
     """Two thread-ranks with column/row sharded weights reproduce the unsharded logits and the
-    replicated-adapter gradients sum to the unsharded gradients."""
+    replicated-adapter gradients sum to the unsharded gradients, with the residual stream replicated or
+    sharded over the token rows."""
     from ferrl_b200.comm import run_ranks
     single = _load("tiny_qwen3")
     ids = torch.tensor(_golden("tiny_qwen3")["full_b2"]["input_ids"])
@@ -144,7 +146,8 @@ def test_tensor_parallel_matches_single_rank():
     ref_grads = [p.grad.clone() for p in single.trainable_params()]
 
     def body(comm):
-        m = _load("tiny_qwen3", tp=(comm.rank, comm.world_size))
+        m = _load("tiny_qwen3", tp=(comm.rank, comm.world_size), remat=remat)
+        m.sequence_parallel = sequence_parallel
         with torch.no_grad():
             for a, b in zip(m.trainable_params(), single.trainable_params()):
                 a.copy_(b)
