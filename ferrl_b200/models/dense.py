@@ -27,7 +27,7 @@ from __future__ import annotations
 
 import math
 import os
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 import torch
@@ -35,7 +35,7 @@ from torch import nn
 
 from .. import ops
 from ..comm import Comm, SoloComm
-from ..parallel.tp import TensorParallelPlan, copy_to_tp, reduce_from_tp
+from ..parallel.tp import TensorParallelPlan, copy_to_tp
 from ..remat import remat_segment
 from .lora import BaseQuantization, DenseLoraTargets, FusedLoraLinear, LoraSpec, Shard
 

@@ -32,7 +32,7 @@ from torch import nn
 
 from .. import ops
 from ..comm import Comm, SoloComm
-from ..parallel.tp import TensorParallelPlan, copy_to_tp, reduce_from_tp
+from ..parallel.tp import TensorParallelPlan, copy_to_tp
 from ..remat import remat_segment
 from .dense import ops_cache_write
 from .lora import BaseQuantization, DenseLoraTargets, FusedLoraLinear, LoraSpec, Shard

@@ -10,7 +10,6 @@ silently.
 from __future__ import annotations
 
 import os
-from typing import Optional
 
 import torch
 import torch.nn.functional as F
