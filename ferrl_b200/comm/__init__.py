@@ -58,6 +58,9 @@ class Comm:
 
     rank: int = 0
     world_size: int = 1
+    # seconds this rank's host thread has spent blocked inside collectives (waiting for slower peers plus the
+    # exchange itself); the trainer reports the per-step difference as the ``comm_wait`` phase
+    wait_s: float = 0.0
 
     def validate_all_reduce_sum(self, tensors: Sequence[torch.Tensor]) -> None:
         for t in tensors:
@@ -187,6 +190,13 @@ class ThreadComm(Comm):
             self._w.cv.notify_all()
 
     def _exchange(self, payload, reduce_fn):
+        t0 = time.perf_counter()
+        try:
+            return self._exchange_inner(payload, reduce_fn)
+        finally:
+            self.wait_s += time.perf_counter() - t0
+
+    def _exchange_inner(self, payload, reduce_fn):
         w = self._w
         deadline = time.monotonic() + w.timeout
         with w.cv:

@@ -15,6 +15,7 @@ is the *baseline* data plane; the product data plane is ``SymmComm``.
 from __future__ import annotations
 
 import datetime
+import time
 import os
 from dataclasses import dataclass
 from typing import Mapping, Optional
@@ -110,6 +111,7 @@ class TorchDistComm(Comm):
 
     def _wrap(self, fn):
         self._guard()
+        t0 = time.perf_counter()
         try:
             self.collective_calls += 1
             return fn()
@@ -121,6 +123,10 @@ class TorchDistComm(Comm):
             if "imeout" in msg or "timed out" in msg:
                 raise CommTimeout(msg) from e
             raise CommError(msg) from e
+        finally:
+            # host-blocking time only: a collective on device tensors returns when it is enqueued, the control-plane
+            # exchanges (scalars, byte blobs, barriers) return when every rank has arrived
+            self.wait_s += time.perf_counter() - t0
 
     def all_reduce_sum(self, tensors):
         self.validate_all_reduce_sum(tensors)
@@ -152,8 +158,11 @@ class TorchDistComm(Comm):
         if self.world_size == 1:
             return float(value)
         t = torch.tensor([float(value)], dtype=torch.float64, device=self.device)
-        self._wrap(lambda: self._dist.all_reduce(t, group=self._group))
-        return float(t.item())
+
+        def go():
+            self._dist.all_reduce(t, group=self._group)
+            return float(t.item())          # the read-back is where the host waits for the slowest rank
+        return self._wrap(go)
 
     def all_gather_bytes(self, blob):
         if self.world_size == 1:

@@ -774,6 +774,7 @@ class Trainer:
         snap = self._snapshot() if self.comm.world_size > 1 or self.fault_hook is not None else None
         cand_mark = self.candidate_writer.mark() if self.candidate_writer is not None else None
         t0 = time.perf_counter()
+        wait0 = float(getattr(self.comm, "wait_s", 0.0))
         try:
             m, local_tokens = self.run_window(step, lr, beta)
         except CommError:
@@ -788,6 +789,10 @@ class Trainer:
         m.step_secs = time.perf_counter() - t0
         m.tokens_per_sec = local_tokens / m.step_secs if m.step_secs > 0 else 0.0
         m.phase_ms = {k: round(v, 3) for k, v in phases.items()}
+        if self.comm.world_size > 1:
+            # host time blocked inside collectives during this step: the wait for the slowest rank at each
+            # agreement point plus the exchanges themselves (it overlaps the device phases above)
+            m.phase_ms["comm_wait"] = round(1e3 * (float(getattr(self.comm, "wait_s", 0.0)) - wait0), 3)
         if self._probe.enabled:
             m.cuda_mem_start_used_bytes, m.cuda_mem_peak_used_bytes = self._probe.start, self._probe.peak
             m.cuda_mem_end_used_bytes, m.cuda_mem_total_bytes = self._probe.end, self._probe.total

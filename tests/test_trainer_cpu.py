@@ -584,3 +584,28 @@ def test_failed_window_leaves_no_candidate_rows(tmp_path):
     tr.fault_hook = None
     tr.step(1)
     assert [r.step for r in read_candidates(path)] == [0, 0, 1, 1]
+
+
+def test_host_time_blocked_in_collectives_is_reported_per_step():
+    """A rank that reaches an agreement point early waits there for the slowest rank: the communicator accumulates
+    that time and the trainer reports the per-step difference as the ``comm_wait`` phase."""
+    import time as _time
+    from ferrl_b200.comm import run_ranks
+
+    def body(comm):
+        if comm.rank == 1:
+            _time.sleep(0.25)
+        comm.barrier()
+        first = comm.wait_s
+        comm.all_reduce_scalar_sum(1.0)
+        return first, comm.wait_s
+    (w0, w0b), (w1, w1b) = run_ranks(2, body)
+    assert w0 >= 0.2 and w1 < 0.2 and w0b >= w0 and w1b >= w1
+
+    def train(comm):
+        tr = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1), comm=comm)
+        return tr.step(0).phase_ms.get("comm_wait")
+    waits = run_ranks(2, train, timeout=120)
+    assert all(w is not None and w >= 0.0 for w in waits)
+    solo = Trainer(make_policy(), ListTok(), FnReward(echo_reward), samples(), cfg(steps=1))
+    assert "comm_wait" not in solo.step(0).phase_ms          # a single rank has nothing to wait for
