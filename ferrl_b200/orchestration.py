@@ -132,13 +132,14 @@ def build_task(cfg: RunConfig):
         else:
             probs = generate_dataset(d.seed, d.train_n + d.eval_n, CountdownConfig())
             samples = [Sample(build_prompt(p), p) for p in probs]
-        train, ev = train_eval_split_by_key(samples, d.eval_n, d.seed, lambda s: (s.target.numbers, s.target.target))
+        train, ev = train_eval_split_by_key(samples, d.eval_n, d.seed, lambda s: s.target.split_key())
         return train[:d.train_n] if d.train_n else train, ev, CountdownReward()
     if cfg.task == "math":
         if not d.path:
             raise OrchestrationError("the math task needs data.path (a JSONL of {prompt, target:{answer}})")
+        from .rewards.math import math_split_key
         samples = read_jsonl(d.path, MathProblem.from_json)
-        train, ev = train_eval_split(samples, d.eval_n, d.seed)
+        train, ev = train_eval_split_by_key(samples, d.eval_n, d.seed, math_split_key)
         return train[:d.train_n] if d.train_n else train, ev, MathReward()
     if cfg.task == "trimul":
         from .rewards.trimul import TrimulCase, TrimulReward, TrimulRewardProfile, default_eval_dir
@@ -206,7 +207,8 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
         check_device(idx)
         guard_first_kernel()
         device = f"cuda:{idx}"
-    train_samples, eval_samples, reward_fn = build_task(cfg)
+    # a rank that cannot build its task data stops all of them together (orchestration.rs:1202-1242)
+    train_samples, eval_samples, reward_fn = comm.coordinate(lambda: build_task(cfg), f"{cfg.task} task setup")
     # ---- policy
     pc = cfg.policy
     lora = LoraSpec(pc.lora_rank, pc.lora_alpha, DenseLoraTargets.parse(pc.lora_targets))

@@ -40,6 +40,20 @@ class CountdownProblem:
     def to_json(self):
         return {"numbers": list(self.numbers), "target": self.target}
 
+    def split_key(self):
+        """Identity of the problem for a train/eval split: the numbers as a multiset plus the target, so that a
+        permutation of a training problem cannot land on the held-out side (crates/ferrl/src/countdown.rs:74-82)."""
+        return tuple(sorted(self.numbers)), self.target
+
+    def check(self, expression: str) -> bool:
+        """Whether ``expression`` parses, uses every number exactly once and nothing else, and evaluates exactly
+        to the target (crates/ferrl/src/countdown.rs:84-95)."""
+        res = eval_expression(expression)
+        if res is None:
+            return False
+        value, leaves = res
+        return is_legal(leaves, self.numbers) and value.denominator == 1 and value.numerator == self.target
+
 
 @dataclass(frozen=True)
 class CountdownConfig:
@@ -201,6 +215,11 @@ class _Parser:
         return None
 
 
+def is_legal(leaves, numbers) -> bool:
+    """The expression's leaves are the problem's numbers as a multiset."""
+    return sorted(leaves) == sorted(numbers)
+
+
 def eval_expression(s: str):
     """``(value, leaves)`` or ``None`` when the text is not a well-formed expression."""
     toks = _tokenize(s)
@@ -228,7 +247,7 @@ class CountdownReward:
         if res is None:
             return reward
         value, leaves = res
-        if sorted(leaves) == sorted(problem.numbers):
+        if is_legal(leaves, problem.numbers):
             reward += self.legal_reward
             if value.denominator == 1 and value.numerator == problem.target:
                 reward += self.correct_reward

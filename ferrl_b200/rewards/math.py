@@ -21,12 +21,19 @@ class MathProblem:
         return {"answer": self.answer}
 
 
+def math_split_key(sample):
+    """Identity of a sample for a train/eval split: prompt and answer with ASCII whitespace and thousands separators
+    removed, so that ``1, 000 + 234`` and ``1000 + 234`` cannot sit on both sides (crates/ferrl/src/math.rs:55-62)."""
+    return normalize(sample.prompt), normalize(sample.target.answer)
+
+
 def math_prompt(question: str) -> str:
     return f"{question}\nPut your final answer inside <answer></answer> tags.\n"
 
 
 def normalize(s: str) -> str:
-    return "".join(c for c in s if c not in " \t\n\r\x0b\x0c,")
+    # space, tab, line feed, form feed, carriage return (Rust's ``is_ascii_whitespace``: no vertical tab) and ','
+    return "".join(c for c in s if c not in " \t\n\x0c\r,")
 
 
 @dataclass

@@ -1170,3 +1170,55 @@ def test_sequence_parallel_key_reaches_the_model_or_is_refused(tmp_path):
         sharded = run_ranks(2, lambda c: train(c, True, model), timeout=180)
         plain = run_ranks(2, lambda c: train(c, False, model), timeout=180)
         assert sharded[0][0] == 2 and sharded[0][1] == plain[0][1]
+
+
+def test_countdown_and_math_tasks_follow_the_reference_unit_vectors():
+    """The reference's own unit cases, read as golden vectors (crates/ferrl/src/countdown.rs:662-955,
+    crates/ferrl/src/math.rs:149-231): expression grammar, first-answer extraction, legality, reward tiers and
+    weights, split keys that close permutation / formatting leakage between train and held-out samples."""
+    from ferrl_b200.rewards import CountdownProblem, CountdownReward, MathProblem, MathReward, Sample, build_prompt
+    from ferrl_b200.rewards.countdown import eval_expression, extract_answer, is_legal
+    from ferrl_b200.rewards.math import math_prompt, math_split_key
+
+    def value(text):
+        return eval_expression(text)[0]
+    assert value("2 + 3 * 4") == 14 and value("(2 + 3) * 4") == 20 and value("2 * (3 + 4)") == 14 and value("10 - 2 - 3") == 5
+    assert value("6 / 4 * 2") == 3 and value("1 / 3") != 0 and value("8 / 2 / 2") == 2 and eval_expression("5 / 0") is None
+    assert list(eval_expression("2 * (3 + 4)")[1]) == [2, 3, 4]
+    for bad in ("", "   ", "2 +", "2 3", "(2 + 3", "2 + 3)", "2 ^ 3", "2 + a", "99999999999"):
+        assert eval_expression(bad) is None, bad
+    assert extract_answer("noise <answer> 1 + 2 </answer>").strip() == "1 + 2"
+    assert extract_answer("<answer>first</answer> then <answer>second</answer>") == "first"
+    assert extract_answer("no tags here") is None and extract_answer("<answer>unclosed forever") is None
+    assert is_legal([2, 3, 4], [4, 2, 3]) and is_legal([5, 5, 2], [5, 2, 5])
+    assert not is_legal([2, 3], [2, 3, 4]) and not is_legal([2, 3, 3], [2, 3, 4])
+    p = CountdownProblem((2, 3, 4), 14)
+    assert p.check("2 * (3 + 4)")
+    for wrong in ("2 + 3 + 4", "2 * 7", "2 * (3 + 4", "2 * 3 * 4 * 1"):
+        assert not p.check(wrong), wrong
+    assert "Numbers: 6, 3, 7" in build_prompt(CountdownProblem((6, 3, 7), 16)) and "Target: 16" in build_prompt(CountdownProblem((6, 3, 7), 16))
+    r, s = CountdownReward(), Sample(build_prompt(p), p)
+    parroted = "<answer>2 * (3 + 4)</answer>\n\nNumbers: 1, 1, 1\nTarget: 3\n<answer>1 + 1 + 1</answer>"
+    assert abs(r.reward(s, parroted) - 1.0) < 1e-6
+    assert r.reward(s, "I think it is 2 * 7") == 0.0
+    assert r.reward(s, "<answer>2 * </answer>") == 0.1 and r.reward(s, "<answer>2 * 7</answer>") == 0.1
+    assert abs(r.reward(s, "<answer>2 + 3 + 4</answer>") - 0.2) < 1e-6
+    assert abs(r.reward(s, "reason... <answer>2 * (3 + 4)</answer>") - 1.0) < 1e-6
+    s5 = Sample("x", CountdownProblem((5, 5, 2), 12))
+    got = r.reward_group(s5, ["<answer>5 + 5 + 2</answer>", "<answer>5 + 5</answer>", "no answer"])
+    assert abs(got[0] - 1.0) < 1e-6 and abs(got[1] - 0.1) < 1e-6 and got[2] == 0.0
+    w = CountdownReward(format_reward=0.05, legal_reward=0.25, correct_reward=0.7)
+    assert abs(w.reward(s, "<answer>2 + 3 + 4</answer>") - 0.30) < 1e-6 and abs(w.reward(s, "<answer>2 * (3 + 4)</answer>") - 1.0) < 1e-6
+    assert CountdownProblem((2, 3, 4), 14).split_key() == CountdownProblem((4, 2, 3), 14).split_key()
+    m = MathReward()
+    q = Sample("2 + 3 = ?", MathProblem("5"))
+    assert m.reward(q, "the sum is <answer>5</answer>") == 1.0 and m.reward(q, "<answer>6</answer>") == 0.0
+    assert m.score("5", "the answer is <answer>5") == 0.0 and m.score("5", "the answer is 5") == 0.0
+    assert m.score("1234", "<answer>1, 234</answer>") == 1.0 and m.score("1234", "<answer> 1234 </answer>") == 1.0
+    assert m.score("5", "<answer>4</answer> ... <answer>5</answer>") == 0.0
+    assert MathReward(correct_reward=2.5).score("42", "<answer>42</answer>") == 2.5
+    assert "What is 6 * 7?" in math_prompt("What is 6 * 7?") and "<answer></answer>" in math_prompt("What is 6 * 7?")
+    assert json.loads(Sample("q", MathProblem("99")).key()) == {"prompt": "q", "target": {"answer": "99"}}
+    assert math_split_key(Sample("What is 1, 000 + 234?", MathProblem("1,234"))) == \
+        math_split_key(Sample("What is 1000 + 234?", MathProblem(" 1234 ")))
+    assert m.score("12", "<answer>1\x0b2</answer>") == 0.0          # a vertical tab is not ASCII whitespace there
