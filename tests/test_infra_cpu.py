@@ -1222,3 +1222,51 @@ def test_countdown_and_math_tasks_follow_the_reference_unit_vectors():
     assert math_split_key(Sample("What is 1, 000 + 234?", MathProblem("1,234"))) == \
         math_split_key(Sample("What is 1000 + 234?", MathProblem(" 1234 ")))
     assert m.score("12", "<answer>1\x0b2</answer>") == 0.0          # a vertical tab is not ASCII whitespace there
+
+
+def test_checkpoint_eos_resolution_follows_the_reference_unit_vectors(tmp_path):
+    """crates/ferrl/src/hf.rs:516-660 read as golden cases: strict default needs exactly one declared id, an explicit
+    id may fill in or override a scalar but must be a member of a declared list, the id must lie inside the model
+    vocabulary and be known to the tokenizer, and ``None`` is not the same resolution as id 0."""
+    from ferrl_b200.comm import run_ranks
+    from ferrl_b200.hf import HfError, resolve_eos, validate_resolved_eos_consensus
+
+    class Tok:
+        def __init__(self, ids):
+            self.ids = set(ids)
+
+        def contains_id(self, i):
+            return i in self.ids
+
+    def ckpt(name, cfg):
+        d = tmp_path / name
+        d.mkdir()
+        (d / "config.json").write_text(json.dumps(cfg))
+        return str(d)
+    tok = Tok(range(4))
+    missing = ckpt("missing", {"vocab_size": 4})
+    with pytest.raises(HfError, match="declares no eos_token_id"):
+        resolve_eos(missing, "checkpoint", None, tok)
+    assert resolve_eos(missing, "disabled", None, tok) is None
+    assert resolve_eos(missing, "explicit", 3, tok) == 3
+    multi = ckpt("multi", {"vocab_size": 4, "eos_token_id": [2, 3]})
+    with pytest.raises(HfError, match="multiple EOS ids"):
+        resolve_eos(multi, "checkpoint", None, tok)
+    assert resolve_eos(multi, "explicit", 3, tok) == 3
+    with pytest.raises(HfError, match="not a member"):
+        resolve_eos(multi, "explicit", 1, tok)
+    assert resolve_eos(ckpt("scalar", {"vocab_size": 4, "eos_token_id": 2}), "explicit", 3, tok) == 3
+    with pytest.raises(HfError, match="EOS id 4 is not present in the loaded tokenizer vocabulary"):
+        resolve_eos(ckpt("membership", {"vocab_size": 5, "eos_token_id": 4}), "checkpoint", None, tok)
+    with pytest.raises(HfError, match="outside model vocab_size 4"):
+        resolve_eos(ckpt("bound", {"vocab_size": 4, "eos_token_id": 4}), "checkpoint", None, Tok(range(5)))
+    nested = ckpt("nested", {"eos_token_id": 1, "text_config": {"eos_token_id": 2, "vocab_size": 4}})
+    assert resolve_eos(nested, "checkpoint", None, tok) == 2              # the nested text config wins
+
+    def body(comm):
+        try:
+            validate_resolved_eos_consensus(0 if comm.rank == 0 else None, comm)
+        except HfError:
+            return "refused"
+        return "accepted"
+    assert run_ranks(2, body) == ["refused", "refused"]
