@@ -41,14 +41,33 @@ class BaseQuantization(str, enum.Enum):
     Q8_0 = "q8_0"
 
 
-def validated_lora_scale(rank: int, alpha: float) -> float:
+# closed ranges of finite, positive values of the 16-bit compute dtypes (smallest subnormal .. largest finite)
+_SCALE_RANGE = {torch.float16: (5.960464477539063e-08, 65504.0),
+                torch.bfloat16: (9.183549615799121e-41, 3.3895313892515355e38)}
+_DTYPE_NAME = {torch.float64: "F64", torch.float32: "F32", torch.float16: "F16", torch.bfloat16: "BF16"}
+
+
+def validated_lora_scale(rank: int, alpha: float, compute_dtype: Optional[torch.dtype] = None) -> float:
+    """``alpha / rank``, which must stay finite and nonzero when narrowed to the dtype the base weight computes in
+    (``None``: float64).  Reference: crates/ferrl/src/lora.rs:1072-1100."""
     if rank <= 0:
-        raise ValueError("LoRA rank must be > 0")
+        raise ValueError("lora rank must be > 0")
     if not math.isfinite(alpha) or alpha <= 0:
-        raise ValueError("LoRA alpha must be finite and > 0")
+        raise ValueError("lora alpha must be finite and > 0")
     s = alpha / rank
-    if not math.isfinite(s) or s <= 0:
-        raise ValueError("LoRA scale alpha/rank must be finite and > 0")
+    dt = compute_dtype or torch.float64
+    if dt == torch.float64:
+        ok = math.isfinite(s) and s > 0
+    elif dt == torch.float32:
+        narrowed = float(torch.tensor(s, dtype=torch.float64).to(torch.float32))
+        ok = math.isfinite(narrowed) and narrowed > 0
+    elif dt in _SCALE_RANGE:
+        ok = _SCALE_RANGE[dt][0] <= s <= _SCALE_RANGE[dt][1]
+    else:
+        ok = False
+    if not ok:
+        raise ValueError(f"lora scale alpha/rank = {s} must be finite and nonzero in compute dtype "
+                         f"{_DTYPE_NAME.get(dt, str(dt))}")
     return s
 
 
@@ -174,7 +193,8 @@ class FusedLoraLinear(nn.Module):
         self.register_buffer("weight_merged", None, persistent=False)
         self.weight_decode = None               # see enable_decode_fold()
         self._q = None
-        self.scale = lora.scale if lora is not None else 0.0
+        # the scale multiplies values of the base weight's dtype: it must survive the narrowing
+        self.scale = validated_lora_scale(lora.rank, lora.alpha, dtype) if lora is not None else 0.0
         self.rank = lora.rank if lora is not None else 0
         self.lora_A = nn.ParameterList()
         self.lora_B = nn.ParameterList()

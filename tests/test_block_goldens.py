@@ -112,3 +112,34 @@ def test_sparse_moe_block_with_gated_shared_expert(name):
     out = M.sparse_moe_block(T(c, "x", b, t, h), T(c, "router_weight", e, h), T(c, "gate_up_proj", e, 2 * i, h),
                              T(c, "down_proj", e, h, i), k, shared=shared, shared_gate_w=T(c, "shared_expert_gate", 1, h))
     assert err(out, T(c, "out", b, t, h)) < 5e-6
+
+
+def test_lora_scale_must_survive_the_base_compute_dtype():
+    """crates/ferrl/src/lora.rs:1597-1632 as golden cases: alpha / rank is checked in the dtype the frozen base
+    computes in, with closed ranges for the 16-bit types."""
+    import sys
+
+    import pytest
+    import torch
+
+    from ferrl_b200.models.lora import FusedLoraLinear, LoraSpec, validated_lora_scale
+    for dtype in (torch.float32, torch.bfloat16):
+        assert validated_lora_scale(2, 8.0, dtype) == 4.0
+        for alpha in (sys.float_info.min, sys.float_info.max):
+            with pytest.raises(ValueError, match="lora scale"):
+                validated_lora_scale(2, alpha, dtype)
+    for scale in (5.960464477539063e-8, 1.0, 65504.0):
+        assert validated_lora_scale(1, scale, torch.float16) == scale
+    for scale in (5.960464477539063e-8 / 2.0, 65536.0):
+        with pytest.raises(ValueError, match="compute dtype F16"):
+            validated_lora_scale(1, scale, torch.float16)
+    with pytest.raises(ValueError, match="rank must be > 0"):
+        validated_lora_scale(0, 8.0)
+    for alpha in (0.0, -1.0, float("nan"), float("inf")):
+        with pytest.raises(ValueError, match="alpha must be finite and > 0"):
+            validated_lora_scale(2, alpha)
+    # a scale that float32 can hold but bfloat16 cannot: the constructor checks in the base's dtype
+    tiny = LoraSpec(1, 1e-42)
+    FusedLoraLinear(3, [4], ("p",), (True,), tiny, dtype=torch.float32)
+    with pytest.raises(ValueError, match="compute dtype BF16"):
+        FusedLoraLinear(3, [4], ("p",), (True,), tiny, dtype=torch.bfloat16)
