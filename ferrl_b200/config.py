@@ -159,11 +159,14 @@ class TrainerConfig:
             _require(math.isfinite(self.max_grad_norm) and self.max_grad_norm > 0,
                      "max_grad_norm must be finite and > 0 when set (use null to disable clipping)")
         if self.checkpoint_every is not None:
-            _require(self.checkpoint_every >= 1, "checkpoint_every must be >= 1 when set")
+            _require(self.checkpoint_every >= 1, "checkpoint_every must be >= 1 when set (0 would checkpoint every step)")
         _require(math.isfinite(self.tis_imp_ratio_cap) and self.tis_imp_ratio_cap >= 1.0
-                 and self.tis_imp_ratio_cap < 3.4e38, "tis_imp_ratio_cap must be finite and >= 1")
+                 and _finite_as_f32(self.tis_imp_ratio_cap),
+                 "tis_imp_ratio_cap must be finite, >= 1, and remain finite when narrowed to the f32 TIS weight dtype "
+                 "(a cap below 1 would down-weight exactly on-policy tokens)")
         _require(not (self.tis and self.importance_sampling_level == ImportanceSamplingLevel.SEQUENCE.value),
-                 "tis is a token-level correction and cannot combine with sequence-level importance sampling")
+                 "tis is a token-level correction and cannot combine with sequence-level importance sampling (GSPO) "
+                 "— pick one")
         if self.top_p is not None:
             _require(math.isfinite(self.top_p) and 0 < self.top_p <= 1.0, "top_p must be in (0, 1]")
         try:
@@ -215,6 +218,15 @@ class TrainerConfig:
 
     def digest(self) -> str:
         return canonical_digest(self.to_json(), b"ferrl-b200/trainer-config/v1")
+
+
+def _finite_as_f32(x: float) -> bool:
+    """Whether ``x`` rounds to a finite float32 (round-to-nearest, as a narrowing cast does)."""
+    import struct
+    try:
+        return math.isfinite(struct.unpack("<f", struct.pack("<f", x))[0])
+    except OverflowError:
+        return False
 
 
 def _strict(d: Any, allowed: set, what: str) -> None:
