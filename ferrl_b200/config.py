@@ -16,6 +16,7 @@ import dataclasses
 import hashlib
 import json
 import math
+import os
 from dataclasses import dataclass, field
 from typing import Any, Optional
 
@@ -383,8 +384,52 @@ class RunConfig:
                      "expert_parallel shards experts over data-parallel ranks: it needs distributed.enabled and no tensor_parallel")
             _require(self.expert_parallel.capacity_factor >= 1.0, "expert_parallel.capacity_factor must be >= 1")
         self.trainer.validate()
+        # the remaining rules follow the reference's launch validation (crates/ferrl/src/bin/ferrl.rs:1260-1380)
+        if (not self.distributed.enabled and self.trainer.reward_group_scope == RewardGroupScope.DISTRIBUTED_SAME_PROMPT
+                and self.trainer.group_size < 2):
+            raise ConfigError("distributed_same_prompt group_size = 1 requires a live data-parallel world of at least two ranks")
+        try:
+            import torch
+            from .models.lora import validated_lora_scale
+            validated_lora_scale(self.policy.lora_rank, self.policy.lora_alpha,
+                                 {"f32": torch.float32, "bf16": torch.bfloat16, "f16": torch.float16}[self.policy.base_dtype])
+        except ValueError as e:
+            raise ConfigError(f"invalid policy LoRA scale: {e}") from e
+        if self.task in ("countdown", "trimul"):
+            _require(self.data.train_n >= 1, f"task {self.task!r} requires data.train_n >= 1")
+        if self.task == "trimul":
+            self._validate_trimul()
         from .run_health import validate_run_health
         validate_run_health(self.run_health, self.trainer)
+
+    TRIMUL_CASE_SEED_MAX = (1 << 32) - 1
+
+    def _validate_trimul(self) -> None:
+        t = self.trimul
+        seed = t.get("secret_seed", 0)
+        _require(isinstance(seed, int) and not isinstance(seed, bool) and 0 <= seed <= self.TRIMUL_CASE_SEED_MAX,
+                 f"trimul.secret_seed must be between 0 and {self.TRIMUL_CASE_SEED_MAX}")
+        held = t.get("held_out_secret_seed")
+        if self.data.eval_n == 0:
+            _require(held is None, "trimul.held_out_secret_seed requires data.eval_n >= 1")
+        else:
+            _require(held is not None, "TriMul held-out eval requires trimul.held_out_secret_seed")
+            _require(isinstance(held, int) and not isinstance(held, bool) and 0 <= held <= self.TRIMUL_CASE_SEED_MAX
+                     and held != seed,
+                     "trimul.held_out_secret_seed must be in the u32 range and differ from trimul.secret_seed")
+        tier = t.get("verifier_isolation_tier", "same_uid_apptainer_v1")
+        if tier == "same_uid_apptainer_v1":
+            _require(t.get("verifier_executor_socket") is None,
+                     "trimul.verifier_executor_socket is valid only with \"dedicated_uid_service_v1\"; same-UID "
+                     "verification never falls back to or contacts the executor service")
+            bin_ = t.get("verifier_apptainer_bin")
+            _require(bin_ is None or os.path.isabs(str(bin_)), "trimul.verifier_apptainer_bin must be an absolute path")
+        elif tier == "dedicated_uid_service_v1":
+            _require(t.get("verifier_apptainer_bin") is None,
+                     "trimul.verifier_apptainer_bin is valid only with \"same_uid_apptainer_v1\"; the dedicated "
+                     "service owns its Apptainer executable")
+        else:
+            raise ConfigError(f"unknown trimul.verifier_isolation_tier {tier!r}")
 
     def to_json(self, *, for_consensus: bool = False) -> dict:
         t = self.trainer.to_json()

@@ -163,6 +163,10 @@ def build_task(cfg: RunConfig):
                               scratch_max_bytes=int(t.get("scratch_max_bytes", 2 << 30)),
                               parallelism=int(t.get("verifier_parallelism", 1)),
                               extract_mode=t.get("submission_extract_mode") or "final_fence")
+        if t.get("held_out_secret_seed") is not None:
+            # held-out evaluation runs on hidden inputs the policy was never scored on (ferrl.rs:1700-1712)
+            import copy
+            reward.held_out_reward = copy.copy(reward).with_secret_seed(int(t["held_out_secret_seed"]))
         samples = [Sample(prompt, {"trimul": i}) for i in range(max(d.train_n, 1))]
         return samples, samples[:max(d.eval_n, 0)], reward
     raise OrchestrationError(f"unknown task {cfg.task!r}")
@@ -291,7 +295,7 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     if eval_samples and stop is RunStop.COMPLETED and health.verdict != "fail":
         gen = GenConfig(cfg.trainer.group_size, cfg.trainer.max_new_tokens, cfg.trainer.temperature,
                         cfg.trainer.eos_token_id)
-        report = evaluate(policy, reward_fn, tokenizer, eval_samples, gen)
+        report = evaluate(policy, getattr(reward_fn, "held_out_reward", None) or reward_fn, tokenizer, eval_samples, gen)
         if comm.rank == 0:
             with open(run_dir.path(T.RunDir.EVAL_REPORT_FILE), "w") as f:
                 json.dump(report.to_json(), f, indent=2, sort_keys=True)

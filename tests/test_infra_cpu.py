@@ -1270,3 +1270,43 @@ def test_checkpoint_eos_resolution_follows_the_reference_unit_vectors(tmp_path):
             return "refused"
         return "accepted"
     assert run_ranks(2, body) == ["refused", "refused"]
+
+
+def test_run_config_launch_rules_follow_the_reference(tmp_path):
+    """crates/ferrl/src/bin/ferrl.rs:1260-1380: LoRA scale in the base dtype, tasks that need training samples, the
+    TriMul seeds and isolation-tier keys, and the held-out reward on its own hidden inputs."""
+    from ferrl_b200.config import ConfigError
+
+    def cfg(**over):
+        base = {"task": "countdown", "model_dir": "/m", "trainer": {"steps": 2}}
+        base.update(over)
+        return RunConfig.from_json(base)
+    with pytest.raises(ConfigError, match="invalid policy LoRA scale: lora scale .* compute dtype BF16"):
+        cfg(policy={"lora_rank": 1, "lora_alpha": 1e-42, "base_dtype": "bf16"})
+    cfg(policy={"lora_rank": 1, "lora_alpha": 1e-42, "base_dtype": "f32"})
+    with pytest.raises(ConfigError, match="requires data.train_n >= 1"):
+        cfg(data={"train_n": 0})
+    with pytest.raises(ConfigError, match="group_size = 1 requires a live data-parallel world"):
+        cfg(trainer={"steps": 2, "group_size": 1, "reward_group_scope": "distributed_same_prompt"})
+    tri = {"prompt_path": "p", "image": "i"}
+    for extra, msg in (({"secret_seed": 2 ** 32}, "secret_seed must be between 0 and 4294967295"),
+                       ({"held_out_secret_seed": 5}, "held_out_secret_seed requires data.eval_n >= 1"),
+                       ({"verifier_executor_socket": "/s"}, "valid only with \"dedicated_uid_service_v1\""),
+                       ({"verifier_apptainer_bin": "apptainer"}, "must be an absolute path"),
+                       ({"verifier_isolation_tier": "dedicated_uid_service_v1", "verifier_apptainer_bin": "/usr/bin/apptainer"},
+                        "valid only with \"same_uid_apptainer_v1\"")):
+        with pytest.raises(ConfigError, match=msg):
+            cfg(task="trimul", trimul=dict(tri, **extra), data={"train_n": 4, "eval_n": 0})
+    with pytest.raises(ConfigError, match="held-out eval requires trimul.held_out_secret_seed"):
+        cfg(task="trimul", trimul=tri, data={"train_n": 4, "eval_n": 2})
+    with pytest.raises(ConfigError, match="differ from trimul.secret_seed"):
+        cfg(task="trimul", trimul=dict(tri, secret_seed=7, held_out_secret_seed=7), data={"train_n": 4, "eval_n": 2})
+    prompt = tmp_path / "prompt.txt"
+    prompt.write_text("write a kernel")
+    from ferrl_b200.orchestration import build_task
+    good = cfg(task="trimul", data={"train_n": 4, "eval_n": 2},
+               trimul={"prompt_path": str(prompt), "image": "img.sif", "secret_seed": 7, "held_out_secret_seed": 1000})
+    train, held, reward = build_task(good)
+    assert len(train) == 4 and len(held) == 2
+    assert [c.seed for c in reward.cases] == [7] and [c.seed for c in reward.held_out_reward.cases] == [1000]
+    assert reward.held_out_reward is not reward and reward.held_out_reward.image == reward.image
