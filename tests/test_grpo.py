@@ -141,3 +141,35 @@ def test_masked_mean_rejects_bad_inputs():
     with pytest.raises(ValueError):
         grpo.masked_mean([[1.0]], [[-1.0]])
     assert grpo.zero_mask_rows([[0.0, 0.0], [1.0, 0.0]]) == 1
+
+
+def test_group_advantages_on_the_reference_extreme_vectors():
+    """crates/ferrl/src/grpo.rs:734-835 as golden cases: inexact identical rewards stay exactly degenerate, values at
+    the float32 limit neither overflow nor lose the group's shape, and the result does not depend on the order of
+    the rewards (compensated canonical sum)."""
+    import itertools
+    import struct
+
+    import pytest
+
+    from ferrl_b200.grpo import ScaleRewards, group_advantages, tis_weight
+    mag = struct.unpack("<f", struct.pack("<I", 0x7F7FFFFF))[0]          # f32::MAX
+    for scale in ScaleRewards:
+        assert group_advantages([0.1] * 3, scale) == [0.0] * 3
+        assert group_advantages([mag, mag], scale) == [0.0, 0.0]
+    for rewards in ([mag, -mag], [mag, -mag, -mag]):
+        adv = group_advantages(rewards, ScaleRewards.GROUP)
+        assert all(math.isfinite(a) for a in adv) and any(abs(a) > 0.5 for a in adv)
+    canonical = [mag, 1.0, -mag]
+    for scale in ScaleRewards:
+        want = group_advantages(canonical, scale)
+        for perm in itertools.permutations(canonical):
+            got = group_advantages(list(perm), scale)
+            assert all(a == want[canonical.index(r)] for r, a in zip(perm, got))
+    assert abs(group_advantages(canonical, ScaleRewards.NONE)[1] - 2.0 / 3.0) <= 1e-15
+    for bad, msg in (([], "empty reward group"), ([1.0, float("nan"), 3.0], "rewards must be finite"),
+                     ([float("nan")] * 2, "rewards must be finite"), ([1.0, float("inf"), 3.0], "rewards must be finite")):
+        with pytest.raises(ValueError, match=msg):
+            group_advantages(bad, ScaleRewards.GROUP)
+    assert abs(tis_weight(-1.5, -1.5, 2.0) - 1.0) < 1e-12 and abs(tis_weight(-1.0, -1.5, 2.0) - math.exp(0.5)) < 1e-12
+    assert abs(tis_weight(-0.5, -2.0, 2.0) - 2.0) < 1e-12 and abs(tis_weight(-2.0, -0.5, 2.0) - math.exp(-1.5)) < 1e-12
