@@ -27,7 +27,8 @@ import shutil
 from dataclasses import dataclass, field
 from typing import Optional, Sequence
 
-from ..sandbox import Bind, ProtectedOutput, ResourceLimits, RunSpec, Sandbox, SandboxOutcome, Verdict, make_scratch, sealed_memfd
+from ..sandbox import (Bind, ProtectedOutput, ResourceLimits, RunSpec, Sandbox, SandboxInfrastructureError, SandboxOutcome, Verdict,
+                       make_scratch, sealed_memfd)
 from . import RewardError, RewardOutcome
 
 FORMAT_EXTRACTED_REWARD = 0.02
@@ -233,6 +234,9 @@ class TrimulReward:
             out: SandboxOutcome = self.sandbox.run(self.run_spec(scratch, fds))
         except OSError as e:
             raise RewardError(f"TriMul eval could not be staged: {e}") from e
+        except SandboxInfrastructureError as e:
+            # the verifier never started: this says nothing about the candidate and must not score it
+            raise RewardError(f"TriMul verifier infrastructure failed: {e}") from e
         finally:
             for fd in fds.values():
                 os.close(fd)

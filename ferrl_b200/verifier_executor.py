@@ -27,6 +27,7 @@ from dataclasses import dataclass
 from typing import Optional
 
 from .sandbox import (ApptainerSandbox, Bind, NetworkPolicy, ProtectedOutput, ResourceLimits, RunSpec, Sandbox, SandboxError,
+                      SandboxInfrastructureError,
                       SandboxOutcome, Verdict)
 
 
@@ -133,8 +134,11 @@ class VerifierExecutorSandbox(Sandbox):
                 _send_msg(s, _spec_to_json(spec, names), fds)
                 body, _ = _recv_msg(s)
             except OSError as e:
-                return SandboxOutcome(Verdict.LAUNCH_FAILED, 126, b"", f"verifier executor: {e}".encode())
+                # the service could not be reached or answered: nothing was learned about the command
+                raise SandboxInfrastructureError(Verdict.LAUNCH_FAILED, 126, f"verifier executor: {e}".encode()) from e
         d = json.loads(body.decode())
+        if d.get("infrastructure"):
+            raise SandboxInfrastructureError(Verdict(d["verdict"]), int(d["exit_code"]), base64.b64decode(d["stderr"]))
         po = d.get("protected_output")
         return SandboxOutcome(Verdict(d["verdict"]), int(d["exit_code"]), base64.b64decode(d["stdout"]),
                               base64.b64decode(d["stderr"]), bool(d.get("truncated")),
@@ -169,10 +173,16 @@ def serve_verifier_executor(socket_path: str, inner: Sandbox, *, max_requests: O
                 continue
             with conn:
                 fds = []
+                infrastructure = False
                 try:
                     body, fds = _recv_msg(conn)
                     out = inner.run(_spec_from_json(body, fds))
+                except SandboxInfrastructureError as e:     # the wrapper failed before the command: tell the client so
+                    infrastructure = True
+                    out = SandboxOutcome(e.verdict if isinstance(e.verdict, Verdict) else Verdict.LAUNCH_FAILED,
+                                         e.exit_code, b"", e.stderr)
                 except Exception as e:  # noqa: BLE001 - reported to the client, service keeps running
+                    infrastructure = True
                     out = SandboxOutcome(Verdict.LAUNCH_FAILED, 126, b"", repr(e).encode())
                 finally:
                     for fd in fds:
@@ -183,7 +193,7 @@ def serve_verifier_executor(socket_path: str, inner: Sandbox, *, max_requests: O
                 _send_msg(conn, json.dumps({"verdict": out.verdict.value, "exit_code": out.exit_code,
                                             "stdout": base64.b64encode(out.stdout).decode(),
                                             "stderr": base64.b64encode(out.stderr).decode(),
-                                            "truncated": out.truncated,
+                                            "truncated": out.truncated, "infrastructure": infrastructure,
                                             "protected_output": None if out.protected_output is None
                                             else base64.b64encode(out.protected_output).decode()}).encode())
             served += 1
