@@ -146,6 +146,18 @@ class TrimulEval:
         return any(0 <= x < MIN_PLAUSIBLE_NS for x in self.benchmark_means_ns)
 
 
+def run_status_label(out: SandboxOutcome) -> str:
+    """How the sandboxed run ended, as it appears in reward diagnostics (``trimul:sandbox_<label>``; the labels of
+    crates/ferrl/src/trimul.rs:3293-3300)."""
+    if out.verdict is Verdict.TIMEOUT:
+        return "timed_out"
+    if out.verdict is Verdict.SIGNALED:
+        return f"signaled_{out.exit_code - 128 if out.exit_code > 128 else out.exit_code}"
+    if out.verdict is Verdict.EXITED:
+        return f"exited_{out.exit_code}"
+    return out.verdict.value          # scratch_exceeded, launch_failed
+
+
 def parse_eval_log(text: str, outcome_ok: bool = True, verdict: str = "exited") -> TrimulEval:
     """Parse the driver's ``key: value`` log. Sections: ``test-count``, ``test.<i>.status``,
     ``check: pass|fail``, ``test-exit``, ``benchmark-count``, ``benchmark.<i>.mean`` (ns),
@@ -245,7 +257,7 @@ class TrimulReward:
         # the grade is what arrived on the protected socket; standard output is only the fallback of
         # sandboxes that do not offer the channel (scripted doubles)
         log = out.protected_output if out.protected_output is not None else out.stdout
-        return parse_eval_log(log.decode(errors="replace"), ok, out.verdict.value)
+        return parse_eval_log(log.decode(errors="replace"), ok, run_status_label(out))
 
     # --------------------------------------------------------------- reward
     def speed_value(self, geomean_ns: Optional[float]) -> float:

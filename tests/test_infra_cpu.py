@@ -465,8 +465,17 @@ def test_trimul_reward_shaping_and_executor_socket(tmp_path):
     assert sb.calls[0].gpu and sb.calls[0].binds[0].read_only
     with pytest.raises(ValueError):
         TrimulRewardProfile(format_extracted=0.2).validate()
-    timeout_eval = parse_eval_log("", False, "timeout")
-    assert r.reward_from_extracted_eval(timeout_eval) == r.profile.format_extracted and r.diagnostic(timeout_eval) == "trimul:sandbox_timeout"
+    from ferrl_b200.rewards.trimul import run_status_label
+    from ferrl_b200.sandbox import SandboxOutcome, Verdict
+    labels = [run_status_label(SandboxOutcome(v, c, b"", b"")) for v, c in
+              ((Verdict.TIMEOUT, 124), (Verdict.SIGNALED, 137), (Verdict.EXITED, 3), (Verdict.SCRATCH_EXCEEDED, 125))]
+    assert labels == ["timed_out", "signaled_9", "exited_3", "scratch_exceeded"]          # trimul.rs:3293-3300
+    timeout_eval = parse_eval_log("", False, labels[0])
+    assert r.reward_from_extracted_eval(timeout_eval) == r.profile.format_extracted and r.diagnostic(timeout_eval) == "trimul:sandbox_timed_out"
+    # a parsed grade cannot survive a sandbox failure (trimul.rs:4457-4480)
+    forged = parse_eval_log("test-count: 1\ntest.0.status: pass\ncheck: pass\ntest-exit: 0\n--- benchmark ---\n"
+                            "benchmark-count: 1\nbenchmark.0.mean: 500000.0\nbenchmark-exit: 0\n", False, "timed_out")
+    assert r.reward_from_eval(forged) == 0.0 and r.diagnostic(forged) == "trimul:sandbox_timed_out"
     sock = str(tmp_path / "ve.sock")
     ready = threading.Event()
     t = threading.Thread(target=serve_verifier_executor, args=(sock, LocalSandbox()), kwargs=dict(max_requests=1, ready=ready))
