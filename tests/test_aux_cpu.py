@@ -160,13 +160,54 @@ def test_evaluate_compares_base_and_adapter_and_restores_state():
     rep = evaluate(pol, Nine(), Tok(), samples, GenConfig(group_size=2, max_new_tokens=3), batch_prompts=2)
     assert rep.base_reward_mean == 0.0 and rep.adapter_reward_mean == 1.0 and rep.improvement() == 1.0 and len(rep.per_prompt) == 5
     assert rep.to_json()["improvement"] == 1.0 and rep.n_prompts == 5 and rep.group_size == 2
-    assert pol.enabled is False and pol.state == 7                       # adapter switch and sampler rolled back
+    # the adapter switch is restored; a successful evaluation keeps the sampler's progression (eval.rs:
+    # successful_eval_keeps_generated_sampler_progression_and_restores_adapter)
+    assert pol.enabled is False and pol.state == 7 + 6
     assert [c[0] for c in pol.calls] == [False] * 3 + [True] * 3           # paired: same row bases for both passes
     assert [c[1] for c in pol.calls[:3]] == [c[1] for c in pol.calls[3:]]
     with pytest.raises(EvalError):
         evaluate(pol, Nine(), Tok(), [], GenConfig(group_size=2, max_new_tokens=3))
     with pytest.raises(EvalError):
         evaluate(pol, Nine(), Tok(), samples, GenConfig(group_size=0, max_new_tokens=3))
+    # contract errors of the reference's unit cases; a failed evaluation rolls the sampler back exactly
+    gen = GenConfig(group_size=2, max_new_tokens=3)
+
+    class Empty(Tok):
+        def encode(self, s):
+            return []
+
+    class Rewards:
+        def __init__(self, values):
+            self.values = values
+
+        def reward_group(self, sample, comps):
+            return list(self.values)
+    for tok, rew, msg in ((Empty(), Nine(), "prompt encoded to zero tokens"),
+                          (Tok(), Rewards([1.0]), "reward_group returned 1 rewards for 2 completions"),
+                          (Tok(), Rewards([1.0, float("nan")]), "non-finite reward"),
+                          (Tok(), Rewards([float("inf"), float("inf")]), "non-finite reward")):
+        pol.state, pol.enabled = 7, True
+        with pytest.raises(EvalError, match=msg):
+            evaluate(pol, rew, tok, samples, gen)
+        assert pol.state == 7 and pol.enabled is True
+
+    class Stuck(FakePolicy):
+        def set_adapter_enabled(self, on):
+            pass                                                            # full fine-tuning: nothing to switch off
+    with pytest.raises(EvalError, match="cannot disable its adapter"):
+        evaluate(Stuck(), Nine(), Tok(), samples, gen)
+
+    class Short(FakePolicy):
+        def generate_batch(self, prompts, gen, bases):
+            return [FakeRollout([[9] * 3]) for _ in prompts]                # one row for a group of two
+    with pytest.raises(EvalError, match="returned 1 completions for group_size 2"):
+        evaluate(Short(), Nine(), Tok(), samples, gen)
+    # means do not depend on the order of extreme finite rewards, and an improvement float32 cannot hold is refused
+    from ferrl_b200.eval import EvalReport, validated_mean
+    big = 3.4028234663852886e38
+    assert validated_mean([big, 1.0, -big]) == validated_mean([1.0, -big, big]) == validated_mean([-big, big, 1.0])
+    with pytest.raises(EvalError, match="outside finite f32"):
+        EvalReport(1, 1, -big, big).improvement()
 
 
 _EP_WORKER = r'''
