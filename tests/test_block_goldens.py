@@ -143,3 +143,23 @@ def test_lora_scale_must_survive_the_base_compute_dtype():
     FusedLoraLinear(3, [4], ("p",), (True,), tiny, dtype=torch.float32)
     with pytest.raises(ValueError, match="compute dtype BF16"):
         FusedLoraLinear(3, [4], ("p",), (True,), tiny, dtype=torch.bfloat16)
+
+
+def test_chunked_delta_rule_survives_cumulative_decay_underflow():
+    """crates/ferrl/src/gdn.rs:1062-1081: with log-decays near -2.3 per step the cumulative decay of a 64-token chunk
+    underflows float32 (exp(-150)); the chunked form must still equal the recurrence and stay finite, within a chunk
+    and with the state carried across chunks."""
+    import torch
+
+    from ferrl_b200.models import gdn as G
+    gen = torch.Generator().manual_seed(71)
+    for t in (64, 200):
+        q, k = torch.randn(1, t, 1, 3, generator=gen), torch.randn(1, t, 1, 3, generator=gen)
+        v = torch.randn(1, t, 1, 3, generator=gen)
+        beta = torch.sigmoid(torch.randn(1, t, 1, generator=gen))
+        g = -(2.2 + 0.3 * torch.rand(1, t, 1, generator=gen))
+        for l2 in (False, True):
+            o_r, s_r = G.gated_delta_rule_recurrent(q, k, v, g, beta, None, use_qk_l2norm=l2)
+            o_c, s_c = G.gated_delta_rule_chunked(q, k, v, g, beta, None, use_qk_l2norm=l2)
+            assert torch.isfinite(o_c).all() and torch.isfinite(s_c).all()
+            assert float((o_r - o_c).abs().max()) <= 2e-5 and float((s_r - s_c).abs().max()) <= 2e-5
