@@ -506,4 +506,4 @@ def load_gemma4(model_dir: str, opts):
     for l in model.layers:
         for pr in l.projections():
             pr.init_adapters(g)
-    return model, _identity(model_dir, cfg, src)
+    return model, _identity(model_dir, cfg, src, opts)

@@ -41,15 +41,38 @@ class LoaderOpts:
 
 @dataclass(frozen=True)
 class PolicyLoadIdentity:
+    """What a checkpoint is bound to: the checkpoint's bytes and the recipe the policy executes under (adapter rank
+    and alpha, base and adapter dtypes, base quantisation, activation checkpointing, full fine-tuning, the
+    tensor- and expert-parallel world sizes), but neither the rank inside such a group nor anything that only
+    positions a random stream (reference: ``checkpoint_policy_digest``, crates/ferrl/src/loader.rs:269-307)."""
     model_type: str
     config_sha256: str
     weights_sha256: str
+    recipe: str = ""
 
     def digest(self) -> str:
-        h = hashlib.sha256(b"ferrl-b200/policy-identity/v1\0")
-        for part in (self.model_type, self.config_sha256, self.weights_sha256):
+        h = hashlib.sha256(b"ferrl-b200/policy-identity/v2\0")
+        for part in (self.model_type, self.config_sha256, self.weights_sha256, self.recipe):
             h.update(part.encode() + b"\0")
         return h.hexdigest()
+
+
+def execution_recipe(opts: "LoaderOpts") -> str:
+    """Canonical JSON of the options that change what the loaded policy computes."""
+    import struct
+    lora = None if (opts.lora is None or opts.full_ft) else opts.lora
+    return json.dumps({
+        "lora_rank": lora.rank if lora else 0,
+        "lora_alpha_bits": struct.unpack("<Q", struct.pack("<d", float(lora.alpha)))[0] if lora else 0,
+        "lora_targets": lora.targets.canonical() if lora and getattr(lora, "targets", None) is not None else "",
+        "base_dtype": str(opts.dtype).replace("torch.", ""),
+        "adapter_dtype": "float32",
+        "base_quantization": BaseQuantization(opts.quantization).value,
+        "activation_checkpointing": bool(opts.remat),
+        "full_fine_tuning": bool(opts.full_ft),
+        "tensor_parallel_world_size": opts.tp[1] if opts.tp is not None else 1,
+        "expert_parallel_world_size": opts.ep[1] if opts.ep is not None else 1,
+    }, sort_keys=True, separators=(",", ":"))
 
 
 class _SafeOpenFile:
@@ -180,10 +203,11 @@ def read_config(model_dir: str) -> dict:
         return json.load(f)
 
 
-def _identity(model_dir: str, cfg: dict, src: TensorSource) -> PolicyLoadIdentity:
+def _identity(model_dir: str, cfg: dict, src: TensorSource, opts: Optional["LoaderOpts"] = None) -> PolicyLoadIdentity:
     with open(os.path.join(model_dir, "config.json"), "rb") as f:
         csha = hashlib.sha256(f.read()).hexdigest()
-    return PolicyLoadIdentity(str(cfg.get("model_type")), csha, src.files_sha256())
+    return PolicyLoadIdentity(str(cfg.get("model_type")), csha, src.files_sha256(),
+                              execution_recipe(opts) if opts is not None else "")
 
 
 def load_dense(model_dir: str, spec_fn: Callable[[dict], DenseSpec], opts: LoaderOpts):
@@ -203,7 +227,7 @@ def load_dense(model_dir: str, spec_fn: Callable[[dict], DenseSpec], opts: Loade
     for l in model.layers:
         for pr in l.projections():
             pr.init_adapters(g)
-    return model, _identity(model_dir, cfg, src)
+    return model, _identity(model_dir, cfg, src, opts)
 
 
 def load_auto_policy(model_dir: str, opts: Optional[LoaderOpts] = None):

@@ -345,3 +345,30 @@ def test_gemma_sliding_layers_retain_only_their_window_and_decode_matches_uncach
         for b in range(2):
             seqs[b].append(int(nxt[b]))
         logits = dec.decode(nxt)
+
+
+def test_policy_identity_binds_the_execution_recipe_but_no_rank_or_stream_position():
+    """crates/ferrl/src/loader.rs:1358-1450 as golden cases: every option that changes what the policy computes
+    changes the identity a checkpoint is bound to; the rank inside a tensor-parallel group and the adapter seed
+    (which only positions a random stream) do not; the same directory loads to the same identity twice."""
+    import dataclasses
+
+    from ferrl_b200.models.lora import BaseQuantization, LoraSpec
+    d = os.path.join(FIX, "tiny_qwen3")
+    base = LoaderOpts()
+    want = load_auto_policy(d, base)[1].digest()
+    assert load_auto_policy(d, LoaderOpts())[1].digest() == want
+    changed = {"LoRA rank": dataclasses.replace(base, lora=LoraSpec(base.lora.rank + 1, base.lora.alpha)),
+               "LoRA alpha": dataclasses.replace(base, lora=LoraSpec(base.lora.rank, base.lora.alpha + 1.0)),
+               "base dtype": dataclasses.replace(base, dtype=torch.bfloat16),
+               "activation checkpointing": dataclasses.replace(base, remat=True),
+               "tensor-parallel world": dataclasses.replace(base, tp=(0, 2))}
+    for label, opts in changed.items():
+        assert load_auto_policy(d, opts)[1].digest() != want, label
+    # (the tiny fixture's widths are no multiple of the Q8_0 block, so that option is checked on the recipe itself)
+    from ferrl_b200.models.loader import execution_recipe
+    assert execution_recipe(dataclasses.replace(base, quantization=BaseQuantization.Q8_0)) != execution_recipe(base)
+    assert load_auto_policy(d, dataclasses.replace(base, adapter_seed=base.adapter_seed + 1))[1].digest() == want
+    rank0 = load_auto_policy(d, dataclasses.replace(base, tp=(0, 2)))[1].digest()
+    rank1 = load_auto_policy(d, dataclasses.replace(base, tp=(1, 2)))[1].digest()
+    assert rank0 == rank1                      # the rank must not split one logical policy identity
