@@ -291,8 +291,13 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     cands = T.read_candidates(run_dir.candidates_path) if comm.rank == 0 else []
     health = evaluate_run_health(rows, cfg.run_health, cands, group_size=cfg.trainer.group_size,
                                  prompt_groups_per_step=cfg.trainer.grad_accum_steps * cfg.trainer.prompts_per_item)
+    # every rank holds its own metric rows (and rank 0 the candidate rows), so the verdicts may differ: a failure
+    # anywhere stops the held-out evaluation everywhere, or the ranks would part ways in front of its collectives
+    # (the reference aborts all ranks in lockstep on a failed post-run health check, orchestration.rs:2365-2410)
+    health_failed = comm.all_reduce_scalar_sum(1.0 if health.verdict == "fail" else 0.0) > 0 if comm.world_size > 1 \
+        else health.verdict == "fail"
     report = None
-    if eval_samples and stop is RunStop.COMPLETED and health.verdict != "fail":
+    if eval_samples and stop is RunStop.COMPLETED and not health_failed:
         gen = GenConfig(cfg.trainer.group_size, cfg.trainer.max_new_tokens, cfg.trainer.temperature,
                         cfg.trainer.eos_token_id)
         report = evaluate(policy, getattr(reward_fn, "held_out_reward", None) or reward_fn, tokenizer, eval_samples, gen)
