@@ -342,7 +342,8 @@ def cmd_trimul_baseline(args) -> int:
 
 def cmd_verifier_executor(args) -> int:
     from .sandbox import ApptainerSandbox
-    from .verifier_executor import serve_verifier_executor
+    from .verifier_executor import serve_verifier_executor, validate_service_config
+    validate_service_config(args.socket, args.work_root, args.client_uid, args.apptainer, args.socket_mode)
     os.makedirs(args.work_root, exist_ok=True)
     serve_verifier_executor(args.socket, ApptainerSandbox(args.apptainer), client_uid=args.client_uid,
                             socket_mode=args.socket_mode)

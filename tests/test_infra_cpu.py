@@ -1385,3 +1385,30 @@ def test_in_image_script_and_verifier_entry_protocol(tmp_path):
     reward = TrimulReward(NeverEnters(), "img.sif", str(tmp_path), [TrimulCase(32, 1, 16, 16, 1)])
     with pytest.raises(RewardError, match="infrastructure failed"):
         reward.reward(None, "```python\ndef custom_kernel(data):\n    return data\n```")
+
+
+def test_dedicated_verifier_service_refuses_deployments_that_isolate_nothing(tmp_path):
+    """crates/ferrl/src/verifier_executor.rs:750-788 and its unit cases: distinct non-root users, absolute paths,
+    no world access to the socket, a socket parent the client cannot write."""
+    from ferrl_b200.sandbox import SandboxError
+    from ferrl_b200.verifier_executor import validate_service_config
+    parent = tmp_path / "run"
+    parent.mkdir(mode=0o755)
+    ok = dict(socket_path=str(parent / "ve.sock"), work_root=str(tmp_path / "work"), client_uid=1000,
+              apptainer_bin="/usr/bin/apptainer", socket_mode=0o660, service_uid=os.stat(parent).st_uid or 4242)
+    if os.stat(parent).st_uid == 0:            # running as root here: play a service user that owns the directory
+        os.chown(parent, 4242, -1)
+    validate_service_config(**ok)
+    for change, msg in ((dict(client_uid=ok["service_uid"]), "distinct non-root UIDs"), (dict(client_uid=0), "distinct non-root UIDs"),
+                        (dict(service_uid=0), "distinct non-root UIDs"), (dict(socket_path="run/ve.sock"), "absolute"),
+                        (dict(work_root=str(tmp_path / "a" / ".." / "work")), "absolute"),
+                        (dict(apptainer_bin="apptainer"), "absolute path"), (dict(socket_mode=0o666), "no world access")):
+        with pytest.raises(SandboxError, match=msg):
+            validate_service_config(**dict(ok, **change))
+    (parent / "ve.sock").write_text("")
+    with pytest.raises(SandboxError, match="already exists"):
+        validate_service_config(**ok)
+    (parent / "ve.sock").unlink()
+    os.chmod(parent, 0o775)
+    with pytest.raises(SandboxError, match="closed to group/world writes"):
+        validate_service_config(**ok)
