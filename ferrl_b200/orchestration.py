@@ -222,16 +222,23 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
                       tp=(cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size) if cfg.tensor_parallel.enabled else None,
                       ep=(comm.rank, comm.world_size) if ep_on else None,
                       adapter_seed=pc.seed)
-    model, pident = model_and_identity or load_auto_policy(cfg.model_dir, opts)
+    # a rank that cannot load its share of the checkpoint stops all of them together instead of leaving the others
+    # waiting in the first collective (orchestration.rs:1899-2025 coordinates every setup stage)
+    model, pident = model_and_identity or comm.coordinate(lambda: load_auto_policy(cfg.model_dir, opts), "policy load")
     if cfg.tensor_parallel.enabled and cfg.tensor_parallel.sequence_parallel:
         if not hasattr(model, "sequence_parallel"):
             raise OrchestrationError("tensor_parallel.sequence_parallel is not supported by this model family")
         model.sequence_parallel = True
-    if tokenizer is None:
-        from .tokenizer import HfTokenizer
-        tokenizer = HfTokenizer.from_file(cfg.model_dir)
-    if cfg.eos_selection != "disabled" and os.path.exists(os.path.join(cfg.model_dir, "config.json")):
-        cfg.trainer.eos_token_id = resolve_eos(cfg.model_dir, cfg.eos_selection, cfg.trainer.eos_token_id, tokenizer)
+    def tokenizer_and_eos():
+        tok = tokenizer
+        if tok is None:
+            from .tokenizer import HfTokenizer
+            tok = HfTokenizer.from_file(cfg.model_dir)
+        eos = cfg.trainer.eos_token_id
+        if cfg.eos_selection != "disabled" and os.path.exists(os.path.join(cfg.model_dir, "config.json")):
+            eos = resolve_eos(cfg.model_dir, cfg.eos_selection, eos, tok)
+        return tok, eos
+    tokenizer, cfg.trainer.eos_token_id = comm.coordinate(tokenizer_and_eos, "tokenizer load and EOS resolution")
     validate_resolved_eos_consensus(cfg.trainer.eos_token_id, comm)
     policy = LmPolicy(model, GrpoSampler(pc.seed, cfg.trainer.temperature), comm if topology == "tp" else None,
                       pad_token_id=cfg.trainer.eos_token_id or 0,

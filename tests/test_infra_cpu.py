@@ -1412,3 +1412,32 @@ def test_dedicated_verifier_service_refuses_deployments_that_isolate_nothing(tmp
     os.chmod(parent, 0o775)
     with pytest.raises(SandboxError, match="closed to group/world writes"):
         validate_service_config(**ok)
+
+
+def test_a_rank_that_cannot_load_its_policy_stops_every_rank_before_the_first_collective(tmp_path):
+    """Setup stages are coordinated (crates/ferrl/src/orchestration.rs:1899-2025): one rank failing to load raises a
+    coordinated failure everywhere instead of leaving its peers waiting in a collective."""
+    from ferrl_b200.comm import PeerFailure, run_ranks
+    from ferrl_b200.orchestration import run_cli_train_setup
+    from ferrl_b200.tokenizer import SyntheticTokenizer
+    import ferrl_b200.orchestration as orch
+    real, who = orch.load_auto_policy, threading.local()
+
+    def flaky(model_dir, opts):
+        if who.rank == 1:
+            raise OSError("shard 2 of 2 is missing")
+        return real(model_dir, opts)
+
+    def body(comm):
+        who.rank = comm.rank
+        try:
+            run_cli_train_setup(_tp_cfg(tmp_path, comm.rank), comm, allow_dirty=True, tokenizer=SyntheticTokenizer(32, 4, 8))
+        except PeerFailure as e:
+            return "local" if e.local is not None else "peer"
+        return "completed"
+    orch.load_auto_policy = flaky
+    try:
+        out = run_ranks(2, body, timeout=60)
+    finally:
+        orch.load_auto_policy = real
+    assert out == ["peer", "local"]
