@@ -264,12 +264,16 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     comm.require_consensus(json.dumps({k: v for k, v in manifest.to_json().items()
                                        if k not in ("candidate_public_key", "created_unix")}, sort_keys=True).encode(),
                            "launch manifest")
-    run_dir = None
-    if comm.rank == 0:
-        run_dir = T.RunDir.create(cfg.out_dir, run_id)
-        run_dir.write_json_once(T.RunDir.LAUNCH_FILE, dict(manifest.to_json(), launch_sha256=manifest.digest()))
-        run_dir.write_json_once(T.RunDir.CONFIG_FILE, cfg.to_json())
-    comm.barrier() if comm.world_size > 1 else None
+    def publish_run_dir():
+        if comm.rank != 0:
+            return None
+        rd = T.RunDir.create(cfg.out_dir, run_id)
+        rd.write_json_once(T.RunDir.LAUNCH_FILE, dict(manifest.to_json(), launch_sha256=manifest.digest()))
+        rd.write_json_once(T.RunDir.CONFIG_FILE, cfg.to_json())
+        return rd
+    # the status exchange doubles as the barrier behind which the other ranks open the directory; a rank 0 that
+    # cannot publish (duplicate run id, read-only root) stops every rank instead of leaving them at a barrier
+    run_dir = comm.coordinate(publish_run_dir, "run directory publication") if comm.world_size > 1 else publish_run_dir()
     if run_dir is None:
         run_dir = T.RunDir(os.path.join(cfg.out_dir, run_id), run_id)
     binding = CheckpointBinding(pident.digest(), cfg.trainer.digest(), policy.lora_recipe())
