@@ -300,8 +300,10 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     # ---- health, eval, candidates (rank 0 owns publication)
     rows = trainer.history
     cands = T.read_candidates(run_dir.candidates_path) if comm.rank == 0 else []
-    health = evaluate_run_health(rows, cfg.run_health, cands, group_size=cfg.trainer.group_size,
-                                 prompt_groups_per_step=cfg.trainer.grad_accum_steps * cfg.trainer.prompts_per_item)
+    health = comm.coordinate(
+        lambda: evaluate_run_health(rows, cfg.run_health, cands, group_size=cfg.trainer.group_size,
+                                    prompt_groups_per_step=cfg.trainer.grad_accum_steps * cfg.trainer.prompts_per_item),
+        "post-run health")
     # every rank holds its own metric rows (and rank 0 the candidate rows), so the verdicts may differ: a failure
     # anywhere stops the held-out evaluation everywhere, or the ranks would part ways in front of its collectives
     # (the reference aborts all ranks in lockstep on a failed post-run health check, orchestration.rs:2365-2410)
