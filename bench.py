@@ -103,7 +103,7 @@ CONFIGS = {
                          "ffn768 + shared, vocab151936)", lora="r8 attention+shared expert", prompts=16, group=8, max_new=1024,
                    prompt_lo=512, prompt_hi=512, microbatch=4, remat=1, beta=0.0, parallelism="ep", rank_lora=8),
     "hybrid27b-dp": dict(label="Qwen3.6-27B-class dense hybrid (64L, h5120, GDN:GQA 3:1, 24q/4kv d256, ffn17408, vocab151936)",
-                         lora="r32 all-linear", prompts=4, group=16, max_new=4096, prompt_lo=1024, prompt_hi=1024, microbatch=1,
+                         lora="r32 attn:qkvo|mlp:gud|gdn:qzo", prompts=4, group=16, max_new=4096, prompt_lo=1024, prompt_hi=1024, microbatch=1,
                          remat=1, beta=0.04, parallelism="dp", rank_lora=32),
 }
 

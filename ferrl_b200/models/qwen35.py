@@ -49,21 +49,36 @@ class MoeDims:
 class Qwen35LoraTargets:
     attn: str = "qkvo"
     mlp: str = "gud"
-    gdn: str = ""          # opt-in: any of "i" (in_proj qkv|z) and "o" (out_proj)
+    # opt-in GatedDeltaNet projections, the reference's letters (crates/ferrl/src/qwen35.rs:735-887): q = in_proj_qkv,
+    # z = in_proj_z, b = in_proj_b, a = in_proj_a, o = out_proj; "i" is shorthand for "qz"
+    gdn: str = ""
+
+    def gdn_letters(self) -> str:
+        want = set(self.gdn.replace("i", "qz"))
+        return "".join(c for c in "qzbao" if c in want)
 
     def canonical(self) -> str:
-        return f"attn:{self.attn or '-'}|mlp:{self.mlp or '-'}|gdn:{self.gdn or '-'}"
+        return f"attn:{self.attn or '-'}|mlp:{self.mlp or '-'}|gdn:{self.gdn_letters() or '-'}"
+
+    def any(self) -> bool:
+        return bool(self.attn or self.mlp or self.gdn)
+
+    @staticmethod
+    def all_linear() -> "Qwen35LoraTargets":
+        return Qwen35LoraTargets("qkvo", "gud", "qzbao")
 
     @staticmethod
     def parse(s: str) -> "Qwen35LoraTargets":
         if s in ("industrial", "all"):
             return Qwen35LoraTargets()
+        if s == "all_linear":
+            return Qwen35LoraTargets.all_linear()
         if s == "attention_shared":
             return Qwen35LoraTargets("qkvo", "gud", "")
         parts = dict(p.split(":") for p in s.split("|"))
         clean = lambda v: "" if v == "-" else v  # noqa: E731
         t = Qwen35LoraTargets(clean(parts.get("attn", "-")), clean(parts.get("mlp", "-")), clean(parts.get("gdn", "-")))
-        if set(t.attn) - set("qkvo") or set(t.mlp) - set("gud") or set(t.gdn) - set("io"):
+        if set(t.attn) - set("qkvo") or set(t.mlp) - set("gud") or set(t.gdn) - set("qzbaoi"):
             raise ValueError(f"bad LoRA target string {s!r}")
         return t
 
@@ -183,10 +198,10 @@ class Qwen35Layer(nn.Module):
             self.kh, self.vh, self.kd, self.vd = spec.lin_k_heads, spec.lin_v_heads, spec.lin_k_dim, spec.lin_v_dim
             self.key_dim, self.value_dim = self.kh * self.kd, self.vh * self.vd
             self.conv_dim = 2 * self.key_dim + self.value_dim
-            gi, go = "i" in tg.gdn, "o" in tg.gdn
+            g = tg.gdn_letters()
             self.inp = FusedLoraLinear(H, [self.conv_dim, self.value_dim, self.vh, self.vh], ("qkv", "z", "b", "a"),
-                                       (gi, gi, False, False), lora, **kw)
-            self.out = FusedLoraLinear(self.value_dim, [H], ("out",), (go,), lora, **kw)
+                                       ("q" in g, "z" in g, "b" in g, "a" in g), lora, **kw)
+            self.out = FusedLoraLinear(self.value_dim, [H], ("out",), ("o" in g,), lora, **kw)
             reg("conv_w", torch.zeros(self.conv_dim, spec.conv_kernel, dtype=dtype, device=device))
             reg("A_log", torch.zeros(self.vh, dtype=torch.float32, device=device))
             reg("dt_bias", torch.ones(self.vh, dtype=torch.float32, device=device))
@@ -361,6 +376,9 @@ class Qwen35GradModel(nn.Module):
             if full_ft:
                 raise ValueError("expert parallelism keeps the routed experts frozen: not available with full fine-tuning")
         self.targets = targets or Qwen35LoraTargets()
+        if lora is not None and not full_ft and not self.targets.any():
+            # the reference refuses a load whose recipe selects nothing (crates/ferrl/src/qwen35.rs:3546-3560)
+            raise ValueError("the LoRA target recipe selects no projection: the model would train nothing")
         dev = torch.device(device) if device is not None else torch.device("cpu")
         if keep_transpose is None:
             keep_transpose = dev.type == "cuda" and not full_ft

@@ -372,3 +372,23 @@ def test_policy_identity_binds_the_execution_recipe_but_no_rank_or_stream_positi
     rank0 = load_auto_policy(d, dataclasses.replace(base, tp=(0, 2)))[1].digest()
     rank1 = load_auto_policy(d, dataclasses.replace(base, tp=(1, 2)))[1].digest()
     assert rank0 == rank1                      # the rank must not split one logical policy identity
+
+
+def test_hybrid_lora_target_recipes_follow_the_reference_spellings():
+    """crates/ferrl/src/qwen35.rs:3524-3600: canonical recipe strings (they are written into checkpoint manifests),
+    the five GatedDeltaNet projections of the all-linear recipe, and the refusal of a recipe that selects nothing."""
+    from ferrl_b200.models.lora import LoraSpec
+    from ferrl_b200.models.qwen35 import Qwen35GradModel, Qwen35LoraTargets as T
+    assert T().canonical() == "attn:qkvo|mlp:gud|gdn:-"
+    assert T.all_linear().canonical() == "attn:qkvo|mlp:gud|gdn:qzbao" == T.parse("all_linear").canonical()
+    assert T("", "", "").canonical() == "attn:-|mlp:-|gdn:-" and not T("", "", "").any()
+    assert T.parse("attn:qv|mlp:-|gdn:zo").canonical() == "attn:qv|mlp:-|gdn:zo"
+    assert T("qkvo", "gud", "io").canonical() == "attn:qkvo|mlp:gud|gdn:qzo"          # "i" abbreviates q and z
+    with pytest.raises(ValueError):
+        T.parse("attn:qx|mlp:-|gdn:-")
+    base = _load("tiny_qwen35")
+    linear_layers = sum(1 for l in base.layers if l.kind != "full_attention")
+    wide = Qwen35GradModel(base.spec, LoraSpec(2, 4.0), T.all_linear())
+    assert len(wide.trainable_params()) == len(base.trainable_params()) + 2 * 5 * linear_layers
+    with pytest.raises(ValueError, match="would train nothing"):
+        Qwen35GradModel(base.spec, LoraSpec(2, 4.0), T("", "", ""))
