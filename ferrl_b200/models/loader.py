@@ -37,6 +37,7 @@ class LoaderOpts:
     full_ft: bool = False
     adapter_seed: int = 0
     max_position_embeddings: Optional[int] = None
+    gdn_targets: str = ""     # hybrid families: adapted GatedDeltaNet projections, letters of q z b a o (see qwen35.py)
 
 
 @dataclass(frozen=True)
@@ -64,7 +65,8 @@ def execution_recipe(opts: "LoaderOpts") -> str:
     return json.dumps({
         "lora_rank": lora.rank if lora else 0,
         "lora_alpha_bits": struct.unpack("<Q", struct.pack("<d", float(lora.alpha)))[0] if lora else 0,
-        "lora_targets": lora.targets.canonical() if lora and getattr(lora, "targets", None) is not None else "",
+        "lora_targets": (lora.targets.canonical() + ("|gdn:" + opts.gdn_targets if opts.gdn_targets else ""))
+        if lora and getattr(lora, "targets", None) is not None else "",
         "base_dtype": str(opts.dtype).replace("torch.", ""),
         "adapter_dtype": "float32",
         "base_quantization": BaseQuantization(opts.quantization).value,

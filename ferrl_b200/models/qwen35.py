@@ -650,7 +650,11 @@ def load_qwen35(model_dir: str, opts):
         spec.max_position_embeddings = opts.max_position_embeddings
     if opts.tp is not None:
         raise ValueError("tensor parallelism is not supported for the Qwen3.5 family")
-    model = Qwen35GradModel(spec, None if opts.full_ft else opts.lora, dtype=opts.dtype, device=opts.device,
+    targets = None
+    if opts.lora is not None and not opts.full_ft:
+        # the dense recipe names the attention and MLP projections; the GatedDeltaNet letters come beside it
+        targets = Qwen35LoraTargets.parse(opts.lora.targets.canonical() + "|gdn:" + (opts.gdn_targets or "-"))
+    model = Qwen35GradModel(spec, None if opts.full_ft else opts.lora, targets, dtype=opts.dtype, device=opts.device,
                             quant=opts.quantization, remat=opts.remat, full_ft=opts.full_ft, ep=opts.ep)
     src = TensorSource(model_dir)
     load_qwen35_weights(model, src)

@@ -215,13 +215,20 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
     train_samples, eval_samples, reward_fn = comm.coordinate(lambda: build_task(cfg), f"{cfg.task} task setup")
     # ---- policy
     pc = cfg.policy
-    lora = LoraSpec(pc.lora_rank, pc.lora_alpha, DenseLoraTargets.parse(pc.lora_targets))
+    # "all_linear" and a trailing "|gdn:<letters>" also select GatedDeltaNet projections of the hybrid families
+    dense_targets, gdn_targets = pc.lora_targets, ""
+    if dense_targets == "all_linear":
+        dense_targets, gdn_targets = "industrial", "qzbao"
+    elif "|gdn:" in dense_targets:
+        dense_targets, gdn_targets = dense_targets.rsplit("|gdn:", 1)
+        gdn_targets = "" if gdn_targets == "-" else gdn_targets
+    lora = LoraSpec(pc.lora_rank, pc.lora_alpha, DenseLoraTargets.parse(dense_targets))
     ep_on = cfg.expert_parallel.enabled and comm.world_size > 1
     opts = LoaderOpts(dtype=_DTYPES[pc.base_dtype], device=device, lora=lora,
                       quantization=BaseQuantization(pc.base_quantization), remat=pc.activation_checkpointing,
                       tp=(cfg.tensor_parallel.rank, cfg.tensor_parallel.world_size) if cfg.tensor_parallel.enabled else None,
                       ep=(comm.rank, comm.world_size) if ep_on else None,
-                      adapter_seed=pc.seed)
+                      adapter_seed=pc.seed, gdn_targets=gdn_targets)
     # a rank that cannot load its share of the checkpoint stops all of them together instead of leaving the others
     # waiting in the first collective (orchestration.rs:1899-2025 coordinates every setup stage)
     model, pident = model_and_identity or comm.coordinate(lambda: load_auto_policy(cfg.model_dir, opts), "policy load")

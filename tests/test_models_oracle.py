@@ -392,3 +392,17 @@ def test_hybrid_lora_target_recipes_follow_the_reference_spellings():
     assert len(wide.trainable_params()) == len(base.trainable_params()) + 2 * 5 * linear_layers
     with pytest.raises(ValueError, match="would train nothing"):
         Qwen35GradModel(base.spec, LoraSpec(2, 4.0), T("", "", ""))
+
+
+def test_configured_lora_targets_reach_the_hybrid_family():
+    """``policy.lora_targets`` names the dense recipe and, for the hybrid families, the GatedDeltaNet projections;
+    the loader builds exactly those adapters and binds the recipe into the policy identity."""
+    from ferrl_b200.models.lora import DenseLoraTargets, LoraSpec
+    d = os.path.join(FIX, "tiny_qwen35")
+    default, wide = load_auto_policy(d, LoaderOpts()), load_auto_policy(d, LoaderOpts(gdn_targets="qzbao"))
+    narrow = load_auto_policy(d, LoaderOpts(lora=LoraSpec(4, 8.0, DenseLoraTargets.legacy())))
+    assert default[0].targets.canonical() == "attn:qkvo|mlp:gud|gdn:-"
+    assert wide[0].targets.canonical() == "attn:qkvo|mlp:gud|gdn:qzbao" and narrow[0].targets.canonical() == "attn:qv|mlp:-|gdn:-"
+    assert len(narrow[0].trainable_params()) < len(default[0].trainable_params()) < len(wide[0].trainable_params())
+    assert len({default[1].digest(), wide[1].digest(), narrow[1].digest()}) == 3
+    assert "gdn:qzbao" in wide[0].lora_recipe()
