@@ -84,6 +84,10 @@ class Gemma4Spec:
 
 def gemma4_spec(cfg: Mapping[str, Any]) -> Gemma4Spec:
     t = cfg.get("text_config", cfg)
+    if t.get("model_type") is not None and t["model_type"] not in ("gemma4_text", "gemma4_unified_text"):
+        # the multimodal wrappers carry audio / vision towers under other text model types (gemma4.rs:519-532)
+        raise ValueError(f"gemma4 config: text_config.model_type {t['model_type']!r}, expected \"gemma4_text\" or "
+                         "\"gemma4_unified_text\"")
     for key, why in (("hidden_size_per_layer_input", "per-layer inputs"), ("num_kv_shared_layers", "kv-shared layers")):
         if int(t.get(key, 0) or 0) != 0:
             raise ValueError(f"Gemma 4 checkpoints with {why} are not supported (dense text decoder only)")

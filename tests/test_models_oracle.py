@@ -406,3 +406,22 @@ def test_configured_lora_targets_reach_the_hybrid_family():
     assert len(narrow[0].trainable_params()) < len(default[0].trainable_params()) < len(wide[0].trainable_params())
     assert len({default[1].digest(), wide[1].digest(), narrow[1].digest()}) == 3
     assert "gdn:qzbao" in wide[0].lora_recipe()
+
+
+def test_gemma4_config_rejections_follow_the_reference():
+    """crates/ferrl/src/gemma4.rs:5752-5810: other text model types, MoE fields and per-layer embeddings are refused
+    before any weight is read; an unknown top-level model type never reaches a family loader."""
+    import copy
+
+    from ferrl_b200.models.gemma4 import gemma4_spec
+    cfg = json.load(open(os.path.join(FIX, "tiny_gemma4", "config.json")))
+    gemma4_spec(cfg)
+    for change, msg in ((dict(model_type="gemma4_unified_audio"), "model_type"), (dict(enable_moe_block=True, num_experts=128), "MoE"),
+                        (dict(hidden_size_per_layer_input=128), "per-layer")):
+        bad = copy.deepcopy(cfg)
+        bad["text_config"].update(change)
+        with pytest.raises(ValueError, match=msg):
+            gemma4_spec(bad)
+    unified = copy.deepcopy(cfg)
+    unified["text_config"]["model_type"] = "gemma4_unified_text"
+    gemma4_spec(unified)
