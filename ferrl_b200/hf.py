@@ -44,6 +44,15 @@ def _token_id(raw) -> Optional[int]:
     return raw if 0 <= raw < 2 ** 32 else None
 
 
+def model_vocab_size(cfg: dict) -> int:
+    """The model's vocabulary bound (nested ``text_config`` first): a positive integer, or the checkpoint is refused
+    (crates/ferrl/src/hf.rs ``vocab_size_from_json``)."""
+    raw = _preferred(cfg, "vocab_size")
+    if isinstance(raw, bool) or not isinstance(raw, int) or raw <= 0:
+        raise HfError(f"config vocab_size {raw!r} must be a positive integer")
+    return raw
+
+
 def checkpoint_eos(model_dir: str) -> Union[None, int, list]:
     """``None`` (missing), one id, or the declared list."""
     raw = _preferred(_read_config(model_dir), "eos_token_id")
@@ -80,8 +89,8 @@ def resolve_eos(model_dir: str, selection: str, explicit: Optional[int], tokeniz
         chosen = explicit
     else:
         raise HfError(f"unknown EOS selection {selection!r}")
-    vocab = _preferred(_read_config(model_dir), "vocab_size")
-    if isinstance(vocab, int) and chosen >= vocab:
+    vocab = model_vocab_size(_read_config(model_dir))
+    if chosen >= vocab:
         raise HfError(f"EOS id {chosen} is outside model vocab_size {vocab}")
     if tokenizer is not None and not tokenizer.contains_id(chosen):
         raise HfError(f"EOS id {chosen} is not present in the loaded tokenizer vocabulary")

@@ -391,24 +391,40 @@ def test_countdown_math_and_data(tmp_path):
     assert {x.target for x in tr}.isdisjoint({x.target for x in ev}) and len(ev) >= 3
 
 
-def test_hf_eos_resolution_and_tokenizer():
-    from ferrl_b200.hf import HfError, chatml, checkpoint_eos, resolve_eos
+def test_hf_eos_resolution_and_tokenizer(tmp_path):
+    from ferrl_b200.hf import HfError, chatml, checkpoint_eos, model_vocab_size, resolve_eos
     from ferrl_b200.tokenizer import ByteTokenizer, HfTokenizer
 
     class Tok:
         def contains_id(self, i):
             return i < 200000
+    # the committed fixtures declare no vocabulary size, which resolution needs (hf.rs: vocab_size_from_json)
+    assert model_vocab_size({"vocab_size": 8, "text_config": {"vocab_size": 16}}) == 16
+    for bad in ({}, {"vocab_size": 0}, {"vocab_size": "16"}):
+        with pytest.raises(HfError):
+            model_vocab_size(bad)
+    with pytest.raises(HfError, match="vocab_size"):
+        resolve_eos(os.path.join(FIX, "eos_config"), "checkpoint", None, Tok())
+
+    def with_vocab(name):
+        d = tmp_path / name
+        d.mkdir()
+        cfg = json.load(open(os.path.join(FIX, name, "config.json")))
+        cfg["vocab_size"] = 200000
+        (d / "config.json").write_text(json.dumps(cfg))
+        return str(d)
+    single, multi = with_vocab("eos_config"), with_vocab("eos_config_multi")
     assert checkpoint_eos(os.path.join(FIX, "eos_config")) == 151645
     assert checkpoint_eos(os.path.join(FIX, "eos_config_multi")) == [3, 4]
     with pytest.raises(HfError):
         checkpoint_eos(os.path.join(FIX, "eos_config_malformed"))
-    assert resolve_eos(os.path.join(FIX, "eos_config"), "checkpoint", None, Tok()) == 151645
-    assert resolve_eos(os.path.join(FIX, "eos_config"), "disabled", None, Tok()) is None
+    assert resolve_eos(single, "checkpoint", None, Tok()) == 151645
+    assert resolve_eos(single, "disabled", None, Tok()) is None
     with pytest.raises(HfError):
-        resolve_eos(os.path.join(FIX, "eos_config_multi"), "checkpoint", None, Tok())
-    assert resolve_eos(os.path.join(FIX, "eos_config_multi"), "explicit", 4, Tok()) == 4
+        resolve_eos(multi, "checkpoint", None, Tok())
+    assert resolve_eos(multi, "explicit", 4, Tok()) == 4
     with pytest.raises(HfError):
-        resolve_eos(os.path.join(FIX, "eos_config_multi"), "explicit", 9, Tok())
+        resolve_eos(multi, "explicit", 9, Tok())
     assert chatml("sys", "hi") == "<|im_start|>system\nsys<|im_end|>\n<|im_start|>user\nhi<|im_end|>\n<|im_start|>assistant\n"
     bt = ByteTokenizer()
     assert bt.decode(bt.encode("héllo")) == "héllo"
