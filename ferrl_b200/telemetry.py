@@ -186,10 +186,17 @@ class RunDir:
         return RunDir(root, run_id)
 
     @staticmethod
-    def open(root: str) -> "RunDir":
+    def open(root: str, run_id: Optional[str] = None) -> "RunDir":
+        """Continue an existing run: ``open(run_root)`` or, as the reference spells it, ``open(out_dir, run_id)``.
+        A missing directory is an error (a mistyped run id must not start an empty "resume"); the eager layout
+        (the checkpoints directory) is materialised as ``create`` does (telemetry.rs:2927-2936, :3245-3264)."""
+        if run_id is not None:
+            root = os.path.join(root, run_id)
         if not os.path.isdir(root):
             raise FileNotFoundError(f"run directory {root} does not exist")
-        return RunDir(root, os.path.basename(os.path.normpath(root)))
+        rd = RunDir(root, os.path.basename(os.path.normpath(root)))
+        os.makedirs(rd.checkpoints_dir, exist_ok=True)
+        return rd
 
     def path(self, name: str) -> str:
         return os.path.join(self.root, name)

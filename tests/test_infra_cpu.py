@@ -1457,3 +1457,26 @@ def test_a_rank_that_cannot_load_its_policy_stops_every_rank_before_the_first_co
     finally:
         orch.load_auto_policy = real
     assert out == ["peer", "local"]
+
+
+def test_run_directory_layout_and_reuse_rules_follow_the_reference(tmp_path):
+    """crates/ferrl/src/telemetry.rs:2883-3030, 3245-3264: a fresh run directory holds exactly the checkpoints
+    directory (no per-run log file), a run id is never reused, also not after a crash that left only candidate rows,
+    and a run is continued only from a directory that exists."""
+    rd = T.RunDir.create(str(tmp_path), "run-001")
+    assert os.listdir(rd.root) == ["checkpoints"] and rd.run_id == "run-001" and not os.path.exists(rd.path("run.log"))
+    T.CandidateWriter(rd.candidates_path, None).append(T.CandidateRecord(0, 0, 1, 0, 0, 1.0, 2, "candidate"))
+    assert not os.path.exists(rd.metrics_path)                         # the crash-before-metrics window
+    with pytest.raises(FileExistsError):
+        T.RunDir.create(str(tmp_path), "run-001")
+    w = T.MetricsWriter(rd.metrics_path)
+    w.append(T.Metrics(step=0))
+    again = T.RunDir.open(str(tmp_path), "run-001")
+    assert again.root == rd.root
+    T.MetricsWriter(again.metrics_path).append(T.Metrics(step=1))
+    assert len(open(again.metrics_path).read().splitlines()) == 2       # open() continues the stream
+    with pytest.raises(FileNotFoundError):
+        T.RunDir.open(str(tmp_path), "run-nope")
+    bare = tmp_path / "run-002"
+    bare.mkdir()
+    assert os.listdir(T.RunDir.open(str(bare)).root) == ["checkpoints"]
