@@ -306,15 +306,25 @@ def verify_candidate(rec: CandidateRecord, public_key_hex: str, launch_sha256: s
 
 
 class CandidateWriter:
+    """Appends candidate rows.  With a signer every row is bound to the launch; such a writer refuses a ledger that
+    already holds rows, because the process-local key that signed them is gone and mixed provenance could not be
+    told apart (telemetry.rs:1229-1250).  A non-finite reward is refused before anything is written
+    (telemetry.rs:3152-3185): the ledger is strict JSON."""
+
     def __init__(self, path: str, signer: Optional[CandidateSigner] = None):
         self.path = path
         self.signer = signer
+        if signer is not None and os.path.exists(path) and os.path.getsize(path) != 0:
+            raise ValueError(f"refuse to bind launch-authenticated candidate appends to non-empty ledger {path}; "
+                             "the original process-local signing capability is unavailable")
 
     def append(self, rec: CandidateRecord) -> None:
+        if not math.isfinite(float(rec.reward)):
+            raise ValueError(f"candidate reward {rec.reward!r} is not finite")
         if self.signer is not None:
             rec = self.signer.sign(rec)
         d = {k: v for k, v in dataclasses.asdict(rec).items() if v is not None}
-        _append_line(self.path, json.dumps(d, sort_keys=True))
+        _append_line(self.path, json.dumps(d, sort_keys=True, allow_nan=False))
 
     def mark(self) -> int:
         """Current end of the ledger: what ``rollback`` cuts back to."""

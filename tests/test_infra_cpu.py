@@ -1480,3 +1480,18 @@ def test_run_directory_layout_and_reuse_rules_follow_the_reference(tmp_path):
     bare = tmp_path / "run-002"
     bare.mkdir()
     assert os.listdir(T.RunDir.open(str(bare)).root) == ["checkpoints"]
+
+
+def test_candidate_ledger_refuses_nonfinite_rewards_and_a_second_signing_process(tmp_path):
+    """crates/ferrl/src/telemetry.rs:3115-3185: nothing is written for a non-finite reward, and a launch-bound writer
+    never appends to rows an earlier process signed with a key that no longer exists."""
+    rd = T.RunDir.create(str(tmp_path), "run")
+    plain = T.CandidateWriter(rd.candidates_path, None)
+    for reward in (float("nan"), float("-inf"), float("inf")):
+        with pytest.raises(ValueError, match="not finite"):
+            plain.append(T.CandidateRecord(0, 0, 1, 0, 0, reward, 1, "candidate"))
+    assert not os.path.exists(rd.candidates_path) or open(rd.candidates_path).read() == ""
+    plain.append(T.CandidateRecord(0, 0, 1, 0, 0, 1.0, 1, "existing"))
+    with pytest.raises(ValueError, match="non-empty ledger .* signing capability is unavailable"):
+        T.CandidateWriter(rd.candidates_path, T.CandidateSigner("ab" * 32))
+    assert len(open(rd.candidates_path).read().splitlines()) == 1
