@@ -322,8 +322,9 @@ def run_cli_train_setup(cfg: RunConfig, comm: Optional[Comm] = None, *, allow_di
                         cfg.trainer.eos_token_id)
         report = evaluate(policy, getattr(reward_fn, "held_out_reward", None) or reward_fn, tokenizer, eval_samples, gen)
         if comm.rank == 0:
-            with open(run_dir.path(T.RunDir.EVAL_REPORT_FILE), "w") as f:
-                json.dump(report.to_json(), f, indent=2, sort_keys=True)
+            # published once, through a temporary file and a rename; an existing report is never replaced
+            # (telemetry.rs: eval_report_publication_is_immutable)
+            run_dir.write_json_once(T.RunDir.EVAL_REPORT_FILE, report.to_json())
     ranked = load_and_rank_candidates(run_dir.root, steps=cfg.trainer.steps, group_size=cfg.trainer.group_size,
                                       max_new_tokens=cfg.trainer.max_new_tokens, rank=0,
                                       world_size=comm.world_size) if comm.rank == 0 else []
