@@ -1495,3 +1495,35 @@ def test_candidate_ledger_refuses_nonfinite_rewards_and_a_second_signing_process
     with pytest.raises(ValueError, match="non-empty ledger .* signing capability is unavailable"):
         T.CandidateWriter(rd.candidates_path, T.CandidateSigner("ab" * 32))
     assert len(open(rd.candidates_path).read().splitlines()) == 1
+
+
+def test_countdown_generator_is_solvable_by_an_independent_solver():
+    """crates/ferrl/src/countdown.rs:838-942: every generated problem is reachable by combining all numbers with
+    + - * / over exact rationals (checked without the generator's own fold), also with large products, and the
+    degenerate one-number configuration yields the number itself."""
+    from fractions import Fraction
+
+    from ferrl_b200.rewards.countdown import CountdownConfig, generate_dataset
+
+    def reachable(nums):
+        if len(nums) == 1:
+            return {nums[0]}
+        out = set()
+        for i in range(len(nums)):
+            for j in range(len(nums)):
+                if i == j:
+                    continue
+                a, b = nums[i], nums[j]
+                rest = [nums[k] for k in range(len(nums)) if k not in (i, j)]
+                for c in [a + b, a - b, a * b] + ([a / b] if b != 0 else []):
+                    out |= reachable(rest + [c])
+        return out
+
+    def solvable(p):
+        return Fraction(p.target) in reachable([Fraction(n) for n in p.numbers])
+    data = generate_dataset(7, 40, CountdownConfig(4, 1, 12, 200))
+    assert len(data) == 40
+    assert all(len(p.numbers) == 4 and all(1 <= n <= 12 for n in p.numbers) and p.target > 0 and solvable(p) for p in data)
+    assert all(p.target > 0 and solvable(p) for p in generate_dataset(99, 30, CountdownConfig(4, 10, 80, 100_000)))
+    assert [(p.numbers, p.target) for p in generate_dataset(1, 3, CountdownConfig(1, 5, 5, 1000))] == [((5,), 5)] * 3
+    assert generate_dataset(42, 8) == generate_dataset(42, 8) != generate_dataset(43, 8)
