@@ -109,6 +109,7 @@ class Metrics:
     cuda_mem_peak_used_bytes: int = 0
     cuda_mem_end_used_bytes: int = 0
     cuda_mem_total_bytes: int = 0
+    cuda_mem_peak_delta_bytes: int = 0      # peak increase over the step's first probe; 0 = unmeasured or no increase
     cuda_mem_probe_events: list = field(default_factory=list)
     decoder_cache_bytes: int = 0
     phase_ms: dict = field(default_factory=dict)

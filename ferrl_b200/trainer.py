@@ -796,6 +796,7 @@ class Trainer:
         if self._probe.enabled:
             m.cuda_mem_start_used_bytes, m.cuda_mem_peak_used_bytes = self._probe.start, self._probe.peak
             m.cuda_mem_end_used_bytes, m.cuda_mem_total_bytes = self._probe.end, self._probe.total
+            m.cuda_mem_peak_delta_bytes = max(0, int(self._probe.peak) - int(self._probe.start))
             m.cuda_mem_probe_events = self._probe.events
         m.decoder_cache_bytes = int(getattr(self.policy, "last_cache_bytes", 0))
         self.history.append(m)
